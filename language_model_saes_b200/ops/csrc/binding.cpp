@@ -1,0 +1,356 @@
+// Python bindings (torch extension) for the sm_100a kernels. Tensors are checked for device, dtype and
+// contiguity here; the kernels assume what these checks guarantee.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <torch/extension.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "kernels.h"
+
+namespace {
+
+using torch::Tensor;
+
+void check_cuda(int code, const char* what) {
+  TORCH_CHECK(code == 0, what, " failed: ", cudaGetErrorString(static_cast<cudaError_t>(code)));
+}
+
+#define CHECK_T(t, dt)                                                       \
+  TORCH_CHECK((t).is_cuda(), #t " must be a CUDA tensor");                   \
+  TORCH_CHECK((t).scalar_type() == (dt), #t " has the wrong dtype");         \
+  TORCH_CHECK((t).is_contiguous(), #t " must be contiguous")
+
+template <typename T>
+T* opt_ptr(const c10::optional<Tensor>& t) {
+  return t.has_value() ? reinterpret_cast<T*>(t->data_ptr()) : nullptr;
+}
+
+// ---- tensor maps -----------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
+    TORCH_CHECK(e == cudaSuccess && p != nullptr, "cuTensorMapEncodeTiled is not available from this driver");
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// 2-D bf16 row-major [rows, cols] tensor, box = {64 columns, box_rows}, 128-byte swizzle.
+CUtensorMap make_bf16_tile_map(const void* base, int64_t rows, int64_t cols, int box_rows) {
+  TORCH_CHECK(reinterpret_cast<uintptr_t>(base) % 16 == 0, "TMA base address must be 16-byte aligned");
+  TORCH_CHECK((cols * 2) % 16 == 0, "TMA row pitch must be a multiple of 16 bytes (K % 8 == 0)");
+  CUtensorMap m;
+  cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t gstride[1] = {(cuuint64_t)cols * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t estride[2] = {1, 1};
+  CUresult r = get_encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstride, box,
+                               estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code ", (int)r);
+  return m;
+}
+
+// ---- encoder GEMM ----------------------------------------------------------------------------------
+// mode bit 0: write H (bf16 [M, N]); bit 1: fused per-row top-k candidates.
+// Returns the number of candidate slots per range (KS) so that callers can size / interpret the buffers.
+int64_t encoder_gemm(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& bias,
+                     const c10::optional<Tensor>& gate, int64_t mode, int64_t k, int64_t num_splits,
+                     const c10::optional<Tensor>& H, const c10::optional<Tensor>& cand_val,
+                     const c10::optional<Tensor>& cand_idx, const Tensor& status) {
+  CHECK_T(x, torch::kBFloat16);
+  CHECK_T(w, torch::kBFloat16);
+  CHECK_T(status, torch::kInt32);
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && x.size(1) == w.size(1), "x [M,K] and w [N,K] must share K");
+  const c10::cuda::CUDAGuard guard(x.device());
+  lmsae::EncGemmParams p{};
+  p.M = (int)x.size(0);
+  p.K = (int)x.size(1);
+  p.N = (int)w.size(0);
+  TORCH_CHECK(p.K % 8 == 0 && p.N % 8 == 0, "K and N must be multiples of 8");
+  p.num_panels = (p.M + 127) / 128;
+  p.num_splits = (int)num_splits;
+  const int n_tiles = (p.N + 255) / 256;
+  TORCH_CHECK(p.num_splits >= 1 && p.num_splits <= n_tiles, "num_splits must be in [1, number of N tiles]");
+  if (bias.has_value()) { CHECK_T(*bias, torch::kFloat32); TORCH_CHECK(bias->numel() == p.N); }
+  if (gate.has_value()) { CHECK_T(*gate, torch::kFloat32); TORCH_CHECK(gate->numel() == p.N); }
+  p.bias = opt_ptr<const float>(bias);
+  p.gate = opt_ptr<const float>(gate);
+  p.status = status.data_ptr<int>();
+  p.k = (int)k;
+  int ks = 0;
+  if (mode & 1) {
+    TORCH_CHECK(H.has_value(), "mode bit 0 needs H");
+    CHECK_T(*H, torch::kBFloat16);
+    TORCH_CHECK(H->size(0) == p.M && H->size(1) == p.N);
+    p.H = reinterpret_cast<__nv_bfloat16*>(H->data_ptr());
+    p.ldh = p.N;
+  }
+  if (mode & 2) {
+    TORCH_CHECK(k >= 1 && k <= 64, "fused top-k supports 1 <= k <= 64");
+    ks = lmsae::enc_gemm_slots_for_k((int)k);
+    TORCH_CHECK(cand_val.has_value() && cand_idx.has_value());
+    CHECK_T(*cand_val, torch::kFloat32);
+    CHECK_T(*cand_idx, torch::kInt32);
+    TORCH_CHECK(cand_val->numel() >= (int64_t)p.M * p.num_splits * ks && cand_idx->numel() >= (int64_t)p.M * p.num_splits * ks,
+                "candidate buffers too small");
+    p.cand_val = cand_val->data_ptr<float>();
+    p.cand_idx = cand_idx->data_ptr<int>();
+  }
+  TORCH_CHECK(mode & 3, "mode must request H and/or top-k");
+  const CUtensorMap ta = make_bf16_tile_map(x.data_ptr(), p.M, p.K, 128);
+  const CUtensorMap tb = make_bf16_tile_map(w.data_ptr(), p.N, p.K, 256);
+  check_cuda(lmsae::enc_gemm_launch(ta, tb, p, (int)mode, at::cuda::getCurrentCUDAStream()), "encoder_gemm launch");
+  return ks;
+}
+
+void topk_merge(const Tensor& cand_val, const Tensor& cand_idx, int64_t M, int64_t C, int64_t k,
+                const c10::optional<Tensor>& gate, int64_t own_lo, int64_t own_hi, bool emit_gated,
+                const Tensor& out_idx, const Tensor& out_val) {
+  CHECK_T(cand_val, torch::kFloat32);
+  CHECK_T(cand_idx, torch::kInt32);
+  CHECK_T(out_idx, torch::kInt32);
+  CHECK_T(out_val, torch::kFloat32);
+  TORCH_CHECK(cand_val.numel() >= M * C && cand_idx.numel() >= M * C && out_idx.numel() >= M * k && out_val.numel() >= M * k);
+  TORCH_CHECK(0 <= own_lo && own_lo <= own_hi && own_hi <= C);
+  const c10::cuda::CUDAGuard guard(cand_val.device());
+  check_cuda(lmsae::topk_merge_launch(cand_val.data_ptr<float>(), cand_idx.data_ptr<int>(), (int)M, (int)C, (int)k,
+                                      opt_ptr<const float>(gate), (int)own_lo, (int)own_hi, emit_gated ? 1 : 0,
+                                      out_idx.data_ptr<int>(), out_val.data_ptr<float>(),
+                                      at::cuda::getCurrentCUDAStream()),
+             "topk_merge launch");
+}
+
+void row_topk(const Tensor& H, int64_t k, const c10::optional<Tensor>& gate, const c10::optional<Tensor>& alive,
+              const Tensor& out_idx, const Tensor& out_val) {
+  CHECK_T(H, torch::kBFloat16);
+  CHECK_T(out_idx, torch::kInt32);
+  CHECK_T(out_val, torch::kFloat32);
+  TORCH_CHECK(H.dim() == 2 && out_idx.numel() >= H.size(0) * k && out_val.numel() >= H.size(0) * k);
+  if (alive.has_value()) { CHECK_T(*alive, torch::kUInt8); TORCH_CHECK(alive->numel() == H.size(1)); }
+  if (gate.has_value()) { CHECK_T(*gate, torch::kFloat32); TORCH_CHECK(gate->numel() == H.size(1)); }
+  const c10::cuda::CUDAGuard guard(H.device());
+  check_cuda(lmsae::row_topk_launch(reinterpret_cast<const __nv_bfloat16*>(H.data_ptr()), H.size(1), (int)H.size(0),
+                                    (int)H.size(1), (int)k, opt_ptr<const float>(gate), opt_ptr<const uint8_t>(alive),
+                                    out_idx.data_ptr<int>(), out_val.data_ptr<float>(),
+                                    at::cuda::getCurrentCUDAStream()),
+             "row_topk launch");
+}
+
+// x_hat = decode(idx, val); optional outputs and fused loss as described in sparse_ops.cu.
+void sparse_decode(const Tensor& idx, const Tensor& val, const Tensor& W, const c10::optional<Tensor>& bias,
+                   const c10::optional<Tensor>& xhat_f32, const c10::optional<Tensor>& xhat_bf16,
+                   const c10::optional<Tensor>& label, const c10::optional<Tensor>& row_weight, double grad_scale,
+                   const c10::optional<Tensor>& dxhat, const c10::optional<Tensor>& loss_sum,
+                   const c10::optional<Tensor>& row_loss, const c10::optional<Tensor>& dval) {
+  CHECK_T(idx, torch::kInt32);
+  CHECK_T(val, torch::kFloat32);
+  CHECK_T(W, torch::kBFloat16);
+  TORCH_CHECK(idx.dim() == 2 && val.sizes() == idx.sizes() && W.dim() == 2);
+  const c10::cuda::CUDAGuard guard(idx.device());
+  lmsae::DecodeParams p{};
+  p.idx = idx.data_ptr<int>();
+  p.val = val.data_ptr<float>();
+  p.B = (int)idx.size(0);
+  p.k = (int)idx.size(1);
+  p.d = (int)W.size(1);
+  p.W = reinterpret_cast<const __nv_bfloat16*>(W.data_ptr());
+  if (bias.has_value()) { CHECK_T(*bias, torch::kFloat32); TORCH_CHECK(bias->numel() == p.d); }
+  p.bias = opt_ptr<const float>(bias);
+  if (xhat_f32.has_value()) { CHECK_T(*xhat_f32, torch::kFloat32); TORCH_CHECK(xhat_f32->numel() == (int64_t)p.B * p.d); }
+  if (xhat_bf16.has_value()) { CHECK_T(*xhat_bf16, torch::kBFloat16); TORCH_CHECK(xhat_bf16->numel() == (int64_t)p.B * p.d); }
+  p.xhat_f32 = opt_ptr<float>(xhat_f32);
+  p.xhat_bf16 = opt_ptr<__nv_bfloat16>(xhat_bf16);
+  if (label.has_value()) {
+    CHECK_T(*label, torch::kBFloat16);
+    TORCH_CHECK(label->numel() == (int64_t)p.B * p.d);
+    TORCH_CHECK(dxhat.has_value() && loss_sum.has_value(), "fused loss needs dxhat and loss_sum");
+    CHECK_T(*dxhat, torch::kBFloat16);
+    CHECK_T(*loss_sum, torch::kFloat32);
+    TORCH_CHECK(dxhat->numel() == (int64_t)p.B * p.d);
+    if (row_weight.has_value()) { CHECK_T(*row_weight, torch::kFloat32); TORCH_CHECK(row_weight->numel() == p.B); }
+    if (row_loss.has_value()) { CHECK_T(*row_loss, torch::kFloat32); TORCH_CHECK(row_loss->numel() == p.B); }
+    if (dval.has_value()) { CHECK_T(*dval, torch::kFloat32); TORCH_CHECK(dval->numel() == (int64_t)p.B * p.k); }
+    p.label = reinterpret_cast<const __nv_bfloat16*>(label->data_ptr());
+    p.row_weight = opt_ptr<const float>(row_weight);
+    p.grad_scale = (float)grad_scale;
+    p.dxhat = opt_ptr<__nv_bfloat16>(dxhat);
+    p.loss_sum = opt_ptr<float>(loss_sum);
+    p.row_loss = opt_ptr<float>(row_loss);
+    p.dval = opt_ptr<float>(dval);
+  }
+  check_cuda(lmsae::sparse_decode_launch(p, at::cuda::getCurrentCUDAStream()), "sparse_decode launch");
+}
+
+void sparse_dact(const Tensor& idx, const Tensor& W, const Tensor& dxhat, const Tensor& dval) {
+  CHECK_T(idx, torch::kInt32);
+  CHECK_T(W, torch::kBFloat16);
+  CHECK_T(dxhat, torch::kBFloat16);
+  CHECK_T(dval, torch::kFloat32);
+  TORCH_CHECK(idx.dim() == 2 && dval.numel() == idx.numel() && dxhat.numel() == idx.size(0) * W.size(1));
+  const c10::cuda::CUDAGuard guard(idx.device());
+  check_cuda(lmsae::sparse_dact_launch(idx.data_ptr<int>(), (int)idx.size(0), (int)idx.size(1), (int)W.size(1),
+                                       reinterpret_cast<const __nv_bfloat16*>(W.data_ptr()),
+                                       reinterpret_cast<const __nv_bfloat16*>(dxhat.data_ptr()),
+                                       dval.data_ptr<float>(), at::cuda::getCurrentCUDAStream()),
+             "sparse_dact launch");
+}
+
+void mse_loss_grad(const Tensor& xhat, const Tensor& label, const c10::optional<Tensor>& bias,
+                   const c10::optional<Tensor>& row_weight, double grad_scale, const Tensor& dxhat,
+                   const Tensor& loss_sum, const c10::optional<Tensor>& row_loss) {
+  CHECK_T(xhat, torch::kFloat32);
+  CHECK_T(label, torch::kBFloat16);
+  CHECK_T(dxhat, torch::kBFloat16);
+  CHECK_T(loss_sum, torch::kFloat32);
+  TORCH_CHECK(xhat.dim() == 2 && label.numel() == xhat.numel() && dxhat.numel() == xhat.numel());
+  const c10::cuda::CUDAGuard guard(xhat.device());
+  check_cuda(lmsae::mse_loss_grad_launch(xhat.data_ptr<float>(), reinterpret_cast<const __nv_bfloat16*>(label.data_ptr()),
+                                         opt_ptr<const float>(bias), opt_ptr<const float>(row_weight),
+                                         (int)xhat.size(0), (int)xhat.size(1), (float)grad_scale,
+                                         reinterpret_cast<__nv_bfloat16*>(dxhat.data_ptr()), loss_sum.data_ptr<float>(),
+                                         opt_ptr<float>(row_loss), at::cuda::getCurrentCUDAStream()),
+             "mse_loss_grad launch");
+}
+
+void csc_build(const Tensor& idx, int64_t F, const Tensor& counts, const Tensor& offsets, const Tensor& cursor,
+               const Tensor& entries, const Tensor& block_sums) {
+  CHECK_T(idx, torch::kInt32);
+  CHECK_T(counts, torch::kInt32);
+  CHECK_T(offsets, torch::kInt32);
+  CHECK_T(cursor, torch::kInt32);
+  CHECK_T(entries, torch::kInt32);
+  CHECK_T(block_sums, torch::kInt32);
+  TORCH_CHECK(counts.numel() >= F && offsets.numel() >= F + 1 && cursor.numel() >= F && entries.numel() >= idx.numel());
+  TORCH_CHECK(block_sums.numel() >= (F + 4095) / 4096, "block_sums needs one int per 4096 features");
+  const c10::cuda::CUDAGuard guard(idx.device());
+  check_cuda(lmsae::csc_build_launch(idx.data_ptr<int>(), idx.numel(), (int)F, counts.data_ptr<int>(),
+                                     offsets.data_ptr<int>(), cursor.data_ptr<int>(), entries.data_ptr<int>(),
+                                     block_sums.data_ptr<int>(), at::cuda::getCurrentCUDAStream()),
+             "csc_build launch");
+}
+
+lmsae::AdamHyper make_hyper(double lr, double beta1, double beta2, double eps, int64_t step) {
+  lmsae::AdamHyper h;
+  h.lr = (float)lr;
+  h.beta1 = (float)beta1;
+  h.beta2 = (float)beta2;
+  h.eps = (float)eps;
+  h.bias_correction1 = (float)(1.0 - std::pow(beta1, (double)step));
+  h.bias_correction2_sqrt = (float)std::sqrt(1.0 - std::pow(beta2, (double)step));
+  return h;
+}
+
+void sparse_grad_adam(const Tensor& offsets, const Tensor& entries, const Tensor& act, const Tensor& dact,
+                      const Tensor& x, const Tensor& dxhat, const Tensor& WD, const Tensor& mD, const Tensor& vD,
+                      const Tensor& WD_bf16, const Tensor& WE, const Tensor& mE, const Tensor& vE,
+                      const Tensor& WE_bf16, const c10::optional<Tensor>& bE, const c10::optional<Tensor>& mbE,
+                      const c10::optional<Tensor>& vbE, const c10::optional<Tensor>& dec_norm,
+                      const c10::optional<Tensor>& grad_mul, const c10::optional<Tensor>& grad_sq_sum, double lr,
+                      double beta1, double beta2, double eps, int64_t step, bool update) {
+  CHECK_T(offsets, torch::kInt32);
+  CHECK_T(entries, torch::kInt32);
+  CHECK_T(act, torch::kFloat32);
+  CHECK_T(dact, torch::kFloat32);
+  CHECK_T(x, torch::kBFloat16);
+  CHECK_T(dxhat, torch::kBFloat16);
+  CHECK_T(WD, torch::kFloat32); CHECK_T(mD, torch::kFloat32); CHECK_T(vD, torch::kFloat32); CHECK_T(WD_bf16, torch::kBFloat16);
+  CHECK_T(WE, torch::kFloat32); CHECK_T(mE, torch::kFloat32); CHECK_T(vE, torch::kFloat32); CHECK_T(WE_bf16, torch::kBFloat16);
+  TORCH_CHECK(WD.dim() == 2 && WE.sizes() == WD.sizes() && act.dim() == 2 && dact.sizes() == act.sizes());
+  const c10::cuda::CUDAGuard guard(WD.device());
+  lmsae::GradAdamParams p{};
+  p.F = (int)WD.size(0);
+  p.d = (int)WD.size(1);
+  p.k = (int)act.size(1);
+  TORCH_CHECK(offsets.numel() >= p.F + 1 && x.size(1) == p.d && dxhat.sizes() == x.sizes());
+  for (const Tensor* t : {&mD, &vD, &WD_bf16, &mE, &vE, &WE_bf16}) TORCH_CHECK(t->numel() == WD.numel());
+  p.offsets = offsets.data_ptr<int>();
+  p.entries = entries.data_ptr<int>();
+  p.act = act.data_ptr<float>();
+  p.dact = dact.data_ptr<float>();
+  p.x = reinterpret_cast<const __nv_bfloat16*>(x.data_ptr());
+  p.dxhat = reinterpret_cast<const __nv_bfloat16*>(dxhat.data_ptr());
+  p.WD = WD.data_ptr<float>(); p.mD = mD.data_ptr<float>(); p.vD = vD.data_ptr<float>();
+  p.WD_bf16 = reinterpret_cast<__nv_bfloat16*>(WD_bf16.data_ptr());
+  p.WE = WE.data_ptr<float>(); p.mE = mE.data_ptr<float>(); p.vE = vE.data_ptr<float>();
+  p.WE_bf16 = reinterpret_cast<__nv_bfloat16*>(WE_bf16.data_ptr());
+  if (bE.has_value()) {
+    TORCH_CHECK(mbE.has_value() && vbE.has_value());
+    CHECK_T(*bE, torch::kFloat32); CHECK_T(*mbE, torch::kFloat32); CHECK_T(*vbE, torch::kFloat32);
+    TORCH_CHECK(bE->numel() == p.F && mbE->numel() == p.F && vbE->numel() == p.F);
+  }
+  p.bE = opt_ptr<float>(bE); p.mbE = opt_ptr<float>(mbE); p.vbE = opt_ptr<float>(vbE);
+  if (dec_norm.has_value()) { CHECK_T(*dec_norm, torch::kFloat32); TORCH_CHECK(dec_norm->numel() == p.F); }
+  p.dec_norm = opt_ptr<float>(dec_norm);
+  p.grad_mul = opt_ptr<const float>(grad_mul);
+  p.grad_sq_sum = opt_ptr<float>(grad_sq_sum);
+  p.h = make_hyper(lr, beta1, beta2, eps, step);
+  p.update = update ? 1 : 0;
+  check_cuda(lmsae::sparse_grad_adam_launch(p, at::cuda::getCurrentCUDAStream()), "sparse_grad_adam launch");
+}
+
+void colsum_bf16(const Tensor& a, const Tensor& out) {
+  CHECK_T(a, torch::kBFloat16);
+  CHECK_T(out, torch::kFloat32);
+  TORCH_CHECK(a.dim() == 2 && out.numel() == a.size(1));
+  const c10::cuda::CUDAGuard guard(a.device());
+  check_cuda(lmsae::colsum_bf16_launch(reinterpret_cast<const __nv_bfloat16*>(a.data_ptr()), (int)a.size(0),
+                                       (int)a.size(1), out.data_ptr<float>(), at::cuda::getCurrentCUDAStream()),
+             "colsum_bf16 launch");
+}
+
+void adam_flat(const Tensor& p, const Tensor& g, const Tensor& m, const Tensor& v, const c10::optional<Tensor>& grad_mul,
+               const c10::optional<Tensor>& shadow, const c10::optional<Tensor>& grad_sq_sum, double lr, double beta1,
+               double beta2, double eps, int64_t step, bool update) {
+  CHECK_T(p, torch::kFloat32); CHECK_T(g, torch::kFloat32); CHECK_T(m, torch::kFloat32); CHECK_T(v, torch::kFloat32);
+  TORCH_CHECK(g.numel() == p.numel() && m.numel() == p.numel() && v.numel() == p.numel());
+  if (shadow.has_value()) { CHECK_T(*shadow, torch::kBFloat16); TORCH_CHECK(shadow->numel() == p.numel()); }
+  const c10::cuda::CUDAGuard guard(p.device());
+  check_cuda(lmsae::adam_flat_launch(p.data_ptr<float>(), g.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(),
+                                     p.numel(), make_hyper(lr, beta1, beta2, eps, step), opt_ptr<const float>(grad_mul),
+                                     opt_ptr<__nv_bfloat16>(shadow), opt_ptr<float>(grad_sq_sum), update ? 1 : 0,
+                                     at::cuda::getCurrentCUDAStream()),
+             "adam_flat launch");
+}
+
+void row_norm_shadow(const Tensor& W, const c10::optional<Tensor>& norm, const c10::optional<Tensor>& shadow) {
+  CHECK_T(W, torch::kFloat32);
+  TORCH_CHECK(W.dim() == 2);
+  if (norm.has_value()) { CHECK_T(*norm, torch::kFloat32); TORCH_CHECK(norm->numel() == W.size(0)); }
+  if (shadow.has_value()) { CHECK_T(*shadow, torch::kBFloat16); TORCH_CHECK(shadow->numel() == W.numel()); }
+  const c10::cuda::CUDAGuard guard(W.device());
+  check_cuda(lmsae::row_norm_shadow_launch(W.data_ptr<float>(), (int)W.size(0), (int)W.size(1), opt_ptr<float>(norm),
+                                           opt_ptr<__nv_bfloat16>(shadow), at::cuda::getCurrentCUDAStream()),
+             "row_norm_shadow launch");
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.doc() = "sm_100a kernels for sparse-dictionary training";
+  m.def("encoder_gemm", &encoder_gemm);
+  m.def("topk_merge", &topk_merge);
+  m.def("row_topk", &row_topk);
+  m.def("sparse_decode", &sparse_decode);
+  m.def("sparse_dact", &sparse_dact);
+  m.def("mse_loss_grad", &mse_loss_grad);
+  m.def("csc_build", &csc_build);
+  m.def("sparse_grad_adam", &sparse_grad_adam);
+  m.def("colsum_bf16", &colsum_bf16);
+  m.def("adam_flat", &adam_flat);
+  m.def("row_norm_shadow", &row_norm_shadow);
+}

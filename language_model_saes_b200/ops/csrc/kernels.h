@@ -1,0 +1,83 @@
+// Parameter blocks and host launchers of the sm_100a kernels, shared by the .cu files and the bindings.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace lmsae {
+
+struct EncGemmParams {
+  int M, N, K;
+  int num_panels;
+  int num_splits;
+  const float* bias;
+  const float* gate;
+  __nv_bfloat16* H;
+  long long ldh;
+  int k;
+  float* cand_val;
+  int* cand_idx;
+  int* status;
+};
+int enc_gemm_launch(const CUtensorMap& ta, const CUtensorMap& tb, const EncGemmParams& p, int mode, cudaStream_t stream);
+int enc_gemm_slots_for_k(int k);
+
+int topk_merge_launch(const float* cand_val, const int* cand_idx, int M, int C, int k, const float* gate, int own_lo,
+                      int own_hi, int emit_gated, int* out_idx, float* out_val, cudaStream_t stream);
+int row_topk_launch(const __nv_bfloat16* H, long long ldh, int M, int N, int k, const float* gate,
+                    const uint8_t* alive, int* out_idx, float* out_val, cudaStream_t stream);
+
+struct DecodeParams {
+  const int* idx;
+  const float* val;
+  int B, k, d;
+  const __nv_bfloat16* W;
+  const float* bias;
+  float* xhat_f32;
+  __nv_bfloat16* xhat_bf16;
+  const __nv_bfloat16* label;
+  const float* row_weight;
+  float grad_scale;
+  __nv_bfloat16* dxhat;
+  float* loss_sum;
+  float* row_loss;
+  float* dval;
+};
+int sparse_decode_launch(const DecodeParams& p, cudaStream_t stream);
+int sparse_dact_launch(const int* idx, int B, int k, int d, const __nv_bfloat16* W, const __nv_bfloat16* dxhat,
+                       float* dval, cudaStream_t stream);
+int mse_loss_grad_launch(const float* xhat, const __nv_bfloat16* label, const float* bias, const float* row_weight,
+                         int rows, int d, float grad_scale, __nv_bfloat16* dxhat, float* loss_sum, float* row_loss,
+                         cudaStream_t stream);
+int csc_build_launch(const int* idx, long long n, int F, int* counts, int* offsets, int* cursor, int* entries,
+                     int* block_sums_buf, cudaStream_t stream);
+
+struct AdamHyper {
+  float lr, beta1, beta2, eps;
+  float bias_correction1, bias_correction2_sqrt;
+};
+struct GradAdamParams {
+  int F, d, k;
+  const int* offsets;
+  const int* entries;
+  const float* act;
+  const float* dact;
+  const __nv_bfloat16* x;
+  const __nv_bfloat16* dxhat;
+  float* WD; float* mD; float* vD; __nv_bfloat16* WD_bf16;
+  float* WE; float* mE; float* vE; __nv_bfloat16* WE_bf16;
+  float* bE; float* mbE; float* vbE;
+  float* dec_norm;
+  const float* grad_mul;
+  float* grad_sq_sum;
+  AdamHyper h;
+  int update;
+};
+int sparse_grad_adam_launch(const GradAdamParams& p, cudaStream_t stream);
+int colsum_bf16_launch(const __nv_bfloat16* a, int rows, int d, float* out, cudaStream_t stream);
+int adam_flat_launch(float* p, const float* g, float* m, float* v, long long n, AdamHyper h, const float* grad_mul,
+                     __nv_bfloat16* shadow, float* grad_sq_sum, int update, cudaStream_t stream);
+int row_norm_shadow_launch(const float* W, int F, int d, float* norm, __nv_bfloat16* shadow, cudaStream_t stream);
+
+}  // namespace lmsae

@@ -1,0 +1,612 @@
+// Sparse decoder forward / backward and the fused gradient + Adam update (sm_100a, plain SIMT kernels:
+// these ops are gather- and HBM-bound, not tensor-core work).
+//
+// Layouts: W_D and W_E^T are both stored feature-major [F, d] (row f contiguous), with an fp32 master
+// copy and a bf16 shadow used by the forward kernels. Sparse codes are [B, k] (idx int32, -1 = empty).
+//
+//  sparse_decode_kernel   x_hat[b,:] = sum_j val[b,j] * W[idx[b,j],:] (+ bias); optional fused MSE loss,
+//                         d(x_hat) and d(val) (decoder math of models/sae.py:347-377, loss of
+//                         models/sparse_dictionary.py:880-886, gather-GEMM of kernels/kernels.py:383-436
+//                         in the reference project)
+//  sparse_dact_kernel     d val[b,j] = d x_hat[b,:] . W[idx[b,j],:]           (kernels/kernels.py:327-379)
+//  csc_* kernels          group the (row, slot) pairs by feature (counting sort)
+//  sparse_grad_adam_kernel  for every feature row f: rebuild dW_D[f,:] = sum act * d x_hat[b,:] and
+//                         dW_E^T[f,:] = sum d h * x[b,:] in registers from the feature's entry list and
+//                         apply Adam to both rows in the same pass -- the dense gradient is never written
+//                         (replaces kernels/kernels.py:137-225 + torch.optim.Adam in the reference).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace lmsae {
+
+// ---------------------------------------------------------------------------------------------
+// decode (+ loss, + dact)
+// ---------------------------------------------------------------------------------------------
+constexpr int DEC_THREADS = 512;
+constexpr int DEC_MAX_VEC = 2;  // each thread owns up to 2 chunks of 8 columns -> d <= 8192
+
+
+__device__ __forceinline__ void bf16x8_to_float(const uint4& u, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+
+__global__ void __launch_bounds__(DEC_THREADS)
+sparse_decode_kernel(const DecodeParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  int* s_idx = reinterpret_cast<int*>(smem_raw);                 // [k]
+  float* s_val = reinterpret_cast<float*>(smem_raw) + p.k;       // [k]
+  float* s_dx = reinterpret_cast<float*>(smem_raw) + 2 * p.k;    // [d] (dval only)
+  __shared__ float s_red[DEC_THREADS / 32];
+  const int nvec = p.d / 8;  // d % 8 == 0
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  for (int row = blockIdx.x; row < p.B; row += gridDim.x) {
+    __syncthreads();
+    for (int j = threadIdx.x; j < p.k; j += DEC_THREADS) {
+      s_idx[j] = p.idx[(size_t)row * p.k + j];
+      s_val[j] = p.val[(size_t)row * p.k + j];
+    }
+    __syncthreads();
+
+    float acc[DEC_MAX_VEC][8];
+#pragma unroll
+    for (int u = 0; u < DEC_MAX_VEC; ++u)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[u][i] = 0.0f;
+
+    for (int j = 0; j < p.k; ++j) {
+      const int f = s_idx[j];
+      if (f < 0) continue;
+      const float a = s_val[j];
+      const uint4* wrow = reinterpret_cast<const uint4*>(p.W + (size_t)f * p.d);
+#pragma unroll
+      for (int u = 0; u < DEC_MAX_VEC; ++u) {
+        const int v = threadIdx.x + u * DEC_THREADS;
+        if (v < nvec) {
+          float w[8];
+          bf16x8_to_float(__ldg(wrow + v), w);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[u][i] = fmaf(a, w[i], acc[u][i]);
+        }
+      }
+    }
+
+    float local_sq = 0.0f;
+    const float rw = (p.row_weight != nullptr) ? p.row_weight[row] : 1.0f;
+#pragma unroll
+    for (int u = 0; u < DEC_MAX_VEC; ++u) {
+      const int v = threadIdx.x + u * DEC_THREADS;
+      if (v < nvec) {
+        const int c = v * 8;
+        if (p.bias != nullptr) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[u][i] += p.bias[c + i];
+        }
+        if (p.xhat_f32 != nullptr) {
+          float4* o = reinterpret_cast<float4*>(p.xhat_f32 + (size_t)row * p.d + c);
+          o[0] = make_float4(acc[u][0], acc[u][1], acc[u][2], acc[u][3]);
+          o[1] = make_float4(acc[u][4], acc[u][5], acc[u][6], acc[u][7]);
+        }
+        if (p.xhat_bf16 != nullptr) {
+          uint4 o;
+          o.x = pack_bf16x2(acc[u][0], acc[u][1]);
+          o.y = pack_bf16x2(acc[u][2], acc[u][3]);
+          o.z = pack_bf16x2(acc[u][4], acc[u][5]);
+          o.w = pack_bf16x2(acc[u][6], acc[u][7]);
+          *reinterpret_cast<uint4*>(p.xhat_bf16 + (size_t)row * p.d + c) = o;
+        }
+        if (p.label != nullptr) {
+          float y[8];
+          bf16x8_to_float(__ldg(reinterpret_cast<const uint4*>(p.label + (size_t)row * p.d) + v), y);
+          float e[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            e[i] = acc[u][i] - y[i];
+            local_sq = fmaf(e[i], e[i], local_sq);
+            e[i] *= p.grad_scale * rw;
+          }
+          uint4 o;
+          o.x = pack_bf16x2(e[0], e[1]);
+          o.y = pack_bf16x2(e[2], e[3]);
+          o.z = pack_bf16x2(e[4], e[5]);
+          o.w = pack_bf16x2(e[6], e[7]);
+          *reinterpret_cast<uint4*>(p.dxhat + (size_t)row * p.d + c) = o;
+          if (p.dval != nullptr) {
+            // keep the bf16-rounded gradient so that every consumer sees the same d x_hat
+            float er[8];
+            bf16x8_to_float(o, er);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) s_dx[c + i] = er[i];
+          }
+        }
+      }
+    }
+    if (p.label != nullptr) {
+      local_sq = warp_sum(local_sq);
+      if (lane == 0) s_red[warp] = local_sq;
+      __syncthreads();
+      if (warp == 0) {
+        float t = (lane < DEC_THREADS / 32) ? s_red[lane] : 0.0f;
+        t = warp_sum(t);
+        if (lane == 0) {
+          if (p.row_loss != nullptr) p.row_loss[row] = t;
+          atomicAdd(p.loss_sum, t * rw);
+        }
+      }
+      if (p.dval != nullptr) {
+        // second pass over the same (L2-resident) decoder rows: d val[j] = d x_hat . W[idx[j], :]
+        __syncthreads();
+        for (int j = warp; j < p.k; j += DEC_THREADS / 32) {
+          const int f = s_idx[j];
+          float dot = 0.0f;
+          if (f >= 0) {
+            const uint4* wrow = reinterpret_cast<const uint4*>(p.W + (size_t)f * p.d);
+            for (int v = lane; v < nvec; v += 32) {
+              float w[8];
+              bf16x8_to_float(__ldg(wrow + v), w);
+              const float* dx = s_dx + v * 8;
+#pragma unroll
+              for (int i = 0; i < 8; ++i) dot = fmaf(w[i], dx[i], dot);
+            }
+          }
+          dot = warp_sum(dot);
+          if (lane == 0) p.dval[(size_t)row * p.k + j] = dot;
+        }
+      }
+    }
+  }
+}
+
+int sparse_decode_launch(const DecodeParams& p, cudaStream_t stream) {
+  if (p.d % 8 != 0 || p.d > DEC_THREADS * DEC_MAX_VEC * 8) return (int)cudaErrorInvalidValue;
+  size_t smem = (size_t)p.k * 8 + (p.dval != nullptr ? (size_t)p.d * 4 : 0);
+  cudaError_t e = cudaFuncSetAttribute(sparse_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+  if (e != cudaSuccess) return (int)e;
+  if (smem > 100 * 1024) return (int)cudaErrorInvalidValue;
+  int blocks = p.B < 148 * 16 ? p.B : 148 * 16;
+  sparse_decode_kernel<<<blocks, DEC_THREADS, smem, stream>>>(p);
+  return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
+// d val[b,j] = d x_hat[b,:] . W[idx[b,j],:]    (stand-alone, for the feature-sharded path where
+// d x_hat only exists after the cross-shard reduction)
+// ---------------------------------------------------------------------------------------------
+constexpr int DACT_THREADS = 256;
+
+__global__ void __launch_bounds__(DACT_THREADS)
+sparse_dact_kernel(const int* __restrict__ idx, int B, int k, int d, const __nv_bfloat16* __restrict__ W,
+                   const __nv_bfloat16* __restrict__ dxhat, float* __restrict__ dval) {
+  extern __shared__ float s_dx[];  // [d]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = d / 8;
+  for (int row = blockIdx.x; row < B; row += gridDim.x) {
+    __syncthreads();
+    for (int v = threadIdx.x; v < nvec; v += DACT_THREADS) {
+      float f[8];
+      bf16x8_to_float(__ldg(reinterpret_cast<const uint4*>(dxhat + (size_t)row * d) + v), f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s_dx[v * 8 + i] = f[i];
+    }
+    __syncthreads();
+    for (int j = warp; j < k; j += DACT_THREADS / 32) {
+      const int f = idx[(size_t)row * k + j];
+      float dot = 0.0f;
+      if (f >= 0) {
+        const uint4* wrow = reinterpret_cast<const uint4*>(W + (size_t)f * d);
+        for (int v = lane; v < nvec; v += 32) {
+          float w[8];
+          bf16x8_to_float(__ldg(wrow + v), w);
+          const float* dx = s_dx + v * 8;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) dot = fmaf(w[i], dx[i], dot);
+        }
+      }
+      dot = warp_sum(dot);
+      if (lane == 0) dval[(size_t)row * k + j] = dot;
+    }
+  }
+}
+
+int sparse_dact_launch(const int* idx, int B, int k, int d, const __nv_bfloat16* W, const __nv_bfloat16* dxhat,
+                       float* dval, cudaStream_t stream) {
+  if (d % 8 != 0 || (size_t)d * 4 > 160 * 1024) return (int)cudaErrorInvalidValue;
+  cudaError_t e = cudaFuncSetAttribute(sparse_dact_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+  if (e != cudaSuccess) return (int)e;
+  int blocks = B < 148 * 8 ? B : 148 * 8;
+  sparse_dact_kernel<<<blocks, DACT_THREADS, (size_t)d * 4, stream>>>(idx, B, k, d, W, dxhat, dval);
+  return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
+// MSE loss + gradient on dense rows (feature-sharded path: x_hat arrives from the cross-shard reduce)
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+mse_loss_grad_kernel(const float* __restrict__ xhat, const __nv_bfloat16* __restrict__ label,
+                     const float* __restrict__ bias, const float* __restrict__ row_weight, int rows, int d,
+                     float grad_scale, __nv_bfloat16* __restrict__ dxhat, float* __restrict__ loss_sum,
+                     float* __restrict__ row_loss) {
+  __shared__ float s_red[8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float rw = row_weight != nullptr ? row_weight[row] : 1.0f;
+    float sq = 0.0f;
+    for (int c = threadIdx.x; c < d; c += 256) {
+      float xh = xhat[(size_t)row * d + c];
+      if (bias != nullptr) xh += bias[c];
+      const float e = xh - __bfloat162float(label[(size_t)row * d + c]);
+      sq = fmaf(e, e, sq);
+      dxhat[(size_t)row * d + c] = __float2bfloat16(e * grad_scale * rw);
+    }
+    sq = warp_sum(sq);
+    __syncthreads();
+    if (lane == 0) s_red[warp] = sq;
+    __syncthreads();
+    if (warp == 0) {
+      float t = lane < 8 ? s_red[lane] : 0.0f;
+      t = warp_sum(t);
+      if (lane == 0) {
+        if (row_loss != nullptr) row_loss[row] = t;
+        atomicAdd(loss_sum, t * rw);
+      }
+    }
+  }
+}
+
+int mse_loss_grad_launch(const float* xhat, const __nv_bfloat16* label, const float* bias, const float* row_weight,
+                         int rows, int d, float grad_scale, __nv_bfloat16* dxhat, float* loss_sum, float* row_loss,
+                         cudaStream_t stream) {
+  int blocks = rows < 148 * 8 ? rows : 148 * 8;
+  mse_loss_grad_kernel<<<blocks, 256, 0, stream>>>(xhat, label, bias, row_weight, rows, d, grad_scale, dxhat,
+                                                   loss_sum, row_loss);
+  return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
+// group (row, slot) pairs by feature: counts -> offsets (exclusive scan) -> entries
+// ---------------------------------------------------------------------------------------------
+__global__ void csc_count_kernel(const int* __restrict__ idx, long long n, int F, int* __restrict__ counts) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const int f = idx[i];
+    if (f >= 0 && f < F) atomicAdd(&counts[f], 1);
+  }
+}
+
+// Exclusive scan of counts[F] in three small launches: per-block scan of 4096 elements (coalesced int4
+// loads) + block totals, scan of the totals by one block, then add-back while writing offsets and cursors.
+constexpr int SCAN_THREADS = 1024;
+constexpr int SCAN_ELEMS = SCAN_THREADS * 4;
+
+__device__ __forceinline__ int block_exclusive_scan_1024(int v, int* s_warp, int& total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += t;
+  }
+  if (lane == 31) s_warp[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {
+    int w = s_warp[lane];
+    int winc = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, winc, o);
+      if (lane >= o) winc += t;
+    }
+    s_warp[lane] = winc - w;  // exclusive prefix of the warp totals
+    if (lane == 31) s_warp[32] = winc;
+  }
+  __syncthreads();
+  total = s_warp[32];
+  return s_warp[warp] + inc - v;
+}
+
+__global__ void __launch_bounds__(SCAN_THREADS)
+csc_scan_local_kernel(const int* __restrict__ counts, int F, int* __restrict__ offsets, int* __restrict__ block_sums) {
+  __shared__ int s_warp[33];
+  const int base = blockIdx.x * SCAN_ELEMS + threadIdx.x * 4;
+  int c[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) c[i] = (base + i < F) ? counts[base + i] : 0;
+  const int mine = c[0] + c[1] + c[2] + c[3];
+  int total;
+  int run = block_exclusive_scan_1024(mine, s_warp, total);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (base + i < F) offsets[base + i] = run;
+    run += c[i];
+  }
+  if (threadIdx.x == 0) block_sums[blockIdx.x] = total;
+}
+
+__global__ void __launch_bounds__(SCAN_THREADS)
+csc_scan_sums_kernel(int* __restrict__ block_sums, int nblocks, int* __restrict__ offsets, int F) {
+  __shared__ int s_warp[33];
+  __shared__ int s_carry;
+  if (threadIdx.x == 0) s_carry = 0;
+  __syncthreads();
+  for (int b0 = 0; b0 < nblocks; b0 += SCAN_THREADS) {
+    const int i = b0 + threadIdx.x;
+    const int v = i < nblocks ? block_sums[i] : 0;
+    int total;
+    const int ex = block_exclusive_scan_1024(v, s_warp, total);
+    const int carry = s_carry;
+    if (i < nblocks) block_sums[i] = carry + ex;
+    __syncthreads();
+    if (threadIdx.x == 0) s_carry = carry + total;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) offsets[F] = s_carry;
+}
+
+__global__ void __launch_bounds__(SCAN_THREADS)
+csc_scan_add_kernel(const int* __restrict__ block_sums, int F, int* __restrict__ offsets, int* __restrict__ cursor) {
+  const int add = block_sums[blockIdx.x];
+  const int base = blockIdx.x * SCAN_ELEMS + threadIdx.x * 4;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (base + i < F) {
+      const int o = offsets[base + i] + add;
+      offsets[base + i] = o;
+      cursor[base + i] = o;
+    }
+  }
+}
+
+__global__ void csc_fill_kernel(const int* __restrict__ idx, long long n, int F, int* __restrict__ cursor,
+                                int* __restrict__ entries) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const int f = idx[i];
+    if (f >= 0 && f < F) {
+      const int pos = atomicAdd(&cursor[f], 1);
+      entries[pos] = (int)i;
+    }
+  }
+}
+
+int csc_build_launch(const int* idx, long long n, int F, int* counts, int* offsets, int* cursor, int* entries,
+                     int* block_sums_buf, cudaStream_t stream) {
+  cudaError_t e = cudaMemsetAsync(counts, 0, (size_t)F * sizeof(int), stream);
+  if (e != cudaSuccess) return (int)e;
+  const int threads = 256;
+  int blocks = (int)((n + threads - 1) / threads);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks < 1) blocks = 1;
+  csc_count_kernel<<<blocks, threads, 0, stream>>>(idx, n, F, counts);
+  // `block_sums_buf` holds one int per 4096 features
+  const int nblocks = (F + SCAN_ELEMS - 1) / SCAN_ELEMS;
+  int* block_sums = block_sums_buf;
+  csc_scan_local_kernel<<<nblocks, SCAN_THREADS, 0, stream>>>(counts, F, offsets, block_sums);
+  csc_scan_sums_kernel<<<1, SCAN_THREADS, 0, stream>>>(block_sums, nblocks, offsets, F);
+  csc_scan_add_kernel<<<nblocks, SCAN_THREADS, 0, stream>>>(block_sums, F, offsets, cursor);
+  csc_fill_kernel<<<blocks, threads, 0, stream>>>(idx, n, F, cursor, entries);
+  return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
+// fused sparse gradient + Adam over feature rows
+// ---------------------------------------------------------------------------------------------
+
+
+constexpr int GA_THREADS = 256;
+
+__device__ __forceinline__ float4 ldcs4(const float* p) { return __ldcs(reinterpret_cast<const float4*>(p)); }
+__device__ __forceinline__ void stcs4(float* p, const float4& v) { __stcs(reinterpret_cast<float4*>(p), v); }
+
+__device__ __forceinline__ void adam_elem(float& p, float& m, float& v, float g, const AdamHyper& h) {
+  m = h.beta1 * m + (1.0f - h.beta1) * g;
+  v = h.beta2 * v + (1.0f - h.beta2) * g * g;
+  const float denom = sqrtf(v) / h.bias_correction2_sqrt + h.eps;
+  p -= (h.lr / h.bias_correction1) * (m / denom);
+}
+
+// One CTA walks feature rows (grid-stride). For a row it first rebuilds the two gradient rows from the
+// feature's entry list (gathers of x / d x_hat rows, normally L2 hits), then streams p, m, v once.
+__global__ void __launch_bounds__(GA_THREADS, 4)
+sparse_grad_adam_kernel(const GradAdamParams p) {
+  __shared__ float s_red[GA_THREADS / 32];
+  __shared__ float s_gsq[GA_THREADS / 32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float gmul = p.grad_mul != nullptr ? *p.grad_mul : 1.0f;
+  float gsq_local = 0.0f;
+
+  for (int f = blockIdx.x; f < p.F; f += gridDim.x) {
+    const int e0 = p.offsets[f], e1 = p.offsets[f + 1];
+    float bias_g = 0.0f;
+    float norm_sq = 0.0f;
+    for (int c0 = 0; c0 < p.d; c0 += GA_THREADS * 4) {
+      const int c = c0 + threadIdx.x * 4;
+      const bool in = c < p.d;  // d % 4 == 0
+      float gD[4] = {0.f, 0.f, 0.f, 0.f}, gE[4] = {0.f, 0.f, 0.f, 0.f};
+      const size_t o = (size_t)f * p.d + (in ? c : 0);
+      for (int e = e0; e < e1; ++e) {
+        const int ent = p.entries[e];
+        const int row = ent / p.k;
+        const float a = p.act[ent];
+        const float da = p.dact[ent];
+        if (c0 == 0 && threadIdx.x == 0) bias_g += da;
+        if (in) {
+          const uint2 ux = __ldg(reinterpret_cast<const uint2*>(p.x + (size_t)row * p.d + c));
+          const uint2 ud = __ldg(reinterpret_cast<const uint2*>(p.dxhat + (size_t)row * p.d + c));
+          const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ux.x));
+          const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ux.y));
+          const float2 d01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ud.x));
+          const float2 d23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ud.y));
+          gD[0] = fmaf(a, d01.x, gD[0]); gD[1] = fmaf(a, d01.y, gD[1]);
+          gD[2] = fmaf(a, d23.x, gD[2]); gD[3] = fmaf(a, d23.y, gD[3]);
+          gE[0] = fmaf(da, x01.x, gE[0]); gE[1] = fmaf(da, x01.y, gE[1]);
+          gE[2] = fmaf(da, x23.x, gE[2]); gE[3] = fmaf(da, x23.y, gE[3]);
+        }
+      }
+      if (!in) continue;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        gD[i] *= gmul;
+        gE[i] *= gmul;
+        gsq_local += gD[i] * gD[i] + gE[i] * gE[i];
+      }
+      if (p.update) {
+        {
+          float4 w = ldcs4(p.WD + o), m = ldcs4(p.mD + o), v = ldcs4(p.vD + o);
+          adam_elem(w.x, m.x, v.x, gD[0], p.h); adam_elem(w.y, m.y, v.y, gD[1], p.h);
+          adam_elem(w.z, m.z, v.z, gD[2], p.h); adam_elem(w.w, m.w, v.w, gD[3], p.h);
+          stcs4(p.WD + o, w); stcs4(p.mD + o, m); stcs4(p.vD + o, v);
+          norm_sq += w.x * w.x + w.y * w.y + w.z * w.z + w.w * w.w;
+          uint2 sh; sh.x = pack_bf16x2(w.x, w.y); sh.y = pack_bf16x2(w.z, w.w);
+          *reinterpret_cast<uint2*>(p.WD_bf16 + o) = sh;
+        }
+        {
+          float4 w = ldcs4(p.WE + o), m = ldcs4(p.mE + o), v = ldcs4(p.vE + o);
+          adam_elem(w.x, m.x, v.x, gE[0], p.h); adam_elem(w.y, m.y, v.y, gE[1], p.h);
+          adam_elem(w.z, m.z, v.z, gE[2], p.h); adam_elem(w.w, m.w, v.w, gE[3], p.h);
+          stcs4(p.WE + o, w); stcs4(p.mE + o, m); stcs4(p.vE + o, v);
+          uint2 sh; sh.x = pack_bf16x2(w.x, w.y); sh.y = pack_bf16x2(w.z, w.w);
+          *reinterpret_cast<uint2*>(p.WE_bf16 + o) = sh;
+        }
+      }
+    }
+    if (threadIdx.x == 0) {
+      bias_g *= gmul;
+      gsq_local += bias_g * bias_g;
+      if (p.update && p.bE != nullptr) {
+        float b = p.bE[f], m = p.mbE[f], v = p.vbE[f];
+        adam_elem(b, m, v, bias_g, p.h);
+        p.bE[f] = b; p.mbE[f] = m; p.vbE[f] = v;
+      }
+    }
+    if (p.update && p.dec_norm != nullptr) {
+      norm_sq = warp_sum(norm_sq);
+      __syncthreads();
+      if (lane == 0) s_red[warp] = norm_sq;
+      __syncthreads();
+      if (warp == 0) {
+        float t = lane < GA_THREADS / 32 ? s_red[lane] : 0.0f;
+        t = warp_sum(t);
+        if (lane == 0) p.dec_norm[f] = sqrtf(t);
+      }
+    }
+  }
+  if (p.grad_sq_sum != nullptr) {
+    gsq_local = warp_sum(gsq_local);
+    if (lane == 0) s_gsq[warp] = gsq_local;
+    __syncthreads();
+    if (warp == 0) {
+      float t = lane < GA_THREADS / 32 ? s_gsq[lane] : 0.0f;
+      t = warp_sum(t);
+      if (lane == 0) atomicAdd(p.grad_sq_sum, t);
+    }
+  }
+}
+
+int sparse_grad_adam_launch(const GradAdamParams& p, cudaStream_t stream) {
+  if (p.d % 4 != 0) return (int)cudaErrorInvalidValue;
+  int blocks = p.F < 148 * 8 ? p.F : 148 * 8;
+  sparse_grad_adam_kernel<<<blocks, GA_THREADS, 0, stream>>>(p);
+  return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
+// dense helpers: column sum of a bf16 matrix, and a flat Adam step with an explicit gradient
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+colsum_bf16_kernel(const __nv_bfloat16* __restrict__ a, int rows, int d, int rows_per_block, float* __restrict__ out) {
+  const int r0 = blockIdx.y * rows_per_block;
+  const int r1 = min(rows, r0 + rows_per_block);
+  for (int c = blockIdx.x * 256 + threadIdx.x; c < d; c += gridDim.x * 256) {
+    float s = 0.0f;
+    for (int r = r0; r < r1; ++r) s += __bfloat162float(a[(size_t)r * d + c]);
+    atomicAdd(out + c, s);
+  }
+}
+
+int colsum_bf16_launch(const __nv_bfloat16* a, int rows, int d, float* out, cudaStream_t stream) {
+  cudaError_t e = cudaMemsetAsync(out, 0, (size_t)d * sizeof(float), stream);
+  if (e != cudaSuccess) return (int)e;
+  const int rows_per_block = 64;
+  dim3 grid((d + 255) / 256, (rows + rows_per_block - 1) / rows_per_block);
+  colsum_bf16_kernel<<<grid, 256, 0, stream>>>(a, rows, d, rows_per_block, out);
+  return (int)cudaGetLastError();
+}
+
+// Flat Adam (torch.optim.Adam semantics without weight decay / amsgrad), optional bf16 shadow and
+// squared-gradient accumulation. Used for small dense parameters (b_D, thresholds) and by the generic
+// multi-tensor optimizer.
+__global__ void __launch_bounds__(256)
+adam_flat_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
+                 long long n, AdamHyper h, const float* __restrict__ grad_mul, __nv_bfloat16* __restrict__ shadow,
+                 float* __restrict__ grad_sq_sum, int update) {
+  __shared__ float s_gsq[8];
+  const float gmul = grad_mul != nullptr ? *grad_mul : 1.0f;
+  float gsq = 0.0f;
+  for (long long i = blockIdx.x * 256LL + threadIdx.x; i < n; i += (long long)gridDim.x * 256) {
+    const float gi = g[i] * gmul;
+    gsq += gi * gi;
+    if (update) {
+      float pi = p[i], mi = m[i], vi = v[i];
+      adam_elem(pi, mi, vi, gi, h);
+      p[i] = pi; m[i] = mi; v[i] = vi;
+      if (shadow != nullptr) shadow[i] = __float2bfloat16(pi);
+    }
+  }
+  if (grad_sq_sum != nullptr) {
+    gsq = warp_sum(gsq);
+    if ((threadIdx.x & 31) == 0) s_gsq[threadIdx.x >> 5] = gsq;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      float t = threadIdx.x < 8 ? s_gsq[threadIdx.x] : 0.0f;
+      t = warp_sum(t);
+      if (threadIdx.x == 0) atomicAdd(grad_sq_sum, t);
+    }
+  }
+}
+
+int adam_flat_launch(float* p, const float* g, float* m, float* v, long long n, AdamHyper h, const float* grad_mul,
+                     __nv_bfloat16* shadow, float* grad_sq_sum, int update, cudaStream_t stream) {
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks < 1) blocks = 1;
+  adam_flat_kernel<<<(int)blocks, 256, 0, stream>>>(p, g, m, v, n, h, grad_mul, shadow, grad_sq_sum, update);
+  return (int)cudaGetLastError();
+}
+
+// Row L2 norms of an fp32 [F, d] matrix (+ optional bf16 shadow refresh): used at set-up and after
+// loading weights so that dec_norm / shadows agree with the master copy.
+__global__ void __launch_bounds__(256)
+row_norm_shadow_kernel(const float* __restrict__ W, int F, int d, float* __restrict__ norm,
+                       __nv_bfloat16* __restrict__ shadow) {
+  __shared__ float s_red[8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int f = blockIdx.x; f < F; f += gridDim.x) {
+    float s = 0.0f;
+    for (int c = threadIdx.x; c < d; c += 256) {
+      const float w = W[(size_t)f * d + c];
+      s = fmaf(w, w, s);
+      if (shadow != nullptr) shadow[(size_t)f * d + c] = __float2bfloat16(w);
+    }
+    s = warp_sum(s);
+    __syncthreads();
+    if (lane == 0) s_red[warp] = s;
+    __syncthreads();
+    if (warp == 0) {
+      float t = lane < 8 ? s_red[lane] : 0.0f;
+      t = warp_sum(t);
+      if (lane == 0 && norm != nullptr) norm[f] = sqrtf(t);
+    }
+  }
+}
+
+int row_norm_shadow_launch(const float* W, int F, int d, float* norm, __nv_bfloat16* shadow, cudaStream_t stream) {
+  int blocks = F < 148 * 16 ? F : 148 * 16;
+  row_norm_shadow_kernel<<<blocks, 256, 0, stream>>>(W, F, d, norm, shadow);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace lmsae

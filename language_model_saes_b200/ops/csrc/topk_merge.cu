@@ -1,0 +1,179 @@
+// Exact top-k merge of per-range candidate lists.
+//
+// The encoder GEMM emits, for every row, C = (number of ranges) * KS candidates (gated value, column or
+// -1). This kernel ranks them (value descending, ties by position) and keeps the k best. Under feature
+// sharding it runs twice: once per rank on its own ranges (emit_gated = 1, output = k (g, local column)
+// pairs that are exchanged between the shards), and once on the gathered lists of all shards, where only
+// candidates in [own_lo, own_hi) -- this shard's segment -- are written out; positions won by other
+// shards stay (-1, 0). That reproduces a global per-row TopK over the sharded feature axis (the job of
+// distributed_topk in utils/distributed/ops.py:158-266 of the reference) with one exchange instead of
+// an iterative threshold search.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace lmsae {
+
+constexpr int MERGE_WARPS = 4;
+
+__global__ void __launch_bounds__(MERGE_WARPS * 32)
+topk_merge_kernel(const float* __restrict__ cand_val, const int* __restrict__ cand_idx, int M, int C, int k,
+                  const float* __restrict__ gate, int own_lo, int own_hi, int emit_gated,
+                  int* __restrict__ out_idx, float* __restrict__ out_val) {
+  extern __shared__ uint8_t smem_raw[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* sval = reinterpret_cast<float*>(smem_raw) + (size_t)warp * C;
+  int* sidx = reinterpret_cast<int*>(smem_raw + (size_t)MERGE_WARPS * C * 4) + (size_t)warp * C;
+
+  for (int row = blockIdx.x * MERGE_WARPS + warp; row < M; row += gridDim.x * MERGE_WARPS) {
+    const float* cv = cand_val + (size_t)row * C;
+    const int* ci = cand_idx + (size_t)row * C;
+    for (int i = lane; i < C; i += 32) {
+      const int id = ci[i];
+      sidx[i] = id;
+      sval[i] = (id >= 0) ? cv[i] : -1.0f;  // valid candidates are > 0
+    }
+    for (int i = lane; i < k; i += 32) {
+      out_idx[(size_t)row * k + i] = -1;
+      out_val[(size_t)row * k + i] = 0.0f;
+    }
+    __syncwarp();
+    for (int i = own_lo + lane; i < own_hi; i += 32) {
+      const int id = sidx[i];
+      if (id < 0) continue;
+      const float v = sval[i];
+      int rank = 0;
+      for (int j = 0; j < C; ++j) {
+        const float u = sval[j];
+        rank += (u > v) || (u == v && j < i);
+      }
+      if (rank < k) {
+        float o = v;
+        if (!emit_gated && gate != nullptr) o = v / gate[id];
+        out_idx[(size_t)row * k + rank] = id;
+        out_val[(size_t)row * k + rank] = o;
+      }
+    }
+    __syncwarp();
+  }
+}
+
+int topk_merge_launch(const float* cand_val, const int* cand_idx, int M, int C, int k, const float* gate,
+                      int own_lo, int own_hi, int emit_gated, int* out_idx, float* out_val,
+                      cudaStream_t stream) {
+  const size_t smem = (size_t)MERGE_WARPS * C * 8;
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  cudaError_t e = cudaFuncSetAttribute(topk_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return (int)e;
+  int blocks = (M + MERGE_WARPS - 1) / MERGE_WARPS;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  topk_merge_kernel<<<blocks, MERGE_WARPS * 32, smem, stream>>>(cand_val, cand_idx, M, C, k, gate, own_lo, own_hi,
+                                                               emit_gated, out_idx, out_val);
+  return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------
+// Row top-k over a materialised bf16 matrix H[M, N] (used when k is larger than the fused epilogue
+// supports, for Aux-K over dead features and for the generic autograd path).
+// One CTA per row. Pass 1 finds the k-th largest gated value by a radix descent over the fp32 bit pattern
+// (4 passes of 8 bits, 256-bin histogram in shared memory); pass 2 writes the survivors.
+// value = H * gate (gate optional) * alive (alive optional byte mask: only features with alive != 0
+// compete); only values > 0 compete.
+// ------------------------------------------------------------------------------------------------
+constexpr int RT_THREADS = 512;
+
+__device__ __forceinline__ float gated_value(const __nv_bfloat16* __restrict__ hrow, const float* __restrict__ gate,
+                                             const uint8_t* __restrict__ alive, int c) {
+  float v = __bfloat162float(hrow[c]);
+  if (gate != nullptr) v *= gate[c];
+  if (alive != nullptr && alive[c] == 0) v = 0.0f;
+  return v;
+}
+
+__global__ void __launch_bounds__(RT_THREADS)
+row_topk_kernel(const __nv_bfloat16* __restrict__ H, long long ldh, int M, int N, int k,
+                const float* __restrict__ gate, const uint8_t* __restrict__ alive, int* __restrict__ out_idx,
+                float* __restrict__ out_val) {
+  __shared__ unsigned hist[256];
+  __shared__ unsigned s_prefix, s_remaining, s_count_gt, s_cursor_gt, s_cursor_eq;
+  const int row = blockIdx.x;
+  if (row >= M) return;
+  const __nv_bfloat16* hrow = H + (long long)row * ldh;
+
+  unsigned prefix = 0;     // bits decided so far (from the top)
+  unsigned remaining = k;  // how many of the top-k are still inside the undecided bucket
+  bool fewer_than_k = false;
+  for (int pass = 0; pass < 4; ++pass) {
+    const int shift = 24 - 8 * pass;
+    for (int i = threadIdx.x; i < 256; i += RT_THREADS) hist[i] = 0;
+    __syncthreads();
+    const unsigned hi_mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+    for (int c = threadIdx.x; c < N; c += RT_THREADS) {
+      const float v = gated_value(hrow, gate, alive, c);
+      if (v > 0.0f) {
+        const unsigned b = __float_as_uint(v);
+        if ((b & hi_mask) == prefix) atomicAdd(&hist[(b >> shift) & 0xff], 1u);
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      unsigned acc = 0;
+      int bin = 255;
+      for (; bin >= 0; --bin) {
+        if (acc + hist[bin] >= remaining) break;
+        acc += hist[bin];
+      }
+      if (bin < 0) {  // fewer than `remaining` positive values in this bucket: keep them all
+        s_prefix = 0xffffffffu;
+        s_remaining = 0;
+      } else {
+        s_prefix = prefix | ((unsigned)bin << shift);
+        s_remaining = remaining - acc;
+      }
+    }
+    __syncthreads();
+    if (s_prefix == 0xffffffffu) {
+      fewer_than_k = true;
+      break;
+    }
+    prefix = s_prefix;
+    remaining = s_remaining;
+    __syncthreads();
+  }
+  // threshold bit pattern = prefix (exact k-th value); `remaining` = how many equal to it to keep
+  const unsigned thr = fewer_than_k ? 0u : prefix;
+  if (threadIdx.x == 0) {
+    s_cursor_gt = 0;
+    s_cursor_eq = 0;
+    s_count_gt = fewer_than_k ? 0u : (unsigned)k - remaining;
+  }
+  for (int i = threadIdx.x; i < k; i += RT_THREADS) {
+    out_idx[(size_t)row * k + i] = -1;
+    out_val[(size_t)row * k + i] = 0.0f;
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < N; c += RT_THREADS) {
+    const float v = gated_value(hrow, gate, alive, c);
+    if (v > 0.0f) {
+      const unsigned b = __float_as_uint(v);
+      int pos = -1;
+      if (fewer_than_k || b > thr) {
+        pos = (int)atomicAdd(&s_cursor_gt, 1u);
+      } else if (b == thr) {
+        const unsigned e = atomicAdd(&s_cursor_eq, 1u);
+        if (e < remaining) pos = (int)(s_count_gt + e);
+      }
+      if (pos >= 0 && pos < k) {
+        out_idx[(size_t)row * k + pos] = c;
+        out_val[(size_t)row * k + pos] = (gate != nullptr) ? v / gate[c] : v;
+      }
+    }
+  }
+}
+
+int row_topk_launch(const __nv_bfloat16* H, long long ldh, int M, int N, int k, const float* gate,
+                    const uint8_t* alive, int* out_idx, float* out_val, cudaStream_t stream) {
+  row_topk_kernel<<<M, RT_THREADS, 0, stream>>>(H, ldh, M, N, k, gate, alive, out_idx, out_val);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace lmsae

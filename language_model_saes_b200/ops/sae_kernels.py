@@ -1,0 +1,438 @@
+"""Python entry points of the sm_100a kernels, each paired with a plain PyTorch definition.
+
+The ``ref_*`` functions state the math of each kernel in fp32 PyTorch. They are the oracles of the GPU
+numerics tests and what the CPU code paths run. On a CUDA device the kernel wrappers call the compiled
+extension (``ops/native.py``) and raise if it is missing.
+
+Layouts shared by all kernels: encoder and decoder weights are feature-major ``[F, d]``; sparse codes are
+``(idx int32 [B, k], val fp32 [B, k])`` with ``idx == -1`` marking an empty slot.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import native
+
+NUM_SMS_B200 = 148
+
+_status_buffers: dict[torch.device, torch.Tensor] = {}
+
+
+class KernelStatusError(RuntimeError):
+    """A kernel reported a bounded-wait expiry or a bad argument through its status word."""
+
+
+_STATUS_NAMES = {
+    1: "timeout waiting for a TMA stage (full barrier)",
+    2: "timeout waiting for a free smem stage (empty barrier)",
+    3: "timeout waiting for an accumulator (tmem full)",
+    4: "timeout waiting for the epilogue (tmem empty)",
+    5: "timeout waiting for a peer flag",
+    6: "bad argument",
+    7: "capacity overflow",
+}
+
+
+def _ext():
+    return native.load(required=True)
+
+
+def status_buffer(device: torch.device) -> torch.Tensor:
+    device = torch.device(device)
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    buf = _status_buffers.get(device)
+    if buf is None:
+        buf = torch.zeros(4, dtype=torch.int32, device=device)
+        _status_buffers[device] = buf
+    return buf
+
+
+def check_status(device: torch.device) -> None:
+    """Synchronising read of the status word; raises if any kernel on ``device`` recorded an error."""
+    buf = status_buffer(device)
+    vals = buf.tolist()
+    if vals[0] != 0:
+        buf.zero_()
+        raise KernelStatusError(
+            f"kernel status {vals[0]} ({_STATUS_NAMES.get(vals[0], 'unknown')}), detail={vals[1]}, block={vals[2]}, aux={vals[3]}"
+        )
+
+
+def choose_splits(M: int, N: int, num_sms: int = NUM_SMS_B200) -> int:
+    """How many CTAs share one 128-row panel of the encoder GEMM (each sweeps a range of 256-column tiles)."""
+    panels = (M + 127) // 128
+    n_tiles = (N + 255) // 256
+    return max(1, min(n_tiles, num_sms // max(panels, 1)))
+
+
+def candidate_slots(k: int) -> int:
+    return 32 if k <= 32 else 64
+
+
+# --------------------------------------------------------------------------------------------------
+# encoder
+# --------------------------------------------------------------------------------------------------
+def ref_hidden(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None) -> torch.Tensor:
+    h = x.float() @ w.float().t()
+    if bias is not None:
+        h = h + bias.float()
+    return h
+
+
+def ref_topk_codes(
+    h: torch.Tensor, k: int, gate: torch.Tensor | None = None, alive: torch.Tensor | None = None
+) -> tuple[torch.Tensor, torch.Tensor]:
+    """Per-row top-k of the positive gated values; returns (idx int32, act fp32 = h at the winners)."""
+    g = h.float()
+    if gate is not None:
+        g = g * gate.float()
+    if alive is not None:
+        g = g * alive.to(g.dtype)
+    g = torch.where(g > 0, g, torch.zeros_like(g))
+    k_eff = min(k, g.shape[-1])
+    vals, idx = torch.topk(g, k_eff, dim=-1)
+    if k_eff < k:
+        pad = k - k_eff
+        vals = torch.cat([vals, vals.new_zeros(*vals.shape[:-1], pad)], dim=-1)
+        idx = torch.cat([idx, idx.new_zeros(*idx.shape[:-1], pad)], dim=-1)
+    keep = vals > 0
+    act = vals
+    if gate is not None:
+        act = vals / gate.float()[idx.clamp_min(0)]
+    act = torch.where(keep, act, torch.zeros_like(act))
+    idx = torch.where(keep, idx, torch.full_like(idx, -1))
+    return idx.to(torch.int32), act
+
+
+def encoder_hidden(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None) -> torch.Tensor:
+    """H = x @ w.T + bias as bf16 via the tcgen05 GEMM (x [M,K] bf16, w [N,K] bf16, bias fp32)."""
+    if not x.is_cuda:
+        return ref_hidden(x, w, bias).to(torch.bfloat16)
+    M, N = x.shape[0], w.shape[0]
+    H = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    _ext().encoder_gemm(x, w, bias, None, 1, 0, choose_splits(M, N), H, None, None, status_buffer(x.device))
+    return H
+
+
+def encoder_topk_candidates(
+    x: torch.Tensor,
+    w: torch.Tensor,
+    bias: torch.Tensor | None,
+    gate: torch.Tensor | None,
+    k: int,
+    num_splits: int | None = None,
+    H: torch.Tensor | None = None,
+) -> tuple[torch.Tensor, torch.Tensor, int]:
+    """Run the GEMM with the fused top-k epilogue; returns (cand_val [M, C], cand_idx [M, C], C)."""
+    M, N = x.shape[0], w.shape[0]
+    S = num_splits or choose_splits(M, N)
+    KS = candidate_slots(k)
+    C = S * KS
+    cand_val = torch.empty(M, C, dtype=torch.float32, device=x.device)
+    cand_idx = torch.empty(M, C, dtype=torch.int32, device=x.device)
+    mode = 2 | (1 if H is not None else 0)
+    _ext().encoder_gemm(x, w, bias, gate, mode, k, S, H, cand_val, cand_idx, status_buffer(x.device))
+    return cand_val, cand_idx, C
+
+
+def topk_merge(
+    cand_val: torch.Tensor,
+    cand_idx: torch.Tensor,
+    k: int,
+    gate: torch.Tensor | None,
+    own: tuple[int, int] | None = None,
+    emit_gated: bool = False,
+) -> tuple[torch.Tensor, torch.Tensor]:
+    M, C = cand_val.shape
+    out_idx = torch.empty(M, k, dtype=torch.int32, device=cand_val.device)
+    out_val = torch.empty(M, k, dtype=torch.float32, device=cand_val.device)
+    lo, hi = own if own is not None else (0, C)
+    _ext().topk_merge(cand_val, cand_idx, M, C, k, gate, lo, hi, emit_gated, out_idx, out_val)
+    return out_idx, out_val
+
+
+def encoder_topk(
+    x: torch.Tensor,
+    w: torch.Tensor,
+    bias: torch.Tensor | None,
+    gate: torch.Tensor | None,
+    k: int,
+    return_hidden: bool = False,
+) -> tuple[torch.Tensor, torch.Tensor] | tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Sparse codes of a TopK encoder: (idx [M,k], act [M,k]) (+ hidden_pre bf16 when asked).
+
+    ``k <= 64`` uses the GEMM's fused top-k epilogue (the dense pre-activations are never written unless
+    ``return_hidden``); larger k materialises H and selects with the radix row-top-k kernel.
+    """
+    if not x.is_cuda:
+        h = ref_hidden(x, w, bias)
+        idx, act = ref_topk_codes(h, k, gate)
+        return (idx, act, h.to(torch.bfloat16)) if return_hidden else (idx, act)
+    M, N = x.shape[0], w.shape[0]
+    H = torch.empty(M, N, dtype=torch.bfloat16, device=x.device) if (return_hidden or k > 64) else None
+    if k <= 64:
+        cv, ci, _ = encoder_topk_candidates(x, w, bias, gate, k, H=H)
+        idx, act = topk_merge(cv, ci, k, gate)
+    else:
+        _ext().encoder_gemm(x, w, bias, None, 1, 0, choose_splits(M, N), H, None, None, status_buffer(x.device))
+        idx, act = row_topk(H, k, gate, None)
+    return (idx, act, H) if return_hidden else (idx, act)
+
+
+def row_topk(
+    H: torch.Tensor, k: int, gate: torch.Tensor | None = None, alive: torch.Tensor | None = None
+) -> tuple[torch.Tensor, torch.Tensor]:
+    if not H.is_cuda:
+        return ref_topk_codes(H.float(), k, gate, alive)
+    M = H.shape[0]
+    out_idx = torch.empty(M, k, dtype=torch.int32, device=H.device)
+    out_val = torch.empty(M, k, dtype=torch.float32, device=H.device)
+    alive_u8 = alive.to(torch.uint8).contiguous() if alive is not None else None
+    _ext().row_topk(H.contiguous(), k, gate, alive_u8, out_idx, out_val)
+    return out_idx, out_val
+
+
+# --------------------------------------------------------------------------------------------------
+# decoder
+# --------------------------------------------------------------------------------------------------
+def ref_sparse_decode(idx: torch.Tensor, val: torch.Tensor, W: torch.Tensor, bias: torch.Tensor | None) -> torch.Tensor:
+    safe = idx.clamp_min(0).long()
+    rows = W.float()[safe]  # [B, k, d]
+    coef = torch.where(idx >= 0, val.float(), torch.zeros_like(val, dtype=torch.float32))
+    out = (rows * coef.unsqueeze(-1)).sum(dim=1)
+    if bias is not None:
+        out = out + bias.float()
+    return out
+
+
+def sparse_decode(
+    idx: torch.Tensor, val: torch.Tensor, W: torch.Tensor, bias: torch.Tensor | None, out_dtype: torch.dtype = torch.float32
+) -> torch.Tensor:
+    if not idx.is_cuda:
+        return ref_sparse_decode(idx, val, W, bias).to(out_dtype)
+    B, d = idx.shape[0], W.shape[1]
+    out = torch.empty(B, d, dtype=out_dtype, device=idx.device)
+    f32 = out if out_dtype == torch.float32 else None
+    b16 = out if out_dtype == torch.bfloat16 else None
+    assert f32 is not None or b16 is not None, "out_dtype must be float32 or bfloat16"
+    _ext().sparse_decode(idx, val, W, bias, f32, b16, None, None, 0.0, None, None, None, None)
+    return out
+
+
+def ref_decode_loss(idx, val, W, bias, label, row_weight, grad_scale):
+    xhat = ref_sparse_decode(idx, val, W, bias)
+    e = xhat - label.float()
+    row_loss = (e * e).sum(-1)
+    rw = row_weight.float() if row_weight is not None else torch.ones_like(row_loss)
+    loss_sum = (row_loss * rw).sum()
+    dxhat = (e * grad_scale * rw.unsqueeze(-1)).to(torch.bfloat16)
+    safe = idx.clamp_min(0).long()
+    dval = torch.einsum("bd,bkd->bk", dxhat.float(), W.float()[safe])
+    dval = torch.where(idx >= 0, dval, torch.zeros_like(dval))
+    return xhat, dxhat, loss_sum, row_loss, dval
+
+
+def sparse_decode_loss(
+    idx: torch.Tensor,
+    val: torch.Tensor,
+    W: torch.Tensor,
+    bias: torch.Tensor | None,
+    label: torch.Tensor,
+    row_weight: torch.Tensor | None,
+    grad_scale: float,
+    loss_sum: torch.Tensor,
+    want_dval: bool = True,
+    want_xhat: bool = False,
+    row_loss: torch.Tensor | None = None,
+):
+    """Decode, accumulate sum_b w_b * ||x_hat_b - label_b||^2 into ``loss_sum`` and return
+    (dxhat bf16, dval fp32 | None, xhat fp32 | None)."""
+    B, k = idx.shape
+    d = W.shape[1]
+    dxhat = torch.empty(B, d, dtype=torch.bfloat16, device=idx.device)
+    dval = torch.empty(B, k, dtype=torch.float32, device=idx.device) if want_dval else None
+    xhat = torch.empty(B, d, dtype=torch.float32, device=idx.device) if want_xhat else None
+    if not idx.is_cuda:
+        xh, dx, ls, rl, dv = ref_decode_loss(idx, val, W, bias, label, row_weight, grad_scale)
+        loss_sum += ls
+        if row_loss is not None:
+            row_loss.copy_(rl)
+        return dx, (dv if want_dval else None), (xh if want_xhat else None)
+    _ext().sparse_decode(idx, val, W, bias, xhat, None, label, row_weight, grad_scale, dxhat, loss_sum, row_loss, dval)
+    return dxhat, dval, xhat
+
+
+def sparse_dact(idx: torch.Tensor, W: torch.Tensor, dxhat: torch.Tensor) -> torch.Tensor:
+    if not idx.is_cuda:
+        safe = idx.clamp_min(0).long()
+        dv = torch.einsum("bd,bkd->bk", dxhat.float(), W.float()[safe])
+        return torch.where(idx >= 0, dv, torch.zeros_like(dv))
+    dval = torch.empty(idx.shape, dtype=torch.float32, device=idx.device)
+    _ext().sparse_dact(idx, W, dxhat, dval)
+    return dval
+
+
+def mse_loss_grad(xhat, label, bias, row_weight, grad_scale, loss_sum, row_loss=None):
+    """dxhat (bf16) and loss accumulation for dense fp32 rows (x_hat optionally still missing its bias)."""
+    if not xhat.is_cuda:
+        xh = xhat + (bias if bias is not None else 0.0)
+        e = xh - label.float()
+        rl = (e * e).sum(-1)
+        rw = row_weight.float() if row_weight is not None else torch.ones_like(rl)
+        loss_sum += (rl * rw).sum()
+        if row_loss is not None:
+            row_loss.copy_(rl)
+        return (e * grad_scale * rw.unsqueeze(-1)).to(torch.bfloat16)
+    dxhat = torch.empty(xhat.shape, dtype=torch.bfloat16, device=xhat.device)
+    _ext().mse_loss_grad(xhat, label, bias, row_weight, grad_scale, dxhat, loss_sum, row_loss)
+    return dxhat
+
+
+# --------------------------------------------------------------------------------------------------
+# backward / optimizer
+# --------------------------------------------------------------------------------------------------
+class FeatureGroups:
+    """(row, slot) pairs grouped by feature: ``entries[offsets[f]:offsets[f+1]]`` are flat positions
+    ``row * k + slot`` whose code index is ``f``. Buffers are reused across steps."""
+
+    def __init__(self, F: int, capacity: int, device: torch.device):
+        self.F = F
+        self.counts = torch.zeros(F, dtype=torch.int32, device=device)
+        self.offsets = torch.zeros(F + 1, dtype=torch.int32, device=device)
+        self.cursor = torch.zeros(F, dtype=torch.int32, device=device)
+        self.entries = torch.zeros(capacity, dtype=torch.int32, device=device)
+        self.block_sums = torch.zeros((F + 4095) // 4096, dtype=torch.int32, device=device)
+
+    def build(self, idx: torch.Tensor) -> "FeatureGroups":
+        n = idx.numel()
+        if self.entries.numel() < n:
+            self.entries = torch.zeros(n, dtype=torch.int32, device=idx.device)
+        if idx.is_cuda:
+            _ext().csc_build(idx, self.F, self.counts, self.offsets, self.cursor, self.entries, self.block_sums)
+        else:
+            flat = idx.reshape(-1)
+            valid = flat >= 0
+            order = torch.argsort(torch.where(valid, flat, torch.full_like(flat, self.F)), stable=True)
+            nvalid = int(valid.sum())
+            self.entries[:nvalid] = order[:nvalid].to(torch.int32)
+            counts = torch.bincount(flat[valid].long(), minlength=self.F)
+            self.counts.copy_(counts.to(torch.int32))
+            self.offsets[0] = 0
+            self.offsets[1:] = torch.cumsum(counts, 0).to(torch.int32)
+        return self
+
+
+def ref_sparse_grads(idx, act, dact, x, dxhat, F):
+    """Dense fp32 gradients (dW_D [F,d], dW_E^T [F,d], db_E [F]) of the sparse codes, for tests / CPU."""
+    B, k = idx.shape
+    d = x.shape[1]
+    flat = idx.reshape(-1).long()
+    valid = flat >= 0
+    rows = torch.arange(B, device=idx.device).repeat_interleave(k)[valid]
+    f = flat[valid]
+    a = act.reshape(-1)[valid].float()
+    da = dact.reshape(-1)[valid].float()
+    gD = torch.zeros(F, d, dtype=torch.float32, device=idx.device)
+    gE = torch.zeros(F, d, dtype=torch.float32, device=idx.device)
+    gb = torch.zeros(F, dtype=torch.float32, device=idx.device)
+    gD.index_add_(0, f, a.unsqueeze(1) * dxhat.float()[rows])
+    gE.index_add_(0, f, da.unsqueeze(1) * x.float()[rows])
+    gb.index_add_(0, f, da)
+    return gD, gE, gb
+
+
+def ref_adam(p, g, m, v, lr, beta1, beta2, eps, step):
+    m.mul_(beta1).add_(g, alpha=1 - beta1)
+    v.mul_(beta2).addcmul_(g, g, value=1 - beta2)
+    bc1 = 1 - beta1**step
+    bc2 = 1 - beta2**step
+    denom = v.sqrt() / (bc2**0.5) + eps
+    p.addcdiv_(m, denom, value=-lr / bc1)
+
+
+def sparse_grad_adam(
+    groups: FeatureGroups,
+    act,
+    dact,
+    x,
+    dxhat,
+    WD,
+    mD,
+    vD,
+    WD_bf16,
+    WE,
+    mE,
+    vE,
+    WE_bf16,
+    bE,
+    mbE,
+    vbE,
+    dec_norm,
+    grad_mul,
+    grad_sq_sum,
+    lr,
+    beta1,
+    beta2,
+    eps,
+    step,
+    update=True,
+):
+    """Rebuild the two sparse gradient rows per feature and apply Adam in the same pass (in place)."""
+    if not WD.is_cuda:
+        idx_like = torch.full((act.numel(),), -1, dtype=torch.int64)
+        off = groups.offsets.long()
+        for f in range(groups.F):
+            idx_like[groups.entries[off[f] : off[f + 1]].long()] = f
+        gD, gE, gb = ref_sparse_grads(idx_like.reshape(act.shape), act, dact, x, dxhat, groups.F)
+        mul = float(grad_mul) if grad_mul is not None else 1.0
+        gD, gE, gb = gD * mul, gE * mul, gb * mul
+        if grad_sq_sum is not None:
+            grad_sq_sum += gD.pow(2).sum() + gE.pow(2).sum() + gb.pow(2).sum()
+        if update:
+            ref_adam(WD, gD, mD, vD, lr, beta1, beta2, eps, step)
+            ref_adam(WE, gE, mE, vE, lr, beta1, beta2, eps, step)
+            if bE is not None:
+                ref_adam(bE, gb, mbE, vbE, lr, beta1, beta2, eps, step)
+            WD_bf16.copy_(WD)
+            WE_bf16.copy_(WE)
+            if dec_norm is not None:
+                dec_norm.copy_(WD.norm(dim=1))
+        return
+    _ext().sparse_grad_adam(
+        groups.offsets, groups.entries, act, dact, x, dxhat, WD, mD, vD, WD_bf16, WE, mE, vE, WE_bf16, bE, mbE, vbE,
+        dec_norm, grad_mul, grad_sq_sum, lr, beta1, beta2, eps, step, update,
+    )  # fmt: skip
+
+
+def colsum_bf16(a: torch.Tensor) -> torch.Tensor:
+    if not a.is_cuda:
+        return a.float().sum(0)
+    out = torch.empty(a.shape[1], dtype=torch.float32, device=a.device)
+    _ext().colsum_bf16(a, out)
+    return out
+
+
+def adam_flat(p, g, m, v, lr, beta1, beta2, eps, step, grad_mul=None, shadow=None, grad_sq_sum=None, update=True):
+    if not p.is_cuda:
+        gg = g * (float(grad_mul) if grad_mul is not None else 1.0)
+        if grad_sq_sum is not None:
+            grad_sq_sum += gg.pow(2).sum()
+        if update:
+            ref_adam(p, gg, m, v, lr, beta1, beta2, eps, step)
+            if shadow is not None:
+                shadow.copy_(p)
+        return
+    _ext().adam_flat(p, g, m, v, grad_mul, shadow, grad_sq_sum, lr, beta1, beta2, eps, step, update)
+
+
+def row_norm_shadow(W: torch.Tensor, norm: torch.Tensor | None, shadow: torch.Tensor | None) -> None:
+    """norm[f] = ||W[f,:]||_2 and shadow = bf16(W) in one pass."""
+    if not W.is_cuda:
+        if norm is not None:
+            norm.copy_(W.norm(dim=1))
+        if shadow is not None:
+            shadow.copy_(W)
+        return
+    _ext().row_norm_shadow(W, norm, shadow)

@@ -1,0 +1,178 @@
+"""Numerics of every sm_100a kernel against its plain PyTorch fp32 definition (ops/sae_kernels.py ref_*)."""
+
+import pytest
+import torch
+
+from language_model_saes_b200.ops import sae_kernels as K
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _mk(M, N, Kd, seed=0, scale=1.0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    x = (torch.randn(M, Kd, generator=g) * scale).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, Kd, generator=g) / Kd**0.5).to(torch.bfloat16).to(DEV)
+    b = (torch.randn(N, generator=g) * 0.1).to(DEV)
+    gate = (torch.rand(N, generator=g) + 0.5).to(DEV)
+    return x, w, b, gate
+
+
+@pytest.mark.parametrize("M,N,Kd", [(128, 256, 64), (256, 512, 128), (300, 1032, 200), (4096, 4096, 512), (77, 264, 72)])
+def test_encoder_hidden(M, N, Kd):
+    x, w, b, _ = _mk(M, N, Kd)
+    H = K.encoder_hidden(x, w, b)
+    K.check_status(x.device)
+    ref = K.ref_hidden(x, w, b)
+    err = (H.float() - ref).abs().max().item()
+    tol = 2e-2 * max(1.0, ref.abs().max().item())
+    assert err < tol, (err, tol)
+
+
+def _codes_to_dense(idx, val, N):
+    out = torch.zeros(idx.shape[0], N, device=idx.device)
+    m = idx >= 0
+    rows = torch.arange(idx.shape[0], device=idx.device).unsqueeze(1).expand_as(idx)
+    out[rows[m], idx[m].long()] = val[m]
+    return out
+
+
+@pytest.mark.parametrize("M,N,Kd,k", [(128, 512, 64, 8), (256, 2048, 128, 32), (300, 4104, 256, 50), (1024, 8192, 256, 64), (64, 264, 64, 1)])
+@pytest.mark.parametrize("use_gate", [False, True])
+def test_encoder_topk_fused(M, N, Kd, k, use_gate):
+    x, w, b, gate = _mk(M, N, Kd, seed=1)
+    gate = gate if use_gate else None
+    idx, act = K.encoder_topk(x, w, b, gate, k)
+    K.check_status(x.device)
+    h = K.ref_hidden(x, w, b)
+    g = h * gate if use_gate else h
+    g = torch.where(g > 0, g, torch.zeros_like(g))
+    kth = torch.topk(g, k, dim=-1).values[:, -1:]
+    # every selected entry must be >= the exact k-th largest (up to fp32 accumulation-order noise) and the
+    # selected activation must equal the reference pre-activation
+    dense = _codes_to_dense(idx, act, N)
+    sel = dense != 0
+    assert ((sel.sum(-1) == (g > 0).sum(-1).clamp(max=k))).all()
+    gsel = torch.where(sel, g, torch.full_like(g, float("inf")))
+    assert (gsel.min(-1).values >= kth.squeeze(-1) - 1e-3).all()
+    assert torch.allclose(dense[sel], h[sel], atol=2e-3, rtol=2e-3)
+    # no duplicates
+    srt = torch.sort(torch.where(idx >= 0, idx, torch.arange(-k, 0, device=DEV).expand_as(idx)), dim=-1).values
+    assert (srt[:, 1:] != srt[:, :-1]).all()
+
+
+@pytest.mark.parametrize("k", [16, 100, 512])
+def test_row_topk(k):
+    M, N = 64, 4096
+    g = torch.Generator().manual_seed(3)
+    H = torch.randn(M, N, generator=g).to(torch.bfloat16).to(DEV)
+    gate = (torch.rand(N, generator=g) + 0.5).to(DEV)
+    alive = (torch.rand(N, generator=g) > 0.3).to(DEV)
+    idx, val = K.row_topk(H, k, gate, alive)
+    ridx, rval = K.ref_topk_codes(H.float(), k, gate, alive)
+    d1 = _codes_to_dense(idx, val, N)
+    d2 = _codes_to_dense(ridx, rval, N)
+    # ties in bf16 inputs can swap equal values; compare the multiset of selected values
+    assert torch.allclose(torch.sort(d1, dim=-1).values, torch.sort(d2, dim=-1).values, atol=1e-5)
+
+
+def _codes(B, k, F, seed=5):
+    g = torch.Generator().manual_seed(seed)
+    idx = torch.stack([torch.randperm(F, generator=g)[:k] for _ in range(B)]).to(torch.int32)
+    idx[0, -1] = -1
+    val = torch.rand(B, k, generator=g) + 0.1
+    val[0, -1] = 0
+    return idx.to(DEV), val.to(DEV)
+
+
+@pytest.mark.parametrize("B,k,F,d", [(33, 7, 300, 64), (128, 50, 2048, 4096), (16, 64, 512, 776)])
+def test_sparse_decode_and_loss(B, k, F, d):
+    idx, val = _codes(B, k, F)
+    g = torch.Generator().manual_seed(7)
+    W = (torch.randn(F, d, generator=g) / d**0.5).to(torch.bfloat16).to(DEV)
+    bias = torch.randn(d, generator=g).to(DEV) * 0.1
+    label = torch.randn(B, d, generator=g).to(torch.bfloat16).to(DEV)
+    rw = (torch.rand(B, generator=g) > 0.2).float().to(DEV)
+    out = K.sparse_decode(idx, val, W, bias)
+    ref = K.ref_sparse_decode(idx, val, W, bias)
+    assert torch.allclose(out, ref, atol=1e-4, rtol=1e-4)
+    out16 = K.sparse_decode(idx, val, W, bias, torch.bfloat16)
+    assert torch.allclose(out16.float(), ref, atol=2e-2, rtol=2e-2)
+
+    loss = torch.zeros(1, device=DEV)
+    row_loss = torch.empty(B, device=DEV)
+    gs = 2.0 / B
+    dx, dval, xh = K.sparse_decode_loss(idx, val, W, bias, label, rw, gs, loss, True, True, row_loss)
+    rxh, rdx, rls, rrl, rdv = K.ref_decode_loss(idx, val, W, bias, label, rw, gs)
+    assert torch.allclose(xh, rxh, atol=1e-4, rtol=1e-4)
+    assert torch.allclose(dx.float(), rdx.float(), atol=1e-3, rtol=2e-2)
+    assert torch.allclose(loss[0], rls, rtol=1e-4)
+    assert torch.allclose(row_loss, rrl, rtol=1e-4, atol=1e-4)
+    assert torch.allclose(dval, rdv, atol=2e-3, rtol=2e-2)
+    dv2 = K.sparse_dact(idx, W, dx)
+    assert torch.allclose(dv2, dval, atol=1e-4, rtol=1e-3)
+
+    # dense-row loss kernel (feature-sharded path)
+    loss2 = torch.zeros(1, device=DEV)
+    dx2 = K.mse_loss_grad(K.sparse_decode(idx, val, W, None), label, bias, rw, gs, loss2)
+    assert torch.allclose(dx2.float(), rdx.float(), atol=1e-3, rtol=2e-2)
+    assert torch.allclose(loss2[0], rls, rtol=1e-4)
+
+
+@pytest.mark.parametrize("B,k,F,d", [(64, 8, 256, 128), (512, 50, 4096, 1024), (100, 3, 1000, 4096)])
+def test_sparse_grad_adam(B, k, F, d):
+    idx, act = _codes(B, k, F, seed=11)
+    g = torch.Generator().manual_seed(13)
+    dact = torch.randn(B, k, generator=g).to(DEV)
+    dact[idx < 0] = 0
+    x = torch.randn(B, d, generator=g).to(torch.bfloat16).to(DEV)
+    dxhat = (torch.randn(B, d, generator=g) * 0.01).to(torch.bfloat16).to(DEV)
+    WD = torch.randn(F, d, generator=g).to(DEV)
+    WE = torch.randn(F, d, generator=g).to(DEV)
+    bE = torch.randn(F, generator=g).to(DEV)
+    st = [torch.rand(F, d, generator=g).to(DEV) * 0.01 for _ in range(4)]
+    sb = [torch.rand(F, generator=g).to(DEV) * 0.01 for _ in range(2)]
+    ref = [t.clone() for t in (WD, st[0], st[1], WE, st[2], st[3], bE, sb[0], sb[1])]
+    groups = K.FeatureGroups(F, B * k, torch.device(DEV)).build(idx)
+    off = groups.offsets.cpu()
+    cnt = torch.bincount(idx[idx >= 0].long().cpu(), minlength=F)
+    assert torch.equal(off[1:] - off[:-1], cnt.to(torch.int32))
+    ent = groups.entries[: int(off[-1])].long()
+    assert torch.equal(torch.sort(ent).values, torch.sort(torch.nonzero(idx.reshape(-1) >= 0).squeeze(1)).values)
+    assert (idx.reshape(-1)[ent].cpu() == torch.repeat_interleave(torch.arange(F), cnt)).all()
+
+    WDb = torch.empty(F, d, dtype=torch.bfloat16, device=DEV)
+    WEb = torch.empty(F, d, dtype=torch.bfloat16, device=DEV)
+    dn = torch.empty(F, device=DEV)
+    gsq = torch.zeros(1, device=DEV)
+    hp = dict(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, step=3)
+    K.sparse_grad_adam(groups, act, dact, x, dxhat, WD, st[0], st[1], WDb, WE, st[2], st[3], WEb, bE, sb[0], sb[1], dn, None, gsq, **hp)
+    gD, gE, gb = K.ref_sparse_grads(idx, act, dact, x, dxhat, F)
+    K.ref_adam(ref[0], gD, ref[1], ref[2], **hp)
+    K.ref_adam(ref[3], gE, ref[4], ref[5], **hp)
+    K.ref_adam(ref[6], gb, ref[7], ref[8], **hp)
+    for got, want in zip((WD, st[0], st[1], WE, st[2], st[3], bE, sb[0], sb[1]), ref):
+        assert torch.allclose(got, want, atol=1e-5, rtol=1e-4)
+    assert torch.allclose(WDb.float(), WD, atol=1e-2, rtol=1e-2)
+    assert torch.allclose(dn, WD.norm(dim=1), rtol=1e-4)
+    want_sq = gD.pow(2).sum() + gE.pow(2).sum() + gb.pow(2).sum()
+    assert torch.allclose(gsq[0], want_sq, rtol=1e-3)
+
+
+def test_dense_helpers():
+    g = torch.Generator().manual_seed(17)
+    a = torch.randn(300, 520, generator=g).to(torch.bfloat16).to(DEV)
+    assert torch.allclose(K.colsum_bf16(a), a.float().sum(0), atol=1e-3, rtol=1e-4)
+    p = torch.randn(1000, generator=g).to(DEV)
+    gr = torch.randn(1000, generator=g).to(DEV)
+    m = torch.zeros(1000, device=DEV)
+    v = torch.zeros(1000, device=DEV)
+    rp, rm, rv = p.clone(), m.clone(), v.clone()
+    K.adam_flat(p, gr, m, v, 1e-2, 0.9, 0.999, 1e-8, 1)
+    K.ref_adam(rp, gr, rm, rv, 1e-2, 0.9, 0.999, 1e-8, 1)
+    assert torch.allclose(p, rp, atol=1e-5) and torch.allclose(m, rm, rtol=1e-4) and torch.allclose(v, rv, rtol=1e-4)
+    W = torch.randn(77, 130, generator=g).to(DEV)
+    n = torch.empty(77, device=DEV)
+    sh = torch.empty(77, 130, dtype=torch.bfloat16, device=DEV)
+    K.row_norm_shadow(W, n, sh)
+    assert torch.allclose(n, W.norm(dim=1), rtol=1e-5) and torch.equal(sh, W.to(torch.bfloat16))
