@@ -1,0 +1,228 @@
+"""Headline benchmark: SAE training tokens/s, d_model 4096 x d_sae 131072 TopK(k=50), batch 4096, bf16 compute.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+One rank per GPU (launched through torch.distributed.run for N > 1); the dictionary is feature-sharded N ways
+("model" mesh dimension) and the global batch stays 4096 tokens, so scaling is strong. Prints ONE JSON line on
+rank 0. ``value`` is the device-timed training throughput (CUDA events around exactly K steps, max over
+ranks, inputs rotated through a pool of device batches larger than L2); ``e2e`` is the same metric measured
+through the public ``Trainer.fit`` call with every step's batch copied from pinned host memory and the loss
+read back to the host each step.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+D_MODEL, EXPANSION, TOP_K, BATCH, LR = 4096, 32, 50, 4096, 2e-4
+POOL = 8  # distinct synthetic batches: 8 x 32 MiB bf16 = 256 MiB > 126 MB L2
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of this rank's GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.rows: list[list[str]] = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+            )  # fmt: skip
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        assert self.proc is not None and self.proc.stdout is not None
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        rows = [r for r in self.rows if len(r) >= 7 and r[0].replace(".", "").isdigit()]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        busy = [r for r in rows if float(r[2] or 0) > 300] or rows
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[3 + i].lower().startswith("active") for r in rows)]
+        return {
+            "sm_mhz": statistics.median(float(r[0]) for r in busy),
+            "sm_max_mhz": float(rows[0][1]),
+            "power_w_max": max(float(r[2] or 0) for r in rows),
+            "samples": len(rows),
+            "reasons": reasons,
+        }
+
+
+def synthetic_batches(n: int, seed: int = 1234):
+    """x = z A + eps with z ~ N(0, I_256), A a seeded 256 x 4096 Gaussian, eps ~ N(0, 0.1^2), rescaled to a mean
+    norm of sqrt(4096); bf16, pinned host memory. Every rank generates the same batches."""
+    import torch
+
+    g = torch.Generator().manual_seed(seed)
+    A = torch.randn(256, D_MODEL, generator=g)
+    out = []
+    for _ in range(n):
+        z = torch.randn(BATCH, 256, generator=g)
+        x = z @ A + 0.1 * torch.randn(BATCH, D_MODEL, generator=g)
+        x = x * (D_MODEL**0.5 / x.norm(dim=-1).mean())
+        out.append(x.to(torch.bfloat16).pin_memory())
+    return out
+
+
+def emit(rec: dict):
+    print(json.dumps(rec), flush=True)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    import language_model_saes_b200 as lm
+    from language_model_saes_b200.models.sae import SAEConfig, SparseAutoEncoder
+    from language_model_saes_b200.ops import sae_kernels as K
+    from language_model_saes_b200.ops.fused_step import FusedTopKSAEStep
+    from language_model_saes_b200.trainer import Trainer, TrainerConfig
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    mesh = None
+    if world > 1:
+        from language_model_saes_b200.parallel.mesh import build_mesh
+
+        dist.init_process_group("nccl", device_id=dev)
+        mesh = build_mesh("cuda", (1, world), ("data", "model"))
+
+    torch.manual_seed(0)
+    cfg = SAEConfig(hook_point_in="blocks.16.hook_resid_post", hook_point_out="blocks.16.hook_resid_post",
+                    d_model=D_MODEL, expansion_factor=EXPANSION, act_fn="topk", top_k=TOP_K,
+                    device=f"cuda:{local}", dtype=torch.float32)  # fmt: skip
+    sae = SparseAutoEncoder(cfg, mesh)
+    bound = 1.0 / D_MODEL**0.5
+    sae.init_parameters(encoder_uniform_bound=bound, decoder_uniform_bound=bound)
+    sae.set_decoder_to_fixed_norm(1.0, force_exact=True)
+    sae.init_encoder_with_decoder_transpose()
+    sae.set_dataset_average_activation_norm({cfg.hook_point_in: D_MODEL**0.5})
+
+    host = synthetic_batches(POOL)
+    tokens = torch.zeros(BATCH, dtype=torch.long)
+    W, Ksteps = args.warmup, args.steps
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-timed kernel path --------------------------------------------------------------------
+    engine = FusedTopKSAEStep(sae, betas=(0.9, 0.999))
+    pool = [h.to(dev) for h in host]
+    for i in range(W):
+        engine.step(pool[i % POOL], pool[i % POOL], TOP_K, LR)
+    K.check_status(dev)
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    launches0 = K.kernel_launch_count()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(Ksteps):
+        loss = engine.step(pool[(W + i) % POOL], pool[(W + i) % POOL], TOP_K, LR)
+    end.record()
+    barrier()
+    launches = K.kernel_launch_count() - launches0
+    clocks = sampler.stop()
+    ms = start.elapsed_time(end)
+    K.check_status(dev)
+    final_loss = float(loss)
+    del engine, pool
+    torch.cuda.empty_cache()
+
+    # ---- end to end through Trainer.fit --------------------------------------------------------------
+    marks: dict[str, float] = {}
+
+    def stream():
+        for i in range(W + Ksteps + 1):
+            if i == W:
+                barrier()
+                marks["t0"] = time.perf_counter()
+            yield {cfg.hook_point_in: host[i % POOL], "tokens": tokens}
+
+    with tempfile.TemporaryDirectory() as tmp:
+        tcfg = TrainerConfig(total_training_tokens=(W + Ksteps) * BATCH, lr=LR, lr_warm_up_steps=0, lr_cool_down_steps=0,
+                             lr_scheduler_name="constant", log_frequency=1, skip_metrics_calculation=True,
+                             n_checkpoints=0, exp_result_path=tmp, k_warmup_steps=0, l1_coefficient=None)  # fmt: skip
+        trainer = Trainer(tcfg)
+        trainer.fit(sae, stream())
+        barrier()
+        marks["t1"] = time.perf_counter()
+    e2e_s = marks["t1"] - marks["t0"]
+
+    t = torch.tensor([ms, e2e_s * 1e3], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = t.tolist()
+    if rank == 0:
+        value = Ksteps * BATCH / (ms / 1e3)
+        emit({
+            "metric": "SAE train tokens/s (d4096 x 131072 TopK k50)", "value": value, "unit": "tokens/s",
+            "n_gpus": world, "steps": Ksteps, "warmup": W, "ms_per_step": ms / Ksteps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"model": "TopK SAE d_model 4096, d_sae 131072, k 50, Adam lr 2e-4, fp32 master weights + bf16 compute",
+                       "global_batch": BATCH, "seq_len": 1, "parallelism": f"tp{world}",
+                       "l2": f"inputs rotate through {POOL} batches (256 MiB) > L2; weights 2 x 2.1 GB"},
+            "clocks": clocks,
+            "e2e": {"value": Ksteps * BATCH / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms / Ksteps,
+                    "h2d_bytes_per_step": BATCH * D_MODEL * 2 + BATCH * 8, "d2h_bytes_per_step": 4,
+                    "api": "Trainer.fit(sae, stream of pinned host batches), loss read back every step"},
+            "gpu_launches": launches, "final_loss": final_loss, "impl": "ours", "package": lm.__name__,
+        })  # fmt: skip
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        from baseline.reference_arm import run_reference
+
+        run_reference(args, emit, synthetic_batches, ClockSampler,
+                      dict(d_model=D_MODEL, expansion=EXPANSION, top_k=TOP_K, batch=BATCH, lr=LR, pool=POOL))
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

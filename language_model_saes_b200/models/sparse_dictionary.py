@@ -419,6 +419,278 @@ class SparseDictionary(HookedRootModule, ABC):
                               fold_activation_scale=fold_activation_scale, **kwargs)  # fmt: skip
 
 
+    # ---- activation normalisation ------------------------------------------------------------
+    def compute_norm_factor(self, x: torch.Tensor, hook_point: str) -> torch.Tensor:
+        """Scale that brings activations to an average norm of sqrt(d_model) under the configured mode."""
+        mode = self.cfg.norm_activation
+        root = math.sqrt(self.cfg.d_model)
+        if mode == "token-wise":
+            return root / torch.norm(x, 2, dim=-1, keepdim=True)
+        if mode == "batch-wise":
+            return root / torch.norm(x, 2, dim=-1, keepdim=True).mean(dim=-2, keepdim=True)
+        if mode == "dataset-wise":
+            assert self.dataset_average_activation_norm is not None, (
+                "dataset_average_activation_norm must be provided from Initializer"
+            )
+            return torch.tensor(root / self.dataset_average_activation_norm[hook_point], device=x.device, dtype=x.dtype)
+        if mode == "inference":
+            return torch.tensor(1.0, device=x.device, dtype=x.dtype)
+        raise ValueError(f"Not implemented norm_activation {mode}")
+
+    @timer.time("normalize_activations")
+    def normalize_activations(self, batch: dict[str, torch.Tensor], *, return_scale_factor: bool = False):
+        hooks = set(self.cfg.associated_hook_points)
+        scale = {k: self.compute_norm_factor(v, hook_point=k) for k, v in batch.items() if k in hooks}
+        out = {k: (v * scale[k] if k in hooks else v) for k, v in batch.items()}
+        return (out, scale) if return_scale_factor else out
+
+    def denormalize_activations(self, batch: dict[str, torch.Tensor], scale_factors: dict[str, torch.Tensor]):
+        return {k: v / scale_factors[k] for k, v in batch.items()}
+
+    # ---- optimisation helpers ----------------------------------------------------------------
+    def get_parameters(self) -> list[dict[str, Any]]:
+        """Two parameter groups: ``jumprelu`` (threshold, own learning-rate factor) and ``others``."""
+        jr = list(self.activation_function.parameters()) if isinstance(self.activation_function, JumpReLU) else []
+        jr_ids = {id(p) for p in jr}
+        others = [p for p in self.parameters() if id(p) not in jr_ids]
+        return [{"params": others, "name": "others"}, {"params": jr, "name": "jumprelu"}]
+
+    @torch.no_grad()
+    def log_statistics(self) -> dict[str, Any]:
+        out: dict[str, Any] = {}
+        if isinstance(self, NormComputing):
+            out["metrics/encoder_norm"] = self._mean_over_shards(self.encoder_norm())
+            out["metrics/decoder_norm"] = self._mean_over_shards(self.decoder_norm())
+            if self.cfg.use_decoder_bias:
+                out["metrics/decoder_bias_norm"] = float(self.decoder_bias_norm().mean())
+        if "topk" in self.cfg.act_fn:
+            out["sparsity/k"] = self.current_k
+        if isinstance(self.activation_function, JumpReLU):
+            out["metrics/mean_jumprelu_threshold"] = self._mean_over_shards(
+                self.activation_function.log_jumprelu_threshold.exp()
+            )
+        return out
+
+    def _mean_over_shards(self, t: torch.Tensor) -> float:
+        """Mean of a per-feature quantity whose feature axis may be sharded over ``model``."""
+        s = torch.stack([t.float().sum(), torch.tensor(float(t.numel()), device=t.device)])
+        if self.tp_size > 1:
+            dist.all_reduce(s, group=self.tp_group)
+        return float(s[0] / s[1])
+
+    # ---- activation functions ----------------------------------------------------------------
+    def activation_function_factory(self, device_mesh: DeviceMesh | None = None):
+        """relu | jumprelu | topk | batchtopk on (possibly feature-sharded) pre-activations.
+
+        Single-process TopK applies ReLU first and keeps exactly k entries; under feature sharding the global
+        k-th value is found with one candidate all-gather. BatchTopK keeps the ``k * batch`` largest entries
+        of the whole (local-batch x full-feature) matrix.
+        """
+        act = self.cfg.act_fn.lower()
+        assert act in ("relu", "topk", "jumprelu", "batchtopk"), f"Not implemented activation function {act}"
+        if act == "relu":
+            return lambda x: x * x.gt(0).to(x.dtype)
+        if act == "jumprelu":
+            return JumpReLU(
+                self.cfg.jumprelu_threshold_window, shape=(self.cfg.d_sae,), device=self.cfg.device,
+                dtype=self.cfg.dtype, device_mesh=device_mesh,
+            )  # fmt: skip
+        if act == "topk":
+
+            def topk_activation(x: torch.Tensor):
+                if self.tp_size > 1:
+                    return distributed_topk(x, self.current_k, self.tp_group, dim=-1)
+                x = x * x.gt(0).to(x.dtype)
+                return topk(x, k=min(self.current_k, x.shape[-1]), dim=-1)
+
+            return topk_activation
+
+        def batch_topk(x: torch.Tensor):
+            x = x * x.gt(0).to(x.dtype)
+            shape = x.shape
+            if x.ndim == 3:
+                x = x.flatten(end_dim=1)
+            k_total = self.current_k * x.size(0)
+            if self.tp_size > 1:
+                out = distributed_topk(x, k_total, self.tp_group, dim=(-2, -1))
+            else:
+                out = topk(x, k=min(k_total, x.numel()), dim=(-2, -1), abs=True)
+            return out.reshape(shape)
+
+        return batch_topk
+
+    @torch.no_grad()
+    def init_parameters(self, **kwargs):
+        if isinstance(self.activation_function, JumpReLU):
+            self.activation_function.log_jumprelu_threshold.data.fill_(kwargs["init_log_jumprelu_threshold_value"])
+
+    # ---- abstract model interface ------------------------------------------------------------
+    @abstractmethod
+    def encode(self, x: torch.Tensor, return_hidden_pre: bool = False, **kwargs): ...
+
+    @abstractmethod
+    def decode(self, feature_acts: torch.Tensor, **kwargs) -> torch.Tensor: ...
+
+    @timer.time("forward")
+    def forward(self, x: torch.Tensor, encoder_kwargs: dict[str, Any] = {}, decoder_kwargs: dict[str, Any] = {}):
+        return self.decode(self.encode(x, **encoder_kwargs), **decoder_kwargs)
+
+    @abstractmethod
+    def prepare_input(self, batch: dict[str, torch.Tensor], **kwargs) -> tuple[torch.Tensor, dict[str, Any], dict[str, Any]]: ...
+
+    @abstractmethod
+    def prepare_label(self, batch: dict[str, torch.Tensor], **kwargs) -> torch.Tensor: ...
+
+    @torch.no_grad()
+    def compute_training_metrics(self, **kwargs) -> dict[str, float]:
+        return {}
+
+    def dim_maps(self) -> dict[str, DimMap]:
+        maps: dict[str, DimMap] = {}
+        if isinstance(self.activation_function, JumpReLU):
+            maps.update({f"activation_function.{k}": v for k, v in self.activation_function.dim_maps().items()})
+        return maps
+
+    def override_dtypes(self) -> dict[str, torch.dtype]:
+        if isinstance(self.activation_function, JumpReLU):
+            return {f"activation_function.{k}": v for k, v in self.activation_function.override_dtypes().items()}
+        return {}
+
+    def _sum_over_features(self, t: torch.Tensor) -> torch.Tensor:
+        """Finish a sum over the (sharded) feature axis: adds the other shards' partial sums."""
+        if self.tp_size > 1:
+            from ..parallel.collectives import all_reduce_sum
+
+            return all_reduce_sum(t, self.tp_group)
+        return t
+
+    # ---- loss --------------------------------------------------------------------------------
+    @timer.time("compute_loss")
+    def compute_loss(
+        self,
+        batch: dict[str, torch.Tensor],
+        label: torch.Tensor | None = None,
+        *,
+        sparsity_loss_type: Literal["power", "tanh", "tanh-quad", None] = None,
+        tanh_stretch_coefficient: float = 4.0,
+        frequency_scale: float = 0.01,
+        p: int = 1,
+        l1_coefficient: float = 1.0,
+        lp_coefficient: float = 0.0,
+        auxk_coefficient: float = 0.0,
+        k_aux: int = 512,
+        update_dead_statistics: Callable[[torch.Tensor, torch.Tensor | None, tuple[str, ...]], torch.Tensor] | None = None,
+        return_aux_data: bool = True,
+        **kwargs,
+    ):
+        """Reconstruction MSE (sum over d_model, mean over tokens) plus the optional sparsity, JumpReLU-Lp and
+        Aux-K terms. Inputs must already be normalised. Under feature sharding ``feature_acts`` and
+        ``hidden_pre`` are local shards and per-token sums over features are completed across shards; under
+        data parallelism the returned loss is the mean over this rank's tokens."""
+        x, encoder_kwargs, decoder_kwargs = self.prepare_input(batch)
+        label = self.prepare_label(batch, **kwargs)
+        mask = batch.get("mask")
+
+        with timer.time("encode"):
+            feature_acts, hidden_pre = self.encode(x, return_hidden_pre=True, **encoder_kwargs)
+        with timer.time("decode"):
+            reconstructed = self.decode(feature_acts, **decoder_kwargs)
+
+        with timer.time("loss_calculation"):
+            l_rec = (reconstructed - label).pow(2).sum(dim=-1)
+            l_rec, _ = apply_token_mask(l_rec, self.specs.loss(l_rec), mask, "mean")
+            loss_dict: dict[str, torch.Tensor | None] = {"l_rec": l_rec}
+            loss = l_rec
+
+            if sparsity_loss_type is not None:
+                assert isinstance(self, NormComputing), "NormComputing is required for sparsity loss computation"
+                gated = feature_acts * self.decoder_norm()
+                if sparsity_loss_type == "power":
+                    if p == 1:
+                        l_s = self._sum_over_features(gated.abs().sum(dim=-1))
+                    else:
+                        l_s = self._sum_over_features(gated.abs().pow(p).sum(dim=-1)).pow(1.0 / p)
+                elif sparsity_loss_type == "tanh":
+                    l_s = self._sum_over_features(torch.tanh(tanh_stretch_coefficient * gated).sum(dim=-1))
+                elif sparsity_loss_type == "tanh-quad":
+                    score = torch.tanh(tanh_stretch_coefficient * gated)
+                    freq = score.reshape(-1, score.shape[-1]).mean(dim=0)
+                    if self.dp_size > 1:
+                        from ..parallel.collectives import all_reduce_sum
+
+                        freq = all_reduce_sum(freq, self.dp_group) / self.dp_size
+                    l_s = self._sum_over_features((freq * (1 + freq / frequency_scale)).sum(dim=-1))
+                else:
+                    raise ValueError(f"sparsity_loss_type {sparsity_loss_type} not supported.")
+                l_s = l1_coefficient * l_s
+                loss_dict["l_s"] = l_s
+                if l_s.ndim > 0:
+                    l_s, _ = apply_token_mask(l_s, self.specs.loss(l_s), mask, "mean")
+                loss = loss + l_s
+            else:
+                loss_dict["l_s"] = None
+
+            if lp_coefficient > 0.0 and isinstance(self.activation_function, JumpReLU):
+                assert isinstance(self, NormComputing), "NormComputing is required for Lp loss computation"
+                thr = self.activation_function.get_jumprelu_threshold()
+                l_p = torch.nn.functional.relu(thr - hidden_pre) * self.decoder_norm()
+                l_p = lp_coefficient * self._sum_over_features(l_p.sum(dim=-1))
+                l_p, _ = apply_token_mask(l_p, self.specs.loss(l_p), mask, "mean")
+                loss_dict["l_p"] = l_p
+                loss = loss + l_p
+            else:
+                loss_dict["l_p"] = None
+
+            if auxk_coefficient > 0.0:
+                assert update_dead_statistics is not None, "update_dead_statistics must be set when auxk_coefficient > 0.0"
+                is_dead = update_dead_statistics(feature_acts, mask, self.specs.feature_acts(feature_acts))
+                e = label - reconstructed
+                saved_k = self.current_k
+                n_dead = is_dead.sum()
+                if self.tp_size > 1:
+                    n_dead = n_dead.clone()
+                    dist.all_reduce(n_dead, group=self.tp_group)
+                self.current_k = min(k_aux, int(n_dead))
+                if self.current_k > 0:
+                    gate = self.decoder_norm() if self.cfg.sparsity_include_decoder_norm else None  # type: ignore[attr-defined]
+                    dead_pre = hidden_pre * is_dead.to(hidden_pre.dtype)
+                    if gate is not None:
+                        dead_pre = dead_pre * gate
+                    dead_acts = self.activation_function(dead_pre)
+                    if gate is not None:
+                        dead_acts = dead_acts / gate
+                    aux_rec = self._sum_over_features(self._decode_linear(dead_acts))
+                    l_aux = auxk_coefficient * (e - aux_rec).pow(2).sum(dim=-1)
+                    l_aux, _ = apply_token_mask(l_aux, self.specs.loss(l_aux), mask, "mean")
+                    loss_dict["l_aux"] = l_aux
+                    loss = loss + l_aux
+                else:
+                    loss_dict["l_aux"] = torch.zeros_like(l_rec)
+                self.current_k = saved_k
+
+        if not return_aux_data:
+            return loss
+        n_tokens = batch["tokens"].numel() if mask is None else int(mask.sum())
+        return {
+            "loss": loss,
+            **loss_dict,
+            "label": label,
+            "mask": mask,
+            "n_tokens": n_tokens,
+            "feature_acts": feature_acts,
+            "reconstructed": reconstructed,
+            "hidden_pre": hidden_pre,
+            "l1_coefficient": l1_coefficient,
+            "lp_coefficient": lp_coefficient,
+            "auxk_coefficient": auxk_coefficient,
+        }
+
+    def _decode_linear(self, feature_acts: torch.Tensor) -> torch.Tensor:
+        """``feature_acts @ W_D`` on the local shard, without bias, hooks or cross-shard reduction
+        (the Aux-K reconstruction of models/sparse_dictionary.py:975 in the reference)."""
+        return feature_acts @ self.W_D  # type: ignore[attr-defined]
+
+
 def _find_checkpoint(path: str) -> str:
     """Weights file for a checkpoint directory, in the reference's priority order."""
     if path.endswith((".pt", ".safetensors", ".dcp")):

@@ -1,0 +1,219 @@
+"""One training step of a TopK sparse autoencoder as a fixed sequence of sm_100a kernels, without autograd.
+
+What it computes is the reference's step for a TopK ``SparseAutoEncoder`` trained with the MSE loss and Adam
+(trainer.py:576-671, models/sae.py:288-377, models/sparse_dictionary.py:841-886 of the reference project):
+encode, per-token top-k of the decoder-norm-gated pre-activations, decode, mean-over-tokens of the summed
+squared error, backward, Adam. How it computes it:
+
+1. encoder GEMM (tcgen05) with the top-k epilogue        -> candidates per row and column range
+2. candidate merge (+ one exchange between feature shards) -> sparse codes (idx, act) [B, k]
+3. sparse decode fused with loss, d x_hat and d act        -> no dense [B, F] tensor exists at any point
+4. counting sort of the codes by feature
+5. per feature row: rebuild the sparse gradient rows of W_D and W_E^T in registers and apply Adam, refresh
+   the bf16 shadows and the decoder row norms                -> no dense gradient tensor exists either
+
+Parallel layouts: ``model`` (features sharded; candidates are exchanged and the partial reconstructions
+summed) and ``data`` (batch sharded; instead of all-reducing dense gradients of size 2*d*F, ranks exchange
+their rows of x, d x_hat and the sparse codes, which is all the gradient depends on, and every replica
+rebuilds the identical full-batch gradient).
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..parallel.mesh import mesh_dim_size, mesh_group, mesh_local_rank
+from . import sae_kernels as K
+
+
+class FusedTopKSAEStep:
+    def __init__(self, sae, betas: tuple[float, float] = (0.9, 0.999), eps: float = 1e-8, comm=None):
+        cfg = sae.cfg
+        self.sae = sae
+        self.mesh = sae.device_mesh
+        self.tp = mesh_dim_size(self.mesh, "model")
+        self.dp = mesh_dim_size(self.mesh, "data")
+        self.tp_rank = mesh_local_rank(self.mesh, "model")
+        self.tp_group = mesh_group(self.mesh, "model")
+        self.dp_group = mesh_group(self.mesh, "data")
+        self.comm = comm  # optional peer-memory communicator (parallel.symm.SymmComm) for the model group
+        self.betas, self.eps = betas, eps
+        self.use_gate = cfg.sparsity_include_decoder_norm
+        self.WE = sae.W_E.data.t()
+        self.WD = sae.W_D.data
+        assert self.WE.is_contiguous() and self.WD.is_contiguous(), "weights must be feature-major and contiguous"
+        assert self.WE.dtype == torch.float32, "the fused step keeps fp32 master weights"
+        self.bE = sae.b_E.data
+        self.bD = sae.b_D.data if cfg.use_decoder_bias else None
+        F, d = self.WD.shape
+        self.F, self.d = F, d
+        dev = self.WD.device
+        z = lambda *s: torch.zeros(*s, dtype=torch.float32, device=dev)  # noqa: E731
+        self.WE_bf16 = torch.empty(F, d, dtype=torch.bfloat16, device=dev)
+        self.WD_bf16 = torch.empty(F, d, dtype=torch.bfloat16, device=dev)
+        self.dec_norm = torch.empty(F, dtype=torch.float32, device=dev)
+        self.state = {
+            "W_E": (z(F, d), z(F, d)), "W_D": (z(F, d), z(F, d)), "b_E": (z(F), z(F)),
+            "b_D": (z(d), z(d)) if self.bD is not None else None,
+        }  # fmt: skip
+        self.groups: K.FeatureGroups | None = None
+        self.loss_sum = z(1)
+        self.grad_sq = z(1)
+        self.t = 0
+        self.refresh()
+
+    # ---- bookkeeping -------------------------------------------------------------------------
+    @staticmethod
+    def supports(sae, trainer_cfg=None) -> tuple[bool, str]:
+        """Whether this model / training configuration can run on the fused path, and if not, why."""
+        from ..models.sae import SparseAutoEncoder
+
+        cfg = sae.cfg
+        checks = [
+            (type(sae) is SparseAutoEncoder, "model is not a plain SparseAutoEncoder"),
+            (cfg.act_fn == "topk", "activation is not topk"),
+            (not cfg.use_glu_encoder, "GLU encoder"),
+            (sae.W_D.is_cuda, "not on a CUDA device"),
+            (cfg.dtype == torch.float32, "parameters are not fp32"),
+            (cfg.d_model % 8 == 0 and sae.W_D.shape[0] % 8 == 0, "d_model / local d_sae not multiples of 8"),
+            (cfg.d_model <= 8192, "d_model > 8192"),
+            (not any(hp.fwd_hooks or hp.bwd_hooks for hp in sae.hook_points()), "hooks are attached"),
+            (mesh_dim_size(sae.device_mesh, "head") == 1 and mesh_dim_size(sae.device_mesh, "sweep") == 1, "head/sweep mesh"),
+        ]
+        if trainer_cfg is not None:
+            checks += [
+                (trainer_cfg.sparsity_loss_type is None, "sparsity loss"),
+                (not trainer_cfg.lp_coefficient, "lp loss"),
+                (not trainer_cfg.auxk_coefficient, "aux-k loss"),
+                (trainer_cfg.optimizer_class == "adam", "optimizer is not adam"),
+                (trainer_cfg.amp_dtype == torch.bfloat16, "amp dtype is not bf16"),
+                (trainer_cfg.gradient_accumulation_steps == 1, "gradient accumulation"),
+            ]
+        for ok, why in checks:
+            if not ok:
+                return False, why
+        return True, ""
+
+    def refresh(self) -> None:
+        """Re-derive bf16 shadows and decoder norms from the fp32 masters (after loading / editing weights)."""
+        K.row_norm_shadow(self.WD, self.dec_norm, self.WD_bf16)
+        K.row_norm_shadow(self.WE, None, self.WE_bf16)
+
+    def optimizer_state(self) -> dict:
+        """Adam state in logical parameter shapes (W_E as [d, F])."""
+        out = {"step": self.t}
+        for name, st in self.state.items():
+            if st is None:
+                continue
+            m, v = st
+            out[name] = {"exp_avg": m.t() if name == "W_E" else m, "exp_avg_sq": v.t() if name == "W_E" else v}
+        return out
+
+    def load_optimizer_state(self, sd: dict) -> None:
+        self.t = int(sd["step"])
+        for name, st in self.state.items():
+            if st is None or name not in sd:
+                continue
+            m, v = st
+            src_m, src_v = sd[name]["exp_avg"], sd[name]["exp_avg_sq"]
+            m.copy_(src_m.t() if name == "W_E" else src_m)
+            v.copy_(src_v.t() if name == "W_E" else src_v)
+
+    # ---- the step ----------------------------------------------------------------------------
+    def encode(self, x: torch.Tensor, k: int) -> tuple[torch.Tensor, torch.Tensor]:
+        """Sparse codes (idx, act) [B, k] of bf16 inputs ``x`` [B, d] over this rank's features; under
+        feature sharding only globally selected entries survive."""
+        gate = self.dec_norm if self.use_gate else None
+        if k <= 64:
+            cv, ci, _ = K.encoder_topk_candidates(x, self.WE_bf16, self.bE, gate, k)
+            if self.tp == 1:
+                return K.topk_merge(cv, ci, k, gate)
+            idx_l, g_l = K.topk_merge(cv, ci, k, gate, emit_gated=True)
+        else:
+            H = K.encoder_hidden(x, self.WE_bf16, self.bE)
+            idx_l, act_l = K.row_topk(H, k, gate, None)
+            if self.tp == 1:
+                return idx_l, act_l
+            g_l = act_l * gate[idx_l.clamp_min(0).long()] if gate is not None else act_l
+        if self.comm is not None:
+            all_g, all_i = self.comm.exchange_candidates(g_l, idx_l)
+        else:
+            B = x.shape[0]
+            all_g = torch.empty(self.tp, B, k, dtype=torch.float32, device=x.device)
+            all_i = torch.empty(self.tp, B, k, dtype=torch.int32, device=x.device)
+            dist.all_gather_into_tensor(all_g, g_l, group=self.tp_group)
+            dist.all_gather_into_tensor(all_i, idx_l, group=self.tp_group)
+            all_g = all_g.permute(1, 0, 2).reshape(B, self.tp * k).contiguous()
+            all_i = all_i.permute(1, 0, 2).reshape(B, self.tp * k).contiguous()
+        return K.topk_merge(all_g, all_i, k, gate, own=(self.tp_rank * k, (self.tp_rank + 1) * k))
+
+    def step(
+        self,
+        x: torch.Tensor,
+        label: torch.Tensor,
+        k: int,
+        lr: float,
+        row_weight: torch.Tensor | None = None,
+        n_tokens_global: int | None = None,
+        grad_mul: torch.Tensor | None = None,
+        want_grad_norm: bool = False,
+    ) -> torch.Tensor:
+        """Forward, backward and Adam update for one batch; returns the mean loss (0-d device tensor, local
+        batch). ``x`` / ``label``: normalised bf16 [B, d]; ``row_weight``: optional 0/1 token mask."""
+        B = x.shape[0]
+        n_global = n_tokens_global if n_tokens_global is not None else B * self.dp
+        grad_scale = 2.0 / n_global
+        idx, act = self.encode(x, k)
+        self.loss_sum.zero_()
+        if self.tp == 1:
+            dxhat, dact, _ = K.sparse_decode_loss(idx, act, self.WD_bf16, self.bD, label, row_weight, grad_scale, self.loss_sum)
+        else:
+            partial = K.sparse_decode(idx, act, self.WD_bf16, None, torch.float32)
+            if self.comm is not None:
+                partial = self.comm.all_reduce_rows(partial)
+            else:
+                dist.all_reduce(partial, group=self.tp_group)
+            dxhat = K.mse_loss_grad(partial, label, self.bD, row_weight, grad_scale, self.loss_sum)
+            dact = K.sparse_dact(idx, self.WD_bf16, dxhat)
+        if self.dp > 1:
+            x, dxhat, idx, act, dact = self._gather_rows(x, dxhat, idx, act, dact)
+        if self.groups is None or self.groups.entries.numel() < idx.numel():
+            self.groups = K.FeatureGroups(self.F, idx.numel(), x.device)
+        self.groups.build(idx)
+        self.t += 1
+        b1, b2 = self.betas
+        (mE, vE), (mD, vD), (mb, vb) = self.state["W_E"], self.state["W_D"], self.state["b_E"]
+        gsq = None
+        if want_grad_norm:
+            self.grad_sq.zero_()
+            gsq = self.grad_sq
+        K.sparse_grad_adam(
+            self.groups, act, dact, x, dxhat, self.WD, mD, vD, self.WD_bf16, self.WE, mE, vE, self.WE_bf16,
+            self.bE, mb, vb, self.dec_norm, grad_mul, gsq, lr, b1, b2, self.eps, self.t, True,
+        )  # fmt: skip
+        if self.bD is not None:
+            g_bD = K.colsum_bf16(dxhat)
+            m, v = self.state["b_D"]
+            K.adam_flat(self.bD, g_bD, m, v, lr, b1, b2, self.eps, self.t, grad_mul=grad_mul, grad_sq_sum=gsq)
+        n_local = B if row_weight is None else row_weight.sum()
+        return (self.loss_sum / n_local).squeeze(0)
+
+    def _gather_rows(self, *tensors: torch.Tensor) -> list[torch.Tensor]:
+        out = []
+        for t in tensors:
+            buf = torch.empty(self.dp * t.shape[0], *t.shape[1:], dtype=t.dtype, device=t.device)
+            dist.all_gather_into_tensor(buf, t.contiguous(), group=self.dp_group)
+            out.append(buf)
+        return out
+
+    @torch.no_grad()
+    def forward_dense(self, x: torch.Tensor, k: int):
+        """Codes and reconstruction for metric computation: (idx, act, x_hat fp32)."""
+        idx, act = self.encode(x, k)
+        xhat = K.sparse_decode(idx, act, self.WD_bf16, None, torch.float32)
+        if self.tp > 1:
+            dist.all_reduce(xhat, group=self.tp_group)
+        if self.bD is not None:
+            xhat = xhat + self.bD
+        return idx, act, xhat

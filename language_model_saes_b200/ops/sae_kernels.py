@@ -34,8 +34,40 @@ _STATUS_NAMES = {
 }
 
 
+class _Counting:
+    """Proxy of the extension module that counts the device kernels each entry point launches."""
+
+    KERNELS_PER_CALL = {"csc_build": 5}
+
+    def __init__(self, mod):
+        self._mod = mod
+        self.launches = 0
+
+    def __getattr__(self, name):
+        fn = getattr(self._mod, name)
+        n = self.KERNELS_PER_CALL.get(name, 1)
+
+        def call(*args, **kwargs):
+            self.launches += n
+            return fn(*args, **kwargs)
+
+        self.__dict__[name] = call
+        return call
+
+
+_counting: _Counting | None = None
+
+
 def _ext():
-    return native.load(required=True)
+    global _counting
+    if _counting is None:
+        _counting = _Counting(native.load(required=True))
+    return _counting
+
+
+def kernel_launch_count() -> int:
+    """Number of kernels of this package launched so far in this process."""
+    return _counting.launches if _counting is not None else 0
 
 
 def status_buffer(device: torch.device) -> torch.Tensor:

@@ -1,0 +1,642 @@
+"""Training loop.
+
+Configuration fields, schedules (k, l1 coefficient, learning rate), checkpoint layout and logged keys follow
+trainer.py of the reference project (TrainerConfig :51-125, checkpoints :155-307, initialisation :309-401,
+dead-feature statistics :403-454, step :456-510, logging :512-562, fit :576-671).
+
+Two execution paths share this loop:
+
+* the fused path (``ops.fused_step.FusedTopKSAEStep``) for TopK sparse autoencoders on CUDA: one fixed
+  sequence of hand-written kernels per step, no autograd graph, no dense [batch, d_sae] tensor;
+* the generic path for every other model / loss: autograd over the model's ``compute_loss``, gradients
+  averaged explicitly over the ``data`` mesh dimension, torch or SparseAdam optimizer.
+
+Neither path synchronises with the host inside a step: the progress-bar loss, token counts and metrics are read
+back only every ``log_frequency`` steps.
+"""
+
+from __future__ import annotations
+
+import json
+import math
+import os
+from pathlib import Path
+from typing import Any, Callable, Iterable, Literal, Tuple
+
+import torch
+import torch.distributed as dist
+from pydantic import ConfigDict, Field
+from torch import Tensor
+from torch.optim import Adam, Optimizer
+
+from .config import BaseConfig, OptionalTorchDType
+from .metrics import (
+    ExplainedVarianceMetric,
+    FrequencyMetric,
+    GradientNormMetric,
+    L0Metric,
+    L2NormErrorMetric,
+    LossMetric,
+    MeanFeatureActMetric,
+    Metric,
+    ModelSpecificMetric,
+)
+from .models.sparse_dictionary import SparseDictionary
+from .optim import SparseAdam, clip_grad_norm, get_scheduler
+from .parallel.data_parallel import reduce_gradients
+from .parallel.mesh import is_primary_rank, mesh_dim_size, mesh_group
+from .utils.logging import get_distributed_logger, log_metrics
+from .utils.tensor_specs import apply_token_mask
+from .utils.timer import timer
+
+logger = get_distributed_logger("trainer")
+
+
+class TrainerConfig(BaseConfig):
+    model_config = ConfigDict(arbitrary_types_allowed=True)
+
+    l1_coefficient: float | None = 0.00008
+    l1_coefficient_warmup_steps: int | float = 0.1
+    lp_coefficient: float | None = None
+    auxk_coefficient: float | None = None
+    amp_dtype: OptionalTorchDType = Field(default=torch.bfloat16, exclude=True, validate_default=False)
+    sparsity_loss_type: Literal["power", "tanh", "tanh-quad", None] = None
+    tanh_stretch_coefficient: float = 4.0
+    frequency_scale: float = 0.01
+    p: int = 1
+    initial_k: int | float | None = None
+    k_warmup_steps: int | float = 0.1
+    k_cold_booting_steps: int | float = 0
+    k_schedule_type: Literal["linear", "exponential"] = "linear"
+    k_exponential_factor: float = 3.0
+    k_aux: int = 512
+    dead_threshold: float = 10_000_000
+    skip_metrics_calculation: bool = False
+    gradient_accumulation_steps: int = 1
+
+    lr: float | dict[str, float] = 0.0004
+    betas: Tuple[float, float] = (0.9, 0.999)
+    optimizer_class: Literal["adam", "sparseadam"] = "adam"
+    optimizer_foreach: bool = True
+    lr_scheduler_name: Literal[
+        "constant", "constantwithwarmup", "linearwarmupdecay", "cosineannealing", "cosineannealingwarmup", "exponentialwarmup"
+    ] = "constantwithwarmup"
+    lr_end_ratio: float = 1 / 32
+    lr_warm_up_steps: int | float = 5000
+    lr_cool_down_steps: int | float = 0.2
+    jumprelu_lr_factor: float = 1.0
+    clip_grad_norm: float = 0.0
+    feature_sampling_window: int = 1000
+    total_training_tokens: int = 300_000_000
+
+    log_frequency: int = 1000
+    eval_frequency: int = 1000
+    n_checkpoints: int = 10
+    check_point_save_mode: Literal["log", "linear"] = "log"
+
+    from_pretrained_path: str | None = None
+    exp_result_path: str = "results"
+
+    use_fused_kernels: bool = True
+    """Run eligible models (TopK SAE, MSE loss, Adam, CUDA) on the fused kernel path."""
+
+    def model_post_init(self, __context):
+        super().model_post_init(__context)
+        Path(self.exp_result_path, "checkpoints").mkdir(parents=True, exist_ok=True)
+        assert self.lr_end_ratio <= 1, "lr_end_ratio must be in 0 to 1 (inclusive)."
+        if self.from_pretrained_path is not None:
+            assert os.path.exists(self.from_pretrained_path), f"from_pretrained_path {self.from_pretrained_path} does not exist"
+
+
+class WandbConfig(BaseConfig):
+    wandb_project: str = "gpt2-sae-training"
+    exp_name: str | None = None
+    wandb_entity: str | None = None
+    wandb_run_id: str | None = None
+    wandb_resume: Literal["allow", "must", "never", "auto"] = "never"
+
+
+class Trainer:
+    def __init__(self, cfg: TrainerConfig):
+        self.cfg = cfg
+        self.checkpoint_thresholds: list[int] = []
+        self.total_training_steps: int = 0
+        self.lr_warm_up_steps: int = 0
+        self.lr_cool_down_steps: int = 0
+        self.k_warmup_steps: int = 0
+        self.k_cold_booting_steps: int = 0
+        self.l1_coefficient_warmup_steps: int = 0
+        self.cur_step: int = 0
+        self.cur_tokens: int = 0
+        self.optimizer: Optimizer | None = None
+        self.scheduler = None
+        self.wandb_logger = None
+        self.metrics: list[Metric] = []
+        self.tokens_since_last_activation: Tensor | None = None
+        self.is_dead: Tensor | None = None
+        self.fused = None  # FusedTopKSAEStep when the fused path is active
+        self._lr_lambda: Callable[[int], float] | None = None
+        self._pending_optimizer_state: dict | None = None
+        self._interval: dict[str, Any] = {}
+
+    # ---- checkpoints -------------------------------------------------------------------------
+    def save_checkpoint(self, sae: SparseDictionary, checkpoint_path: Path | str) -> None:
+        """Model + optimizer + scheduler + trainer state under ``<path>/checkpoints/step_<N>/``. Beyond the
+        reference's files it also writes ``extra_state.pt`` (dead-feature counters and RNG state), which
+        older readers ignore."""
+        ckpt_dir = Path(checkpoint_path) / "checkpoints" / f"step_{self.cur_step}"
+        primary = is_primary_rank(sae.device_mesh)
+        if primary:
+            os.makedirs(ckpt_dir, exist_ok=True)
+        if sae.device_mesh is not None and dist.is_initialized():
+            dist.barrier()
+        if primary:
+            sae.cfg.save_hyperparameters(ckpt_dir)
+        sae.save_checkpoint(ckpt_dir / "sae_weights.safetensors")
+        opt_state = self._gather_optimizer_state(sae)
+        if primary:
+            torch.save(
+                {
+                    "cur_step": self.cur_step,
+                    "cur_tokens": self.cur_tokens,
+                    "total_training_steps": self.total_training_steps,
+                    "lr_warm_up_steps": self.lr_warm_up_steps,
+                    "lr_cool_down_steps": self.lr_cool_down_steps,
+                    "k_warmup_steps": self.k_warmup_steps,
+                    "k_cold_booting_steps": self.k_cold_booting_steps,
+                    "l1_coefficient_warmup_steps": self.l1_coefficient_warmup_steps,
+                    "checkpoint_thresholds": self.checkpoint_thresholds,
+                    "cfg": self.cfg,
+                },
+                ckpt_dir / "trainer.pt",
+            )
+            if self.wandb_logger is not None:
+                with open(ckpt_dir / "wandb_run_id.json", "w") as f:
+                    json.dump({"wandb_run_id": self.wandb_logger.id}, f)
+            if opt_state is not None:
+                torch.save(opt_state, ckpt_dir / "optimizer.pt")
+            if self.scheduler is not None:
+                torch.save(self.scheduler.state_dict(), ckpt_dir / "scheduler.pt")
+            extra = {"torch_rng": torch.get_rng_state()}
+            if self.tokens_since_last_activation is not None:
+                extra["tokens_since_last_activation"] = self.tokens_since_last_activation.cpu()
+            torch.save(extra, ckpt_dir / "extra_state.pt")
+        logger.info(f"Checkpoint saved to {ckpt_dir}")
+
+    def _gather_optimizer_state(self, sae: SparseDictionary) -> dict | None:
+        """Optimizer state with full (un-sharded) logical tensors, keyed by parameter name. Collective."""
+        maps = sae.dim_maps()
+        names = {id(p): n for n, p in sae.named_parameters()}
+
+        def full(name: str, t: Tensor) -> Tensor:
+            if sae.device_mesh is not None and name in maps and t.ndim > 0:
+                t = maps[name].gather(t, sae.device_mesh)
+            return t.detach().cpu().contiguous()
+
+        if self.fused is not None:
+            st = self.fused.optimizer_state()
+            out = {"format": "by_name", "step": st["step"], "state": {}}
+            for name, d in st.items():
+                if name != "step":
+                    out["state"][name] = {k: full(name, v) for k, v in d.items()}
+            return out
+        if self.optimizer is None:
+            return None
+        out = {"format": "by_name", "state": {}, "param_groups": [
+            {k: v for k, v in g.items() if k != "params"} for g in self.optimizer.param_groups]}  # fmt: skip
+        for p, st in self.optimizer.state.items():
+            name = names[id(p)]
+            out["state"][name] = {k: (full(name, v) if isinstance(v, Tensor) else v) for k, v in st.items()}
+        return out
+
+    def _load_optimizer_state(self, sae: SparseDictionary, sd: dict) -> None:
+        maps = sae.dim_maps()
+
+        def local(name: str, t: Tensor, like: Tensor) -> Tensor:
+            if sae.device_mesh is not None and name in maps and t.ndim > 0 and tuple(t.shape) != tuple(like.shape):
+                t = maps[name].shard(t, sae.device_mesh)
+            return t.to(like.device)
+
+        if self.fused is not None:
+            params = dict(sae.named_parameters())
+            st = {"step": sd.get("step", 0)}
+            for name, d in sd["state"].items():
+                if name in params:
+                    st[name] = {k: local(name, v, params[name]) for k, v in d.items() if isinstance(v, Tensor) and v.ndim > 0}
+                    if "step" in d and not st["step"]:
+                        st["step"] = int(d["step"])
+            self.fused.load_optimizer_state(st)
+            return
+        assert self.optimizer is not None
+        for name, p in sae.named_parameters():
+            if name in sd["state"]:
+                self.optimizer.state[p] = {
+                    k: (local(name, v, p).to(p.dtype if v.is_floating_point() and v.ndim > 0 else v.dtype) if isinstance(v, Tensor) else v)
+                    for k, v in sd["state"][name].items()
+                }
+
+    @classmethod
+    def from_checkpoint(cls, sae: SparseDictionary, checkpoint_path: str) -> "Trainer":
+        ckpt_dir = Path(checkpoint_path)
+        trainer_path = ckpt_dir / "trainer.pt"
+        if not os.path.exists(trainer_path):
+            raise ValueError(f"Trainer checkpoint not found at {trainer_path}")
+        state = torch.load(trainer_path, map_location="cpu", weights_only=False)
+        cfg = state.get("cfg")
+        if cfg is None:
+            raise ValueError("Checkpoint does not contain trainer config")
+        trainer = cls(cfg)
+        trainer.cfg.from_pretrained_path = checkpoint_path
+        for key in ("cur_step", "cur_tokens", "total_training_steps", "lr_warm_up_steps", "lr_cool_down_steps",
+                    "k_warmup_steps", "k_cold_booting_steps", "l1_coefficient_warmup_steps", "checkpoint_thresholds"):  # fmt: skip
+            setattr(trainer, key, state[key])
+        trainer._initialize_optimizer(sae)
+        opt_path = ckpt_dir / "optimizer.pt"
+        if opt_path.exists():
+            sd = torch.load(opt_path, map_location="cpu", weights_only=False)
+            if sd.get("format") == "by_name":
+                trainer._load_optimizer_state(sae, sd)
+            elif trainer.optimizer is not None:
+                trainer.optimizer.load_state_dict(sd)
+        sched_path = ckpt_dir / "scheduler.pt"
+        if sched_path.exists() and trainer.scheduler is not None:
+            trainer.scheduler.load_state_dict(torch.load(sched_path, map_location="cpu", weights_only=False))
+        extra_path = ckpt_dir / "extra_state.pt"
+        if extra_path.exists():
+            extra = torch.load(extra_path, map_location="cpu", weights_only=False)
+            trainer._restored_dead_counter = extra.get("tokens_since_last_activation")
+        logger.info(f"Checkpoint loaded from {checkpoint_path} (step {trainer.cur_step})")
+        return trainer
+
+    # ---- initialisation ----------------------------------------------------------------------
+    @timer.time("initialize_trainer")
+    def _initialize_trainer(self, sae: SparseDictionary, first_batch: dict[str, Tensor], wandb_logger=None):
+        bs = first_batch["tokens"].numel() * mesh_dim_size(sae.device_mesh, "data")
+        self.total_training_steps = self.cfg.total_training_tokens // bs
+
+        def steps(v: float | int) -> int:
+            if isinstance(v, float):
+                assert 0 <= v <= 1.0
+                return int(v * self.total_training_steps)
+            return v
+
+        self.lr_warm_up_steps = steps(self.cfg.lr_warm_up_steps)
+        self.lr_cool_down_steps = steps(self.cfg.lr_cool_down_steps)
+        self.k_warmup_steps = steps(self.cfg.k_warmup_steps)
+        self.k_cold_booting_steps = steps(self.cfg.k_cold_booting_steps)
+        self.l1_coefficient_warmup_steps = steps(self.cfg.l1_coefficient_warmup_steps)
+        n = self.cfg.n_checkpoints
+        if n > 0 and self.total_training_steps > 0:
+            if self.cfg.check_point_save_mode == "linear":
+                stride = max(self.total_training_steps // n, 1)
+                self.checkpoint_thresholds = list(range(0, self.total_training_steps, stride))[1:]
+            else:
+                # log-spaced in steps (the thresholds are compared with the step counter)
+                self.checkpoint_thresholds = sorted(
+                    {math.ceil(2 ** (i / n * math.log2(self.total_training_steps))) for i in range(1, n)}
+                )
+        self.wandb_logger = wandb_logger
+
+    @timer.time("initialize_optimizer")
+    def _initialize_optimizer(self, sae: SparseDictionary):
+        assert isinstance(self.cfg.lr, float)
+        sched_kwargs = dict(
+            warm_up_steps=self.lr_warm_up_steps, cool_down_steps=self.lr_cool_down_steps,
+            training_steps=self.total_training_steps, lr_end_ratio=self.cfg.lr_end_ratio,
+        )  # fmt: skip
+        from .ops.fused_step import FusedTopKSAEStep
+        from .optim import schedule_lambda
+
+        ok, why = (False, "disabled") if not self.cfg.use_fused_kernels else FusedTopKSAEStep.supports(sae, self.cfg)
+        if ok:
+            self.fused = FusedTopKSAEStep(sae, betas=self.cfg.betas)
+            logger.info("Training on the fused sm_100a kernel path")
+        else:
+            logger.info(f"Training on the generic autograd path ({why})")
+        groups = []
+        for g in sae.get_parameters():
+            if not g["params"]:
+                continue
+            groups.append({**g, "lr": self.cfg.jumprelu_lr_factor * self.cfg.lr} if g["name"] == "jumprelu" else g)
+        if self.cfg.optimizer_class == "adam":
+            kw: dict[str, Any] = {"foreach": self.cfg.optimizer_foreach}
+            if all(p.is_cuda for g in groups for p in g["params"]):
+                kw = {"fused": True}
+            optimizer: Optimizer = Adam(groups, lr=self.cfg.lr, betas=self.cfg.betas, **kw)
+        else:
+            optimizer = SparseAdam(groups, lr=self.cfg.lr, betas=self.cfg.betas)
+        self.optimizer = optimizer
+        self.scheduler = get_scheduler(self.cfg.lr_scheduler_name, optimizer, **sched_kwargs)
+        if self.cfg.lr_scheduler_name not in ("cosineannealing",):
+            self._lr_lambda = schedule_lambda(self.cfg.lr_scheduler_name, **sched_kwargs)
+
+    def _initialize_dead_statistics(self, sae: SparseDictionary) -> None:
+        n_local = sae.local_shape("b_E", (sae.cfg.d_sae,))[0] if "b_E" in sae.dim_maps() else sae.cfg.d_sae
+        dev = next(sae.parameters()).device
+        self.tokens_since_last_activation = torch.zeros(n_local, device=dev, dtype=torch.long)
+        restored = getattr(self, "_restored_dead_counter", None)
+        if restored is not None and restored.numel() == n_local:
+            self.tokens_since_last_activation.copy_(restored)
+        self.is_dead = self.tokens_since_last_activation >= self.cfg.dead_threshold
+
+    @torch.no_grad()
+    def update_dead_statistics(self, feature_acts: Tensor, mask: Tensor | None, specs: tuple[str, ...]) -> Tensor:
+        """Reset the counter of every feature that fired in this batch, advance the others by the number of
+        valid tokens (summed over data-parallel ranks), and return ``counter >= dead_threshold``."""
+        assert self.tokens_since_last_activation is not None and self.is_dead is not None
+        valid = mask.sum() if mask is not None else torch.tensor(feature_acts[..., 0].numel(), device=feature_acts.device)
+        fired, _ = apply_token_mask(feature_acts, specs, mask, "sum")
+        fired = fired.gt(0)
+        group = getattr(self, "_dp_group", None)
+        if group is not None and dist.get_world_size(group) > 1:
+            fired_i = fired.to(torch.int32)
+            dist.all_reduce(fired_i, group=group)
+            fired = fired_i > 0
+            valid = valid.clone()
+            dist.all_reduce(valid, group=group)
+        self.tokens_since_last_activation = torch.where(
+            fired, torch.zeros_like(self.tokens_since_last_activation), self.tokens_since_last_activation + valid
+        )
+        self.is_dead = self.tokens_since_last_activation >= self.cfg.dead_threshold
+        return self.is_dead
+
+    # ---- schedules ---------------------------------------------------------------------------
+    def _current_k(self, sae: SparseDictionary) -> int | None:
+        if "topk" not in sae.cfg.act_fn or self.k_warmup_steps <= 0 or self.cfg.initial_k is None:
+            return None  # no k schedule (the reference insists on initial_k here; leaving it unset means "constant k")
+        assert self.cfg.initial_k >= sae.cfg.top_k, "initial_k must be greater than or equal to top_k"
+        if self.cur_step < self.k_cold_booting_steps:
+            return int(self.cfg.initial_k)
+        progress = min(1.0, (self.cur_step - self.k_cold_booting_steps) / self.k_warmup_steps)
+        if self.cfg.k_schedule_type == "exponential":
+            f = self.cfg.k_exponential_factor
+            progress = (1.0 - math.exp(-f * progress)) / (1.0 - math.exp(-f))
+        k = self.cfg.initial_k + (sae.cfg.top_k - self.cfg.initial_k) * progress
+        return max(sae.cfg.top_k, math.ceil(k))
+
+    def _l1_coefficient(self) -> float:
+        if self.cfg.l1_coefficient is None:
+            return 1.0
+        if self.l1_coefficient_warmup_steps <= 0:
+            return self.cfg.l1_coefficient
+        return min(1.0, self.cur_step / self.l1_coefficient_warmup_steps) * self.cfg.l1_coefficient
+
+    @timer.time("training_step")
+    def _training_step(self, sae: SparseDictionary, batch: dict[str, Tensor]) -> dict[str, Any]:
+        k = self._current_k(sae)
+        if k is not None:
+            sae.set_current_k(k)
+        auxk = self.cfg.auxk_coefficient or 0.0
+        return sae.compute_loss(
+            batch,
+            sparsity_loss_type=self.cfg.sparsity_loss_type,
+            tanh_stretch_coefficient=self.cfg.tanh_stretch_coefficient,
+            p=self.cfg.p,
+            return_aux_data=True,
+            l1_coefficient=self._l1_coefficient(),
+            lp_coefficient=self.cfg.lp_coefficient or 0.0,
+            auxk_coefficient=auxk,
+            frequency_scale=self.cfg.frequency_scale,
+            k_aux=self.cfg.k_aux,
+            update_dead_statistics=self.update_dead_statistics if auxk > 0.0 else None,
+        )
+
+    # ---- logging -----------------------------------------------------------------------------
+    def _emit(self, sae: SparseDictionary, metrics: dict[str, Any]) -> None:
+        if is_primary_rank(sae.device_mesh):
+            log_metrics(logger.logger, metrics, step=self.cur_step + 1, title="Training Metrics")
+        if timer.enabled:
+            logger.info(f"\nTimer Summary:\n{timer.summary()}\n")
+        if self.wandb_logger is not None:
+            self.wandb_logger.log(metrics, step=self.cur_step + 1)
+
+    def _details(self, ctx: dict[str, Any], lr: float) -> dict[str, Any]:
+        return {
+            "details/current_learning_rate": lr,
+            "details/n_training_tokens": self.cur_tokens,
+            "details/l1_coefficient": ctx.get("l1_coefficient"),
+            "details/lp_coefficient": ctx.get("lp_coefficient"),
+            "details/auxk_coefficient": ctx.get("auxk_coefficient"),
+        }
+
+    @torch.no_grad()
+    @timer.time("log")
+    def _log(self, sae: SparseDictionary, ctx: dict[str, Any]):
+        assert self.optimizer is not None, "Optimizer must be initialized"
+        if not self.metrics:
+            self.metrics = [
+                FrequencyMetric(sae), LossMetric(sae), MeanFeatureActMetric(sae), ExplainedVarianceMetric(sae),
+                L0Metric(sae), L2NormErrorMetric(sae), ModelSpecificMetric(sae), GradientNormMetric(sae),
+            ]  # fmt: skip
+        for metric in self.metrics:
+            ctx = {**ctx, **metric.update(ctx)}
+        if (self.cur_step + 1) % self.cfg.log_frequency == 0:
+            out: dict[str, Any] = {}
+            for metric in self.metrics:
+                out.update(metric.compute())
+            out.update(self._details(ctx, self.optimizer.param_groups[0]["lr"]))
+            out.update(sae.log_statistics())
+            self._emit(sae, out)
+
+    @torch.no_grad()
+    def _log_fused(self, sae: SparseDictionary, x: Tensor, label: Tensor, mask: Tensor | None, loss: Tensor, lr: float):
+        """Metrics of the fused path. Per step only three small device accumulations happen (loss, per-feature
+        fire counts from the step's counting sort, token count); the dense quantities (explained variance,
+        error norms) are evaluated on the logging step's batch."""
+        f = self.fused
+        acc = self._interval
+        if not acc:
+            acc["loss"] = torch.zeros((), device=x.device)
+            acc["fire"] = torch.zeros(f.F, device=x.device, dtype=torch.float32)
+            acc["tokens"] = 0
+            acc["steps"] = 0
+        acc["loss"] += loss
+        n_rows = f.groups.entries.numel() and (x.shape[0] * f.dp)
+        acc["fire"] += f.groups.counts.float()
+        acc["tokens"] += n_rows
+        acc["steps"] += 1
+        if (self.cur_step + 1) % self.cfg.log_frequency != 0:
+            return
+        idx, act, xhat = f.forward_dense(x, sae.current_k)
+        lab = label.float()
+        err = (xhat - lab).pow(2).sum(-1)
+        var = (lab - lab.mean(0)).pow(2).sum(-1)
+        stats = torch.stack([
+            err.mean(), var.mean(), (1 - err / var).mean(), err.sqrt().mean(), lab.norm(dim=-1).mean(),
+        ])  # fmt: skip
+        sparse = torch.stack([act.sum(), (idx >= 0).sum().float()])
+        if f.tp > 1:
+            dist.all_reduce(sparse, group=f.tp_group)
+        freq = acc["fire"] / max(acc["tokens"], 1)
+        counts = torch.stack([(freq > 1e-1).sum(), (freq > 1e-2).sum(), (freq < 1e-5).sum(), (freq < 1e-6).sum(),
+                              (freq < 1e-7).sum(), freq.sum()]).float()  # fmt: skip
+        if f.tp > 1:
+            dist.all_reduce(counts, group=f.tp_group)
+        mean_loss = acc["loss"] / acc["steps"]
+        if f.dp > 1:
+            pack = torch.cat([stats, mean_loss.reshape(1)])
+            dist.all_reduce(pack, group=f.dp_group)
+            pack /= f.dp
+            stats, mean_loss = pack[:5], pack[5]
+        s, c, sp = stats.tolist(), counts.tolist(), sparse.tolist()
+        out = {
+            "losses/overall_loss": float(mean_loss), "losses/mse_loss": float(mean_loss),
+            "metrics/explained_variance": 1 - s[0] / s[1], "metrics/explained_variance_legacy": s[2],
+            "metrics/l0": c[5], "metrics/l2_norm_error": s[3], "metrics/l2_norm_error_ratio": s[3] / s[4],
+            "metrics/mean_feature_act": sp[0] / max(sp[1], 1.0),
+            "sparsity/above_1e-1": c[0], "sparsity/above_1e-2": c[1], "sparsity/below_1e-5": c[2],
+            "sparsity/below_1e-6": c[3], "sparsity/below_1e-7": c[4],
+        }  # fmt: skip
+        out.update(self._details({}, lr))
+        out.update(sae.log_statistics())
+        self._interval = {}
+        self._emit(sae, out)
+
+    @timer.time("save_checkpoint")
+    def _maybe_save_sae_checkpoint(self, sae: SparseDictionary):
+        if self.checkpoint_thresholds and self.cur_step >= self.checkpoint_thresholds[0]:
+            sae.save_checkpoint(os.path.join(self.cfg.exp_result_path, "checkpoints", f"{self.cur_step}.safetensors"))
+            self.checkpoint_thresholds.pop(0)
+
+    # ---- main loop ---------------------------------------------------------------------------
+    def fit(
+        self,
+        sae: SparseDictionary,
+        activation_stream: Iterable[dict[str, Tensor]],
+        eval_fn: Callable[[SparseDictionary], None] | None = None,
+        wandb_logger=None,
+    ) -> bool | None:
+        """Train until ``total_training_tokens`` are consumed. Returns True when the stream ended first."""
+        from tqdm import tqdm
+
+        timer.reset()
+        stream = iter(activation_stream)
+        try:
+            batch = next(stream)
+        except StopIteration:
+            logger.info("the activation stream is empty")
+            return True
+        if self.cfg.from_pretrained_path is None:
+            self._initialize_trainer(sae, batch, wandb_logger)
+            self._initialize_optimizer(sae)
+        else:
+            self.wandb_logger = wandb_logger
+        self._dp_group = mesh_group(sae.device_mesh, "data")
+        if self.cfg.auxk_coefficient is not None and self.cfg.auxk_coefficient > 0.0:
+            self._initialize_dead_statistics(sae)
+        assert self.optimizer is not None and self.scheduler is not None
+        bar = tqdm(total=self.total_training_steps, smoothing=0.001, disable=not is_primary_rank(sae.device_mesh))
+        bar.update(self.cur_step)
+        dp = mesh_dim_size(sae.device_mesh, "data")
+        accum = max(1, self.cfg.gradient_accumulation_steps)
+        try:
+            while True:
+                with timer.time("training_iteration"):
+                    bar.update(1)
+                    sae.train()
+                    batch = self._to_model_device(sae, batch)
+                    if self.fused is not None:
+                        loss = self._fused_iteration(sae, batch)
+                    else:
+                        loss = self._generic_iteration(sae, batch, accum)
+                    if (self.cur_step + 1) % self.cfg.log_frequency == 0:
+                        bar.set_description(f"loss: {float(loss):.2f}")
+                    if eval_fn is not None and (self.cur_step + 1) % self.cfg.eval_frequency == 0:
+                        with timer.time("evaluation"):
+                            eval_fn(sae)
+                    self.cur_step += 1
+                    mask = batch.get("mask")
+                    n_tok = batch["tokens"].numel() if mask is None else int(mask.sum())
+                    self.cur_tokens += n_tok * dp
+                    self._maybe_save_sae_checkpoint(sae)
+                    if self.cur_step >= self.total_training_steps:
+                        break
+                    with timer.time("refresh_batch"):
+                        del batch
+                        batch = next(stream)
+        except StopIteration:
+            logger.info("the current stream has ended")
+            return True
+        except Exception as e:
+            logger.error(f"Training failed: {e}")
+            raise
+        finally:
+            bar.close()
+        return None
+
+    @staticmethod
+    def _to_model_device(sae: SparseDictionary, batch: dict[str, Any]) -> dict[str, Any]:
+        """Host batches (ideally pinned) are copied to the model's device asynchronously on the current stream."""
+        dev = torch.device(sae.cfg.device)
+        if dev.type != "cuda":
+            return batch
+        return {
+            k: (v.to(dev, non_blocking=True) if isinstance(v, Tensor) and v.device.type == "cpu" else v)
+            for k, v in batch.items()
+        }
+
+    def _generic_iteration(self, sae: SparseDictionary, batch: dict[str, Tensor], accum: int) -> Tensor:
+        assert self.optimizer is not None and self.scheduler is not None
+        batch = sae.normalize_activations(batch)
+        dev_type = torch.device(sae.cfg.device).type
+        amp = self.cfg.amp_dtype is not None and (dev_type == "cuda" or self.cfg.amp_dtype == torch.bfloat16)
+        with torch.autocast(device_type=dev_type, dtype=self.cfg.amp_dtype, enabled=amp):
+            ctx = self._training_step(sae, batch)
+        with timer.time("backward"):
+            (ctx["loss"] / accum).backward()
+        if (self.cur_step + 1) % accum != 0:
+            return ctx["loss"].detach()
+        with timer.time("reduce_gradients"):
+            reduce_gradients(sae.parameters(), mesh_group(sae.device_mesh, "data"))
+        with timer.time("clip_grad_norm"):
+            ctx["grad_norm_before_clipping"] = clip_grad_norm(
+                [p for n, p in sae.named_parameters() if p.grad is not None and "log_jumprelu_threshold" not in n],
+                max_norm=self.cfg.clip_grad_norm if self.cfg.clip_grad_norm > 0 else math.inf,
+                device_mesh=sae.device_mesh,
+            )
+        if not self.cfg.skip_metrics_calculation:
+            with torch.autocast(device_type=dev_type, dtype=self.cfg.amp_dtype, enabled=amp):
+                self._log(sae, ctx)
+        with timer.time("optimizer_step"):
+            self.optimizer.step()
+            self.optimizer.zero_grad(set_to_none=True)
+        with timer.time("scheduler_step"):
+            self.scheduler.step()
+        return ctx["loss"].detach()
+
+    def _fused_iteration(self, sae: SparseDictionary, batch: dict[str, Tensor]) -> Tensor:
+        f = self.fused
+        hin, hout = sae.cfg.hook_point_in, sae.cfg.hook_point_out
+        x_raw = batch[hin]
+        assert x_raw.ndim == 2, "the fused path trains on [tokens, d_model] activations"
+        x = (x_raw * sae.compute_norm_factor(x_raw, hin)).to(torch.bfloat16).contiguous()
+        if hout == hin:
+            label = x
+        else:
+            y_raw = batch[hout]
+            label = (y_raw * sae.compute_norm_factor(y_raw, hout)).to(torch.bfloat16).contiguous()
+        mask = batch.get("mask")
+        row_weight, n_global = None, None
+        if mask is not None and mask.dtype != torch.bool or (mask is not None and not bool(mask.all())):
+            row_weight = mask.reshape(-1).float()
+            n = row_weight.sum()
+            if f.dp > 1:
+                dist.all_reduce(n, group=f.dp_group)
+            n_global = int(n)
+        k = self._current_k(sae)
+        if k is not None:
+            sae.set_current_k(k)
+        lr_factor = self._lr_lambda(self.cur_step) if self._lr_lambda is not None else 1.0
+        lr = float(self.cfg.lr) * lr_factor
+        grad_mul = None
+        if self.cfg.clip_grad_norm > 0:
+            grad_mul = self._fused_clip_factor(f, x, label, sae.current_k, row_weight, n_global)
+        loss = f.step(x, label, sae.current_k, lr, row_weight=row_weight, n_tokens_global=n_global, grad_mul=grad_mul)
+        if not self.cfg.skip_metrics_calculation:
+            self._log_fused(sae, x, label, mask, loss, lr)
+        return loss
+
+    def _fused_clip_factor(self, f, x, label, k, row_weight, n_global) -> Tensor:
+        """Clipping needs the gradient norm before the update; on the fused path that costs one extra
+        forward/backward pass that only accumulates squared gradients (no parameter is written)."""
+        raise NotImplementedError("gradient clipping is not available on the fused path; set use_fused_kernels=False")

@@ -1,0 +1,78 @@
+"""The fused kernel training step against the same step written with autograd + torch.optim.Adam."""
+
+import copy
+
+import pytest
+import torch
+
+from language_model_saes_b200.models.sae import SAEConfig, SparseAutoEncoder
+from language_model_saes_b200.ops import sae_kernels as K
+from language_model_saes_b200.ops.fused_step import FusedTopKSAEStep
+
+pytestmark = pytest.mark.gpu
+
+
+def _model(d=256, expansion=8, k=16, gate=True, bias=True):
+    torch.manual_seed(0)
+    cfg = SAEConfig(hook_point_in="h", hook_point_out="h", d_model=d, expansion_factor=expansion, act_fn="topk", top_k=k,
+                    sparsity_include_decoder_norm=gate, use_decoder_bias=bias, device="cuda", dtype=torch.float32)  # fmt: skip
+    sae = SparseAutoEncoder(cfg)
+    sae.init_parameters(encoder_uniform_bound=0.06, decoder_uniform_bound=0.06)
+    sae.set_decoder_to_fixed_norm(0.7, True)
+    sae.init_encoder_with_decoder_transpose()
+    sae.set_dataset_average_activation_norm({"h": d**0.5})
+    return sae
+
+
+def _data(n, B, d, rank=32):
+    g = torch.Generator(device="cuda").manual_seed(1)
+    A = torch.randn(rank, d, device="cuda", generator=g)
+    out = []
+    for _ in range(n):
+        x = torch.randn(B, rank, device="cuda", generator=g) @ A + 0.1 * torch.randn(B, d, device="cuda", generator=g)
+        x = x * (d**0.5 / x.norm(dim=-1).mean())
+        out.append(x.to(torch.bfloat16))
+    return out
+
+
+@pytest.mark.parametrize("gate,bias,k", [(True, True, 16), (False, False, 8), (True, True, 50), (True, True, 100)])
+def test_fused_matches_autograd(gate, bias, k):
+    d, B, steps, lr = 256, 512, 12, 1e-3
+    ref = _model(d=d, k=k, gate=gate, bias=bias)
+    fused_model = copy.deepcopy(ref)
+    engine = FusedTopKSAEStep(fused_model)
+    data = _data(steps, B, d)
+    opt = torch.optim.Adam(ref.parameters(), lr=lr)
+    ref_losses, fused_losses = [], []
+    tokens = torch.zeros(B, dtype=torch.long, device="cuda")
+    for x in data:
+        opt.zero_grad()
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = ref.compute_loss({"h": x.float(), "tokens": tokens})["loss"]
+        loss.backward()
+        opt.step()
+        ref_losses.append(float(loss.detach()))
+        fused_losses.append(float(engine.step(x, x, k, lr)))
+    K.check_status(torch.device("cuda"))
+    r, f = torch.tensor(ref_losses), torch.tensor(fused_losses)
+    assert torch.allclose(r, f, rtol=3e-2), (ref_losses, fused_losses)
+    assert f[-1] < f[0]
+    # parameters moved the same way
+    for name in ("W_D", "W_E", "b_E") + (("b_D",) if bias else ()):
+        a, b = getattr(ref, name).detach().float(), getattr(fused_model, name).detach().float()
+        cos = torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0)
+        # biases take Adam steps of size ~lr whose sign flips on near-zero gradients: looser bound
+        assert cos > (0.99 if name.startswith("b_") else 0.999), (name, float(cos))
+
+
+def test_fused_row_mask_and_transcoder_label():
+    d, B, k = 128, 256, 8
+    sae = _model(d=d, k=k)
+    engine = FusedTopKSAEStep(sae)
+    x, y = _data(2, B, d)
+    w = (torch.rand(B, device="cuda") > 0.3).float()
+    idx, act = engine.encode(x, k)
+    xhat = K.ref_sparse_decode(idx, act, engine.WD_bf16, engine.bD)
+    want = (((xhat - y.float()) ** 2).sum(-1) * w).sum() / w.sum()
+    got = engine.step(x, y, k, 1e-3, row_weight=w, n_tokens_global=int(w.sum()))
+    assert torch.allclose(got, want, rtol=1e-3)
