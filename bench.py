@@ -147,7 +147,12 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     # ---- device-timed kernel path --------------------------------------------------------------------
-    engine = FusedTopKSAEStep(sae, betas=(0.9, 0.999))
+    comm = None
+    if world > 1 and os.environ.get("LMSAE_BENCH_NCCL", "0") != "1":
+        from language_model_saes_b200.parallel.symm import SymmComm
+
+        comm = SymmComm(mesh.get_group("model"), dev, BATCH, TOP_K, D_MODEL)
+    engine = FusedTopKSAEStep(sae, betas=(0.9, 0.999), comm=comm)
     pool = [h.to(dev) for h in host]
     for i in range(W):
         engine.step(pool[i % POOL], pool[i % POOL], TOP_K, LR)
@@ -167,7 +172,8 @@ def run_ours(args):
     ms = start.elapsed_time(end)
     K.check_status(dev)
     final_loss = float(loss)
-    del engine, pool
+    collectives = "none" if world == 1 else ("fused peer-memory kernels" if comm is not None else "nccl")
+    del engine, pool, comm
     torch.cuda.empty_cache()
 
     # ---- end to end through Trainer.fit --------------------------------------------------------------
@@ -202,6 +208,7 @@ def run_ours(args):
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"model": "TopK SAE d_model 4096, d_sae 131072, k 50, Adam lr 2e-4, fp32 master weights + bf16 compute",
                        "global_batch": BATCH, "seq_len": 1, "parallelism": f"tp{world}",
+                       "collectives": collectives,
                        "l2": f"inputs rotate through {POOL} batches (256 MiB) > L2; weights 2 x 2.1 GB"},
             "clocks": clocks,
             "e2e": {"value": Ksteps * BATCH / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms / Ksteps,

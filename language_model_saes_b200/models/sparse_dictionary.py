@@ -596,8 +596,12 @@ class SparseDictionary(HookedRootModule, ABC):
         with timer.time("decode"):
             reconstructed = self.decode(feature_acts, **decoder_kwargs)
 
+        full_mask = mask
         with timer.time("loss_calculation"):
             l_rec = (reconstructed - label).pow(2).sum(dim=-1)
+            if mask is not None and mask.ndim < l_rec.ndim:
+                # per-token losses with extra trailing axes (heads / layers): every entry of a token shares its mask
+                mask = mask.reshape(*mask.shape, *([1] * (l_rec.ndim - mask.ndim))).expand_as(l_rec)
             l_rec, _ = apply_token_mask(l_rec, self.specs.loss(l_rec), mask, "mean")
             loss_dict: dict[str, torch.Tensor | None] = {"l_rec": l_rec}
             loss = l_rec
@@ -670,12 +674,12 @@ class SparseDictionary(HookedRootModule, ABC):
 
         if not return_aux_data:
             return loss
-        n_tokens = batch["tokens"].numel() if mask is None else int(mask.sum())
+        n_tokens = batch["tokens"].numel() if full_mask is None else int(full_mask.sum())
         return {
             "loss": loss,
             **loss_dict,
             "label": label,
-            "mask": mask,
+            "mask": full_mask,
             "n_tokens": n_tokens,
             "feature_acts": feature_acts,
             "reconstructed": reconstructed,

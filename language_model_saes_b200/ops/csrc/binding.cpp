@@ -338,9 +338,91 @@ void row_norm_shadow(const Tensor& W, const c10::optional<Tensor>& norm, const c
              "row_norm_shadow launch");
 }
 
+// ---- peer-memory collectives -----------------------------------------------------------------------
+// `table` = [world, rank, flags_off, cand_val_off, cand_idx_off, partial_off, dxhat_off, ptr_0 .. ptr_{world-1}]
+lmsae::PeerTable make_peer_table(const std::vector<int64_t>& table) {
+  TORCH_CHECK(table.size() >= 8, "peer table too short");
+  lmsae::PeerTable pt{};
+  pt.world = (int)table[0];
+  pt.rank = (int)table[1];
+  TORCH_CHECK(pt.world >= 1 && pt.world <= lmsae::kMaxPeers && pt.rank >= 0 && pt.rank < pt.world, "bad world/rank");
+  TORCH_CHECK((int)table.size() == 7 + pt.world, "peer table needs one pointer per rank");
+  pt.flags_off = table[2];
+  pt.cand_val_off = table[3];
+  pt.cand_idx_off = table[4];
+  pt.partial_off = table[5];
+  pt.dxhat_off = table[6];
+  for (int i = 0; i < pt.world; ++i) pt.base[i] = reinterpret_cast<char*>(static_cast<uintptr_t>(table[7 + i]));
+  return pt;
+}
+
+void comm_push_candidates(const std::vector<int64_t>& table, const Tensor& val, const Tensor& idx, int64_t epoch,
+                          const Tensor& done_counter) {
+  CHECK_T(val, torch::kFloat32);
+  CHECK_T(idx, torch::kInt32);
+  CHECK_T(done_counter, torch::kInt32);
+  TORCH_CHECK(val.dim() == 2 && idx.sizes() == val.sizes());
+  const c10::cuda::CUDAGuard guard(val.device());
+  check_cuda(lmsae::push_candidates_launch(make_peer_table(table), val.data_ptr<float>(), idx.data_ptr<int>(),
+                                           (int)val.size(0), (int)val.size(1), (uint32_t)epoch,
+                                           reinterpret_cast<unsigned*>(done_counter.data_ptr<int>()),
+                                           at::cuda::getCurrentCUDAStream()),
+             "push_candidates launch");
+}
+
+void comm_wait(const std::vector<int64_t>& table, int64_t phase, int64_t epoch, const Tensor& status) {
+  CHECK_T(status, torch::kInt32);
+  const c10::cuda::CUDAGuard guard(status.device());
+  check_cuda(lmsae::wait_flags_launch(make_peer_table(table), (int)phase, (uint32_t)epoch, status.data_ptr<int>(),
+                                      at::cuda::getCurrentCUDAStream()),
+             "wait_flags launch");
+}
+
+void comm_decode_scatter(const std::vector<int64_t>& table, const Tensor& idx, const Tensor& val, const Tensor& W,
+                         int64_t epoch, const Tensor& done_counter) {
+  CHECK_T(idx, torch::kInt32);
+  CHECK_T(val, torch::kFloat32);
+  CHECK_T(W, torch::kBFloat16);
+  CHECK_T(done_counter, torch::kInt32);
+  TORCH_CHECK(idx.dim() == 2 && val.sizes() == idx.sizes() && W.dim() == 2);
+  const c10::cuda::CUDAGuard guard(idx.device());
+  check_cuda(lmsae::sparse_decode_scatter_launch(make_peer_table(table), idx.data_ptr<int>(), val.data_ptr<float>(),
+                                                 (int)idx.size(0), (int)idx.size(1), (int)W.size(1),
+                                                 reinterpret_cast<const __nv_bfloat16*>(W.data_ptr()), (uint32_t)epoch,
+                                                 reinterpret_cast<unsigned*>(done_counter.data_ptr<int>()),
+                                                 at::cuda::getCurrentCUDAStream()),
+             "sparse_decode_scatter launch");
+}
+
+void comm_reduce_loss_push(const std::vector<int64_t>& table, int64_t B, int64_t d, const Tensor& label,
+                           const c10::optional<Tensor>& bias, const c10::optional<Tensor>& row_weight,
+                           double grad_scale, const Tensor& loss_sum, const c10::optional<Tensor>& xhat_out,
+                           int64_t epoch, const Tensor& done_counter, const Tensor& status) {
+  CHECK_T(label, torch::kBFloat16);
+  CHECK_T(loss_sum, torch::kFloat32);
+  CHECK_T(done_counter, torch::kInt32);
+  CHECK_T(status, torch::kInt32);
+  TORCH_CHECK(label.numel() == B * d);
+  if (bias.has_value()) { CHECK_T(*bias, torch::kFloat32); TORCH_CHECK(bias->numel() == d); }
+  if (row_weight.has_value()) { CHECK_T(*row_weight, torch::kFloat32); TORCH_CHECK(row_weight->numel() == B); }
+  if (xhat_out.has_value()) { CHECK_T(*xhat_out, torch::kFloat32); TORCH_CHECK(xhat_out->numel() == B * d); }
+  const c10::cuda::CUDAGuard guard(label.device());
+  check_cuda(lmsae::reduce_loss_push_launch(make_peer_table(table), (int)B, (int)d,
+                                            reinterpret_cast<const __nv_bfloat16*>(label.data_ptr()),
+                                            opt_ptr<const float>(bias), opt_ptr<const float>(row_weight),
+                                            (float)grad_scale, loss_sum.data_ptr<float>(), opt_ptr<float>(xhat_out),
+                                            (uint32_t)epoch, reinterpret_cast<unsigned*>(done_counter.data_ptr<int>()),
+                                            status.data_ptr<int>(), at::cuda::getCurrentCUDAStream()),
+             "reduce_loss_push launch");
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("comm_push_candidates", &comm_push_candidates);
+  m.def("comm_wait", &comm_wait);
+  m.def("comm_decode_scatter", &comm_decode_scatter);
+  m.def("comm_reduce_loss_push", &comm_reduce_loss_push);
   m.doc() = "sm_100a kernels for sparse-dictionary training";
   m.def("encoder_gemm", &encoder_gemm);
   m.def("topk_merge", &topk_merge);

@@ -1,0 +1,256 @@
+// Fused compute + collective kernels over NVLink peer memory for the feature-sharded ("model" parallel) step.
+//
+// Every rank owns one symmetric buffer (allocated and exchanged by the host side, parallel/symm.py) whose
+// peer mappings are plain device pointers here. All transfers are ordinary stores / loads through those
+// pointers (no TMA on peer memory, no multicast); completion is signalled with monotonically growing epoch
+// flags written with st.release.sys and awaited with bounded ld.acquire.sys spins that report a status code
+// on expiry instead of hanging.
+//
+//   push_candidates_kernel     all-gather of the per-rank top-k candidates (k (value, column) pairs per row):
+//                              each rank stores its pairs straight into every peer's merge input
+//   sparse_decode_scatter      gather-GEMM decode whose epilogue IS the reduce-scatter: every finished row of
+//                              the partial reconstruction is stored into the symmetric buffer of the rank that
+//                              owns that row, while other rows are still being computed
+//   reduce_loss_push_kernel    the row owner sums the tp partials (+ bias), evaluates the MSE loss and its
+//                              gradient, and all-gathers the bf16 gradient rows by storing them into every peer
+//   wait_flags_kernel          bounded wait for one phase of one epoch (consumers run after it in stream order)
+//
+// They replace: the all-reduces of the reference's distributed top-k (utils/distributed/ops.py:226-250) and
+// the Partial->Replicate all-reduce after its decoder matmul (models/sae.py:374-375).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace lmsae {
+
+__device__ __forceinline__ void bf16x8_to_float_c(const uint4& u, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+
+// After all of this grid's stores: the last block to arrive publishes `epoch` in every peer's flag slot.
+__device__ __forceinline__ void signal_peers_when_grid_done(const PeerTable& pt, int phase, uint32_t epoch,
+                                                            unsigned* done_counter) {
+  __shared__ int s_last;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(done_counter, 1u);
+    s_last = (prev == gridDim.x - 1);
+    if (s_last) *done_counter = 0;
+  }
+  __syncthreads();
+  if (s_last) {
+    __threadfence_system();
+    if ((int)threadIdx.x < pt.world) {
+      uint32_t* flag = reinterpret_cast<uint32_t*>(pt.base[threadIdx.x] + pt.flags_off) + phase * kMaxPeers + pt.rank;
+      st_release_sys(flag, epoch);
+    }
+  }
+}
+
+// Block-wide bounded wait until every source rank has published `epoch` for `phase` in OUR flag slots.
+// Returns false (uniformly) on expiry.
+__device__ __forceinline__ bool wait_all_sources(const PeerTable& pt, int phase, uint32_t epoch, int* status) {
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if ((int)threadIdx.x < pt.world) {
+    const uint32_t* flag =
+        reinterpret_cast<const uint32_t*>(pt.base[pt.rank] + pt.flags_off) + phase * kMaxPeers + threadIdx.x;
+    if (!wait_flag_sys(flag, epoch)) {
+      report_status(status, kTimeoutPeerFlag, phase, (int)threadIdx.x);
+      s_ok = 0;
+    }
+  }
+  __syncthreads();
+  return s_ok != 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+push_candidates_kernel(const PeerTable pt, const float* __restrict__ val, const int* __restrict__ idx, int B, int k,
+                       uint32_t epoch, unsigned* done_counter) {
+  // peer layout: val [B][world * k] floats at cand_val_off, idx likewise at cand_idx_off; our segment = rank
+  const long long n = (long long)B * k;
+  for (int p = 0; p < pt.world; ++p) {
+    float* dv = reinterpret_cast<float*>(pt.base[p] + pt.cand_val_off);
+    int* di = reinterpret_cast<int*>(pt.base[p] + pt.cand_idx_off);
+    for (long long i = blockIdx.x * 256LL + threadIdx.x; i < n; i += (long long)gridDim.x * 256) {
+      const long long row = i / k, j = i - row * k;
+      const long long o = row * ((long long)pt.world * k) + (long long)pt.rank * k + j;
+      dv[o] = val[i];
+      di[o] = idx[i];
+    }
+  }
+  signal_peers_when_grid_done(pt, kPhaseCand, epoch, done_counter);
+}
+
+__global__ void wait_flags_kernel(const PeerTable pt, int phase, uint32_t epoch, int* status) {
+  wait_all_sources(pt, phase, epoch, status);
+}
+
+// ---------------------------------------------------------------------------------------------
+constexpr int SC_THREADS = 512;
+constexpr int SC_MAX_VEC = 2;
+
+__global__ void __launch_bounds__(SC_THREADS)
+sparse_decode_scatter_kernel(const PeerTable pt, const int* __restrict__ idx, const float* __restrict__ val, int B, int k,
+                             int d, const __nv_bfloat16* __restrict__ W, uint32_t epoch, unsigned* done_counter) {
+  extern __shared__ uint8_t smem_raw[];
+  int* s_idx = reinterpret_cast<int*>(smem_raw);
+  float* s_val = reinterpret_cast<float*>(smem_raw) + k;
+  const int nvec = d / 8;
+  const int rows_per_rank = B / pt.world;
+  for (int row = blockIdx.x; row < B; row += gridDim.x) {
+    __syncthreads();
+    for (int j = threadIdx.x; j < k; j += SC_THREADS) {
+      s_idx[j] = idx[(size_t)row * k + j];
+      s_val[j] = val[(size_t)row * k + j];
+    }
+    __syncthreads();
+    float acc[SC_MAX_VEC][8];
+#pragma unroll
+    for (int u = 0; u < SC_MAX_VEC; ++u)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[u][i] = 0.0f;
+    for (int j = 0; j < k; ++j) {
+      const int f = s_idx[j];
+      if (f < 0) continue;
+      const float a = s_val[j];
+      const uint4* wrow = reinterpret_cast<const uint4*>(W + (size_t)f * d);
+#pragma unroll
+      for (int u = 0; u < SC_MAX_VEC; ++u) {
+        const int v = threadIdx.x + u * SC_THREADS;
+        if (v < nvec) {
+          float w[8];
+          bf16x8_to_float_c(__ldg(wrow + v), w);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[u][i] = fmaf(a, w[i], acc[u][i]);
+        }
+      }
+    }
+    // epilogue = reduce-scatter: this row belongs to rank `owner`; our partial goes to slot [rank] there
+    const int owner = row / rows_per_rank;
+    const int lrow = row - owner * rows_per_rank;
+    float* dst = reinterpret_cast<float*>(pt.base[owner] + pt.partial_off) +
+                 ((size_t)pt.rank * rows_per_rank + lrow) * d;
+#pragma unroll
+    for (int u = 0; u < SC_MAX_VEC; ++u) {
+      const int v = threadIdx.x + u * SC_THREADS;
+      if (v < nvec) {
+        float4* o = reinterpret_cast<float4*>(dst + v * 8);
+        o[0] = make_float4(acc[u][0], acc[u][1], acc[u][2], acc[u][3]);
+        o[1] = make_float4(acc[u][4], acc[u][5], acc[u][6], acc[u][7]);
+      }
+    }
+  }
+  signal_peers_when_grid_done(pt, kPhasePartial, epoch, done_counter);
+}
+
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+reduce_loss_push_kernel(const PeerTable pt, int B, int d, const __nv_bfloat16* __restrict__ label,
+                        const float* __restrict__ bias, const float* __restrict__ row_weight, float grad_scale,
+                        float* __restrict__ loss_sum, float* __restrict__ xhat_out, uint32_t epoch,
+                        unsigned* done_counter, int* status) {
+  __shared__ float s_red[8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rows_per_rank = B / pt.world;
+  const bool ok = wait_all_sources(pt, kPhasePartial, epoch, status);
+  if (ok) {
+    const float* partial = reinterpret_cast<const float*>(pt.base[pt.rank] + pt.partial_off);
+    const int nvec = d / 8;
+    for (int lrow = blockIdx.x; lrow < rows_per_rank; lrow += gridDim.x) {
+      const int row = pt.rank * rows_per_rank + lrow;
+      const float rw = row_weight != nullptr ? row_weight[row] : 1.0f;
+      float sq = 0.0f;
+      for (int v = threadIdx.x; v < nvec; v += 256) {
+        float x[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = bias != nullptr ? bias[v * 8 + i] : 0.0f;
+        for (int s = 0; s < pt.world; ++s) {
+          const float4* src = reinterpret_cast<const float4*>(partial + ((size_t)s * rows_per_rank + lrow) * d + v * 8);
+          const float4 a = src[0], b = src[1];
+          x[0] += a.x; x[1] += a.y; x[2] += a.z; x[3] += a.w;
+          x[4] += b.x; x[5] += b.y; x[6] += b.z; x[7] += b.w;
+        }
+        if (xhat_out != nullptr) {
+          float4* o = reinterpret_cast<float4*>(xhat_out + (size_t)row * d + v * 8);
+          o[0] = make_float4(x[0], x[1], x[2], x[3]);
+          o[1] = make_float4(x[4], x[5], x[6], x[7]);
+        }
+        float y[8];
+        bf16x8_to_float_c(__ldg(reinterpret_cast<const uint4*>(label + (size_t)row * d) + v), y);
+        float e[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          e[i] = x[i] - y[i];
+          sq = fmaf(e[i], e[i], sq);
+          e[i] *= grad_scale * rw;
+        }
+        uint4 o;
+        o.x = pack_bf16x2(e[0], e[1]);
+        o.y = pack_bf16x2(e[2], e[3]);
+        o.z = pack_bf16x2(e[4], e[5]);
+        o.w = pack_bf16x2(e[6], e[7]);
+        // all-gather of the gradient rows: store into every rank's full [B, d] gradient buffer
+        for (int p = 0; p < pt.world; ++p) {
+          uint4* dst = reinterpret_cast<uint4*>(pt.base[p] + pt.dxhat_off) + ((size_t)row * d) / 8 + v;
+          *dst = o;
+        }
+      }
+      sq = warp_sum(sq);
+      __syncthreads();
+      if (lane == 0) s_red[warp] = sq;
+      __syncthreads();
+      if (warp == 0) {
+        float t = lane < 8 ? s_red[lane] : 0.0f;
+        t = warp_sum(t);
+        if (lane == 0) atomicAdd(loss_sum, t * rw);
+      }
+    }
+  }
+  // signal even after a failed wait so that peers do not pile further timeouts on top of the first one
+  signal_peers_when_grid_done(pt, kPhaseDxhat, epoch, done_counter);
+}
+
+// ---- launchers ----------------------------------------------------------------------------------
+int push_candidates_launch(const PeerTable& pt, const float* val, const int* idx, int B, int k, uint32_t epoch,
+                           unsigned* done_counter, cudaStream_t stream) {
+  int blocks = (int)(((long long)B * k + 255) / 256);
+  if (blocks > 148 * 2) blocks = 148 * 2;
+  push_candidates_kernel<<<blocks, 256, 0, stream>>>(pt, val, idx, B, k, epoch, done_counter);
+  return (int)cudaGetLastError();
+}
+
+int wait_flags_launch(const PeerTable& pt, int phase, uint32_t epoch, int* status, cudaStream_t stream) {
+  wait_flags_kernel<<<1, 32, 0, stream>>>(pt, phase, epoch, status);
+  return (int)cudaGetLastError();
+}
+
+int sparse_decode_scatter_launch(const PeerTable& pt, const int* idx, const float* val, int B, int k, int d,
+                                 const __nv_bfloat16* W, uint32_t epoch, unsigned* done_counter, cudaStream_t stream) {
+  if (d % 8 != 0 || d > SC_THREADS * SC_MAX_VEC * 8 || B % pt.world != 0) return (int)cudaErrorInvalidValue;
+  int blocks = B < 148 * 4 ? B : 148 * 4;
+  sparse_decode_scatter_kernel<<<blocks, SC_THREADS, (size_t)k * 8, stream>>>(pt, idx, val, B, k, d, W, epoch,
+                                                                              done_counter);
+  return (int)cudaGetLastError();
+}
+
+int reduce_loss_push_launch(const PeerTable& pt, int B, int d, const __nv_bfloat16* label, const float* bias,
+                            const float* row_weight, float grad_scale, float* loss_sum, float* xhat_out, uint32_t epoch,
+                            unsigned* done_counter, int* status, cudaStream_t stream) {
+  if (d % 8 != 0 || B % pt.world != 0) return (int)cudaErrorInvalidValue;
+  const int rows = B / pt.world;
+  int blocks = rows < 148 * 4 ? rows : 148 * 4;
+  reduce_loss_push_kernel<<<blocks, 256, 0, stream>>>(pt, B, d, label, bias, row_weight, grad_scale, loss_sum, xhat_out,
+                                                      epoch, done_counter, status);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace lmsae

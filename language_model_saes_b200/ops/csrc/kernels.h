@@ -80,4 +80,28 @@ int adam_flat_launch(float* p, const float* g, float* m, float* v, long long n, 
                      __nv_bfloat16* shadow, float* grad_sq_sum, int update, cudaStream_t stream);
 int row_norm_shadow_launch(const float* W, int F, int d, float* norm, __nv_bfloat16* shadow, cudaStream_t stream);
 
+// ---- peer-memory collectives (comm_ops.cu) -------------------------------------------------------
+constexpr int kMaxPeers = 8;
+enum CommPhase : int { kPhaseCand = 0, kPhasePartial = 1, kPhaseDxhat = 2, kNumPhases = 4 };
+
+// Peer mappings of every rank's symmetric buffer plus the byte offsets of its regions (same on all ranks).
+struct PeerTable {
+  char* base[kMaxPeers];
+  int world, rank;
+  long long flags_off;     // uint32 [kNumPhases][kMaxPeers]: flag[phase][src] = last epoch published by src
+  long long cand_val_off;  // float [B][world * k]
+  long long cand_idx_off;  // int   [B][world * k]
+  long long partial_off;   // float [world][B / world][d]
+  long long dxhat_off;     // bf16  [B][d]
+};
+
+int push_candidates_launch(const PeerTable& pt, const float* val, const int* idx, int B, int k, uint32_t epoch,
+                           unsigned* done_counter, cudaStream_t stream);
+int wait_flags_launch(const PeerTable& pt, int phase, uint32_t epoch, int* status, cudaStream_t stream);
+int sparse_decode_scatter_launch(const PeerTable& pt, const int* idx, const float* val, int B, int k, int d,
+                                 const __nv_bfloat16* W, uint32_t epoch, unsigned* done_counter, cudaStream_t stream);
+int reduce_loss_push_launch(const PeerTable& pt, int B, int d, const __nv_bfloat16* label, const float* bias,
+                            const float* row_weight, float grad_scale, float* loss_sum, float* xhat_out, uint32_t epoch,
+                            unsigned* done_counter, int* status, cudaStream_t stream);
+
 }  // namespace lmsae

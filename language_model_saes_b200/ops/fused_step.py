@@ -29,6 +29,8 @@ from . import sae_kernels as K
 
 class FusedTopKSAEStep:
     def __init__(self, sae, betas: tuple[float, float] = (0.9, 0.999), eps: float = 1e-8, comm=None):
+        """``comm``: a ``parallel.symm.SymmComm`` over the model group switches the two cross-shard exchanges
+        from NCCL collectives to the fused peer-memory kernels."""
         cfg = sae.cfg
         self.sae = sae
         self.mesh = sae.device_mesh
@@ -125,7 +127,7 @@ class FusedTopKSAEStep:
         """Sparse codes (idx, act) [B, k] of bf16 inputs ``x`` [B, d] over this rank's features; under
         feature sharding only globally selected entries survive."""
         gate = self.dec_norm if self.use_gate else None
-        if k <= 64:
+        if k <= 64 and x.is_cuda:
             cv, ci, _ = K.encoder_topk_candidates(x, self.WE_bf16, self.bE, gate, k)
             if self.tp == 1:
                 return K.topk_merge(cv, ci, k, gate)
@@ -136,16 +138,16 @@ class FusedTopKSAEStep:
             if self.tp == 1:
                 return idx_l, act_l
             g_l = act_l * gate[idx_l.clamp_min(0).long()] if gate is not None else act_l
-        if self.comm is not None:
+        if self.comm is not None and x.shape[0] == self.comm.B and k <= self.comm.k_max:
             all_g, all_i = self.comm.exchange_candidates(g_l, idx_l)
         else:
             B = x.shape[0]
-            all_g = torch.empty(self.tp, B, k, dtype=torch.float32, device=x.device)
-            all_i = torch.empty(self.tp, B, k, dtype=torch.int32, device=x.device)
-            dist.all_gather_into_tensor(all_g, g_l, group=self.tp_group)
-            dist.all_gather_into_tensor(all_i, idx_l, group=self.tp_group)
-            all_g = all_g.permute(1, 0, 2).reshape(B, self.tp * k).contiguous()
-            all_i = all_i.permute(1, 0, 2).reshape(B, self.tp * k).contiguous()
+            all_g = torch.empty(self.tp * B, k, dtype=torch.float32, device=x.device)
+            all_i = torch.empty(self.tp * B, k, dtype=torch.int32, device=x.device)
+            dist.all_gather_into_tensor(all_g, g_l.contiguous(), group=self.tp_group)
+            dist.all_gather_into_tensor(all_i, idx_l.contiguous(), group=self.tp_group)
+            all_g = all_g.view(self.tp, B, k).permute(1, 0, 2).reshape(B, self.tp * k).contiguous()
+            all_i = all_i.view(self.tp, B, k).permute(1, 0, 2).reshape(B, self.tp * k).contiguous()
         return K.topk_merge(all_g, all_i, k, gate, own=(self.tp_rank * k, (self.tp_rank + 1) * k))
 
     def step(
@@ -164,16 +166,20 @@ class FusedTopKSAEStep:
         B = x.shape[0]
         n_global = n_tokens_global if n_tokens_global is not None else B * self.dp
         grad_scale = 2.0 / n_global
+        use_comm = self.comm is not None and B == self.comm.B and k <= self.comm.k_max
+        if use_comm:
+            self.comm.next_epoch()
         idx, act = self.encode(x, k)
         self.loss_sum.zero_()
-        if self.tp == 1:
+        if use_comm:
+            # loss_sum collects the rows this rank owns; scale to a local-batch estimate for the return value
+            dxhat, _ = self.comm.decode_reduce_loss(idx, act, self.WD_bf16, label, self.bD, row_weight, grad_scale, self.loss_sum)
+            dact = K.sparse_dact(idx, self.WD_bf16, dxhat)
+        elif self.tp == 1:
             dxhat, dact, _ = K.sparse_decode_loss(idx, act, self.WD_bf16, self.bD, label, row_weight, grad_scale, self.loss_sum)
         else:
             partial = K.sparse_decode(idx, act, self.WD_bf16, None, torch.float32)
-            if self.comm is not None:
-                partial = self.comm.all_reduce_rows(partial)
-            else:
-                dist.all_reduce(partial, group=self.tp_group)
+            dist.all_reduce(partial, group=self.tp_group)
             dxhat = K.mse_loss_grad(partial, label, self.bD, row_weight, grad_scale, self.loss_sum)
             dact = K.sparse_dact(idx, self.WD_bf16, dxhat)
         if self.dp > 1:
@@ -197,6 +203,8 @@ class FusedTopKSAEStep:
             m, v = self.state["b_D"]
             K.adam_flat(self.bD, g_bD, m, v, lr, b1, b2, self.eps, self.t, grad_mul=grad_mul, grad_sq_sum=gsq)
         n_local = B if row_weight is None else row_weight.sum()
+        if use_comm:
+            n_local = n_local / self.tp  # each rank evaluated the loss on the B / tp rows it owns
         return (self.loss_sum / n_local).squeeze(0)
 
     def _gather_rows(self, *tensors: torch.Tensor) -> list[torch.Tensor]:

@@ -47,6 +47,31 @@ class _IdentityFwdAllReduceBwd(torch.autograd.Function):
         return g, None
 
 
+class _AllReduceSumBoth(torch.autograd.Function):
+    """Sum over the group in forward AND backward: for a value that every rank then uses in its own, different
+    part of the computation (e.g. the head-summed crosscoder pre-activations), so that the gradients of the
+    ranks have to be added up as well."""
+
+    @staticmethod
+    def forward(ctx, x: torch.Tensor, group):
+        ctx.group = group
+        out = x.contiguous().clone()
+        dist.all_reduce(out, op=dist.ReduceOp.SUM, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad):
+        g = grad.contiguous().clone()
+        dist.all_reduce(g, op=dist.ReduceOp.SUM, group=ctx.group)
+        return g, None
+
+
+def all_reduce_sum_both(x: torch.Tensor, group) -> torch.Tensor:
+    if group is None or dist.get_world_size(group) == 1:
+        return x
+    return _AllReduceSumBoth.apply(x, group)
+
+
 def all_reduce_sum(x: torch.Tensor, group) -> torch.Tensor:
     if group is None or dist.get_world_size(group) == 1:
         return x

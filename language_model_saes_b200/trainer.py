@@ -99,6 +99,9 @@ class TrainerConfig(BaseConfig):
 
     use_fused_kernels: bool = True
     """Run eligible models (TopK SAE, MSE loss, Adam, CUDA) on the fused kernel path."""
+    use_peer_memory_collectives: bool = True
+    """Under feature sharding on the fused path, exchange candidates / partial reconstructions with the fused
+    peer-memory kernels (NVLink loads and stores issued by the compute kernels) instead of NCCL collectives."""
 
     def model_post_init(self, __context):
         super().model_post_init(__context)
@@ -272,6 +275,7 @@ class Trainer:
     @timer.time("initialize_trainer")
     def _initialize_trainer(self, sae: SparseDictionary, first_batch: dict[str, Tensor], wandb_logger=None):
         bs = first_batch["tokens"].numel() * mesh_dim_size(sae.device_mesh, "data")
+        self._first_batch_rows = first_batch["tokens"].numel()
         self.total_training_steps = self.cfg.total_training_tokens // bs
 
         def steps(v: float | int) -> int:
@@ -309,8 +313,18 @@ class Trainer:
 
         ok, why = (False, "disabled") if not self.cfg.use_fused_kernels else FusedTopKSAEStep.supports(sae, self.cfg)
         if ok:
-            self.fused = FusedTopKSAEStep(sae, betas=self.cfg.betas)
-            logger.info("Training on the fused sm_100a kernel path")
+            comm = None
+            rows = getattr(self, "_first_batch_rows", None)
+            if self.cfg.use_peer_memory_collectives and mesh_dim_size(sae.device_mesh, "model") > 1 and rows:
+                try:
+                    from .parallel.symm import SymmComm
+
+                    k_max = int(max(sae.cfg.top_k, self.cfg.initial_k or 0))
+                    comm = SymmComm(mesh_group(sae.device_mesh, "model"), torch.device(sae.cfg.device), rows, k_max, sae.cfg.d_model)
+                except Exception as e:  # noqa: BLE001
+                    logger.warning(f"peer-memory collectives unavailable ({e}); using NCCL collectives")
+            self.fused = FusedTopKSAEStep(sae, betas=self.cfg.betas, comm=comm)
+            logger.info("Training on the fused sm_100a kernel path" + (" with peer-memory collectives" if comm else ""))
         else:
             logger.info(f"Training on the generic autograd path ({why})")
         groups = []

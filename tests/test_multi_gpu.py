@@ -1,0 +1,92 @@
+"""Feature-sharded fused step on 2 GPUs: peer-memory kernels vs NCCL collectives vs one GPU; and the bounded
+wait of the peer-flag kernels (a flag that nothing sets must end in a status code, not a hang)."""
+
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+
+from language_model_saes_b200.testing import distributed_test
+
+pytestmark = pytest.mark.gpu
+
+needs2 = pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+
+
+def _full_model(dev, d=256, F=4096, k=16):
+    from language_model_saes_b200.models.sae import SAEConfig, SparseAutoEncoder
+
+    torch.manual_seed(0)
+    cfg = SAEConfig(hook_point_in="h", hook_point_out="h", d_model=d, expansion_factor=F / d, act_fn="topk", top_k=k,
+                    device=str(dev), dtype=torch.float32)  # fmt: skip
+    sae = SparseAutoEncoder(cfg)
+    sae.init_parameters(encoder_uniform_bound=0.06, decoder_uniform_bound=0.06)
+    sae.set_decoder_to_fixed_norm(0.7, True)
+    sae.init_encoder_with_decoder_transpose()
+    sae.set_dataset_average_activation_norm({"h": d**0.5})
+    return sae
+
+
+@needs2
+@distributed_test(nproc_per_node=2, backend="nccl")
+def test_peer_memory_step_matches_nccl_and_single_gpu():
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    from language_model_saes_b200.models.sae import SparseAutoEncoder
+    from language_model_saes_b200.ops import sae_kernels as K
+    from language_model_saes_b200.ops.fused_step import FusedTopKSAEStep
+    from language_model_saes_b200.parallel.mesh import DimMap, build_mesh
+    from language_model_saes_b200.parallel.symm import SymmComm
+
+    rank = dist.get_rank()
+    dev = torch.device("cuda", rank)
+    mesh = build_mesh("cuda", (1, 2), ("data", "model"))
+    full = _full_model(dev)
+    B, d, k, lr = 512, 256, 16, 1e-3
+    g = torch.Generator(device=dev).manual_seed(3)
+    xs = [(torch.randn(B, d, device=dev, generator=g) * 1.0).to(torch.bfloat16) for _ in range(4)]
+    for x in xs:
+        dist.broadcast(x, src=0)
+
+    def run(model, comm):
+        eng = FusedTopKSAEStep(model, comm=comm)
+        return torch.stack([eng.step(x, x, k, lr) for x in xs])
+
+    single = SparseAutoEncoder(full.cfg.model_copy())
+    single.load_full_state_dict(full.full_state_dict())
+    want = run(single, None)
+
+    def shard():
+        m = SparseAutoEncoder(full.cfg.model_copy(), mesh)
+        m.load_full_state_dict(full.full_state_dict())
+        return m
+
+    m_nccl, m_p2p = shard(), shard()
+    got_nccl = run(m_nccl, None)
+    comm = SymmComm(mesh.get_group("model"), dev, B, k, d)
+    got_p2p = run(m_p2p, comm)
+    K.check_status(dev)
+    # the peer-memory path reports the loss of the rows each rank owns: average the two halves
+    dist.all_reduce(got_p2p)
+    got_p2p /= 2
+    assert torch.allclose(got_nccl, want, rtol=2e-3), (got_nccl, want)
+    assert torch.allclose(got_p2p, want, rtol=2e-3), (got_p2p, want)
+    for m in (m_nccl, m_p2p):
+        W = DimMap({"model": 0}).gather(m.W_D.data, mesh)
+        assert torch.allclose(W, single.W_D.data, atol=2e-4), float((W - single.W_D.data).abs().max())
+
+
+def test_peer_flag_wait_times_out_with_status_code():
+    from language_model_saes_b200.ops import sae_kernels as K
+
+    dev = torch.device("cuda", 0)
+    buf = torch.zeros(4096, dtype=torch.uint8, device=dev)
+    table = [1, 0, 0, 1024, 2048, 3072, 3584, buf.data_ptr()]
+    st = K.status_buffer(dev)
+    st.zero_()
+    K._ext().comm_wait(table, 0, 7, st)  # epoch 7 was never published
+    torch.cuda.synchronize()
+    with pytest.raises(K.KernelStatusError, match="peer flag"):
+        K.check_status(dev)
+    # the context is still usable afterwards
+    assert float((torch.ones(8, device=dev) * 2).sum()) == 16.0
