@@ -345,7 +345,8 @@ class SparseDictionary(HookedRootModule, ABC):
         else:
             raise ValueError(f"Unsupported checkpoint format: {ckpt}")
         model.load_full_state_dict(state, strict=strict_loading)
-        if fold_activation_scale:
+        if fold_activation_scale and cfg.norm_activation == "dataset-wise":
+            # checkpoints saved with the scale already folded carry norm_activation="inference" and need nothing
             assert isinstance(model, DatasetNormStandardizable), f"{type(model).__name__} cannot fold the dataset norm"
             model.standardize_parameters_of_dataset_norm()
         return model
