@@ -224,17 +224,29 @@ class LocalStore:
         (self.root / "blobs").mkdir(exist_ok=True)
         self._lock = threading.RLock()
         self._cache: dict[str, dict[str, dict]] = {}
+        self._stamps: dict[str, int] = {}
 
     def _coll(self, name: str) -> dict[str, dict]:
+        """Documents of a collection, cached in memory. Files are replaced atomically (write + rename), which bumps the
+        directory's modification time; a cache older than the directory is re-read, so that several processes (a job
+        and the command line, say) see each other's writes."""
         with self._lock:
-            if name not in self._cache:
-                d = self.root / name
-                d.mkdir(exist_ok=True)
+            d = self.root / name
+            d.mkdir(exist_ok=True)
+            stamp = d.stat().st_mtime_ns
+            if name not in self._cache or self._stamps.get(name) != stamp:
                 self._cache[name] = {p.stem: json.loads(p.read_text()) for p in d.glob("*.json")}
+                self._stamps[name] = stamp
             return self._cache[name]
 
+    def _touch(self, coll: str) -> None:
+        self._stamps[coll] = (self.root / coll).stat().st_mtime_ns
+
     def _write(self, coll: str, _id: str, doc: dict) -> None:
-        (self.root / coll / f"{_id}.json").write_text(json.dumps(doc, default=str))
+        tmp = self.root / coll / f".{_id}.tmp"
+        tmp.write_text(json.dumps(doc, default=str))
+        os.replace(tmp, self.root / coll / f"{_id}.json")
+        self._touch(coll)
 
     def find(self, coll: str, query: dict) -> list[dict]:
         with self._lock:
@@ -275,10 +287,12 @@ class LocalStore:
 
     def delete_many(self, coll: str, query: dict) -> int:
         with self._lock:
-            ids = [i for i, d in self._coll(coll).items() if _matches(d, query)]
+            docs = self._coll(coll)
+            ids = [i for i, d in docs.items() if _matches(d, query)]
             for i in ids:
-                del self._coll(coll)[i]
+                del docs[i]
                 (self.root / coll / f"{i}.json").unlink(missing_ok=True)
+            self._touch(coll)
             return len(ids)
 
     def put_blob(self, data: bytes) -> str:

@@ -1,0 +1,76 @@
+"""Command line against the local file store: create / show / remove, and config-file loading."""
+
+import json
+
+import numpy as np
+import pytest
+from conftest import tiny_lm_config
+from typer.testing import CliRunner
+
+from language_model_saes_b200.cli import app, load_config
+from language_model_saes_b200.database import MongoClient, MongoDBConfig
+from language_model_saes_b200.models.sae import SAEConfig, SparseAutoEncoder
+
+runner = CliRunner()
+
+
+def test_load_config_formats(tmp_path):
+    (tmp_path / "a.json").write_text(json.dumps({"x": 1}))
+    (tmp_path / "a.yaml").write_text("x: 1\ny: [1, 2]\n")
+    (tmp_path / "a.toml").write_text('x = 1\n[t]\nz = "s"\n')
+    (tmp_path / "a.py").write_text("config = {'x': 1}\n")
+    (tmp_path / "a.txt").write_text("x")
+    assert load_config(tmp_path / "a.json") == {"x": 1}
+    assert load_config(tmp_path / "a.yaml") == {"x": 1, "y": [1, 2]}
+    assert load_config(tmp_path / "a.toml") == {"x": 1, "t": {"z": "s"}}
+    assert load_config(tmp_path / "a.py") == {"x": 1}
+    import typer
+
+    with pytest.raises(typer.BadParameter):
+        load_config(tmp_path / "a.txt")
+    with pytest.raises(typer.BadParameter):
+        load_config(tmp_path / "missing.json")
+
+
+def test_create_show_remove_roundtrip(tiny_lm_workspace, tmp_path):
+    uri, db = f"file://{tmp_path / 'db'}", "cli"
+    common = ["--mongo-uri", uri, "--mongo-db", db]
+    (tmp_path / "ds.json").write_text(json.dumps({"dataset_name_or_path": str(tiny_lm_workspace / "data"), "is_dataset_on_disk": True}))
+    lm = tiny_lm_config(tiny_lm_workspace).model_dump()
+    (tmp_path / "lm.json").write_text(json.dumps(lm))
+    assert runner.invoke(app, ["create", "dataset", "toy", str(tmp_path / "ds.json"), *common]).exit_code == 0
+    r = runner.invoke(app, ["create", "model", "tiny", str(tmp_path / "lm.json"), *common])
+    assert r.exit_code == 0, r.output
+
+    sae = SparseAutoEncoder(SAEConfig(hook_point_in="h", hook_point_out="h", d_model=16, expansion_factor=2, act_fn="relu"))
+    sae.init_parameters(encoder_uniform_bound=0.1, decoder_uniform_bound=0.1)
+    sae.save_pretrained(tmp_path / "sae")
+    sae.cfg.save_hyperparameters(tmp_path / "sae")
+    r = runner.invoke(app, ["create", "sae", "toy-sae", str(tmp_path / "sae"), "-s", "ser", *common])
+    assert r.exit_code == 0, r.output
+
+    client = MongoClient(MongoDBConfig(mongo_uri=uri, mongo_db=db))
+    assert client.get_dataset_cfg("toy").is_dataset_on_disk and client.get_model_cfg("tiny").max_length == 32
+    assert client.get_sae("toy-sae", "ser").cfg.d_sae == 32
+    acts = np.zeros((2, 16), dtype=np.float32)
+    acts[0, 3], acts[0, 4], acts[1, 7] = 2.0, 0.5, 1.0
+    rows, cols = np.nonzero(acts)
+    record = {
+        "act_times": 3, "n_analyzed_tokens": 100, "max_feature_acts": 2.0,
+        "samplings": [{"name": "top_activations", "feature_acts_indices": np.stack([rows, cols]).astype(np.float32),
+                       "feature_acts_values": acts[rows, cols], "context_idx": np.array([5, 9]), "dataset_name": ["toy", "toy"],
+                       "model_name": ["tiny", "tiny"], "shard_idx": np.array([0, 0]), "n_shards": np.array([1, 1])}],
+    }  # fmt: skip
+    client.add_feature_analysis("default", "toy-sae", "ser", [record], start_idx=0)
+    client.update_feature("toy-sae", 0, {"interpretation": {"text": "a test feature"}}, "ser")
+
+    r = runner.invoke(app, ["show", "feature", "toy-sae", "0", "-s", "ser", "-n", "2", "-r", "4", *common])
+    assert r.exit_code == 0, r.output
+    assert "Feature #0" in r.output and "a test feature" in r.output and "Activation Times" in r.output and "Sample 2" in r.output
+    r = runner.invoke(app, ["show", "feature", "toy-sae", "999", "-s", "ser", *common])
+    assert r.exit_code == 1
+
+    assert runner.invoke(app, ["remove", "analysis", "toy-sae", "default", "-s", "ser", *common]).exit_code == 0
+    assert client.get_feature("toy-sae", "ser", 0).analyses == []
+    assert runner.invoke(app, ["remove", "sae", "toy-sae", "-s", "ser", *common]).exit_code == 0
+    assert client.get_sae("toy-sae", "ser") is None

@@ -32,41 +32,25 @@ from language_model_saes_b200.runners import (
 )
 from language_model_saes_b200.trainer import TrainerConfig
 
+from conftest import tiny_lm_config
+
 HOOK = "blocks.1.hook_resid_post"
-WORDS = ["the", "cat", "sat", "on", "a", "mat", "dog", "ran", "far", "away", "big", "red", "sun", "sky", "is", "blue"]
 
 
-@pytest.fixture(scope="module")
-def workspace(tmp_path_factory):
-    import datasets
-    from tokenizers import Tokenizer, models, pre_tokenizers
-    from transformers import GPT2Config, GPT2LMHeadModel, PreTrainedTokenizerFast
-
-    root = tmp_path_factory.mktemp("runners")
-    vocab = {"<bos>": 0, "<pad>": 1, "<unk>": 2, **{w: i + 3 for i, w in enumerate(WORDS)}}
-    tok = Tokenizer(models.WordLevel(vocab, unk_token="<unk>"))
-    tok.pre_tokenizer = pre_tokenizers.Whitespace()
-    fast = PreTrainedTokenizerFast(tokenizer_object=tok, bos_token="<bos>", eos_token="<bos>", pad_token="<pad>", unk_token="<unk>")
-    torch.manual_seed(0)
-    hf = GPT2LMHeadModel(GPT2Config(vocab_size=len(vocab), n_positions=32, n_embd=16, n_layer=2, n_head=2))
-    hf.save_pretrained(root / "model")
-    fast.save_pretrained(root / "model")
-    g = torch.Generator().manual_seed(0)
-    texts = [" ".join(WORDS[int(i)] for i in torch.randint(0, len(WORDS), (20,), generator=g)) for _ in range(64)]
-    datasets.Dataset.from_dict({"text": texts}).save_to_disk(str(root / "data"))
-    return root
+@pytest.fixture()
+def workspace(tiny_lm_workspace, tmp_path):
+    return tiny_lm_workspace, tmp_path
 
 
-def _lm(root) -> LanguageModelConfig:
-    return LanguageModelConfig(model_name="gpt2", model_from_pretrained_path=str(root / "model"), local_files_only=True,
-                               backend="hooked", device="cpu", dtype=torch.float32, max_length=32, bos_token_id=0, eos_token_id=0, pad_token_id=1)  # fmt: skip
+def _lm(root):
+    return tiny_lm_config(root)
 
 
 def test_pipeline_generate_train_analyze_evaluate(workspace):
-    root = workspace
+    src, root = workspace
     acts = root / "acts"
     generate_activations(GenerateActivationsSettings(
-        model=_lm(root), model_name="tiny", dataset=DatasetConfig(dataset_name_or_path=str(root / "data"), is_dataset_on_disk=True),
+        model=_lm(src), model_name="tiny", dataset=DatasetConfig(dataset_name_or_path=str(src / "data"), is_dataset_on_disk=True),
         dataset_name="toy", hook_points=[HOOK], output_dir=str(acts), total_tokens=16 * 64, context_size=16,
         model_batch_size=4, batch_size=4, device_type="cpu", format="safetensors",
     ))  # fmt: skip
@@ -110,7 +94,7 @@ def test_pipeline_generate_train_analyze_evaluate(workspace):
     assert top["name"] == "top_activations" and len(top["context_idx"]) > 0 and top["dataset_name"][0] == "toy"
 
     direct_logit_attribute(DirectLogitAttributeSettings(
-        sae=pre, sae_name="toy-sae", sae_series="test", model=_lm(root), model_name="tiny",
+        sae=pre, sae_name="toy-sae", sae_series="test", model=_lm(src), model_name="tiny",
         direct_logit_attributor=DirectLogitAttributorConfig(top_k=3), analysis_file=pkl, device_type="cpu",
     ))  # fmt: skip
     with open(pkl, "rb") as f:
