@@ -57,8 +57,25 @@ def unstructure(obj: Any) -> Any:
     return obj
 
 
+def _substitute(tp: Any, typevar_map: dict[Any, Any]) -> Any:
+    """Replace type variables inside ``tp`` (``V`` -> ``list[int]``, ``tuple[V, ...]`` -> ``tuple[list[int], ...]``)."""
+    if not typevar_map:
+        return tp
+    if isinstance(tp, typing.TypeVar):
+        return typevar_map.get(tp, Any)
+    args = get_args(tp)
+    if not args:
+        return tp
+    new_args = tuple(a if a is Ellipsis else _substitute(a, typevar_map) for a in args)
+    origin = get_origin(tp)
+    try:
+        return origin[new_args] if origin not in (typing.Union, types.UnionType) else typing.Union[new_args]
+    except TypeError:
+        return tp
+
+
 def structure(data: Any, cls: Any) -> Any:
-    if cls is Any or cls is None or data is None:
+    if cls is Any or cls is None or data is None or isinstance(cls, typing.TypeVar):
         return data
     origin = get_origin(cls)
     if origin in (typing.Union, types.UnionType):
@@ -88,7 +105,11 @@ def structure(data: Any, cls: Any) -> Any:
     if origin is dict:
         ka, va = get_args(cls) or (Any, Any)
         return {structure(k, ka) if ka in (int, str, float) else k: structure(v, va) for k, v in data.items()}
+    typevar_map: dict[Any, Any] = {}
     if origin is not None:
+        # a parametrised generic dataclass (Box[int]): remember what its type variables stand for
+        params = getattr(origin, "__parameters__", ())
+        typevar_map = dict(zip(params, get_args(cls)))
         cls = origin
     if isinstance(cls, type):
         version = _loading_source_version.get()
@@ -103,7 +124,7 @@ def structure(data: Any, cls: Any) -> Any:
             kwargs, later = {}, {}
             for f in dataclasses.fields(cls):
                 if f.name in data:
-                    (kwargs if f.init else later)[f.name] = structure(data[f.name], hints.get(f.name, Any))
+                    (kwargs if f.init else later)[f.name] = structure(data[f.name], _substitute(hints.get(f.name, Any), typevar_map))
             obj = cls(**kwargs)
             for k, v in later.items():
                 object.__setattr__(obj, k, v)

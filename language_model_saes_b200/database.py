@@ -607,12 +607,15 @@ class MongoClient:
             names.update((f.get("metric") or {}).keys())
         return sorted(names)
 
-    def count_features_with_filters(self, sae_name: str, sae_series: str, name: str = "default",
+    def count_features_with_filters(self, sae_name: str, sae_series: str, name: str | None = None,
                                     metric_filters: dict[str, dict[str, float]] | None = None) -> int:  # fmt: skip
+        """Features that fired at least once in the analysis ``name`` (any analysis when None) and pass the metric
+        filters (``{"metric": {"$gte": a, "$lte": b}}``)."""
         q: dict[str, Any] = {"sae_name": sae_name, "sae_series": sae_series}
         for m, bounds in (metric_filters or {}).items():
             q[f"metric.{m}"] = bounds
-        return sum(1 for f in self.store.find("features", q) if any(a.get("name") == name for a in f.get("analyses", [])))
+        alive = lambda a: (name is None or a.get("name") == name) and (a.get("max_feature_acts") or 0) > 0  # noqa: E731
+        return sum(1 for f in self.store.find("features", q) if any(alive(a) for a in f.get("analyses", [])))
 
     # ---- bookmarks ---------------------------------------------------------------------------
     def add_bookmark(self, sae_name: str, sae_series: str, feature_index: int, tags: list[str] | None = None, notes: str | None = None) -> bool:

@@ -229,3 +229,4 @@ def test_lorsa_splice_completeness_and_qk_tracing(spliced_with_lorsa):
     assert len(direct.pairs) == 1 and direct.pairs.value[0].value.numel() <= 3
     again = loads(dumps(res), AttributionResult)
     assert again.qk_trace_results is not None and len(again.qk_trace_results.pairs) == len(qk.pairs)
+    assert isinstance(again.qk_trace_results.pairs.value[0], NodeIndexed) and isinstance(again.qk_trace_results.pairs.value[0].dimensions[0], NodeDimension)
