@@ -16,6 +16,7 @@ import io
 import json
 import os
 import threading
+import time
 import uuid
 from datetime import datetime, timezone
 from pathlib import Path
@@ -225,6 +226,7 @@ class LocalStore:
         self._lock = threading.RLock()
         self._cache: dict[str, dict[str, dict]] = {}
         self._stamps: dict[str, int] = {}
+        self._own: dict[str, int] = {}
 
     def _coll(self, name: str) -> dict[str, dict]:
         """Documents of a collection, cached in memory. Files are replaced atomically (write + rename), which bumps the
@@ -234,13 +236,16 @@ class LocalStore:
             d = self.root / name
             d.mkdir(exist_ok=True)
             stamp = d.stat().st_mtime_ns
-            if name not in self._cache or self._stamps.get(name) != stamp:
+            # File-system timestamps tick coarsely (a few ms): an equal stamp only proves "unchanged" once it is older
+            # than a tick, or when it is the stamp of this object's own last write.
+            settled = time.time_ns() - stamp > 20_000_000 or self._own.get(name) == stamp
+            if name not in self._cache or self._stamps.get(name) != stamp or not settled:
                 self._cache[name] = {p.stem: json.loads(p.read_text()) for p in d.glob("*.json")}
                 self._stamps[name] = stamp
             return self._cache[name]
 
     def _touch(self, coll: str) -> None:
-        self._stamps[coll] = (self.root / coll).stat().st_mtime_ns
+        self._stamps[coll] = self._own[coll] = (self.root / coll).stat().st_mtime_ns
 
     def _write(self, coll: str, _id: str, doc: dict) -> None:
         tmp = self.root / coll / f".{_id}.tmp"
