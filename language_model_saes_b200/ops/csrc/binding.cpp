@@ -112,8 +112,10 @@ int64_t encoder_gemm(const Tensor& x, const Tensor& w, const c10::optional<Tenso
     p.cand_idx = cand_idx->data_ptr<int>();
   }
   TORCH_CHECK(mode & 3, "mode must request H and/or top-k");
+  // bit 3 asks for the CTA-pair kernel; it needs whole pairs of 128-row panels, otherwise the single-CTA kernel runs
+  if ((mode & 8) && (p.num_panels % 2 != 0)) mode &= ~(int64_t)8;
   const CUtensorMap ta = make_bf16_tile_map(x.data_ptr(), p.M, p.K, 128);
-  const CUtensorMap tb = make_bf16_tile_map(w.data_ptr(), p.N, p.K, 256);
+  const CUtensorMap tb = make_bf16_tile_map(w.data_ptr(), p.N, p.K, (mode & 8) ? 128 : 256);
   check_cuda(lmsae::enc_gemm_launch(ta, tb, p, (int)mode, at::cuda::getCurrentCUDAStream()), "encoder_gemm launch");
   return ks;
 }

@@ -21,6 +21,15 @@
 //   warps 4-7 : epilogue; thread r of the warpgroup owns accumulator row r (TMEM lane r)
 // Every mbarrier wait is bounded; on expiry the CTA records a status code, raises a CTA-wide abort flag,
 // drains and frees its TMEM.
+//
+// PAIR variant (tcgen05 cta_group::2): two CTAs on neighbouring SMs form a cluster and work on two adjacent
+// 128-row panels with ONE 256x256x16 instruction stream issued by the leader (cluster rank 0). Each CTA loads
+// its own A tile and only HALF of the B tile (128 of the 256 dictionary rows), so a stage is 32 KB instead of
+// 48 KB per CTA: B crosses L2 -> shared memory once per pair, and the ring is 5-6 stages deep even with the
+// 64-slot top-k state resident. Both producers complete their bytes on the LEADER's "full" barrier; the
+// leader's commits arrive on the "empty" / "accumulator full" barriers of BOTH CTAs; both epilogues release an
+// accumulator buffer on the leader's "accumulator empty" barrier. Each CTA's epilogue is unchanged: it reads
+// its own 128 TMEM lanes (its panel's rows) x 256 columns.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -31,16 +40,16 @@ constexpr int BN = 256;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KB
-constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KB
-constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int TMEM_COLS = 512;
 constexpr int NUM_THREADS = 256;
 
-
-template <int STAGES, int KS>
+template <int STAGES, int KS, bool PAIR>
 struct SmemLayout {
+  static constexpr int kBRows = PAIR ? BN / 2 : BN;       // dictionary rows of a B tile held by one CTA
+  static constexpr int kBStageBytes = kBRows * BK * 2;    // 16 KB (pair) / 32 KB
+  static constexpr int kStageBytes = A_STAGE_BYTES + kBStageBytes;
   static constexpr int kStageOff = 0;
-  static constexpr int kSlotValOff = STAGES * STAGE_BYTES;
+  static constexpr int kSlotValOff = STAGES * kStageBytes;
   static constexpr int kSlotIdxOff = kSlotValOff + BM * KS * 4;
   static constexpr int kBarOff = kSlotIdxOff + BM * KS * 4;
   static constexpr int kNumBars = 2 * STAGES + 4;
@@ -64,11 +73,12 @@ __device__ __forceinline__ float select32(const float (&v)[32], int j) {
   return (j & 16) ? d1 : d0;
 }
 
-template <bool WRITE_H, bool TOPK, int STAGES, int KS>
+template <bool WRITE_H, bool TOPK, int STAGES, int KS, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 enc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                 const EncGemmParams p) {
-  using L = SmemLayout<STAGES, KS>;
+  using L = SmemLayout<STAGES, KS, PAIR>;
+  constexpr int STAGE_BYTES = L::kStageBytes;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -84,8 +94,13 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  const int panel = blockIdx.x % p.num_panels;
-  const int split = blockIdx.x / p.num_panels;
+  // work unit = one CTA (one panel) or one CTA pair (two adjacent panels); units of a split are consecutive
+  const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
+  const bool leader = cta_rank == 0;
+  const int unit = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int units_per_split = PAIR ? p.num_panels / 2 : p.num_panels;
+  const int panel = PAIR ? (unit % units_per_split) * 2 + (int)cta_rank : unit % units_per_split;
+  const int split = unit / units_per_split;
   const int num_n_tiles = (p.N + BN - 1) / BN;
   const int tile_begin = (int)(((long long)split * num_n_tiles) / p.num_splits);
   const int tile_end = (int)(((long long)(split + 1) * num_n_tiles) / p.num_splits);
@@ -99,8 +114,8 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     }
     mbar_init(&tmem_full_bar[0], 1);
     mbar_init(&tmem_full_bar[1], 1);
-    mbar_init(&tmem_empty_bar[0], 4);
-    mbar_init(&tmem_empty_bar[1], 4);
+    mbar_init(&tmem_empty_bar[0], PAIR ? 8 : 4);  // epilogue warps of the CTA (of both CTAs of a pair)
+    mbar_init(&tmem_empty_bar[1], PAIR ? 8 : 4);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -109,8 +124,13 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     prefetch_tensormap(&tmap_b);
   }
   if (warp == 2) {
-    tmem_alloc(tmem_ptr_smem, TMEM_COLS);
-    tmem_relinquish();
+    if constexpr (PAIR) {
+      tmem_alloc_pair(tmem_ptr_smem, TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_ptr_smem, TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   if constexpr (TOPK) {
     // slots are stored slot-major, [KS][128 rows], so that the thread owning a row reads and writes its
@@ -124,6 +144,7 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();  // the peer's barriers exist before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
 
@@ -145,16 +166,25 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           }
           uint8_t* a_dst = smem + L::kStageOff + s * STAGE_BYTES;
           uint8_t* b_dst = a_dst + A_STAGE_BYTES;
-          mbar_arrive_expect_tx(&full_bar[s], STAGE_BYTES);
-          tma_load_2d(a_dst, &tmap_a, &full_bar[s], ks * BK, m0);
-          tma_load_2d(b_dst, &tmap_b, &full_bar[s], ks * BK, n0);
+          if constexpr (PAIR) {
+            // the leader's barrier counts the bytes of both CTAs; bytes landing before the leader has
+            // announced them only make the pending count negative for a moment
+            if (leader) mbar_arrive_expect_tx(&full_bar[s], 2 * STAGE_BYTES);
+            const uint32_t bar = mapa_u32(smem_u32(&full_bar[s]), 0);
+            tma_load_2d_pair(a_dst, &tmap_a, bar, ks * BK, m0);
+            tma_load_2d_pair(b_dst, &tmap_b, bar, ks * BK, n0 + (int)cta_rank * L::kBRows);
+          } else {
+            mbar_arrive_expect_tx(&full_bar[s], STAGE_BYTES);
+            tma_load_2d(a_dst, &tmap_a, &full_bar[s], ks * BK, m0);
+            tma_load_2d(b_dst, &tmap_b, &full_bar[s], ks * BK, n0);
+          }
         }
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (elect_one()) {
-      constexpr uint32_t idesc = make_idesc_bf16(BM, BN);
+    // ------------------------------------------------------------------ MMA issuer (pair: leader CTA only)
+    if ((!PAIR || leader) && elect_one()) {
+      constexpr uint32_t idesc = make_idesc_bf16(PAIR ? 2 * BM : BM, BN);
       uint32_t it = 0;
       bool ok = true;
       int lt = 0;
@@ -185,12 +215,19 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 #pragma unroll
           for (int kk = 0; kk < BK / UMMA_K; ++kk) {
             // +32 bytes per 16-element K step: the start-address field is in 16-byte units
-            umma_bf16_ss(tmem_d, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 2), idesc,
-                         (ks > 0 || kk > 0) ? 1u : 0u);
+            const uint32_t acc = (ks > 0 || kk > 0) ? 1u : 0u;
+            if constexpr (PAIR) {
+              umma_bf16_ss_pair(tmem_d, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 2), idesc, acc);
+            } else {
+              umma_bf16_ss(tmem_d, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 2), idesc, acc);
+            }
           }
-          umma_commit(&empty_bar[s]);  // stage reusable once these MMAs have read it
+          // stage reusable (in both CTAs of a pair) once these MMAs have read it
+          if constexpr (PAIR) umma_commit_pair(&empty_bar[s], 3); else umma_commit(&empty_bar[s]);
         }
-        if (ok) umma_commit(&tmem_full_bar[buf]);
+        if (ok) {
+          if constexpr (PAIR) umma_commit_pair(&tmem_full_bar[buf], 3); else umma_commit(&tmem_full_bar[buf]);
+        }
       }
     }
   } else if (warp >= 4) {
@@ -329,7 +366,10 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       // release this accumulator buffer to the MMA warp
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
+      if (lane == 0) {
+        if constexpr (PAIR) mbar_arrive_cluster(mapa_u32(smem_u32(&tmem_empty_bar[buf]), 0));
+        else mbar_arrive(&tmem_empty_bar[buf]);
+      }
     }
     if constexpr (TOPK) if (ok && row_ok) {
       // emit this sweep's candidates: [row][split * KS + slot]
@@ -349,38 +389,57 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     for (int i = 0; i < 200; ++i) __nanosleep(1000);
     __syncthreads();
   }
+  // pair: neither CTA may free TMEM or leave while the other can still touch its barriers, shared memory or
+  // accumulator rows
+  if constexpr (PAIR) cluster_sync_all();
   if (warp == 2) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if constexpr (PAIR) tmem_dealloc_pair(tmem_base, TMEM_COLS); else tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
 // ---- host side -------------------------------------------------------------------------------
-template <bool WRITE_H, bool TOPK, int STAGES, int KS>
+template <bool WRITE_H, bool TOPK, int STAGES, int KS, bool PAIR>
 static cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const EncGemmParams& p,
                                   cudaStream_t stream) {
-  using L = SmemLayout<STAGES, KS>;
-  auto kern = enc_gemm_kernel<WRITE_H, TOPK, STAGES, KS>;
+  using L = SmemLayout<STAGES, KS, PAIR>;
+  static_assert(L::kDynamicBytes <= 232448, "shared memory of one CTA exceeds 227 KB");
+  auto kern = enc_gemm_kernel<WRITE_H, TOPK, STAGES, KS, PAIR>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
   if (e != cudaSuccess) return e;
-  dim3 grid(p.num_panels * p.num_splits);
-  kern<<<grid, NUM_THREADS, L::kDynamicBytes, stream>>>(ta, tb, p);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.num_panels * p.num_splits);
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = L::kDynamicBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = PAIR ? 2 : 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, ta, tb, p);
 }
 
-// mode: bit 0 = WRITE_H, bit 1 = TOPK, bit 2 = use a 3-stage ring for the plain variant (a tuning probe).
+// mode: bit 0 = WRITE_H, bit 1 = TOPK, bit 2 = 3-stage ring for the plain single-CTA variant (a tuning probe),
+// bit 3 = CTA-pair variant (needs an even number of panels; `tb` must then have a 128-row box).
 // Returns a CUDA error code (0 = launched).
 int enc_gemm_launch(const CUtensorMap& ta, const CUtensorMap& tb, const EncGemmParams& p, int mode,
                     cudaStream_t stream) {
-  const bool wh = mode & 1, tk = mode & 2;
+  const bool wh = mode & 1, tk = mode & 2, pair = mode & 8;
+  if (pair && (p.num_panels % 2 != 0)) return (int)cudaErrorInvalidValue;
   cudaError_t e;
   if (!tk) {
-    e = (mode & 4) ? launch_variant<true, false, 3, 0>(ta, tb, p, stream)
-                   : launch_variant<true, false, 4, 0>(ta, tb, p, stream);
+    if (pair) e = launch_variant<true, false, 6, 0, true>(ta, tb, p, stream);
+    else e = (mode & 4) ? launch_variant<true, false, 3, 0, false>(ta, tb, p, stream)
+                        : launch_variant<true, false, 4, 0, false>(ta, tb, p, stream);
   } else if (p.k <= 32) {
-    e = wh ? launch_variant<true, true, 4, 32>(ta, tb, p, stream) : launch_variant<false, true, 4, 32>(ta, tb, p, stream);
+    if (pair) e = wh ? launch_variant<true, true, 6, 32, true>(ta, tb, p, stream) : launch_variant<false, true, 6, 32, true>(ta, tb, p, stream);
+    else e = wh ? launch_variant<true, true, 4, 32, false>(ta, tb, p, stream) : launch_variant<false, true, 4, 32, false>(ta, tb, p, stream);
   } else {
-    e = wh ? launch_variant<true, true, 3, 64>(ta, tb, p, stream) : launch_variant<false, true, 3, 64>(ta, tb, p, stream);
+    if (pair) e = wh ? launch_variant<true, true, 5, 64, true>(ta, tb, p, stream) : launch_variant<false, true, 5, 64, true>(ta, tb, p, stream);
+    else e = wh ? launch_variant<true, true, 3, 64, false>(ta, tb, p, stream) : launch_variant<false, true, 3, 64, false>(ta, tb, p, stream);
   }
   return (int)e;
 }

@@ -36,7 +36,7 @@ def _timeit(fn, iters: int, warmup: int, flush: torch.Tensor | None):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default="all", help="all | cublas | hidden | topk | merge | decode | csc | adam")
+    ap.add_argument("--case", default="all", help="all | cublas | hidden | hidden3 | hidden_pair | topk | topk_pair | merge | decode | csc | adam")
     ap.add_argument("--M", type=int, default=4096)
     ap.add_argument("--N", type=int, default=16384, help="dictionary size on this GPU")
     ap.add_argument("--K", type=int, default=4096, help="d_model")
@@ -81,6 +81,14 @@ def main(argv=None):
         fn3 = lambda: K._ext().encoder_gemm(x, w, b, None, 1 | 4, 0, K.choose_splits(M, F), H3, None, None, st)  # noqa: E731
         report("encoder_gemm_write_h_3stages", _timeit(fn3, a.iters, a.warmup, flush), flops=flops)
         del H3
+    if want("hidden_pair"):
+        report("encoder_gemm_write_h_pair", _timeit(lambda: K.encoder_hidden(x, w, b, pair=True), a.iters, a.warmup, flush), flops=flops)
+    if want("topk_pair") and k <= 64:
+        report(
+            "encoder_gemm_fused_topk_pair",
+            _timeit(lambda: K.encoder_topk_candidates(x, w, b, gate, k, pair=True), a.iters, a.warmup, flush),
+            flops=flops,
+        )
     if want("topk") and k <= 64:
         report(
             "encoder_gemm_fused_topk",
@@ -88,7 +96,7 @@ def main(argv=None):
             flops=flops,
         )
     K.check_status(dev)
-    if a.case in ("cublas", "hidden", "hidden3", "topk"):
+    if a.case in ("cublas", "hidden", "hidden3", "topk", "hidden_pair", "topk_pair"):
         return
     kk = min(k, 64)
     cv, ci, _ = K.encoder_topk_candidates(x, w, b, gate, kk)

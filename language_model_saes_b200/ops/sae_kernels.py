@@ -10,6 +10,8 @@ Layouts shared by all kernels: encoder and decoder weights are feature-major ``[
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import native
@@ -92,6 +94,9 @@ def check_status(device: torch.device) -> None:
         )
 
 
+GEMM_PAIR_DEFAULT = os.environ.get("LMSAE_GEMM_PAIR", "1") == "1"
+
+
 def choose_splits(M: int, N: int, num_sms: int = NUM_SMS_B200) -> int:
     """How many CTAs share one 128-row panel of the encoder GEMM (each sweeps a range of 256-column tiles)."""
     panels = (M + 127) // 128
@@ -138,13 +143,20 @@ def ref_topk_codes(
     return idx.to(torch.int32), act
 
 
-def encoder_hidden(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None) -> torch.Tensor:
+def _pair_bit(pair: bool | None) -> int:
+    """Mode bit 3 of the encoder GEMM: run on CTA pairs (tcgen05 cta_group::2). The extension falls back to the
+    single-CTA kernel by itself when the batch is not a whole number of 256-row panel pairs."""
+    use = GEMM_PAIR_DEFAULT if pair is None else pair
+    return 8 if use else 0
+
+
+def encoder_hidden(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, pair: bool | None = None) -> torch.Tensor:
     """H = x @ w.T + bias as bf16 via the tcgen05 GEMM (x [M,K] bf16, w [N,K] bf16, bias fp32)."""
     if not x.is_cuda:
         return ref_hidden(x, w, bias).to(torch.bfloat16)
     M, N = x.shape[0], w.shape[0]
     H = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
-    _ext().encoder_gemm(x, w, bias, None, 1, 0, choose_splits(M, N), H, None, None, status_buffer(x.device))
+    _ext().encoder_gemm(x, w, bias, None, 1 | _pair_bit(pair), 0, choose_splits(M, N), H, None, None, status_buffer(x.device))
     return H
 
 
@@ -156,6 +168,7 @@ def encoder_topk_candidates(
     k: int,
     num_splits: int | None = None,
     H: torch.Tensor | None = None,
+    pair: bool | None = None,
 ) -> tuple[torch.Tensor, torch.Tensor, int]:
     """Run the GEMM with the fused top-k epilogue; returns (cand_val [M, C], cand_idx [M, C], C)."""
     M, N = x.shape[0], w.shape[0]
@@ -164,7 +177,7 @@ def encoder_topk_candidates(
     C = S * KS
     cand_val = torch.empty(M, C, dtype=torch.float32, device=x.device)
     cand_idx = torch.empty(M, C, dtype=torch.int32, device=x.device)
-    mode = 2 | (1 if H is not None else 0)
+    mode = 2 | (1 if H is not None else 0) | _pair_bit(pair)
     _ext().encoder_gemm(x, w, bias, gate, mode, k, S, H, cand_val, cand_idx, status_buffer(x.device))
     return cand_val, cand_idx, C
 
@@ -205,6 +218,7 @@ def encoder_topk(
     gate: torch.Tensor | None,
     k: int,
     return_hidden: bool = False,
+    pair: bool | None = None,
 ) -> tuple[torch.Tensor, torch.Tensor] | tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Sparse codes of a TopK encoder: (idx [M,k], act [M,k]) (+ hidden_pre bf16 when asked).
 
@@ -218,10 +232,10 @@ def encoder_topk(
     M, N = x.shape[0], w.shape[0]
     H = torch.empty(M, N, dtype=torch.bfloat16, device=x.device) if (return_hidden or k > 64) else None
     if k <= 64:
-        cv, ci, _ = encoder_topk_candidates(x, w, bias, gate, k, H=H)
+        cv, ci, _ = encoder_topk_candidates(x, w, bias, gate, k, H=H, pair=pair)
         idx, act = topk_merge(cv, ci, k, gate)
     else:
-        _ext().encoder_gemm(x, w, bias, None, 1, 0, choose_splits(M, N), H, None, None, status_buffer(x.device))
+        _ext().encoder_gemm(x, w, bias, None, 1 | _pair_bit(pair), 0, choose_splits(M, N), H, None, None, status_buffer(x.device))
         idx, act = row_topk(H, k, gate, None)
     return (idx, act, H) if return_hidden else (idx, act)
 

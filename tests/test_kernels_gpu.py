@@ -18,10 +18,13 @@ def _mk(M, N, Kd, seed=0, scale=1.0):
     return x, w, b, gate
 
 
-@pytest.mark.parametrize("M,N,Kd", [(128, 256, 64), (256, 512, 128), (300, 1032, 200), (4096, 4096, 512), (77, 264, 72)])
-def test_encoder_hidden(M, N, Kd):
+@pytest.mark.parametrize("pair", [False, True])
+@pytest.mark.parametrize("M,N,Kd", [(128, 256, 64), (256, 512, 128), (300, 1032, 200), (4096, 4096, 512), (77, 264, 72), (512, 1288, 328)])
+def test_encoder_hidden(M, N, Kd, pair):
+    # pair=True runs the CTA-pair (cta_group::2) kernel when M fills whole pairs of 128-row panels (256, 4096, 512
+    # here; M = 300 has three panels and exercises the fall-back to the single-CTA kernel)
     x, w, b, _ = _mk(M, N, Kd)
-    H = K.encoder_hidden(x, w, b)
+    H = K.encoder_hidden(x, w, b, pair=pair)
     K.check_status(x.device)
     ref = K.ref_hidden(x, w, b)
     err = (H.float() - ref).abs().max().item()
@@ -37,12 +40,14 @@ def _codes_to_dense(idx, val, N):
     return out
 
 
-@pytest.mark.parametrize("M,N,Kd,k", [(128, 512, 64, 8), (256, 2048, 128, 32), (300, 4104, 256, 50), (1024, 8192, 256, 64), (64, 264, 64, 1)])
+@pytest.mark.parametrize("pair", [False, True])
+@pytest.mark.parametrize("M,N,Kd,k", [(128, 512, 64, 8), (256, 2048, 128, 32), (300, 4104, 256, 50), (1024, 8192, 256, 64), (64, 264, 64, 1),
+                                      (512, 4104, 264, 50)])
 @pytest.mark.parametrize("use_gate", [False, True])
-def test_encoder_topk_fused(M, N, Kd, k, use_gate):
+def test_encoder_topk_fused(M, N, Kd, k, use_gate, pair):
     x, w, b, gate = _mk(M, N, Kd, seed=1)
     gate = gate if use_gate else None
-    idx, act = K.encoder_topk(x, w, b, gate, k)
+    idx, act = K.encoder_topk(x, w, b, gate, k, pair=pair)
     K.check_status(x.device)
     h = K.ref_hidden(x, w, b)
     g = h * gate if use_gate else h
