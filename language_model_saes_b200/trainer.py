@@ -21,7 +21,7 @@ import json
 import math
 import os
 from pathlib import Path
-from typing import Any, Callable, Iterable, Literal, Tuple
+from typing import Any, Callable, Iterable, Iterator, Literal, Tuple
 
 import torch
 import torch.distributed as dist
@@ -97,6 +97,8 @@ class TrainerConfig(BaseConfig):
     from_pretrained_path: str | None = None
     exp_result_path: str = "results"
 
+    prefetch_to_device: bool = True
+    """Copy the next host batch to the GPU on a side stream while the current step runs."""
     use_fused_kernels: bool = True
     """Run eligible models (TopK SAE, MSE loss, Adam, CUDA) on the fused kernel path."""
     use_peer_memory_collectives: bool = True
@@ -117,6 +119,52 @@ class WandbConfig(BaseConfig):
     wandb_entity: str | None = None
     wandb_run_id: str | None = None
     wandb_resume: Literal["allow", "must", "never", "auto"] = "never"
+
+
+class _DevicePrefetcher:
+    """Iterator over device batches that keeps ONE batch in flight: while step ``i`` computes, the host->device copy
+    of batch ``i + 1`` runs on its own stream (the copy engine), so the copy costs no step time. Host tensors should be
+    pinned, otherwise the copy is synchronous on the host. Batches that are already on the device pass through."""
+
+    def __init__(self, host_iter: Iterator[dict[str, Any]], device: torch.device):
+        self.host_iter = host_iter
+        self.device = device
+        self.copy_stream = torch.cuda.Stream(device=device)
+        self._ready: tuple[dict[str, Any], torch.cuda.Event | None] | None = None
+        self._exhausted = False
+        self._issue()
+
+    def _issue(self) -> None:
+        try:
+            batch = next(self.host_iter)
+        except StopIteration:
+            self._ready, self._exhausted = None, True
+            return
+        if not any(isinstance(v, Tensor) and v.device.type == "cpu" for v in batch.values()):
+            self._ready = (batch, None)
+            return
+        with torch.cuda.stream(self.copy_stream):
+            moved = {k: (v.to(self.device, non_blocking=True) if isinstance(v, Tensor) and v.device.type == "cpu" else v)
+                     for k, v in batch.items()}  # fmt: skip
+            ev = torch.cuda.Event()
+            ev.record(self.copy_stream)
+        self._ready = (moved, ev)
+
+    def __iter__(self):
+        return self
+
+    def __next__(self) -> dict[str, Any]:
+        if self._ready is None:
+            raise StopIteration
+        batch, ev = self._ready
+        self._issue()  # next copy starts before this batch's kernels are launched
+        if ev is not None:
+            cur = torch.cuda.current_stream(self.device)
+            cur.wait_event(ev)
+            for v in batch.values():
+                if isinstance(v, Tensor) and v.is_cuda:
+                    v.record_stream(cur)
+        return batch
 
 
 class Trainer:
@@ -525,6 +573,9 @@ class Trainer:
 
         timer.reset()
         stream = iter(activation_stream)
+        dev = torch.device(sae.cfg.device)
+        if dev.type == "cuda" and self.cfg.prefetch_to_device:
+            stream = _DevicePrefetcher(stream, next(sae.parameters()).device)
         try:
             batch = next(stream)
         except StopIteration:
