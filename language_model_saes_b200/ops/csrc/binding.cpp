@@ -71,7 +71,8 @@ CUtensorMap make_bf16_tile_map(const void* base, int64_t rows, int64_t cols, int
 int64_t encoder_gemm(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& bias,
                      const c10::optional<Tensor>& gate, int64_t mode, int64_t k, int64_t num_splits,
                      const c10::optional<Tensor>& H, const c10::optional<Tensor>& cand_val,
-                     const c10::optional<Tensor>& cand_idx, const Tensor& status) {
+                     const c10::optional<Tensor>& cand_idx, const Tensor& status, int64_t n_index_offset,
+                     bool resume_topk) {
   CHECK_T(x, torch::kBFloat16);
   CHECK_T(w, torch::kBFloat16);
   CHECK_T(status, torch::kInt32);
@@ -92,6 +93,8 @@ int64_t encoder_gemm(const Tensor& x, const Tensor& w, const c10::optional<Tenso
   p.gate = opt_ptr<const float>(gate);
   p.status = status.data_ptr<int>();
   p.k = (int)k;
+  p.n_index_offset = (int)n_index_offset;
+  p.resume_topk = resume_topk ? 1 : 0;
   int ks = 0;
   if (mode & 1) {
     TORCH_CHECK(H.has_value(), "mode bit 0 needs H");
@@ -263,7 +266,8 @@ void sparse_grad_adam(const Tensor& offsets, const Tensor& entries, const Tensor
                       const Tensor& WE_bf16, const c10::optional<Tensor>& bE, const c10::optional<Tensor>& mbE,
                       const c10::optional<Tensor>& vbE, const c10::optional<Tensor>& dec_norm,
                       const c10::optional<Tensor>& grad_mul, const c10::optional<Tensor>& grad_sq_sum, double lr,
-                      double beta1, double beta2, double eps, int64_t step, bool update) {
+                      double beta1, double beta2, double eps, int64_t step, bool update, int64_t f_begin,
+                      int64_t f_end, int64_t ctas_per_sm) {
   CHECK_T(offsets, torch::kInt32);
   CHECK_T(entries, torch::kInt32);
   CHECK_T(act, torch::kFloat32);
@@ -302,6 +306,10 @@ void sparse_grad_adam(const Tensor& offsets, const Tensor& entries, const Tensor
   p.grad_sq_sum = opt_ptr<float>(grad_sq_sum);
   p.h = make_hyper(lr, beta1, beta2, eps, step);
   p.update = update ? 1 : 0;
+  p.f_begin = (int)f_begin;
+  p.f_end = f_end < 0 ? p.F : (int)f_end;
+  p.ctas_per_sm = (int)ctas_per_sm;
+  TORCH_CHECK(0 <= p.f_begin && p.f_begin <= p.f_end && p.f_end <= p.F, "feature range out of bounds");
   check_cuda(lmsae::sparse_grad_adam_launch(p, at::cuda::getCurrentCUDAStream()), "sparse_grad_adam launch");
 }
 

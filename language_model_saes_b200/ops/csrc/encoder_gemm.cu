@@ -138,8 +138,19 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     // it"; the rest hold +inf so they are never the minimum and never replaced.
     for (int i = threadIdx.x; i < BM * KS; i += NUM_THREADS) {
       const int s = i / BM;
-      slot_val[i] = (s < p.k) ? 0.0f : __int_as_float(0x7f800000);
-      slot_idx[i] = -1;
+      float v = (s < p.k) ? 0.0f : __int_as_float(0x7f800000);
+      int ix = -1;
+      if (p.resume_topk && s < p.k) {
+        // continue the sweep of an earlier launch: its result for (row, this column range) is the state
+        const int r = m0 + (i - s * BM);
+        if (r < p.M) {
+          const long long o = (long long)r * ((long long)p.num_splits * KS) + (long long)split * KS + s;
+          v = p.cand_val[o];
+          ix = p.cand_idx[o];
+        }
+      }
+      slot_val[i] = v;
+      slot_idx[i] = ix;
     }
   }
   tc_fence_before();
@@ -242,12 +253,23 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     constexpr int NG = KS > 0 ? KS / 8 : 1;
     float gmin[NG];
     float tau = 0.0f;
-    if constexpr (TOPK) {
-#pragma unroll
-      for (int g = 0; g < NG; ++g) gmin[g] = (g * 8 < p.k) ? 0.0f : __int_as_float(0x7f800000);
-    }
     float* my_slot_val = slot_val + row_in_tile;
     int* my_slot_idx = slot_idx + row_in_tile;
+    if constexpr (TOPK) {
+      // (the slot arrays were filled before the CTA-wide barrier above)
+#pragma unroll
+      for (int g = 0; g < NG; ++g) {
+        float m = __int_as_float(0x7f800000);
+        if (p.resume_topk) {
+#pragma unroll
+          for (int t = 0; t < 8; ++t) m = fminf(m, my_slot_val[(g * 8 + t) * BM]);
+        } else if (g * 8 < p.k) {
+          m = 0.0f;
+        }
+        gmin[g] = m;
+        tau = (g == 0) ? m : fminf(tau, m);
+      }
+    }
     int lt = 0;
     bool ok = true;
     for (int tile = tile_begin; tile < tile_end && ok; ++tile, ++lt) {
@@ -348,7 +370,7 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 #pragma unroll
               for (int t = 7; t >= 0; --t) sel = (sv[t] == gm) ? t : sel;
               gv[sel * BM] = g;
-              my_slot_idx[(gi * 8 + sel) * BM] = c0 + j;
+              my_slot_idx[(gi * 8 + sel) * BM] = p.n_index_offset + c0 + j;
               float nm = g;
 #pragma unroll
               for (int t = 0; t < 8; ++t) nm = fminf(nm, (t == sel) ? g : sv[t]);
@@ -423,11 +445,13 @@ static cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, 
 }
 
 // mode: bit 0 = WRITE_H, bit 1 = TOPK, bit 2 = 3-stage ring for the plain single-CTA variant (a tuning probe),
-// bit 3 = CTA-pair variant (needs an even number of panels; `tb` must then have a 128-row box).
+// bit 3 = CTA-pair variant (needs an even number of panels; `tb` must then have a 128-row box),
+// bit 4 = with bit 3 and TOPK: a 4-stage ring (under 200 KB of shared memory), which leaves room on the SM for
+//         CTAs of a bandwidth-bound kernel running at the same time on another stream.
 // Returns a CUDA error code (0 = launched).
 int enc_gemm_launch(const CUtensorMap& ta, const CUtensorMap& tb, const EncGemmParams& p, int mode,
                     cudaStream_t stream) {
-  const bool wh = mode & 1, tk = mode & 2, pair = mode & 8;
+  const bool wh = mode & 1, tk = mode & 2, pair = mode & 8, compact = mode & 16;
   if (pair && (p.num_panels % 2 != 0)) return (int)cudaErrorInvalidValue;
   cudaError_t e;
   if (!tk) {
@@ -435,10 +459,12 @@ int enc_gemm_launch(const CUtensorMap& ta, const CUtensorMap& tb, const EncGemmP
     else e = (mode & 4) ? launch_variant<true, false, 3, 0, false>(ta, tb, p, stream)
                         : launch_variant<true, false, 4, 0, false>(ta, tb, p, stream);
   } else if (p.k <= 32) {
-    if (pair) e = wh ? launch_variant<true, true, 6, 32, true>(ta, tb, p, stream) : launch_variant<false, true, 6, 32, true>(ta, tb, p, stream);
+    if (pair && compact && !wh) e = launch_variant<false, true, 4, 32, true>(ta, tb, p, stream);
+    else if (pair) e = wh ? launch_variant<true, true, 6, 32, true>(ta, tb, p, stream) : launch_variant<false, true, 6, 32, true>(ta, tb, p, stream);
     else e = wh ? launch_variant<true, true, 4, 32, false>(ta, tb, p, stream) : launch_variant<false, true, 4, 32, false>(ta, tb, p, stream);
   } else {
-    if (pair) e = wh ? launch_variant<true, true, 5, 64, true>(ta, tb, p, stream) : launch_variant<false, true, 5, 64, true>(ta, tb, p, stream);
+    if (pair && compact && !wh) e = launch_variant<false, true, 4, 64, true>(ta, tb, p, stream);
+    else if (pair) e = wh ? launch_variant<true, true, 5, 64, true>(ta, tb, p, stream) : launch_variant<false, true, 5, 64, true>(ta, tb, p, stream);
     else e = wh ? launch_variant<true, true, 3, 64, false>(ta, tb, p, stream) : launch_variant<false, true, 3, 64, false>(ta, tb, p, stream);
   }
   return (int)e;

@@ -19,6 +19,12 @@ struct EncGemmParams {
   float* cand_val;
   int* cand_idx;
   int* status;
+  // Sweeping the dictionary in several launches (one per feature chunk): this launch covers columns
+  // [n_index_offset, n_index_offset + N) of the whole dictionary (W, bias and gate already point at the chunk),
+  // writes global column indices, and when resume_topk != 0 continues the running top-k that the previous
+  // chunk's launch left in cand_val / cand_idx instead of starting empty.
+  int n_index_offset;
+  int resume_topk;
 };
 int enc_gemm_launch(const CUtensorMap& ta, const CUtensorMap& tb, const EncGemmParams& p, int mode, cudaStream_t stream);
 int enc_gemm_slots_for_k(int k);
@@ -73,6 +79,8 @@ struct GradAdamParams {
   float* grad_sq_sum;
   AdamHyper h;
   int update;
+  int f_begin, f_end;  // feature rows handled by this launch
+  int ctas_per_sm;     // 0 = fill the GPU (4 per SM); 1..4 = leave registers free for a concurrently running kernel
 };
 int sparse_grad_adam_launch(const GradAdamParams& p, cudaStream_t stream);
 int colsum_bf16_launch(const __nv_bfloat16* a, int rows, int d, float* out, cudaStream_t stream);

@@ -418,7 +418,7 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
   const float gmul = p.grad_mul != nullptr ? *p.grad_mul : 1.0f;
   float gsq_local = 0.0f;
 
-  for (int f = blockIdx.x; f < p.F; f += gridDim.x) {
+  for (int f = p.f_begin + blockIdx.x; f < p.f_end; f += gridDim.x) {
     const int e0 = p.offsets[f], e1 = p.offsets[f + 1];
     float bias_g = 0.0f;
     float norm_sq = 0.0f;
@@ -508,7 +508,11 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
 
 int sparse_grad_adam_launch(const GradAdamParams& p, cudaStream_t stream) {
   if (p.d % 4 != 0) return (int)cudaErrorInvalidValue;
-  int blocks = p.F < 148 * 8 ? p.F : 148 * 8;
+  const int rows = p.f_end - p.f_begin;
+  if (rows <= 0) return 0;
+  // CTAs are persistent (grid-stride over feature rows): the grid size sets how many share an SM
+  const int cap = (p.ctas_per_sm >= 1 && p.ctas_per_sm <= 4) ? 148 * p.ctas_per_sm : 148 * 8;
+  int blocks = rows < cap ? rows : cap;
   sparse_grad_adam_kernel<<<blocks, GA_THREADS, 0, stream>>>(p);
   return (int)cudaGetLastError();
 }

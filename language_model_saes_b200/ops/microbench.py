@@ -78,7 +78,7 @@ def main(argv=None):
     if want("hidden3"):
         H3 = torch.empty(M, F, dtype=torch.bfloat16, device=dev)
         st = K.status_buffer(dev)
-        fn3 = lambda: K._ext().encoder_gemm(x, w, b, None, 1 | 4, 0, K.choose_splits(M, F), H3, None, None, st)  # noqa: E731
+        fn3 = lambda: K._ext().encoder_gemm(x, w, b, None, 1 | 4, 0, K.choose_splits(M, F), H3, None, None, st, 0, False)  # noqa: E731
         report("encoder_gemm_write_h_3stages", _timeit(fn3, a.iters, a.warmup, flush), flops=flops)
         del H3
     if want("hidden_pair"):

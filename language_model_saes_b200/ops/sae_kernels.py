@@ -156,7 +156,7 @@ def encoder_hidden(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, 
         return ref_hidden(x, w, bias).to(torch.bfloat16)
     M, N = x.shape[0], w.shape[0]
     H = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
-    _ext().encoder_gemm(x, w, bias, None, 1 | _pair_bit(pair), 0, choose_splits(M, N), H, None, None, status_buffer(x.device))
+    _ext().encoder_gemm(x, w, bias, None, 1 | _pair_bit(pair), 0, choose_splits(M, N), H, None, None, status_buffer(x.device), 0, False)
     return H
 
 
@@ -169,16 +169,27 @@ def encoder_topk_candidates(
     num_splits: int | None = None,
     H: torch.Tensor | None = None,
     pair: bool | None = None,
+    n_index_offset: int = 0,
+    resume: tuple[torch.Tensor, torch.Tensor] | None = None,
+    compact_smem: bool = False,
 ) -> tuple[torch.Tensor, torch.Tensor, int]:
-    """Run the GEMM with the fused top-k epilogue; returns (cand_val [M, C], cand_idx [M, C], C)."""
+    """Run the GEMM with the fused top-k epilogue; returns (cand_val [M, C], cand_idx [M, C], C).
+
+    A dictionary can be swept in several calls, one per chunk of its rows: pass the chunk as ``w`` (with the matching
+    slices of ``bias`` / ``gate``), its first row as ``n_index_offset`` and, from the second chunk on, the previous
+    call's ``(cand_val, cand_idx)`` as ``resume``; the buffers are updated in place and the result equals one sweep."""
     M, N = x.shape[0], w.shape[0]
     S = num_splits or choose_splits(M, N)
     KS = candidate_slots(k)
     C = S * KS
-    cand_val = torch.empty(M, C, dtype=torch.float32, device=x.device)
-    cand_idx = torch.empty(M, C, dtype=torch.int32, device=x.device)
-    mode = 2 | (1 if H is not None else 0) | _pair_bit(pair)
-    _ext().encoder_gemm(x, w, bias, gate, mode, k, S, H, cand_val, cand_idx, status_buffer(x.device))
+    if resume is not None:
+        cand_val, cand_idx = resume
+        assert cand_val.shape == (M, C) and cand_idx.shape == (M, C), "resume buffers do not match this launch's splits"
+    else:
+        cand_val = torch.empty(M, C, dtype=torch.float32, device=x.device)
+        cand_idx = torch.empty(M, C, dtype=torch.int32, device=x.device)
+    mode = 2 | (1 if H is not None else 0) | _pair_bit(pair) | (16 if compact_smem else 0)
+    _ext().encoder_gemm(x, w, bias, gate, mode, k, S, H, cand_val, cand_idx, status_buffer(x.device), n_index_offset, resume is not None)
     return cand_val, cand_idx, C
 
 
@@ -235,7 +246,7 @@ def encoder_topk(
         cv, ci, _ = encoder_topk_candidates(x, w, bias, gate, k, H=H, pair=pair)
         idx, act = topk_merge(cv, ci, k, gate)
     else:
-        _ext().encoder_gemm(x, w, bias, None, 1 | _pair_bit(pair), 0, choose_splits(M, N), H, None, None, status_buffer(x.device))
+        _ext().encoder_gemm(x, w, bias, None, 1 | _pair_bit(pair), 0, choose_splits(M, N), H, None, None, status_buffer(x.device), 0, False)
         idx, act = row_topk(H, k, gate, None)
     return (idx, act, H) if return_hidden else (idx, act)
 
@@ -437,8 +448,11 @@ def sparse_grad_adam(
     eps,
     step,
     update=True,
+    f_range: tuple[int, int] | None = None,
+    ctas_per_sm: int = 0,
 ):
-    """Rebuild the two sparse gradient rows per feature and apply Adam in the same pass (in place)."""
+    """Rebuild the two sparse gradient rows per feature and apply Adam in the same pass (in place). ``f_range``
+    restricts the launch to feature rows ``[begin, end)`` (the CUDA path only)."""
     if not WD.is_cuda:
         idx_like = torch.full((act.numel(),), -1, dtype=torch.int64)
         off = groups.offsets.long()
@@ -461,7 +475,7 @@ def sparse_grad_adam(
         return
     _ext().sparse_grad_adam(
         groups.offsets, groups.entries, act, dact, x, dxhat, WD, mD, vD, WD_bf16, WE, mE, vE, WE_bf16, bE, mbE, vbE,
-        dec_norm, grad_mul, grad_sq_sum, lr, beta1, beta2, eps, step, update,
+        dec_norm, grad_mul, grad_sq_sum, lr, beta1, beta2, eps, step, update, *(f_range if f_range is not None else (0, -1)), ctas_per_sm,
     )  # fmt: skip
 
 

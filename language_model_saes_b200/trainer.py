@@ -557,6 +557,8 @@ class Trainer:
     @timer.time("save_checkpoint")
     def _maybe_save_sae_checkpoint(self, sae: SparseDictionary):
         if self.checkpoint_thresholds and self.cur_step >= self.checkpoint_thresholds[0]:
+            if self.fused is not None:
+                self.fused.join()
             sae.save_checkpoint(os.path.join(self.cfg.exp_result_path, "checkpoints", f"{self.cur_step}.safetensors"))
             self.checkpoint_thresholds.pop(0)
 
@@ -608,6 +610,8 @@ class Trainer:
                         bar.set_description(f"loss: {float(loss):.2f}")
                     if eval_fn is not None and (self.cur_step + 1) % self.cfg.eval_frequency == 0:
                         with timer.time("evaluation"):
+                            if self.fused is not None:
+                                self.fused.join()
                             eval_fn(sae)
                     self.cur_step += 1
                     mask = batch.get("mask")
@@ -627,6 +631,8 @@ class Trainer:
             raise
         finally:
             bar.close()
+            if self.fused is not None:
+                self.fused.join()  # the last update may still be running on its own stream
         return None
 
     @staticmethod

@@ -35,12 +35,16 @@ def _data(n, B, d, rank=32):
     return out
 
 
+@pytest.mark.parametrize("chunks", [1, 3])
 @pytest.mark.parametrize("gate,bias,k", [(True, True, 16), (False, False, 8), (True, True, 50), (True, True, 100)])
-def test_fused_matches_autograd(gate, bias, k):
+def test_fused_matches_autograd(gate, bias, k, chunks):
+    # chunks > 1: the update runs per feature chunk on its own stream and the next step's encoder GEMM follows it
+    # chunk by chunk; results must not depend on it
     d, B, steps, lr = 256, 512, 12, 1e-3
     ref = _model(d=d, k=k, gate=gate, bias=bias)
     fused_model = copy.deepcopy(ref)
-    engine = FusedTopKSAEStep(fused_model)
+    engine = FusedTopKSAEStep(fused_model, overlap_chunks=chunks)
+    assert len(engine.chunks) == chunks
     data = _data(steps, B, d)
     opt = torch.optim.Adam(ref.parameters(), lr=lr)
     ref_losses, fused_losses = [], []
@@ -53,6 +57,7 @@ def test_fused_matches_autograd(gate, bias, k):
         opt.step()
         ref_losses.append(float(loss.detach()))
         fused_losses.append(float(engine.step(x, x, k, lr)))
+    engine.join()
     K.check_status(torch.device("cuda"))
     r, f = torch.tensor(ref_losses), torch.tensor(fused_losses)
     assert torch.allclose(r, f, rtol=3e-2), (ref_losses, fused_losses)

@@ -49,8 +49,10 @@ def test_peer_memory_step_matches_nccl_and_single_gpu():
         dist.broadcast(x, src=0)
 
     def run(model, comm):
-        eng = FusedTopKSAEStep(model, comm=comm)
-        return torch.stack([eng.step(x, x, k, lr) for x in xs])
+        eng = FusedTopKSAEStep(model, comm=comm, overlap_chunks=2)
+        out = torch.stack([eng.step(x, x, k, lr) for x in xs])
+        eng.join()
+        return out
 
     single = SparseAutoEncoder(full.cfg.model_copy())
     single.load_full_state_dict(full.full_state_dict())
