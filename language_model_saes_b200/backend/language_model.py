@@ -253,6 +253,31 @@ class HookedLanguageModel(_TokenizerMixin, HookedTransformer, LanguageModel):
         model.device = next(model.parameters()).device
         return model  # type: ignore[return-value]
 
+    # ---- circuit tracing (the functions live in ``circuits``; the reference exposes them as model methods) ----
+    def apply_saes(self, saes):
+        """Context manager: splice sparse dictionaries into the forward pass (``circuits.hooks.apply_saes``)."""
+        from ..circuits.hooks import apply_saes
+
+        return apply_saes(self, saes)
+
+    def detach_at(self, hook_points: list[str]):
+        """Context manager: cut the autograd graph at hook points (``circuits.hooks.detach_at``)."""
+        from ..circuits.hooks import detach_at
+
+        return detach_at(self, hook_points)
+
+    def attribute(self, inputs, replacement_modules, **kwargs):
+        """Attribution graph of one prompt (``circuits.attribution.attribute``)."""
+        from ..circuits.attribution import attribute
+
+        return attribute(self, inputs, replacement_modules, **kwargs)
+
+    def qk_trace(self, inputs, replacement_modules, lorsa_features, **kwargs):
+        """QK tracing of attention-dictionary features (``circuits.attribution.qk_trace``)."""
+        from ..circuits.attribution import qk_trace
+
+        return qk_trace(self, inputs, replacement_modules, lorsa_features, **kwargs)
+
     @torch.no_grad()
     def to_activations(self, raw: dict[str, Any], hook_points: list[str], n_context: Optional[int] = None) -> dict[str, torch.Tensor]:
         tokens = self._common_context(self._tokens_of(raw, self.device), n_context, self.device_mesh)

@@ -74,3 +74,20 @@ def test_create_show_remove_roundtrip(tiny_lm_workspace, tmp_path):
     assert client.get_feature("toy-sae", "ser", 0).analyses == []
     assert runner.invoke(app, ["remove", "sae", "toy-sae", "-s", "ser", *common]).exit_code == 0
     assert client.get_sae("toy-sae", "ser") is None
+
+
+def test_public_names_and_alias_packages():
+    import llamascopium
+    import lm_saes
+
+    import language_model_saes_b200 as L
+
+    for name in L.__all__:
+        assert getattr(llamascopium, name) is getattr(L, name) and getattr(lm_saes, name) is getattr(L, name)
+    from llamascopium.models.sae import SparseAutoEncoder
+    from lm_saes.circuits.attribution import attribute
+
+    assert SparseAutoEncoder is L.SparseAutoEncoder and attribute is L.attribute
+    assert L.TransformerLensLanguageModel is L.HookedLanguageModel
+    for method in ("apply_saes", "detach_at", "attribute", "qk_trace", "run_with_cache_until", "run_with_ref_cache", "trace", "to_activations"):
+        assert callable(getattr(L.HookedLanguageModel, method))
