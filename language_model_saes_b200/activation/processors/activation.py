@@ -22,6 +22,10 @@ from .core import BaseActivationProcessor
 class BufferShuffleConfig(BaseConfig):
     perm_seed: int = 42
     generator_device: str | None = None
+    cross_rank: bool = False
+    """Under data parallelism, also permute rows ACROSS the data-parallel ranks each time the buffer is shuffled (CUDA
+    tensors only; an all-to-all over NVLink peer memory, ``parallel.symm.ShuffleComm``). Off: every rank shuffles
+    only what it generated itself, as the reference does."""
 
 
 def _rows(d: dict[str, Any]) -> int:
@@ -73,13 +77,62 @@ class ActivationBuffer:
         batch = {k: _cat([d[k] for d in taken]) for k in taken[0].keys()}
         return batch, ActivationBuffer(rest, self.device_mesh, self.generator)
 
-    def shuffle(self) -> "ActivationBuffer":
-        """Seeded random permutation of the rows held by this rank."""
+    def shuffle(self, cross_rank: "CrossRankShuffler | None" = None) -> "ActivationBuffer":
+        """Seeded random permutation of the rows held by this rank; with ``cross_rank`` the rows are then permuted
+        across the data-parallel ranks too."""
         data = self.consume()
         assert all(isinstance(v, torch.Tensor) for v in data.values()), "All data must be tensors to perform shuffling"
         n = _rows(data)
         perm = torch.randperm(n, generator=self.generator, device=self.generator.device)
-        return ActivationBuffer([{k: v[perm.to(v.device)] for k, v in data.items()}], self.device_mesh, self.generator)
+        data = {k: v[perm.to(v.device)] for k, v in data.items()}
+        if cross_rank is not None:
+            data = cross_rank(data)
+        return ActivationBuffer([data], self.device_mesh, self.generator)
+
+
+class CrossRankShuffler:
+    """Mixes the shuffle buffers of the data-parallel ranks: the first ``m`` rows of every rank (``m`` = the smallest
+    buffer length among the ranks) go through one seeded global permutation; rows beyond ``m`` stay where they are.
+    All tensors of a record move with the same permutation. Rows whose byte size is not a multiple of 16 (token ids,
+    masks) are padded for the transfer."""
+
+    def __init__(self, device_mesh, seed: int, capacity_rows: int):
+        self.group = device_mesh.get_group("data")
+        self.seed = seed
+        self.capacity = capacity_rows
+        self.comm = None
+        self.calls = 0
+
+    def __call__(self, data: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
+        import torch.distributed as dist
+
+        from ...parallel.symm import ShuffleComm
+
+        first = next(iter(data.values()))
+        assert first.is_cuda, "the cross-rank shuffle moves rows between GPUs: keep the buffer on the device"
+        n = torch.tensor([_rows(data)], device=first.device)
+        dist.all_reduce(n, op=dist.ReduceOp.MIN, group=self.group)
+        m = int(n)
+        if m == 0:
+            return data
+        row_bytes = {k: -(-(v[0].numel() * v.element_size()) // 16) * 16 for k, v in data.items()}
+        if self.comm is None or m > self.comm.rows_per_rank or max(row_bytes.values()) > self.comm.max_row_bytes:
+            self.comm = ShuffleComm(self.group, first.device, max(m, self.capacity), max(row_bytes.values()))
+        self.calls += 1
+        perm = self.comm.permutation(m, self.seed + self.calls)
+        out = {}
+        for k, v in data.items():
+            head = v[:m].contiguous()
+            raw = head.view(torch.uint8).reshape(m, -1)
+            pad = row_bytes[k] - raw.shape[1]
+            if pad:
+                raw = torch.nn.functional.pad(raw, (0, pad))
+            mixed = self.comm.shuffle(raw, 0, perm=perm)
+            if pad:
+                mixed = mixed[:, : raw.shape[1] - pad].contiguous()
+            mixed = mixed.view(v.dtype).reshape(m, *v.shape[1:])
+            out[k] = mixed if v.shape[0] == m else torch.cat([mixed, v[m:]], dim=0)
+        return out
 
 
 class ActivationGenerator(BaseActivationProcessor[Iterable[dict[str, Any]], Iterable[dict[str, Any]]]):
@@ -134,9 +187,13 @@ class ActivationBatchler(BaseActivationProcessor[Iterable[dict[str, Any]], Itera
         self.buffer_size = buffer_size
         self.device_mesh = device_mesh
         self.perm_generator = torch.Generator()
+        self.cross_rank: CrossRankShuffler | None = None
         if buffer_shuffle_config is not None:
             self.perm_generator = torch.Generator(buffer_shuffle_config.generator_device or "cpu")
             self.perm_generator.manual_seed(buffer_shuffle_config.perm_seed)
+            dp = mesh_dim_size(device_mesh, "data")
+            if buffer_shuffle_config.cross_rank and dp > 1 and buffer_size is not None:
+                self.cross_rank = CrossRankShuffler(device_mesh, buffer_shuffle_config.perm_seed, max(buffer_size // dp, 1) * 2)
 
     def process(self, data: Iterable[dict[str, Any]], **kwargs) -> Iterable[dict[str, torch.Tensor]]:
         buffer = ActivationBuffer(device_mesh=self.device_mesh, generator=self.perm_generator)
@@ -149,7 +206,7 @@ class ActivationBatchler(BaseActivationProcessor[Iterable[dict[str, Any]], Itera
             buffer = buffer.cat(d)
             if local_cap is not None:
                 if len(buffer) >= local_cap:
-                    buffer = buffer.shuffle()
+                    buffer = buffer.shuffle(self.cross_rank)
                     while len(buffer) >= local_cap // 2 and len(buffer) >= local_batch:
                         batch, buffer = buffer.yield_batch(self.batch_size)
                         yield batch

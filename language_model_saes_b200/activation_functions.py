@@ -37,6 +37,40 @@ class STEFunction(torch.autograd.Function):
         return grad_output * mask, grad_thr, None, None
 
 
+class FusedSTEFunction(torch.autograd.Function):
+    """The same function as ``STEFunction`` for thresholds that cover the trailing dimensions of a contiguous CUDA
+    input, as two streaming sm_100a kernels (``ops/csrc/jumprelu.cu``): the mask is never materialised, the backward
+    reads ``x`` and ``dy`` once, writes ``dx`` once and sends the rare window hits to fp32 atomics. Takes
+    ``log_theta`` (the parameter itself), so ``exp`` and its chain rule are inside the kernels too."""
+
+    @staticmethod
+    def forward(ctx, input: torch.Tensor, log_threshold: torch.Tensor, window: float):
+        from .ops import native
+
+        ctx.save_for_backward(input, log_threshold)
+        ctx.window = float(window)
+        return native.load().jumprelu(input, log_threshold.contiguous(), None, None, float(window))
+
+    @staticmethod
+    def backward(ctx, grad_output: torch.Tensor):
+        from .ops import native
+
+        input, log_threshold = ctx.saved_tensors
+        dlog = torch.zeros(log_threshold.numel(), dtype=torch.float32, device=input.device)
+        dx = native.load().jumprelu(input, log_threshold.contiguous(), grad_output.contiguous(), dlog, ctx.window)
+        return dx, dlog.view_as(log_threshold).to(log_threshold.dtype), None
+
+
+def _fusable(input: torch.Tensor, log_threshold: torch.Tensor, keep: tuple[int, ...]) -> bool:
+    n = log_threshold.ndim
+    return (
+        input.is_cuda and input.is_contiguous() and input.dtype in (torch.float32, torch.bfloat16)
+        and log_threshold.numel() % 4 == 0 and log_threshold.numel() > 0
+        and tuple(input.shape[-n:]) == tuple(log_threshold.shape)
+        and tuple(sorted(d % input.ndim for d in keep)) == tuple(range(input.ndim - n, input.ndim))
+    )  # fmt: skip
+
+
 class JumpReLU(torch.nn.Module):
     def __init__(
         self,
@@ -61,9 +95,11 @@ class JumpReLU(torch.nn.Module):
         self.log_jumprelu_threshold = torch.nn.Parameter(torch.empty(local_shape, device=device, dtype=dtype))
 
     def forward(self, input: torch.Tensor) -> torch.Tensor:
-        out = STEFunction.apply(
-            input.to(self.dtype), self.log_jumprelu_threshold.exp(), self.jumprelu_threshold_window, self.dims_to_keep_in_bwd
-        )
+        x = input.to(self.dtype)
+        if _fusable(x, self.log_jumprelu_threshold, self.dims_to_keep_in_bwd):
+            out = FusedSTEFunction.apply(x, self.log_jumprelu_threshold, self.jumprelu_threshold_window)
+        else:
+            out = STEFunction.apply(x, self.log_jumprelu_threshold.exp(), self.jumprelu_threshold_window, self.dims_to_keep_in_bwd)
         return out.to(input.dtype)
 
     def get_jumprelu_threshold(self) -> torch.Tensor:

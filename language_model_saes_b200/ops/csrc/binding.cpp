@@ -348,6 +348,31 @@ void row_norm_shadow(const Tensor& W, const c10::optional<Tensor>& norm, const c
              "row_norm_shadow launch");
 }
 
+// ---- JumpReLU --------------------------------------------------------------------------------------
+// forward: returns y; backward (dy given): returns dx and accumulates d log_theta into `dlog` (fp32 [P], zeroed here).
+Tensor jumprelu(const Tensor& x, const Tensor& log_theta, const c10::optional<Tensor>& dy, const c10::optional<Tensor>& dlog,
+                double window) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && log_theta.is_contiguous(), "jumprelu needs contiguous CUDA tensors");
+  TORCH_CHECK(x.scalar_type() == log_theta.scalar_type(), "x and log_theta must share a dtype");
+  const int dtype = x.scalar_type() == torch::kFloat32 ? 0 : (x.scalar_type() == torch::kBFloat16 ? 1 : -1);
+  TORCH_CHECK(dtype >= 0, "jumprelu supports fp32 and bf16");
+  const int64_t P = log_theta.numel();
+  TORCH_CHECK(P > 0 && P % 4 == 0 && x.numel() % P == 0, "thresholds must cover the trailing dimensions of x (multiple of 4)");
+  const c10::cuda::CUDAGuard guard(x.device());
+  Tensor out = torch::empty_like(x);
+  const bool bwd = dy.has_value();
+  float* dlog_ptr = nullptr;
+  if (bwd) {
+    TORCH_CHECK(dy->is_contiguous() && dy->scalar_type() == x.scalar_type() && dy->numel() == x.numel());
+    TORCH_CHECK(dlog.has_value() && dlog->scalar_type() == torch::kFloat32 && dlog->numel() == P && dlog->is_contiguous());
+    dlog_ptr = dlog->data_ptr<float>();
+  }
+  check_cuda(lmsae::jumprelu_launch(dtype, x.data_ptr(), log_theta.data_ptr(), bwd ? dy->data_ptr() : nullptr, out.data_ptr(),
+                                    dlog_ptr, x.numel(), (int)P, (float)window, bwd ? 1 : 0, at::cuda::getCurrentCUDAStream()),
+             "jumprelu launch");
+  return out;
+}
+
 // ---- peer-memory collectives -----------------------------------------------------------------------
 // `table` = [world, rank, flags_off, cand_val_off, cand_idx_off, partial_off, dxhat_off, ptr_0 .. ptr_{world-1}]
 lmsae::PeerTable make_peer_table(const std::vector<int64_t>& table) {
@@ -378,6 +403,23 @@ void comm_push_candidates(const std::vector<int64_t>& table, const Tensor& val, 
                                            reinterpret_cast<unsigned*>(done_counter.data_ptr<int>()),
                                            at::cuda::getCurrentCUDAStream()),
              "push_candidates launch");
+}
+
+// Row all-to-all: `src` [n_local, row_bytes] (any dtype, contiguous), `dest` int64 [n_local] global positions.
+void comm_shuffle_rows(const std::vector<int64_t>& table, const Tensor& src, const Tensor& dest, int64_t rows_per_rank,
+                       int64_t recv_off, int64_t phase, int64_t epoch, const Tensor& done_counter) {
+  CHECK_T(dest, torch::kInt64);
+  CHECK_T(done_counter, torch::kInt32);
+  TORCH_CHECK(src.is_cuda() && src.is_contiguous() && src.dim() >= 1 && dest.numel() == src.size(0));
+  const int64_t row_bytes = src.size(0) > 0 ? (int64_t)(src.numel() / src.size(0)) * (int64_t)src.element_size() : 16;
+  TORCH_CHECK(row_bytes % 16 == 0, "rows must be a multiple of 16 bytes");
+  TORCH_CHECK(reinterpret_cast<uintptr_t>(src.data_ptr()) % 16 == 0 && recv_off % 16 == 0, "16-byte alignment");
+  const c10::cuda::CUDAGuard guard(src.device());
+  check_cuda(lmsae::shuffle_rows_launch(make_peer_table(table), src.data_ptr(), reinterpret_cast<const long long*>(dest.data_ptr<int64_t>()),
+                                        (int)src.size(0), (int)rows_per_rank, (int)row_bytes, (long long)recv_off, (int)phase,
+                                        (uint32_t)epoch, reinterpret_cast<unsigned*>(done_counter.data_ptr<int>()),
+                                        at::cuda::getCurrentCUDAStream()),
+             "shuffle_rows launch");
 }
 
 void comm_wait(const std::vector<int64_t>& table, int64_t phase, int64_t epoch, const Tensor& status) {
@@ -431,10 +473,12 @@ void comm_reduce_loss_push(const std::vector<int64_t>& table, int64_t B, int64_t
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("comm_push_candidates", &comm_push_candidates);
   m.def("comm_wait", &comm_wait);
+  m.def("comm_shuffle_rows", &comm_shuffle_rows);
   m.def("comm_decode_scatter", &comm_decode_scatter);
   m.def("comm_reduce_loss_push", &comm_reduce_loss_push);
   m.doc() = "sm_100a kernels for sparse-dictionary training";
   m.def("encoder_gemm", &encoder_gemm);
+  m.def("jumprelu", &jumprelu);
   m.def("topk_merge", &topk_merge);
   m.def("row_topk", &row_topk);
   m.def("sparse_decode", &sparse_decode);

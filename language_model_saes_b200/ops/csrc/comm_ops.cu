@@ -220,6 +220,38 @@ reduce_loss_push_kernel(const PeerTable pt, int B, int d, const __nv_bfloat16* _
 }
 
 // ---- launchers ----------------------------------------------------------------------------------
+// ---------------------------------------------------------------------------------------------
+// Row all-to-all for the activation shuffle: local row i goes to global position dest[i] of the logical
+// [world * rows_per_rank] array, i.e. to slot dest[i] % rows_per_rank of rank dest[i] / rows_per_rank. Every CTA
+// copies whole rows with 16-byte peer stores (a row of d_model 4096 bf16 values is 8 KB); the last CTA to finish
+// publishes the epoch in every peer's flag slot. `dest` restricted to one rank is injective, and the union over
+// ranks is a permutation, so no two stores touch the same bytes.
+__global__ void __launch_bounds__(256)
+shuffle_rows_kernel(const PeerTable pt, const uint4* __restrict__ src, const long long* __restrict__ dest, int n_local,
+                    int rows_per_rank, int vec_per_row, long long recv_off, int phase, uint32_t epoch,
+                    unsigned* done_counter) {
+  for (int i = blockIdx.x; i < n_local; i += gridDim.x) {
+    const long long g = dest[i];
+    const int r = (int)(g / rows_per_rank);
+    const long long slot = g - (long long)r * rows_per_rank;
+    if (r < 0 || r >= pt.world) continue;  // never for a valid permutation; keeps a bad index off the wire
+    uint4* dst = reinterpret_cast<uint4*>(pt.base[r] + recv_off) + slot * vec_per_row;
+    const uint4* s = src + (long long)i * vec_per_row;
+    for (int v = threadIdx.x; v < vec_per_row; v += 256) dst[v] = __ldg(s + v);
+  }
+  signal_peers_when_grid_done(pt, phase, epoch, done_counter);
+}
+
+int shuffle_rows_launch(const PeerTable& pt, const void* src, const long long* dest, int n_local, int rows_per_rank,
+                        int row_bytes, long long recv_off, int phase, uint32_t epoch, unsigned* done_counter,
+                        cudaStream_t stream) {
+  if (row_bytes % 16 != 0 || n_local > rows_per_rank || phase < 0 || phase >= kNumPhases) return (int)cudaErrorInvalidValue;
+  int blocks = n_local < 148 * 4 ? (n_local > 0 ? n_local : 1) : 148 * 4;
+  shuffle_rows_kernel<<<blocks, 256, 0, stream>>>(pt, reinterpret_cast<const uint4*>(src), dest, n_local, rows_per_rank,
+                                                  row_bytes / 16, recv_off, phase, epoch, done_counter);
+  return (int)cudaGetLastError();
+}
+
 int push_candidates_launch(const PeerTable& pt, const float* val, const int* idx, int B, int k, uint32_t epoch,
                            unsigned* done_counter, cudaStream_t stream) {
   int blocks = (int)(((long long)B * k + 255) / 256);

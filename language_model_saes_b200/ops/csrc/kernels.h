@@ -88,6 +88,10 @@ int adam_flat_launch(float* p, const float* g, float* m, float* v, long long n, 
                      __nv_bfloat16* shadow, float* grad_sq_sum, int update, cudaStream_t stream);
 int row_norm_shadow_launch(const float* W, int F, int d, float* norm, __nv_bfloat16* shadow, cudaStream_t stream);
 
+// ---- elementwise (jumprelu.cu) ---------------------------------------------------------------------
+int jumprelu_launch(int dtype, const void* x, const void* log_theta, const void* dy, void* out, float* dlog, long long n,
+                    int P, float window, int backward, cudaStream_t stream);
+
 // ---- peer-memory collectives (comm_ops.cu) -------------------------------------------------------
 constexpr int kMaxPeers = 8;
 enum CommPhase : int { kPhaseCand = 0, kPhasePartial = 1, kPhaseDxhat = 2, kNumPhases = 4 };
@@ -105,6 +109,9 @@ struct PeerTable {
 
 int push_candidates_launch(const PeerTable& pt, const float* val, const int* idx, int B, int k, uint32_t epoch,
                            unsigned* done_counter, cudaStream_t stream);
+int shuffle_rows_launch(const PeerTable& pt, const void* src, const long long* dest, int n_local, int rows_per_rank,
+                        int row_bytes, long long recv_off, int phase, uint32_t epoch, unsigned* done_counter,
+                        cudaStream_t stream);
 int wait_flags_launch(const PeerTable& pt, int phase, uint32_t epoch, int* status, cudaStream_t stream);
 int sparse_decode_scatter_launch(const PeerTable& pt, const int* idx, const float* val, int B, int k, int d,
                                  const __nv_bfloat16* W, uint32_t epoch, unsigned* done_counter, cudaStream_t stream);

@@ -103,3 +103,67 @@ class SymmComm:
                                   self.epoch, self.done_counter, st)  # fmt: skip
         ext.comm_wait(self.table, PHASE_DXHAT, self.epoch, st)
         return self._view(self.dxhat_off, (self.B, self.d), torch.bfloat16), xhat
+
+
+PHASE_SHUFFLE = 3
+
+
+class ShuffleComm:
+    """All-to-all of rows between the ranks of a group by direct peer stores: ``shuffle(x, seed)`` applies ONE seeded
+    permutation to the logical concatenation of every rank's rows and returns this rank's slice of the result.
+
+    The reference shuffles its activation buffer per rank only and refuses to do it under a device mesh
+    (activation/processors/activation.py:144-163 of the reference project); with this, data-parallel ranks mix their
+    buffers, so a batch is a sample of what ALL ranks generated. Two landing buffers alternate between calls: a peer
+    can start call t+1 while this rank still copies call t's result out, and nobody can be two calls ahead of anyone
+    because every call waits for all peers' flags.
+    """
+
+    def __init__(self, group: dist.ProcessGroup, device: torch.device, rows_per_rank: int, max_row_bytes: int):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group, self.device = group, device
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        assert self.world <= _MAX_PEERS
+        self.rows_per_rank = rows_per_rank
+        self.max_row_bytes = _align(max_row_bytes, 16)
+        self.flags_off = 0
+        self.recv_off = [_align(_NUM_PHASES * _MAX_PEERS * 4)]
+        self.recv_off.append(_align(self.recv_off[0] + rows_per_rank * self.max_row_bytes))
+        self.nbytes = _align(self.recv_off[1] + rows_per_rank * self.max_row_bytes)
+        try:
+            symm_mem.enable_symm_mem_for_group(group.group_name)
+        except Exception:  # noqa: BLE001
+            pass
+        self.buf = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        self.handle = symm_mem.rendezvous(self.buf, group.group_name)
+        self.table = [self.world, self.rank, self.flags_off, 0, 0, 0, 0, *[int(p) for p in self.handle.buffer_ptrs]]
+        self.done_counter = torch.zeros(1, dtype=torch.int32, device=device)
+        self.epoch = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)
+
+    def permutation(self, n: int, seed: int) -> torch.Tensor:
+        """The permutation of ``world * n`` positions that every rank derives from ``seed`` (CPU generator)."""
+        g = torch.Generator().manual_seed(int(seed))
+        return torch.randperm(self.world * n, generator=g)
+
+    def shuffle(self, x: torch.Tensor, seed: int, perm: torch.Tensor | None = None) -> torch.Tensor:
+        """``x``: this rank's ``[n, ...]`` rows (same ``n`` on every rank, ``n <= rows_per_rank``, rows a multiple of
+        16 bytes). Row ``i`` of rank ``r`` lands at global position ``perm[r * n + i]``."""
+        n = x.shape[0]
+        assert n <= self.rows_per_rank and x.is_cuda
+        x = x.contiguous()
+        row_bytes = (x.numel() // max(n, 1)) * x.element_size()
+        assert row_bytes % 16 == 0 and row_bytes <= self.max_row_bytes, f"row of {row_bytes} bytes does not fit"
+        if perm is None:
+            perm = self.permutation(n, seed)
+        dest = perm[self.rank * n : (self.rank + 1) * n].to(self.device, non_blocking=True)
+        self.epoch += 1
+        off = self.recv_off[self.epoch & 1]
+        ext = K._ext()
+        ext.comm_shuffle_rows(self.table, x, dest, n, off, PHASE_SHUFFLE, self.epoch, self.done_counter)
+        ext.comm_wait(self.table, PHASE_SHUFFLE, self.epoch, K.status_buffer(self.device))
+        out = self.buf[off : off + n * row_bytes].view(x.dtype).view(n, *x.shape[1:])
+        return out.clone()

@@ -181,3 +181,28 @@ def test_dense_helpers():
     sh = torch.empty(77, 130, dtype=torch.bfloat16, device=DEV)
     K.row_norm_shadow(W, n, sh)
     assert torch.allclose(n, W.norm(dim=1), rtol=1e-5) and torch.equal(sh, W.to(torch.bfloat16))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape,tshape", [((64, 1024), (1024,)), ((8, 16, 512), (512,)), ((32, 3, 256), (3, 256))])
+def test_jumprelu_fused_matches_autograd(dtype, shape, tshape):
+    from language_model_saes_b200.activation_functions import FusedSTEFunction, STEFunction
+
+    g = torch.Generator(device="cpu").manual_seed(0)
+    x = (torch.randn(shape, generator=g) * 0.5 + 0.3).to(dtype).to(DEV)
+    log_t = (torch.randn(tshape, generator=g) * 0.3 - 1.0).to(dtype).to(DEV)
+    dy = torch.randn(shape, generator=g).to(dtype).to(DEV)
+    window = 0.5  # wide window: many hits, a strict test of the threshold gradient
+    keep = tuple(range(-len(tshape), 0))
+
+    xr, lr = x.clone().requires_grad_(), log_t.clone().requires_grad_()
+    yr = STEFunction.apply(xr, lr.exp(), window, keep)
+    yr.backward(dy)
+    xf, lf = x.clone().requires_grad_(), log_t.clone().requires_grad_()
+    yf = FusedSTEFunction.apply(xf, lf, window)
+    yf.backward(dy)
+    assert torch.equal(yf, yr)
+    assert torch.equal(xf.grad, xr.grad)
+    tol = dict(rtol=1e-4, atol=1e-4) if dtype == torch.float32 else dict(rtol=5e-2, atol=5e-2)
+    assert torch.allclose(lf.grad.float(), lr.grad.float(), **tol), (lf.grad.float() - lr.grad.float()).abs().max()
+    assert lf.grad.abs().sum() > 0

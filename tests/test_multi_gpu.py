@@ -92,3 +92,48 @@ def test_peer_flag_wait_times_out_with_status_code():
         K.check_status(dev)
     # the context is still usable afterwards
     assert float((torch.ones(8, device=dev) * 2).sum()) == 16.0
+
+
+@needs2
+@distributed_test(nproc_per_node=2, backend="nccl")
+def test_shuffle_all_to_all_is_the_seeded_global_permutation():
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    from language_model_saes_b200.activation.processors.activation import CrossRankShuffler
+    from language_model_saes_b200.ops import sae_kernels as K
+    from language_model_saes_b200.parallel.mesh import build_mesh
+    from language_model_saes_b200.parallel.symm import ShuffleComm
+
+    rank = dist.get_rank()
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    mesh = build_mesh("cuda", (2, 1), ("data", "model"))
+    n, d = 1000, 256
+    comm = ShuffleComm(mesh.get_group("data"), dev, rows_per_rank=1024, max_row_bytes=d * 2)
+    for call in range(3):  # three calls: both landing buffers and their re-use
+        x = (torch.arange(n, device=dev)[:, None] + 10_000 * rank + 100_000 * call).expand(n, d).to(torch.bfloat16).contiguous()
+        y = comm.shuffle(x, seed=7 + call)
+        K.check_status(dev)
+        both_x = [torch.empty_like(x) for _ in range(2)]
+        both_y = [torch.empty_like(y) for _ in range(2)]
+        dist.all_gather(both_x, x)
+        dist.all_gather(both_y, y)
+        X, Y = torch.cat(both_x), torch.cat(both_y)
+        perm = comm.permutation(n, 7 + call).to(dev)
+        want = torch.empty_like(X)
+        want[perm] = X
+        assert torch.equal(Y, want)
+
+    # through the activation buffer: uneven buffers, a tensor with 8-byte rows
+    shuf = CrossRankShuffler(mesh, seed=3, capacity_rows=64)
+    m_local = 40 + 8 * rank
+    data = {"h": torch.randn(m_local, 64, device=dev), "tokens": torch.arange(m_local, device=dev) + 1000 * rank}
+    data["h"][:, 0] = data["tokens"].float()
+    out = shuf(data)
+    K.check_status(dev)
+    assert out["h"].shape == data["h"].shape and out["tokens"].shape == data["tokens"].shape
+    assert torch.equal(out["h"][:, 0], out["tokens"].float())  # rows travel whole, all tensors with the same permutation
+    assert torch.equal(out["tokens"][40:], data["tokens"][40:])  # rows beyond the common length stay
+    mixed = [torch.empty(40, dtype=torch.long, device=dev) for _ in range(2)]
+    dist.all_gather(mixed, out["tokens"][:40].contiguous())
+    assert sorted(torch.cat(mixed).tolist()) == sorted(list(range(40)) + list(range(1000, 1040)))
+    assert (out["tokens"][:40] >= 1000).any() and (out["tokens"][:40] < 1000).any()
