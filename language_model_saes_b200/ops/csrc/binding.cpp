@@ -232,6 +232,28 @@ void mse_loss_grad(const Tensor& xhat, const Tensor& label, const c10::optional<
              "mse_loss_grad launch");
 }
 
+void auxk_loss_grad(const Tensor& xhat, const Tensor& aux_rec, const Tensor& label, const c10::optional<Tensor>& bias,
+                    const c10::optional<Tensor>& row_weight, double grad_scale, double alpha, const Tensor& g_main,
+                    const Tensor& g_aux, const Tensor& loss_sum, const Tensor& aux_sum) {
+  CHECK_T(xhat, torch::kFloat32);
+  CHECK_T(aux_rec, torch::kFloat32);
+  CHECK_T(label, torch::kBFloat16);
+  CHECK_T(g_main, torch::kBFloat16);
+  CHECK_T(g_aux, torch::kBFloat16);
+  CHECK_T(loss_sum, torch::kFloat32);
+  CHECK_T(aux_sum, torch::kFloat32);
+  TORCH_CHECK(xhat.dim() == 2 && aux_rec.sizes() == xhat.sizes() && label.numel() == xhat.numel() &&
+              g_main.numel() == xhat.numel() && g_aux.numel() == xhat.numel());
+  const c10::cuda::CUDAGuard guard(xhat.device());
+  check_cuda(lmsae::auxk_loss_grad_launch(xhat.data_ptr<float>(), aux_rec.data_ptr<float>(),
+                                          reinterpret_cast<const __nv_bfloat16*>(label.data_ptr()), opt_ptr<const float>(bias),
+                                          opt_ptr<const float>(row_weight), (int)xhat.size(0), (int)xhat.size(1),
+                                          (float)grad_scale, (float)alpha, reinterpret_cast<__nv_bfloat16*>(g_main.data_ptr()),
+                                          reinterpret_cast<__nv_bfloat16*>(g_aux.data_ptr()), loss_sum.data_ptr<float>(),
+                                          aux_sum.data_ptr<float>(), at::cuda::getCurrentCUDAStream()),
+             "auxk_loss_grad launch");
+}
+
 void csc_build(const Tensor& idx, int64_t F, const Tensor& counts, const Tensor& offsets, const Tensor& cursor,
                const Tensor& entries, const Tensor& block_sums) {
   CHECK_T(idx, torch::kInt32);
@@ -267,7 +289,7 @@ void sparse_grad_adam(const Tensor& offsets, const Tensor& entries, const Tensor
                       const c10::optional<Tensor>& vbE, const c10::optional<Tensor>& dec_norm,
                       const c10::optional<Tensor>& grad_mul, const c10::optional<Tensor>& grad_sq_sum, double lr,
                       double beta1, double beta2, double eps, int64_t step, bool update, int64_t f_begin,
-                      int64_t f_end, int64_t ctas_per_sm) {
+                      int64_t f_end, int64_t ctas_per_sm, const c10::optional<Tensor>& dxhat_aux, int64_t k_main) {
   CHECK_T(offsets, torch::kInt32);
   CHECK_T(entries, torch::kInt32);
   CHECK_T(act, torch::kFloat32);
@@ -309,6 +331,9 @@ void sparse_grad_adam(const Tensor& offsets, const Tensor& entries, const Tensor
   p.f_begin = (int)f_begin;
   p.f_end = f_end < 0 ? p.F : (int)f_end;
   p.ctas_per_sm = (int)ctas_per_sm;
+  if (dxhat_aux.has_value()) { CHECK_T(*dxhat_aux, torch::kBFloat16); TORCH_CHECK(dxhat_aux->sizes() == dxhat.sizes()); }
+  p.dxhat_aux = dxhat_aux.has_value() ? reinterpret_cast<const __nv_bfloat16*>(dxhat_aux->data_ptr()) : nullptr;
+  p.k_main = (int)k_main;
   TORCH_CHECK(0 <= p.f_begin && p.f_begin <= p.f_end && p.f_end <= p.F, "feature range out of bounds");
   check_cuda(lmsae::sparse_grad_adam_launch(p, at::cuda::getCurrentCUDAStream()), "sparse_grad_adam launch");
 }
@@ -485,6 +510,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sparse_dact", &sparse_dact);
   m.def("mse_loss_grad", &mse_loss_grad);
   m.def("csc_build", &csc_build);
+  m.def("auxk_loss_grad", &auxk_loss_grad);
   m.def("sparse_grad_adam", &sparse_grad_adam);
   m.def("colsum_bf16", &colsum_bf16);
   m.def("adam_flat", &adam_flat);

@@ -269,6 +269,64 @@ int mse_loss_grad_launch(const float* xhat, const __nv_bfloat16* label, const fl
 }
 
 // ---------------------------------------------------------------------------------------------
+// Aux-K: losses and gradients of   l = |e|^2 + alpha |e - e_aux|^2   per row, with e = label - x_hat (x_hat from
+// the main codes) and e_aux the reconstruction of the residual from dead features
+// (models/sparse_dictionary.py:941-991 of the reference project; e is NOT detached there, so the auxiliary term
+// also pulls on x_hat). Outputs, per row scaled by grad_scale * row_weight:
+//   g_main = d l / d x_hat = (x_hat - label) - alpha * r,      g_aux = d l / d e_aux = -alpha * r,   r = e - e_aux
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+auxk_loss_grad_kernel(const float* __restrict__ xhat, const float* __restrict__ aux_rec,
+                      const __nv_bfloat16* __restrict__ label, const float* __restrict__ bias,
+                      const float* __restrict__ row_weight, int rows, int d, float grad_scale, float alpha,
+                      __nv_bfloat16* __restrict__ g_main, __nv_bfloat16* __restrict__ g_aux,
+                      float* __restrict__ loss_sum, float* __restrict__ aux_sum) {
+  __shared__ float s_red[2][8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float rw = row_weight != nullptr ? row_weight[row] : 1.0f;
+    const float sc = grad_scale * rw;
+    float sq = 0.0f, sq_aux = 0.0f;
+    for (int c = threadIdx.x; c < d; c += 256) {
+      const size_t o = (size_t)row * d + c;
+      float xh = xhat[o];
+      if (bias != nullptr) xh += bias[c];
+      const float e = __bfloat162float(label[o]) - xh;
+      const float r = e - aux_rec[o];
+      sq = fmaf(e, e, sq);
+      sq_aux = fmaf(r, r, sq_aux);
+      g_main[o] = __float2bfloat16(-(e + alpha * r) * sc);
+      g_aux[o] = __float2bfloat16(-alpha * r * sc);
+    }
+    sq = warp_sum(sq);
+    sq_aux = warp_sum(sq_aux);
+    __syncthreads();
+    if (lane == 0) { s_red[0][warp] = sq; s_red[1][warp] = sq_aux; }
+    __syncthreads();
+    if (warp == 0) {
+      float t = lane < 8 ? s_red[0][lane] : 0.0f, u = lane < 8 ? s_red[1][lane] : 0.0f;
+      t = warp_sum(t);
+      u = warp_sum(u);
+      if (lane == 0) {
+        atomicAdd(loss_sum, t * rw);
+        atomicAdd(aux_sum, alpha * u * rw);
+      }
+    }
+  }
+}
+
+int auxk_loss_grad_launch(const float* xhat, const float* aux_rec, const __nv_bfloat16* label, const float* bias,
+                          const float* row_weight, int rows, int d, float grad_scale, float alpha,
+                          __nv_bfloat16* g_main, __nv_bfloat16* g_aux, float* loss_sum, float* aux_sum,
+                          cudaStream_t stream) {
+  int blocks = rows < 148 * 8 ? rows : 148 * 8;
+  if (blocks <= 0) return 0;
+  auxk_loss_grad_kernel<<<blocks, 256, 0, stream>>>(xhat, aux_rec, label, bias, row_weight, rows, d, grad_scale, alpha,
+                                                    g_main, g_aux, loss_sum, aux_sum);
+  return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
 // group (row, slot) pairs by feature: counts -> offsets (exclusive scan) -> entries
 // ---------------------------------------------------------------------------------------------
 __global__ void csc_count_kernel(const int* __restrict__ idx, long long n, int F, int* __restrict__ counts) {
@@ -432,10 +490,12 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
         const int row = ent / p.k;
         const float a = p.act[ent];
         const float da = p.dact[ent];
+        // codes beyond the first k_main slots of a row (auxiliary codes) multiply the auxiliary output gradient
+        const __nv_bfloat16* gmat = (p.dxhat_aux != nullptr && ent - row * p.k >= p.k_main) ? p.dxhat_aux : p.dxhat;
         if (c0 == 0 && threadIdx.x == 0) bias_g += da;
         if (in) {
           const uint2 ux = __ldg(reinterpret_cast<const uint2*>(p.x + (size_t)row * p.d + c));
-          const uint2 ud = __ldg(reinterpret_cast<const uint2*>(p.dxhat + (size_t)row * p.d + c));
+          const uint2 ud = __ldg(reinterpret_cast<const uint2*>(gmat + (size_t)row * p.d + c));
           const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ux.x));
           const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ux.y));
           const float2 d01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ud.x));

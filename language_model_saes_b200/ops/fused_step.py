@@ -35,6 +35,22 @@ from ..parallel.mesh import mesh_dim_size, mesh_group, mesh_local_rank
 from . import sae_kernels as K
 
 
+class AuxK:
+    """State and settings of the Aux-K loss on the fused path: per-feature count of valid tokens since the feature
+    last fired; a feature is dead once the count reaches ``dead_threshold`` (trainer.py:403-454 of the reference)."""
+
+    def __init__(self, n_features: int, k_aux: int, coefficient: float, dead_threshold: float, device, counter: torch.Tensor | None = None):
+        self.k_aux, self.coefficient, self.dead_threshold = int(k_aux), float(coefficient), dead_threshold
+        self.tokens_since_last_activation = counter if counter is not None else torch.zeros(n_features, dtype=torch.long, device=device)
+        self.is_dead = self.tokens_since_last_activation >= dead_threshold
+
+    def update(self, fire_counts: torch.Tensor, n_valid_tokens) -> torch.Tensor:
+        c = self.tokens_since_last_activation
+        self.tokens_since_last_activation = torch.where(fire_counts > 0, torch.zeros_like(c), c + int(n_valid_tokens))
+        self.is_dead = self.tokens_since_last_activation >= self.dead_threshold
+        return self.is_dead
+
+
 class FusedTopKSAEStep:
     def __init__(self, sae, betas: tuple[float, float] = (0.9, 0.999), eps: float = 1e-8, comm=None,
                  overlap_chunks: int | None = None):
@@ -71,6 +87,9 @@ class FusedTopKSAEStep:
         }  # fmt: skip
         self.groups: K.FeatureGroups | None = None
         self.loss_sum = z(1)
+        self.aux_sum = z(1)
+        self.last_aux_loss: torch.Tensor | None = None
+        self.main_counts: torch.Tensor | None = None
         self.grad_sq = z(1)
         self.t = 0
         # ---- update / next-encode overlap ----
@@ -116,7 +135,8 @@ class FusedTopKSAEStep:
             checks += [
                 (trainer_cfg.sparsity_loss_type is None, "sparsity loss"),
                 (not trainer_cfg.lp_coefficient, "lp loss"),
-                (not trainer_cfg.auxk_coefficient, "aux-k loss"),
+                (not trainer_cfg.auxk_coefficient or (mesh_dim_size(sae.device_mesh, "model") == 1 and mesh_dim_size(sae.device_mesh, "data") == 1),
+                 "aux-k loss under a device mesh"),
                 (trainer_cfg.optimizer_class == "adam", "optimizer is not adam"),
                 (trainer_cfg.amp_dtype == torch.bfloat16, "amp dtype is not bf16"),
                 (trainer_cfg.gradient_accumulation_steps == 1, "gradient accumulation"),
@@ -238,9 +258,13 @@ class FusedTopKSAEStep:
         n_tokens_global: int | None = None,
         grad_mul: torch.Tensor | None = None,
         want_grad_norm: bool = False,
+        aux: "AuxK | None" = None,
     ) -> torch.Tensor:
         """Forward, backward and Adam update for one batch; returns the mean loss (0-d device tensor, local
-        batch). ``x`` / ``label``: normalised bf16 [B, d]; ``row_weight``: optional 0/1 token mask."""
+        batch). ``x`` / ``label``: normalised bf16 [B, d]; ``row_weight``: optional 0/1 token mask. ``aux`` adds the
+        Aux-K dead-feature loss (its mean is left in ``self.last_aux_loss`` and included in the returned loss)."""
+        if aux is not None:
+            return self._step_auxk(x, label, k, lr, row_weight, n_tokens_global, aux)
         B = x.shape[0]
         n_global = n_tokens_global if n_tokens_global is not None else B * self.dp
         grad_scale = 2.0 / n_global
@@ -310,6 +334,71 @@ class FusedTopKSAEStep:
         if use_comm:
             n_local = n_local / self.tp  # each rank evaluated the loss on the B / tp rows it owns
         return (self.loss_sum / n_local).squeeze(0)
+
+    def _step_auxk(self, x, label, k, lr, row_weight, n_tokens_global, aux: "AuxK") -> torch.Tensor:
+        """The step with the Aux-K loss (single GPU): ``l = |e|^2 + alpha |e - e_aux|^2`` where ``e_aux`` decodes the
+        ``k_aux`` largest gated pre-activations among DEAD features (models/sparse_dictionary.py:941-991 and
+        trainer.py:428-454 of the reference project). The dead features are gathered into a compact dictionary
+        first, so the second encoder pass costs ``n_dead / F`` of the main one instead of a full pass."""
+        assert self.tp == 1 and self.dp == 1, "the fused Aux-K step runs on one GPU (use the generic path under a mesh)"
+        self.join()
+        B = x.shape[0]
+        n_global = n_tokens_global if n_tokens_global is not None else B
+        grad_scale = 2.0 / n_global
+        gate = self.dec_norm if self.use_gate else None
+        idx, act = self.encode(x, k)
+        if self.groups is None or self.groups.entries.numel() < B * (k + aux.k_aux):
+            self.groups = K.FeatureGroups(self.F, B * (k + aux.k_aux), x.device)
+        # dead statistics first (they include this batch), from the per-feature fire counts of the main codes
+        self.groups.build(idx)
+        n_valid = B if row_weight is None else row_weight.sum()
+        self.main_counts = self.groups.counts[: self.F].clone()  # fire counts of the real codes (for metrics)
+        is_dead = aux.update(self.main_counts, n_valid)
+        dead_idx = is_dead.nonzero().squeeze(-1)
+        n_dead = int(dead_idx.numel())  # host sync, as in the reference (min(k_aux, n_dead) is a Python int there)
+        k_aux = min(aux.k_aux, n_dead)
+        self.loss_sum.zero_()
+        self.aux_sum.zero_()
+        xhat = K.sparse_decode(idx, act, self.WD_bf16, None, torch.float32)
+        if k_aux > 0:
+            pad = (-n_dead) % 8
+            rows = torch.cat([dead_idx, dead_idx.new_zeros(pad)]) if pad else dead_idx
+            w_dead = self.WE_bf16[rows]
+            b_dead = self.bE[rows]
+            g_dead = (gate[rows] if gate is not None else torch.ones(rows.numel(), device=x.device)).clone()
+            if pad:
+                g_dead[n_dead:] = 0.0  # padding rows can never be selected: their gated value is 0
+            idx_c, act_aux = K.encoder_topk(x, w_dead, b_dead, g_dead, k_aux)
+            idx_aux = torch.where(idx_c >= 0, rows[idx_c.clamp_min(0).long()].to(torch.int32), idx_c)
+            aux_rec = K.sparse_decode(idx_aux, act_aux, self.WD_bf16, None, torch.float32)
+        else:
+            idx_aux = torch.full((B, 0), -1, dtype=torch.int32, device=x.device)
+            act_aux = torch.zeros(B, 0, device=x.device)
+            aux_rec = torch.zeros_like(xhat)
+        alpha = aux.coefficient if k_aux > 0 else 0.0  # no dead feature: the auxiliary term is absent, not |e|^2
+        g_main, g_aux = K.auxk_loss_grad(xhat, aux_rec, label, self.bD, row_weight, grad_scale, alpha, self.loss_sum, self.aux_sum)
+        dact = K.sparse_dact(idx, self.WD_bf16, g_main)
+        if k_aux > 0:
+            idx_all = torch.cat([idx, idx_aux], dim=1).contiguous()
+            act_all = torch.cat([act, act_aux], dim=1).contiguous()
+            dact_all = torch.cat([dact, K.sparse_dact(idx_aux, self.WD_bf16, g_aux)], dim=1).contiguous()
+            self.groups.build(idx_all)
+        else:
+            idx_all, act_all, dact_all = idx, act, dact
+        self.t += 1
+        b1, b2 = self.betas
+        (mE, vE), (mD, vD), (mb, vb) = self.state["W_E"], self.state["W_D"], self.state["b_E"]
+        K.sparse_grad_adam(
+            self.groups, act_all, dact_all, x, g_main, self.WD, mD, vD, self.WD_bf16, self.WE, mE, vE, self.WE_bf16,
+            self.bE, mb, vb, self.dec_norm, None, None, lr, b1, b2, self.eps, self.t, True,
+            dxhat_aux=g_aux if k_aux > 0 else None, k_main=k,
+        )  # fmt: skip
+        if self.bD is not None:
+            m, v = self.state["b_D"]
+            K.adam_flat(self.bD, K.colsum_bf16(g_main), m, v, lr, b1, b2, self.eps, self.t)
+        n_local = B if row_weight is None else row_weight.sum()
+        self.last_aux_loss = (self.aux_sum / n_local).squeeze(0)
+        return ((self.loss_sum + self.aux_sum) / n_local).squeeze(0)
 
     def _gather_rows(self, *tensors: torch.Tensor) -> list[torch.Tensor]:
         out = []

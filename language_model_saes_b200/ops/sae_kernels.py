@@ -360,6 +360,26 @@ def mse_loss_grad(xhat, label, bias, row_weight, grad_scale, loss_sum, row_loss=
     return dxhat
 
 
+def auxk_loss_grad(xhat, aux_rec, label, bias, row_weight, grad_scale, alpha, loss_sum, aux_sum):
+    """Main and auxiliary (dead-feature) reconstruction losses and their output gradients for fp32 rows:
+    ``e = label - (xhat + bias)``, ``r = e - aux_rec``; accumulates ``sum rw * |e|^2`` into ``loss_sum`` and
+    ``alpha * sum rw * |r|^2`` into ``aux_sum``; returns bf16 ``(g_main, g_aux)`` with
+    ``g_main = -(e + alpha r) * grad_scale * rw`` and ``g_aux = -alpha r * grad_scale * rw``."""
+    if not xhat.is_cuda:
+        xh = xhat + (bias if bias is not None else 0.0)
+        e = label.float() - xh
+        r = e - aux_rec
+        rw = row_weight.float() if row_weight is not None else torch.ones(xhat.shape[0])
+        loss_sum += ((e * e).sum(-1) * rw).sum()
+        aux_sum += alpha * ((r * r).sum(-1) * rw).sum()
+        sc = (grad_scale * rw).unsqueeze(-1)
+        return (-(e + alpha * r) * sc).to(torch.bfloat16), (-alpha * r * sc).to(torch.bfloat16)
+    g_main = torch.empty(xhat.shape, dtype=torch.bfloat16, device=xhat.device)
+    g_aux = torch.empty_like(g_main)
+    _ext().auxk_loss_grad(xhat, aux_rec, label, bias, row_weight, grad_scale, alpha, g_main, g_aux, loss_sum, aux_sum)
+    return g_main, g_aux
+
+
 # --------------------------------------------------------------------------------------------------
 # backward / optimizer
 # --------------------------------------------------------------------------------------------------
@@ -450,15 +470,24 @@ def sparse_grad_adam(
     update=True,
     f_range: tuple[int, int] | None = None,
     ctas_per_sm: int = 0,
+    dxhat_aux=None,
+    k_main: int = 0,
 ):
     """Rebuild the two sparse gradient rows per feature and apply Adam in the same pass (in place). ``f_range``
-    restricts the launch to feature rows ``[begin, end)`` (the CUDA path only)."""
+    restricts the launch to feature rows ``[begin, end)`` (the CUDA path only). With ``dxhat_aux`` the code slots
+    ``>= k_main`` of every row take their output gradient from that matrix instead of ``dxhat`` (auxiliary codes)."""
     if not WD.is_cuda:
         idx_like = torch.full((act.numel(),), -1, dtype=torch.int64)
         off = groups.offsets.long()
         for f in range(groups.F):
             idx_like[groups.entries[off[f] : off[f + 1]].long()] = f
-        gD, gE, gb = ref_sparse_grads(idx_like.reshape(act.shape), act, dact, x, dxhat, groups.F)
+        idx_like = idx_like.reshape(act.shape)
+        if dxhat_aux is None:
+            gD, gE, gb = ref_sparse_grads(idx_like, act, dact, x, dxhat, groups.F)
+        else:
+            parts = [ref_sparse_grads(idx_like[:, sl], act[:, sl], dact[:, sl], x, g, groups.F)
+                     for sl, g in ((slice(0, k_main), dxhat), (slice(k_main, None), dxhat_aux))]  # fmt: skip
+            gD, gE, gb = (a + b for a, b in zip(*parts))
         mul = float(grad_mul) if grad_mul is not None else 1.0
         gD, gE, gb = gD * mul, gE * mul, gb * mul
         if grad_sq_sum is not None:
@@ -475,7 +504,7 @@ def sparse_grad_adam(
         return
     _ext().sparse_grad_adam(
         groups.offsets, groups.entries, act, dact, x, dxhat, WD, mD, vD, WD_bf16, WE, mE, vE, WE_bf16, bE, mbE, vbE,
-        dec_norm, grad_mul, grad_sq_sum, lr, beta1, beta2, eps, step, update, *(f_range if f_range is not None else (0, -1)), ctas_per_sm,
+        dec_norm, grad_mul, grad_sq_sum, lr, beta1, beta2, eps, step, update, *(f_range if f_range is not None else (0, -1)), ctas_per_sm, dxhat_aux, k_main,
     )  # fmt: skip
 
 

@@ -186,6 +186,7 @@ class Trainer:
         self.tokens_since_last_activation: Tensor | None = None
         self.is_dead: Tensor | None = None
         self.fused = None  # FusedTopKSAEStep when the fused path is active
+        self._fused_aux = None  # ops.fused_step.AuxK when the fused path trains with the Aux-K loss
         self._lr_lambda: Callable[[int], float] | None = None
         self._pending_optimizer_state: dict | None = None
         self._interval: dict[str, Any] = {}
@@ -514,7 +515,7 @@ class Trainer:
             acc["steps"] = 0
         acc["loss"] += loss
         n_rows = f.groups.entries.numel() and (x.shape[0] * f.dp)
-        acc["fire"] += f.groups.counts.float()
+        acc["fire"] += (f.main_counts if f.main_counts is not None else f.groups.counts[: f.F]).float()
         acc["tokens"] += n_rows
         acc["steps"] += 1
         if (self.cur_step + 1) % self.cfg.log_frequency != 0:
@@ -702,7 +703,18 @@ class Trainer:
         grad_mul = None
         if self.cfg.clip_grad_norm > 0:
             grad_mul = self._fused_clip_factor(f, x, label, sae.current_k, row_weight, n_global)
-        loss = f.step(x, label, sae.current_k, lr, row_weight=row_weight, n_tokens_global=n_global, grad_mul=grad_mul)
+        aux = None
+        if self.cfg.auxk_coefficient:
+            if self._fused_aux is None:
+                from .ops.fused_step import AuxK
+
+                assert self.tokens_since_last_activation is not None, "dead statistics are initialised in fit()"
+                self._fused_aux = AuxK(f.F, self.cfg.k_aux, self.cfg.auxk_coefficient, self.cfg.dead_threshold, x.device,
+                                       counter=self.tokens_since_last_activation)  # fmt: skip
+            aux = self._fused_aux
+        loss = f.step(x, label, sae.current_k, lr, row_weight=row_weight, n_tokens_global=n_global, grad_mul=grad_mul, aux=aux)
+        if aux is not None:  # keep the trainer's view (checkpoints, logging) in step with the engine's counters
+            self.tokens_since_last_activation, self.is_dead = aux.tokens_since_last_activation, aux.is_dead
         if not self.cfg.skip_metrics_calculation:
             self._log_fused(sae, x, label, mask, loss, lr)
         return loss

@@ -81,3 +81,55 @@ def test_fused_row_mask_and_transcoder_label():
     want = (((xhat - y.float()) ** 2).sum(-1) * w).sum() / w.sum()
     got = engine.step(x, y, k, 1e-3, row_weight=w, n_tokens_global=int(w.sum()))
     assert torch.allclose(got, want, rtol=1e-3)
+
+
+@pytest.mark.parametrize("k_aux", [16, 96])
+def test_fused_auxk_matches_autograd(k_aux):
+    """Aux-K on the fused path against the autograd path: same dead set, same losses, same parameter motion."""
+    from language_model_saes_b200.ops.fused_step import AuxK
+
+    d, B, k, steps, lr, alpha, thr = 256, 512, 16, 6, 1e-3, 1 / 32, 1000
+    ref = _model(d=d, k=k)
+    F = ref.cfg.d_sae
+    with torch.no_grad():
+        ref.b_E[: F // 4] -= 0.5  # a quarter of the dictionary rarely fires: it goes dead after two batches
+    fused_model = copy.deepcopy(ref)
+    engine = FusedTopKSAEStep(fused_model)
+    aux = AuxK(F, k_aux, alpha, thr, "cuda")
+    counter = torch.zeros(F, dtype=torch.long, device="cuda")
+
+    def update_dead(feature_acts, mask, specs):
+        nonlocal counter
+        fired = (feature_acts > 0).any(dim=0)
+        counter = torch.where(fired, torch.zeros_like(counter), counter + feature_acts.shape[0])
+        return counter >= thr
+
+    opt = torch.optim.Adam(ref.parameters(), lr=lr)
+    tokens = torch.zeros(B, dtype=torch.long, device="cuda")
+    ref_l, ref_a, fus_l, fus_a, n_dead = [], [], [], [], []
+    for x in _data(steps, B, d):
+        opt.zero_grad()
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            out = ref.compute_loss({"h": x.float(), "tokens": tokens}, auxk_coefficient=alpha, k_aux=k_aux,
+                                   update_dead_statistics=update_dead, return_aux_data=True)  # fmt: skip
+        out["loss"].backward()
+        opt.step()
+        ref_l.append(float(out["loss"].detach()))
+        ref_a.append(float(out["l_aux"].detach().mean()))
+        fus_l.append(float(engine.step(x, x, k, lr, aux=aux)))
+        fus_a.append(float(engine.last_aux_loss))
+        n_dead.append(int(aux.is_dead.sum()))
+        assert torch.equal(aux.is_dead, counter >= thr)
+    K.check_status(torch.device("cuda"))
+    assert n_dead[-1] > 0 and max(fus_a) > 0, (n_dead, fus_a)
+    assert torch.allclose(torch.tensor(ref_l), torch.tensor(fus_l), rtol=3e-2), (ref_l, fus_l)
+    assert torch.allclose(torch.tensor(ref_a), torch.tensor(fus_a), rtol=6e-2, atol=1e-3), (ref_a, fus_a)
+    for name in ("W_D", "W_E"):
+        a, b = getattr(ref, name).detach().float(), getattr(fused_model, name).detach().float()
+        assert torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0) > 0.999
+    # the dead features moved (only the auxiliary loss reaches them) and moved the same way
+    dead = aux.is_dead
+    moved_ref = (ref.W_D.detach()[dead] - _model(d=d, k=k).W_D.detach()[dead]).flatten()
+    moved_fus = (fused_model.W_D.detach()[dead] - _model(d=d, k=k).W_D.detach()[dead]).flatten()
+    assert moved_fus.abs().sum() > 0
+    assert torch.nn.functional.cosine_similarity(moved_ref, moved_fus, dim=0) > 0.9
