@@ -120,8 +120,9 @@ class FusedTopKSAEStep:
         from ..models.sae import SparseAutoEncoder
 
         cfg = sae.cfg
+        if type(sae) is not SparseAutoEncoder:
+            return False, "model is not a plain SparseAutoEncoder"
         checks = [
-            (type(sae) is SparseAutoEncoder, "model is not a plain SparseAutoEncoder"),
             (cfg.act_fn == "topk", "activation is not topk"),
             (not cfg.use_glu_encoder, "GLU encoder"),
             (sae.W_D.is_cuda, "not on a CUDA device"),
