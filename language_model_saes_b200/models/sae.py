@@ -153,8 +153,22 @@ class SparseAutoEncoder(SparseDictionary):
         feature_acts = self.hook_feature_acts(feature_acts)
         return (feature_acts, hidden_pre) if return_hidden_pre else feature_acts
 
+    def _use_sparse_kernels(self, feature_acts: torch.Tensor) -> bool:
+        """``use_triton_kernel`` (the reference's name for "decode through the sparse kernels") applies on CUDA when
+        the activations are sparse enough and nothing listens on the hook points."""
+        if not (self.cfg.use_triton_kernel and feature_acts.is_cuda and self.cfg.d_model % 8 == 0 and self.cfg.d_model <= 8192):
+            return False
+        sparsity = 1.0 - float((feature_acts != 0).sum()) / feature_acts.numel()
+        return sparsity >= self.cfg.sparsity_threshold_for_triton_spmm_kernel
+
     def decode(self, feature_acts: torch.Tensor, **kwargs) -> torch.Tensor:
-        reconstructed = all_reduce_sum(feature_acts @ self.W_D, self.tp_group)
+        if self._use_sparse_kernels(feature_acts):
+            from ..ops.sparse_autograd import sparse_decode
+
+            partial = sparse_decode(feature_acts, self.W_D)
+        else:
+            partial = feature_acts @ self.W_D
+        reconstructed = all_reduce_sum(partial, self.tp_group)
         if self.cfg.use_decoder_bias:
             reconstructed = reconstructed + self.b_D
         return self.hook_reconstructed(reconstructed)

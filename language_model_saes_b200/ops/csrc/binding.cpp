@@ -289,7 +289,8 @@ void sparse_grad_adam(const Tensor& offsets, const Tensor& entries, const Tensor
                       const c10::optional<Tensor>& vbE, const c10::optional<Tensor>& dec_norm,
                       const c10::optional<Tensor>& grad_mul, const c10::optional<Tensor>& grad_sq_sum, double lr,
                       double beta1, double beta2, double eps, int64_t step, bool update, int64_t f_begin,
-                      int64_t f_end, int64_t ctas_per_sm, const c10::optional<Tensor>& dxhat_aux, int64_t k_main) {
+                      int64_t f_end, int64_t ctas_per_sm, const c10::optional<Tensor>& dxhat_aux, int64_t k_main,
+                      const c10::optional<Tensor>& gD_out, const c10::optional<Tensor>& gE_out) {
   CHECK_T(offsets, torch::kInt32);
   CHECK_T(entries, torch::kInt32);
   CHECK_T(act, torch::kFloat32);
@@ -305,7 +306,8 @@ void sparse_grad_adam(const Tensor& offsets, const Tensor& entries, const Tensor
   p.d = (int)WD.size(1);
   p.k = (int)act.size(1);
   TORCH_CHECK(offsets.numel() >= p.F + 1 && x.size(1) == p.d && dxhat.sizes() == x.sizes());
-  for (const Tensor* t : {&mD, &vD, &WD_bf16, &mE, &vE, &WE_bf16}) TORCH_CHECK(t->numel() == WD.numel());
+  // state and shadow tensors are only touched when the update is applied
+  if (update) for (const Tensor* t : {&mD, &vD, &WD_bf16, &mE, &vE, &WE_bf16}) TORCH_CHECK(t->numel() == WD.numel());
   p.offsets = offsets.data_ptr<int>();
   p.entries = entries.data_ptr<int>();
   p.act = act.data_ptr<float>();
@@ -334,6 +336,11 @@ void sparse_grad_adam(const Tensor& offsets, const Tensor& entries, const Tensor
   if (dxhat_aux.has_value()) { CHECK_T(*dxhat_aux, torch::kBFloat16); TORCH_CHECK(dxhat_aux->sizes() == dxhat.sizes()); }
   p.dxhat_aux = dxhat_aux.has_value() ? reinterpret_cast<const __nv_bfloat16*>(dxhat_aux->data_ptr()) : nullptr;
   p.k_main = (int)k_main;
+  for (const auto* t : {&gD_out, &gE_out}) {
+    if (t->has_value()) { CHECK_T(**t, torch::kFloat32); TORCH_CHECK((*t)->numel() == WD.numel()); }
+  }
+  p.gD_out = opt_ptr<float>(gD_out);
+  p.gE_out = opt_ptr<float>(gE_out);
   TORCH_CHECK(0 <= p.f_begin && p.f_begin <= p.f_end && p.f_end <= p.F, "feature range out of bounds");
   check_cuda(lmsae::sparse_grad_adam_launch(p, at::cuda::getCurrentCUDAStream()), "sparse_grad_adam launch");
 }

@@ -83,6 +83,8 @@ struct GradAdamParams {
   int ctas_per_sm;     // 0 = fill the GPU (4 per SM); 1..4 = leave registers free for a concurrently running kernel
   const __nv_bfloat16* dxhat_aux;  // output gradient seen by the code slots >= k_main of every row (nullptr: none)
   int k_main;
+  float* gD_out;  // optional dense [F, d] outputs of the rebuilt gradient rows (for autograd callers)
+  float* gE_out;
 };
 int auxk_loss_grad_launch(const float* xhat, const float* aux_rec, const __nv_bfloat16* label, const float* bias,
                           const float* row_weight, int rows, int d, float grad_scale, float alpha,

@@ -513,6 +513,8 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
         gE[i] *= gmul;
         gsq_local += gD[i] * gD[i] + gE[i] * gE[i];
       }
+      if (p.gD_out != nullptr) *reinterpret_cast<float4*>(p.gD_out + o) = make_float4(gD[0], gD[1], gD[2], gD[3]);
+      if (p.gE_out != nullptr) *reinterpret_cast<float4*>(p.gE_out + o) = make_float4(gE[0], gE[1], gE[2], gE[3]);
       if (p.update) {
         {
           float4 w = ldcs4(p.WD + o), m = ldcs4(p.mD + o), v = ldcs4(p.vD + o);

@@ -472,6 +472,7 @@ def sparse_grad_adam(
     ctas_per_sm: int = 0,
     dxhat_aux=None,
     k_main: int = 0,
+    grad_out: tuple[torch.Tensor | None, torch.Tensor | None] = (None, None),
 ):
     """Rebuild the two sparse gradient rows per feature and apply Adam in the same pass (in place). ``f_range``
     restricts the launch to feature rows ``[begin, end)`` (the CUDA path only). With ``dxhat_aux`` the code slots
@@ -504,7 +505,7 @@ def sparse_grad_adam(
         return
     _ext().sparse_grad_adam(
         groups.offsets, groups.entries, act, dact, x, dxhat, WD, mD, vD, WD_bf16, WE, mE, vE, WE_bf16, bE, mbE, vbE,
-        dec_norm, grad_mul, grad_sq_sum, lr, beta1, beta2, eps, step, update, *(f_range if f_range is not None else (0, -1)), ctas_per_sm, dxhat_aux, k_main,
+        dec_norm, grad_mul, grad_sq_sum, lr, beta1, beta2, eps, step, update, *(f_range if f_range is not None else (0, -1)), ctas_per_sm, dxhat_aux, k_main, grad_out[0], grad_out[1],
     )  # fmt: skip
 
 

@@ -206,3 +206,29 @@ def test_jumprelu_fused_matches_autograd(dtype, shape, tshape):
     tol = dict(rtol=1e-4, atol=1e-4) if dtype == torch.float32 else dict(rtol=5e-2, atol=5e-2)
     assert torch.allclose(lf.grad.float(), lr.grad.float(), **tol), (lf.grad.float() - lr.grad.float()).abs().max()
     assert lf.grad.abs().sum() > 0
+
+
+def test_sparse_decode_autograd_matches_dense():
+    from language_model_saes_b200.ops.sparse_autograd import dense_to_padded_sparse, sparse_decode
+
+    g = torch.Generator(device="cpu").manual_seed(0)
+    B, F, d, k = 96, 2048, 256, 12
+    acts = torch.zeros(B, F)
+    cols = torch.stack([torch.randperm(F, generator=g)[:k] for _ in range(B)])
+    acts.scatter_(1, cols, torch.rand(B, k, generator=g) + 0.1)
+    acts[3] = 0  # a row without any non-zero
+    acts = acts.to(DEV).requires_grad_()
+    W = (torch.randn(F, d, generator=g) / d**0.5).to(DEV).requires_grad_()
+    dy = torch.randn(B, d, generator=g).to(DEV)
+    idx, val = dense_to_padded_sparse(acts.detach())
+    assert idx.shape[1] % 8 == 0 and int((idx >= 0).sum()) == int((acts != 0).sum())
+    out = sparse_decode(acts, W)
+    out.backward(dy)
+    Wb = W.detach().to(torch.bfloat16).float()
+    ref_out = acts.detach() @ Wb
+    assert torch.allclose(out, ref_out, atol=2e-3, rtol=2e-3)
+    dyb = dy.to(torch.bfloat16).float()
+    ref_dW = acts.detach().t() @ dyb
+    assert torch.allclose(W.grad, ref_dW, atol=2e-3, rtol=2e-3)
+    ref_da = (dyb @ Wb.t()) * (acts.detach() != 0)
+    assert torch.allclose(acts.grad, ref_da, atol=5e-3, rtol=5e-3)
