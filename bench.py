@@ -261,8 +261,10 @@ def run_ours(args):
                        "l2": f"inputs rotate through {POOL} batches (256 MiB) > L2; weights 2 x 2.1 GB"},
             "clocks": clocks,
             "e2e": {"value": Ksteps * BATCH / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms / Ksteps,
-                    "h2d_bytes_per_step": BATCH * D_MODEL * 2 + BATCH * 8, "d2h_bytes_per_step": 4,
-                    "api": "Trainer.fit(sae, stream of pinned host batches), copy of batch i+1 overlaps step i, loss read back every step"},
+                    # every rank copies 1/N of the activation rows (then NVLink all-gather) and the whole token-id vector
+                    "h2d_bytes_per_step": BATCH * D_MODEL * 2 + world * BATCH * 8, "d2h_bytes_per_step": 4 * world,
+                    "api": "Trainer.fit(sae, stream of pinned host batches): copy of batch i+1 overlaps step i, each rank copies "
+                           "1/N of the rows over PCIe and all-gathers them over NVLink, loss read back every step on every rank"},
             "gpu_launches": launches, "final_loss": final_loss, "impl": "ours", "package": lm.__name__,
         })  # fmt: skip
     if world > 1:
