@@ -163,6 +163,16 @@ class ActivationGenerator(BaseActivationProcessor[Iterable[dict[str, Any]], Iter
             yield {**acts, "meta": [{"model_name": model_name} | existing[i] for i in range(len(existing))]}
 
 
+def _drop_masked(v: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
+    """``v[mask]`` over the leading (batch, context) dimensions; activations on a GPU go through the one-pass scan +
+    row-gather kernels instead of a boolean index (which materialises an index tensor and syncs twice)."""
+    if v.is_cuda and v.ndim == mask.ndim + 1 and v.is_floating_point() and v.dtype in (torch.float32, torch.bfloat16):
+        from ...ops.select_kernels import compact_rows
+
+        return compact_rows(v.reshape(-1, v.shape[-1]), mask.reshape(-1))
+    return v[mask]
+
+
 class ActivationTransformer(BaseActivationProcessor[Iterable[dict[str, Any]], Iterable[dict[str, Any]]]):
     """``[batch, context, d]`` -> ``[kept tokens, d]``: drops masked tokens (or the given token ids) and the meta."""
 
@@ -174,7 +184,7 @@ class ActivationTransformer(BaseActivationProcessor[Iterable[dict[str, Any]], It
                 mask = torch.isin(tokens, torch.tensor(ignore_token_ids, device=tokens.device), invert=True)
             else:
                 mask = d["mask"].bool()
-            yield {k: v[mask] for k, v in d.items() if isinstance(v, torch.Tensor)}
+            yield {k: _drop_masked(v, mask) for k, v in d.items() if isinstance(v, torch.Tensor)}
 
 
 class ActivationBatchler(BaseActivationProcessor[Iterable[dict[str, Any]], Iterable[dict[str, Any]]]):

@@ -25,6 +25,7 @@ from torch import nn
 from ..activation_functions import JumpReLU
 from ..parallel.collectives import all_reduce_sum, distributed_topk
 from ..parallel.mesh import DeviceMesh, DimMap
+from ..ops.select_kernels import positive_topk
 from ..utils.math import topk
 from ..utils.tensor_specs import TensorSpecs
 from ..utils.timer import timer
@@ -142,6 +143,10 @@ class CrossLayerTranscoder(SparseDictionary):
             else:
                 dims = tuple(d % x.ndim for d in dims_spec)
             k = count(n_tokens)
+            if len(dims) > 1:  # batch-level selections: radix-select threshold on a GPU
+                out = positive_topk(x, k, dims, self.tp_group if self.tp_size > 1 else None)
+                if out is not None:
+                    return out
             if self.tp_size > 1:
                 return distributed_topk(x, k, self.tp_group, dim=dims)
             n_sel = 1
@@ -287,13 +292,13 @@ class CrossLayerTranscoder(SparseDictionary):
         if not isinstance(acts, (list, tuple)) and self.cfg.decode_with_csr and (
             self.current_k / (self.cfg.d_sae * self.cfg.n_layers) < self.cfg.sparsity_threshold_for_csr
         ):
-            flat = acts.reshape(-1, *acts.shape[-2:])
-            lead = acts.shape[:-2]
-            sparse = [flat[:, s].to_sparse_csr() for s in range(self.cfg.n_layers)]
-            parts = [self._contribution(sparse, t).reshape(*lead, -1) for t in range(self.cfg.n_layers)]
+            # one gather kernel for every (source, target) pair instead of L (L + 1) / 2 CSR products
+            from ..ops.clt_kernels import clt_sparse_decode
+
+            partial = clt_sparse_decode(acts, list(self.W_D), None).to(acts.dtype)
         else:
-            parts = [self._contribution(acts, t) for t in range(self.cfg.n_layers)]
-        stacked = all_reduce_sum(torch.stack(parts, dim=0), self.tp_group)
+            partial = torch.stack([self._contribution(acts, t) for t in range(self.cfg.n_layers)], dim=0)
+        stacked = all_reduce_sum(partial, self.tp_group)
         stacked = stacked + torch.stack(list(self.b_D)).reshape(self.cfg.n_layers, *([1] * (stacked.ndim - 2)), -1)
         if batch_first:
             return stacked.movedim(0, -2)

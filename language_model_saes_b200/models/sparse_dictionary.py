@@ -37,6 +37,7 @@ from ..parallel.mesh import (
     mesh_group,
 )
 from ..utils.logging import get_distributed_logger
+from ..ops.select_kernels import positive_topk
 from ..utils.math import topk
 from ..utils.tensor_specs import TensorSpecs, apply_token_mask
 from ..utils.timer import timer
@@ -512,9 +513,11 @@ class SparseDictionary(HookedRootModule, ABC):
             if x.ndim == 3:
                 x = x.flatten(end_dim=1)
             k_total = self.current_k * x.size(0)
-            if self.tp_size > 1:
+            # on a GPU: exact threshold by radix select (two streaming passes; shards add their histograms)
+            out = positive_topk(x, k_total, (-2, -1), self.tp_group if self.tp_size > 1 else None)
+            if out is None and self.tp_size > 1:
                 out = distributed_topk(x, k_total, self.tp_group, dim=(-2, -1))
-            else:
+            elif out is None:
                 out = topk(x, k=min(k_total, x.numel()), dim=(-2, -1), abs=True)
             return out.reshape(shape)
 

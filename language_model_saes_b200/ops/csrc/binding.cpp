@@ -405,6 +405,177 @@ Tensor jumprelu(const Tensor& x, const Tensor& log_theta, const c10::optional<Te
   return out;
 }
 
+// ---- selection / compaction ----------------------------------------------------------------------------
+int dtype_code(const Tensor& t) {
+  if (t.scalar_type() == torch::kFloat32) return 0;
+  if (t.scalar_type() == torch::kBFloat16) return 1;
+  TORCH_CHECK(false, "fp32 or bf16 expected");
+  return -1;
+}
+
+int64_t radix_hi_bins() { return lmsae::radix_hi_bins(); }
+
+// x: contiguous, viewed as [A, S, N]; level 0 fills hist[radix_hi_bins()], level 1 fills hist[65536] with the members of
+// bin sel[0]. hist is uint32 storage handed in as int32.
+void radix_hist(const Tensor& x, int64_t A, int64_t S, int64_t N, int64_t s, int64_t level, const c10::optional<Tensor>& sel,
+                const Tensor& hist) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.numel() == A * S * N, "x must be a contiguous [A, S, N] array");
+  CHECK_T(hist, torch::kInt32);
+  TORCH_CHECK(hist.numel() >= (level == 0 ? lmsae::radix_hi_bins() : 65536), "histogram too small");
+  if (level == 1) {
+    TORCH_CHECK(sel.has_value(), "level 1 needs the level-0 pick");
+    CHECK_T(*sel, torch::kInt64);
+  }
+  const c10::cuda::CUDAGuard guard(x.device());
+  check_cuda(lmsae::radix_hist_launch(dtype_code(x), x.data_ptr(), A, S, N, s, (int)level,
+                                      level == 1 ? reinterpret_cast<const long long*>(sel->data_ptr<int64_t>()) : nullptr,
+                                      reinterpret_cast<unsigned*>(hist.data_ptr<int>()), at::cuda::getCurrentCUDAStream()),
+             "radix_hist launch");
+}
+
+void radix_pick(const Tensor& hist, int64_t nbins, int64_t k, const c10::optional<Tensor>& sel_in, int64_t level,
+                const Tensor& sel_out, const c10::optional<Tensor>& thr) {
+  CHECK_T(hist, torch::kInt32);
+  CHECK_T(sel_out, torch::kInt64);
+  TORCH_CHECK(hist.numel() >= nbins && sel_out.numel() >= 3, "radix_pick: buffers too small");
+  if (thr.has_value()) { CHECK_T(*thr, torch::kFloat32); }
+  if (sel_in.has_value()) { CHECK_T(*sel_in, torch::kInt64); }
+  const c10::cuda::CUDAGuard guard(hist.device());
+  check_cuda(lmsae::radix_pick_launch(reinterpret_cast<const unsigned*>(hist.data_ptr<int>()), (int)nbins, k,
+                                      sel_in.has_value() ? reinterpret_cast<const long long*>(sel_in->data_ptr<int64_t>()) : nullptr,
+                                      (int)level, reinterpret_cast<long long*>(sel_out.data_ptr<int64_t>()),
+                                      opt_ptr<float>(thr), at::cuda::getCurrentCUDAStream()),
+             "radix_pick launch");
+}
+
+// x [B, N] -> idx / val [B, cap] (both optional: count only) and nnz [B] (optional)
+void row_compact(const Tensor& x, const c10::optional<Tensor>& idx, const c10::optional<Tensor>& val,
+                 const c10::optional<Tensor>& nnz) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.dim() == 2, "x must be a contiguous CUDA matrix");
+  int cap = 0;
+  if (idx.has_value()) {
+    CHECK_T(*idx, torch::kInt32);
+    TORCH_CHECK(val.has_value(), "idx and val come together");
+    CHECK_T(*val, torch::kFloat32);
+    TORCH_CHECK(idx->dim() == 2 && idx->size(0) == x.size(0) && val->sizes() == idx->sizes(), "idx / val must be [B, cap]");
+    cap = (int)idx->size(1);
+  }
+  if (nnz.has_value()) {
+    CHECK_T(*nnz, torch::kInt32);
+    TORCH_CHECK(nnz->numel() == x.size(0), "nnz must be [B]");
+  }
+  const c10::cuda::CUDAGuard guard(x.device());
+  check_cuda(lmsae::row_compact_launch(dtype_code(x), x.data_ptr(), (int)x.size(0), x.size(1), cap, opt_ptr<int>(idx),
+                                       opt_ptr<float>(val), opt_ptr<int>(nnz), at::cuda::getCurrentCUDAStream()),
+             "row_compact launch");
+}
+
+void exclusive_scan(const Tensor& counts, const Tensor& offsets, const Tensor& block_sums) {
+  CHECK_T(counts, torch::kInt32);
+  CHECK_T(offsets, torch::kInt32);
+  CHECK_T(block_sums, torch::kInt32);
+  const int64_t n = counts.numel();
+  TORCH_CHECK(offsets.numel() == n + 1 && block_sums.numel() >= (n + 4095) / 4096 && n < 2147483647LL, "exclusive_scan: sizes");
+  const c10::cuda::CUDAGuard guard(counts.device());
+  check_cuda(lmsae::exclusive_scan_launch(counts.data_ptr<int>(), (int)n, offsets.data_ptr<int>(), block_sums.data_ptr<int>(),
+                                          at::cuda::getCurrentCUDAStream()),
+             "exclusive_scan launch");
+}
+
+// out[pos[i], :] = cast(src[i, :]) where keep[i] != 0
+void gather_rows_cast(const Tensor& src, const Tensor& keep, const Tensor& pos, const Tensor& out) {
+  TORCH_CHECK(src.is_cuda() && src.is_contiguous() && src.dim() == 2 && out.is_cuda() && out.is_contiguous() && out.dim() == 2,
+              "src / out must be contiguous CUDA matrices");
+  CHECK_T(keep, torch::kInt32);
+  CHECK_T(pos, torch::kInt32);
+  TORCH_CHECK(keep.numel() == src.size(0) && pos.numel() >= src.size(0) && out.size(1) == src.size(1), "gather_rows_cast: sizes");
+  const c10::cuda::CUDAGuard guard(src.device());
+  check_cuda(lmsae::gather_rows_cast_launch(dtype_code(src), dtype_code(out), src.data_ptr(), keep.data_ptr<int>(),
+                                            pos.data_ptr<int>(), src.size(0), (int)src.size(1), out.data_ptr(), out.size(0),
+                                            at::cuda::getCurrentCUDAStream()),
+             "gather_rows_cast launch");
+}
+
+// ---- cross-layer transcoder decoder fan-out ----------------------------------------------------------
+// `weights[t]`: bf16 [t + 1, F, d]. idx / val: [B, K] codes c = s * F + f (-1 = empty).
+lmsae::CltTable make_clt_table(const std::vector<Tensor>& weights, int64_t F, int64_t d) {
+  TORCH_CHECK(!weights.empty() && (int)weights.size() <= lmsae::kMaxCltLayers, "1..64 target layers");
+  lmsae::CltTable tab{};
+  for (size_t t = 0; t < weights.size(); ++t) {
+    const Tensor& w = weights[t];
+    CHECK_T(w, torch::kBFloat16);
+    TORCH_CHECK(w.dim() == 3 && w.size(0) == (int64_t)t + 1 && w.size(1) == F && w.size(2) == d,
+                "decoder of target layer t must be [t + 1, F, d]");
+    tab.W[t] = reinterpret_cast<const __nv_bfloat16*>(w.data_ptr());
+  }
+  return tab;
+}
+
+void clt_decode(const Tensor& idx, const Tensor& val, const std::vector<Tensor>& weights, const c10::optional<Tensor>& bias,
+                const Tensor& out) {
+  CHECK_T(idx, torch::kInt32);
+  CHECK_T(val, torch::kFloat32);
+  TORCH_CHECK(idx.dim() == 2 && val.sizes() == idx.sizes(), "idx / val must be [B, K]");
+  const int64_t B = idx.size(0), K = idx.size(1), L = (int64_t)weights.size();
+  const int64_t F = weights[0].size(1), d = weights[0].size(2);
+  const c10::cuda::CUDAGuard guard(idx.device());
+  const lmsae::CltTable tab = make_clt_table(weights, F, d);
+  TORCH_CHECK(out.is_cuda() && out.is_contiguous() && out.numel() == L * B * d, "out must be [L, B, d]");
+  float* o32 = nullptr;
+  __nv_bfloat16* o16 = nullptr;
+  if (out.scalar_type() == torch::kFloat32) o32 = out.data_ptr<float>();
+  else if (out.scalar_type() == torch::kBFloat16) o16 = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
+  else TORCH_CHECK(false, "out must be fp32 or bf16");
+  if (bias.has_value()) {
+    CHECK_T(*bias, torch::kFloat32);
+    TORCH_CHECK(bias->numel() == L * d, "bias must be [L, d]");
+  }
+  check_cuda(lmsae::clt_decode_launch(tab, idx.data_ptr<int>(), val.data_ptr<float>(), (int)B, (int)K, (int)L, (int)F, (int)d,
+                                      opt_ptr<float>(bias), o32, o16, at::cuda::getCurrentCUDAStream()),
+             "clt_decode launch");
+}
+
+void clt_dact(const Tensor& idx, const std::vector<Tensor>& weights, const Tensor& dy, const Tensor& dval) {
+  CHECK_T(idx, torch::kInt32);
+  CHECK_T(dy, torch::kBFloat16);
+  CHECK_T(dval, torch::kFloat32);
+  const int64_t B = idx.size(0), K = idx.size(1), L = (int64_t)weights.size();
+  const int64_t F = weights[0].size(1), d = weights[0].size(2);
+  TORCH_CHECK(dy.numel() == L * B * d && dval.numel() == B * K, "dy must be [L, B, d], dval [B, K]");
+  const c10::cuda::CUDAGuard guard(idx.device());
+  const lmsae::CltTable tab = make_clt_table(weights, F, d);
+  check_cuda(lmsae::clt_dact_launch(tab, idx.data_ptr<int>(), (int)B, (int)K, (int)L, (int)F, (int)d,
+                                    reinterpret_cast<const __nv_bfloat16*>(dy.data_ptr()), dval.data_ptr<float>(),
+                                    at::cuda::getCurrentCUDAStream()),
+             "clt_dact launch");
+}
+
+// `grads[t]`: fp32 [t + 1, F, d], zero-filled by the caller; rows of the codes that occur are overwritten.
+void clt_wgrad(const Tensor& offsets, const Tensor& entries, const Tensor& act, const Tensor& dy,
+               const std::vector<Tensor>& grads, int64_t B, int64_t K) {
+  CHECK_T(offsets, torch::kInt32);
+  CHECK_T(entries, torch::kInt32);
+  CHECK_T(act, torch::kFloat32);
+  CHECK_T(dy, torch::kBFloat16);
+  const int64_t L = (int64_t)grads.size();
+  TORCH_CHECK(L >= 1 && L <= lmsae::kMaxCltLayers, "1..64 target layers");
+  const int64_t F = grads[0].size(1), d = grads[0].size(2);
+  lmsae::CltGradTable tab{};
+  for (int64_t t = 0; t < L; ++t) {
+    const Tensor& g = grads[t];
+    CHECK_T(g, torch::kFloat32);
+    TORCH_CHECK(g.dim() == 3 && g.size(0) == t + 1 && g.size(1) == F && g.size(2) == d, "gradient of target layer t must be [t + 1, F, d]");
+    tab.G[t] = g.data_ptr<float>();
+  }
+  TORCH_CHECK(offsets.numel() == L * F + 1 && act.numel() == B * K && entries.numel() >= B * K && dy.numel() == L * B * d,
+              "clt_wgrad: inconsistent sizes");
+  const c10::cuda::CUDAGuard guard(dy.device());
+  check_cuda(lmsae::clt_wgrad_launch(tab, offsets.data_ptr<int>(), entries.data_ptr<int>(), act.data_ptr<float>(), (int)B, (int)K,
+                                     (int)L, (int)F, (int)d, reinterpret_cast<const __nv_bfloat16*>(dy.data_ptr()),
+                                     at::cuda::getCurrentCUDAStream()),
+             "clt_wgrad launch");
+}
+
 // ---- peer-memory collectives -----------------------------------------------------------------------
 // `table` = [world, rank, flags_off, cand_val_off, cand_idx_off, partial_off, dxhat_off, ptr_0 .. ptr_{world-1}]
 lmsae::PeerTable make_peer_table(const std::vector<int64_t>& table) {
@@ -511,6 +682,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "sm_100a kernels for sparse-dictionary training";
   m.def("encoder_gemm", &encoder_gemm);
   m.def("jumprelu", &jumprelu);
+  m.def("radix_hi_bins", &radix_hi_bins);
+  m.def("radix_hist", &radix_hist);
+  m.def("radix_pick", &radix_pick);
+  m.def("row_compact", &row_compact);
+  m.def("exclusive_scan", &exclusive_scan);
+  m.def("gather_rows_cast", &gather_rows_cast);
+  m.def("clt_decode", &clt_decode);
+  m.def("clt_dact", &clt_dact);
+  m.def("clt_wgrad", &clt_wgrad);
   m.def("topk_merge", &topk_merge);
   m.def("row_topk", &row_topk);
   m.def("sparse_decode", &sparse_decode);

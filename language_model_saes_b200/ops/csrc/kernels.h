@@ -96,6 +96,30 @@ int adam_flat_launch(float* p, const float* g, float* m, float* v, long long n, 
                      __nv_bfloat16* shadow, float* grad_sq_sum, int update, cudaStream_t stream);
 int row_norm_shadow_launch(const float* W, int F, int d, float* norm, __nv_bfloat16* shadow, cudaStream_t stream);
 
+// ---- cross-layer transcoder decoder fan-out (clt_ops.cu) --------------------------------------------
+constexpr int kMaxCltLayers = 64;
+struct CltTable { const __nv_bfloat16* W[kMaxCltLayers]; };  // W[t]: bf16 [t + 1, F, d], one allocation per target layer
+struct CltGradTable { float* G[kMaxCltLayers]; };            // G[t]: fp32 [t + 1, F, d]
+int clt_decode_launch(const CltTable& tab, const int* idx, const float* val, int B, int K, int L, int F, int d,
+                      const float* bias, float* out_f32, __nv_bfloat16* out_bf16, cudaStream_t stream);
+int clt_dact_launch(const CltTable& tab, const int* idx, int B, int K, int L, int F, int d, const __nv_bfloat16* dy,
+                    float* dval, cudaStream_t stream);
+int clt_wgrad_launch(const CltGradTable& tab, const int* offsets, const int* entries, const float* act, int B, int K,
+                     int L, int F, int d, const __nv_bfloat16* dy, cudaStream_t stream);
+
+// ---- selection / compaction (select_ops.cu) --------------------------------------------------------
+// dtype: 0 = fp32, 1 = bf16. x is a contiguous [A, S, N] array and the selection covers segment s.
+int radix_hi_bins();
+int radix_hist_launch(int dtype, const void* x, long long A, long long S, long long N, long long s, int level,
+                      const long long* sel, unsigned* hist, cudaStream_t stream);
+int radix_pick_launch(const unsigned* hist, int nbins, long long k, const long long* sel_in, int level, long long* sel_out,
+                      float* thr, cudaStream_t stream);
+int row_compact_launch(int dtype, const void* x, int B, long long N, int cap, int* idx, float* val, int* nnz,
+                       cudaStream_t stream);
+int gather_rows_cast_launch(int in_dtype, int out_dtype, const void* src, const int* keep, const int* pos, long long n,
+                            int d, void* out, long long out_rows, cudaStream_t stream);
+int exclusive_scan_launch(const int* counts, int n, int* offsets, int* block_sums_buf, cudaStream_t stream);
+
 // ---- elementwise (jumprelu.cu) ---------------------------------------------------------------------
 int jumprelu_launch(int dtype, const void* x, const void* log_theta, const void* dy, void* out, float* dlog, long long n,
                     int P, float window, int backward, cudaStream_t stream);

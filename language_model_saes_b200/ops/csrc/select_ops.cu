@@ -1,0 +1,362 @@
+// Selection and compaction kernels (sm_100a, streaming SIMT kernels: one or two passes over the data at HBM speed).
+//
+//  radix_hist_hi / radix_hist_lo / radix_pick
+//        exact k-th largest POSITIVE value of a big tensor by a two-level radix select on the float bit pattern
+//        (positive IEEE floats order like their bits): a 32,640-bin shared-memory histogram of the upper 16 bits, one
+//        CTA picks the bin that holds the k-th value, a second pass histograms the lower 16 bits of that bin's members.
+//        This is the batch-level top-k ("BatchTopK": keep the k * batch largest pre-activations of the whole batch,
+//        models/sparse_dictionary.py:775-788 and utils/distributed/ops.py:158-266 of the reference project, which sorts
+//        or bisects with one all-reduce per iteration). Feature- or data-sharded callers sum the histograms across ranks
+//        between a histogram and its pick, so the whole exchange is two small all-reduces.
+//  row_nnz / row_compact
+//        dense [B, N] activations -> padded sparse (column, value) lists in ascending column order.
+//  gather_rows_cast
+//        out[pos[i], :] = cast(src[i, :]) for rows with keep[i] != 0: token-mask compaction of cached activations
+//        (activation/processors/cached_activation.py:301-320, activation/processors/activation.py:277-285).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace lmsae {
+
+namespace {
+
+constexpr int kHiBins = 0x7F80;  // upper 16 bits of positive finite floats and +inf: 0 .. 0x7F80 - 1 (+inf = 0x7F80 clipped)
+constexpr int HIST_THREADS = 1024;
+
+template <typename T>
+__device__ __forceinline__ uint32_t positive_bits(T v);
+template <>
+__device__ __forceinline__ uint32_t positive_bits<float>(float v) {
+  return v > 0.0f ? __float_as_uint(v) : 0u;
+}
+template <>
+__device__ __forceinline__ uint32_t positive_bits<__nv_bfloat16>(__nv_bfloat16 v) {
+  const float f = __bfloat162float(v);
+  return f > 0.0f ? __float_as_uint(f) : 0u;
+}
+
+template <typename T>
+struct Vec;
+template <>
+struct Vec<float> {
+  static constexpr int N = 4;
+  __device__ static void load(const float* p, uint32_t (&b)[4]) {
+    const float4 v = __ldcs(reinterpret_cast<const float4*>(p));
+    b[0] = positive_bits(v.x); b[1] = positive_bits(v.y); b[2] = positive_bits(v.z); b[3] = positive_bits(v.w);
+  }
+};
+template <>
+struct Vec<__nv_bfloat16> {
+  static constexpr int N = 8;
+  __device__ static void load(const __nv_bfloat16* p, uint32_t (&b)[8]) {
+    const uint4 v = __ldcs(reinterpret_cast<const uint4*>(p));
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      // a bf16 is the upper half of the float with the same value; sign bit set or zero = not positive
+      const uint32_t lo = w[i] << 16, hi = w[i] & 0xFFFF0000u;
+      b[2 * i] = (lo & 0x80000000u) || (lo & 0x7FFFFFFFu) > 0x7F800000u ? 0u : lo;
+      b[2 * i + 1] = (hi & 0x80000000u) || (hi & 0x7FFFFFFFu) > 0x7F800000u ? 0u : hi;
+    }
+  }
+};
+
+// x is a contiguous [A, S, N] array; the selection runs over all (a, n) of segment s: A rows of N contiguous elements.
+// `visit(bits)` is called for every positive element. Rows are cut into chunks of threads x 16 bytes.
+template <typename T, int THREADS, typename Fn>
+__device__ __forceinline__ void for_each_positive(const T* __restrict__ x, long long A, long long S, long long N,
+                                                  long long s, Fn visit) {
+  constexpr int V = Vec<T>::N;
+  const long long chunk = (long long)THREADS * V;
+  const long long chunks_per_row = (N + chunk - 1) / chunk;
+  const bool vec_ok = (N % V == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0);
+  for (long long item = blockIdx.x; item < A * chunks_per_row; item += gridDim.x) {
+    const long long a = item / chunks_per_row, ch = item - a * chunks_per_row;
+    const T* row = x + (a * S + s) * N;
+    const long long e = ch * chunk + (long long)threadIdx.x * V;
+    if (e >= N) continue;
+    if (vec_ok) {
+      uint32_t b[V];
+      Vec<T>::load(row + e, b);
+#pragma unroll
+      for (int i = 0; i < V; ++i)
+        if (b[i] != 0) visit(b[i]);
+    } else {
+      for (int i = 0; i < V && e + i < N; ++i) {
+        const uint32_t b = positive_bits<T>(row[e + i]);
+        if (b != 0) visit(b);
+      }
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(HIST_THREADS)
+radix_hist_hi_kernel(const T* __restrict__ x, long long A, long long S, long long N, long long s,
+                     unsigned* __restrict__ hist) {
+  extern __shared__ unsigned s_hist[];  // [kHiBins]
+  for (int i = threadIdx.x; i < kHiBins; i += HIST_THREADS) s_hist[i] = 0;
+  __syncthreads();
+  for_each_positive<T, HIST_THREADS>(x, A, S, N, s, [&](uint32_t b) {
+    uint32_t bin = b >> 16;
+    if (bin >= (uint32_t)kHiBins) bin = kHiBins - 1;
+    atomicAdd(&s_hist[bin], 1u);
+  });
+  __syncthreads();
+  for (int i = threadIdx.x; i < kHiBins; i += HIST_THREADS) {
+    const unsigned c = s_hist[i];
+    if (c != 0) atomicAdd(&hist[i], c);
+  }
+}
+
+// second level: members of the bin sel[0] only (a small fraction of the data), straight to global memory
+template <typename T>
+__global__ void __launch_bounds__(256)
+radix_hist_lo_kernel(const T* __restrict__ x, long long A, long long S, long long N, long long s,
+                     const long long* __restrict__ sel, unsigned* __restrict__ hist) {
+  const uint32_t want = (uint32_t)sel[0];
+  for_each_positive<T, 256>(x, A, S, N, s, [&](uint32_t b) {
+    uint32_t bin = b >> 16;
+    if (bin >= (uint32_t)kHiBins) bin = kHiBins - 1;
+    if (bin == want) atomicAdd(&hist[b & 0xFFFFu], 1u);
+  });
+}
+
+// One CTA: the largest bin b with  count(bins >= b) >= k.  sel_out = {b, k - count(bins > b), count(all bins)}.
+// With fewer than k members in total the pick is bin 0 (everything positive passes). `level` 0 = upper bits, 1 = lower
+// bits: level 1 takes k from sel_in[1], and writes the threshold  float((sel_in[0] << 16) | b)  to thr.
+__global__ void __launch_bounds__(1024)
+radix_pick_kernel(const unsigned* __restrict__ hist, int nbins, long long k, const long long* __restrict__ sel_in,
+                  int level, long long* __restrict__ sel_out, float* __restrict__ thr) {
+  __shared__ long long s_part[1024];
+  __shared__ long long s_above;  // count in the chunks above the chosen chunk
+  __shared__ int s_chunk;
+  if (level == 1) k = sel_in[1];
+  const bool take_all = k <= 0;  // fewer than k positive values overall: every positive value passes
+  const int per = (nbins + 1023) / 1024;
+  // thread i owns bins [hi - per, hi) counted from the top, so that a scan over threads walks downwards
+  const int hi = nbins - (int)threadIdx.x * per;
+  long long mine = 0;
+  for (int b = hi - 1; b >= hi - per && b >= 0; --b) mine += hist[b];
+  s_part[threadIdx.x] = mine;
+  if (threadIdx.x == 0) { s_chunk = -1; s_above = 0; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    long long run = 0;
+    for (int i = 0; i < 1024; ++i) {
+      if (run + s_part[i] >= k && s_chunk < 0) { s_chunk = i; s_above = run; }
+      run += s_part[i];
+    }
+    sel_out[2] = run;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    long long bin = 0, remaining = k;
+    if (s_chunk >= 0) {
+      long long run = s_above;
+      const int top = nbins - s_chunk * per;
+      for (int b = top - 1; b >= top - per && b >= 0; --b) {
+        const long long c = hist[b];
+        if (run + c >= k) { bin = b; remaining = k - run; break; }
+        run += c;
+      }
+    } else {
+      remaining = 0;  // fewer than k positive values: keep them all
+    }
+    if (take_all) { bin = 0; remaining = 0; }
+    sel_out[0] = bin;
+    sel_out[1] = remaining;
+    if (level == 1 && thr != nullptr) {
+      const uint32_t bits = ((uint32_t)sel_in[0] << 16) | (uint32_t)bin;
+      // bin 0 of both levels = "everything positive": the smallest positive float keeps x > 0 as the rule
+      *thr = bits == 0 ? __uint_as_float(1u) : __uint_as_float(bits);
+    }
+    if (level == 0 && thr != nullptr) {
+      const uint32_t bits = (uint32_t)bin << 16;  // bf16 data: the upper half IS the value
+      *thr = bits == 0 ? __uint_as_float(1u) : __uint_as_float(bits);
+    }
+  }
+}
+
+// ---- dense rows -> padded sparse lists --------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ float to_float(T v);
+template <>
+__device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+constexpr int RC_THREADS = 256;
+
+// One CTA per row (grid-stride). Columns are visited 256 at a time; a ballot per warp plus a prefix over the eight warp
+// counts gives every non-zero its slot, so the list comes out in ascending column order (deterministic).
+template <typename T>
+__global__ void __launch_bounds__(RC_THREADS)
+row_compact_kernel(const T* __restrict__ x, int B, long long N, int cap, int* __restrict__ idx, float* __restrict__ val,
+                   int* __restrict__ nnz) {
+  __shared__ int s_warp[RC_THREADS / 32];
+  __shared__ int s_base;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int row = blockIdx.x; row < B; row += gridDim.x) {
+    __syncthreads();
+    if (threadIdx.x == 0) s_base = 0;
+    __syncthreads();
+    const T* xr = x + (size_t)row * N;
+    for (long long c0 = 0; c0 < N; c0 += RC_THREADS) {
+      const long long c = c0 + threadIdx.x;
+      const float v = c < N ? to_float<T>(xr[c]) : 0.0f;
+      const bool nz = v != 0.0f;
+      const unsigned bal = __ballot_sync(0xffffffffu, nz);
+      if (lane == 0) s_warp[warp] = __popc(bal);
+      __syncthreads();
+      int before = 0, total = 0;
+#pragma unroll
+      for (int w = 0; w < RC_THREADS / 32; ++w) {
+        const int cnt = s_warp[w];
+        if (w < warp) before += cnt;
+        total += cnt;
+      }
+      const int base = s_base;
+      if (nz && idx != nullptr) {
+        const int slot = base + before + __popc(bal & ((1u << lane) - 1u));
+        if (slot < cap) {
+          idx[(size_t)row * cap + slot] = (int)c;
+          val[(size_t)row * cap + slot] = v;
+        }
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) s_base = base + total;
+    }
+    __syncthreads();
+    const int count = s_base;
+    if (threadIdx.x == 0 && nnz != nullptr) nnz[row] = count;
+    if (idx != nullptr) {
+      for (int j = count + threadIdx.x; j < cap; j += RC_THREADS) {
+        idx[(size_t)row * cap + j] = -1;
+        val[(size_t)row * cap + j] = 0.0f;
+      }
+    }
+  }
+}
+
+// ---- masked row gather with a dtype cast ------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float (&f)[8]);
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float (&f)[8]) {
+  const float4 a = __ldcs(reinterpret_cast<const float4*>(p)), b = __ldcs(reinterpret_cast<const float4*>(p) + 1);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&f)[8]) {
+  const uint4 u = __ldcs(reinterpret_cast<const uint4*>(p));
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+template <typename T>
+__device__ __forceinline__ void store8(T* p, const float (&f)[8]);
+template <>
+__device__ __forceinline__ void store8<float>(float* p, const float (&f)[8]) {
+  reinterpret_cast<float4*>(p)[0] = make_float4(f[0], f[1], f[2], f[3]);
+  reinterpret_cast<float4*>(p)[1] = make_float4(f[4], f[5], f[6], f[7]);
+}
+template <>
+__device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const float (&f)[8]) {
+  uint4 o;
+  o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]); o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
+  *reinterpret_cast<uint4*>(p) = o;
+}
+
+// pos = exclusive prefix sum of keep; rows with keep != 0 land at out[pos[i], :]. d % 8 == 0; 8 elements per thread step
+// (fp32 -> bf16 rounds to nearest even; the other three combinations are exact).
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256)
+gather_rows_cast_kernel(const TI* __restrict__ src, const int* __restrict__ keep, const int* __restrict__ pos, long long n,
+                        int d, TO* __restrict__ out, long long out_rows) {
+  for (long long i = blockIdx.x; i < n; i += gridDim.x) {
+    if (keep[i] == 0 || pos[i] < 0 || pos[i] >= out_rows) continue;  // a row that does not fit is dropped, never written
+    const TI* s = src + (size_t)i * d;
+    TO* o = out + (size_t)pos[i] * d;
+    for (int c = threadIdx.x * 8; c < d; c += 256 * 8) {
+      float f[8];
+      load8<TI>(s + c, f);
+      store8<TO>(o + c, f);
+    }
+  }
+}
+
+}  // namespace
+
+int radix_hist_launch(int dtype, const void* x, long long A, long long S, long long N, long long s, int level,
+                      const long long* sel, unsigned* hist, cudaStream_t stream) {
+  if (A <= 0 || N <= 0 || s < 0 || s >= S) return (int)cudaErrorInvalidValue;
+  if (level == 0) {
+    const size_t smem = (size_t)kHiBins * 4;
+    cudaError_t e;
+    if (dtype == 0) {
+      e = cudaFuncSetAttribute(radix_hist_hi_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+      radix_hist_hi_kernel<float><<<148, HIST_THREADS, smem, stream>>>(static_cast<const float*>(x), A, S, N, s, hist);
+    } else {
+      e = cudaFuncSetAttribute(radix_hist_hi_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+      radix_hist_hi_kernel<__nv_bfloat16>
+          <<<148, HIST_THREADS, smem, stream>>>(static_cast<const __nv_bfloat16*>(x), A, S, N, s, hist);
+    }
+  } else {
+    if (dtype == 0)
+      radix_hist_lo_kernel<float><<<148 * 8, 256, 0, stream>>>(static_cast<const float*>(x), A, S, N, s, sel, hist);
+    else
+      radix_hist_lo_kernel<__nv_bfloat16>
+          <<<148 * 8, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), A, S, N, s, sel, hist);
+  }
+  return (int)cudaGetLastError();
+}
+
+int radix_hi_bins() { return kHiBins; }
+
+int radix_pick_launch(const unsigned* hist, int nbins, long long k, const long long* sel_in, int level, long long* sel_out,
+                      float* thr, cudaStream_t stream) {
+  if (nbins <= 0 || nbins > 65536 || (level == 1 && sel_in == nullptr)) return (int)cudaErrorInvalidValue;
+  radix_pick_kernel<<<1, 1024, 0, stream>>>(hist, nbins, k, sel_in, level, sel_out, thr);
+  return (int)cudaGetLastError();
+}
+
+int row_compact_launch(int dtype, const void* x, int B, long long N, int cap, int* idx, float* val, int* nnz,
+                       cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (N > 2147483647LL) return (int)cudaErrorInvalidValue;
+  const int blocks = B < 148 * 8 ? B : 148 * 8;
+  if (dtype == 0)
+    row_compact_kernel<float><<<blocks, RC_THREADS, 0, stream>>>(static_cast<const float*>(x), B, N, cap, idx, val, nnz);
+  else
+    row_compact_kernel<__nv_bfloat16>
+        <<<blocks, RC_THREADS, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), B, N, cap, idx, val, nnz);
+  return (int)cudaGetLastError();
+}
+
+int gather_rows_cast_launch(int in_dtype, int out_dtype, const void* src, const int* keep, const int* pos, long long n,
+                            int d, void* out, long long out_rows, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (d % 8 != 0) return (int)cudaErrorInvalidValue;
+  const int blocks = (int)(n < 148LL * 16 ? n : 148LL * 16);
+  using bf = __nv_bfloat16;
+  if (in_dtype == 0 && out_dtype == 0)
+    gather_rows_cast_kernel<float, float><<<blocks, 256, 0, stream>>>((const float*)src, keep, pos, n, d, (float*)out, out_rows);
+  else if (in_dtype == 0 && out_dtype == 1)
+    gather_rows_cast_kernel<float, bf><<<blocks, 256, 0, stream>>>((const float*)src, keep, pos, n, d, (bf*)out, out_rows);
+  else if (in_dtype == 1 && out_dtype == 0)
+    gather_rows_cast_kernel<bf, float><<<blocks, 256, 0, stream>>>((const bf*)src, keep, pos, n, d, (float*)out, out_rows);
+  else if (in_dtype == 1 && out_dtype == 1)
+    gather_rows_cast_kernel<bf, bf><<<blocks, 256, 0, stream>>>((const bf*)src, keep, pos, n, d, (bf*)out, out_rows);
+  else
+    return (int)cudaErrorInvalidValue;
+  return (int)cudaGetLastError();
+}
+
+}  // namespace lmsae

@@ -414,7 +414,7 @@ csc_scan_add_kernel(const int* __restrict__ block_sums, int F, int* __restrict__
     if (base + i < F) {
       const int o = offsets[base + i] + add;
       offsets[base + i] = o;
-      cursor[base + i] = o;
+      if (cursor != nullptr) cursor[base + i] = o;
     }
   }
 }
@@ -446,6 +446,16 @@ int csc_build_launch(const int* idx, long long n, int F, int* counts, int* offse
   csc_scan_sums_kernel<<<1, SCAN_THREADS, 0, stream>>>(block_sums, nblocks, offsets, F);
   csc_scan_add_kernel<<<nblocks, SCAN_THREADS, 0, stream>>>(block_sums, F, offsets, cursor);
   csc_fill_kernel<<<blocks, threads, 0, stream>>>(idx, n, F, cursor, entries);
+  return (int)cudaGetLastError();
+}
+
+// offsets[0..n] = exclusive prefix sum of counts[0..n-1] (offsets[n] = total); `block_sums_buf`: one int per 4096 counts
+int exclusive_scan_launch(const int* counts, int n, int* offsets, int* block_sums_buf, cudaStream_t stream) {
+  if (n <= 0) return (int)cudaErrorInvalidValue;
+  const int nblocks = (n + SCAN_ELEMS - 1) / SCAN_ELEMS;
+  csc_scan_local_kernel<<<nblocks, SCAN_THREADS, 0, stream>>>(counts, n, offsets, block_sums_buf);
+  csc_scan_sums_kernel<<<1, SCAN_THREADS, 0, stream>>>(block_sums_buf, nblocks, offsets, n);
+  csc_scan_add_kernel<<<nblocks, SCAN_THREADS, 0, stream>>>(block_sums_buf, n, offsets, nullptr);
   return (int)cudaGetLastError();
 }
 

@@ -1,0 +1,174 @@
+"""Selection and compaction on the GPU: batch-level top-k thresholds by radix select, dense rows to padded sparse lists,
+and masked row compaction with a dtype cast (kernels of ``csrc/select_ops.cu``), each with a plain-torch oracle.
+
+* ``positive_topk(x, k, dims, group)`` keeps the ``k`` largest positive entries over ``dims`` (mask-multiply, straight-
+  through gradient), the batch-level selection of BatchTopK dictionaries (models/sparse_dictionary.py:775-788 of the
+  reference project) and of the cross-layer transcoder's ``batchtopk`` / ``batchlayertopk`` (models/clt.py:330-368 there).
+  On a GPU the threshold is the exact k-th largest value found by a two-level histogram of the float bit patterns: two
+  streaming passes over ``x`` instead of a sort; under feature or data sharding the ranks add their histograms (two
+  all-reduces of at most 256 KB) where the reference bisects with one all-reduce per iteration
+  (utils/distributed/ops.py:226-250 there). Entries equal to the threshold all pass, so ties keep more than ``k``.
+* ``dense_rows_to_sparse`` turns ``[B, N]`` activations into ``(idx, val)`` lists in ascending column order.
+* ``compact_rows`` drops masked-out token rows (and casts) in one pass: activation/processors/activation.py:277-285.
+"""
+
+from __future__ import annotations
+
+from typing import Sequence
+
+import torch
+import torch.distributed as dist
+
+from . import sae_kernels as K
+
+_MAX_SEGMENTS = 64
+
+
+def ref_positive_threshold(values: torch.Tensor, k: int) -> torch.Tensor:
+    """k-th largest positive entry of a flat tensor (fp32 scalar); the smallest positive float if there are fewer."""
+    pos = values[values > 0].float()
+    if pos.numel() < k or k <= 0:
+        return torch.tensor(1e-45, dtype=torch.float32, device=values.device)
+    return torch.topk(pos, k).values[-1]
+
+
+def _kernel_ok(x: torch.Tensor) -> bool:
+    return x.is_cuda and x.dtype in (torch.float32, torch.bfloat16) and x.numel() > 0
+
+
+@torch.no_grad()
+def positive_thresholds(x3: torch.Tensor, k: int, group=None) -> torch.Tensor:
+    """``x3``: contiguous ``[A, S, N]``. Returns fp32 ``[S]``: for every segment ``s`` the k-th largest positive value of
+    ``x3[:, s, :]``, taken over the union of all ranks of ``group`` when one is given."""
+    A, S, N = x3.shape
+    world = dist.get_world_size(group) if group is not None else 1
+    if not _kernel_ok(x3):
+        out = []
+        for s in range(S):
+            vals = x3[:, s, :].reshape(-1)
+            if world > 1:
+                kk = min(k, vals.numel())
+                top = torch.topk(vals.float().clamp_min(0), kk).values
+                parts = [torch.empty_like(top) for _ in range(world)]
+                dist.all_gather(parts, top, group=group)
+                vals = torch.cat(parts)
+            out.append(ref_positive_threshold(vals, k))
+        return torch.stack(out)
+    ext = K._ext()
+    dev = x3.device
+    nhi = int(ext.radix_hi_bins())
+    hist_hi = torch.empty(nhi, dtype=torch.int32, device=dev)
+    hist_lo = torch.empty(65536, dtype=torch.int32, device=dev)
+    sel0 = torch.zeros(4, dtype=torch.int64, device=dev)
+    sel1 = torch.zeros(4, dtype=torch.int64, device=dev)
+    thr = torch.empty(S, dtype=torch.float32, device=dev)
+    half = x3.dtype == torch.bfloat16  # 16-bit data: the first level already resolves the value
+    for s in range(S):
+        hist_hi.zero_()
+        ext.radix_hist(x3, A, S, N, s, 0, None, hist_hi)
+        if world > 1:
+            dist.all_reduce(hist_hi, group=group)
+        ext.radix_pick(hist_hi, nhi, int(k), None, 0, sel0, thr[s : s + 1] if half else None)
+        if not half:
+            hist_lo.zero_()
+            ext.radix_hist(x3, A, S, N, s, 1, sel0, hist_lo)
+            if world > 1:
+                dist.all_reduce(hist_lo, group=group)
+            ext.radix_pick(hist_lo, 65536, 0, sel0, 1, sel1, thr[s : s + 1])
+    return thr
+
+
+def _middle_block(ndim: int, dims: Sequence[int]) -> tuple[int, int] | None:
+    """The kept dimensions must be one contiguous block ``[i, j)`` (possibly empty, anywhere): returns ``(i, j)``."""
+    sel = sorted(d % ndim for d in dims)
+    keep = [d for d in range(ndim) if d not in sel]
+    if not keep:
+        return (0, 0)
+    if keep != list(range(keep[0], keep[-1] + 1)):
+        return None
+    return keep[0], keep[-1] + 1
+
+
+def positive_topk(x: torch.Tensor, k: int, dims: Sequence[int], group=None) -> torch.Tensor | None:
+    """``x * mask`` where ``mask`` marks the ``k`` largest positive entries over ``dims`` (separately for every index of
+    the other dimensions). Returns None when the layout is not one this path handles (callers then use the sort-based
+    implementation): the kept dimensions must be adjacent, with at most 64 index combinations, and the last dimension
+    must be selected over."""
+    blk = _middle_block(x.ndim, dims)
+    if blk is None or not _kernel_ok(x) or (x.ndim - 1) not in {d % x.ndim for d in dims}:
+        return None
+    i, j = blk
+    S = 1
+    for s_ in x.shape[i:j]:
+        S *= s_
+    if S > _MAX_SEGMENTS:
+        return None
+    xc = x.contiguous()
+    A = 1
+    for a_ in x.shape[:i]:
+        A *= a_
+    N = xc.numel() // (A * S)
+    thr = positive_thresholds(xc.detach().view(A, S, N), k, group)
+    shape = [1] * x.ndim
+    for d_ in range(i, j):
+        shape[d_] = x.shape[d_]
+    with torch.no_grad():
+        mask = (xc.detach() >= thr.view(shape).to(xc.dtype)) & (xc.detach() > 0)
+    return xc * mask.to(xc.dtype)
+
+
+# ---- dense rows -> padded sparse ---------------------------------------------------------------------
+def ref_dense_rows_to_sparse(acts: torch.Tensor, cap: int) -> tuple[torch.Tensor, torch.Tensor]:
+    B, N = acts.shape
+    idx = torch.full((B, cap), -1, dtype=torch.int32, device=acts.device)
+    val = torch.zeros(B, cap, dtype=torch.float32, device=acts.device)
+    for b in range(B):
+        cols = torch.nonzero(acts[b], as_tuple=False).flatten()[:cap]
+        idx[b, : cols.numel()] = cols.to(torch.int32)
+        val[b, : cols.numel()] = acts[b, cols].float()
+    return idx, val
+
+
+@torch.no_grad()
+def dense_rows_to_sparse(acts: torch.Tensor, cap: int | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """``[B, N]`` -> ``(idx int32 [B, cap], val fp32 [B, cap])``, ascending columns, ``-1`` / ``0`` padding. ``cap`` None:
+    the largest row count, rounded up to a multiple of 8 (costs a counting pass and one host read)."""
+    assert acts.ndim == 2
+    if not _kernel_ok(acts):
+        if cap is None:
+            cap = max(8, -(-int((acts != 0).sum(-1).max()) // 8) * 8) if acts.numel() else 8
+        return ref_dense_rows_to_sparse(acts, cap)
+    acts = acts.contiguous()
+    ext = K._ext()
+    B = acts.shape[0]
+    nnz = torch.empty(B, dtype=torch.int32, device=acts.device)
+    if cap is None:
+        ext.row_compact(acts, None, None, nnz)
+        cap = max(8, -(-int(nnz.max()) // 8) * 8)
+    idx = torch.empty(B, cap, dtype=torch.int32, device=acts.device)
+    val = torch.empty(B, cap, dtype=torch.float32, device=acts.device)
+    ext.row_compact(acts, idx, val, nnz)
+    return idx, val
+
+
+# ---- masked row compaction ---------------------------------------------------------------------------
+@torch.no_grad()
+def compact_rows(src: torch.Tensor, keep: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """Rows of ``src [n, d]`` whose ``keep [n]`` entry is set, in order, cast to ``out_dtype``."""
+    out_dtype = out_dtype or src.dtype
+    ok = (
+        _kernel_ok(src) and src.ndim == 2 and src.shape[1] % 8 == 0 and out_dtype in (torch.float32, torch.bfloat16)
+        and src.shape[0] < 2**31 - 1
+    )  # fmt: skip
+    if not ok:
+        return src[keep.bool()].to(out_dtype)
+    ext = K._ext()
+    n = src.shape[0]
+    keep32 = keep.to(torch.int32).contiguous()
+    pos = torch.empty(n + 1, dtype=torch.int32, device=src.device)
+    sums = torch.empty((n + 4095) // 4096, dtype=torch.int32, device=src.device)
+    ext.exclusive_scan(keep32, pos, sums)
+    m = int(pos[n])
+    out = torch.empty(m, src.shape[1], dtype=out_dtype, device=src.device)
+    ext.gather_rows_cast(src.contiguous(), keep32, pos, out)
+    return out

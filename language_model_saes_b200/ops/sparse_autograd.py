@@ -18,6 +18,10 @@ from . import sae_kernels as K
 def dense_to_padded_sparse(acts: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     """``[B, F]`` -> ``(idx int32 [B, kmax], val fp32 [B, kmax])`` holding every non-zero of each row (``idx = -1`` in
     the padding), ``kmax`` = largest number of non-zeros in a row, rounded up to a multiple of 8."""
+    if acts.is_cuda and acts.dtype in (torch.float32, torch.bfloat16):
+        from .select_kernels import dense_rows_to_sparse  # one counting pass + one ordered compaction pass
+
+        return dense_rows_to_sparse(acts)
     nz = acts != 0
     kmax = max(8, -(-int(nz.sum(dim=-1).max()) // 8) * 8)
     kmax = min(kmax, acts.shape[-1])
