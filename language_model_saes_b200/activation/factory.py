@@ -53,6 +53,9 @@ class ActivationFactoryActivationsSource(ActivationFactorySource):
     dtype: OptionalTorchDType = None
     num_workers: int = 4
     prefetch: int | None = 8
+    peer_broadcast: bool = False
+    """Under model parallelism: one rank of each ``model`` group reads the files and pushes the rows into the other ranks'
+    GPU memory over NVLink instead of every rank reading them (CUDA devices only)."""
 
 
 class ActivationFactoryTarget(Enum):
@@ -141,7 +144,8 @@ class ActivationFactory:
             raise ValueError("Activations sources are only supported for target >= ACTIVATIONS_2D")
         dirs = source.path if isinstance(source.path, dict) else {hp: Path(source.path) / hp for hp in self.cfg.hook_points}
         loader = CachedActivationLoader(cache_dirs=dirs, device=source.device, dtype=source.dtype, num_workers=source.num_workers,
-                                        prefetch_factor=source.prefetch, device_mesh=self.device_mesh)  # fmt: skip
+                                        prefetch_factor=source.prefetch, device_mesh=self.device_mesh,
+                                        peer_broadcast=source.peer_broadcast)  # fmt: skip
         steps = [ActivationTransformer()] if self.cfg.target >= ActivationFactoryTarget.ACTIVATIONS_1D else []
 
         def run(**kwargs: Any) -> Iterable[dict[str, Any]]:

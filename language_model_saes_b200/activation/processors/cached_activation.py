@@ -9,7 +9,8 @@ Reading is overlapped with consumption: a small pool of threads loads upcoming c
 (bounded look-ahead) and, for a CUDA target, the host-to-device copy is issued on a side stream one chunk
 ahead. Under data parallelism rank r reads chunks r, r+dp, r+2dp, ... (the reference's striding); ranks of the
 same ``model`` / ``sweep`` group read the same chunks themselves (the page cache serves the repeats) instead of
-loading different hook points and all-gathering them.
+loading different hook points and all-gathering them; with ``peer_broadcast`` only the first rank of a ``model`` group
+reads, and one kernel pushes the rows into the other ranks' memory over NVLink.
 """
 
 from __future__ import annotations
@@ -59,7 +60,10 @@ class CachedActivationLoader(BaseActivationProcessor[None, Iterable[dict[str, An
         num_workers: int = 0,
         prefetch_factor: int | None = None,
         device_mesh=None,
+        peer_broadcast: bool = False,
     ):
+        self.peer_broadcast = peer_broadcast
+        self._bcast = None
         self.cache_dirs = {k: Path(v) for k, v in cache_dirs.items()}
         self.device = device
         self.dtype = dtype
@@ -130,6 +134,58 @@ class CachedActivationLoader(BaseActivationProcessor[None, Iterable[dict[str, An
         return moved
 
     def process(self, data: None = None, **kwargs) -> Iterator[dict[str, Any]]:
+        tp = mesh_dim_size(self.device_mesh, "model")
+        if self.peer_broadcast and tp > 1 and torch.device(self.device).type == "cuda":
+            yield from self._process_peer_broadcast()
+            return
+        yield from self._process_local()
+
+    # ---- one reader per model-parallel group, rows pushed to the peers over NVLink -----------------------
+    def _process_peer_broadcast(self) -> Iterator[dict[str, Any]]:
+        """The first rank of every ``model`` group reads, pins and uploads the chunks; every activation tensor then goes
+        to the other ranks of the group through ``BroadcastComm`` (peer stores from one kernel), the small integer
+        tensors and the meta through the process group. The other ranks open no file."""
+        import torch.distributed as dist
+
+        from ...parallel.dist_ops import broadcast_object
+        from ...parallel.symm import BroadcastComm
+
+        group = self.device_mesh.get_group("model")
+        dev = torch.device(self.device)
+        loader = mesh_local_rank(self.device_mesh, "model") == 0
+        src_global = dist.get_global_rank(group, 0)
+        stream = self._process_local() if loader else None
+        while True:
+            rec = next(stream, None) if loader else None
+            header = None
+            if loader and rec is not None:
+                header = {k: ((tuple(v.shape), v.dtype) if isinstance(v, torch.Tensor) else ("obj", v)) for k, v in rec.items()}
+            header = broadcast_object(header, group_src=0, group=group)
+            if header is None:
+                return
+            out: dict[str, Any] = {}
+            for key, info in header.items():
+                if info[0] == "obj":
+                    out[key] = info[1]
+                    continue
+                shape, dtype = info
+                wide = dtype in (torch.float32, torch.bfloat16) and len(shape) >= 2 and shape[-1] % 8 == 0
+                if wide:
+                    d = shape[-1]
+                    n_rows = 1
+                    for s_ in shape[:-1]:
+                        n_rows *= s_
+                    if self._bcast is None or self._bcast.max_rows < n_rows or self._bcast.max_row_bytes < d * dtype.itemsize:
+                        self._bcast = BroadcastComm(group, dev, n_rows, d * dtype.itemsize)
+                    rows = rec[key].reshape(n_rows, d) if loader else None
+                    out[key] = self._bcast.broadcast_rows(0, d, dtype, rows).view(*shape)
+                else:
+                    t = rec[key].contiguous() if loader else torch.empty(shape, dtype=dtype, device=dev)
+                    dist.broadcast(t, src=src_global, group=group)
+                    out[key] = t
+            yield out
+
+    def _process_local(self) -> Iterator[dict[str, Any]]:
         hook_chunks = {hp: self._get_sorted_chunks(hp) for hp in self.cache_dirs}
         counts = {hp: len(c) for hp, c in hook_chunks.items()}
         if len(set(counts.values())) != 1:

@@ -46,6 +46,10 @@ class CrosscoderSpecs(TensorSpecs):
 class CrosscoderConfig(SparseDictionaryConfig):
     sae_type: str = "crosscoder"
     hook_points: list[str]
+    fused_head_sum: bool | None = None
+    """Sum the encoder pre-activations over heads inside the encoder GEMM (local heads in its K loop, other ranks of
+    the ``head`` group through a reduce-scatter epilogue over peer memory). None: on for bf16 models under head
+    parallelism on CUDA; True also uses the kernel without a ``head`` group."""
 
     @property
     def associated_hook_points(self) -> list[str]:
@@ -62,6 +66,41 @@ class CrosscoderConfig(SparseDictionaryConfig):
     @property
     def n_heads(self) -> int:
         return len(self.hook_points)
+
+
+class _HeadSumEncode(torch.autograd.Function):
+    """``sum over all heads of (x_h W_E[h] + b_E[h])`` through ``HeadSumComm`` (bf16 operands, fp32 accumulation and
+    reduction). The value is used by every rank's own heads, so the incoming gradient is summed over the group first
+    (as in ``all_reduce_sum_both``); the weight and input gradients are plain batched products."""
+
+    @staticmethod
+    def forward(ctx, x, W_E, b_E, comm, group):
+        B, H, d = x.shape
+        F = W_E.shape[-1]
+        x16 = x.detach().to(torch.bfloat16).reshape(B, H * d).contiguous()
+        w16 = W_E.detach().transpose(1, 2).to(torch.bfloat16).contiguous().view(H * F, d)  # feature-major blocks
+        out = comm.head_sum(x16, w16, b_E.detach().float().sum(dim=0).contiguous(), H, F, torch.float32)
+        ctx.save_for_backward(x16, w16)
+        ctx.group, ctx.shape, ctx.dtypes = group, (B, H, d, F), (x.dtype, W_E.dtype, b_E.dtype)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad):
+        x16, w16 = ctx.saved_tensors
+        B, H, d, F = ctx.shape
+        g = grad.contiguous().float()
+        if ctx.group is not None and dist.get_world_size(ctx.group) > 1:
+            g = g.clone()
+            dist.all_reduce(g, group=ctx.group)
+        g16 = g.to(torch.bfloat16)
+        dx = dW = db = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.einsum("bf,hfd->bhd", g16, w16.view(H, F, d)).to(ctx.dtypes[0])
+        if ctx.needs_input_grad[1]:
+            dW = torch.einsum("bhd,bf->hdf", x16.view(B, H, d), g16).to(ctx.dtypes[1])
+        if ctx.needs_input_grad[2]:
+            db = g.sum(dim=0).to(ctx.dtypes[2]).unsqueeze(0).expand(H, F)
+        return dx, dW, db, None, None
 
 
 @register_sae_model("crosscoder")
@@ -82,6 +121,7 @@ class Crosscoder(SparseDictionary):
         self.b_E = nn.Parameter(torch.empty(H_l, F_l, device=dev, dtype=dt))
         self.W_D = nn.Parameter(torch.empty(H_l, F_l, d, device=dev, dtype=dt))
         self.b_D = nn.Parameter(torch.empty(H_l, d, device=dev, dtype=dt))
+        self._head_sum_comm = None
         self.setup()
 
     @property
@@ -165,9 +205,32 @@ class Crosscoder(SparseDictionary):
         """[..., H_l, d] -> [..., H_l, F_l]"""
         return torch.einsum("...hd,hdf->...hf", x.to(self.W_E.dtype), self.W_E) + self.b_E
 
-    def encode(self, x: torch.Tensor, return_hidden_pre: bool = False, **kwargs):
+    def _fused_head_sum_ok(self, x: torch.Tensor) -> bool:
+        want = self.cfg.fused_head_sum
+        if want is None:
+            want = self.cfg.dtype == torch.bfloat16 and self.head_size > 1
+        return bool(
+            want and x.is_cuda and x.ndim >= 2 and self.cfg.d_model % 64 == 0
+            and self.d_sae_local % (self.head_size * 32) == 0
+        )  # fmt: skip
+
+    def _summed_pre(self, x: torch.Tensor) -> torch.Tensor:
+        """Pre-activations summed over ALL heads (local heads and the other ranks of the ``head`` group)."""
+        if self._fused_head_sum_ok(x):
+            # one tcgen05 GEMM over K = local heads x d_model whose epilogue reduce-scatters into peer memory
+            from ..parallel.symm import HeadSumComm
+
+            rows = x[..., 0, 0].numel()
+            if self._head_sum_comm is None or self._head_sum_comm.max_rows < rows:
+                self._head_sum_comm = HeadSumComm(self.head_group, x.device, rows, self.d_sae_local)
+            lead = x.shape[:-2]
+            out = _HeadSumEncode.apply(x.reshape(rows, *x.shape[-2:]), self.W_E, self.b_E, self._head_sum_comm, self.head_group)
+            return out.reshape(*lead, self.d_sae_local).to(self.cfg.dtype)
         summed = self._per_head_pre(x).sum(dim=-2)
-        summed = all_reduce_sum_both(summed, self.head_group)
+        return all_reduce_sum_both(summed, self.head_group)
+
+    def encode(self, x: torch.Tensor, return_hidden_pre: bool = False, **kwargs):
+        summed = self._summed_pre(x)
         hidden_pre = summed.unsqueeze(-2).expand(*summed.shape[:-1], self.n_heads_local, summed.shape[-1])
         norm = self.decoder_norm()
         feature_acts = self.activation_function(hidden_pre * norm) / norm

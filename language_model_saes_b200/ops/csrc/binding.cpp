@@ -625,6 +625,96 @@ void comm_shuffle_rows(const std::vector<int64_t>& table, const Tensor& src, con
              "shuffle_rows launch");
 }
 
+// src [n, d] (fp32 / bf16) on the sending rank; keep / pos int32 [n] / [n + 1] or absent; the landing zone at
+// `recv_off` holds `cap_rows` rows of d elements of `out_dtype` (0 = fp32, 1 = bf16).
+void comm_bcast_rows(const std::vector<int64_t>& table, const Tensor& src, const c10::optional<Tensor>& keep,
+                     const c10::optional<Tensor>& pos, int64_t out_dtype, int64_t recv_off, int64_t cap_rows, int64_t phase,
+                     int64_t epoch, const Tensor& done_counter) {
+  TORCH_CHECK(src.is_cuda() && src.is_contiguous() && src.dim() == 2, "src must be a contiguous CUDA matrix");
+  CHECK_T(done_counter, torch::kInt32);
+  if (keep.has_value()) {
+    CHECK_T(*keep, torch::kInt32);
+    TORCH_CHECK(pos.has_value() && keep->numel() == src.size(0), "keep and pos come together");
+    CHECK_T(*pos, torch::kInt32);
+    TORCH_CHECK(pos->numel() >= src.size(0), "pos too short");
+  }
+  const c10::cuda::CUDAGuard guard(src.device());
+  lmsae::PeerTable pt = make_peer_table(table);
+  check_cuda(lmsae::bcast_rows_cast_launch(pt, dtype_code(src), (int)out_dtype, src.data_ptr(), opt_ptr<int>(keep), opt_ptr<int>(pos),
+                                           src.size(0), (int)src.size(1), recv_off, cap_rows, (int)phase, (uint32_t)epoch,
+                                           reinterpret_cast<unsigned*>(done_counter.data_ptr<int>()),
+                                           at::cuda::getCurrentCUDAStream()),
+             "comm_bcast_rows launch");
+}
+
+// Head-summed encoder GEMM with the reduce-scatter epilogue: x [M, heads * d] bf16, w [heads * rows_per_head, d] bf16
+// (head h's rows start at h * rows_per_head; the first N of them are used), bias fp32 [N] or absent. The fp32 result
+// tile is ADDED into slabs[c / (N / world)], an fp32 [M, N / world] array per rank (device pointers, peer mappings).
+void head_sum_gemm(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& bias, int64_t heads, int64_t rows_per_head,
+                   int64_t N, const std::vector<int64_t>& slabs, bool pair, const Tensor& status) {
+  CHECK_T(x, torch::kBFloat16);
+  CHECK_T(w, torch::kBFloat16);
+  CHECK_T(status, torch::kInt32);
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && heads >= 1 && x.size(1) == heads * w.size(1), "x [M, heads*d], w [heads*rows, d]");
+  TORCH_CHECK(w.size(0) == heads * rows_per_head && N <= rows_per_head, "w must hold `heads` blocks of rows_per_head rows");
+  const int64_t world = (int64_t)slabs.size();
+  TORCH_CHECK(world >= 1 && world <= 8 && N % world == 0 && (N / world) % 32 == 0, "N / world must be a multiple of 32");
+  TORCH_CHECK(w.size(1) % 64 == 0, "d must be a multiple of 64");
+  const c10::cuda::CUDAGuard guard(x.device());
+  lmsae::EncGemmParams p{};
+  p.M = (int)x.size(0);
+  p.K = (int)x.size(1);
+  p.N = (int)N;
+  p.num_panels = (p.M + 127) / 128;
+  const int n_tiles = (p.N + 255) / 256;
+  // as many column ranges as fill the GPU (one CTA per panel and range)
+  int splits = 148 / p.num_panels;
+  if (splits < 1) splits = 1;
+  if (splits > n_tiles) splits = n_tiles;
+  p.num_splits = splits;
+  if (bias.has_value()) { CHECK_T(*bias, torch::kFloat32); TORCH_CHECK(bias->numel() == p.N); }
+  p.bias = opt_ptr<const float>(bias);
+  p.status = status.data_ptr<int>();
+  p.heads = (int)heads;
+  p.b_rows_per_head = (int)rows_per_head;
+  p.red_world = (int)world;
+  p.red_cols = (int)(N / world);
+  for (int64_t i = 0; i < world; ++i) {
+    TORCH_CHECK(slabs[i] % 16 == 0, "slab pointers must be 16-byte aligned");
+    p.red_base[i] = reinterpret_cast<float*>(static_cast<uintptr_t>(slabs[i]));
+  }
+  int mode = 1;
+  if (pair && p.num_panels % 2 == 0) mode |= 8;
+  const CUtensorMap ta = make_bf16_tile_map(x.data_ptr(), p.M, p.K, 128);
+  const CUtensorMap tb = make_bf16_tile_map(w.data_ptr(), w.size(0), w.size(1), (mode & 8) ? 128 : 256);
+  check_cuda(lmsae::enc_gemm_launch(ta, tb, p, mode, at::cuda::getCurrentCUDAStream()), "head_sum_gemm launch");
+}
+
+void comm_headsum_gather(const std::vector<int64_t>& table, int64_t slab_off, int64_t out_off, int64_t B, int64_t cols,
+                         int64_t out_dtype, int64_t phase_in, int64_t phase_out, int64_t epoch, const Tensor& done_counter,
+                         const Tensor& status) {
+  CHECK_T(done_counter, torch::kInt32);
+  CHECK_T(status, torch::kInt32);
+  lmsae::PeerTable pt = make_peer_table(table);
+  check_cuda(lmsae::headsum_gather_launch(pt, slab_off, out_off, (int)B, (int)cols, (int)out_dtype, (int)phase_in, (int)phase_out,
+                                          (uint32_t)epoch, reinterpret_cast<unsigned*>(done_counter.data_ptr<int>()),
+                                          status.data_ptr<int>(), at::cuda::getCurrentCUDAStream()),
+             "comm_headsum_gather launch");
+}
+
+void comm_signal(const std::vector<int64_t>& table, int64_t phase, int64_t epoch) {
+  lmsae::PeerTable pt = make_peer_table(table);
+  check_cuda(lmsae::signal_flags_launch(pt, (int)phase, (uint32_t)epoch, at::cuda::getCurrentCUDAStream()), "comm_signal launch");
+}
+
+void comm_wait_src(const std::vector<int64_t>& table, int64_t phase, int64_t epoch, int64_t src, const Tensor& status) {
+  CHECK_T(status, torch::kInt32);
+  lmsae::PeerTable pt = make_peer_table(table);
+  check_cuda(lmsae::wait_flag_src_launch(pt, (int)phase, (uint32_t)epoch, (int)src, status.data_ptr<int>(),
+                                         at::cuda::getCurrentCUDAStream()),
+             "comm_wait_src launch");
+}
+
 void comm_wait(const std::vector<int64_t>& table, int64_t phase, int64_t epoch, const Tensor& status) {
   CHECK_T(status, torch::kInt32);
   const c10::cuda::CUDAGuard guard(status.device());
@@ -676,6 +766,11 @@ void comm_reduce_loss_push(const std::vector<int64_t>& table, int64_t B, int64_t
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("comm_push_candidates", &comm_push_candidates);
   m.def("comm_wait", &comm_wait);
+  m.def("comm_bcast_rows", &comm_bcast_rows);
+  m.def("comm_signal", &comm_signal);
+  m.def("head_sum_gemm", &head_sum_gemm);
+  m.def("comm_headsum_gather", &comm_headsum_gather);
+  m.def("comm_wait_src", &comm_wait_src);
   m.def("comm_shuffle_rows", &comm_shuffle_rows);
   m.def("comm_decode_scatter", &comm_decode_scatter);
   m.def("comm_reduce_loss_push", &comm_reduce_loss_push);

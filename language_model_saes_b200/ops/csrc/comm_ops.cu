@@ -252,6 +252,151 @@ int shuffle_rows_launch(const PeerTable& pt, const void* src, const long long* d
   return (int)cudaGetLastError();
 }
 
+// ---------------------------------------------------------------------------------------------
+// Broadcast of (optionally masked and cast) rows from one rank to every rank of the group: the rank that read a chunk of
+// cached activations from disk drops the masked-out token rows, casts to the training dtype and stores the result
+// straight into every peer's landing zone, one read of the source for `world` NVLink writes. Replaces a boolean index,
+// a dtype cast and a broadcast collective (activation/processors/cached_activation.py:301-320 and the loader-side
+// redistribute of the reference project). `pos` = exclusive prefix sum of `keep` (both nullptr: keep every row).
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256)
+bcast_rows_cast_kernel(const PeerTable pt, const TI* __restrict__ src, const int* __restrict__ keep,
+                       const int* __restrict__ pos, long long n, int d, long long recv_off, long long cap_rows, int phase,
+                       uint32_t epoch, unsigned* done_counter) {
+  for (long long i = blockIdx.x; i < n; i += gridDim.x) {
+    if (keep != nullptr && keep[i] == 0) continue;
+    const long long o = pos != nullptr ? pos[i] : i;
+    if (o < 0 || o >= cap_rows) continue;  // never written past the landing zone
+    const TI* s = src + (size_t)i * d;
+    for (int c = threadIdx.x * 8; c < d; c += 256 * 8) {
+      float f[8];
+      if constexpr (sizeof(TI) == 4) {
+        const float4 a = __ldcs(reinterpret_cast<const float4*>(s + c)), b = __ldcs(reinterpret_cast<const float4*>(s + c) + 1);
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+      } else {
+        bf16x8_to_float_c(__ldcs(reinterpret_cast<const uint4*>(s + c)), f);
+      }
+      for (int p = 0; p < pt.world; ++p) {
+        TO* dst = reinterpret_cast<TO*>(pt.base[p] + recv_off) + (size_t)o * d + c;
+        if constexpr (sizeof(TO) == 4) {
+          reinterpret_cast<float4*>(dst)[0] = make_float4(f[0], f[1], f[2], f[3]);
+          reinterpret_cast<float4*>(dst)[1] = make_float4(f[4], f[5], f[6], f[7]);
+        } else {
+          uint4 u;
+          u.x = pack_bf16x2(f[0], f[1]); u.y = pack_bf16x2(f[2], f[3]); u.z = pack_bf16x2(f[4], f[5]); u.w = pack_bf16x2(f[6], f[7]);
+          *reinterpret_cast<uint4*>(dst) = u;
+        }
+      }
+    }
+  }
+  signal_peers_when_grid_done(pt, phase, epoch, done_counter);
+}
+
+int bcast_rows_cast_launch(const PeerTable& pt, int in_dtype, int out_dtype, const void* src, const int* keep, const int* pos,
+                           long long n, int d, long long recv_off, long long cap_rows, int phase, uint32_t epoch,
+                           unsigned* done_counter, cudaStream_t stream) {
+  if (d % 8 != 0 || recv_off % 16 != 0 || phase < 0 || phase >= kNumPhases) return (int)cudaErrorInvalidValue;
+  const int blocks = (int)(n < 148LL * 8 ? (n > 0 ? n : 1) : 148LL * 8);
+  using bf = __nv_bfloat16;
+#define LMSAE_BCAST(TI, TO)                                                                                              \
+  bcast_rows_cast_kernel<TI, TO><<<blocks, 256, 0, stream>>>(pt, static_cast<const TI*>(src), keep, pos, n, d, recv_off, \
+                                                             cap_rows, phase, epoch, done_counter)
+  if (in_dtype == 0 && out_dtype == 0) LMSAE_BCAST(float, float);
+  else if (in_dtype == 0 && out_dtype == 1) LMSAE_BCAST(float, bf);
+  else if (in_dtype == 1 && out_dtype == 0) LMSAE_BCAST(bf, float);
+  else if (in_dtype == 1 && out_dtype == 1) LMSAE_BCAST(bf, bf);
+  else return (int)cudaErrorInvalidValue;
+#undef LMSAE_BCAST
+  return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Second half of the head-summed encoder: after every rank's GEMM epilogue has added its partial pre-activations into
+// the column slab this rank owns (reduce-scatter by vector reductions over NVLink, encoder_gemm.cu), the owner reads
+// its fp32 slab [B, cols] once, stores the sums into every rank's full [B, world * cols] output (all-gather by peer
+// stores) and clears the slab for the call after next. Replaces the all-reduce of a [batch, d_sae] tensor per step
+// in models/crosscoder.py:350-375 of the reference project.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+headsum_gather_kernel(const PeerTable pt, long long slab_off, long long out_off, int B, int cols, int phase_in,
+                      int phase_out, uint32_t epoch, unsigned* done_counter, int* status) {
+  const bool ok = wait_all_sources(pt, phase_in, epoch, status);
+  if (ok) {
+    float* slab = reinterpret_cast<float*>(pt.base[pt.rank] + slab_off);
+    const int N = cols * pt.world;
+    const int vec_per_row = cols / 8;
+    for (long long i = blockIdx.x * 256LL + threadIdx.x; i < (long long)B * vec_per_row; i += (long long)gridDim.x * 256) {
+      const long long row = i / vec_per_row;
+      const int c = (int)(i - row * vec_per_row) * 8;
+      float4* sp = reinterpret_cast<float4*>(slab + row * cols + c);
+      const float4 a = sp[0], b = sp[1];
+      sp[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+      sp[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+      const long long o = row * N + (long long)pt.rank * cols + c;
+      for (int p = 0; p < pt.world; ++p) {
+        TO* dst = reinterpret_cast<TO*>(pt.base[p] + out_off) + o;
+        if constexpr (sizeof(TO) == 4) {
+          reinterpret_cast<float4*>(dst)[0] = a;
+          reinterpret_cast<float4*>(dst)[1] = b;
+        } else {
+          uint4 u;
+          u.x = pack_bf16x2(a.x, a.y); u.y = pack_bf16x2(a.z, a.w); u.z = pack_bf16x2(b.x, b.y); u.w = pack_bf16x2(b.z, b.w);
+          *reinterpret_cast<uint4*>(dst) = u;
+        }
+      }
+    }
+  }
+  // signal even after a failed wait so that peers do not pile further timeouts on top of the first one
+  signal_peers_when_grid_done(pt, phase_out, epoch, done_counter);
+}
+
+int headsum_gather_launch(const PeerTable& pt, long long slab_off, long long out_off, int B, int cols, int out_dtype,
+                          int phase_in, int phase_out, uint32_t epoch, unsigned* done_counter, int* status,
+                          cudaStream_t stream) {
+  if (cols % 8 != 0 || slab_off % 16 != 0 || out_off % 16 != 0) return (int)cudaErrorInvalidValue;
+  if (phase_in < 0 || phase_in >= kNumPhases || phase_out < 0 || phase_out >= kNumPhases) return (int)cudaErrorInvalidValue;
+  const long long work = (long long)B * (cols / 8);
+  int blocks = (int)((work + 255) / 256);
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  if (blocks < 1) blocks = 1;
+  if (out_dtype == 0)
+    headsum_gather_kernel<float><<<blocks, 256, 0, stream>>>(pt, slab_off, out_off, B, cols, phase_in, phase_out, epoch,
+                                                            done_counter, status);
+  else
+    headsum_gather_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(pt, slab_off, out_off, B, cols, phase_in, phase_out,
+                                                                    epoch, done_counter, status);
+  return (int)cudaGetLastError();
+}
+
+// One warp publishes `epoch` for `phase` in every peer's flag slot (an acknowledgement: "I have consumed epoch").
+__global__ void signal_flags_kernel(const PeerTable pt, int phase, uint32_t epoch) {
+  __threadfence_system();
+  if ((int)threadIdx.x < pt.world) {
+    uint32_t* flag = reinterpret_cast<uint32_t*>(pt.base[threadIdx.x] + pt.flags_off) + phase * kMaxPeers + pt.rank;
+    st_release_sys(flag, epoch);
+  }
+}
+
+int signal_flags_launch(const PeerTable& pt, int phase, uint32_t epoch, cudaStream_t stream) {
+  if (phase < 0 || phase >= kNumPhases) return (int)cudaErrorInvalidValue;
+  signal_flags_kernel<<<1, 32, 0, stream>>>(pt, phase, epoch);
+  return (int)cudaGetLastError();
+}
+
+// Bounded wait for ONE source rank's flag.
+__global__ void wait_flag_src_kernel(const PeerTable pt, int phase, uint32_t epoch, int src, int* status) {
+  if (threadIdx.x == 0) {
+    const uint32_t* flag = reinterpret_cast<const uint32_t*>(pt.base[pt.rank] + pt.flags_off) + phase * kMaxPeers + src;
+    if (!wait_flag_sys(flag, epoch)) report_status(status, kTimeoutPeerFlag, phase, src);
+  }
+}
+
+int wait_flag_src_launch(const PeerTable& pt, int phase, uint32_t epoch, int src, int* status, cudaStream_t stream) {
+  if (phase < 0 || phase >= kNumPhases || src < 0 || src >= pt.world) return (int)cudaErrorInvalidValue;
+  wait_flag_src_kernel<<<1, 32, 0, stream>>>(pt, phase, epoch, src, status);
+  return (int)cudaGetLastError();
+}
+
 int push_candidates_launch(const PeerTable& pt, const float* val, const int* idx, int B, int k, uint32_t epoch,
                            unsigned* done_counter, cudaStream_t stream) {
   int blocks = (int)(((long long)B * k + 255) / 256);

@@ -164,11 +164,16 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     if (elect_one()) {
       uint32_t it = 0;
       bool ok = true;
+      const int k_stages_per_head = p.heads > 1 ? num_k_stages / p.heads : num_k_stages;
       for (int tile = tile_begin; tile < tile_end && ok; ++tile) {
         const int n0 = tile * BN;
         for (int ks = 0; ks < num_k_stages; ++ks, ++it) {
           const int s = it % STAGES;
           const uint32_t parity = ((it / STAGES) & 1) ^ 1;
+          // head-summed encoders: K block ks belongs to head h and reads that head's rows of the weight map
+          const int head = ks / k_stages_per_head;
+          const int bk = (ks - head * k_stages_per_head) * BK;
+          const int brow = n0 + head * p.b_rows_per_head;
           if (!mbar_wait_bounded(&empty_bar[s], parity, abort_flag)) {
             report_status(p.status, kTimeoutEmptyBarrier, (int)it);
             *abort_flag = 1;
@@ -183,11 +188,11 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             if (leader) mbar_arrive_expect_tx(&full_bar[s], 2 * STAGE_BYTES);
             const uint32_t bar = mapa_u32(smem_u32(&full_bar[s]), 0);
             tma_load_2d_pair(a_dst, &tmap_a, bar, ks * BK, m0);
-            tma_load_2d_pair(b_dst, &tmap_b, bar, ks * BK, n0 + (int)cta_rank * L::kBRows);
+            tma_load_2d_pair(b_dst, &tmap_b, bar, bk, brow + (int)cta_rank * L::kBRows);
           } else {
             mbar_arrive_expect_tx(&full_bar[s], STAGE_BYTES);
             tma_load_2d(a_dst, &tmap_a, &full_bar[s], ks * BK, m0);
-            tma_load_2d(b_dst, &tmap_b, &full_bar[s], ks * BK, n0);
+            tma_load_2d(b_dst, &tmap_b, &full_bar[s], bk, brow);
           }
         }
       }
@@ -305,6 +310,18 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j) if (c0 + j < p.N) v[j] += __ldg(p.bias + c0 + j);
+          }
+        }
+        if constexpr (WRITE_H && !TOPK) {
+          if (p.red_world > 0) {
+            // reduce-scatter epilogue: add this 32-column piece into the slab of the rank that owns the columns
+            if (row_ok && full_chunk) {
+              const int owner = c0 / p.red_cols;
+              float* dst = p.red_base[owner] + (long long)row * p.red_cols + (c0 - owner * p.red_cols);
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) red_add_v4_f32_sys(dst + j, v[j], v[j + 1], v[j + 2], v[j + 3]);
+            }
+            continue;
           }
         }
         if constexpr (WRITE_H) {
@@ -453,6 +470,9 @@ int enc_gemm_launch(const CUtensorMap& ta, const CUtensorMap& tb, const EncGemmP
                     cudaStream_t stream) {
   const bool wh = mode & 1, tk = mode & 2, pair = mode & 8, compact = mode & 16;
   if (pair && (p.num_panels % 2 != 0)) return (int)cudaErrorInvalidValue;
+  if (p.heads > 1 && (p.K % (p.heads * BK) != 0 || p.b_rows_per_head < p.N)) return (int)cudaErrorInvalidValue;
+  if (p.red_world > 0 && (tk || !wh || p.red_world > 8 || p.red_cols % 32 != 0 || p.red_cols * p.red_world != p.N))
+    return (int)cudaErrorInvalidValue;
   cudaError_t e;
   if (!tk) {
     if (pair) e = launch_variant<true, false, 6, 0, true>(ta, tb, p, stream);

@@ -25,6 +25,17 @@ struct EncGemmParams {
   // chunk's launch left in cand_val / cand_idx instead of starting empty.
   int n_index_offset;
   int resume_topk;
+  // Head-summed encoders (crosscoders): the K dimension is `heads` blocks of K / heads columns; block h of A pairs with
+  // rows [h * b_rows_per_head, h * b_rows_per_head + N) of the B tensor map, so one accumulation sums
+  // x_h . W_h^T over the heads. heads <= 1: a plain GEMM.
+  int heads;
+  int b_rows_per_head;
+  // Reduce-scatter epilogue (WRITE_H variants, red_world > 0): instead of storing H, the fp32 tile is added into
+  // the slab of the rank that owns its columns: red_base[c / red_cols] is an fp32 [M, red_cols] array in that rank's
+  // memory (a peer mapping), updated with vector reductions. red_cols % 32 == 0.
+  int red_world;
+  int red_cols;
+  float* red_base[8];
 };
 int enc_gemm_launch(const CUtensorMap& ta, const CUtensorMap& tb, const EncGemmParams& p, int mode, cudaStream_t stream);
 int enc_gemm_slots_for_k(int k);
@@ -144,6 +155,14 @@ int push_candidates_launch(const PeerTable& pt, const float* val, const int* idx
 int shuffle_rows_launch(const PeerTable& pt, const void* src, const long long* dest, int n_local, int rows_per_rank,
                         int row_bytes, long long recv_off, int phase, uint32_t epoch, unsigned* done_counter,
                         cudaStream_t stream);
+int bcast_rows_cast_launch(const PeerTable& pt, int in_dtype, int out_dtype, const void* src, const int* keep, const int* pos,
+                           long long n, int d, long long recv_off, long long cap_rows, int phase, uint32_t epoch,
+                           unsigned* done_counter, cudaStream_t stream);
+int headsum_gather_launch(const PeerTable& pt, long long slab_off, long long out_off, int B, int cols, int out_dtype,
+                          int phase_in, int phase_out, uint32_t epoch, unsigned* done_counter, int* status,
+                          cudaStream_t stream);
+int signal_flags_launch(const PeerTable& pt, int phase, uint32_t epoch, cudaStream_t stream);
+int wait_flag_src_launch(const PeerTable& pt, int phase, uint32_t epoch, int src, int* status, cudaStream_t stream);
 int wait_flags_launch(const PeerTable& pt, int phase, uint32_t epoch, int* status, cudaStream_t stream);
 int sparse_decode_scatter_launch(const PeerTable& pt, const int* idx, const float* val, int B, int k, int d,
                                  const __nv_bfloat16* W, uint32_t epoch, unsigned* done_counter, cudaStream_t stream);

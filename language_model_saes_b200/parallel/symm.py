@@ -167,3 +167,148 @@ class ShuffleComm:
         ext.comm_wait(self.table, PHASE_SHUFFLE, self.epoch, K.status_buffer(self.device))
         out = self.buf[off : off + n * row_bytes].view(x.dtype).view(n, *x.shape[1:])
         return out.clone()
+
+
+PHASE_BCAST_DATA, PHASE_BCAST_ACK = 0, 1
+
+
+class BroadcastComm:
+    """One rank's rows to every rank of the group by direct peer stores, fused with token-mask compaction and a dtype
+    cast (``comm_bcast_rows``): the rank that read a chunk of cached activations pushes the cleaned rows into every
+    peer's landing zone over NVLink; the others never touch the disk or the host copy engine for that chunk.
+
+    Two landing zones alternate. Before the sender overwrites the zone of call ``t - 2`` it waits (bounded) for every
+    rank's acknowledgement of that call, which each rank publishes after it has copied the rows out. The row count
+    travels in a one-element all-reduce that also orders the ranks: receivers run behind the sender's launch and the
+    sender behind the receivers' previous copies, so the bounded flag waits only cover stores and flags in flight.
+    """
+
+    def __init__(self, group: dist.ProcessGroup, device: torch.device, max_rows: int, max_row_bytes: int):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group, self.device = group, device
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        assert self.world <= _MAX_PEERS
+        self.max_rows, self.max_row_bytes = max_rows, _align(max_row_bytes, 16)
+        self.flags_off = 0
+        zone = _align(max_rows * self.max_row_bytes)
+        self.recv_off = [_align(_NUM_PHASES * _MAX_PEERS * 4)]
+        self.recv_off.append(self.recv_off[0] + zone)
+        self.nbytes = self.recv_off[1] + zone
+        try:
+            symm_mem.enable_symm_mem_for_group(group.group_name)
+        except Exception:  # noqa: BLE001
+            pass
+        self.buf = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        self.handle = symm_mem.rendezvous(self.buf, group.group_name)
+        self.table = [self.world, self.rank, self.flags_off, 0, 0, 0, 0, *[int(p) for p in self.handle.buffer_ptrs]]
+        self.done_counter = torch.zeros(1, dtype=torch.int32, device=device)
+        self.count = torch.zeros(1, dtype=torch.int64, device=device)
+        self.epoch = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)
+
+    def broadcast_rows(self, src_rank: int, d: int, out_dtype: torch.dtype, rows: torch.Tensor | None = None,
+                       keep: torch.Tensor | None = None) -> torch.Tensor:  # fmt: skip
+        """Every rank calls this with the same ``src_rank`` (rank within the group), ``d`` and ``out_dtype``; the sender
+        also passes ``rows [n, d]`` (fp32 or bf16) and optionally ``keep [n]``. Returns the kept rows, cast, on every
+        rank."""
+        ext = K._ext()
+        st = K.status_buffer(self.device)
+        self.epoch += 1
+        off = self.recv_off[self.epoch & 1]
+        row_bytes = d * out_dtype.itemsize
+        assert row_bytes <= self.max_row_bytes and d % 8 == 0 and out_dtype in (torch.float32, torch.bfloat16)
+        cap_rows = (self.max_rows * self.max_row_bytes) // row_bytes
+        if self.rank == src_rank:
+            assert rows is not None and rows.is_cuda and rows.ndim == 2 and rows.shape[1] == d
+            rows = rows.contiguous()
+            n = rows.shape[0]
+            keep32 = pos = None
+            if keep is not None:
+                keep32 = keep.reshape(-1).to(torch.int32).contiguous()
+                pos = torch.empty(n + 1, dtype=torch.int32, device=self.device)
+                ext.exclusive_scan(keep32, pos, torch.empty((n + 4095) // 4096, dtype=torch.int32, device=self.device))
+                self.count.copy_(pos[n : n + 1])
+            else:
+                self.count.fill_(n)
+            if self.epoch > 2:  # the zone still holds call epoch - 2: everyone must have copied it out
+                ext.comm_wait(self.table, PHASE_BCAST_ACK, self.epoch - 2, st)
+            ext.comm_bcast_rows(self.table, rows, keep32, pos, 0 if out_dtype == torch.float32 else 1, off, cap_rows,
+                                PHASE_BCAST_DATA, self.epoch, self.done_counter)  # fmt: skip
+        else:
+            self.count.zero_()
+        # the row count, summed (the others add zero): unlike a broadcast, an all-reduce completes on the sender only after
+        # every rank has reached this call, i.e. after their copies and acknowledgements of the previous call
+        dist.all_reduce(self.count, group=self.group)
+        ext.comm_wait_src(self.table, PHASE_BCAST_DATA, self.epoch, src_rank, st)
+        m = int(self.count)
+        assert m <= cap_rows, f"{m} rows do not fit the landing zone of {cap_rows}"
+        out = self.buf[off : off + m * row_bytes].view(out_dtype).view(m, d).clone()
+        ext.comm_signal(self.table, PHASE_BCAST_ACK, self.epoch)
+        return out
+
+
+PHASE_HS_REDUCED, PHASE_HS_GATHERED = 0, 1
+
+
+class HeadSumComm:
+    """Sum of per-rank encoder pre-activations over a ``head`` group, fused into the GEMM that produces them.
+
+    ``head_sum(x, w, bias, ...)`` computes ``sum_ranks (sum_local_heads x_h W_h^T + b_h)`` as ``[M, N]`` on every rank:
+    the tcgen05 GEMM accumulates the local heads in one K loop (K = heads x d) and its epilogue adds each finished tile
+    into the fp32 slab of the rank that owns those columns with vector reductions through the peer mapping
+    (reduce-scatter while other tiles are still being multiplied); the owners then store the sums into every rank's output
+    (all-gather by peer stores). Two slabs alternate between calls and are cleared by their owner after use.
+    """
+
+    def __init__(self, group: dist.ProcessGroup | None, device: torch.device, max_rows: int, n_cols: int):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group, self.device = group, device
+        self.world = dist.get_world_size(group) if group is not None else 1
+        self.rank = dist.get_rank(group) if group is not None else 0
+        assert self.world <= _MAX_PEERS and n_cols % (self.world * 32) == 0, "d_sae must divide into 32-column slabs per rank"
+        self.max_rows, self.n_cols, self.cols = max_rows, n_cols, n_cols // self.world
+        off = _align(_NUM_PHASES * _MAX_PEERS * 4)
+        self.slab_off = [off, _align(off + max_rows * self.cols * 4)]
+        self.out_off = _align(self.slab_off[1] + max_rows * self.cols * 4)
+        self.nbytes = _align(self.out_off + max_rows * n_cols * 4)
+        if group is not None and self.world > 1:
+            try:
+                symm_mem.enable_symm_mem_for_group(group.group_name)
+            except Exception:  # noqa: BLE001
+                pass
+            self.buf = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=device)
+            self.buf.zero_()
+            self.handle = symm_mem.rendezvous(self.buf, group.group_name)
+            ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        else:
+            self.buf = torch.zeros(self.nbytes, dtype=torch.uint8, device=device)
+            ptrs = [self.buf.data_ptr()]
+        self.ptrs = ptrs
+        self.table = [self.world, self.rank, 0, 0, 0, 0, 0, *ptrs]
+        self.done_counter = torch.zeros(1, dtype=torch.int32, device=device)
+        self.epoch = 0
+        torch.cuda.synchronize(device)
+        if group is not None and self.world > 1:
+            dist.barrier(group=group)
+
+    def head_sum(self, x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, heads: int, rows_per_head: int,
+                 out_dtype: torch.dtype = torch.float32, pair: bool = True) -> torch.Tensor:  # fmt: skip
+        """``x [M, heads * d]`` bf16, ``w [heads * rows_per_head, d]`` bf16 (feature-major blocks, one per local head),
+        ``bias [N]`` fp32 = this rank's summed encoder biases. Returns ``[M, N]`` in ``out_dtype`` (fp32 or bf16)."""
+        M = x.shape[0]
+        assert M <= self.max_rows and out_dtype in (torch.float32, torch.bfloat16)
+        ext = K._ext()
+        st = K.status_buffer(self.device)
+        self.epoch += 1
+        slab_off = self.slab_off[self.epoch & 1]
+        ext.head_sum_gemm(x, w, bias, heads, rows_per_head, self.n_cols, [p + slab_off for p in self.ptrs], pair, st)
+        ext.comm_signal(self.table, PHASE_HS_REDUCED, self.epoch)
+        ext.comm_headsum_gather(self.table, slab_off, self.out_off, M, self.cols, 0 if out_dtype == torch.float32 else 1,
+                                PHASE_HS_REDUCED, PHASE_HS_GATHERED, self.epoch, self.done_counter, st)  # fmt: skip
+        ext.comm_wait(self.table, PHASE_HS_GATHERED, self.epoch, st)
+        n = M * self.n_cols * out_dtype.itemsize
+        return self.buf[self.out_off : self.out_off + n].view(out_dtype).view(M, self.n_cols).clone()

@@ -232,3 +232,55 @@ def test_sparse_decode_autograd_matches_dense():
     assert torch.allclose(W.grad, ref_dW, atol=2e-3, rtol=2e-3)
     ref_da = (dyb @ Wb.t()) * (acts.detach() != 0)
     assert torch.allclose(acts.grad, ref_da, atol=5e-3, rtol=5e-3)
+
+
+@pytest.mark.parametrize("M,heads,d,N,pair", [(256, 3, 128, 1024, True), (128, 2, 64, 256, False), (384, 1, 256, 4096, True), (200, 4, 64, 512, True)])
+def test_head_sum_gemm_single_rank(M, heads, d, N, pair):
+    """K-concatenated head sum + reduction epilogue + gather on one rank (the slab owner is this GPU)."""
+    from language_model_saes_b200.parallel.symm import HeadSumComm
+
+    dev = torch.device("cuda")
+    torch.manual_seed(0)
+    rows_per_head = N + 64  # the weight blocks may be longer than the columns in use
+    x = torch.randn(M, heads * d, device=dev).to(torch.bfloat16)
+    w = (torch.randn(heads * rows_per_head, d, device=dev) / d**0.5).to(torch.bfloat16)
+    bias = torch.randn(N, device=dev)
+    comm = HeadSumComm(None, dev, max_rows=M, n_cols=N)
+    want = bias + sum(x[:, h * d : (h + 1) * d].float() @ w[h * rows_per_head : h * rows_per_head + N].float().T for h in range(heads))
+    for call in range(3):  # both slabs and the cleared slab of the first call
+        got = comm.head_sum(x, w, bias, heads, rows_per_head, torch.float32, pair=pair)
+        K.check_status(dev)
+        assert torch.allclose(got, want, atol=2e-3, rtol=2e-3), (call, float((got - want).abs().max()))
+    got16 = comm.head_sum(x, w, bias, heads, rows_per_head, torch.bfloat16, pair=pair)
+    assert torch.allclose(got16.float(), want, atol=5e-2, rtol=2e-2)
+
+
+def test_crosscoder_fused_head_sum_matches_generic():
+    from language_model_saes_b200.models.crosscoder import Crosscoder, CrosscoderConfig
+
+    def make(fused):
+        torch.manual_seed(0)
+        cfg = CrosscoderConfig(hook_points=["a", "b", "c"], d_model=128, expansion_factor=8, act_fn="relu", device="cuda",
+                               dtype=torch.bfloat16, norm_activation="inference", fused_head_sum=fused)  # fmt: skip
+        m = Crosscoder(cfg)
+        m.init_parameters(encoder_uniform_bound=0.1, decoder_uniform_bound=0.1, init_log_jumprelu_threshold_value=0.0)
+        with torch.no_grad():
+            m.b_E.normal_(std=0.05)
+            m.W_E.mul_(1 + 0.1 * torch.arange(3, device="cuda").view(3, 1, 1))  # the heads differ
+        return m
+
+    a, b = make(True), make(False)
+    x = torch.randn(256, 3, 128, device="cuda", dtype=torch.bfloat16)
+    xa, xb = x.clone().requires_grad_(), x.clone().requires_grad_()
+    fa, ha = a.encode(xa, return_hidden_pre=True)
+    fb, hb = b.encode(xb, return_hidden_pre=True)
+    K.check_status(torch.device("cuda"))
+    assert torch.allclose(ha.float(), hb.float(), atol=5e-2, rtol=5e-2)
+    g = torch.randn_like(fa)
+    (fa * g).sum().backward()
+    (fb * g).sum().backward()
+
+    def close(u, v):  # a few ReLU gates flip between the two roundings of the pre-activations: compare in norm
+        return float((u.float() - v.float()).norm() / v.float().norm()) < 0.05
+
+    assert close(xa.grad, xb.grad) and close(a.W_E.grad, b.W_E.grad) and close(a.b_E.grad, b.b_E.grad)

@@ -137,3 +137,117 @@ def test_shuffle_all_to_all_is_the_seeded_global_permutation():
     dist.all_gather(mixed, out["tokens"][:40].contiguous())
     assert sorted(torch.cat(mixed).tolist()) == sorted(list(range(40)) + list(range(1000, 1040)))
     assert (out["tokens"][:40] >= 1000).any() and (out["tokens"][:40] < 1000).any()
+
+
+@needs2
+@distributed_test(nproc_per_node=2, backend="nccl")
+def test_peer_broadcast_of_masked_cast_rows_and_cached_loader():
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import tempfile
+    from pathlib import Path
+
+    from safetensors.torch import save_file
+
+    from language_model_saes_b200.activation.processors.cached_activation import CachedActivationLoader
+    from language_model_saes_b200.ops import sae_kernels as K
+    from language_model_saes_b200.parallel.mesh import build_mesh
+    from language_model_saes_b200.parallel.symm import BroadcastComm
+
+    rank = dist.get_rank()
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    mesh = build_mesh("cuda", (1, 2), ("data", "model"))
+    group = mesh.get_group("model")
+    n, d = 3000, 512
+    comm = BroadcastComm(group, dev, max_rows=n, max_row_bytes=d * 4)
+    g = torch.Generator(device="cpu").manual_seed(5)
+    for call in range(5):  # both landing zones, their re-use, and both ranks as the sender
+        src = call % 2
+        rows_cpu = torch.randn(n - 100 * call, d, generator=g)
+        keep_cpu = torch.rand(n - 100 * call, generator=g) > 0.25
+        use_mask, out_dtype = call % 3 != 2, (torch.bfloat16 if call % 2 == 0 else torch.float32)
+        rows = rows_cpu.to(dev) if rank == src else None
+        keep = keep_cpu.to(dev) if (rank == src and use_mask) else None
+        got = comm.broadcast_rows(src, d, out_dtype, rows, keep)
+        K.check_status(dev)
+        want = (rows_cpu[keep_cpu] if use_mask else rows_cpu).to(out_dtype).to(dev)
+        assert torch.equal(got, want), (call, got.shape, want.shape)
+
+    # the cached-activation loader: rank 0 of the model group reads, rank 1 receives the same records
+    root = Path(tempfile.gettempdir()) / "lmsae_peer_bcast_cache"
+    if rank == 0:
+        for hp in ("h0", "h1"):
+            (root / hp).mkdir(parents=True, exist_ok=True)
+            for c in range(3):
+                gg = torch.Generator().manual_seed(100 * c + (hp == "h1"))
+                save_file({"activation": torch.randn(4, 16, 64, generator=gg).to(torch.bfloat16),
+                           "tokens": torch.arange(64).view(4, 16) + 1000 * c, "mask": torch.ones(4, 16, dtype=torch.bool),
+                           "attention_mask": torch.ones(4, 16, dtype=torch.bool)}, str(root / hp / f"chunk-{c}.safetensors"))  # fmt: skip
+    dist.barrier()
+    dirs = {hp: root / hp for hp in ("h0", "h1")}
+    pushed = list(CachedActivationLoader(dirs, device=str(dev), device_mesh=mesh, peer_broadcast=True).process())
+    plain = list(CachedActivationLoader(dirs, device=str(dev)).process())
+    K.check_status(dev)
+    assert len(pushed) == len(plain) == 3
+    for a, b in zip(pushed, plain):
+        assert set(a) == set(b)
+        for key in b:
+            assert torch.equal(a[key], b[key]) if isinstance(b[key], torch.Tensor) else a[key] == b[key]
+
+
+@needs2
+@distributed_test(nproc_per_node=2, backend="nccl")
+def test_head_parallel_crosscoder_sums_pre_activations_in_the_gemm_epilogue():
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    from language_model_saes_b200.models.crosscoder import Crosscoder, CrosscoderConfig
+    from language_model_saes_b200.ops import sae_kernels as K
+    from language_model_saes_b200.parallel.mesh import build_mesh
+    from language_model_saes_b200.parallel.symm import HeadSumComm
+
+    rank = dist.get_rank()
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    mesh = build_mesh("cuda", (2, 1, 1), ("head", "data", "model"))
+    group = mesh.get_group("head")
+
+    # the collective alone: every rank contributes its own heads, all ranks get the total
+    M, heads, d, N = 256, 2, 128, 1024
+    torch.manual_seed(10 + rank)
+    x = torch.randn(M, heads * d, device=dev).to(torch.bfloat16)
+    w = (torch.randn(heads * N, d, device=dev) / d**0.5).to(torch.bfloat16)
+    bias = torch.randn(N, device=dev)
+    local = bias + sum(x[:, h * d : (h + 1) * d].float() @ w[h * N : (h + 1) * N].float().T for h in range(heads))
+    want = local.clone()
+    dist.all_reduce(want)
+    comm = HeadSumComm(group, dev, max_rows=M, n_cols=N)
+    for call in range(4):
+        got = comm.head_sum(x, w, bias, heads, N, torch.float32)
+        K.check_status(dev)
+        assert torch.allclose(got, want, atol=3e-3, rtol=3e-3), (call, float((got - want).abs().max()))
+
+    # the model: fused against the all-reduce path, values and gradients
+    def make(fused):
+        torch.manual_seed(0)
+        cfg = CrosscoderConfig(hook_points=["a", "b", "c", "e"], d_model=128, expansion_factor=8, act_fn="relu", device="cuda",
+                               dtype=torch.bfloat16, norm_activation="inference", fused_head_sum=fused)  # fmt: skip
+        m = Crosscoder(cfg, device_mesh=mesh)
+        m.init_parameters(encoder_uniform_bound=0.1, decoder_uniform_bound=0.1, init_log_jumprelu_threshold_value=0.0)
+        with torch.no_grad():
+            m.W_E.mul_(1 + 0.1 * (torch.arange(2, device=dev) + 2 * rank).view(2, 1, 1))
+        return m
+
+    a, b = make(True), make(False)
+    torch.manual_seed(100 + rank)
+    x = torch.randn(256, 2, 128, device=dev, dtype=torch.bfloat16)
+    fa, ha = a.encode(x, return_hidden_pre=True)
+    fb, hb = b.encode(x, return_hidden_pre=True)
+    K.check_status(dev)
+    assert torch.allclose(ha.float(), hb.float(), atol=5e-2, rtol=5e-2)
+    g = torch.randn_like(fa)
+    (fa * g).sum().backward()
+    (fb * g).sum().backward()
+
+    def close(u, v):
+        return float((u.float() - v.float()).norm() / v.float().norm()) < 0.05
+
+    assert close(a.W_E.grad, b.W_E.grad) and close(a.b_E.grad, b.b_E.grad)
