@@ -1,0 +1,51 @@
+"""Causal attention whose value width differs from the query/key width, on the sm_100a tensor cores.
+
+A low-rank sparse attention dictionary runs one attention per QK head with the head's whole OV group as the value
+(models/lorsa.py:642-661,864-904 of the reference project, which calls ``scaled_dot_product_attention``): ``q, k`` are
+``[batch, seq, heads, d_qk]`` and ``v`` is ``[batch, seq, heads, d_v]`` with ``d_v`` a multiple of ``d_qk`` or unrelated
+to it. ``csrc/attention.cu`` implements the forward pass with tcgen05 MMAs, accumulators in TMEM and TMA-fed operands;
+``ref_causal_attention`` is the plain-torch oracle.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import sae_kernels as K
+
+
+def ref_causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float) -> tuple[torch.Tensor, torch.Tensor]:
+    """fp32 ``(out [b, s, h, dv], lse [b, h, s])``."""
+    s = q.shape[1]
+    scores = torch.einsum("bqhd,bkhd->bhqk", q.float(), k.float()) * scale
+    mask = torch.ones(s, s, dtype=torch.bool, device=q.device).tril()
+    scores = scores.masked_fill(~mask, float("-inf"))
+    lse = torch.logsumexp(scores, dim=-1)
+    out = torch.einsum("bhqk,bkhg->bqhg", torch.softmax(scores, dim=-1), v.float())
+    return out, lse
+
+
+def supported(q: torch.Tensor, v: torch.Tensor) -> bool:
+    return (
+        q.is_cuda and q.ndim == 4 and v.ndim == 4 and q.shape[-1] in (64, 128) and v.shape[-1] % 64 == 0
+        and q.shape[1] % 8 == 0 and q.shape[0] <= 65535
+    )  # fmt: skip
+
+
+@torch.no_grad()
+def causal_attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float | None = None,
+                         want_lse: bool = False) -> tuple[torch.Tensor, torch.Tensor | None]:  # fmt: skip
+    """``q, k [b, s, h, d_qk]``, ``v [b, s, h, d_v]`` -> bf16 ``out [b, s, h, d_v]`` (and fp32 ``lse [b, h, s]``)."""
+    scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
+    if not supported(q, v):
+        out, lse = ref_causal_attention(q, k, v, scale)
+        return out.to(torch.bfloat16), (lse if want_lse else None)
+    b, s, h, _ = q.shape
+    q16, k16 = q.to(torch.bfloat16).contiguous(), k.to(torch.bfloat16).contiguous()
+    vt = v.to(torch.bfloat16).permute(0, 2, 3, 1).contiguous()  # [b, h, d_v, s]: keys contiguous for the P V product
+    out = torch.empty(b, s, h, v.shape[-1], dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty(b, h, s, dtype=torch.float32, device=q.device) if want_lse else None
+    K._ext().attn_fwd(q16, k16, vt, out, lse, float(scale), K.status_buffer(q.device))
+    return out, lse

@@ -405,6 +405,43 @@ Tensor jumprelu(const Tensor& x, const Tensor& log_theta, const c10::optional<Te
   return out;
 }
 
+// ---- attention ---------------------------------------------------------------------------------------------
+// q, k: bf16 [batch, seq, heads, d_qk]; vt: bf16 [batch, heads, d_v, seq] (values transposed, keys contiguous);
+// out: bf16 [batch, seq, heads, d_v]; lse: fp32 [batch, heads, seq] or absent. Causal.
+void attn_fwd(const Tensor& q, const Tensor& k, const Tensor& vt, const Tensor& out, const c10::optional<Tensor>& lse,
+              double scale, const Tensor& status) {
+  CHECK_T(q, torch::kBFloat16);
+  CHECK_T(k, torch::kBFloat16);
+  CHECK_T(vt, torch::kBFloat16);
+  CHECK_T(out, torch::kBFloat16);
+  CHECK_T(status, torch::kInt32);
+  TORCH_CHECK(q.dim() == 4 && k.sizes() == q.sizes() && vt.dim() == 4, "q, k [b, s, h, dqk]; vt [b, h, dv, s]");
+  lmsae::AttnParams p{};
+  p.batch = (int)q.size(0);
+  p.seq = (int)q.size(1);
+  p.heads = (int)q.size(2);
+  p.dqk = (int)q.size(3);
+  p.dv = (int)vt.size(2);
+  TORCH_CHECK(vt.size(0) == p.batch && vt.size(1) == p.heads && vt.size(3) == p.seq, "vt must be [b, h, dv, s]");
+  TORCH_CHECK(out.dim() == 4 && out.size(0) == p.batch && out.size(1) == p.seq && out.size(2) == p.heads && out.size(3) == p.dv,
+              "out must be [b, s, h, dv]");
+  const int dvc = lmsae::attn_value_chunk(p.dv);
+  TORCH_CHECK(dvc != 0 && (p.dqk == 64 || p.dqk == 128) && p.seq % 8 == 0, "attn_fwd: d_qk in {64, 128}, d_v % 64 == 0, seq % 8 == 0");
+  if (lse.has_value()) {
+    CHECK_T(*lse, torch::kFloat32);
+    TORCH_CHECK(lse->numel() == (int64_t)p.batch * p.heads * p.seq, "lse must be [b, h, s]");
+  }
+  p.scale_log2 = (float)(scale * 1.4426950408889634);
+  p.out = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
+  p.lse = opt_ptr<float>(lse);
+  p.status = status.data_ptr<int>();
+  const c10::cuda::CUDAGuard guard(q.device());
+  const CUtensorMap tq = make_bf16_tile_map(q.data_ptr(), (int64_t)p.batch * p.seq, (int64_t)p.heads * p.dqk, 128);
+  const CUtensorMap tk = make_bf16_tile_map(k.data_ptr(), (int64_t)p.batch * p.seq, (int64_t)p.heads * p.dqk, 128);
+  const CUtensorMap tvt = make_bf16_tile_map(vt.data_ptr(), (int64_t)p.batch * p.heads * p.dv, p.seq, dvc);
+  check_cuda(lmsae::attn_fwd_launch(tq, tk, tvt, p, at::cuda::getCurrentCUDAStream()), "attn_fwd launch");
+}
+
 // ---- selection / compaction ----------------------------------------------------------------------------
 int dtype_code(const Tensor& t) {
   if (t.scalar_type() == torch::kFloat32) return 0;
@@ -777,6 +814,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "sm_100a kernels for sparse-dictionary training";
   m.def("encoder_gemm", &encoder_gemm);
   m.def("jumprelu", &jumprelu);
+  m.def("attn_fwd", &attn_fwd);
   m.def("radix_hi_bins", &radix_hi_bins);
   m.def("radix_hist", &radix_hist);
   m.def("radix_pick", &radix_pick);

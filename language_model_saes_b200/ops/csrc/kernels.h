@@ -131,6 +131,18 @@ int gather_rows_cast_launch(int in_dtype, int out_dtype, const void* src, const 
                             int d, void* out, long long out_rows, cudaStream_t stream);
 int exclusive_scan_launch(const int* counts, int n, int* offsets, int* block_sums_buf, cudaStream_t stream);
 
+// ---- causal attention with d_v != d_qk (attention.cu) ------------------------------------------------
+struct AttnParams {
+  int batch, seq, heads, dqk, dv;
+  float scale_log2;       // softmax scale * log2(e)
+  __nv_bfloat16* out;     // [batch, seq, heads, dv]
+  float* lse;             // [batch, heads, seq] natural-log sum of exponentials (nullptr: not wanted)
+  int* status;
+};
+int attn_value_chunk(int dv);
+int attn_fwd_launch(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tvt, const AttnParams& p,
+                    cudaStream_t stream);
+
 // ---- elementwise (jumprelu.cu) ---------------------------------------------------------------------
 int jumprelu_launch(int dtype, const void* x, const void* log_theta, const void* dy, void* out, float* dlog, long long n,
                     int P, float window, int backward, cudaStream_t stream);

@@ -21,7 +21,7 @@ import torch
 _NAME = "_lmsae_native"
 _CSRC = Path(__file__).resolve().parent / "csrc"
 _BUILD_DIR = Path(__file__).resolve().parent / "_native_build"
-_SOURCES = ["binding.cpp", "encoder_gemm.cu", "topk_merge.cu", "sparse_ops.cu", "comm_ops.cu", "no_alloc.cu", "jumprelu.cu", "clt_ops.cu", "select_ops.cu"]
+_SOURCES = ["binding.cpp", "encoder_gemm.cu", "topk_merge.cu", "sparse_ops.cu", "comm_ops.cu", "no_alloc.cu", "jumprelu.cu", "clt_ops.cu", "select_ops.cu", "attention.cu"]
 _CUDA_FLAGS = [
     "-gencode",
     "arch=compute_100a,code=sm_100a",
