@@ -25,6 +25,7 @@ import torch.nn.functional as F
 from torch import nn
 
 from ..hooks import HookPoint
+from ..ops import attention as attention_kernels
 from ..parallel.collectives import all_reduce_sum
 from ..parallel.mesh import DeviceMesh, DimMap, mesh_local_rank
 from .sae import shard_generator
@@ -389,7 +390,12 @@ class LowRankSparseAttention(SparseDictionary):
     def _attend(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
         """Fused causal attention: one attention head per QK head whose value / output width is the OV group."""
         b, s, h, _ = q.shape
-        value = v.view(b, s, h, -1).permute(0, 2, 1, 3)
+        vg = v.view(b, s, h, -1)
+        if q.dtype == torch.bfloat16 and attention_kernels.supported(q, vg):
+            # tcgen05 kernels (forward, dQ, dK/dV) that take a value width different from the query/key width
+            z = attention_kernels.causal_attention(q, k, vg, 1 / self.attn_scale)
+            return z.reshape(b, s, -1)
+        value = vg.permute(0, 2, 1, 3)
         z = F.scaled_dot_product_attention(q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), value,
                                            scale=1 / self.attn_scale, is_causal=True)  # fmt: skip
         return z.permute(0, 2, 1, 3).reshape(b, s, -1)

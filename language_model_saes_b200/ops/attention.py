@@ -49,3 +49,45 @@ def causal_attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scal
     lse = torch.empty(b, h, s, dtype=torch.float32, device=q.device) if want_lse else None
     K._ext().attn_fwd(q16, k16, vt, out, lse, float(scale), K.status_buffer(q.device))
     return out, lse
+
+
+class CausalAttention(torch.autograd.Function):
+    """Differentiable ``causal_attention_fwd``: three tcgen05 kernels (forward, dQ, dK/dV). Inputs of any float dtype are
+    rounded to bf16 for the tensor cores; gradients are accumulated in fp32 and returned in the inputs' dtypes."""
+
+    @staticmethod
+    def forward(ctx, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float) -> torch.Tensor:
+        q16, k16, v16 = (t.detach().to(torch.bfloat16).contiguous() for t in (q, k, v))
+        b, s, h, _ = q16.shape
+        vt = v16.permute(0, 2, 3, 1).contiguous()
+        out = torch.empty(b, s, h, v16.shape[-1], dtype=torch.bfloat16, device=q.device)
+        lse = torch.empty(b, h, s, dtype=torch.float32, device=q.device)
+        K._ext().attn_fwd(q16, k16, vt, out, lse, float(scale), K.status_buffer(q.device))
+        ctx.save_for_backward(q16, k16, v16, out, lse)
+        ctx.scale, ctx.dtypes = float(scale), (q.dtype, k.dtype, v.dtype)
+        return out.to(v.dtype)
+
+    @staticmethod
+    def backward(ctx, dout: torch.Tensor):
+        q16, k16, v16, out, lse = ctx.saved_tensors
+        do16 = dout.to(torch.bfloat16).contiguous()
+        delta = (do16.float() * out.float()).sum(dim=-1).permute(0, 2, 1).contiguous()  # [b, h, s]
+        qt = q16.permute(0, 2, 3, 1).contiguous()
+        kt = k16.permute(0, 2, 3, 1).contiguous()
+        dot = do16.permute(0, 2, 3, 1).contiguous()
+        dq = torch.empty(q16.shape, dtype=torch.float32, device=q16.device)
+        dk = torch.empty_like(dq)
+        dv = torch.empty(v16.shape, dtype=torch.float32, device=q16.device)
+        ext = K._ext()
+        ext.launches += 1  # two kernels in one entry point
+        ext.attn_bwd(q16, k16, v16, do16, qt, kt, dot, lse, delta, dq, dk, dv, ctx.scale, K.status_buffer(q16.device))
+        return dq.to(ctx.dtypes[0]), dk.to(ctx.dtypes[1]), dv.to(ctx.dtypes[2]), None
+
+
+def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float | None = None) -> torch.Tensor:
+    """Differentiable causal attention ``[b, s, h, d_qk] x [b, s, h, d_v] -> [b, s, h, d_v]``; the tensor-core kernels
+    when the shape is supported on a GPU, the torch oracle otherwise."""
+    scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
+    if not supported(q, v):
+        return ref_causal_attention(q, k, v, scale)[0].to(v.dtype)
+    return CausalAttention.apply(q, k, v, scale)

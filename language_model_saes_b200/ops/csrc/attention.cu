@@ -4,15 +4,15 @@
 // attention per QK head whose value / output width is the head's OV group: q, k are [batch, seq, heads, d_qk] and
 // v is [batch, seq, heads, d_v] with d_v != d_qk in general, which the flash kernels of the usual libraries do not take.
 //
-// Forward (attn_fwd_kernel): one CTA per (128-query block, head, value chunk of DV columns, batch element), 128 threads,
-// thread r owns query row r (= TMEM lane r).
+// Forward (attn_fwd_kernel): one CTA per (128-query block, head, value chunk of DV columns, batch element); four warps
+// whose thread r owns query row r (= TMEM lane r) and a fifth warp that issues the TMA loads and the MMAs.
 //   per 128-key block (causal: only blocks up to the diagonal):
 //     TMA      K block [128 x DQK] and V^T block [DV x 128] (both K-major, 128-byte swizzle) -> shared memory
 //     tcgen05  S = Q K^T            (128 x 128 x DQK, accumulator in TMEM columns [0, 128))
 //     threads  read their S row from TMEM, online softmax in the exp2 domain, write P as bf16 into shared memory in the
 //              swizzled K-major layout the tensor core reads
-//     tcgen05  O_blk = P V          (128 x DV x 128, TMEM columns [128, 128 + DV))
-//     threads  O = O * alpha + O_blk in registers
+//     tcgen05  O += P V             (128 x DV x 128, TMEM columns [128, 128 + DV))
+//              (accumulating in TMEM; the rows rescale it in place only when their maximum has grown a lot)
 //   epilogue: O / l as bf16, log-sum-exp per row for the backward pass.
 // V is consumed as V^T [batch, heads, d_v, seq] so that both operands of P V are K-major (keys contiguous).
 // Every mbarrier wait is bounded; on expiry the CTA records a status code, stops issuing work and frees its TMEM.
@@ -39,7 +39,7 @@ struct AttnSmem {
   static constexpr int kPOff = kVOff + kVBytes;
   static constexpr int kPBytes = 2 * ATOM_BYTES_128;
   static constexpr int kBarOff = kPOff + kPBytes;
-  static constexpr int kTmemPtrOff = kBarOff + 4 * 8;
+  static constexpr int kTmemPtrOff = kBarOff + 8 * 8;
   static constexpr int kAbortOff = kTmemPtrOff + 4;
   static constexpr int kTotal = kAbortOff + 4;
   static constexpr int kDynamicBytes = kTotal + 1024;
@@ -52,21 +52,36 @@ __device__ __forceinline__ uint32_t sw128_chunk_off(int row, int chunk) {
 
 }  // namespace
 
+constexpr int FWD_THREADS = 160;       // warps 0-3: one query row per thread; warp 4: TMA + MMA issue
+constexpr float kRescaleSlack = 8.0f;  // log2 units the running reference may lag behind the true row maximum
+
+// Roles and hand-offs (all through mbarriers; the loop has no CTA-wide barrier):
+//   issuer   K(kb+1) load as soon as S(kb) has been computed; S(kb+1) as soon as the rows hold S(kb) in registers, so the
+//            tensor core works on the next scores while the rows do their exponentials; P V (kb) when P(kb) is written;
+//            V(kb+1) load when P V (kb) has completed.
+//   rows     S(kb) TMEM -> 128 registers (one wait), release S; block maximum; the output accumulator stays in TMEM and is
+//            only rescaled when the maximum has grown by more than 2^8 since the reference was set (rarely after the
+//            first blocks), which keeps p <= 256 and the sums well inside fp32 / bf16 range; exponentials -> P (bf16,
+//            swizzled K-major) -> signal.
 template <int DQK, int DV>
-__global__ void __launch_bounds__(ATT_THREADS)
+__global__ void __launch_bounds__(FWD_THREADS, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_vt, const AttnParams p) {
   using L = AttnSmem<DQK, DV>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bar_q = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
-  uint64_t* bar_kv = bar_q + 1;
-  uint64_t* bar_s = bar_q + 2;
-  uint64_t* bar_o = bar_q + 3;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+  uint64_t* bar_q = bars + 0;
+  uint64_t* bar_k = bars + 1;
+  uint64_t* bar_v = bars + 2;
+  uint64_t* bar_s_full = bars + 3;
+  uint64_t* bar_s_free = bars + 4;
+  uint64_t* bar_p_full = bars + 5;
+  uint64_t* bar_pv_done = bars + 6;
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + L::kTmemPtrOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOff);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
   const int n_qblocks = (p.seq + ATT_BM - 1) / ATT_BM;
   const int qblk = n_qblocks - 1 - (int)blockIdx.x;  // longest rows first
   const int dv_chunks = p.dv / DV;
@@ -74,22 +89,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const int dv0 = ((int)blockIdx.y - head * dv_chunks) * DV;
   const int batch = (int)blockIdx.z;
   const int q0 = qblk * ATT_BM;
-  const int row = (int)threadIdx.x;
-  const int qpos = q0 + row;
-  const bool row_ok = qpos < p.seq;
+  const int n_kblocks = qblk + 1;  // causal: key blocks 0 .. diagonal
 
   if (threadIdx.x == 0) {
     mbar_init(bar_q, 1);
-    mbar_init(bar_kv, 1);
-    mbar_init(bar_s, 1);
-    mbar_init(bar_o, 1);
+    mbar_init(bar_k, 1);
+    mbar_init(bar_v, 1);
+    mbar_init(bar_s_full, 1);
+    mbar_init(bar_s_free, ATT_BM);
+    mbar_init(bar_p_full, ATT_BM);
+    mbar_init(bar_pv_done, 1);
     *abort_flag = 0;
     fence_barrier_init();
-    prefetch_tensormap(&tmap_q);
-    prefetch_tensormap(&tmap_k);
-    prefetch_tensormap(&tmap_vt);
   }
-  if (warp == 0) {
+  if (warp == 4) {
     tmem_alloc(tmem_ptr_smem, 256);
     tmem_relinquish();
   }
@@ -99,43 +112,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const uint32_t tmem_base = *tmem_ptr_smem;
   const uint32_t tmem_s = tmem_base;
   const uint32_t tmem_o = tmem_base + ATT_BN;
-  const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
 
-  if (threadIdx.x == 0) {
-    mbar_arrive_expect_tx(bar_q, L::kQBytes);
-#pragma unroll
-    for (int a = 0; a < DQK / 64; ++a)
-      tma_load_2d(smem + L::kQOff + a * ATOM_BYTES_128, &tmap_q, bar_q, head * DQK + a * 64, batch * p.seq + q0);
-  }
-
-  float o_acc[DV];
-#pragma unroll
-  for (int i = 0; i < DV; ++i) o_acc[i] = 0.0f;
-  float m_run = -INFINITY, l_run = 0.0f;
-  const float sc = p.scale_log2;
-
-  const int n_kblocks = qblk + 1;  // causal: key blocks 0 .. diagonal
-  bool ok = true;
-  for (int kb = 0; kb < n_kblocks && ok; ++kb) {
-    const int k0 = kb * ATT_BN;
-    const uint32_t parity = kb & 1;
-    if (threadIdx.x == 0) {
-      mbar_arrive_expect_tx(bar_kv, L::kQBytes + L::kVBytes);
-#pragma unroll
-      for (int a = 0; a < DQK / 64; ++a)
-        tma_load_2d(smem + L::kKOff + a * ATOM_BYTES_128, &tmap_k, bar_kv, head * DQK + a * 64, batch * p.seq + k0);
-#pragma unroll
-      for (int a = 0; a < 2; ++a)
-        tma_load_2d(smem + L::kVOff + a * L::kVAtomBytes, &tmap_vt, bar_kv, k0 + a * 64,
-                    (batch * p.heads + head) * p.dv + dv0);
-      bool got = true;
-      if (kb == 0) got = mbar_wait_bounded(bar_q, 0, abort_flag);
-      got = got && mbar_wait_bounded(bar_kv, parity, abort_flag);
-      if (!got) {
-        report_status(p.status, kTimeoutFullBarrier, kb);
-        *abort_flag = 1;
-      } else {
-        tc_fence_after();
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA + MMA issuer
+    if (elect_one()) {
+      auto load_k = [&](int kb) {
+        mbar_arrive_expect_tx(bar_k, L::kQBytes);
+        for (int a = 0; a < DQK / 64; ++a)
+          tma_load_2d(smem + L::kKOff + a * ATOM_BYTES_128, &tmap_k, bar_k, head * DQK + a * 64, batch * p.seq + kb * ATT_BN);
+      };
+      auto load_v = [&](int kb) {
+        mbar_arrive_expect_tx(bar_v, L::kVBytes);
+        for (int a = 0; a < 2; ++a)
+          tma_load_2d(smem + L::kVOff + a * L::kVAtomBytes, &tmap_vt, bar_v, kb * ATT_BN + a * 64,
+                      (batch * p.heads + head) * p.dv + dv0);
+      };
+      auto issue_s = [&]() {
         constexpr uint32_t idesc_s = make_idesc_bf16(ATT_BM, ATT_BN);
 #pragma unroll
         for (int kk = 0; kk < DQK / 16; ++kk) {
@@ -144,59 +136,131 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           umma_bf16_ss(tmem_s, make_sw128_kmajor_desc(qa) + (uint64_t)((kk % 4) * 2),
                        make_sw128_kmajor_desc(ka) + (uint64_t)((kk % 4) * 2), idesc_s, kk > 0 ? 1u : 0u);
         }
+        umma_commit(bar_s_full);
+      };
+      mbar_arrive_expect_tx(bar_q, L::kQBytes);
+      for (int a = 0; a < DQK / 64; ++a)
+        tma_load_2d(smem + L::kQOff + a * ATOM_BYTES_128, &tmap_q, bar_q, head * DQK + a * 64, batch * p.seq + q0);
+      load_k(0);
+      load_v(0);
+      bool ok = mbar_wait_bounded(bar_q, 0, abort_flag) && mbar_wait_bounded(bar_k, 0, abort_flag);
+      int where = 0;
+      if (ok) {
+        tc_fence_after();
+        issue_s();
       }
-      umma_commit(bar_s);  // also after an abort, so that the waiters below leave promptly
+      for (int kb = 0; kb < n_kblocks && ok; ++kb) {
+        const uint32_t par = kb & 1;
+        const bool more = kb + 1 < n_kblocks;
+        where = 10 * kb + 1;
+        ok = mbar_wait_bounded(bar_s_full, par, abort_flag);  // S(kb) computed: the K buffer is free
+        if (!ok) break;
+        if (more) load_k(kb + 1);
+        where = 10 * kb + 2;
+        ok = mbar_wait_bounded(bar_s_free, par, abort_flag);  // every row holds S(kb) in registers
+        if (ok && more) ok = mbar_wait_bounded(bar_k, par ^ 1, abort_flag);
+        if (!ok) break;
+        if (more) {
+          tc_fence_after();
+          issue_s();
+        }
+        where = 10 * kb + 3;
+        ok = mbar_wait_bounded(bar_p_full, par, abort_flag) && mbar_wait_bounded(bar_v, par, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        constexpr uint32_t idesc_o = make_idesc_bf16(ATT_BM, DV);
+#pragma unroll
+        for (int kk = 0; kk < ATT_BN / 16; ++kk) {
+          const uint32_t pa = smem_u32(smem + L::kPOff + (kk / 4) * ATOM_BYTES_128);
+          const uint32_t va = smem_u32(smem + L::kVOff + (kk / 4) * L::kVAtomBytes);
+          umma_bf16_ss(tmem_o, make_sw128_kmajor_desc(pa) + (uint64_t)((kk % 4) * 2),
+                       make_sw128_kmajor_desc(va) + (uint64_t)((kk % 4) * 2), idesc_o, (kb > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(bar_pv_done);
+        if (more) {
+          where = 10 * kb + 4;
+          ok = mbar_wait_bounded(bar_pv_done, par, abort_flag);  // P V (kb) has read V: load the next block's values
+          if (!ok) break;
+          load_v(kb + 1);
+        }
+      }
+      if (!ok) {
+        report_status(p.status, kTimeoutFullBarrier, where);
+        *abort_flag = 1;
+      }
     }
-    if (!mbar_wait_bounded(bar_s, parity, abort_flag) || *abort_flag != 0) {
-      if (*abort_flag == 0) report_status(p.status, kTimeoutTmemFull, kb);
-      *abort_flag = 1;
-      ok = false;
-    }
-    // (every thread takes the same branches from here on: abort_flag is re-read after a CTA-wide barrier)
-    __syncthreads();
-    ok = (*abort_flag == 0);
-    if (!ok) break;
-    tc_fence_after();
-
-    // ---- pass 1: row maximum of the scaled, masked scores
-    float m_blk = -INFINITY;
-#pragma unroll 1
-    for (int c = 0; c < ATT_BN / 32; ++c) {
-      uint32_t r[32];
-      tmem_ld_32x32b_x32(tmem_s + lane_off + (uint32_t)(c * 32), r);
+  } else {
+    // ------------------------------------------------------------------ softmax rows
+    const int row = (int)threadIdx.x;
+    const int qpos = q0 + row;
+    const bool row_ok = qpos < p.seq;
+    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    const float sc = p.scale_log2;
+    float m_ref = -INFINITY, l_run = 0.0f;
+    bool ok = true;
+    for (int kb = 0; kb < n_kblocks && ok; ++kb) {
+      const int k0 = kb * ATT_BN;
+      const uint32_t par = kb & 1;
+      // (a failed wait ends the loop for the whole warp: the TMEM accesses and votes below are warp-wide)
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar_s_full, par, abort_flag))) { ok = false; break; }
+      tc_fence_after();
+      uint32_t s[ATT_BN];
+#pragma unroll
+      for (int c = 0; c < ATT_BN / 32; ++c)
+        tmem_ld_32x32b_x32(tmem_s + lane_off + (uint32_t)(c * 32), *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
       tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(bar_s_free);
+      // scaled, masked scores and their maximum (only the diagonal and the last block have anything to mask)
+      const bool need_mask = (k0 + ATT_BN - 1 > qpos) || (k0 + ATT_BN > p.seq);
+      float m_blk = -INFINITY;
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const int kpos = k0 + c * 32 + j;
-        const float s = (kpos <= qpos && kpos < p.seq) ? __uint_as_float(r[j]) * sc : -INFINITY;
-        m_blk = fmaxf(m_blk, s);
+      for (int j = 0; j < ATT_BN; ++j) {
+        float v = __uint_as_float(s[j]) * sc;
+        if (need_mask && !(k0 + j <= qpos && k0 + j < p.seq)) v = -INFINITY;
+        s[j] = __float_as_uint(v);
+        m_blk = fmaxf(m_blk, v);
       }
-    }
-    const float m_new = fmaxf(m_run, m_blk);
-    const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;  // a fully masked row keeps exp2(-inf) = 0 everywhere
-    const float alpha = exp2f(m_run - m_use);                 // m_run = -inf on the first block: alpha = 0
-    float l_blk = 0.0f;
-    // ---- pass 2: probabilities -> bf16 in shared memory (swizzled K-major, two 64-key atoms)
+      float alpha = 1.0f;
+      bool rescale = false;
+      if (m_blk > m_ref + kRescaleSlack || m_ref == -INFINITY) {
+        const float m_new = fmaxf(m_ref, m_blk);
+        if (m_new != -INFINITY) {
+          alpha = exp2f(m_ref - m_new);  // 0 when nothing was accumulated under the old reference
+          rescale = kb > 0;
+          m_ref = m_new;
+        }
+      }
+      const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
+      if (kb > 0) {
+        // P and the output accumulator belong to the tensor core until P V (kb - 1) has completed
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar_pv_done, par ^ 1, abort_flag))) { ok = false; break; }
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll 1
-    for (int c = 0; c < ATT_BN / 32; ++c) {
-      uint32_t r[32];
-      tmem_ld_32x32b_x32(tmem_s + lane_off + (uint32_t)(c * 32), r);
-      tmem_wait_ld();
-      float pv[32];
+          for (int c = 0; c < DV / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(tmem_o + lane_off + (uint32_t)(c * 32), r);
+            tmem_wait_ld();
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const int kpos = k0 + c * 32 + j;
-        const float s = (kpos <= qpos && kpos < p.seq) ? __uint_as_float(r[j]) * sc : -INFINITY;
-        pv[j] = exp2f(s - m_use);
+            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * alpha);
+            tmem_st_32x32b_x32(tmem_o + lane_off + (uint32_t)(c * 32), r);
+          }
+          tmem_wait_st();
+        }
       }
-      uint8_t* atom = smem + L::kPOff + (c / 2) * ATOM_BYTES_128;
+      l_run *= alpha;
+      float l_blk = 0.0f;
 #pragma unroll
-      for (int g = 0; g < 4; ++g) {
+      for (int g = 0; g < ATT_BN / 8; ++g) {
+        float pv[8];
+#pragma unroll
+        for (int t = 0; t < 8; ++t) pv[t] = exp2f(__uint_as_float(s[g * 8 + t]) - m_use);
         uint4 u;
-        u.x = pack_bf16x2(pv[g * 8 + 0], pv[g * 8 + 1]);
-        u.y = pack_bf16x2(pv[g * 8 + 2], pv[g * 8 + 3]);
-        u.z = pack_bf16x2(pv[g * 8 + 4], pv[g * 8 + 5]);
-        u.w = pack_bf16x2(pv[g * 8 + 6], pv[g * 8 + 7]);
+        u.x = pack_bf16x2(pv[0], pv[1]);
+        u.y = pack_bf16x2(pv[2], pv[3]);
+        u.z = pack_bf16x2(pv[4], pv[5]);
+        u.w = pack_bf16x2(pv[6], pv[7]);
         // the sum uses the rounded values, so that O / l is an exact convex combination of the V rows seen by the MMA
         const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
 #pragma unroll
@@ -204,64 +268,41 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           const float2 f = __bfloat1622float2(h[t]);
           l_blk += f.x + f.y;
         }
-        *reinterpret_cast<uint4*>(atom + sw128_chunk_off(row, (c % 2) * 4 + g)) = u;
+        *reinterpret_cast<uint4*>(smem + L::kPOff + (g / 8) * ATOM_BYTES_128 + sw128_chunk_off(row, g % 8)) = u;
       }
+      l_run += l_blk;
+      fence_proxy_async();  // the generic-proxy stores of P must be visible to the tensor core's reads
+      tc_fence_before();
+      mbar_arrive(bar_p_full);
     }
-    l_run = l_run * alpha + l_blk;
-    m_run = m_new;
-#pragma unroll
-    for (int i = 0; i < DV; ++i) o_acc[i] *= alpha;
-
-    fence_proxy_async();  // the generic-proxy stores of P must be visible to the tensor core's reads
-    tc_fence_before();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      tc_fence_after();
-      constexpr uint32_t idesc_o = make_idesc_bf16(ATT_BM, DV);
-#pragma unroll
-      for (int kk = 0; kk < ATT_BN / 16; ++kk) {
-        const uint32_t pa = smem_u32(smem + L::kPOff + (kk / 4) * ATOM_BYTES_128);
-        const uint32_t va = smem_u32(smem + L::kVOff + (kk / 4) * L::kVAtomBytes);
-        umma_bf16_ss(tmem_o, make_sw128_kmajor_desc(pa) + (uint64_t)((kk % 4) * 2),
-                     make_sw128_kmajor_desc(va) + (uint64_t)((kk % 4) * 2), idesc_o, kk > 0 ? 1u : 0u);
-      }
-      umma_commit(bar_o);
-    }
-    if (!mbar_wait_bounded(bar_o, parity, abort_flag)) {
-      report_status(p.status, kTimeoutTmemFull, 1000 + kb);
+    ok = __all_sync(0xffffffffu, ok && mbar_wait_bounded(bar_pv_done, (n_kblocks - 1) & 1, abort_flag));
+    if (!ok) {
+      report_status(p.status, kTimeoutTmemFull, row);
       *abort_flag = 1;
-    }
-    __syncthreads();
-    ok = (*abort_flag == 0);
-    if (!ok) break;
-    tc_fence_after();
+    } else {
+      tc_fence_after();
+      const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+      __nv_bfloat16* dst = p.out + (((size_t)batch * p.seq + (row_ok ? qpos : 0)) * p.heads + head) * p.dv + dv0;
+#pragma unroll 1
+      for (int c = 0; c < DV / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_o + lane_off + (uint32_t)(c * 32), r);
+        tmem_wait_ld();
+        if (row_ok) {
 #pragma unroll
-    for (int c = 0; c < DV / 32; ++c) {
-      uint32_t r[32];
-      tmem_ld_32x32b_x32(tmem_o + lane_off + (uint32_t)(c * 32), r);
-      tmem_wait_ld();
-#pragma unroll
-      for (int j = 0; j < 32; ++j) o_acc[c * 32 + j] += __uint_as_float(r[j]);
+          for (int i = 0; i < 32; i += 8) {
+            uint4 u;
+            u.x = pack_bf16x2(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+            u.y = pack_bf16x2(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+            u.z = pack_bf16x2(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+            u.w = pack_bf16x2(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + i) = u;
+          }
+        }
+      }
+      if (row_ok && p.lse != nullptr && dv0 == 0)
+        p.lse[((size_t)batch * p.heads + head) * p.seq + qpos] = m_ref * 0.6931471805599453f + __logf(l_run);
     }
-    // the next block's TMA and MMAs overwrite K, V, P and both accumulators: everyone must be done reading
-    tc_fence_before();
-    __syncthreads();
-  }
-
-  if (ok && row_ok) {
-    const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-    __nv_bfloat16* dst = p.out + (((size_t)batch * p.seq + qpos) * p.heads + head) * p.dv + dv0;
-#pragma unroll
-    for (int i = 0; i < DV; i += 8) {
-      uint4 u;
-      u.x = pack_bf16x2(o_acc[i] * inv, o_acc[i + 1] * inv);
-      u.y = pack_bf16x2(o_acc[i + 2] * inv, o_acc[i + 3] * inv);
-      u.z = pack_bf16x2(o_acc[i + 4] * inv, o_acc[i + 5] * inv);
-      u.w = pack_bf16x2(o_acc[i + 6] * inv, o_acc[i + 7] * inv);
-      *reinterpret_cast<uint4*>(dst + i) = u;
-    }
-    if (p.lse != nullptr && dv0 == 0)
-      p.lse[((size_t)batch * p.heads + head) * p.seq + qpos] = m_run * 0.6931471805599453f + __logf(l_run);
   }
 
   tc_fence_before();
@@ -270,7 +311,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     for (int i = 0; i < 200; ++i) __nanosleep(1000);  // copies that may still be in flight land first
     __syncthreads();
   }
-  if (warp == 0) {
+  if (warp == 4) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 256);
   }
@@ -284,11 +325,538 @@ static cudaError_t attn_fwd_variant(const CUtensorMap& tq, const CUtensorMap& tk
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
   if (e != cudaSuccess) return e;
   dim3 grid((p.seq + ATT_BM - 1) / ATT_BM, p.heads * (p.dv / DV), p.batch);
-  kern<<<grid, ATT_THREADS, L::kDynamicBytes, stream>>>(tq, tk, tvt, p);
+  kern<<<grid, FWD_THREADS, L::kDynamicBytes, stream>>>(tq, tk, tvt, p);
   return cudaGetLastError();
 }
 
 int attn_value_chunk(int dv) { return dv % 128 == 0 ? 128 : (dv % 64 == 0 ? 64 : 0); }
+
+// =============================================================================================================
+// Backward. With P = softmax(scale * Q K^T) (causal), O = P V, D = rowsum(dO * O):
+//   dV = P^T dO,   dP = dO V^T,   dS = P * (dP - D) * scale,   dQ = dS K,   dK = dS^T Q.
+// Two kernels, both built from the same pieces as the forward pass and with every MMA operand K-major (the host
+// passes transposed copies K^T, Q^T, dO^T [batch, heads, width, seq] where a product contracts over positions):
+//   attn_bwd_dq_kernel   one CTA per query block; per key block: S and dP on the tensor cores (dP contracts over
+//                        the FULL value width, streamed through a two-stage ring of 64-column atoms), the threads
+//                        (one query row each) form dS, and dQ += dS K accumulates in TMEM over the key blocks.
+//   attn_bwd_dkv_kernel  one CTA per key block (and value chunk); per query block: S^T = K Q^T and dP^T = V dO^T, the
+//                        threads (one key row each) form P^T and dS^T, and dV += P^T dO, dK += dS^T Q accumulate in
+//                        TMEM over the query blocks.
+// =============================================================================================================
+namespace {
+
+// D[tmem] (+)= A * B^T over K = 16 * steps, both tiles made of 64-column swizzle atoms `a_atom` / `b_atom` bytes apart.
+__device__ __forceinline__ void issue_mma_atoms(uint32_t tmem_d, uint32_t a_base, uint32_t a_atom, uint32_t b_base,
+                                                uint32_t b_atom, int steps, uint32_t idesc, bool accumulate) {
+  for (int kk = 0; kk < steps; ++kk) {
+    const uint64_t da = make_sw128_kmajor_desc(a_base + (uint32_t)(kk / 4) * a_atom) + (uint64_t)((kk % 4) * 2);
+    const uint64_t db = make_sw128_kmajor_desc(b_base + (uint32_t)(kk / 4) * b_atom) + (uint64_t)((kk % 4) * 2);
+    umma_bf16_ss(tmem_d, da, db, idesc, (accumulate || kk > 0) ? 1u : 0u);
+  }
+}
+
+template <int DQK>
+struct BwdDqSmem {
+  static constexpr int kQBytes = (DQK / 64) * ATOM_BYTES_128;
+  static constexpr int kQOff = 0;
+  static constexpr int kKOff = kQOff + kQBytes;
+  static constexpr int kKtAtomBytes = DQK * 128;
+  static constexpr int kKtOff = kKOff + kQBytes;
+  static constexpr int kDsOff = kKtOff + 2 * kKtAtomBytes;
+  static constexpr int kRingOff = kDsOff + 2 * ATOM_BYTES_128;  // 2 stages x {dO atom, V atom}
+  static constexpr int kBarOff = kRingOff + 4 * ATOM_BYTES_128;
+  static constexpr int kNumBars = 8;
+  static constexpr int kTmemPtrOff = kBarOff + kNumBars * 8;
+  static constexpr int kAbortOff = kTmemPtrOff + 4;
+  static constexpr int kDynamicBytes = kAbortOff + 4 + 1024;
+};
+
+template <int DQK, int DVC>
+struct BwdDkvSmem {
+  static constexpr int kKBytes = (DQK / 64) * ATOM_BYTES_128;
+  static constexpr int kKOff = 0;
+  static constexpr int kQOff = kKOff + kKBytes;              // Q_i, later Q_i^T (same size)
+  static constexpr int kQtAtomBytes = DQK * 128;
+  static constexpr int kRingOff = kQOff + kKBytes;           // 2 stages x {V atom, dO atom}; later dO^T chunk
+  static constexpr int kDotAtomBytes = DVC * 128;
+  static constexpr int kPtOff = kRingOff + 4 * ATOM_BYTES_128;
+  static constexpr int kDstOff = kPtOff + 2 * ATOM_BYTES_128;
+  static constexpr int kLseOff = kDstOff + 2 * ATOM_BYTES_128;
+  static constexpr int kDeltaOff = kLseOff + 128 * 4;
+  static constexpr int kBarOff = kDeltaOff + 128 * 4;
+  static constexpr int kNumBars = 8;
+  static constexpr int kTmemPtrOff = kBarOff + kNumBars * 8;
+  static constexpr int kAbortOff = kTmemPtrOff + 4;
+  static constexpr int kDynamicBytes = kAbortOff + 4 + 1024;
+};
+
+}  // namespace
+
+template <int DQK>
+__global__ void __launch_bounds__(ATT_THREADS)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                   const __grid_constant__ CUtensorMap tmap_kt, const __grid_constant__ CUtensorMap tmap_do,
+                   const __grid_constant__ CUtensorMap tmap_v, const AttnBwdParams p) {
+  using L = BwdDqSmem<DQK>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+  uint64_t* bar_q = bars + 0;
+  uint64_t* bar_k = bars + 1;
+  uint64_t* bar_mma1 = bars + 2;
+  uint64_t* bar_mma2 = bars + 3;
+  uint64_t* ring_full = bars + 4;  // [2]
+  uint64_t* ring_free = bars + 6;  // [2]
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + L::kTmemPtrOff);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOff);
+
+  const int warp = threadIdx.x >> 5;
+  const int n_qblocks = (p.seq + ATT_BM - 1) / ATT_BM;
+  const int qblk = n_qblocks - 1 - (int)blockIdx.x;
+  const int head = (int)blockIdx.y, batch = (int)blockIdx.z;
+  const int q0 = qblk * ATT_BM;
+  const int row = (int)threadIdx.x;
+  const int qpos = q0 + row;
+  const bool row_ok = qpos < p.seq;
+  const int dv_atoms = p.dv / 64;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < L::kNumBars; ++i) mbar_init(&bars[i], 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_ptr_smem, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+  const uint32_t tmem_s = tmem_base, tmem_dp = tmem_base + 128, tmem_dq = tmem_base + 256;
+  const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+
+  const size_t stat = ((size_t)batch * p.heads + head) * p.seq + (row_ok ? qpos : 0);
+  const float lse2 = row_ok ? p.lse[stat] * 1.4426950408889634f : INFINITY;  // +inf: every probability of the row is 0
+  const float delta = row_ok ? p.delta[stat] : 0.0f;
+
+  if (threadIdx.x == 0) {
+    mbar_arrive_expect_tx(bar_q, L::kQBytes);
+    for (int a = 0; a < DQK / 64; ++a)
+      tma_load_2d(smem + L::kQOff + a * ATOM_BYTES_128, &tmap_q, bar_q, head * DQK + a * 64, batch * p.seq + q0);
+  }
+
+  const int n_kblocks = qblk + 1;
+  uint32_t ring_n = 0;  // atom steps issued so far (thread 0 only)
+  bool ok = true;
+  for (int kb = 0; kb < n_kblocks && ok; ++kb) {
+    const int k0 = kb * ATT_BN;
+    const uint32_t parity = kb & 1;
+    if (threadIdx.x == 0) {
+      bool got = true;
+      mbar_arrive_expect_tx(bar_k, L::kQBytes + 2 * L::kKtAtomBytes);
+      for (int a = 0; a < DQK / 64; ++a)
+        tma_load_2d(smem + L::kKOff + a * ATOM_BYTES_128, &tmap_k, bar_k, head * DQK + a * 64, batch * p.seq + k0);
+      for (int a = 0; a < 2; ++a)
+        tma_load_2d(smem + L::kKtOff + a * L::kKtAtomBytes, &tmap_kt, bar_k, k0 + a * 64, (batch * p.heads + head) * DQK);
+      // dP = dO V^T over the whole value width: atoms through a two-stage ring, the next load in flight during the MMAs
+      auto load_atom = [&](uint32_t n, int a) -> bool {
+        const int st = n & 1;
+        if (!mbar_wait_bounded(&ring_free[st], ((n >> 1) & 1) ^ 1, abort_flag)) return false;
+        uint8_t* base = smem + L::kRingOff + st * 2 * ATOM_BYTES_128;
+        mbar_arrive_expect_tx(&ring_full[st], 2 * ATOM_BYTES_128);
+        tma_load_2d(base, &tmap_do, &ring_full[st], head * p.dv + a * 64, batch * p.seq + q0);
+        tma_load_2d(base + ATOM_BYTES_128, &tmap_v, &ring_full[st], head * p.dv + a * 64, batch * p.seq + k0);
+        return true;
+      };
+      got = load_atom(ring_n, 0);
+      if (kb == 0) got = got && mbar_wait_bounded(bar_q, 0, abort_flag);
+      got = got && mbar_wait_bounded(bar_k, parity, abort_flag);
+      if (got) {
+        tc_fence_after();
+        issue_mma_atoms(tmem_s, smem_u32(smem + L::kQOff), ATOM_BYTES_128, smem_u32(smem + L::kKOff), ATOM_BYTES_128,
+                        DQK / 16, make_idesc_bf16(ATT_BM, ATT_BN), false);
+        for (int a = 0; a < dv_atoms && got; ++a) {
+          const uint32_t n = ring_n + a;
+          if (a + 1 < dv_atoms) got = load_atom(n + 1, a + 1);
+          got = got && mbar_wait_bounded(&ring_full[n & 1], (n >> 1) & 1, abort_flag);
+          if (!got) break;
+          tc_fence_after();
+          const uint32_t base = smem_u32(smem + L::kRingOff + (n & 1) * 2 * ATOM_BYTES_128);
+          issue_mma_atoms(tmem_dp, base, 0, base + ATOM_BYTES_128, 0, 4, make_idesc_bf16(ATT_BM, ATT_BN), a > 0);
+          umma_commit(&ring_free[n & 1]);
+        }
+        ring_n += dv_atoms;
+      }
+      if (!got) {
+        report_status(p.status, kTimeoutFullBarrier, kb);
+        *abort_flag = 1;
+      }
+      umma_commit(bar_mma1);
+    }
+    if (!mbar_wait_bounded(bar_mma1, parity, abort_flag)) {
+      report_status(p.status, kTimeoutTmemFull, kb);
+      *abort_flag = 1;
+    }
+    __syncthreads();
+    ok = (*abort_flag == 0);
+    if (!ok) break;
+    tc_fence_after();
+
+#pragma unroll 1
+    for (int c = 0; c < ATT_BN / 32; ++c) {
+      uint32_t rs[32], rp[32];
+      tmem_ld_32x32b_x32(tmem_s + lane_off + (uint32_t)(c * 32), rs);
+      tmem_ld_32x32b_x32(tmem_dp + lane_off + (uint32_t)(c * 32), rp);
+      tmem_wait_ld();
+      float ds[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int kpos = k0 + c * 32 + j;
+        const bool valid = kpos <= qpos && kpos < p.seq;
+        const float pr = valid ? exp2f(__uint_as_float(rs[j]) * p.scale_log2 - lse2) : 0.0f;
+        ds[j] = pr * (__uint_as_float(rp[j]) - delta) * p.scale;
+      }
+      uint8_t* atom = smem + L::kDsOff + (c / 2) * ATOM_BYTES_128;
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        uint4 u;
+        u.x = pack_bf16x2(ds[g * 8 + 0], ds[g * 8 + 1]);
+        u.y = pack_bf16x2(ds[g * 8 + 2], ds[g * 8 + 3]);
+        u.z = pack_bf16x2(ds[g * 8 + 4], ds[g * 8 + 5]);
+        u.w = pack_bf16x2(ds[g * 8 + 6], ds[g * 8 + 7]);
+        *reinterpret_cast<uint4*>(atom + sw128_chunk_off(row, (c % 2) * 4 + g)) = u;
+      }
+    }
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      tc_fence_after();
+      // dQ += dS [128 q x 128 keys] * (K^T [DQK x 128 keys])^T
+      issue_mma_atoms(tmem_dq, smem_u32(smem + L::kDsOff), ATOM_BYTES_128, smem_u32(smem + L::kKtOff), L::kKtAtomBytes,
+                      ATT_BN / 16, make_idesc_bf16(ATT_BM, DQK), kb > 0);
+      umma_commit(bar_mma2);
+    }
+    if (!mbar_wait_bounded(bar_mma2, parity, abort_flag)) {
+      report_status(p.status, kTimeoutTmemFull, 1000 + kb);
+      *abort_flag = 1;
+    }
+    tc_fence_before();
+    __syncthreads();
+    ok = (*abort_flag == 0);
+  }
+
+  if (ok) {
+    tc_fence_after();
+#pragma unroll 1
+    for (int c = 0; c < DQK / 32; ++c) {
+      uint32_t r[32];
+      tmem_ld_32x32b_x32(tmem_dq + lane_off + (uint32_t)(c * 32), r);
+      tmem_wait_ld();
+      if (row_ok) {
+        float* dst = p.dq + (((size_t)batch * p.seq + qpos) * p.heads + head) * DQK + c * 32;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                            __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int DQK, int DVC>
+__global__ void __launch_bounds__(ATT_THREADS)
+attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_q,
+                    const __grid_constant__ CUtensorMap tmap_qt, const __grid_constant__ CUtensorMap tmap_v,
+                    const __grid_constant__ CUtensorMap tmap_do, const __grid_constant__ CUtensorMap tmap_dot,
+                    const AttnBwdParams p) {
+  using L = BwdDkvSmem<DQK, DVC>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+  uint64_t* bar_k = bars + 0;
+  uint64_t* bar_q = bars + 1;
+  uint64_t* bar_mma1 = bars + 2;
+  uint64_t* bar_mma2 = bars + 3;
+  uint64_t* ring_full = bars + 4;
+  uint64_t* ring_free = bars + 6;
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + L::kTmemPtrOff);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOff);
+  float* s_lse = reinterpret_cast<float*>(smem + L::kLseOff);
+  float* s_delta = reinterpret_cast<float*>(smem + L::kDeltaOff);
+
+  const int warp = threadIdx.x >> 5;
+  const int n_blocks = (p.seq + ATT_BM - 1) / ATT_BM;
+  const int kblk = (int)blockIdx.x;  // key block 0 meets every query block: longest first
+  const int dv_chunks = p.dv / DVC;
+  const int head = (int)blockIdx.y / dv_chunks;
+  const int chunk = (int)blockIdx.y - head * dv_chunks;
+  const int dv0 = chunk * DVC;
+  const bool do_dk = chunk == 0;
+  const int batch = (int)blockIdx.z;
+  const int k0 = kblk * ATT_BN;
+  const int row = (int)threadIdx.x;
+  const int kpos = k0 + row;
+  const bool row_ok = kpos < p.seq;
+  const int dv_atoms = p.dv / 64;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < L::kNumBars; ++i) mbar_init(&bars[i], 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_ptr_smem, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+  const uint32_t tmem_st = tmem_base, tmem_dpt = tmem_base + 128, tmem_dv = tmem_base + 256, tmem_dk = tmem_base + 384;
+  const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+
+  if (threadIdx.x == 0) {
+    mbar_arrive_expect_tx(bar_k, L::kKBytes);
+    for (int a = 0; a < DQK / 64; ++a)
+      tma_load_2d(smem + L::kKOff + a * ATOM_BYTES_128, &tmap_k, bar_k, head * DQK + a * 64, batch * p.seq + k0);
+  }
+
+  uint32_t ring_n = 0;
+  bool ok = true;
+  int it = 0;
+  for (int qb = kblk; qb < n_blocks && ok; ++qb, ++it) {
+    const int q0 = qb * ATT_BM;
+    const uint32_t parity = it & 1;
+    {
+      // statistics of this query block's rows (columns of S^T)
+      const int qp = q0 + row;
+      const size_t o = ((size_t)batch * p.heads + head) * p.seq + (qp < p.seq ? qp : 0);
+      s_lse[row] = qp < p.seq ? p.lse[o] * 1.4426950408889634f : INFINITY;
+      s_delta[row] = qp < p.seq ? p.delta[o] : 0.0f;
+    }
+    if (threadIdx.x == 0) {
+      bool got = true;
+      mbar_arrive_expect_tx(bar_q, L::kKBytes);
+      for (int a = 0; a < DQK / 64; ++a)
+        tma_load_2d(smem + L::kQOff + a * ATOM_BYTES_128, &tmap_q, bar_q, head * DQK + a * 64, batch * p.seq + q0);
+      auto load_atom = [&](uint32_t n, int a) -> bool {
+        const int st = n & 1;
+        if (!mbar_wait_bounded(&ring_free[st], ((n >> 1) & 1) ^ 1, abort_flag)) return false;
+        uint8_t* base = smem + L::kRingOff + st * 2 * ATOM_BYTES_128;
+        mbar_arrive_expect_tx(&ring_full[st], 2 * ATOM_BYTES_128);
+        tma_load_2d(base, &tmap_v, &ring_full[st], head * p.dv + a * 64, batch * p.seq + k0);
+        tma_load_2d(base + ATOM_BYTES_128, &tmap_do, &ring_full[st], head * p.dv + a * 64, batch * p.seq + q0);
+        return true;
+      };
+      got = load_atom(ring_n, 0);
+      if (it == 0) got = got && mbar_wait_bounded(bar_k, 0, abort_flag);
+      got = got && mbar_wait_bounded(bar_q, 0 ^ ((2 * it) & 1), abort_flag);  // bar_q completes twice per iteration
+      if (got) {
+        tc_fence_after();
+        // S^T = K_j Q_i^T
+        issue_mma_atoms(tmem_st, smem_u32(smem + L::kKOff), ATOM_BYTES_128, smem_u32(smem + L::kQOff), ATOM_BYTES_128,
+                        DQK / 16, make_idesc_bf16(ATT_BM, ATT_BN), false);
+        // dP^T = V_j dO_i^T over the whole value width
+        for (int a = 0; a < dv_atoms && got; ++a) {
+          const uint32_t n = ring_n + a;
+          if (a + 1 < dv_atoms) got = load_atom(n + 1, a + 1);
+          got = got && mbar_wait_bounded(&ring_full[n & 1], (n >> 1) & 1, abort_flag);
+          if (!got) break;
+          tc_fence_after();
+          const uint32_t base = smem_u32(smem + L::kRingOff + (n & 1) * 2 * ATOM_BYTES_128);
+          issue_mma_atoms(tmem_dpt, base, 0, base + ATOM_BYTES_128, 0, 4, make_idesc_bf16(ATT_BM, ATT_BN), a > 0);
+          umma_commit(&ring_free[n & 1]);
+        }
+        ring_n += dv_atoms;
+      }
+      if (!got) {
+        report_status(p.status, kTimeoutFullBarrier, it);
+        *abort_flag = 1;
+      }
+      umma_commit(bar_mma1);
+    }
+    if (!mbar_wait_bounded(bar_mma1, parity, abort_flag)) {
+      report_status(p.status, kTimeoutTmemFull, it);
+      *abort_flag = 1;
+    }
+    __syncthreads();  // also publishes s_lse / s_delta
+    ok = (*abort_flag == 0);
+    if (!ok) break;
+    tc_fence_after();
+
+    // Q_i and the ring are free now (their MMAs completed): fetch Q_i^T and the dO_i^T chunk while the threads work.
+    if (threadIdx.x == 0) {
+      // both ring stages must be idle before the dO^T chunk overwrites them (their last MMAs were committed above)
+      bool got = mbar_wait_bounded(&ring_free[0], (((ring_n + 1) >> 1) & 1) ^ 1, abort_flag) &&
+                 mbar_wait_bounded(&ring_free[1], ((ring_n >> 1) & 1) ^ 1, abort_flag);
+      if (got) {
+        mbar_arrive_expect_tx(bar_q, (do_dk ? 2 * L::kQtAtomBytes : 0) + 2 * L::kDotAtomBytes);
+        if (do_dk)
+          for (int a = 0; a < 2; ++a)
+            tma_load_2d(smem + L::kQOff + a * L::kQtAtomBytes, &tmap_qt, bar_q, q0 + a * 64, (batch * p.heads + head) * DQK);
+        for (int a = 0; a < 2; ++a)
+          tma_load_2d(smem + L::kRingOff + a * L::kDotAtomBytes, &tmap_dot, bar_q, q0 + a * 64,
+                      (batch * p.heads + head) * p.dv + dv0);
+      } else {
+        report_status(p.status, kTimeoutEmptyBarrier, it);
+        *abort_flag = 1;
+      }
+    }
+    __syncwarp();  // warp 0 is whole again before its warp-wide TMEM loads
+
+#pragma unroll 1
+    for (int c = 0; c < ATT_BM / 32; ++c) {
+      uint32_t rs[32], rp[32];
+      tmem_ld_32x32b_x32(tmem_st + lane_off + (uint32_t)(c * 32), rs);
+      tmem_ld_32x32b_x32(tmem_dpt + lane_off + (uint32_t)(c * 32), rp);
+      tmem_wait_ld();
+      float pt[32], ds[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int col = c * 32 + j;
+        const int qp = q0 + col;
+        const bool valid = row_ok && kpos <= qp && qp < p.seq;
+        pt[j] = valid ? exp2f(__uint_as_float(rs[j]) * p.scale_log2 - s_lse[col]) : 0.0f;
+        ds[j] = pt[j] * (__uint_as_float(rp[j]) - s_delta[col]) * p.scale;
+      }
+      uint8_t* atom_p = smem + L::kPtOff + (c / 2) * ATOM_BYTES_128;
+      uint8_t* atom_d = smem + L::kDstOff + (c / 2) * ATOM_BYTES_128;
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        uint4 u, w;
+        u.x = pack_bf16x2(pt[g * 8 + 0], pt[g * 8 + 1]);
+        u.y = pack_bf16x2(pt[g * 8 + 2], pt[g * 8 + 3]);
+        u.z = pack_bf16x2(pt[g * 8 + 4], pt[g * 8 + 5]);
+        u.w = pack_bf16x2(pt[g * 8 + 6], pt[g * 8 + 7]);
+        w.x = pack_bf16x2(ds[g * 8 + 0], ds[g * 8 + 1]);
+        w.y = pack_bf16x2(ds[g * 8 + 2], ds[g * 8 + 3]);
+        w.z = pack_bf16x2(ds[g * 8 + 4], ds[g * 8 + 5]);
+        w.w = pack_bf16x2(ds[g * 8 + 6], ds[g * 8 + 7]);
+        const uint32_t off = sw128_chunk_off(row, (c % 2) * 4 + g);
+        *reinterpret_cast<uint4*>(atom_p + off) = u;
+        *reinterpret_cast<uint4*>(atom_d + off) = w;
+      }
+    }
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      bool got = (*abort_flag == 0) && mbar_wait_bounded(bar_q, 1 ^ ((2 * it) & 1), abort_flag);
+      if (got) {
+        tc_fence_after();
+        // dV += P^T [128 keys x 128 q] * (dO^T chunk [DVC x 128 q])^T
+        issue_mma_atoms(tmem_dv, smem_u32(smem + L::kPtOff), ATOM_BYTES_128, smem_u32(smem + L::kRingOff), L::kDotAtomBytes,
+                        ATT_BM / 16, make_idesc_bf16(ATT_BM, DVC), it > 0);
+        // dK += dS^T [128 keys x 128 q] * (Q^T [DQK x 128 q])^T
+        if (do_dk)
+          issue_mma_atoms(tmem_dk, smem_u32(smem + L::kDstOff), ATOM_BYTES_128, smem_u32(smem + L::kQOff), L::kQtAtomBytes,
+                          ATT_BM / 16, make_idesc_bf16(ATT_BM, DQK), it > 0);
+      } else {
+        report_status(p.status, kTimeoutFullBarrier, 2000 + it);
+        *abort_flag = 1;
+      }
+      umma_commit(bar_mma2);
+    }
+    if (!mbar_wait_bounded(bar_mma2, parity, abort_flag)) {
+      report_status(p.status, kTimeoutTmemFull, 1000 + it);
+      *abort_flag = 1;
+    }
+    tc_fence_before();
+    __syncthreads();
+    ok = (*abort_flag == 0);
+  }
+
+  if (ok) {
+    tc_fence_after();
+#pragma unroll 1
+    for (int c = 0; c < DVC / 32; ++c) {
+      uint32_t r[32];
+      tmem_ld_32x32b_x32(tmem_dv + lane_off + (uint32_t)(c * 32), r);
+      tmem_wait_ld();
+      if (row_ok) {
+        float* dst = p.dv_out + (((size_t)batch * p.seq + kpos) * p.heads + head) * p.dv + dv0 + c * 32;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                            __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+      }
+    }
+    if (do_dk) {
+#pragma unroll 1
+      for (int c = 0; c < DQK / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_dk + lane_off + (uint32_t)(c * 32), r);
+        tmem_wait_ld();
+        if (row_ok) {
+          float* dst = p.dk + (((size_t)batch * p.seq + kpos) * p.heads + head) * DQK + c * 32;
+#pragma unroll
+          for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                              __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int DQK>
+static cudaError_t attn_bwd_dq_variant(const CUtensorMap* maps, const AttnBwdParams& p, cudaStream_t stream) {
+  using L = BwdDqSmem<DQK>;
+  static_assert(L::kDynamicBytes <= 232448, "shared memory of one CTA exceeds 227 KB");
+  auto kern = attn_bwd_dq_kernel<DQK>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
+  if (e != cudaSuccess) return e;
+  dim3 grid((p.seq + ATT_BM - 1) / ATT_BM, p.heads, p.batch);
+  kern<<<grid, ATT_THREADS, L::kDynamicBytes, stream>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
+  return cudaGetLastError();
+}
+
+template <int DQK, int DVC>
+static cudaError_t attn_bwd_dkv_variant(const CUtensorMap* maps, const AttnBwdParams& p, cudaStream_t stream) {
+  using L = BwdDkvSmem<DQK, DVC>;
+  static_assert(L::kDynamicBytes <= 232448, "shared memory of one CTA exceeds 227 KB");
+  auto kern = attn_bwd_dkv_kernel<DQK, DVC>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
+  if (e != cudaSuccess) return e;
+  dim3 grid((p.seq + ATT_BM - 1) / ATT_BM, p.heads * (p.dv / DVC), p.batch);
+  kern<<<grid, ATT_THREADS, L::kDynamicBytes, stream>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], p);
+  return cudaGetLastError();
+}
+
+// maps_dq = {q, k, k^T, dO, v}; maps_dkv = {k, q, q^T, v, dO, dO^T}
+int attn_bwd_launch(const CUtensorMap* maps_dq, const CUtensorMap* maps_dkv, const AttnBwdParams& p, cudaStream_t stream) {
+  const int dvc = attn_value_chunk(p.dv);
+  if (dvc == 0 || (p.dqk != 64 && p.dqk != 128) || p.seq % 8 != 0 || p.batch > 65535 || p.heads * (p.dv / dvc) > 65535)
+    return (int)cudaErrorInvalidValue;
+  cudaError_t e = p.dqk == 64 ? attn_bwd_dq_variant<64>(maps_dq, p, stream) : attn_bwd_dq_variant<128>(maps_dq, p, stream);
+  if (e != cudaSuccess) return (int)e;
+  if (p.dqk == 64) e = dvc == 128 ? attn_bwd_dkv_variant<64, 128>(maps_dkv, p, stream) : attn_bwd_dkv_variant<64, 64>(maps_dkv, p, stream);
+  else e = dvc == 128 ? attn_bwd_dkv_variant<128, 128>(maps_dkv, p, stream) : attn_bwd_dkv_variant<128, 64>(maps_dkv, p, stream);
+  return (int)e;
+}
+
 
 int attn_fwd_launch(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tvt, const AttnParams& p,
                     cudaStream_t stream) {

@@ -442,6 +442,50 @@ void attn_fwd(const Tensor& q, const Tensor& k, const Tensor& vt, const Tensor& 
   check_cuda(lmsae::attn_fwd_launch(tq, tk, tvt, p, at::cuda::getCurrentCUDAStream()), "attn_fwd launch");
 }
 
+// q, k, v, dout: bf16 [b, s, h, *]; kt, qt: bf16 [b, h, dqk, s]; dot: bf16 [b, h, dv, s]; lse, delta: fp32 [b, h, s];
+// dq, dk: fp32 [b, s, h, dqk]; dv: fp32 [b, s, h, dv].
+void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& dout, const Tensor& qt, const Tensor& kt,
+              const Tensor& dot, const Tensor& lse, const Tensor& delta, const Tensor& dq, const Tensor& dk, const Tensor& dv,
+              double scale, const Tensor& status) {
+  for (const Tensor* t : {&q, &k, &v, &dout, &qt, &kt, &dot}) { CHECK_T(*t, torch::kBFloat16); }
+  for (const Tensor* t : {&lse, &delta, &dq, &dk, &dv}) { CHECK_T(*t, torch::kFloat32); }
+  CHECK_T(status, torch::kInt32);
+  lmsae::AttnBwdParams p{};
+  p.batch = (int)q.size(0);
+  p.seq = (int)q.size(1);
+  p.heads = (int)q.size(2);
+  p.dqk = (int)q.size(3);
+  p.dv = (int)v.size(3);
+  const int64_t bs = (int64_t)p.batch * p.seq, bh = (int64_t)p.batch * p.heads;
+  TORCH_CHECK(k.sizes() == q.sizes() && dq.sizes() == q.sizes() && dk.sizes() == q.sizes(), "q, k, dq, dk: [b, s, h, dqk]");
+  TORCH_CHECK(v.size(0) == p.batch && v.size(1) == p.seq && v.size(2) == p.heads && dout.sizes() == v.sizes() && dv.sizes() == v.sizes(),
+              "v, dout, dv: [b, s, h, dv]");
+  TORCH_CHECK(qt.numel() == q.numel() && kt.numel() == q.numel() && qt.size(3) == p.seq && kt.size(3) == p.seq &&
+                  dot.numel() == v.numel() && dot.size(3) == p.seq, "qt, kt: [b, h, dqk, s]; dot: [b, h, dv, s]");
+  TORCH_CHECK(lse.numel() == bh * p.seq && delta.numel() == bh * p.seq, "lse, delta: [b, h, s]");
+  const int dvc = lmsae::attn_value_chunk(p.dv);
+  TORCH_CHECK(dvc != 0 && (p.dqk == 64 || p.dqk == 128) && p.seq % 8 == 0, "attn_bwd: d_qk in {64, 128}, d_v % 64 == 0, seq % 8 == 0");
+  p.scale = (float)scale;
+  p.scale_log2 = (float)(scale * 1.4426950408889634);
+  p.lse = lse.data_ptr<float>();
+  p.delta = delta.data_ptr<float>();
+  p.dq = dq.data_ptr<float>();
+  p.dk = dk.data_ptr<float>();
+  p.dv_out = dv.data_ptr<float>();
+  p.status = status.data_ptr<int>();
+  const c10::cuda::CUDAGuard guard(q.device());
+  const CUtensorMap mq = make_bf16_tile_map(q.data_ptr(), bs, (int64_t)p.heads * p.dqk, 128);
+  const CUtensorMap mk = make_bf16_tile_map(k.data_ptr(), bs, (int64_t)p.heads * p.dqk, 128);
+  const CUtensorMap mv = make_bf16_tile_map(v.data_ptr(), bs, (int64_t)p.heads * p.dv, 128);
+  const CUtensorMap mdo = make_bf16_tile_map(dout.data_ptr(), bs, (int64_t)p.heads * p.dv, 128);
+  const CUtensorMap mqt = make_bf16_tile_map(qt.data_ptr(), bh * p.dqk, p.seq, p.dqk);
+  const CUtensorMap mkt = make_bf16_tile_map(kt.data_ptr(), bh * p.dqk, p.seq, p.dqk);
+  const CUtensorMap mdot = make_bf16_tile_map(dot.data_ptr(), bh * p.dv, p.seq, dvc);
+  const CUtensorMap maps_dq[5] = {mq, mk, mkt, mdo, mv};
+  const CUtensorMap maps_dkv[6] = {mk, mq, mqt, mv, mdo, mdot};
+  check_cuda(lmsae::attn_bwd_launch(maps_dq, maps_dkv, p, at::cuda::getCurrentCUDAStream()), "attn_bwd launch");
+}
+
 // ---- selection / compaction ----------------------------------------------------------------------------
 int dtype_code(const Tensor& t) {
   if (t.scalar_type() == torch::kFloat32) return 0;
@@ -815,6 +859,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("encoder_gemm", &encoder_gemm);
   m.def("jumprelu", &jumprelu);
   m.def("attn_fwd", &attn_fwd);
+  m.def("attn_bwd", &attn_bwd);
   m.def("radix_hi_bins", &radix_hi_bins);
   m.def("radix_hist", &radix_hist);
   m.def("radix_pick", &radix_pick);

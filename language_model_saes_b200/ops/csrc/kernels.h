@@ -139,6 +139,17 @@ struct AttnParams {
   float* lse;             // [batch, heads, seq] natural-log sum of exponentials (nullptr: not wanted)
   int* status;
 };
+struct AttnBwdParams {
+  int batch, seq, heads, dqk, dv;
+  float scale, scale_log2;
+  const float* lse;    // [batch, heads, seq] from the forward pass
+  const float* delta;  // [batch, heads, seq] rowsum(dO * O)
+  float* dq;           // [batch, seq, heads, dqk]
+  float* dk;           // [batch, seq, heads, dqk]
+  float* dv_out;       // [batch, seq, heads, dv]
+  int* status;
+};
+int attn_bwd_launch(const CUtensorMap* maps_dq, const CUtensorMap* maps_dkv, const AttnBwdParams& p, cudaStream_t stream);
 int attn_value_chunk(int dv);
 int attn_fwd_launch(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tvt, const AttnParams& p,
                     cudaStream_t stream);

@@ -1,0 +1,127 @@
+"""Micro-benchmarks of the kernels behind the other dictionary families and the batch-level selections, each against
+the library path it replaces: ``python -m language_model_saes_b200.ops.microbench_families --case all``.
+
+Timing as in ``ops.microbench``: CUDA events on the launching stream after warm-up, a synchronise on both sides, and
+a buffer larger than L2 written between timed iterations. One JSON object per line.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+import torch.nn.functional as F
+
+from . import attention as A
+from . import clt_kernels as CK
+from . import sae_kernels as K
+from . import select_kernels as S
+from .microbench import _timeit
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case", default="all", help="all | attn | batchtopk | clt | compact | headsum")
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    a = ap.parse_args(argv)
+    dev = torch.device("cuda")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    want = lambda c: a.case in ("all", c)  # noqa: E731
+
+    def report(name, ours, ref, **extra):
+        rec = {"case": name, "ms_ours": round(ours[0], 4), "ms_reference_path": round(ref[0], 4),
+               "speedup": round(ref[0] / ours[0], 2), **extra}  # fmt: skip
+        print(json.dumps(rec), flush=True)
+
+    if want("attn"):
+        # low-rank sparse attention at d_sae 8192: 64 QK heads of width 64, OV groups of 128, 4 x 1024 tokens
+        b, s, h, dqk, dv = 4, 1024, 64, 64, 128
+        q, k = (torch.randn(b, s, h, dqk, device=dev, dtype=torch.bfloat16).requires_grad_() for _ in range(2))
+        v = torch.randn(b, s, h, dv, device=dev, dtype=torch.bfloat16).requires_grad_()
+        do = torch.randn(b, s, h, dv, device=dev, dtype=torch.bfloat16)
+        scale = dqk**-0.5
+
+        def sdpa():
+            return F.scaled_dot_product_attention(q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3),
+                                                  scale=scale, is_causal=True).permute(0, 2, 1, 3)  # fmt: skip
+
+        def train(fn):
+            out = fn()
+            out.backward(do)
+            q.grad = k.grad = v.grad = None
+
+        flops_fwd = 2.0 * b * h * s * s * (dqk + dv) / 2  # causal: half of the score matrix
+        with torch.no_grad():
+            t_o = _timeit(lambda: A.causal_attention_fwd(q, k, v, scale), a.iters, a.warmup, flush)
+            t_r = _timeit(sdpa, a.iters, a.warmup, flush)
+        report("attention_fwd_b4_s1024_h64_dqk64_dv128", t_o, t_r, tflops_ours=round(flops_fwd / t_o[0] / 1e9, 1))
+        t_o = _timeit(lambda: train(lambda: A.causal_attention(q, k, v, scale)), a.iters, a.warmup, flush)
+        t_r = _timeit(lambda: train(sdpa), a.iters, a.warmup, flush)
+        report("attention_fwd_bwd_b4_s1024_h64_dqk64_dv128", t_o, t_r, tflops_ours=round(3.5 * flops_fwd / t_o[0] / 1e9, 1))
+        K.check_status(dev)
+        del q, k, v, do
+
+    if want("batchtopk"):
+        for dtype in (torch.float32, torch.bfloat16):
+            B, N, k = 4096, 32768, 50
+            x = torch.randn(B, N, device=dev).relu_().to(dtype)
+            t_o = _timeit(lambda: S.positive_topk(x, k * B, (0, 1)), a.iters, a.warmup, flush)
+            from ..utils.math import topk
+
+            t_r = _timeit(lambda: topk(x, k=k * B, dim=(0, 1), abs=True), max(2, a.iters // 2), 1, flush)
+            report(f"batchtopk_mask_4096x32768_k50_{str(dtype).split('.')[-1]}", t_o, t_r,
+                   gbs_ours=round(x.numel() * x.element_size() * 4 / t_o[0] / 1e6, 1))  # fmt: skip
+            del x
+
+    if want("clt"):
+        B, L, Fd, d, k = 4096, 12, 8192, 768, 32
+        w16 = [(torch.randn(t + 1, Fd, d, device=dev) / d**0.5).to(torch.bfloat16) for t in range(L)]
+        acts = torch.zeros(B, L * Fd, device=dev, dtype=torch.bfloat16)
+        cols = torch.randint(0, L * Fd, (B, k * L), device=dev)
+        acts.scatter_(1, cols, torch.rand(B, k * L, device=dev).to(torch.bfloat16) + 0.1)
+        acts = acts.view(B, L, Fd)
+        idx, val = S.dense_rows_to_sparse(acts.view(B, L * Fd))
+
+        def dense():
+            return torch.stack([torch.einsum("blf,lfd->bd", acts[:, : t + 1], w16[t]) for t in range(L)])
+
+        t_o = _timeit(lambda: CK.clt_decode(idx, val, w16, None, torch.bfloat16), a.iters, a.warmup, flush)
+        t_r = _timeit(dense, a.iters, a.warmup, flush)
+        report("clt_decode_fanout_B4096_L12_F8192_d768_k32perlayer", t_o, t_r)
+        t_c = _timeit(lambda: S.dense_rows_to_sparse(acts.view(B, L * Fd)), a.iters, a.warmup, flush)
+        print(json.dumps({"case": "row_compact_4096x98304_bf16", "ms_ours": round(t_c[0], 4),
+                          "gbs": round(acts.numel() * 2 * 2 / t_c[0] / 1e6, 1)}), flush=True)  # fmt: skip
+        dy = torch.randn(L, B, d, device=dev).to(torch.bfloat16)
+        t_g = _timeit(lambda: (CK.clt_dact(idx, w16, dy), CK.clt_wgrad(idx, val, dy, L, Fd)), a.iters, a.warmup, flush)
+        print(json.dumps({"case": "clt_backward_dact_wgrad", "ms_ours": round(t_g[0], 4)}), flush=True)
+        del w16, acts, dy
+
+    if want("compact"):
+        n, d = 1 << 20, 1024
+        src = torch.randn(n, d, device=dev)
+        keep = torch.rand(n, device=dev) > 0.1
+        t_o = _timeit(lambda: S.compact_rows(src, keep, torch.bfloat16), a.iters, a.warmup, flush)
+        t_r = _timeit(lambda: src[keep].to(torch.bfloat16), a.iters, a.warmup, flush)
+        report("mask_compact_cast_1Mx1024_fp32_to_bf16", t_o, t_r, gbs_ours=round(n * d * 0.9 * 6 / t_o[0] / 1e6, 1))
+        del src
+
+    if want("headsum"):
+        from ..parallel.symm import HeadSumComm
+
+        M, heads, d, N = 4096, 4, 768, 24576
+        x = torch.randn(M, heads * d, device=dev).to(torch.bfloat16)
+        w = (torch.randn(heads * N, d, device=dev) / d**0.5).to(torch.bfloat16)
+        bias = torch.zeros(N, device=dev)
+        comm = HeadSumComm(None, dev, M, N)
+        t_o = _timeit(lambda: comm.head_sum(x, w, bias, heads, N, torch.bfloat16), a.iters, a.warmup, flush)
+        x3, w3 = x.view(M, heads, d), w.view(heads, N, d)
+        t_r = _timeit(lambda: torch.einsum("bhd,hfd->bhf", x3, w3).sum(1), a.iters, a.warmup, flush)
+        report("crosscoder_head_sum_gemm_M4096_4heads_d768_F24576", t_o, t_r,
+               tflops_ours=round(2.0 * M * heads * d * N / t_o[0] / 1e9, 1))  # fmt: skip
+        K.check_status(dev)
+
+
+if __name__ == "__main__":
+    main()

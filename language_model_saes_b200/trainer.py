@@ -333,6 +333,10 @@ class Trainer:
         sched_path = ckpt_dir / "scheduler.pt"
         if sched_path.exists() and trainer.scheduler is not None:
             trainer.scheduler.load_state_dict(torch.load(sched_path, map_location="cpu", weights_only=False))
+            # a freshly built scheduler has put its step-0 rate into the optimizer: restore the rate of the saved step
+            if trainer.optimizer is not None:
+                for group, lr in zip(trainer.optimizer.param_groups, trainer.scheduler.get_last_lr()):
+                    group["lr"] = lr
         extra_path = ckpt_dir / "extra_state.pt"
         if extra_path.exists():
             extra = torch.load(extra_path, map_location="cpu", weights_only=False)
