@@ -529,6 +529,19 @@ void radix_pick(const Tensor& hist, int64_t nbins, int64_t k, const c10::optiona
              "radix_pick launch");
 }
 
+// out = where(x >= thr[segment], x, 0) for x viewed as [A, S, N]
+Tensor threshold_mask(const Tensor& x, const Tensor& thr, int64_t A, int64_t S, int64_t N) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.numel() == A * S * N, "x must be a contiguous [A, S, N] array");
+  CHECK_T(thr, torch::kFloat32);
+  TORCH_CHECK(thr.numel() == S, "one threshold per segment");
+  const c10::cuda::CUDAGuard guard(x.device());
+  Tensor out = torch::empty_like(x);
+  check_cuda(lmsae::threshold_mask_launch(dtype_code(x), x.data_ptr(), thr.data_ptr<float>(), A, S, N, out.data_ptr(),
+                                          at::cuda::getCurrentCUDAStream()),
+             "threshold_mask launch");
+  return out;
+}
+
 // x [B, N] -> idx / val [B, cap] (both optional: count only) and nnz [B] (optional)
 void row_compact(const Tensor& x, const c10::optional<Tensor>& idx, const c10::optional<Tensor>& val,
                  const c10::optional<Tensor>& nnz) {
@@ -863,6 +876,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("radix_hi_bins", &radix_hi_bins);
   m.def("radix_hist", &radix_hist);
   m.def("radix_pick", &radix_pick);
+  m.def("threshold_mask", &threshold_mask);
   m.def("row_compact", &row_compact);
   m.def("exclusive_scan", &exclusive_scan);
   m.def("gather_rows_cast", &gather_rows_cast);

@@ -125,6 +125,8 @@ int radix_hist_launch(int dtype, const void* x, long long A, long long S, long l
                       const long long* sel, unsigned* hist, cudaStream_t stream);
 int radix_pick_launch(const unsigned* hist, int nbins, long long k, const long long* sel_in, int level, long long* sel_out,
                       float* thr, cudaStream_t stream);
+int threshold_mask_launch(int dtype, const void* x, const float* thr, long long A, long long S, long long N, void* out,
+                          cudaStream_t stream);
 int row_compact_launch(int dtype, const void* x, int B, long long N, int cap, int* idx, float* val, int* nnz,
                        cudaStream_t stream);
 int gather_rows_cast_launch(int in_dtype, int out_dtype, const void* src, const int* keep, const int* pos, long long n,

@@ -35,6 +35,15 @@ __device__ __forceinline__ uint32_t positive_bits<__nv_bfloat16>(__nv_bfloat16 v
   return f > 0.0f ? __float_as_uint(f) : 0u;
 }
 
+__device__ __forceinline__ float to_float_any(float v) { return v; }
+__device__ __forceinline__ float to_float_any(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T>
+__device__ __forceinline__ T from_float_any(float v);
+template <>
+__device__ __forceinline__ float from_float_any<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float_any<__nv_bfloat16>(float v) { return __float2bfloat16(v); }
+
 template <typename T>
 struct Vec;
 template <>
@@ -174,6 +183,48 @@ radix_pick_kernel(const unsigned* __restrict__ hist, int nbins, long long k, con
     if (level == 0 && thr != nullptr) {
       const uint32_t bits = (uint32_t)bin << 16;  // bf16 data: the upper half IS the value
       *thr = bits == 0 ? __uint_as_float(1u) : __uint_as_float(bits);
+    }
+  }
+}
+
+// out = x where x >= thr[segment] (thr > 0, so non-positive entries never pass), else 0; x is [A, S, N] contiguous.
+template <typename T>
+__global__ void __launch_bounds__(256)
+threshold_mask_kernel(const T* __restrict__ x, const float* __restrict__ thr, long long rows, long long S, long long N,
+                      T* __restrict__ out) {
+  constexpr int V = Vec<T>::N;
+  const bool vec_ok = (N % V == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0) && (reinterpret_cast<uintptr_t>(out) % 16 == 0);
+  const long long chunk = 256LL * V;
+  const long long chunks_per_row = (N + chunk - 1) / chunk;
+  for (long long item = blockIdx.x; item < rows * chunks_per_row; item += gridDim.x) {
+    const long long r = item / chunks_per_row, ch = item - r * chunks_per_row;
+    const float t = thr[r % S];
+    const long long e = ch * chunk + (long long)threadIdx.x * V;
+    if (e >= N) continue;
+    const T* src = x + r * N + e;
+    T* dst = out + r * N + e;
+    if (vec_ok) {
+      if constexpr (sizeof(T) == 4) {
+        float4 v = __ldcs(reinterpret_cast<const float4*>(src));
+        v.x = v.x >= t ? v.x : 0.f; v.y = v.y >= t ? v.y : 0.f; v.z = v.z >= t ? v.z : 0.f; v.w = v.w >= t ? v.w : 0.f;
+        __stcs(reinterpret_cast<float4*>(dst), v);
+      } else {
+        uint4 u = __ldcs(reinterpret_cast<const uint4*>(src));
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float2 f = __bfloat1622float2(h[i]);
+          f.x = f.x >= t ? f.x : 0.f;
+          f.y = f.y >= t ? f.y : 0.f;
+          h[i] = __floats2bfloat162_rn(f.x, f.y);
+        }
+        __stcs(reinterpret_cast<uint4*>(dst), u);
+      }
+    } else {
+      for (int i = 0; i < V && e + i < N; ++i) {
+        const float f = to_float_any(src[i]);
+        dst[i] = f >= t ? src[i] : from_float_any<T>(0.f);
+      }
     }
   }
 }
@@ -324,6 +375,18 @@ int radix_pick_launch(const unsigned* hist, int nbins, long long k, const long l
                       float* thr, cudaStream_t stream) {
   if (nbins <= 0 || nbins > 65536 || (level == 1 && sel_in == nullptr)) return (int)cudaErrorInvalidValue;
   radix_pick_kernel<<<1, 1024, 0, stream>>>(hist, nbins, k, sel_in, level, sel_out, thr);
+  return (int)cudaGetLastError();
+}
+
+int threshold_mask_launch(int dtype, const void* x, const float* thr, long long A, long long S, long long N, void* out,
+                          cudaStream_t stream) {
+  const long long rows = A * S;
+  if (rows <= 0 || N <= 0) return 0;
+  if (dtype == 0)
+    threshold_mask_kernel<float><<<148 * 8, 256, 0, stream>>>(static_cast<const float*>(x), thr, rows, S, N, static_cast<float*>(out));
+  else
+    threshold_mask_kernel<__nv_bfloat16><<<148 * 8, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), thr, rows, S, N,
+                                                                     static_cast<__nv_bfloat16*>(out));
   return (int)cudaGetLastError();
 }
 

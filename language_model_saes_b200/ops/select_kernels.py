@@ -109,12 +109,22 @@ def positive_topk(x: torch.Tensor, k: int, dims: Sequence[int], group=None) -> t
         A *= a_
     N = xc.numel() // (A * S)
     thr = positive_thresholds(xc.detach().view(A, S, N), k, group)
-    shape = [1] * x.ndim
-    for d_ in range(i, j):
-        shape[d_] = x.shape[d_]
-    with torch.no_grad():
-        mask = (xc.detach() >= thr.view(shape).to(xc.dtype)) & (xc.detach() > 0)
-    return xc * mask.to(xc.dtype)
+    return _ThresholdMask.apply(xc, thr, A, S, N)
+
+
+class _ThresholdMask(torch.autograd.Function):
+    """``where(x >= thr[segment], x, 0)`` in one streaming pass; the gradient passes where the output is non-zero."""
+
+    @staticmethod
+    def forward(ctx, x, thr, A, S, N):
+        out = K._ext().threshold_mask(x.detach(), thr, A, S, N)
+        ctx.save_for_backward(out)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad):
+        (out,) = ctx.saved_tensors
+        return grad * (out != 0).to(grad.dtype), None, None, None, None
 
 
 # ---- dense rows -> padded sparse ---------------------------------------------------------------------
