@@ -264,7 +264,8 @@ def run_ours(args):
                     # every rank copies 1/N of the activation rows (then NVLink all-gather) and the whole token-id vector
                     "h2d_bytes_per_step": BATCH * D_MODEL * 2 + world * BATCH * 8, "d2h_bytes_per_step": 4 * world,
                     "api": "Trainer.fit(sae, stream of pinned host batches): copy of batch i+1 overlaps step i, each rank copies "
-                           "1/N of the rows over PCIe and all-gathers them over NVLink, loss read back every step on every rank"},
+                           "1/N of the rows over PCIe and all-gathers them over NVLink; the loss of every step is copied to pinned host memory "
+                           "on every rank and read one step later, so the host runs one step ahead of the device"},
             "gpu_launches": launches, "final_loss": final_loss, "impl": "ours", "package": lm.__name__,
         })  # fmt: skip
     if world > 1:

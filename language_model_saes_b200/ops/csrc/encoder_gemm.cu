@@ -4,7 +4,7 @@
 //
 // with two optional epilogues that run while the next tile's MMAs are in flight:
 //   * WRITE_H : store H as bf16 (the "hidden_pre" tensor of the reference encoder,
-//               models/sae.py:323-331 in the reference project);
+//               models/sae.py:323-331 in the reference project); with a gate and no top-k, H * gate[n] is stored;
 //   * TOPK    : keep, per row, the k largest *gated* values g = H * gate[n] (gate = decoder row norm when
 //               sparsity_include_decoder_norm is set, models/sae.py:333-341) that are > 0, without ever
 //               writing the dense pre-activation matrix. Each CTA sweeps a contiguous range of N-tiles for
@@ -313,6 +313,11 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           }
         }
         if constexpr (WRITE_H && !TOPK) {
+          // plain store variants: an optional per-column gate (decoder row norm) is applied to the stored value
+          if (p.gate != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) if (full_chunk || c0 + j < p.N) v[j] *= __ldg(p.gate + c0 + j);
+          }
           if (p.red_world > 0) {
             // reduce-scatter epilogue: add this 32-column piece into the slab of the rank that owns the columns
             if (row_ok && full_chunk) {

@@ -244,7 +244,10 @@ constexpr int RC_THREADS = 256;
 template <typename T>
 __global__ void __launch_bounds__(RC_THREADS)
 row_compact_kernel(const T* __restrict__ x, int B, long long N, int cap, int* __restrict__ idx, float* __restrict__ val,
-                   int* __restrict__ nnz) {
+                   int* __restrict__ nnz, const float* __restrict__ thr, const float* __restrict__ col_div) {
+  // with thr: an entry is kept when x >= *thr (thr > 0) instead of x != 0; with col_div: the stored value is
+  // x / col_div[column] (gated pre-activation back to the activation)
+  const float t = thr != nullptr ? *thr : 0.0f;
   __shared__ int s_warp[RC_THREADS / 32];
   __shared__ int s_base;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -256,7 +259,7 @@ row_compact_kernel(const T* __restrict__ x, int B, long long N, int cap, int* __
     for (long long c0 = 0; c0 < N; c0 += RC_THREADS) {
       const long long c = c0 + threadIdx.x;
       const float v = c < N ? to_float<T>(xr[c]) : 0.0f;
-      const bool nz = v != 0.0f;
+      const bool nz = thr != nullptr ? (v >= t) : (v != 0.0f);
       const unsigned bal = __ballot_sync(0xffffffffu, nz);
       if (lane == 0) s_warp[warp] = __popc(bal);
       __syncthreads();
@@ -272,7 +275,7 @@ row_compact_kernel(const T* __restrict__ x, int B, long long N, int cap, int* __
         const int slot = base + before + __popc(bal & ((1u << lane) - 1u));
         if (slot < cap) {
           idx[(size_t)row * cap + slot] = (int)c;
-          val[(size_t)row * cap + slot] = v;
+          val[(size_t)row * cap + slot] = col_div != nullptr ? v / col_div[c] : v;
         }
       }
       __syncthreads();
@@ -391,15 +394,15 @@ int threshold_mask_launch(int dtype, const void* x, const float* thr, long long 
 }
 
 int row_compact_launch(int dtype, const void* x, int B, long long N, int cap, int* idx, float* val, int* nnz,
-                       cudaStream_t stream) {
+                       const float* thr, const float* col_div, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (N > 2147483647LL) return (int)cudaErrorInvalidValue;
   const int blocks = B < 148 * 8 ? B : 148 * 8;
   if (dtype == 0)
-    row_compact_kernel<float><<<blocks, RC_THREADS, 0, stream>>>(static_cast<const float*>(x), B, N, cap, idx, val, nnz);
+    row_compact_kernel<float><<<blocks, RC_THREADS, 0, stream>>>(static_cast<const float*>(x), B, N, cap, idx, val, nnz, thr, col_div);
   else
     row_compact_kernel<__nv_bfloat16>
-        <<<blocks, RC_THREADS, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), B, N, cap, idx, val, nnz);
+        <<<blocks, RC_THREADS, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), B, N, cap, idx, val, nnz, thr, col_div);
   return (int)cudaGetLastError();
 }
 

@@ -1,4 +1,4 @@
-"""One training step of a TopK sparse autoencoder as a fixed sequence of sm_100a kernels, without autograd.
+"""One training step of a TopK (or BatchTopK) sparse autoencoder as a fixed sequence of sm_100a kernels, without autograd.
 
 What it computes is the reference's step for a TopK ``SparseAutoEncoder`` trained with the MSE loss and Adam
 (trainer.py:576-671, models/sae.py:288-377, models/sparse_dictionary.py:841-886 of the reference project):
@@ -68,6 +68,7 @@ class FusedTopKSAEStep:
         self.comm = comm  # optional peer-memory communicator (parallel.symm.SymmComm) for the model group
         self.betas, self.eps = betas, eps
         self.use_gate = cfg.sparsity_include_decoder_norm
+        self.batch_level = cfg.act_fn == "batchtopk"
         self.WE = sae.W_E.data.t()
         self.WD = sae.W_D.data
         assert self.WE.is_contiguous() and self.WD.is_contiguous(), "weights must be feature-major and contiguous"
@@ -123,7 +124,7 @@ class FusedTopKSAEStep:
         if type(sae) is not SparseAutoEncoder:
             return False, "model is not a plain SparseAutoEncoder"
         checks = [
-            (cfg.act_fn == "topk", "activation is not topk"),
+            (cfg.act_fn in ("topk", "batchtopk"), "activation is neither topk nor batchtopk"),
             (not cfg.use_glu_encoder, "GLU encoder"),
             (sae.W_D.is_cuda, "not on a CUDA device"),
             (cfg.dtype == torch.float32, "parameters are not fp32"),
@@ -138,6 +139,7 @@ class FusedTopKSAEStep:
                 (not trainer_cfg.lp_coefficient, "lp loss"),
                 (not trainer_cfg.auxk_coefficient or (mesh_dim_size(sae.device_mesh, "model") == 1 and mesh_dim_size(sae.device_mesh, "data") == 1),
                  "aux-k loss under a device mesh"),
+                (not trainer_cfg.auxk_coefficient or cfg.act_fn == "topk", "aux-k loss with a batch-level top-k"),
                 (trainer_cfg.optimizer_class == "adam", "optimizer is not adam"),
                 (trainer_cfg.amp_dtype == torch.bfloat16, "amp dtype is not bf16"),
                 (trainer_cfg.gradient_accumulation_steps == 1, "gradient accumulation"),
@@ -220,6 +222,8 @@ class FusedTopKSAEStep:
         """Sparse codes (idx, act) [B, k] of bf16 inputs ``x`` [B, d] over this rank's features; under
         feature sharding only globally selected entries survive."""
         gate = self.dec_norm if self.use_gate else None
+        if self.batch_level:
+            return self._encode_batch_level(x, k, gate)
         chunked = _in_step and len(self.chunks) > 1 and k <= 64 and x.is_cuda
         if not chunked:
             self.join()
@@ -249,6 +253,20 @@ class FusedTopKSAEStep:
             all_i = all_i.view(self.tp, B, k).permute(1, 0, 2).reshape(B, self.tp * k).contiguous()
         return K.topk_merge(all_g, all_i, k, gate, own=(self.tp_rank * k, (self.tp_rank + 1) * k))
 
+    def _encode_batch_level(self, x: torch.Tensor, k: int, gate) -> tuple[torch.Tensor, torch.Tensor]:
+        """BatchTopK: keep the ``k * batch`` largest gated pre-activations of the whole batch (over all feature shards)
+        instead of ``k`` per token (models/sparse_dictionary.py:775-788 of the reference project). The GEMM stores the
+        gated pre-activations in bf16, a radix select over their bit patterns finds the threshold (shards add their
+        histograms), and one compaction pass turns the survivors into padded code lists: the rows' code counts differ,
+        the list width is the largest count (one host read per step)."""
+        from . import select_kernels as S
+
+        self.join()
+        G = K.encoder_hidden(x, self.WE_bf16, self.bE, gate=gate)
+        B = x.shape[0]
+        thr = S.positive_thresholds(G.view(1, 1, -1), k * B, self.tp_group if self.tp > 1 else None)
+        return S.threshold_rows_to_sparse(G, thr, gate, width_group=self.dp_group if self.dp > 1 else None)
+
     def step(
         self,
         x: torch.Tensor,
@@ -269,7 +287,7 @@ class FusedTopKSAEStep:
         B = x.shape[0]
         n_global = n_tokens_global if n_tokens_global is not None else B * self.dp
         grad_scale = 2.0 / n_global
-        use_comm = self.comm is not None and B == self.comm.B and k <= self.comm.k_max
+        use_comm = self.comm is not None and B == self.comm.B and k <= self.comm.k_max and not self.batch_level
         if use_comm:
             self.comm.next_epoch()
         overlap = len(self.chunks) > 1 and k <= 64 and grad_mul is None and not want_grad_norm

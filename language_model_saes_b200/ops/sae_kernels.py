@@ -150,13 +150,16 @@ def _pair_bit(pair: bool | None) -> int:
     return 8 if use else 0
 
 
-def encoder_hidden(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, pair: bool | None = None) -> torch.Tensor:
-    """H = x @ w.T + bias as bf16 via the tcgen05 GEMM (x [M,K] bf16, w [N,K] bf16, bias fp32)."""
+def encoder_hidden(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, pair: bool | None = None,
+                   gate: torch.Tensor | None = None) -> torch.Tensor:  # fmt: skip
+    """H = x @ w.T + bias as bf16 via the tcgen05 GEMM (x [M,K] bf16, w [N,K] bf16, bias fp32); with ``gate`` (fp32 [N])
+    the stored value is ``H * gate`` (gated pre-activations)."""
     if not x.is_cuda:
-        return ref_hidden(x, w, bias).to(torch.bfloat16)
+        h = ref_hidden(x, w, bias)
+        return (h * gate if gate is not None else h).to(torch.bfloat16)
     M, N = x.shape[0], w.shape[0]
     H = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
-    _ext().encoder_gemm(x, w, bias, None, 1 | _pair_bit(pair), 0, choose_splits(M, N), H, None, None, status_buffer(x.device), 0, False)
+    _ext().encoder_gemm(x, w, bias, gate, 1 | _pair_bit(pair), 0, choose_splits(M, N), H, None, None, status_buffer(x.device), 0, False)
     return H
 
 

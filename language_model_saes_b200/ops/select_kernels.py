@@ -153,11 +153,32 @@ def dense_rows_to_sparse(acts: torch.Tensor, cap: int | None = None) -> tuple[to
     B = acts.shape[0]
     nnz = torch.empty(B, dtype=torch.int32, device=acts.device)
     if cap is None:
-        ext.row_compact(acts, None, None, nnz)
+        ext.row_compact(acts, None, None, nnz, None, None)
         cap = max(8, -(-int(nnz.max()) // 8) * 8)
     idx = torch.empty(B, cap, dtype=torch.int32, device=acts.device)
     val = torch.empty(B, cap, dtype=torch.float32, device=acts.device)
-    ext.row_compact(acts, idx, val, nnz)
+    ext.row_compact(acts, idx, val, nnz, None, None)
+    return idx, val
+
+
+@torch.no_grad()
+def threshold_rows_to_sparse(g: torch.Tensor, thr: torch.Tensor, col_div: torch.Tensor | None = None,
+                             width_group=None) -> tuple[torch.Tensor, torch.Tensor]:  # fmt: skip
+    """Entries of ``g [B, N]`` that reach the (positive) threshold ``thr`` (one-element fp32 tensor) as padded sparse lists,
+    values divided by ``col_div[column]`` when given: the codes of a batch-level top-k straight from the gated
+    pre-activations, without a masked dense tensor in between."""
+    ext = K._ext()
+    g = g.contiguous()
+    B = g.shape[0]
+    nnz = torch.empty(B, dtype=torch.int32, device=g.device)
+    ext.row_compact(g, None, None, nnz, thr, None)
+    widest = nnz.max()
+    if width_group is not None and dist.get_world_size(width_group) > 1:
+        dist.all_reduce(widest, op=dist.ReduceOp.MAX, group=width_group)  # ranks that exchange their lists need one width
+    cap = max(8, -(-int(widest) // 8) * 8)
+    idx = torch.empty(B, cap, dtype=torch.int32, device=g.device)
+    val = torch.empty(B, cap, dtype=torch.float32, device=g.device)
+    ext.row_compact(g, idx, val, nnz, thr, col_div)
     return idx, val
 
 

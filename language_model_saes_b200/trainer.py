@@ -187,9 +187,52 @@ class _DevicePrefetcher:
         return batch
 
 
+class _LossReader:
+    """Reads the loss of every logged step back to the host without stalling the launch of the next step: the value is
+    copied into one of two pinned scalars on the producing stream and picked up one step later, when its copy has long
+    finished, so the host stays one step ahead of the device instead of waiting for each step to end. On CPU tensors it
+    is an ordinary read."""
+
+    def __init__(self):
+        self._slots: list[tuple[Tensor, Any] | None] = [None, None]
+        self._pinned: list[Tensor | None] = [None, None]
+        self._n = 0
+
+    def _take(self, slot: int) -> float | None:
+        entry = self._slots[slot]
+        if entry is None:
+            return None
+        host, ev = entry
+        ev.synchronize()
+        self._slots[slot] = None
+        return float(host)
+
+    def push(self, loss: Tensor) -> float | None:
+        """Queue ``loss`` and return the most recent value whose copy has completed (None on the first call)."""
+        if not loss.is_cuda:
+            return float(loss)
+        slot = self._n & 1
+        self._n += 1
+        if self._pinned[slot] is None:
+            self._pinned[slot] = torch.empty((), dtype=torch.float32, pin_memory=True)
+        host = self._pinned[slot]
+        host.copy_(loss.detach().float().reshape(()), non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._slots[slot] = (host, ev)
+        return self._take(slot ^ 1)
+
+    def flush(self) -> float | None:
+        """The last queued value (waits for it)."""
+        vals = [self._take((self._n + i) & 1) for i in range(2)]
+        vals = [v for v in vals if v is not None]
+        return vals[-1] if vals else None
+
+
 class Trainer:
     def __init__(self, cfg: TrainerConfig):
         self.cfg = cfg
+        self.last_loss: float | None = None  # most recent loss value read back by fit()
         self.checkpoint_thresholds: list[int] = []
         self.total_training_steps: int = 0
         self.lr_warm_up_steps: int = 0
@@ -623,6 +666,7 @@ class Trainer:
         bar.update(self.cur_step)
         dp = mesh_dim_size(sae.device_mesh, "data")
         accum = max(1, self.cfg.gradient_accumulation_steps)
+        loss_reader = _LossReader()
         try:
             while True:
                 with timer.time("training_iteration"):
@@ -634,7 +678,9 @@ class Trainer:
                     else:
                         loss = self._generic_iteration(sae, batch, accum)
                     if (self.cur_step + 1) % self.cfg.log_frequency == 0:
-                        bar.set_description(f"loss: {float(loss):.2f}")
+                        shown = loss_reader.push(loss)
+                        if shown is not None:
+                            bar.set_description(f"loss: {shown:.2f}")
                     if eval_fn is not None and (self.cur_step + 1) % self.cfg.eval_frequency == 0:
                         with timer.time("evaluation"):
                             if self.fused is not None:
@@ -657,6 +703,9 @@ class Trainer:
             logger.error(f"Training failed: {e}")
             raise
         finally:
+            last = loss_reader.flush()
+            if last is not None:
+                self.last_loss = last
             bar.close()
             if self.fused is not None:
                 self.fused.join()  # the last update may still be running on its own stream
