@@ -544,7 +544,10 @@ Tensor threshold_mask(const Tensor& x, const Tensor& thr, int64_t A, int64_t S, 
 
 // x [B, N] -> idx / val [B, cap] (both optional: count only) and nnz [B] (optional)
 void row_compact(const Tensor& x, const c10::optional<Tensor>& idx, const c10::optional<Tensor>& val,
-                 const c10::optional<Tensor>& nnz, const c10::optional<Tensor>& thr, const c10::optional<Tensor>& col_div) {
+                 const c10::optional<Tensor>& nnz, const c10::optional<Tensor>& thr, const c10::optional<Tensor>& col_div,
+                 const c10::optional<Tensor>& ties, const c10::optional<Tensor>& tie_quota) {
+  if (ties.has_value()) { CHECK_T(*ties, torch::kInt32); TORCH_CHECK(ties->numel() == x.size(0) && thr.has_value(), "ties: [B], with thr"); }
+  if (tie_quota.has_value()) { CHECK_T(*tie_quota, torch::kInt32); TORCH_CHECK(tie_quota->numel() == x.size(0) && thr.has_value(), "tie_quota: [B], with thr"); }
   if (thr.has_value()) { CHECK_T(*thr, torch::kFloat32); TORCH_CHECK(thr->numel() >= 1); }
   if (col_div.has_value()) { CHECK_T(*col_div, torch::kFloat32); TORCH_CHECK(col_div->numel() == x.size(1), "one divisor per column"); }
   TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.dim() == 2, "x must be a contiguous CUDA matrix");
@@ -563,7 +566,7 @@ void row_compact(const Tensor& x, const c10::optional<Tensor>& idx, const c10::o
   const c10::cuda::CUDAGuard guard(x.device());
   check_cuda(lmsae::row_compact_launch(dtype_code(x), x.data_ptr(), (int)x.size(0), x.size(1), cap, opt_ptr<int>(idx),
                                        opt_ptr<float>(val), opt_ptr<int>(nnz), opt_ptr<float>(thr), opt_ptr<float>(col_div),
-                                       at::cuda::getCurrentCUDAStream()),
+                                       opt_ptr<int>(ties), opt_ptr<int>(tie_quota), at::cuda::getCurrentCUDAStream()),
              "row_compact launch");
 }
 

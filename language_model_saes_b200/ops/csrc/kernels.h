@@ -128,7 +128,7 @@ int radix_pick_launch(const unsigned* hist, int nbins, long long k, const long l
 int threshold_mask_launch(int dtype, const void* x, const float* thr, long long A, long long S, long long N, void* out,
                           cudaStream_t stream);
 int row_compact_launch(int dtype, const void* x, int B, long long N, int cap, int* idx, float* val, int* nnz,
-                       const float* thr, const float* col_div, cudaStream_t stream);
+                       const float* thr, const float* col_div, int* ties, const int* tie_quota, cudaStream_t stream);
 int gather_rows_cast_launch(int in_dtype, int out_dtype, const void* src, const int* keep, const int* pos, long long n,
                             int d, void* out, long long out_rows, cudaStream_t stream);
 int exclusive_scan_launch(const int* counts, int n, int* offsets, int* block_sums_buf, cudaStream_t stream);

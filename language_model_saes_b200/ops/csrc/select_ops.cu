@@ -244,23 +244,50 @@ constexpr int RC_THREADS = 256;
 template <typename T>
 __global__ void __launch_bounds__(RC_THREADS)
 row_compact_kernel(const T* __restrict__ x, int B, long long N, int cap, int* __restrict__ idx, float* __restrict__ val,
-                   int* __restrict__ nnz, const float* __restrict__ thr, const float* __restrict__ col_div) {
-  // with thr: an entry is kept when x >= *thr (thr > 0) instead of x != 0; with col_div: the stored value is
-  // x / col_div[column] (gated pre-activation back to the activation)
+                   int* __restrict__ nnz, const float* __restrict__ thr, const float* __restrict__ col_div,
+                   int* __restrict__ ties, const int* __restrict__ tie_quota) {
+  // Without thr an entry is kept when x != 0. With thr (> 0): entries above *thr are kept; entries EQUAL to it are
+  // kept too, unless tie_quota is given, in which case only the first tie_quota[row] of them (in column order) are:
+  // that is how a caller keeps an exact number of entries when the threshold value repeats. A counting call
+  // (idx == nullptr) with `ties` reports the two kinds separately: nnz = entries above, ties = entries equal.
+  // With col_div the stored value is x / col_div[column] (gated pre-activation back to the activation).
   const float t = thr != nullptr ? *thr : 0.0f;
+  const bool split_ties = thr != nullptr && (ties != nullptr || tie_quota != nullptr);
   __shared__ int s_warp[RC_THREADS / 32];
-  __shared__ int s_base;
+  __shared__ int s_warp_t[RC_THREADS / 32];
+  __shared__ int s_base, s_tie_base;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const unsigned lt = (1u << lane) - 1u;
   for (int row = blockIdx.x; row < B; row += gridDim.x) {
     __syncthreads();
-    if (threadIdx.x == 0) s_base = 0;
+    if (threadIdx.x == 0) { s_base = 0; s_tie_base = 0; }
     __syncthreads();
+    const int quota = tie_quota != nullptr ? tie_quota[row] : 0x7fffffff;
     const T* xr = x + (size_t)row * N;
     for (long long c0 = 0; c0 < N; c0 += RC_THREADS) {
       const long long c = c0 + threadIdx.x;
       const float v = c < N ? to_float<T>(xr[c]) : 0.0f;
-      const bool nz = thr != nullptr ? (v >= t) : (v != 0.0f);
-      const unsigned bal = __ballot_sync(0xffffffffu, nz);
+      bool keep;
+      int tie_total = 0;
+      if (split_ties) {
+        const bool is_tie = c < N && v == t;
+        const unsigned bt = __ballot_sync(0xffffffffu, is_tie);
+        if (lane == 0) s_warp_t[warp] = __popc(bt);
+        __syncthreads();
+        int tie_before = 0;
+#pragma unroll
+        for (int w = 0; w < RC_THREADS / 32; ++w) {
+          const int cnt = s_warp_t[w];
+          if (w < warp) tie_before += cnt;
+          tie_total += cnt;
+        }
+        const int tie_rank = s_tie_base + tie_before + __popc(bt & lt);
+        // a counting call keeps the two kinds apart: `keep` then means "above the threshold"
+        keep = (v > t) || (idx != nullptr && is_tie && tie_rank < quota);
+      } else {
+        keep = thr != nullptr ? (v >= t) : (v != 0.0f);
+      }
+      const unsigned bal = __ballot_sync(0xffffffffu, keep);
       if (lane == 0) s_warp[warp] = __popc(bal);
       __syncthreads();
       int before = 0, total = 0;
@@ -271,19 +298,25 @@ row_compact_kernel(const T* __restrict__ x, int B, long long N, int cap, int* __
         total += cnt;
       }
       const int base = s_base;
-      if (nz && idx != nullptr) {
-        const int slot = base + before + __popc(bal & ((1u << lane) - 1u));
+      if (keep && idx != nullptr) {
+        const int slot = base + before + __popc(bal & lt);
         if (slot < cap) {
           idx[(size_t)row * cap + slot] = (int)c;
           val[(size_t)row * cap + slot] = col_div != nullptr ? v / col_div[c] : v;
         }
       }
       __syncthreads();
-      if (threadIdx.x == 0) s_base = base + total;
+      if (threadIdx.x == 0) {
+        s_base = base + total;
+        s_tie_base += tie_total;
+      }
     }
     __syncthreads();
     const int count = s_base;
-    if (threadIdx.x == 0 && nnz != nullptr) nnz[row] = count;
+    if (threadIdx.x == 0) {
+      if (nnz != nullptr) nnz[row] = count;
+      if (ties != nullptr) ties[row] = s_tie_base;
+    }
     if (idx != nullptr) {
       for (int j = count + threadIdx.x; j < cap; j += RC_THREADS) {
         idx[(size_t)row * cap + j] = -1;
@@ -394,15 +427,17 @@ int threshold_mask_launch(int dtype, const void* x, const float* thr, long long 
 }
 
 int row_compact_launch(int dtype, const void* x, int B, long long N, int cap, int* idx, float* val, int* nnz,
-                       const float* thr, const float* col_div, cudaStream_t stream) {
+                       const float* thr, const float* col_div, int* ties, const int* tie_quota, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (N > 2147483647LL) return (int)cudaErrorInvalidValue;
   const int blocks = B < 148 * 8 ? B : 148 * 8;
   if (dtype == 0)
-    row_compact_kernel<float><<<blocks, RC_THREADS, 0, stream>>>(static_cast<const float*>(x), B, N, cap, idx, val, nnz, thr, col_div);
+    row_compact_kernel<float><<<blocks, RC_THREADS, 0, stream>>>(static_cast<const float*>(x), B, N, cap, idx, val, nnz, thr, col_div, ties,
+                                                                 tie_quota);
   else
     row_compact_kernel<__nv_bfloat16>
-        <<<blocks, RC_THREADS, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), B, N, cap, idx, val, nnz, thr, col_div);
+        <<<blocks, RC_THREADS, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), B, N, cap, idx, val, nnz, thr, col_div, ties,
+                                            tie_quota);
   return (int)cudaGetLastError();
 }
 

@@ -264,8 +264,11 @@ class FusedTopKSAEStep:
         self.join()
         G = K.encoder_hidden(x, self.WE_bf16, self.bE, gate=gate)
         B = x.shape[0]
-        thr = S.positive_thresholds(G.view(1, 1, -1), k * B, self.tp_group if self.tp > 1 else None)
-        return S.threshold_rows_to_sparse(G, thr, gate, width_group=self.dp_group if self.dp > 1 else None)
+        tp_group = self.tp_group if self.tp > 1 else None
+        thr, n_ties = S.positive_thresholds(G.view(1, 1, -1), k * B, tp_group, return_remaining=True)
+        # exactly k * B codes: of the entries equal to the (bf16) threshold only as many as the selection still needs
+        return S.threshold_rows_to_sparse(G, thr, gate, width_group=self.dp_group if self.dp > 1 else None,
+                                          n_ties=n_ties, tie_group=tp_group)
 
     def step(
         self,

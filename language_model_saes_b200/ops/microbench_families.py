@@ -22,7 +22,8 @@ from .microbench import _timeit
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default="all", help="all | attn | batchtopk | clt | compact | headsum")
+    ap.add_argument("--case", default="all", help="all | attn | attn_fwd | batchtopk | clt | compact | headsum")
+    ap.add_argument("--attn-shape", default="4,1024,64,64,128", help="batch,seq,heads,d_qk,d_v of the attention cases")
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args(argv)
@@ -35,9 +36,9 @@ def main(argv=None):
                "speedup": round(ref[0] / ours[0], 2), **extra}  # fmt: skip
         print(json.dumps(rec), flush=True)
 
-    if want("attn"):
-        # low-rank sparse attention at d_sae 8192: 64 QK heads of width 64, OV groups of 128, 4 x 1024 tokens
-        b, s, h, dqk, dv = 4, 1024, 64, 64, 128
+    if want("attn") or a.case == "attn_fwd":
+        # default: low-rank sparse attention at d_sae 8192: 64 QK heads of width 64, OV groups of 128, 4 x 1024 tokens
+        b, s, h, dqk, dv = (int(t) for t in a.attn_shape.split(","))
         q, k = (torch.randn(b, s, h, dqk, device=dev, dtype=torch.bfloat16).requires_grad_() for _ in range(2))
         v = torch.randn(b, s, h, dv, device=dev, dtype=torch.bfloat16).requires_grad_()
         do = torch.randn(b, s, h, dv, device=dev, dtype=torch.bfloat16)
@@ -56,10 +57,13 @@ def main(argv=None):
         with torch.no_grad():
             t_o = _timeit(lambda: A.causal_attention_fwd(q, k, v, scale), a.iters, a.warmup, flush)
             t_r = _timeit(sdpa, a.iters, a.warmup, flush)
-        report("attention_fwd_b4_s1024_h64_dqk64_dv128", t_o, t_r, tflops_ours=round(flops_fwd / t_o[0] / 1e9, 1))
-        t_o = _timeit(lambda: train(lambda: A.causal_attention(q, k, v, scale)), a.iters, a.warmup, flush)
-        t_r = _timeit(lambda: train(sdpa), a.iters, a.warmup, flush)
-        report("attention_fwd_bwd_b4_s1024_h64_dqk64_dv128", t_o, t_r, tflops_ours=round(3.5 * flops_fwd / t_o[0] / 1e9, 1))
+        tag = f"b{b}_s{s}_h{h}_dqk{dqk}_dv{dv}"
+        report(f"attention_fwd_{tag}", t_o, t_r, tflops_ours=round(flops_fwd / t_o[0] / 1e9, 1),
+               tflops_reference_path=round(flops_fwd / t_r[0] / 1e9, 1))  # fmt: skip
+        if a.case != "attn_fwd":
+            t_o = _timeit(lambda: train(lambda: A.causal_attention(q, k, v, scale)), a.iters, a.warmup, flush)
+            t_r = _timeit(lambda: train(sdpa), a.iters, a.warmup, flush)
+            report(f"attention_fwd_bwd_{tag}", t_o, t_r, tflops_ours=round(3.5 * flops_fwd / t_o[0] / 1e9, 1))
         K.check_status(dev)
         del q, k, v, do
 

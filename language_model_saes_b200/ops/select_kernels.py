@@ -37,9 +37,10 @@ def _kernel_ok(x: torch.Tensor) -> bool:
 
 
 @torch.no_grad()
-def positive_thresholds(x3: torch.Tensor, k: int, group=None) -> torch.Tensor:
+def positive_thresholds(x3: torch.Tensor, k: int, group=None, return_remaining: bool = False):
     """``x3``: contiguous ``[A, S, N]``. Returns fp32 ``[S]``: for every segment ``s`` the k-th largest positive value of
-    ``x3[:, s, :]``, taken over the union of all ranks of ``group`` when one is given."""
+    ``x3[:, s, :]``, taken over the union of all ranks of ``group`` when one is given. ``return_remaining`` (GPU kernels
+    only) also returns int64 ``[S]``: how many of the entries equal to the threshold the selection of ``k`` includes."""
     A, S, N = x3.shape
     world = dist.get_world_size(group) if group is not None else 1
     if not _kernel_ok(x3):
@@ -62,6 +63,7 @@ def positive_thresholds(x3: torch.Tensor, k: int, group=None) -> torch.Tensor:
     sel0 = torch.zeros(4, dtype=torch.int64, device=dev)
     sel1 = torch.zeros(4, dtype=torch.int64, device=dev)
     thr = torch.empty(S, dtype=torch.float32, device=dev)
+    remaining = torch.zeros(S, dtype=torch.int64, device=dev)
     half = x3.dtype == torch.bfloat16  # 16-bit data: the first level already resolves the value
     for s in range(S):
         hist_hi.zero_()
@@ -75,7 +77,8 @@ def positive_thresholds(x3: torch.Tensor, k: int, group=None) -> torch.Tensor:
             if world > 1:
                 dist.all_reduce(hist_lo, group=group)
             ext.radix_pick(hist_lo, 65536, 0, sel0, 1, sel1, thr[s : s + 1])
-    return thr
+        remaining[s : s + 1].copy_((sel0 if half else sel1)[1:2])
+    return (thr, remaining) if return_remaining else thr
 
 
 def _middle_block(ndim: int, dims: Sequence[int]) -> tuple[int, int] | None:
@@ -153,32 +156,51 @@ def dense_rows_to_sparse(acts: torch.Tensor, cap: int | None = None) -> tuple[to
     B = acts.shape[0]
     nnz = torch.empty(B, dtype=torch.int32, device=acts.device)
     if cap is None:
-        ext.row_compact(acts, None, None, nnz, None, None)
+        ext.row_compact(acts, None, None, nnz, None, None, None, None)
         cap = max(8, -(-int(nnz.max()) // 8) * 8)
     idx = torch.empty(B, cap, dtype=torch.int32, device=acts.device)
     val = torch.empty(B, cap, dtype=torch.float32, device=acts.device)
-    ext.row_compact(acts, idx, val, nnz, None, None)
+    ext.row_compact(acts, idx, val, nnz, None, None, None, None)
     return idx, val
 
 
 @torch.no_grad()
-def threshold_rows_to_sparse(g: torch.Tensor, thr: torch.Tensor, col_div: torch.Tensor | None = None,
-                             width_group=None) -> tuple[torch.Tensor, torch.Tensor]:  # fmt: skip
+def threshold_rows_to_sparse(g: torch.Tensor, thr: torch.Tensor, col_div: torch.Tensor | None = None, width_group=None,
+                             n_ties: torch.Tensor | None = None, tie_group=None) -> tuple[torch.Tensor, torch.Tensor]:  # fmt: skip
     """Entries of ``g [B, N]`` that reach the (positive) threshold ``thr`` (one-element fp32 tensor) as padded sparse lists,
     values divided by ``col_div[column]`` when given: the codes of a batch-level top-k straight from the gated
-    pre-activations, without a masked dense tensor in between."""
+    pre-activations, without a masked dense tensor in between.
+
+    ``n_ties`` (one-element integer tensor: how many entries EQUAL to the threshold belong to the selection, as
+    ``positive_thresholds(..., return_remaining=True)`` reports it) makes the number of codes exact when the threshold
+    value repeats (16-bit data): ties are granted in (rank of ``tie_group``, row, column) order until the count is
+    used up. Without it every tie is kept."""
     ext = K._ext()
     g = g.contiguous()
     B = g.shape[0]
     nnz = torch.empty(B, dtype=torch.int32, device=g.device)
-    ext.row_compact(g, None, None, nnz, thr, None)
-    widest = nnz.max()
+    quota = None
+    if n_ties is None:
+        ext.row_compact(g, None, None, nnz, thr, None, None, None)
+        widest = nnz.max()
+    else:
+        ties = torch.empty(B, dtype=torch.int32, device=g.device)
+        ext.row_compact(g, None, None, nnz, thr, None, ties, None)
+        budget = n_ties.reshape(()).to(torch.int64)
+        if tie_group is not None and dist.get_world_size(tie_group) > 1:
+            mine = ties.sum(dtype=torch.int64).reshape(1)
+            every = [torch.empty_like(mine) for _ in range(dist.get_world_size(tie_group))]
+            dist.all_gather(every, mine, group=tie_group)
+            budget = budget - torch.cat(every)[: dist.get_rank(tie_group)].sum()  # earlier ranks are served first
+        before = torch.cumsum(ties, 0, dtype=torch.int64) - ties
+        quota = (budget - before).clamp(min=0).minimum(ties.to(torch.int64)).to(torch.int32)
+        widest = (nnz + quota).max()
     if width_group is not None and dist.get_world_size(width_group) > 1:
         dist.all_reduce(widest, op=dist.ReduceOp.MAX, group=width_group)  # ranks that exchange their lists need one width
     cap = max(8, -(-int(widest) // 8) * 8)
     idx = torch.empty(B, cap, dtype=torch.int32, device=g.device)
     val = torch.empty(B, cap, dtype=torch.float32, device=g.device)
-    ext.row_compact(g, idx, val, nnz, thr, col_div)
+    ext.row_compact(g, idx, val, nnz, thr, col_div, None, quota)
     return idx, val
 
 

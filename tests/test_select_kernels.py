@@ -98,3 +98,29 @@ def test_masked_row_compaction(src_dtype, out_dtype):
     got = S.compact_rows(src, keep, out_dtype)
     assert torch.equal(got, src[keep].to(out_dtype))
     assert S.compact_rows(src, torch.zeros(n, dtype=torch.bool, device="cuda"), out_dtype).shape == (0, d)
+
+
+@pytest.mark.gpu
+def test_threshold_compaction_rations_ties_to_an_exact_count():
+    torch.manual_seed(4)
+    B, N, k = 64, 4096, 16
+    g = torch.randn(B, N, device="cuda").relu_().to(torch.bfloat16)  # 16-bit data: the k-th largest value repeats
+    thr, rem = S.positive_thresholds(g.view(1, 1, -1), k * B, return_remaining=True)
+    n_above, n_equal = int((g.float() > thr).sum()), int((g.float() == thr).sum())
+    assert n_equal > 1 and n_above < k * B <= n_above + n_equal and int(rem) == k * B - n_above
+    idx_all, _ = S.threshold_rows_to_sparse(g, thr)
+    assert int((idx_all >= 0).sum()) == n_above + n_equal  # without a budget every tie is kept
+    div = torch.rand(N, device="cuda") + 0.5
+    idx, val = S.threshold_rows_to_sparse(g, thr, div, n_ties=rem)
+    assert int((idx >= 0).sum()) == k * B
+    rows = torch.arange(B, device="cuda")[:, None].expand_as(idx)[idx >= 0]
+    cols = idx[idx >= 0].long()
+    assert bool((g[rows, cols].float() >= thr).all())
+    assert torch.allclose(val[idx >= 0], g[rows, cols].float() / div[cols])
+    strict = g.float() > thr
+    got = torch.zeros_like(strict)
+    got[rows, cols] = True
+    assert bool((got | ~strict).all())  # everything above the threshold is there; the rest of the budget went to ties
+    for r in range(B):  # ascending columns within a row
+        c = idx[r][idx[r] >= 0]
+        assert bool((c[1:] > c[:-1]).all())
