@@ -38,7 +38,8 @@ struct AttnSmem {
   static constexpr int kVBytes = 2 * kVAtomBytes;
   static constexpr int kPOff = kVOff + kVBytes;
   static constexpr int kPBytes = 2 * ATOM_BYTES_128;
-  static constexpr int kBarOff = kPOff + kPBytes;
+  static constexpr int kXchOff = kPOff + kPBytes;      // float [2][2][128]: row statistics exchanged between column halves
+  static constexpr int kBarOff = kXchOff + 2 * 2 * 128 * 4;
   static constexpr int kTmemPtrOff = kBarOff + 8 * 8;
   static constexpr int kAbortOff = kTmemPtrOff + 4;
   static constexpr int kTotal = kAbortOff + 4;
@@ -52,19 +53,22 @@ __device__ __forceinline__ uint32_t sw128_chunk_off(int row, int chunk) {
 
 }  // namespace
 
-constexpr int FWD_THREADS = 160;       // warps 0-3: one query row per thread; warp 4: TMA + MMA issue
+constexpr int FWD_ROW_THREADS = 256;   // warps 0-7: warp w works on query rows 32 (w % 4) .. + 31, key columns 64 (w / 4) .. + 63
+constexpr int FWD_THREADS = 288;       // + warp 8: TMA + MMA issue
 constexpr float kRescaleSlack = 8.0f;  // log2 units the running reference may lag behind the true row maximum
 
-// Roles and hand-offs (all through mbarriers; the loop has no CTA-wide barrier):
+// Roles and hand-offs (all through mbarriers and 64-thread named barriers; the loop has no CTA-wide barrier):
 //   issuer   K(kb+1) load as soon as S(kb) has been computed; S(kb+1) as soon as the rows hold S(kb) in registers, so the
 //            tensor core works on the next scores while the rows do their exponentials; P V (kb) when P(kb) is written;
 //            V(kb+1) load when P V (kb) has completed.
-//   rows     S(kb) TMEM -> 128 registers (one wait), release S; block maximum; the output accumulator stays in TMEM and is
-//            only rescaled when the maximum has grown by more than 2^8 since the reference was set (rarely after the
-//            first blocks), which keeps p <= 256 and the sums well inside fp32 / bf16 range; exponentials -> P (bf16,
-//            swizzled K-major) -> signal.
+//   rows     two threads per query row, one per half of the 128 keys of a block (eight warps keep the issue slots of the
+//            SM busy where four leave them idle half of the time): S(kb) TMEM -> 64 registers, release S; the two halves
+//            exchange their maxima through shared memory; the output accumulator stays in TMEM and is only rescaled when
+//            the maximum has grown by more than 2^8 since the reference was set (rarely after the first blocks), which
+//            keeps p <= 256 and the sums well inside fp32 / bf16 range; exponentials -> P (bf16, swizzled K-major; a
+//            half is exactly one 64-key atom) -> signal.
 template <int DQK, int DV>
-__global__ void __launch_bounds__(FWD_THREADS, 2)
+__global__ void __maxnreg__(112)  // 288 threads x 112 registers: two CTAs per SM
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_vt, const AttnParams p) {
   using L = AttnSmem<DQK, DV>;
@@ -96,13 +100,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     mbar_init(bar_k, 1);
     mbar_init(bar_v, 1);
     mbar_init(bar_s_full, 1);
-    mbar_init(bar_s_free, ATT_BM);
-    mbar_init(bar_p_full, ATT_BM);
+    mbar_init(bar_s_free, FWD_ROW_THREADS);
+    mbar_init(bar_p_full, FWD_ROW_THREADS);
     mbar_init(bar_pv_done, 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 4) {
+  if (warp == 8) {
     tmem_alloc(tmem_ptr_smem, 256);
     tmem_relinquish();
   }
@@ -113,7 +117,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const uint32_t tmem_s = tmem_base;
   const uint32_t tmem_o = tmem_base + ATT_BN;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ------------------------------------------------------------------ TMA + MMA issuer
     if (elect_one()) {
       auto load_k = [&](int kb) {
@@ -191,36 +195,48 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     }
   } else {
     // ------------------------------------------------------------------ softmax rows
-    const int row = (int)threadIdx.x;
+    const int quarter = warp & 3, half = warp >> 2, lane = (int)threadIdx.x & 31;
+    const int row = quarter * 32 + lane;
     const int qpos = q0 + row;
     const bool row_ok = qpos < p.seq;
-    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+    const uint32_t s_col = (uint32_t)(half * (ATT_BN / 2));
+    const uint32_t o_col = (uint32_t)(half * (DV / 2));
+    float* xch = reinterpret_cast<float*>(smem + L::kXchOff);  // [2 parities][2 halves][128 rows]
     const float sc = p.scale_log2;
     float m_ref = -INFINITY, l_run = 0.0f;
     bool ok = true;
     for (int kb = 0; kb < n_kblocks && ok; ++kb) {
-      const int k0 = kb * ATT_BN;
+      const int k0 = kb * ATT_BN + (int)s_col;
       const uint32_t par = kb & 1;
       // (a failed wait ends the loop for the whole warp: the TMEM accesses and votes below are warp-wide)
       if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar_s_full, par, abort_flag))) { ok = false; break; }
       tc_fence_after();
-      uint32_t s[ATT_BN];
+      uint32_t s[ATT_BN / 64][32];
 #pragma unroll
-      for (int c = 0; c < ATT_BN / 32; ++c)
-        tmem_ld_32x32b_x32(tmem_s + lane_off + (uint32_t)(c * 32), *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
+      for (int c = 0; c < ATT_BN / 64; ++c) tmem_ld_32x32b_x32(tmem_s + lane_off + s_col + (uint32_t)(c * 32), s[c]);
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive(bar_s_free);
-      // scaled, masked scores and their maximum (only the diagonal and the last block have anything to mask)
-      const bool need_mask = (k0 + ATT_BN - 1 > qpos) || (k0 + ATT_BN > p.seq);
-      float m_blk = -INFINITY;
+      // masked raw scores and their maximum (only the diagonal and the last block have anything to mask)
+      const bool need_mask = (k0 + ATT_BN / 2 - 1 > qpos) || (k0 + ATT_BN / 2 > p.seq);
+      float m_raw = -INFINITY;
 #pragma unroll
-      for (int j = 0; j < ATT_BN; ++j) {
-        float v = __uint_as_float(s[j]) * sc;
-        if (need_mask && !(k0 + j <= qpos && k0 + j < p.seq)) v = -INFINITY;
-        s[j] = __float_as_uint(v);
-        m_blk = fmaxf(m_blk, v);
+      for (int c = 0; c < ATT_BN / 64; ++c) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float v = __uint_as_float(s[c][j]);
+          if (need_mask && !(k0 + c * 32 + j <= qpos && k0 + c * 32 + j < p.seq)) {
+            v = -INFINITY;
+            s[c][j] = __float_as_uint(v);
+          }
+          m_raw = fmaxf(m_raw, v);
+        }
       }
+      // the other half of the row: exchange through shared memory, 64-thread barrier of the two warps of this quarter
+      xch[(par * 2 + half) * ATT_BM + row] = m_raw;
+      asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+      const float m_blk = fmaxf(m_raw, xch[(par * 2 + (half ^ 1)) * ATT_BM + row]) * sc;  // sc > 0
       float alpha = 1.0f;
       bool rescale = false;
       if (m_blk > m_ref + kRescaleSlack || m_ref == -INFINITY) {
@@ -236,39 +252,36 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         // P and the output accumulator belong to the tensor core until P V (kb - 1) has completed
         if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar_pv_done, par ^ 1, abort_flag))) { ok = false; break; }
         tc_fence_after();
-        if (__any_sync(0xffffffffu, rescale)) {
+        if (__any_sync(0xffffffffu, rescale)) {  // this warp's half of the output columns
 #pragma unroll 1
-          for (int c = 0; c < DV / 32; ++c) {
+          for (int c = 0; c < DV / 64; ++c) {
             uint32_t r[32];
-            tmem_ld_32x32b_x32(tmem_o + lane_off + (uint32_t)(c * 32), r);
+            tmem_ld_32x32b_x32(tmem_o + lane_off + o_col + (uint32_t)(c * 32), r);
             tmem_wait_ld();
 #pragma unroll
             for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * alpha);
-            tmem_st_32x32b_x32(tmem_o + lane_off + (uint32_t)(c * 32), r);
+            tmem_st_32x32b_x32(tmem_o + lane_off + o_col + (uint32_t)(c * 32), r);
           }
           tmem_wait_st();
         }
       }
       l_run *= alpha;
       float l_blk = 0.0f;
+      uint8_t* atom = smem + L::kPOff + half * ATOM_BYTES_128;  // this half's 64 keys are one swizzle atom
 #pragma unroll
-      for (int g = 0; g < ATT_BN / 8; ++g) {
+      for (int g = 0; g < ATT_BN / 16; ++g) {
         float pv[8];
 #pragma unroll
-        for (int t = 0; t < 8; ++t) pv[t] = exp2f(__uint_as_float(s[g * 8 + t]) - m_use);
+        for (int t = 0; t < 8; ++t) {
+          pv[t] = exp2f(fmaf(__uint_as_float(s[g / 4][(g % 4) * 8 + t]), sc, -m_use));
+          l_blk += pv[t];
+        }
         uint4 u;
         u.x = pack_bf16x2(pv[0], pv[1]);
         u.y = pack_bf16x2(pv[2], pv[3]);
         u.z = pack_bf16x2(pv[4], pv[5]);
         u.w = pack_bf16x2(pv[6], pv[7]);
-        // the sum uses the rounded values, so that O / l is an exact convex combination of the V rows seen by the MMA
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const float2 f = __bfloat1622float2(h[t]);
-          l_blk += f.x + f.y;
-        }
-        *reinterpret_cast<uint4*>(smem + L::kPOff + (g / 8) * ATOM_BYTES_128 + sw128_chunk_off(row, g % 8)) = u;
+        *reinterpret_cast<uint4*>(atom + sw128_chunk_off(row, g)) = u;
       }
       l_run += l_blk;
       fence_proxy_async();  // the generic-proxy stores of P must be visible to the tensor core's reads
@@ -281,12 +294,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       *abort_flag = 1;
     } else {
       tc_fence_after();
-      const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-      __nv_bfloat16* dst = p.out + (((size_t)batch * p.seq + (row_ok ? qpos : 0)) * p.heads + head) * p.dv + dv0;
+      // total of the two halves' sums (the slots of the next parity are free: nobody reads them any more)
+      const int slot = (n_kblocks & 1) * 2;
+      xch[(slot + half) * ATT_BM + row] = l_run;
+      asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+      const float l_tot = l_run + xch[(slot + (half ^ 1)) * ATT_BM + row];
+      const float inv = l_tot > 0.0f ? 1.0f / l_tot : 0.0f;
+      __nv_bfloat16* dst = p.out + (((size_t)batch * p.seq + (row_ok ? qpos : 0)) * p.heads + head) * p.dv + dv0 + o_col;
 #pragma unroll 1
-      for (int c = 0; c < DV / 32; ++c) {
+      for (int c = 0; c < DV / 64; ++c) {
         uint32_t r[32];
-        tmem_ld_32x32b_x32(tmem_o + lane_off + (uint32_t)(c * 32), r);
+        tmem_ld_32x32b_x32(tmem_o + lane_off + o_col + (uint32_t)(c * 32), r);
         tmem_wait_ld();
         if (row_ok) {
 #pragma unroll
@@ -300,8 +318,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           }
         }
       }
-      if (row_ok && p.lse != nullptr && dv0 == 0)
-        p.lse[((size_t)batch * p.heads + head) * p.seq + qpos] = m_ref * 0.6931471805599453f + __logf(l_run);
+      if (row_ok && half == 0 && p.lse != nullptr && dv0 == 0)
+        p.lse[((size_t)batch * p.heads + head) * p.seq + qpos] = m_ref * 0.6931471805599453f + __logf(l_tot);
     }
   }
 
@@ -311,7 +329,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     for (int i = 0; i < 200; ++i) __nanosleep(1000);  // copies that may still be in flight land first
     __syncthreads();
   }
-  if (warp == 4) {
+  if (warp == 8) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 256);
   }

@@ -239,89 +239,167 @@ __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { retu
 
 constexpr int RC_THREADS = 256;
 
-// One CTA per row (grid-stride). Columns are visited 256 at a time; a ballot per warp plus a prefix over the eight warp
-// counts gives every non-zero its slot, so the list comes out in ascending column order (deterministic).
+template <typename T>
+struct RowVec;
+template <>
+struct RowVec<float> {
+  static constexpr int V = 4;
+  __device__ static void load(const float* p, float (&f)[4]) {
+    const float4 v = __ldcs(reinterpret_cast<const float4*>(p));
+    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+  }
+};
+template <>
+struct RowVec<__nv_bfloat16> {
+  static constexpr int V = 8;
+  __device__ static void load(const __nv_bfloat16* p, float (&f)[8]) {
+    const uint4 u = __ldcs(reinterpret_cast<const uint4*>(p));
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 t = __bfloat1622float2(h[i]);
+      f[2 * i] = t.x;
+      f[2 * i + 1] = t.y;
+    }
+  }
+};
+
+// One CTA per row (grid-stride); a thread takes 16 bytes of the row per step, so a step covers 256 x 16 bytes.
+//   Without thr an entry is kept when x != 0. With thr (> 0): entries above *thr are kept; entries EQUAL to it are
+//   kept too, unless tie_quota is given, in which case only the first tie_quota[row] of them (in column order) are:
+//   that is how a caller keeps an exact number of entries when the threshold value repeats.
+//   A counting call (idx == nullptr) is a pure streaming pass; with `ties` it reports the two kinds separately
+//   (nnz = entries above the threshold, ties = entries equal to it).
+//   A compacting call finds every kept entry's slot with one block-wide scan per step (a thread's entries are
+//   consecutive columns, threads are in column order), so the list comes out in ascending column order.
+//   With col_div the stored value is x / col_div[column] (gated pre-activation back to the activation).
 template <typename T>
 __global__ void __launch_bounds__(RC_THREADS)
 row_compact_kernel(const T* __restrict__ x, int B, long long N, int cap, int* __restrict__ idx, float* __restrict__ val,
                    int* __restrict__ nnz, const float* __restrict__ thr, const float* __restrict__ col_div,
                    int* __restrict__ ties, const int* __restrict__ tie_quota) {
-  // Without thr an entry is kept when x != 0. With thr (> 0): entries above *thr are kept; entries EQUAL to it are
-  // kept too, unless tie_quota is given, in which case only the first tie_quota[row] of them (in column order) are:
-  // that is how a caller keeps an exact number of entries when the threshold value repeats. A counting call
-  // (idx == nullptr) with `ties` reports the two kinds separately: nnz = entries above, ties = entries equal.
-  // With col_div the stored value is x / col_div[column] (gated pre-activation back to the activation).
-  const float t = thr != nullptr ? *thr : 0.0f;
-  const bool split_ties = thr != nullptr && (ties != nullptr || tie_quota != nullptr);
-  __shared__ int s_warp[RC_THREADS / 32];
-  __shared__ int s_warp_t[RC_THREADS / 32];
+  constexpr int V = RowVec<T>::V;
+  constexpr int NW = RC_THREADS / 32;
+  const bool has_thr = thr != nullptr;
+  const float t = has_thr ? *thr : 0.0f;
+  const bool split_ties = has_thr && (ties != nullptr || tie_quota != nullptr);
+  const bool vec_ok = (N % V == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0);
+  __shared__ int s_a[NW], s_b[NW];
   __shared__ int s_base, s_tie_base;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const unsigned lt = (1u << lane) - 1u;
+  const long long step = (long long)RC_THREADS * V;
+
   for (int row = blockIdx.x; row < B; row += gridDim.x) {
+    const T* xr = x + (size_t)row * N;
+    if (idx == nullptr) {
+      // ---- counting: no ordering needed
+      int n_keep = 0, n_tie = 0;
+      for (long long c = (long long)threadIdx.x * V; c < N; c += step) {
+        float f[V];
+        if (vec_ok) {
+          RowVec<T>::load(xr + c, f);
+        } else {
+#pragma unroll
+          for (int i = 0; i < V; ++i) f[i] = c + i < N ? to_float<T>(xr[c + i]) : 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          if (split_ties) {
+            n_keep += f[i] > t;
+            n_tie += (f[i] == t) && (c + i < N);
+          } else {
+            n_keep += has_thr ? (f[i] >= t) : (f[i] != 0.0f);
+          }
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        n_keep += __shfl_xor_sync(0xffffffffu, n_keep, o);
+        n_tie += __shfl_xor_sync(0xffffffffu, n_tie, o);
+      }
+      __syncthreads();
+      if (lane == 0) { s_a[warp] = n_keep; s_b[warp] = n_tie; }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        int a = 0, b = 0;
+        for (int w = 0; w < NW; ++w) { a += s_a[w]; b += s_b[w]; }
+        if (nnz != nullptr) nnz[row] = a;
+        if (ties != nullptr) ties[row] = b;
+      }
+      continue;
+    }
+    // ---- compaction
     __syncthreads();
     if (threadIdx.x == 0) { s_base = 0; s_tie_base = 0; }
     __syncthreads();
     const int quota = tie_quota != nullptr ? tie_quota[row] : 0x7fffffff;
-    const T* xr = x + (size_t)row * N;
-    for (long long c0 = 0; c0 < N; c0 += RC_THREADS) {
-      const long long c = c0 + threadIdx.x;
-      const float v = c < N ? to_float<T>(xr[c]) : 0.0f;
-      bool keep;
-      int tie_total = 0;
-      if (split_ties) {
-        const bool is_tie = c < N && v == t;
-        const unsigned bt = __ballot_sync(0xffffffffu, is_tie);
-        if (lane == 0) s_warp_t[warp] = __popc(bt);
-        __syncthreads();
-        int tie_before = 0;
-#pragma unroll
-        for (int w = 0; w < RC_THREADS / 32; ++w) {
-          const int cnt = s_warp_t[w];
-          if (w < warp) tie_before += cnt;
-          tie_total += cnt;
-        }
-        const int tie_rank = s_tie_base + tie_before + __popc(bt & lt);
-        // a counting call keeps the two kinds apart: `keep` then means "above the threshold"
-        keep = (v > t) || (idx != nullptr && is_tie && tie_rank < quota);
+    for (long long c0 = 0; c0 < N; c0 += step) {
+      const long long c = c0 + (long long)threadIdx.x * V;
+      float f[V];
+      if (c < N && vec_ok) {
+        RowVec<T>::load(xr + c, f);
       } else {
-        keep = thr != nullptr ? (v >= t) : (v != 0.0f);
-      }
-      const unsigned bal = __ballot_sync(0xffffffffu, keep);
-      if (lane == 0) s_warp[warp] = __popc(bal);
-      __syncthreads();
-      int before = 0, total = 0;
 #pragma unroll
-      for (int w = 0; w < RC_THREADS / 32; ++w) {
-        const int cnt = s_warp[w];
-        if (w < warp) before += cnt;
-        total += cnt;
+        for (int i = 0; i < V; ++i) f[i] = c + i < N ? to_float<T>(xr[c + i]) : 0.0f;
       }
-      const int base = s_base;
-      if (keep && idx != nullptr) {
-        const int slot = base + before + __popc(bal & lt);
-        if (slot < cap) {
-          idx[(size_t)row * cap + slot] = (int)c;
-          val[(size_t)row * cap + slot] = col_div != nullptr ? v / col_div[c] : v;
+      unsigned m_strict = 0, m_tie = 0;  // bit i: element i is above the threshold / equal to it
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        const bool in = c + i < N;
+        if (split_ties) {
+          m_strict |= (unsigned)(in && f[i] > t) << i;
+          m_tie |= (unsigned)(in && f[i] == t) << i;
+        } else {
+          m_strict |= (unsigned)(in && (has_thr ? (f[i] >= t) : (f[i] != 0.0f))) << i;
+        }
+      }
+      // block-wide exclusive scan of (strict, tie) counts in thread (= column) order
+      const int n_s = __popc(m_strict), n_t = __popc(m_tie);
+      int inc_s = n_s, inc_t = n_t;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int a = __shfl_up_sync(0xffffffffu, inc_s, o), b = __shfl_up_sync(0xffffffffu, inc_t, o);
+        if (lane >= o) { inc_s += a; inc_t += b; }
+      }
+      if (lane == 31) { s_a[warp] = inc_s; s_b[warp] = inc_t; }
+      __syncthreads();
+      int s_before = inc_s - n_s, t_before = inc_t - n_t, s_total = 0, t_total = 0;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) {
+        if (w < warp) { s_before += s_a[w]; t_before += s_b[w]; }
+        s_total += s_a[w];
+        t_total += s_b[w];
+      }
+      const int base = s_base, tie_base = s_tie_base;
+      // ties granted so far = min(ties seen so far, quota), in closed form for any prefix
+      int tie_rank = tie_base + t_before;
+      int slot = base + s_before + (min(tie_rank, quota) - min(tie_base, quota));
+      // `base` already holds the ties granted in earlier steps
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        const bool strict = (m_strict >> i) & 1u, tie = (m_tie >> i) & 1u;
+        const bool keep = strict || (tie && tie_rank < quota);
+        tie_rank += tie;
+        if (keep) {
+          if (slot < cap) {
+            idx[(size_t)row * cap + slot] = (int)(c + i);
+            val[(size_t)row * cap + slot] = col_div != nullptr ? f[i] / col_div[c + i] : f[i];
+          }
+          ++slot;
         }
       }
       __syncthreads();
       if (threadIdx.x == 0) {
-        s_base = base + total;
-        s_tie_base += tie_total;
+        s_base = base + s_total + (min(tie_base + t_total, quota) - min(tie_base, quota));
+        s_tie_base = tie_base + t_total;
       }
     }
     __syncthreads();
     const int count = s_base;
-    if (threadIdx.x == 0) {
-      if (nnz != nullptr) nnz[row] = count;
-      if (ties != nullptr) ties[row] = s_tie_base;
-    }
-    if (idx != nullptr) {
-      for (int j = count + threadIdx.x; j < cap; j += RC_THREADS) {
-        idx[(size_t)row * cap + j] = -1;
-        val[(size_t)row * cap + j] = 0.0f;
-      }
+    if (threadIdx.x == 0 && nnz != nullptr) nnz[row] = count;
+    for (int j = count + threadIdx.x; j < cap; j += RC_THREADS) {
+      idx[(size_t)row * cap + j] = -1;
+      val[(size_t)row * cap + j] = 0.0f;
     }
   }
 }

@@ -22,7 +22,7 @@ from .microbench import _timeit
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default="all", help="all | attn | attn_fwd | batchtopk | clt | compact | headsum")
+    ap.add_argument("--case", default="all", help="all | attn | attn_fwd | batchtopk | batchtopk_step | clt | compact | headsum")
     ap.add_argument("--attn-shape", default="4,1024,64,64,128", help="batch,seq,heads,d_qk,d_v of the attention cases")
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
@@ -110,6 +110,41 @@ def main(argv=None):
         t_r = _timeit(lambda: src[keep].to(torch.bfloat16), a.iters, a.warmup, flush)
         report("mask_compact_cast_1Mx1024_fp32_to_bf16", t_o, t_r, gbs_ours=round(n * d * 0.9 * 6 / t_o[0] / 1e6, 1))
         del src
+
+    if want("batchtopk_step"):
+        # one training step of a BatchTopK SAE: the fused kernel sequence against autograd + torch.optim.Adam on the same model
+        import copy
+
+        from ..models.sae import SAEConfig, SparseAutoEncoder
+        from .fused_step import FusedTopKSAEStep
+
+        d, expansion, k, B, lr = 4096, 8, 50, 4096, 2e-4
+        cfg = SAEConfig(hook_point_in="h", hook_point_out="h", d_model=d, expansion_factor=expansion, act_fn="batchtopk", top_k=k,
+                        device="cuda", dtype=torch.float32)  # fmt: skip
+        ref = SparseAutoEncoder(cfg)
+        ref.init_parameters(encoder_uniform_bound=d**-0.5, decoder_uniform_bound=d**-0.5)
+        ref.set_decoder_to_fixed_norm(1.0, True)
+        ref.init_encoder_with_decoder_transpose()
+        ref.set_dataset_average_activation_norm({"h": d**0.5})
+        fused_model = copy.deepcopy(ref)
+        fused_model.activation_function = fused_model.activation_function_factory(None)
+        engine = FusedTopKSAEStep(fused_model)
+        x = torch.randn(B, d, device=dev).to(torch.bfloat16)
+        tokens = torch.zeros(B, dtype=torch.long, device=dev)
+        opt = torch.optim.Adam(ref.parameters(), lr=lr)
+
+        def generic():
+            opt.zero_grad(set_to_none=True)
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                loss = ref.compute_loss({"h": x.float(), "tokens": tokens})["loss"]
+            loss.backward()
+            opt.step()
+
+        t_o = _timeit(lambda: engine.step(x, x, k, lr), a.iters, a.warmup, flush)
+        t_r = _timeit(generic, a.iters, a.warmup, flush)
+        report(f"batchtopk_sae_train_step_d{d}_F{d * expansion}_k{k}_B{B}", t_o, t_r, tokens_per_s_ours=round(B / t_o[0] * 1e3))
+        K.check_status(dev)
+        del ref, fused_model, engine, opt
 
     if want("headsum"):
         from ..parallel.symm import HeadSumComm
