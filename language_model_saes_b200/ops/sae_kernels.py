@@ -22,7 +22,15 @@ _status_buffers: dict[torch.device, torch.Tensor] = {}
 
 
 class KernelStatusError(RuntimeError):
-    """A kernel reported a bounded-wait expiry or a bad argument through its status word."""
+    """A kernel reported a bounded-wait expiry or a bad argument through its status word. ``code`` is the status code
+    (5 = a peer's flag did not arrive in time: a collective timed out)."""
+
+    code: int = 0
+
+
+class CollectiveTimeout(KernelStatusError):
+    """A bounded wait on another GPU's flag ran out: the peer is late, stuck or gone. The kernels involved have left
+    through their normal exit and the context is usable; the data of that step is not."""
 
 
 _STATUS_NAMES = {
@@ -89,9 +97,11 @@ def check_status(device: torch.device) -> None:
     vals = buf.tolist()
     if vals[0] != 0:
         buf.zero_()
-        raise KernelStatusError(
+        err = (CollectiveTimeout if vals[0] == 5 else KernelStatusError)(
             f"kernel status {vals[0]} ({_STATUS_NAMES.get(vals[0], 'unknown')}), detail={vals[1]}, block={vals[2]}, aux={vals[3]}"
         )
+        err.code = vals[0]
+        raise err
 
 
 GEMM_PAIR_DEFAULT = os.environ.get("LMSAE_GEMM_PAIR", "1") == "1"

@@ -44,6 +44,7 @@ from .metrics import (
 from .models.sparse_dictionary import SparseDictionary
 from .optim import SparseAdam, clip_grad_norm, get_scheduler
 from .parallel.data_parallel import reduce_gradients
+from .parallel.health import PeerLost
 from .parallel.mesh import is_primary_rank, mesh_dim_size, mesh_group
 from .utils.logging import get_distributed_logger, log_metrics
 from .utils.tensor_specs import apply_token_mask
@@ -103,6 +104,12 @@ class TrainerConfig(BaseConfig):
     """With ``prefetch_to_device`` under feature (``model``) parallelism: every rank of a replica copies 1/n of each
     host batch and the rows are all-gathered over NVLink. Requires what the activation pipeline guarantees: the ranks
     of one replica see the same batches."""
+    heartbeat_timeout_s: float | None = None
+    """Multi-process runs: publish a heartbeat every step through the process group's store and, before each step, raise
+    ``parallel.health.PeerLost`` when a peer has left or has been silent for this long (None: off)."""
+    checkpoint_on_failure: bool = False
+    """Save a full trainer checkpoint under ``exp_result_path`` when ``fit`` ends with an exception (a lost peer included;
+    only this rank's view is saved then, without collectives, so it is meant for unsharded or data-parallel models)."""
     use_fused_kernels: bool = True
     """Run eligible models (TopK SAE, MSE loss, Adam, CUDA) on the fused kernel path."""
     use_peer_memory_collectives: bool = True
@@ -205,18 +212,32 @@ class _LossReader:
         host, ev = entry
         ev.synchronize()
         self._slots[slot] = None
-        return float(host)
+        if host[1] != 0:
+            from .ops import sae_kernels as K
 
-    def push(self, loss: Tensor) -> float | None:
-        """Queue ``loss`` and return the most recent value whose copy has completed (None on the first call)."""
+            code = int(host[1])
+            err = (K.CollectiveTimeout if code == 5 else K.KernelStatusError)(
+                f"kernel status {code} ({K._STATUS_NAMES.get(code, 'unknown')}), detail={int(host[2])}, block={int(host[3])}, aux={int(host[4])}"
+            )
+            err.code = code
+            raise err
+        return float(host[0])
+
+    def push(self, loss: Tensor, status: Tensor | None = None) -> float | None:
+        """Queue ``loss`` and return the most recent value whose copy has completed (None on the first call). ``status``
+        (the kernels' int32 status word) travels with it: a recorded bounded-wait expiry raises when it is picked up."""
         if not loss.is_cuda:
             return float(loss)
         slot = self._n & 1
         self._n += 1
         if self._pinned[slot] is None:
-            self._pinned[slot] = torch.empty((), dtype=torch.float32, pin_memory=True)
+            self._pinned[slot] = torch.empty(5, dtype=torch.float32, pin_memory=True)
         host = self._pinned[slot]
-        host.copy_(loss.detach().float().reshape(()), non_blocking=True)
+        host[:1].copy_(loss.detach().float().reshape(1), non_blocking=True)
+        if status is not None:
+            host[1:5].copy_(status[:4], non_blocking=True)  # int32 -> fp32: the codes are small integers
+        else:
+            host[1:5].zero_()
         ev = torch.cuda.Event()
         ev.record()
         self._slots[slot] = (host, ev)
@@ -667,9 +688,13 @@ class Trainer:
         dp = mesh_dim_size(sae.device_mesh, "data")
         accum = max(1, self.cfg.gradient_accumulation_steps)
         loss_reader = _LossReader()
+        heartbeat = self._make_heartbeat()
         try:
             while True:
                 with timer.time("training_iteration"):
+                    if heartbeat is not None:
+                        heartbeat.beat(self.cur_step)
+                        heartbeat.check()  # before this step's collectives: a lost peer ends the run here, not in a hang
                     bar.update(1)
                     sae.train()
                     batch = self._to_model_device(sae, batch)
@@ -678,7 +703,7 @@ class Trainer:
                     else:
                         loss = self._generic_iteration(sae, batch, accum)
                     if (self.cur_step + 1) % self.cfg.log_frequency == 0:
-                        shown = loss_reader.push(loss)
+                        shown = loss_reader.push(loss, self._kernel_status(sae))
                         if shown is not None:
                             bar.set_description(f"loss: {shown:.2f}")
                     if eval_fn is not None and (self.cur_step + 1) % self.cfg.eval_frequency == 0:
@@ -698,9 +723,15 @@ class Trainer:
                         batch = next(stream)
         except StopIteration:
             logger.info("the current stream has ended")
+            if heartbeat is not None:
+                heartbeat.leave("end of the activation stream")
             return True
         except Exception as e:
             logger.error(f"Training failed: {e}")
+            if heartbeat is not None and not isinstance(e, PeerLost):
+                heartbeat.leave(f"{type(e).__name__}: {e}")
+            if self.cfg.checkpoint_on_failure:
+                self._save_failure_checkpoint(sae)
             raise
         finally:
             last = loss_reader.flush()
@@ -710,6 +741,43 @@ class Trainer:
             if self.fused is not None:
                 self.fused.join()  # the last update may still be running on its own stream
         return None
+
+    def _kernel_status(self, sae: SparseDictionary) -> Tensor | None:
+        """The status word of this model's device when hand-written kernels are in play (read back with the loss)."""
+        if self.fused is None:
+            return None
+        from .ops import sae_kernels as K
+
+        return K.status_buffer(next(sae.parameters()).device)
+
+    def _make_heartbeat(self):
+        if self.cfg.heartbeat_timeout_s is None or not dist.is_initialized() or dist.get_world_size() == 1:
+            return None
+        from .parallel.health import Heartbeat, default_store
+
+        return Heartbeat(default_store(), dist.get_rank(), dist.get_world_size(), timeout_s=self.cfg.heartbeat_timeout_s)
+
+    def _save_failure_checkpoint(self, sae: SparseDictionary) -> None:
+        """Best effort, this rank only and without collectives (the other ranks may be gone): the model's local tensors,
+        the optimizer and the trainer state under ``<exp_result_path>/failure/rank_<r>/``."""
+        try:
+            if self.fused is not None:
+                self.fused.join()
+            rank = dist.get_rank() if dist.is_initialized() else 0
+            out = Path(self.cfg.exp_result_path) / "failure" / f"rank_{rank}"
+            os.makedirs(out, exist_ok=True)
+            torch.save({k: v.detach().cpu() for k, v in sae.state_dict().items()}, out / "local_state.pt")
+            sae.cfg.save_hyperparameters(out)
+            state = {"cur_step": self.cur_step, "cur_tokens": self.cur_tokens, "total_training_steps": self.total_training_steps,
+                     "cfg": self.cfg}  # fmt: skip
+            if self.optimizer is not None:
+                state["optimizer"] = self.optimizer.state_dict()
+            if self.scheduler is not None:
+                state["scheduler"] = self.scheduler.state_dict()
+            torch.save(state, out / "trainer.pt")
+            logger.info(f"failure checkpoint saved to {out} (step {self.cur_step})")
+        except Exception as e:  # noqa: BLE001  (the original exception matters more)
+            logger.error(f"could not save a failure checkpoint: {e}")
 
     @staticmethod
     def _to_model_device(sae: SparseDictionary, batch: dict[str, Any]) -> dict[str, Any]:

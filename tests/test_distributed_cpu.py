@@ -1,6 +1,7 @@
 """Multi-rank logic on CPU (gloo, 2 ranks): sharded models and the fused step's orchestration must reproduce
 the single-process result."""
 
+import pytest
 import torch
 import torch.distributed as dist
 
@@ -88,3 +89,70 @@ def test_fused_step_feature_and_data_parallel_match_single():
     assert torch.allclose(mean / 2, want, rtol=1e-4)
     assert torch.allclose(dp.W_D.data, ref.W_D.data, atol=1e-5)
     assert torch.allclose(dp.W_E.data, ref.W_E.data, atol=1e-5)
+
+
+@distributed_test(nproc_per_node=2, backend="gloo")
+def test_heartbeat_reports_a_rank_that_leaves_and_one_that_goes_silent():
+    import time
+
+    import torch.distributed as dist
+
+    from language_model_saes_b200.parallel.health import Heartbeat, PeerLost, default_store
+
+    rank = dist.get_rank()
+    hb = Heartbeat(default_store(), rank, 2, timeout_s=1.0, prefix="t1")
+    hb.beat(0)
+    dist.barrier()
+    hb.check()  # both alive
+    if rank == 1:
+        hb.leave("ValueError: injected on the host")  # what Trainer.fit does in its exception handler
+        dist.barrier()
+    else:
+        dist.barrier()
+        with pytest.raises(PeerLost, match="rank 1: left: ValueError"):
+            hb.check()
+    # silence: rank 1 stops beating (it stays in the job, so the barriers below still work)
+    hb2 = Heartbeat(default_store(), rank, 2, timeout_s=0.5, prefix="t2")
+    hb2.beat(1)
+    dist.barrier()
+    if rank == 0:
+        deadline = time.time() + 10
+        while True:
+            hb2.beat(2)
+            try:
+                hb2.check()
+            except PeerLost as e:
+                assert list(e.ranks) == [1] and "silent" in e.ranks[1]
+                break
+            assert time.time() < deadline, "the silent peer was never reported"
+            time.sleep(0.1)
+    dist.barrier()
+
+
+def test_trainer_saves_a_failure_checkpoint_and_reports_kernel_status(tmp_path):
+    import torch
+
+    from language_model_saes_b200.models.sae import SAEConfig, SparseAutoEncoder
+    from language_model_saes_b200.trainer import Trainer, TrainerConfig, _LossReader
+
+    cfg = SAEConfig(hook_point_in="in", hook_point_out="in", d_model=16, expansion_factor=2, act_fn="relu", device="cpu",
+                    dtype=torch.float32, norm_activation="inference")  # fmt: skip
+    sae = SparseAutoEncoder(cfg)
+    sae.init_parameters(encoder_uniform_bound=0.3, decoder_uniform_bound=0.3, init_log_jumprelu_threshold_value=0.0)
+
+    def stream():
+        for i in range(10):
+            if i == 4:
+                raise OSError("disk went away")  # a host-side failure in the middle of the run
+            yield {"in": torch.randn(8, 16), "tokens": torch.ones(8, dtype=torch.long)}
+
+    tcfg = TrainerConfig(lr=1e-3, total_training_tokens=80, lr_warm_up_steps=0, n_checkpoints=0, log_frequency=100,
+                         exp_result_path=str(tmp_path), checkpoint_on_failure=True, l1_coefficient=1e-4, sparsity_loss_type="power")  # fmt: skip
+    trainer = Trainer(tcfg)
+    with pytest.raises(OSError, match="disk went away"):
+        trainer.fit(sae, stream())
+    out = tmp_path / "failure" / "rank_0"
+    state = torch.load(out / "trainer.pt", weights_only=False)
+    assert state["cur_step"] == 4 and "optimizer" in state and (out / "local_state.pt").exists() and (out / "config.json").exists()
+    # the status word that travels with the loss: nothing to report on CPU tensors
+    assert _LossReader().push(torch.tensor(1.5)) == 1.5
