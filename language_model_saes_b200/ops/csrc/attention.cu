@@ -32,15 +32,16 @@ template <int DQK, int DV>
 struct AttnSmem {
   static constexpr int kQOff = 0;
   static constexpr int kQBytes = (DQK / 64) * ATOM_BYTES_128;
-  static constexpr int kKOff = kQOff + kQBytes;
-  static constexpr int kVOff = kKOff + kQBytes;
-  static constexpr int kVAtomBytes = DV * 128;  // DV rows x 64 keys
+  static constexpr int kKOff = kQOff + kQBytes;        // two K buffers
+  static constexpr int kVOff = kKOff + 2 * kQBytes;    // two V^T buffers
+  static constexpr int kVAtomBytes = DV * 128;         // DV rows x 64 keys
   static constexpr int kVBytes = 2 * kVAtomBytes;
-  static constexpr int kPOff = kVOff + kVBytes;
+  static constexpr int kPOff = kVOff + 2 * kVBytes;    // two P buffers
   static constexpr int kPBytes = 2 * ATOM_BYTES_128;
-  static constexpr int kXchOff = kPOff + kPBytes;      // float [2][2][128]: row statistics exchanged between column halves
+  static constexpr int kXchOff = kPOff + 2 * kPBytes;  // float [2][2][128]: row statistics exchanged between column halves
   static constexpr int kBarOff = kXchOff + 2 * 2 * 128 * 4;
-  static constexpr int kTmemPtrOff = kBarOff + 8 * 8;
+  static constexpr int kNumBars = 13;
+  static constexpr int kTmemPtrOff = kBarOff + kNumBars * 8;
   static constexpr int kAbortOff = kTmemPtrOff + 4;
   static constexpr int kTotal = kAbortOff + 4;
   static constexpr int kDynamicBytes = kTotal + 1024;
@@ -57,18 +58,18 @@ constexpr int FWD_ROW_THREADS = 256;   // warps 0-7: warp w works on query rows 
 constexpr int FWD_THREADS = 288;       // + warp 8: TMA + MMA issue
 constexpr float kRescaleSlack = 8.0f;  // log2 units the running reference may lag behind the true row maximum
 
-// Roles and hand-offs (all through mbarriers and 64-thread named barriers; the loop has no CTA-wide barrier):
-//   issuer   K(kb+1) load as soon as S(kb) has been computed; S(kb+1) as soon as the rows hold S(kb) in registers, so the
-//            tensor core works on the next scores while the rows do their exponentials; P V (kb) when P(kb) is written;
-//            V(kb+1) load when P V (kb) has completed.
-//   rows     two threads per query row, one per half of the 128 keys of a block (eight warps keep the issue slots of the
-//            SM busy where four leave them idle half of the time): S(kb) TMEM -> 64 registers, release S; the two halves
-//            exchange their maxima through shared memory; the output accumulator stays in TMEM and is only rescaled when
-//            the maximum has grown by more than 2^8 since the reference was set (rarely after the first blocks), which
-//            keeps p <= 256 and the sums well inside fp32 / bf16 range; exponentials -> P (bf16, swizzled K-major; a
-//            half is exactly one 64-key atom) -> signal.
+// One CTA per SM; K, V^T, P (shared memory) and S (TMEM) are double-buffered, key block kb uses buffer kb & 1 and the
+// b-th use of a buffer completes phase b of its barriers. Roles and hand-offs (mbarriers and 64-thread named barriers;
+// the loop has no CTA-wide barrier):
+//   issuer   loads two key blocks ahead; S(kb+1) is computed while the rows work on S(kb); P V (kb) as soon as P(kb) is
+//            written; a K / V^T buffer is refilled for block kb + 2 when S(kb) / P V (kb) has consumed it.
+//   rows     two threads per query row, one per half of the 128 keys of a block: S(kb) TMEM -> 64 registers, release the
+//            S buffer; the two halves exchange their maxima through shared memory; the output accumulator stays in TMEM
+//            and is only rescaled when the maximum has grown by more than 2^8 since the reference was set (rarely
+//            after the first blocks), which keeps p <= 256 and the sums well inside fp32 / bf16 range; exponentials ->
+//            P (bf16, swizzled K-major; a half is exactly one 64-key atom) -> signal.
 template <int DQK, int DV>
-__global__ void __maxnreg__(112)  // 288 threads x 112 registers: two CTAs per SM
+__global__ void __launch_bounds__(FWD_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_vt, const AttnParams p) {
   using L = AttnSmem<DQK, DV>;
@@ -76,12 +77,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
   uint64_t* bar_q = bars + 0;
-  uint64_t* bar_k = bars + 1;
-  uint64_t* bar_v = bars + 2;
-  uint64_t* bar_s_full = bars + 3;
-  uint64_t* bar_s_free = bars + 4;
-  uint64_t* bar_p_full = bars + 5;
-  uint64_t* bar_pv_done = bars + 6;
+  uint64_t* bar_k = bars + 1;        // [2]
+  uint64_t* bar_v = bars + 3;        // [2]
+  uint64_t* bar_s_full = bars + 5;   // [2]
+  uint64_t* bar_s_free = bars + 7;   // [2]
+  uint64_t* bar_p_full = bars + 9;   // [2]
+  uint64_t* bar_pv_done = bars + 11; // [2]
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + L::kTmemPtrOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOff);
 
@@ -97,93 +98,107 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 
   if (threadIdx.x == 0) {
     mbar_init(bar_q, 1);
-    mbar_init(bar_k, 1);
-    mbar_init(bar_v, 1);
-    mbar_init(bar_s_full, 1);
-    mbar_init(bar_s_free, FWD_ROW_THREADS);
-    mbar_init(bar_p_full, FWD_ROW_THREADS);
-    mbar_init(bar_pv_done, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bar_k[i], 1);
+      mbar_init(&bar_v[i], 1);
+      mbar_init(&bar_s_full[i], 1);
+      mbar_init(&bar_s_free[i], FWD_ROW_THREADS);
+      mbar_init(&bar_p_full[i], FWD_ROW_THREADS);
+      mbar_init(&bar_pv_done[i], 1);
+    }
     *abort_flag = 0;
     fence_barrier_init();
   }
   if (warp == 8) {
-    tmem_alloc(tmem_ptr_smem, 256);
+    tmem_alloc(tmem_ptr_smem, 512);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
-  const uint32_t tmem_s = tmem_base;
-  const uint32_t tmem_o = tmem_base + ATT_BN;
+  const uint32_t tmem_o = tmem_base + 2 * ATT_BN;  // S buffers at columns [0, 128) and [128, 256)
 
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA + MMA issuer
     if (elect_one()) {
       auto load_k = [&](int kb) {
-        mbar_arrive_expect_tx(bar_k, L::kQBytes);
+        const int u = kb & 1;
+        mbar_arrive_expect_tx(&bar_k[u], L::kQBytes);
         for (int a = 0; a < DQK / 64; ++a)
-          tma_load_2d(smem + L::kKOff + a * ATOM_BYTES_128, &tmap_k, bar_k, head * DQK + a * 64, batch * p.seq + kb * ATT_BN);
+          tma_load_2d(smem + L::kKOff + u * L::kQBytes + a * ATOM_BYTES_128, &tmap_k, &bar_k[u], head * DQK + a * 64,
+                      batch * p.seq + kb * ATT_BN);
       };
       auto load_v = [&](int kb) {
-        mbar_arrive_expect_tx(bar_v, L::kVBytes);
+        const int u = kb & 1;
+        mbar_arrive_expect_tx(&bar_v[u], L::kVBytes);
         for (int a = 0; a < 2; ++a)
-          tma_load_2d(smem + L::kVOff + a * L::kVAtomBytes, &tmap_vt, bar_v, kb * ATT_BN + a * 64,
+          tma_load_2d(smem + L::kVOff + u * L::kVBytes + a * L::kVAtomBytes, &tmap_vt, &bar_v[u], kb * ATT_BN + a * 64,
                       (batch * p.heads + head) * p.dv + dv0);
       };
-      auto issue_s = [&]() {
+      auto issue_s = [&](int kb) {
+        const int u = kb & 1;
         constexpr uint32_t idesc_s = make_idesc_bf16(ATT_BM, ATT_BN);
 #pragma unroll
         for (int kk = 0; kk < DQK / 16; ++kk) {
           const uint32_t qa = smem_u32(smem + L::kQOff + (kk / 4) * ATOM_BYTES_128);
-          const uint32_t ka = smem_u32(smem + L::kKOff + (kk / 4) * ATOM_BYTES_128);
-          umma_bf16_ss(tmem_s, make_sw128_kmajor_desc(qa) + (uint64_t)((kk % 4) * 2),
+          const uint32_t ka = smem_u32(smem + L::kKOff + u * L::kQBytes + (kk / 4) * ATOM_BYTES_128);
+          umma_bf16_ss(tmem_base + (uint32_t)(u * ATT_BN), make_sw128_kmajor_desc(qa) + (uint64_t)((kk % 4) * 2),
                        make_sw128_kmajor_desc(ka) + (uint64_t)((kk % 4) * 2), idesc_s, kk > 0 ? 1u : 0u);
         }
-        umma_commit(bar_s_full);
+        umma_commit(&bar_s_full[u]);
       };
       mbar_arrive_expect_tx(bar_q, L::kQBytes);
       for (int a = 0; a < DQK / 64; ++a)
         tma_load_2d(smem + L::kQOff + a * ATOM_BYTES_128, &tmap_q, bar_q, head * DQK + a * 64, batch * p.seq + q0);
       load_k(0);
       load_v(0);
-      bool ok = mbar_wait_bounded(bar_q, 0, abort_flag) && mbar_wait_bounded(bar_k, 0, abort_flag);
+      if (n_kblocks > 1) {
+        load_k(1);
+        load_v(1);
+      }
+      bool ok = mbar_wait_bounded(bar_q, 0, abort_flag) && mbar_wait_bounded(&bar_k[0], 0, abort_flag);
       int where = 0;
       if (ok) {
         tc_fence_after();
-        issue_s();
+        issue_s(0);
       }
       for (int kb = 0; kb < n_kblocks && ok; ++kb) {
-        const uint32_t par = kb & 1;
+        const int u = kb & 1;
+        const uint32_t ph = (kb >> 1) & 1;  // phase of this block's use of buffer u
         const bool more = kb + 1 < n_kblocks;
-        where = 10 * kb + 1;
-        ok = mbar_wait_bounded(bar_s_full, par, abort_flag);  // S(kb) computed: the K buffer is free
-        if (!ok) break;
-        if (more) load_k(kb + 1);
-        where = 10 * kb + 2;
-        ok = mbar_wait_bounded(bar_s_free, par, abort_flag);  // every row holds S(kb) in registers
-        if (ok && more) ok = mbar_wait_bounded(bar_k, par ^ 1, abort_flag);
-        if (!ok) break;
         if (more) {
+          // S(kb+1): its K block has landed and the rows have released the S buffer it overwrites (block kb - 1)
+          where = 10 * kb + 1;
+          ok = mbar_wait_bounded(&bar_k[u ^ 1], ((kb + 1) >> 1) & 1, abort_flag);
+          if (ok && kb >= 1) ok = mbar_wait_bounded(&bar_s_free[u ^ 1], ((kb - 1) >> 1) & 1, abort_flag);
+          if (!ok) break;
           tc_fence_after();
-          issue_s();
+          issue_s(kb + 1);
         }
+        // K buffer u is free once S(kb) has been computed: fetch block kb + 2 into it
+        where = 10 * kb + 2;
+        ok = mbar_wait_bounded(&bar_s_full[u], ph, abort_flag);
+        if (!ok) break;
+        if (kb + 2 < n_kblocks) load_k(kb + 2);
+        // P V (kb)
         where = 10 * kb + 3;
-        ok = mbar_wait_bounded(bar_p_full, par, abort_flag) && mbar_wait_bounded(bar_v, par, abort_flag);
+        ok = mbar_wait_bounded(&bar_p_full[u], ph, abort_flag) && mbar_wait_bounded(&bar_v[u], ph, abort_flag);
         if (!ok) break;
         tc_fence_after();
         constexpr uint32_t idesc_o = make_idesc_bf16(ATT_BM, DV);
 #pragma unroll
         for (int kk = 0; kk < ATT_BN / 16; ++kk) {
-          const uint32_t pa = smem_u32(smem + L::kPOff + (kk / 4) * ATOM_BYTES_128);
-          const uint32_t va = smem_u32(smem + L::kVOff + (kk / 4) * L::kVAtomBytes);
+          const uint32_t pa = smem_u32(smem + L::kPOff + u * L::kPBytes + (kk / 4) * ATOM_BYTES_128);
+          const uint32_t va = smem_u32(smem + L::kVOff + u * L::kVBytes + (kk / 4) * L::kVAtomBytes);
           umma_bf16_ss(tmem_o, make_sw128_kmajor_desc(pa) + (uint64_t)((kk % 4) * 2),
                        make_sw128_kmajor_desc(va) + (uint64_t)((kk % 4) * 2), idesc_o, (kb > 0 || kk > 0) ? 1u : 0u);
         }
-        umma_commit(bar_pv_done);
-        if (more) {
+        umma_commit(&bar_pv_done[u]);
+        // the V buffer of the PREVIOUS block is certainly free by now (its P V ran before this one): refill it
+        if (kb >= 1 && kb + 1 < n_kblocks) {
           where = 10 * kb + 4;
-          ok = mbar_wait_bounded(bar_pv_done, par, abort_flag);  // P V (kb) has read V: load the next block's values
+          ok = mbar_wait_bounded(&bar_pv_done[u ^ 1], ((kb - 1) >> 1) & 1, abort_flag);
           if (!ok) break;
           load_v(kb + 1);
         }
@@ -207,17 +222,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     float m_ref = -INFINITY, l_run = 0.0f;
     bool ok = true;
     for (int kb = 0; kb < n_kblocks && ok; ++kb) {
+      const int u = kb & 1;
+      const uint32_t ph = (kb >> 1) & 1;
       const int k0 = kb * ATT_BN + (int)s_col;
-      const uint32_t par = kb & 1;
       // (a failed wait ends the loop for the whole warp: the TMEM accesses and votes below are warp-wide)
-      if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar_s_full, par, abort_flag))) { ok = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait_bounded(&bar_s_full[u], ph, abort_flag))) { ok = false; break; }
       tc_fence_after();
       uint32_t s[ATT_BN / 64][32];
 #pragma unroll
-      for (int c = 0; c < ATT_BN / 64; ++c) tmem_ld_32x32b_x32(tmem_s + lane_off + s_col + (uint32_t)(c * 32), s[c]);
+      for (int c = 0; c < ATT_BN / 64; ++c)
+        tmem_ld_32x32b_x32(tmem_base + (uint32_t)(u * ATT_BN) + lane_off + s_col + (uint32_t)(c * 32), s[c]);
       tmem_wait_ld();
       tc_fence_before();
-      mbar_arrive(bar_s_free);
+      mbar_arrive(&bar_s_free[u]);
       // masked raw scores and their maximum (only the diagonal and the last block have anything to mask)
       const bool need_mask = (k0 + ATT_BN / 2 - 1 > qpos) || (k0 + ATT_BN / 2 > p.seq);
       float m_raw = -INFINITY;
@@ -234,9 +251,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         }
       }
       // the other half of the row: exchange through shared memory, 64-thread barrier of the two warps of this quarter
-      xch[(par * 2 + half) * ATT_BM + row] = m_raw;
+      xch[(u * 2 + half) * ATT_BM + row] = m_raw;
       asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
-      const float m_blk = fmaxf(m_raw, xch[(par * 2 + (half ^ 1)) * ATT_BM + row]) * sc;  // sc > 0
+      const float m_blk = fmaxf(m_raw, xch[(u * 2 + (half ^ 1)) * ATT_BM + row]) * sc;  // sc > 0
       float alpha = 1.0f;
       bool rescale = false;
       if (m_blk > m_ref + kRescaleSlack || m_ref == -INFINITY) {
@@ -248,26 +265,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         }
       }
       const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
-      if (kb > 0) {
-        // P and the output accumulator belong to the tensor core until P V (kb - 1) has completed
-        if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar_pv_done, par ^ 1, abort_flag))) { ok = false; break; }
+      if (__any_sync(0xffffffffu, rescale)) {  // this warp's half of the output columns
+        // the accumulator belongs to the tensor core until P V (kb - 1) has completed
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(&bar_pv_done[u ^ 1], ((kb - 1) >> 1) & 1, abort_flag))) { ok = false; break; }
         tc_fence_after();
-        if (__any_sync(0xffffffffu, rescale)) {  // this warp's half of the output columns
 #pragma unroll 1
-          for (int c = 0; c < DV / 64; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(tmem_o + lane_off + o_col + (uint32_t)(c * 32), r);
-            tmem_wait_ld();
+        for (int c = 0; c < DV / 64; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(tmem_o + lane_off + o_col + (uint32_t)(c * 32), r);
+          tmem_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * alpha);
-            tmem_st_32x32b_x32(tmem_o + lane_off + o_col + (uint32_t)(c * 32), r);
-          }
-          tmem_wait_st();
+          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * alpha);
+          tmem_st_32x32b_x32(tmem_o + lane_off + o_col + (uint32_t)(c * 32), r);
         }
+        tmem_wait_st();
+      }
+      if (kb >= 2) {
+        // P buffer u was read by P V (kb - 2)
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(&bar_pv_done[u], ((kb - 2) >> 1) & 1, abort_flag))) { ok = false; break; }
       }
       l_run *= alpha;
       float l_blk = 0.0f;
-      uint8_t* atom = smem + L::kPOff + half * ATOM_BYTES_128;  // this half's 64 keys are one swizzle atom
+      uint8_t* atom = smem + L::kPOff + u * L::kPBytes + half * ATOM_BYTES_128;  // this half's 64 keys are one swizzle atom
 #pragma unroll
       for (int g = 0; g < ATT_BN / 16; ++g) {
         float pv[8];
@@ -276,19 +295,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           pv[t] = exp2f(fmaf(__uint_as_float(s[g / 4][(g % 4) * 8 + t]), sc, -m_use));
           l_blk += pv[t];
         }
-        uint4 u;
-        u.x = pack_bf16x2(pv[0], pv[1]);
-        u.y = pack_bf16x2(pv[2], pv[3]);
-        u.z = pack_bf16x2(pv[4], pv[5]);
-        u.w = pack_bf16x2(pv[6], pv[7]);
-        *reinterpret_cast<uint4*>(atom + sw128_chunk_off(row, g)) = u;
+        uint4 w;
+        w.x = pack_bf16x2(pv[0], pv[1]);
+        w.y = pack_bf16x2(pv[2], pv[3]);
+        w.z = pack_bf16x2(pv[4], pv[5]);
+        w.w = pack_bf16x2(pv[6], pv[7]);
+        *reinterpret_cast<uint4*>(atom + sw128_chunk_off(row, g)) = w;
       }
       l_run += l_blk;
       fence_proxy_async();  // the generic-proxy stores of P must be visible to the tensor core's reads
       tc_fence_before();
-      mbar_arrive(bar_p_full);
+      mbar_arrive(&bar_p_full[u]);
     }
-    ok = __all_sync(0xffffffffu, ok && mbar_wait_bounded(bar_pv_done, (n_kblocks - 1) & 1, abort_flag));
+    ok = __all_sync(0xffffffffu, ok && mbar_wait_bounded(&bar_pv_done[(n_kblocks - 1) & 1], ((n_kblocks - 1) >> 1) & 1, abort_flag));
     if (!ok) {
       report_status(p.status, kTimeoutTmemFull, row);
       *abort_flag = 1;
@@ -309,12 +328,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         if (row_ok) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
-            uint4 u;
-            u.x = pack_bf16x2(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
-            u.y = pack_bf16x2(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
-            u.z = pack_bf16x2(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
-            u.w = pack_bf16x2(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
-            *reinterpret_cast<uint4*>(dst + c * 32 + i) = u;
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+            w.y = pack_bf16x2(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+            w.z = pack_bf16x2(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+            w.w = pack_bf16x2(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + i) = w;
           }
         }
       }
@@ -331,7 +350,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   }
   if (warp == 8) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 256);
+    tmem_dealloc(tmem_base, 512);
   }
 }
 
@@ -339,6 +358,7 @@ template <int DQK, int DV>
 static cudaError_t attn_fwd_variant(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tvt,
                                     const AttnParams& p, cudaStream_t stream) {
   using L = AttnSmem<DQK, DV>;
+  static_assert(L::kDynamicBytes <= 232448, "shared memory of one CTA exceeds 227 KB");
   auto kern = attn_fwd_kernel<DQK, DV>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
   if (e != cudaSuccess) return e;
@@ -375,15 +395,19 @@ __device__ __forceinline__ void issue_mma_atoms(uint32_t tmem_d, uint32_t a_base
 
 template <int DQK>
 struct BwdDqSmem {
+  // with 64-wide queries there is room for two K / K^T buffers: the next key block's tiles (and the first dO / V atom)
+  // are fetched while the threads work on the current one
+  static constexpr bool kDouble = DQK == 64;
+  static constexpr int kKBufs = kDouble ? 2 : 1;
   static constexpr int kQBytes = (DQK / 64) * ATOM_BYTES_128;
   static constexpr int kQOff = 0;
   static constexpr int kKOff = kQOff + kQBytes;
   static constexpr int kKtAtomBytes = DQK * 128;
-  static constexpr int kKtOff = kKOff + kQBytes;
-  static constexpr int kDsOff = kKtOff + 2 * kKtAtomBytes;
+  static constexpr int kKtOff = kKOff + kKBufs * kQBytes;
+  static constexpr int kDsOff = kKtOff + kKBufs * 2 * kKtAtomBytes;
   static constexpr int kRingOff = kDsOff + 2 * ATOM_BYTES_128;  // 2 stages x {dO atom, V atom}
   static constexpr int kBarOff = kRingOff + 4 * ATOM_BYTES_128;
-  static constexpr int kNumBars = 8;
+  static constexpr int kNumBars = 9;
   static constexpr int kTmemPtrOff = kBarOff + kNumBars * 8;
   static constexpr int kAbortOff = kTmemPtrOff + 4;
   static constexpr int kDynamicBytes = kAbortOff + 4 + 1024;
@@ -391,18 +415,22 @@ struct BwdDqSmem {
 
 template <int DQK, int DVC>
 struct BwdDkvSmem {
+  // with 64-wide queries there is room for two Q buffers: the next query block's Q tile (and the first V / dO atom) are
+  // fetched while the threads work on the current one
+  static constexpr bool kDouble = DQK == 64;
+  static constexpr int kQBufs = kDouble ? 2 : 1;
   static constexpr int kKBytes = (DQK / 64) * ATOM_BYTES_128;
   static constexpr int kKOff = 0;
-  static constexpr int kQOff = kKOff + kKBytes;              // Q_i, later Q_i^T (same size)
+  static constexpr int kQOff = kKOff + kKBytes;              // Q_i, later Q_i^T (same size), per buffer
   static constexpr int kQtAtomBytes = DQK * 128;
-  static constexpr int kRingOff = kQOff + kKBytes;           // 2 stages x {V atom, dO atom}; later dO^T chunk
+  static constexpr int kRingOff = kQOff + kQBufs * kKBytes;  // 2 stages x {V atom, dO atom}; later dO^T chunk
   static constexpr int kDotAtomBytes = DVC * 128;
   static constexpr int kPtOff = kRingOff + 4 * ATOM_BYTES_128;
   static constexpr int kDstOff = kPtOff + 2 * ATOM_BYTES_128;
   static constexpr int kLseOff = kDstOff + 2 * ATOM_BYTES_128;
   static constexpr int kDeltaOff = kLseOff + 128 * 4;
   static constexpr int kBarOff = kDeltaOff + 128 * 4;
-  static constexpr int kNumBars = 8;
+  static constexpr int kNumBars = 10;
   static constexpr int kTmemPtrOff = kBarOff + kNumBars * 8;
   static constexpr int kAbortOff = kTmemPtrOff + 4;
   static constexpr int kDynamicBytes = kAbortOff + 4 + 1024;
@@ -420,11 +448,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
   uint64_t* bar_q = bars + 0;
-  uint64_t* bar_k = bars + 1;
-  uint64_t* bar_mma1 = bars + 2;
-  uint64_t* bar_mma2 = bars + 3;
-  uint64_t* ring_full = bars + 4;  // [2]
-  uint64_t* ring_free = bars + 6;  // [2]
+  uint64_t* bar_k = bars + 1;      // [2]
+  uint64_t* bar_mma1 = bars + 3;
+  uint64_t* bar_mma2 = bars + 4;
+  uint64_t* ring_full = bars + 5;  // [2]
+  uint64_t* ring_free = bars + 7;  // [2]
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + L::kTmemPtrOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOff);
 
@@ -470,33 +498,42 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   for (int kb = 0; kb < n_kblocks && ok; ++kb) {
     const int k0 = kb * ATT_BN;
     const uint32_t parity = kb & 1;
+    const int ub = L::kDouble ? (kb & 1) : 0;  // K / K^T buffer of this key block
     if (threadIdx.x == 0) {
       bool got = true;
-      mbar_arrive_expect_tx(bar_k, L::kQBytes + 2 * L::kKtAtomBytes);
-      for (int a = 0; a < DQK / 64; ++a)
-        tma_load_2d(smem + L::kKOff + a * ATOM_BYTES_128, &tmap_k, bar_k, head * DQK + a * 64, batch * p.seq + k0);
-      for (int a = 0; a < 2; ++a)
-        tma_load_2d(smem + L::kKtOff + a * L::kKtAtomBytes, &tmap_kt, bar_k, k0 + a * 64, (batch * p.heads + head) * DQK);
+      auto load_block = [&](int blk) {
+        const int u = L::kDouble ? (blk & 1) : 0;
+        mbar_arrive_expect_tx(&bar_k[u], L::kQBytes + 2 * L::kKtAtomBytes);
+        for (int a = 0; a < DQK / 64; ++a)
+          tma_load_2d(smem + L::kKOff + u * L::kQBytes + a * ATOM_BYTES_128, &tmap_k, &bar_k[u], head * DQK + a * 64,
+                      batch * p.seq + blk * ATT_BN);
+        for (int a = 0; a < 2; ++a)
+          tma_load_2d(smem + L::kKtOff + (u * 2 + a) * L::kKtAtomBytes, &tmap_kt, &bar_k[u], blk * ATT_BN + a * 64,
+                      (batch * p.heads + head) * DQK);
+      };
       // dP = dO V^T over the whole value width: atoms through a two-stage ring, the next load in flight during the MMAs
-      auto load_atom = [&](uint32_t n, int a) -> bool {
+      auto load_atom = [&](uint32_t n, int a, int blk) -> bool {
         const int st = n & 1;
         if (!mbar_wait_bounded(&ring_free[st], ((n >> 1) & 1) ^ 1, abort_flag)) return false;
         uint8_t* base = smem + L::kRingOff + st * 2 * ATOM_BYTES_128;
         mbar_arrive_expect_tx(&ring_full[st], 2 * ATOM_BYTES_128);
         tma_load_2d(base, &tmap_do, &ring_full[st], head * p.dv + a * 64, batch * p.seq + q0);
-        tma_load_2d(base + ATOM_BYTES_128, &tmap_v, &ring_full[st], head * p.dv + a * 64, batch * p.seq + k0);
+        tma_load_2d(base + ATOM_BYTES_128, &tmap_v, &ring_full[st], head * p.dv + a * 64, batch * p.seq + blk * ATT_BN);
         return true;
       };
-      got = load_atom(ring_n, 0);
+      if (kb == 0 || !L::kDouble) {  // (double-buffered: issued during the previous block, see below)
+        load_block(kb);
+        got = load_atom(ring_n, 0, kb);
+      }
       if (kb == 0) got = got && mbar_wait_bounded(bar_q, 0, abort_flag);
-      got = got && mbar_wait_bounded(bar_k, parity, abort_flag);
+      got = got && mbar_wait_bounded(&bar_k[ub], L::kDouble ? ((kb >> 1) & 1) : parity, abort_flag);
       if (got) {
         tc_fence_after();
-        issue_mma_atoms(tmem_s, smem_u32(smem + L::kQOff), ATOM_BYTES_128, smem_u32(smem + L::kKOff), ATOM_BYTES_128,
-                        DQK / 16, make_idesc_bf16(ATT_BM, ATT_BN), false);
+        issue_mma_atoms(tmem_s, smem_u32(smem + L::kQOff), ATOM_BYTES_128, smem_u32(smem + L::kKOff + ub * L::kQBytes),
+                        ATOM_BYTES_128, DQK / 16, make_idesc_bf16(ATT_BM, ATT_BN), false);
         for (int a = 0; a < dv_atoms && got; ++a) {
           const uint32_t n = ring_n + a;
-          if (a + 1 < dv_atoms) got = load_atom(n + 1, a + 1);
+          if (a + 1 < dv_atoms) got = load_atom(n + 1, a + 1, kb);
           got = got && mbar_wait_bounded(&ring_full[n & 1], (n >> 1) & 1, abort_flag);
           if (!got) break;
           tc_fence_after();
@@ -511,6 +548,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         *abort_flag = 1;
       }
       umma_commit(bar_mma1);
+      if (L::kDouble && got && kb + 1 < n_kblocks) {
+        // next key block: its K / K^T buffer was last read by the MMAs of block kb - 1 (complete); the ring stage
+        // frees up when this block's last dP MMAs have read it
+        load_block(kb + 1);
+        if (!load_atom(ring_n, 0, kb + 1)) {
+          report_status(p.status, kTimeoutEmptyBarrier, kb);
+          *abort_flag = 1;
+        }
+      }
     }
     if (!mbar_wait_bounded(bar_mma1, parity, abort_flag)) {
       report_status(p.status, kTimeoutTmemFull, kb);
@@ -552,8 +598,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     if (threadIdx.x == 0) {
       tc_fence_after();
       // dQ += dS [128 q x 128 keys] * (K^T [DQK x 128 keys])^T
-      issue_mma_atoms(tmem_dq, smem_u32(smem + L::kDsOff), ATOM_BYTES_128, smem_u32(smem + L::kKtOff), L::kKtAtomBytes,
-                      ATT_BN / 16, make_idesc_bf16(ATT_BM, DQK), kb > 0);
+      issue_mma_atoms(tmem_dq, smem_u32(smem + L::kDsOff), ATOM_BYTES_128,
+                      smem_u32(smem + L::kKtOff + ub * 2 * L::kKtAtomBytes), L::kKtAtomBytes, ATT_BN / 16,
+                      make_idesc_bf16(ATT_BM, DQK), kb > 0);
       umma_commit(bar_mma2);
     }
     if (!mbar_wait_bounded(bar_mma2, parity, abort_flag)) {
@@ -604,11 +651,12 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
   uint64_t* bar_k = bars + 0;
-  uint64_t* bar_q = bars + 1;
-  uint64_t* bar_mma1 = bars + 2;
-  uint64_t* bar_mma2 = bars + 3;
-  uint64_t* ring_full = bars + 4;
-  uint64_t* ring_free = bars + 6;
+  uint64_t* bar_q = bars + 1;      // [2] Q_i loads, one per buffer
+  uint64_t* bar_t = bars + 3;      // Q_i^T / dO_i^T loads
+  uint64_t* bar_mma1 = bars + 4;
+  uint64_t* bar_mma2 = bars + 5;
+  uint64_t* ring_full = bars + 6;  // [2]
+  uint64_t* ring_free = bars + 8;  // [2]
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + L::kTmemPtrOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOff);
   float* s_lse = reinterpret_cast<float*>(smem + L::kLseOff);
@@ -664,32 +712,39 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
       s_lse[row] = qp < p.seq ? p.lse[o] * 1.4426950408889634f : INFINITY;
       s_delta[row] = qp < p.seq ? p.delta[o] : 0.0f;
     }
+    const int uq = L::kDouble ? (it & 1) : 0;  // Q buffer of this query block
+    auto load_q = [&](int blk, int u) {
+      mbar_arrive_expect_tx(&bar_q[u], L::kKBytes);
+      for (int a = 0; a < DQK / 64; ++a)
+        tma_load_2d(smem + L::kQOff + u * L::kKBytes + a * ATOM_BYTES_128, &tmap_q, &bar_q[u], head * DQK + a * 64,
+                    batch * p.seq + blk * ATT_BM);
+    };
+    auto load_atom = [&](uint32_t n, int a, int blk) -> bool {
+      const int st = n & 1;
+      if (!mbar_wait_bounded(&ring_free[st], ((n >> 1) & 1) ^ 1, abort_flag)) return false;
+      uint8_t* base = smem + L::kRingOff + st * 2 * ATOM_BYTES_128;
+      mbar_arrive_expect_tx(&ring_full[st], 2 * ATOM_BYTES_128);
+      tma_load_2d(base, &tmap_v, &ring_full[st], head * p.dv + a * 64, batch * p.seq + k0);
+      tma_load_2d(base + ATOM_BYTES_128, &tmap_do, &ring_full[st], head * p.dv + a * 64, batch * p.seq + blk * ATT_BM);
+      return true;
+    };
     if (threadIdx.x == 0) {
       bool got = true;
-      mbar_arrive_expect_tx(bar_q, L::kKBytes);
-      for (int a = 0; a < DQK / 64; ++a)
-        tma_load_2d(smem + L::kQOff + a * ATOM_BYTES_128, &tmap_q, bar_q, head * DQK + a * 64, batch * p.seq + q0);
-      auto load_atom = [&](uint32_t n, int a) -> bool {
-        const int st = n & 1;
-        if (!mbar_wait_bounded(&ring_free[st], ((n >> 1) & 1) ^ 1, abort_flag)) return false;
-        uint8_t* base = smem + L::kRingOff + st * 2 * ATOM_BYTES_128;
-        mbar_arrive_expect_tx(&ring_full[st], 2 * ATOM_BYTES_128);
-        tma_load_2d(base, &tmap_v, &ring_full[st], head * p.dv + a * 64, batch * p.seq + k0);
-        tma_load_2d(base + ATOM_BYTES_128, &tmap_do, &ring_full[st], head * p.dv + a * 64, batch * p.seq + q0);
-        return true;
-      };
-      got = load_atom(ring_n, 0);
+      if (it == 0 || !L::kDouble) {  // (double-buffered: issued during the previous block, see below)
+        load_q(qb, uq);
+        got = load_atom(ring_n, 0, qb);
+      }
       if (it == 0) got = got && mbar_wait_bounded(bar_k, 0, abort_flag);
-      got = got && mbar_wait_bounded(bar_q, 0 ^ ((2 * it) & 1), abort_flag);  // bar_q completes twice per iteration
+      got = got && mbar_wait_bounded(&bar_q[uq], L::kDouble ? ((it >> 1) & 1) : parity, abort_flag);
       if (got) {
         tc_fence_after();
         // S^T = K_j Q_i^T
-        issue_mma_atoms(tmem_st, smem_u32(smem + L::kKOff), ATOM_BYTES_128, smem_u32(smem + L::kQOff), ATOM_BYTES_128,
-                        DQK / 16, make_idesc_bf16(ATT_BM, ATT_BN), false);
+        issue_mma_atoms(tmem_st, smem_u32(smem + L::kKOff), ATOM_BYTES_128, smem_u32(smem + L::kQOff + uq * L::kKBytes),
+                        ATOM_BYTES_128, DQK / 16, make_idesc_bf16(ATT_BM, ATT_BN), false);
         // dP^T = V_j dO_i^T over the whole value width
         for (int a = 0; a < dv_atoms && got; ++a) {
           const uint32_t n = ring_n + a;
-          if (a + 1 < dv_atoms) got = load_atom(n + 1, a + 1);
+          if (a + 1 < dv_atoms) got = load_atom(n + 1, a + 1, qb);
           got = got && mbar_wait_bounded(&ring_full[n & 1], (n >> 1) & 1, abort_flag);
           if (!got) break;
           tc_fence_after();
@@ -714,20 +769,29 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     if (!ok) break;
     tc_fence_after();
 
-    // Q_i and the ring are free now (their MMAs completed): fetch Q_i^T and the dO_i^T chunk while the threads work.
+    // Q_i and the ring are free now (their MMAs completed): fetch Q_i^T and the dO_i^T chunk while the threads work. The
+    // chunk goes into the ring stage that the NEXT query block's first atom does not use, so that atom (and the next Q
+    // tile, into the other Q buffer) can be fetched now as well.
+    const int dot_stage = L::kDouble ? (int)((ring_n & 1) ^ 1) : 0;
     if (threadIdx.x == 0) {
-      // both ring stages must be idle before the dO^T chunk overwrites them (their last MMAs were committed above)
+      // both ring stages must be idle before anything overwrites them (their last MMAs were committed above)
       bool got = mbar_wait_bounded(&ring_free[0], (((ring_n + 1) >> 1) & 1) ^ 1, abort_flag) &&
                  mbar_wait_bounded(&ring_free[1], ((ring_n >> 1) & 1) ^ 1, abort_flag);
       if (got) {
-        mbar_arrive_expect_tx(bar_q, (do_dk ? 2 * L::kQtAtomBytes : 0) + 2 * L::kDotAtomBytes);
+        mbar_arrive_expect_tx(bar_t, (do_dk ? 2 * L::kQtAtomBytes : 0) + 2 * L::kDotAtomBytes);
         if (do_dk)
           for (int a = 0; a < 2; ++a)
-            tma_load_2d(smem + L::kQOff + a * L::kQtAtomBytes, &tmap_qt, bar_q, q0 + a * 64, (batch * p.heads + head) * DQK);
+            tma_load_2d(smem + L::kQOff + uq * L::kKBytes + a * L::kQtAtomBytes, &tmap_qt, bar_t, q0 + a * 64,
+                        (batch * p.heads + head) * DQK);
         for (int a = 0; a < 2; ++a)
-          tma_load_2d(smem + L::kRingOff + a * L::kDotAtomBytes, &tmap_dot, bar_q, q0 + a * 64,
-                      (batch * p.heads + head) * p.dv + dv0);
-      } else {
+          tma_load_2d(smem + L::kRingOff + dot_stage * 2 * ATOM_BYTES_128 + a * L::kDotAtomBytes, &tmap_dot, bar_t,
+                      q0 + a * 64, (batch * p.heads + head) * p.dv + dv0);
+        if (L::kDouble && qb + 1 < n_blocks) {
+          load_q(qb + 1, uq ^ 1);  // that buffer held Q^T of block qb - 1, read by MMAs that have completed
+          got = load_atom(ring_n, 0, qb + 1);
+        }
+      }
+      if (!got) {
         report_status(p.status, kTimeoutEmptyBarrier, it);
         *abort_flag = 1;
       }
@@ -771,16 +835,17 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 0) {
-      bool got = (*abort_flag == 0) && mbar_wait_bounded(bar_q, 1 ^ ((2 * it) & 1), abort_flag);
+      bool got = (*abort_flag == 0) && mbar_wait_bounded(bar_t, parity, abort_flag);
       if (got) {
         tc_fence_after();
         // dV += P^T [128 keys x 128 q] * (dO^T chunk [DVC x 128 q])^T
-        issue_mma_atoms(tmem_dv, smem_u32(smem + L::kPtOff), ATOM_BYTES_128, smem_u32(smem + L::kRingOff), L::kDotAtomBytes,
-                        ATT_BM / 16, make_idesc_bf16(ATT_BM, DVC), it > 0);
+        issue_mma_atoms(tmem_dv, smem_u32(smem + L::kPtOff), ATOM_BYTES_128,
+                        smem_u32(smem + L::kRingOff + dot_stage * 2 * ATOM_BYTES_128), L::kDotAtomBytes, ATT_BM / 16,
+                        make_idesc_bf16(ATT_BM, DVC), it > 0);
         // dK += dS^T [128 keys x 128 q] * (Q^T [DQK x 128 q])^T
         if (do_dk)
-          issue_mma_atoms(tmem_dk, smem_u32(smem + L::kDstOff), ATOM_BYTES_128, smem_u32(smem + L::kQOff), L::kQtAtomBytes,
-                          ATT_BM / 16, make_idesc_bf16(ATT_BM, DQK), it > 0);
+          issue_mma_atoms(tmem_dk, smem_u32(smem + L::kDstOff), ATOM_BYTES_128, smem_u32(smem + L::kQOff + uq * L::kKBytes),
+                          L::kQtAtomBytes, ATT_BM / 16, make_idesc_bf16(ATT_BM, DQK), it > 0);
       } else {
         report_status(p.status, kTimeoutFullBarrier, 2000 + it);
         *abort_flag = 1;
@@ -876,14 +941,20 @@ int attn_bwd_launch(const CUtensorMap* maps_dq, const CUtensorMap* maps_dkv, con
 }
 
 
+// Value columns per CTA of the forward kernel: with 128-wide queries the double-buffered tiles only fit for 64.
+int attn_fwd_value_chunk(int dqk, int dv) {
+  const int c = attn_value_chunk(dv);
+  return (dqk == 128 && c == 128) ? 64 : c;
+}
+
 int attn_fwd_launch(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tvt, const AttnParams& p,
                     cudaStream_t stream) {
-  const int dvc = attn_value_chunk(p.dv);
+  const int dvc = attn_fwd_value_chunk(p.dqk, p.dv);
   if (dvc == 0 || (p.dqk != 64 && p.dqk != 128) || p.seq % 8 != 0 || p.batch > 65535 || p.heads * (p.dv / dvc) > 65535)
     return (int)cudaErrorInvalidValue;
   cudaError_t e;
   if (p.dqk == 64) e = dvc == 128 ? attn_fwd_variant<64, 128>(tq, tk, tvt, p, stream) : attn_fwd_variant<64, 64>(tq, tk, tvt, p, stream);
-  else e = dvc == 128 ? attn_fwd_variant<128, 128>(tq, tk, tvt, p, stream) : attn_fwd_variant<128, 64>(tq, tk, tvt, p, stream);
+  else e = attn_fwd_variant<128, 64>(tq, tk, tvt, p, stream);
   return (int)e;
 }
 

@@ -425,7 +425,7 @@ void attn_fwd(const Tensor& q, const Tensor& k, const Tensor& vt, const Tensor& 
   TORCH_CHECK(vt.size(0) == p.batch && vt.size(1) == p.heads && vt.size(3) == p.seq, "vt must be [b, h, dv, s]");
   TORCH_CHECK(out.dim() == 4 && out.size(0) == p.batch && out.size(1) == p.seq && out.size(2) == p.heads && out.size(3) == p.dv,
               "out must be [b, s, h, dv]");
-  const int dvc = lmsae::attn_value_chunk(p.dv);
+  const int dvc = lmsae::attn_fwd_value_chunk(p.dqk, p.dv);
   TORCH_CHECK(dvc != 0 && (p.dqk == 64 || p.dqk == 128) && p.seq % 8 == 0, "attn_fwd: d_qk in {64, 128}, d_v % 64 == 0, seq % 8 == 0");
   if (lse.has_value()) {
     CHECK_T(*lse, torch::kFloat32);

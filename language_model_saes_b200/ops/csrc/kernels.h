@@ -153,6 +153,7 @@ struct AttnBwdParams {
 };
 int attn_bwd_launch(const CUtensorMap* maps_dq, const CUtensorMap* maps_dkv, const AttnBwdParams& p, cudaStream_t stream);
 int attn_value_chunk(int dv);
+int attn_fwd_value_chunk(int dqk, int dv);
 int attn_fwd_launch(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tvt, const AttnParams& p,
                     cudaStream_t stream);
 

@@ -58,6 +58,16 @@ def main(argv=None):
             t_o = _timeit(lambda: A.causal_attention_fwd(q, k, v, scale), a.iters, a.warmup, flush)
             t_r = _timeit(sdpa, a.iters, a.warmup, flush)
         tag = f"b{b}_s{s}_h{h}_dqk{dqk}_dv{dv}"
+        with torch.no_grad():  # the kernel alone, operands already laid out (values transposed to [b, h, d_v, s])
+            vt = v.detach().permute(0, 2, 3, 1).contiguous()
+            out = torch.empty(b, s, h, dv, dtype=torch.bfloat16, device=dev)
+            lse = torch.empty(b, h, s, dtype=torch.float32, device=dev)
+            st = K.status_buffer(dev)
+            qd, kd = q.detach(), k.detach()
+            t_k = _timeit(lambda: K._ext().attn_fwd(qd, kd, vt, out, lse, scale, st), a.iters, a.warmup, flush)
+            t_t = _timeit(lambda: v.detach().permute(0, 2, 3, 1).contiguous(), a.iters, a.warmup, flush)
+        print(json.dumps({"case": f"attention_fwd_kernel_only_{tag}", "ms_kernel": round(t_k[0], 4), "ms_value_transpose": round(t_t[0], 4),
+                          "tflops_kernel": round(flops_fwd / t_k[0] / 1e9, 1)}), flush=True)  # fmt: skip
         report(f"attention_fwd_{tag}", t_o, t_r, tflops_ours=round(flops_fwd / t_o[0] / 1e9, 1),
                tflops_reference_path=round(flops_fwd / t_r[0] / 1e9, 1))  # fmt: skip
         if a.case != "attn_fwd":
