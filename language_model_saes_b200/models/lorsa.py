@@ -51,6 +51,10 @@ class LorsaConfig(SparseDictionaryConfig):
     old_context_len: int = 2048
     n_ctx: int
     attn_scale: float | None = None
+    attention_kernel: Literal["library", "tensor_core"] = "library"
+    """``tensor_core``: this package's tcgen05 kernels (``ops/csrc/attention.cu``: forward, dQ, dK/dV; bf16 models, d_qk 64
+    or 128, OV group a multiple of 64). ``library``: ``scaled_dot_product_attention``, which on a B200 is currently the
+    faster of the two at the shapes measured (see ``ops/microbench_families.py --case attn``)."""
     use_post_qk_ln: bool = False
     normalization_type: Literal["LN", "RMS"] | None = None
     eps: float = 1e-6
@@ -391,7 +395,7 @@ class LowRankSparseAttention(SparseDictionary):
         """Fused causal attention: one attention head per QK head whose value / output width is the OV group."""
         b, s, h, _ = q.shape
         vg = v.view(b, s, h, -1)
-        if q.dtype == torch.bfloat16 and attention_kernels.supported(q, vg):
+        if self.cfg.attention_kernel == "tensor_core" and q.dtype == torch.bfloat16 and attention_kernels.supported(q, vg):
             # tcgen05 kernels (forward, dQ, dK/dV) that take a value width different from the query/key width
             z = attention_kernels.causal_attention(q, k, vg, 1 / self.attn_scale)
             return z.reshape(b, s, -1)

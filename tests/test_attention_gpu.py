@@ -56,7 +56,7 @@ def test_lorsa_encode_uses_the_tensor_core_attention_and_matches_the_score_path(
     torch.manual_seed(0)
     cfg = LorsaConfig(hook_point_in="in", hook_point_out="out", d_model=128, expansion_factor=4, n_qk_heads=4, d_qk_head=64,
                       n_ctx=64, act_fn="relu", device="cuda", dtype=torch.bfloat16, norm_activation="inference",
-                      positional_embedding_type="rotary", rotary_dim=64)  # fmt: skip
+                      positional_embedding_type="rotary", rotary_dim=64, attention_kernel="tensor_core")  # fmt: skip
     m = LowRankSparseAttention(cfg)
     m.init_parameters(encoder_uniform_bound=0.2, decoder_uniform_bound=0.2, init_log_jumprelu_threshold_value=0.0)
     x = torch.randn(2, 64, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
