@@ -359,12 +359,20 @@ class LowRankSparseAttention(SparseDictionary):
         self.cfg.norm_activation = "inference"
 
     # ---- forward -----------------------------------------------------------------------------
-    def _compute_qkv(self, x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-        """``x [b, s, d]`` -> ``q, k [b, s, nqk_l, dqk]``, ``v [b, s, F_l]``."""
+    def _tensor_core_attention(self, x: torch.Tensor) -> bool:
+        """Whether the forward pass of ``x [b, s, d]`` goes through this package's attention kernels."""
+        group = self.W_V.shape[0] // max(self.n_qk_heads_local, 1)
+        return (
+            self.cfg.attention_kernel == "tensor_core" and x.is_cuda and x.ndim == 3 and self.W_Q.dtype == torch.bfloat16
+            and self.cfg.d_qk_head in (64, 128) and group % 64 == 0 and x.shape[1] % 8 == 0
+        )  # fmt: skip
+
+    def _compute_qkv(self, x: torch.Tensor, with_v: bool = True) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor | None]:
+        """``x [b, s, d]`` -> ``q, k [b, s, nqk_l, dqk]``, ``v [b, s, F_l]`` (None when not wanted)."""
         x = x.to(self.W_Q.dtype)
         q = self.hook_q(torch.einsum("bsd,hdq->bshq", x, self.W_Q) + self.b_Q)
         k = self.hook_k(torch.einsum("bsd,hdq->bshq", x, self.W_K) + self.b_K)
-        v = x @ self.W_V.T + self.b_V
+        v = x @ self.W_V.T + self.b_V if with_v else None
         if self.cfg.use_post_qk_ln:
             q, k = self.ln_q(q), self.ln_k(k)
         if self.cfg.positional_embedding_type == "rotary":
@@ -388,17 +396,19 @@ class LowRankSparseAttention(SparseDictionary):
         return z.reshape(b, s, -1)
 
     def compute_hidden_pre(self, x: torch.Tensor) -> torch.Tensor:
-        q, k, v = self._compute_qkv(x)
-        return self._attend(q, k, v)
+        q, k, v = self._compute_qkv(x, with_v=not self._tensor_core_attention(x))
+        return self._attend(q, k, v, x)
 
-    def _attend(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+    def _attend(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, x: torch.Tensor | None = None) -> torch.Tensor:
         """Fused causal attention: one attention head per QK head whose value / output width is the OV group."""
         b, s, h, _ = q.shape
+        if v is None:
+            # tcgen05 kernels (forward, dQ, dK/dV) that take a value width different from the query/key width; the values
+            # are produced straight in the layout the forward kernel reads, [b, h, group, s]: one GEMM, no transpose pass
+            assert x is not None
+            vt = (torch.matmul(self.W_V, x.to(self.W_V.dtype).transpose(1, 2)) + self.b_V[:, None]).view(b, h, -1, s)
+            return attention_kernels.causal_attention(q, k, None, 1 / self.attn_scale, vt=vt).reshape(b, s, -1)
         vg = v.view(b, s, h, -1)
-        if self.cfg.attention_kernel == "tensor_core" and q.dtype == torch.bfloat16 and attention_kernels.supported(q, vg):
-            # tcgen05 kernels (forward, dQ, dK/dV) that take a value width different from the query/key width
-            z = attention_kernels.causal_attention(q, k, vg, 1 / self.attn_scale)
-            return z.reshape(b, s, -1)
         value = vg.permute(0, 2, 1, 3)
         z = F.scaled_dot_product_attention(q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), value,
                                            scale=1 / self.attn_scale, is_causal=True)  # fmt: skip
@@ -414,12 +424,12 @@ class LowRankSparseAttention(SparseDictionary):
         **kwargs,
     ):
         """``x [batch, seq, d_model]`` -> sparse OV-head activations ``[batch, seq, F_l]``."""
-        q, k, v = self._compute_qkv(x)
         pattern = scores = None
         slow = return_attention_pattern or return_attention_score or hook_attn_scores
         slow = slow or bool(self.hook_attn_pattern.fwd_hooks or self.hook_attn_score.fwd_hooks)
+        q, k, v = self._compute_qkv(x, with_v=slow or not self._tensor_core_attention(x))
         if not slow:
-            hidden_pre = self._attend(q, k, v)
+            hidden_pre = self._attend(q, k, v, x)
         else:
             scores = torch.einsum("bqhd,bkhd->bhqk", q, k) / self.attn_scale
             scores = self.hook_attn_score(self._apply_causal_mask(scores))

@@ -56,10 +56,16 @@ class CausalAttention(torch.autograd.Function):
     rounded to bf16 for the tensor cores; gradients are accumulated in fp32 and returned in the inputs' dtypes."""
 
     @staticmethod
-    def forward(ctx, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float) -> torch.Tensor:
-        q16, k16, v16 = (t.detach().to(torch.bfloat16).contiguous() for t in (q, k, v))
+    def forward(ctx, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, v_is_transposed: bool = False) -> torch.Tensor:
+        q16, k16 = (t.detach().to(torch.bfloat16).contiguous() for t in (q, k))
         b, s, h, _ = q16.shape
-        vt = v16.permute(0, 2, 3, 1).contiguous()
+        if v_is_transposed:  # the caller produced V^T [b, h, d_v, s] directly (no transpose pass in the forward)
+            vt = v.detach().to(torch.bfloat16).contiguous()
+            v16 = vt.permute(0, 3, 1, 2).contiguous()  # the backward kernels read V rows ([b, s, h, d_v])
+        else:
+            v16 = v.detach().to(torch.bfloat16).contiguous()
+            vt = v16.permute(0, 2, 3, 1).contiguous()
+        ctx.v_is_transposed = v_is_transposed
         out = torch.empty(b, s, h, v16.shape[-1], dtype=torch.bfloat16, device=q.device)
         lse = torch.empty(b, h, s, dtype=torch.float32, device=q.device)
         K._ext().attn_fwd(q16, k16, vt, out, lse, float(scale), K.status_buffer(q.device))
@@ -81,13 +87,22 @@ class CausalAttention(torch.autograd.Function):
         ext = K._ext()
         ext.launches += 1  # two kernels in one entry point
         ext.attn_bwd(q16, k16, v16, do16, qt, kt, dot, lse, delta, dq, dk, dv, ctx.scale, K.status_buffer(q16.device))
-        return dq.to(ctx.dtypes[0]), dk.to(ctx.dtypes[1]), dv.to(ctx.dtypes[2]), None
+        if ctx.v_is_transposed:
+            dv = dv.permute(0, 2, 3, 1)
+        return dq.to(ctx.dtypes[0]), dk.to(ctx.dtypes[1]), dv.to(ctx.dtypes[2]), None, None
 
 
-def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float | None = None) -> torch.Tensor:
+def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor | None = None, scale: float | None = None,
+                     vt: torch.Tensor | None = None) -> torch.Tensor:  # fmt: skip
     """Differentiable causal attention ``[b, s, h, d_qk] x [b, s, h, d_v] -> [b, s, h, d_v]``; the tensor-core kernels
-    when the shape is supported on a GPU, the torch oracle otherwise."""
+    when the shape is supported on a GPU, the torch oracle otherwise. The values may be given transposed instead, as
+    ``vt [b, h, d_v, s]`` (what the forward kernel reads), which saves a transpose pass when the caller can produce
+    that layout directly."""
     scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
+    if vt is not None:
+        if supported(q, vt.permute(0, 3, 1, 2)):
+            return CausalAttention.apply(q, k, vt, scale, True)
+        v = vt.permute(0, 3, 1, 2)
     if not supported(q, v):
         return ref_causal_attention(q, k, v, scale)[0].to(v.dtype)
     return CausalAttention.apply(q, k, v, scale)

@@ -40,7 +40,7 @@ struct AttnSmem {
   static constexpr int kPBytes = 2 * ATOM_BYTES_128;
   static constexpr int kXchOff = kPOff + 2 * kPBytes;  // float [2][2][128]: row statistics exchanged between column halves
   static constexpr int kBarOff = kXchOff + 2 * 2 * 128 * 4;
-  static constexpr int kNumBars = 13;
+  static constexpr int kNumBars = 15;
   static constexpr int kTmemPtrOff = kBarOff + kNumBars * 8;
   static constexpr int kAbortOff = kTmemPtrOff + 4;
   static constexpr int kTotal = kAbortOff + 4;
@@ -58,16 +58,20 @@ constexpr int FWD_ROW_THREADS = 256;   // warps 0-7: warp w works on query rows 
 constexpr int FWD_THREADS = 288;       // + warp 8: TMA + MMA issue
 constexpr float kRescaleSlack = 8.0f;  // log2 units the running reference may lag behind the true row maximum
 
-// One CTA per SM; K, V^T, P (shared memory) and S (TMEM) are double-buffered, key block kb uses buffer kb & 1 and the
-// b-th use of a buffer completes phase b of its barriers. Roles and hand-offs (mbarriers and 64-thread named barriers;
-// the loop has no CTA-wide barrier):
-//   issuer   loads two key blocks ahead; S(kb+1) is computed while the rows work on S(kb); P V (kb) as soon as P(kb) is
-//            written; a K / V^T buffer is refilled for block kb + 2 when S(kb) / P V (kb) has consumed it.
-//   rows     two threads per query row, one per half of the 128 keys of a block: S(kb) TMEM -> 64 registers, release the
+// Persistent: one CTA per SM walks a list of tiles (query block, head, value chunk, batch element), longest first, so
+// that the loads and first MMAs of the next tile run while the softmax warps finish and store the current one.
+// K, V^T, P (shared memory) and S (TMEM) are double-buffered over the sequence of key blocks of ALL tiles of the CTA:
+// the g-th key block uses buffer g & 1 and completes phase g >> 1 of that buffer's barriers. The output accumulator is
+// double-buffered over tiles (tile t uses buffer t & 1). Roles and hand-offs (mbarriers and 64-thread named barriers; no
+// CTA-wide barrier inside the loops):
+//   issuer   loads two key blocks ahead inside a tile; S(g+1) is computed while the rows work on S(g); P V (g) as soon
+//            as P(g) is written; a K / V^T buffer is refilled when S / P V of its previous block has consumed it.
+//   rows     two threads per query row, one per half of the 128 keys of a block: S(g) TMEM -> 64 registers, release the
 //            S buffer; the two halves exchange their maxima through shared memory; the output accumulator stays in TMEM
 //            and is only rescaled when the maximum has grown by more than 2^8 since the reference was set (rarely
 //            after the first blocks), which keeps p <= 256 and the sums well inside fp32 / bf16 range; exponentials ->
-//            P (bf16, swizzled K-major; a half is exactly one 64-key atom) -> signal.
+//            P (bf16, swizzled K-major; a half is exactly one 64-key atom) -> signal. After a tile's last block: O / l
+//            to global memory, release the accumulator buffer.
 template <int DQK, int DV>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -83,18 +87,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   uint64_t* bar_s_free = bars + 7;   // [2]
   uint64_t* bar_p_full = bars + 9;   // [2]
   uint64_t* bar_pv_done = bars + 11; // [2]
+  uint64_t* bar_o_free = bars + 13;  // [2]
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem + L::kTmemPtrOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOff);
 
   const int warp = threadIdx.x >> 5;
   const int n_qblocks = (p.seq + ATT_BM - 1) / ATT_BM;
-  const int qblk = n_qblocks - 1 - (int)blockIdx.x;  // longest rows first
   const int dv_chunks = p.dv / DV;
-  const int head = (int)blockIdx.y / dv_chunks;
-  const int dv0 = ((int)blockIdx.y - head * dv_chunks) * DV;
-  const int batch = (int)blockIdx.z;
-  const int q0 = qblk * ATT_BM;
-  const int n_kblocks = qblk + 1;  // causal: key blocks 0 .. diagonal
+  const int per_qblock = p.heads * dv_chunks * p.batch;  // tiles that share a query block index (same length)
+  const int n_tiles = n_qblocks * per_qblock;
 
   if (threadIdx.x == 0) {
     mbar_init(bar_q, 1);
@@ -105,6 +106,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       mbar_init(&bar_s_free[i], FWD_ROW_THREADS);
       mbar_init(&bar_p_full[i], FWD_ROW_THREADS);
       mbar_init(&bar_pv_done[i], 1);
+      mbar_init(&bar_o_free[i], FWD_ROW_THREADS);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -116,92 +118,122 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_ptr_smem;
-  const uint32_t tmem_o = tmem_base + 2 * ATT_BN;  // S buffers at columns [0, 128) and [128, 256)
+  const uint32_t tmem_base = *tmem_ptr_smem;  // S buffers at columns [0, 128) and [128, 256), O buffers at 256 and 384
+
+  // tile w of the global list (longest query blocks first): query block, then (batch, head, value chunk)
+  auto decode_tile = [&](int w, int& qblk, int& head, int& dv0, int& batch) {
+    qblk = n_qblocks - 1 - w / per_qblock;
+    int r = w % per_qblock;
+    batch = r / (p.heads * dv_chunks);
+    r -= batch * (p.heads * dv_chunks);
+    head = r / dv_chunks;
+    dv0 = (r - head * dv_chunks) * DV;
+  };
 
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA + MMA issuer
     if (elect_one()) {
-      auto load_k = [&](int kb) {
-        const int u = kb & 1;
-        mbar_arrive_expect_tx(&bar_k[u], L::kQBytes);
-        for (int a = 0; a < DQK / 64; ++a)
-          tma_load_2d(smem + L::kKOff + u * L::kQBytes + a * ATOM_BYTES_128, &tmap_k, &bar_k[u], head * DQK + a * 64,
-                      batch * p.seq + kb * ATT_BN);
-      };
-      auto load_v = [&](int kb) {
-        const int u = kb & 1;
-        mbar_arrive_expect_tx(&bar_v[u], L::kVBytes);
-        for (int a = 0; a < 2; ++a)
-          tma_load_2d(smem + L::kVOff + u * L::kVBytes + a * L::kVAtomBytes, &tmap_vt, &bar_v[u], kb * ATT_BN + a * 64,
-                      (batch * p.heads + head) * p.dv + dv0);
-      };
-      auto issue_s = [&](int kb) {
-        const int u = kb & 1;
-        constexpr uint32_t idesc_s = make_idesc_bf16(ATT_BM, ATT_BN);
-#pragma unroll
-        for (int kk = 0; kk < DQK / 16; ++kk) {
-          const uint32_t qa = smem_u32(smem + L::kQOff + (kk / 4) * ATOM_BYTES_128);
-          const uint32_t ka = smem_u32(smem + L::kKOff + u * L::kQBytes + (kk / 4) * ATOM_BYTES_128);
-          umma_bf16_ss(tmem_base + (uint32_t)(u * ATT_BN), make_sw128_kmajor_desc(qa) + (uint64_t)((kk % 4) * 2),
-                       make_sw128_kmajor_desc(ka) + (uint64_t)((kk % 4) * 2), idesc_s, kk > 0 ? 1u : 0u);
-        }
-        umma_commit(&bar_s_full[u]);
-      };
-      mbar_arrive_expect_tx(bar_q, L::kQBytes);
-      for (int a = 0; a < DQK / 64; ++a)
-        tma_load_2d(smem + L::kQOff + a * ATOM_BYTES_128, &tmap_q, bar_q, head * DQK + a * 64, batch * p.seq + q0);
-      load_k(0);
-      load_v(0);
-      if (n_kblocks > 1) {
-        load_k(1);
-        load_v(1);
-      }
-      bool ok = mbar_wait_bounded(bar_q, 0, abort_flag) && mbar_wait_bounded(&bar_k[0], 0, abort_flag);
+      bool ok = true;
       int where = 0;
-      if (ok) {
+      uint32_t g0 = 0;  // key blocks issued by this CTA before the current tile
+      int t = 0;
+      for (int w = (int)blockIdx.x; w < n_tiles && ok; w += (int)gridDim.x, ++t) {
+        int qblk, head, dv0, batch;
+        decode_tile(w, qblk, head, dv0, batch);
+        const int q0 = qblk * ATT_BM;
+        const int n_kblocks = qblk + 1;  // causal: key blocks 0 .. diagonal
+        const uint32_t tmem_o = tmem_base + 2 * ATT_BN + (uint32_t)((t & 1) * DV);
+        auto load_k = [&](int kb) {
+          const int u = (g0 + kb) & 1;
+          mbar_arrive_expect_tx(&bar_k[u], L::kQBytes);
+          for (int a = 0; a < DQK / 64; ++a)
+            tma_load_2d(smem + L::kKOff + u * L::kQBytes + a * ATOM_BYTES_128, &tmap_k, &bar_k[u], head * DQK + a * 64,
+                        batch * p.seq + kb * ATT_BN);
+        };
+        auto load_v = [&](int kb) -> bool {
+          const uint32_t g = g0 + kb;
+          const int u = g & 1;
+          // the buffer's previous block is g - 2: its P V must have read it
+          if (g >= 2 && !mbar_wait_bounded(&bar_pv_done[u], ((g - 2) >> 1) & 1, abort_flag)) return false;
+          mbar_arrive_expect_tx(&bar_v[u], L::kVBytes);
+          for (int a = 0; a < 2; ++a)
+            tma_load_2d(smem + L::kVOff + u * L::kVBytes + a * L::kVAtomBytes, &tmap_vt, &bar_v[u], kb * ATT_BN + a * 64,
+                        (batch * p.heads + head) * p.dv + dv0);
+          return true;
+        };
+        auto issue_s = [&](int kb) {
+          const int u = (g0 + kb) & 1;
+          constexpr uint32_t idesc_s = make_idesc_bf16(ATT_BM, ATT_BN);
+#pragma unroll
+          for (int kk = 0; kk < DQK / 16; ++kk) {
+            const uint32_t qa = smem_u32(smem + L::kQOff + (kk / 4) * ATOM_BYTES_128);
+            const uint32_t ka = smem_u32(smem + L::kKOff + u * L::kQBytes + (kk / 4) * ATOM_BYTES_128);
+            umma_bf16_ss(tmem_base + (uint32_t)(u * ATT_BN), make_sw128_kmajor_desc(qa) + (uint64_t)((kk % 4) * 2),
+                         make_sw128_kmajor_desc(ka) + (uint64_t)((kk % 4) * 2), idesc_s, kk > 0 ? 1u : 0u);
+          }
+          umma_commit(&bar_s_full[u]);
+        };
+        // The previous tile's S MMAs have all completed (their barriers were waited for below), so Q and the K buffers
+        // are free; V buffers are checked in load_v.
+        where = 1;
+        mbar_arrive_expect_tx(bar_q, L::kQBytes);
+        for (int a = 0; a < DQK / 64; ++a)
+          tma_load_2d(smem + L::kQOff + a * ATOM_BYTES_128, &tmap_q, bar_q, head * DQK + a * 64, batch * p.seq + q0);
+        load_k(0);
+        if (n_kblocks > 1) load_k(1);
+        ok = load_v(0);
+        // S(0): Q and K(0) landed; the S buffer's previous block (g0 - 2) was read by the rows
+        ok = ok && mbar_wait_bounded(bar_q, t & 1, abort_flag) && mbar_wait_bounded(&bar_k[g0 & 1], (g0 >> 1) & 1, abort_flag);
+        if (ok && g0 >= 2) ok = mbar_wait_bounded(&bar_s_free[g0 & 1], ((g0 - 2) >> 1) & 1, abort_flag);
+        if (!ok) break;
         tc_fence_after();
         issue_s(0);
-      }
-      for (int kb = 0; kb < n_kblocks && ok; ++kb) {
-        const int u = kb & 1;
-        const uint32_t ph = (kb >> 1) & 1;  // phase of this block's use of buffer u
-        const bool more = kb + 1 < n_kblocks;
-        if (more) {
-          // S(kb+1): its K block has landed and the rows have released the S buffer it overwrites (block kb - 1)
-          where = 10 * kb + 1;
-          ok = mbar_wait_bounded(&bar_k[u ^ 1], ((kb + 1) >> 1) & 1, abort_flag);
-          if (ok && kb >= 1) ok = mbar_wait_bounded(&bar_s_free[u ^ 1], ((kb - 1) >> 1) & 1, abort_flag);
+        // V(1) goes into the buffer that the previous tile's LAST block used: this wait is the one place where the
+        // issuer depends on the rows having finished that tile's last softmax, so it comes after S(0) is under way
+        where = 2;
+        if (n_kblocks > 1) ok = load_v(1);
+        // the accumulator buffer of this tile was last used by tile t - 2: its rows must have stored their outputs
+        if (ok && t >= 2) ok = mbar_wait_bounded(&bar_o_free[t & 1], ((t - 2) >> 1) & 1, abort_flag);
+        for (int kb = 0; kb < n_kblocks && ok; ++kb) {
+          const uint32_t g = g0 + kb;
+          const int u = g & 1;
+          const uint32_t ph = (g >> 1) & 1;  // phase of this block's use of buffer u
+          const bool more = kb + 1 < n_kblocks;
+          if (more) {
+            // S(kb+1): its K block has landed and the rows have released the S buffer it overwrites (block g - 1)
+            where = 10 * kb + 3;
+            ok = mbar_wait_bounded(&bar_k[u ^ 1], ((g + 1) >> 1) & 1, abort_flag);
+            if (ok && g >= 1) ok = mbar_wait_bounded(&bar_s_free[u ^ 1], ((g - 1) >> 1) & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            issue_s(kb + 1);
+          }
+          // K buffer u is free once S(kb) has been computed: fetch block kb + 2 into it
+          where = 10 * kb + 4;
+          ok = mbar_wait_bounded(&bar_s_full[u], ph, abort_flag);
+          if (!ok) break;
+          if (kb + 2 < n_kblocks) load_k(kb + 2);
+          // P V (kb)
+          where = 10 * kb + 5;
+          ok = mbar_wait_bounded(&bar_p_full[u], ph, abort_flag) && mbar_wait_bounded(&bar_v[u], ph, abort_flag);
           if (!ok) break;
           tc_fence_after();
-          issue_s(kb + 1);
-        }
-        // K buffer u is free once S(kb) has been computed: fetch block kb + 2 into it
-        where = 10 * kb + 2;
-        ok = mbar_wait_bounded(&bar_s_full[u], ph, abort_flag);
-        if (!ok) break;
-        if (kb + 2 < n_kblocks) load_k(kb + 2);
-        // P V (kb)
-        where = 10 * kb + 3;
-        ok = mbar_wait_bounded(&bar_p_full[u], ph, abort_flag) && mbar_wait_bounded(&bar_v[u], ph, abort_flag);
-        if (!ok) break;
-        tc_fence_after();
-        constexpr uint32_t idesc_o = make_idesc_bf16(ATT_BM, DV);
+          constexpr uint32_t idesc_o = make_idesc_bf16(ATT_BM, DV);
 #pragma unroll
-        for (int kk = 0; kk < ATT_BN / 16; ++kk) {
-          const uint32_t pa = smem_u32(smem + L::kPOff + u * L::kPBytes + (kk / 4) * ATOM_BYTES_128);
-          const uint32_t va = smem_u32(smem + L::kVOff + u * L::kVBytes + (kk / 4) * L::kVAtomBytes);
-          umma_bf16_ss(tmem_o, make_sw128_kmajor_desc(pa) + (uint64_t)((kk % 4) * 2),
-                       make_sw128_kmajor_desc(va) + (uint64_t)((kk % 4) * 2), idesc_o, (kb > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < ATT_BN / 16; ++kk) {
+            const uint32_t pa = smem_u32(smem + L::kPOff + u * L::kPBytes + (kk / 4) * ATOM_BYTES_128);
+            const uint32_t va = smem_u32(smem + L::kVOff + u * L::kVBytes + (kk / 4) * L::kVAtomBytes);
+            umma_bf16_ss(tmem_o, make_sw128_kmajor_desc(pa) + (uint64_t)((kk % 4) * 2),
+                         make_sw128_kmajor_desc(va) + (uint64_t)((kk % 4) * 2), idesc_o, (kb > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(&bar_pv_done[u]);
+          // the V buffer of the previous block is free once its P V has completed (it ran before this one): refill it
+          if (kb >= 1 && more) {
+            where = 10 * kb + 6;
+            ok = load_v(kb + 1);
+          }
         }
-        umma_commit(&bar_pv_done[u]);
-        // the V buffer of the PREVIOUS block is certainly free by now (its P V ran before this one): refill it
-        if (kb >= 1 && kb + 1 < n_kblocks) {
-          where = 10 * kb + 4;
-          ok = mbar_wait_bounded(&bar_pv_done[u ^ 1], ((kb - 1) >> 1) & 1, abort_flag);
-          if (!ok) break;
-          load_v(kb + 1);
-        }
+        g0 += (uint32_t)n_kblocks;
       }
       if (!ok) {
         report_status(p.status, kTimeoutFullBarrier, where);
@@ -212,112 +244,121 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     // ------------------------------------------------------------------ softmax rows
     const int quarter = warp & 3, half = warp >> 2, lane = (int)threadIdx.x & 31;
     const int row = quarter * 32 + lane;
-    const int qpos = q0 + row;
-    const bool row_ok = qpos < p.seq;
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
     const uint32_t s_col = (uint32_t)(half * (ATT_BN / 2));
     const uint32_t o_col = (uint32_t)(half * (DV / 2));
     float* xch = reinterpret_cast<float*>(smem + L::kXchOff);  // [2 parities][2 halves][128 rows]
     const float sc = p.scale_log2;
-    float m_ref = -INFINITY, l_run = 0.0f;
     bool ok = true;
-    for (int kb = 0; kb < n_kblocks && ok; ++kb) {
-      const int u = kb & 1;
-      const uint32_t ph = (kb >> 1) & 1;
-      const int k0 = kb * ATT_BN + (int)s_col;
-      // (a failed wait ends the loop for the whole warp: the TMEM accesses and votes below are warp-wide)
-      if (!__all_sync(0xffffffffu, mbar_wait_bounded(&bar_s_full[u], ph, abort_flag))) { ok = false; break; }
-      tc_fence_after();
-      uint32_t s[ATT_BN / 64][32];
-#pragma unroll
-      for (int c = 0; c < ATT_BN / 64; ++c)
-        tmem_ld_32x32b_x32(tmem_base + (uint32_t)(u * ATT_BN) + lane_off + s_col + (uint32_t)(c * 32), s[c]);
-      tmem_wait_ld();
-      tc_fence_before();
-      mbar_arrive(&bar_s_free[u]);
-      // masked raw scores and their maximum (only the diagonal and the last block have anything to mask)
-      const bool need_mask = (k0 + ATT_BN / 2 - 1 > qpos) || (k0 + ATT_BN / 2 > p.seq);
-      float m_raw = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < ATT_BN / 64; ++c) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          float v = __uint_as_float(s[c][j]);
-          if (need_mask && !(k0 + c * 32 + j <= qpos && k0 + c * 32 + j < p.seq)) {
-            v = -INFINITY;
-            s[c][j] = __float_as_uint(v);
-          }
-          m_raw = fmaxf(m_raw, v);
-        }
-      }
-      // the other half of the row: exchange through shared memory, 64-thread barrier of the two warps of this quarter
-      xch[(u * 2 + half) * ATT_BM + row] = m_raw;
-      asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
-      const float m_blk = fmaxf(m_raw, xch[(u * 2 + (half ^ 1)) * ATT_BM + row]) * sc;  // sc > 0
-      float alpha = 1.0f;
-      bool rescale = false;
-      if (m_blk > m_ref + kRescaleSlack || m_ref == -INFINITY) {
-        const float m_new = fmaxf(m_ref, m_blk);
-        if (m_new != -INFINITY) {
-          alpha = exp2f(m_ref - m_new);  // 0 when nothing was accumulated under the old reference
-          rescale = kb > 0;
-          m_ref = m_new;
-        }
-      }
-      const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
-      if (__any_sync(0xffffffffu, rescale)) {  // this warp's half of the output columns
-        // the accumulator belongs to the tensor core until P V (kb - 1) has completed
-        if (!__all_sync(0xffffffffu, mbar_wait_bounded(&bar_pv_done[u ^ 1], ((kb - 1) >> 1) & 1, abort_flag))) { ok = false; break; }
+    uint32_t g0 = 0;
+    int t = 0;
+    for (int w = (int)blockIdx.x; w < n_tiles && ok; w += (int)gridDim.x, ++t) {
+      int qblk, head, dv0, batch;
+      decode_tile(w, qblk, head, dv0, batch);
+      const int q0 = qblk * ATT_BM;
+      const int n_kblocks = qblk + 1;
+      const int qpos = q0 + row;
+      const bool row_ok = qpos < p.seq;
+      const uint32_t tmem_o = tmem_base + 2 * ATT_BN + (uint32_t)((t & 1) * DV);
+      float m_ref = -INFINITY, l_run = 0.0f;
+      for (int kb = 0; kb < n_kblocks && ok; ++kb) {
+        const uint32_t g = g0 + kb;
+        const int u = g & 1;
+        const uint32_t ph = (g >> 1) & 1;
+        const int k0 = kb * ATT_BN + (int)s_col;
+        // (a failed wait ends the loops for the whole warp: the TMEM accesses and votes below are warp-wide)
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(&bar_s_full[u], ph, abort_flag))) { ok = false; break; }
         tc_fence_after();
+        uint32_t s[ATT_BN / 64][32];
+#pragma unroll
+        for (int c = 0; c < ATT_BN / 64; ++c)
+          tmem_ld_32x32b_x32(tmem_base + (uint32_t)(u * ATT_BN) + lane_off + s_col + (uint32_t)(c * 32), s[c]);
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(&bar_s_free[u]);
+        // masked raw scores and their maximum (only the diagonal and the last block have anything to mask)
+        const bool need_mask = (k0 + ATT_BN / 2 - 1 > qpos) || (k0 + ATT_BN / 2 > p.seq);
+        float m_raw = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < ATT_BN / 64; ++c) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float v = __uint_as_float(s[c][j]);
+            if (need_mask && !(k0 + c * 32 + j <= qpos && k0 + c * 32 + j < p.seq)) {
+              v = -INFINITY;
+              s[c][j] = __float_as_uint(v);
+            }
+            m_raw = fmaxf(m_raw, v);
+          }
+        }
+        // the other half of the row: exchange through shared memory, 64-thread barrier of the two warps of this quarter
+        xch[(u * 2 + half) * ATT_BM + row] = m_raw;
+        asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+        const float m_blk = fmaxf(m_raw, xch[(u * 2 + (half ^ 1)) * ATT_BM + row]) * sc;  // sc > 0
+        float alpha = 1.0f;
+        bool rescale = false;
+        if (m_blk > m_ref + kRescaleSlack || m_ref == -INFINITY) {
+          const float m_new = fmaxf(m_ref, m_blk);
+          if (m_new != -INFINITY) {
+            alpha = exp2f(m_ref - m_new);  // 0 when nothing was accumulated under the old reference
+            rescale = kb > 0;
+            m_ref = m_new;
+          }
+        }
+        const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
+        if (__any_sync(0xffffffffu, rescale)) {  // this warp's half of the output columns
+          // the accumulator belongs to the tensor core until P V (g - 1) has completed
+          if (!__all_sync(0xffffffffu, mbar_wait_bounded(&bar_pv_done[u ^ 1], ((g - 1) >> 1) & 1, abort_flag))) { ok = false; break; }
+          tc_fence_after();
 #pragma unroll 1
-        for (int c = 0; c < DV / 64; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(tmem_o + lane_off + o_col + (uint32_t)(c * 32), r);
-          tmem_wait_ld();
+          for (int c = 0; c < DV / 64; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(tmem_o + lane_off + o_col + (uint32_t)(c * 32), r);
+            tmem_wait_ld();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * alpha);
-          tmem_st_32x32b_x32(tmem_o + lane_off + o_col + (uint32_t)(c * 32), r);
+            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * alpha);
+            tmem_st_32x32b_x32(tmem_o + lane_off + o_col + (uint32_t)(c * 32), r);
+          }
+          tmem_wait_st();
         }
-        tmem_wait_st();
-      }
-      if (kb >= 2) {
-        // P buffer u was read by P V (kb - 2)
-        if (!__all_sync(0xffffffffu, mbar_wait_bounded(&bar_pv_done[u], ((kb - 2) >> 1) & 1, abort_flag))) { ok = false; break; }
-      }
-      l_run *= alpha;
-      float l_blk = 0.0f;
-      uint8_t* atom = smem + L::kPOff + u * L::kPBytes + half * ATOM_BYTES_128;  // this half's 64 keys are one swizzle atom
-#pragma unroll
-      for (int g = 0; g < ATT_BN / 16; ++g) {
-        float pv[8];
-#pragma unroll
-        for (int t = 0; t < 8; ++t) {
-          pv[t] = exp2f(fmaf(__uint_as_float(s[g / 4][(g % 4) * 8 + t]), sc, -m_use));
-          l_blk += pv[t];
+        if (g >= 2) {
+          // P buffer u was read by P V (g - 2)
+          if (!__all_sync(0xffffffffu, mbar_wait_bounded(&bar_pv_done[u], ((g - 2) >> 1) & 1, abort_flag))) { ok = false; break; }
         }
-        uint4 w;
-        w.x = pack_bf16x2(pv[0], pv[1]);
-        w.y = pack_bf16x2(pv[2], pv[3]);
-        w.z = pack_bf16x2(pv[4], pv[5]);
-        w.w = pack_bf16x2(pv[6], pv[7]);
-        *reinterpret_cast<uint4*>(atom + sw128_chunk_off(row, g)) = w;
+        l_run *= alpha;
+        float l_blk = 0.0f;
+        uint8_t* atom = smem + L::kPOff + u * L::kPBytes + half * ATOM_BYTES_128;  // this half's 64 keys are one swizzle atom
+#pragma unroll
+        for (int gq = 0; gq < ATT_BN / 16; ++gq) {
+          float pv[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            pv[i] = exp2f(fmaf(__uint_as_float(s[gq / 4][(gq % 4) * 8 + i]), sc, -m_use));
+            l_blk += pv[i];
+          }
+          uint4 wv;
+          wv.x = pack_bf16x2(pv[0], pv[1]);
+          wv.y = pack_bf16x2(pv[2], pv[3]);
+          wv.z = pack_bf16x2(pv[4], pv[5]);
+          wv.w = pack_bf16x2(pv[6], pv[7]);
+          *reinterpret_cast<uint4*>(atom + sw128_chunk_off(row, gq)) = wv;
+        }
+        l_run += l_blk;
+        fence_proxy_async();  // the generic-proxy stores of P must be visible to the tensor core's reads
+        tc_fence_before();
+        mbar_arrive(&bar_p_full[u]);
       }
-      l_run += l_blk;
-      fence_proxy_async();  // the generic-proxy stores of P must be visible to the tensor core's reads
-      tc_fence_before();
-      mbar_arrive(&bar_p_full[u]);
-    }
-    ok = __all_sync(0xffffffffu, ok && mbar_wait_bounded(&bar_pv_done[(n_kblocks - 1) & 1], ((n_kblocks - 1) >> 1) & 1, abort_flag));
-    if (!ok) {
-      report_status(p.status, kTimeoutTmemFull, row);
-      *abort_flag = 1;
-    } else {
+      // ---- the tile's epilogue
+      const uint32_t g_last = g0 + (uint32_t)n_kblocks - 1;
+      ok = __all_sync(0xffffffffu, ok && mbar_wait_bounded(&bar_pv_done[g_last & 1], (g_last >> 1) & 1, abort_flag));
+      if (!ok) break;
       tc_fence_after();
-      // total of the two halves' sums (the slots of the next parity are free: nobody reads them any more)
-      const int slot = (n_kblocks & 1) * 2;
+      // total of the two halves' sums; slot parity continues the per-block sequence (block g_last used g_last & 1)
+      const int slot = (int)((g_last + 1) & 1) * 2;
       xch[(slot + half) * ATT_BM + row] = l_run;
       asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
       const float l_tot = l_run + xch[(slot + (half ^ 1)) * ATT_BM + row];
+      // (the next tile's first block writes the same slots only after another 64-thread barrier: see below)
       const float inv = l_tot > 0.0f ? 1.0f / l_tot : 0.0f;
       __nv_bfloat16* dst = p.out + (((size_t)batch * p.seq + (row_ok ? qpos : 0)) * p.heads + head) * p.dv + dv0 + o_col;
 #pragma unroll 1
@@ -328,17 +369,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         if (row_ok) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
-            uint4 w;
-            w.x = pack_bf16x2(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
-            w.y = pack_bf16x2(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
-            w.z = pack_bf16x2(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
-            w.w = pack_bf16x2(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
-            *reinterpret_cast<uint4*>(dst + c * 32 + i) = w;
+            uint4 wv;
+            wv.x = pack_bf16x2(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+            wv.y = pack_bf16x2(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+            wv.z = pack_bf16x2(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+            wv.w = pack_bf16x2(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + i) = wv;
           }
         }
       }
+      tc_fence_before();
+      mbar_arrive(&bar_o_free[t & 1]);
       if (row_ok && half == 0 && p.lse != nullptr && dv0 == 0)
         p.lse[((size_t)batch * p.heads + head) * p.seq + qpos] = m_ref * 0.6931471805599453f + __logf(l_tot);
+      // keep the two warps of a quarter together across tiles: the sum exchange above and the next maximum exchange use
+      // the same slots
+      asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+      g0 += (uint32_t)n_kblocks;
+    }
+    if (!ok) {
+      report_status(p.status, kTimeoutTmemFull, row);
+      *abort_flag = 1;
     }
   }
 
@@ -362,7 +413,15 @@ static cudaError_t attn_fwd_variant(const CUtensorMap& tq, const CUtensorMap& tk
   auto kern = attn_fwd_kernel<DQK, DV>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
   if (e != cudaSuccess) return e;
-  dim3 grid((p.seq + ATT_BM - 1) / ATT_BM, p.heads * (p.dv / DV), p.batch);
+  static int num_sms = 0;  // persistent grid: one CTA per SM
+  if (num_sms == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+      num_sms = 148;
+  }
+  const long long tiles = (long long)((p.seq + ATT_BM - 1) / ATT_BM) * p.heads * (p.dv / DV) * p.batch;
+  if (tiles <= 0 || tiles > 2147483647LL) return cudaErrorInvalidValue;
+  const int grid = (int)(tiles < num_sms ? tiles : num_sms);
   kern<<<grid, FWD_THREADS, L::kDynamicBytes, stream>>>(tq, tk, tvt, p);
   return cudaGetLastError();
 }

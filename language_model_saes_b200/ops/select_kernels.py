@@ -54,7 +54,13 @@ def positive_thresholds(x3: torch.Tensor, k: int, group=None, return_remaining: 
                 dist.all_gather(parts, top, group=group)
                 vals = torch.cat(parts)
             out.append(ref_positive_threshold(vals, k))
-        return torch.stack(out)
+        thr = torch.stack(out)
+        if not return_remaining:
+            return thr
+        above = torch.stack([(x3[:, s, :].float() > thr[s]).sum() for s in range(S)]).to(torch.int64)
+        if world > 1:
+            dist.all_reduce(above, group=group)
+        return thr, (k - above).clamp(min=0)
     ext = K._ext()
     dev = x3.device
     nhi = int(ext.radix_hi_bins())
@@ -175,6 +181,8 @@ def threshold_rows_to_sparse(g: torch.Tensor, thr: torch.Tensor, col_div: torch.
     ``positive_thresholds(..., return_remaining=True)`` reports it) makes the number of codes exact when the threshold
     value repeats (16-bit data): ties are granted in (rank of ``tie_group``, row, column) order until the count is
     used up. Without it every tie is kept."""
+    if not _kernel_ok(g):
+        return _ref_threshold_rows_to_sparse(g, thr, col_div, width_group, n_ties, tie_group)
     ext = K._ext()
     g = g.contiguous()
     B = g.shape[0]
@@ -201,6 +209,38 @@ def threshold_rows_to_sparse(g: torch.Tensor, thr: torch.Tensor, col_div: torch.
     idx = torch.empty(B, cap, dtype=torch.int32, device=g.device)
     val = torch.empty(B, cap, dtype=torch.float32, device=g.device)
     ext.row_compact(g, idx, val, nnz, thr, col_div, None, quota)
+    return idx, val
+
+
+def _ref_threshold_rows_to_sparse(g, thr, col_div, width_group, n_ties, tie_group):
+    """Plain-torch statement of ``threshold_rows_to_sparse`` (any device): same selection, same order."""
+    gf = g.float()
+    t = thr.reshape(()).float()
+    keep = gf > t
+    ties = gf == t
+    if n_ties is None:
+        keep = keep | ties
+    else:
+        budget = n_ties.reshape(()).to(torch.int64)
+        if tie_group is not None and dist.get_world_size(tie_group) > 1:
+            mine = ties.sum().to(torch.int64).reshape(1)
+            every = [torch.empty_like(mine) for _ in range(dist.get_world_size(tie_group))]
+            dist.all_gather(every, mine, group=tie_group)
+            budget = budget - torch.cat(every)[: dist.get_rank(tie_group)].sum()
+        rank_of_tie = torch.cumsum(ties.reshape(-1).to(torch.int64), 0).reshape(ties.shape) - 1  # row-major order
+        keep = keep | (ties & (rank_of_tie < budget))
+    widest = keep.sum(-1).max()
+    if width_group is not None and dist.get_world_size(width_group) > 1:
+        dist.all_reduce(widest, op=dist.ReduceOp.MAX, group=width_group)
+    cap = max(8, -(-int(widest) // 8) * 8)
+    vals = gf / col_div.float() if col_div is not None else gf
+    B = g.shape[0]
+    idx = torch.full((B, cap), -1, dtype=torch.int32, device=g.device)
+    val = torch.zeros(B, cap, dtype=torch.float32, device=g.device)
+    for b in range(B):
+        cols = torch.nonzero(keep[b], as_tuple=False).flatten()
+        idx[b, : cols.numel()] = cols.to(torch.int32)
+        val[b, : cols.numel()] = vals[b, cols]
     return idx, val
 
 

@@ -92,6 +92,58 @@ def test_fused_step_feature_and_data_parallel_match_single():
 
 
 @distributed_test(nproc_per_node=2, backend="gloo")
+def test_fused_batchtopk_step_feature_and_data_parallel_match_single():
+    """Batch-level top-k on the fused path: feature shards share one threshold (and ration the ties between them), data
+    shards agree on the width of their code lists; both reproduce the single-process run."""
+    full = _full_model()
+    full.cfg.act_fn = "batchtopk"
+    xs = [(_data() + i).to(torch.bfloat16) for i in range(3)]
+    ref = SparseAutoEncoder(full.cfg.model_copy())
+    ref.load_full_state_dict(full.full_state_dict())
+    eng, want = _run_fused(ref, xs, 8)
+    assert eng.batch_level
+    idx, _ = eng.encode(xs[0], 8)
+    assert int((idx >= 0).sum()) == 8 * xs[0].shape[0]  # exactly k codes per token on average
+
+    tp_mesh = build_mesh("cpu", (1, 2), ("data", "model"))
+    tp = _sharded_copy(full, tp_mesh)
+    # before any update: the shards together keep exactly k * batch codes, the same ones as one process except for which
+    # of the entries EQUAL to the (bf16) threshold get the last places (one process grants them in row order, shards in
+    # rank order; the reference's sort breaks such ties arbitrarily too)
+    tp0 = _sharded_copy(full, tp_mesh)
+    ref0 = SparseAutoEncoder(full.cfg.model_copy())
+    ref0.load_full_state_dict(full.full_state_dict())
+    idx_1, act_1 = FusedTopKSAEStep(ref0).encode(xs[0], 8)
+    idx_l, act_l = FusedTopKSAEStep(tp0).encode(xs[0], 8)
+    n = (idx_l >= 0).sum()
+    dist.all_reduce(n)
+    assert int(n) == 8 * xs[0].shape[0]
+    F_l, r = tp0.W_D.shape[0], dist.get_rank()
+    dense_1 = torch.zeros(xs[0].shape[0], 2 * F_l)
+    rows = torch.arange(xs[0].shape[0])[:, None].expand_as(idx_1)
+    dense_1[rows[idx_1 >= 0], idx_1[idx_1 >= 0].long()] = act_1[idx_1 >= 0]
+    dense_l = torch.zeros(xs[0].shape[0], F_l)
+    rows = torch.arange(xs[0].shape[0])[:, None].expand_as(idx_l)
+    dense_l[rows[idx_l >= 0], idx_l[idx_l >= 0].long()] = act_l[idx_l >= 0]
+    mine = dense_1[:, r * F_l : (r + 1) * F_l]
+    differ = (mine != 0) != (dense_l != 0)
+    assert int(differ.sum()) <= 8 and torch.equal(mine[~differ], dense_l[~differ])
+    eng_tp, got = _run_fused(tp, xs, 8)
+    assert torch.allclose(got, want, rtol=2e-2), (got, want)
+
+    # data parallel: every replica thresholds its own half batch (k * local batch codes), as the reference does
+    dp_mesh = build_mesh("cpu", (2, 1), ("data", "model"))
+    dp = _sharded_copy(full, dp_mesh)
+    r = dist.get_rank()
+    half = xs[0].shape[0] // 2
+    eng_dp, got_dp = _run_fused(dp, [x[r * half : (r + 1) * half] for x in xs], 8)
+    assert torch.isfinite(got_dp).all()
+    both = [torch.empty_like(dp.W_D.data) for _ in range(2)]
+    dist.all_gather(both, dp.W_D.data.contiguous())
+    assert torch.equal(both[0], both[1])  # replicas stay identical
+
+
+@distributed_test(nproc_per_node=2, backend="gloo")
 def test_heartbeat_reports_a_rank_that_leaves_and_one_that_goes_silent():
     import time
 
