@@ -152,7 +152,8 @@ def test_heartbeat_reports_a_rank_that_leaves_and_one_that_goes_silent():
     from language_model_saes_b200.parallel.health import Heartbeat, PeerLost, default_store
 
     rank = dist.get_rank()
-    hb = Heartbeat(default_store(), rank, 2, timeout_s=1.0, prefix="t1")
+    hb = Heartbeat(default_store(), rank, 2, timeout_s=30.0, prefix="t1")
+    dist.barrier()  # (the two processes may have started seconds apart)
     hb.beat(0)
     dist.barrier()
     hb.check()  # both alive
