@@ -38,8 +38,8 @@ struct AttnSmem {
   static constexpr int kVBytes = 2 * kVAtomBytes;
   static constexpr int kPOff = kVOff + 2 * kVBytes;    // two P buffers
   static constexpr int kPBytes = 2 * ATOM_BYTES_128;
-  static constexpr int kXchOff = kPOff + 2 * kPBytes;  // float [2][2][128]: row statistics exchanged between column halves
-  static constexpr int kBarOff = kXchOff + 2 * 2 * 128 * 4;
+  static constexpr int kXchOff = kPOff + 2 * kPBytes;  // float [2][4][128]: row statistics exchanged between column quarters
+  static constexpr int kBarOff = kXchOff + 2 * 4 * 128 * 4;
   static constexpr int kNumBars = 15;
   static constexpr int kTmemPtrOff = kBarOff + kNumBars * 8;
   static constexpr int kAbortOff = kTmemPtrOff + 4;
@@ -54,8 +54,9 @@ __device__ __forceinline__ uint32_t sw128_chunk_off(int row, int chunk) {
 
 }  // namespace
 
-constexpr int FWD_ROW_THREADS = 256;   // warps 0-7: warp w works on query rows 32 (w % 4) .. + 31, key columns 64 (w / 4) .. + 63
-constexpr int FWD_THREADS = 288;       // + warp 8: TMA + MMA issue
+constexpr int FWD_ROW_WARPS = 16;      // warp w works on query rows 32 (w % 4) .. + 31 and key columns 32 (w / 4) .. + 31
+constexpr int FWD_ROW_THREADS = FWD_ROW_WARPS * 32;
+constexpr int FWD_THREADS = FWD_ROW_THREADS + 32;  // + the last warp: TMA + MMA issue
 constexpr float kRescaleSlack = 8.0f;  // log2 units the running reference may lag behind the true row maximum
 
 // Persistent: one CTA per SM walks a list of tiles (query block, head, value chunk, batch element), longest first, so
@@ -66,11 +67,12 @@ constexpr float kRescaleSlack = 8.0f;  // log2 units the running reference may l
 // CTA-wide barrier inside the loops):
 //   issuer   loads two key blocks ahead inside a tile; S(g+1) is computed while the rows work on S(g); P V (g) as soon
 //            as P(g) is written; a K / V^T buffer is refilled when S / P V of its previous block has consumed it.
-//   rows     two threads per query row, one per half of the 128 keys of a block: S(g) TMEM -> 64 registers, release the
-//            S buffer; the two halves exchange their maxima through shared memory; the output accumulator stays in TMEM
+//   rows     four threads per query row, one per quarter of the 128 keys of a block (sixteen warps: the softmax work is
+//            latency-bound, so the warps are there to hide each other's TMEM loads and barrier polls): S(g) TMEM -> 32
+//            registers, release the S buffer; the four exchange their maxima through shared memory; the output accumulator stays in TMEM
 //            and is only rescaled when the maximum has grown by more than 2^8 since the reference was set (rarely
 //            after the first blocks), which keeps p <= 256 and the sums well inside fp32 / bf16 range; exponentials ->
-//            P (bf16, swizzled K-major; a half is exactly one 64-key atom) -> signal. After a tile's last block: O / l
+//            P (bf16, swizzled K-major, two 64-key atoms) -> signal. After a tile's last block: O / l
 //            to global memory, release the accumulator buffer.
 template <int DQK, int DV>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
@@ -103,15 +105,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       mbar_init(&bar_k[i], 1);
       mbar_init(&bar_v[i], 1);
       mbar_init(&bar_s_full[i], 1);
-      mbar_init(&bar_s_free[i], FWD_ROW_THREADS);
-      mbar_init(&bar_p_full[i], FWD_ROW_THREADS);
+      // (one arrival per softmax warp: hundreds of arrivals on one shared-memory word per key block would serialise)
+      mbar_init(&bar_s_free[i], FWD_ROW_WARPS);
+      mbar_init(&bar_p_full[i], FWD_ROW_WARPS);
       mbar_init(&bar_pv_done[i], 1);
-      mbar_init(&bar_o_free[i], FWD_ROW_THREADS);
+      mbar_init(&bar_o_free[i], FWD_ROW_WARPS);
     }
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 8) {
+  if (warp == FWD_ROW_WARPS) {
     tmem_alloc(tmem_ptr_smem, 512);
     tmem_relinquish();
   }
@@ -130,7 +133,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     dv0 = (r - head * dv_chunks) * DV;
   };
 
-  if (warp == 8) {
+  if (warp == FWD_ROW_WARPS) {
     // ------------------------------------------------------------------ TMA + MMA issuer
     if (elect_one()) {
       bool ok = true;
@@ -242,12 +245,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     }
   } else {
     // ------------------------------------------------------------------ softmax rows
-    const int quarter = warp & 3, half = warp >> 2, lane = (int)threadIdx.x & 31;
+    const int quarter = warp & 3, cq = warp >> 2, lane = (int)threadIdx.x & 31;
     const int row = quarter * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
-    const uint32_t s_col = (uint32_t)(half * (ATT_BN / 2));
-    const uint32_t o_col = (uint32_t)(half * (DV / 2));
-    float* xch = reinterpret_cast<float*>(smem + L::kXchOff);  // [2 parities][2 halves][128 rows]
+    const uint32_t s_col = (uint32_t)(cq * 32);
+    // output columns of this thread (rescale and final store): a quarter of DV, at least one 32-column TMEM load
+    constexpr int O_W = DV / 4 >= 32 ? DV / 4 : 32;
+    const bool o_active = cq * O_W < DV;
+    const uint32_t o_col = (uint32_t)(cq * O_W);
+    float* xch = reinterpret_cast<float*>(smem + L::kXchOff);  // [2 parities][4 column quarters][128 rows]
     const float sc = p.scale_log2;
     bool ok = true;
     uint32_t g0 = 0;
@@ -269,32 +275,30 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         // (a failed wait ends the loops for the whole warp: the TMEM accesses and votes below are warp-wide)
         if (!__all_sync(0xffffffffu, mbar_wait_bounded(&bar_s_full[u], ph, abort_flag))) { ok = false; break; }
         tc_fence_after();
-        uint32_t s[ATT_BN / 64][32];
-#pragma unroll
-        for (int c = 0; c < ATT_BN / 64; ++c)
-          tmem_ld_32x32b_x32(tmem_base + (uint32_t)(u * ATT_BN) + lane_off + s_col + (uint32_t)(c * 32), s[c]);
+        uint32_t s[32];
+        tmem_ld_32x32b_x32(tmem_base + (uint32_t)(u * ATT_BN) + lane_off + s_col, s);
         tmem_wait_ld();
         tc_fence_before();
-        mbar_arrive(&bar_s_free[u]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_s_free[u]);
         // masked raw scores and their maximum (only the diagonal and the last block have anything to mask)
-        const bool need_mask = (k0 + ATT_BN / 2 - 1 > qpos) || (k0 + ATT_BN / 2 > p.seq);
+        const bool need_mask = (k0 + 31 > qpos) || (k0 + 32 > p.seq);
         float m_raw = -INFINITY;
 #pragma unroll
-        for (int c = 0; c < ATT_BN / 64; ++c) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float v = __uint_as_float(s[c][j]);
-            if (need_mask && !(k0 + c * 32 + j <= qpos && k0 + c * 32 + j < p.seq)) {
-              v = -INFINITY;
-              s[c][j] = __float_as_uint(v);
-            }
-            m_raw = fmaxf(m_raw, v);
+        for (int j = 0; j < 32; ++j) {
+          float v = __uint_as_float(s[j]);
+          if (need_mask && !(k0 + j <= qpos && k0 + j < p.seq)) {
+            v = -INFINITY;
+            s[j] = __float_as_uint(v);
           }
+          m_raw = fmaxf(m_raw, v);
         }
-        // the other half of the row: exchange through shared memory, 64-thread barrier of the two warps of this quarter
-        xch[(u * 2 + half) * ATT_BM + row] = m_raw;
-        asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
-        const float m_blk = fmaxf(m_raw, xch[(u * 2 + (half ^ 1)) * ATT_BM + row]) * sc;  // sc > 0
+        // the other three quarters of the row: exchange through shared memory, 128-thread barrier of the four warps
+        // that share these 32 rows
+        float* xr = xch + (u * 4) * ATT_BM + row;
+        xr[cq * ATT_BM] = m_raw;
+        asm volatile("bar.sync %0, 128;" ::"r"(1 + quarter) : "memory");
+        const float m_blk = fmaxf(fmaxf(xr[0], xr[ATT_BM]), fmaxf(xr[2 * ATT_BM], xr[3 * ATT_BM])) * sc;  // sc > 0
         float alpha = 1.0f;
         bool rescale = false;
         if (m_blk > m_ref + kRescaleSlack || m_ref == -INFINITY) {
@@ -306,20 +310,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           }
         }
         const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
-        if (__any_sync(0xffffffffu, rescale)) {  // this warp's half of the output columns
+        if (__any_sync(0xffffffffu, rescale)) {  // this warp's share of the output columns
           // the accumulator belongs to the tensor core until P V (g - 1) has completed
           if (!__all_sync(0xffffffffu, mbar_wait_bounded(&bar_pv_done[u ^ 1], ((g - 1) >> 1) & 1, abort_flag))) { ok = false; break; }
           tc_fence_after();
+          if (o_active) {
 #pragma unroll 1
-          for (int c = 0; c < DV / 64; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(tmem_o + lane_off + o_col + (uint32_t)(c * 32), r);
-            tmem_wait_ld();
+            for (int c = 0; c < O_W / 32; ++c) {
+              uint32_t r[32];
+              tmem_ld_32x32b_x32(tmem_o + lane_off + o_col + (uint32_t)(c * 32), r);
+              tmem_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * alpha);
-            tmem_st_32x32b_x32(tmem_o + lane_off + o_col + (uint32_t)(c * 32), r);
+              for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * alpha);
+              tmem_st_32x32b_x32(tmem_o + lane_off + o_col + (uint32_t)(c * 32), r);
+            }
+            tmem_wait_st();
           }
-          tmem_wait_st();
         }
         if (g >= 2) {
           // P buffer u was read by P V (g - 2)
@@ -327,13 +333,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         }
         l_run *= alpha;
         float l_blk = 0.0f;
-        uint8_t* atom = smem + L::kPOff + u * L::kPBytes + half * ATOM_BYTES_128;  // this half's 64 keys are one swizzle atom
+        // this quarter's 32 keys are half of a 64-key swizzle atom: 16-byte chunks (cq % 2) * 4 .. + 3 of atom cq / 2
+        uint8_t* atom = smem + L::kPOff + u * L::kPBytes + (cq >> 1) * ATOM_BYTES_128;
 #pragma unroll
-        for (int gq = 0; gq < ATT_BN / 16; ++gq) {
+        for (int gq = 0; gq < 4; ++gq) {
           float pv[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            pv[i] = exp2f(fmaf(__uint_as_float(s[gq / 4][(gq % 4) * 8 + i]), sc, -m_use));
+            pv[i] = exp2f(fmaf(__uint_as_float(s[gq * 8 + i]), sc, -m_use));
             l_blk += pv[i];
           }
           uint4 wv;
@@ -341,50 +348,53 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           wv.y = pack_bf16x2(pv[2], pv[3]);
           wv.z = pack_bf16x2(pv[4], pv[5]);
           wv.w = pack_bf16x2(pv[6], pv[7]);
-          *reinterpret_cast<uint4*>(atom + sw128_chunk_off(row, gq)) = wv;
+          *reinterpret_cast<uint4*>(atom + sw128_chunk_off(row, (cq & 1) * 4 + gq)) = wv;
         }
         l_run += l_blk;
         fence_proxy_async();  // the generic-proxy stores of P must be visible to the tensor core's reads
         tc_fence_before();
-        mbar_arrive(&bar_p_full[u]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_p_full[u]);
       }
       // ---- the tile's epilogue
       const uint32_t g_last = g0 + (uint32_t)n_kblocks - 1;
       ok = __all_sync(0xffffffffu, ok && mbar_wait_bounded(&bar_pv_done[g_last & 1], (g_last >> 1) & 1, abort_flag));
       if (!ok) break;
       tc_fence_after();
-      // total of the two halves' sums; slot parity continues the per-block sequence (block g_last used g_last & 1)
-      const int slot = (int)((g_last + 1) & 1) * 2;
-      xch[(slot + half) * ATT_BM + row] = l_run;
-      asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
-      const float l_tot = l_run + xch[(slot + (half ^ 1)) * ATT_BM + row];
-      // (the next tile's first block writes the same slots only after another 64-thread barrier: see below)
+      // total of the four partial sums; slot parity continues the per-block sequence (block g_last used g_last & 1)
+      float* xl = xch + (int)((g_last + 1) & 1) * 4 * ATT_BM + row;
+      xl[cq * ATT_BM] = l_run;
+      asm volatile("bar.sync %0, 128;" ::"r"(1 + quarter) : "memory");
+      const float l_tot = (xl[0] + xl[ATT_BM]) + (xl[2 * ATT_BM] + xl[3 * ATT_BM]);
       const float inv = l_tot > 0.0f ? 1.0f / l_tot : 0.0f;
-      __nv_bfloat16* dst = p.out + (((size_t)batch * p.seq + (row_ok ? qpos : 0)) * p.heads + head) * p.dv + dv0 + o_col;
+      if (o_active) {
+        __nv_bfloat16* dst = p.out + (((size_t)batch * p.seq + (row_ok ? qpos : 0)) * p.heads + head) * p.dv + dv0 + o_col;
 #pragma unroll 1
-      for (int c = 0; c < DV / 64; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(tmem_o + lane_off + o_col + (uint32_t)(c * 32), r);
-        tmem_wait_ld();
-        if (row_ok) {
+        for (int c = 0; c < O_W / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(tmem_o + lane_off + o_col + (uint32_t)(c * 32), r);
+          tmem_wait_ld();
+          if (row_ok) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 wv;
-            wv.x = pack_bf16x2(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
-            wv.y = pack_bf16x2(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
-            wv.z = pack_bf16x2(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
-            wv.w = pack_bf16x2(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
-            *reinterpret_cast<uint4*>(dst + c * 32 + i) = wv;
+            for (int i = 0; i < 32; i += 8) {
+              uint4 wv;
+              wv.x = pack_bf16x2(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+              wv.y = pack_bf16x2(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+              wv.z = pack_bf16x2(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+              wv.w = pack_bf16x2(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + c * 32 + i) = wv;
+            }
           }
         }
       }
       tc_fence_before();
-      mbar_arrive(&bar_o_free[t & 1]);
-      if (row_ok && half == 0 && p.lse != nullptr && dv0 == 0)
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_o_free[t & 1]);
+      if (row_ok && cq == 0 && p.lse != nullptr && dv0 == 0)
         p.lse[((size_t)batch * p.heads + head) * p.seq + qpos] = m_ref * 0.6931471805599453f + __logf(l_tot);
-      // keep the two warps of a quarter together across tiles: the sum exchange above and the next maximum exchange use
-      // the same slots
-      asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+      // keep the four warps of a row quarter together across tiles: the sum exchange above and the next maximum exchange
+      // use the same slots
+      asm volatile("bar.sync %0, 128;" ::"r"(1 + quarter) : "memory");
       g0 += (uint32_t)n_kblocks;
     }
     if (!ok) {
@@ -399,7 +409,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     for (int i = 0; i < 200; ++i) __nanosleep(1000);  // copies that may still be in flight land first
     __syncthreads();
   }
-  if (warp == 8) {
+  if (warp == FWD_ROW_WARPS) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
