@@ -526,8 +526,10 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
       if (p.gD_out != nullptr) *reinterpret_cast<float4*>(p.gD_out + o) = make_float4(gD[0], gD[1], gD[2], gD[3]);
       if (p.gE_out != nullptr) *reinterpret_cast<float4*>(p.gE_out + o) = make_float4(gE[0], gE[1], gE[2], gE[3]);
       if (p.update) {
+        // all six streams of this chunk are requested before the first is used (96 bytes in flight per thread)
+        float4 w = ldcs4(p.WD + o), m = ldcs4(p.mD + o), v = ldcs4(p.vD + o);
+        float4 we = ldcs4(p.WE + o), me = ldcs4(p.mE + o), ve = ldcs4(p.vE + o);
         {
-          float4 w = ldcs4(p.WD + o), m = ldcs4(p.mD + o), v = ldcs4(p.vD + o);
           adam_elem(w.x, m.x, v.x, gD[0], p.h); adam_elem(w.y, m.y, v.y, gD[1], p.h);
           adam_elem(w.z, m.z, v.z, gD[2], p.h); adam_elem(w.w, m.w, v.w, gD[3], p.h);
           stcs4(p.WD + o, w); stcs4(p.mD + o, m); stcs4(p.vD + o, v);
@@ -536,11 +538,10 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
           *reinterpret_cast<uint2*>(p.WD_bf16 + o) = sh;
         }
         {
-          float4 w = ldcs4(p.WE + o), m = ldcs4(p.mE + o), v = ldcs4(p.vE + o);
-          adam_elem(w.x, m.x, v.x, gE[0], p.h); adam_elem(w.y, m.y, v.y, gE[1], p.h);
-          adam_elem(w.z, m.z, v.z, gE[2], p.h); adam_elem(w.w, m.w, v.w, gE[3], p.h);
-          stcs4(p.WE + o, w); stcs4(p.mE + o, m); stcs4(p.vE + o, v);
-          uint2 sh; sh.x = pack_bf16x2(w.x, w.y); sh.y = pack_bf16x2(w.z, w.w);
+          adam_elem(we.x, me.x, ve.x, gE[0], p.h); adam_elem(we.y, me.y, ve.y, gE[1], p.h);
+          adam_elem(we.z, me.z, ve.z, gE[2], p.h); adam_elem(we.w, me.w, ve.w, gE[3], p.h);
+          stcs4(p.WE + o, we); stcs4(p.mE + o, me); stcs4(p.vE + o, ve);
+          uint2 sh; sh.x = pack_bf16x2(we.x, we.y); sh.y = pack_bf16x2(we.z, we.w);
           *reinterpret_cast<uint2*>(p.WE_bf16 + o) = sh;
         }
       }
