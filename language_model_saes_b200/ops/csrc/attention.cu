@@ -47,6 +47,31 @@ struct AttnSmem {
   static constexpr int kDynamicBytes = kTotal + 1024;
 };
 
+// Two-element fp32 arithmetic (one instruction for a pair): d = a * b + c and d = a + b on (lo, hi) pairs.
+__device__ __forceinline__ void fma_f32x2(float& d0, float& d1, float a0, float a1, float b, float c) {
+  asm("{\n\t"
+      ".reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\t"
+      "mov.b64 rb, {%4, %4};\n\t"
+      "mov.b64 rc, {%5, %5};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t"
+      "}"
+      : "=f"(d0), "=f"(d1)
+      : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+__device__ __forceinline__ void add_f32x2(float& d0, float& d1, float a0, float a1) {
+  asm("{\n\t"
+      ".reg .b64 ra, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\t"
+      "mov.b64 rd, {%0, %1};\n\t"
+      "add.rn.f32x2 rd, rd, ra;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t"
+      "}"
+      : "+f"(d0), "+f"(d1)
+      : "f"(a0), "f"(a1));
+}
+
 // byte offset of the 16-byte chunk `chunk` (0..7) of row `row` inside a 128-byte-swizzled K-major atom
 __device__ __forceinline__ uint32_t sw128_chunk_off(int row, int chunk) {
   return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4));
@@ -282,16 +307,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar_s_free[u]);
         // masked raw scores and their maximum (only the diagonal and the last block have anything to mask)
-        const bool need_mask = (k0 + 31 > qpos) || (k0 + 32 > p.seq);
+        // (warp-uniform branch: the common, unmasked case costs one maximum per element and nothing else)
+        const int last_ok = min(qpos, p.seq - 1) - k0;  // columns 0 .. last_ok of this thread's 32 are visible
         float m_raw = -INFINITY;
+        if (__any_sync(0xffffffffu, last_ok < 31)) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          float v = __uint_as_float(s[j]);
-          if (need_mask && !(k0 + j <= qpos && k0 + j < p.seq)) {
-            v = -INFINITY;
-            s[j] = __float_as_uint(v);
+          for (int j = 0; j < 32; ++j) {
+            if (j > last_ok) s[j] = 0xff800000u;  // -inf
+            m_raw = fmaxf(m_raw, __uint_as_float(s[j]));
           }
-          m_raw = fmaxf(m_raw, v);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) m_raw = fmaxf(m_raw, fmaxf(__uint_as_float(s[j]), __uint_as_float(s[j + 1])));
         }
         // the other three quarters of the row: exchange through shared memory, 128-thread barrier of the four warps
         // that share these 32 rows
@@ -332,16 +359,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           if (!__all_sync(0xffffffffu, mbar_wait_bounded(&bar_pv_done[u], ((g - 2) >> 1) & 1, abort_flag))) { ok = false; break; }
         }
         l_run *= alpha;
-        float l_blk = 0.0f;
+        float l_blk = 0.0f, l_blk1 = 0.0f;
         // this quarter's 32 keys are half of a 64-key swizzle atom: 16-byte chunks (cq % 2) * 4 .. + 3 of atom cq / 2
         uint8_t* atom = smem + L::kPOff + u * L::kPBytes + (cq >> 1) * ATOM_BYTES_128;
+        const float neg_m = -m_use;
 #pragma unroll
         for (int gq = 0; gq < 4; ++gq) {
           float pv[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            pv[i] = exp2f(fmaf(__uint_as_float(s[gq * 8 + i]), sc, -m_use));
-            l_blk += pv[i];
+          for (int i = 0; i < 8; i += 2) {
+            // exponent arguments and the running sums two elements per instruction; the exponentials one by one
+            float a0, a1;
+            fma_f32x2(a0, a1, __uint_as_float(s[gq * 8 + i]), __uint_as_float(s[gq * 8 + i + 1]), sc, neg_m);
+            pv[i] = exp2f(a0);
+            pv[i + 1] = exp2f(a1);
+            add_f32x2(l_blk, l_blk1, pv[i], pv[i + 1]);
           }
           uint4 wv;
           wv.x = pack_bf16x2(pv[0], pv[1]);
@@ -350,7 +382,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           wv.w = pack_bf16x2(pv[6], pv[7]);
           *reinterpret_cast<uint4*>(atom + sw128_chunk_off(row, (cq & 1) * 4 + gq)) = wv;
         }
-        l_run += l_blk;
+        l_run += l_blk + l_blk1;
         fence_proxy_async();  // the generic-proxy stores of P must be visible to the tensor core's reads
         tc_fence_before();
         __syncwarp();
