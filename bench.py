@@ -208,10 +208,12 @@ def run_ours(args):
     launches0 = K.kernel_launch_count()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
+    t_issue0 = time.perf_counter()
     for i in range(Ksteps):
         loss = engine.step(pool[(W + i) % POOL], pool[(W + i) % POOL], TOP_K, LR)
     engine.join()  # ... and before it stops: the last step's update is inside the timed region
     end.record()
+    host_issue_ms = (time.perf_counter() - t_issue0) * 1e3 / Ksteps  # host time to enqueue one step (no synchronisation)
     barrier()
     launches = K.kernel_launch_count() - launches0
     clocks = sampler.stop()
@@ -266,7 +268,8 @@ def run_ours(args):
                     "api": "Trainer.fit(sae, stream of pinned host batches): copy of batch i+1 overlaps step i, each rank copies "
                            "1/N of the rows over PCIe and all-gathers them over NVLink; the loss of every step is copied to pinned host memory "
                            "on every rank and read one step later, so the host runs one step ahead of the device"},
-            "gpu_launches": launches, "final_loss": final_loss, "impl": "ours", "package": lm.__name__,
+            "gpu_launches": launches, "host_issue_ms_per_step": round(host_issue_ms, 4), "final_loss": final_loss, "impl": "ours",
+            "package": lm.__name__,
         })  # fmt: skip
     if world > 1:
         dist.destroy_process_group()

@@ -60,6 +60,12 @@ __device__ __forceinline__ void fma_f32x2(float& d0, float& d1, float a0, float 
       : "=f"(d0), "=f"(d1)
       : "f"(a0), "f"(a1), "f"(b), "f"(c));
 }
+// max of three in one instruction
+__device__ __forceinline__ float max3_f32(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 __device__ __forceinline__ void add_f32x2(float& d0, float& d1, float a0, float a1) {
   asm("{\n\t"
       ".reg .b64 ra, rd;\n\t"
@@ -318,7 +324,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           }
         } else {
 #pragma unroll
-          for (int j = 0; j < 32; j += 2) m_raw = fmaxf(m_raw, fmaxf(__uint_as_float(s[j]), __uint_as_float(s[j + 1])));
+          for (int j = 0; j < 32; j += 2) m_raw = max3_f32(m_raw, __uint_as_float(s[j]), __uint_as_float(s[j + 1]));
         }
         // the other three quarters of the row: exchange through shared memory, 128-thread barrier of the four warps
         // that share these 32 rows
