@@ -681,12 +681,21 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       tmem_ld_32x32b_x32(tmem_dp + lane_off + (uint32_t)(c * 32), rp);
       tmem_wait_ld();
       float ds[32];
+      if (kb < qblk && k0 + ATT_BN <= p.seq) {
+        // a block below the diagonal and inside the sequence: nothing to mask (uniform over the CTA)
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const int kpos = k0 + c * 32 + j;
-        const bool valid = kpos <= qpos && kpos < p.seq;
-        const float pr = valid ? exp2f(__uint_as_float(rs[j]) * p.scale_log2 - lse2) : 0.0f;
-        ds[j] = pr * (__uint_as_float(rp[j]) - delta) * p.scale;
+        for (int j = 0; j < 32; ++j) {
+          const float pr = exp2f(fmaf(__uint_as_float(rs[j]), p.scale_log2, -lse2));
+          ds[j] = pr * (__uint_as_float(rp[j]) - delta) * p.scale;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int kpos = k0 + c * 32 + j;
+          const bool valid = kpos <= qpos && kpos < p.seq;
+          const float pr = valid ? exp2f(fmaf(__uint_as_float(rs[j]), p.scale_log2, -lse2)) : 0.0f;
+          ds[j] = pr * (__uint_as_float(rp[j]) - delta) * p.scale;
+        }
       }
       uint8_t* atom = smem + L::kDsOff + (c / 2) * ATOM_BYTES_128;
 #pragma unroll
@@ -912,13 +921,23 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
       tmem_ld_32x32b_x32(tmem_dpt + lane_off + (uint32_t)(c * 32), rp);
       tmem_wait_ld();
       float pt[32], ds[32];
+      if (qb > kblk && q0 + ATT_BM <= p.seq && k0 + ATT_BN <= p.seq) {
+        // a query block above the diagonal, both blocks inside the sequence: nothing to mask (uniform over the CTA)
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const int col = c * 32 + j;
-        const int qp = q0 + col;
-        const bool valid = row_ok && kpos <= qp && qp < p.seq;
-        pt[j] = valid ? exp2f(__uint_as_float(rs[j]) * p.scale_log2 - s_lse[col]) : 0.0f;
-        ds[j] = pt[j] * (__uint_as_float(rp[j]) - s_delta[col]) * p.scale;
+        for (int j = 0; j < 32; ++j) {
+          const int col = c * 32 + j;
+          pt[j] = exp2f(fmaf(__uint_as_float(rs[j]), p.scale_log2, -s_lse[col]));
+          ds[j] = pt[j] * (__uint_as_float(rp[j]) - s_delta[col]) * p.scale;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int col = c * 32 + j;
+          const int qp = q0 + col;
+          const bool valid = row_ok && kpos <= qp && qp < p.seq;
+          pt[j] = valid ? exp2f(fmaf(__uint_as_float(rs[j]), p.scale_log2, -s_lse[col])) : 0.0f;
+          ds[j] = pt[j] * (__uint_as_float(rp[j]) - s_delta[col]) * p.scale;
+        }
       }
       uint8_t* atom_p = smem + L::kPtOff + (c / 2) * ATOM_BYTES_128;
       uint8_t* atom_d = smem + L::kDstOff + (c / 2) * ATOM_BYTES_128;
