@@ -92,6 +92,7 @@ class FusedTopKSAEStep:
         self.last_aux_loss: torch.Tensor | None = None
         self.main_counts: torch.Tensor | None = None
         self.grad_sq = z(1)
+        self.last_grad_norm: torch.Tensor | None = None  # global gradient norm before clipping (set when clipping is on)
         self.t = 0
         # ---- update / next-encode overlap ----
         tiles = (F + 255) // 256
@@ -281,19 +282,23 @@ class FusedTopKSAEStep:
         grad_mul: torch.Tensor | None = None,
         want_grad_norm: bool = False,
         aux: "AuxK | None" = None,
+        clip_grad_norm: float = 0.0,
     ) -> torch.Tensor:
         """Forward, backward and Adam update for one batch; returns the mean loss (0-d device tensor, local
         batch). ``x`` / ``label``: normalised bf16 [B, d]; ``row_weight``: optional 0/1 token mask. ``aux`` adds the
-        Aux-K dead-feature loss (its mean is left in ``self.last_aux_loss`` and included in the returned loss)."""
+        Aux-K dead-feature loss (its mean is left in ``self.last_aux_loss`` and included in the returned loss).
+        ``clip_grad_norm`` > 0 scales the gradient so that its global 2-norm is at most that value (the norm before
+        clipping is left in ``self.last_grad_norm``): the gradient is never materialised, so the sparse gradient
+        kernel runs twice, first without writing anything to accumulate the squared norm, then with the factor."""
         if aux is not None:
-            return self._step_auxk(x, label, k, lr, row_weight, n_tokens_global, aux)
+            return self._step_auxk(x, label, k, lr, row_weight, n_tokens_global, aux, clip_grad_norm)
         B = x.shape[0]
         n_global = n_tokens_global if n_tokens_global is not None else B * self.dp
         grad_scale = 2.0 / n_global
         use_comm = self.comm is not None and B == self.comm.B and k <= self.comm.k_max and not self.batch_level
         if use_comm:
             self.comm.next_epoch()
-        overlap = len(self.chunks) > 1 and k <= 64 and grad_mul is None and not want_grad_norm
+        overlap = len(self.chunks) > 1 and k <= 64 and grad_mul is None and not want_grad_norm and not clip_grad_norm
         idx, act = self.encode(x, k, _in_step=overlap)
         self.loss_sum.zero_()
         if use_comm:
@@ -319,15 +324,19 @@ class FusedTopKSAEStep:
         if want_grad_norm:
             self.grad_sq.zero_()
             gsq = self.grad_sq
-        adam = lambda f_range=None, ctas_per_sm=0: K.sparse_grad_adam(  # noqa: E731
+        sparse = lambda mul, sq, update, f_range=None, ctas_per_sm=0: K.sparse_grad_adam(  # noqa: E731
             self.groups, act, dact, x, dxhat, self.WD, mD, vD, self.WD_bf16, self.WE, mE, vE, self.WE_bf16,
-            self.bE, mb, vb, self.dec_norm, grad_mul, gsq, lr, b1, b2, self.eps, self.t, True, f_range=f_range,
+            self.bE, mb, vb, self.dec_norm, mul, sq, lr, b1, b2, self.eps, self.t, update, f_range=f_range,
             ctas_per_sm=ctas_per_sm,
         )  # fmt: skip
+        g_bD = K.colsum_bf16(dxhat) if self.bD is not None else None
+        if clip_grad_norm:
+            assert grad_mul is None, "pass either a gradient factor or a clipping norm"
+            grad_mul, gsq = self._clip_factor(sparse, g_bD, clip_grad_norm), None
+        adam = lambda f_range=None, ctas_per_sm=0: sparse(grad_mul, gsq, True, f_range, ctas_per_sm)  # noqa: E731
 
         def bias_update():
             if self.bD is not None:
-                g_bD = K.colsum_bf16(dxhat)
                 m, v = self.state["b_D"]
                 K.adam_flat(self.bD, g_bD, m, v, lr, b1, b2, self.eps, self.t, grad_mul=grad_mul, grad_sq_sum=gsq)
 
@@ -357,7 +366,21 @@ class FusedTopKSAEStep:
             n_local = n_local / self.tp  # each rank evaluated the loss on the B / tp rows it owns
         return (self.loss_sum / n_local).squeeze(0)
 
-    def _step_auxk(self, x, label, k, lr, row_weight, n_tokens_global, aux: "AuxK") -> torch.Tensor:
+    def _clip_factor(self, sparse, g_bD: torch.Tensor | None, max_norm: float) -> torch.Tensor:
+        """The factor ``min(1, max_norm / (|g| + 1e-6))`` of torch.nn.utils.clip_grad_norm_ as a 1-element device
+        tensor. ``sparse(mul, sq, update)`` launches the sparse gradient kernel; here it only accumulates squared
+        gradient entries of this rank's feature rows. Sharded parameters add up over the model group, the decoder bias
+        is replicated and counted once."""
+        self.grad_sq.zero_()
+        sparse(None, self.grad_sq, False)
+        if self.tp > 1:
+            dist.all_reduce(self.grad_sq, group=self.tp_group)
+        total = self.grad_sq if g_bD is None else self.grad_sq + g_bD.square().sum()
+        norm = total.sqrt()
+        self.last_grad_norm = norm.squeeze(0)
+        return (max_norm / (norm + 1e-6)).clamp(max=1.0)
+
+    def _step_auxk(self, x, label, k, lr, row_weight, n_tokens_global, aux: "AuxK", clip_grad_norm: float = 0.0) -> torch.Tensor:
         """The step with the Aux-K loss (single GPU): ``l = |e|^2 + alpha |e - e_aux|^2`` where ``e_aux`` decodes the
         ``k_aux`` largest gated pre-activations among DEAD features (models/sparse_dictionary.py:941-991 and
         trainer.py:428-454 of the reference project). The dead features are gathered into a compact dictionary
@@ -410,14 +433,17 @@ class FusedTopKSAEStep:
         self.t += 1
         b1, b2 = self.betas
         (mE, vE), (mD, vD), (mb, vb) = self.state["W_E"], self.state["W_D"], self.state["b_E"]
-        K.sparse_grad_adam(
+        sparse = lambda mul, sq, update: K.sparse_grad_adam(  # noqa: E731
             self.groups, act_all, dact_all, x, g_main, self.WD, mD, vD, self.WD_bf16, self.WE, mE, vE, self.WE_bf16,
-            self.bE, mb, vb, self.dec_norm, None, None, lr, b1, b2, self.eps, self.t, True,
+            self.bE, mb, vb, self.dec_norm, mul, sq, lr, b1, b2, self.eps, self.t, update,
             dxhat_aux=g_aux if k_aux > 0 else None, k_main=k,
         )  # fmt: skip
+        g_bD = K.colsum_bf16(g_main) if self.bD is not None else None
+        grad_mul = self._clip_factor(sparse, g_bD, clip_grad_norm) if clip_grad_norm else None
+        sparse(grad_mul, None, True)
         if self.bD is not None:
             m, v = self.state["b_D"]
-            K.adam_flat(self.bD, K.colsum_bf16(g_main), m, v, lr, b1, b2, self.eps, self.t)
+            K.adam_flat(self.bD, g_bD, m, v, lr, b1, b2, self.eps, self.t, grad_mul=grad_mul)
         n_local = B if row_weight is None else row_weight.sum()
         self.last_aux_loss = (self.aux_sum / n_local).squeeze(0)
         return ((self.loss_sum + self.aux_sum) / n_local).squeeze(0)

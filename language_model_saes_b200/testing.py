@@ -34,6 +34,10 @@ def _child(rank: int, world: int, port: int, backend: str, module_path: str, fun
     try:
         if backend == "nccl":
             torch.cuda.set_device(rank)
+        else:
+            # one thread per rank: CPU reductions then add in the same order whatever the load of the machine, so a
+            # comparison between a sharded and an unsharded run does not depend on how many cores were free
+            torch.set_num_threads(1)
         dist.init_process_group(backend, rank=rank, world_size=world)
         spec = importlib.util.spec_from_file_location("_dist_test_module", module_path)
         mod = importlib.util.module_from_spec(spec)

@@ -602,6 +602,8 @@ class Trainer:
             acc["tokens"] = 0
             acc["steps"] = 0
         acc["loss"] += loss
+        if f.last_grad_norm is not None and self.cfg.clip_grad_norm > 0:  # interval maximum, as GradientNormMetric keeps it
+            acc["grad_norm"] = torch.maximum(acc.get("grad_norm", f.last_grad_norm), f.last_grad_norm)
         n_rows = f.groups.entries.numel() and (x.shape[0] * f.dp)
         acc["fire"] += (f.main_counts if f.main_counts is not None else f.groups.counts[: f.F]).float()
         acc["tokens"] += n_rows
@@ -638,6 +640,10 @@ class Trainer:
             "sparsity/above_1e-1": c[0], "sparsity/above_1e-2": c[1], "sparsity/below_1e-5": c[2],
             "sparsity/below_1e-6": c[3], "sparsity/below_1e-7": c[4],
         }  # fmt: skip
+        if "grad_norm" in acc:
+            before = float(acc["grad_norm"])
+            out["metrics/gradient_norm_before_clipping"] = before
+            out["metrics/gradient_norm_per_param"] = min(before, self.cfg.clip_grad_norm)
         out.update(self._details({}, lr))
         out.update(sae.log_statistics())
         self._interval = {}
@@ -843,9 +849,6 @@ class Trainer:
             sae.set_current_k(k)
         lr_factor = self._lr_lambda(self.cur_step) if self._lr_lambda is not None else 1.0
         lr = float(self.cfg.lr) * lr_factor
-        grad_mul = None
-        if self.cfg.clip_grad_norm > 0:
-            grad_mul = self._fused_clip_factor(f, x, label, sae.current_k, row_weight, n_global)
         aux = None
         if self.cfg.auxk_coefficient:
             if self._fused_aux is None:
@@ -855,14 +858,11 @@ class Trainer:
                 self._fused_aux = AuxK(f.F, self.cfg.k_aux, self.cfg.auxk_coefficient, self.cfg.dead_threshold, x.device,
                                        counter=self.tokens_since_last_activation)  # fmt: skip
             aux = self._fused_aux
-        loss = f.step(x, label, sae.current_k, lr, row_weight=row_weight, n_tokens_global=n_global, grad_mul=grad_mul, aux=aux)
+        loss = f.step(x, label, sae.current_k, lr, row_weight=row_weight, n_tokens_global=n_global, aux=aux,
+                      clip_grad_norm=max(0.0, self.cfg.clip_grad_norm))
         if aux is not None:  # keep the trainer's view (checkpoints, logging) in step with the engine's counters
             self.tokens_since_last_activation, self.is_dead = aux.tokens_since_last_activation, aux.is_dead
         if not self.cfg.skip_metrics_calculation:
             self._log_fused(sae, x, label, mask, loss, lr)
         return loss
 
-    def _fused_clip_factor(self, f, x, label, k, row_weight, n_global) -> Tensor:
-        """Clipping needs the gradient norm before the update; on the fused path that costs one extra
-        forward/backward pass that only accumulates squared gradients (no parameter is written)."""
-        raise NotImplementedError("gradient clipping is not available on the fused path; set use_fused_kernels=False")

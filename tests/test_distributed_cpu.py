@@ -91,6 +91,60 @@ def test_fused_step_feature_and_data_parallel_match_single():
     assert torch.allclose(dp.W_E.data, ref.W_E.data, atol=1e-5)
 
 
+def _moment_norm(eng) -> torch.Tensor:
+    return torch.sqrt(sum(st[0].square().sum() for st in eng.state.values() if st is not None))
+
+
+def _clip_case(make):
+    """First Adam moments after one step are 0.1 x the (clipped) gradient: their norm shows the factor that was applied."""
+    x = _data().to(torch.bfloat16)
+    e0 = FusedTopKSAEStep(make())
+    e0.step(x, x, 8, 1e-2)
+    g = _moment_norm(e0) / 0.1
+    e1 = FusedTopKSAEStep(make())
+    e1.step(x, x, 8, 1e-2, clip_grad_norm=float(g) / 4)
+    e2 = FusedTopKSAEStep(make())
+    e2.step(x, x, 8, 1e-2, clip_grad_norm=float(g) * 10)
+    return g, e0, e1, e2
+
+
+def test_fused_step_clips_the_global_gradient_norm():
+    full = _full_model()
+
+    def make():
+        m = SparseAutoEncoder(full.cfg.model_copy())
+        m.load_full_state_dict(full.full_state_dict())
+        return m
+
+    g, e0, e1, e2 = _clip_case(make)
+    assert torch.allclose(e1.last_grad_norm, g, rtol=1e-4) and torch.allclose(e2.last_grad_norm, g, rtol=1e-4)
+    assert torch.allclose(_moment_norm(e1), 0.1 * g / 4, rtol=1e-3)  # clipped to a quarter of the norm
+    assert torch.allclose(e2.WD, e0.WD) and torch.allclose(e2.bD, e0.bD)  # a bound above the norm changes nothing
+    # the norm agrees with autograd on the same loss (the fused path rounds operands to bf16: loose tolerance)
+    ref = make()
+    x = _data().to(torch.bfloat16).float()
+    ref.compute_loss({"h": x, "tokens": torch.zeros(x.shape[0], dtype=torch.long)})["loss"].backward()
+    want = torch.sqrt(sum(p.grad.square().sum() for p in ref.parameters() if p.grad is not None))
+    assert torch.allclose(g, want, rtol=5e-2), (g, want)
+
+
+@distributed_test(nproc_per_node=2, backend="gloo")
+def test_fused_step_clipping_feature_parallel_matches_single():
+    full = _full_model()
+
+    def single():
+        m = SparseAutoEncoder(full.cfg.model_copy())
+        m.load_full_state_dict(full.full_state_dict())
+        return m
+
+    g, _, e1, _ = _clip_case(single)
+    mesh = build_mesh("cpu", (1, 2), ("data", "model"))
+    gt, _, t1, _ = _clip_case(lambda: _sharded_copy(full, mesh))
+    assert torch.allclose(t1.last_grad_norm, g, rtol=1e-4)  # sharded rows add up over the group, the decoder bias counts once
+    W = DimMap({"model": 0}).gather(t1.WD, mesh)
+    assert torch.allclose(W, e1.WD, atol=1e-5)
+
+
 @distributed_test(nproc_per_node=2, backend="gloo")
 def test_fused_batchtopk_step_feature_and_data_parallel_match_single():
     """Batch-level top-k on the fused path: feature shards share one threshold (and ration the ties between them), data
@@ -157,6 +211,7 @@ def test_heartbeat_reports_a_rank_that_leaves_and_one_that_goes_silent():
     hb.beat(0)
     dist.barrier()
     hb.check()  # both alive
+    dist.barrier()  # rank 1 must not announce that it leaves before rank 0 has looked
     if rank == 1:
         hb.leave("ValueError: injected on the host")  # what Trainer.fit does in its exception handler
         dist.barrier()
