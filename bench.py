@@ -207,10 +207,14 @@ def run_ours(args):
     sampler.start()
     launches0 = K.kernel_launch_count()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # one more event after every step (a marker in the stream, no synchronisation): the spread of the per-step times
+    # shows whether a slow average comes from every step or from a few stalls
+    marks_ev = [torch.cuda.Event(enable_timing=True) for _ in range(Ksteps)]
     start.record()
     t_issue0 = time.perf_counter()
     for i in range(Ksteps):
         loss = engine.step(pool[(W + i) % POOL], pool[(W + i) % POOL], TOP_K, LR)
+        marks_ev[i].record()
     engine.join()  # ... and before it stops: the last step's update is inside the timed region
     end.record()
     host_issue_ms = (time.perf_counter() - t_issue0) * 1e3 / Ksteps  # host time to enqueue one step (no synchronisation)
@@ -218,8 +222,22 @@ def run_ours(args):
     launches = K.kernel_launch_count() - launches0
     clocks = sampler.stop()
     ms = start.elapsed_time(end)
+    per_step = torch.tensor([a.elapsed_time(b) for a, b in zip([start] + marks_ev[:-1], marks_ev)], device=dev, dtype=torch.float64)
     K.check_status(dev)
     final_loss = float(loss)
+    phases = None
+    if os.environ.get("LMSAE_BENCH_PHASES", "0") == "1":  # diagnostics, after and outside the timed region
+        engine.start_phase_timing()
+        for i in range(Ksteps):
+            engine.step(pool[i % POOL], pool[i % POOL], TOP_K, LR)
+        pt = engine.phase_times()
+        names = list(pt)
+        vals = torch.tensor([pt[n] for n in names], device=dev, dtype=torch.float64)
+        lo = vals.clone()
+        if world > 1:
+            dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        phases = {n: [round(a, 4), round(b, 4)] for n, a, b in zip(names, lo.tolist(), vals.tolist())}  # [min, max] over ranks
     collectives = "none" if world == 1 else ("fused peer-memory kernels" if comm is not None else "nccl")
     del engine, pool, comm
     torch.cuda.empty_cache()
@@ -251,6 +269,10 @@ def run_ours(args):
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, e2e_ms = t.tolist()
+    if world > 1:
+        dist.all_reduce(per_step, op=dist.ReduceOp.MAX)
+    step_ms = {"min": round(float(per_step.min()), 4), "median": round(float(per_step.median()), 4),
+               "max": round(float(per_step.max()), 4)}  # fmt: skip
     if rank == 0:
         value = Ksteps * BATCH / (ms / 1e3)
         emit({
@@ -268,7 +290,7 @@ def run_ours(args):
                     "api": "Trainer.fit(sae, stream of pinned host batches): copy of batch i+1 overlaps step i, each rank copies "
                            "1/N of the rows over PCIe and all-gathers them over NVLink; the loss of every step is copied to pinned host memory "
                            "on every rank and read one step later, so the host runs one step ahead of the device"},
-            "gpu_launches": launches, "host_issue_ms_per_step": round(host_issue_ms, 4), "final_loss": final_loss, "impl": "ours",
+            "gpu_launches": launches, "host_issue_ms_per_step": round(host_issue_ms, 4), "step_ms": step_ms, **({"phase_ms_min_max_over_ranks": phases} if phases else {}), "final_loss": final_loss, "impl": "ours",
             "package": lm.__name__,
         })  # fmt: skip
     if world > 1:

@@ -93,6 +93,7 @@ class FusedTopKSAEStep:
         self.main_counts: torch.Tensor | None = None
         self.grad_sq = z(1)
         self.last_grad_norm: torch.Tensor | None = None  # global gradient norm before clipping (set when clipping is on)
+        self.phase_marks: list[tuple[str, torch.cuda.Event]] | None = None  # see start_phase_timing()
         self.t = 0
         # ---- update / next-encode overlap ----
         tiles = (F + 255) // 256
@@ -149,6 +150,31 @@ class FusedTopKSAEStep:
             if not ok:
                 return False, why
         return True, ""
+
+    # ---- per-phase device timing (diagnostics) -------------------------------------------------
+    def start_phase_timing(self) -> None:
+        """From now on ``step`` drops a timing event into the stream after each of its phases. Events are markers, not
+        synchronisation points; ``phase_times`` reads them back."""
+        self.phase_marks = []
+
+    def _mark(self, name: str) -> None:
+        if self.phase_marks is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.phase_marks.append((name, ev))
+
+    def phase_times(self) -> dict[str, float]:
+        """Mean milliseconds per step of every phase since ``start_phase_timing`` (synchronises), and stops the marking.
+        A phase's time runs from the previous mark to its own, so it contains the wait for peers that the phase's
+        kernels do on entry."""
+        marks, self.phase_marks = self.phase_marks or [], None
+        torch.cuda.synchronize()
+        total: dict[str, float] = {}
+        steps = max(1, sum(1 for n, _ in marks if n == "begin"))
+        for (_, a), (name, b) in zip(marks, marks[1:]):
+            name = "between_steps" if name == "begin" else name
+            total[name] = total.get(name, 0.0) + a.elapsed_time(b)
+        return {n: t / steps for n, t in total.items()}
 
     def join(self) -> None:
         """Make the current stream wait for every update launched so far (call before reading or writing the weights,
@@ -233,9 +259,11 @@ class FusedTopKSAEStep:
                 cv, ci = self._candidates_chunked(x, k, gate)
             else:
                 cv, ci, _ = K.encoder_topk_candidates(x, self.WE_bf16, self.bE, gate, k)
+            self._mark("encoder_gemm_topk")
             if self.tp == 1:
                 return K.topk_merge(cv, ci, k, gate)
             idx_l, g_l = K.topk_merge(cv, ci, k, gate, emit_gated=True)
+            self._mark("local_merge")
         else:
             H = K.encoder_hidden(x, self.WE_bf16, self.bE)
             idx_l, act_l = K.row_topk(H, k, gate, None)
@@ -244,6 +272,7 @@ class FusedTopKSAEStep:
             g_l = act_l * gate[idx_l.clamp_min(0).long()] if gate is not None else act_l
         if self.comm is not None and x.shape[0] == self.comm.B and k <= self.comm.k_max:
             all_g, all_i = self.comm.exchange_candidates(g_l, idx_l)
+            self._mark("exchange_candidates")
         else:
             B = x.shape[0]
             all_g = torch.empty(self.tp * B, k, dtype=torch.float32, device=x.device)
@@ -299,12 +328,16 @@ class FusedTopKSAEStep:
         if use_comm:
             self.comm.next_epoch()
         overlap = len(self.chunks) > 1 and k <= 64 and grad_mul is None and not want_grad_norm and not clip_grad_norm
+        self._mark("begin")
         idx, act = self.encode(x, k, _in_step=overlap)
+        self._mark("merge")
         self.loss_sum.zero_()
         if use_comm:
             # loss_sum collects the rows this rank owns; scale to a local-batch estimate for the return value
             dxhat, _ = self.comm.decode_reduce_loss(idx, act, self.WD_bf16, label, self.bD, row_weight, grad_scale, self.loss_sum)
+            self._mark("decode_reduce_loss")
             dact = K.sparse_dact(idx, self.WD_bf16, dxhat)
+            self._mark("dact")
         elif self.tp == 1:
             dxhat, dact, _ = K.sparse_decode_loss(idx, act, self.WD_bf16, self.bD, label, row_weight, grad_scale, self.loss_sum)
         else:
@@ -316,7 +349,10 @@ class FusedTopKSAEStep:
             x, dxhat, idx, act, dact = self._gather_rows(x, dxhat, idx, act, dact)
         if self.groups is None or self.groups.entries.numel() < idx.numel():
             self.groups = K.FeatureGroups(self.F, idx.numel(), x.device)
+        if not use_comm:
+            self._mark("decode_loss_dact")
         self.groups.build(idx)
+        self._mark("sort_by_feature")
         self.t += 1
         b1, b2 = self.betas
         (mE, vE), (mD, vD), (mb, vb) = self.state["W_E"], self.state["W_D"], self.state["b_E"]
@@ -360,7 +396,9 @@ class FusedTopKSAEStep:
                     self.adam_done[c] = ev
         else:
             adam()
+            self._mark("sparse_grad_adam")
             bias_update()
+            self._mark("bias_update")
         n_local = B if row_weight is None else row_weight.sum()
         if use_comm:
             n_local = n_local / self.tp  # each rank evaluated the loss on the B / tp rows it owns
