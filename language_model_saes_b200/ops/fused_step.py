@@ -316,8 +316,8 @@ class FusedTopKSAEStep:
         """Forward, backward and Adam update for one batch; returns the mean loss (0-d device tensor, local
         batch). ``x`` / ``label``: normalised bf16 [B, d]; ``row_weight``: optional 0/1 token mask. ``aux`` adds the
         Aux-K dead-feature loss (its mean is left in ``self.last_aux_loss`` and included in the returned loss).
-        ``clip_grad_norm`` > 0 scales the gradient so that its global 2-norm is at most that value (the norm before
-        clipping is left in ``self.last_grad_norm``): the gradient is never materialised, so the sparse gradient
+        ``clip_grad_norm`` > 0 scales the gradient down when its norm (2-norm over the root of the number of non-zero
+        entries, the trainer's definition; left in ``self.last_grad_norm``) exceeds that value: the gradient is never materialised, so the sparse gradient
         kernel runs twice, first without writing anything to accumulate the squared norm, then with the factor."""
         if aux is not None:
             return self._step_auxk(x, label, k, lr, row_weight, n_tokens_global, aux, clip_grad_norm)
@@ -405,18 +405,23 @@ class FusedTopKSAEStep:
         return (self.loss_sum / n_local).squeeze(0)
 
     def _clip_factor(self, sparse, g_bD: torch.Tensor | None, max_norm: float) -> torch.Tensor:
-        """The factor ``min(1, max_norm / (|g| + 1e-6))`` of torch.nn.utils.clip_grad_norm_ as a 1-element device
-        tensor. ``sparse(mul, sq, update)`` launches the sparse gradient kernel; here it only accumulates squared
-        gradient entries of this rank's feature rows. Sharded parameters add up over the model group, the decoder bias
-        is replicated and counted once."""
+        """The trainer's clipping factor as a 1-element device tensor. The norm is the reference project's
+        (optim.py:255-292 there): ``|g|_2 / sqrt(number of non-zero gradient entries)``, and the gradient is scaled by
+        ``max_norm / (norm + 1e-6)`` only when the norm exceeds ``max_norm``. ``sparse(mul, sq, update)`` launches the
+        sparse gradient kernel; here it only accumulates squared gradient entries of this rank's feature rows. A
+        feature that fired has ``2 d + 1`` gradient entries (its decoder row, encoder row and encoder bias), counted as
+        non-zero; sharded parameters add up over the model group, the replicated decoder bias is counted once."""
         self.grad_sq.zero_()
         sparse(None, self.grad_sq, False)
+        fired = (self.groups.counts[: self.F] > 0).sum().float().reshape(1)
+        acc = torch.cat([self.grad_sq, fired * (2 * self.d + 1)])
         if self.tp > 1:
-            dist.all_reduce(self.grad_sq, group=self.tp_group)
-        total = self.grad_sq if g_bD is None else self.grad_sq + g_bD.square().sum()
-        norm = total.sqrt()
-        self.last_grad_norm = norm.squeeze(0)
-        return (max_norm / (norm + 1e-6)).clamp(max=1.0)
+            dist.all_reduce(acc, group=self.tp_group)
+        if g_bD is not None:
+            acc = acc + torch.stack([g_bD.square().sum(), (g_bD != 0).sum().float()])
+        norm = (acc[0] / acc[1].clamp_min(1.0)).sqrt()
+        self.last_grad_norm = norm
+        return torch.where(norm > max_norm, max_norm / (norm + 1e-6), torch.ones_like(norm)).reshape(1)
 
     def _step_auxk(self, x, label, k, lr, row_weight, n_tokens_global, aux: "AuxK", clip_grad_norm: float = 0.0) -> torch.Tensor:
         """The step with the Aux-K loss (single GPU): ``l = |e|^2 + alpha |e - e_aux|^2`` where ``e_aux`` decodes the

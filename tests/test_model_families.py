@@ -79,7 +79,7 @@ def test_sae_fused_with_auxk(dev="cuda"):
 @pytest.mark.parametrize("auxk", [None, 1 / 32])
 def test_sae_fused_with_gradient_clipping(auxk, dev="cuda"):
     cfg = SAEConfig(hook_point_in="h", hook_point_out="h", d_model=D, expansion_factor=32, act_fn="topk", top_k=8, device=dev, dtype=torch.float32)
-    sae, trainer = _fit(cfg, ["h"], l1_coefficient=None, clip_grad_norm=0.05, auxk_coefficient=auxk, k_aux=32, dead_threshold=2000)
+    sae, trainer = _fit(cfg, ["h"], l1_coefficient=None, clip_grad_norm=1e-5, auxk_coefficient=auxk, k_aux=32, dead_threshold=2000)
     assert trainer.fused is not None and float(trainer.fused.last_grad_norm) > 0
 
 
