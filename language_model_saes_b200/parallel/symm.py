@@ -31,6 +31,20 @@ def _align(n: int, a: int = 256) -> int:
     return (n + a - 1) // a * a
 
 
+def step_buffer_layout(batch: int, world: int, k_max: int, d_model: int) -> dict[str, int]:
+    """Byte offsets of the regions of one rank's buffer for the fused step (the same on every rank): ``flags``
+    ``[phase][source rank]`` epoch words, ``cand_val`` / ``cand_idx`` ``[B][world * k]``, ``partial``
+    ``[world][B / world][d]`` fp32, ``dxhat`` ``[B][d]`` bf16, and the total ``nbytes``."""
+    lay, off = {}, 0
+    for name, nbytes in (("flags", _NUM_PHASES * _MAX_PEERS * 4), ("cand_val", batch * world * k_max * 4),
+                         ("cand_idx", batch * world * k_max * 4), ("partial", batch * d_model * 4),
+                         ("dxhat", batch * d_model * 2)):  # fmt: skip
+        lay[name] = off
+        off = _align(off + nbytes)
+    lay["nbytes"] = off
+    return lay
+
+
 class SymmComm:
     def __init__(self, group: dist.ProcessGroup, device: torch.device, batch: int, k_max: int, d_model: int):
         import torch.distributed._symmetric_memory as symm_mem
@@ -41,18 +55,9 @@ class SymmComm:
         assert self.world <= _MAX_PEERS, f"at most {_MAX_PEERS} feature shards per peer-memory group"
         assert batch % self.world == 0, "batch must be divisible by the number of feature shards"
         self.B, self.k_max, self.d = batch, k_max, d_model
-        off = 0
-        self.flags_off = off
-        off = _align(off + _NUM_PHASES * _MAX_PEERS * 4)
-        self.cand_val_off = off
-        off = _align(off + batch * self.world * k_max * 4)
-        self.cand_idx_off = off
-        off = _align(off + batch * self.world * k_max * 4)
-        self.partial_off = off
-        off = _align(off + batch * d_model * 4)
-        self.dxhat_off = off
-        off = _align(off + batch * d_model * 2)
-        self.nbytes = off
+        lay = step_buffer_layout(batch, self.world, k_max, d_model)
+        self.flags_off, self.cand_val_off, self.cand_idx_off = lay["flags"], lay["cand_val"], lay["cand_idx"]
+        self.partial_off, self.dxhat_off, self.nbytes = lay["partial"], lay["dxhat"], lay["nbytes"]
         try:
             symm_mem.enable_symm_mem_for_group(group.group_name)
         except Exception:  # noqa: BLE001  (newer torch enables groups implicitly)

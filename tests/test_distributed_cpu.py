@@ -199,6 +199,62 @@ def test_fused_batchtopk_step_feature_and_data_parallel_match_single():
     assert torch.equal(both[0], both[1])  # replicas stay identical
 
 
+def _run_fused_comm(sae, xs, k, comm, lr=1e-2):
+    eng = FusedTopKSAEStep(sae, comm=comm)
+    return eng, torch.stack([eng.step(x, x, k, lr) for x in xs])
+
+
+@distributed_test(nproc_per_node=2, backend="gloo")
+def test_peer_memory_protocol_on_the_host_matches_collectives():
+    """The peer-buffer protocol of the fused step (stores into peers' buffers, epoch flags, bounded waits) run by the
+    host over a shared-memory file: same losses and weights as the all-reduce path, over several steps (the buffers are
+    re-used without a barrier), also when one rank publishes a flag late."""
+    from language_model_saes_b200.parallel.host_transport import HostPeerComm
+    from language_model_saes_b200.parallel.mesh import mesh_group
+    from language_model_saes_b200.parallel.symm import PHASE_PARTIAL
+
+    full = _full_model()
+    xs = [(_data() + i).to(torch.bfloat16) for i in range(4)]
+    mesh = build_mesh("cpu", (1, 2), ("data", "model"))
+    _, want = _run_fused(_sharded_copy(full, mesh), xs, 8)  # gloo all-gather / all-reduce between the shards
+    late = {"delay_flag": (PHASE_PARTIAL, 0.2)} if dist.get_rank() == 1 else None
+    comm = HostPeerComm(mesh_group(mesh, "model"), xs[0].shape[0], 8, 32, timeout_s=20.0, faults=late)
+    tp = _sharded_copy(full, mesh)
+    eng, got = _run_fused_comm(tp, xs, 8, comm)
+    assert comm.epoch == len(xs)
+    # each rank reports the loss of the rows it owns: the mean over ranks is the batch loss
+    dist.all_reduce(got)
+    assert torch.allclose(got / 2, want, rtol=1e-4), (got / 2, want)
+    ref = _sharded_copy(full, mesh)
+    _run_fused(ref, xs, 8)
+    assert torch.allclose(tp.W_D.data, ref.W_D.data, atol=1e-5) and torch.allclose(tp.W_E.data, ref.W_E.data, atol=1e-5)
+    assert torch.allclose(tp.b_D.data, ref.b_D.data, atol=1e-5)
+
+
+@distributed_test(nproc_per_node=2, backend="gloo")
+def test_peer_memory_protocol_reports_a_flag_that_never_arrives():
+    """Rank 1 never publishes its partial-rows flag: rank 0's bounded wait runs out and its step raises
+    ``CollectiveTimeout`` naming the phase and the silent rank; rank 1, whose own sources all arrived, finishes."""
+    from language_model_saes_b200.ops.sae_kernels import CollectiveTimeout
+    from language_model_saes_b200.parallel.host_transport import HostPeerComm
+    from language_model_saes_b200.parallel.mesh import mesh_group
+    from language_model_saes_b200.parallel.symm import PHASE_PARTIAL
+
+    full = _full_model()
+    x = _data().to(torch.bfloat16)
+    mesh = build_mesh("cpu", (1, 2), ("data", "model"))
+    rank = dist.get_rank()
+    comm = HostPeerComm(mesh_group(mesh, "model"), x.shape[0], 8, 32, timeout_s=1.0,
+                        faults={"drop_flag": PHASE_PARTIAL} if rank == 1 else None)  # fmt: skip
+    eng = FusedTopKSAEStep(_sharded_copy(full, mesh), comm=comm)
+    if rank == 0:
+        with pytest.raises(CollectiveTimeout, match=r"phase 1 .*rank\(s\) \[1\]") as info:
+            eng.step(x, x, 8, 1e-2)
+        assert info.value.code == 5 and info.value.sources == [1]
+    else:
+        assert torch.isfinite(eng.step(x, x, 8, 1e-2))
+
+
 @distributed_test(nproc_per_node=2, backend="gloo")
 def test_heartbeat_reports_a_rank_that_leaves_and_one_that_goes_silent():
     import time
