@@ -144,3 +144,26 @@ def test_circuit_job_roundtrip(server):
     assert http.get("/admin/circuits").json()["circuits"][0]["group"] == "g"
     assert http.delete(f"/circuits/{cid}").status_code == 200
     assert http.get(f"/circuits/{cid}").status_code == 404
+
+
+def test_ui_pages_are_served_and_call_existing_routes(server):
+    """The browser pages are static files next to the server; every API path they name is a route of the app."""
+    import re
+
+    http, _, names = server
+    page, script = http.get("/ui/index.html"), http.get("/ui/pages.js")
+    assert page.status_code == 200 and 'src="pages.js"' in page.text and script.status_code == 200
+    routes = {(m, r.path) for r in http.app.routes for m in getattr(r, "methods", ())}
+    as_route = lambda p: re.sub(r"\$\{[^}]*\}", "{}", p.split("?")[0])  # noqa: E731
+    known = {(m, re.sub(r"\{[^}]*\}", "{}", p)) for m, p in routes}
+    called = set()
+    for text in (page.text, script.text):
+        for m in re.finditer(r"api\((`|\")(/[^`\"]*)\1(?:,\s*(?:jsonOpts\(\"(\w+)\"|\{\s*method:\s*(?:\"(\w+)\"|[^}]*\?\s*\"(\w+)\"\s*:\s*\"(\w+)\")))?", text):
+            methods = [g for g in m.groups()[2:] if g] or ["GET"]
+            called |= {(meth, as_route(m.group(2))) for meth in methods}
+    assert len(called) > 20
+    missing = sorted(c for c in called if c not in known)
+    assert not missing, missing
+    # the pages' data sources answer for the fixtures of this module
+    assert http.get("/admin/stats").json()["sae_count"] == len(names)
+    assert http.get(f"/dictionaries/{names[0]}/features", params={"start": 0, "end": 2, "sample_length": 1}).status_code == 200
