@@ -306,16 +306,19 @@ class HookedTransformer(HookedRootModule):
 
     # ---- caching helpers -----------------------------------------------------------------------
     def run_with_cache_until(self, *args, names_filter: NameFilter = None, until: str | None = None, **kwargs):
-        """Forward pass that caches the requested hooks and stops right after ``until`` has fired (by default the
-        last requested hook in module order): later layers are never executed."""
+        """Forward pass that caches the requested hooks and stops as soon as it can: right after ``until`` has fired
+        when that is given, otherwise once every requested hook has fired (hook points are registered in the order the
+        modules were defined, which is not the order they run in, so "the last one" is found by counting); later
+        layers are never executed."""
         names = self._match(names_filter)
-        order = list(self.hook_dict)
-        if until is None and names:
-            until = max(names, key=order.index)
         cache: dict[str, torch.Tensor] = {}
+        pending = set(names)
 
         def save(t, hook):
             cache[hook.name] = t.detach()
+            pending.discard(hook.name)
+            if until is None and not pending:
+                raise StopAtHook
 
         def stop(t, hook):
             raise StopAtHook

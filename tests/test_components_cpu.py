@@ -1,0 +1,142 @@
+"""Behaviour specs of the components around the models: database client, hooked-transformer cache helpers and module
+mounting, evaluator, initializer, local checkpoint loading (single process and sharded), and sharded state-dict loading
+of every dictionary family. Same cases as the reference project's tests/unit/{test_database, test_tl_addons,
+test_evaluator, test_initializer, test_from_local}.py and tests/distributed/{test_load_state_dict, test_utils}.py, on
+this package's embedded store, own transformer and gloo ranks."""
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from language_model_saes_b200.backend.hooked_transformer import HookedTransformer, HookedTransformerConfig
+from language_model_saes_b200.database import MongoClient, MongoDBConfig, SAERecord
+from language_model_saes_b200.evaluator import EvalConfig, Evaluator
+from language_model_saes_b200.hooks import HookPoint
+from language_model_saes_b200.initializer import Initializer, InitializerConfig
+from language_model_saes_b200.models.clt import CLTConfig, CrossLayerTranscoder
+from language_model_saes_b200.models.crosscoder import Crosscoder, CrosscoderConfig
+from language_model_saes_b200.models.lorsa import LorsaConfig, LowRankSparseAttention
+from language_model_saes_b200.models.sae import SAEConfig, SparseAutoEncoder
+from language_model_saes_b200.models.sparse_dictionary import SparseDictionary
+from language_model_saes_b200.parallel.mesh import build_mesh, execute_and_broadcast
+from language_model_saes_b200.testing import distributed_test
+
+
+# ---- database (embedded directory store behind the MongoClient interface) ---------------------------------------------
+@pytest.fixture
+def db(tmp_path):
+    return MongoClient(MongoDBConfig(mongo_uri=f"file://{tmp_path / 'db'}", mongo_db="t"))
+
+
+def _cfg(d_model=8, expansion=2):
+    return SAEConfig(hook_point_in="h", hook_point_out="h", d_model=d_model, expansion_factor=expansion)
+
+
+def test_database_saes_analyses_and_features(db):
+    db.create_sae("sae1", "series1", "/p/1", _cfg())
+    db.create_sae("sae2", "series1", "/p/2", _cfg())
+    db.create_sae("sae3", "series2", "/p/3", _cfg(expansion=4))
+    got = db.get_sae("sae3", "series2")
+    assert isinstance(got, SAERecord) and (got.name, got.series, got.path) == ("sae3", "series2", "/p/3") and got.cfg.d_sae == 32
+    assert set(db.list_saes()) == {"sae1", "sae2", "sae3"} and set(db.list_saes("series1")) == {"sae1", "sae2"}
+    assert db.get_sae("nonexistent", "series1") is None and db.get_sae_path("sae1", "series1") == "/p/1"
+    # creating a dictionary creates one feature record per latent
+    f0 = db.get_feature("sae1", "series1", 0)
+    assert f0 is not None and (f0.sae_name, f0.sae_series, f0.index) == ("sae1", "series1", 0)
+    assert len(db.list_features("sae1", "series1", indices=range(4))) == 4 and db.get_feature("sae1", "series1", 16) is None
+    db.create_analysis("probe", "sae1", "series1")
+    assert db.list_analyses("sae1", "series1") == ["probe"] and db.list_saes("series1", has_analyses=True) == ["sae1"]
+    rec = {"act_times": 3, "n_analyzed_tokens": 10, "max_feature_acts": 1.5, "samplings": []}
+    db.add_feature_analysis("default", "sae1", "series1", [rec, {**rec, "act_times": 0, "max_feature_acts": 0.0}], start_idx=2)
+    assert db.get_feature("sae1", "series1", 2).analyses[0].act_times == 3
+    assert db.get_alive_feature_count("sae1", "series1") == 1 and db.get_max_feature_acts("sae1", "series1")[2] == 1.5
+    db.update_feature("sae1", 2, {"interpretation": {"text": "a probe"}}, "series1")
+    assert db.get_feature("sae1", "series1", 2).interpretation["text"] == "a probe"
+    db.remove_sae("sae1", "series1")
+    assert db.get_sae("sae1", "series1") is None and db.list_saes("series1") == ["sae2"] and db.get_feature("sae1", "series1", 0) is None
+
+
+def test_database_bookmarks_sets_and_circuits(db):
+    from language_model_saes_b200.database import CircuitConfig, CircuitStatus, CircuitTextInput
+
+    db.create_sae("a", "s", "/a", _cfg())
+    assert db.add_bookmark("a", "s", 1, tags=["x"], notes="n") and not db.add_bookmark("a", "s", 1)  # a second time: already there
+    assert db.is_bookmarked("a", "s", 1) and db.get_bookmark("a", "s", 1).tags == ["x"] and db.get_bookmark_count("a", "s") == 1
+    assert db.update_bookmark("a", "s", 1, notes="m") and db.list_bookmarks("a", "s")[0].notes == "m"
+    assert db.remove_bookmark("a", "s", 1) and not db.is_bookmarked("a", "s", 1)
+    db.add_sae_set("all", "s", ["a"])
+    assert db.get_sae_set("all").sae_names == ["a"] and [x.name for x in db.list_sae_sets()] == ["all"]
+    cid = db.create_circuit("all", "s", "a prompt", CircuitTextInput(text="a prompt"), CircuitConfig(), name="c", group=None)
+    assert db.get_circuit(cid).status == CircuitStatus.PENDING and db.get_circuit_status(cid)["progress"] in (None, 0, 0.0)
+    db.update_circuit_progress(cid, 0.5, "attributing")
+    db.update_circuit_status(cid, CircuitStatus.FAILED, error_message="boom")
+    st = db.get_circuit_status(cid)
+    assert st["progress"] == 0.5 and st["progress_phase"] == "attributing" and st["error_message"] == "boom"
+    assert db.update_circuits_group([cid], "g") == 1 and db.list_circuits("s", group="g")[0].id == cid
+    assert db.delete_circuit(cid) and db.get_circuit(cid) is None
+
+
+# ---- hooked transformer: partial forward with a cache, graph-attached cache, mounting extra hooked modules ------------
+def _tiny_transformer():
+    torch.manual_seed(0)
+    return HookedTransformer(HookedTransformerConfig(n_layers=3, d_model=16, n_heads=2, d_vocab=50, n_ctx=32))
+
+
+class _Probe(nn.Module):
+    """A stand-in for a dictionary: one hook point that sees whatever is passed through."""
+
+    def __init__(self):
+        super().__init__()
+        self.hook_seen = HookPoint()
+
+    def forward(self, x):
+        return self.hook_seen(x)
+
+
+def test_run_with_cache_until_matches_run_with_cache_and_skips_later_layers():
+    m, toks = _tiny_transformer(), torch.randint(0, 50, (2, 8))
+    names = ["blocks.0.hook_resid_pre", "blocks.0.attn.hook_q", "blocks.1.hook_mlp_out"]  # not in module-definition order
+    _, full = m.run_with_cache(toks, names_filter=names)
+    ran = []
+    m.add_hook("blocks.2.hook_resid_pre", lambda t, hook: ran.append(hook.name))
+    out, part = m.run_with_cache_until(toks, names_filter=names)
+    m.reset_hooks()
+    assert out is None and ran == []  # stopped before the last block ran
+    assert set(part) == set(names) and all(torch.equal(part[n], full[n]) for n in names)
+    _, early = m.run_with_cache_until(toks, names_filter=names[:2])  # the later-defined hook of the two runs first
+    assert set(early) == set(names[:2])
+    logits, explicit = m.run_with_cache_until(toks, names_filter=names[:1], until="blocks.1.hook_resid_post")
+    assert logits is None and set(explicit) == {names[0]}
+
+
+def test_run_with_ref_cache_keeps_the_graph():
+    m, toks = _tiny_transformer(), torch.randint(0, 50, (2, 8))
+    names = ["blocks.0.hook_resid_post", "blocks.1.hook_resid_post"]
+    _, detached = m.run_with_cache(toks, names_filter=names)
+    logits, ref = m.run_with_ref_cache(toks, names_filter=names, retain_grad=True)
+    assert all(torch.equal(ref[n], detached[n]) for n in names)
+    assert all(ref[n].requires_grad and ref[n].grad_fn is not None for n in names) and not detached[names[0]].requires_grad
+    logits.sum().backward()
+    assert ref[names[1]].grad is not None and float(ref[names[1]].grad.abs().sum()) > 0
+
+
+def test_mount_hooked_modules_attaches_and_always_detaches():
+    m, toks = _tiny_transformer(), torch.randint(0, 50, (2, 8))
+    before = set(m.hook_dict)
+    want = m(toks)
+    a, b = _Probe(), _Probe()
+    with m.mount_hooked_modules([("blocks.0.hook_mlp_out", "sae", a), ("blocks.1.hook_attn_out", "lorsa", b)]):
+        assert m.mod_dict["blocks.0.hook_mlp_out.sae"] is a and "blocks.1.hook_attn_out.lorsa.hook_seen" in m.hook_dict
+        # a hook on the mounted child fires when the parent hook's user calls the child during the forward pass
+        seen = []
+        m.add_hook("blocks.0.hook_mlp_out", lambda t, hook: a(t))
+        m.add_hook("blocks.0.hook_mlp_out.sae.hook_seen", lambda t, hook: seen.append(t.shape))
+        assert torch.equal(m(toks), want) and seen == [(2, 8, 16)]
+        m.reset_hooks()
+    assert set(m.hook_dict) == before and not hasattr(m.blocks[0].hook_mlp_out, "sae")
+    with pytest.raises(RuntimeError, match="inside"):
+        with m.mount_hooked_modules([("blocks.0.hook_mlp_out", "sae", a)]):
+            raise RuntimeError("inside")
+    assert set(m.hook_dict) == before  # removed although the block raised
+    assert torch.equal(m(toks), want)
