@@ -140,3 +140,144 @@ def test_mount_hooked_modules_attaches_and_always_detaches():
             raise RuntimeError("inside")
     assert set(m.hook_dict) == before  # removed although the block raised
     assert torch.equal(m(toks), want)
+
+
+# ---- evaluator and initializer ------------------------------------------------------------------------------------
+def _stream(n, batch=64, d=8, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    basis = torch.randn(4, d, generator=g)
+    for _ in range(n):
+        x = torch.randn(batch, 4, generator=g) @ basis
+        yield {"h": x, "tokens": torch.ones(batch, dtype=torch.long), "mask": torch.ones(batch, dtype=torch.bool)}
+
+
+def test_evaluator_reports_the_standard_metrics_and_honours_the_token_budget():
+    torch.manual_seed(0)
+    sae = SparseAutoEncoder(SAEConfig(hook_point_in="h", hook_point_out="h", d_model=8, expansion_factor=4, act_fn="topk", top_k=4))
+    sae.init_parameters(encoder_uniform_bound=0.5, decoder_uniform_bound=0.5)
+    sae.set_dataset_average_activation_norm({"h": 8**0.5})
+    seen = []
+
+    def counted():
+        for b in _stream(10):
+            seen.append(b["tokens"].numel())
+            yield b
+
+    logged = []
+
+    class Log:
+        def log(self, d, **kw):
+            logged.append(d)
+
+    out = Evaluator(EvalConfig(total_eval_tokens=150)).evaluate(sae, counted(), wandb_logger=Log())
+    assert sum(seen) == 192  # three batches of 64: the stream is left as soon as the budget is reached
+    for key in ("metrics/l0", "metrics/explained_variance", "metrics/l2_norm_error"):
+        assert key in out and isinstance(out[key], float)
+    assert out["metrics/l0"] == pytest.approx(4.0) and out["metrics/explained_variance"] <= 1.0
+    assert logged == [out]
+
+
+def test_initializer_ties_the_encoder_and_searches_the_norm():
+    cfg = SAEConfig(hook_point_in="h", hook_point_out="h", d_model=8, expansion_factor=4, act_fn="relu", norm_activation="dataset-wise")
+    init = Initializer(InitializerConfig(grid_search_init_norm=True, init_encoder_with_decoder_transpose=True,
+                                         init_encoder_with_decoder_transpose_factor=1.0))  # fmt: skip
+    torch.manual_seed(0)
+    sae = init.initialize_sae_from_config(cfg, activation_stream=_stream(4), activation_norm={"h": 8**0.5})
+    assert isinstance(sae, SparseAutoEncoder) and sae.dataset_average_activation_norm == {"h": 8**0.5}
+    # after the search every decoder row has ONE common norm and the encoder is the decoder's transpose
+    norms = sae.W_D.detach().norm(dim=1)
+    assert torch.allclose(norms, norms[0].expand_as(norms), rtol=1e-4) and torch.allclose(sae.W_E.detach(), sae.W_D.detach().t())
+    # the norm it picked is no worse than its neighbours on the batch it searched with
+    batch = sae.normalize_activations(next(_stream(1)))
+
+    def mse(scale):
+        probe = SparseAutoEncoder(cfg)
+        probe.load_state_dict(sae.state_dict())
+        probe.set_dataset_average_activation_norm({"h": 8**0.5})
+        with torch.no_grad():
+            probe.W_D.mul_(scale)
+            probe.W_E.copy_(probe.W_D.t())
+        return float(probe.compute_loss(batch)["l_rec"].float().mean())
+
+    assert mse(1.0) <= mse(3.0) and mse(1.0) <= mse(0.3)
+    # without the search the uniform bounds of the config are used as they are
+    plain = Initializer(InitializerConfig(encoder_uniform_bound=0.25, decoder_uniform_bound=0.5, init_encoder_with_decoder_transpose=False))
+    sae2 = plain.initialize_sae_from_config(cfg.model_copy(update={"norm_activation": "token-wise"}), activation_stream=_stream(1))
+    assert float(sae2.W_D.abs().max()) <= 0.5 and float(sae2.W_E.abs().max()) <= 0.25 and float(sae2.b_E.abs().max()) == 0.0
+
+
+# ---- local checkpoints and sharded loading ---------------------------------------------------------------------------
+def _family_configs():
+    return {
+        "sae": SAEConfig(hook_point_in="h", hook_point_out="h", d_model=8, expansion_factor=4, act_fn="topk", top_k=4),
+        "crosscoder": CrosscoderConfig(hook_points=["a", "b"], d_model=8, expansion_factor=4, act_fn="topk", top_k=4),
+        "clt": CLTConfig(hook_points_in=["i0", "i1"], hook_points_out=["o0", "o1"], d_model=8, expansion_factor=4, act_fn="topk", top_k=4),
+        "lorsa": LorsaConfig(hook_point_in="x", hook_point_out="y", d_model=8, expansion_factor=4, n_qk_heads=4, d_qk_head=4,
+                             rotary_dim=4, n_ctx=16, act_fn="topk", top_k=4),  # fmt: skip
+    }
+
+
+def _saved(cfg, path, seed=0):
+    torch.manual_seed(seed)
+    m = SparseDictionary.from_config(cfg)
+    m.init_parameters(encoder_uniform_bound=0.5, decoder_uniform_bound=0.5)
+    m.set_dataset_average_activation_norm({h: 2.0 + i for i, h in enumerate(cfg.associated_hook_points)})
+    m.save_pretrained(path)
+    m.cfg.save_hyperparameters(path)
+    return m
+
+
+@pytest.mark.parametrize("family", ["sae", "crosscoder", "clt", "lorsa"])
+def test_from_local_restores_config_and_weights(tmp_path, family):
+    cfg = _family_configs()[family]
+    src = _saved(cfg, tmp_path / family)
+    got = SparseDictionary.from_pretrained(str(tmp_path / family))
+    assert type(got) is type(src) and got.cfg.d_sae == src.cfg.d_sae
+    want = src.full_state_dict()
+    have = got.full_state_dict()
+    assert set(have) == set(want) and all(torch.equal(have[k], want[k]) for k in want)
+
+
+@distributed_test(nproc_per_node=2, backend="gloo")
+def test_sharded_loading_of_every_family_matches_the_full_state(tmp_path_factory=None):
+    """Every rank loads its shard (from the full state dict and from a local checkpoint); gathering gives the full
+    tensors back, for SAE, crosscoder, cross-layer transcoder and Lorsa."""
+    import tempfile
+
+    mesh = build_mesh("cpu", (1, 2), ("data", "model"))
+    root = execute_and_broadcast(lambda: tempfile.mkdtemp(prefix="lmsae_fromlocal_"), mesh)
+    for family, cfg in _family_configs().items():
+        torch.manual_seed(0)
+        full = SparseDictionary.from_config(cfg)
+        full.init_parameters(encoder_uniform_bound=0.5, decoder_uniform_bound=0.5)
+        full.set_dataset_average_activation_norm({h: 2.0 + i for i, h in enumerate(cfg.associated_hook_points)})
+        want = full.full_state_dict()
+        if dist.get_rank() == 0:
+            full.save_pretrained(f"{root}/{family}")
+            full.cfg.save_hyperparameters(f"{root}/{family}")
+        dist.barrier()
+        sharded = SparseDictionary.from_config(cfg, device_mesh=mesh)
+        sharded.load_full_state_dict(want)
+        local = SparseDictionary.from_pretrained(f"{root}/{family}", device_mesh=mesh)
+        for m in (sharded, local):
+            have = m.full_state_dict()
+            assert set(have) == set(want), family
+            for k in want:
+                assert torch.equal(have[k], want[k]), (family, k)
+            # something really is sharded: the local parameter count is below the full one
+            assert sum(p.numel() for p in m.parameters()) < sum(p.numel() for p in full.parameters()), family
+
+
+@distributed_test(nproc_per_node=2, backend="gloo")
+def test_execute_and_broadcast_runs_once_and_shares_the_result():
+    mesh = build_mesh("cpu", (2,), ("data",))
+    calls = []
+
+    def fn():
+        calls.append(dist.get_rank())
+        return {"rank": dist.get_rank(), "value": [1, 2, 3]}
+
+    out = execute_and_broadcast(fn, mesh)
+    assert out == {"rank": 0, "value": [1, 2, 3]}  # rank 0's result everywhere
+    assert calls == ([0] if dist.get_rank() == 0 else [])
+    assert execute_and_broadcast(lambda: 7, None) == 7  # no mesh: just a call
