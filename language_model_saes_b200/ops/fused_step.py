@@ -139,8 +139,7 @@ class FusedTopKSAEStep:
             checks += [
                 (trainer_cfg.sparsity_loss_type is None, "sparsity loss"),
                 (not trainer_cfg.lp_coefficient, "lp loss"),
-                (not trainer_cfg.auxk_coefficient or (mesh_dim_size(sae.device_mesh, "model") == 1 and mesh_dim_size(sae.device_mesh, "data") == 1),
-                 "aux-k loss under a device mesh"),
+                (not trainer_cfg.auxk_coefficient or mesh_dim_size(sae.device_mesh, "data") == 1, "aux-k loss with data parallelism"),
                 (not trainer_cfg.auxk_coefficient or cfg.act_fn == "topk", "aux-k loss with a batch-level top-k"),
                 (trainer_cfg.optimizer_class == "adam", "optimizer is not adam"),
                 (trainer_cfg.amp_dtype == torch.bfloat16, "amp dtype is not bf16"),
@@ -424,16 +423,18 @@ class FusedTopKSAEStep:
         return torch.where(norm > max_norm, max_norm / (norm + 1e-6), torch.ones_like(norm)).reshape(1)
 
     def _step_auxk(self, x, label, k, lr, row_weight, n_tokens_global, aux: "AuxK", clip_grad_norm: float = 0.0) -> torch.Tensor:
-        """The step with the Aux-K loss (single GPU): ``l = |e|^2 + alpha |e - e_aux|^2`` where ``e_aux`` decodes the
+        """The step with the Aux-K loss (one GPU or feature shards): ``l = |e|^2 + alpha |e - e_aux|^2`` where ``e_aux`` decodes the
         ``k_aux`` largest gated pre-activations among DEAD features (models/sparse_dictionary.py:941-991 and
         trainer.py:428-454 of the reference project). The dead features are gathered into a compact dictionary
         first, so the second encoder pass costs ``n_dead / F`` of the main one instead of a full pass."""
-        assert self.tp == 1 and self.dp == 1, "the fused Aux-K step runs on one GPU (use the generic path under a mesh)"
+        assert self.dp == 1, "the fused Aux-K step is not data parallel (use the generic path for that mesh)"
         self.join()
         B = x.shape[0]
         n_global = n_tokens_global if n_tokens_global is not None else B
         grad_scale = 2.0 / n_global
         gate = self.dec_norm if self.use_gate else None
+        if self.comm is not None and B == self.comm.B and k <= self.comm.k_max:
+            self.comm.next_epoch()  # the candidate exchange of encode() is the only peer-memory phase of this step
         idx, act = self.encode(x, k)
         if self.groups is None or self.groups.entries.numel() < B * (k + aux.k_aux):
             self.groups = K.FeatureGroups(self.F, B * (k + aux.k_aux), x.device)
@@ -444,12 +445,18 @@ class FusedTopKSAEStep:
         is_dead = aux.update(self.main_counts, n_valid)
         dead_idx = is_dead.nonzero().squeeze(-1)
         n_dead = int(dead_idx.numel())  # host sync, as in the reference (min(k_aux, n_dead) is a Python int there)
-        k_aux = min(aux.k_aux, n_dead)
+        n_dead_all = n_dead
+        if self.tp > 1:  # the auxiliary top-k runs over the dead features of ALL shards
+            t = torch.tensor([n_dead], device=x.device)
+            dist.all_reduce(t, group=self.tp_group)
+            n_dead_all = int(t)
+        k_aux = min(aux.k_aux, n_dead_all)
         self.loss_sum.zero_()
         self.aux_sum.zero_()
         xhat = K.sparse_decode(idx, act, self.WD_bf16, None, torch.float32)
         if k_aux > 0:
-            pad = (-n_dead) % 8
+            # compact dictionary of this shard's dead features, padded to a multiple of 8 rows and to at least k_aux
+            pad = -(-max(n_dead, k_aux) // 8) * 8 - n_dead
             rows = torch.cat([dead_idx, dead_idx.new_zeros(pad)]) if pad else dead_idx
             w_dead = self.WE_bf16[rows]
             b_dead = self.bE[rows]
@@ -457,12 +464,18 @@ class FusedTopKSAEStep:
             if pad:
                 g_dead[n_dead:] = 0.0  # padding rows can never be selected: their gated value is 0
             idx_c, act_aux = K.encoder_topk(x, w_dead, b_dead, g_dead, k_aux)
+            if self.tp > 1:
+                idx_c, act_aux = self._merge_shard_codes(idx_c, act_aux, g_dead, k_aux)
             idx_aux = torch.where(idx_c >= 0, rows[idx_c.clamp_min(0).long()].to(torch.int32), idx_c)
             aux_rec = K.sparse_decode(idx_aux, act_aux, self.WD_bf16, None, torch.float32)
         else:
             idx_aux = torch.full((B, 0), -1, dtype=torch.int32, device=x.device)
             act_aux = torch.zeros(B, 0, device=x.device)
             aux_rec = torch.zeros_like(xhat)
+        if self.tp > 1:  # both reconstructions are sums over the shards' features
+            both = torch.stack([xhat, aux_rec])
+            dist.all_reduce(both, group=self.tp_group)
+            xhat, aux_rec = both[0], both[1]
         alpha = aux.coefficient if k_aux > 0 else 0.0  # no dead feature: the auxiliary term is absent, not |e|^2
         g_main, g_aux = K.auxk_loss_grad(xhat, aux_rec, label, self.bD, row_weight, grad_scale, alpha, self.loss_sum, self.aux_sum)
         dact = K.sparse_dact(idx, self.WD_bf16, g_main)
@@ -490,6 +503,20 @@ class FusedTopKSAEStep:
         n_local = B if row_weight is None else row_weight.sum()
         self.last_aux_loss = (self.aux_sum / n_local).squeeze(0)
         return ((self.loss_sum + self.aux_sum) / n_local).squeeze(0)
+
+    def _merge_shard_codes(self, idx_l: torch.Tensor, act_l: torch.Tensor, gate_l: torch.Tensor | None, k: int):
+        """Every shard holds its own top-``k`` codes ``(idx_l, act_l)`` of each row; keep those that are among the
+        ``k`` largest gated values of the row over all shards (all-gather of the lists, merge, own slots only)."""
+        B = idx_l.shape[0]
+        g_l = act_l * gate_l[idx_l.clamp_min(0).long()] if gate_l is not None else act_l
+        all_g = torch.empty(self.tp * B, k, dtype=torch.float32, device=idx_l.device)
+        all_i = torch.empty(self.tp * B, k, dtype=torch.int32, device=idx_l.device)
+        dist.all_gather_into_tensor(all_g, g_l.float().contiguous(), group=self.tp_group)
+        dist.all_gather_into_tensor(all_i, idx_l.contiguous(), group=self.tp_group)
+        all_g = all_g.view(self.tp, B, k).permute(1, 0, 2).reshape(B, self.tp * k).contiguous()
+        all_i = all_i.view(self.tp, B, k).permute(1, 0, 2).reshape(B, self.tp * k).contiguous()
+        merge = K.topk_merge if k <= 64 else K.ref_topk_merge  # the merge kernel's lists hold at most 64 codes per row
+        return merge(all_g, all_i, k, gate_l, own=(self.tp_rank * k, (self.tp_rank + 1) * k))
 
     def _gather_rows(self, *tensors: torch.Tensor) -> list[torch.Tensor]:
         out = []

@@ -206,6 +206,26 @@ def encoder_topk_candidates(
     return cand_val, cand_idx, C
 
 
+def ref_topk_merge(cand_val, cand_idx, k: int, gate, own: tuple[int, int] | None = None, emit_gated: bool = False):
+    """Plain-torch statement of ``topk_merge`` (any device): the ``k`` largest positive candidates of every row; only
+    winners whose candidate slot lies in ``own`` are kept (the rest become -1 / 0), values divided by ``gate[idx]``
+    unless ``emit_gated``."""
+    M, C = cand_val.shape
+    lo, hi = own if own is not None else (0, C)
+    score = torch.where(cand_idx >= 0, cand_val.float(), torch.full_like(cand_val, -1.0, dtype=torch.float32))
+    kk = min(k, C)
+    top, pos = torch.topk(score, kk, dim=-1)
+    keep = (top > 0) & (pos >= lo) & (pos < hi)
+    idx = torch.where(keep, torch.gather(cand_idx, 1, pos), torch.full_like(pos, -1, dtype=cand_idx.dtype))
+    val = torch.where(keep, top, torch.zeros_like(top))
+    if not emit_gated and gate is not None:
+        val = torch.where(keep, val / gate.float()[idx.clamp_min(0).long()], val)
+    if kk < k:
+        idx = torch.cat([idx, idx.new_full((M, k - kk), -1)], dim=1)
+        val = torch.cat([val, val.new_zeros(M, k - kk)], dim=1)
+    return idx.to(torch.int32), val
+
+
 def topk_merge(
     cand_val: torch.Tensor,
     cand_idx: torch.Tensor,
@@ -217,18 +237,7 @@ def topk_merge(
     M, C = cand_val.shape
     lo, hi = own if own is not None else (0, C)
     if not cand_val.is_cuda:
-        score = torch.where(cand_idx >= 0, cand_val.float(), torch.full_like(cand_val, -1.0, dtype=torch.float32))
-        kk = min(k, C)
-        top, pos = torch.topk(score, kk, dim=-1)
-        keep = (top > 0) & (pos >= lo) & (pos < hi)
-        idx = torch.where(keep, torch.gather(cand_idx, 1, pos), torch.full_like(pos, -1, dtype=cand_idx.dtype))
-        val = torch.where(keep, top, torch.zeros_like(top))
-        if not emit_gated and gate is not None:
-            val = torch.where(keep, val / gate.float()[idx.clamp_min(0).long()], val)
-        if kk < k:
-            idx = torch.cat([idx, idx.new_full((M, k - kk), -1)], dim=1)
-            val = torch.cat([val, val.new_zeros(M, k - kk)], dim=1)
-        return idx.to(torch.int32), val
+        return ref_topk_merge(cand_val, cand_idx, k, gate, own, emit_gated)
     out_idx = torch.empty(M, k, dtype=torch.int32, device=cand_val.device)
     out_val = torch.empty(M, k, dtype=torch.float32, device=cand_val.device)
     _ext().topk_merge(cand_val, cand_idx, M, C, k, gate, lo, hi, emit_gated, out_idx, out_val)

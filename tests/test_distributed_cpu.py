@@ -199,6 +199,39 @@ def test_fused_batchtopk_step_feature_and_data_parallel_match_single():
     assert torch.equal(both[0], both[1])  # replicas stay identical
 
 
+@distributed_test(nproc_per_node=2, backend="gloo")
+def test_fused_auxk_step_feature_parallel_matches_single():
+    """Aux-K on the fused path with feature shards: the dead features' top-k runs over all shards, both reconstructions
+    are summed over shards; losses, auxiliary losses and weights follow the single-process run. With ``dead_threshold``
+    below one batch every feature that did not fire in the step is dead, on whichever shard it lives."""
+    from language_model_saes_b200.ops.fused_step import AuxK
+
+    full = _full_model()
+    xs = [(_data() + i).to(torch.bfloat16) for i in range(3)]
+
+    def run(sae):
+        eng = FusedTopKSAEStep(sae)
+        aux = AuxK(eng.F, k_aux=12, coefficient=1 / 8, dead_threshold=32, device="cpu")
+        out = []
+        for x in xs:
+            loss = eng.step(x, x, 8, 1e-2, aux=aux)
+            out.append(torch.stack([loss, eng.last_aux_loss]))
+        return eng, aux, torch.stack(out)
+
+    ref = SparseAutoEncoder(full.cfg.model_copy())
+    ref.load_full_state_dict(full.full_state_dict())
+    _, aux1, want = run(ref)
+    assert float(want[:, 1].min()) > 0  # the auxiliary term is active in every step
+    mesh = build_mesh("cpu", (1, 2), ("data", "model"))
+    tp = _sharded_copy(full, mesh)
+    eng, aux2, got = run(tp)
+    assert torch.allclose(got, want, rtol=1e-4), (got, want)
+    assert torch.allclose(DimMap({"model": 0}).gather(tp.W_D.data, mesh), ref.W_D.data, atol=1e-5)
+    assert torch.allclose(DimMap({"model": 1}).gather(tp.W_E.data, mesh), ref.W_E.data, atol=1e-5)
+    F_l, r = eng.F, dist.get_rank()
+    assert torch.equal(aux2.tokens_since_last_activation, aux1.tokens_since_last_activation[r * F_l : (r + 1) * F_l])
+
+
 def _run_fused_comm(sae, xs, k, comm, lr=1e-2):
     eng = FusedTopKSAEStep(sae, comm=comm)
     return eng, torch.stack([eng.step(x, x, k, lr) for x in xs])
