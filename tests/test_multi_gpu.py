@@ -78,6 +78,50 @@ def test_peer_memory_step_matches_nccl_and_single_gpu():
         assert torch.allclose(W, single.W_D.data, atol=2e-4), float((W - single.W_D.data).abs().max())
 
 
+@needs2
+@distributed_test(nproc_per_node=2, backend="nccl")
+def test_auxk_step_with_feature_shards_matches_single_gpu():
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    from language_model_saes_b200.models.sae import SparseAutoEncoder
+    from language_model_saes_b200.ops import sae_kernels as K
+    from language_model_saes_b200.ops.fused_step import AuxK, FusedTopKSAEStep
+    from language_model_saes_b200.parallel.mesh import DimMap, build_mesh
+    from language_model_saes_b200.parallel.symm import SymmComm
+
+    rank = dist.get_rank()
+    dev = torch.device("cuda", rank)
+    mesh = build_mesh("cuda", (1, 2), ("data", "model"))
+    full = _full_model(dev)
+    B, d, k, lr = 512, 256, 16, 1e-3
+    g = torch.Generator(device=dev).manual_seed(5)
+    xs = [(torch.randn(B, d, device=dev, generator=g) * 1.0).to(torch.bfloat16) for _ in range(3)]
+    for x in xs:
+        dist.broadcast(x, src=0)
+
+    def run(model, comm, k_aux):
+        eng = FusedTopKSAEStep(model, comm=comm)
+        aux = AuxK(eng.F, k_aux=k_aux, coefficient=1 / 32, dead_threshold=B // 2, device=dev)  # dead = did not fire in the step
+        out = []
+        for x in xs:
+            loss = eng.step(x, x, k, lr, aux=aux)
+            out.append(torch.stack([loss, eng.last_aux_loss]))
+        return torch.stack(out)
+
+    for k_aux in (32, 96):  # 96: lists longer than the merge kernel's, merged with the plain-torch statement
+        single = SparseAutoEncoder(full.cfg.model_copy())
+        single.load_full_state_dict(full.full_state_dict())
+        want = run(single, None, k_aux)
+        assert float(want[:, 1].min()) > 0
+        for use_comm in (False, True):
+            m = SparseAutoEncoder(full.cfg.model_copy(), mesh)
+            m.load_full_state_dict(full.full_state_dict())
+            got = run(m, SymmComm(mesh.get_group("model"), dev, B, k, d) if use_comm else None, k_aux)
+            K.check_status(dev)
+            assert torch.allclose(got, want, rtol=3e-3), (k_aux, use_comm, got, want)
+            W = DimMap({"model": 0}).gather(m.W_D.data, mesh)
+            assert torch.allclose(W, single.W_D.data, atol=2e-4), float((W - single.W_D.data).abs().max())
+
+
 def test_peer_flag_wait_times_out_with_status_code():
     from language_model_saes_b200.ops import sae_kernels as K
 
