@@ -13,6 +13,7 @@ read back to the host each step.
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import statistics
@@ -45,7 +46,7 @@ class ClockSampler:
 
     REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
 
-    def __init__(self, gpu_index: int, period_s: float = 0.005):
+    def __init__(self, gpu_index: int, period_s: float = 0.02):
         self.gpu = gpu_index
         self.period = period_s
         self.samples: list[tuple[float, float, int]] = []  # (sm MHz, watts, reason bits)
@@ -84,6 +85,11 @@ class ClockSampler:
 
             self._thread = threading.Thread(target=poll, daemon=True)
             self._thread.start()
+            # the first queries of a process are slow (the library sets itself up) and the management library and kernel
+            # launches share locks in the driver: let them happen here, before the timed region opens
+            t0 = time.perf_counter()
+            while len(self.samples) < 2 and time.perf_counter() - t0 < 2.0:
+                time.sleep(0.005)
         except Exception:  # noqa: BLE001 - no NVML bindings: nvidia-smi
             self._start_smi()
 
@@ -202,9 +208,11 @@ def run_ours(args):
         engine.step(pool[i % POOL], pool[i % POOL], TOP_K, LR)
     engine.join()  # the update of a step runs on its own stream: fold it back before timing starts
     K.check_status(dev)
-    barrier()
     sampler = ClockSampler(local)
     sampler.start()
+    gc.collect()
+    gc.disable()  # no collector pauses on any rank inside the timed region (a stalled rank stalls its peers' flag waits)
+    barrier()
     launches0 = K.kernel_launch_count()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     # one more event after every step (a marker in the stream, no synchronisation): the spread of the per-step times
@@ -219,6 +227,7 @@ def run_ours(args):
     end.record()
     host_issue_ms = (time.perf_counter() - t_issue0) * 1e3 / Ksteps  # host time to enqueue one step (no synchronisation)
     barrier()
+    gc.enable()
     launches = K.kernel_launch_count() - launches0
     clocks = sampler.stop()
     ms = start.elapsed_time(end)
@@ -272,7 +281,7 @@ def run_ours(args):
     if world > 1:
         dist.all_reduce(per_step, op=dist.ReduceOp.MAX)
     step_ms = {"min": round(float(per_step.min()), 4), "median": round(float(per_step.median()), 4),
-               "max": round(float(per_step.max()), 4)}  # fmt: skip
+               "max": round(float(per_step.max()), 4), "slowest_step": int(per_step.argmax())}  # fmt: skip
     if rank == 0:
         value = Ksteps * BATCH / (ms / 1e3)
         emit({
