@@ -121,9 +121,13 @@ def test_auxk_step_with_feature_shards_matches_single_gpu():
             W = DimMap({"model": 0}).gather(m.W_D.data, mesh)
             off = ((W - single.W_D.data).abs() > 2e-4).any(dim=1).float().mean()
             # k_aux > 64 selects on pre-activations stored in bf16, where equal values are common: which of several
-            # equal candidates gets the last place depends on how the lists were split, and an Adam step moves such a
-            # row by +-lr either way. The losses above agree; only a few rows may differ.
-            assert float(off) <= (0.0 if k_aux <= 64 else 0.02), (k_aux, use_comm, float(off))
+            # equal candidates gets the last places depends on how the lists were split. The losses above agree (equal
+            # values contribute equally), but Adam's first steps move every row that got any gradient by about lr, so
+            # rows whose tied features differ end up lr apart: bounded by the steps taken, not by a rounding tolerance.
+            if k_aux <= 64:
+                assert float(off) == 0.0, (k_aux, use_comm, float(off))
+            else:
+                assert float((W - single.W_D.data).abs().max()) <= 2.2 * lr * len(xs), (k_aux, use_comm)
 
 
 def test_peer_flag_wait_times_out_with_status_code():
