@@ -37,20 +37,45 @@ topk_merge_kernel(const float* __restrict__ cand_val, const int* __restrict__ ca
       out_val[(size_t)row * k + i] = 0.0f;
     }
     __syncwarp();
-    for (int i = own_lo + lane; i < own_hi; i += 32) {
-      const int id = sidx[i];
-      if (id < 0) continue;
-      const float v = sval[i];
-      int rank = 0;
-      for (int j = 0; j < C; ++j) {
-        const float u = sval[j];
-        rank += (u > v) || (u == v && j < i);
+    // Rank by counting: a candidate's place is the number of candidates that beat it (larger value, or equal value
+    // and earlier slot). Each lane ranks two of its candidates per sweep over the row, and when the row length allows
+    // it the sweep reads four values per shared-memory load: the loop is bound by those loads.
+    const bool vec4 = (C & 3) == 0;
+    for (int i0 = own_lo + lane; i0 < own_hi; i0 += 64) {
+      const int i1 = i0 + 32;
+      const bool has1 = i1 < own_hi;
+      const int id0 = sidx[i0], id1 = has1 ? sidx[i1] : -1;
+      if (id0 < 0 && id1 < 0) continue;
+      const float v0 = sval[i0], v1 = has1 ? sval[i1] : 0.0f;
+      int r0 = 0, r1 = 0;
+      int j = 0;
+      if (vec4) {
+        const float4* s4 = reinterpret_cast<const float4*>(sval);
+        for (; j < C; j += 4) {
+          const float4 u = s4[j >> 2];
+          r0 += (u.x > v0) || (u.x == v0 && j < i0);
+          r1 += (u.x > v1) || (u.x == v1 && j < i1);
+          r0 += (u.y > v0) || (u.y == v0 && j + 1 < i0);
+          r1 += (u.y > v1) || (u.y == v1 && j + 1 < i1);
+          r0 += (u.z > v0) || (u.z == v0 && j + 2 < i0);
+          r1 += (u.z > v1) || (u.z == v1 && j + 2 < i1);
+          r0 += (u.w > v0) || (u.w == v0 && j + 3 < i0);
+          r1 += (u.w > v1) || (u.w == v1 && j + 3 < i1);
+        }
+      } else {
+        for (; j < C; ++j) {
+          const float u = sval[j];
+          r0 += (u > v0) || (u == v0 && j < i0);
+          r1 += (u > v1) || (u == v1 && j < i1);
+        }
       }
-      if (rank < k) {
-        float o = v;
-        if (!emit_gated && gate != nullptr) o = v / gate[id];
-        out_idx[(size_t)row * k + rank] = id;
-        out_val[(size_t)row * k + rank] = o;
+      if (id0 >= 0 && r0 < k) {
+        out_idx[(size_t)row * k + r0] = id0;
+        out_val[(size_t)row * k + r0] = (!emit_gated && gate != nullptr) ? v0 / gate[id0] : v0;
+      }
+      if (id1 >= 0 && r1 < k) {
+        out_idx[(size_t)row * k + r1] = id1;
+        out_val[(size_t)row * k + r1] = (!emit_gated && gate != nullptr) ? v1 / gate[id1] : v1;
       }
     }
     __syncwarp();
