@@ -79,45 +79,22 @@ __device__ __forceinline__ void for_each_positive(const T* __restrict__ x, long 
   const long long chunk = (long long)THREADS * V;
   const long long chunks_per_row = (N + chunk - 1) / chunk;
   const bool vec_ok = (N % V == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0);
-  const long long total = A * chunks_per_row;
-  if (vec_ok) {
-    // four chunks per trip, all loads issued before the first value is used: one 16-byte load per thread in flight
-    // left the kernel waiting on memory latency (a third of the copy bandwidth), not on the histogram updates
-    constexpr int U = 4;
-    for (long long item = blockIdx.x; item < total; item += (long long)gridDim.x * U) {
-      uint32_t b[U][V];
-      bool ok[U];
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const long long it = item + (long long)u * gridDim.x;
-        ok[u] = false;
-        if (it < total) {
-          const long long a = it / chunks_per_row, ch = it - a * chunks_per_row;
-          const long long e = ch * chunk + (long long)threadIdx.x * V;
-          if (e < N) {
-            ok[u] = true;
-            Vec<T>::load(x + (a * S + s) * N + e, b[u]);
-          }
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (!ok[u]) continue;
-#pragma unroll
-        for (int i = 0; i < V; ++i)
-          if (b[u][i] != 0) visit(b[u][i]);
-      }
-    }
-    return;
-  }
-  for (long long item = blockIdx.x; item < total; item += gridDim.x) {
+  for (long long item = blockIdx.x; item < A * chunks_per_row; item += gridDim.x) {
     const long long a = item / chunks_per_row, ch = item - a * chunks_per_row;
     const T* row = x + (a * S + s) * N;
     const long long e = ch * chunk + (long long)threadIdx.x * V;
     if (e >= N) continue;
-    for (int i = 0; i < V && e + i < N; ++i) {
-      const uint32_t b = positive_bits<T>(row[e + i]);
-      if (b != 0) visit(b);
+    if (vec_ok) {
+      uint32_t b[V];
+      Vec<T>::load(row + e, b);
+#pragma unroll
+      for (int i = 0; i < V; ++i)
+        if (b[i] != 0) visit(b[i]);
+    } else {
+      for (int i = 0; i < V && e + i < N; ++i) {
+        const uint32_t b = positive_bits<T>(row[e + i]);
+        if (b != 0) visit(b);
+      }
     }
   }
 }
