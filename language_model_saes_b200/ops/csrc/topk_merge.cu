@@ -1,7 +1,7 @@
 // Exact top-k merge of per-range candidate lists.
 //
 // The encoder GEMM emits, for every row, C = (number of ranges) * KS candidates (gated value, column or
-// -1). This kernel ranks them (value descending, ties by position) and keeps the k best. Under feature
+// -1). This kernel keeps the k best (value descending, ties by position). Under feature
 // sharding it runs twice: once per rank on its own ranges (emit_gated = 1, output = k (g, local column)
 // pairs that are exchanged between the shards), and once on the gathered lists of all shards, where only
 // candidates in [own_lo, own_hi) -- this shard's segment -- are written out; positions won by other
@@ -15,68 +15,82 @@ namespace lmsae {
 
 constexpr int MERGE_WARPS = 4;
 
+// One warp per row. Positive floats order like their bit patterns, so the k-th largest candidate is found by a
+// descent over the 31 value bits (count(key >= t) per trial, one warp reduction each) instead of ranking every
+// candidate against every other one; candidates equal to the threshold get the remaining places in slot order. The
+// (at most k) winners are compacted into shared memory and ranked among themselves, which gives each its place in the
+// value-descending output. Work per row: 31 C + k^2 comparisons instead of C^2.
 __global__ void __launch_bounds__(MERGE_WARPS * 32)
 topk_merge_kernel(const float* __restrict__ cand_val, const int* __restrict__ cand_idx, int M, int C, int k,
                   const float* __restrict__ gate, int own_lo, int own_hi, int emit_gated,
                   int* __restrict__ out_idx, float* __restrict__ out_val) {
   extern __shared__ uint8_t smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  float* sval = reinterpret_cast<float*>(smem_raw) + (size_t)warp * C;
-  int* sidx = reinterpret_cast<int*>(smem_raw + (size_t)MERGE_WARPS * C * 4) + (size_t)warp * C;
+  const unsigned lt_mask = (1u << lane) - 1u;
+  // per warp: keys[C], ids[C], winner keys[k], winner slots[k]
+  uint32_t* skey = reinterpret_cast<uint32_t*>(smem_raw) + (size_t)warp * (2 * C + 2 * k);
+  int* sidx = reinterpret_cast<int*>(skey + C);
+  uint32_t* wkey = reinterpret_cast<uint32_t*>(sidx + C);
+  int* wslot = reinterpret_cast<int*>(wkey + k);
 
   for (int row = blockIdx.x * MERGE_WARPS + warp; row < M; row += gridDim.x * MERGE_WARPS) {
     const float* cv = cand_val + (size_t)row * C;
     const int* ci = cand_idx + (size_t)row * C;
     for (int i = lane; i < C; i += 32) {
       const int id = ci[i];
+      const float v = cv[i];
       sidx[i] = id;
-      sval[i] = (id >= 0) ? cv[i] : -1.0f;  // valid candidates are > 0
+      skey[i] = (id >= 0 && v > 0.0f) ? __float_as_uint(v) : 0u;  // only positive candidates compete
     }
     for (int i = lane; i < k; i += 32) {
       out_idx[(size_t)row * k + i] = -1;
       out_val[(size_t)row * k + i] = 0.0f;
     }
     __syncwarp();
-    // Rank by counting: a candidate's place is the number of candidates that beat it (larger value, or equal value
-    // and earlier slot). Each lane ranks two of its candidates per sweep over the row, and when the row length allows
-    // it the sweep reads four values per shared-memory load: the loop is bound by those loads.
-    const bool vec4 = (C & 3) == 0;
-    for (int i0 = own_lo + lane; i0 < own_hi; i0 += 64) {
-      const int i1 = i0 + 32;
-      const bool has1 = i1 < own_hi;
-      const int id0 = sidx[i0], id1 = has1 ? sidx[i1] : -1;
-      if (id0 < 0 && id1 < 0) continue;
-      const float v0 = sval[i0], v1 = has1 ? sval[i1] : 0.0f;
-      int r0 = 0, r1 = 0;
-      int j = 0;
-      if (vec4) {
-        const float4* s4 = reinterpret_cast<const float4*>(sval);
-        for (; j < C; j += 4) {
-          const float4 u = s4[j >> 2];
-          r0 += (u.x > v0) || (u.x == v0 && j < i0);
-          r1 += (u.x > v1) || (u.x == v1 && j < i1);
-          r0 += (u.y > v0) || (u.y == v0 && j + 1 < i0);
-          r1 += (u.y > v1) || (u.y == v1 && j + 1 < i1);
-          r0 += (u.z > v0) || (u.z == v0 && j + 2 < i0);
-          r1 += (u.z > v1) || (u.z == v1 && j + 2 < i1);
-          r0 += (u.w > v0) || (u.w == v0 && j + 3 < i0);
-          r1 += (u.w > v1) || (u.w == v1 && j + 3 < i1);
-        }
-      } else {
-        for (; j < C; ++j) {
-          const float u = sval[j];
-          r0 += (u > v0) || (u == v0 && j < i0);
-          r1 += (u > v1) || (u == v1 && j < i1);
-        }
+    // threshold: the largest t with count(key >= t) >= k (0 when fewer than k candidates are positive)
+    uint32_t t = 0;
+    for (int bit = 30; bit >= 0; --bit) {
+      const uint32_t trial = t | (1u << bit);
+      int c = 0;
+      for (int i = lane; i < C; i += 32) c += skey[i] >= trial;
+      if (__reduce_add_sync(0xffffffffu, c) >= k) t = trial;
+    }
+    int above = 0;
+    for (int i = lane; i < C; i += 32) above += skey[i] > t;
+    above = __reduce_add_sync(0xffffffffu, above);
+    const int ties_wanted = (t == 0u) ? 0 : k - above;  // t == 0: every positive candidate is in, nothing equals t
+    // compaction of the winners in slot order
+    int n_win = 0, ties_seen = 0;
+    for (int base = 0; base < C; base += 32) {
+      const int i = base + lane;
+      const uint32_t key = i < C ? skey[i] : 0u;
+      const bool eq = t != 0u && key == t;
+      const unsigned eq_ballot = __ballot_sync(0xffffffffu, eq);
+      const bool win = key > t || (eq && ties_seen + __popc(eq_ballot & lt_mask) < ties_wanted);
+      const unsigned win_ballot = __ballot_sync(0xffffffffu, win);
+      if (win) {
+        const int pos = n_win + __popc(win_ballot & lt_mask);
+        wkey[pos] = key;
+        wslot[pos] = i;
       }
-      if (id0 >= 0 && r0 < k) {
-        out_idx[(size_t)row * k + r0] = id0;
-        out_val[(size_t)row * k + r0] = (!emit_gated && gate != nullptr) ? v0 / gate[id0] : v0;
+      n_win += __popc(win_ballot);
+      ties_seen += __popc(eq_ballot);
+    }
+    __syncwarp();
+    // place of each of this shard's winners among all winners (value descending, earlier slot first among equals)
+    for (int w = lane; w < n_win; w += 32) {
+      const int slot = wslot[w];
+      if (slot < own_lo || slot >= own_hi) continue;
+      const uint32_t key = wkey[w];
+      int place = 0;
+      for (int j = 0; j < n_win; ++j) {
+        const uint32_t u = wkey[j];
+        place += (u > key) || (u == key && wslot[j] < slot);
       }
-      if (id1 >= 0 && r1 < k) {
-        out_idx[(size_t)row * k + r1] = id1;
-        out_val[(size_t)row * k + r1] = (!emit_gated && gate != nullptr) ? v1 / gate[id1] : v1;
-      }
+      const int id = sidx[slot];
+      const float v = __uint_as_float(key);
+      out_idx[(size_t)row * k + place] = id;
+      out_val[(size_t)row * k + place] = (!emit_gated && gate != nullptr) ? v / gate[id] : v;
     }
     __syncwarp();
   }
@@ -85,7 +99,7 @@ topk_merge_kernel(const float* __restrict__ cand_val, const int* __restrict__ ca
 int topk_merge_launch(const float* cand_val, const int* cand_idx, int M, int C, int k, const float* gate,
                       int own_lo, int own_hi, int emit_gated, int* out_idx, float* out_val,
                       cudaStream_t stream) {
-  const size_t smem = (size_t)MERGE_WARPS * C * 8;
+  const size_t smem = (size_t)MERGE_WARPS * ((size_t)C + (size_t)k) * 8;
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
   cudaError_t e = cudaFuncSetAttribute(topk_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
