@@ -284,3 +284,44 @@ def test_crosscoder_fused_head_sum_matches_generic():
         return float((u.float() - v.float()).norm() / v.float().norm()) < 0.05
 
     assert close(xa.grad, xb.grad) and close(a.W_E.grad, b.W_E.grad) and close(a.b_E.grad, b.b_E.grad)
+
+
+@pytest.mark.parametrize("M,C,k,own", [(257, 256, 50, None), (64, 400, 50, (100, 150)), (33, 96, 64, (32, 64)), (16, 24, 32, None), (8, 37, 5, (0, 37))])
+@pytest.mark.parametrize("use_gate,emit_gated", [(False, False), (True, False), (True, True)])
+def test_topk_merge_matches_its_plain_statement(M, C, k, own, use_gate, emit_gated):
+    """Candidate lists with empty slots, repeated values (ties go to the earlier slot), rows with fewer than k positive
+    candidates, a restricted own range, and k larger than the list."""
+    torch.manual_seed(C + k)
+    if own is None:
+        val = torch.randint(1, 40, (M, C), device="cuda").float() / 8  # few distinct values: many ties
+    else:  # which of several equal candidates wins decides whether a winner lies in the own range: distinct values here
+        val = torch.rand(M, C, device="cuda") + 0.01
+    idx = torch.stack([torch.randperm(4096, device="cuda")[:C] for _ in range(M)]).to(torch.int32)
+    empty = torch.rand(M, C, device="cuda") < 0.3
+    idx[empty] = -1
+    val[torch.rand(M, C, device="cuda") < 0.1] = 0.0  # non-positive candidates never win
+    idx[0] = -1  # a row with nothing
+    idx[1, 3:] = -1  # a row with fewer than k candidates
+    gate = torch.rand(4096, device="cuda") + 0.5 if use_gate else None
+    got_i, got_v = K.topk_merge(val, idx, k, gate, own=own, emit_gated=emit_gated)
+    want_i, want_v = K.ref_topk_merge(val, idx, k, gate, own=own, emit_gated=emit_gated)
+    K.check_status(torch.device("cuda"))
+    # the plain statement uses torch.topk, whose order among EQUAL values is unspecified: compare as sets per row and
+    # per value, and check the kernel's own rule (value descending, earlier slot first among equals) separately
+    assert torch.equal((got_i >= 0).sum(1), (want_i >= 0).sum(1))
+    if own is not None:  # distinct values: the winners and their places are determined
+        assert torch.equal(got_i, want_i) and torch.allclose(got_v, want_v, rtol=1e-6)
+    if own is not None or gate is None or emit_gated:  # (with ties AND a division by the winner's gate the values depend on who won)
+        assert torch.allclose(torch.sort(got_v, dim=1, descending=True).values, torch.sort(want_v, dim=1, descending=True).values, rtol=1e-6)
+    if own is None and not use_gate:
+        kept = got_i >= 0
+        n = kept.sum(1)
+        assert all(bool(kept[r, : n[r]].all()) for r in range(M))  # winners fill the first places
+        assert bool((got_v[:, 1:] <= got_v[:, :-1]).all())  # value descending (empty places hold 0 at the end)
+        # every winner's value is at least every loser's value of that row
+        low = torch.where(kept, got_v, torch.full_like(got_v, float("inf"))).min(1).values
+        pool = torch.where(idx >= 0, val, torch.zeros_like(val))
+        for r in range(M):
+            won = set(got_i[r][kept[r]].tolist())
+            lost = [float(pool[r, c]) for c in range(C) if int(idx[r, c]) >= 0 and int(idx[r, c]) not in won]
+            assert not lost or max(lost) <= float(low[r])
