@@ -31,6 +31,28 @@ T* opt_ptr(const c10::optional<Tensor>& t) {
   return t.has_value() ? reinterpret_cast<T*>(t->data_ptr()) : nullptr;
 }
 
+// ---- peer tables -----------------------------------------------------------------------------------
+// `table` = [world, rank, flags_off, cand_val_off, cand_idx_off, partial_off, dxhat_off, multicast base pointer (0: none),
+//            pointer to the exposed-wait counters (0: none), ptr_0 .. ptr_{world-1}]
+constexpr int kPeerTableHeader = 9;
+lmsae::PeerTable make_peer_table(const std::vector<int64_t>& table) {
+  TORCH_CHECK((int)table.size() >= kPeerTableHeader + 1, "peer table too short");
+  lmsae::PeerTable pt{};
+  pt.world = (int)table[0];
+  pt.rank = (int)table[1];
+  TORCH_CHECK(pt.world >= 1 && pt.world <= lmsae::kMaxPeers && pt.rank >= 0 && pt.rank < pt.world, "bad world/rank");
+  TORCH_CHECK((int)table.size() == kPeerTableHeader + pt.world, "peer table needs one pointer per rank");
+  pt.flags_off = table[2];
+  pt.cand_val_off = table[3];
+  pt.cand_idx_off = table[4];
+  pt.partial_off = table[5];
+  pt.dxhat_off = table[6];
+  pt.mc_base = reinterpret_cast<char*>(static_cast<uintptr_t>(table[7]));
+  pt.stats = reinterpret_cast<unsigned long long*>(static_cast<uintptr_t>(table[8]));
+  for (int i = 0; i < pt.world; ++i) pt.base[i] = reinterpret_cast<char*>(static_cast<uintptr_t>(table[kPeerTableHeader + i]));
+  return pt;
+}
+
 // ---- tensor maps -----------------------------------------------------------------------------------
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -123,19 +145,43 @@ int64_t encoder_gemm(const Tensor& x, const Tensor& w, const c10::optional<Tenso
   return ks;
 }
 
+// comm_mode 0: plain merge. 1: the k winners of every row are stored into every rank's merge input (`table`, candidate
+// offsets already pointing at the buffer of this exchange) instead of out_idx / out_val, and the epoch is published.
+// 2: wait for every rank's candidate flag of `epoch` first; cand_val / cand_idx are views of this rank's buffer.
 void topk_merge(const Tensor& cand_val, const Tensor& cand_idx, int64_t M, int64_t C, int64_t k,
                 const c10::optional<Tensor>& gate, int64_t own_lo, int64_t own_hi, bool emit_gated,
-                const Tensor& out_idx, const Tensor& out_val) {
+                const c10::optional<Tensor>& out_idx, const c10::optional<Tensor>& out_val, int64_t comm_mode,
+                const std::vector<int64_t>& table, int64_t epoch, const c10::optional<Tensor>& done_counter,
+                const c10::optional<Tensor>& status) {
   CHECK_T(cand_val, torch::kFloat32);
   CHECK_T(cand_idx, torch::kInt32);
-  CHECK_T(out_idx, torch::kInt32);
-  CHECK_T(out_val, torch::kFloat32);
-  TORCH_CHECK(cand_val.numel() >= M * C && cand_idx.numel() >= M * C && out_idx.numel() >= M * k && out_val.numel() >= M * k);
+  TORCH_CHECK(cand_val.numel() >= M * C && cand_idx.numel() >= M * C);
   TORCH_CHECK(0 <= own_lo && own_lo <= own_hi && own_hi <= C);
+  lmsae::MergeComm comm{};
+  comm.mode = (int)comm_mode;
+  TORCH_CHECK(comm_mode >= 0 && comm_mode <= 2, "comm_mode must be 0, 1 or 2");
+  if (comm_mode != lmsae::kMergePush) {
+    TORCH_CHECK(out_idx.has_value() && out_val.has_value());
+    CHECK_T(*out_idx, torch::kInt32);
+    CHECK_T(*out_val, torch::kFloat32);
+    TORCH_CHECK(out_idx->numel() >= M * k && out_val->numel() >= M * k);
+  }
+  if (comm_mode != lmsae::kMergeLocal) {
+    comm.pt = make_peer_table(table);
+    comm.epoch = (uint32_t)epoch;
+    TORCH_CHECK(status.has_value());
+    CHECK_T(*status, torch::kInt32);
+    comm.status = status->data_ptr<int>();
+    if (comm_mode == lmsae::kMergePush) {
+      TORCH_CHECK(done_counter.has_value());
+      CHECK_T(*done_counter, torch::kInt32);
+      comm.done_counter = reinterpret_cast<unsigned*>(done_counter->data_ptr<int>());
+    }
+  }
   const c10::cuda::CUDAGuard guard(cand_val.device());
   check_cuda(lmsae::topk_merge_launch(cand_val.data_ptr<float>(), cand_idx.data_ptr<int>(), (int)M, (int)C, (int)k,
                                       opt_ptr<const float>(gate), (int)own_lo, (int)own_hi, emit_gated ? 1 : 0,
-                                      out_idx.data_ptr<int>(), out_val.data_ptr<float>(),
+                                      opt_ptr<int>(out_idx), opt_ptr<float>(out_val), comm,
                                       at::cuda::getCurrentCUDAStream()),
              "topk_merge launch");
 }
@@ -201,17 +247,27 @@ void sparse_decode(const Tensor& idx, const Tensor& val, const Tensor& W, const 
   check_cuda(lmsae::sparse_decode_launch(p, at::cuda::getCurrentCUDAStream()), "sparse_decode launch");
 }
 
-void sparse_dact(const Tensor& idx, const Tensor& W, const Tensor& dxhat, const Tensor& dval) {
+// `table` non-empty: dxhat is the gradient buffer of the fused feature-sharded step; the kernel waits for the row owners'
+// flags of `epoch` before reading it.
+void sparse_dact(const Tensor& idx, const Tensor& W, const Tensor& dxhat, const Tensor& dval,
+                 const std::vector<int64_t>& table, int64_t epoch, const c10::optional<Tensor>& status) {
   CHECK_T(idx, torch::kInt32);
   CHECK_T(W, torch::kBFloat16);
   CHECK_T(dxhat, torch::kBFloat16);
   CHECK_T(dval, torch::kFloat32);
   TORCH_CHECK(idx.dim() == 2 && dval.numel() == idx.numel() && dxhat.numel() == idx.size(0) * W.size(1));
   const c10::cuda::CUDAGuard guard(idx.device());
+  lmsae::PeerTable pt{};
+  if (!table.empty()) {
+    pt = make_peer_table(table);
+    TORCH_CHECK(status.has_value());
+    CHECK_T(*status, torch::kInt32);
+  }
   check_cuda(lmsae::sparse_dact_launch(idx.data_ptr<int>(), (int)idx.size(0), (int)idx.size(1), (int)W.size(1),
                                        reinterpret_cast<const __nv_bfloat16*>(W.data_ptr()),
                                        reinterpret_cast<const __nv_bfloat16*>(dxhat.data_ptr()),
-                                       dval.data_ptr<float>(), at::cuda::getCurrentCUDAStream()),
+                                       dval.data_ptr<float>(), table.empty() ? nullptr : &pt, (uint32_t)epoch,
+                                       opt_ptr<int>(status), at::cuda::getCurrentCUDAStream()),
              "sparse_dact launch");
 }
 
@@ -290,7 +346,10 @@ void sparse_grad_adam(const Tensor& offsets, const Tensor& entries, const Tensor
                       const c10::optional<Tensor>& grad_mul, const c10::optional<Tensor>& grad_sq_sum, double lr,
                       double beta1, double beta2, double eps, int64_t step, bool update, int64_t f_begin,
                       int64_t f_end, int64_t ctas_per_sm, const c10::optional<Tensor>& dxhat_aux, int64_t k_main,
-                      const c10::optional<Tensor>& gD_out, const c10::optional<Tensor>& gE_out) {
+                      const c10::optional<Tensor>& gD_out, const c10::optional<Tensor>& gE_out,
+                      const c10::optional<Tensor>& status, int64_t state_f0, const std::vector<int64_t>& pub_table,
+                      const std::vector<int64_t>& pub_offsets, int64_t pub_epoch,
+                      const c10::optional<Tensor>& pub_done) {
   CHECK_T(offsets, torch::kInt32);
   CHECK_T(entries, torch::kInt32);
   CHECK_T(act, torch::kFloat32);
@@ -306,8 +365,18 @@ void sparse_grad_adam(const Tensor& offsets, const Tensor& entries, const Tensor
   p.d = (int)WD.size(1);
   p.k = (int)act.size(1);
   TORCH_CHECK(offsets.numel() >= p.F + 1 && x.size(1) == p.d && dxhat.sizes() == x.sizes());
-  // state and shadow tensors are only touched when the update is applied
-  if (update) for (const Tensor* t : {&mD, &vD, &WD_bf16, &mE, &vE, &WE_bf16}) TORCH_CHECK(t->numel() == WD.numel());
+  p.f_begin = (int)f_begin;
+  p.f_end = f_end < 0 ? p.F : (int)f_end;
+  TORCH_CHECK(0 <= p.f_begin && p.f_begin <= p.f_end && p.f_end <= p.F, "feature range out of bounds");
+  p.state_f0 = (int)state_f0;
+  TORCH_CHECK(0 <= p.state_f0 && p.state_f0 <= p.f_begin, "state_f0 must not exceed the first updated row");
+  // state and shadow tensors are only touched when the update is applied; with state_f0 > 0 the moments cover rows
+  // [state_f0, f_end) at least
+  if (update) {
+    for (const Tensor* t : {&WD_bf16, &WE_bf16}) TORCH_CHECK(t->numel() == WD.numel());
+    for (const Tensor* t : {&mD, &vD, &mE, &vE})
+      TORCH_CHECK(t->numel() >= (int64_t)(p.f_end - p.state_f0) * p.d, "moment arrays too small for the updated rows");
+  }
   p.offsets = offsets.data_ptr<int>();
   p.entries = entries.data_ptr<int>();
   p.act = act.data_ptr<float>();
@@ -321,7 +390,7 @@ void sparse_grad_adam(const Tensor& offsets, const Tensor& entries, const Tensor
   if (bE.has_value()) {
     TORCH_CHECK(mbE.has_value() && vbE.has_value());
     CHECK_T(*bE, torch::kFloat32); CHECK_T(*mbE, torch::kFloat32); CHECK_T(*vbE, torch::kFloat32);
-    TORCH_CHECK(bE->numel() == p.F && mbE->numel() == p.F && vbE->numel() == p.F);
+    TORCH_CHECK(bE->numel() == p.F && mbE->numel() >= p.f_end - p.state_f0 && vbE->numel() >= p.f_end - p.state_f0);
   }
   p.bE = opt_ptr<float>(bE); p.mbE = opt_ptr<float>(mbE); p.vbE = opt_ptr<float>(vbE);
   if (dec_norm.has_value()) { CHECK_T(*dec_norm, torch::kFloat32); TORCH_CHECK(dec_norm->numel() == p.F); }
@@ -330,9 +399,19 @@ void sparse_grad_adam(const Tensor& offsets, const Tensor& entries, const Tensor
   p.grad_sq_sum = opt_ptr<float>(grad_sq_sum);
   p.h = make_hyper(lr, beta1, beta2, eps, step);
   p.update = update ? 1 : 0;
-  p.f_begin = (int)f_begin;
-  p.f_end = f_end < 0 ? p.F : (int)f_end;
   p.ctas_per_sm = (int)ctas_per_sm;
+  if (status.has_value()) { CHECK_T(*status, torch::kInt32); }
+  p.status = opt_ptr<const int>(status);
+  if (!pub_table.empty()) {
+    p.pub = make_peer_table(pub_table);
+    p.n_pub = p.pub.world;
+    TORCH_CHECK(pub_offsets.size() == 4 && pub_done.has_value(), "publication needs four offsets and a counter");
+    CHECK_T(*pub_done, torch::kInt32);
+    p.pub_wd_off = pub_offsets[0]; p.pub_we_off = pub_offsets[1]; p.pub_norm_off = pub_offsets[2]; p.pub_be_off = pub_offsets[3];
+    for (int64_t o : pub_offsets) TORCH_CHECK(o % 16 == 0, "publication offsets must be 16-byte aligned");
+    p.pub_epoch = (uint32_t)pub_epoch;
+    p.pub_done = reinterpret_cast<unsigned*>(pub_done->data_ptr<int>());
+  }
   if (dxhat_aux.has_value()) { CHECK_T(*dxhat_aux, torch::kBFloat16); TORCH_CHECK(dxhat_aux->sizes() == dxhat.sizes()); }
   p.dxhat_aux = dxhat_aux.has_value() ? reinterpret_cast<const __nv_bfloat16*>(dxhat_aux->data_ptr()) : nullptr;
   p.k_main = (int)k_main;
@@ -341,7 +420,6 @@ void sparse_grad_adam(const Tensor& offsets, const Tensor& entries, const Tensor
   }
   p.gD_out = opt_ptr<float>(gD_out);
   p.gE_out = opt_ptr<float>(gE_out);
-  TORCH_CHECK(0 <= p.f_begin && p.f_begin <= p.f_end && p.f_end <= p.F, "feature range out of bounds");
   check_cuda(lmsae::sparse_grad_adam_launch(p, at::cuda::getCurrentCUDAStream()), "sparse_grad_adam launch");
 }
 
@@ -357,7 +435,7 @@ void colsum_bf16(const Tensor& a, const Tensor& out) {
 
 void adam_flat(const Tensor& p, const Tensor& g, const Tensor& m, const Tensor& v, const c10::optional<Tensor>& grad_mul,
                const c10::optional<Tensor>& shadow, const c10::optional<Tensor>& grad_sq_sum, double lr, double beta1,
-               double beta2, double eps, int64_t step, bool update) {
+               double beta2, double eps, int64_t step, bool update, const c10::optional<Tensor>& status) {
   CHECK_T(p, torch::kFloat32); CHECK_T(g, torch::kFloat32); CHECK_T(m, torch::kFloat32); CHECK_T(v, torch::kFloat32);
   TORCH_CHECK(g.numel() == p.numel() && m.numel() == p.numel() && v.numel() == p.numel());
   if (shadow.has_value()) { CHECK_T(*shadow, torch::kBFloat16); TORCH_CHECK(shadow->numel() == p.numel()); }
@@ -365,7 +443,7 @@ void adam_flat(const Tensor& p, const Tensor& g, const Tensor& m, const Tensor& 
   check_cuda(lmsae::adam_flat_launch(p.data_ptr<float>(), g.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(),
                                      p.numel(), make_hyper(lr, beta1, beta2, eps, step), opt_ptr<const float>(grad_mul),
                                      opt_ptr<__nv_bfloat16>(shadow), opt_ptr<float>(grad_sq_sum), update ? 1 : 0,
-                                     at::cuda::getCurrentCUDAStream()),
+                                     opt_ptr<const int>(status), at::cuda::getCurrentCUDAStream()),
              "adam_flat launch");
 }
 
@@ -677,23 +755,6 @@ void clt_wgrad(const Tensor& offsets, const Tensor& entries, const Tensor& act, 
 }
 
 // ---- peer-memory collectives -----------------------------------------------------------------------
-// `table` = [world, rank, flags_off, cand_val_off, cand_idx_off, partial_off, dxhat_off, ptr_0 .. ptr_{world-1}]
-lmsae::PeerTable make_peer_table(const std::vector<int64_t>& table) {
-  TORCH_CHECK(table.size() >= 8, "peer table too short");
-  lmsae::PeerTable pt{};
-  pt.world = (int)table[0];
-  pt.rank = (int)table[1];
-  TORCH_CHECK(pt.world >= 1 && pt.world <= lmsae::kMaxPeers && pt.rank >= 0 && pt.rank < pt.world, "bad world/rank");
-  TORCH_CHECK((int)table.size() == 7 + pt.world, "peer table needs one pointer per rank");
-  pt.flags_off = table[2];
-  pt.cand_val_off = table[3];
-  pt.cand_idx_off = table[4];
-  pt.partial_off = table[5];
-  pt.dxhat_off = table[6];
-  for (int i = 0; i < pt.world; ++i) pt.base[i] = reinterpret_cast<char*>(static_cast<uintptr_t>(table[7 + i]));
-  return pt;
-}
-
 void comm_push_candidates(const std::vector<int64_t>& table, const Tensor& val, const Tensor& idx, int64_t epoch,
                           const Tensor& done_counter) {
   CHECK_T(val, torch::kFloat32);
@@ -823,8 +884,11 @@ void comm_wait(const std::vector<int64_t>& table, int64_t phase, int64_t epoch, 
              "wait_flags launch");
 }
 
+// partial_dtype: 0 = fp32, 1 = bf16 partial rows; use_multicast: keep the rows local and let the owner sum them through the
+// switch; compact_codes: the codes of a row are packed from slot 0 on.
 void comm_decode_scatter(const std::vector<int64_t>& table, const Tensor& idx, const Tensor& val, const Tensor& W,
-                         int64_t epoch, const Tensor& done_counter) {
+                         int64_t partial_dtype, bool use_multicast, bool compact_codes, int64_t epoch,
+                         const Tensor& done_counter) {
   CHECK_T(idx, torch::kInt32);
   CHECK_T(val, torch::kFloat32);
   CHECK_T(W, torch::kBFloat16);
@@ -833,7 +897,8 @@ void comm_decode_scatter(const std::vector<int64_t>& table, const Tensor& idx, c
   const c10::cuda::CUDAGuard guard(idx.device());
   check_cuda(lmsae::sparse_decode_scatter_launch(make_peer_table(table), idx.data_ptr<int>(), val.data_ptr<float>(),
                                                  (int)idx.size(0), (int)idx.size(1), (int)W.size(1),
-                                                 reinterpret_cast<const __nv_bfloat16*>(W.data_ptr()), (uint32_t)epoch,
+                                                 reinterpret_cast<const __nv_bfloat16*>(W.data_ptr()), (int)partial_dtype,
+                                                 use_multicast ? 1 : 0, compact_codes ? 1 : 0, (uint32_t)epoch,
                                                  reinterpret_cast<unsigned*>(done_counter.data_ptr<int>()),
                                                  at::cuda::getCurrentCUDAStream()),
              "sparse_decode_scatter launch");
@@ -842,7 +907,8 @@ void comm_decode_scatter(const std::vector<int64_t>& table, const Tensor& idx, c
 void comm_reduce_loss_push(const std::vector<int64_t>& table, int64_t B, int64_t d, const Tensor& label,
                            const c10::optional<Tensor>& bias, const c10::optional<Tensor>& row_weight,
                            double grad_scale, const Tensor& loss_sum, const c10::optional<Tensor>& xhat_out,
-                           int64_t epoch, const Tensor& done_counter, const Tensor& status) {
+                           int64_t partial_dtype, bool use_multicast, int64_t epoch_in, int64_t epoch_out,
+                           const Tensor& done_counter, const Tensor& status) {
   CHECK_T(label, torch::kBFloat16);
   CHECK_T(loss_sum, torch::kFloat32);
   CHECK_T(done_counter, torch::kInt32);
@@ -856,15 +922,43 @@ void comm_reduce_loss_push(const std::vector<int64_t>& table, int64_t B, int64_t
                                             reinterpret_cast<const __nv_bfloat16*>(label.data_ptr()),
                                             opt_ptr<const float>(bias), opt_ptr<const float>(row_weight),
                                             (float)grad_scale, loss_sum.data_ptr<float>(), opt_ptr<float>(xhat_out),
-                                            (uint32_t)epoch, reinterpret_cast<unsigned*>(done_counter.data_ptr<int>()),
+                                            (int)partial_dtype, use_multicast ? 1 : 0, (uint32_t)epoch_in,
+                                            (uint32_t)epoch_out, reinterpret_cast<unsigned*>(done_counter.data_ptr<int>()),
                                             status.data_ptr<int>(), at::cuda::getCurrentCUDAStream()),
              "reduce_loss_push launch");
+}
+
+// All-gather of up to eight row-sharded tensors over the ranks of `table` by peer stores, in one kernel: tensor i (any
+// dtype, contiguous, the same byte size on every rank) lands at byte offset dst_offsets[i] + rank * nbytes_i of every
+// rank's buffer; the kernel returns once every rank's rows have arrived here (bounded wait by its last block).
+void comm_exchange_rows(const std::vector<int64_t>& table, const std::vector<Tensor>& src,
+                        const std::vector<int64_t>& dst_offsets, int64_t epoch, const Tensor& done_counter,
+                        const Tensor& status) {
+  CHECK_T(done_counter, torch::kInt32);
+  CHECK_T(status, torch::kInt32);
+  TORCH_CHECK(!src.empty() && src.size() <= 8 && src.size() == dst_offsets.size(), "one offset per tensor, at most eight");
+  lmsae::RowExchange ex{};
+  ex.n = (int)src.size();
+  for (int i = 0; i < ex.n; ++i) {
+    TORCH_CHECK(src[i].is_cuda() && src[i].is_contiguous(), "exchange tensors must be contiguous CUDA tensors");
+    ex.src[i] = src[i].data_ptr();
+    ex.nbytes[i] = (long long)src[i].numel() * (long long)src[i].element_size();
+    ex.dst_off[i] = dst_offsets[i];
+    TORCH_CHECK(ex.nbytes[i] % 16 == 0 && ex.dst_off[i] % 16 == 0 && reinterpret_cast<uintptr_t>(ex.src[i]) % 16 == 0,
+                "exchange tensors must be multiples of 16 bytes at 16-byte aligned addresses");
+  }
+  const c10::cuda::CUDAGuard guard(src[0].device());
+  check_cuda(lmsae::exchange_rows_launch(make_peer_table(table), ex, (uint32_t)epoch,
+                                         reinterpret_cast<unsigned*>(done_counter.data_ptr<int>()), status.data_ptr<int>(),
+                                         at::cuda::getCurrentCUDAStream()),
+             "exchange_rows launch");
 }
 
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("comm_push_candidates", &comm_push_candidates);
+  m.def("comm_exchange_rows", &comm_exchange_rows);
   m.def("comm_wait", &comm_wait);
   m.def("comm_bcast_rows", &comm_bcast_rows);
   m.def("comm_signal", &comm_signal);

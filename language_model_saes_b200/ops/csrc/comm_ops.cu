@@ -17,59 +17,9 @@
 //
 // They replace: the all-reduces of the reference's distributed top-k (utils/distributed/ops.py:226-250) and
 // the Partial->Replicate all-reduce after its decoder matmul (models/sae.py:374-375).
-#include "common.cuh"
-#include "kernels.h"
+#include "comm_common.cuh"
 
 namespace lmsae {
-
-__device__ __forceinline__ void bf16x8_to_float_c(const uint4& u, float (&f)[8]) {
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 t = __bfloat1622float2(h[i]);
-    f[2 * i] = t.x;
-    f[2 * i + 1] = t.y;
-  }
-}
-
-// After all of this grid's stores: the last block to arrive publishes `epoch` in every peer's flag slot.
-__device__ __forceinline__ void signal_peers_when_grid_done(const PeerTable& pt, int phase, uint32_t epoch,
-                                                            unsigned* done_counter) {
-  __shared__ int s_last;
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const unsigned prev = atomicAdd(done_counter, 1u);
-    s_last = (prev == gridDim.x - 1);
-    if (s_last) *done_counter = 0;
-  }
-  __syncthreads();
-  if (s_last) {
-    __threadfence_system();
-    if ((int)threadIdx.x < pt.world) {
-      uint32_t* flag = reinterpret_cast<uint32_t*>(pt.base[threadIdx.x] + pt.flags_off) + phase * kMaxPeers + pt.rank;
-      st_release_sys(flag, epoch);
-    }
-  }
-}
-
-// Block-wide bounded wait until every source rank has published `epoch` for `phase` in OUR flag slots.
-// Returns false (uniformly) on expiry.
-__device__ __forceinline__ bool wait_all_sources(const PeerTable& pt, int phase, uint32_t epoch, int* status) {
-  __shared__ int s_ok;
-  if (threadIdx.x == 0) s_ok = 1;
-  __syncthreads();
-  if ((int)threadIdx.x < pt.world) {
-    const uint32_t* flag =
-        reinterpret_cast<const uint32_t*>(pt.base[pt.rank] + pt.flags_off) + phase * kMaxPeers + threadIdx.x;
-    if (!wait_flag_sys(flag, epoch)) {
-      report_status(status, kTimeoutPeerFlag, phase, (int)threadIdx.x);
-      s_ok = 0;
-    }
-  }
-  __syncthreads();
-  return s_ok != 0;
-}
 
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
@@ -95,57 +45,82 @@ __global__ void wait_flags_kernel(const PeerTable pt, int phase, uint32_t epoch,
 }
 
 // ---------------------------------------------------------------------------------------------
+// Sparse decode of this shard's codes whose epilogue is the reduce-scatter of the partial reconstruction.
+//   PT       element type of the partial rows on the wire: float, or __nv_bfloat16 (half the NVLink bytes; what a
+//            bf16 all-reduce of the decoder output moves)
+//   LOCAL    false: each finished row is stored into slot [rank] of the landing zone of the rank that OWNS the row
+//            (peer store); true: rows stay in this rank's own buffer as [B][d] and the owner pulls the sum of all
+//            ranks' copies through the switch (multimem.ld_reduce in reduce_loss_push_kernel)
+// `compact`: codes of a row are packed from slot 0 on (what the merge kernel writes), so the slot loop stops at the
+// first empty one; under feature sharding a row holds about k / world codes.
+// ---------------------------------------------------------------------------------------------
 constexpr int SC_THREADS = 512;
 constexpr int SC_MAX_VEC = 2;
+constexpr int SC_UNROLL = 4;
 
+template <typename PT, bool LOCAL>
 __global__ void __launch_bounds__(SC_THREADS)
 sparse_decode_scatter_kernel(const PeerTable pt, const int* __restrict__ idx, const float* __restrict__ val, int B, int k,
-                             int d, const __nv_bfloat16* __restrict__ W, uint32_t epoch, unsigned* done_counter) {
-  extern __shared__ uint8_t smem_raw[];
-  int* s_idx = reinterpret_cast<int*>(smem_raw);
-  float* s_val = reinterpret_cast<float*>(smem_raw) + k;
+                             int d, const __nv_bfloat16* __restrict__ W, int compact, uint32_t epoch,
+                             unsigned* done_counter) {
   const int nvec = d / 8;
   const int rows_per_rank = B / pt.world;
   for (int row = blockIdx.x; row < B; row += gridDim.x) {
-    __syncthreads();
-    for (int j = threadIdx.x; j < k; j += SC_THREADS) {
-      s_idx[j] = idx[(size_t)row * k + j];
-      s_val[j] = val[(size_t)row * k + j];
-    }
-    __syncthreads();
+    const int* ridx = idx + (size_t)row * k;
+    const float* rval = val + (size_t)row * k;
     float acc[SC_MAX_VEC][8];
 #pragma unroll
     for (int u = 0; u < SC_MAX_VEC; ++u)
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[u][i] = 0.0f;
-    for (int j = 0; j < k; ++j) {
-      const int f = s_idx[j];
-      if (f < 0) continue;
-      const float a = s_val[j];
-      const uint4* wrow = reinterpret_cast<const uint4*>(W + (size_t)f * d);
+    for (int j0 = 0; j0 < k; j0 += SC_UNROLL) {
+      // the codes of a row are the same for every thread: these loads are broadcasts served by L1
+      int f[SC_UNROLL];
+      float a[SC_UNROLL];
 #pragma unroll
-      for (int u = 0; u < SC_MAX_VEC; ++u) {
-        const int v = threadIdx.x + u * SC_THREADS;
-        if (v < nvec) {
-          float w[8];
-          bf16x8_to_float_c(__ldg(wrow + v), w);
+      for (int t = 0; t < SC_UNROLL; ++t) {
+        const int j = j0 + t;
+        f[t] = j < k ? __ldg(ridx + j) : -1;
+        a[t] = j < k ? __ldg(rval + j) : 0.0f;
+      }
+      if (compact && f[0] < 0) break;
+      // all gathers of the group are issued before the first is used
+      uint4 w[SC_UNROLL][SC_MAX_VEC];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) acc[u][i] = fmaf(a, w[i], acc[u][i]);
+      for (int t = 0; t < SC_UNROLL; ++t) {
+        const uint4* wrow = reinterpret_cast<const uint4*>(W + (size_t)(f[t] < 0 ? 0 : f[t]) * d);
+#pragma unroll
+        for (int u = 0; u < SC_MAX_VEC; ++u) {
+          const int v = threadIdx.x + u * SC_THREADS;
+          w[t][u] = (f[t] >= 0 && v < nvec) ? __ldg(wrow + v) : make_uint4(0u, 0u, 0u, 0u);
         }
       }
+#pragma unroll
+      for (int t = 0; t < SC_UNROLL; ++t)
+#pragma unroll
+        for (int u = 0; u < SC_MAX_VEC; ++u) {
+          float wf[8];
+          bf16x8_to_float_c(w[t][u], wf);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[u][i] = fmaf(a[t], wf[i], acc[u][i]);
+        }
     }
-    // epilogue = reduce-scatter: this row belongs to rank `owner`; our partial goes to slot [rank] there
+    // epilogue = reduce-scatter
     const int owner = row / rows_per_rank;
     const int lrow = row - owner * rows_per_rank;
-    float* dst = reinterpret_cast<float*>(pt.base[owner] + pt.partial_off) +
-                 ((size_t)pt.rank * rows_per_rank + lrow) * d;
+    PT* dst = LOCAL ? reinterpret_cast<PT*>(pt.base[pt.rank] + pt.partial_off) + (size_t)row * d
+                    : reinterpret_cast<PT*>(pt.base[owner] + pt.partial_off) + ((size_t)pt.rank * rows_per_rank + lrow) * d;
 #pragma unroll
     for (int u = 0; u < SC_MAX_VEC; ++u) {
       const int v = threadIdx.x + u * SC_THREADS;
       if (v < nvec) {
-        float4* o = reinterpret_cast<float4*>(dst + v * 8);
-        o[0] = make_float4(acc[u][0], acc[u][1], acc[u][2], acc[u][3]);
-        o[1] = make_float4(acc[u][4], acc[u][5], acc[u][6], acc[u][7]);
+        if constexpr (sizeof(PT) == 4) {
+          float4* o = reinterpret_cast<float4*>(dst + v * 8);
+          o[0] = make_float4(acc[u][0], acc[u][1], acc[u][2], acc[u][3]);
+          o[1] = make_float4(acc[u][4], acc[u][5], acc[u][6], acc[u][7]);
+        } else {
+          *reinterpret_cast<uint4*>(dst + v * 8) = float8_to_bf16x8(acc[u]);
+        }
       }
     }
   }
@@ -153,17 +128,25 @@ sparse_decode_scatter_kernel(const PeerTable pt, const int* __restrict__ idx, co
 }
 
 // ---------------------------------------------------------------------------------------------
+// The owner of a block of rows sums the partial reconstructions of all shards (+ bias), evaluates the loss and its
+// gradient and all-gathers the bf16 gradient rows into every rank's [B][d] buffer.
+//   MC = false  partials are read from the `world` slots of this rank's landing zone; the gradient row is stored into
+//               every peer (world peer stores per 16 bytes)
+//   MC = true   one multimem.ld_reduce per 16 bytes returns the sum over all ranks' [B][d] buffers (added inside the
+//               NVSwitch), one multimem.st publishes the gradient to every rank
+// ---------------------------------------------------------------------------------------------
+template <typename PT, bool MC>
 __global__ void __launch_bounds__(256)
 reduce_loss_push_kernel(const PeerTable pt, int B, int d, const __nv_bfloat16* __restrict__ label,
                         const float* __restrict__ bias, const float* __restrict__ row_weight, float grad_scale,
-                        float* __restrict__ loss_sum, float* __restrict__ xhat_out, uint32_t epoch,
+                        float* __restrict__ loss_sum, float* __restrict__ xhat_out, uint32_t epoch_in, uint32_t epoch_out,
                         unsigned* done_counter, int* status) {
   __shared__ float s_red[8];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rows_per_rank = B / pt.world;
-  const bool ok = wait_all_sources(pt, kPhasePartial, epoch, status);
+  const bool ok = wait_all_sources(pt, kPhasePartial, epoch_in, status);
   if (ok) {
-    const float* partial = reinterpret_cast<const float*>(pt.base[pt.rank] + pt.partial_off);
+    const PT* partial = reinterpret_cast<const PT*>(pt.base[pt.rank] + pt.partial_off);
     const int nvec = d / 8;
     for (int lrow = blockIdx.x; lrow < rows_per_rank; lrow += gridDim.x) {
       const int row = pt.rank * rows_per_rank + lrow;
@@ -173,11 +156,34 @@ reduce_loss_push_kernel(const PeerTable pt, int B, int d, const __nv_bfloat16* _
         float x[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) x[i] = bias != nullptr ? bias[v * 8 + i] : 0.0f;
-        for (int s = 0; s < pt.world; ++s) {
-          const float4* src = reinterpret_cast<const float4*>(partial + ((size_t)s * rows_per_rank + lrow) * d + v * 8);
-          const float4 a = src[0], b = src[1];
-          x[0] += a.x; x[1] += a.y; x[2] += a.z; x[3] += a.w;
-          x[4] += b.x; x[5] += b.y; x[6] += b.z; x[7] += b.w;
+        if constexpr (MC) {
+          const char* mc = pt.mc_base + pt.partial_off + ((size_t)row * d + (size_t)v * 8) * sizeof(__nv_bfloat16);
+          float t[8];
+          bf16x8_to_float_c(multimem_ld_reduce_add_bf16x8(mc), t);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) x[i] += t[i];
+        } else if constexpr (sizeof(PT) == 4) {
+          for (int s = 0; s < pt.world; ++s) {
+            const float4* src = reinterpret_cast<const float4*>(partial + ((size_t)s * rows_per_rank + lrow) * d + v * 8);
+            const float4 a = src[0], b = src[1];
+            x[0] += a.x; x[1] += a.y; x[2] += a.z; x[3] += a.w;
+            x[4] += b.x; x[5] += b.y; x[6] += b.z; x[7] += b.w;
+          }
+        } else {
+          // issue the loads of all slots before the first conversion (world <= 8)
+          uint4 raw[kMaxPeers];
+#pragma unroll
+          for (int s = 0; s < kMaxPeers; ++s)
+            if (s < pt.world)
+              raw[s] = *(reinterpret_cast<const uint4*>(partial + ((size_t)s * rows_per_rank + lrow) * d) + v);
+#pragma unroll
+          for (int s = 0; s < kMaxPeers; ++s)
+            if (s < pt.world) {
+              float t[8];
+              bf16x8_to_float_c(raw[s], t);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) x[i] += t[i];
+            }
         }
         if (xhat_out != nullptr) {
           float4* o = reinterpret_cast<float4*>(xhat_out + (size_t)row * d + v * 8);
@@ -193,15 +199,13 @@ reduce_loss_push_kernel(const PeerTable pt, int B, int d, const __nv_bfloat16* _
           sq = fmaf(e[i], e[i], sq);
           e[i] *= grad_scale * rw;
         }
-        uint4 o;
-        o.x = pack_bf16x2(e[0], e[1]);
-        o.y = pack_bf16x2(e[2], e[3]);
-        o.z = pack_bf16x2(e[4], e[5]);
-        o.w = pack_bf16x2(e[6], e[7]);
-        // all-gather of the gradient rows: store into every rank's full [B, d] gradient buffer
-        for (int p = 0; p < pt.world; ++p) {
-          uint4* dst = reinterpret_cast<uint4*>(pt.base[p] + pt.dxhat_off) + ((size_t)row * d) / 8 + v;
-          *dst = o;
+        const uint4 o = float8_to_bf16x8(e);
+        const size_t off16 = ((size_t)row * d) / 8 + v;
+        if constexpr (MC) {
+          multimem_st_16B(reinterpret_cast<uint4*>(pt.mc_base + pt.dxhat_off) + off16, o);
+        } else {
+          // all-gather of the gradient rows: store into every rank's full [B, d] gradient buffer
+          for (int p = 0; p < pt.world; ++p) *(reinterpret_cast<uint4*>(pt.base[p] + pt.dxhat_off) + off16) = o;
         }
       }
       sq = warp_sum(sq);
@@ -216,7 +220,39 @@ reduce_loss_push_kernel(const PeerTable pt, int B, int d, const __nv_bfloat16* _
     }
   }
   // signal even after a failed wait so that peers do not pile further timeouts on top of the first one
-  signal_peers_when_grid_done(pt, kPhaseDxhat, epoch, done_counter);
+  signal_peers_when_grid_done(pt, kPhaseDxhat, epoch_out, done_counter);
+}
+
+// ---------------------------------------------------------------------------------------------
+// All-gather of several row-sharded tensors over a (data-parallel) group in ONE kernel: every rank stores its part of
+// each tensor at offset rank * nbytes of the gathered tensor in every rank's buffer (its own included), the last block
+// publishes the epoch and then waits (bounded) for the other ranks' flags, so that the kernels after this one in the
+// stream find every rank's rows in place. Replaces one collective per tensor (x, d x_hat and the three code tensors of
+// a data-parallel step).
+__global__ void __launch_bounds__(256)
+exchange_rows_kernel(const PeerTable pt, const RowExchange ex, uint32_t epoch, unsigned* done_counter, int* status) {
+  for (int i = 0; i < ex.n; ++i) {
+    const uint4* s = reinterpret_cast<const uint4*>(ex.src[i]);
+    const long long nvec = ex.nbytes[i] / 16;
+    for (int p = 0; p < pt.world; ++p) {
+      uint4* dst = reinterpret_cast<uint4*>(pt.base[p] + ex.dst_off[i] + (long long)pt.rank * ex.nbytes[i]);
+      for (long long v = blockIdx.x * 256LL + threadIdx.x; v < nvec; v += (long long)gridDim.x * 256) dst[v] = __ldg(s + v);
+    }
+  }
+  const bool last = signal_peers_when_grid_done(pt, kPhaseRows, epoch, done_counter);
+  if (last) wait_all_sources(pt, kPhaseRows, epoch, status);
+}
+
+int exchange_rows_launch(const PeerTable& pt, const RowExchange& ex, uint32_t epoch, unsigned* done_counter, int* status,
+                         cudaStream_t stream) {
+  if (ex.n < 1 || ex.n > 8) return (int)cudaErrorInvalidValue;
+  long long total = 0;
+  for (int i = 0; i < ex.n; ++i) total += ex.nbytes[i] / 16;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  if (blocks < 1) blocks = 1;
+  exchange_rows_kernel<<<(int)blocks, 256, 0, stream>>>(pt, ex, epoch, done_counter, status);
+  return (int)cudaGetLastError();
 }
 
 // ---- launchers ----------------------------------------------------------------------------------
@@ -411,22 +447,37 @@ int wait_flags_launch(const PeerTable& pt, int phase, uint32_t epoch, int* statu
 }
 
 int sparse_decode_scatter_launch(const PeerTable& pt, const int* idx, const float* val, int B, int k, int d,
-                                 const __nv_bfloat16* W, uint32_t epoch, unsigned* done_counter, cudaStream_t stream) {
+                                 const __nv_bfloat16* W, int partial_dtype, int use_multicast, int compact_codes,
+                                 uint32_t epoch, unsigned* done_counter, cudaStream_t stream) {
   if (d % 8 != 0 || d > SC_THREADS * SC_MAX_VEC * 8 || B % pt.world != 0) return (int)cudaErrorInvalidValue;
+  if (use_multicast && (partial_dtype != 1 || pt.mc_base == nullptr)) return (int)cudaErrorInvalidValue;
   int blocks = B < 148 * 4 ? B : 148 * 4;
-  sparse_decode_scatter_kernel<<<blocks, SC_THREADS, (size_t)k * 8, stream>>>(pt, idx, val, B, k, d, W, epoch,
-                                                                              done_counter);
+  using bf = __nv_bfloat16;
+#define LMSAE_SCATTER(PT, LOCAL) \
+  sparse_decode_scatter_kernel<PT, LOCAL><<<blocks, SC_THREADS, 0, stream>>>(pt, idx, val, B, k, d, W, compact_codes, epoch, done_counter)
+  if (use_multicast) LMSAE_SCATTER(bf, true);
+  else if (partial_dtype == 1) LMSAE_SCATTER(bf, false);
+  else LMSAE_SCATTER(float, false);
+#undef LMSAE_SCATTER
   return (int)cudaGetLastError();
 }
 
 int reduce_loss_push_launch(const PeerTable& pt, int B, int d, const __nv_bfloat16* label, const float* bias,
-                            const float* row_weight, float grad_scale, float* loss_sum, float* xhat_out, uint32_t epoch,
+                            const float* row_weight, float grad_scale, float* loss_sum, float* xhat_out,
+                            int partial_dtype, int use_multicast, uint32_t epoch_in, uint32_t epoch_out,
                             unsigned* done_counter, int* status, cudaStream_t stream) {
   if (d % 8 != 0 || B % pt.world != 0) return (int)cudaErrorInvalidValue;
+  if (use_multicast && (partial_dtype != 1 || pt.mc_base == nullptr)) return (int)cudaErrorInvalidValue;
   const int rows = B / pt.world;
   int blocks = rows < 148 * 4 ? rows : 148 * 4;
-  reduce_loss_push_kernel<<<blocks, 256, 0, stream>>>(pt, B, d, label, bias, row_weight, grad_scale, loss_sum, xhat_out,
-                                                      epoch, done_counter, status);
+  using bf = __nv_bfloat16;
+#define LMSAE_REDUCE(PT, MC)                                                                                         \
+  reduce_loss_push_kernel<PT, MC><<<blocks, 256, 0, stream>>>(pt, B, d, label, bias, row_weight, grad_scale, loss_sum, \
+                                                              xhat_out, epoch_in, epoch_out, done_counter, status)
+  if (use_multicast) LMSAE_REDUCE(bf, true);
+  else if (partial_dtype == 1) LMSAE_REDUCE(bf, false);
+  else LMSAE_REDUCE(float, false);
+#undef LMSAE_REDUCE
   return (int)cudaGetLastError();
 }
 

@@ -40,8 +40,39 @@ struct EncGemmParams {
 int enc_gemm_launch(const CUtensorMap& ta, const CUtensorMap& tb, const EncGemmParams& p, int mode, cudaStream_t stream);
 int enc_gemm_slots_for_k(int k);
 
+// ---- peer-memory collectives (comm_ops.cu) -------------------------------------------------------
+constexpr int kMaxPeers = 8;
+// Flag words of a symmetric buffer: flag[phase][src] = last epoch that rank `src` published for `phase`. Every
+// communicator object owns its buffer and therefore its own set of phases; the names below are those of the fused
+// training step (model group) and of the data-parallel row exchange / parameter publication (data group).
+enum CommPhase : int {
+  kPhaseCand = 0, kPhasePartial = 1, kPhaseDxhat = 2, kPhaseAux = 3, kPhaseRows = 4, kPhaseParams = 5, kNumPhases = 8
+};
+
+// Peer mappings of every rank's symmetric buffer plus the byte offsets of its regions (same on all ranks).
+struct PeerTable {
+  char* base[kMaxPeers];
+  int world, rank;
+  long long flags_off;     // uint32 [kNumPhases][kMaxPeers]
+  long long cand_val_off;  // float [B][world * k]   (the host alternates between two such buffers)
+  long long cand_idx_off;  // int   [B][world * k]
+  long long partial_off;   // partial reconstruction rows: [world][B / world][d] (peer stores) or [B][d] (multicast reads)
+  long long dxhat_off;     // bf16  [B][d]
+  char* mc_base;           // multicast (NVLS) mapping of the same buffers, nullptr when the group has none
+  unsigned long long* stats;  // exposed-wait accounting: {cycles, calls} per phase, local device memory or nullptr
+};
+
+enum MergeCommMode : int { kMergeLocal = 0, kMergePush = 1, kMergeWait = 2 };
+struct MergeComm {
+  PeerTable pt;
+  int mode;
+  uint32_t epoch;
+  unsigned* done_counter;
+  int* status;
+};
+
 int topk_merge_launch(const float* cand_val, const int* cand_idx, int M, int C, int k, const float* gate, int own_lo,
-                      int own_hi, int emit_gated, int* out_idx, float* out_val, cudaStream_t stream);
+                      int own_hi, int emit_gated, int* out_idx, float* out_val, const MergeComm& comm, cudaStream_t stream);
 int row_topk_launch(const __nv_bfloat16* H, long long ldh, int M, int N, int k, const float* gate,
                     const uint8_t* alive, int* out_idx, float* out_val, cudaStream_t stream);
 
@@ -62,8 +93,9 @@ struct DecodeParams {
   float* dval;
 };
 int sparse_decode_launch(const DecodeParams& p, cudaStream_t stream);
+// `wait`: optional (pt.world > 0) bounded wait for the gradient rows of the fused step (phase kPhaseDxhat) at kernel entry
 int sparse_dact_launch(const int* idx, int B, int k, int d, const __nv_bfloat16* W, const __nv_bfloat16* dxhat,
-                       float* dval, cudaStream_t stream);
+                       float* dval, const PeerTable* wait, uint32_t epoch, int* status, cudaStream_t stream);
 int mse_loss_grad_launch(const float* xhat, const __nv_bfloat16* label, const float* bias, const float* row_weight,
                          int rows, int d, float grad_scale, __nv_bfloat16* dxhat, float* loss_sum, float* row_loss,
                          cudaStream_t stream);
@@ -92,10 +124,23 @@ struct GradAdamParams {
   int update;
   int f_begin, f_end;  // feature rows handled by this launch
   int ctas_per_sm;     // 0 = fill the GPU (4 per SM); 1..4 = leave registers free for a concurrently running kernel
+  const int* status;   // kernels' status word: a recorded error turns the update into a no-op (nullptr: not checked)
   const __nv_bfloat16* dxhat_aux;  // output gradient seen by the code slots >= k_main of every row (nullptr: none)
   int k_main;
   float* gD_out;  // optional dense [F, d] outputs of the rebuilt gradient rows (for autograd callers)
   float* gE_out;
+  // Optimizer state sharded by feature row over data-parallel replicas: this launch owns rows [f_begin, f_end); its
+  // moments are arrays of (f_end - state_f0) rows that start at row state_f0 of the dictionary (0: full-size arrays).
+  int state_f0;
+  // Publication of the updated rows to the other replicas (n_pub > 0): the bf16 shadows, decoder norms and encoder
+  // biases are stored at byte offsets pub_*_off of EVERY rank's symmetric buffer in pub (this rank's own included, the
+  // local WD_bf16 / WE_bf16 / dec_norm / bE pointers above are then views of that buffer), and the last block
+  // publishes pub_epoch for phase kPhaseParams.
+  int n_pub;
+  PeerTable pub;
+  long long pub_wd_off, pub_we_off, pub_norm_off, pub_be_off;
+  uint32_t pub_epoch;
+  unsigned* pub_done;
 };
 int auxk_loss_grad_launch(const float* xhat, const float* aux_rec, const __nv_bfloat16* label, const float* bias,
                           const float* row_weight, int rows, int d, float grad_scale, float alpha,
@@ -104,7 +149,7 @@ int auxk_loss_grad_launch(const float* xhat, const float* aux_rec, const __nv_bf
 int sparse_grad_adam_launch(const GradAdamParams& p, cudaStream_t stream);
 int colsum_bf16_launch(const __nv_bfloat16* a, int rows, int d, float* out, cudaStream_t stream);
 int adam_flat_launch(float* p, const float* g, float* m, float* v, long long n, AdamHyper h, const float* grad_mul,
-                     __nv_bfloat16* shadow, float* grad_sq_sum, int update, cudaStream_t stream);
+                     __nv_bfloat16* shadow, float* grad_sq_sum, int update, const int* status, cudaStream_t stream);
 int row_norm_shadow_launch(const float* W, int F, int d, float* norm, __nv_bfloat16* shadow, cudaStream_t stream);
 
 // ---- cross-layer transcoder decoder fan-out (clt_ops.cu) --------------------------------------------
@@ -161,21 +206,15 @@ int attn_fwd_launch(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensor
 int jumprelu_launch(int dtype, const void* x, const void* log_theta, const void* dy, void* out, float* dlog, long long n,
                     int P, float window, int backward, cudaStream_t stream);
 
-// ---- peer-memory collectives (comm_ops.cu) -------------------------------------------------------
-constexpr int kMaxPeers = 8;
-enum CommPhase : int { kPhaseCand = 0, kPhasePartial = 1, kPhaseDxhat = 2, kNumPhases = 4 };
-
-// Peer mappings of every rank's symmetric buffer plus the byte offsets of its regions (same on all ranks).
-struct PeerTable {
-  char* base[kMaxPeers];
-  int world, rank;
-  long long flags_off;     // uint32 [kNumPhases][kMaxPeers]: flag[phase][src] = last epoch published by src
-  long long cand_val_off;  // float [B][world * k]
-  long long cand_idx_off;  // int   [B][world * k]
-  long long partial_off;   // float [world][B / world][d]
-  long long dxhat_off;     // bf16  [B][d]
+// All-gather of several row-sharded tensors in one kernel (comm_ops.cu::exchange_rows_kernel).
+struct RowExchange {
+  const void* src[8];
+  long long nbytes[8];   // bytes of this rank's part (the same on every rank), multiples of 16
+  long long dst_off[8];  // byte offset of the gathered tensor in every rank's buffer
+  int n;
 };
-
+int exchange_rows_launch(const PeerTable& pt, const RowExchange& ex, uint32_t epoch, unsigned* done_counter, int* status,
+                         cudaStream_t stream);
 int push_candidates_launch(const PeerTable& pt, const float* val, const int* idx, int B, int k, uint32_t epoch,
                            unsigned* done_counter, cudaStream_t stream);
 int shuffle_rows_launch(const PeerTable& pt, const void* src, const long long* dest, int n_local, int rows_per_rank,
@@ -190,10 +229,15 @@ int headsum_gather_launch(const PeerTable& pt, long long slab_off, long long out
 int signal_flags_launch(const PeerTable& pt, int phase, uint32_t epoch, cudaStream_t stream);
 int wait_flag_src_launch(const PeerTable& pt, int phase, uint32_t epoch, int src, int* status, cudaStream_t stream);
 int wait_flags_launch(const PeerTable& pt, int phase, uint32_t epoch, int* status, cudaStream_t stream);
+// partial_dtype: 0 = fp32, 1 = bf16 partial rows. use_multicast: partial rows stay in the producer's own buffer ([B][d])
+// and the owner sums them with multimem.ld_reduce; the gradient rows are published with multimem.st (needs pt.mc_base,
+// bf16 partials).
 int sparse_decode_scatter_launch(const PeerTable& pt, const int* idx, const float* val, int B, int k, int d,
-                                 const __nv_bfloat16* W, uint32_t epoch, unsigned* done_counter, cudaStream_t stream);
+                                 const __nv_bfloat16* W, int partial_dtype, int use_multicast, int compact_codes,
+                                 uint32_t epoch, unsigned* done_counter, cudaStream_t stream);
 int reduce_loss_push_launch(const PeerTable& pt, int B, int d, const __nv_bfloat16* label, const float* bias,
-                            const float* row_weight, float grad_scale, float* loss_sum, float* xhat_out, uint32_t epoch,
+                            const float* row_weight, float grad_scale, float* loss_sum, float* xhat_out,
+                            int partial_dtype, int use_multicast, uint32_t epoch_in, uint32_t epoch_out,
                             unsigned* done_counter, int* status, cudaStream_t stream);
 
 }  // namespace lmsae

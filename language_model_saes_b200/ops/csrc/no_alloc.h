@@ -24,11 +24,12 @@ extern "C" {
 // `idx`, `offsets` and `entries` are device pointers owned by the caller; the work is enqueued on `stream`.
 //
 // Returns 0 on success, otherwise a cudaError_t value (cudaErrorInvalidValue when F exceeds
-// LMSAE_NOALLOC_MAX_FEATURES or an argument is null / negative). It never calls cudaMalloc, cudaFree or any
-// allocating library routine.
+// LMSAE_NOALLOC_MAX_FEATURES, when n exceeds INT_MAX (entry positions are 32-bit) or an argument is null /
+// negative). It never calls cudaMalloc, cudaFree or any allocating library routine.
 //
 // The first call on a device looks up the device address of the scratch array (cudaGetSymbolAddress, with
-// that device current); make that first call outside of any stream capture. All calls share the one scratch
+// that device current); make that first call outside of any stream capture. Two host threads may make their first
+// call at the same time: the look-up is idempotent and its result is published atomically. All calls share the one scratch
 // array, which still holds the previous call's counters when a call starts: the function clears what it needs,
 // but two calls that overlap on the same GPU (different streams, different threads) race on it and must be
 // serialised by the caller.

@@ -14,8 +14,7 @@
 //                         dW_E^T[f,:] = sum d h * x[b,:] in registers from the feature's entry list and
 //                         apply Adam to both rows in the same pass -- the dense gradient is never written
 //                         (replaces kernels/kernels.py:137-225 + torch.optim.Adam in the reference).
-#include "common.cuh"
-#include "kernels.h"
+#include "comm_common.cuh"
 
 namespace lmsae {
 
@@ -180,17 +179,28 @@ int sparse_decode_launch(const DecodeParams& p, cudaStream_t stream) {
 // ---------------------------------------------------------------------------------------------
 constexpr int DACT_THREADS = 256;
 
+// `wait_pt.world > 0`: d x_hat is the gradient buffer of the fused feature-sharded step, filled by the row owners'
+// peer stores; the kernel then waits (bounded) for every owner's flag of `epoch` itself instead of relying on a
+// separate wait launch before it.
 __global__ void __launch_bounds__(DACT_THREADS)
 sparse_dact_kernel(const int* __restrict__ idx, int B, int k, int d, const __nv_bfloat16* __restrict__ W,
-                   const __nv_bfloat16* __restrict__ dxhat, float* __restrict__ dval) {
+                   const __nv_bfloat16* dxhat /* may be peer-written: no read-only path */, float* __restrict__ dval, const PeerTable wait_pt,
+                   uint32_t epoch, int* status) {
   extern __shared__ float s_dx[];  // [d]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nvec = d / 8;
+  if (wait_pt.world > 0 && !wait_all_sources(wait_pt, kPhaseDxhat, epoch, status)) {
+    // the gradient rows never arrived: leave zeros so that nothing downstream consumes stale data
+    for (long long i = blockIdx.x * (long long)DACT_THREADS + threadIdx.x; i < (long long)B * k;
+         i += (long long)gridDim.x * DACT_THREADS)
+      dval[i] = 0.0f;
+    return;
+  }
   for (int row = blockIdx.x; row < B; row += gridDim.x) {
     __syncthreads();
     for (int v = threadIdx.x; v < nvec; v += DACT_THREADS) {
       float f[8];
-      bf16x8_to_float(__ldg(reinterpret_cast<const uint4*>(dxhat + (size_t)row * d) + v), f);
+      bf16x8_to_float(*(reinterpret_cast<const uint4*>(dxhat + (size_t)row * d) + v), f);
 #pragma unroll
       for (int i = 0; i < 8; ++i) s_dx[v * 8 + i] = f[i];
     }
@@ -200,6 +210,7 @@ sparse_dact_kernel(const int* __restrict__ idx, int B, int k, int d, const __nv_
       float dot = 0.0f;
       if (f >= 0) {
         const uint4* wrow = reinterpret_cast<const uint4*>(W + (size_t)f * d);
+#pragma unroll 4
         for (int v = lane; v < nvec; v += 32) {
           float w[8];
           bf16x8_to_float(__ldg(wrow + v), w);
@@ -215,12 +226,14 @@ sparse_dact_kernel(const int* __restrict__ idx, int B, int k, int d, const __nv_
 }
 
 int sparse_dact_launch(const int* idx, int B, int k, int d, const __nv_bfloat16* W, const __nv_bfloat16* dxhat,
-                       float* dval, cudaStream_t stream) {
+                       float* dval, const PeerTable* wait, uint32_t epoch, int* status, cudaStream_t stream) {
   if (d % 8 != 0 || (size_t)d * 4 > 160 * 1024) return (int)cudaErrorInvalidValue;
   cudaError_t e = cudaFuncSetAttribute(sparse_dact_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
   if (e != cudaSuccess) return (int)e;
   int blocks = B < 148 * 8 ? B : 148 * 8;
-  sparse_dact_kernel<<<blocks, DACT_THREADS, (size_t)d * 4, stream>>>(idx, B, k, d, W, dxhat, dval);
+  PeerTable pt{};
+  if (wait != nullptr) pt = *wait;
+  sparse_dact_kernel<<<blocks, DACT_THREADS, (size_t)d * 4, stream>>>(idx, B, k, d, W, dxhat, dval, pt, epoch, status);
   return (int)cudaGetLastError();
 }
 
@@ -432,6 +445,7 @@ __global__ void csc_fill_kernel(const int* __restrict__ idx, long long n, int F,
 
 int csc_build_launch(const int* idx, long long n, int F, int* counts, int* offsets, int* cursor, int* entries,
                      int* block_sums_buf, cudaStream_t stream) {
+  if (n < 0 || n > 2147483647LL || F <= 0) return (int)cudaErrorInvalidValue;  // positions are stored as 32-bit ints
   cudaError_t e = cudaMemsetAsync(counts, 0, (size_t)F * sizeof(int), stream);
   if (e != cudaSuccess) return (int)e;
   const int threads = 256;
@@ -485,8 +499,12 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const float gmul = p.grad_mul != nullptr ? *p.grad_mul : 1.0f;
   float gsq_local = 0.0f;
+  // An earlier kernel of this step gave up on a bounded wait (its inputs never arrived): the codes and gradient rows
+  // this kernel would consume are stale, so the parameters and moments stay as they are until the host has seen the
+  // status word.
+  const bool skip = p.status != nullptr && *reinterpret_cast<const volatile int*>(p.status) != 0;
 
-  for (int f = p.f_begin + blockIdx.x; f < p.f_end; f += gridDim.x) {
+  for (int f = p.f_begin + blockIdx.x; f < p.f_end && !skip; f += gridDim.x) {
     const int e0 = p.offsets[f], e1 = p.offsets[f + 1];
     float bias_g = 0.0f;
     float norm_sq = 0.0f;
@@ -494,7 +512,8 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
       const int c = c0 + threadIdx.x * 4;
       const bool in = c < p.d;  // d % 4 == 0
       float gD[4] = {0.f, 0.f, 0.f, 0.f}, gE[4] = {0.f, 0.f, 0.f, 0.f};
-      const size_t o = (size_t)f * p.d + (in ? c : 0);
+      const size_t o = (size_t)f * p.d + (in ? c : 0);                  // parameters, shadows, dense gradient outputs
+      const size_t os = (size_t)(f - p.state_f0) * p.d + (in ? c : 0);  // moments
       for (int e = e0; e < e1; ++e) {
         const int ent = p.entries[e];
         const int row = ent / p.k;
@@ -527,22 +546,32 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
       if (p.gE_out != nullptr) *reinterpret_cast<float4*>(p.gE_out + o) = make_float4(gE[0], gE[1], gE[2], gE[3]);
       if (p.update) {
         // all six streams of this chunk are requested before the first is used (96 bytes in flight per thread)
-        float4 w = ldcs4(p.WD + o), m = ldcs4(p.mD + o), v = ldcs4(p.vD + o);
-        float4 we = ldcs4(p.WE + o), me = ldcs4(p.mE + o), ve = ldcs4(p.vE + o);
+        float4 w = ldcs4(p.WD + o), m = ldcs4(p.mD + os), v = ldcs4(p.vD + os);
+        float4 we = ldcs4(p.WE + o), me = ldcs4(p.mE + os), ve = ldcs4(p.vE + os);
         {
           adam_elem(w.x, m.x, v.x, gD[0], p.h); adam_elem(w.y, m.y, v.y, gD[1], p.h);
           adam_elem(w.z, m.z, v.z, gD[2], p.h); adam_elem(w.w, m.w, v.w, gD[3], p.h);
-          stcs4(p.WD + o, w); stcs4(p.mD + o, m); stcs4(p.vD + o, v);
+          stcs4(p.WD + o, w); stcs4(p.mD + os, m); stcs4(p.vD + os, v);
           norm_sq += w.x * w.x + w.y * w.y + w.z * w.z + w.w * w.w;
           uint2 sh; sh.x = pack_bf16x2(w.x, w.y); sh.y = pack_bf16x2(w.z, w.w);
-          *reinterpret_cast<uint2*>(p.WD_bf16 + o) = sh;
+          if (p.n_pub > 0) {
+            for (int q = 0; q < p.n_pub; ++q)
+              *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.pub.base[q] + p.pub_wd_off) + o) = sh;
+          } else {
+            *reinterpret_cast<uint2*>(p.WD_bf16 + o) = sh;
+          }
         }
         {
           adam_elem(we.x, me.x, ve.x, gE[0], p.h); adam_elem(we.y, me.y, ve.y, gE[1], p.h);
           adam_elem(we.z, me.z, ve.z, gE[2], p.h); adam_elem(we.w, me.w, ve.w, gE[3], p.h);
-          stcs4(p.WE + o, we); stcs4(p.mE + o, me); stcs4(p.vE + o, ve);
+          stcs4(p.WE + o, we); stcs4(p.mE + os, me); stcs4(p.vE + os, ve);
           uint2 sh; sh.x = pack_bf16x2(we.x, we.y); sh.y = pack_bf16x2(we.z, we.w);
-          *reinterpret_cast<uint2*>(p.WE_bf16 + o) = sh;
+          if (p.n_pub > 0) {
+            for (int q = 0; q < p.n_pub; ++q)
+              *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.pub.base[q] + p.pub_we_off) + o) = sh;
+          } else {
+            *reinterpret_cast<uint2*>(p.WE_bf16 + o) = sh;
+          }
         }
       }
     }
@@ -550,9 +579,14 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
       bias_g *= gmul;
       gsq_local += bias_g * bias_g;
       if (p.update && p.bE != nullptr) {
-        float b = p.bE[f], m = p.mbE[f], v = p.vbE[f];
+        float b = p.bE[f], m = p.mbE[f - p.state_f0], v = p.vbE[f - p.state_f0];
         adam_elem(b, m, v, bias_g, p.h);
-        p.bE[f] = b; p.mbE[f] = m; p.vbE[f] = v;
+        p.mbE[f - p.state_f0] = m; p.vbE[f - p.state_f0] = v;
+        if (p.n_pub > 0) {
+          for (int q = 0; q < p.n_pub; ++q) reinterpret_cast<float*>(p.pub.base[q] + p.pub_be_off)[f] = b;
+        } else {
+          p.bE[f] = b;
+        }
       }
     }
     if (p.update && p.dec_norm != nullptr) {
@@ -563,7 +597,13 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
       if (warp == 0) {
         float t = lane < GA_THREADS / 32 ? s_red[lane] : 0.0f;
         t = warp_sum(t);
-        if (lane == 0) p.dec_norm[f] = sqrtf(t);
+        if (lane == 0) {
+          if (p.n_pub > 0) {
+            for (int q = 0; q < p.n_pub; ++q) reinterpret_cast<float*>(p.pub.base[q] + p.pub_norm_off)[f] = sqrtf(t);
+          } else {
+            p.dec_norm[f] = sqrtf(t);
+          }
+        }
       }
     }
   }
@@ -577,6 +617,8 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
       if (lane == 0) atomicAdd(p.grad_sq_sum, t);
     }
   }
+  // published even when the update was skipped, so that the replicas waiting for this rank's rows do not time out too
+  if (p.n_pub > 0 && p.update) signal_peers_when_grid_done(p.pub, kPhaseParams, p.pub_epoch, p.pub_done);
 }
 
 int sparse_grad_adam_launch(const GradAdamParams& p, cudaStream_t stream) {
@@ -584,6 +626,8 @@ int sparse_grad_adam_launch(const GradAdamParams& p, cudaStream_t stream) {
   const int rows = p.f_end - p.f_begin;
   if (rows <= 0) return 0;
   // CTAs are persistent (grid-stride over feature rows): the grid size sets how many share an SM
+  if (p.n_pub < 0 || p.n_pub > kMaxPeers || (p.n_pub > 0 && p.n_pub != p.pub.world)) return (int)cudaErrorInvalidValue;
+  if (p.state_f0 < 0 || p.state_f0 > p.f_begin) return (int)cudaErrorInvalidValue;
   const int cap = (p.ctas_per_sm >= 1 && p.ctas_per_sm <= 4) ? 148 * p.ctas_per_sm : 148 * 8;
   int blocks = rows < cap ? rows : cap;
   sparse_grad_adam_kernel<<<blocks, GA_THREADS, 0, stream>>>(p);
@@ -619,8 +663,9 @@ int colsum_bf16_launch(const __nv_bfloat16* a, int rows, int d, float* out, cuda
 __global__ void __launch_bounds__(256)
 adam_flat_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
                  long long n, AdamHyper h, const float* __restrict__ grad_mul, __nv_bfloat16* __restrict__ shadow,
-                 float* __restrict__ grad_sq_sum, int update) {
+                 float* __restrict__ grad_sq_sum, int update, const int* __restrict__ status) {
   __shared__ float s_gsq[8];
+  if (status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0) return;  // see sparse_grad_adam_kernel
   const float gmul = grad_mul != nullptr ? *grad_mul : 1.0f;
   float gsq = 0.0f;
   for (long long i = blockIdx.x * 256LL + threadIdx.x; i < n; i += (long long)gridDim.x * 256) {
@@ -646,11 +691,11 @@ adam_flat_kernel(float* __restrict__ p, const float* __restrict__ g, float* __re
 }
 
 int adam_flat_launch(float* p, const float* g, float* m, float* v, long long n, AdamHyper h, const float* grad_mul,
-                     __nv_bfloat16* shadow, float* grad_sq_sum, int update, cudaStream_t stream) {
+                     __nv_bfloat16* shadow, float* grad_sq_sum, int update, const int* status, cudaStream_t stream) {
   long long blocks = (n + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (blocks < 1) blocks = 1;
-  adam_flat_kernel<<<(int)blocks, 256, 0, stream>>>(p, g, m, v, n, h, grad_mul, shadow, grad_sq_sum, update);
+  adam_flat_kernel<<<(int)blocks, 256, 0, stream>>>(p, g, m, v, n, h, grad_mul, shadow, grad_sq_sum, update, status);
   return (int)cudaGetLastError();
 }
 

@@ -53,10 +53,14 @@ class AuxK:
 
 class FusedTopKSAEStep:
     def __init__(self, sae, betas: tuple[float, float] = (0.9, 0.999), eps: float = 1e-8, comm=None,
-                 overlap_chunks: int | None = None):
+                 overlap_chunks: int | None = None, dp_comm=None):
         """``comm``: a ``parallel.symm.SymmComm`` over the model group switches the two cross-shard exchanges
-        from NCCL collectives to the fused peer-memory kernels. ``overlap_chunks``: number of feature chunks of the
-        update / next-encode overlap (default: environment variable ``LMSAE_OVERLAP_CHUNKS``, else 1 = off)."""
+        from NCCL collectives to the fused peer-memory kernels. ``dp_comm``: a ``parallel.symm.DataParallelComm`` over
+        the data group: the replicas exchange their rows in one peer-store kernel and the optimizer state is sharded by
+        feature row (each replica updates ``F / dp`` rows and stores the new bf16 rows, norms and biases into every
+        replica; the fp32 master rows of the other replicas' shares go stale until ``sync_params``).
+        ``overlap_chunks``: number of feature chunks of the update / next-encode overlap (default: environment variable
+        ``LMSAE_OVERLAP_CHUNKS``, else 1 = off)."""
         cfg = sae.cfg
         self.sae = sae
         self.mesh = sae.device_mesh
@@ -66,6 +70,7 @@ class FusedTopKSAEStep:
         self.tp_group = mesh_group(self.mesh, "model")
         self.dp_group = mesh_group(self.mesh, "data")
         self.comm = comm  # optional peer-memory communicator (parallel.symm.SymmComm) for the model group
+        self.dp_comm = dp_comm if self.dp > 1 else None
         self.betas, self.eps = betas, eps
         self.use_gate = cfg.sparsity_include_decoder_norm
         self.batch_level = cfg.act_fn == "batchtopk"
@@ -79,13 +84,27 @@ class FusedTopKSAEStep:
         self.F, self.d = F, d
         dev = self.WD.device
         z = lambda *s: torch.zeros(*s, dtype=torch.float32, device=dev)  # noqa: E731
-        self.WE_bf16 = torch.empty(F, d, dtype=torch.bfloat16, device=dev)
-        self.WD_bf16 = torch.empty(F, d, dtype=torch.bfloat16, device=dev)
-        self.dec_norm = torch.empty(F, dtype=torch.float32, device=dev)
+        if self.dp_comm is not None:
+            # shadows, norms and the encoder bias live in the data group's symmetric buffer: the replica that updates a
+            # feature row stores the new values into every replica's copy
+            assert self.dp_comm.F == F and self.dp_comm.d == d and F % self.dp == 0
+            views = self.dp_comm.param_views()
+            self.WE_bf16, self.WD_bf16, self.dec_norm = views["WE_bf16"], views["WD_bf16"], views["dec_norm"]
+            views["bE"].copy_(self.bE)
+            sae.b_E.data = views["bE"]
+            self.bE = sae.b_E.data
+            self.own_rows = self.dp_comm.own_rows()
+        else:
+            self.WE_bf16 = torch.empty(F, d, dtype=torch.bfloat16, device=dev)
+            self.WD_bf16 = torch.empty(F, d, dtype=torch.bfloat16, device=dev)
+            self.dec_norm = torch.empty(F, dtype=torch.float32, device=dev)
+            self.own_rows = (0, F)
+        Fo = self.own_rows[1] - self.own_rows[0]  # rows whose optimizer state this rank holds
         self.state = {
-            "W_E": (z(F, d), z(F, d)), "W_D": (z(F, d), z(F, d)), "b_E": (z(F), z(F)),
+            "W_E": (z(Fo, d), z(Fo, d)), "W_D": (z(Fo, d), z(Fo, d)), "b_E": (z(Fo), z(Fo)),
             "b_D": (z(d), z(d)) if self.bD is not None else None,
         }  # fmt: skip
+        self._masters_stale = False
         self.groups: K.FeatureGroups | None = None
         self.loss_sum = z(1)
         self.aux_sum = z(1)
@@ -192,27 +211,55 @@ class FusedTopKSAEStep:
         K.row_norm_shadow(self.WD, self.dec_norm, self.WD_bf16)
         K.row_norm_shadow(self.WE, None, self.WE_bf16)
 
+    def _full_rows(self, t: torch.Tensor) -> torch.Tensor:
+        """A row-sharded state tensor (this replica's feature rows) as the full local-shard tensor (collective)."""
+        if self.dp_comm is None:
+            return t
+        out = torch.empty(self.dp * t.shape[0], *t.shape[1:], dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(out, t.contiguous(), group=self.dp_group)
+        return out
+
+    def sync_params(self) -> None:
+        """With the optimizer state sharded over replicas, each replica's fp32 master rows of the OTHER replicas' shares
+        are stale between steps (only the bf16 shadows, norms and biases are published every step). This gathers the
+        current master rows into every replica's ``W_E`` / ``W_D`` (collective; call before saving or inspecting the
+        parameters)."""
+        self.join()
+        if self.dp_comm is None or not self._masters_stale:
+            return
+        lo, hi = self.own_rows
+        self.WD.copy_(self._full_rows(self.WD[lo:hi]))
+        self.WE.copy_(self._full_rows(self.WE[lo:hi]))
+        self._masters_stale = False
+
     def optimizer_state(self) -> dict:
-        """Adam state in logical parameter shapes (W_E as [d, F])."""
+        """Adam state in logical parameter shapes (W_E as [d, F]); collective when the state is sharded over replicas."""
         self.join()
         out = {"step": self.t}
         for name, st in self.state.items():
             if st is None:
                 continue
             m, v = st
+            if name != "b_D":
+                m, v = self._full_rows(m), self._full_rows(v)
             out[name] = {"exp_avg": m.t() if name == "W_E" else m, "exp_avg_sq": v.t() if name == "W_E" else v}
         return out
 
     def load_optimizer_state(self, sd: dict) -> None:
         self.join()
         self.t = int(sd["step"])
+        lo, hi = self.own_rows
         for name, st in self.state.items():
             if st is None or name not in sd:
                 continue
             m, v = st
             src_m, src_v = sd[name]["exp_avg"], sd[name]["exp_avg_sq"]
-            m.copy_(src_m.t() if name == "W_E" else src_m)
-            v.copy_(src_v.t() if name == "W_E" else src_v)
+            if name == "W_E":
+                src_m, src_v = src_m.t(), src_v.t()
+            if name != "b_D" and src_m.shape[0] != m.shape[0]:
+                src_m, src_v = src_m[lo:hi], src_v[lo:hi]
+            m.copy_(src_m)
+            v.copy_(src_v)
 
     # ---- the step ----------------------------------------------------------------------------
     def _candidates_chunked(self, x: torch.Tensor, k: int, gate) -> tuple[torch.Tensor, torch.Tensor]:
@@ -246,14 +293,16 @@ class FusedTopKSAEStep:
 
     def encode(self, x: torch.Tensor, k: int, _in_step: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
         """Sparse codes (idx, act) [B, k] of bf16 inputs ``x`` [B, d] over this rank's features; under
-        feature sharding only globally selected entries survive."""
+        feature sharding only globally selected entries survive, packed from slot 0 of every row on."""
         gate = self.dec_norm if self.use_gate else None
         if self.batch_level:
             return self._encode_batch_level(x, k, gate)
         chunked = _in_step and len(self.chunks) > 1 and k <= 64 and x.is_cuda
         if not chunked:
             self.join()
-        if k <= 64 and x.is_cuda:
+        fused_topk = k <= 64 and x.is_cuda
+        use_comm = self.tp > 1 and self.comm is not None and x.shape[0] == self.comm.B and k <= self.comm.k_max
+        if fused_topk:
             if chunked:
                 cv, ci = self._candidates_chunked(x, k, gate)
             else:
@@ -261,6 +310,14 @@ class FusedTopKSAEStep:
             self._mark("encoder_gemm_topk")
             if self.tp == 1:
                 return K.topk_merge(cv, ci, k, gate)
+            if use_comm:
+                # local merge whose epilogue is the all-gather of the shard's list, then the merge over shards, which
+                # waits for the peers' flags inside its kernel
+                self.comm.merge_push(cv, ci, k)
+                self._mark("local_merge_push")
+                out = self.comm.merge_shards(k, gate)
+                self._mark("merge_shards")
+                return out
             idx_l, g_l = K.topk_merge(cv, ci, k, gate, emit_gated=True)
             self._mark("local_merge")
         else:
@@ -269,17 +326,16 @@ class FusedTopKSAEStep:
             if self.tp == 1:
                 return idx_l, act_l
             g_l = act_l * gate[idx_l.clamp_min(0).long()] if gate is not None else act_l
-        if self.comm is not None and x.shape[0] == self.comm.B and k <= self.comm.k_max:
-            all_g, all_i = self.comm.exchange_candidates(g_l, idx_l)
-            self._mark("exchange_candidates")
-        else:
-            B = x.shape[0]
-            all_g = torch.empty(self.tp * B, k, dtype=torch.float32, device=x.device)
-            all_i = torch.empty(self.tp * B, k, dtype=torch.int32, device=x.device)
-            dist.all_gather_into_tensor(all_g, g_l.contiguous(), group=self.tp_group)
-            dist.all_gather_into_tensor(all_i, idx_l.contiguous(), group=self.tp_group)
-            all_g = all_g.view(self.tp, B, k).permute(1, 0, 2).reshape(B, self.tp * k).contiguous()
-            all_i = all_i.view(self.tp, B, k).permute(1, 0, 2).reshape(B, self.tp * k).contiguous()
+            if use_comm:
+                self.comm.push_candidates(g_l, idx_l)
+                return self.comm.merge_shards(k, gate)
+        B = x.shape[0]
+        all_g = torch.empty(self.tp * B, k, dtype=torch.float32, device=x.device)
+        all_i = torch.empty(self.tp * B, k, dtype=torch.int32, device=x.device)
+        dist.all_gather_into_tensor(all_g, g_l.contiguous(), group=self.tp_group)
+        dist.all_gather_into_tensor(all_i, idx_l.contiguous(), group=self.tp_group)
+        all_g = all_g.view(self.tp, B, k).permute(1, 0, 2).reshape(B, self.tp * k).contiguous()
+        all_i = all_i.view(self.tp, B, k).permute(1, 0, 2).reshape(B, self.tp * k).contiguous()
         return K.topk_merge(all_g, all_i, k, gate, own=(self.tp_rank * k, (self.tp_rank + 1) * k))
 
     def _encode_batch_level(self, x: torch.Tensor, k: int, gate) -> tuple[torch.Tensor, torch.Tensor]:
@@ -323,19 +379,21 @@ class FusedTopKSAEStep:
         B = x.shape[0]
         n_global = n_tokens_global if n_tokens_global is not None else B * self.dp
         grad_scale = 2.0 / n_global
-        use_comm = self.comm is not None and B == self.comm.B and k <= self.comm.k_max and not self.batch_level
-        if use_comm:
-            self.comm.next_epoch()
-        overlap = len(self.chunks) > 1 and k <= 64 and grad_mul is None and not want_grad_norm and not clip_grad_norm
+        use_comm = self.tp > 1 and self.comm is not None and B == self.comm.B and k <= self.comm.k_max and not self.batch_level
+        sharded = self.dp_comm is not None
+        overlap = len(self.chunks) > 1 and k <= 64 and grad_mul is None and not want_grad_norm and not clip_grad_norm and not sharded
         self._mark("begin")
+        if self.dp_comm is not None:
+            self.dp_comm.wait_params()  # the other replicas' rows of the previous update must have landed in the shadows
         idx, act = self.encode(x, k, _in_step=overlap)
         self._mark("merge")
         self.loss_sum.zero_()
         if use_comm:
             # loss_sum collects the rows this rank owns; scale to a local-batch estimate for the return value
-            dxhat, _ = self.comm.decode_reduce_loss(idx, act, self.WD_bf16, label, self.bD, row_weight, grad_scale, self.loss_sum)
+            dxhat, _ = self.comm.decode_reduce_loss(idx, act, self.WD_bf16, label, self.bD, row_weight, grad_scale, self.loss_sum,
+                                                    compact_codes=not self.batch_level)  # fmt: skip
             self._mark("decode_reduce_loss")
-            dact = K.sparse_dact(idx, self.WD_bf16, dxhat)
+            dact = self.comm.dact(idx, self.WD_bf16)  # waits for the owners' gradient rows inside the kernel
             self._mark("dact")
         elif self.tp == 1:
             dxhat, dact, _ = K.sparse_decode_loss(idx, act, self.WD_bf16, self.bD, label, row_weight, grad_scale, self.loss_sum)
@@ -344,7 +402,11 @@ class FusedTopKSAEStep:
             dist.all_reduce(partial, group=self.tp_group)
             dxhat = K.mse_loss_grad(partial, label, self.bD, row_weight, grad_scale, self.loss_sum)
             dact = K.sparse_dact(idx, self.WD_bf16, dxhat)
-        if self.dp > 1:
+        if self.dp_comm is not None:
+            g = self.dp_comm.exchange({"x": x, "dxhat": dxhat, "idx": idx, "act": act, "dact": dact})
+            x, dxhat, idx, act, dact = g["x"], g["dxhat"], g["idx"], g["act"], g["dact"]
+            self._mark("dp_exchange_rows")
+        elif self.dp > 1:
             x, dxhat, idx, act, dact = self._gather_rows(x, dxhat, idx, act, dact)
         if self.groups is None or self.groups.entries.numel() < idx.numel():
             self.groups = K.FeatureGroups(self.F, idx.numel(), x.device)
@@ -359,11 +421,16 @@ class FusedTopKSAEStep:
         if want_grad_norm:
             self.grad_sq.zero_()
             gsq = self.grad_sq
-        sparse = lambda mul, sq, update, f_range=None, ctas_per_sm=0: K.sparse_grad_adam(  # noqa: E731
-            self.groups, act, dact, x, dxhat, self.WD, mD, vD, self.WD_bf16, self.WE, mE, vE, self.WE_bf16,
-            self.bE, mb, vb, self.dec_norm, mul, sq, lr, b1, b2, self.eps, self.t, update, f_range=f_range,
-            ctas_per_sm=ctas_per_sm,
-        )  # fmt: skip
+        def sparse(mul, sq, update, f_range=None, ctas_per_sm=0):
+            K.sparse_grad_adam(
+                self.groups, act, dact, x, dxhat, self.WD, mD, vD, self.WD_bf16, self.WE, mE, vE, self.WE_bf16,
+                self.bE, mb, vb, self.dec_norm, mul, sq, lr, b1, b2, self.eps, self.t, update,
+                f_range=f_range if not sharded else self.own_rows, ctas_per_sm=ctas_per_sm,
+                state_f0=self.own_rows[0], publish=self.dp_comm.pub_args() if sharded and update else None,
+            )  # fmt: skip
+            if sharded and update:
+                self._masters_stale = True
+
         g_bD = K.colsum_bf16(dxhat) if self.bD is not None else None
         if clip_grad_norm:
             assert grad_mul is None, "pass either a gradient factor or a clipping norm"
@@ -412,10 +479,13 @@ class FusedTopKSAEStep:
         non-zero; sharded parameters add up over the model group, the replicated decoder bias is counted once."""
         self.grad_sq.zero_()
         sparse(None, self.grad_sq, False)
-        fired = (self.groups.counts[: self.F] > 0).sum().float().reshape(1)
+        lo, hi = self.own_rows  # the rows this replica rebuilt gradients for (all of them unless the state is sharded)
+        fired = (self.groups.counts[lo:hi] > 0).sum().float().reshape(1)
         acc = torch.cat([self.grad_sq, fired * (2 * self.d + 1)])
         if self.tp > 1:
             dist.all_reduce(acc, group=self.tp_group)
+        if self.dp_comm is not None:
+            dist.all_reduce(acc, group=self.dp_group)
         if g_bD is not None:
             acc = acc + torch.stack([g_bD.square().sum(), (g_bD != 0).sum().float()])
         norm = (acc[0] / acc[1].clamp_min(1.0)).sqrt()
@@ -428,13 +498,12 @@ class FusedTopKSAEStep:
         trainer.py:428-454 of the reference project). The dead features are gathered into a compact dictionary
         first, so the second encoder pass costs ``n_dead / F`` of the main one instead of a full pass."""
         assert self.dp == 1, "the fused Aux-K step is not data parallel (use the generic path for that mesh)"
+        assert self.dp_comm is None
         self.join()
         B = x.shape[0]
         n_global = n_tokens_global if n_tokens_global is not None else B
         grad_scale = 2.0 / n_global
         gate = self.dec_norm if self.use_gate else None
-        if self.comm is not None and B == self.comm.B and k <= self.comm.k_max:
-            self.comm.next_epoch()  # the candidate exchange of encode() is the only peer-memory phase of this step
         idx, act = self.encode(x, k)
         if self.groups is None or self.groups.entries.numel() < B * (k + aux.k_aux):
             self.groups = K.FeatureGroups(self.F, B * (k + aux.k_aux), x.device)

@@ -208,8 +208,8 @@ def encoder_topk_candidates(
 
 def ref_topk_merge(cand_val, cand_idx, k: int, gate, own: tuple[int, int] | None = None, emit_gated: bool = False):
     """Plain-torch statement of ``topk_merge`` (any device): the ``k`` largest positive candidates of every row; only
-    winners whose candidate slot lies in ``own`` are kept (the rest become -1 / 0), values divided by ``gate[idx]``
-    unless ``emit_gated``."""
+    winners whose candidate slot lies in ``own`` are kept, packed in value-descending order from slot 0 on (the rest of
+    the row is -1 / 0); values divided by ``gate[idx]`` unless ``emit_gated``."""
     M, C = cand_val.shape
     lo, hi = own if own is not None else (0, C)
     score = torch.where(cand_idx >= 0, cand_val.float(), torch.full_like(cand_val, -1.0, dtype=torch.float32))
@@ -220,6 +220,9 @@ def ref_topk_merge(cand_val, cand_idx, k: int, gate, own: tuple[int, int] | None
     val = torch.where(keep, top, torch.zeros_like(top))
     if not emit_gated and gate is not None:
         val = torch.where(keep, val / gate.float()[idx.clamp_min(0).long()], val)
+    # pack the kept entries to the front, order preserved
+    order = torch.sort((~keep).to(torch.int8), dim=1, stable=True).indices
+    idx, val = torch.gather(idx, 1, order), torch.gather(val, 1, order)
     if kk < k:
         idx = torch.cat([idx, idx.new_full((M, k - kk), -1)], dim=1)
         val = torch.cat([val, val.new_zeros(M, k - kk)], dim=1)
@@ -240,7 +243,7 @@ def topk_merge(
         return ref_topk_merge(cand_val, cand_idx, k, gate, own, emit_gated)
     out_idx = torch.empty(M, k, dtype=torch.int32, device=cand_val.device)
     out_val = torch.empty(M, k, dtype=torch.float32, device=cand_val.device)
-    _ext().topk_merge(cand_val, cand_idx, M, C, k, gate, lo, hi, emit_gated, out_idx, out_val)
+    _ext().topk_merge(cand_val, cand_idx, M, C, k, gate, lo, hi, emit_gated, out_idx, out_val, 0, [], 0, None, None)
     return out_idx, out_val
 
 
@@ -362,7 +365,7 @@ def sparse_dact(idx: torch.Tensor, W: torch.Tensor, dxhat: torch.Tensor) -> torc
         dv = torch.einsum("bd,bkd->bk", dxhat.float(), W.float()[safe])
         return torch.where(idx >= 0, dv, torch.zeros_like(dv))
     dval = torch.empty(idx.shape, dtype=torch.float32, device=idx.device)
-    _ext().sparse_dact(idx, W, dxhat, dval)
+    _ext().sparse_dact(idx, W, dxhat, dval, [], 0, None)
     return dval
 
 
@@ -495,15 +498,33 @@ def sparse_grad_adam(
     dxhat_aux=None,
     k_main: int = 0,
     grad_out: tuple[torch.Tensor | None, torch.Tensor | None] = (None, None),
+    state_f0: int = 0,
+    publish: tuple[list[int], list[int], int, torch.Tensor] | None = None,
 ):
     """Rebuild the two sparse gradient rows per feature and apply Adam in the same pass (in place). ``f_range``
-    restricts the launch to feature rows ``[begin, end)`` (the CUDA path only). With ``dxhat_aux`` the code slots
-    ``>= k_main`` of every row take their output gradient from that matrix instead of ``dxhat`` (auxiliary codes)."""
+    restricts the launch to feature rows ``[begin, end)``. With ``dxhat_aux`` the code slots ``>= k_main`` of every row
+    take their output gradient from that matrix instead of ``dxhat`` (auxiliary codes). ``state_f0``: the moment arrays
+    start at that feature row (optimizer state sharded by feature row). ``publish`` = ``DataParallelComm.pub_args()``:
+    the new shadow rows, norms and biases are stored into every replica's copy. A non-zero kernel status word turns
+    the update into a no-op (CUDA path)."""
     if not WD.is_cuda:
+        if f_range is not None and tuple(f_range) != (0, groups.F):
+            lo, hi = f_range
+            sub = FeatureGroups.__new__(FeatureGroups)
+            sub.F = hi - lo
+            sub.offsets, sub.entries = groups.offsets[lo : hi + 1], groups.entries
+            sl = slice(lo, hi)
+            st = slice(lo - state_f0, hi - state_f0)
+            sparse_grad_adam(sub, act, dact, x, dxhat, WD[sl], mD[st], vD[st], WD_bf16[sl], WE[sl], mE[st], vE[st], WE_bf16[sl],
+                             bE[sl] if bE is not None else None, mbE[st] if mbE is not None else None,
+                             vbE[st] if vbE is not None else None, dec_norm[sl] if dec_norm is not None else None, grad_mul,
+                             grad_sq_sum, lr, beta1, beta2, eps, step, update, None, 0, dxhat_aux, k_main)  # fmt: skip
+            return
         idx_like = torch.full((act.numel(),), -1, dtype=torch.int64)
         off = groups.offsets.long()
-        for f in range(groups.F):
-            idx_like[groups.entries[off[f] : off[f + 1]].long()] = f
+        n_ent = int(off[groups.F] - off[0])
+        owner = torch.repeat_interleave(torch.arange(groups.F), (off[1 : groups.F + 1] - off[:groups.F]))
+        idx_like[groups.entries[int(off[0]) : int(off[0]) + n_ent].long()] = owner
         idx_like = idx_like.reshape(act.shape)
         if dxhat_aux is None:
             gD, gE, gb = ref_sparse_grads(idx_like, act, dact, x, dxhat, groups.F)
@@ -528,6 +549,7 @@ def sparse_grad_adam(
     _ext().sparse_grad_adam(
         groups.offsets, groups.entries, act, dact, x, dxhat, WD, mD, vD, WD_bf16, WE, mE, vE, WE_bf16, bE, mbE, vbE,
         dec_norm, grad_mul, grad_sq_sum, lr, beta1, beta2, eps, step, update, *(f_range if f_range is not None else (0, -1)), ctas_per_sm, dxhat_aux, k_main, grad_out[0], grad_out[1],
+        status_buffer(WD.device), state_f0, *(publish if publish is not None else ([], [], 0, None)),
     )  # fmt: skip
 
 
@@ -549,7 +571,7 @@ def adam_flat(p, g, m, v, lr, beta1, beta2, eps, step, grad_mul=None, shadow=Non
             if shadow is not None:
                 shadow.copy_(p)
         return
-    _ext().adam_flat(p, g, m, v, grad_mul, shadow, grad_sq_sum, lr, beta1, beta2, eps, step, update)
+    _ext().adam_flat(p, g, m, v, grad_mul, shadow, grad_sq_sum, lr, beta1, beta2, eps, step, update, status_buffer(p.device))
 
 
 def row_norm_shadow(W: torch.Tensor, norm: torch.Tensor | None, shadow: torch.Tensor | None) -> None:

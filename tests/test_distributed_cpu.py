@@ -244,24 +244,40 @@ def test_peer_memory_protocol_on_the_host_matches_collectives():
     re-used without a barrier), also when one rank publishes a flag late."""
     from language_model_saes_b200.parallel.host_transport import HostPeerComm
     from language_model_saes_b200.parallel.mesh import mesh_group
-    from language_model_saes_b200.parallel.symm import PHASE_PARTIAL
+    from language_model_saes_b200.parallel.symm import PHASE_CAND, PHASE_PARTIAL
 
     full = _full_model()
     xs = [(_data() + i).to(torch.bfloat16) for i in range(4)]
     mesh = build_mesh("cpu", (1, 2), ("data", "model"))
     _, want = _run_fused(_sharded_copy(full, mesh), xs, 8)  # gloo all-gather / all-reduce between the shards
     late = {"delay_flag": (PHASE_PARTIAL, 0.2)} if dist.get_rank() == 1 else None
-    comm = HostPeerComm(mesh_group(mesh, "model"), xs[0].shape[0], 8, 32, timeout_s=20.0, faults=late)
+    comm = HostPeerComm(mesh_group(mesh, "model"), xs[0].shape[0], 8, 32, timeout_s=20.0, faults=late, partial_dtype=torch.float32)
     tp = _sharded_copy(full, mesh)
     eng, got = _run_fused_comm(tp, xs, 8, comm)
-    assert comm.epoch == len(xs)
+    assert comm.epochs[PHASE_PARTIAL] == len(xs)
     # each rank reports the loss of the rows it owns: the mean over ranks is the batch loss
     dist.all_reduce(got)
     assert torch.allclose(got / 2, want, rtol=1e-4), (got / 2, want)
     ref = _sharded_copy(full, mesh)
-    _run_fused(ref, xs, 8)
+    ref_eng, _ = _run_fused(ref, xs, 8)
     assert torch.allclose(tp.W_D.data, ref.W_D.data, atol=1e-5) and torch.allclose(tp.W_E.data, ref.W_E.data, atol=1e-5)
     assert torch.allclose(tp.b_D.data, ref.b_D.data, atol=1e-5)
+    # codes and reconstruction for metrics, twice in a row between training steps: the candidate exchange then runs
+    # without the later phases of a step behind it (its landing zone alternates, its epoch advances per exchange)
+    for x in xs[:2]:
+        idx_a, act_a, xhat_a = eng.forward_dense(x, 8)
+        idx_b, act_b, xhat_b = ref_eng.forward_dense(x, 8)
+        assert torch.equal(idx_a.sort(dim=1).values, idx_b.sort(dim=1).values)
+        assert torch.allclose(xhat_a, xhat_b, atol=1e-4)
+    assert comm.epochs[PHASE_CAND] == len(xs) + 2
+    more, more_ref = eng.step(xs[0], xs[0], 8, 1e-2), ref_eng.step(xs[0], xs[0], 8, 1e-2)
+    dist.all_reduce(more)
+    assert torch.allclose(more / 2, more_ref, rtol=1e-4)
+    # partial rows in bf16 (the default on the wire): same protocol, reconstruction rounded like a bf16 all-reduce
+    comm16 = HostPeerComm(mesh_group(mesh, "model"), xs[0].shape[0], 8, 32, timeout_s=20.0)
+    _, got16 = _run_fused_comm(_sharded_copy(full, mesh), xs, 8, comm16)
+    dist.all_reduce(got16)
+    assert torch.allclose(got16 / 2, want, rtol=2e-2), (got16 / 2, want)
 
 
 @distributed_test(nproc_per_node=2, backend="gloo")
@@ -277,13 +293,20 @@ def test_peer_memory_protocol_reports_a_flag_that_never_arrives():
     x = _data().to(torch.bfloat16)
     mesh = build_mesh("cpu", (1, 2), ("data", "model"))
     rank = dist.get_rank()
-    comm = HostPeerComm(mesh_group(mesh, "model"), x.shape[0], 8, 32, timeout_s=1.0,
+    # rank 1 waits for rank 0's gradient flag, which rank 0 publishes only after its own wait has run out: give it longer
+    comm = HostPeerComm(mesh_group(mesh, "model"), x.shape[0], 8, 32, timeout_s=1.0 if rank == 0 else 20.0,
                         faults={"drop_flag": PHASE_PARTIAL} if rank == 1 else None)  # fmt: skip
-    eng = FusedTopKSAEStep(_sharded_copy(full, mesh), comm=comm)
+    sae = _sharded_copy(full, mesh)
+    eng = FusedTopKSAEStep(sae, comm=comm)
+    before = {n: p.detach().clone() for n, p in sae.named_parameters()}
     if rank == 0:
         with pytest.raises(CollectiveTimeout, match=r"phase 1 .*rank\(s\) \[1\]") as info:
             eng.step(x, x, 8, 1e-2)
         assert info.value.code == 5 and info.value.sources == [1]
+        # the step gave up before its update: parameters and moments are those of before the step
+        for n, p in sae.named_parameters():
+            assert torch.equal(p.detach(), before[n]), n
+        assert all(float(m.abs().sum()) == 0.0 for st in eng.state.values() if st is not None for m in st)
     else:
         assert torch.isfinite(eng.step(x, x, 8, 1e-2))
 

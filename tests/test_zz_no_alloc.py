@@ -64,3 +64,6 @@ def test_no_alloc_entry_point_rejects_oversized_problems():
     too_many = (1 << 20) + 1
     rc = fn(idx.data_ptr(), idx.numel(), too_many, out.data_ptr(), out.data_ptr(), torch.cuda.current_stream().cuda_stream)
     assert rc != 0
+    # positions are stored as 32-bit integers: more entries than INT_MAX are refused before anything is launched
+    rc = fn(idx.data_ptr(), (1 << 31) + 5, 8, out.data_ptr(), out.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc != 0
