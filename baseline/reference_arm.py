@@ -122,10 +122,8 @@ def run_reference(args, emit, synthetic_batches, ClockSampler, c):
         emit({
             "impl": "reference", "metric": "SAE train tokens/s (d4096 x 131072 TopK k50)", "value": K * B / (ms / 1e3),
             "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "bf16 autocast, fp32 parameters", "data": "synthetic",
-            "config": {"model": "reference SparseAutoEncoder TopK d_model 4096, d_sae 131072, k 50, torch Adam lr 2e-4",
-                       "global_batch": B, "seq_len": 1, "parallelism": f"tp{world}",
-                       "path": "llamascopium.Trainer.fit, skip_metrics_calculation=True"},
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": c["config"], "path": "llamascopium.Trainer.fit(SparseAutoEncoder), skip_metrics_calculation=True",
             "clocks": clocks,
             "e2e": {"value": K * B / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms / K,
                     "h2d_bytes_per_step": B * D * 2, "d2h_bytes_per_step": 4},

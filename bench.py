@@ -153,6 +153,52 @@ def emit(rec: dict):
     print(json.dumps(rec), flush=True)
 
 
+def bench_config(world: int) -> dict:
+    """The benchmark configuration as both arms report it (identical keys and values)."""
+    return {"model": f"TopK SAE d_model {D_MODEL}, d_sae {D_MODEL * EXPANSION}, k {TOP_K}, Adam lr {LR:g}, fp32 parameters, bf16 autocast",
+            "global_batch": BATCH, "seq_len": 1, "parallelism": f"tp{world}",
+            "l2": f"inputs rotate through {POOL} batches ({POOL * BATCH * D_MODEL * 2 >> 20} MiB) > L2; weights 2 x 2.1 GB"}  # fmt: skip
+
+
+def measured_peaks() -> dict:
+    """Roofline denominators measured on this pool (MEASURED_PEAKS.json beside this file), else the stated fallback."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops_sustained"], "nvlink_gbs": 770.0, "source": "measured"}
+    except Exception:  # noqa: BLE001
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1400.0, "nvlink_gbs": 770.0, "source": "fallback"}
+
+
+def roofline(phases: dict, world: int, partial_itemsize: int) -> dict:
+    """Achieved fraction of the roofline of every fused phase of the step: bound = the slowest of its FLOPs at the
+    measured tensor throughput, its NVLink bytes (per rank and direction) at the measured peer-copy rate, and its local
+    memory bytes at the measured copy bandwidth; fraction = bound / measured phase time (max over ranks)."""
+    pk = measured_peaks()
+    F_l, B, d, k, N = D_MODEL * EXPANSION // world, BATCH, D_MODEL, TOP_K, world
+    far = (N - 1) / N
+    model = {
+        "encoder_gemm_topk": {"flops": 2.0 * B * d * F_l, "hbm": F_l * d * 2 + B * d * 2},
+        "local_merge_push": {"nvlink": B * k * 8 * (N - 1), "hbm": B * 4 * 64 * 8},
+        "decode_reduce_loss": {"nvlink": far * B * d * partial_itemsize + far * B * d * 2,
+                               "hbm": B * (k / N) * d * 2 + 2 * B * d * partial_itemsize + B * d * 2 / N},
+        "dact": {"hbm": B * (k / N + 1) * d * 2},
+        "sparse_grad_adam": {"hbm": 26.0 * 2 * F_l * d},
+    }  # fmt: skip
+    out = {}
+    for name, m in model.items():
+        if name not in phases:
+            continue
+        t = phases[name][1]
+        bounds = {"tensor": m.get("flops", 0) / (pk["bf16_tflops"] * 1e12) * 1e3,
+                  "nvlink": m.get("nvlink", 0) / (pk["nvlink_gbs"] * 1e9) * 1e3,
+                  "hbm": m.get("hbm", 0) / (pk["hbm_gbs"] * 1e9) * 1e3}  # fmt: skip
+        which = max(bounds, key=bounds.get)
+        out[name] = {"ms": round(t, 4), "bound_ms": round(bounds[which], 4), "bound_by": which,
+                     "frac_of_" + pk["source"]: round(bounds[which] / t, 3) if t > 0 else None}  # fmt: skip
+    return out
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -188,7 +234,8 @@ def run_ours(args):
     sae.set_dataset_average_activation_norm({cfg.hook_point_in: D_MODEL**0.5})
 
     host = synthetic_batches(POOL)
-    tokens = torch.zeros(BATCH, dtype=torch.long)
+    tokens = torch.zeros(BATCH, dtype=torch.long).pin_memory()
+    mask = torch.ones(BATCH, dtype=torch.bool).pin_memory()
     W, Ksteps = args.warmup, args.steps
 
     def barrier():
@@ -208,6 +255,8 @@ def run_ours(args):
         engine.step(pool[i % POOL], pool[i % POOL], TOP_K, LR)
     engine.join()  # the update of a step runs on its own stream: fold it back before timing starts
     K.check_status(dev)
+    if comm is not None:
+        comm.stats.reset()
     sampler = ClockSampler(local)
     sampler.start()
     gc.collect()
@@ -234,8 +283,20 @@ def run_ours(args):
     per_step = torch.tensor([a.elapsed_time(b) for a, b in zip([start] + marks_ev[:-1], marks_ev)], device=dev, dtype=torch.float64)
     K.check_status(dev)
     final_loss = float(loss)
+    # time the kernels of the timed steps spent in bounded waits for their peers' flags (device counters, block 0 of every
+    # waiting kernel), converted with the SM clock sampled during the region: the communication the step could not hide
+    exposed = None
+    if comm is not None:
+        waits = comm.stats.read(float(clocks.get("sm_mhz") or clocks.get("sm_max_mhz") or 1965.0))
+        ex = torch.tensor([sum(v["ms"] for v in waits.values()) / Ksteps] + [waits.get(n, {"ms": 0.0})["ms"] / Ksteps for n in ("candidates", "partial rows", "gradient rows")],
+                          device=dev, dtype=torch.float64)  # fmt: skip
+        dist.all_reduce(ex, op=dist.ReduceOp.MAX)
+        exposed = {"total": round(float(ex[0]), 4), "candidates": round(float(ex[1]), 4), "partial_rows": round(float(ex[2]), 4),
+                   "gradient_rows": round(float(ex[3]), 4)}  # fmt: skip
+    partial_itemsize = comm.partial_dtype.itemsize if comm is not None else 4
+    step_multicast = bool(comm is not None and comm.use_multicast)
     phases = None
-    if os.environ.get("LMSAE_BENCH_PHASES", "0") == "1":  # diagnostics, after and outside the timed region
+    if os.environ.get("LMSAE_BENCH_PHASES", "1") == "1":  # diagnostics, after and outside the timed region
         engine.start_phase_timing()
         for i in range(Ksteps):
             engine.step(pool[i % POOL], pool[i % POOL], TOP_K, LR)
@@ -247,7 +308,9 @@ def run_ours(args):
             dist.all_reduce(vals, op=dist.ReduceOp.MAX)
             dist.all_reduce(lo, op=dist.ReduceOp.MIN)
         phases = {n: [round(a, 4), round(b, 4)] for n, a, b in zip(names, lo.tolist(), vals.tolist())}  # [min, max] over ranks
-    collectives = "none" if world == 1 else ("fused peer-memory kernels" if comm is not None else "nccl")
+    collectives = "none" if world == 1 else ("nccl" if comm is None else
+                                             "fused peer-memory kernels, " + ("multimem through the switch" if step_multicast else "peer loads/stores")
+                                             + (", bf16 partial rows" if partial_itemsize == 2 else ", fp32 partial rows"))  # fmt: skip
     del engine, pool, comm
     torch.cuda.empty_cache()
 
@@ -261,7 +324,7 @@ def run_ours(args):
             if i == W + 1:
                 barrier()
                 marks["t0"] = time.perf_counter()
-            yield {cfg.hook_point_in: host[i % POOL], "tokens": tokens}
+            yield {cfg.hook_point_in: host[i % POOL], "tokens": tokens, "mask": mask}
 
     with tempfile.TemporaryDirectory() as tmp:
         tcfg = TrainerConfig(total_training_tokens=(W + Ksteps) * BATCH, lr=LR, lr_warm_up_steps=0, lr_cool_down_steps=0,
@@ -288,18 +351,17 @@ def run_ours(args):
             "metric": "SAE train tokens/s (d4096 x 131072 TopK k50)", "value": value, "unit": "tokens/s",
             "n_gpus": world, "steps": Ksteps, "warmup": W, "ms_per_step": ms / Ksteps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"model": "TopK SAE d_model 4096, d_sae 131072, k 50, Adam lr 2e-4, fp32 master weights + bf16 compute",
-                       "global_batch": BATCH, "seq_len": 1, "parallelism": f"tp{world}",
-                       "collectives": collectives,
-                       "l2": f"inputs rotate through {POOL} batches (256 MiB) > L2; weights 2 x 2.1 GB"},
+            "config": bench_config(world), "collectives": collectives,
             "clocks": clocks,
             "e2e": {"value": Ksteps * BATCH / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms / Ksteps,
                     # every rank copies 1/N of the activation rows (then NVLink all-gather) and the whole token-id vector
-                    "h2d_bytes_per_step": BATCH * D_MODEL * 2 + world * BATCH * 8, "d2h_bytes_per_step": 4 * world,
+                    "h2d_bytes_per_step": BATCH * D_MODEL * 2 + world * BATCH * 9, "d2h_bytes_per_step": 4 * world,
                     "api": "Trainer.fit(sae, stream of pinned host batches): copy of batch i+1 overlaps step i, each rank copies "
                            "1/N of the rows over PCIe and all-gathers them over NVLink; the loss of every step is copied to pinned host memory "
                            "on every rank and read one step later, so the host runs one step ahead of the device"},
-            "gpu_launches": launches, "host_issue_ms_per_step": round(host_issue_ms, 4), "step_ms": step_ms, **({"phase_ms_min_max_over_ranks": phases} if phases else {}), "final_loss": final_loss, "impl": "ours",
+            "gpu_launches": launches, "host_issue_ms_per_step": round(host_issue_ms, 4), "step_ms": step_ms, **({"phase_ms_min_max_over_ranks": phases, "roofline": roofline(phases, world, partial_itemsize)} if phases else {}),
+            **({"exposed_comm_ms_per_step": exposed["total"], "exposed_comm_ms_per_step_by_phase": exposed} if exposed else {"exposed_comm_ms_per_step": 0.0}),
+            "final_loss": final_loss, "impl": "ours",
             "package": lm.__name__,
         })  # fmt: skip
     if world > 1:
@@ -312,7 +374,8 @@ def main():
         from baseline.reference_arm import run_reference
 
         run_reference(args, emit, synthetic_batches, ClockSampler,
-                      dict(d_model=D_MODEL, expansion=EXPANSION, top_k=TOP_K, batch=BATCH, lr=LR, pool=POOL))
+                      dict(d_model=D_MODEL, expansion=EXPANSION, top_k=TOP_K, batch=BATCH, lr=LR, pool=POOL,
+                           config=bench_config(int(os.environ.get("WORLD_SIZE", "1")))))
     else:
         run_ours(args)
 

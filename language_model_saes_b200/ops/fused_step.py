@@ -509,7 +509,7 @@ class FusedTopKSAEStep:
             self.groups = K.FeatureGroups(self.F, B * (k + aux.k_aux), x.device)
         # dead statistics first (they include this batch), from the per-feature fire counts of the main codes
         self.groups.build(idx)
-        n_valid = B if row_weight is None else row_weight.sum()
+        n_valid = B if row_weight is None else (row_weight > 0).sum()  # the weights may carry a normalisation factor
         self.main_counts = self.groups.counts[: self.F].clone()  # fire counts of the real codes (for metrics)
         is_dead = aux.update(self.main_counts, n_valid)
         dead_idx = is_dead.nonzero().squeeze(-1)

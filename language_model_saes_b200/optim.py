@@ -58,6 +58,13 @@ def schedule_lambda(name: str | None, **kw: Any):
         return f
     if name == "linearwarmupdecay":
         return lambda s: (s + 1) / warm if s < warm else (total - s) / (total - warm)
+    if name == "cosineannealing":
+        # closed form of torch's CosineAnnealingLR(T_max=training_steps, eta_min=lr_end) when nothing else touches the
+        # rate: eta_min + (base - eta_min) * (1 + cos(pi * s / T_max)) / 2, as a factor of the base rate
+        eta_min, base = kw.get("lr_end", 0.0), kw.get("base_lr")
+        assert eta_min == 0.0 or base, "a non-zero lr_end needs base_lr to express the schedule as a factor"
+        floor = eta_min / base if base else 0.0
+        return lambda s: floor + (1 - floor) * 0.5 * (1 + math.cos(math.pi * s / total))
     if name == "cosineannealingwarmup":
         end = kw.get("lr_end", 0.0)
 

@@ -168,6 +168,7 @@ class _DevicePrefetcher:
         except StopIteration:
             self._ready, self._exhausted = None, True
             return
+        batch = Trainer._mask_summary(batch)
         if not any(isinstance(v, Tensor) and v.device.type == "cpu" for v in batch.values()):
             self._ready = (batch, None)
             return
@@ -274,12 +275,14 @@ class Trainer:
         self._lr_lambda: Callable[[int], float] | None = None
         self._pending_optimizer_state: dict | None = None
         self._interval: dict[str, Any] = {}
+        self._tokens_on_device: Tensor | None = None
 
     # ---- checkpoints -------------------------------------------------------------------------
     def save_checkpoint(self, sae: SparseDictionary, checkpoint_path: Path | str) -> None:
         """Model + optimizer + scheduler + trainer state under ``<path>/checkpoints/step_<N>/``. Beyond the
         reference's files it also writes ``extra_state.pt`` (dead-feature counters and RNG state), which
         older readers ignore."""
+        self._before_parameters_leave(sae)
         ckpt_dir = Path(checkpoint_path) / "checkpoints" / f"step_{self.cur_step}"
         primary = is_primary_rank(sae.device_mesh)
         if primary:
@@ -392,6 +395,19 @@ class Trainer:
             sd = torch.load(opt_path, map_location="cpu", weights_only=False)
             if sd.get("format") == "by_name":
                 trainer._load_optimizer_state(sae, sd)
+            elif trainer.fused is not None:
+                # a torch-format state_dict (the reference's layout): its entries are keyed by parameter position in the
+                # param groups, which are in named_parameters order here
+                names = [n for n, _ in sae.named_parameters()]
+                order = [i for g in sd.get("param_groups", []) for i in g["params"]]
+                by_name = {"format": "by_name", "state": {}}
+                for pos, i in enumerate(order):
+                    if i in sd["state"] and pos < len(names):
+                        by_name["state"][names[pos]] = sd["state"][i]
+                if by_name["state"]:
+                    trainer._load_optimizer_state(sae, by_name)
+                else:
+                    logger.warning("optimizer.pt holds no per-parameter state that maps onto this model: the fused path starts from zero moments")
             elif trainer.optimizer is not None:
                 trainer.optimizer.load_state_dict(sd)
         sched_path = ckpt_dir / "scheduler.pt"
@@ -460,8 +476,24 @@ class Trainer:
                     comm = SymmComm(mesh_group(sae.device_mesh, "model"), torch.device(sae.cfg.device), rows, k_max, sae.cfg.d_model)
                 except Exception as e:  # noqa: BLE001
                     logger.warning(f"peer-memory collectives unavailable ({e}); using NCCL collectives")
-            self.fused = FusedTopKSAEStep(sae, betas=self.cfg.betas, comm=comm)
-            logger.info("Training on the fused sm_100a kernel path" + (" with peer-memory collectives" if comm else ""))
+            dp_comm = None
+            dp = mesh_dim_size(sae.device_mesh, "data")
+            F_l = sae.W_D.shape[0]
+            if self.cfg.use_peer_memory_collectives and dp > 1 and rows and F_l % dp == 0 and not self.cfg.auxk_coefficient:
+                try:
+                    from .parallel.symm import DataParallelComm
+
+                    # every replica keeps the gathered rows of x, d x_hat and the three code tensors of a step; a
+                    # batch-level top-k gives rows of varying width, bounded by the list capacity of its compaction
+                    k_cap = int(max(sae.cfg.top_k, self.cfg.initial_k or 0)) * (4 if sae.cfg.act_fn == "batchtopk" else 1)
+                    n_rows, d = rows * dp, sae.cfg.d_model
+                    zones = {"x": n_rows * d * 2, "dxhat": n_rows * d * 2, "idx": n_rows * k_cap * 4,
+                             "act": n_rows * k_cap * 4, "dact": n_rows * k_cap * 4}  # fmt: skip
+                    dp_comm = DataParallelComm(mesh_group(sae.device_mesh, "data"), torch.device(sae.cfg.device), F_l, d, zones)
+                except Exception as e:  # noqa: BLE001
+                    logger.warning(f"peer-memory data parallelism unavailable ({e}); replicas repeat the full update")
+            self.fused = FusedTopKSAEStep(sae, betas=self.cfg.betas, comm=comm, dp_comm=dp_comm)
+            logger.info("Training on the fused sm_100a kernel path" + (" with peer-memory collectives" if comm or dp_comm else ""))
         else:
             logger.info(f"Training on the generic autograd path ({why})")
         groups = []
@@ -478,8 +510,8 @@ class Trainer:
             optimizer = SparseAdam(groups, lr=self.cfg.lr, betas=self.cfg.betas)
         self.optimizer = optimizer
         self.scheduler = get_scheduler(self.cfg.lr_scheduler_name, optimizer, **sched_kwargs)
-        if self.cfg.lr_scheduler_name not in ("cosineannealing",):
-            self._lr_lambda = schedule_lambda(self.cfg.lr_scheduler_name, **sched_kwargs)
+        # the fused path never steps the torch scheduler: it evaluates the same schedule in closed form
+        self._lr_lambda = schedule_lambda(self.cfg.lr_scheduler_name, base_lr=float(self.cfg.lr), **sched_kwargs)
 
     def _initialize_dead_statistics(self, sae: SparseDictionary) -> None:
         n_local = sae.local_shape("b_E", (sae.cfg.d_sae,))[0] if "b_E" in sae.dim_maps() else sae.cfg.d_sae
@@ -652,8 +684,7 @@ class Trainer:
     @timer.time("save_checkpoint")
     def _maybe_save_sae_checkpoint(self, sae: SparseDictionary):
         if self.checkpoint_thresholds and self.cur_step >= self.checkpoint_thresholds[0]:
-            if self.fused is not None:
-                self.fused.join()
+            self._before_parameters_leave(sae)
             sae.save_checkpoint(os.path.join(self.cfg.exp_result_path, "checkpoints", f"{self.cur_step}.safetensors"))
             self.checkpoint_thresholds.pop(0)
 
@@ -695,6 +726,7 @@ class Trainer:
         accum = max(1, self.cfg.gradient_accumulation_steps)
         loss_reader = _LossReader()
         heartbeat = self._make_heartbeat()
+        finished = False
         try:
             while True:
                 with timer.time("training_iteration"):
@@ -714,20 +746,19 @@ class Trainer:
                             bar.set_description(f"loss: {shown:.2f}")
                     if eval_fn is not None and (self.cur_step + 1) % self.cfg.eval_frequency == 0:
                         with timer.time("evaluation"):
-                            if self.fused is not None:
-                                self.fused.join()
+                            self._before_parameters_leave(sae)
                             eval_fn(sae)
                     self.cur_step += 1
-                    mask = batch.get("mask")
-                    n_tok = batch["tokens"].numel() if mask is None else int(mask.sum())
-                    self.cur_tokens += n_tok * dp
+                    self.cur_tokens += self._count_tokens(batch) * dp
                     self._maybe_save_sae_checkpoint(sae)
                     if self.cur_step >= self.total_training_steps:
+                        finished = True
                         break
                     with timer.time("refresh_batch"):
                         del batch
                         batch = next(stream)
         except StopIteration:
+            finished = True
             logger.info("the current stream has ended")
             if heartbeat is not None:
                 heartbeat.leave("end of the activation stream")
@@ -746,7 +777,51 @@ class Trainer:
             bar.close()
             if self.fused is not None:
                 self.fused.join()  # the last update may still be running on its own stream
+                if finished:  # collective: only when every rank left the loop in step
+                    self.fused.sync_params()
         return None
+
+    def _before_parameters_leave(self, sae: SparseDictionary) -> None:
+        """Before parameters are written out or handed to other code on the fused path: fold the update stream back,
+        raise if a kernel recorded an error (a timed-out collective leaves the step's data unusable; the update kernels
+        skip themselves after one, so the parameters are those of the last good step, but nothing more must be saved as
+        if training had gone on), and gather the master rows that other replicas own."""
+        if self.fused is None:
+            return
+        self.fused.join()
+        dev = next(sae.parameters()).device
+        if dev.type == "cuda":
+            from .ops import sae_kernels as K
+
+            K.check_status(dev)
+        self.fused.sync_params()
+
+    @staticmethod
+    def _mask_summary(batch: dict[str, Any]) -> dict[str, Any]:
+        """For a batch whose token mask is still in host memory: note the number of valid tokens and whether all are valid
+        under private keys, so that no later step needs to ask the device."""
+        mask = batch.get("mask")
+        if isinstance(mask, Tensor) and mask.device.type == "cpu" and "_n_valid" not in batch:
+            n = int(mask.sum())
+            batch = {**batch, "_n_valid": n, "_mask_all": n == mask.numel()}
+        return batch
+
+    def _count_tokens(self, batch: dict[str, Any]) -> int:
+        """Valid tokens of a batch for the progress counters. A mask that lives on the device is counted there and folded
+        in at the next logging step (one read per logging interval instead of one per step)."""
+        if "_n_valid" in batch:
+            return int(batch["_n_valid"])
+        mask = batch.get("mask")
+        if mask is None:
+            return batch["tokens"].numel()
+        if not mask.is_cuda:
+            return int(mask.sum())
+        total = mask.sum()
+        self._tokens_on_device = total if self._tokens_on_device is None else self._tokens_on_device + total
+        if (self.cur_step % max(1, self.cfg.log_frequency)) == 0:
+            n, self._tokens_on_device = int(self._tokens_on_device), None
+            return n
+        return 0
 
     def _kernel_status(self, sae: SparseDictionary) -> Tensor | None:
         """The status word of this model's device when hand-written kernels are in play (read back with the loss)."""
@@ -763,6 +838,30 @@ class Trainer:
 
         return Heartbeat(default_store(), dist.get_rank(), dist.get_world_size(), timeout_s=self.cfg.heartbeat_timeout_s)
 
+    def restore_failure_checkpoint(self, sae: SparseDictionary, path: str | Path) -> None:
+        """Load what ``_save_failure_checkpoint`` wrote for this rank (``<path>/rank_<r>/``): local parameter tensors, the
+        step / token counters and, on the fused path, this rank's Adam moments. Call after ``fit`` has built the
+        optimizer for the same mesh, or on a trainer whose optimizer is initialised."""
+        rank = dist.get_rank() if dist.is_initialized() else 0
+        src = Path(path) / f"rank_{rank}"
+        local = torch.load(src / "local_state.pt", map_location="cpu", weights_only=False)
+        with torch.no_grad():
+            for k, v in sae.state_dict().items():
+                if k in local:
+                    v.copy_(local[k].to(v.device))
+        state = torch.load(src / "trainer.pt", map_location="cpu", weights_only=False)
+        self.cur_step, self.cur_tokens = state["cur_step"], state["cur_tokens"]
+        fo = state.get("fused_optimizer")
+        if self.fused is not None and fo is not None:
+            assert tuple(fo["own_rows"]) == tuple(self.fused.own_rows), "the failure checkpoint was written for another layout"
+            self.fused.t = int(fo["step"])
+            for n, pair in fo["state"].items():
+                for dst, srct in zip(self.fused.state[n], pair):
+                    dst.copy_(srct.to(dst.device))
+            self.fused.refresh()
+        elif self.optimizer is not None and "optimizer" in state:
+            self.optimizer.load_state_dict(state["optimizer"])
+
     def _save_failure_checkpoint(self, sae: SparseDictionary) -> None:
         """Best effort, this rank only and without collectives (the other ranks may be gone): the model's local tensors,
         the optimizer and the trainer state under ``<exp_result_path>/failure/rank_<r>/``."""
@@ -776,7 +875,13 @@ class Trainer:
             sae.cfg.save_hyperparameters(out)
             state = {"cur_step": self.cur_step, "cur_tokens": self.cur_tokens, "total_training_steps": self.total_training_steps,
                      "cfg": self.cfg}  # fmt: skip
-            if self.optimizer is not None:
+            if self.fused is not None:
+                # this rank's moments as they are (its shard, and under a sharded optimizer state its feature rows only)
+                state["fused_optimizer"] = {
+                    "step": self.fused.t, "own_rows": tuple(self.fused.own_rows),
+                    "state": {n: tuple(t.detach().cpu() for t in st) for n, st in self.fused.state.items() if st is not None},
+                }
+            elif self.optimizer is not None:
                 state["optimizer"] = self.optimizer.state_dict()
             if self.scheduler is not None:
                 state["scheduler"] = self.scheduler.state_dict()
@@ -791,6 +896,7 @@ class Trainer:
         dev = torch.device(sae.cfg.device)
         if dev.type != "cuda":
             return batch
+        batch = Trainer._mask_summary(batch)
         return {
             k: (v.to(dev, non_blocking=True) if isinstance(v, Tensor) and v.device.type == "cpu" else v)
             for k, v in batch.items()
@@ -838,12 +944,16 @@ class Trainer:
             label = (y_raw * sae.compute_norm_factor(y_raw, hout)).to(torch.bfloat16).contiguous()
         mask = batch.get("mask")
         row_weight, n_global = None, None
-        if mask is not None and mask.dtype != torch.bool or (mask is not None and not bool(mask.all())):
-            row_weight = mask.reshape(-1).float()
-            n = row_weight.sum()
+        if mask is not None and not batch.get("_mask_all", False):
+            # Masked rows get weight 0, valid rows B_global / n_valid, computed on the device: the kernels keep their host
+            # constant 2 / B_global as the gradient scale and no step waits for the device to count its valid tokens.
+            w = mask.reshape(-1).float()
+            n = w.sum()
             if f.dp > 1:
+                n = n.clone()
                 dist.all_reduce(n, group=f.dp_group)
-            n_global = int(n)
+            n_global = w.numel() * f.dp
+            row_weight = w * (n_global / n.clamp_min(1.0))
         k = self._current_k(sae)
         if k is not None:
             sae.set_current_k(k)

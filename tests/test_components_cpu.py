@@ -281,3 +281,23 @@ def test_execute_and_broadcast_runs_once_and_shares_the_result():
     assert out == {"rank": 0, "value": [1, 2, 3]}  # rank 0's result everywhere
     assert calls == ([0] if dist.get_rank() == 0 else [])
     assert execute_and_broadcast(lambda: 7, None) == 7  # no mesh: just a call
+
+
+def test_closed_form_lr_factor_equals_the_torch_scheduler_for_every_schedule():
+    """The fused path never steps the torch scheduler; it evaluates ``schedule_lambda`` instead. Both must give the same
+    learning rate at every step, for every scheduler name the trainer configuration accepts."""
+    import torch
+
+    from language_model_saes_b200.optim import get_scheduler, schedule_lambda
+
+    base, total = 3e-4, 40
+    kw = dict(warm_up_steps=5, cool_down_steps=8, training_steps=total, lr_end_ratio=1 / 32)
+    for name in ("constant", "constantwithwarmup", "linearwarmupdecay", "cosineannealing", "cosineannealingwarmup", "exponentialwarmup"):
+        p = torch.nn.Parameter(torch.zeros(2))
+        opt = torch.optim.Adam([p], lr=base)
+        sched = get_scheduler(name, opt, **kw)
+        factor = schedule_lambda(name, base_lr=base, **kw)
+        for s in range(total):
+            assert abs(sched.get_last_lr()[0] - base * factor(s)) <= 1e-9 + 1e-6 * base, (name, s)
+            opt.step()
+            sched.step()

@@ -63,19 +63,100 @@ def test_peer_memory_step_matches_nccl_and_single_gpu():
         m.load_full_state_dict(full.full_state_dict())
         return m
 
-    m_nccl, m_p2p = shard(), shard()
+    m_nccl = shard()
     got_nccl = run(m_nccl, None)
-    comm = SymmComm(mesh.get_group("model"), dev, B, k, d)
-    got_p2p = run(m_p2p, comm)
-    K.check_status(dev)
-    # the peer-memory path reports the loss of the rows each rank owns: average the two halves
-    dist.all_reduce(got_p2p)
-    got_p2p /= 2
     assert torch.allclose(got_nccl, want, rtol=2e-3), (got_nccl, want)
-    assert torch.allclose(got_p2p, want, rtol=2e-3), (got_p2p, want)
-    for m in (m_nccl, m_p2p):
-        W = DimMap({"model": 0}).gather(m.W_D.data, mesh)
-        assert torch.allclose(W, single.W_D.data, atol=2e-4), float((W - single.W_D.data).abs().max())
+    W_ref = single.W_D.data
+    W = DimMap({"model": 0}).gather(m_nccl.W_D.data, mesh)
+    assert torch.allclose(W, W_ref, atol=2e-4), float((W - W_ref).abs().max())
+    # peer-memory variants: fp32 partial rows (exact protocol check), bf16 partial rows (the default on the wire) and, where
+    # the fabric offers a multicast mapping, the owner-side sum and the gradient all-gather through the switch
+    variants = [("fp32", dict(partial_dtype=torch.float32, use_multicast=False), 2e-3, 2e-4),
+                ("bf16", dict(partial_dtype=torch.bfloat16, use_multicast=False), 1e-2, None),
+                ("multicast", dict(partial_dtype=torch.bfloat16, use_multicast=True), 1e-2, None)]  # fmt: skip
+    for name, kw, rtol, w_atol in variants:
+        comm = SymmComm(mesh.get_group("model"), dev, B, k, d, **kw)
+        if name == "multicast" and not comm.use_multicast:
+            print("no multicast mapping for this group: the multimem variant is not exercised here")
+            continue
+        m_p2p = shard()
+        got_p2p = run(m_p2p, comm)
+        K.check_status(dev)
+        # the peer-memory path reports the loss of the rows each rank owns: average the two halves
+        dist.all_reduce(got_p2p)
+        got_p2p /= 2
+        assert torch.allclose(got_p2p, want, rtol=rtol), (name, got_p2p, want)
+        W = DimMap({"model": 0}).gather(m_p2p.W_D.data, mesh)
+        if w_atol is not None:
+            assert torch.allclose(W, W_ref, atol=w_atol), (name, float((W - W_ref).abs().max()))
+        else:  # partial rows rounded to bf16: Adam's first steps move a weight by about lr whatever the gradient's size
+            assert float((W - W_ref).abs().max()) <= 2.2 * lr * len(xs), (name, float((W - W_ref).abs().max()))
+        waits = comm.stats.read(1500.0)
+        assert set(waits) == {"candidates", "partial rows", "gradient rows"} and all(v["calls"] == len(xs) for v in waits.values()), waits
+        # codes outside a training step, twice (metrics path): the candidate exchange alone, on its alternating zones
+        eng_a, eng_b = FusedTopKSAEStep(m_p2p, comm=comm), FusedTopKSAEStep(m_p2p, comm=None)
+        for x in xs[:2]:
+            ia, aa, xa = eng_a.forward_dense(x, k)
+            ib, ab, xb = eng_b.forward_dense(x, k)
+            K.check_status(dev)
+            assert torch.equal(ia.sort(dim=1).values, ib.sort(dim=1).values), name
+            assert torch.allclose(xa, xb, atol=1e-3, rtol=1e-3), name
+
+
+@needs2
+@distributed_test(nproc_per_node=2, backend="nccl")
+def test_data_parallel_step_with_row_sharded_optimizer_state_matches_single_gpu():
+    """Two replicas, each with half of the batch: rows exchanged by one peer-store kernel, each replica updates half of
+    the feature rows and publishes the new bf16 rows, norms and biases to the other. Same losses and, after gathering
+    the master rows, the same parameters and Adam moments as one GPU on the whole batch."""
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    from language_model_saes_b200.models.sae import SparseAutoEncoder
+    from language_model_saes_b200.ops import sae_kernels as K
+    from language_model_saes_b200.ops.fused_step import FusedTopKSAEStep
+    from language_model_saes_b200.parallel.mesh import build_mesh
+    from language_model_saes_b200.parallel.symm import DataParallelComm
+
+    rank = dist.get_rank()
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    mesh = build_mesh("cuda", (2, 1), ("data", "model"))
+    full = _full_model(dev)
+    B, d, k, lr, F = 512, 256, 16, 1e-3, 4096
+    g = torch.Generator(device=dev).manual_seed(3)
+    xs = [(torch.randn(B, d, device=dev, generator=g) * 1.0).to(torch.bfloat16) for _ in range(4)]
+    for x in xs:
+        dist.broadcast(x, src=0)
+    single = SparseAutoEncoder(full.cfg.model_copy())
+    single.load_full_state_dict(full.full_state_dict())
+    eng1 = FusedTopKSAEStep(single)
+    want = torch.stack([eng1.step(x, x, k, lr, clip_grad_norm=(0.5 if i == 3 else 0.0)) for i, x in enumerate(xs)])
+
+    half = B // 2
+    for sharded in (True, False):
+        m = SparseAutoEncoder(full.cfg.model_copy(), mesh)
+        m.load_full_state_dict(full.full_state_dict())
+        dp_comm = None
+        if sharded:
+            n = B
+            zones = {"x": n * d * 2, "dxhat": n * d * 2, "idx": n * k * 4, "act": n * k * 4, "dact": n * k * 4}
+            dp_comm = DataParallelComm(mesh.get_group("data"), dev, F, d, zones)
+        eng = FusedTopKSAEStep(m, dp_comm=dp_comm)
+        got = torch.stack([eng.step(x[rank * half : (rank + 1) * half], x[rank * half : (rank + 1) * half], k, lr,
+                                    clip_grad_norm=(0.5 if i == 3 else 0.0)) for i, x in enumerate(xs)])  # fmt: skip
+        K.check_status(dev)
+        dist.all_reduce(got)
+        got /= 2  # each replica reports the mean loss of its half of the batch
+        assert torch.allclose(got, want, rtol=2e-3), (sharded, got, want)
+        eng.sync_params()
+        assert torch.allclose(m.W_D.data, single.W_D.data, atol=2e-4), (sharded, float((m.W_D.data - single.W_D.data).abs().max()))
+        assert torch.allclose(m.W_E.data, single.W_E.data, atol=2e-4)
+        assert torch.allclose(m.b_E.data, single.b_E.data, atol=2e-4) and torch.allclose(m.b_D.data, single.b_D.data, atol=2e-4)
+        assert torch.allclose(eng.dec_norm, eng1.dec_norm, atol=2e-4)
+        st, st1 = eng.optimizer_state(), eng1.optimizer_state()
+        assert torch.allclose(st["W_D"]["exp_avg_sq"], st1["W_D"]["exp_avg_sq"], atol=1e-6, rtol=1e-2)
+        if sharded:
+            assert eng.state["W_D"][0].shape[0] == F // 2  # the moments of half of the rows only
+            assert dp_comm.stats.read(1500.0)["data-parallel rows"]["calls"] == len(xs) + 0
 
 
 @needs2
@@ -133,17 +214,26 @@ def test_auxk_step_with_feature_shards_matches_single_gpu():
 def test_peer_flag_wait_times_out_with_status_code():
     from language_model_saes_b200.ops import sae_kernels as K
 
+    from language_model_saes_b200.parallel.symm import peer_table
+
     dev = torch.device("cuda", 0)
     buf = torch.zeros(4096, dtype=torch.uint8, device=dev)
-    table = [1, 0, 0, 1024, 2048, 3072, 3584, buf.data_ptr()]
+    table = peer_table(1, 0, [buf.data_ptr()], 0, 1024, 2048, 3072, 3584)
     st = K.status_buffer(dev)
     st.zero_()
     K._ext().comm_wait(table, 0, 7, st)  # epoch 7 was never published
     torch.cuda.synchronize()
+    # while the error is on record the update kernels leave parameters and moments alone
+    p, g = torch.ones(64, device=dev), torch.ones(64, device=dev)
+    m, v = torch.zeros(64, device=dev), torch.zeros(64, device=dev)
+    K.adam_flat(p, g, m, v, 0.1, 0.9, 0.999, 1e-8, 1)
+    assert float(p.sum()) == 64.0 and float(m.abs().sum()) == 0.0
     with pytest.raises(K.KernelStatusError, match="peer flag"):
         K.check_status(dev)
-    # the context is still usable afterwards
+    # the context is still usable afterwards, and with the status cleared the update runs
     assert float((torch.ones(8, device=dev) * 2).sum()) == 16.0
+    K.adam_flat(p, g, m, v, 0.1, 0.9, 0.999, 1e-8, 1)
+    assert float(p.sum()) < 64.0
 
 
 @needs2
