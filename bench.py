@@ -248,7 +248,8 @@ def run_ours(args):
     if world > 1 and os.environ.get("LMSAE_BENCH_NCCL", "0") != "1":
         from language_model_saes_b200.parallel.symm import SymmComm
 
-        comm = SymmComm(mesh.get_group("model"), dev, BATCH, TOP_K, D_MODEL)
+        comm = SymmComm(mesh.get_group("model"), dev, BATCH, TOP_K, D_MODEL,
+                        partial_dtype=torch.float32 if os.environ.get("LMSAE_PARTIAL_FP32", "0") == "1" else torch.bfloat16)
     engine = FusedTopKSAEStep(sae, betas=(0.9, 0.999), comm=comm)
     pool = [h.to(dev) for h in host]
     for i in range(W):

@@ -936,12 +936,24 @@ class Trainer:
         hin, hout = sae.cfg.hook_point_in, sae.cfg.hook_point_out
         x_raw = batch[hin]
         assert x_raw.ndim == 2, "the fused path trains on [tokens, d_model] activations"
-        x = (x_raw * sae.compute_norm_factor(x_raw, hin)).to(torch.bfloat16).contiguous()
-        if hout == hin:
-            label = x
-        else:
-            y_raw = batch[hout]
-            label = (y_raw * sae.compute_norm_factor(y_raw, hout)).to(torch.bfloat16).contiguous()
+
+        def normalised(raw: Tensor, hook_point: str) -> Tensor:
+            # A constant factor stays a Python number: building a device scalar from it every step (what
+            # compute_norm_factor returns) is a synchronous copy, after which the host can no longer run ahead of the
+            # device; a factor of exactly 1 costs no kernel at all.
+            mode = sae.cfg.norm_activation
+            if mode == "inference":
+                scaled = raw
+            elif mode == "dataset-wise":
+                assert sae.dataset_average_activation_norm is not None, "dataset_average_activation_norm must be provided from Initializer"
+                factor = math.sqrt(sae.cfg.d_model) / float(sae.dataset_average_activation_norm[hook_point])
+                scaled = raw if factor == 1.0 else raw * factor
+            else:
+                scaled = raw * sae.compute_norm_factor(raw, hook_point)
+            return scaled.to(torch.bfloat16).contiguous()
+
+        x = normalised(x_raw, hin)
+        label = x if hout == hin else normalised(batch[hout], hout)
         mask = batch.get("mask")
         row_weight, n_global = None, None
         if mask is not None and not batch.get("_mask_all", False):
