@@ -290,7 +290,9 @@ void mse_loss_grad(const Tensor& xhat, const Tensor& label, const c10::optional<
 
 void auxk_loss_grad(const Tensor& xhat, const Tensor& aux_rec, const Tensor& label, const c10::optional<Tensor>& bias,
                     const c10::optional<Tensor>& row_weight, double grad_scale, double alpha, const Tensor& g_main,
-                    const Tensor& g_aux, const Tensor& loss_sum, const Tensor& aux_sum) {
+                    const Tensor& g_aux, const Tensor& loss_sum, const Tensor& aux_sum,
+                    const c10::optional<Tensor>& alpha_factor) {
+  if (alpha_factor.has_value()) { CHECK_T(*alpha_factor, torch::kFloat32); TORCH_CHECK(alpha_factor->numel() == 1); }
   CHECK_T(xhat, torch::kFloat32);
   CHECK_T(aux_rec, torch::kFloat32);
   CHECK_T(label, torch::kBFloat16);
@@ -304,7 +306,8 @@ void auxk_loss_grad(const Tensor& xhat, const Tensor& aux_rec, const Tensor& lab
   check_cuda(lmsae::auxk_loss_grad_launch(xhat.data_ptr<float>(), aux_rec.data_ptr<float>(),
                                           reinterpret_cast<const __nv_bfloat16*>(label.data_ptr()), opt_ptr<const float>(bias),
                                           opt_ptr<const float>(row_weight), (int)xhat.size(0), (int)xhat.size(1),
-                                          (float)grad_scale, (float)alpha, reinterpret_cast<__nv_bfloat16*>(g_main.data_ptr()),
+                                          (float)grad_scale, (float)alpha, opt_ptr<const float>(alpha_factor),
+                                          reinterpret_cast<__nv_bfloat16*>(g_main.data_ptr()),
                                           reinterpret_cast<__nv_bfloat16*>(g_aux.data_ptr()), loss_sum.data_ptr<float>(),
                                           aux_sum.data_ptr<float>(), at::cuda::getCurrentCUDAStream()),
              "auxk_loss_grad launch");

@@ -55,8 +55,10 @@ __device__ __forceinline__ bool signal_peers_when_grid_done(const PeerTable& pt,
 // Block-wide bounded wait until every source rank has published `epoch` for `phase` in OUR flag slots.
 // Returns false (uniformly) on expiry. Block 0 adds the cycles it spent here to the rank's exposed-wait
 // counters (pt.stats: one {cycles, calls} pair of 64-bit words per phase), which is how the time a step
-// spends waiting for its peers is measured without a profiler.
-__device__ __forceinline__ bool wait_all_sources(const PeerTable& pt, int phase, uint32_t epoch, int* status) {
+// spends waiting for its peers is measured without a profiler (`record_always`: for kernels in which one block only
+// waits, whichever it is).
+__device__ __forceinline__ bool wait_all_sources(const PeerTable& pt, int phase, uint32_t epoch, int* status,
+                                                 bool record_always = false) {
   __shared__ int s_ok;
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
@@ -70,7 +72,7 @@ __device__ __forceinline__ bool wait_all_sources(const PeerTable& pt, int phase,
       }
       waited = clock64() - t0;
     }
-    if (blockIdx.x == 0 && pt.stats != nullptr) {
+    if ((blockIdx.x == 0 || record_always) && pt.stats != nullptr) {
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) {
         const long long other = __shfl_xor_sync(0xffffffffu, waited, o);

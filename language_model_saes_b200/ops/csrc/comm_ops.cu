@@ -240,7 +240,7 @@ exchange_rows_kernel(const PeerTable pt, const RowExchange ex, uint32_t epoch, u
     }
   }
   const bool last = signal_peers_when_grid_done(pt, kPhaseRows, epoch, done_counter);
-  if (last) wait_all_sources(pt, kPhaseRows, epoch, status);
+  if (last) wait_all_sources(pt, kPhaseRows, epoch, status, /*record_always=*/true);
 }
 
 int exchange_rows_launch(const PeerTable& pt, const RowExchange& ex, uint32_t epoch, unsigned* done_counter, int* status,

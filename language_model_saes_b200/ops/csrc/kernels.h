@@ -144,8 +144,8 @@ struct GradAdamParams {
 };
 int auxk_loss_grad_launch(const float* xhat, const float* aux_rec, const __nv_bfloat16* label, const float* bias,
                           const float* row_weight, int rows, int d, float grad_scale, float alpha,
-                          __nv_bfloat16* g_main, __nv_bfloat16* g_aux, float* loss_sum, float* aux_sum,
-                          cudaStream_t stream);
+                          const float* alpha_factor, __nv_bfloat16* g_main, __nv_bfloat16* g_aux, float* loss_sum,
+                          float* aux_sum, cudaStream_t stream);
 int sparse_grad_adam_launch(const GradAdamParams& p, cudaStream_t stream);
 int colsum_bf16_launch(const __nv_bfloat16* a, int rows, int d, float* out, cudaStream_t stream);
 int adam_flat_launch(float* p, const float* g, float* m, float* v, long long n, AdamHyper h, const float* grad_mul,

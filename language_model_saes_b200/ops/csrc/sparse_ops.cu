@@ -291,10 +291,13 @@ int mse_loss_grad_launch(const float* xhat, const __nv_bfloat16* label, const fl
 __global__ void __launch_bounds__(256)
 auxk_loss_grad_kernel(const float* __restrict__ xhat, const float* __restrict__ aux_rec,
                       const __nv_bfloat16* __restrict__ label, const float* __restrict__ bias,
-                      const float* __restrict__ row_weight, int rows, int d, float grad_scale, float alpha,
-                      __nv_bfloat16* __restrict__ g_main, __nv_bfloat16* __restrict__ g_aux,
-                      float* __restrict__ loss_sum, float* __restrict__ aux_sum) {
+                      const float* __restrict__ row_weight, int rows, int d, float grad_scale, float alpha_host,
+                      const float* __restrict__ alpha_factor, __nv_bfloat16* __restrict__ g_main,
+                      __nv_bfloat16* __restrict__ g_aux, float* __restrict__ loss_sum, float* __restrict__ aux_sum) {
   __shared__ float s_red[2][8];
+  // alpha_factor (one device float, optional): 0 switches the auxiliary term off without the host knowing, e.g. in a step
+  // that has no dead feature
+  const float alpha = alpha_factor != nullptr ? alpha_host * *alpha_factor : alpha_host;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const float rw = row_weight != nullptr ? row_weight[row] : 1.0f;
@@ -330,12 +333,12 @@ auxk_loss_grad_kernel(const float* __restrict__ xhat, const float* __restrict__ 
 
 int auxk_loss_grad_launch(const float* xhat, const float* aux_rec, const __nv_bfloat16* label, const float* bias,
                           const float* row_weight, int rows, int d, float grad_scale, float alpha,
-                          __nv_bfloat16* g_main, __nv_bfloat16* g_aux, float* loss_sum, float* aux_sum,
-                          cudaStream_t stream) {
+                          const float* alpha_factor, __nv_bfloat16* g_main, __nv_bfloat16* g_aux, float* loss_sum,
+                          float* aux_sum, cudaStream_t stream) {
   int blocks = rows < 148 * 8 ? rows : 148 * 8;
   if (blocks <= 0) return 0;
   auxk_loss_grad_kernel<<<blocks, 256, 0, stream>>>(xhat, aux_rec, label, bias, row_weight, rows, d, grad_scale, alpha,
-                                                    g_main, g_aux, loss_sum, aux_sum);
+                                                    alpha_factor, g_main, g_aux, loss_sum, aux_sum);
   return (int)cudaGetLastError();
 }
 
@@ -492,7 +495,12 @@ __device__ __forceinline__ void adam_elem(float& p, float& m, float& v, float g,
 
 // One CTA walks feature rows (grid-stride). For a row it first rebuilds the two gradient rows from the
 // feature's entry list (gathers of x / d x_hat rows, normally L2 hits), then streams p, m, v once.
-__global__ void __launch_bounds__(GA_THREADS, 4)
+// VEC = float4 groups per thread and chunk step. VEC 1 with four CTAs per SM is the stand-alone form (most warps to
+// hide latency). VEC 2 with two CTAs per SM keeps the same number of bytes in flight per SM (twelve 16-byte loads per
+// thread) with half the warps and registers-per-SM to spare: the form that shares the SMs with a concurrently running
+// encoder GEMM of the next step.
+template <int VEC, int MIN_CTAS>
+__global__ void __launch_bounds__(GA_THREADS, MIN_CTAS)
 sparse_grad_adam_kernel(const GradAdamParams p) {
   __shared__ float s_red[GA_THREADS / 32];
   __shared__ float s_gsq[GA_THREADS / 32];
@@ -508,12 +516,20 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
     const int e0 = p.offsets[f], e1 = p.offsets[f + 1];
     float bias_g = 0.0f;
     float norm_sq = 0.0f;
-    for (int c0 = 0; c0 < p.d; c0 += GA_THREADS * 4) {
-      const int c = c0 + threadIdx.x * 4;
-      const bool in = c < p.d;  // d % 4 == 0
-      float gD[4] = {0.f, 0.f, 0.f, 0.f}, gE[4] = {0.f, 0.f, 0.f, 0.f};
-      const size_t o = (size_t)f * p.d + (in ? c : 0);                  // parameters, shadows, dense gradient outputs
-      const size_t os = (size_t)(f - p.state_f0) * p.d + (in ? c : 0);  // moments
+    for (int c0 = 0; c0 < p.d; c0 += GA_THREADS * 4 * VEC) {
+      int c[VEC];
+      bool in[VEC];
+      size_t o[VEC], os[VEC];
+      float gD[VEC][4], gE[VEC][4];
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) {
+        c[v] = c0 + v * GA_THREADS * 4 + threadIdx.x * 4;
+        in[v] = c[v] < p.d;  // d % 4 == 0
+        o[v] = (size_t)f * p.d + (in[v] ? c[v] : 0);                  // parameters, shadows, dense gradient outputs
+        os[v] = (size_t)(f - p.state_f0) * p.d + (in[v] ? c[v] : 0);  // moments
+#pragma unroll
+        for (int i = 0; i < 4; ++i) gD[v][i] = gE[v][i] = 0.0f;
+      }
       for (int e = e0; e < e1; ++e) {
         const int ent = p.entries[e];
         const int row = ent / p.k;
@@ -522,55 +538,71 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
         // codes beyond the first k_main slots of a row (auxiliary codes) multiply the auxiliary output gradient
         const __nv_bfloat16* gmat = (p.dxhat_aux != nullptr && ent - row * p.k >= p.k_main) ? p.dxhat_aux : p.dxhat;
         if (c0 == 0 && threadIdx.x == 0) bias_g += da;
-        if (in) {
-          const uint2 ux = __ldg(reinterpret_cast<const uint2*>(p.x + (size_t)row * p.d + c));
-          const uint2 ud = __ldg(reinterpret_cast<const uint2*>(gmat + (size_t)row * p.d + c));
-          const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ux.x));
-          const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ux.y));
-          const float2 d01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ud.x));
-          const float2 d23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ud.y));
-          gD[0] = fmaf(a, d01.x, gD[0]); gD[1] = fmaf(a, d01.y, gD[1]);
-          gD[2] = fmaf(a, d23.x, gD[2]); gD[3] = fmaf(a, d23.y, gD[3]);
-          gE[0] = fmaf(da, x01.x, gE[0]); gE[1] = fmaf(da, x01.y, gE[1]);
-          gE[2] = fmaf(da, x23.x, gE[2]); gE[3] = fmaf(da, x23.y, gE[3]);
-        }
-      }
-      if (!in) continue;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        gD[i] *= gmul;
-        gE[i] *= gmul;
-        gsq_local += gD[i] * gD[i] + gE[i] * gE[i];
-      }
-      if (p.gD_out != nullptr) *reinterpret_cast<float4*>(p.gD_out + o) = make_float4(gD[0], gD[1], gD[2], gD[3]);
-      if (p.gE_out != nullptr) *reinterpret_cast<float4*>(p.gE_out + o) = make_float4(gE[0], gE[1], gE[2], gE[3]);
-      if (p.update) {
-        // all six streams of this chunk are requested before the first is used (96 bytes in flight per thread)
-        float4 w = ldcs4(p.WD + o), m = ldcs4(p.mD + os), v = ldcs4(p.vD + os);
-        float4 we = ldcs4(p.WE + o), me = ldcs4(p.mE + os), ve = ldcs4(p.vE + os);
-        {
-          adam_elem(w.x, m.x, v.x, gD[0], p.h); adam_elem(w.y, m.y, v.y, gD[1], p.h);
-          adam_elem(w.z, m.z, v.z, gD[2], p.h); adam_elem(w.w, m.w, v.w, gD[3], p.h);
-          stcs4(p.WD + o, w); stcs4(p.mD + os, m); stcs4(p.vD + os, v);
-          norm_sq += w.x * w.x + w.y * w.y + w.z * w.z + w.w * w.w;
-          uint2 sh; sh.x = pack_bf16x2(w.x, w.y); sh.y = pack_bf16x2(w.z, w.w);
-          if (p.n_pub > 0) {
-            for (int q = 0; q < p.n_pub; ++q)
-              *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.pub.base[q] + p.pub_wd_off) + o) = sh;
-          } else {
-            *reinterpret_cast<uint2*>(p.WD_bf16 + o) = sh;
+        for (int v = 0; v < VEC; ++v) {
+          if (in[v]) {
+            const uint2 ux = __ldg(reinterpret_cast<const uint2*>(p.x + (size_t)row * p.d + c[v]));
+            const uint2 ud = __ldg(reinterpret_cast<const uint2*>(gmat + (size_t)row * p.d + c[v]));
+            const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ux.x));
+            const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ux.y));
+            const float2 d01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ud.x));
+            const float2 d23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ud.y));
+            gD[v][0] = fmaf(a, d01.x, gD[v][0]); gD[v][1] = fmaf(a, d01.y, gD[v][1]);
+            gD[v][2] = fmaf(a, d23.x, gD[v][2]); gD[v][3] = fmaf(a, d23.y, gD[v][3]);
+            gE[v][0] = fmaf(da, x01.x, gE[v][0]); gE[v][1] = fmaf(da, x01.y, gE[v][1]);
+            gE[v][2] = fmaf(da, x23.x, gE[v][2]); gE[v][3] = fmaf(da, x23.y, gE[v][3]);
           }
         }
-        {
-          adam_elem(we.x, me.x, ve.x, gE[0], p.h); adam_elem(we.y, me.y, ve.y, gE[1], p.h);
-          adam_elem(we.z, me.z, ve.z, gE[2], p.h); adam_elem(we.w, me.w, ve.w, gE[3], p.h);
-          stcs4(p.WE + o, we); stcs4(p.mE + os, me); stcs4(p.vE + os, ve);
-          uint2 sh; sh.x = pack_bf16x2(we.x, we.y); sh.y = pack_bf16x2(we.z, we.w);
-          if (p.n_pub > 0) {
-            for (int q = 0; q < p.n_pub; ++q)
-              *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.pub.base[q] + p.pub_we_off) + o) = sh;
-          } else {
-            *reinterpret_cast<uint2*>(p.WE_bf16 + o) = sh;
+      }
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) {
+        if (!in[v]) continue;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          gD[v][i] *= gmul;
+          gE[v][i] *= gmul;
+          gsq_local += gD[v][i] * gD[v][i] + gE[v][i] * gE[v][i];
+        }
+        if (p.gD_out != nullptr) *reinterpret_cast<float4*>(p.gD_out + o[v]) = make_float4(gD[v][0], gD[v][1], gD[v][2], gD[v][3]);
+        if (p.gE_out != nullptr) *reinterpret_cast<float4*>(p.gE_out + o[v]) = make_float4(gE[v][0], gE[v][1], gE[v][2], gE[v][3]);
+      }
+      if (p.update) {
+        // all streams of this chunk step are requested before the first is used (96 bytes in flight per thread and VEC)
+        float4 w[VEC], m[VEC], vv[VEC], we[VEC], me[VEC], ve[VEC];
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+          if (in[v]) {
+            w[v] = ldcs4(p.WD + o[v]); m[v] = ldcs4(p.mD + os[v]); vv[v] = ldcs4(p.vD + os[v]);
+            we[v] = ldcs4(p.WE + o[v]); me[v] = ldcs4(p.mE + os[v]); ve[v] = ldcs4(p.vE + os[v]);
+          }
+        }
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+          if (!in[v]) continue;
+          {
+            adam_elem(w[v].x, m[v].x, vv[v].x, gD[v][0], p.h); adam_elem(w[v].y, m[v].y, vv[v].y, gD[v][1], p.h);
+            adam_elem(w[v].z, m[v].z, vv[v].z, gD[v][2], p.h); adam_elem(w[v].w, m[v].w, vv[v].w, gD[v][3], p.h);
+            stcs4(p.WD + o[v], w[v]); stcs4(p.mD + os[v], m[v]); stcs4(p.vD + os[v], vv[v]);
+            norm_sq += w[v].x * w[v].x + w[v].y * w[v].y + w[v].z * w[v].z + w[v].w * w[v].w;
+            uint2 sh; sh.x = pack_bf16x2(w[v].x, w[v].y); sh.y = pack_bf16x2(w[v].z, w[v].w);
+            if (p.n_pub > 0) {
+              for (int q = 0; q < p.n_pub; ++q)
+                *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.pub.base[q] + p.pub_wd_off) + o[v]) = sh;
+            } else {
+              *reinterpret_cast<uint2*>(p.WD_bf16 + o[v]) = sh;
+            }
+          }
+          {
+            adam_elem(we[v].x, me[v].x, ve[v].x, gE[v][0], p.h); adam_elem(we[v].y, me[v].y, ve[v].y, gE[v][1], p.h);
+            adam_elem(we[v].z, me[v].z, ve[v].z, gE[v][2], p.h); adam_elem(we[v].w, me[v].w, ve[v].w, gE[v][3], p.h);
+            stcs4(p.WE + o[v], we[v]); stcs4(p.mE + os[v], me[v]); stcs4(p.vE + os[v], ve[v]);
+            uint2 sh; sh.x = pack_bf16x2(we[v].x, we[v].y); sh.y = pack_bf16x2(we[v].z, we[v].w);
+            if (p.n_pub > 0) {
+              for (int q = 0; q < p.n_pub; ++q)
+                *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.pub.base[q] + p.pub_we_off) + o[v]) = sh;
+            } else {
+              *reinterpret_cast<uint2*>(p.WE_bf16 + o[v]) = sh;
+            }
           }
         }
       }
@@ -630,7 +662,10 @@ int sparse_grad_adam_launch(const GradAdamParams& p, cudaStream_t stream) {
   if (p.state_f0 < 0 || p.state_f0 > p.f_begin) return (int)cudaErrorInvalidValue;
   const int cap = (p.ctas_per_sm >= 1 && p.ctas_per_sm <= 4) ? 148 * p.ctas_per_sm : 148 * 8;
   int blocks = rows < cap ? rows : cap;
-  sparse_grad_adam_kernel<<<blocks, GA_THREADS, 0, stream>>>(p);
+  if (p.ctas_per_sm >= 1 && p.ctas_per_sm <= 2)
+    sparse_grad_adam_kernel<2, 2><<<blocks, GA_THREADS, 0, stream>>>(p);
+  else
+    sparse_grad_adam_kernel<1, 4><<<blocks, GA_THREADS, 0, stream>>>(p);
   return (int)cudaGetLastError();
 }
 

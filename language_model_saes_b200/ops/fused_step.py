@@ -37,18 +37,52 @@ from . import sae_kernels as K
 
 class AuxK:
     """State and settings of the Aux-K loss on the fused path: per-feature count of valid tokens since the feature
-    last fired; a feature is dead once the count reaches ``dead_threshold`` (trainer.py:403-454 of the reference)."""
+    last fired; a feature is dead once the count reaches ``dead_threshold`` (trainer.py:403-454 of the reference).
+
+    Nothing here makes the host wait for the device. The dead features of a step are gathered into a compact dictionary
+    of ``capacity`` rows for the auxiliary encoder pass; the capacity follows the number of dead features with a lag: the
+    count of every step is copied to pinned memory and read once its copy has completed, a step or two later, and the
+    capacity is then set to twice that count (at least ``k_aux``, in steps of 256 rows). Should the dead features of a
+    step outnumber the capacity (they grow faster than 2x within the lag), that step's auxiliary top-k sees the first
+    ``capacity`` of them by index; ``truncated_steps`` counts such steps."""
 
     def __init__(self, n_features: int, k_aux: int, coefficient: float, dead_threshold: float, device, counter: torch.Tensor | None = None):
         self.k_aux, self.coefficient, self.dead_threshold = int(k_aux), float(coefficient), dead_threshold
+        self.n_features = n_features
         self.tokens_since_last_activation = counter if counter is not None else torch.zeros(n_features, dtype=torch.long, device=device)
         self.is_dead = self.tokens_since_last_activation >= dead_threshold
+        self.capacity = self._bucket(int(self.is_dead.sum()))
+        self.truncated_steps = torch.zeros((), dtype=torch.long, device=device)
+        self._pending: tuple[torch.Tensor, object] | None = None
 
-    def update(self, fire_counts: torch.Tensor, n_valid_tokens) -> torch.Tensor:
+    def _bucket(self, n_dead: int) -> int:
+        rows = max(self.k_aux, 2 * n_dead, 1024)
+        return min(-(-self.n_features // 8) * 8, -(-rows // 256) * 256)
+
+    def update(self, fired: torch.Tensor, n_valid_tokens) -> torch.Tensor:
+        """``fired``: per feature, non-zero where it fired in this step (over every replica); ``n_valid_tokens``: number or
+        0-d tensor of valid tokens of the (global) step."""
         c = self.tokens_since_last_activation
-        self.tokens_since_last_activation = torch.where(fire_counts > 0, torch.zeros_like(c), c + int(n_valid_tokens))
+        self.tokens_since_last_activation = torch.where(fired > 0, torch.zeros_like(c), c + n_valid_tokens)
         self.is_dead = self.tokens_since_last_activation >= self.dead_threshold
         return self.is_dead
+
+    def observe(self, n_dead: torch.Tensor) -> None:
+        """Feed the lagged capacity estimate with this step's number of dead features (0-d device tensor)."""
+        self.truncated_steps += n_dead > self.capacity
+        if not n_dead.is_cuda:
+            self.capacity = self._bucket(int(n_dead))
+            return
+        if self._pending is not None:
+            host, ev = self._pending
+            if not ev.query():
+                return  # the previous copy is still in flight: keep the capacity, look again next step
+            self.capacity = self._bucket(int(host))
+        host = torch.empty((), dtype=torch.long, pin_memory=True)
+        host.copy_(n_dead, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._pending = (host, ev)
 
 
 class FusedTopKSAEStep:
@@ -108,6 +142,8 @@ class FusedTopKSAEStep:
         self.groups: K.FeatureGroups | None = None
         self.loss_sum = z(1)
         self.aux_sum = z(1)
+        self.batch_list_factor = int(os.environ.get("LMSAE_BATCH_LIST_FACTOR", "4"))
+        self.list_overflow = torch.zeros(1, dtype=torch.int64, device=dev)  # tokens whose batch-level codes did not fit
         self.last_aux_loss: torch.Tensor | None = None
         self.main_counts: torch.Tensor | None = None
         self.grad_sq = z(1)
@@ -158,8 +194,6 @@ class FusedTopKSAEStep:
             checks += [
                 (trainer_cfg.sparsity_loss_type is None, "sparsity loss"),
                 (not trainer_cfg.lp_coefficient, "lp loss"),
-                (not trainer_cfg.auxk_coefficient or mesh_dim_size(sae.device_mesh, "data") == 1, "aux-k loss with data parallelism"),
-                (not trainer_cfg.auxk_coefficient or cfg.act_fn == "topk", "aux-k loss with a batch-level top-k"),
                 (trainer_cfg.optimizer_class == "adam", "optimizer is not adam"),
                 (trainer_cfg.amp_dtype == torch.bfloat16, "amp dtype is not bf16"),
                 (trainer_cfg.gradient_accumulation_steps == 1, "gradient accumulation"),
@@ -342,8 +376,10 @@ class FusedTopKSAEStep:
         """BatchTopK: keep the ``k * batch`` largest gated pre-activations of the whole batch (over all feature shards)
         instead of ``k`` per token (models/sparse_dictionary.py:775-788 of the reference project). The GEMM stores the
         gated pre-activations in bf16, a radix select over their bit patterns finds the threshold (shards add their
-        histograms), and one compaction pass turns the survivors into padded code lists: the rows' code counts differ,
-        the list width is the largest count (one host read per step)."""
+        histograms), and one compaction pass turns the survivors into padded code lists. The rows' code counts differ;
+        the lists have a fixed width of ``batch_list_factor * k`` (default 4) so that nothing is read back to the host.
+        A token with more codes than that keeps its first ones by column and is counted in ``self.list_overflow``,
+        which the trainer reports with the metrics."""
         from . import select_kernels as S
 
         self.join()
@@ -352,8 +388,8 @@ class FusedTopKSAEStep:
         tp_group = self.tp_group if self.tp > 1 else None
         thr, n_ties = S.positive_thresholds(G.view(1, 1, -1), k * B, tp_group, return_remaining=True)
         # exactly k * B codes: of the entries equal to the (bf16) threshold only as many as the selection still needs
-        return S.threshold_rows_to_sparse(G, thr, gate, width_group=self.dp_group if self.dp > 1 else None,
-                                          n_ties=n_ties, tie_group=tp_group)
+        cap = -(-self.batch_list_factor * k // 8) * 8
+        return S.threshold_rows_to_sparse(G, thr, gate, n_ties=n_ties, tie_group=tp_group, cap=cap, overflow=self.list_overflow)
 
     def step(
         self,
@@ -379,7 +415,7 @@ class FusedTopKSAEStep:
         B = x.shape[0]
         n_global = n_tokens_global if n_tokens_global is not None else B * self.dp
         grad_scale = 2.0 / n_global
-        use_comm = self.tp > 1 and self.comm is not None and B == self.comm.B and k <= self.comm.k_max and not self.batch_level
+        use_comm = self.tp > 1 and self.comm is not None and B == self.comm.B and (self.batch_level or k <= self.comm.k_max)
         sharded = self.dp_comm is not None
         overlap = len(self.chunks) > 1 and k <= 64 and grad_mul is None and not want_grad_norm and not clip_grad_norm and not sharded
         self._mark("begin")
@@ -390,8 +426,7 @@ class FusedTopKSAEStep:
         self.loss_sum.zero_()
         if use_comm:
             # loss_sum collects the rows this rank owns; scale to a local-batch estimate for the return value
-            dxhat, _ = self.comm.decode_reduce_loss(idx, act, self.WD_bf16, label, self.bD, row_weight, grad_scale, self.loss_sum,
-                                                    compact_codes=not self.batch_level)  # fmt: skip
+            dxhat, _ = self.comm.decode_reduce_loss(idx, act, self.WD_bf16, label, self.bD, row_weight, grad_scale, self.loss_sum)
             self._mark("decode_reduce_loss")
             dact = self.comm.dact(idx, self.WD_bf16)  # waits for the owners' gradient rows inside the kernel
             self._mark("dact")
@@ -493,75 +528,79 @@ class FusedTopKSAEStep:
         return torch.where(norm > max_norm, max_norm / (norm + 1e-6), torch.ones_like(norm)).reshape(1)
 
     def _step_auxk(self, x, label, k, lr, row_weight, n_tokens_global, aux: "AuxK", clip_grad_norm: float = 0.0) -> torch.Tensor:
-        """The step with the Aux-K loss (one GPU or feature shards): ``l = |e|^2 + alpha |e - e_aux|^2`` where ``e_aux`` decodes the
-        ``k_aux`` largest gated pre-activations among DEAD features (models/sparse_dictionary.py:941-991 and
-        trainer.py:428-454 of the reference project). The dead features are gathered into a compact dictionary
-        first, so the second encoder pass costs ``n_dead / F`` of the main one instead of a full pass."""
-        assert self.dp == 1, "the fused Aux-K step is not data parallel (use the generic path for that mesh)"
-        assert self.dp_comm is None
+        """The step with the Aux-K loss: ``l = |e|^2 + alpha |e - e_aux|^2`` where ``e_aux`` decodes the ``k_aux`` largest
+        gated pre-activations among DEAD features (models/sparse_dictionary.py:941-991 and trainer.py:428-454 of the
+        reference project). The dead features are gathered into a compact dictionary of fixed capacity first (see
+        ``AuxK``), so the second encoder pass costs ``capacity / F`` of the main one instead of a full pass, and no size
+        travels through the host: with fewer dead features than ``k_aux`` the lists simply hold fewer codes, and with
+        none the auxiliary term is switched off by a device-side factor. Works on one GPU, with feature shards (the
+        auxiliary top-k is merged over shards, both reconstructions are summed over them) and with data-parallel
+        replicas (dead statistics over the global batch, rows of both gradients exchanged before the update)."""
+        assert self.dp_comm is None, "Aux-K with data parallelism uses the collective row exchange"
         self.join()
         B = x.shape[0]
-        n_global = n_tokens_global if n_tokens_global is not None else B
+        n_global = n_tokens_global if n_tokens_global is not None else B * self.dp
         grad_scale = 2.0 / n_global
         gate = self.dec_norm if self.use_gate else None
         idx, act = self.encode(x, k)
-        if self.groups is None or self.groups.entries.numel() < B * (k + aux.k_aux):
-            self.groups = K.FeatureGroups(self.F, B * (k + aux.k_aux), x.device)
+        kw = idx.shape[1]  # width of the main code lists (k, or the fixed list width of a batch-level top-k)
+        if self.groups is None or self.groups.entries.numel() < B * self.dp * (kw + aux.k_aux):
+            self.groups = K.FeatureGroups(self.F, B * self.dp * (kw + aux.k_aux), x.device)
         # dead statistics first (they include this batch), from the per-feature fire counts of the main codes
         self.groups.build(idx)
-        n_valid = B if row_weight is None else (row_weight > 0).sum()  # the weights may carry a normalisation factor
         self.main_counts = self.groups.counts[: self.F].clone()  # fire counts of the real codes (for metrics)
-        is_dead = aux.update(self.main_counts, n_valid)
-        dead_idx = is_dead.nonzero().squeeze(-1)
-        n_dead = int(dead_idx.numel())  # host sync, as in the reference (min(k_aux, n_dead) is a Python int there)
-        n_dead_all = n_dead
+        fired = self.main_counts
+        n_valid = torch.tensor(B, device=x.device) if row_weight is None else (row_weight > 0).sum()
+        if self.dp > 1:  # a feature is alive when it fired on any replica; the counters advance by the global token count
+            fired, n_valid = fired.clone(), n_valid.clone()
+            dist.all_reduce(fired, group=self.dp_group)
+            dist.all_reduce(n_valid, group=self.dp_group)
+        is_dead = aux.update(fired, n_valid)
+        n_dead = is_dead.sum()
+        cap = min(aux.capacity, -(-self.F // 8) * 8)
+        aux.observe(n_dead)
+        n_dead_all = n_dead.clone()
         if self.tp > 1:  # the auxiliary top-k runs over the dead features of ALL shards
-            t = torch.tensor([n_dead], device=x.device)
-            dist.all_reduce(t, group=self.tp_group)
-            n_dead_all = int(t)
-        k_aux = min(aux.k_aux, n_dead_all)
+            dist.all_reduce(n_dead_all, group=self.tp_group)
+        alpha_on = (n_dead_all > 0).float().reshape(1)  # no dead feature anywhere: the auxiliary term is absent, not |e|^2
+        # compact dictionary of this shard's dead features: dead rows first (ascending), alive rows behind them with gate 0
+        order = torch.argsort((~is_dead).to(torch.int8), stable=True)[:cap]
+        if order.numel() < cap:  # fewer rows than the (rounded) capacity: repeat row 0 with gate 0
+            order = torch.cat([order, order.new_zeros(cap - order.numel())])
+            valid = torch.cat([is_dead[order[: self.F]], is_dead.new_zeros(cap - self.F)])
+        else:
+            valid = is_dead[order]
+        w_dead = self.WE_bf16[order]
+        b_dead = self.bE[order]
+        g_dead = (gate[order] if gate is not None else torch.ones(cap, device=x.device)) * valid
         self.loss_sum.zero_()
         self.aux_sum.zero_()
         xhat = K.sparse_decode(idx, act, self.WD_bf16, None, torch.float32)
-        if k_aux > 0:
-            # compact dictionary of this shard's dead features, padded to a multiple of 8 rows and to at least k_aux
-            pad = -(-max(n_dead, k_aux) // 8) * 8 - n_dead
-            rows = torch.cat([dead_idx, dead_idx.new_zeros(pad)]) if pad else dead_idx
-            w_dead = self.WE_bf16[rows]
-            b_dead = self.bE[rows]
-            g_dead = (gate[rows] if gate is not None else torch.ones(rows.numel(), device=x.device)).clone()
-            if pad:
-                g_dead[n_dead:] = 0.0  # padding rows can never be selected: their gated value is 0
-            idx_c, act_aux = K.encoder_topk(x, w_dead, b_dead, g_dead, k_aux)
-            if self.tp > 1:
-                idx_c, act_aux = self._merge_shard_codes(idx_c, act_aux, g_dead, k_aux)
-            idx_aux = torch.where(idx_c >= 0, rows[idx_c.clamp_min(0).long()].to(torch.int32), idx_c)
-            aux_rec = K.sparse_decode(idx_aux, act_aux, self.WD_bf16, None, torch.float32)
-        else:
-            idx_aux = torch.full((B, 0), -1, dtype=torch.int32, device=x.device)
-            act_aux = torch.zeros(B, 0, device=x.device)
-            aux_rec = torch.zeros_like(xhat)
+        idx_c, act_aux = K.encoder_topk(x, w_dead, b_dead, g_dead, aux.k_aux)
+        if self.tp > 1:
+            idx_c, act_aux = self._merge_shard_codes(idx_c, act_aux, g_dead, aux.k_aux)
+        idx_aux = torch.where(idx_c >= 0, order[idx_c.clamp_min(0).long()].to(torch.int32), idx_c)
+        aux_rec = K.sparse_decode(idx_aux, act_aux, self.WD_bf16, None, torch.float32)
         if self.tp > 1:  # both reconstructions are sums over the shards' features
             both = torch.stack([xhat, aux_rec])
             dist.all_reduce(both, group=self.tp_group)
             xhat, aux_rec = both[0], both[1]
-        alpha = aux.coefficient if k_aux > 0 else 0.0  # no dead feature: the auxiliary term is absent, not |e|^2
-        g_main, g_aux = K.auxk_loss_grad(xhat, aux_rec, label, self.bD, row_weight, grad_scale, alpha, self.loss_sum, self.aux_sum)
+        g_main, g_aux = K.auxk_loss_grad(xhat, aux_rec, label, self.bD, row_weight, grad_scale, aux.coefficient, self.loss_sum,
+                                         self.aux_sum, alpha_factor=alpha_on)  # fmt: skip
         dact = K.sparse_dact(idx, self.WD_bf16, g_main)
-        if k_aux > 0:
-            idx_all = torch.cat([idx, idx_aux], dim=1).contiguous()
-            act_all = torch.cat([act, act_aux], dim=1).contiguous()
-            dact_all = torch.cat([dact, K.sparse_dact(idx_aux, self.WD_bf16, g_aux)], dim=1).contiguous()
-            self.groups.build(idx_all)
-        else:
-            idx_all, act_all, dact_all = idx, act, dact
+        idx_all = torch.cat([idx, idx_aux], dim=1).contiguous()
+        act_all = torch.cat([act, act_aux], dim=1).contiguous()
+        dact_all = torch.cat([dact, K.sparse_dact(idx_aux, self.WD_bf16, g_aux)], dim=1).contiguous()
+        if self.dp > 1:
+            x, g_main, g_aux, idx_all, act_all, dact_all = self._gather_rows(x, g_main, g_aux, idx_all, act_all, dact_all)
+        self.groups.build(idx_all)
         self.t += 1
         b1, b2 = self.betas
         (mE, vE), (mD, vD), (mb, vb) = self.state["W_E"], self.state["W_D"], self.state["b_E"]
         sparse = lambda mul, sq, update: K.sparse_grad_adam(  # noqa: E731
             self.groups, act_all, dact_all, x, g_main, self.WD, mD, vD, self.WD_bf16, self.WE, mE, vE, self.WE_bf16,
             self.bE, mb, vb, self.dec_norm, mul, sq, lr, b1, b2, self.eps, self.t, update,
-            dxhat_aux=g_aux if k_aux > 0 else None, k_main=k,
+            dxhat_aux=g_aux, k_main=kw,
         )  # fmt: skip
         g_bD = K.colsum_bf16(g_main) if self.bD is not None else None
         grad_mul = self._clip_factor(sparse, g_bD, clip_grad_norm) if clip_grad_norm else None

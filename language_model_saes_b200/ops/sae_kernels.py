@@ -385,12 +385,15 @@ def mse_loss_grad(xhat, label, bias, row_weight, grad_scale, loss_sum, row_loss=
     return dxhat
 
 
-def auxk_loss_grad(xhat, aux_rec, label, bias, row_weight, grad_scale, alpha, loss_sum, aux_sum):
+def auxk_loss_grad(xhat, aux_rec, label, bias, row_weight, grad_scale, alpha, loss_sum, aux_sum, alpha_factor=None):
     """Main and auxiliary (dead-feature) reconstruction losses and their output gradients for fp32 rows:
     ``e = label - (xhat + bias)``, ``r = e - aux_rec``; accumulates ``sum rw * |e|^2`` into ``loss_sum`` and
     ``alpha * sum rw * |r|^2`` into ``aux_sum``; returns bf16 ``(g_main, g_aux)`` with
-    ``g_main = -(e + alpha r) * grad_scale * rw`` and ``g_aux = -alpha r * grad_scale * rw``."""
+    ``g_main = -(e + alpha r) * grad_scale * rw`` and ``g_aux = -alpha r * grad_scale * rw``. ``alpha_factor``: optional
+    one-element fp32 device tensor that multiplies ``alpha`` (0 switches the auxiliary term off without a host read)."""
     if not xhat.is_cuda:
+        if alpha_factor is not None:
+            alpha = alpha * float(alpha_factor)
         xh = xhat + (bias if bias is not None else 0.0)
         e = label.float() - xh
         r = e - aux_rec
@@ -401,7 +404,7 @@ def auxk_loss_grad(xhat, aux_rec, label, bias, row_weight, grad_scale, alpha, lo
         return (-(e + alpha * r) * sc).to(torch.bfloat16), (-alpha * r * sc).to(torch.bfloat16)
     g_main = torch.empty(xhat.shape, dtype=torch.bfloat16, device=xhat.device)
     g_aux = torch.empty_like(g_main)
-    _ext().auxk_loss_grad(xhat, aux_rec, label, bias, row_weight, grad_scale, alpha, g_main, g_aux, loss_sum, aux_sum)
+    _ext().auxk_loss_grad(xhat, aux_rec, label, bias, row_weight, grad_scale, alpha, g_main, g_aux, loss_sum, aux_sum, alpha_factor)
     return g_main, g_aux
 
 

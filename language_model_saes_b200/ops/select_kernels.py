@@ -172,7 +172,8 @@ def dense_rows_to_sparse(acts: torch.Tensor, cap: int | None = None) -> tuple[to
 
 @torch.no_grad()
 def threshold_rows_to_sparse(g: torch.Tensor, thr: torch.Tensor, col_div: torch.Tensor | None = None, width_group=None,
-                             n_ties: torch.Tensor | None = None, tie_group=None) -> tuple[torch.Tensor, torch.Tensor]:  # fmt: skip
+                             n_ties: torch.Tensor | None = None, tie_group=None, cap: int | None = None,
+                             overflow: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:  # fmt: skip
     """Entries of ``g [B, N]`` that reach the (positive) threshold ``thr`` (one-element fp32 tensor) as padded sparse lists,
     values divided by ``col_div[column]`` when given: the codes of a batch-level top-k straight from the gated
     pre-activations, without a masked dense tensor in between.
@@ -180,17 +181,23 @@ def threshold_rows_to_sparse(g: torch.Tensor, thr: torch.Tensor, col_div: torch.
     ``n_ties`` (one-element integer tensor: how many entries EQUAL to the threshold belong to the selection, as
     ``positive_thresholds(..., return_remaining=True)`` reports it) makes the number of codes exact when the threshold
     value repeats (16-bit data): ties are granted in (rank of ``tie_group``, row, column) order until the count is
-    used up. Without it every tie is kept."""
+    used up. Without it every tie is kept.
+
+    ``cap``: fixed list width (a multiple of 8). Without it the width is the widest row's count, which costs one host
+    read per call; with it nothing is read back: a row with more than ``cap`` selected entries keeps its first ``cap``
+    (ascending column) and the number of such rows is added to ``overflow`` (one-element integer device tensor) for
+    the caller to look at when it next synchronises anyway."""
     if not _kernel_ok(g):
-        return _ref_threshold_rows_to_sparse(g, thr, col_div, width_group, n_ties, tie_group)
+        return _ref_threshold_rows_to_sparse(g, thr, col_div, width_group, n_ties, tie_group, cap, overflow)
     ext = K._ext()
     g = g.contiguous()
     B = g.shape[0]
     nnz = torch.empty(B, dtype=torch.int32, device=g.device)
     quota = None
     if n_ties is None:
-        ext.row_compact(g, None, None, nnz, thr, None, None, None)
-        widest = nnz.max()
+        if cap is None:
+            ext.row_compact(g, None, None, nnz, thr, None, None, None)
+            widest = nnz.max()
     else:
         ties = torch.empty(B, dtype=torch.int32, device=g.device)
         ext.row_compact(g, None, None, nnz, thr, None, ties, None)
@@ -202,17 +209,22 @@ def threshold_rows_to_sparse(g: torch.Tensor, thr: torch.Tensor, col_div: torch.
             budget = budget - torch.cat(every)[: dist.get_rank(tie_group)].sum()  # earlier ranks are served first
         before = torch.cumsum(ties, 0, dtype=torch.int64) - ties
         quota = (budget - before).clamp(min=0).minimum(ties.to(torch.int64)).to(torch.int32)
-        widest = (nnz + quota).max()
-    if width_group is not None and dist.get_world_size(width_group) > 1:
-        dist.all_reduce(widest, op=dist.ReduceOp.MAX, group=width_group)  # ranks that exchange their lists need one width
-    cap = max(8, -(-int(widest) // 8) * 8)
+        if cap is None:
+            widest = (nnz + quota).max()
+    if cap is None:
+        if width_group is not None and dist.get_world_size(width_group) > 1:
+            dist.all_reduce(widest, op=dist.ReduceOp.MAX, group=width_group)  # ranks that exchange their lists need one width
+        cap = max(8, -(-int(widest) // 8) * 8)
+    assert cap % 8 == 0 and cap > 0
     idx = torch.empty(B, cap, dtype=torch.int32, device=g.device)
     val = torch.empty(B, cap, dtype=torch.float32, device=g.device)
-    ext.row_compact(g, idx, val, nnz, thr, col_div, None, quota)
+    ext.row_compact(g, idx, val, nnz, thr, col_div, None, quota)  # nnz: the row's full count, also beyond the list width
+    if overflow is not None:
+        overflow += (nnz > cap).sum()
     return idx, val
 
 
-def _ref_threshold_rows_to_sparse(g, thr, col_div, width_group, n_ties, tie_group):
+def _ref_threshold_rows_to_sparse(g, thr, col_div, width_group, n_ties, tie_group, cap=None, overflow=None):
     """Plain-torch statement of ``threshold_rows_to_sparse`` (any device): same selection, same order."""
     gf = g.float()
     t = thr.reshape(()).float()
@@ -229,16 +241,19 @@ def _ref_threshold_rows_to_sparse(g, thr, col_div, width_group, n_ties, tie_grou
             budget = budget - torch.cat(every)[: dist.get_rank(tie_group)].sum()
         rank_of_tie = torch.cumsum(ties.reshape(-1).to(torch.int64), 0).reshape(ties.shape) - 1  # row-major order
         keep = keep | (ties & (rank_of_tie < budget))
-    widest = keep.sum(-1).max()
-    if width_group is not None and dist.get_world_size(width_group) > 1:
-        dist.all_reduce(widest, op=dist.ReduceOp.MAX, group=width_group)
-    cap = max(8, -(-int(widest) // 8) * 8)
+    if cap is None:
+        widest = keep.sum(-1).max()
+        if width_group is not None and dist.get_world_size(width_group) > 1:
+            dist.all_reduce(widest, op=dist.ReduceOp.MAX, group=width_group)
+        cap = max(8, -(-int(widest) // 8) * 8)
+    elif overflow is not None:
+        overflow += (keep.sum(-1) > cap).sum()
     vals = gf / col_div.float() if col_div is not None else gf
     B = g.shape[0]
     idx = torch.full((B, cap), -1, dtype=torch.int32, device=g.device)
     val = torch.zeros(B, cap, dtype=torch.float32, device=g.device)
     for b in range(B):
-        cols = torch.nonzero(keep[b], as_tuple=False).flatten()
+        cols = torch.nonzero(keep[b], as_tuple=False).flatten()[:cap]
         idx[b, : cols.numel()] = cols.to(torch.int32)
         val[b, : cols.numel()] = vals[b, cols]
     return idx, val

@@ -676,7 +676,14 @@ class Trainer:
             before = float(acc["grad_norm"])
             out["metrics/gradient_norm_before_clipping"] = before
             out["metrics/gradient_norm_per_param"] = min(before, self.cfg.clip_grad_norm)
+        if f.batch_level:  # tokens whose batch-level codes exceeded the fixed list width since the last report
+            out["details/batchtopk_list_overflow_tokens"] = int(f.list_overflow)
+            f.list_overflow.zero_()
+        if self._fused_aux is not None:
+            out["details/auxk_dead_capacity"] = self._fused_aux.capacity
+            out["details/auxk_truncated_steps"] = int(self._fused_aux.truncated_steps)
         out.update(self._details({}, lr))
+        f.sync_params()  # (no-op unless the optimizer state is sharded over replicas)
         out.update(sae.log_statistics())
         self._interval = {}
         self._emit(sae, out)
