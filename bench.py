@@ -1,6 +1,6 @@
 """Headline benchmark: SAE training tokens/s, d_model 4096 x d_sae 131072 TopK(k=50), batch 4096, bf16 compute.
 
-    python bench.py --gpus N --steps K --warmup W [--impl reference]
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--config 3|4|5]
 
 One rank per GPU (launched through torch.distributed.run for N > 1); the dictionary is feature-sharded N ways
 ("model" mesh dimension) and the global batch stays 4096 tokens, so scaling is strong. Prints ONE JSON line on
@@ -36,6 +36,8 @@ def parse():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", type=int, default=2, choices=[2, 3, 4, 5],
+                    help="benchmark configuration: 2 = the headline TopK SAE (default); 3, 4, 5: see bench_configs.py")
     return ap.parse_args()
 
 
@@ -371,6 +373,11 @@ def run_ours(args):
 
 def main():
     args = parse()
+    if args.config != 2:
+        import bench_configs
+
+        getattr(bench_configs, f"run_config{args.config}")(args, sys.modules[__name__])
+        return
     if args.impl == "reference":
         from baseline.reference_arm import run_reference
 

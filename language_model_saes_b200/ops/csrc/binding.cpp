@@ -352,7 +352,9 @@ void sparse_grad_adam(const Tensor& offsets, const Tensor& entries, const Tensor
                       const c10::optional<Tensor>& gD_out, const c10::optional<Tensor>& gE_out,
                       const c10::optional<Tensor>& status, int64_t state_f0, const std::vector<int64_t>& pub_table,
                       const std::vector<int64_t>& pub_offsets, int64_t pub_epoch,
-                      const c10::optional<Tensor>& pub_done) {
+                      const c10::optional<Tensor>& pub_done, const c10::optional<Tensor>& extra_row,
+                      const c10::optional<Tensor>& extra_gD, const c10::optional<Tensor>& extra_gE,
+                      const c10::optional<Tensor>& extra_gb) {
   CHECK_T(offsets, torch::kInt32);
   CHECK_T(entries, torch::kInt32);
   CHECK_T(act, torch::kFloat32);
@@ -405,6 +407,16 @@ void sparse_grad_adam(const Tensor& offsets, const Tensor& entries, const Tensor
   p.ctas_per_sm = (int)ctas_per_sm;
   if (status.has_value()) { CHECK_T(*status, torch::kInt32); }
   p.status = opt_ptr<const int>(status);
+  if (extra_row.has_value()) {
+    TORCH_CHECK(extra_gD.has_value() && extra_gE.has_value(), "extra gradient rows come with both matrices");
+    CHECK_T(*extra_row, torch::kInt32); CHECK_T(*extra_gD, torch::kFloat32); CHECK_T(*extra_gE, torch::kFloat32);
+    TORCH_CHECK(extra_row->numel() == p.F && extra_gD->dim() == 2 && extra_gD->size(1) == p.d && extra_gE->sizes() == extra_gD->sizes());
+    p.extra_row = extra_row->data_ptr<int>();
+    p.extra_gD = extra_gD->data_ptr<float>();
+    p.extra_gE = extra_gE->data_ptr<float>();
+    if (extra_gb.has_value()) { CHECK_T(*extra_gb, torch::kFloat32); TORCH_CHECK(extra_gb->numel() == extra_gD->size(0)); }
+    p.extra_gb = opt_ptr<const float>(extra_gb);
+  }
   if (!pub_table.empty()) {
     p.pub = make_peer_table(pub_table);
     p.n_pub = p.pub.world;

@@ -125,6 +125,10 @@ struct GradAdamParams {
   int f_begin, f_end;  // feature rows handled by this launch
   int ctas_per_sm;     // 0 = fill the GPU (4 per SM); 1..4 = leave registers free for a concurrently running kernel
   const int* status;   // kernels' status word: a recorded error turns the update into a no-op (nullptr: not checked)
+  // Dense gradient rows for a subset of the features, added to the rows rebuilt from the entry lists: feature f takes
+  // row extra_row[f] (when >= 0) of the fp32 matrices extra_gD / extra_gE [rows, d] and element extra_row[f] of extra_gb.
+  const int* extra_row;
+  const float* extra_gD; const float* extra_gE; const float* extra_gb;
   const __nv_bfloat16* dxhat_aux;  // output gradient seen by the code slots >= k_main of every row (nullptr: none)
   int k_main;
   float* gD_out;  // optional dense [F, d] outputs of the rebuilt gradient rows (for autograd callers)

@@ -514,7 +514,8 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
 
   for (int f = p.f_begin + blockIdx.x; f < p.f_end && !skip; f += gridDim.x) {
     const int e0 = p.offsets[f], e1 = p.offsets[f + 1];
-    float bias_g = 0.0f;
+    const int xr = p.extra_row != nullptr ? p.extra_row[f] : -1;
+    float bias_g = (xr >= 0 && p.extra_gb != nullptr) ? p.extra_gb[xr] : 0.0f;
     float norm_sq = 0.0f;
     for (int c0 = 0; c0 < p.d; c0 += GA_THREADS * 4 * VEC) {
       int c[VEC];
@@ -529,6 +530,12 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
         os[v] = (size_t)(f - p.state_f0) * p.d + (in[v] ? c[v] : 0);  // moments
 #pragma unroll
         for (int i = 0; i < 4; ++i) gD[v][i] = gE[v][i] = 0.0f;
+        if (xr >= 0 && in[v]) {
+          const float4 a = *reinterpret_cast<const float4*>(p.extra_gD + (size_t)xr * p.d + c[v]);
+          const float4 b = *reinterpret_cast<const float4*>(p.extra_gE + (size_t)xr * p.d + c[v]);
+          gD[v][0] = a.x; gD[v][1] = a.y; gD[v][2] = a.z; gD[v][3] = a.w;
+          gE[v][0] = b.x; gE[v][1] = b.y; gE[v][2] = b.z; gE[v][3] = b.w;
+        }
       }
       for (int e = e0; e < e1; ++e) {
         const int ent = p.entries[e];

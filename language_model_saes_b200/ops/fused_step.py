@@ -35,6 +35,17 @@ from ..parallel.mesh import mesh_dim_size, mesh_group, mesh_local_rank
 from . import sae_kernels as K
 
 
+def _mm_f32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """``a @ b`` for bf16 matrices with an fp32 result (a plain library GEMM: fp32 accumulation, no bf16 rounding of the
+    output, so that sums over feature shards or replicas do not depend on how the work was split)."""
+    if a.is_cuda:
+        try:
+            return torch.mm(a, b, out_dtype=torch.float32)
+        except (TypeError, RuntimeError):  # a build without the out_dtype overload: bf16 output, widened afterwards
+            return (a @ b).float()
+    return a.float() @ b.float()
+
+
 class AuxK:
     """State and settings of the Aux-K loss on the fused path: per-feature count of valid tokens since the feature
     last fired; a feature is dead once the count reaches ``dead_threshold`` (trainer.py:403-454 of the reference).
@@ -142,7 +153,7 @@ class FusedTopKSAEStep:
         self.groups: K.FeatureGroups | None = None
         self.loss_sum = z(1)
         self.aux_sum = z(1)
-        self.batch_list_factor = int(os.environ.get("LMSAE_BATCH_LIST_FACTOR", "4"))
+        self.batch_list_factor = int(os.environ.get("LMSAE_BATCH_LIST_FACTOR", "8"))
         self.list_overflow = torch.zeros(1, dtype=torch.int64, device=dev)  # tokens whose batch-level codes did not fit
         self.last_aux_loss: torch.Tensor | None = None
         self.main_counts: torch.Tensor | None = None
@@ -377,7 +388,7 @@ class FusedTopKSAEStep:
         instead of ``k`` per token (models/sparse_dictionary.py:775-788 of the reference project). The GEMM stores the
         gated pre-activations in bf16, a radix select over their bit patterns finds the threshold (shards add their
         histograms), and one compaction pass turns the survivors into padded code lists. The rows' code counts differ;
-        the lists have a fixed width of ``batch_list_factor * k`` (default 4) so that nothing is read back to the host.
+        the lists have a fixed width of ``batch_list_factor * k`` (default 8) so that nothing is read back to the host.
         A token with more codes than that keeps its first ones by column and is counted in ``self.list_overflow``,
         which the trainer reports with the metrics."""
         from . import select_kernels as S
@@ -505,7 +516,7 @@ class FusedTopKSAEStep:
             n_local = n_local / self.tp  # each rank evaluated the loss on the B / tp rows it owns
         return (self.loss_sum / n_local).squeeze(0)
 
-    def _clip_factor(self, sparse, g_bD: torch.Tensor | None, max_norm: float) -> torch.Tensor:
+    def _clip_factor(self, sparse, g_bD: torch.Tensor | None, max_norm: float, extra_fired: torch.Tensor | None = None) -> torch.Tensor:
         """The trainer's clipping factor as a 1-element device tensor. The norm is the reference project's
         (optim.py:255-292 there): ``|g|_2 / sqrt(number of non-zero gradient entries)``, and the gradient is scaled by
         ``max_norm / (norm + 1e-6)`` only when the norm exceeds ``max_norm``. ``sparse(mul, sq, update)`` launches the
@@ -516,6 +527,8 @@ class FusedTopKSAEStep:
         sparse(None, self.grad_sq, False)
         lo, hi = self.own_rows  # the rows this replica rebuilt gradients for (all of them unless the state is sharded)
         fired = (self.groups.counts[lo:hi] > 0).sum().float().reshape(1)
+        if extra_fired is not None:  # features that received gradient rows from elsewhere only (dead features of Aux-K)
+            fired = fired + extra_fired
         acc = torch.cat([self.grad_sq, fired * (2 * self.d + 1)])
         if self.tp > 1:
             dist.all_reduce(acc, group=self.tp_group)
@@ -536,16 +549,17 @@ class FusedTopKSAEStep:
         none the auxiliary term is switched off by a device-side factor. Works on one GPU, with feature shards (the
         auxiliary top-k is merged over shards, both reconstructions are summed over them) and with data-parallel
         replicas (dead statistics over the global batch, rows of both gradients exchanged before the update)."""
-        assert self.dp_comm is None, "Aux-K with data parallelism uses the collective row exchange"
         self.join()
+        if self.dp_comm is not None:
+            self.dp_comm.wait_params()  # the other replicas' rows of the previous update must have landed in the shadows
         B = x.shape[0]
         n_global = n_tokens_global if n_tokens_global is not None else B * self.dp
         grad_scale = 2.0 / n_global
         gate = self.dec_norm if self.use_gate else None
         idx, act = self.encode(x, k)
         kw = idx.shape[1]  # width of the main code lists (k, or the fixed list width of a batch-level top-k)
-        if self.groups is None or self.groups.entries.numel() < B * self.dp * (kw + aux.k_aux):
-            self.groups = K.FeatureGroups(self.F, B * self.dp * (kw + aux.k_aux), x.device)
+        if self.groups is None or self.groups.entries.numel() < B * self.dp * kw:
+            self.groups = K.FeatureGroups(self.F, B * self.dp * kw, x.device)
         # dead statistics first (they include this batch), from the per-feature fire counts of the main codes
         self.groups.build(idx)
         self.main_counts = self.groups.counts[: self.F].clone()  # fire counts of the real codes (for metrics)
@@ -571,16 +585,24 @@ class FusedTopKSAEStep:
         else:
             valid = is_dead[order]
         w_dead = self.WE_bf16[order]
+        wd_dead = self.WD_bf16[order]
         b_dead = self.bE[order]
         g_dead = (gate[order] if gate is not None else torch.ones(cap, device=x.device)) * valid
         self.loss_sum.zero_()
         self.aux_sum.zero_()
         xhat = K.sparse_decode(idx, act, self.WD_bf16, None, torch.float32)
+        # The auxiliary codes hold up to k_aux (hundreds of) entries per token, several times the main codes, but all of
+        # them index the compact dictionary: products with its [cap, d] matrices are small dense GEMMs, far cheaper than
+        # gathering a decoder row per code, so the auxiliary decode and its three gradients are dense over the compact
+        # dictionary and only their result rows are handed to the update kernel.
+        # (the selection itself: fused into the GEMM epilogue up to 64 codes, else over stored bf16 pre-activations)
         idx_c, act_aux = K.encoder_topk(x, w_dead, b_dead, g_dead, aux.k_aux)
         if self.tp > 1:
             idx_c, act_aux = self._merge_shard_codes(idx_c, act_aux, g_dead, aux.k_aux)
-        idx_aux = torch.where(idx_c >= 0, order[idx_c.clamp_min(0).long()].to(torch.int32), idx_c)
-        aux_rec = K.sparse_decode(idx_aux, act_aux, self.WD_bf16, None, torch.float32)
+        A = torch.zeros(B, cap + 1, dtype=torch.bfloat16, device=x.device)  # dense dead activations (+ one dump column)
+        A.scatter_(1, torch.where(idx_c >= 0, idx_c, torch.full_like(idx_c, cap)).long(), act_aux.to(torch.bfloat16))
+        A = A[:, :cap]
+        aux_rec = _mm_f32(A, wd_dead)
         if self.tp > 1:  # both reconstructions are sums over the shards' features
             both = torch.stack([xhat, aux_rec])
             dist.all_reduce(both, group=self.tp_group)
@@ -588,22 +610,44 @@ class FusedTopKSAEStep:
         g_main, g_aux = K.auxk_loss_grad(xhat, aux_rec, label, self.bD, row_weight, grad_scale, aux.coefficient, self.loss_sum,
                                          self.aux_sum, alpha_factor=alpha_on)  # fmt: skip
         dact = K.sparse_dact(idx, self.WD_bf16, g_main)
-        idx_all = torch.cat([idx, idx_aux], dim=1).contiguous()
-        act_all = torch.cat([act, act_aux], dim=1).contiguous()
-        dact_all = torch.cat([dact, K.sparse_dact(idx_aux, self.WD_bf16, g_aux)], dim=1).contiguous()
-        if self.dp > 1:
-            x, g_main, g_aux, idx_all, act_all, dact_all = self._gather_rows(x, g_main, g_aux, idx_all, act_all, dact_all)
-        self.groups.build(idx_all)
+        dA = _mm_f32(g_aux, wd_dead.t()) * (A != 0)  # gradient of the dead activations where they were selected
+        extra_gD = _mm_f32(A.t(), g_aux)  # d W_D rows of the compact dictionary
+        extra_gE = _mm_f32(dA.to(torch.bfloat16).t(), x)  # d W_E^T rows
+        extra_gb = dA.sum(0)
+        if self.dp > 1:  # dense rows: summed over replicas (the sparse main part is rebuilt from the exchanged rows below)
+            for t in (extra_gD, extra_gE, extra_gb):
+                dist.all_reduce(t, group=self.dp_group)
+        row_of = torch.full((self.F,), -1, dtype=torch.int32, device=x.device)
+        slots = torch.arange(cap, dtype=torch.int32, device=x.device)
+        row_of.scatter_(0, order.long(), torch.where(valid, slots, torch.full_like(slots, -1)))
+        sharded = self.dp_comm is not None
+        if sharded:
+            g = self.dp_comm.exchange({"x": x, "dxhat": g_main, "idx": idx, "act": act, "dact": dact})
+            x, g_main, idx, act, dact = g["x"], g["dxhat"], g["idx"], g["act"], g["dact"]
+        elif self.dp > 1:
+            x, g_main, idx, act, dact = self._gather_rows(x, g_main, idx, act, dact)
+        self.groups.build(idx)
         self.t += 1
         b1, b2 = self.betas
         (mE, vE), (mD, vD), (mb, vb) = self.state["W_E"], self.state["W_D"], self.state["b_E"]
-        sparse = lambda mul, sq, update: K.sparse_grad_adam(  # noqa: E731
-            self.groups, act_all, dact_all, x, g_main, self.WD, mD, vD, self.WD_bf16, self.WE, mE, vE, self.WE_bf16,
-            self.bE, mb, vb, self.dec_norm, mul, sq, lr, b1, b2, self.eps, self.t, update,
-            dxhat_aux=g_aux, k_main=kw,
-        )  # fmt: skip
+
+        def sparse(mul, sq, update):
+            K.sparse_grad_adam(
+                self.groups, act, dact, x, g_main, self.WD, mD, vD, self.WD_bf16, self.WE, mE, vE, self.WE_bf16,
+                self.bE, mb, vb, self.dec_norm, mul, sq, lr, b1, b2, self.eps, self.t, update,
+                f_range=self.own_rows if sharded else None, state_f0=self.own_rows[0],
+                publish=self.dp_comm.pub_args() if sharded and update else None,
+                extra=(row_of, extra_gD, extra_gE, extra_gb),
+            )  # fmt: skip
+            if sharded and update:
+                self._masters_stale = True
+
         g_bD = K.colsum_bf16(g_main) if self.bD is not None else None
-        grad_mul = self._clip_factor(sparse, g_bD, clip_grad_norm) if clip_grad_norm else None
+        grad_mul = None
+        if clip_grad_norm:
+            lo, hi = self.own_rows
+            got_aux = ((row_of[lo:hi] >= 0) & (self.groups.counts[lo:hi] == 0)).sum().float().reshape(1)
+            grad_mul = self._clip_factor(sparse, g_bD, clip_grad_norm, extra_fired=got_aux)
         sparse(grad_mul, None, True)
         if self.bD is not None:
             m, v = self.state["b_D"]

@@ -503,13 +503,16 @@ def sparse_grad_adam(
     grad_out: tuple[torch.Tensor | None, torch.Tensor | None] = (None, None),
     state_f0: int = 0,
     publish: tuple[list[int], list[int], int, torch.Tensor] | None = None,
+    extra: tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor | None] | None = None,
 ):
     """Rebuild the two sparse gradient rows per feature and apply Adam in the same pass (in place). ``f_range``
     restricts the launch to feature rows ``[begin, end)``. With ``dxhat_aux`` the code slots ``>= k_main`` of every row
     take their output gradient from that matrix instead of ``dxhat`` (auxiliary codes). ``state_f0``: the moment arrays
     start at that feature row (optimizer state sharded by feature row). ``publish`` = ``DataParallelComm.pub_args()``:
-    the new shadow rows, norms and biases are stored into every replica's copy. A non-zero kernel status word turns
-    the update into a no-op (CUDA path)."""
+    the new shadow rows, norms and biases are stored into every replica's copy. ``extra`` = ``(row_of_feature int32 [F],
+    gD fp32 [R, d], gE fp32 [R, d], gb fp32 [R] | None)``: dense gradient rows that are added for the features with
+    ``row_of_feature >= 0`` (e.g. the auxiliary loss over a compact dictionary of dead features). A non-zero kernel
+    status word turns the update into a no-op (CUDA path)."""
     if not WD.is_cuda:
         if f_range is not None and tuple(f_range) != (0, groups.F):
             lo, hi = f_range
@@ -518,10 +521,11 @@ def sparse_grad_adam(
             sub.offsets, sub.entries = groups.offsets[lo : hi + 1], groups.entries
             sl = slice(lo, hi)
             st = slice(lo - state_f0, hi - state_f0)
+            sub_extra = (extra[0][sl], *extra[1:]) if extra is not None else None
             sparse_grad_adam(sub, act, dact, x, dxhat, WD[sl], mD[st], vD[st], WD_bf16[sl], WE[sl], mE[st], vE[st], WE_bf16[sl],
                              bE[sl] if bE is not None else None, mbE[st] if mbE is not None else None,
                              vbE[st] if vbE is not None else None, dec_norm[sl] if dec_norm is not None else None, grad_mul,
-                             grad_sq_sum, lr, beta1, beta2, eps, step, update, None, 0, dxhat_aux, k_main)  # fmt: skip
+                             grad_sq_sum, lr, beta1, beta2, eps, step, update, None, 0, dxhat_aux, k_main, extra=sub_extra)  # fmt: skip
             return
         idx_like = torch.full((act.numel(),), -1, dtype=torch.int64)
         off = groups.offsets.long()
@@ -535,6 +539,14 @@ def sparse_grad_adam(
             parts = [ref_sparse_grads(idx_like[:, sl], act[:, sl], dact[:, sl], x, g, groups.F)
                      for sl, g in ((slice(0, k_main), dxhat), (slice(k_main, None), dxhat_aux))]  # fmt: skip
             gD, gE, gb = (a + b for a, b in zip(*parts))
+        if extra is not None:
+            row_of, xD, xE, xb = extra
+            sel = (row_of >= 0).nonzero().squeeze(-1)
+            r = row_of[sel].long()
+            gD[sel] += xD[r]
+            gE[sel] += xE[r]
+            if xb is not None:
+                gb[sel] += xb[r]
         mul = float(grad_mul) if grad_mul is not None else 1.0
         gD, gE, gb = gD * mul, gE * mul, gb * mul
         if grad_sq_sum is not None:
@@ -553,6 +565,7 @@ def sparse_grad_adam(
         groups.offsets, groups.entries, act, dact, x, dxhat, WD, mD, vD, WD_bf16, WE, mE, vE, WE_bf16, bE, mbE, vbE,
         dec_norm, grad_mul, grad_sq_sum, lr, beta1, beta2, eps, step, update, *(f_range if f_range is not None else (0, -1)), ctas_per_sm, dxhat_aux, k_main, grad_out[0], grad_out[1],
         status_buffer(WD.device), state_f0, *(publish if publish is not None else ([], [], 0, None)),
+        *(extra if extra is not None else (None, None, None, None)),
     )  # fmt: skip
 
 

@@ -479,13 +479,13 @@ class Trainer:
             dp_comm = None
             dp = mesh_dim_size(sae.device_mesh, "data")
             F_l = sae.W_D.shape[0]
-            if self.cfg.use_peer_memory_collectives and dp > 1 and rows and F_l % dp == 0 and not self.cfg.auxk_coefficient:
+            if self.cfg.use_peer_memory_collectives and dp > 1 and rows and F_l % dp == 0:
                 try:
                     from .parallel.symm import DataParallelComm
 
                     # every replica keeps the gathered rows of x, d x_hat and the three code tensors of a step; a
                     # batch-level top-k gives rows of varying width, bounded by the list capacity of its compaction
-                    k_cap = int(max(sae.cfg.top_k, self.cfg.initial_k or 0)) * (4 if sae.cfg.act_fn == "batchtopk" else 1)
+                    k_cap = -(-int(max(sae.cfg.top_k, self.cfg.initial_k or 0)) * (8 if sae.cfg.act_fn == "batchtopk" else 1) // 8) * 8
                     n_rows, d = rows * dp, sae.cfg.d_model
                     zones = {"x": n_rows * d * 2, "dxhat": n_rows * d * 2, "idx": n_rows * k_cap * 4,
                              "act": n_rows * k_cap * 4, "dact": n_rows * k_cap * 4}  # fmt: skip

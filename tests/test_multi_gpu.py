@@ -156,7 +156,38 @@ def test_data_parallel_step_with_row_sharded_optimizer_state_matches_single_gpu(
         assert torch.allclose(st["W_D"]["exp_avg_sq"], st1["W_D"]["exp_avg_sq"], atol=1e-6, rtol=1e-2)
         if sharded:
             assert eng.state["W_D"][0].shape[0] == F // 2  # the moments of half of the rows only
-            assert dp_comm.stats.read(1500.0)["data-parallel rows"]["calls"] == len(xs) + 0
+            assert dp_comm.stats.read(1500.0)["data-parallel rows"]["calls"] == len(xs)
+
+    # the same with the Aux-K loss: dead statistics over the global batch, auxiliary codes and their gradient rows exchanged too
+    from language_model_saes_b200.ops.fused_step import AuxK
+
+    k_aux = 32
+
+    def run_aux(model, dp_comm, rows):
+        eng = FusedTopKSAEStep(model, dp_comm=dp_comm)
+        aux = AuxK(eng.F, k_aux=k_aux, coefficient=1 / 32, dead_threshold=B // 2, device=dev)
+        out = []
+        for x in xs[:3]:
+            loss = eng.step(x[rows], x[rows], k, lr, aux=aux)
+            out.append(torch.stack([loss, eng.last_aux_loss]))
+        eng.sync_params()
+        return eng, aux, torch.stack(out)
+
+    single = SparseAutoEncoder(full.cfg.model_copy())
+    single.load_full_state_dict(full.full_state_dict())
+    _, aux1, want = run_aux(single, None, slice(0, B))
+    assert float(want[:, 1].min()) > 0
+    m = SparseAutoEncoder(full.cfg.model_copy(), mesh)
+    m.load_full_state_dict(full.full_state_dict())
+    n = B
+    zones = {"x": n * d * 2, "dxhat": n * d * 2, "idx": n * k * 4, "act": n * k * 4, "dact": n * k * 4}
+    _, aux2, got = run_aux(m, DataParallelComm(mesh.get_group("data"), dev, F, d, zones), slice(rank * half, (rank + 1) * half))
+    K.check_status(dev)
+    dist.all_reduce(got)
+    got /= 2
+    assert torch.allclose(got, want, rtol=3e-3), (got, want)
+    assert torch.equal(aux2.tokens_since_last_activation, aux1.tokens_since_last_activation)
+    assert torch.allclose(m.W_D.data, single.W_D.data, atol=2e-4), float((m.W_D.data - single.W_D.data).abs().max())
 
 
 @needs2
