@@ -431,7 +431,7 @@ def run_config4(args, bench) -> None:
     world, rank, local = (int(os.environ.get(k, d)) for k, d in (("WORLD_SIZE", "1"), ("RANK", "0"), ("LOCAL_RANK", "0")))
     assert c["heads"] % world == 0, "the number of GPUs must divide the 8 heads"
     config = {"model": f"Crosscoder {c['heads']} heads, d_model {c['d_model']}, d_sae {c['d_model'] * c['expansion']}, JumpReLU "
-                       "(threshold exp(0.5), window 2.0, tanh sparsity loss 1e-3), Adam lr 2e-4, fp32 parameters, bf16 autocast",
+                       "(threshold exp(1.2), encoder = decoder^T / heads, window 2.0, tanh sparsity loss 1e-3), Adam lr 2e-4, fp32 parameters, bf16 autocast",
               "global_batch": c["batch"], "seq_len": 1, "parallelism": f"head{world}", "l2": "inputs rotate through 4 batches"}  # fmt: skip
     metric = f"Crosscoder train tokens/s ({c['heads']} heads x d{c['d_model']} -> {c['d_model'] * c['expansion']} JumpReLU)"
     try:
@@ -458,14 +458,17 @@ def run_config4(args, bench) -> None:
         cfg = pkg.CrosscoderConfig(**kw)
         sae = pkg.SparseDictionary.from_config(cfg, device_mesh=mesh) if hasattr(pkg, "SparseDictionary") else None
         bound = 1.0 / D**0.5
-        sae.init_parameters(encoder_uniform_bound=bound, decoder_uniform_bound=bound, init_log_jumprelu_threshold_value=0.5)
+        # encoder = decoder^T / heads and a threshold of exp(1.2): a few dozen features per token pass at the start
+        sae.init_parameters(encoder_uniform_bound=bound, decoder_uniform_bound=bound, init_log_jumprelu_threshold_value=1.2)
         sae.set_decoder_to_fixed_norm(1.0, force_exact=True)
-        sae.init_encoder_with_decoder_transpose()
+        sae.init_encoder_with_decoder_transpose(1.0 / H)
         sae.set_dataset_average_activation_norm({hp: D**0.5 for hp in hooks})
         host = _crosscoder_batches(c, c["pool"], mine)
         tokens_h = torch.zeros(B, dtype=torch.long).pin_memory()
         pool_dev = [{h: v.to(dev) for h, v in rec.items()} for rec in host]
         tokens_d = tokens_h.to(dev)
+        mask_h = torch.ones(B, dtype=torch.bool).pin_memory()
+        mask_d = mask_h.to(dev)
         W, Ks = args.warmup, args.steps
         lead = 1 if impl == "reference" else 0  # the reference consumes one batch while sizing its schedule
 
@@ -481,6 +484,7 @@ def run_config4(args, bench) -> None:
                     if impl == "reference":
                         out = {k: v.float() for k, v in out.items()}
                     out["tokens"] = tokens_d if (on_device or impl == "reference") else tokens_h
+                    out["mask"] = mask_d if (on_device or impl == "reference") else mask_h
                     yield out
 
             return gen()
@@ -600,9 +604,10 @@ def run_config5(args, bench) -> None:
             pool_dev = [{k: v.to(dev) for k, v in rec.items()} for rec in host]
             tok_h = torch.zeros(*shape, dtype=torch.long).pin_memory()
             tok_d = tok_h.to(dev)
-            names = ("data", "model") if mesh is not None else None
+            mask_h = torch.ones(*shape, dtype=torch.bool).pin_memory()
+            mask_d = mask_h.to(dev)
 
-            def stream_of(source, on_start, pool_dev=pool_dev, keys=keys, tok_h=tok_h, tok_d=tok_d):
+            def stream_of(source, on_start, pool_dev=pool_dev, keys=keys, tok_h=tok_h, tok_d=tok_d, mask_h=mask_h, mask_d=mask_d):
                 on_device = source is pool_dev
 
                 def gen():
@@ -613,9 +618,11 @@ def run_config5(args, bench) -> None:
                         if impl == "reference":
                             out = {k: wrap((v if on_device else v.to(dev, non_blocking=True)).float(), mesh, None) for k, v in rec.items()}
                             out["tokens"] = wrap(tok_d, mesh, None)
+                            out["mask"] = wrap(mask_d, mesh, None)
                         else:
                             out = dict(rec)
                             out["tokens"] = tok_d if on_device else tok_h
+                            out["mask"] = mask_d if on_device else mask_h
                         yield out
 
                 return gen()

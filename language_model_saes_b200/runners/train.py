@@ -14,6 +14,8 @@ trains on the ("data", "model") sub-mesh of its coordinate and all members read 
 
 from __future__ import annotations
 
+import torch
+
 from pathlib import Path
 from typing import Any, Iterable, Optional
 
@@ -215,10 +217,47 @@ class SweepSAESettings(BaseSettings):
     datasets: Optional[dict[str, Optional[DatasetConfig]]] = None
     device_type: str = "cuda"
     fold_activation_scale: bool = True
+    share_activation_stream: bool = True
+    """Produce the activation stream once (on sweep coordinate 0) and broadcast every batch to the other members, so that all
+    members train on the very same batches and the language model runs once instead of once per member. False: every
+    member builds its own factory."""
+
+
+def _shared_sweep_stream(own_stream, group, device):
+    """The stream of sweep member 0, seen by every member of ``group``: per batch one small object broadcast (keys, shapes,
+    dtypes, non-tensor values; ``None`` ends the stream) and one tensor broadcast per entry."""
+    import torch.distributed as dist
+
+    src = dist.get_rank(group) == 0
+    it = iter(own_stream) if src else None
+    while True:
+        meta = None
+        batch = None
+        if src:
+            try:
+                batch = next(it)
+                meta = {k: (("t", tuple(v.shape), v.dtype) if isinstance(v, torch.Tensor) else ("o", v)) for k, v in batch.items()}
+            except StopIteration:
+                meta = None
+        box = [meta]
+        dist.broadcast_object_list(box, group=group, group_src=0)
+        meta = box[0]
+        if meta is None:
+            return
+        out = {}
+        for k, spec in meta.items():
+            if spec[0] == "o":
+                out[k] = spec[1]
+                continue
+            t = batch[k].to(device).contiguous() if src else torch.empty(spec[1], dtype=spec[2], device=device)
+            dist.broadcast(t, group=group, group_src=0)
+            out[k] = t
+        yield out
 
 
 def sweep_sae(settings: SweepSAESettings) -> None:
-    """Train ``len(items)`` dictionaries side by side; member i runs on the sweep coordinate i of the mesh."""
+    """Train ``len(items)`` dictionaries side by side; member i runs on the sweep coordinate i of the mesh
+    (runners/train.py:1179-1338 of the reference project, which replicates one stream over the ``sweep`` dimension)."""
     setup_logging(level="INFO")
     n = len(settings.items)
     mesh = make_mesh(settings.device_type, (n, settings.data_parallel_size, settings.model_parallel_size), ("sweep", "data", "model"))
@@ -228,8 +267,17 @@ def sweep_sae(settings: SweepSAESettings) -> None:
         sub_mesh = None
     item = settings.items[mesh.get_local_rank("sweep") if mesh is not None else 0]
     logger.info(f"Processing sweep item: {item.sae_name}/{item.sae_series}")
-    factory = ActivationFactory(settings.activation_factory, device_mesh=sub_mesh)
-    stream = factory.process(model=model, model_name=settings.model_name, datasets=datasets)
+    shared = settings.share_activation_stream and mesh is not None and n > 1
+    sweep_rank = mesh.get_local_rank("sweep") if mesh is not None else 0
+    stream = None
+    if not shared or sweep_rank == 0:
+        factory = ActivationFactory(settings.activation_factory, device_mesh=sub_mesh)
+        stream = factory.process(model=model, model_name=settings.model_name, datasets=datasets)
+    if shared:
+        dev = torch.device(item.sae.device) if hasattr(item.sae, "device") else torch.device(settings.device_type)
+        if dev.type == "cuda" and dev.index is None:
+            dev = torch.device("cuda", torch.cuda.current_device())
+        stream = _shared_sweep_stream(stream, mesh.get_group("sweep"), dev)
     wandb_logger = init_wandb(settings.wandb, settings, sub_mesh)
     sae = _build_sae(item.sae, item.initializer, stream, sub_mesh, wandb_logger, model)
     _fit_and_save(sae, item.trainer, stream, wandb_logger, mongo, item.sae_name, item.sae_series, settings.fold_activation_scale,

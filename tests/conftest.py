@@ -27,11 +27,15 @@ TINY_WORDS = ["the", "cat", "sat", "on", "a", "mat", "dog", "ran", "far", "away"
 def tiny_lm_workspace(tmp_path_factory):
     """A directory with ``model/`` (random 2-layer GPT-2, d_model 16, word-level tokenizer: ids 0 bos/eos, 1 pad, 2 unk)
     and ``data/`` (64 texts of 20 words, saved with ``datasets``)."""
+    return build_tiny_lm(tmp_path_factory.mktemp("tiny_lm"))
+
+
+def build_tiny_lm(root):
+    """Write the tiny model and dataset under ``root`` (a ``pathlib.Path``) and return it."""
     import datasets
     from tokenizers import Tokenizer, models, pre_tokenizers
     from transformers import GPT2Config, GPT2LMHeadModel, PreTrainedTokenizerFast
 
-    root = tmp_path_factory.mktemp("tiny_lm")
     vocab = {"<bos>": 0, "<pad>": 1, "<unk>": 2, **{w: i + 3 for i, w in enumerate(TINY_WORDS)}}
     tok = Tokenizer(models.WordLevel(vocab, unk_token="<unk>"))
     tok.pre_tokenizer = pre_tokenizers.Whitespace()

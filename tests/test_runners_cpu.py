@@ -110,3 +110,55 @@ def test_pipeline_generate_train_analyze_evaluate(workspace):
     assert any("explained_variance" in k for k in metrics) and any("l0" in k.lower() for k in metrics)
     l0 = next(v for k, v in metrics.items() if k.lower().endswith("l0"))
     assert abs(l0 - 4) < 1e-3
+
+
+from language_model_saes_b200.testing import distributed_test  # noqa: E402
+
+
+@distributed_test(nproc_per_node=2, backend="gloo")
+def test_sweep_trains_two_dictionaries_on_one_shared_stream():
+    """Two sweep members (one gloo rank each) train dictionaries with different k from ONE activation stream: member 0
+    builds the factory and broadcasts every batch; member 1 is even given a source path that does not exist, which it
+    never opens (runners/train.py:1179-1338 of the reference project replicates one stream over the sweep dimension)."""
+    import tempfile
+
+    import torch.distributed as dist
+
+    from conftest import build_tiny_lm
+    from language_model_saes_b200.runners import SweepSAESettings, sweep_sae
+    from language_model_saes_b200.runners.train import SweepingItem
+
+    rank = dist.get_rank()
+    box = [None]
+    if rank == 0:
+        root = Path(tempfile.mkdtemp(prefix="lmsae_sweep_"))
+        src = build_tiny_lm(root / "lm")
+        generate_activations(GenerateActivationsSettings(
+            model=_lm(src), model_name="tiny", dataset=DatasetConfig(dataset_name_or_path=str(src / "data"), is_dataset_on_disk=True),
+            dataset_name="toy", hook_points=[HOOK], output_dir=str(root / "acts"), total_tokens=16 * 64, context_size=16,
+            model_batch_size=4, batch_size=4, device_type="cpu", format="safetensors",
+        ))  # fmt: skip
+        box[0] = str(root)
+    dist.broadcast_object_list(box, src=0)
+    root = Path(box[0])
+    acts = root / "acts" if rank == 0 else root / "no-such-directory"
+    items = [
+        SweepingItem(
+            sae=SAEConfig(hook_point_in=HOOK, hook_point_out=HOOK, d_model=16, expansion_factor=4, act_fn="topk", top_k=k, device="cpu",
+                          dtype=torch.float32),
+            sae_name=f"toy-k{k}", sae_series="sweep", initializer=InitializerConfig(),
+            trainer=TrainerConfig(lr=1e-3, total_training_tokens=384, log_frequency=4, eval_frequency=10**6, n_checkpoints=0,
+                                  lr_warm_up_steps=2, exp_result_path=str(root / f"out_k{k}"), amp_dtype=torch.float32, l1_coefficient=None),
+        )
+        for k in (2, 6)
+    ]  # fmt: skip
+    factory = ActivationFactoryConfig(
+        sources=[ActivationFactoryActivationsSource(name="toy", path=str(acts), device="cpu", num_workers=0, prefetch=None)],
+        target=ActivationFactoryTarget.ACTIVATIONS_1D, hook_points=[HOOK], batch_size=32, num_workers=0,
+    )  # fmt: skip
+    sweep_sae(SweepSAESettings(items=items, activation_factory=factory, device_type="cpu"))
+    dist.barrier()
+    mine = root / f"out_k{(2, 6)[rank]}"
+    # (weights sit at the top level, or under checkpoints/step_N when the stream ended before the token budget)
+    assert (mine / "config.json").exists() and list(mine.rglob("sae_weights.safetensors"))
+    assert json.loads((mine / "config.json").read_text())["top_k"] == (2, 6)[rank]
