@@ -354,7 +354,7 @@ void sparse_grad_adam(const Tensor& offsets, const Tensor& entries, const Tensor
                       const std::vector<int64_t>& pub_offsets, int64_t pub_epoch,
                       const c10::optional<Tensor>& pub_done, const c10::optional<Tensor>& extra_row,
                       const c10::optional<Tensor>& extra_gD, const c10::optional<Tensor>& extra_gE,
-                      const c10::optional<Tensor>& extra_gb) {
+                      const c10::optional<Tensor>& extra_gb, const c10::optional<Tensor>& wd_self_scale) {
   CHECK_T(offsets, torch::kInt32);
   CHECK_T(entries, torch::kInt32);
   CHECK_T(act, torch::kFloat32);
@@ -407,6 +407,8 @@ void sparse_grad_adam(const Tensor& offsets, const Tensor& entries, const Tensor
   p.ctas_per_sm = (int)ctas_per_sm;
   if (status.has_value()) { CHECK_T(*status, torch::kInt32); }
   p.status = opt_ptr<const int>(status);
+  if (wd_self_scale.has_value()) { CHECK_T(*wd_self_scale, torch::kFloat32); TORCH_CHECK(wd_self_scale->numel() == p.F); }
+  p.wd_self_scale = opt_ptr<const float>(wd_self_scale);
   if (extra_row.has_value()) {
     TORCH_CHECK(extra_gD.has_value() && extra_gE.has_value(), "extra gradient rows come with both matrices");
     CHECK_T(*extra_row, torch::kInt32); CHECK_T(*extra_gD, torch::kFloat32); CHECK_T(*extra_gE, torch::kFloat32);
@@ -638,7 +640,9 @@ Tensor threshold_mask(const Tensor& x, const Tensor& thr, int64_t A, int64_t S, 
 // x [B, N] -> idx / val [B, cap] (both optional: count only) and nnz [B] (optional)
 void row_compact(const Tensor& x, const c10::optional<Tensor>& idx, const c10::optional<Tensor>& val,
                  const c10::optional<Tensor>& nnz, const c10::optional<Tensor>& thr, const c10::optional<Tensor>& col_div,
-                 const c10::optional<Tensor>& ties, const c10::optional<Tensor>& tie_quota) {
+                 const c10::optional<Tensor>& ties, const c10::optional<Tensor>& tie_quota,
+                 const c10::optional<Tensor>& col_thr) {
+  if (col_thr.has_value()) { CHECK_T(*col_thr, torch::kFloat32); TORCH_CHECK(col_thr->numel() == x.size(1) && !thr.has_value(), "col_thr: one per column, instead of thr"); }
   if (ties.has_value()) { CHECK_T(*ties, torch::kInt32); TORCH_CHECK(ties->numel() == x.size(0) && thr.has_value(), "ties: [B], with thr"); }
   if (tie_quota.has_value()) { CHECK_T(*tie_quota, torch::kInt32); TORCH_CHECK(tie_quota->numel() == x.size(0) && thr.has_value(), "tie_quota: [B], with thr"); }
   if (thr.has_value()) { CHECK_T(*thr, torch::kFloat32); TORCH_CHECK(thr->numel() >= 1); }
@@ -659,8 +663,26 @@ void row_compact(const Tensor& x, const c10::optional<Tensor>& idx, const c10::o
   const c10::cuda::CUDAGuard guard(x.device());
   check_cuda(lmsae::row_compact_launch(dtype_code(x), x.data_ptr(), (int)x.size(0), x.size(1), cap, opt_ptr<int>(idx),
                                        opt_ptr<float>(val), opt_ptr<int>(nnz), opt_ptr<float>(thr), opt_ptr<float>(col_div),
-                                       opt_ptr<int>(ties), opt_ptr<int>(tie_quota), at::cuda::getCurrentCUDAStream()),
+                                       opt_ptr<int>(ties), opt_ptr<int>(tie_quota), opt_ptr<float>(col_thr),
+                                       at::cuda::getCurrentCUDAStream()),
              "row_compact launch");
+}
+
+// d theta[f] += window-weighted column sums of G / n (see select_ops.cu); G, S bf16 [B, F], n / theta / dtheta fp32 [F].
+void jumprelu_window_grad(const Tensor& G, const Tensor& S, const Tensor& n, const Tensor& theta, double window,
+                          double add_per_hit, const Tensor& dtheta) {
+  CHECK_T(G, torch::kBFloat16);
+  CHECK_T(S, torch::kBFloat16);
+  CHECK_T(n, torch::kFloat32);
+  CHECK_T(theta, torch::kFloat32);
+  CHECK_T(dtheta, torch::kFloat32);
+  TORCH_CHECK(G.dim() == 2 && S.sizes() == G.sizes() && n.numel() == G.size(1) && theta.numel() == G.size(1) && dtheta.numel() == G.size(1));
+  const c10::cuda::CUDAGuard guard(G.device());
+  check_cuda(lmsae::jumprelu_window_grad_launch(reinterpret_cast<const __nv_bfloat16*>(G.data_ptr()),
+                                                reinterpret_cast<const __nv_bfloat16*>(S.data_ptr()), (int)G.size(0), (int)G.size(1),
+                                                n.data_ptr<float>(), theta.data_ptr<float>(), (float)window, (float)add_per_hit, dtheta.data_ptr<float>(),
+                                                at::cuda::getCurrentCUDAStream()),
+             "jumprelu_window_grad launch");
 }
 
 void exclusive_scan(const Tensor& counts, const Tensor& offsets, const Tensor& block_sums) {
@@ -826,15 +848,18 @@ void comm_bcast_rows(const std::vector<int64_t>& table, const Tensor& src, const
 // Head-summed encoder GEMM with the reduce-scatter epilogue: x [M, heads * d] bf16, w [heads * rows_per_head, d] bf16
 // (head h's rows start at h * rows_per_head; the first N of them are used), bias fp32 [N] or absent. The fp32 result
 // tile is ADDED into slabs[c / (N / world)], an fp32 [M, N / world] array per rank (device pointers, peer mappings).
+// With `H_out` (bf16 [M, N], `slabs` empty) the sum over the local heads is stored instead of reduced into slabs.
 void head_sum_gemm(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& bias, int64_t heads, int64_t rows_per_head,
-                   int64_t N, const std::vector<int64_t>& slabs, bool pair, const Tensor& status) {
+                   int64_t N, const std::vector<int64_t>& slabs, bool pair, const Tensor& status,
+                   const c10::optional<Tensor>& H_out) {
   CHECK_T(x, torch::kBFloat16);
   CHECK_T(w, torch::kBFloat16);
   CHECK_T(status, torch::kInt32);
   TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && heads >= 1 && x.size(1) == heads * w.size(1), "x [M, heads*d], w [heads*rows, d]");
   TORCH_CHECK(w.size(0) == heads * rows_per_head && N <= rows_per_head, "w must hold `heads` blocks of rows_per_head rows");
   const int64_t world = (int64_t)slabs.size();
-  TORCH_CHECK(world >= 1 && world <= 8 && N % world == 0 && (N / world) % 32 == 0, "N / world must be a multiple of 32");
+  TORCH_CHECK(world >= 1 || H_out.has_value(), "either slabs to reduce into or an output matrix");
+  if (world > 0) TORCH_CHECK(world <= 8 && N % world == 0 && (N / world) % 32 == 0, "N / world must be a multiple of 32");
   TORCH_CHECK(w.size(1) % 64 == 0, "d must be a multiple of 64");
   const c10::cuda::CUDAGuard guard(x.device());
   lmsae::EncGemmParams p{};
@@ -854,7 +879,13 @@ void head_sum_gemm(const Tensor& x, const Tensor& w, const c10::optional<Tensor>
   p.heads = (int)heads;
   p.b_rows_per_head = (int)rows_per_head;
   p.red_world = (int)world;
-  p.red_cols = (int)(N / world);
+  p.red_cols = world > 0 ? (int)(N / world) : 0;
+  if (world == 0) {
+    CHECK_T(*H_out, torch::kBFloat16);
+    TORCH_CHECK(H_out->dim() == 2 && H_out->size(0) == x.size(0) && H_out->size(1) == N, "H_out must be [M, N]");
+    p.H = reinterpret_cast<__nv_bfloat16*>(H_out->data_ptr());
+    p.ldh = p.N;
+  }
   for (int64_t i = 0; i < world; ++i) {
     TORCH_CHECK(slabs[i] % 16 == 0, "slab pointers must be 16-byte aligned");
     p.red_base[i] = reinterpret_cast<float*>(static_cast<uintptr_t>(slabs[i]));
@@ -876,6 +907,20 @@ void comm_headsum_gather(const std::vector<int64_t>& table, int64_t slab_off, in
                                           (uint32_t)epoch, reinterpret_cast<unsigned*>(done_counter.data_ptr<int>()),
                                           status.data_ptr<int>(), at::cuda::getCurrentCUDAStream()),
              "comm_headsum_gather launch");
+}
+
+// In-place sum over the ranks of `table` of the bf16 array at byte offset `off` (n16 16-byte vectors) of every rank's
+// symmetric buffer; see allreduce_bf16_inplace_kernel.
+void comm_allreduce_bf16(const std::vector<int64_t>& table, int64_t off, int64_t n16, int64_t phase_in, int64_t phase_out,
+                         int64_t epoch, bool use_multicast, const Tensor& done_counter, const Tensor& status) {
+  CHECK_T(done_counter, torch::kInt32);
+  CHECK_T(status, torch::kInt32);
+  TORCH_CHECK(off % 16 == 0 && n16 >= 0);
+  const c10::cuda::CUDAGuard guard(status.device());
+  check_cuda(lmsae::allreduce_bf16_launch(make_peer_table(table), off, n16, (int)phase_in, (int)phase_out, (uint32_t)epoch,
+                                          use_multicast ? 1 : 0, reinterpret_cast<unsigned*>(done_counter.data_ptr<int>()),
+                                          status.data_ptr<int>(), at::cuda::getCurrentCUDAStream()),
+             "allreduce_bf16 launch");
 }
 
 void comm_signal(const std::vector<int64_t>& table, int64_t phase, int64_t epoch) {
@@ -977,6 +1022,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("comm_wait", &comm_wait);
   m.def("comm_bcast_rows", &comm_bcast_rows);
   m.def("comm_signal", &comm_signal);
+  m.def("comm_allreduce_bf16", &comm_allreduce_bf16);
   m.def("head_sum_gemm", &head_sum_gemm);
   m.def("comm_headsum_gather", &comm_headsum_gather);
   m.def("comm_wait_src", &comm_wait_src);
@@ -993,6 +1039,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("radix_pick", &radix_pick);
   m.def("threshold_mask", &threshold_mask);
   m.def("row_compact", &row_compact);
+  m.def("jumprelu_window_grad", &jumprelu_window_grad);
   m.def("exclusive_scan", &exclusive_scan);
   m.def("gather_rows_cast", &gather_rows_cast);
   m.def("clt_decode", &clt_decode);

@@ -255,6 +255,71 @@ int exchange_rows_launch(const PeerTable& pt, const RowExchange& ex, uint32_t ep
   return (int)cudaGetLastError();
 }
 
+// ---------------------------------------------------------------------------------------------
+// In-place all-reduce (sum) of a bf16 array that every rank holds at the same offset of its symmetric buffer, in one
+// kernel: the crosscoder's sum of encoder pre-activations over head ranks (models/crosscoder.py:350-375 of the
+// reference project all-reduces that [batch, d_sae] tensor with NCCL). Protocol:
+//   1. block 0 publishes "my array is written" (phase_in) to every rank; every block waits for all ranks' flags
+//   2. rank r owns the r-th share of the 16-byte vectors. MC: one multimem.ld_reduce returns the sum over all ranks'
+//      copies (added inside the NVSwitch, fp32 accumulation) and one multimem.st writes it back into every rank's copy.
+//      Without a multicast mapping the same is done with `world` peer loads and `world` peer stores.
+//      No element is read after its owner has overwritten it: only the owner reads it at all.
+//   3. the last block publishes "my share is reduced everywhere" (phase_out) and waits for the other ranks' flags, so
+//      that the kernels behind this one in the stream find the complete sums.
+// ---------------------------------------------------------------------------------------------
+template <bool MC>
+__global__ void __launch_bounds__(512)
+allreduce_bf16_inplace_kernel(const PeerTable pt, long long off, long long n16, int phase_in, int phase_out, uint32_t epoch,
+                              unsigned* done_counter, int* status) {
+  if (blockIdx.x == 0) {
+    __threadfence_system();
+    if ((int)threadIdx.x < pt.world) st_release_sys(flag_slot(pt, threadIdx.x, phase_in, pt.rank), epoch);
+  }
+  const bool ok = wait_all_sources(pt, phase_in, epoch, status);
+  if (ok) {
+    const long long per = (n16 + pt.world - 1) / pt.world;
+    const long long lo = per * pt.rank, hi = lo + per < n16 ? lo + per : n16;
+    for (long long v = lo + blockIdx.x * 512LL + threadIdx.x; v < hi; v += (long long)gridDim.x * 512) {
+      if constexpr (MC) {
+        char* a = pt.mc_base + off + v * 16;
+        multimem_st_16B(a, multimem_ld_reduce_add_bf16x8(a));
+      } else {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        uint4 raw[kMaxPeers];
+#pragma unroll
+        for (int s = 0; s < kMaxPeers; ++s)
+          if (s < pt.world) raw[s] = *(reinterpret_cast<const uint4*>(pt.base[s] + off) + v);
+#pragma unroll
+        for (int s = 0; s < kMaxPeers; ++s)
+          if (s < pt.world) {
+            float t[8];
+            bf16x8_to_float_c(raw[s], t);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] += t[i];
+          }
+        const uint4 o = float8_to_bf16x8(acc);
+        for (int s = 0; s < pt.world; ++s) *(reinterpret_cast<uint4*>(pt.base[s] + off) + v) = o;
+      }
+    }
+  }
+  const bool last = signal_peers_when_grid_done(pt, phase_out, epoch, done_counter);
+  if (last) wait_all_sources(pt, phase_out, epoch, status, /*record_always=*/true);
+}
+
+int allreduce_bf16_launch(const PeerTable& pt, long long off, long long n16, int phase_in, int phase_out, uint32_t epoch,
+                          int use_multicast, unsigned* done_counter, int* status, cudaStream_t stream) {
+  if (phase_in < 0 || phase_in >= kNumPhases || phase_out < 0 || phase_out >= kNumPhases || phase_in == phase_out)
+    return (int)cudaErrorInvalidValue;
+  if (use_multicast && pt.mc_base == nullptr) return (int)cudaErrorInvalidValue;
+  // every block waits at the start: the grid must be resident at once (one CTA of 512 threads per SM at most two)
+  const int blocks = 148 * 2;
+  if (use_multicast)
+    allreduce_bf16_inplace_kernel<true><<<blocks, 512, 0, stream>>>(pt, off, n16, phase_in, phase_out, epoch, done_counter, status);
+  else
+    allreduce_bf16_inplace_kernel<false><<<blocks, 512, 0, stream>>>(pt, off, n16, phase_in, phase_out, epoch, done_counter, status);
+  return (int)cudaGetLastError();
+}
+
 // ---- launchers ----------------------------------------------------------------------------------
 // ---------------------------------------------------------------------------------------------
 // Row all-to-all for the activation shuffle: local row i goes to global position dest[i] of the logical

@@ -129,6 +129,9 @@ struct GradAdamParams {
   // row extra_row[f] (when >= 0) of the fp32 matrices extra_gD / extra_gE [rows, d] and element extra_row[f] of extra_gb.
   const int* extra_row;
   const float* extra_gD; const float* extra_gE; const float* extra_gb;
+  // Gradient that reaches a decoder row through its own norm (a sparsity penalty on a * ||W_D row||): the row's gradient
+  // gets wd_self_scale[f] * W_D[f, :] added, with the row read in the same pass that updates it (nullptr: none).
+  const float* wd_self_scale;
   const __nv_bfloat16* dxhat_aux;  // output gradient seen by the code slots >= k_main of every row (nullptr: none)
   int k_main;
   float* gD_out;  // optional dense [F, d] outputs of the rebuilt gradient rows (for autograd callers)
@@ -177,7 +180,10 @@ int radix_pick_launch(const unsigned* hist, int nbins, long long k, const long l
 int threshold_mask_launch(int dtype, const void* x, const float* thr, long long A, long long S, long long N, void* out,
                           cudaStream_t stream);
 int row_compact_launch(int dtype, const void* x, int B, long long N, int cap, int* idx, float* val, int* nnz,
-                       const float* thr, const float* col_div, int* ties, const int* tie_quota, cudaStream_t stream);
+                       const float* thr, const float* col_div, int* ties, const int* tie_quota, const float* col_thr,
+                       cudaStream_t stream);
+int jumprelu_window_grad_launch(const __nv_bfloat16* G, const __nv_bfloat16* S, int B, int F, const float* n,
+                                const float* theta, float window, float add_per_hit, float* dtheta, cudaStream_t stream);
 int gather_rows_cast_launch(int in_dtype, int out_dtype, const void* src, const int* keep, const int* pos, long long n,
                             int d, void* out, long long out_rows, cudaStream_t stream);
 int exclusive_scan_launch(const int* counts, int n, int* offsets, int* block_sums_buf, cudaStream_t stream);
@@ -230,6 +236,8 @@ int bcast_rows_cast_launch(const PeerTable& pt, int in_dtype, int out_dtype, con
 int headsum_gather_launch(const PeerTable& pt, long long slab_off, long long out_off, int B, int cols, int out_dtype,
                           int phase_in, int phase_out, uint32_t epoch, unsigned* done_counter, int* status,
                           cudaStream_t stream);
+int allreduce_bf16_launch(const PeerTable& pt, long long off, long long n16, int phase_in, int phase_out, uint32_t epoch,
+                          int use_multicast, unsigned* done_counter, int* status, cudaStream_t stream);
 int signal_flags_launch(const PeerTable& pt, int phase, uint32_t epoch, cudaStream_t stream);
 int wait_flag_src_launch(const PeerTable& pt, int phase, uint32_t epoch, int src, int* status, cudaStream_t stream);
 int wait_flags_launch(const PeerTable& pt, int phase, uint32_t epoch, int* status, cudaStream_t stream);

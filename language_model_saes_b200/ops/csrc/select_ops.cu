@@ -273,11 +273,13 @@ struct RowVec<__nv_bfloat16> {
 //   A compacting call finds every kept entry's slot with one block-wide scan per step (a thread's entries are
 //   consecutive columns, threads are in column order), so the list comes out in ascending column order.
 //   With col_div the stored value is x / col_div[column] (gated pre-activation back to the activation).
+//   With col_thr (one threshold per column, instead of thr) an entry is kept when x > col_thr[column]: the JumpReLU
+//   selection of pre-activations against per-feature thresholds.
 template <typename T>
 __global__ void __launch_bounds__(RC_THREADS)
 row_compact_kernel(const T* __restrict__ x, int B, long long N, int cap, int* __restrict__ idx, float* __restrict__ val,
                    int* __restrict__ nnz, const float* __restrict__ thr, const float* __restrict__ col_div,
-                   int* __restrict__ ties, const int* __restrict__ tie_quota) {
+                   int* __restrict__ ties, const int* __restrict__ tie_quota, const float* __restrict__ col_thr) {
   constexpr int V = RowVec<T>::V;
   constexpr int NW = RC_THREADS / 32;
   const bool has_thr = thr != nullptr;
@@ -307,6 +309,8 @@ row_compact_kernel(const T* __restrict__ x, int B, long long N, int cap, int* __
           if (split_ties) {
             n_keep += f[i] > t;
             n_tie += (f[i] == t) && (c + i < N);
+          } else if (col_thr != nullptr) {
+            n_keep += (c + i < N) && f[i] > col_thr[c + i];
           } else {
             n_keep += has_thr ? (f[i] >= t) : (f[i] != 0.0f);
           }
@@ -349,6 +353,8 @@ row_compact_kernel(const T* __restrict__ x, int B, long long N, int cap, int* __
         if (split_ties) {
           m_strict |= (unsigned)(in && f[i] > t) << i;
           m_tie |= (unsigned)(in && f[i] == t) << i;
+        } else if (col_thr != nullptr) {
+          m_strict |= (unsigned)(in && f[i] > col_thr[in ? c + i : 0]) << i;
         } else {
           m_strict |= (unsigned)(in && (has_thr ? (f[i] >= t) : (f[i] != 0.0f))) << i;
         }
@@ -505,17 +511,70 @@ int threshold_mask_launch(int dtype, const void* x, const float* thr, long long 
 }
 
 int row_compact_launch(int dtype, const void* x, int B, long long N, int cap, int* idx, float* val, int* nnz,
-                       const float* thr, const float* col_div, int* ties, const int* tie_quota, cudaStream_t stream) {
+                       const float* thr, const float* col_div, int* ties, const int* tie_quota, const float* col_thr,
+                       cudaStream_t stream) {
+  if (col_thr != nullptr && (thr != nullptr || ties != nullptr || tie_quota != nullptr)) return (int)cudaErrorInvalidValue;
   if (B <= 0) return 0;
   if (N > 2147483647LL) return (int)cudaErrorInvalidValue;
   const int blocks = B < 148 * 8 ? B : 148 * 8;
   if (dtype == 0)
     row_compact_kernel<float><<<blocks, RC_THREADS, 0, stream>>>(static_cast<const float*>(x), B, N, cap, idx, val, nnz, thr, col_div, ties,
-                                                                 tie_quota);
+                                                                 tie_quota, col_thr);
   else
     row_compact_kernel<__nv_bfloat16>
         <<<blocks, RC_THREADS, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), B, N, cap, idx, val, nnz, thr, col_div, ties,
-                                            tie_quota);
+                                            tie_quota, col_thr);
+  return (int)cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// JumpReLU threshold gradient of one crosscoder head from dense matrices: G[b, f] = d loss / d a[b, f] (reconstruction
+// part, = d x_hat[b, :] . W_D[f, :]) and S[b, f] = summed pre-activation, both bf16 [B, F]; n[f] = decoder norm of the
+// head, theta[f] = threshold. With x = S n:  d theta[f] += sum_b (G / n) * (-theta / w) * 1[|x - theta| < w / 2 and x > 0]
+// (activation_functions.py:15-64 of the reference project: rectangle window of width w around the threshold).
+// `add_per_hit` is added to G / n at every entry inside the window (a loss term whose derivative with respect to the
+// JumpReLU output is the same constant at every entry, e.g. a tanh penalty at zero activation). Each thread owns eight
+// consecutive columns and walks a chunk of rows; partial column sums go to fp32 atomics.
+// ---------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+jumprelu_window_grad_kernel(const __nv_bfloat16* __restrict__ G, const __nv_bfloat16* __restrict__ S, int B, int F,
+                            const float* __restrict__ n, const float* __restrict__ theta, float window, float add_per_hit,
+                            int rows_per_block, float* __restrict__ dtheta) {
+  const int c = (blockIdx.x * 256 + threadIdx.x) * 8;
+  if (c >= F) return;
+  const int r0 = blockIdx.y * rows_per_block, r1 = min(B, r0 + rows_per_block);
+  float nn[8], th[8], acc[8], hits[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    nn[i] = n[c + i];
+    th[i] = theta[c + i];
+    acc[i] = hits[i] = 0.0f;
+  }
+  const float half_w = 0.5f * window;
+  for (int r = r0; r < r1; ++r) {
+    float g[8], s[8];
+    load8<__nv_bfloat16>(G + (size_t)r * F + c, g);
+    load8<__nv_bfloat16>(S + (size_t)r * F + c, s);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float x = s[i] * nn[i];
+      if (x > 0.0f && fabsf(x - th[i]) < half_w) {
+        acc[i] += g[i];
+        hits[i] += 1.0f;
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    if (hits[i] != 0.0f) atomicAdd(dtheta + c + i, (acc[i] / nn[i] + add_per_hit * hits[i]) * (-th[i] / window));
+}
+
+int jumprelu_window_grad_launch(const __nv_bfloat16* G, const __nv_bfloat16* S, int B, int F, const float* n,
+                                const float* theta, float window, float add_per_hit, float* dtheta, cudaStream_t stream) {
+  if (F % 8 != 0 || B <= 0) return (int)cudaErrorInvalidValue;
+  const int rows_per_block = 128;
+  dim3 grid((F / 8 + 255) / 256, (B + rows_per_block - 1) / rows_per_block);
+  jumprelu_window_grad_kernel<<<grid, 256, 0, stream>>>(G, S, B, F, n, theta, window, add_per_hit, rows_per_block, dtheta);
   return (int)cudaGetLastError();
 }
 

@@ -515,6 +515,7 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
   for (int f = p.f_begin + blockIdx.x; f < p.f_end && !skip; f += gridDim.x) {
     const int e0 = p.offsets[f], e1 = p.offsets[f + 1];
     const int xr = p.extra_row != nullptr ? p.extra_row[f] : -1;
+    const float self_scale = p.wd_self_scale != nullptr ? p.wd_self_scale[f] * gmul : 0.0f;
     float bias_g = (xr >= 0 && p.extra_gb != nullptr) ? p.extra_gb[xr] : 0.0f;
     float norm_sq = 0.0f;
     for (int c0 = 0; c0 < p.d; c0 += GA_THREADS * 4 * VEC) {
@@ -587,6 +588,10 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
         for (int v = 0; v < VEC; ++v) {
           if (!in[v]) continue;
           {
+            if (self_scale != 0.0f) {  // (not part of the squared-norm accumulation above: a penalty term's share is small)
+              gD[v][0] = fmaf(self_scale, w[v].x, gD[v][0]); gD[v][1] = fmaf(self_scale, w[v].y, gD[v][1]);
+              gD[v][2] = fmaf(self_scale, w[v].z, gD[v][2]); gD[v][3] = fmaf(self_scale, w[v].w, gD[v][3]);
+            }
             adam_elem(w[v].x, m[v].x, vv[v].x, gD[v][0], p.h); adam_elem(w[v].y, m[v].y, vv[v].y, gD[v][1], p.h);
             adam_elem(w[v].z, m[v].z, vv[v].z, gD[v][2], p.h); adam_elem(w[v].w, m[v].w, vv[v].w, gD[v][3], p.h);
             stcs4(p.WD + o[v], w[v]); stcs4(p.mD + os[v], m[v]); stcs4(p.vD + os[v], vv[v]);

@@ -1,0 +1,235 @@
+"""One training step of a JumpReLU crosscoder as a fixed sequence of sm_100a kernels, without autograd.
+
+What it computes is the reference's step for a ``Crosscoder`` (models/crosscoder.py:350-378 encode, :384-469 decode,
+models/sparse_dictionary.py:841-936 loss, activation_functions.py:15-64 JumpReLU with its straight-through threshold
+gradient): every head encodes its own activation, the pre-activations are summed over ALL heads, each head gates the sum
+with its decoder norms, applies ``JumpReLU`` and decodes with its own decoder; the loss is the mean over tokens and heads
+of the squared error plus, optionally, the ``tanh`` sparsity penalty; Adam on every parameter. How it computes it:
+
+1. head sum: one tcgen05 GEMM accumulates the local heads in its K loop (K = local heads x d_model) and stores bf16 into a
+   symmetric buffer; one kernel sums that matrix over the head ranks in place (``parallel.symm.AllReduceComm``: the owner
+   of a share reads the sum with ``multimem.ld_reduce`` -- added inside the NVSwitch -- and writes it to every rank with
+   ``multimem.st``; peer loads / stores without a multicast mapping)                        -> S [B, F] bf16, all ranks
+2. selection: one compaction pass keeps, per token, the features whose sum passes the threshold of ANY head
+   (``S > min_h theta / ||W_D,h row||``): every rank derives the same lists in the same order; a head's codes are the
+   list entries that pass ITS threshold (zero otherwise)                      -> idx [B, cap], per head act [B, cap]
+3. per local head: sparse decode fused with the loss, d x_hat and d act (``sparse_decode_loss``)
+4. the gradient of the shared sum is the sum over all heads of the heads' code gradients where the head is active: the
+   lists are aligned on all ranks, so this is a small all-reduce of a [B, cap] array
+5. per local head: the sparse gradient + Adam kernel rebuilds d W_D (codes x d x_hat) and d W_E^T (d S x inputs) rows from
+   the lists and updates both matrices, bf16 shadows and decoder norms in one pass; no dense gradient exists
+6. threshold gradient: the rectangle window of the straight-through estimator is wide (the default width 2 covers most
+   positive pre-activations), so this gradient needs d loss / d act at INACTIVE entries too: one dense tcgen05 GEMM per
+   head, G = d x_hat . W_D^T [B, F] bf16, and one streaming kernel that adds up G inside the window against S.
+
+Restrictions: ``jumprelu`` activation, MSE loss with optional ``tanh`` sparsity loss, Adam, fp32 parameters with bf16
+compute, heads split over the ``head`` mesh dimension only (no ``model`` / ``data`` sharding). A token with more
+candidate features than the list width keeps its first ones by column and is counted in ``list_overflow``.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.distributed as dist
+
+from ..parallel.mesh import mesh_dim_size, mesh_group
+from . import sae_kernels as K
+from . import select_kernels as S
+
+
+class FusedCrosscoderStep:
+    def __init__(self, cc, betas: tuple[float, float] = (0.9, 0.999), eps: float = 1e-8, list_width: int = 256,
+                 jumprelu_lr_factor: float = 1.0):  # fmt: skip
+        cfg = cc.cfg
+        self.cc = cc
+        self.betas, self.eps = betas, eps
+        self.head_size = mesh_dim_size(cc.device_mesh, "head")
+        self.head_group = mesh_group(cc.device_mesh, "head")
+        self.H, self.H_l = cfg.n_heads, cc.n_heads_local
+        self.F, self.d = cc.d_sae_local, cfg.d_model
+        self.window = float(cfg.jumprelu_threshold_window)
+        self.cap = -(-list_width // 8) * 8
+        self.jumprelu_lr_factor = jumprelu_lr_factor
+        self.WE = cc.W_E.data.transpose(1, 2)  # [H_l, F, d], contiguous views of the parameters' storage
+        self.WD = cc.W_D.data
+        assert self.WE.is_contiguous() and self.WD.is_contiguous() and self.WE.dtype == torch.float32
+        self.bE, self.bD = cc.b_E.data, cc.b_D.data
+        self.log_theta = cc.activation_function.log_jumprelu_threshold.data
+        dev = self.WD.device
+        H_l, F, d = self.H_l, self.F, self.d
+        z = lambda *s: torch.zeros(*s, dtype=torch.float32, device=dev)  # noqa: E731
+        self.WE_bf16 = torch.empty(H_l, F, d, dtype=torch.bfloat16, device=dev)
+        self.WD_bf16 = torch.empty(H_l, F, d, dtype=torch.bfloat16, device=dev)
+        self.dec_norm = torch.empty(H_l, F, dtype=torch.float32, device=dev)
+        self.state = {"W_E": (z(H_l, F, d), z(H_l, F, d)), "W_D": (z(H_l, F, d), z(H_l, F, d)), "b_E": (z(H_l, F), z(H_l, F)),
+                      "b_D": (z(H_l, d), z(H_l, d)), "log_theta": (z(F), z(F))}  # fmt: skip
+        self.groups: K.FeatureGroups | None = None
+        self.loss_sum = z(1)
+        self.list_overflow = torch.zeros(1, dtype=torch.int64, device=dev)
+        self.last: dict[str, torch.Tensor] = {}
+        self.comm = None
+        self.own_rows = (0, F)
+        self.t = 0
+        self.refresh()
+
+    @staticmethod
+    def supports(cc, trainer_cfg=None) -> tuple[bool, str]:
+        from ..models.crosscoder import Crosscoder
+
+        cfg = cc.cfg
+        if type(cc) is not Crosscoder:
+            return False, "model is not a Crosscoder"
+        checks = [
+            (cfg.act_fn == "jumprelu", "activation is not jumprelu"),
+            (cc.W_D.is_cuda or trainer_cfg is None, "not on a CUDA device"),
+            (cfg.dtype == torch.float32, "parameters are not fp32"),
+            (cfg.d_model % 64 == 0, "d_model is not a multiple of 64"),
+            (cc.d_sae_local % (max(1, mesh_dim_size(cc.device_mesh, "head")) * 32) == 0, "d_sae does not split into 32-column slabs per head rank"),
+            (mesh_dim_size(cc.device_mesh, "model") == 1 and mesh_dim_size(cc.device_mesh, "data") == 1, "model/data sharding"),
+            (not any(hp.fwd_hooks or hp.bwd_hooks for hp in cc.hook_points()), "hooks are attached"),
+        ]  # fmt: skip
+        if trainer_cfg is not None:
+            checks += [
+                (trainer_cfg.sparsity_loss_type in (None, "tanh"), "sparsity loss other than tanh"),
+                (not trainer_cfg.lp_coefficient, "lp loss"),
+                (not trainer_cfg.auxk_coefficient, "aux-k loss"),
+                (trainer_cfg.optimizer_class == "adam", "optimizer is not adam"),
+                (trainer_cfg.amp_dtype == torch.bfloat16, "amp dtype is not bf16"),
+                (trainer_cfg.gradient_accumulation_steps == 1, "gradient accumulation"),
+                (not trainer_cfg.clip_grad_norm, "gradient clipping"),
+            ]
+        for ok, why in checks:
+            if not ok:
+                return False, why
+        return True, ""
+
+    def refresh(self) -> None:
+        """Re-derive bf16 shadows and decoder norms from the fp32 masters (after loading / editing weights)."""
+        for h in range(self.H_l):
+            K.row_norm_shadow(self.WD[h], self.dec_norm[h], self.WD_bf16[h])
+            K.row_norm_shadow(self.WE[h], None, self.WE_bf16[h])
+
+    def join(self) -> None:
+        pass
+
+    def sync_params(self) -> None:
+        pass
+
+    def _head_sum(self, x16: torch.Tensor) -> torch.Tensor:
+        """``sum over all heads of (x_h W_E,h^T + b_E,h)`` as bf16 [B, F] on every rank."""
+        from ..parallel.symm import AllReduceComm
+
+        B = x16.shape[0]
+        if not x16.is_cuda:  # plain statement (CPU): local heads in one product, the other ranks by an all-reduce
+            w = self.WE_bf16.view(self.H_l * self.F, self.d).float().view(self.H_l, self.F, self.d)
+            s = torch.einsum("bhd,hfd->bf", x16.float().view(B, self.H_l, self.d), w) + self.bE.sum(0)
+            if self.head_size > 1:
+                dist.all_reduce(s, group=self.head_group)
+            return s.to(torch.bfloat16)
+        if self.comm is None or self.comm.max_rows < B:
+            self.comm = AllReduceComm(self.head_group if self.head_size > 1 else None, x16.device, B, self.F)
+        # the GEMM accumulates the local heads in one K loop and stores bf16 straight into the symmetric buffer ...
+        P = self.comm.matrix(B)
+        K._ext().head_sum_gemm(x16, self.WE_bf16.view(self.H_l * self.F, self.d), self.bE.sum(0).contiguous(), self.H_l, self.F, self.F,
+                               [], True, K.status_buffer(x16.device), P)  # fmt: skip
+        # ... which one kernel then sums over the head ranks in place (NVSwitch multicast loads / stores where available)
+        return self.comm.all_reduce(B) if self.head_size > 1 else P
+
+    def step(self, x: torch.Tensor, lr: float, l1_coefficient: float = 0.0, tanh_stretch: float = 4.0,
+             row_weight: torch.Tensor | None = None) -> torch.Tensor:  # fmt: skip
+        """``x``: normalised bf16 activations ``[B, H_l, d]`` of this rank's heads (they are also the labels). Returns the
+        mean loss over tokens and this rank's heads (0-d device tensor); ``self.last`` holds its parts."""
+        assert row_weight is None, "token masks are not supported on this path"
+        B, H_l, d = x.shape
+        H, F, cap = self.H, self.F, self.cap
+        grad_scale = 2.0 / (B * H)
+        x = x.contiguous()
+        S_sum = self._head_sum(x.view(B, H_l * d))
+        theta = self.log_theta.exp()
+        t_head = theta / self.dec_norm  # [H_l, F]: a head is active where S > theta / ||W_D,h row||
+        t_min = t_head.amin(0)
+        if self.head_size > 1:
+            dist.all_reduce(t_min, op=dist.ReduceOp.MIN, group=self.head_group)
+        idx, s_val = S.column_threshold_rows_to_sparse(S_sum, t_min, cap, overflow=self.list_overflow)
+        safe = idx.clamp_min(0).long()
+        valid = idx >= 0
+        if self.groups is None or self.groups.entries.numel() < idx.numel():
+            self.groups = K.FeatureGroups(F, idx.numel(), x.device)
+        self.groups.build(idx)
+        self.loss_sum.zero_()
+        dS = torch.zeros(B, cap, dtype=torch.float32, device=x.device)
+        dtheta = torch.zeros(F, dtype=torch.float32, device=x.device)
+        l_s_sum = torch.zeros((), dtype=torch.float32, device=x.device)
+        per_head = []
+        c = float(tanh_stretch)
+        for h in range(H_l):
+            xh = x[:, h].contiguous()
+            n_h = self.dec_norm[h]
+            active = valid & (s_val > t_head[h][safe])
+            act = torch.where(active, s_val, torch.zeros_like(s_val))
+            dxhat, dact, _ = K.sparse_decode_loss(idx, act, self.WD_bf16[h], self.bD[h], xh, None, grad_scale, self.loss_sum)
+            n_e = n_h[safe]
+            self_scale = None
+            coef = 0.0
+            if l1_coefficient:
+                u = torch.tanh(c * act * n_e)
+                sech2 = 1.0 - u * u
+                l_s_sum = l_s_sum + (u * active).sum()
+                coef = l1_coefficient * c / (B * H)
+                dact = dact + coef * n_e * sech2 * active
+                # the penalty also pulls on the decoder norm: d / d W_D[f] = (sum_b coef * act * sech^2) * W_D[f] / ||W_D[f]||
+                per_feat = torch.zeros(F, dtype=torch.float32, device=x.device)
+                per_feat.index_add_(0, safe.reshape(-1), (coef * act * sech2 * active).reshape(-1))
+                self_scale = per_feat / n_h
+            dS_h = dact * active
+            dS += dS_h
+            # threshold gradient: dense part (reconstruction gradient at every entry inside the window) ...
+            # (the tanh penalty's derivative with respect to the JumpReLU output is coef at every entry with zero activation:
+            # the dense pass adds it per window hit)
+            G = K.encoder_hidden(dxhat, self.WD_bf16[h], None)  # [B, F] bf16 = d x_hat . W_D^T
+            S.jumprelu_window_grad(G, S_sum, n_h, theta, self.window, dtheta, add_per_hit=coef if l1_coefficient else 0.0)
+            if l1_coefficient:  # ... and the active entries, whose derivative is coef * sech^2, are corrected on the lists
+                x_e = s_val * n_e
+                hit = active & ((x_e - theta[safe]).abs() < 0.5 * self.window)
+                contrib = coef * (sech2 - 1.0) * (-theta[safe] / self.window) * hit
+                dtheta.index_add_(0, safe.reshape(-1), contrib.reshape(-1))
+            per_head.append((xh, act, dxhat, self_scale))
+        if self.head_size > 1:  # the lists are the same on every rank: the sum over heads is element-wise
+            dist.all_reduce(dS, group=self.head_group)
+            dist.all_reduce(dtheta, group=self.head_group)
+        self.t += 1
+        b1, b2 = self.betas
+        for h, (xh, act, dxhat, self_scale) in enumerate(per_head):
+            (mE, vE), (mD, vD), (mb, vb) = self.state["W_E"], self.state["W_D"], self.state["b_E"]
+            K.sparse_grad_adam(self.groups, act, dS, xh, dxhat, self.WD[h], mD[h], vD[h], self.WD_bf16[h], self.WE[h], mE[h], vE[h],
+                               self.WE_bf16[h], self.bE[h], mb[h], vb[h], self.dec_norm[h], None, None, lr, b1, b2, self.eps, self.t,
+                               True, wd_self_scale=self_scale)  # fmt: skip
+            m, v = self.state["b_D"]
+            K.adam_flat(self.bD[h], K.colsum_bf16(dxhat), m[h], v[h], lr, b1, b2, self.eps, self.t)
+        m, v = self.state["log_theta"]
+        K.adam_flat(self.log_theta, dtheta * theta, m, v, lr * self.jumprelu_lr_factor, b1, b2, self.eps, self.t)
+        l_rec = (self.loss_sum / (B * H_l)).squeeze(0)
+        l_s = l1_coefficient * l_s_sum / (B * H_l)
+        self.last = {"l_rec": l_rec, "l_s": l_s, "l0": valid.sum() / B}
+        return l_rec + l_s
+
+    def optimizer_state(self) -> dict:
+        out = {"step": self.t}
+        names = {"W_E": "W_E", "W_D": "W_D", "b_E": "b_E", "b_D": "b_D", "log_theta": "activation_function.log_jumprelu_threshold"}
+        for key, (m, v) in self.state.items():
+            tr = (lambda t: t.transpose(1, 2)) if key == "W_E" else (lambda t: t)
+            out[names[key]] = {"exp_avg": tr(m), "exp_avg_sq": tr(v)}
+        return out
+
+    def load_optimizer_state(self, sd: dict) -> None:
+        self.t = int(sd["step"])
+        names = {"W_E": "W_E", "W_D": "W_D", "b_E": "b_E", "b_D": "b_D", "log_theta": "activation_function.log_jumprelu_threshold"}
+        for key, (m, v) in self.state.items():
+            if names[key] in sd:
+                src_m, src_v = sd[names[key]]["exp_avg"], sd[names[key]]["exp_avg_sq"]
+                if key == "W_E":
+                    src_m, src_v = src_m.transpose(1, 2), src_v.transpose(1, 2)
+                m.copy_(src_m)
+                v.copy_(src_v)

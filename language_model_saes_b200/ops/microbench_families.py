@@ -17,6 +17,8 @@ from . import attention as A
 from . import clt_kernels as CK
 from . import sae_kernels as K
 from . import select_kernels as S
+from ..utils.clocks import ClockSampler
+from . import microbench as _mb
 from .microbench import _timeit
 
 
@@ -26,15 +28,22 @@ def main(argv=None):
     ap.add_argument("--attn-shape", default="4,1024,64,64,128", help="batch,seq,heads,d_qk,d_v of the attention cases")
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--min-seconds", type=float, default=1.0, help="repeat every timed case until this much timed work has accumulated")
     a = ap.parse_args(argv)
+    _mb.MIN_SECONDS = a.min_seconds
     dev = torch.device("cuda")
+    # one clock record per report: SM clock (median under load), power, throttle reasons since the previous report
+    sampler = [ClockSampler(torch.cuda.current_device())]
+    sampler[0].start()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     want = lambda c: a.case in ("all", c)  # noqa: E731
 
     def report(name, ours, ref, **extra):
         rec = {"case": name, "ms_ours": round(ours[0], 4), "ms_reference_path": round(ref[0], 4),
-               "speedup": round(ref[0] / ours[0], 2), **extra}  # fmt: skip
+               "speedup": round(ref[0] / ours[0], 2), **extra, "clocks": sampler[0].stop()}  # fmt: skip
         print(json.dumps(rec), flush=True)
+        sampler[0] = ClockSampler(torch.cuda.current_device())
+        sampler[0].start()
 
     if want("attn") or a.case == "attn_fwd":
         # default: low-rank sparse attention at d_sae 8192: 64 QK heads of width 64, OV groups of 128, 4 x 1024 tokens
@@ -170,6 +179,9 @@ def main(argv=None):
         report("crosscoder_head_sum_gemm_M4096_4heads_d768_F24576", t_o, t_r,
                tflops_ours=round(2.0 * M * heads * d * N / t_o[0] / 1e9, 1))  # fmt: skip
         K.check_status(dev)
+
+
+    sampler[0].stop()
 
 
 if __name__ == "__main__":

@@ -504,6 +504,7 @@ def sparse_grad_adam(
     state_f0: int = 0,
     publish: tuple[list[int], list[int], int, torch.Tensor] | None = None,
     extra: tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor | None] | None = None,
+    wd_self_scale: torch.Tensor | None = None,
 ):
     """Rebuild the two sparse gradient rows per feature and apply Adam in the same pass (in place). ``f_range``
     restricts the launch to feature rows ``[begin, end)``. With ``dxhat_aux`` the code slots ``>= k_main`` of every row
@@ -511,8 +512,9 @@ def sparse_grad_adam(
     start at that feature row (optimizer state sharded by feature row). ``publish`` = ``DataParallelComm.pub_args()``:
     the new shadow rows, norms and biases are stored into every replica's copy. ``extra`` = ``(row_of_feature int32 [F],
     gD fp32 [R, d], gE fp32 [R, d], gb fp32 [R] | None)``: dense gradient rows that are added for the features with
-    ``row_of_feature >= 0`` (e.g. the auxiliary loss over a compact dictionary of dead features). A non-zero kernel
-    status word turns the update into a no-op (CUDA path)."""
+    ``row_of_feature >= 0`` (e.g. the auxiliary loss over a compact dictionary of dead features). ``wd_self_scale`` fp32
+    ``[F]``: the decoder row's gradient gets ``wd_self_scale[f] * W_D[f, :]`` added (the gradient that a penalty on the
+    row's norm sends into the row). A non-zero kernel status word turns the update into a no-op (CUDA path)."""
     if not WD.is_cuda:
         if f_range is not None and tuple(f_range) != (0, groups.F):
             lo, hi = f_range
@@ -525,7 +527,8 @@ def sparse_grad_adam(
             sparse_grad_adam(sub, act, dact, x, dxhat, WD[sl], mD[st], vD[st], WD_bf16[sl], WE[sl], mE[st], vE[st], WE_bf16[sl],
                              bE[sl] if bE is not None else None, mbE[st] if mbE is not None else None,
                              vbE[st] if vbE is not None else None, dec_norm[sl] if dec_norm is not None else None, grad_mul,
-                             grad_sq_sum, lr, beta1, beta2, eps, step, update, None, 0, dxhat_aux, k_main, extra=sub_extra)  # fmt: skip
+                             grad_sq_sum, lr, beta1, beta2, eps, step, update, None, 0, dxhat_aux, k_main, extra=sub_extra,
+                             wd_self_scale=wd_self_scale[sl] if wd_self_scale is not None else None)  # fmt: skip
             return
         idx_like = torch.full((act.numel(),), -1, dtype=torch.int64)
         off = groups.offsets.long()
@@ -551,6 +554,8 @@ def sparse_grad_adam(
         gD, gE, gb = gD * mul, gE * mul, gb * mul
         if grad_sq_sum is not None:
             grad_sq_sum += gD.pow(2).sum() + gE.pow(2).sum() + gb.pow(2).sum()
+        if wd_self_scale is not None:
+            gD = gD + (wd_self_scale * mul).unsqueeze(1) * WD
         if update:
             ref_adam(WD, gD, mD, vD, lr, beta1, beta2, eps, step)
             ref_adam(WE, gE, mE, vE, lr, beta1, beta2, eps, step)
@@ -565,7 +570,7 @@ def sparse_grad_adam(
         groups.offsets, groups.entries, act, dact, x, dxhat, WD, mD, vD, WD_bf16, WE, mE, vE, WE_bf16, bE, mbE, vbE,
         dec_norm, grad_mul, grad_sq_sum, lr, beta1, beta2, eps, step, update, *(f_range if f_range is not None else (0, -1)), ctas_per_sm, dxhat_aux, k_main, grad_out[0], grad_out[1],
         status_buffer(WD.device), state_f0, *(publish if publish is not None else ([], [], 0, None)),
-        *(extra if extra is not None else (None, None, None, None)),
+        *(extra if extra is not None else (None, None, None, None)), wd_self_scale,
     )  # fmt: skip
 
 

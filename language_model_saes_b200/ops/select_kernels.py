@@ -162,11 +162,11 @@ def dense_rows_to_sparse(acts: torch.Tensor, cap: int | None = None) -> tuple[to
     B = acts.shape[0]
     nnz = torch.empty(B, dtype=torch.int32, device=acts.device)
     if cap is None:
-        ext.row_compact(acts, None, None, nnz, None, None, None, None)
+        ext.row_compact(acts, None, None, nnz, None, None, None, None, None)
         cap = max(8, -(-int(nnz.max()) // 8) * 8)
     idx = torch.empty(B, cap, dtype=torch.int32, device=acts.device)
     val = torch.empty(B, cap, dtype=torch.float32, device=acts.device)
-    ext.row_compact(acts, idx, val, nnz, None, None, None, None)
+    ext.row_compact(acts, idx, val, nnz, None, None, None, None, None)
     return idx, val
 
 
@@ -196,11 +196,11 @@ def threshold_rows_to_sparse(g: torch.Tensor, thr: torch.Tensor, col_div: torch.
     quota = None
     if n_ties is None:
         if cap is None:
-            ext.row_compact(g, None, None, nnz, thr, None, None, None)
+            ext.row_compact(g, None, None, nnz, thr, None, None, None, None)
             widest = nnz.max()
     else:
         ties = torch.empty(B, dtype=torch.int32, device=g.device)
-        ext.row_compact(g, None, None, nnz, thr, None, ties, None)
+        ext.row_compact(g, None, None, nnz, thr, None, ties, None, None)
         budget = n_ties.reshape(()).to(torch.int64)
         if tie_group is not None and dist.get_world_size(tie_group) > 1:
             mine = ties.sum(dtype=torch.int64).reshape(1)
@@ -218,10 +218,54 @@ def threshold_rows_to_sparse(g: torch.Tensor, thr: torch.Tensor, col_div: torch.
     assert cap % 8 == 0 and cap > 0
     idx = torch.empty(B, cap, dtype=torch.int32, device=g.device)
     val = torch.empty(B, cap, dtype=torch.float32, device=g.device)
-    ext.row_compact(g, idx, val, nnz, thr, col_div, None, quota)  # nnz: the row's full count, also beyond the list width
+    ext.row_compact(g, idx, val, nnz, thr, col_div, None, quota, None)  # nnz: the row's full count, also beyond the list width
     if overflow is not None:
         overflow += (nnz > cap).sum()
     return idx, val
+
+
+@torch.no_grad()
+def column_threshold_rows_to_sparse(x: torch.Tensor, col_thr: torch.Tensor, cap: int,
+                                    overflow: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """Entries of ``x [B, N]`` above their column's threshold ``col_thr [N]`` as padded sparse lists of fixed width ``cap``
+    (ascending columns, values unchanged): the JumpReLU selection of pre-activations against per-feature thresholds. Rows
+    with more than ``cap`` such entries keep the first ones and are counted in ``overflow``."""
+    assert x.ndim == 2 and cap % 8 == 0 and cap > 0
+    B = x.shape[0]
+    if not _kernel_ok(x):
+        keep = x.float() > col_thr.float()
+        if overflow is not None:
+            overflow += (keep.sum(-1) > cap).sum()
+        idx = torch.full((B, cap), -1, dtype=torch.int32, device=x.device)
+        val = torch.zeros(B, cap, dtype=torch.float32, device=x.device)
+        for b in range(B):
+            cols = torch.nonzero(keep[b], as_tuple=False).flatten()[:cap]
+            idx[b, : cols.numel()] = cols.to(torch.int32)
+            val[b, : cols.numel()] = x[b, cols].float()
+        return idx, val
+    x = x.contiguous()
+    idx = torch.empty(B, cap, dtype=torch.int32, device=x.device)
+    val = torch.empty(B, cap, dtype=torch.float32, device=x.device)
+    nnz = torch.empty(B, dtype=torch.int32, device=x.device)
+    K._ext().row_compact(x, idx, val, nnz, None, None, None, None, col_thr.float().contiguous())
+    if overflow is not None:
+        overflow += (nnz > cap).sum()
+    return idx, val
+
+
+def jumprelu_window_grad(G: torch.Tensor, S: torch.Tensor, n: torch.Tensor, theta: torch.Tensor, window: float,
+                         dtheta: torch.Tensor, add_per_hit: float = 0.0) -> None:
+    """``dtheta[f] += sum_b (G[b, f] / n[f] + add_per_hit) * (-theta[f] / window) * 1[|S n - theta| < window / 2 and S n > 0]``:
+    the JumpReLU threshold gradient of a head from the dense reconstruction gradient ``G`` and the summed pre-activations
+    ``S`` (both ``[B, F]`` bf16 on the GPU); ``add_per_hit`` is a loss derivative that is the same at every entry."""
+    if not (G.is_cuda and G.dtype == torch.bfloat16 and S.dtype == torch.bfloat16 and G.shape[1] % 8 == 0):
+        x = S.float() * n
+        hit = ((x - theta).abs() < 0.5 * window) & (x > 0)
+        total = torch.where(hit, G.float(), torch.zeros((), device=G.device)).sum(0) / n + add_per_hit * hit.sum(0)
+        dtheta += total * (-theta / window)
+        return
+    K._ext().jumprelu_window_grad(G.contiguous(), S.contiguous(), n.contiguous(), theta.contiguous(), float(window),
+                                  float(add_per_hit), dtheta)
 
 
 def _ref_threshold_rows_to_sparse(g, thr, col_div, width_group, n_ties, tie_group, cap=None, overflow=None):

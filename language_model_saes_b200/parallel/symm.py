@@ -426,6 +426,57 @@ class BroadcastComm:
         return out
 
 
+class AllReduceComm:
+    """In-place sum over a group of a bf16 matrix that lives in this communicator's symmetric buffer: ``matrix(rows, cols)``
+    hands out the view to fill (e.g. as the output of a GEMM), ``all_reduce(rows, cols)`` replaces it on every rank by the
+    sum over ranks in ONE kernel (``ops/csrc/comm_ops.cu::allreduce_bf16_inplace_kernel``): with an NVSwitch multicast
+    mapping the owner of a share reads the sum with ``multimem.ld_reduce`` (added inside the switch) and writes it to
+    every rank with ``multimem.st``; without one, by peer loads and stores. Two buffers alternate between calls, so a
+    rank may fill the next matrix while a slower peer still reads the previous sums."""
+
+    PHASE_READY, PHASE_DONE = 0, 1
+
+    def __init__(self, group: dist.ProcessGroup | None, device: torch.device, max_rows: int, n_cols: int, use_multicast: bool | None = None):
+        self.group, self.device = group, device
+        self.world = dist.get_world_size(group) if group is not None else 1
+        self.rank = dist.get_rank(group) if group is not None else 0
+        assert self.world <= _MAX_PEERS and n_cols % 8 == 0
+        self.max_rows, self.n_cols = max_rows, n_cols
+        zone = _align(max_rows * n_cols * 2)
+        self.off = [_align(FLAG_BYTES), _align(FLAG_BYTES) + zone]
+        self.nbytes = self.off[1] + zone
+        if group is not None and self.world > 1:
+            self.buf, self.handle, ptrs, mc = _rendezvous(self.nbytes, group, device)
+        else:
+            self.buf, ptrs, mc = torch.zeros(self.nbytes, dtype=torch.uint8, device=device), None, 0
+            ptrs = [self.buf.data_ptr()]
+        if use_multicast is None:
+            use_multicast = os.environ.get("LMSAE_ALLREDUCE_MULTICAST", "1") == "1"
+        self.use_multicast = bool(use_multicast and mc)
+        self.stats = WaitStats(device)
+        self.table = peer_table(self.world, self.rank, ptrs, 0, multicast_ptr=mc, stats_ptr=self.stats.buf.data_ptr())
+        self.done_counter = torch.zeros(1, dtype=torch.int32, device=device)
+        self.epoch = 0
+        torch.cuda.synchronize(device)
+        if group is not None and self.world > 1:
+            dist.barrier(group=group)
+
+    def matrix(self, rows: int, cols: int | None = None) -> torch.Tensor:
+        """The bf16 ``[rows, cols]`` view that the NEXT ``all_reduce`` will sum."""
+        cols = cols or self.n_cols
+        assert rows <= self.max_rows and cols == self.n_cols
+        off = self.off[(self.epoch + 1) & 1]
+        return self.buf[off : off + rows * cols * 2].view(torch.bfloat16).view(rows, cols)
+
+    def all_reduce(self, rows: int) -> torch.Tensor:
+        self.epoch += 1
+        off = self.off[self.epoch & 1]
+        n16 = rows * self.n_cols * 2 // 16
+        K._ext().comm_allreduce_bf16(self.table, off, n16, self.PHASE_READY, self.PHASE_DONE, self.epoch, self.use_multicast,
+                                     self.done_counter, K.status_buffer(self.device))  # fmt: skip
+        return self.buf[off : off + rows * self.n_cols * 2].view(torch.bfloat16).view(rows, self.n_cols)
+
+
 PHASE_HS_REDUCED, PHASE_HS_GATHERED = 0, 1
 
 
@@ -472,7 +523,7 @@ class HeadSumComm:
         st = K.status_buffer(self.device)
         self.epoch += 1
         slab_off = self.slab_off[self.epoch & 1]
-        ext.head_sum_gemm(x, w, bias, heads, rows_per_head, self.n_cols, [p + slab_off for p in self.ptrs], pair, st)
+        ext.head_sum_gemm(x, w, bias, heads, rows_per_head, self.n_cols, [p + slab_off for p in self.ptrs], pair, st, None)
         ext.comm_signal(self.table, PHASE_HS_REDUCED, self.epoch)
         ext.comm_headsum_gather(self.table, slab_off, self.out_off, M, self.cols, 0 if out_dtype == torch.float32 else 1,
                                 PHASE_HS_REDUCED, PHASE_HS_GATHERED, self.epoch, self.done_counter, st)  # fmt: skip

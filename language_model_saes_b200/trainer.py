@@ -495,7 +495,14 @@ class Trainer:
             self.fused = FusedTopKSAEStep(sae, betas=self.cfg.betas, comm=comm, dp_comm=dp_comm)
             logger.info("Training on the fused sm_100a kernel path" + (" with peer-memory collectives" if comm or dp_comm else ""))
         else:
-            logger.info(f"Training on the generic autograd path ({why})")
+            from .ops.fused_crosscoder import FusedCrosscoderStep
+
+            ok_cc, why_cc = (False, "disabled") if not self.cfg.use_fused_kernels else FusedCrosscoderStep.supports(sae, self.cfg)
+            if ok_cc:
+                self.fused = FusedCrosscoderStep(sae, betas=self.cfg.betas, jumprelu_lr_factor=self.cfg.jumprelu_lr_factor)
+                logger.info("Training the crosscoder on the fused sm_100a kernel path")
+            else:
+                logger.info(f"Training on the generic autograd path ({why if type(sae).__name__ != 'Crosscoder' else why_cc})")
         groups = []
         for g in sae.get_parameters():
             if not g["params"]:
@@ -922,6 +929,20 @@ class Trainer:
             return ctx["loss"].detach()
         with timer.time("reduce_gradients"):
             reduce_gradients(sae.parameters(), mesh_group(sae.device_mesh, "data"))
+            if mesh_dim_size(sae.device_mesh, "head") > 1:
+                # Parameters that are not split over the head dimension (a crosscoder's shared JumpReLU thresholds) are
+                # replicated on the head ranks, each of which holds the gradient of its own heads only: sum them, or the
+                # replicas drift apart (the model scales its loss by 1 / head ranks, so the sum is the gradient of the
+                # mean over all heads).
+                maps = sae.dim_maps()
+                shared = [p for n, p in sae.named_parameters() if p.grad is not None and "head" not in maps.get(n, {})]
+                if shared:
+                    flat = torch.cat([p.grad.reshape(-1).float() for p in shared])
+                    dist.all_reduce(flat, group=mesh_group(sae.device_mesh, "head"))
+                    off = 0
+                    for p in shared:
+                        p.grad.copy_(flat[off : off + p.numel()].view_as(p.grad))
+                        off += p.numel()
         with timer.time("clip_grad_norm"):
             ctx["grad_norm_before_clipping"] = clip_grad_norm(
                 [p for n, p in sae.named_parameters() if p.grad is not None and "log_jumprelu_threshold" not in n],
@@ -938,8 +959,42 @@ class Trainer:
             self.scheduler.step()
         return ctx["loss"].detach()
 
+    def _fused_crosscoder_iteration(self, sae: SparseDictionary, batch: dict[str, Tensor]) -> Tensor:
+        """One step of ``ops.fused_crosscoder.FusedCrosscoderStep``: this rank's hook points, normalised, stacked to
+        ``[tokens, local heads, d_model]`` in bf16."""
+        f = self.fused
+        mask = batch.get("mask")
+        if mask is not None and not batch.get("_mask_all", None if mask.device.type == "cpu" else bool(mask.all())):
+            raise NotImplementedError("the fused crosscoder path trains on unmasked tokens; set use_fused_kernels=False for masked batches")
+        cols = []
+        for hp in sae.local_hook_points():
+            raw = batch[hp]
+            assert raw.ndim == 2, "the fused path trains on [tokens, d_model] activations"
+            if sae.cfg.norm_activation == "dataset-wise":
+                factor = math.sqrt(sae.cfg.d_model) / float(sae.dataset_average_activation_norm[hp])
+                raw = raw if factor == 1.0 else raw * factor
+            elif sae.cfg.norm_activation != "inference":
+                raw = raw * sae.compute_norm_factor(raw, hp)
+            if raw.shape[-1] < sae.cfg.d_model:
+                raw = torch.nn.functional.pad(raw, (0, sae.cfg.d_model - raw.shape[-1]))
+            cols.append(raw.to(torch.bfloat16))
+        x = torch.stack(cols, dim=1)
+        lr = float(self.cfg.lr) * (self._lr_lambda(self.cur_step) if self._lr_lambda is not None else 1.0)
+        l1 = self._l1_coefficient() if self.cfg.sparsity_loss_type == "tanh" else 0.0
+        loss = f.step(x, lr, l1_coefficient=l1, tanh_stretch=self.cfg.tanh_stretch_coefficient)
+        if not self.cfg.skip_metrics_calculation and (self.cur_step + 1) % self.cfg.log_frequency == 0:
+            last = {k: float(v) for k, v in f.last.items()}
+            out = {"losses/overall_loss": float(loss), "losses/mse_loss": last["l_rec"], "losses/sparsity_loss": last["l_s"],
+                   "metrics/l0_candidates": last["l0"], "details/list_overflow_tokens": int(f.list_overflow)}  # fmt: skip
+            out.update(self._details({"l1_coefficient": l1}, lr))
+            out.update(sae.log_statistics())
+            self._emit(sae, out)
+        return loss
+
     def _fused_iteration(self, sae: SparseDictionary, batch: dict[str, Tensor]) -> Tensor:
         f = self.fused
+        if type(f).__name__ == "FusedCrosscoderStep":
+            return self._fused_crosscoder_iteration(sae, batch)
         hin, hout = sae.cfg.hook_point_in, sae.cfg.hook_point_out
         x_raw = batch[hin]
         assert x_raw.ndim == 2, "the fused path trains on [tokens, d_model] activations"

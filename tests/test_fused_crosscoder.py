@@ -1,0 +1,120 @@
+"""The fused crosscoder step (``ops.fused_crosscoder.FusedCrosscoderStep``) against the generic autograd path of the
+same model: losses and every parameter after a few Adam steps. On the CPU the step runs the plain-torch statements of
+its kernels (the math and the step's own bookkeeping are what is checked); on a GPU the kernels themselves."""
+
+import copy
+
+import pytest
+import torch
+
+from language_model_saes_b200.models.crosscoder import Crosscoder, CrosscoderConfig
+from language_model_saes_b200.ops.fused_crosscoder import FusedCrosscoderStep
+
+DEVICES = [pytest.param("cuda", marks=pytest.mark.gpu), "cpu"]
+
+
+def _model(dev, H=3, d=64, F=512, thr=-0.5):
+    torch.manual_seed(0)
+    cfg = CrosscoderConfig(hook_points=[f"s{i}" for i in range(H)], d_model=d, expansion_factor=F / d, act_fn="jumprelu", device=dev,
+                           dtype=torch.float32, norm_activation="inference")  # fmt: skip
+    m = Crosscoder(cfg)
+    m.init_parameters(encoder_uniform_bound=0.2, decoder_uniform_bound=0.2, init_log_jumprelu_threshold_value=thr)
+    m.set_decoder_to_fixed_norm(1.0, True)
+    m.init_encoder_with_decoder_transpose(1.0 / H)
+    with torch.no_grad():  # heads that differ, non-trivial biases and thresholds
+        m.W_D.mul_(1 + 0.1 * torch.arange(H, device=dev).view(H, 1, 1))
+        m.b_E.add_(0.02 * torch.randn_like(m.b_E))
+        m.b_D.add_(0.02 * torch.randn_like(m.b_D))
+        m.activation_function.log_jumprelu_threshold.add_(0.1 * torch.randn_like(m.activation_function.log_jumprelu_threshold))
+    return m
+
+
+@pytest.mark.parametrize("dev", DEVICES)
+@pytest.mark.parametrize("l1", [0.0, 3e-2])
+def test_fused_crosscoder_step_matches_autograd(dev, l1):
+    H, d, F, B, lr, steps = 3, 64, 512, 256, 1e-3, 4
+    ref = _model(dev, H, d, F)
+    fused_model = copy.deepcopy(ref)
+    engine = FusedCrosscoderStep(fused_model, list_width=F)  # lists wide enough for every candidate
+    assert FusedCrosscoderStep.supports(fused_model)[0]
+    g = torch.Generator(device=dev).manual_seed(1)
+    basis = torch.randn(8, d, device=dev, generator=g)
+    data = []
+    for _ in range(steps):
+        z = torch.randn(B, 8, device=dev, generator=g)
+        x = torch.stack([z @ basis * (1 + 0.2 * h) + 0.3 * torch.randn(B, d, device=dev, generator=g) for h in range(H)], dim=1)
+        data.append((x * (d**0.5 / x.norm(dim=-1).mean())).to(torch.bfloat16))
+    opt = torch.optim.Adam(ref.parameters(), lr=lr)
+    ref_losses, fused_losses = [], []
+    tokens = torch.zeros(B, dtype=torch.long, device=dev)
+    for x in data:
+        opt.zero_grad()
+        batch = {f"s{h}": x[:, h].float() for h in range(H)} | {"tokens": tokens}
+        with torch.autocast(dev, dtype=torch.bfloat16, enabled=dev == "cuda"):
+            out = ref.compute_loss(batch, sparsity_loss_type="tanh" if l1 else None, l1_coefficient=l1, return_aux_data=True)
+        out["loss"].backward()
+        opt.step()
+        ref_losses.append(float(out["loss"].detach()))
+        fused_losses.append(float(engine.step(x, lr, l1_coefficient=l1)))
+    assert int(engine.list_overflow) == 0
+    r, f = torch.tensor(ref_losses), torch.tensor(fused_losses)
+    tol = 3e-2 if dev == "cuda" else 2e-3  # (the GPU reference runs under bf16 autocast)
+    assert torch.allclose(r, f, rtol=tol), (ref_losses, fused_losses)
+    assert r[-1] < r[0]
+    # Adam's first steps move every weight that got any gradient by about lr whatever the gradient's size: compare the
+    # movement, not a rounding tolerance
+    for name in ("W_D", "W_E", "b_E", "b_D", "activation_function.log_jumprelu_threshold"):
+        a = dict(ref.named_parameters())[name].detach().float()
+        b = dict(fused_model.named_parameters())[name].detach().float()
+        moved = (a - dict(_model(dev, H, d, F).named_parameters())[name].detach().float()).abs().mean()
+        assert float((a - b).abs().mean()) < (0.25 if dev == "cuda" else 0.05) * float(moved) + 1e-7, name
+
+
+def test_fused_crosscoder_selection_is_the_union_over_heads_cpu():
+    """A head's codes are exactly its own JumpReLU outputs: the union list only adds zero entries."""
+    m = _model("cpu", 2, 32, 128)
+    engine = FusedCrosscoderStep(m, list_width=128)
+    x = torch.randn(16, 2, 32).to(torch.bfloat16)
+    want, _ = m.encode(x.float(), return_hidden_pre=True)  # [B, H, F]
+    engine.step(x, 0.0)  # lr 0: nothing moves
+    assert float(engine.last["l0"]) >= float((want != 0).any(dim=1).sum(-1).float().mean()) - 1e-6
+
+
+@pytest.mark.gpu
+def test_trainer_picks_the_fused_crosscoder_path_and_the_loss_goes_down():
+    import tempfile
+
+    from language_model_saes_b200.trainer import Trainer, TrainerConfig
+
+    H, d, F, B, steps = 4, 64, 2048, 512, 30
+    m = _model("cuda", H, d, F, thr=0.3)
+    m.cfg.norm_activation = "dataset-wise"
+    m.set_dataset_average_activation_norm({f"s{i}": d**0.5 for i in range(H)})
+    g = torch.Generator(device="cuda").manual_seed(1)
+    basis = torch.randn(12, d, device="cuda", generator=g)
+
+    def stream():
+        for _ in range(steps + 1):
+            z = torch.randn(B, 12, device="cuda", generator=g)
+            rec = {}
+            for h in range(H):
+                x = z @ basis + 0.05 * (h + 1) * torch.randn(B, d, device="cuda", generator=g)
+                rec[f"s{h}"] = (x * (d**0.5 / x.norm(dim=-1).mean())).to(torch.bfloat16)
+            rec["tokens"] = torch.zeros(B, dtype=torch.long, device="cuda")
+            yield rec
+
+    losses = []
+    with tempfile.TemporaryDirectory() as tmp:
+        tr = Trainer(TrainerConfig(total_training_tokens=steps * B, lr=2e-3, lr_warm_up_steps=2, log_frequency=10**6, n_checkpoints=0,
+                                   exp_result_path=tmp, skip_metrics_calculation=True, l1_coefficient=1e-3, sparsity_loss_type="tanh"))  # fmt: skip
+        orig = tr._fused_iteration
+
+        def spy(*a, **kw):
+            out = orig(*a, **kw)
+            losses.append(float(out))
+            return out
+
+        tr._fused_iteration = spy
+        tr.fit(m, stream())
+        assert type(tr.fused).__name__ == "FusedCrosscoderStep"
+    assert len(losses) == steps and all(l == l for l in losses) and sum(losses[-5:]) < sum(losses[:5]), losses

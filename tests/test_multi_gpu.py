@@ -424,3 +424,83 @@ def test_head_parallel_crosscoder_sums_pre_activations_in_the_gemm_epilogue():
         return float((u.float() - v.float()).norm() / v.float().norm()) < 0.05
 
     assert close(a.W_E.grad, b.W_E.grad) and close(a.b_E.grad, b.b_E.grad)
+
+
+@needs2
+@distributed_test(nproc_per_node=2, backend="nccl")
+def test_in_place_all_reduce_kernel_and_head_parallel_fused_crosscoder():
+    """The one-kernel in-place all-reduce of a bf16 matrix (NVSwitch multicast loads / stores where the fabric offers a
+    mapping, peer loads / stores otherwise), and the fused crosscoder step with its heads split over two ranks against the
+    generic autograd path on the same mesh."""
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import copy
+
+    from language_model_saes_b200.models.crosscoder import Crosscoder, CrosscoderConfig
+    from language_model_saes_b200.ops import sae_kernels as K
+    from language_model_saes_b200.ops.fused_crosscoder import FusedCrosscoderStep
+    from language_model_saes_b200.parallel.mesh import build_mesh
+    from language_model_saes_b200.parallel.symm import AllReduceComm
+
+    rank = dist.get_rank()
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    mesh = build_mesh("cuda", (2, 1, 1), ("head", "data", "model"))
+    group = mesh.get_group("head")
+    rows, cols = 1000, 4096
+    for use_mc in (False, True):
+        comm = AllReduceComm(group, dev, rows, cols, use_multicast=use_mc)
+        if use_mc and not comm.use_multicast:
+            print("no multicast mapping for this group: the multimem variant is not exercised here")
+            continue
+        for call in range(3):  # both buffers and their re-use
+            torch.manual_seed(10 * call + rank)
+            mine = torch.randn(rows, cols, device=dev).to(torch.bfloat16)
+            want = mine.float().clone()
+            dist.all_reduce(want)
+            comm.matrix(rows).copy_(mine)
+            got = comm.all_reduce(rows)
+            K.check_status(dev)
+            assert torch.allclose(got.float(), want, atol=3e-2, rtol=2e-2), (use_mc, call, float((got.float() - want).abs().max()))
+
+    # fused crosscoder step, 4 heads over 2 ranks, against autograd on the same mesh
+    H, d, F, B, lr, steps = 4, 64, 2048, 512, 1e-3, 4
+    torch.manual_seed(0)
+    cfg = CrosscoderConfig(hook_points=[f"s{i}" for i in range(H)], d_model=d, expansion_factor=F / d, act_fn="jumprelu", device=str(dev),
+                           dtype=torch.float32, norm_activation="inference")  # fmt: skip
+    ref = Crosscoder(cfg, device_mesh=mesh)
+    ref.init_parameters(encoder_uniform_bound=0.2, decoder_uniform_bound=0.2, init_log_jumprelu_threshold_value=-0.3)
+    ref.set_decoder_to_fixed_norm(1.0, True)
+    ref.init_encoder_with_decoder_transpose(1.0 / H)
+    with torch.no_grad():
+        ref.W_D.mul_(1 + 0.1 * (torch.arange(2, device=dev) + 2 * rank).view(2, 1, 1))
+    fused_model = copy.deepcopy(ref)
+    fused_model.device_mesh = mesh
+    engine = FusedCrosscoderStep(fused_model, list_width=F)
+    g = torch.Generator(device=dev).manual_seed(1)
+    basis = torch.randn(8, d, device=dev, generator=g)
+    opt = torch.optim.Adam(ref.parameters(), lr=lr)
+    tokens = torch.zeros(B, dtype=torch.long, device=dev)
+    ref_losses, fused_losses = [], []
+    for _ in range(steps):
+        z = torch.randn(B, 8, device=dev, generator=g)
+        x = torch.stack([z @ basis * (1 + 0.2 * h) + 0.3 * torch.randn(B, d, device=dev, generator=g) for h in range(H)], dim=1)
+        x = (x * (d**0.5 / x.norm(dim=-1).mean())).to(torch.bfloat16)
+        dist.broadcast(x, src=0)
+        mine = x[:, 2 * rank : 2 * rank + 2].contiguous()
+        opt.zero_grad()
+        batch = {f"s{2 * rank + h}": mine[:, h].float() for h in range(2)} | {"tokens": tokens}
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            out = ref.compute_loss(batch, sparsity_loss_type="tanh", l1_coefficient=3e-2, return_aux_data=True)
+        out["loss"].backward()
+        thr = ref.activation_function.log_jumprelu_threshold
+        dist.all_reduce(thr.grad, group=group)  # shared parameter: the trainer sums its gradient over the head ranks
+        opt.step()
+        ref_losses.append(float(out["loss"].detach()))
+        local = engine.step(mine, lr, l1_coefficient=3e-2)
+        dist.all_reduce(local, group=group)
+        fused_losses.append(float(local) / 2)
+    K.check_status(dev)
+    assert int(engine.list_overflow) == 0
+    assert torch.allclose(torch.tensor(ref_losses), torch.tensor(fused_losses), rtol=3e-2), (ref_losses, fused_losses)
+    a, b = ref.activation_function.log_jumprelu_threshold.detach(), fused_model.activation_function.log_jumprelu_threshold.detach()
+    assert float((a - b).abs().mean()) < 0.3 * lr * steps, float((a - b).abs().mean())
