@@ -494,7 +494,7 @@ def run_config4(args, bench) -> None:
             extra = dict(prefetch_to_device=True, lr_warm_up_steps=0, lr_cool_down_steps=0) if impl == "ours" else dict(amp_dtype=torch.bfloat16)
             tcfg = pkg.TrainerConfig(total_training_tokens=(W + Ks) * B, lr=c["lr"], lr_scheduler_name="constant",
                                      log_frequency=1 if impl == "ours" else 10**9, skip_metrics_calculation=True, n_checkpoints=0,
-                                     exp_result_path=tmp, k_warmup_steps=0, l1_coefficient=1e-3, l1_coefficient_warmup_steps=0,
+                                     exp_result_path=tmp, k_warmup_steps=0, l1_coefficient=1e-3, l1_coefficient_warmup_steps=1,
                                      sparsity_loss_type="tanh", **extra)  # fmt: skip
             return pkg.Trainer(tcfg)
 

@@ -342,9 +342,10 @@ lmsae::AdamHyper make_hyper(double lr, double beta1, double beta2, double eps, i
 }
 
 void sparse_grad_adam(const Tensor& offsets, const Tensor& entries, const Tensor& act, const Tensor& dact,
-                      const Tensor& x, const Tensor& dxhat, const Tensor& WD, const Tensor& mD, const Tensor& vD,
-                      const Tensor& WD_bf16, const Tensor& WE, const Tensor& mE, const Tensor& vE,
-                      const Tensor& WE_bf16, const c10::optional<Tensor>& bE, const c10::optional<Tensor>& mbE,
+                      const Tensor& x, const Tensor& dxhat, const c10::optional<Tensor>& WD_o, const c10::optional<Tensor>& mD_o,
+                      const c10::optional<Tensor>& vD_o, const c10::optional<Tensor>& WD_bf16_o,
+                      const c10::optional<Tensor>& WE_o, const c10::optional<Tensor>& mE_o, const c10::optional<Tensor>& vE_o,
+                      const c10::optional<Tensor>& WE_bf16_o, const c10::optional<Tensor>& bE, const c10::optional<Tensor>& mbE,
                       const c10::optional<Tensor>& vbE, const c10::optional<Tensor>& dec_norm,
                       const c10::optional<Tensor>& grad_mul, const c10::optional<Tensor>& grad_sq_sum, double lr,
                       double beta1, double beta2, double eps, int64_t step, bool update, int64_t f_begin,
@@ -354,7 +355,18 @@ void sparse_grad_adam(const Tensor& offsets, const Tensor& entries, const Tensor
                       const std::vector<int64_t>& pub_offsets, int64_t pub_epoch,
                       const c10::optional<Tensor>& pub_done, const c10::optional<Tensor>& extra_row,
                       const c10::optional<Tensor>& extra_gD, const c10::optional<Tensor>& extra_gE,
-                      const c10::optional<Tensor>& extra_gb, const c10::optional<Tensor>& wd_self_scale) {
+                      const c10::optional<Tensor>& extra_gb, const c10::optional<Tensor>& wd_self_scale,
+                      const c10::optional<Tensor>& norm_sq_accum) {
+  // one-sided launches: the decoder group (WD, mD, vD, WD_bf16) or the encoder group (WE, mE, vE, WE_bf16) may be absent
+  const bool has_d = WD_o.has_value(), has_e = WE_o.has_value();
+  TORCH_CHECK(has_d || has_e, "at least one of the decoder / encoder groups must be given");
+  TORCH_CHECK(!has_d || (mD_o.has_value() && vD_o.has_value() && WD_bf16_o.has_value()), "decoder group incomplete");
+  TORCH_CHECK(!has_e || (mE_o.has_value() && vE_o.has_value() && WE_bf16_o.has_value()), "encoder group incomplete");
+  const Tensor& any_w = has_d ? *WD_o : *WE_o;
+  const Tensor& WD = has_d ? *WD_o : any_w; const Tensor& mD = has_d ? *mD_o : any_w; const Tensor& vD = has_d ? *vD_o : any_w;
+  const Tensor& WE = has_e ? *WE_o : any_w; const Tensor& mE = has_e ? *mE_o : any_w; const Tensor& vE = has_e ? *vE_o : any_w;
+  const Tensor& WD_bf16 = has_d ? *WD_bf16_o : *WE_bf16_o;
+  const Tensor& WE_bf16 = has_e ? *WE_bf16_o : *WD_bf16_o;
   CHECK_T(offsets, torch::kInt32);
   CHECK_T(entries, torch::kInt32);
   CHECK_T(act, torch::kFloat32);
@@ -388,10 +400,16 @@ void sparse_grad_adam(const Tensor& offsets, const Tensor& entries, const Tensor
   p.dact = dact.data_ptr<float>();
   p.x = reinterpret_cast<const __nv_bfloat16*>(x.data_ptr());
   p.dxhat = reinterpret_cast<const __nv_bfloat16*>(dxhat.data_ptr());
-  p.WD = WD.data_ptr<float>(); p.mD = mD.data_ptr<float>(); p.vD = vD.data_ptr<float>();
-  p.WD_bf16 = reinterpret_cast<__nv_bfloat16*>(WD_bf16.data_ptr());
-  p.WE = WE.data_ptr<float>(); p.mE = mE.data_ptr<float>(); p.vE = vE.data_ptr<float>();
-  p.WE_bf16 = reinterpret_cast<__nv_bfloat16*>(WE_bf16.data_ptr());
+  if (has_d) {
+    p.WD = WD.data_ptr<float>(); p.mD = mD.data_ptr<float>(); p.vD = vD.data_ptr<float>();
+    p.WD_bf16 = reinterpret_cast<__nv_bfloat16*>(WD_bf16.data_ptr());
+  }
+  if (has_e) {
+    p.WE = WE.data_ptr<float>(); p.mE = mE.data_ptr<float>(); p.vE = vE.data_ptr<float>();
+    p.WE_bf16 = reinterpret_cast<__nv_bfloat16*>(WE_bf16.data_ptr());
+  }
+  if (norm_sq_accum.has_value()) { CHECK_T(*norm_sq_accum, torch::kFloat32); TORCH_CHECK(norm_sq_accum->numel() == WD.size(0)); }
+  p.norm_sq_accum = opt_ptr<float>(norm_sq_accum);
   if (bE.has_value()) {
     TORCH_CHECK(mbE.has_value() && vbE.has_value());
     CHECK_T(*bE, torch::kFloat32); CHECK_T(*mbE, torch::kFloat32); CHECK_T(*vbE, torch::kFloat32);

@@ -132,6 +132,9 @@ struct GradAdamParams {
   // Gradient that reaches a decoder row through its own norm (a sparsity penalty on a * ||W_D row||): the row's gradient
   // gets wd_self_scale[f] * W_D[f, :] added, with the row read in the same pass that updates it (nullptr: none).
   const float* wd_self_scale;
+  // Instead of writing dec_norm[f] = ||new W_D row||, add the squared norm to norm_sq_accum[f] (nullptr: off): a feature
+  // whose gate is the norm over SEVERAL decoder matrices collects it over one launch per matrix.
+  float* norm_sq_accum;
   const __nv_bfloat16* dxhat_aux;  // output gradient seen by the code slots >= k_main of every row (nullptr: none)
   int k_main;
   float* gD_out;  // optional dense [F, d] outputs of the rebuilt gradient rows (for autograd callers)

@@ -511,6 +511,9 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
   // this kernel would consume are stale, so the parameters and moments stay as they are until the host has seen the
   // status word.
   const bool skip = p.status != nullptr && *reinterpret_cast<const volatile int*>(p.status) != 0;
+  // One-sided launches: without WD only the encoder side (W_E^T, b_E) is rebuilt and updated, without WE only the decoder
+  // side. A cross-layer transcoder has several decoder matrices per encoder, so its sides are updated by separate launches.
+  const bool doD = p.WD != nullptr, doE = p.WE != nullptr;
 
   for (int f = p.f_begin + blockIdx.x; f < p.f_end && !skip; f += gridDim.x) {
     const int e0 = p.offsets[f], e1 = p.offsets[f + 1];
@@ -532,10 +535,14 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) gD[v][i] = gE[v][i] = 0.0f;
         if (xr >= 0 && in[v]) {
-          const float4 a = *reinterpret_cast<const float4*>(p.extra_gD + (size_t)xr * p.d + c[v]);
-          const float4 b = *reinterpret_cast<const float4*>(p.extra_gE + (size_t)xr * p.d + c[v]);
-          gD[v][0] = a.x; gD[v][1] = a.y; gD[v][2] = a.z; gD[v][3] = a.w;
-          gE[v][0] = b.x; gE[v][1] = b.y; gE[v][2] = b.z; gE[v][3] = b.w;
+          if (doD) {
+            const float4 a = *reinterpret_cast<const float4*>(p.extra_gD + (size_t)xr * p.d + c[v]);
+            gD[v][0] = a.x; gD[v][1] = a.y; gD[v][2] = a.z; gD[v][3] = a.w;
+          }
+          if (doE) {
+            const float4 b = *reinterpret_cast<const float4*>(p.extra_gE + (size_t)xr * p.d + c[v]);
+            gE[v][0] = b.x; gE[v][1] = b.y; gE[v][2] = b.z; gE[v][3] = b.w;
+          }
         }
       }
       for (int e = e0; e < e1; ++e) {
@@ -549,16 +556,20 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
 #pragma unroll
         for (int v = 0; v < VEC; ++v) {
           if (in[v]) {
-            const uint2 ux = __ldg(reinterpret_cast<const uint2*>(p.x + (size_t)row * p.d + c[v]));
-            const uint2 ud = __ldg(reinterpret_cast<const uint2*>(gmat + (size_t)row * p.d + c[v]));
-            const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ux.x));
-            const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ux.y));
-            const float2 d01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ud.x));
-            const float2 d23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ud.y));
-            gD[v][0] = fmaf(a, d01.x, gD[v][0]); gD[v][1] = fmaf(a, d01.y, gD[v][1]);
-            gD[v][2] = fmaf(a, d23.x, gD[v][2]); gD[v][3] = fmaf(a, d23.y, gD[v][3]);
-            gE[v][0] = fmaf(da, x01.x, gE[v][0]); gE[v][1] = fmaf(da, x01.y, gE[v][1]);
-            gE[v][2] = fmaf(da, x23.x, gE[v][2]); gE[v][3] = fmaf(da, x23.y, gE[v][3]);
+            if (doD) {
+              const uint2 ud = __ldg(reinterpret_cast<const uint2*>(gmat + (size_t)row * p.d + c[v]));
+              const float2 d01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ud.x));
+              const float2 d23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ud.y));
+              gD[v][0] = fmaf(a, d01.x, gD[v][0]); gD[v][1] = fmaf(a, d01.y, gD[v][1]);
+              gD[v][2] = fmaf(a, d23.x, gD[v][2]); gD[v][3] = fmaf(a, d23.y, gD[v][3]);
+            }
+            if (doE) {
+              const uint2 ux = __ldg(reinterpret_cast<const uint2*>(p.x + (size_t)row * p.d + c[v]));
+              const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ux.x));
+              const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ux.y));
+              gE[v][0] = fmaf(da, x01.x, gE[v][0]); gE[v][1] = fmaf(da, x01.y, gE[v][1]);
+              gE[v][2] = fmaf(da, x23.x, gE[v][2]); gE[v][3] = fmaf(da, x23.y, gE[v][3]);
+            }
           }
         }
       }
@@ -580,14 +591,14 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
 #pragma unroll
         for (int v = 0; v < VEC; ++v) {
           if (in[v]) {
-            w[v] = ldcs4(p.WD + o[v]); m[v] = ldcs4(p.mD + os[v]); vv[v] = ldcs4(p.vD + os[v]);
-            we[v] = ldcs4(p.WE + o[v]); me[v] = ldcs4(p.mE + os[v]); ve[v] = ldcs4(p.vE + os[v]);
+            if (doD) { w[v] = ldcs4(p.WD + o[v]); m[v] = ldcs4(p.mD + os[v]); vv[v] = ldcs4(p.vD + os[v]); }
+            if (doE) { we[v] = ldcs4(p.WE + o[v]); me[v] = ldcs4(p.mE + os[v]); ve[v] = ldcs4(p.vE + os[v]); }
           }
         }
 #pragma unroll
         for (int v = 0; v < VEC; ++v) {
           if (!in[v]) continue;
-          {
+          if (doD) {
             if (self_scale != 0.0f) {  // (not part of the squared-norm accumulation above: a penalty term's share is small)
               gD[v][0] = fmaf(self_scale, w[v].x, gD[v][0]); gD[v][1] = fmaf(self_scale, w[v].y, gD[v][1]);
               gD[v][2] = fmaf(self_scale, w[v].z, gD[v][2]); gD[v][3] = fmaf(self_scale, w[v].w, gD[v][3]);
@@ -604,7 +615,7 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
               *reinterpret_cast<uint2*>(p.WD_bf16 + o[v]) = sh;
             }
           }
-          {
+          if (doE) {
             adam_elem(we[v].x, me[v].x, ve[v].x, gE[v][0], p.h); adam_elem(we[v].y, me[v].y, ve[v].y, gE[v][1], p.h);
             adam_elem(we[v].z, me[v].z, ve[v].z, gE[v][2], p.h); adam_elem(we[v].w, me[v].w, ve[v].w, gE[v][3], p.h);
             stcs4(p.WE + o[v], we[v]); stcs4(p.mE + os[v], me[v]); stcs4(p.vE + os[v], ve[v]);
@@ -622,7 +633,7 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
     if (threadIdx.x == 0) {
       bias_g *= gmul;
       gsq_local += bias_g * bias_g;
-      if (p.update && p.bE != nullptr) {
+      if (p.update && p.bE != nullptr && doE) {
         float b = p.bE[f], m = p.mbE[f - p.state_f0], v = p.vbE[f - p.state_f0];
         adam_elem(b, m, v, bias_g, p.h);
         p.mbE[f - p.state_f0] = m; p.vbE[f - p.state_f0] = v;
@@ -633,7 +644,7 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
         }
       }
     }
-    if (p.update && p.dec_norm != nullptr) {
+    if (p.update && doD && (p.dec_norm != nullptr || p.norm_sq_accum != nullptr)) {
       norm_sq = warp_sum(norm_sq);
       __syncthreads();
       if (lane == 0) s_red[warp] = norm_sq;
@@ -642,7 +653,9 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
         float t = lane < GA_THREADS / 32 ? s_red[lane] : 0.0f;
         t = warp_sum(t);
         if (lane == 0) {
-          if (p.n_pub > 0) {
+          if (p.norm_sq_accum != nullptr) {
+            p.norm_sq_accum[f] += t;  // one CTA per row and launch: the squared norms of several matrices add up here
+          } else if (p.n_pub > 0) {
             for (int q = 0; q < p.n_pub; ++q) reinterpret_cast<float*>(p.pub.base[q] + p.pub_norm_off)[f] = sqrtf(t);
           } else {
             p.dec_norm[f] = sqrtf(t);

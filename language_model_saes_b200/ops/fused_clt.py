@@ -1,0 +1,216 @@
+"""One training step of a cross-layer transcoder with a per-layer TopK activation as a fixed sequence of sm_100a kernels,
+without autograd.
+
+What it computes is the reference's step for a ``CrossLayerTranscoder`` (models/clt.py:526-573 encode, :629-709 decode of
+every source layer into every later target layer, :836-876 per-feature decoder norms, MSE averaged over layers and
+tokens) with Adam. How it computes it:
+
+1. per source layer: encoder GEMM (tcgen05) with the fused top-k epilogue, gated by the feature's decoder norm over all its
+   target layers, and the merge of the candidate lists (+ one all-gather of the lists between feature shards)
+                                                                  -> codes (layer * F + feature, act) [B, L * k]
+2. decoder fan-out: ONE gather kernel adds every active feature's rows into all its target layers (``clt_decode``); the
+   dense [B, L, F] activations and the 78 per-pair products never exist. Feature shards sum their partial outputs with the
+   one-kernel in-place all-reduce over peer memory (``parallel.symm.AllReduceComm``: one reduce of [L, B, d] instead of
+   one collective per target layer)
+3. loss and d y in one kernel, d act in one kernel (``clt_dact``), counting sort of the codes by (layer, feature)
+4. updates: per TARGET layer t one launch of the sparse gradient + Adam kernel over ``W_D[t]`` seen as a
+   ``[(t + 1) F, d]`` matrix (decoder side only: gradient rows rebuilt from the by-feature lists and d y[t], Adam, bf16
+   shadow, squared row norms accumulated into the per-feature norm over target layers); per SOURCE layer one launch over
+   ``W_E[s]`` (encoder side only). No dense gradient tensor exists; the reference materialises one per decoder.
+
+Restrictions: ``topk`` activation with k <= 64, no sparsity loss, Adam, fp32 parameters with bf16 compute, feature
+(``model``) sharding only.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..parallel.mesh import mesh_dim_size, mesh_group, mesh_local_rank
+from . import clt_kernels as CK
+from . import sae_kernels as K
+
+
+class FusedCLTStep:
+    def __init__(self, clt, betas: tuple[float, float] = (0.9, 0.999), eps: float = 1e-8):
+        cfg = clt.cfg
+        self.clt = clt
+        self.betas, self.eps = betas, eps
+        self.tp = mesh_dim_size(clt.device_mesh, "model")
+        self.tp_rank = mesh_local_rank(clt.device_mesh, "model")
+        self.tp_group = mesh_group(clt.device_mesh, "model")
+        self.L, self.F, self.d = cfg.n_layers, clt.d_sae_local, cfg.d_model
+        self.use_gate = cfg.sparsity_include_decoder_norm
+        L, F, d = self.L, self.F, self.d
+        self.WE = clt.W_E.data.transpose(1, 2)  # [L, F, d] contiguous view of the parameter's storage
+        assert self.WE.is_contiguous() and self.WE.dtype == torch.float32
+        self.bE = clt.b_E.data
+        self.WD = [w.data.view((t + 1) * F, d) for t, w in enumerate(clt.W_D)]
+        dev = self.WE.device
+        # the decoder biases as rows of one matrix (one update launch): the parameters become views of it
+        self.bD = torch.stack([b.data for b in clt.b_D]).contiguous()
+        for t, b in enumerate(clt.b_D):
+            b.data = self.bD[t]
+        z = lambda *s: torch.zeros(*s, dtype=torch.float32, device=dev)  # noqa: E731
+        self.WE_bf16 = torch.empty(L, F, d, dtype=torch.bfloat16, device=dev)
+        self.WD_bf16 = [torch.empty(t + 1, F, d, dtype=torch.bfloat16, device=dev) for t in range(L)]
+        self.norm_sq = z(L * F)  # per (source layer, feature): squared decoder norm over all its target layers
+        self.state = {"W_E": (z(L, F, d), z(L, F, d)), "b_E": (z(L, F), z(L, F)), "b_D": (z(L, d), z(L, d)),
+                      "W_D": [(z((t + 1) * F, d), z((t + 1) * F, d)) for t in range(L)]}  # fmt: skip
+        self.groups: K.FeatureGroups | None = None
+        self.loss_sum = z(1)
+        self.comm = None
+        self.own_rows = (0, F)
+        self.t = 0
+        self.refresh()
+
+    @staticmethod
+    def supports(clt, trainer_cfg=None) -> tuple[bool, str]:
+        from ..models.clt import CrossLayerTranscoder
+
+        cfg = clt.cfg
+        if type(clt) is not CrossLayerTranscoder:
+            return False, "model is not a CrossLayerTranscoder"
+        checks = [
+            (cfg.act_fn == "topk", "activation is not the per-layer topk"),
+            (cfg.top_k <= 64, "k > 64"),
+            (clt.b_E.is_cuda or trainer_cfg is None, "not on a CUDA device"),
+            (cfg.dtype == torch.float32, "parameters are not fp32"),
+            (cfg.d_model % 8 == 0 and clt.d_sae_local % 8 == 0, "d_model / local d_sae not multiples of 8"),
+            (mesh_dim_size(clt.device_mesh, "data") == 1, "data parallelism"),
+            (not any(hp.fwd_hooks or hp.bwd_hooks for hp in clt.hook_points()), "hooks are attached"),
+        ]
+        if trainer_cfg is not None:
+            checks += [
+                (trainer_cfg.sparsity_loss_type is None, "sparsity loss"),
+                (trainer_cfg.optimizer_class == "adam", "optimizer is not adam"),
+                (trainer_cfg.amp_dtype == torch.bfloat16, "amp dtype is not bf16"),
+                (trainer_cfg.gradient_accumulation_steps == 1, "gradient accumulation"),
+                (not trainer_cfg.clip_grad_norm, "gradient clipping"),
+                (not trainer_cfg.initial_k or trainer_cfg.initial_k <= 64, "k schedule starting above 64"),
+            ]
+        for ok, why in checks:
+            if not ok:
+                return False, why
+        return True, ""
+
+    def refresh(self) -> None:
+        """Re-derive bf16 shadows and the per-feature decoder norms from the fp32 masters."""
+        self.norm_sq.zero_()
+        for t in range(self.L):
+            n = torch.empty((t + 1) * self.F, dtype=torch.float32, device=self.WE.device)
+            K.row_norm_shadow(self.WD[t], n, self.WD_bf16[t].view((t + 1) * self.F, self.d))
+            self.norm_sq[: (t + 1) * self.F] += n.square()
+        K.row_norm_shadow(self.WE.view(self.L * self.F, self.d), None, self.WE_bf16.view(self.L * self.F, self.d))
+
+    def join(self) -> None:
+        pass
+
+    def sync_params(self) -> None:
+        pass
+
+    def encode(self, x: torch.Tensor, k: int) -> tuple[torch.Tensor, torch.Tensor]:
+        """``x [B, L, d]`` bf16 -> codes ``(idx = layer * F + feature, act) [B, L * k]`` over this rank's features."""
+        B, L, F = x.shape[0], self.L, self.F
+        gate_all = self.norm_sq.sqrt().view(L, F) if self.use_gate else None
+        idxs, acts = [], []
+        for layer in range(L):
+            xl = x[:, layer].contiguous()
+            gate = gate_all[layer] if gate_all is not None else None
+            if self.tp == 1:
+                i, a = K.encoder_topk(xl, self.WE_bf16[layer], self.bE[layer], gate, k)
+            else:
+                if xl.is_cuda:
+                    cv, ci, _ = K.encoder_topk_candidates(xl, self.WE_bf16[layer], self.bE[layer], gate, k)
+                    i_l, g_l = K.topk_merge(cv, ci, k, gate, emit_gated=True)
+                else:
+                    i_l, a_l = K.encoder_topk(xl, self.WE_bf16[layer], self.bE[layer], gate, k)
+                    g_l = a_l * gate[i_l.clamp_min(0).long()] if gate is not None else a_l
+                all_g = torch.empty(self.tp * B, k, dtype=torch.float32, device=x.device)
+                all_i = torch.empty(self.tp * B, k, dtype=torch.int32, device=x.device)
+                dist.all_gather_into_tensor(all_g, g_l.float().contiguous(), group=self.tp_group)
+                dist.all_gather_into_tensor(all_i, i_l.contiguous(), group=self.tp_group)
+                all_g = all_g.view(self.tp, B, k).permute(1, 0, 2).reshape(B, self.tp * k).contiguous()
+                all_i = all_i.view(self.tp, B, k).permute(1, 0, 2).reshape(B, self.tp * k).contiguous()
+                i, a = K.topk_merge(all_g, all_i, k, gate, own=(self.tp_rank * k, (self.tp_rank + 1) * k))
+            idxs.append(torch.where(i >= 0, i + layer * F, i))
+            acts.append(a)
+        return torch.cat(idxs, dim=1).contiguous(), torch.cat(acts, dim=1).contiguous()
+
+    def _decode(self, idx: torch.Tensor, act: torch.Tensor) -> torch.Tensor:
+        """Reconstruction ``[L, B, d]`` fp32 (summed over feature shards, decoder biases added)."""
+        B, L, d = idx.shape[0], self.L, self.d
+        if self.tp == 1:
+            return CK.clt_decode(idx, act, self.WD_bf16, self.bD, torch.float32)
+        if not idx.is_cuda:
+            y = CK.clt_decode(idx, act, self.WD_bf16, None, torch.float32)
+            dist.all_reduce(y, group=self.tp_group)
+            return y + self.bD[:, None, :]
+        from ..parallel.symm import AllReduceComm
+
+        if self.comm is None or self.comm.max_rows < L * B:
+            self.comm = AllReduceComm(self.tp_group, idx.device, L * B, d)
+        part = self.comm.matrix(L * B).view(L, B, d)
+        K._ext().clt_decode(idx, act, list(self.WD_bf16), None, part)  # bf16 partial rows straight into the symmetric buffer
+        return self.comm.all_reduce(L * B).view(L, B, d).float() + self.bD[:, None, :]
+
+    def step(self, x: torch.Tensor, label: torch.Tensor, k: int, lr: float) -> torch.Tensor:
+        """``x [B, L, d]`` normalised bf16 inputs of the L source layers, ``label [L, B, d]`` bf16 targets. Returns the mean
+        loss (0-d device tensor)."""
+        B, L, F, d = x.shape[0], self.L, self.F, self.d
+        idx, act = self.encode(x, k)
+        y = self._decode(idx, act)
+        self.loss_sum.zero_()
+        dy = K.mse_loss_grad(y.view(L * B, d), label.reshape(L * B, d).contiguous(), None, None, 2.0 / (L * B), self.loss_sum)
+        dy = dy.view(L, B, d)
+        dact = CK.clt_dact(idx, self.WD_bf16, dy)
+        if self.groups is None or self.groups.entries.numel() < idx.numel():
+            self.groups = K.FeatureGroups(L * F, idx.numel(), x.device)
+        self.groups.build(idx)
+        off, ent = self.groups.offsets, self.groups.entries
+        self.t += 1
+        b1, b2 = self.betas
+        self.norm_sq.zero_()
+        g = K.FeatureGroups.__new__(K.FeatureGroups)
+        g.entries = ent
+        for t in range(L):  # decoder side, one launch per target layer
+            rows = (t + 1) * F
+            g.F, g.offsets = rows, off[: rows + 1]
+            mD, vD = self.state["W_D"][t]
+            K.sparse_grad_adam(g, act, dact, dy[t], dy[t], self.WD[t], mD, vD, self.WD_bf16[t].view(rows, d), None, None, None, None, None,
+                               None, None, None, None, None, lr, b1, b2, self.eps, self.t, True, norm_sq_accum=self.norm_sq[:rows])  # fmt: skip
+        (mE, vE), (mb, vb) = self.state["W_E"], self.state["b_E"]
+        for s in range(L):  # encoder side, one launch per source layer
+            g.F, g.offsets = F, off[s * F : (s + 1) * F + 1]
+            xs = x[:, s].contiguous()
+            K.sparse_grad_adam(g, act, dact, xs, xs, None, None, None, None, self.WE[s], mE[s], vE[s], self.WE_bf16[s], self.bE[s], mb[s],
+                               vb[s], None, None, None, lr, b1, b2, self.eps, self.t, True)  # fmt: skip
+        m, v = self.state["b_D"]
+        K.adam_flat(self.bD.view(-1), dy.float().sum(dim=1).reshape(-1), m.view(-1), v.view(-1), lr, b1, b2, self.eps, self.t)
+        return (self.loss_sum / (L * B)).squeeze(0)
+
+    def optimizer_state(self) -> dict:
+        out = {"step": self.t, "W_E": {"exp_avg": self.state["W_E"][0].transpose(1, 2), "exp_avg_sq": self.state["W_E"][1].transpose(1, 2)},
+               "b_E": {"exp_avg": self.state["b_E"][0], "exp_avg_sq": self.state["b_E"][1]}}  # fmt: skip
+        for t in range(self.L):
+            m, v = self.state["W_D"][t]
+            out[f"W_D.{t}"] = {"exp_avg": m.view(t + 1, self.F, self.d), "exp_avg_sq": v.view(t + 1, self.F, self.d)}
+            out[f"b_D.{t}"] = {"exp_avg": self.state["b_D"][0][t], "exp_avg_sq": self.state["b_D"][1][t]}
+        return out
+
+    def load_optimizer_state(self, sd: dict) -> None:
+        self.t = int(sd["step"])
+        if "W_E" in sd:
+            self.state["W_E"][0].copy_(sd["W_E"]["exp_avg"].transpose(1, 2))
+            self.state["W_E"][1].copy_(sd["W_E"]["exp_avg_sq"].transpose(1, 2))
+        if "b_E" in sd:
+            self.state["b_E"][0].copy_(sd["b_E"]["exp_avg"])
+            self.state["b_E"][1].copy_(sd["b_E"]["exp_avg_sq"])
+        for t in range(self.L):
+            if f"W_D.{t}" in sd:
+                self.state["W_D"][t][0].copy_(sd[f"W_D.{t}"]["exp_avg"].reshape((t + 1) * self.F, self.d))
+                self.state["W_D"][t][1].copy_(sd[f"W_D.{t}"]["exp_avg_sq"].reshape((t + 1) * self.F, self.d))
+            if f"b_D.{t}" in sd:
+                self.state["b_D"][0][t].copy_(sd[f"b_D.{t}"]["exp_avg"])
+                self.state["b_D"][1][t].copy_(sd[f"b_D.{t}"]["exp_avg_sq"])

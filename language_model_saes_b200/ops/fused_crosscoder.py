@@ -155,12 +155,17 @@ class FusedCrosscoderStep:
         idx, s_val = S.column_threshold_rows_to_sparse(S_sum, t_min, cap, overflow=self.list_overflow)
         safe = idx.clamp_min(0).long()
         valid = idx >= 0
+        # scatter target of the per-feature sums below: empty slots go to a dump element of their own row (sending them all
+        # to one element would serialise a million atomic additions on it)
+        dump = F + (torch.arange(B, device=x.device) % 1024).unsqueeze(1)
+        scat = torch.where(valid, safe, dump.expand_as(safe)).reshape(-1)
         if self.groups is None or self.groups.entries.numel() < idx.numel():
             self.groups = K.FeatureGroups(F, idx.numel(), x.device)
         self.groups.build(idx)
         self.loss_sum.zero_()
         dS = torch.zeros(B, cap, dtype=torch.float32, device=x.device)
-        dtheta = torch.zeros(F, dtype=torch.float32, device=x.device)
+        dtheta_buf = torch.zeros(F + 1024, dtype=torch.float32, device=x.device)
+        dtheta = dtheta_buf[:F]
         l_s_sum = torch.zeros((), dtype=torch.float32, device=x.device)
         per_head = []
         c = float(tanh_stretch)
@@ -180,9 +185,9 @@ class FusedCrosscoderStep:
                 coef = l1_coefficient * c / (B * H)
                 dact = dact + coef * n_e * sech2 * active
                 # the penalty also pulls on the decoder norm: d / d W_D[f] = (sum_b coef * act * sech^2) * W_D[f] / ||W_D[f]||
-                per_feat = torch.zeros(F, dtype=torch.float32, device=x.device)
-                per_feat.index_add_(0, safe.reshape(-1), (coef * act * sech2 * active).reshape(-1))
-                self_scale = per_feat / n_h
+                per_feat = torch.zeros(F + 1024, dtype=torch.float32, device=x.device)
+                per_feat.index_add_(0, scat, (coef * act * sech2 * active).reshape(-1))
+                self_scale = per_feat[:F] / n_h
             dS_h = dact * active
             dS += dS_h
             # threshold gradient: dense part (reconstruction gradient at every entry inside the window) ...
@@ -194,7 +199,7 @@ class FusedCrosscoderStep:
                 x_e = s_val * n_e
                 hit = active & ((x_e - theta[safe]).abs() < 0.5 * self.window)
                 contrib = coef * (sech2 - 1.0) * (-theta[safe] / self.window) * hit
-                dtheta.index_add_(0, safe.reshape(-1), contrib.reshape(-1))
+                dtheta_buf.index_add_(0, scat, contrib.reshape(-1))
             per_head.append((xh, act, dxhat, self_scale))
         if self.head_size > 1:  # the lists are the same on every rank: the sum over heads is element-wise
             dist.all_reduce(dS, group=self.head_group)

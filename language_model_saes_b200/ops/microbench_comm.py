@@ -5,7 +5,9 @@
 
 Cases: ``shuffle`` (seeded row all-to-all of the activation buffer, ``ShuffleComm`` vs ``all_to_all_single`` after a
 local gather), ``bcast`` (masked + cast row broadcast of cached activations, ``BroadcastComm`` vs boolean index + cast +
-``broadcast``), ``headsum`` (crosscoder pre-activation sum inside the GEMM, ``HeadSumComm`` vs ``einsum`` + ``all_reduce``),
+``broadcast``), ``headsum`` (crosscoder pre-activation sum inside the GEMM, ``HeadSumComm`` vs ``einsum`` + ``all_reduce``), ``allreduce``
+(in-place sum of a bf16 [4096, 98304] matrix in one kernel, ``AllReduceComm`` with and without the NVSwitch multicast
+mapping, vs ``all_reduce``),
 ``rows`` (the five tensors of a data-parallel step in one kernel, ``DataParallelComm.exchange`` vs five
 ``all_gather_into_tensor`` calls).
 
@@ -50,7 +52,7 @@ def _time(fn, iters: int, warmup: int, min_seconds: float) -> float:
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default="all", help="all | shuffle | bcast | headsum | rows")
+    ap.add_argument("--case", default="all", help="all | shuffle | bcast | headsum | allreduce | rows")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--min-seconds", type=float, default=0.5)
@@ -137,6 +139,21 @@ def main(argv=None):
             nccl_path, link_bytes=M * N * 4 * (world - 1) / world + M * N * 2 * (world - 1) / world,
             tflops_ours_per_rank=None)  # fmt: skip
         del comm, x, w
+
+    if want("allreduce"):
+        M, N = 4096, 98304  # the crosscoder's summed pre-activations
+        mine = torch.randn(M, N, device=dev).to(torch.bfloat16)
+        ref_buf = mine.clone()
+        for use_mc in (True, False):
+            comm = symm.AllReduceComm(group, dev, M, N, use_multicast=use_mc)
+            if use_mc and not comm.use_multicast:
+                continue
+            comm.matrix(M).copy_(mine)
+            # (the kernel sums in place: repeated calls keep summing the same buffer, values are irrelevant for the timing)
+            run(f"all_reduce_bf16_4096x98304_one_kernel_{'multimem' if comm.use_multicast else 'peer_loads_stores'}",
+                lambda: comm.all_reduce(M), lambda: dist.all_reduce(ref_buf), link_bytes=M * N * 2 * (world - 1) / world)
+            del comm
+        del mine, ref_buf
 
     if want("rows"):
         B, d, k = 4096, 4096, 64  # rows of one replica: x, d x_hat (bf16) and the three code tensors

@@ -505,6 +505,7 @@ def sparse_grad_adam(
     publish: tuple[list[int], list[int], int, torch.Tensor] | None = None,
     extra: tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor | None] | None = None,
     wd_self_scale: torch.Tensor | None = None,
+    norm_sq_accum: torch.Tensor | None = None,
 ):
     """Rebuild the two sparse gradient rows per feature and apply Adam in the same pass (in place). ``f_range``
     restricts the launch to feature rows ``[begin, end)``. With ``dxhat_aux`` the code slots ``>= k_main`` of every row
@@ -514,8 +515,28 @@ def sparse_grad_adam(
     gD fp32 [R, d], gE fp32 [R, d], gb fp32 [R] | None)``: dense gradient rows that are added for the features with
     ``row_of_feature >= 0`` (e.g. the auxiliary loss over a compact dictionary of dead features). ``wd_self_scale`` fp32
     ``[F]``: the decoder row's gradient gets ``wd_self_scale[f] * W_D[f, :]`` added (the gradient that a penalty on the
-    row's norm sends into the row). A non-zero kernel status word turns the update into a no-op (CUDA path)."""
-    if not WD.is_cuda:
+    row's norm sends into the row). One-sided launches: pass ``WD = mD = vD = WD_bf16 = None`` to update the encoder side
+    only, or the ``WE`` group as None for the decoder side only. ``norm_sq_accum`` fp32 ``[F]``: the squared norm of every
+    new decoder row is ADDED there instead of writing ``dec_norm``. A non-zero kernel status word turns the update into
+    a no-op (CUDA path)."""
+    ref_w = WD if WD is not None else WE
+    if not ref_w.is_cuda:
+        if WD is None or WE is None:  # one-sided: run the two-sided statement on a scratch copy of the missing side
+            zero = lambda: torch.zeros_like(ref_w)  # noqa: E731
+            if WD is None:
+                sparse_grad_adam(groups, act, dact, x, dxhat, zero(), zero(), zero(), torch.zeros_like(WE_bf16), WE, mE, vE, WE_bf16, bE, mbE,
+                                 vbE, None, grad_mul, None, lr, beta1, beta2, eps, step, update, f_range, 0, dxhat_aux, k_main,
+                                 state_f0=state_f0, extra=extra)  # fmt: skip
+            else:
+                norms = torch.zeros(ref_w.shape[0]) if (dec_norm is not None or norm_sq_accum is not None) else None
+                sparse_grad_adam(groups, act, dact, x, dxhat, WD, mD, vD, WD_bf16, zero(), zero(), zero(), torch.zeros_like(WD_bf16), None,
+                                 None, None, norms, grad_mul, None, lr, beta1, beta2, eps, step, update, f_range, 0, dxhat_aux,
+                                 k_main, state_f0=state_f0, extra=extra, wd_self_scale=wd_self_scale)  # fmt: skip
+                if norm_sq_accum is not None and update:
+                    norm_sq_accum += norms.square()
+                elif dec_norm is not None and update:
+                    dec_norm.copy_(norms)
+            return
         if f_range is not None and tuple(f_range) != (0, groups.F):
             lo, hi = f_range
             sub = FeatureGroups.__new__(FeatureGroups)
@@ -569,8 +590,8 @@ def sparse_grad_adam(
     _ext().sparse_grad_adam(
         groups.offsets, groups.entries, act, dact, x, dxhat, WD, mD, vD, WD_bf16, WE, mE, vE, WE_bf16, bE, mbE, vbE,
         dec_norm, grad_mul, grad_sq_sum, lr, beta1, beta2, eps, step, update, *(f_range if f_range is not None else (0, -1)), ctas_per_sm, dxhat_aux, k_main, grad_out[0], grad_out[1],
-        status_buffer(WD.device), state_f0, *(publish if publish is not None else ([], [], 0, None)),
-        *(extra if extra is not None else (None, None, None, None)), wd_self_scale,
+        status_buffer(ref_w.device), state_f0, *(publish if publish is not None else ([], [], 0, None)),
+        *(extra if extra is not None else (None, None, None, None)), wd_self_scale, norm_sq_accum,
     )  # fmt: skip
 
 

@@ -497,12 +497,19 @@ class Trainer:
         else:
             from .ops.fused_crosscoder import FusedCrosscoderStep
 
+            from .ops.fused_clt import FusedCLTStep
+
             ok_cc, why_cc = (False, "disabled") if not self.cfg.use_fused_kernels else FusedCrosscoderStep.supports(sae, self.cfg)
+            ok_clt, why_clt = (False, "disabled") if not self.cfg.use_fused_kernels else FusedCLTStep.supports(sae, self.cfg)
             if ok_cc:
                 self.fused = FusedCrosscoderStep(sae, betas=self.cfg.betas, jumprelu_lr_factor=self.cfg.jumprelu_lr_factor)
                 logger.info("Training the crosscoder on the fused sm_100a kernel path")
+            elif ok_clt:
+                self.fused = FusedCLTStep(sae, betas=self.cfg.betas)
+                logger.info("Training the cross-layer transcoder on the fused sm_100a kernel path")
             else:
-                logger.info(f"Training on the generic autograd path ({why if type(sae).__name__ != 'Crosscoder' else why_cc})")
+                reason = {"Crosscoder": why_cc, "CrossLayerTranscoder": why_clt}.get(type(sae).__name__, why)
+                logger.info(f"Training on the generic autograd path ({reason})")
         groups = []
         for g in sae.get_parameters():
             if not g["params"]:
@@ -991,10 +998,42 @@ class Trainer:
             self._emit(sae, out)
         return loss
 
+    def _normalised_bf16(self, sae: SparseDictionary, raw: Tensor, hook_point: str) -> Tensor:
+        """One hook point's activations scaled to the model's norm convention, in bf16, without a device scalar."""
+        if sae.cfg.norm_activation == "dataset-wise":
+            factor = math.sqrt(sae.cfg.d_model) / float(sae.dataset_average_activation_norm[hook_point])
+            raw = raw if factor == 1.0 else raw * factor
+        elif sae.cfg.norm_activation != "inference":
+            raw = raw * sae.compute_norm_factor(raw, hook_point)
+        return raw.to(torch.bfloat16)
+
+    def _fused_clt_iteration(self, sae: SparseDictionary, batch: dict[str, Tensor]) -> Tensor:
+        """One step of ``ops.fused_clt.FusedCLTStep``: inputs ``[tokens, layers, d]``, targets ``[layers, tokens, d]``."""
+        f = self.fused
+        mask = batch.get("mask")
+        if mask is not None and not batch.get("_mask_all", None if mask.device.type == "cpu" else bool(mask.all())):
+            raise NotImplementedError("the fused cross-layer transcoder path trains on unmasked tokens; set use_fused_kernels=False")
+        d = sae.cfg.d_model
+        x = torch.stack([self._normalised_bf16(sae, batch[hp], hp).reshape(-1, d) for hp in sae.cfg.hook_points_in], dim=1)
+        y = torch.stack([self._normalised_bf16(sae, batch[hp], hp).reshape(-1, d) for hp in sae.cfg.hook_points_out], dim=0)
+        k = self._current_k(sae)
+        if k is not None:
+            sae.set_current_k(k)
+        lr = float(self.cfg.lr) * (self._lr_lambda(self.cur_step) if self._lr_lambda is not None else 1.0)
+        loss = f.step(x, y, sae.current_k, lr)
+        if not self.cfg.skip_metrics_calculation and (self.cur_step + 1) % self.cfg.log_frequency == 0:
+            out = {"losses/overall_loss": float(loss), "losses/mse_loss": float(loss)}
+            out.update(self._details({}, lr))
+            out.update(sae.log_statistics())
+            self._emit(sae, out)
+        return loss
+
     def _fused_iteration(self, sae: SparseDictionary, batch: dict[str, Tensor]) -> Tensor:
         f = self.fused
         if type(f).__name__ == "FusedCrosscoderStep":
             return self._fused_crosscoder_iteration(sae, batch)
+        if type(f).__name__ == "FusedCLTStep":
+            return self._fused_clt_iteration(sae, batch)
         hin, hout = sae.cfg.hook_point_in, sae.cfg.hook_point_out
         x_raw = batch[hin]
         assert x_raw.ndim == 2, "the fused path trains on [tokens, d_model] activations"
