@@ -484,7 +484,10 @@ def run_config4(args, bench) -> None:
                     if impl == "reference":
                         out = {k: v.float() for k, v in out.items()}
                     out["tokens"] = tokens_d if (on_device or impl == "reference") else tokens_h
-                    out["mask"] = mask_d if (on_device or impl == "reference") else mask_h
+                    # (the reference's trainer wants a mask in the batch that sizes its schedule, and its crosscoder loss
+                    # rejects a per-token mask afterwards: it gets the all-true mask in that first batch only)
+                    if impl == "ours" or i == 0:
+                        out["mask"] = mask_d if (on_device or impl == "reference") else mask_h
                     yield out
 
             return gen()

@@ -279,26 +279,42 @@ allreduce_bf16_inplace_kernel(const PeerTable pt, long long off, long long n16, 
   if (ok) {
     const long long per = (n16 + pt.world - 1) / pt.world;
     const long long lo = per * pt.rank, hi = lo + per < n16 ? lo + per : n16;
-    for (long long v = lo + blockIdx.x * 512LL + threadIdx.x; v < hi; v += (long long)gridDim.x * 512) {
+    constexpr int U = 4;  // vectors per thread and round: their loads are all in flight before the first store
+    const long long stride = (long long)gridDim.x * 512;
+    for (long long v0 = lo + blockIdx.x * 512LL + threadIdx.x; v0 < hi; v0 += stride * U) {
       if constexpr (MC) {
-        char* a = pt.mc_base + off + v * 16;
-        multimem_st_16B(a, multimem_ld_reduce_add_bf16x8(a));
+        uint4 r[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long v = v0 + u * stride;
+          if (v < hi) r[u] = multimem_ld_reduce_add_bf16x8(pt.mc_base + off + v * 16);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long v = v0 + u * stride;
+          if (v < hi) multimem_st_16B(pt.mc_base + off + v * 16, r[u]);
+        }
       } else {
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        uint4 raw[kMaxPeers];
 #pragma unroll
-        for (int s = 0; s < kMaxPeers; ++s)
-          if (s < pt.world) raw[s] = *(reinterpret_cast<const uint4*>(pt.base[s] + off) + v);
+        for (int u = 0; u < U; ++u) {
+          const long long v = v0 + u * stride;
+          if (v >= hi) break;
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          uint4 raw[kMaxPeers];
 #pragma unroll
-        for (int s = 0; s < kMaxPeers; ++s)
-          if (s < pt.world) {
-            float t[8];
-            bf16x8_to_float_c(raw[s], t);
+          for (int s = 0; s < kMaxPeers; ++s)
+            if (s < pt.world) raw[s] = *(reinterpret_cast<const uint4*>(pt.base[s] + off) + v);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) acc[i] += t[i];
-          }
-        const uint4 o = float8_to_bf16x8(acc);
-        for (int s = 0; s < pt.world; ++s) *(reinterpret_cast<uint4*>(pt.base[s] + off) + v) = o;
+          for (int s = 0; s < kMaxPeers; ++s)
+            if (s < pt.world) {
+              float t[8];
+              bf16x8_to_float_c(raw[s], t);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) acc[i] += t[i];
+            }
+          const uint4 o = float8_to_bf16x8(acc);
+          for (int s = 0; s < pt.world; ++s) *(reinterpret_cast<uint4*>(pt.base[s] + off) + v) = o;
+        }
       }
     }
   }

@@ -115,25 +115,35 @@ class FusedCLTStep:
         B, L, F = x.shape[0], self.L, self.F
         gate_all = self.norm_sq.sqrt().view(L, F) if self.use_gate else None
         idxs, acts = [], []
+        if self.tp == 1:
+            for layer in range(L):
+                gate = gate_all[layer] if gate_all is not None else None
+                i, a = K.encoder_topk(x[:, layer].contiguous(), self.WE_bf16[layer], self.bE[layer], gate, k)
+                idxs.append(torch.where(i >= 0, i + layer * F, i))
+                acts.append(a)
+            return torch.cat(idxs, dim=1).contiguous(), torch.cat(acts, dim=1).contiguous()
+        # feature shards: every layer's local top-k list first, then ONE all-gather of all layers' lists, then the merges
+        loc_g = torch.empty(L, B, k, dtype=torch.float32, device=x.device)
+        loc_i = torch.empty(L, B, k, dtype=torch.int32, device=x.device)
         for layer in range(L):
             xl = x[:, layer].contiguous()
             gate = gate_all[layer] if gate_all is not None else None
-            if self.tp == 1:
-                i, a = K.encoder_topk(xl, self.WE_bf16[layer], self.bE[layer], gate, k)
+            if xl.is_cuda:
+                cv, ci, _ = K.encoder_topk_candidates(xl, self.WE_bf16[layer], self.bE[layer], gate, k)
+                i_l, g_l = K.topk_merge(cv, ci, k, gate, emit_gated=True)
             else:
-                if xl.is_cuda:
-                    cv, ci, _ = K.encoder_topk_candidates(xl, self.WE_bf16[layer], self.bE[layer], gate, k)
-                    i_l, g_l = K.topk_merge(cv, ci, k, gate, emit_gated=True)
-                else:
-                    i_l, a_l = K.encoder_topk(xl, self.WE_bf16[layer], self.bE[layer], gate, k)
-                    g_l = a_l * gate[i_l.clamp_min(0).long()] if gate is not None else a_l
-                all_g = torch.empty(self.tp * B, k, dtype=torch.float32, device=x.device)
-                all_i = torch.empty(self.tp * B, k, dtype=torch.int32, device=x.device)
-                dist.all_gather_into_tensor(all_g, g_l.float().contiguous(), group=self.tp_group)
-                dist.all_gather_into_tensor(all_i, i_l.contiguous(), group=self.tp_group)
-                all_g = all_g.view(self.tp, B, k).permute(1, 0, 2).reshape(B, self.tp * k).contiguous()
-                all_i = all_i.view(self.tp, B, k).permute(1, 0, 2).reshape(B, self.tp * k).contiguous()
-                i, a = K.topk_merge(all_g, all_i, k, gate, own=(self.tp_rank * k, (self.tp_rank + 1) * k))
+                i_l, a_l = K.encoder_topk(xl, self.WE_bf16[layer], self.bE[layer], gate, k)
+                g_l = a_l * gate[i_l.clamp_min(0).long()] if gate is not None else a_l
+            loc_g[layer], loc_i[layer] = g_l, i_l
+        all_g = torch.empty(self.tp, L, B, k, dtype=torch.float32, device=x.device)
+        all_i = torch.empty(self.tp, L, B, k, dtype=torch.int32, device=x.device)
+        dist.all_gather_into_tensor(all_g.view(self.tp * L, B, k), loc_g, group=self.tp_group)
+        dist.all_gather_into_tensor(all_i.view(self.tp * L, B, k), loc_i, group=self.tp_group)
+        all_g = all_g.permute(1, 2, 0, 3).reshape(L, B, self.tp * k).contiguous()
+        all_i = all_i.permute(1, 2, 0, 3).reshape(L, B, self.tp * k).contiguous()
+        for layer in range(L):
+            gate = gate_all[layer] if gate_all is not None else None
+            i, a = K.topk_merge(all_g[layer], all_i[layer], k, gate, own=(self.tp_rank * k, (self.tp_rank + 1) * k))
             idxs.append(torch.where(i >= 0, i + layer * F, i))
             acts.append(a)
         return torch.cat(idxs, dim=1).contiguous(), torch.cat(acts, dim=1).contiguous()

@@ -62,3 +62,39 @@ def test_fused_clt_step_matches_autograd(dev, gate):
     # the engine's running per-feature norms agree with the model's definition
     want = fused_model.decoder_norm_per_feature().reshape(-1)
     assert torch.allclose(engine.norm_sq.sqrt(), want, rtol=1e-3, atol=1e-5)
+
+
+from language_model_saes_b200.testing import distributed_test  # noqa: E402
+
+
+@distributed_test(nproc_per_node=2, backend="gloo")
+def test_fused_clt_step_with_feature_shards_matches_one_process():
+    """Features split over two gloo ranks: per-layer top-k merged over the shards from one exchange of all layers' lists,
+    partial reconstructions summed over the shards; same losses and weights as the unsharded step."""
+    import torch.distributed as dist
+
+    from language_model_saes_b200.parallel.mesh import DimMap, build_mesh
+
+    L, d, F, k, B, lr, steps = 3, 64, 256, 8, 64, 1e-3, 3
+    full = _model("cpu", L, d, F, k, True)
+    mesh = build_mesh("cpu", (1, 2), ("data", "model"))
+    single = copy.deepcopy(full)
+    sharded = CrossLayerTranscoder(full.cfg.model_copy(), mesh)
+    sharded.load_full_state_dict(full.full_state_dict())
+    e1, e2 = FusedCLTStep(single), FusedCLTStep(sharded)
+    g = torch.Generator().manual_seed(1)
+    for _ in range(steps):
+        x = torch.randn(B, L, d, generator=g).to(torch.bfloat16)
+        y = torch.randn(L, B, d, generator=g).to(torch.bfloat16)
+        a, b = e1.step(x, y, k, lr), e2.step(x, y, k, lr)
+        assert torch.allclose(a, b, rtol=1e-4), (a, b)
+    # The partial reconstructions add up in another order than in one process; where that flips a bf16 rounding of the output
+    # gradient, Adam's first steps (which normalise away the gradient's size) move a few weights by up to lr per step.
+    def close(a, b):
+        diff = (a - b).abs()
+        return float(diff.mean()) < 2e-6 and float(diff.max()) <= 2.2 * lr * steps
+
+    for t in range(L):
+        assert close(DimMap({"model": 1}).gather(sharded.W_D[t].data, mesh), single.W_D[t].data), t
+    assert close(DimMap({"model": 2}).gather(sharded.W_E.data, mesh), single.W_E.data)
+    dist.barrier()
