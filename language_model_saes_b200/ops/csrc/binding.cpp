@@ -219,6 +219,7 @@ void sparse_decode(const Tensor& idx, const Tensor& val, const Tensor& W, const 
   p.B = (int)idx.size(0);
   p.k = (int)idx.size(1);
   p.d = (int)W.size(1);
+  p.F = (int)W.size(0);
   p.W = reinterpret_cast<const __nv_bfloat16*>(W.data_ptr());
   if (bias.has_value()) { CHECK_T(*bias, torch::kFloat32); TORCH_CHECK(bias->numel() == p.d); }
   p.bias = opt_ptr<const float>(bias);
@@ -263,7 +264,7 @@ void sparse_dact(const Tensor& idx, const Tensor& W, const Tensor& dxhat, const 
     TORCH_CHECK(status.has_value());
     CHECK_T(*status, torch::kInt32);
   }
-  check_cuda(lmsae::sparse_dact_launch(idx.data_ptr<int>(), (int)idx.size(0), (int)idx.size(1), (int)W.size(1),
+  check_cuda(lmsae::sparse_dact_launch(idx.data_ptr<int>(), (int)idx.size(0), (int)idx.size(1), (int)W.size(1), (int)W.size(0),
                                        reinterpret_cast<const __nv_bfloat16*>(W.data_ptr()),
                                        reinterpret_cast<const __nv_bfloat16*>(dxhat.data_ptr()),
                                        dval.data_ptr<float>(), table.empty() ? nullptr : &pt, (uint32_t)epoch,
@@ -381,6 +382,8 @@ void sparse_grad_adam(const Tensor& offsets, const Tensor& entries, const Tensor
   p.F = (int)WD.size(0);
   p.d = (int)WD.size(1);
   p.k = (int)act.size(1);
+  p.n_rows = (int)x.size(0);
+  p.n_codes = act.numel();
   TORCH_CHECK(offsets.numel() >= p.F + 1 && x.size(1) == p.d && dxhat.sizes() == x.sizes());
   p.f_begin = (int)f_begin;
   p.f_end = f_end < 0 ? p.F : (int)f_end;
@@ -974,7 +977,7 @@ void comm_decode_scatter(const std::vector<int64_t>& table, const Tensor& idx, c
   TORCH_CHECK(idx.dim() == 2 && val.sizes() == idx.sizes() && W.dim() == 2);
   const c10::cuda::CUDAGuard guard(idx.device());
   check_cuda(lmsae::sparse_decode_scatter_launch(make_peer_table(table), idx.data_ptr<int>(), val.data_ptr<float>(),
-                                                 (int)idx.size(0), (int)idx.size(1), (int)W.size(1),
+                                                 (int)idx.size(0), (int)idx.size(1), (int)W.size(1), (int)W.size(0),
                                                  reinterpret_cast<const __nv_bfloat16*>(W.data_ptr()), (int)partial_dtype,
                                                  use_multicast ? 1 : 0, compact_codes ? 1 : 0, (uint32_t)epoch,
                                                  reinterpret_cast<unsigned*>(done_counter.data_ptr<int>()),
@@ -1032,9 +1035,31 @@ void comm_exchange_rows(const std::vector<int64_t>& table, const std::vector<Ten
              "exchange_rows launch");
 }
 
+// Records of the bounds-checked debug build: {translation unit: [source line, offending index, limit, number of
+// violations]} since the last call (all zero in the regular build); reading clears them.
+std::map<std::string, std::vector<int64_t>> bounds_report() {
+  std::map<std::string, std::vector<int64_t>> out;
+  int rec[4];
+  check_cuda(lmsae::bounds_fetch_sparse_ops(rec), "bounds_fetch_sparse_ops");
+  out["sparse_ops.cu"] = {rec[0], rec[1], rec[2], rec[3]};
+  check_cuda(lmsae::bounds_fetch_comm_ops(rec), "bounds_fetch_comm_ops");
+  out["comm_ops.cu"] = {rec[0], rec[1], rec[2], rec[3]};
+  return out;
+}
+
+bool bounds_checked_build() {
+#ifdef LMSAE_BOUNDS_CHECK
+  return true;
+#else
+  return false;
+#endif
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("bounds_report", &bounds_report);
+  m.def("bounds_checked_build", &bounds_checked_build);
   m.def("comm_push_candidates", &comm_push_candidates);
   m.def("comm_exchange_rows", &comm_exchange_rows);
   m.def("comm_wait", &comm_wait);

@@ -21,6 +21,8 @@
 
 namespace lmsae {
 
+LMSAE_DEFINE_BOUNDS_FETCH(bounds_fetch_comm_ops)
+
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 push_candidates_kernel(const PeerTable pt, const float* __restrict__ val, const int* __restrict__ idx, int B, int k,
@@ -61,7 +63,7 @@ constexpr int SC_UNROLL = 4;
 template <typename PT, bool LOCAL>
 __global__ void __launch_bounds__(SC_THREADS)
 sparse_decode_scatter_kernel(const PeerTable pt, const int* __restrict__ idx, const float* __restrict__ val, int B, int k,
-                             int d, const __nv_bfloat16* __restrict__ W, int compact, uint32_t epoch,
+                             int d, int F, const __nv_bfloat16* __restrict__ W, int compact, uint32_t epoch,
                              unsigned* done_counter) {
   const int nvec = d / 8;
   const int rows_per_rank = B / pt.world;
@@ -88,7 +90,7 @@ sparse_decode_scatter_kernel(const PeerTable pt, const int* __restrict__ idx, co
       uint4 w[SC_UNROLL][SC_MAX_VEC];
 #pragma unroll
       for (int t = 0; t < SC_UNROLL; ++t) {
-        const uint4* wrow = reinterpret_cast<const uint4*>(W + (size_t)(f[t] < 0 ? 0 : f[t]) * d);
+        const uint4* wrow = reinterpret_cast<const uint4*>(W + (size_t)(f[t] < 0 ? 0 : LMSAE_IDX(f[t], F)) * d);
 #pragma unroll
         for (int u = 0; u < SC_MAX_VEC; ++u) {
           const int v = threadIdx.x + u * SC_THREADS;
@@ -527,7 +529,7 @@ int wait_flags_launch(const PeerTable& pt, int phase, uint32_t epoch, int* statu
   return (int)cudaGetLastError();
 }
 
-int sparse_decode_scatter_launch(const PeerTable& pt, const int* idx, const float* val, int B, int k, int d,
+int sparse_decode_scatter_launch(const PeerTable& pt, const int* idx, const float* val, int B, int k, int d, int F,
                                  const __nv_bfloat16* W, int partial_dtype, int use_multicast, int compact_codes,
                                  uint32_t epoch, unsigned* done_counter, cudaStream_t stream) {
   if (d % 8 != 0 || d > SC_THREADS * SC_MAX_VEC * 8 || B % pt.world != 0) return (int)cudaErrorInvalidValue;
@@ -535,7 +537,7 @@ int sparse_decode_scatter_launch(const PeerTable& pt, const int* idx, const floa
   int blocks = B < 148 * 4 ? B : 148 * 4;
   using bf = __nv_bfloat16;
 #define LMSAE_SCATTER(PT, LOCAL) \
-  sparse_decode_scatter_kernel<PT, LOCAL><<<blocks, SC_THREADS, 0, stream>>>(pt, idx, val, B, k, d, W, compact_codes, epoch, done_counter)
+  sparse_decode_scatter_kernel<PT, LOCAL><<<blocks, SC_THREADS, 0, stream>>>(pt, idx, val, B, k, d, F, W, compact_codes, epoch, done_counter)
   if (use_multicast) LMSAE_SCATTER(bf, true);
   else if (partial_dtype == 1) LMSAE_SCATTER(bf, false);
   else LMSAE_SCATTER(float, false);

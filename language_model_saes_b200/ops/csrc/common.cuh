@@ -36,6 +36,41 @@ __device__ __forceinline__ void report_status(int* status, int code, int detail,
   }
 }
 
+// ---- bounds-checked debug build ---------------------------------------------------------------
+// Compiled with -DLMSAE_BOUNDS_CHECK (ops/native.py: build(debug=True), loaded with LMSAE_NATIVE_CHECKED=1), every
+// data-dependent index that goes through LMSAE_IDX(index, limit) is compared with its limit first. A violation is
+// RECORDED (source line, offending index, limit, number of violations; one record per translation unit, read back by
+// the extension's bounds_report()) and the index is clamped into range, so the access that follows is legal: nothing
+// traps and the context stays usable. In the regular build the macro is the index itself.
+#ifdef LMSAE_BOUNDS_CHECK
+static __device__ int g_lmsae_bounds[4];
+__device__ __forceinline__ long long lmsae_checked_index(long long i, long long n, int line) {
+  if (i >= 0 && i < n) return i;
+  if (atomicAdd(&g_lmsae_bounds[3], 1) == 0) {
+    g_lmsae_bounds[0] = line;
+    g_lmsae_bounds[1] = (int)i;
+    g_lmsae_bounds[2] = (int)n;
+  }
+  return i < 0 ? 0 : (n > 0 ? n - 1 : 0);
+}
+#define LMSAE_IDX(i, n) lmsae_checked_index((long long)(i), (long long)(n), __LINE__)
+// Host accessor of this translation unit's record: out = {line, index, limit, count}; clears the record.
+#define LMSAE_DEFINE_BOUNDS_FETCH(name)                                              \
+  int name(int* out) {                                                               \
+    cudaError_t e = cudaMemcpyFromSymbol(out, g_lmsae_bounds, 4 * sizeof(int));      \
+    if (e != cudaSuccess) return (int)e;                                             \
+    const int zero[4] = {0, 0, 0, 0};                                                \
+    return (int)cudaMemcpyToSymbol(g_lmsae_bounds, zero, 4 * sizeof(int));           \
+  }
+#else
+#define LMSAE_IDX(i, n) (i)
+#define LMSAE_DEFINE_BOUNDS_FETCH(name) \
+  int name(int* out) {                  \
+    out[0] = out[1] = out[2] = out[3] = 0; \
+    return 0;                           \
+  }
+#endif
+
 // ---- small PTX wrappers ----------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

@@ -76,10 +76,15 @@ int topk_merge_launch(const float* cand_val, const int* cand_idx, int M, int C, 
 int row_topk_launch(const __nv_bfloat16* H, long long ldh, int M, int N, int k, const float* gate,
                     const uint8_t* alive, int* out_idx, float* out_val, cudaStream_t stream);
 
+// Records of the bounds-checked debug build, one per translation unit (all zero in the regular build).
+int bounds_fetch_sparse_ops(int* out);
+int bounds_fetch_comm_ops(int* out);
+
 struct DecodeParams {
   const int* idx;
   const float* val;
   int B, k, d;
+  int F;  // rows of W (the limit of the codes' feature indices; checked in the debug build)
   const __nv_bfloat16* W;
   const float* bias;
   float* xhat_f32;
@@ -94,7 +99,7 @@ struct DecodeParams {
 };
 int sparse_decode_launch(const DecodeParams& p, cudaStream_t stream);
 // `wait`: optional (pt.world > 0) bounded wait for the gradient rows of the fused step (phase kPhaseDxhat) at kernel entry
-int sparse_dact_launch(const int* idx, int B, int k, int d, const __nv_bfloat16* W, const __nv_bfloat16* dxhat,
+int sparse_dact_launch(const int* idx, int B, int k, int d, int F, const __nv_bfloat16* W, const __nv_bfloat16* dxhat,
                        float* dval, const PeerTable* wait, uint32_t epoch, int* status, cudaStream_t stream);
 int mse_loss_grad_launch(const float* xhat, const __nv_bfloat16* label, const float* bias, const float* row_weight,
                          int rows, int d, float grad_scale, __nv_bfloat16* dxhat, float* loss_sum, float* row_loss,
@@ -108,6 +113,8 @@ struct AdamHyper {
 };
 struct GradAdamParams {
   int F, d, k;
+  int n_rows;        // rows of x / dxhat and
+  long long n_codes; // elements of act / dact: limits of the entry lists' positions (checked in the debug build)
   const int* offsets;
   const int* entries;
   const float* act;
@@ -247,7 +254,7 @@ int wait_flags_launch(const PeerTable& pt, int phase, uint32_t epoch, int* statu
 // partial_dtype: 0 = fp32, 1 = bf16 partial rows. use_multicast: partial rows stay in the producer's own buffer ([B][d])
 // and the owner sums them with multimem.ld_reduce; the gradient rows are published with multimem.st (needs pt.mc_base,
 // bf16 partials).
-int sparse_decode_scatter_launch(const PeerTable& pt, const int* idx, const float* val, int B, int k, int d,
+int sparse_decode_scatter_launch(const PeerTable& pt, const int* idx, const float* val, int B, int k, int d, int F,
                                  const __nv_bfloat16* W, int partial_dtype, int use_multicast, int compact_codes,
                                  uint32_t epoch, unsigned* done_counter, cudaStream_t stream);
 int reduce_loss_push_launch(const PeerTable& pt, int B, int d, const __nv_bfloat16* label, const float* bias,

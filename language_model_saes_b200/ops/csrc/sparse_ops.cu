@@ -18,6 +18,8 @@
 
 namespace lmsae {
 
+LMSAE_DEFINE_BOUNDS_FETCH(bounds_fetch_sparse_ops)
+
 // ---------------------------------------------------------------------------------------------
 // decode (+ loss, + dact)
 // ---------------------------------------------------------------------------------------------
@@ -63,7 +65,7 @@ sparse_decode_kernel(const DecodeParams p) {
       const int f = s_idx[j];
       if (f < 0) continue;
       const float a = s_val[j];
-      const uint4* wrow = reinterpret_cast<const uint4*>(p.W + (size_t)f * p.d);
+      const uint4* wrow = reinterpret_cast<const uint4*>(p.W + (size_t)LMSAE_IDX(f, p.F) * p.d);
 #pragma unroll
       for (int u = 0; u < DEC_MAX_VEC; ++u) {
         const int v = threadIdx.x + u * DEC_THREADS;
@@ -145,7 +147,7 @@ sparse_decode_kernel(const DecodeParams p) {
           const int f = s_idx[j];
           float dot = 0.0f;
           if (f >= 0) {
-            const uint4* wrow = reinterpret_cast<const uint4*>(p.W + (size_t)f * p.d);
+            const uint4* wrow = reinterpret_cast<const uint4*>(p.W + (size_t)LMSAE_IDX(f, p.F) * p.d);
             for (int v = lane; v < nvec; v += 32) {
               float w[8];
               bf16x8_to_float(__ldg(wrow + v), w);
@@ -183,7 +185,7 @@ constexpr int DACT_THREADS = 256;
 // peer stores; the kernel then waits (bounded) for every owner's flag of `epoch` itself instead of relying on a
 // separate wait launch before it.
 __global__ void __launch_bounds__(DACT_THREADS)
-sparse_dact_kernel(const int* __restrict__ idx, int B, int k, int d, const __nv_bfloat16* __restrict__ W,
+sparse_dact_kernel(const int* __restrict__ idx, int B, int k, int d, int F, const __nv_bfloat16* __restrict__ W,
                    const __nv_bfloat16* dxhat /* may be peer-written: no read-only path */, float* __restrict__ dval, const PeerTable wait_pt,
                    uint32_t epoch, int* status) {
   extern __shared__ float s_dx[];  // [d]
@@ -209,7 +211,7 @@ sparse_dact_kernel(const int* __restrict__ idx, int B, int k, int d, const __nv_
       const int f = idx[(size_t)row * k + j];
       float dot = 0.0f;
       if (f >= 0) {
-        const uint4* wrow = reinterpret_cast<const uint4*>(W + (size_t)f * d);
+        const uint4* wrow = reinterpret_cast<const uint4*>(W + (size_t)LMSAE_IDX(f, F) * d);
 #pragma unroll 4
         for (int v = lane; v < nvec; v += 32) {
           float w[8];
@@ -225,7 +227,7 @@ sparse_dact_kernel(const int* __restrict__ idx, int B, int k, int d, const __nv_
   }
 }
 
-int sparse_dact_launch(const int* idx, int B, int k, int d, const __nv_bfloat16* W, const __nv_bfloat16* dxhat,
+int sparse_dact_launch(const int* idx, int B, int k, int d, int F, const __nv_bfloat16* W, const __nv_bfloat16* dxhat,
                        float* dval, const PeerTable* wait, uint32_t epoch, int* status, cudaStream_t stream) {
   if (d % 8 != 0 || (size_t)d * 4 > 160 * 1024) return (int)cudaErrorInvalidValue;
   cudaError_t e = cudaFuncSetAttribute(sparse_dact_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
@@ -233,7 +235,7 @@ int sparse_dact_launch(const int* idx, int B, int k, int d, const __nv_bfloat16*
   int blocks = B < 148 * 8 ? B : 148 * 8;
   PeerTable pt{};
   if (wait != nullptr) pt = *wait;
-  sparse_dact_kernel<<<blocks, DACT_THREADS, (size_t)d * 4, stream>>>(idx, B, k, d, W, dxhat, dval, pt, epoch, status);
+  sparse_dact_kernel<<<blocks, DACT_THREADS, (size_t)d * 4, stream>>>(idx, B, k, d, F, W, dxhat, dval, pt, epoch, status);
   return (int)cudaGetLastError();
 }
 
@@ -546,8 +548,8 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
         }
       }
       for (int e = e0; e < e1; ++e) {
-        const int ent = p.entries[e];
-        const int row = ent / p.k;
+        const int ent = (int)LMSAE_IDX(p.entries[e], p.n_codes);
+        const int row = (int)LMSAE_IDX(ent / p.k, p.n_rows);
         const float a = p.act[ent];
         const float da = p.dact[ent];
         // codes beyond the first k_main slots of a row (auxiliary codes) multiply the auxiliary output gradient

@@ -20,7 +20,11 @@ import torch
 
 _NAME = "_lmsae_native"
 _CSRC = Path(__file__).resolve().parent / "csrc"
-_BUILD_DIR = Path(__file__).resolve().parent / "_native_build"
+# LMSAE_NATIVE_CHECKED=1 selects the bounds-checked debug build (compiled with -DLMSAE_BOUNDS_CHECK into a directory of its
+# own): data-dependent indices of the gather kernels are compared with their limits, violations are recorded (see
+# ``bounds_report`` of the extension) and clamped instead of read out of bounds.
+_CHECKED = os.environ.get("LMSAE_NATIVE_CHECKED", "0") == "1"
+_BUILD_DIR = Path(__file__).resolve().parent / ("_native_build_checked" if _CHECKED else "_native_build")
 _SOURCES = ["binding.cpp", "encoder_gemm.cu", "topk_merge.cu", "sparse_ops.cu", "comm_ops.cu", "no_alloc.cu", "jumprelu.cu", "clt_ops.cu", "select_ops.cu", "attention.cu"]
 _CUDA_FLAGS = [
     "-gencode",
@@ -55,7 +59,7 @@ def _source_hash() -> str:
     for p in deps:
         h.update(p.name.encode())
         h.update(p.read_bytes())
-    h.update(" ".join(_CUDA_FLAGS).encode())
+    h.update(" ".join(_CUDA_FLAGS + (["-DLMSAE_BOUNDS_CHECK"] if _CHECKED else [])).encode())
     return h.hexdigest()
 
 
@@ -85,8 +89,8 @@ def build(verbose: bool = False, force: bool = False) -> Path:
     cpp_extension.load(
         name=_NAME,
         sources=sources(),
-        extra_cflags=["-O3", "-std=c++17"],
-        extra_cuda_cflags=_CUDA_FLAGS,
+        extra_cflags=["-O3", "-std=c++17"] + (["-DLMSAE_BOUNDS_CHECK"] if _CHECKED else []),
+        extra_cuda_cflags=_CUDA_FLAGS + (["-DLMSAE_BOUNDS_CHECK"] if _CHECKED else []),
         extra_ldflags=["-lcuda"],
         build_directory=str(_BUILD_DIR),
         with_cuda=True,

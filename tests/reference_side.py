@@ -25,7 +25,30 @@ def main(inp: str, out: str) -> None:
     torch.save(results, out)
 
 
+def run_training(job: dict) -> dict:
+    """A few steps of the reference's own ``Trainer.fit`` on the given batches (on the job's device); returns the
+    parameters afterwards."""
+    import tempfile
+
+    import llamascopium as L
+    import torch
+    from llamascopium.models.sparse_dictionary import SparseDictionary
+
+    kw = dict(job["config"])
+    kw["dtype"] = getattr(torch, kw["dtype"])
+    model = SparseDictionary.from_config(getattr(L, job["config_class"])(**kw))
+    model.load_state_dict({k: v.to(kw["device"]) for k, v in job["state"].items()}, strict=False)
+    model.set_dataset_average_activation_norm(job["norm"])
+    batches = [{k: v.to(kw["device"]) for k, v in b.items()} for b in job["batches"]]
+    with tempfile.TemporaryDirectory() as tmp:
+        tcfg = L.TrainerConfig(exp_result_path=tmp, **job["trainer"])
+        L.Trainer(tcfg).fit(model, iter([batches[0]] + batches))  # (the reference consumes one batch while sizing its schedule)
+    return {"state": {k: v.detach().cpu() for k, v in model.state_dict().items()}}
+
+
 def run_job(job: dict) -> dict:
+    if job.get("kind") == "train":
+        return run_training(job)
     import llamascopium as L
     import torch
     from llamascopium.models.sparse_dictionary import SparseDictionary

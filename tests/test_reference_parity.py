@@ -21,11 +21,13 @@ pytestmark = pytest.mark.skipif(not (REF / "llamascopium").is_dir(), reason="the
 D = 32
 
 
-def _run_reference(jobs: dict) -> dict:
+def _run_reference(jobs: dict, gpu: bool = False) -> dict:
     with tempfile.TemporaryDirectory() as tmp:
         inp, out = os.path.join(tmp, "in.pt"), os.path.join(tmp, "out.pt")
         torch.save(jobs, inp)
-        env = dict(os.environ, PYTHONPATH=os.pathsep.join([str(ROOT / "baseline" / "_stubs"), str(REF)]), CUDA_VISIBLE_DEVICES="")
+        env = dict(os.environ, PYTHONPATH=os.pathsep.join([str(ROOT / "baseline" / "_stubs"), str(REF)]))
+        if not gpu:
+            env["CUDA_VISIBLE_DEVICES"] = ""
         r = subprocess.run([sys.executable, str(Path(__file__).with_name("reference_side.py")), inp, out], env=env, cwd=tmp,
                            capture_output=True, text=True, timeout=1200)  # fmt: skip
         assert r.returncode == 0, r.stderr[-3000:]
@@ -139,3 +141,47 @@ def test_losses_codes_and_gradients_match_the_reference(name, reference_results)
     assert set(ours) == set(ref["grads"]), (sorted(ours), sorted(ref["grads"]))
     for n, g in ref["grads"].items():
         assert torch.allclose(ours[n], g, atol=atol, rtol=1e-3), (n, float((ours[n] - g).abs().max()))
+
+
+@pytest.mark.gpu
+def test_five_fused_steps_follow_five_steps_of_the_reference_trainer():
+    """The same TopK SAE, batches and hyper-parameters through the reference's ``Trainer.fit`` (its autograd path under bf16
+    autocast, torch Adam) and through this package's ``Trainer.fit`` on the fused kernel path: after five steps every
+    parameter has moved the same way (the difference is a small fraction of the movement itself)."""
+    from language_model_saes_b200.models.sae import SAEConfig, SparseAutoEncoder
+    from language_model_saes_b200.trainer import Trainer, TrainerConfig
+
+    d, F, k, B, steps = 64, 2048, 8, 512, 5
+    config = dict(hook_point_in="h", hook_point_out="h", d_model=d, expansion_factor=F / d, act_fn="topk", top_k=k, device="cuda", dtype="float32")
+    torch.manual_seed(0)
+    sae = SparseAutoEncoder(SAEConfig(**{**config, "dtype": torch.float32}))
+    sae.init_parameters(encoder_uniform_bound=0.1, decoder_uniform_bound=0.1)
+    sae.set_decoder_to_fixed_norm(1.0, True)
+    sae.init_encoder_with_decoder_transpose()
+    norm = {"h": float(d**0.5)}
+    sae.set_dataset_average_activation_norm(norm)
+    start = {k_: v.detach().cpu().clone().contiguous() for k_, v in sae.state_dict().items()}
+    g = torch.Generator().manual_seed(3)
+    basis = torch.randn(10, d, generator=g)
+    batches = []
+    for _ in range(steps):
+        x = torch.randn(B, 10, generator=g) @ basis + 0.1 * torch.randn(B, d, generator=g)
+        x = (x * (d**0.5 / x.norm(dim=-1).mean())).to(torch.bfloat16).float()  # bf16-exact values: both sides see the same numbers
+        batches.append({"h": x, "tokens": torch.zeros(B, dtype=torch.long), "mask": torch.ones(B, dtype=torch.bool)})
+    trainer_kw = dict(total_training_tokens=steps * B, lr=1e-3, lr_scheduler_name="constant", log_frequency=10**6, n_checkpoints=0,
+                      skip_metrics_calculation=True, k_warmup_steps=0, l1_coefficient=None)  # fmt: skip
+    ref = _run_reference({"train": {"kind": "train", "config_class": "SAEConfig", "config": config, "state": start, "norm": norm,
+                                    "batches": batches, "trainer": trainer_kw}}, gpu=True)["train"]  # fmt: skip
+    assert "error" not in ref, ref.get("error")
+    with tempfile.TemporaryDirectory() as tmp:
+        tr = Trainer(TrainerConfig(exp_result_path=tmp, lr_warm_up_steps=0, lr_cool_down_steps=0, **trainer_kw))
+        tr.fit(sae, iter([{k_: v.cuda() for k_, v in b.items()} for b in batches]))
+        assert tr.fused is not None
+    for name, after_ref in ref["state"].items():
+        if name not in start or not after_ref.is_floating_point():
+            continue
+        ours = sae.state_dict()[name].detach().cpu().float()
+        moved = (after_ref.float() - start[name].float()).abs().mean()
+        if float(moved) == 0.0:
+            continue
+        assert float((ours - after_ref.float()).abs().mean()) < 0.3 * float(moved), name
