@@ -103,9 +103,15 @@ def run_config3(args, bench) -> None:
                     top_k=c["top_k"], device=f"cuda:{local}", dtype=torch.float32)  # fmt: skip
     sae = SparseAutoEncoder(cfg, mesh)
     bound = 1.0 / D**0.5
-    sae.init_parameters(encoder_uniform_bound=bound, decoder_uniform_bound=bound)
-    sae.set_decoder_to_fixed_norm(1.0, force_exact=True)
-    sae.init_encoder_with_decoder_transpose()
+
+    def init():
+        """Both timed fits start from these parameters (same seed): a step's cost depends on the number of dead features."""
+        torch.manual_seed(0)
+        sae.init_parameters(encoder_uniform_bound=bound, decoder_uniform_bound=bound)
+        sae.set_decoder_to_fixed_norm(1.0, force_exact=True)
+        sae.init_encoder_with_decoder_transpose()
+
+    init()
     sae.set_dataset_average_activation_norm({hook: D**0.5})
     host = _batches(c, c["pool"], slice(dp_rank * B_l, (dp_rank + 1) * B_l))
     tokens = torch.zeros(B_l, dtype=torch.long).pin_memory()
@@ -163,6 +169,7 @@ def run_config3(args, bench) -> None:
     sharded_state = bool(fused and tr.fused.dp_comm is not None)
     del pool, tr
     torch.cuda.empty_cache()
+    init()
     # ---- end to end: pinned host batches copied every step, loss read back every step ---------------------------
     wall = {}
 
@@ -174,6 +181,7 @@ def run_config3(args, bench) -> None:
     barrier()
     e2e_ms = (time.perf_counter() - wall["t0"]) * 1e3
     final_loss = tr.last_loss
+    aux_cap_e2e = tr._fused_aux.capacity if tr._fused_aux is not None else None
     t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -185,7 +193,7 @@ def run_config3(args, bench) -> None:
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": c3_config(world, c), "clocks": clocks,
             "path": "Trainer.fit on the fused kernel path" if fused else "Trainer.fit on the generic autograd path",
-            "optimizer_state_sharded_over_replicas": sharded_state, "auxk_dead_capacity": aux_cap,
+            "optimizer_state_sharded_over_replicas": sharded_state, "auxk_dead_capacity": aux_cap, "auxk_dead_capacity_e2e": aux_cap_e2e,
             "e2e": {"value": Ks * B / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms / Ks,
                     "h2d_bytes_per_step": B * D * 2 // tp + world * B_l * 9, "d2h_bytes_per_step": 4 * world},
             "gpu_launches": launches, "final_loss": final_loss, "impl": "ours", "package": lm.__name__,
@@ -230,9 +238,14 @@ def _run_config3_reference(args, bench, c: dict) -> None:
                         top_k=c["top_k"], device="cuda", dtype=torch.float32)  # fmt: skip
         sae = SparseAutoEncoder(cfg, device_mesh=mesh)
         bound = 1.0 / D**0.5
-        sae.init_parameters(encoder_uniform_bound=bound, decoder_uniform_bound=bound)
-        sae.set_decoder_to_fixed_norm(1.0, force_exact=True)
-        sae.init_encoder_with_decoder_transpose()
+
+        def init():
+            torch.manual_seed(0)
+            sae.init_parameters(encoder_uniform_bound=bound, decoder_uniform_bound=bound)
+            sae.set_decoder_to_fixed_norm(1.0, force_exact=True)
+            sae.init_encoder_with_decoder_transpose()
+
+        init()
         sae.set_dataset_average_activation_norm({hook: D**0.5})
         host = _batches(c, c["pool"], slice(dp_rank * B_l, (dp_rank + 1) * B_l))
 
@@ -280,6 +293,7 @@ def _run_config3_reference(args, bench, c: dict) -> None:
         ms = ev["start"].elapsed_time(ev["end"])
         del pool
         torch.cuda.empty_cache()
+        init()
         wall = {}
         fit_once(lambda i: host[i % len(host)].to(dev, non_blocking=True), lambda n: wall.__setitem__(n, time.perf_counter()))
         e2e_ms = (wall["end"] - wall["start"]) * 1e3
@@ -335,11 +349,28 @@ def _arm(impl: str):
     return pkg, (lambda t, mesh, names: t), lambda shape, names: build_mesh("cuda", shape, names)
 
 
+def _snapshot(sae):
+    """Copies of the dictionary's parameters. Both timed fits of an arm start from them, so that the end-to-end fit
+    repeats the trajectory of the device-timed one (the cost of a step depends on the state: number of dead features, of
+    codes above a threshold) instead of continuing where it stopped."""
+    return [p.detach().clone() for p in sae.parameters()]
+
+
+def _restore(sae, snap) -> None:
+    import torch
+
+    with torch.no_grad():
+        for p, s in zip(sae.parameters(), snap):
+            p.copy_(s)
+
+
 def _timed_fits(bench, args, world, rank, local, tokens_per_step, make_trainer, sae, stream_of, pools, result: dict) -> None:
     """``stream_of(source, on_start)`` yields batches; ``pools = (device batches, host batches)``. Fills ``result`` with
-    ms / e2e_ms (max over ranks) and clocks."""
+    ms / e2e_ms (max over ranks) and clocks. Both fits start from the same parameters."""
     import torch
     import torch.distributed as dist
+
+    snap = _snapshot(sae)
 
     dev = torch.device("cuda", local)
     W, Ks = args.warmup, args.steps
@@ -373,6 +404,8 @@ def _timed_fits(bench, args, world, rank, local, tokens_per_step, make_trainer, 
         barrier()
         wall["t0"] = time.perf_counter()
 
+    _restore(sae, snap)
+    del snap
     tr = make_trainer()
     tr.fit(sae, stream_of(pools[1], start_wall))
     barrier()

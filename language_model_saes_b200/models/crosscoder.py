@@ -47,9 +47,9 @@ class CrosscoderConfig(SparseDictionaryConfig):
     sae_type: str = "crosscoder"
     hook_points: list[str]
     fused_head_sum: bool | None = None
-    """Sum the encoder pre-activations over heads inside the encoder GEMM (local heads in its K loop, other ranks of
-    the ``head`` group through a reduce-scatter epilogue over peer memory). None: on for bf16 models under head
-    parallelism on CUDA; True also uses the kernel without a ``head`` group."""
+    """Sum the encoder pre-activations over heads with the native kernels (local heads in the K loop of one tcgen05 GEMM
+    that stores into a symmetric buffer, other ranks of the ``head`` group by the one-kernel in-place all-reduce).
+    None: on for bf16 models under head parallelism on CUDA; True also uses the GEMM without a ``head`` group."""
 
     @property
     def associated_hook_points(self) -> list[str]:
@@ -69,8 +69,8 @@ class CrosscoderConfig(SparseDictionaryConfig):
 
 
 class _HeadSumEncode(torch.autograd.Function):
-    """``sum over all heads of (x_h W_E[h] + b_E[h])`` through ``HeadSumComm`` (bf16 operands, fp32 accumulation and
-    reduction). The value is used by every rank's own heads, so the incoming gradient is summed over the group first
+    """``sum over all heads of (x_h W_E[h] + b_E[h])`` through ``HeadSumComm`` (bf16 operands and partial sums, fp32
+    accumulation). The value is used by every rank's own heads, so the incoming gradient is summed over the group first
     (as in ``all_reduce_sum_both``); the weight and input gradients are plain batched products."""
 
     @staticmethod
@@ -211,13 +211,13 @@ class Crosscoder(SparseDictionary):
             want = self.cfg.dtype == torch.bfloat16 and self.head_size > 1
         return bool(
             want and x.is_cuda and x.ndim >= 2 and self.cfg.d_model % 64 == 0
-            and self.d_sae_local % (self.head_size * 32) == 0
+            and self.d_sae_local % 8 == 0
         )  # fmt: skip
 
     def _summed_pre(self, x: torch.Tensor) -> torch.Tensor:
         """Pre-activations summed over ALL heads (local heads and the other ranks of the ``head`` group)."""
         if self._fused_head_sum_ok(x):
-            # one tcgen05 GEMM over K = local heads x d_model whose epilogue reduce-scatters into peer memory
+            # one tcgen05 GEMM over K = local heads x d_model into a symmetric buffer, summed over the head ranks in place
             from ..parallel.symm import HeadSumComm
 
             rows = x[..., 0, 0].numel()

@@ -848,7 +848,7 @@ void comm_shuffle_rows(const std::vector<int64_t>& table, const Tensor& src, con
 // `recv_off` holds `cap_rows` rows of d elements of `out_dtype` (0 = fp32, 1 = bf16).
 void comm_bcast_rows(const std::vector<int64_t>& table, const Tensor& src, const c10::optional<Tensor>& keep,
                      const c10::optional<Tensor>& pos, int64_t out_dtype, int64_t recv_off, int64_t cap_rows, int64_t phase,
-                     int64_t epoch, const Tensor& done_counter) {
+                     int64_t epoch, const Tensor& done_counter, bool use_multicast) {
   TORCH_CHECK(src.is_cuda() && src.is_contiguous() && src.dim() == 2, "src must be a contiguous CUDA matrix");
   CHECK_T(done_counter, torch::kInt32);
   if (keep.has_value()) {
@@ -861,26 +861,24 @@ void comm_bcast_rows(const std::vector<int64_t>& table, const Tensor& src, const
   lmsae::PeerTable pt = make_peer_table(table);
   check_cuda(lmsae::bcast_rows_cast_launch(pt, dtype_code(src), (int)out_dtype, src.data_ptr(), opt_ptr<int>(keep), opt_ptr<int>(pos),
                                            src.size(0), (int)src.size(1), recv_off, cap_rows, (int)phase, (uint32_t)epoch,
-                                           reinterpret_cast<unsigned*>(done_counter.data_ptr<int>()),
+                                           reinterpret_cast<unsigned*>(done_counter.data_ptr<int>()), use_multicast,
                                            at::cuda::getCurrentCUDAStream()),
              "comm_bcast_rows launch");
 }
 
-// Head-summed encoder GEMM with the reduce-scatter epilogue: x [M, heads * d] bf16, w [heads * rows_per_head, d] bf16
-// (head h's rows start at h * rows_per_head; the first N of them are used), bias fp32 [N] or absent. The fp32 result
-// tile is ADDED into slabs[c / (N / world)], an fp32 [M, N / world] array per rank (device pointers, peer mappings).
-// With `H_out` (bf16 [M, N], `slabs` empty) the sum over the local heads is stored instead of reduced into slabs.
+// Head-summed encoder GEMM: x [M, heads * d] bf16, w [heads * rows_per_head, d] bf16 (head h's rows start at
+// h * rows_per_head; the first N of them are used), bias fp32 [N] or absent. One accumulation over K = heads * d sums
+// x_h . W_h^T over the local heads; the result (+ bias) is stored as bf16 into H_out [M, N], which may be a view of a
+// symmetric buffer that an all-reduce kernel then sums over the head ranks in place.
 void head_sum_gemm(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& bias, int64_t heads, int64_t rows_per_head,
-                   int64_t N, const std::vector<int64_t>& slabs, bool pair, const Tensor& status,
-                   const c10::optional<Tensor>& H_out) {
+                   int64_t N, bool pair, const Tensor& status, const Tensor& H_out) {
   CHECK_T(x, torch::kBFloat16);
   CHECK_T(w, torch::kBFloat16);
   CHECK_T(status, torch::kInt32);
+  CHECK_T(H_out, torch::kBFloat16);
   TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && heads >= 1 && x.size(1) == heads * w.size(1), "x [M, heads*d], w [heads*rows, d]");
   TORCH_CHECK(w.size(0) == heads * rows_per_head && N <= rows_per_head, "w must hold `heads` blocks of rows_per_head rows");
-  const int64_t world = (int64_t)slabs.size();
-  TORCH_CHECK(world >= 1 || H_out.has_value(), "either slabs to reduce into or an output matrix");
-  if (world > 0) TORCH_CHECK(world <= 8 && N % world == 0 && (N / world) % 32 == 0, "N / world must be a multiple of 32");
+  TORCH_CHECK(H_out.dim() == 2 && H_out.size(0) == x.size(0) && H_out.size(1) == N, "H_out must be [M, N]");
   TORCH_CHECK(w.size(1) % 64 == 0, "d must be a multiple of 64");
   const c10::cuda::CUDAGuard guard(x.device());
   lmsae::EncGemmParams p{};
@@ -899,35 +897,13 @@ void head_sum_gemm(const Tensor& x, const Tensor& w, const c10::optional<Tensor>
   p.status = status.data_ptr<int>();
   p.heads = (int)heads;
   p.b_rows_per_head = (int)rows_per_head;
-  p.red_world = (int)world;
-  p.red_cols = world > 0 ? (int)(N / world) : 0;
-  if (world == 0) {
-    CHECK_T(*H_out, torch::kBFloat16);
-    TORCH_CHECK(H_out->dim() == 2 && H_out->size(0) == x.size(0) && H_out->size(1) == N, "H_out must be [M, N]");
-    p.H = reinterpret_cast<__nv_bfloat16*>(H_out->data_ptr());
-    p.ldh = p.N;
-  }
-  for (int64_t i = 0; i < world; ++i) {
-    TORCH_CHECK(slabs[i] % 16 == 0, "slab pointers must be 16-byte aligned");
-    p.red_base[i] = reinterpret_cast<float*>(static_cast<uintptr_t>(slabs[i]));
-  }
+  p.H = reinterpret_cast<__nv_bfloat16*>(H_out.data_ptr());
+  p.ldh = p.N;
   int mode = 1;
   if (pair && p.num_panels % 2 == 0) mode |= 8;
   const CUtensorMap ta = make_bf16_tile_map(x.data_ptr(), p.M, p.K, 128);
   const CUtensorMap tb = make_bf16_tile_map(w.data_ptr(), w.size(0), w.size(1), (mode & 8) ? 128 : 256);
   check_cuda(lmsae::enc_gemm_launch(ta, tb, p, mode, at::cuda::getCurrentCUDAStream()), "head_sum_gemm launch");
-}
-
-void comm_headsum_gather(const std::vector<int64_t>& table, int64_t slab_off, int64_t out_off, int64_t B, int64_t cols,
-                         int64_t out_dtype, int64_t phase_in, int64_t phase_out, int64_t epoch, const Tensor& done_counter,
-                         const Tensor& status) {
-  CHECK_T(done_counter, torch::kInt32);
-  CHECK_T(status, torch::kInt32);
-  lmsae::PeerTable pt = make_peer_table(table);
-  check_cuda(lmsae::headsum_gather_launch(pt, slab_off, out_off, (int)B, (int)cols, (int)out_dtype, (int)phase_in, (int)phase_out,
-                                          (uint32_t)epoch, reinterpret_cast<unsigned*>(done_counter.data_ptr<int>()),
-                                          status.data_ptr<int>(), at::cuda::getCurrentCUDAStream()),
-             "comm_headsum_gather launch");
 }
 
 // In-place sum over the ranks of `table` of the bf16 array at byte offset `off` (n16 16-byte vectors) of every rank's
@@ -1014,7 +990,7 @@ void comm_reduce_loss_push(const std::vector<int64_t>& table, int64_t B, int64_t
 // rank's buffer; the kernel returns once every rank's rows have arrived here (bounded wait by its last block).
 void comm_exchange_rows(const std::vector<int64_t>& table, const std::vector<Tensor>& src,
                         const std::vector<int64_t>& dst_offsets, int64_t epoch, const Tensor& done_counter,
-                        const Tensor& status) {
+                        const Tensor& status, bool use_multicast) {
   CHECK_T(done_counter, torch::kInt32);
   CHECK_T(status, torch::kInt32);
   TORCH_CHECK(!src.empty() && src.size() <= 8 && src.size() == dst_offsets.size(), "one offset per tensor, at most eight");
@@ -1031,7 +1007,7 @@ void comm_exchange_rows(const std::vector<int64_t>& table, const std::vector<Ten
   const c10::cuda::CUDAGuard guard(src[0].device());
   check_cuda(lmsae::exchange_rows_launch(make_peer_table(table), ex, (uint32_t)epoch,
                                          reinterpret_cast<unsigned*>(done_counter.data_ptr<int>()), status.data_ptr<int>(),
-                                         at::cuda::getCurrentCUDAStream()),
+                                         use_multicast, at::cuda::getCurrentCUDAStream()),
              "exchange_rows launch");
 }
 
@@ -1067,7 +1043,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("comm_signal", &comm_signal);
   m.def("comm_allreduce_bf16", &comm_allreduce_bf16);
   m.def("head_sum_gemm", &head_sum_gemm);
-  m.def("comm_headsum_gather", &comm_headsum_gather);
   m.def("comm_wait_src", &comm_wait_src);
   m.def("comm_shuffle_rows", &comm_shuffle_rows);
   m.def("comm_decode_scatter", &comm_decode_scatter);

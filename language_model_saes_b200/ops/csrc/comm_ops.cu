@@ -231,14 +231,25 @@ reduce_loss_push_kernel(const PeerTable pt, int B, int d, const __nv_bfloat16* _
 // publishes the epoch and then waits (bounded) for the other ranks' flags, so that the kernels after this one in the
 // stream find every rank's rows in place. Replaces one collective per tensor (x, d x_hat and the three code tensors of
 // a data-parallel step).
+//
+// MC: one multimem.st per 16 bytes through the multicast mapping; the switch replicates it into every rank's buffer,
+// so a rank sends its rows over its link once instead of once per peer.
+template <bool MC>
 __global__ void __launch_bounds__(256)
 exchange_rows_kernel(const PeerTable pt, const RowExchange ex, uint32_t epoch, unsigned* done_counter, int* status) {
   for (int i = 0; i < ex.n; ++i) {
     const uint4* s = reinterpret_cast<const uint4*>(ex.src[i]);
     const long long nvec = ex.nbytes[i] / 16;
-    for (int p = 0; p < pt.world; ++p) {
-      uint4* dst = reinterpret_cast<uint4*>(pt.base[p] + ex.dst_off[i] + (long long)pt.rank * ex.nbytes[i]);
-      for (long long v = blockIdx.x * 256LL + threadIdx.x; v < nvec; v += (long long)gridDim.x * 256) dst[v] = __ldg(s + v);
+    const long long off = ex.dst_off[i] + (long long)pt.rank * ex.nbytes[i];
+    if constexpr (MC) {
+      uint4* dst = reinterpret_cast<uint4*>(pt.mc_base + off);
+      for (long long v = blockIdx.x * 256LL + threadIdx.x; v < nvec; v += (long long)gridDim.x * 256)
+        multimem_st_16B(dst + v, __ldg(s + v));
+    } else {
+      for (int p = 0; p < pt.world; ++p) {
+        uint4* dst = reinterpret_cast<uint4*>(pt.base[p] + off);
+        for (long long v = blockIdx.x * 256LL + threadIdx.x; v < nvec; v += (long long)gridDim.x * 256) dst[v] = __ldg(s + v);
+      }
     }
   }
   const bool last = signal_peers_when_grid_done(pt, kPhaseRows, epoch, done_counter);
@@ -246,14 +257,16 @@ exchange_rows_kernel(const PeerTable pt, const RowExchange ex, uint32_t epoch, u
 }
 
 int exchange_rows_launch(const PeerTable& pt, const RowExchange& ex, uint32_t epoch, unsigned* done_counter, int* status,
-                         cudaStream_t stream) {
+                         bool use_multicast, cudaStream_t stream) {
   if (ex.n < 1 || ex.n > 8) return (int)cudaErrorInvalidValue;
+  if (use_multicast && pt.mc_base == nullptr) return (int)cudaErrorInvalidValue;
   long long total = 0;
   for (int i = 0; i < ex.n; ++i) total += ex.nbytes[i] / 16;
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 4) blocks = 148 * 4;
   if (blocks < 1) blocks = 1;
-  exchange_rows_kernel<<<(int)blocks, 256, 0, stream>>>(pt, ex, epoch, done_counter, status);
+  if (use_multicast) exchange_rows_kernel<true><<<(int)blocks, 256, 0, stream>>>(pt, ex, epoch, done_counter, status);
+  else exchange_rows_kernel<false><<<(int)blocks, 256, 0, stream>>>(pt, ex, epoch, done_counter, status);
   return (int)cudaGetLastError();
 }
 
@@ -377,7 +390,8 @@ int shuffle_rows_launch(const PeerTable& pt, const void* src, const long long* d
 // straight into every peer's landing zone, one read of the source for `world` NVLink writes. Replaces a boolean index,
 // a dtype cast and a broadcast collective (activation/processors/cached_activation.py:301-320 and the loader-side
 // redistribute of the reference project). `pos` = exclusive prefix sum of `keep` (both nullptr: keep every row).
-template <typename TI, typename TO>
+// MC: the stores go through the NVSwitch multicast mapping (multimem.st), one message for all ranks.
+template <typename TI, typename TO, bool MC>
 __global__ void __launch_bounds__(256)
 bcast_rows_cast_kernel(const PeerTable pt, const TI* __restrict__ src, const int* __restrict__ keep,
                        const int* __restrict__ pos, long long n, int d, long long recv_off, long long cap_rows, int phase,
@@ -395,15 +409,26 @@ bcast_rows_cast_kernel(const PeerTable pt, const TI* __restrict__ src, const int
       } else {
         bf16x8_to_float_c(__ldcs(reinterpret_cast<const uint4*>(s + c)), f);
       }
-      for (int p = 0; p < pt.world; ++p) {
-        TO* dst = reinterpret_cast<TO*>(pt.base[p] + recv_off) + (size_t)o * d + c;
+      if constexpr (MC) {
+        TO* dst = reinterpret_cast<TO*>(pt.mc_base + recv_off) + (size_t)o * d + c;
         if constexpr (sizeof(TO) == 4) {
-          reinterpret_cast<float4*>(dst)[0] = make_float4(f[0], f[1], f[2], f[3]);
-          reinterpret_cast<float4*>(dst)[1] = make_float4(f[4], f[5], f[6], f[7]);
+          uint4 lo, hi;
+          lo.x = __float_as_uint(f[0]); lo.y = __float_as_uint(f[1]); lo.z = __float_as_uint(f[2]); lo.w = __float_as_uint(f[3]);
+          hi.x = __float_as_uint(f[4]); hi.y = __float_as_uint(f[5]); hi.z = __float_as_uint(f[6]); hi.w = __float_as_uint(f[7]);
+          multimem_st_16B(dst, lo);
+          multimem_st_16B(dst + 4, hi);
         } else {
-          uint4 u;
-          u.x = pack_bf16x2(f[0], f[1]); u.y = pack_bf16x2(f[2], f[3]); u.z = pack_bf16x2(f[4], f[5]); u.w = pack_bf16x2(f[6], f[7]);
-          *reinterpret_cast<uint4*>(dst) = u;
+          multimem_st_16B(dst, float8_to_bf16x8(f));
+        }
+      } else {
+        for (int p = 0; p < pt.world; ++p) {
+          TO* dst = reinterpret_cast<TO*>(pt.base[p] + recv_off) + (size_t)o * d + c;
+          if constexpr (sizeof(TO) == 4) {
+            reinterpret_cast<float4*>(dst)[0] = make_float4(f[0], f[1], f[2], f[3]);
+            reinterpret_cast<float4*>(dst)[1] = make_float4(f[4], f[5], f[6], f[7]);
+          } else {
+            *reinterpret_cast<uint4*>(dst) = float8_to_bf16x8(f);
+          }
         }
       }
     }
@@ -413,77 +438,27 @@ bcast_rows_cast_kernel(const PeerTable pt, const TI* __restrict__ src, const int
 
 int bcast_rows_cast_launch(const PeerTable& pt, int in_dtype, int out_dtype, const void* src, const int* keep, const int* pos,
                            long long n, int d, long long recv_off, long long cap_rows, int phase, uint32_t epoch,
-                           unsigned* done_counter, cudaStream_t stream) {
+                           unsigned* done_counter, bool use_multicast, cudaStream_t stream) {
   if (d % 8 != 0 || recv_off % 16 != 0 || phase < 0 || phase >= kNumPhases) return (int)cudaErrorInvalidValue;
+  if (use_multicast && pt.mc_base == nullptr) return (int)cudaErrorInvalidValue;
   const int blocks = (int)(n < 148LL * 8 ? (n > 0 ? n : 1) : 148LL * 8);
   using bf = __nv_bfloat16;
-#define LMSAE_BCAST(TI, TO)                                                                                              \
-  bcast_rows_cast_kernel<TI, TO><<<blocks, 256, 0, stream>>>(pt, static_cast<const TI*>(src), keep, pos, n, d, recv_off, \
-                                                             cap_rows, phase, epoch, done_counter)
+#define LMSAE_BCAST(TI, TO)                                                                                             \
+  do {                                                                                                                  \
+    if (use_multicast)                                                                                                  \
+      bcast_rows_cast_kernel<TI, TO, true><<<blocks, 256, 0, stream>>>(pt, static_cast<const TI*>(src), keep, pos, n, d, \
+                                                                       recv_off, cap_rows, phase, epoch, done_counter); \
+    else                                                                                                                \
+      bcast_rows_cast_kernel<TI, TO, false><<<blocks, 256, 0, stream>>>(pt, static_cast<const TI*>(src), keep, pos, n, \
+                                                                        d, recv_off, cap_rows, phase, epoch,            \
+                                                                        done_counter);                                  \
+  } while (0)
   if (in_dtype == 0 && out_dtype == 0) LMSAE_BCAST(float, float);
   else if (in_dtype == 0 && out_dtype == 1) LMSAE_BCAST(float, bf);
   else if (in_dtype == 1 && out_dtype == 0) LMSAE_BCAST(bf, float);
   else if (in_dtype == 1 && out_dtype == 1) LMSAE_BCAST(bf, bf);
   else return (int)cudaErrorInvalidValue;
 #undef LMSAE_BCAST
-  return (int)cudaGetLastError();
-}
-
-// ---------------------------------------------------------------------------------------------
-// Second half of the head-summed encoder: after every rank's GEMM epilogue has added its partial pre-activations into
-// the column slab this rank owns (reduce-scatter by vector reductions over NVLink, encoder_gemm.cu), the owner reads
-// its fp32 slab [B, cols] once, stores the sums into every rank's full [B, world * cols] output (all-gather by peer
-// stores) and clears the slab for the call after next. Replaces the all-reduce of a [batch, d_sae] tensor per step
-// in models/crosscoder.py:350-375 of the reference project.
-template <typename TO>
-__global__ void __launch_bounds__(256)
-headsum_gather_kernel(const PeerTable pt, long long slab_off, long long out_off, int B, int cols, int phase_in,
-                      int phase_out, uint32_t epoch, unsigned* done_counter, int* status) {
-  const bool ok = wait_all_sources(pt, phase_in, epoch, status);
-  if (ok) {
-    float* slab = reinterpret_cast<float*>(pt.base[pt.rank] + slab_off);
-    const int N = cols * pt.world;
-    const int vec_per_row = cols / 8;
-    for (long long i = blockIdx.x * 256LL + threadIdx.x; i < (long long)B * vec_per_row; i += (long long)gridDim.x * 256) {
-      const long long row = i / vec_per_row;
-      const int c = (int)(i - row * vec_per_row) * 8;
-      float4* sp = reinterpret_cast<float4*>(slab + row * cols + c);
-      const float4 a = sp[0], b = sp[1];
-      sp[0] = make_float4(0.f, 0.f, 0.f, 0.f);
-      sp[1] = make_float4(0.f, 0.f, 0.f, 0.f);
-      const long long o = row * N + (long long)pt.rank * cols + c;
-      for (int p = 0; p < pt.world; ++p) {
-        TO* dst = reinterpret_cast<TO*>(pt.base[p] + out_off) + o;
-        if constexpr (sizeof(TO) == 4) {
-          reinterpret_cast<float4*>(dst)[0] = a;
-          reinterpret_cast<float4*>(dst)[1] = b;
-        } else {
-          uint4 u;
-          u.x = pack_bf16x2(a.x, a.y); u.y = pack_bf16x2(a.z, a.w); u.z = pack_bf16x2(b.x, b.y); u.w = pack_bf16x2(b.z, b.w);
-          *reinterpret_cast<uint4*>(dst) = u;
-        }
-      }
-    }
-  }
-  // signal even after a failed wait so that peers do not pile further timeouts on top of the first one
-  signal_peers_when_grid_done(pt, phase_out, epoch, done_counter);
-}
-
-int headsum_gather_launch(const PeerTable& pt, long long slab_off, long long out_off, int B, int cols, int out_dtype,
-                          int phase_in, int phase_out, uint32_t epoch, unsigned* done_counter, int* status,
-                          cudaStream_t stream) {
-  if (cols % 8 != 0 || slab_off % 16 != 0 || out_off % 16 != 0) return (int)cudaErrorInvalidValue;
-  if (phase_in < 0 || phase_in >= kNumPhases || phase_out < 0 || phase_out >= kNumPhases) return (int)cudaErrorInvalidValue;
-  const long long work = (long long)B * (cols / 8);
-  int blocks = (int)((work + 255) / 256);
-  if (blocks > 148 * 4) blocks = 148 * 4;
-  if (blocks < 1) blocks = 1;
-  if (out_dtype == 0)
-    headsum_gather_kernel<float><<<blocks, 256, 0, stream>>>(pt, slab_off, out_off, B, cols, phase_in, phase_out, epoch,
-                                                            done_counter, status);
-  else
-    headsum_gather_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(pt, slab_off, out_off, B, cols, phase_in, phase_out,
-                                                                    epoch, done_counter, status);
   return (int)cudaGetLastError();
 }
 

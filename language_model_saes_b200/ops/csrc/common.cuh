@@ -350,12 +350,6 @@ __device__ __forceinline__ void red_release_gpu_add(uint32_t* p, uint32_t v) {
   asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// Four fp32 additions into (possibly peer) global memory in one reduction message; nothing is returned.
-__device__ __forceinline__ void red_add_v4_f32_sys(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
-               : "memory");
-}
-
 // Bounded spin until *flag >= target (flags only grow). Returns false when the budget ran out.
 __device__ __forceinline__ bool wait_flag_sys(const uint32_t* flag, uint32_t target) {
   if (ld_acquire_sys(flag) >= target) return true;

@@ -318,16 +318,6 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 #pragma unroll
             for (int j = 0; j < 32; ++j) if (full_chunk || c0 + j < p.N) v[j] *= __ldg(p.gate + c0 + j);
           }
-          if (p.red_world > 0) {
-            // reduce-scatter epilogue: add this 32-column piece into the slab of the rank that owns the columns
-            if (row_ok && full_chunk) {
-              const int owner = c0 / p.red_cols;
-              float* dst = p.red_base[owner] + (long long)row * p.red_cols + (c0 - owner * p.red_cols);
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) red_add_v4_f32_sys(dst + j, v[j], v[j + 1], v[j + 2], v[j + 3]);
-            }
-            continue;
-          }
         }
         if constexpr (WRITE_H) {
           if (row_ok) {
@@ -476,8 +466,6 @@ int enc_gemm_launch(const CUtensorMap& ta, const CUtensorMap& tb, const EncGemmP
   const bool wh = mode & 1, tk = mode & 2, pair = mode & 8, compact = mode & 16;
   if (pair && (p.num_panels % 2 != 0)) return (int)cudaErrorInvalidValue;
   if (p.heads > 1 && (p.K % (p.heads * BK) != 0 || p.b_rows_per_head < p.N)) return (int)cudaErrorInvalidValue;
-  if (p.red_world > 0 && (tk || !wh || p.red_world > 8 || p.red_cols % 32 != 0 || p.red_cols * p.red_world != p.N))
-    return (int)cudaErrorInvalidValue;
   cudaError_t e;
   if (!tk) {
     if (pair) e = launch_variant<true, false, 6, 0, true>(ta, tb, p, stream);

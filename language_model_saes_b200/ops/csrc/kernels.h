@@ -30,12 +30,6 @@ struct EncGemmParams {
   // x_h . W_h^T over the heads. heads <= 1: a plain GEMM.
   int heads;
   int b_rows_per_head;
-  // Reduce-scatter epilogue (WRITE_H variants, red_world > 0): instead of storing H, the fp32 tile is added into
-  // the slab of the rank that owns its columns: red_base[c / red_cols] is an fp32 [M, red_cols] array in that rank's
-  // memory (a peer mapping), updated with vector reductions. red_cols % 32 == 0.
-  int red_world;
-  int red_cols;
-  float* red_base[8];
 };
 int enc_gemm_launch(const CUtensorMap& ta, const CUtensorMap& tb, const EncGemmParams& p, int mode, cudaStream_t stream);
 int enc_gemm_slots_for_k(int k);
@@ -234,7 +228,7 @@ struct RowExchange {
   int n;
 };
 int exchange_rows_launch(const PeerTable& pt, const RowExchange& ex, uint32_t epoch, unsigned* done_counter, int* status,
-                         cudaStream_t stream);
+                         bool use_multicast, cudaStream_t stream);
 int push_candidates_launch(const PeerTable& pt, const float* val, const int* idx, int B, int k, uint32_t epoch,
                            unsigned* done_counter, cudaStream_t stream);
 int shuffle_rows_launch(const PeerTable& pt, const void* src, const long long* dest, int n_local, int rows_per_rank,
@@ -242,10 +236,7 @@ int shuffle_rows_launch(const PeerTable& pt, const void* src, const long long* d
                         cudaStream_t stream);
 int bcast_rows_cast_launch(const PeerTable& pt, int in_dtype, int out_dtype, const void* src, const int* keep, const int* pos,
                            long long n, int d, long long recv_off, long long cap_rows, int phase, uint32_t epoch,
-                           unsigned* done_counter, cudaStream_t stream);
-int headsum_gather_launch(const PeerTable& pt, long long slab_off, long long out_off, int B, int cols, int out_dtype,
-                          int phase_in, int phase_out, uint32_t epoch, unsigned* done_counter, int* status,
-                          cudaStream_t stream);
+                           unsigned* done_counter, bool use_multicast, cudaStream_t stream);
 int allreduce_bf16_launch(const PeerTable& pt, long long off, long long n16, int phase_in, int phase_out, uint32_t epoch,
                           int use_multicast, unsigned* done_counter, int* status, cudaStream_t stream);
 int signal_flags_launch(const PeerTable& pt, int phase, uint32_t epoch, cudaStream_t stream);

@@ -133,7 +133,7 @@ class FusedCrosscoderStep:
         # the GEMM accumulates the local heads in one K loop and stores bf16 straight into the symmetric buffer ...
         P = self.comm.matrix(B)
         K._ext().head_sum_gemm(x16, self.WE_bf16.view(self.H_l * self.F, self.d), self.bE.sum(0).contiguous(), self.H_l, self.F, self.F,
-                               [], True, K.status_buffer(x16.device), P)  # fmt: skip
+                               True, K.status_buffer(x16.device), P)  # fmt: skip
         # ... which one kernel then sums over the head ranks in place (NVSwitch multicast loads / stores where available)
         return self.comm.all_reduce(B) if self.head_size > 1 else P
 

@@ -5,11 +5,13 @@
 
 Cases: ``shuffle`` (seeded row all-to-all of the activation buffer, ``ShuffleComm`` vs ``all_to_all_single`` after a
 local gather), ``bcast`` (masked + cast row broadcast of cached activations, ``BroadcastComm`` vs boolean index + cast +
-``broadcast``), ``headsum`` (crosscoder pre-activation sum inside the GEMM, ``HeadSumComm`` vs ``einsum`` + ``all_reduce``), ``allreduce``
+``broadcast``), ``headsum`` (crosscoder pre-activation sum: head-summing GEMM into a symmetric buffer + one-kernel all-reduce, ``HeadSumComm``
+vs ``einsum`` + ``all_reduce``), ``allreduce``
 (in-place sum of a bf16 [4096, 98304] matrix in one kernel, ``AllReduceComm`` with and without the NVSwitch multicast
 mapping, vs ``all_reduce``),
 ``rows`` (the five tensors of a data-parallel step in one kernel, ``DataParallelComm.exchange`` vs five
-``all_gather_into_tensor`` calls).
+``all_gather_into_tensor`` calls). ``bcast``, ``allreduce`` and ``rows`` run twice where the group has a multicast
+mapping: through the NVSwitch (``multimem``) and by plain peer loads / stores.
 
 Every time is taken on the device with CUDA events after warm-up and is the MAX over ranks; every JSON line carries the
 SM clock, power and throttle reasons sampled on rank 0 while the case ran. NVLink bytes are counted per rank and
@@ -105,7 +107,6 @@ def main(argv=None):
         n, d = 65536, 4096  # one chunk of cached fp32 activations, a quarter of the tokens masked out, cast to bf16
         src_rows = torch.randn(n, d, device=dev) if rank == 0 else None
         keep = (torch.rand(n, device=dev) > 0.25) if rank == 0 else None
-        comm = symm.BroadcastComm(group, dev, max_rows=n, max_row_bytes=d * 2)
         count = torch.zeros(1, dtype=torch.long, device=dev)
         landing = torch.empty(n, d, dtype=torch.bfloat16, device=dev)
 
@@ -119,9 +120,16 @@ def main(argv=None):
                 landing[:m].copy_(rows)
             dist.broadcast(landing[:m], src=0)
 
-        run("broadcast_masked_cast_rows_65536x4096_fp32_to_bf16", lambda: comm.broadcast_rows(0, d, torch.bfloat16, src_rows, keep),
-            nccl_path, link_bytes=0.75 * n * d * 2 * (world - 1))  # fmt: skip
-        del comm, src_rows, landing
+        for use_mc in (True, False):
+            comm = symm.BroadcastComm(group, dev, max_rows=n, max_row_bytes=d * 2, use_multicast=use_mc)
+            if use_mc and not comm.use_multicast:
+                continue
+            # bytes the sender puts on its link: once through the switch, once per peer otherwise
+            run(f"broadcast_masked_cast_rows_65536x4096_fp32_to_bf16_{'multimem' if use_mc else 'peer_stores'}",
+                lambda: comm.broadcast_rows(0, d, torch.bfloat16, src_rows, keep), nccl_path,
+                link_bytes=0.75 * n * d * 2 * (1 if use_mc else world - 1))  # fmt: skip
+            del comm
+        del src_rows, landing
 
     if want("headsum"):
         M, heads, d, N = 4096, max(1, 8 // world), 768, 98304  # the crosscoder of 8 snapshots, heads spread over the ranks
@@ -161,7 +169,6 @@ def main(argv=None):
              "idx": torch.randint(0, 1 << 17, (B, k), device=dev, dtype=torch.int32), "act": torch.randn(B, k, device=dev),
              "dact": torch.randn(B, k, device=dev)}  # fmt: skip
         zones = {n_: v.numel() * v.element_size() * world for n_, v in t.items()}
-        comm = symm.DataParallelComm(group, dev, 1024, d, zones)
         outs = {n_: torch.empty(world * v.shape[0], *v.shape[1:], dtype=v.dtype, device=dev) for n_, v in t.items()}
 
         def nccl_path():
@@ -169,7 +176,14 @@ def main(argv=None):
                 dist.all_gather_into_tensor(outs[n_], v)
 
         per_rank = sum(v.numel() * v.element_size() for v in t.values())
-        run("data_parallel_row_exchange_5_tensors_B4096_d4096_k64", lambda: comm.exchange(t), nccl_path, link_bytes=per_rank * (world - 1))
+        for use_mc in (True, False):
+            comm = symm.DataParallelComm(group, dev, 1024, d, zones, use_multicast=use_mc)
+            if use_mc and not comm.use_multicast:
+                continue
+            # bytes every rank RECEIVES (the side that bounds an all-gather through the switch)
+            run(f"data_parallel_row_exchange_5_tensors_B4096_d4096_k64_{'multimem' if use_mc else 'peer_stores'}",
+                lambda: comm.exchange(t), nccl_path, link_bytes=per_rank * (world - 1))
+            del comm
     dist.destroy_process_group()
 
 

@@ -72,6 +72,17 @@ def _rendezvous(nbytes: int, group: dist.ProcessGroup, device: torch.device):
     return buf, handle, ptrs, mc
 
 
+def _use_multicast(requested: bool | None, env_name: str, world: int, multicast_ptr: int) -> bool:
+    """Whether a communicator sends through the NVSwitch multicast mapping (``multimem`` instructions): an explicit
+    argument wins, then the environment variable (``1`` / ``0``), else groups of more than two ranks do. With one peer a
+    multicast store saves nothing over a peer store, and the measured in-switch reduction was slower than peer loads at
+    two ranks and faster at eight. Always off without a multicast mapping."""
+    if requested is None:
+        env = os.environ.get(env_name, "")
+        requested = env == "1" if env in ("0", "1") else world > 2
+    return bool(requested and multicast_ptr)
+
+
 class WaitStats:
     """Device counters of the time kernels spent in bounded peer-flag waits: ``{cycles, calls}`` per phase, filled by
     block 0 of every waiting kernel. ``read()`` converts to milliseconds with an SM clock in MHz."""
@@ -228,8 +239,10 @@ class DataParallelComm:
     """
 
     def __init__(self, group: dist.ProcessGroup, device: torch.device, n_features: int, d_model: int,
-                 zones: dict[str, int]):  # fmt: skip
-        """``zones``: name -> capacity in bytes of the GATHERED tensor, for every tensor that ``exchange`` moves."""
+                 zones: dict[str, int], use_multicast: bool | None = None):  # fmt: skip
+        """``zones``: name -> capacity in bytes of the GATHERED tensor, for every tensor that ``exchange`` moves.
+        ``use_multicast``: the row exchange stores through the NVSwitch multicast mapping, one message per 16 bytes for
+        all replicas (default: environment variable ``LMSAE_ROWS_MULTICAST``, else groups of more than two ranks)."""
         self.group, self.device = group, device
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         assert self.world <= _MAX_PEERS
@@ -246,6 +259,7 @@ class DataParallelComm:
             off = _align(off + nbytes)
         self.nbytes = off
         self.buf, self.handle, self.ptrs, self.multicast_ptr = _rendezvous(self.nbytes, group, device)
+        self.use_multicast = _use_multicast(use_multicast, "LMSAE_ROWS_MULTICAST", self.world, self.multicast_ptr)
         self.stats = WaitStats(device)
         self.done_counter = torch.zeros(1, dtype=torch.int32, device=device)
         self.epochs = [0] * _NUM_PHASES
@@ -253,7 +267,8 @@ class DataParallelComm:
         dist.barrier(group=group)
 
     def table(self) -> list[int]:
-        return peer_table(self.world, self.rank, self.ptrs, 0, stats_ptr=self.stats.buf.data_ptr())
+        return peer_table(self.world, self.rank, self.ptrs, 0, multicast_ptr=self.multicast_ptr if self.use_multicast else 0,
+                          stats_ptr=self.stats.buf.data_ptr())  # fmt: skip
 
     def _view(self, off: int, shape: tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
         n = dtype.itemsize
@@ -284,7 +299,7 @@ class DataParallelComm:
             assert nb % 16 == 0 and nb * self.world <= self.zone_cap[n], f"zone {n}: {nb} bytes per rank do not fit"
         e = self.epochs[PHASE_ROWS] = self.epochs[PHASE_ROWS] + 1
         K._ext().comm_exchange_rows(self.table(), parts, [self.zone_off[n] for n in names], e, self.done_counter,
-                                    K.status_buffer(self.device))  # fmt: skip
+                                    K.status_buffer(self.device), self.use_multicast)  # fmt: skip
         return {n: self._view(self.zone_off[n], (self.world * t.shape[0], *t.shape[1:]), t.dtype) for n, t in zip(names, parts)}
 
     def pub_args(self) -> tuple[list[int], list[int], int, torch.Tensor]:
@@ -367,7 +382,10 @@ class BroadcastComm:
     sender behind the receivers' previous copies, so the bounded flag waits only cover stores and flags in flight.
     """
 
-    def __init__(self, group: dist.ProcessGroup, device: torch.device, max_rows: int, max_row_bytes: int):
+    def __init__(self, group: dist.ProcessGroup, device: torch.device, max_rows: int, max_row_bytes: int,
+                 use_multicast: bool | None = None):  # fmt: skip
+        """``use_multicast``: the sender stores every 16 bytes once through the NVSwitch multicast mapping instead of once
+        per peer (default: environment variable ``LMSAE_BCAST_MULTICAST``, else groups of more than two ranks)."""
         self.group, self.device = group, device
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         assert self.world <= _MAX_PEERS
@@ -377,8 +395,9 @@ class BroadcastComm:
         self.recv_off = [_align(FLAG_BYTES)]
         self.recv_off.append(self.recv_off[0] + zone)
         self.nbytes = self.recv_off[1] + zone
-        self.buf, self.handle, ptrs, _ = _rendezvous(self.nbytes, group, device)
-        self.table = peer_table(self.world, self.rank, ptrs)
+        self.buf, self.handle, ptrs, mc = _rendezvous(self.nbytes, group, device)
+        self.use_multicast = _use_multicast(use_multicast, "LMSAE_BCAST_MULTICAST", self.world, mc)
+        self.table = peer_table(self.world, self.rank, ptrs, 0, multicast_ptr=mc if self.use_multicast else 0)
         self.done_counter = torch.zeros(1, dtype=torch.int32, device=device)
         self.count = torch.zeros(1, dtype=torch.int64, device=device)
         self.epoch = 0
@@ -412,7 +431,7 @@ class BroadcastComm:
             if self.epoch > 2:  # the zone still holds call epoch - 2: everyone must have copied it out
                 ext.comm_wait(self.table, PHASE_BCAST_ACK, self.epoch - 2, st)
             ext.comm_bcast_rows(self.table, rows, keep32, pos, 0 if out_dtype == torch.float32 else 1, off, cap_rows,
-                                PHASE_BCAST_DATA, self.epoch, self.done_counter)  # fmt: skip
+                                PHASE_BCAST_DATA, self.epoch, self.done_counter, self.use_multicast)  # fmt: skip
         else:
             self.count.zero_()
         # the row count, summed (the others add zero): unlike a broadcast, an all-reduce completes on the sender only after
@@ -450,9 +469,7 @@ class AllReduceComm:
         else:
             self.buf, ptrs, mc = torch.zeros(self.nbytes, dtype=torch.uint8, device=device), None, 0
             ptrs = [self.buf.data_ptr()]
-        if use_multicast is None:
-            use_multicast = os.environ.get("LMSAE_ALLREDUCE_MULTICAST", "1") == "1"
-        self.use_multicast = bool(use_multicast and mc)
+        self.use_multicast = _use_multicast(use_multicast, "LMSAE_ALLREDUCE_MULTICAST", self.world, mc)
         self.stats = WaitStats(device)
         self.table = peer_table(self.world, self.rank, ptrs, 0, multicast_ptr=mc, stats_ptr=self.stats.buf.data_ptr())
         self.done_counter = torch.zeros(1, dtype=torch.int32, device=device)
@@ -477,56 +494,32 @@ class AllReduceComm:
         return self.buf[off : off + rows * self.n_cols * 2].view(torch.bfloat16).view(rows, self.n_cols)
 
 
-PHASE_HS_REDUCED, PHASE_HS_GATHERED = 0, 1
-
-
 class HeadSumComm:
-    """Sum of per-rank encoder pre-activations over a ``head`` group, fused into the GEMM that produces them.
+    """Sum of per-rank encoder pre-activations over a ``head`` group.
 
     ``head_sum(x, w, bias, ...)`` computes ``sum_ranks (sum_local_heads x_h W_h^T + b_h)`` as ``[M, N]`` on every rank:
-    the tcgen05 GEMM accumulates the local heads in one K loop (K = heads x d) and its epilogue adds each finished tile
-    into the fp32 slab of the rank that owns those columns with vector reductions through the peer mapping
-    (reduce-scatter while other tiles are still being multiplied); the owners then store the sums into every rank's output
-    (all-gather by peer stores). Two slabs alternate between calls and are cleared by their owner after use.
+    the tcgen05 GEMM accumulates the local heads in one K loop (K = heads x d) and stores its bf16 result straight into
+    the symmetric buffer of an ``AllReduceComm``, whose one kernel then sums the matrix over the ranks in place (in the
+    NVSwitch with ``multimem`` on groups of more than two ranks, by peer loads and stores otherwise; fp32 accumulation).
+    models/crosscoder.py:350-375 of the reference project all-reduces the same ``[batch, d_sae]`` tensor with NCCL.
     """
 
-    def __init__(self, group: dist.ProcessGroup | None, device: torch.device, max_rows: int, n_cols: int):
+    def __init__(self, group: dist.ProcessGroup | None, device: torch.device, max_rows: int, n_cols: int,
+                 use_multicast: bool | None = None):  # fmt: skip
+        self.reduce = AllReduceComm(group, device, max_rows, n_cols, use_multicast)
         self.group, self.device = group, device
-        self.world = dist.get_world_size(group) if group is not None else 1
-        self.rank = dist.get_rank(group) if group is not None else 0
-        assert self.world <= _MAX_PEERS and n_cols % (self.world * 32) == 0, "d_sae must divide into 32-column slabs per rank"
-        self.max_rows, self.n_cols, self.cols = max_rows, n_cols, n_cols // self.world
-        off = _align(FLAG_BYTES)
-        self.slab_off = [off, _align(off + max_rows * self.cols * 4)]
-        self.out_off = _align(self.slab_off[1] + max_rows * self.cols * 4)
-        self.nbytes = _align(self.out_off + max_rows * n_cols * 4)
-        if group is not None and self.world > 1:
-            self.buf, self.handle, ptrs, _ = _rendezvous(self.nbytes, group, device)
-        else:
-            self.buf = torch.zeros(self.nbytes, dtype=torch.uint8, device=device)
-            ptrs = [self.buf.data_ptr()]
-        self.ptrs = ptrs
-        self.table = peer_table(self.world, self.rank, ptrs)
-        self.done_counter = torch.zeros(1, dtype=torch.int32, device=device)
-        self.epoch = 0
-        torch.cuda.synchronize(device)
-        if group is not None and self.world > 1:
-            dist.barrier(group=group)
+        self.world, self.rank = self.reduce.world, self.reduce.rank
+        self.max_rows, self.n_cols = max_rows, n_cols
 
     def head_sum(self, x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, heads: int, rows_per_head: int,
                  out_dtype: torch.dtype = torch.float32, pair: bool = True) -> torch.Tensor:  # fmt: skip
         """``x [M, heads * d]`` bf16, ``w [heads * rows_per_head, d]`` bf16 (feature-major blocks, one per local head),
-        ``bias [N]`` fp32 = this rank's summed encoder biases. Returns ``[M, N]`` in ``out_dtype`` (fp32 or bf16)."""
+        ``bias [N]`` fp32 = this rank's summed encoder biases. Returns ``[M, N]`` in ``out_dtype`` (a copy: the buffer is
+        reused by the call after next)."""
         M = x.shape[0]
-        assert M <= self.max_rows and out_dtype in (torch.float32, torch.bfloat16)
-        ext = K._ext()
-        st = K.status_buffer(self.device)
-        self.epoch += 1
-        slab_off = self.slab_off[self.epoch & 1]
-        ext.head_sum_gemm(x, w, bias, heads, rows_per_head, self.n_cols, [p + slab_off for p in self.ptrs], pair, st, None)
-        ext.comm_signal(self.table, PHASE_HS_REDUCED, self.epoch)
-        ext.comm_headsum_gather(self.table, slab_off, self.out_off, M, self.cols, 0 if out_dtype == torch.float32 else 1,
-                                PHASE_HS_REDUCED, PHASE_HS_GATHERED, self.epoch, self.done_counter, st)  # fmt: skip
-        ext.comm_wait(self.table, PHASE_HS_GATHERED, self.epoch, st)
-        n = M * self.n_cols * out_dtype.itemsize
-        return self.buf[self.out_off : self.out_off + n].view(out_dtype).view(M, self.n_cols).clone()
+        assert M <= self.max_rows
+        P = self.reduce.matrix(M)
+        K._ext().head_sum_gemm(x, w, bias, heads, rows_per_head, self.n_cols, pair, K.status_buffer(self.device), P)
+        if self.world > 1:
+            P = self.reduce.all_reduce(M)
+        return P.to(out_dtype, copy=True)

@@ -236,7 +236,7 @@ def test_sparse_decode_autograd_matches_dense():
 
 @pytest.mark.parametrize("M,heads,d,N,pair", [(256, 3, 128, 1024, True), (128, 2, 64, 256, False), (384, 1, 256, 4096, True), (200, 4, 64, 512, True)])
 def test_head_sum_gemm_single_rank(M, heads, d, N, pair):
-    """K-concatenated head sum + reduction epilogue + gather on one rank (the slab owner is this GPU)."""
+    """K-concatenated head sum on one rank: the bf16 result in the communicator's buffer against an fp32 product."""
     from language_model_saes_b200.parallel.symm import HeadSumComm
 
     dev = torch.device("cuda")
@@ -247,10 +247,10 @@ def test_head_sum_gemm_single_rank(M, heads, d, N, pair):
     bias = torch.randn(N, device=dev)
     comm = HeadSumComm(None, dev, max_rows=M, n_cols=N)
     want = bias + sum(x[:, h * d : (h + 1) * d].float() @ w[h * rows_per_head : h * rows_per_head + N].float().T for h in range(heads))
-    for call in range(3):  # both slabs and the cleared slab of the first call
+    for call in range(3):
         got = comm.head_sum(x, w, bias, heads, rows_per_head, torch.float32, pair=pair)
         K.check_status(dev)
-        assert torch.allclose(got, want, atol=2e-3, rtol=2e-3), (call, float((got - want).abs().max()))
+        assert torch.allclose(got, want, atol=2e-2, rtol=8e-3), (call, float((got - want).abs().max()))  # bf16 store
     got16 = comm.head_sum(x, w, bias, heads, rows_per_head, torch.bfloat16, pair=pair)
     assert torch.allclose(got16.float(), want, atol=5e-2, rtol=2e-2)
 

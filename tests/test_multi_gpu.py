@@ -332,19 +332,23 @@ def test_peer_broadcast_of_masked_cast_rows_and_cached_loader():
     mesh = build_mesh("cuda", (1, 2), ("data", "model"))
     group = mesh.get_group("model")
     n, d = 3000, 512
-    comm = BroadcastComm(group, dev, max_rows=n, max_row_bytes=d * 4)
     g = torch.Generator(device="cpu").manual_seed(5)
-    for call in range(5):  # both landing zones, their re-use, and both ranks as the sender
-        src = call % 2
-        rows_cpu = torch.randn(n - 100 * call, d, generator=g)
-        keep_cpu = torch.rand(n - 100 * call, generator=g) > 0.25
-        use_mask, out_dtype = call % 3 != 2, (torch.bfloat16 if call % 2 == 0 else torch.float32)
-        rows = rows_cpu.to(dev) if rank == src else None
-        keep = keep_cpu.to(dev) if (rank == src and use_mask) else None
-        got = comm.broadcast_rows(src, d, out_dtype, rows, keep)
-        K.check_status(dev)
-        want = (rows_cpu[keep_cpu] if use_mask else rows_cpu).to(out_dtype).to(dev)
-        assert torch.equal(got, want), (call, got.shape, want.shape)
+    for use_mc in (False, True):  # peer stores, then one store per 16 bytes through the NVSwitch multicast mapping
+        comm = BroadcastComm(group, dev, max_rows=n, max_row_bytes=d * 4, use_multicast=use_mc)
+        if use_mc and not comm.use_multicast:
+            print("no multicast mapping for this group: the multimem variant is not exercised here")
+            continue
+        for call in range(5):  # both landing zones, their re-use, and both ranks as the sender
+            src = call % 2
+            rows_cpu = torch.randn(n - 100 * call, d, generator=g)
+            keep_cpu = torch.rand(n - 100 * call, generator=g) > 0.25
+            use_mask, out_dtype = call % 3 != 2, (torch.bfloat16 if call % 2 == 0 else torch.float32)
+            rows = rows_cpu.to(dev) if rank == src else None
+            keep = keep_cpu.to(dev) if (rank == src and use_mask) else None
+            got = comm.broadcast_rows(src, d, out_dtype, rows, keep)
+            K.check_status(dev)
+            want = (rows_cpu[keep_cpu] if use_mask else rows_cpu).to(out_dtype).to(dev)
+            assert torch.equal(got, want), (use_mc, call, got.shape, want.shape)
 
     # the cached-activation loader: rank 0 of the model group reads, rank 1 receives the same records
     root = Path(tempfile.gettempdir()) / "lmsae_peer_bcast_cache"
@@ -370,7 +374,7 @@ def test_peer_broadcast_of_masked_cast_rows_and_cached_loader():
 
 @needs2
 @distributed_test(nproc_per_node=2, backend="nccl")
-def test_head_parallel_crosscoder_sums_pre_activations_in_the_gemm_epilogue():
+def test_head_parallel_crosscoder_sums_pre_activations_with_the_all_reduce_kernel():
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     from language_model_saes_b200.models.crosscoder import Crosscoder, CrosscoderConfig
     from language_model_saes_b200.ops import sae_kernels as K
@@ -393,10 +397,10 @@ def test_head_parallel_crosscoder_sums_pre_activations_in_the_gemm_epilogue():
     want = local.clone()
     dist.all_reduce(want)
     comm = HeadSumComm(group, dev, max_rows=M, n_cols=N)
-    for call in range(4):
+    for call in range(4):  # both buffers twice; the ranks' bf16 partial results are summed in fp32 and stored as bf16
         got = comm.head_sum(x, w, bias, heads, N, torch.float32)
         K.check_status(dev)
-        assert torch.allclose(got, want, atol=3e-3, rtol=3e-3), (call, float((got - want).abs().max()))
+        assert torch.allclose(got, want, atol=4e-2, rtol=1e-2), (call, float((got - want).abs().max()))
 
     # the model: fused against the all-reduce path, values and gradients
     def make(fused):
@@ -446,6 +450,25 @@ def test_in_place_all_reduce_kernel_and_head_parallel_fused_crosscoder():
     torch.cuda.set_device(dev)
     mesh = build_mesh("cuda", (2, 1, 1), ("head", "data", "model"))
     group = mesh.get_group("head")
+    # the one-kernel all-gather of several tensors (data-parallel row exchange), peer stores and multicast stores
+    from language_model_saes_b200.parallel.symm import DataParallelComm
+
+    for use_mc in (False, True):
+        torch.manual_seed(3 + rank)
+        parts = {"x": torch.randn(96, 64, device=dev).to(torch.bfloat16), "idx": torch.randint(0, 999, (96, 8), device=dev, dtype=torch.int32),
+                 "act": torch.randn(96, 8, device=dev)}  # fmt: skip
+        dpc = DataParallelComm(group, dev, 64, 64, {n_: 2 * v.numel() * v.element_size() for n_, v in parts.items()}, use_multicast=use_mc)
+        if use_mc and not dpc.use_multicast:
+            continue
+        for call in range(3):
+            mine = {n_: (v + call).to(v.dtype) for n_, v in parts.items()}
+            got = dpc.exchange(mine)
+            K.check_status(dev)
+            for n_, v in mine.items():
+                want = [torch.empty_like(v) for _ in range(2)]
+                dist.all_gather(want, v.contiguous())
+                assert torch.equal(got[n_], torch.cat(want)), (use_mc, call, n_)
+
     rows, cols = 1000, 4096
     for use_mc in (False, True):
         comm = AllReduceComm(group, dev, rows, cols, use_multicast=use_mc)
