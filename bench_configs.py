@@ -137,9 +137,11 @@ def run_config3(args, bench) -> None:
                                  lr_scheduler_name="constant", log_frequency=1, skip_metrics_calculation=True, n_checkpoints=0,
                                  exp_result_path=tmp, k_warmup_steps=0, l1_coefficient=None, auxk_coefficient=c["auxk"],
                                  k_aux=c["k_aux"], dead_threshold=10 * B, prefetch_to_device=True)  # fmt: skip
-            tr = Trainer(tcfg)
+            tr = current["trainer"] = Trainer(tcfg)
             tr.fit(sae, stream())
         return tr
+
+    current: dict = {}
 
     # ---- device-timed: batches resident on the device, CUDA events around the timed steps ------------------------
     pool = [h.to(dev) for h in host]
@@ -182,6 +184,23 @@ def run_config3(args, bench) -> None:
     e2e_ms = (time.perf_counter() - wall["t0"]) * 1e3
     final_loss = tr.last_loss
     aux_cap_e2e = tr._fused_aux.capacity if tr._fused_aux is not None else None
+    # ---- where the time goes: a third fit from the same parameters with an event mark after every phase of the step ----
+    phases = None
+    if fused and os.environ.get("LMSAE_BENCH_PHASES", "1") == "1":
+        del tr
+        torch.cuda.empty_cache()
+        init()
+        pool = [h.to(dev) for h in host]
+        tr = fit(lambda i: pool[i % len(pool)], lambda: current["trainer"].fused.start_phase_timing(), W, Ks)
+        pt = tr.fused.phase_times()
+        names = sorted(pt)
+        vals = torch.tensor([pt[n] for n in names], device=dev, dtype=torch.float64)
+        lo = vals.clone()
+        if world > 1:
+            dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        order_ = sorted(range(len(names)), key=lambda i: -float(vals[i]))
+        phases = {names[i]: [round(float(lo[i]), 3), round(float(vals[i]), 3)] for i in order_}
     t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -194,6 +213,7 @@ def run_config3(args, bench) -> None:
             "config": c3_config(world, c), "clocks": clocks,
             "path": "Trainer.fit on the fused kernel path" if fused else "Trainer.fit on the generic autograd path",
             "optimizer_state_sharded_over_replicas": sharded_state, "auxk_dead_capacity": aux_cap, "auxk_dead_capacity_e2e": aux_cap_e2e,
+            **({"phase_ms_min_max_over_ranks": phases} if phases else {}),
             "e2e": {"value": Ks * B / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms / Ks,
                     "h2d_bytes_per_step": B * D * 2 // tp + world * B_l * 9, "d2h_bytes_per_step": 4 * world},
             "gpu_launches": launches, "final_loss": final_loss, "impl": "ours", "package": lm.__name__,

@@ -501,9 +501,16 @@ __device__ __forceinline__ void adam_elem(float& p, float& m, float& v, float g,
 // hide latency). VEC 2 with two CTAs per SM keeps the same number of bytes in flight per SM (twelve 16-byte loads per
 // thread) with half the warps and registers-per-SM to spare: the form that shares the SMs with a concurrently running
 // encoder GEMM of the next step.
-template <int VEC, int MIN_CTAS>
+// SIDES: 3 = both matrices, 1 = decoder side only, 2 = encoder side only (compile-time, so a one-sided launch carries no
+// registers for the other side). One-sided launches serve dictionaries with short rows and several decoder matrices per
+// encoder (cross-layer transcoders): a row is then one chunk, and what bounds the kernel is the chain offsets -> entries
+// -> codes -> gathered rows -> parameters per row. There the parameter and moment loads are issued BEFORE the entry loop
+// (EARLY), so that their trip to HBM overlaps the gathers, which mostly hit L2.
+template <int VEC, int MIN_CTAS, int SIDES>
 __global__ void __launch_bounds__(GA_THREADS, MIN_CTAS)
 sparse_grad_adam_kernel(const GradAdamParams p) {
+  constexpr bool doD = (SIDES & 1) != 0, doE = (SIDES & 2) != 0;
+  constexpr bool EARLY = SIDES != 3;
   __shared__ float s_red[GA_THREADS / 32];
   __shared__ float s_gsq[GA_THREADS / 32];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -513,9 +520,6 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
   // this kernel would consume are stale, so the parameters and moments stay as they are until the host has seen the
   // status word.
   const bool skip = p.status != nullptr && *reinterpret_cast<const volatile int*>(p.status) != 0;
-  // One-sided launches: without WD only the encoder side (W_E^T, b_E) is rebuilt and updated, without WE only the decoder
-  // side. A cross-layer transcoder has several decoder matrices per encoder, so its sides are updated by separate launches.
-  const bool doD = p.WD != nullptr, doE = p.WE != nullptr;
 
   for (int f = p.f_begin + blockIdx.x; f < p.f_end && !skip; f += gridDim.x) {
     const int e0 = p.offsets[f], e1 = p.offsets[f + 1];
@@ -537,13 +541,25 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) gD[v][i] = gE[v][i] = 0.0f;
         if (xr >= 0 && in[v]) {
-          if (doD) {
+          if constexpr (doD) {
             const float4 a = *reinterpret_cast<const float4*>(p.extra_gD + (size_t)xr * p.d + c[v]);
             gD[v][0] = a.x; gD[v][1] = a.y; gD[v][2] = a.z; gD[v][3] = a.w;
           }
-          if (doE) {
+          if constexpr (doE) {
             const float4 b = *reinterpret_cast<const float4*>(p.extra_gE + (size_t)xr * p.d + c[v]);
             gE[v][0] = b.x; gE[v][1] = b.y; gE[v][2] = b.z; gE[v][3] = b.w;
+          }
+        }
+      }
+      float4 w[VEC], m[VEC], vv[VEC], we[VEC], me[VEC], ve[VEC];
+      if constexpr (EARLY) {
+        if (p.update) {
+#pragma unroll
+          for (int v = 0; v < VEC; ++v) {
+            if (in[v]) {
+              if constexpr (doD) { w[v] = ldcs4(p.WD + o[v]); m[v] = ldcs4(p.mD + os[v]); vv[v] = ldcs4(p.vD + os[v]); }
+              if constexpr (doE) { we[v] = ldcs4(p.WE + o[v]); me[v] = ldcs4(p.mE + os[v]); ve[v] = ldcs4(p.vE + os[v]); }
+            }
           }
         }
       }
@@ -558,14 +574,14 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
 #pragma unroll
         for (int v = 0; v < VEC; ++v) {
           if (in[v]) {
-            if (doD) {
+            if constexpr (doD) {
               const uint2 ud = __ldg(reinterpret_cast<const uint2*>(gmat + (size_t)row * p.d + c[v]));
               const float2 d01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ud.x));
               const float2 d23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ud.y));
               gD[v][0] = fmaf(a, d01.x, gD[v][0]); gD[v][1] = fmaf(a, d01.y, gD[v][1]);
               gD[v][2] = fmaf(a, d23.x, gD[v][2]); gD[v][3] = fmaf(a, d23.y, gD[v][3]);
             }
-            if (doE) {
+            if constexpr (doE) {
               const uint2 ux = __ldg(reinterpret_cast<const uint2*>(p.x + (size_t)row * p.d + c[v]));
               const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ux.x));
               const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ux.y));
@@ -589,18 +605,19 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
       }
       if (p.update) {
         // all streams of this chunk step are requested before the first is used (96 bytes in flight per thread and VEC)
-        float4 w[VEC], m[VEC], vv[VEC], we[VEC], me[VEC], ve[VEC];
+        if constexpr (!EARLY) {
 #pragma unroll
-        for (int v = 0; v < VEC; ++v) {
-          if (in[v]) {
-            if (doD) { w[v] = ldcs4(p.WD + o[v]); m[v] = ldcs4(p.mD + os[v]); vv[v] = ldcs4(p.vD + os[v]); }
-            if (doE) { we[v] = ldcs4(p.WE + o[v]); me[v] = ldcs4(p.mE + os[v]); ve[v] = ldcs4(p.vE + os[v]); }
+          for (int v = 0; v < VEC; ++v) {
+            if (in[v]) {
+              if constexpr (doD) { w[v] = ldcs4(p.WD + o[v]); m[v] = ldcs4(p.mD + os[v]); vv[v] = ldcs4(p.vD + os[v]); }
+              if constexpr (doE) { we[v] = ldcs4(p.WE + o[v]); me[v] = ldcs4(p.mE + os[v]); ve[v] = ldcs4(p.vE + os[v]); }
+            }
           }
         }
 #pragma unroll
         for (int v = 0; v < VEC; ++v) {
           if (!in[v]) continue;
-          if (doD) {
+          if constexpr (doD) {
             if (self_scale != 0.0f) {  // (not part of the squared-norm accumulation above: a penalty term's share is small)
               gD[v][0] = fmaf(self_scale, w[v].x, gD[v][0]); gD[v][1] = fmaf(self_scale, w[v].y, gD[v][1]);
               gD[v][2] = fmaf(self_scale, w[v].z, gD[v][2]); gD[v][3] = fmaf(self_scale, w[v].w, gD[v][3]);
@@ -610,19 +627,19 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
             stcs4(p.WD + o[v], w[v]); stcs4(p.mD + os[v], m[v]); stcs4(p.vD + os[v], vv[v]);
             norm_sq += w[v].x * w[v].x + w[v].y * w[v].y + w[v].z * w[v].z + w[v].w * w[v].w;
             uint2 sh; sh.x = pack_bf16x2(w[v].x, w[v].y); sh.y = pack_bf16x2(w[v].z, w[v].w);
-            if (p.n_pub > 0) {
+            if (SIDES == 3 && p.n_pub > 0) {
               for (int q = 0; q < p.n_pub; ++q)
                 *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.pub.base[q] + p.pub_wd_off) + o[v]) = sh;
             } else {
               *reinterpret_cast<uint2*>(p.WD_bf16 + o[v]) = sh;
             }
           }
-          if (doE) {
+          if constexpr (doE) {
             adam_elem(we[v].x, me[v].x, ve[v].x, gE[v][0], p.h); adam_elem(we[v].y, me[v].y, ve[v].y, gE[v][1], p.h);
             adam_elem(we[v].z, me[v].z, ve[v].z, gE[v][2], p.h); adam_elem(we[v].w, me[v].w, ve[v].w, gE[v][3], p.h);
             stcs4(p.WE + o[v], we[v]); stcs4(p.mE + os[v], me[v]); stcs4(p.vE + os[v], ve[v]);
             uint2 sh; sh.x = pack_bf16x2(we[v].x, we[v].y); sh.y = pack_bf16x2(we[v].z, we[v].w);
-            if (p.n_pub > 0) {
+            if (SIDES == 3 && p.n_pub > 0) {
               for (int q = 0; q < p.n_pub; ++q)
                 *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.pub.base[q] + p.pub_we_off) + o[v]) = sh;
             } else {
@@ -639,7 +656,7 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
         float b = p.bE[f], m = p.mbE[f - p.state_f0], v = p.vbE[f - p.state_f0];
         adam_elem(b, m, v, bias_g, p.h);
         p.mbE[f - p.state_f0] = m; p.vbE[f - p.state_f0] = v;
-        if (p.n_pub > 0) {
+        if (SIDES == 3 && p.n_pub > 0) {
           for (int q = 0; q < p.n_pub; ++q) reinterpret_cast<float*>(p.pub.base[q] + p.pub_be_off)[f] = b;
         } else {
           p.bE[f] = b;
@@ -657,7 +674,7 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
         if (lane == 0) {
           if (p.norm_sq_accum != nullptr) {
             p.norm_sq_accum[f] += t;  // one CTA per row and launch: the squared norms of several matrices add up here
-          } else if (p.n_pub > 0) {
+          } else if (SIDES == 3 && p.n_pub > 0) {
             for (int q = 0; q < p.n_pub; ++q) reinterpret_cast<float*>(p.pub.base[q] + p.pub_norm_off)[f] = sqrtf(t);
           } else {
             p.dec_norm[f] = sqrtf(t);
@@ -677,7 +694,9 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
     }
   }
   // published even when the update was skipped, so that the replicas waiting for this rank's rows do not time out too
-  if (p.n_pub > 0 && p.update) signal_peers_when_grid_done(p.pub, kPhaseParams, p.pub_epoch, p.pub_done);
+  if constexpr (SIDES == 3) {
+    if (p.n_pub > 0 && p.update) signal_peers_when_grid_done(p.pub, kPhaseParams, p.pub_epoch, p.pub_done);
+  }
 }
 
 int sparse_grad_adam_launch(const GradAdamParams& p, cudaStream_t stream) {
@@ -689,10 +708,20 @@ int sparse_grad_adam_launch(const GradAdamParams& p, cudaStream_t stream) {
   if (p.state_f0 < 0 || p.state_f0 > p.f_begin) return (int)cudaErrorInvalidValue;
   const int cap = (p.ctas_per_sm >= 1 && p.ctas_per_sm <= 4) ? 148 * p.ctas_per_sm : 148 * 8;
   int blocks = rows < cap ? rows : cap;
-  if (p.ctas_per_sm >= 1 && p.ctas_per_sm <= 2)
-    sparse_grad_adam_kernel<2, 2><<<blocks, GA_THREADS, 0, stream>>>(p);
-  else
-    sparse_grad_adam_kernel<1, 4><<<blocks, GA_THREADS, 0, stream>>>(p);
+  const bool doD = p.WD != nullptr, doE = p.WE != nullptr;
+  if (!doD && !doE) return (int)cudaErrorInvalidValue;
+  if (!(doD && doE) && p.n_pub > 0) return (int)cudaErrorInvalidValue;  // rows are published by two-sided launches only
+  if (doD && doE) {
+    if (p.ctas_per_sm >= 1 && p.ctas_per_sm <= 2)
+      sparse_grad_adam_kernel<2, 2, 3><<<blocks, GA_THREADS, 0, stream>>>(p);
+    else
+      sparse_grad_adam_kernel<1, 4, 3><<<blocks, GA_THREADS, 0, stream>>>(p);
+  } else {
+    // one-sided: half the registers, so five CTAs (rows in flight) fit an SM
+    if (p.ctas_per_sm < 1 || p.ctas_per_sm > 5) blocks = rows < 148 * 5 ? rows : 148 * 5;
+    if (doD) sparse_grad_adam_kernel<1, 5, 1><<<blocks, GA_THREADS, 0, stream>>>(p);
+    else sparse_grad_adam_kernel<1, 5, 2><<<blocks, GA_THREADS, 0, stream>>>(p);
+  }
   return (int)cudaGetLastError();
 }
 

@@ -25,6 +25,10 @@ of the squared error plus, optionally, the ``tanh`` sparsity penalty; Adam on ev
 Restrictions: ``jumprelu`` activation, MSE loss with optional ``tanh`` sparsity loss, Adam, fp32 parameters with bf16
 compute, heads split over the ``head`` mesh dimension only (no ``model`` / ``data`` sharding). A token with more
 candidate features than the list width keeps its first ones by column and is counted in ``list_overflow``.
+
+A JumpReLU ``SparseAutoEncoder`` that reconstructs its own input (models/sae.py:320-375 of the reference project) is the
+one-head case of the same computation (``JumpReLU(pre * ||W_D row||) / ||W_D row||``, the same loss terms), so the step
+takes it too: its parameters are viewed as ``[1, F, d]`` / ``[1, F]`` / ``[1, d]`` without a copy.
 """
 
 from __future__ import annotations
@@ -45,17 +49,25 @@ class FusedCrosscoderStep:
         cfg = cc.cfg
         self.cc = cc
         self.betas, self.eps = betas, eps
+        self.single = cc.W_D.ndim == 2  # a plain SAE: one head, parameters without the head axis
         self.head_size = mesh_dim_size(cc.device_mesh, "head")
         self.head_group = mesh_group(cc.device_mesh, "head")
-        self.H, self.H_l = cfg.n_heads, cc.n_heads_local
-        self.F, self.d = cc.d_sae_local, cfg.d_model
         self.window = float(cfg.jumprelu_threshold_window)
         self.cap = -(-list_width // 8) * 8
         self.jumprelu_lr_factor = jumprelu_lr_factor
-        self.WE = cc.W_E.data.transpose(1, 2)  # [H_l, F, d], contiguous views of the parameters' storage
-        self.WD = cc.W_D.data
+        if self.single:
+            self.H = self.H_l = 1
+            self.F, self.d = cc.W_D.shape[0], cfg.d_model
+            self.WE = cc.W_E.data.t().unsqueeze(0)  # [1, F, d]: views of the parameters' storage
+            self.WD = cc.W_D.data.unsqueeze(0)
+            self.bE, self.bD = cc.b_E.data.unsqueeze(0), cc.b_D.data.unsqueeze(0)
+        else:
+            self.H, self.H_l = cfg.n_heads, cc.n_heads_local
+            self.F, self.d = cc.d_sae_local, cfg.d_model
+            self.WE = cc.W_E.data.transpose(1, 2)  # [H_l, F, d], contiguous views of the parameters' storage
+            self.WD = cc.W_D.data
+            self.bE, self.bD = cc.b_E.data, cc.b_D.data
         assert self.WE.is_contiguous() and self.WD.is_contiguous() and self.WE.dtype == torch.float32
-        self.bE, self.bD = cc.b_E.data, cc.b_D.data
         self.log_theta = cc.activation_function.log_jumprelu_threshold.data
         dev = self.WD.device
         H_l, F, d = self.H_l, self.F, self.d
@@ -77,16 +89,29 @@ class FusedCrosscoderStep:
     @staticmethod
     def supports(cc, trainer_cfg=None) -> tuple[bool, str]:
         from ..models.crosscoder import Crosscoder
+        from ..models.sae import SparseAutoEncoder
 
         cfg = cc.cfg
-        if type(cc) is not Crosscoder:
-            return False, "model is not a Crosscoder"
-        checks = [
+        if type(cc) is SparseAutoEncoder:
+            sae_checks = [
+                (cfg.hook_point_in == cfg.hook_point_out, "the SAE does not reconstruct its own input"),
+                (not cfg.use_glu_encoder, "GLU encoder"),
+                (cfg.sparsity_include_decoder_norm, "activations are not gated by the decoder norms"),
+                (cfg.use_decoder_bias, "no decoder bias"),
+                (mesh_dim_size(cc.device_mesh, "head") == 1 and mesh_dim_size(cc.device_mesh, "sweep") == 1, "head/sweep mesh"),
+            ]  # fmt: skip
+            n_features = cc.W_D.shape[0]
+        elif type(cc) is Crosscoder:
+            sae_checks = []
+            n_features = cc.d_sae_local
+        else:
+            return False, "model is neither a Crosscoder nor a plain SparseAutoEncoder"
+        checks = sae_checks + [
             (cfg.act_fn == "jumprelu", "activation is not jumprelu"),
             (cc.W_D.is_cuda or trainer_cfg is None, "not on a CUDA device"),
             (cfg.dtype == torch.float32, "parameters are not fp32"),
             (cfg.d_model % 64 == 0, "d_model is not a multiple of 64"),
-            (cc.d_sae_local % (max(1, mesh_dim_size(cc.device_mesh, "head")) * 32) == 0, "d_sae does not split into 32-column slabs per head rank"),
+            (n_features % 8 == 0, "d_sae is not a multiple of 8"),
             (mesh_dim_size(cc.device_mesh, "model") == 1 and mesh_dim_size(cc.device_mesh, "data") == 1, "model/data sharding"),
             (not any(hp.fwd_hooks or hp.bwd_hooks for hp in cc.hook_points()), "hooks are attached"),
         ]  # fmt: skip
@@ -225,7 +250,10 @@ class FusedCrosscoderStep:
         names = {"W_E": "W_E", "W_D": "W_D", "b_E": "b_E", "b_D": "b_D", "log_theta": "activation_function.log_jumprelu_threshold"}
         for key, (m, v) in self.state.items():
             tr = (lambda t: t.transpose(1, 2)) if key == "W_E" else (lambda t: t)
-            out[names[key]] = {"exp_avg": tr(m), "exp_avg_sq": tr(v)}
+            if self.single and key != "log_theta":  # logical shapes of the SAE's parameters (no head axis)
+                out[names[key]] = {"exp_avg": tr(m).squeeze(0), "exp_avg_sq": tr(v).squeeze(0)}
+            else:
+                out[names[key]] = {"exp_avg": tr(m), "exp_avg_sq": tr(v)}
         return out
 
     def load_optimizer_state(self, sd: dict) -> None:
@@ -234,6 +262,8 @@ class FusedCrosscoderStep:
         for key, (m, v) in self.state.items():
             if names[key] in sd:
                 src_m, src_v = sd[names[key]]["exp_avg"], sd[names[key]]["exp_avg_sq"]
+                if self.single and key != "log_theta":
+                    src_m, src_v = src_m.unsqueeze(0), src_v.unsqueeze(0)
                 if key == "W_E":
                     src_m, src_v = src_m.transpose(1, 2), src_v.transpose(1, 2)
                 m.copy_(src_m)

@@ -395,12 +395,16 @@ class FusedTopKSAEStep:
 
         self.join()
         G = K.encoder_hidden(x, self.WE_bf16, self.bE, gate=gate)
+        self._mark("encoder_gemm_hidden")
         B = x.shape[0]
         tp_group = self.tp_group if self.tp > 1 else None
         thr, n_ties = S.positive_thresholds(G.view(1, 1, -1), k * B, tp_group, return_remaining=True)
+        self._mark("batch_threshold_select")
         # exactly k * B codes: of the entries equal to the (bf16) threshold only as many as the selection still needs
         cap = -(-self.batch_list_factor * k // 8) * 8
-        return S.threshold_rows_to_sparse(G, thr, gate, n_ties=n_ties, tie_group=tp_group, cap=cap, overflow=self.list_overflow)
+        out = S.threshold_rows_to_sparse(G, thr, gate, n_ties=n_ties, tie_group=tp_group, cap=cap, overflow=self.list_overflow)
+        self._mark("rows_to_code_lists")
+        return out
 
     def step(
         self,
@@ -550,6 +554,7 @@ class FusedTopKSAEStep:
         auxiliary top-k is merged over shards, both reconstructions are summed over them) and with data-parallel
         replicas (dead statistics over the global batch, rows of both gradients exchanged before the update)."""
         self.join()
+        self._mark("begin")
         if self.dp_comm is not None:
             self.dp_comm.wait_params()  # the other replicas' rows of the previous update must have landed in the shadows
         B = x.shape[0]
@@ -557,6 +562,7 @@ class FusedTopKSAEStep:
         grad_scale = 2.0 / n_global
         gate = self.dec_norm if self.use_gate else None
         idx, act = self.encode(x, k)
+        self._mark("merge")
         kw = idx.shape[1]  # width of the main code lists (k, or the fixed list width of a batch-level top-k)
         if self.groups is None or self.groups.entries.numel() < B * self.dp * kw:
             self.groups = K.FeatureGroups(self.F, B * self.dp * kw, x.device)
@@ -588,17 +594,21 @@ class FusedTopKSAEStep:
         wd_dead = self.WD_bf16[order]
         b_dead = self.bE[order]
         g_dead = (gate[order] if gate is not None else torch.ones(cap, device=x.device)) * valid
+        self._mark("dead_statistics_compact_dictionary")
         self.loss_sum.zero_()
         self.aux_sum.zero_()
         xhat = K.sparse_decode(idx, act, self.WD_bf16, None, torch.float32)
+        self._mark("main_decode")
         # The auxiliary codes hold up to k_aux (hundreds of) entries per token, several times the main codes, but all of
         # them index the compact dictionary: products with its [cap, d] matrices are small dense GEMMs, far cheaper than
         # gathering a decoder row per code, so the auxiliary decode and its three gradients are dense over the compact
         # dictionary and only their result rows are handed to the update kernel.
         # (the selection itself: fused into the GEMM epilogue up to 64 codes, else over stored bf16 pre-activations)
         idx_c, act_aux = K.encoder_topk(x, w_dead, b_dead, g_dead, aux.k_aux)
+        self._mark("aux_encoder_topk")
         if self.tp > 1:
             idx_c, act_aux = self._merge_shard_codes(idx_c, act_aux, g_dead, aux.k_aux)
+            self._mark("aux_merge_shards")
         A = torch.zeros(B, cap + 1, dtype=torch.bfloat16, device=x.device)  # dense dead activations (+ one dump column)
         A.scatter_(1, torch.where(idx_c >= 0, idx_c, torch.full_like(idx_c, cap)).long(), act_aux.to(torch.bfloat16))
         A = A[:, :cap]
@@ -607,9 +617,11 @@ class FusedTopKSAEStep:
             both = torch.stack([xhat, aux_rec])
             dist.all_reduce(both, group=self.tp_group)
             xhat, aux_rec = both[0], both[1]
+        self._mark("aux_decode_and_reduce")
         g_main, g_aux = K.auxk_loss_grad(xhat, aux_rec, label, self.bD, row_weight, grad_scale, aux.coefficient, self.loss_sum,
                                          self.aux_sum, alpha_factor=alpha_on)  # fmt: skip
         dact = K.sparse_dact(idx, self.WD_bf16, g_main)
+        self._mark("loss_grad_dact")
         dA = _mm_f32(g_aux, wd_dead.t()) * (A != 0)  # gradient of the dead activations where they were selected
         extra_gD = _mm_f32(A.t(), g_aux)  # d W_D rows of the compact dictionary
         extra_gE = _mm_f32(dA.to(torch.bfloat16).t(), x)  # d W_E^T rows
@@ -620,13 +632,17 @@ class FusedTopKSAEStep:
         row_of = torch.full((self.F,), -1, dtype=torch.int32, device=x.device)
         slots = torch.arange(cap, dtype=torch.int32, device=x.device)
         row_of.scatter_(0, order.long(), torch.where(valid, slots, torch.full_like(slots, -1)))
+        self._mark("aux_gradients")
         sharded = self.dp_comm is not None
         if sharded:
             g = self.dp_comm.exchange({"x": x, "dxhat": g_main, "idx": idx, "act": act, "dact": dact})
             x, g_main, idx, act, dact = g["x"], g["dxhat"], g["idx"], g["act"], g["dact"]
+            self._mark("dp_exchange_rows")
         elif self.dp > 1:
             x, g_main, idx, act, dact = self._gather_rows(x, g_main, idx, act, dact)
+            self._mark("dp_exchange_rows")
         self.groups.build(idx)
+        self._mark("sort_by_feature")
         self.t += 1
         b1, b2 = self.betas
         (mE, vE), (mD, vD), (mb, vb) = self.state["W_E"], self.state["W_D"], self.state["b_E"]
@@ -649,9 +665,11 @@ class FusedTopKSAEStep:
             got_aux = ((row_of[lo:hi] >= 0) & (self.groups.counts[lo:hi] == 0)).sum().float().reshape(1)
             grad_mul = self._clip_factor(sparse, g_bD, clip_grad_norm, extra_fired=got_aux)
         sparse(grad_mul, None, True)
+        self._mark("sparse_grad_adam")
         if self.bD is not None:
             m, v = self.state["b_D"]
             K.adam_flat(self.bD, g_bD, m, v, lr, b1, b2, self.eps, self.t, grad_mul=grad_mul)
+        self._mark("bias_update")
         n_local = B if row_weight is None else row_weight.sum()
         self.last_aux_loss = (self.aux_sum / n_local).squeeze(0)
         return ((self.loss_sum + self.aux_sum) / n_local).squeeze(0)

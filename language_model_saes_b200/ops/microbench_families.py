@@ -24,7 +24,7 @@ from .microbench import _timeit
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default="all", help="all | attn | attn_fwd | batchtopk | batchtopk_step | clt | compact | headsum")
+    ap.add_argument("--case", default="all", help="all | attn | attn_fwd | batchtopk | batchtopk_step | clt | clt_adam | compact | headsum")
     ap.add_argument("--attn-shape", default="4,1024,64,64,128", help="batch,seq,heads,d_qk,d_v of the attention cases")
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
@@ -120,6 +120,34 @@ def main(argv=None):
         t_g = _timeit(lambda: (CK.clt_dact(idx, w16, dy), CK.clt_wgrad(idx, val, dy, L, Fd)), a.iters, a.warmup, flush)
         print(json.dumps({"case": "clt_backward_dact_wgrad", "ms_ours": round(t_g[0], 4)}), flush=True)
         del w16, acts, dy
+
+    if want("clt_adam"):
+        # decoder-side sparse gradient + Adam of a cross-layer transcoder's last target layer: 12 source layers x 24576
+        # features, rows of 768 columns, 64 codes per token and source layer on 2048 tokens (5.3 codes per feature)
+        B, L, Fd, d, k = 2048, 12, 24576, 768, 64
+        F = L * Fd
+        idx = torch.cat([torch.randint(0, Fd, (B, k), device=dev, dtype=torch.int32) + l * Fd for l in range(L)], dim=1).contiguous()
+        act = torch.rand(B, L * k, device=dev)
+        dy = torch.randn(B, d, device=dev).to(torch.bfloat16)
+        W = torch.randn(F, d, device=dev) / d**0.5
+        m, v = torch.zeros_like(W), torch.zeros_like(W)
+        W16 = W.to(torch.bfloat16)
+        acc = torch.zeros(F, device=dev)
+        groups = K.FeatureGroups(F, idx.numel(), dev).build(idx)
+        step = [0]
+
+        def decoder_side():
+            step[0] += 1
+            K.sparse_grad_adam(groups, act, act, None, dy, W, m, v, W16, None, None, None, None, None, None, None, None, None, None,
+                               2e-4, 0.9, 0.999, 1e-8, step[0], True, norm_sq_accum=acc)  # fmt: skip
+
+        t = _timeit(decoder_side, a.iters, a.warmup, flush)
+        gbs = F * d * 26 / t[0] / 1e6
+        print(json.dumps({"case": "sparse_grad_adam_decoder_side_294912x768_5codes_per_feature", "ms_ours": round(t[0], 4), "gbs": round(gbs, 1),
+                          "fraction_of_measured_copy": round(gbs / 6547.2, 3), "clocks": sampler[0].stop()}), flush=True)  # fmt: skip
+        sampler[0] = ClockSampler(torch.cuda.current_device())
+        sampler[0].start()
+        del W, m, v, W16
 
     if want("compact"):
         n, d = 1 << 20, 1024

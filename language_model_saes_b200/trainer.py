@@ -503,12 +503,14 @@ class Trainer:
             ok_clt, why_clt = (False, "disabled") if not self.cfg.use_fused_kernels else FusedCLTStep.supports(sae, self.cfg)
             if ok_cc:
                 self.fused = FusedCrosscoderStep(sae, betas=self.cfg.betas, jumprelu_lr_factor=self.cfg.jumprelu_lr_factor)
-                logger.info("Training the crosscoder on the fused sm_100a kernel path")
+                logger.info(f"Training the JumpReLU {type(sae).__name__} on the fused sm_100a kernel path")
             elif ok_clt:
                 self.fused = FusedCLTStep(sae, betas=self.cfg.betas)
                 logger.info("Training the cross-layer transcoder on the fused sm_100a kernel path")
             else:
                 reason = {"Crosscoder": why_cc, "CrossLayerTranscoder": why_clt}.get(type(sae).__name__, why)
+                if type(sae).__name__ == "SparseAutoEncoder" and sae.cfg.act_fn == "jumprelu":
+                    reason = why_cc
                 logger.info(f"Training on the generic autograd path ({reason})")
         groups = []
         for g in sae.get_parameters():
@@ -974,7 +976,7 @@ class Trainer:
         if mask is not None and not batch.get("_mask_all", None if mask.device.type == "cpu" else bool(mask.all())):
             raise NotImplementedError("the fused crosscoder path trains on unmasked tokens; set use_fused_kernels=False for masked batches")
         cols = []
-        for hp in sae.local_hook_points():
+        for hp in sae.local_hook_points() if hasattr(sae, "local_hook_points") else [sae.cfg.hook_point_in]:
             raw = batch[hp]
             assert raw.ndim == 2, "the fused path trains on [tokens, d_model] activations"
             if sae.cfg.norm_activation == "dataset-wise":

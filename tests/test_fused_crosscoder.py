@@ -70,6 +70,60 @@ def test_fused_crosscoder_step_matches_autograd(dev, l1):
         assert float((a - b).abs().mean()) < (0.25 if dev == "cuda" else 0.05) * float(moved) + 1e-7, name
 
 
+@pytest.mark.parametrize("dev", DEVICES)
+@pytest.mark.parametrize("l1", [0.0, 3e-2])
+def test_jumprelu_sae_is_the_one_head_case_of_the_fused_step(dev, l1):
+    """A JumpReLU ``SparseAutoEncoder`` on the same step (parameters viewed with a head axis of one) against autograd on the
+    model: losses, every parameter after a few Adam steps, and the optimizer state in the model's parameter shapes."""
+    from language_model_saes_b200.models.sae import SAEConfig, SparseAutoEncoder
+
+    d, F, B, lr, steps = 64, 512, 256, 1e-3, 4
+
+    def make():
+        torch.manual_seed(0)
+        cfg = SAEConfig(hook_point_in="h", hook_point_out="h", d_model=d, expansion_factor=F / d, act_fn="jumprelu", device=dev,
+                        dtype=torch.float32, norm_activation="inference")  # fmt: skip
+        m = SparseAutoEncoder(cfg)
+        m.init_parameters(encoder_uniform_bound=0.2, decoder_uniform_bound=0.2, init_log_jumprelu_threshold_value=-0.5)
+        m.set_decoder_to_fixed_norm(1.0, True)
+        m.init_encoder_with_decoder_transpose()
+        with torch.no_grad():
+            m.b_E.add_(0.02 * torch.randn_like(m.b_E))
+            m.b_D.add_(0.02 * torch.randn_like(m.b_D))
+            m.activation_function.log_jumprelu_threshold.add_(0.1 * torch.randn_like(m.activation_function.log_jumprelu_threshold))
+        return m
+
+    ref, fused_model = make(), make()
+    ok, why = FusedCrosscoderStep.supports(fused_model)
+    assert ok, why
+    engine = FusedCrosscoderStep(fused_model, list_width=F)
+    g = torch.Generator(device=dev).manual_seed(1)
+    basis = torch.randn(8, d, device=dev, generator=g)
+    opt = torch.optim.Adam(ref.parameters(), lr=lr)
+    tokens = torch.zeros(B, dtype=torch.long, device=dev)
+    ref_losses, fused_losses = [], []
+    for _ in range(steps):
+        x = torch.randn(B, 8, device=dev, generator=g) @ basis + 0.3 * torch.randn(B, d, device=dev, generator=g)
+        x = (x * (d**0.5 / x.norm(dim=-1).mean())).to(torch.bfloat16)
+        opt.zero_grad()
+        with torch.autocast(dev, dtype=torch.bfloat16, enabled=dev == "cuda"):
+            out = ref.compute_loss({"h": x.float(), "tokens": tokens}, sparsity_loss_type="tanh" if l1 else None, l1_coefficient=l1)
+        out["loss"].backward()
+        opt.step()
+        ref_losses.append(float(out["loss"].detach()))
+        fused_losses.append(float(engine.step(x.unsqueeze(1), lr, l1_coefficient=l1)))
+    r, f = torch.tensor(ref_losses), torch.tensor(fused_losses)
+    assert torch.allclose(r, f, rtol=3e-2 if dev == "cuda" else 2e-3), (ref_losses, fused_losses)
+    start = dict(make().named_parameters())
+    for name, a in ref.named_parameters():
+        b = dict(fused_model.named_parameters())[name].detach().float()
+        moved = (a.detach().float() - start[name].detach().float()).abs().mean()
+        assert float((a.detach().float() - b).abs().mean()) < (0.25 if dev == "cuda" else 0.05) * float(moved) + 1e-7, name
+    state = engine.optimizer_state()
+    for name, p in fused_model.named_parameters():
+        assert state[name]["exp_avg"].shape == p.shape, name
+
+
 def test_fused_crosscoder_selection_is_the_union_over_heads_cpu():
     """A head's codes are exactly its own JumpReLU outputs: the union list only adds zero entries."""
     m = _model("cpu", 2, 32, 128)
@@ -117,4 +171,45 @@ def test_trainer_picks_the_fused_crosscoder_path_and_the_loss_goes_down():
         tr._fused_iteration = spy
         tr.fit(m, stream())
         assert type(tr.fused).__name__ == "FusedCrosscoderStep"
+    assert len(losses) == steps and all(l == l for l in losses) and sum(losses[-5:]) < sum(losses[:5]), losses
+
+
+@pytest.mark.gpu
+def test_trainer_trains_a_jumprelu_sae_on_the_fused_path():
+    import tempfile
+
+    from language_model_saes_b200.models.sae import SAEConfig, SparseAutoEncoder
+    from language_model_saes_b200.trainer import Trainer, TrainerConfig
+
+    d, F, B, steps = 64, 2048, 512, 30
+    torch.manual_seed(0)
+    cfg = SAEConfig(hook_point_in="h", hook_point_out="h", d_model=d, expansion_factor=F / d, act_fn="jumprelu", device="cuda",
+                    dtype=torch.float32)  # fmt: skip
+    m = SparseAutoEncoder(cfg)
+    m.init_parameters(encoder_uniform_bound=0.2, decoder_uniform_bound=0.2, init_log_jumprelu_threshold_value=0.3)
+    m.set_decoder_to_fixed_norm(1.0, True)
+    m.init_encoder_with_decoder_transpose()
+    m.set_dataset_average_activation_norm({"h": d**0.5})
+    g = torch.Generator(device="cuda").manual_seed(1)
+    basis = torch.randn(12, d, device="cuda", generator=g)
+
+    def stream():
+        for _ in range(steps + 1):
+            x = torch.randn(B, 12, device="cuda", generator=g) @ basis + 0.05 * torch.randn(B, d, device="cuda", generator=g)
+            yield {"h": (x * (d**0.5 / x.norm(dim=-1).mean())).to(torch.bfloat16), "tokens": torch.zeros(B, dtype=torch.long, device="cuda")}
+
+    losses = []
+    with tempfile.TemporaryDirectory() as tmp:
+        tr = Trainer(TrainerConfig(total_training_tokens=steps * B, lr=2e-3, lr_warm_up_steps=2, log_frequency=10**6, n_checkpoints=0,
+                                   exp_result_path=tmp, skip_metrics_calculation=True, l1_coefficient=1e-3, sparsity_loss_type="tanh"))  # fmt: skip
+        orig = tr._fused_iteration
+
+        def spy(*a, **kw):
+            out = orig(*a, **kw)
+            losses.append(float(out))
+            return out
+
+        tr._fused_iteration = spy
+        tr.fit(m, stream())
+        assert type(tr.fused).__name__ == "FusedCrosscoderStep" and tr.fused.single
     assert len(losses) == steps and all(l == l for l in losses) and sum(losses[-5:]) < sum(losses[:5]), losses
