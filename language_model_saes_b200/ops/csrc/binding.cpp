@@ -658,11 +658,14 @@ Tensor threshold_mask(const Tensor& x, const Tensor& thr, int64_t A, int64_t S, 
   return out;
 }
 
-// x [B, N] -> idx / val [B, cap] (both optional: count only) and nnz [B] (optional)
+// x [B, N] -> idx / val [B, cap] (both optional: count only) and nnz [B] (optional). seg_counts int32 [B, 8, 2]
+// (optional): written by a counting call, read by a compacting call of the same matrix and thresholds, which then
+// skips its own counting pass.
 void row_compact(const Tensor& x, const c10::optional<Tensor>& idx, const c10::optional<Tensor>& val,
                  const c10::optional<Tensor>& nnz, const c10::optional<Tensor>& thr, const c10::optional<Tensor>& col_div,
                  const c10::optional<Tensor>& ties, const c10::optional<Tensor>& tie_quota,
-                 const c10::optional<Tensor>& col_thr) {
+                 const c10::optional<Tensor>& col_thr, const c10::optional<Tensor>& seg_counts) {
+  if (seg_counts.has_value()) { CHECK_T(*seg_counts, torch::kInt32); TORCH_CHECK(seg_counts->numel() == x.size(0) * 16, "seg_counts must be [B, 8, 2]"); }
   if (col_thr.has_value()) { CHECK_T(*col_thr, torch::kFloat32); TORCH_CHECK(col_thr->numel() == x.size(1) && !thr.has_value(), "col_thr: one per column, instead of thr"); }
   if (ties.has_value()) { CHECK_T(*ties, torch::kInt32); TORCH_CHECK(ties->numel() == x.size(0) && thr.has_value(), "ties: [B], with thr"); }
   if (tie_quota.has_value()) { CHECK_T(*tie_quota, torch::kInt32); TORCH_CHECK(tie_quota->numel() == x.size(0) && thr.has_value(), "tie_quota: [B], with thr"); }
@@ -685,7 +688,7 @@ void row_compact(const Tensor& x, const c10::optional<Tensor>& idx, const c10::o
   check_cuda(lmsae::row_compact_launch(dtype_code(x), x.data_ptr(), (int)x.size(0), x.size(1), cap, opt_ptr<int>(idx),
                                        opt_ptr<float>(val), opt_ptr<int>(nnz), opt_ptr<float>(thr), opt_ptr<float>(col_div),
                                        opt_ptr<int>(ties), opt_ptr<int>(tie_quota), opt_ptr<float>(col_thr),
-                                       at::cuda::getCurrentCUDAStream()),
+                                       opt_ptr<int>(seg_counts), at::cuda::getCurrentCUDAStream()),
              "row_compact launch");
 }
 

@@ -185,7 +185,7 @@ int threshold_mask_launch(int dtype, const void* x, const float* thr, long long 
                           cudaStream_t stream);
 int row_compact_launch(int dtype, const void* x, int B, long long N, int cap, int* idx, float* val, int* nnz,
                        const float* thr, const float* col_div, int* ties, const int* tie_quota, const float* col_thr,
-                       cudaStream_t stream);
+                       int* seg_counts, cudaStream_t stream);
 int jumprelu_window_grad_launch(const __nv_bfloat16* G, const __nv_bfloat16* S, int B, int F, const float* n,
                                 const float* theta, float window, float add_per_hit, float* dtheta, cudaStream_t stream);
 int gather_rows_cast_launch(int in_dtype, int out_dtype, const void* src, const int* keep, const int* pos, long long n,

@@ -264,144 +264,175 @@ struct RowVec<__nv_bfloat16> {
   }
 };
 
-// One CTA per row (grid-stride); a thread takes 16 bytes of the row per step, so a step covers 256 x 16 bytes.
+// One CTA per row (grid-stride). Every warp owns one contiguous eighth of the row and streams it with RC_U 16-byte
+// loads in flight per lane; nothing in the streaming loops synchronises the block.
 //   Without thr an entry is kept when x != 0. With thr (> 0): entries above *thr are kept; entries EQUAL to it are
 //   kept too, unless tie_quota is given, in which case only the first tie_quota[row] of them (in column order) are:
 //   that is how a caller keeps an exact number of entries when the threshold value repeats.
-//   A counting call (idx == nullptr) is a pure streaming pass; with `ties` it reports the two kinds separately
-//   (nnz = entries above the threshold, ties = entries equal to it).
-//   A compacting call finds every kept entry's slot with one block-wide scan per step (a thread's entries are
-//   consecutive columns, threads are in column order), so the list comes out in ascending column order.
+//   A counting call (idx == nullptr) is one streaming pass; with `ties` it reports the two kinds separately
+//   (nnz = entries above the threshold, ties = entries equal to it); with `seg_counts` it also stores every warp
+//   segment's two counts ([B, 8, 2]).
+//   A compacting call needs those per-segment counts to know where a warp's entries start in the list: it takes them
+//   from `seg_counts` when a counting call of the same matrix and threshold left them there, and counts them itself
+//   in a first pass over the row otherwise. The second pass finds an entry's slot with warp-level scans (lanes hold
+//   consecutive columns, warps consecutive segments), so the list comes out in ascending column order.
 //   With col_div the stored value is x / col_div[column] (gated pre-activation back to the activation).
 //   With col_thr (one threshold per column, instead of thr) an entry is kept when x > col_thr[column]: the JumpReLU
 //   selection of pre-activations against per-feature thresholds.
+constexpr int RC_U = 4;
+
+struct RowPredicate {
+  bool has_thr, split_ties;
+  float t;
+  const float* col_thr;
+};
+
+// bit i of the two masks: element c + i is kept outright / equals the threshold
+template <int V>
+__device__ __forceinline__ void rc_classify(const float (&f)[V], long long c, long long end, const RowPredicate& q,
+                                            unsigned& m_strict, unsigned& m_tie) {
+  m_strict = m_tie = 0;
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    const bool in = c + i < end;
+    if (q.split_ties) {
+      m_strict |= (unsigned)(in && f[i] > q.t) << i;
+      m_tie |= (unsigned)(in && f[i] == q.t) << i;
+    } else if (q.col_thr != nullptr) {
+      m_strict |= (unsigned)(in && f[i] > q.col_thr[in ? c + i : 0]) << i;
+    } else {
+      m_strict |= (unsigned)(in && (q.has_thr ? (f[i] >= q.t) : (f[i] != 0.0f))) << i;
+    }
+  }
+}
+
 template <typename T>
-__global__ void __launch_bounds__(RC_THREADS)
+__device__ __forceinline__ void rc_load(const T* xr, long long c, long long end, bool vec_ok, float (&f)[RowVec<T>::V]) {
+  constexpr int V = RowVec<T>::V;
+  if (c >= end) {
+#pragma unroll
+    for (int i = 0; i < V; ++i) f[i] = 0.0f;
+  } else if (vec_ok) {
+    RowVec<T>::load(xr + c, f);
+  } else {
+#pragma unroll
+    for (int i = 0; i < V; ++i) f[i] = c + i < end ? to_float<T>(xr[c + i]) : 0.0f;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(RC_THREADS, 3)
 row_compact_kernel(const T* __restrict__ x, int B, long long N, int cap, int* __restrict__ idx, float* __restrict__ val,
                    int* __restrict__ nnz, const float* __restrict__ thr, const float* __restrict__ col_div,
-                   int* __restrict__ ties, const int* __restrict__ tie_quota, const float* __restrict__ col_thr) {
+                   int* __restrict__ ties, const int* __restrict__ tie_quota, const float* __restrict__ col_thr,
+                   int* __restrict__ seg_counts) {
   constexpr int V = RowVec<T>::V;
   constexpr int NW = RC_THREADS / 32;
-  const bool has_thr = thr != nullptr;
-  const float t = has_thr ? *thr : 0.0f;
-  const bool split_ties = has_thr && (ties != nullptr || tie_quota != nullptr);
+  RowPredicate q;
+  q.has_thr = thr != nullptr;
+  q.t = q.has_thr ? *thr : 0.0f;
+  q.split_ties = q.has_thr && (ties != nullptr || tie_quota != nullptr);
+  q.col_thr = col_thr;
   const bool vec_ok = (N % V == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0);
   __shared__ int s_a[NW], s_b[NW];
-  __shared__ int s_base, s_tie_base;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const long long step = (long long)RC_THREADS * V;
+  // a warp's segment: an eighth of the row, rounded up to whole vectors
+  const long long seg_len = (((N + NW - 1) / NW) + V - 1) / V * V;
+  const long long s0 = min(N, (long long)warp * seg_len), s1 = min(N, s0 + seg_len);
+  const long long stride = 32LL * V * RC_U;
+  const bool counting = idx == nullptr;
 
   for (int row = blockIdx.x; row < B; row += gridDim.x) {
     const T* xr = x + (size_t)row * N;
-    if (idx == nullptr) {
-      // ---- counting: no ordering needed
-      int n_keep = 0, n_tie = 0;
-      for (long long c = (long long)threadIdx.x * V; c < N; c += step) {
-        float f[V];
-        if (vec_ok) {
-          RowVec<T>::load(xr + c, f);
-        } else {
+    int n_s = 0, n_t = 0;
+    if (counting || seg_counts == nullptr) {
+      // ---- pass 1: this segment's counts
+      for (long long c0 = s0; c0 < s1; c0 += stride) {
+        float f[RC_U][V];
 #pragma unroll
-          for (int i = 0; i < V; ++i) f[i] = c + i < N ? to_float<T>(xr[c + i]) : 0.0f;
-        }
+        for (int u = 0; u < RC_U; ++u) rc_load<T>(xr, c0 + ((long long)u * 32 + lane) * V, s1, vec_ok, f[u]);
 #pragma unroll
-        for (int i = 0; i < V; ++i) {
-          if (split_ties) {
-            n_keep += f[i] > t;
-            n_tie += (f[i] == t) && (c + i < N);
-          } else if (col_thr != nullptr) {
-            n_keep += (c + i < N) && f[i] > col_thr[c + i];
-          } else {
-            n_keep += has_thr ? (f[i] >= t) : (f[i] != 0.0f);
-          }
+        for (int u = 0; u < RC_U; ++u) {
+          unsigned ms, mt;
+          rc_classify<V>(f[u], c0 + ((long long)u * 32 + lane) * V, s1, q, ms, mt);
+          n_s += __popc(ms);
+          n_t += __popc(mt);
         }
       }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) {
-        n_keep += __shfl_xor_sync(0xffffffffu, n_keep, o);
-        n_tie += __shfl_xor_sync(0xffffffffu, n_tie, o);
+        n_s += __shfl_xor_sync(0xffffffffu, n_s, o);
+        n_t += __shfl_xor_sync(0xffffffffu, n_t, o);
       }
-      __syncthreads();
-      if (lane == 0) { s_a[warp] = n_keep; s_b[warp] = n_tie; }
-      __syncthreads();
+      if (counting && seg_counts != nullptr && lane == 0) {
+        seg_counts[((size_t)row * NW + warp) * 2] = n_s;
+        seg_counts[((size_t)row * NW + warp) * 2 + 1] = n_t;
+      }
+    } else {
+      n_s = seg_counts[((size_t)row * NW + warp) * 2];
+      n_t = seg_counts[((size_t)row * NW + warp) * 2 + 1];
+    }
+    __syncthreads();  // (the previous row's readers of s_a / s_b are done)
+    if (lane == 0) { s_a[warp] = n_s; s_b[warp] = n_t; }
+    __syncthreads();
+    int s_before = 0, t_before = 0, s_total = 0, t_total = 0;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) {
+      if (w < warp) { s_before += s_a[w]; t_before += s_b[w]; }
+      s_total += s_a[w];
+      t_total += s_b[w];
+    }
+    if (counting) {
       if (threadIdx.x == 0) {
-        int a = 0, b = 0;
-        for (int w = 0; w < NW; ++w) { a += s_a[w]; b += s_b[w]; }
-        if (nnz != nullptr) nnz[row] = a;
-        if (ties != nullptr) ties[row] = b;
+        if (nnz != nullptr) nnz[row] = s_total;
+        if (ties != nullptr) ties[row] = t_total;
       }
       continue;
     }
-    // ---- compaction
-    __syncthreads();
-    if (threadIdx.x == 0) { s_base = 0; s_tie_base = 0; }
-    __syncthreads();
+    // ---- pass 2: compaction of this segment; S_seen / T_seen: strict entries and ties of the row before the next vector
     const int quota = tie_quota != nullptr ? tie_quota[row] : 0x7fffffff;
-    for (long long c0 = 0; c0 < N; c0 += step) {
-      const long long c = c0 + (long long)threadIdx.x * V;
-      float f[V];
-      if (c < N && vec_ok) {
-        RowVec<T>::load(xr + c, f);
-      } else {
+    int S_seen = s_before, T_seen = t_before;
+    if (n_s + n_t > 0) {
+      for (long long c0 = s0; c0 < s1; c0 += stride) {
+        float f[RC_U][V];
 #pragma unroll
-        for (int i = 0; i < V; ++i) f[i] = c + i < N ? to_float<T>(xr[c + i]) : 0.0f;
-      }
-      unsigned m_strict = 0, m_tie = 0;  // bit i: element i is above the threshold / equal to it
+        for (int u = 0; u < RC_U; ++u) rc_load<T>(xr, c0 + ((long long)u * 32 + lane) * V, s1, vec_ok, f[u]);
 #pragma unroll
-      for (int i = 0; i < V; ++i) {
-        const bool in = c + i < N;
-        if (split_ties) {
-          m_strict |= (unsigned)(in && f[i] > t) << i;
-          m_tie |= (unsigned)(in && f[i] == t) << i;
-        } else if (col_thr != nullptr) {
-          m_strict |= (unsigned)(in && f[i] > col_thr[in ? c + i : 0]) << i;
-        } else {
-          m_strict |= (unsigned)(in && (has_thr ? (f[i] >= t) : (f[i] != 0.0f))) << i;
-        }
-      }
-      // block-wide exclusive scan of (strict, tie) counts in thread (= column) order
-      const int n_s = __popc(m_strict), n_t = __popc(m_tie);
-      int inc_s = n_s, inc_t = n_t;
+        for (int u = 0; u < RC_U; ++u) {
+          const long long c = c0 + ((long long)u * 32 + lane) * V;
+          unsigned ms, mt;
+          rc_classify<V>(f[u], c, s1, q, ms, mt);
+          if (__ballot_sync(0xffffffffu, (ms | mt) != 0u) == 0u) continue;  // nothing kept in these 32 vectors
+          const int mine = __popc(ms) | (__popc(mt) << 16);  // both counts in one word (at most 256 each per warp)
+          int inc = mine;
 #pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int a = __shfl_up_sync(0xffffffffu, inc_s, o), b = __shfl_up_sync(0xffffffffu, inc_t, o);
-        if (lane >= o) { inc_s += a; inc_t += b; }
-      }
-      if (lane == 31) { s_a[warp] = inc_s; s_b[warp] = inc_t; }
-      __syncthreads();
-      int s_before = inc_s - n_s, t_before = inc_t - n_t, s_total = 0, t_total = 0;
-#pragma unroll
-      for (int w = 0; w < NW; ++w) {
-        if (w < warp) { s_before += s_a[w]; t_before += s_b[w]; }
-        s_total += s_a[w];
-        t_total += s_b[w];
-      }
-      const int base = s_base, tie_base = s_tie_base;
-      // ties granted so far = min(ties seen so far, quota), in closed form for any prefix
-      int tie_rank = tie_base + t_before;
-      int slot = base + s_before + (min(tie_rank, quota) - min(tie_base, quota));
-      // `base` already holds the ties granted in earlier steps
-#pragma unroll
-      for (int i = 0; i < V; ++i) {
-        const bool strict = (m_strict >> i) & 1u, tie = (m_tie >> i) & 1u;
-        const bool keep = strict || (tie && tie_rank < quota);
-        tie_rank += tie;
-        if (keep) {
-          if (slot < cap) {
-            idx[(size_t)row * cap + slot] = (int)(c + i);
-            val[(size_t)row * cap + slot] = col_div != nullptr ? f[i] / col_div[c + i] : f[i];
+          for (int o = 1; o < 32; o <<= 1) {
+            const int a = __shfl_up_sync(0xffffffffu, inc, o);
+            if (lane >= o) inc += a;
           }
-          ++slot;
+          const int tot = __shfl_sync(0xffffffffu, inc, 31);
+          const int exc = inc - mine;
+          int tie_rank = T_seen + (exc >> 16);
+          int slot = S_seen + (exc & 0xffff) + min(tie_rank, quota);
+#pragma unroll
+          for (int i = 0; i < V; ++i) {
+            const bool strict = (ms >> i) & 1u, tie = (mt >> i) & 1u;
+            const bool keep = strict || (tie && tie_rank < quota);
+            tie_rank += tie;
+            if (keep) {
+              if (slot < cap) {
+                idx[(size_t)row * cap + slot] = (int)(c + i);
+                val[(size_t)row * cap + slot] = col_div != nullptr ? f[u][i] / col_div[c + i] : f[u][i];
+              }
+              ++slot;
+            }
+          }
+          S_seen += tot & 0xffff;
+          T_seen += tot >> 16;
         }
-      }
-      __syncthreads();
-      if (threadIdx.x == 0) {
-        s_base = base + s_total + (min(tie_base + t_total, quota) - min(tie_base, quota));
-        s_tie_base = tie_base + t_total;
       }
     }
-    __syncthreads();
-    const int count = s_base;
+    const int count = s_total + min(t_total, quota);
     if (threadIdx.x == 0 && nnz != nullptr) nnz[row] = count;
     for (int j = count + threadIdx.x; j < cap; j += RC_THREADS) {
       idx[(size_t)row * cap + j] = -1;
@@ -512,18 +543,18 @@ int threshold_mask_launch(int dtype, const void* x, const float* thr, long long 
 
 int row_compact_launch(int dtype, const void* x, int B, long long N, int cap, int* idx, float* val, int* nnz,
                        const float* thr, const float* col_div, int* ties, const int* tie_quota, const float* col_thr,
-                       cudaStream_t stream) {
+                       int* seg_counts, cudaStream_t stream) {
   if (col_thr != nullptr && (thr != nullptr || ties != nullptr || tie_quota != nullptr)) return (int)cudaErrorInvalidValue;
   if (B <= 0) return 0;
   if (N > 2147483647LL) return (int)cudaErrorInvalidValue;
   const int blocks = B < 148 * 8 ? B : 148 * 8;
   if (dtype == 0)
     row_compact_kernel<float><<<blocks, RC_THREADS, 0, stream>>>(static_cast<const float*>(x), B, N, cap, idx, val, nnz, thr, col_div, ties,
-                                                                 tie_quota, col_thr);
+                                                                 tie_quota, col_thr, seg_counts);
   else
     row_compact_kernel<__nv_bfloat16>
         <<<blocks, RC_THREADS, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), B, N, cap, idx, val, nnz, thr, col_div, ties,
-                                            tie_quota, col_thr);
+                                            tie_quota, col_thr, seg_counts);
   return (int)cudaGetLastError();
 }
 

@@ -53,9 +53,10 @@ class AuxK:
     Nothing here makes the host wait for the device. The dead features of a step are gathered into a compact dictionary
     of ``capacity`` rows for the auxiliary encoder pass; the capacity follows the number of dead features with a lag: the
     count of every step is copied to pinned memory and read once its copy has completed, a step or two later, and the
-    capacity is then set to twice that count (at least ``k_aux``, in steps of 256 rows). Should the dead features of a
-    step outnumber the capacity (they grow faster than 2x within the lag), that step's auxiliary top-k sees the first
-    ``capacity`` of them by index; ``truncated_steps`` counts such steps."""
+    capacity is then set to that count plus a quarter plus 1024 rows (at least ``k_aux``, in steps of 256 rows): every
+    product of the auxiliary pass costs in proportion to the capacity, so the headroom is kept small. Should the dead
+    features of a step outnumber the capacity (they grew by more than that within the lag), that step's auxiliary
+    top-k sees the first ``capacity`` of them by index; ``truncated_steps`` counts such steps."""
 
     def __init__(self, n_features: int, k_aux: int, coefficient: float, dead_threshold: float, device, counter: torch.Tensor | None = None):
         self.k_aux, self.coefficient, self.dead_threshold = int(k_aux), float(coefficient), dead_threshold
@@ -67,7 +68,7 @@ class AuxK:
         self._pending: tuple[torch.Tensor, object] | None = None
 
     def _bucket(self, n_dead: int) -> int:
-        rows = max(self.k_aux, 2 * n_dead, 1024)
+        rows = max(self.k_aux, n_dead + n_dead // 4 + 1024)
         return min(-(-self.n_features // 8) * 8, -(-rows // 256) * 256)
 
     def update(self, fired: torch.Tensor, n_valid_tokens) -> torch.Tensor:
@@ -584,12 +585,23 @@ class FusedTopKSAEStep:
             dist.all_reduce(n_dead_all, group=self.tp_group)
         alpha_on = (n_dead_all > 0).float().reshape(1)  # no dead feature anywhere: the auxiliary term is absent, not |e|^2
         # compact dictionary of this shard's dead features: dead rows first (ascending), alive rows behind them with gate 0
-        order = torch.argsort((~is_dead).to(torch.int8), stable=True)[:cap]
-        if order.numel() < cap:  # fewer rows than the (rounded) capacity: repeat row 0 with gate 0
-            order = torch.cat([order, order.new_zeros(cap - order.numel())])
-            valid = torch.cat([is_dead[order[: self.F]], is_dead.new_zeros(cap - self.F)])
-        else:
+        sharded = self.dp_comm is not None
+        if sharded:
+            # One block of slots per replica's share of the feature rows, so that the dense gradient rows of the compact
+            # dictionary can be reduce-scattered over the replicas (each needs only the rows it updates).
+            cap_r = max(1, min(cap // self.dp, self.F // self.dp))
+            cap = cap_r * self.dp
+            per = self.F // self.dp
+            order = torch.argsort((~is_dead).view(self.dp, per).to(torch.int8), dim=1, stable=True)[:, :cap_r]
+            order = (order + torch.arange(self.dp, device=x.device).unsqueeze(1) * per).reshape(-1)
             valid = is_dead[order]
+        else:
+            order = torch.argsort((~is_dead).to(torch.int8), stable=True)[:cap]
+            if order.numel() < cap:  # fewer rows than the (rounded) capacity: repeat row 0 with gate 0
+                order = torch.cat([order, order.new_zeros(cap - order.numel())])
+                valid = torch.cat([is_dead[order[: self.F]], is_dead.new_zeros(cap - self.F)])
+            else:
+                valid = is_dead[order]
         w_dead = self.WE_bf16[order]
         wd_dead = self.WD_bf16[order]
         b_dead = self.bE[order]
@@ -609,7 +621,9 @@ class FusedTopKSAEStep:
         if self.tp > 1:
             idx_c, act_aux = self._merge_shard_codes(idx_c, act_aux, g_dead, aux.k_aux)
             self._mark("aux_merge_shards")
-        A = torch.zeros(B, cap + 1, dtype=torch.bfloat16, device=x.device)  # dense dead activations (+ one dump column)
+        # dense dead activations; empty slots land in a dump column behind them (eight columns of padding: the rows of
+        # the [B, cap] view below stay 16-byte aligned, which the library GEMMs need to run their fast kernels)
+        A = torch.zeros(B, cap + 8, dtype=torch.bfloat16, device=x.device)
         A.scatter_(1, torch.where(idx_c >= 0, idx_c, torch.full_like(idx_c, cap)).long(), act_aux.to(torch.bfloat16))
         A = A[:, :cap]
         aux_rec = _mm_f32(A, wd_dead)
@@ -622,18 +636,33 @@ class FusedTopKSAEStep:
                                          self.aux_sum, alpha_factor=alpha_on)  # fmt: skip
         dact = K.sparse_dact(idx, self.WD_bf16, g_main)
         self._mark("loss_grad_dact")
-        dA = _mm_f32(g_aux, wd_dead.t()) * (A != 0)  # gradient of the dead activations where they were selected
+        # gradient of the dead activations where they were selected (bf16 on the GPU: it is an operand of the next product)
+        dA = (g_aux @ wd_dead.t() if x.is_cuda else _mm_f32(g_aux, wd_dead.t())) * (A != 0)
         extra_gD = _mm_f32(A.t(), g_aux)  # d W_D rows of the compact dictionary
         extra_gE = _mm_f32(dA.to(torch.bfloat16).t(), x)  # d W_E^T rows
-        extra_gb = dA.sum(0)
-        if self.dp > 1:  # dense rows: summed over replicas (the sparse main part is rebuilt from the exchanged rows below)
-            for t in (extra_gD, extra_gE, extra_gb):
-                dist.all_reduce(t, group=self.dp_group)
-        row_of = torch.full((self.F,), -1, dtype=torch.int32, device=x.device)
+        extra_gb = dA.sum(0, dtype=torch.float32)
         slots = torch.arange(cap, dtype=torch.int32, device=x.device)
-        row_of.scatter_(0, order.long(), torch.where(valid, slots, torch.full_like(slots, -1)))
+        if sharded:
+            # dense rows: summed over replicas, each replica receiving the block of the rows it updates (the sparse main
+            # part is rebuilt from the exchanged rows below)
+            mine = self.dp_comm.rank
+            parts = []
+            for t in (extra_gD, extra_gE):
+                out = torch.empty(cap_r, t.shape[1], dtype=t.dtype, device=t.device)
+                dist.reduce_scatter_tensor(out, t.contiguous(), group=self.dp_group)
+                parts.append(out)
+            dist.all_reduce(extra_gb, group=self.dp_group)
+            extra_gD, extra_gE, extra_gb = parts[0], parts[1], extra_gb[mine * cap_r : (mine + 1) * cap_r].contiguous()
+            slots = slots - mine * cap_r
+            valid_mine = valid & (slots >= 0) & (slots < cap_r)
+        else:
+            if self.dp > 1:
+                for t in (extra_gD, extra_gE, extra_gb):
+                    dist.all_reduce(t, group=self.dp_group)
+            valid_mine = valid
+        row_of = torch.full((self.F,), -1, dtype=torch.int32, device=x.device)
+        row_of.scatter_(0, order.long(), torch.where(valid_mine, slots, torch.full_like(slots, -1)))
         self._mark("aux_gradients")
-        sharded = self.dp_comm is not None
         if sharded:
             g = self.dp_comm.exchange({"x": x, "dxhat": g_main, "idx": idx, "act": act, "dact": dact})
             x, g_main, idx, act, dact = g["x"], g["dxhat"], g["idx"], g["act"], g["dact"]

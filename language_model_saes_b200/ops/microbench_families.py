@@ -26,6 +26,7 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--case", default="all", help="all | attn | attn_fwd | batchtopk | batchtopk_step | clt | clt_adam | compact | headsum")
     ap.add_argument("--attn-shape", default="4,1024,64,64,128", help="batch,seq,heads,d_qk,d_v of the attention cases")
+    ap.add_argument("--clt-layers", type=int, default=12, help="source layers of the clt_adam case (rows = layers x 24576)")
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--min-seconds", type=float, default=1.0, help="repeat every timed case until this much timed work has accumulated")
@@ -124,7 +125,7 @@ def main(argv=None):
     if want("clt_adam"):
         # decoder-side sparse gradient + Adam of a cross-layer transcoder's last target layer: 12 source layers x 24576
         # features, rows of 768 columns, 64 codes per token and source layer on 2048 tokens (5.3 codes per feature)
-        B, L, Fd, d, k = 2048, 12, 24576, 768, 64
+        B, L, Fd, d, k = 2048, a.clt_layers, 24576, 768, 64
         F = L * Fd
         idx = torch.cat([torch.randint(0, Fd, (B, k), device=dev, dtype=torch.int32) + l * Fd for l in range(L)], dim=1).contiguous()
         act = torch.rand(B, L * k, device=dev)
@@ -138,12 +139,12 @@ def main(argv=None):
 
         def decoder_side():
             step[0] += 1
-            K.sparse_grad_adam(groups, act, act, None, dy, W, m, v, W16, None, None, None, None, None, None, None, None, None, None,
+            K.sparse_grad_adam(groups, act, act, dy, dy, W, m, v, W16, None, None, None, None, None, None, None, None, None, None,
                                2e-4, 0.9, 0.999, 1e-8, step[0], True, norm_sq_accum=acc)  # fmt: skip
 
         t = _timeit(decoder_side, a.iters, a.warmup, flush)
         gbs = F * d * 26 / t[0] / 1e6
-        print(json.dumps({"case": "sparse_grad_adam_decoder_side_294912x768_5codes_per_feature", "ms_ours": round(t[0], 4), "gbs": round(gbs, 1),
+        print(json.dumps({"case": f"sparse_grad_adam_decoder_side_{F}x768_5codes_per_feature", "ms_ours": round(t[0], 4), "gbs": round(gbs, 1),
                           "fraction_of_measured_copy": round(gbs / 6547.2, 3), "clocks": sampler[0].stop()}), flush=True)  # fmt: skip
         sampler[0] = ClockSampler(torch.cuda.current_device())
         sampler[0].start()

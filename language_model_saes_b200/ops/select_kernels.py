@@ -162,11 +162,11 @@ def dense_rows_to_sparse(acts: torch.Tensor, cap: int | None = None) -> tuple[to
     B = acts.shape[0]
     nnz = torch.empty(B, dtype=torch.int32, device=acts.device)
     if cap is None:
-        ext.row_compact(acts, None, None, nnz, None, None, None, None, None)
+        ext.row_compact(acts, None, None, nnz, None, None, None, None, None, None)
         cap = max(8, -(-int(nnz.max()) // 8) * 8)
     idx = torch.empty(B, cap, dtype=torch.int32, device=acts.device)
     val = torch.empty(B, cap, dtype=torch.float32, device=acts.device)
-    ext.row_compact(acts, idx, val, nnz, None, None, None, None, None)
+    ext.row_compact(acts, idx, val, nnz, None, None, None, None, None, None)
     return idx, val
 
 
@@ -193,14 +193,15 @@ def threshold_rows_to_sparse(g: torch.Tensor, thr: torch.Tensor, col_div: torch.
     g = g.contiguous()
     B = g.shape[0]
     nnz = torch.empty(B, dtype=torch.int32, device=g.device)
-    quota = None
+    quota = seg = None
     if n_ties is None:
         if cap is None:
-            ext.row_compact(g, None, None, nnz, thr, None, None, None, None)
+            ext.row_compact(g, None, None, nnz, thr, None, None, None, None, None)
             widest = nnz.max()
     else:
         ties = torch.empty(B, dtype=torch.int32, device=g.device)
-        ext.row_compact(g, None, None, nnz, thr, None, ties, None, None)
+        seg = torch.empty(B, 8, 2, dtype=torch.int32, device=g.device)  # per warp segment: the compaction pass starts from them
+        ext.row_compact(g, None, None, nnz, thr, None, ties, None, None, seg)
         budget = n_ties.reshape(()).to(torch.int64)
         if tie_group is not None and dist.get_world_size(tie_group) > 1:
             mine = ties.sum(dtype=torch.int64).reshape(1)
@@ -218,7 +219,7 @@ def threshold_rows_to_sparse(g: torch.Tensor, thr: torch.Tensor, col_div: torch.
     assert cap % 8 == 0 and cap > 0
     idx = torch.empty(B, cap, dtype=torch.int32, device=g.device)
     val = torch.empty(B, cap, dtype=torch.float32, device=g.device)
-    ext.row_compact(g, idx, val, nnz, thr, col_div, None, quota, None)  # nnz: the row's full count, also beyond the list width
+    ext.row_compact(g, idx, val, nnz, thr, col_div, None, quota, None, seg)  # nnz: the row's full count, also beyond the list width
     if overflow is not None:
         overflow += (nnz > cap).sum()
     return idx, val
@@ -247,7 +248,7 @@ def column_threshold_rows_to_sparse(x: torch.Tensor, col_thr: torch.Tensor, cap:
     idx = torch.empty(B, cap, dtype=torch.int32, device=x.device)
     val = torch.empty(B, cap, dtype=torch.float32, device=x.device)
     nnz = torch.empty(B, dtype=torch.int32, device=x.device)
-    K._ext().row_compact(x, idx, val, nnz, None, None, None, None, col_thr.float().contiguous())
+    K._ext().row_compact(x, idx, val, nnz, None, None, None, None, col_thr.float().contiguous(), None)
     if overflow is not None:
         overflow += (nnz > cap).sum()
     return idx, val
