@@ -614,8 +614,11 @@ int64_t radix_hi_bins() { return lmsae::radix_hi_bins(); }
 
 // x: contiguous, viewed as [A, S, N]; level 0 fills hist[radix_hi_bins()], level 1 fills hist[65536] with the members of
 // bin sel[0]. hist is uint32 storage handed in as int32.
+// floor (fp32, one element, level 0 only): count only values of at least *floor. need (int64 [4]): run only if need[3] != 0.
 void radix_hist(const Tensor& x, int64_t A, int64_t S, int64_t N, int64_t s, int64_t level, const c10::optional<Tensor>& sel,
-                const Tensor& hist) {
+                const Tensor& hist, const c10::optional<Tensor>& floor, const c10::optional<Tensor>& need) {
+  if (floor.has_value()) { CHECK_T(*floor, torch::kFloat32); TORCH_CHECK(level == 0 && floor->numel() >= 1, "floor: one fp32 value, first level only"); }
+  if (need.has_value()) { CHECK_T(*need, torch::kInt64); TORCH_CHECK(need->numel() >= 4, "need: int64 [4]"); }
   TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.numel() == A * S * N, "x must be a contiguous [A, S, N] array");
   CHECK_T(hist, torch::kInt32);
   TORCH_CHECK(hist.numel() >= (level == 0 ? lmsae::radix_hi_bins() : 65536), "histogram too small");
@@ -626,22 +629,27 @@ void radix_hist(const Tensor& x, int64_t A, int64_t S, int64_t N, int64_t s, int
   const c10::cuda::CUDAGuard guard(x.device());
   check_cuda(lmsae::radix_hist_launch(dtype_code(x), x.data_ptr(), A, S, N, s, (int)level,
                                       level == 1 ? reinterpret_cast<const long long*>(sel->data_ptr<int64_t>()) : nullptr,
-                                      reinterpret_cast<unsigned*>(hist.data_ptr<int>()), at::cuda::getCurrentCUDAStream()),
+                                      reinterpret_cast<unsigned*>(hist.data_ptr<int>()), opt_ptr<float>(floor),
+                                      need.has_value() ? reinterpret_cast<const long long*>(need->data_ptr<int64_t>()) : nullptr,
+                                      at::cuda::getCurrentCUDAStream()),
              "radix_hist launch");
 }
 
 void radix_pick(const Tensor& hist, int64_t nbins, int64_t k, const c10::optional<Tensor>& sel_in, int64_t level,
-                const Tensor& sel_out, const c10::optional<Tensor>& thr) {
+                const Tensor& sel_out, const c10::optional<Tensor>& thr, const c10::optional<Tensor>& need) {
   CHECK_T(hist, torch::kInt32);
   CHECK_T(sel_out, torch::kInt64);
-  TORCH_CHECK(hist.numel() >= nbins && sel_out.numel() >= 3, "radix_pick: buffers too small");
+  TORCH_CHECK(hist.numel() >= nbins && sel_out.numel() >= 4, "radix_pick: buffers too small");
+  if (need.has_value()) { CHECK_T(*need, torch::kInt64); TORCH_CHECK(need->numel() >= 4, "need: int64 [4]"); }
   if (thr.has_value()) { CHECK_T(*thr, torch::kFloat32); }
   if (sel_in.has_value()) { CHECK_T(*sel_in, torch::kInt64); }
   const c10::cuda::CUDAGuard guard(hist.device());
   check_cuda(lmsae::radix_pick_launch(reinterpret_cast<const unsigned*>(hist.data_ptr<int>()), (int)nbins, k,
                                       sel_in.has_value() ? reinterpret_cast<const long long*>(sel_in->data_ptr<int64_t>()) : nullptr,
                                       (int)level, reinterpret_cast<long long*>(sel_out.data_ptr<int64_t>()),
-                                      opt_ptr<float>(thr), at::cuda::getCurrentCUDAStream()),
+                                      opt_ptr<float>(thr),
+                                      need.has_value() ? reinterpret_cast<const long long*>(need->data_ptr<int64_t>()) : nullptr,
+                                      at::cuda::getCurrentCUDAStream()),
              "radix_pick launch");
 }
 

@@ -178,9 +178,10 @@ int clt_wgrad_launch(const CltGradTable& tab, const int* offsets, const int* ent
 // dtype: 0 = fp32, 1 = bf16. x is a contiguous [A, S, N] array and the selection covers segment s.
 int radix_hi_bins();
 int radix_hist_launch(int dtype, const void* x, long long A, long long S, long long N, long long s, int level,
-                      const long long* sel, unsigned* hist, cudaStream_t stream);
+                      const long long* sel, unsigned* hist, const float* floor, const long long* need,
+                      cudaStream_t stream);
 int radix_pick_launch(const unsigned* hist, int nbins, long long k, const long long* sel_in, int level, long long* sel_out,
-                      float* thr, cudaStream_t stream);
+                      float* thr, const long long* need, cudaStream_t stream);
 int threshold_mask_launch(int dtype, const void* x, const float* thr, long long A, long long S, long long N, void* out,
                           cudaStream_t stream);
 int row_compact_launch(int dtype, const void* x, int B, long long N, int cap, int* idx, float* val, int* nnz,

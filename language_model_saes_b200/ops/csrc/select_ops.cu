@@ -49,16 +49,22 @@ struct Vec;
 template <>
 struct Vec<float> {
   static constexpr int N = 4;
-  __device__ static void load(const float* p, uint32_t (&b)[4]) {
-    const float4 v = __ldcs(reinterpret_cast<const float4*>(p));
-    b[0] = positive_bits(v.x); b[1] = positive_bits(v.y); b[2] = positive_bits(v.z); b[3] = positive_bits(v.w);
+  __device__ static bool all_below(const uint4&, uint32_t) { return false; }
+  __device__ static void decode(const uint4& v, uint32_t (&b)[4]) {
+    b[0] = positive_bits(__uint_as_float(v.x)); b[1] = positive_bits(__uint_as_float(v.y));
+    b[2] = positive_bits(__uint_as_float(v.z)); b[3] = positive_bits(__uint_as_float(v.w));
   }
 };
 template <>
 struct Vec<__nv_bfloat16> {
   static constexpr int N = 8;
-  __device__ static void load(const __nv_bfloat16* p, uint32_t (&b)[8]) {
-    const uint4 v = __ldcs(reinterpret_cast<const uint4*>(p));
+  // floor2: a positive bf16 pattern in both halves of a word (0: none). True when none of the eight elements reaches it
+  // (as signed 16-bit integers positive floats order like their patterns, negative floats sort below all of them).
+  __device__ static bool all_below(const uint4& v, uint32_t floor2) {
+    return floor2 != 0u &&
+           (__vcmpges2(v.x, floor2) | __vcmpges2(v.y, floor2) | __vcmpges2(v.z, floor2) | __vcmpges2(v.w, floor2)) == 0u;
+  }
+  __device__ static void decode(const uint4& v, uint32_t (&b)[8]) {
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -71,29 +77,34 @@ struct Vec<__nv_bfloat16> {
 };
 
 // x is a contiguous [A, S, N] array; the selection runs over all (a, n) of segment s: A rows of N contiguous elements.
-// `visit(bits)` is called for every positive element. Rows are cut into chunks of threads x 16 bytes.
+// `visit(bits)` is called for every positive element whose float bits are at least `floor_bits` (0: every positive
+// element). Rows are cut into chunks of threads x 16 bytes; 16-bit vectors without any element at the floor are
+// rejected with four packed comparisons.
 template <typename T, int THREADS, typename Fn>
 __device__ __forceinline__ void for_each_positive(const T* __restrict__ x, long long A, long long S, long long N,
-                                                  long long s, Fn visit) {
+                                                  long long s, uint32_t floor_bits, Fn visit) {
   constexpr int V = Vec<T>::N;
   const long long chunk = (long long)THREADS * V;
   const long long chunks_per_row = (N + chunk - 1) / chunk;
   const bool vec_ok = (N % V == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0);
+  const uint32_t floor2 = (floor_bits >> 16) * 0x10001u;  // the floor rounded down to 16 bits, in both halves
   for (long long item = blockIdx.x; item < A * chunks_per_row; item += gridDim.x) {
     const long long a = item / chunks_per_row, ch = item - a * chunks_per_row;
     const T* row = x + (a * S + s) * N;
     const long long e = ch * chunk + (long long)threadIdx.x * V;
     if (e >= N) continue;
     if (vec_ok) {
+      const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(row + e));
+      if (Vec<T>::all_below(raw, floor2)) continue;
       uint32_t b[V];
-      Vec<T>::load(row + e, b);
+      Vec<T>::decode(raw, b);
 #pragma unroll
       for (int i = 0; i < V; ++i)
-        if (b[i] != 0) visit(b[i]);
+        if (b[i] != 0 && b[i] >= floor_bits) visit(b[i]);
     } else {
       for (int i = 0; i < V && e + i < N; ++i) {
         const uint32_t b = positive_bits<T>(row[e + i]);
-        if (b != 0) visit(b);
+        if (b != 0 && b >= floor_bits) visit(b);
       }
     }
   }
@@ -102,11 +113,17 @@ __device__ __forceinline__ void for_each_positive(const T* __restrict__ x, long 
 template <typename T>
 __global__ void __launch_bounds__(HIST_THREADS)
 radix_hist_hi_kernel(const T* __restrict__ x, long long A, long long S, long long N, long long s,
-                     unsigned* __restrict__ hist) {
+                     unsigned* __restrict__ hist, const float* __restrict__ floor, const long long* __restrict__ need) {
+  // `floor`: only values of at least *floor are counted (a caller that knows a lower bound of the value it is looking
+  // for saves nearly all of the shared-memory atomics). `need`: the pass runs only if need[3] != 0 (the repeat without
+  // a floor, for the case that the floor turned out to lie above the value sought).
+  if (need != nullptr && need[3] == 0) return;
   extern __shared__ unsigned s_hist[];  // [kHiBins]
   for (int i = threadIdx.x; i < kHiBins; i += HIST_THREADS) s_hist[i] = 0;
   __syncthreads();
-  for_each_positive<T, HIST_THREADS>(x, A, S, N, s, [&](uint32_t b) {
+  const float fl = floor != nullptr ? *floor : 0.0f;
+  const uint32_t floor_bits = fl > 0.0f ? __float_as_uint(fl) : 0u;
+  for_each_positive<T, HIST_THREADS>(x, A, S, N, s, floor_bits, [&](uint32_t b) {
     uint32_t bin = b >> 16;
     if (bin >= (uint32_t)kHiBins) bin = kHiBins - 1;
     atomicAdd(&s_hist[bin], 1u);
@@ -124,7 +141,7 @@ __global__ void __launch_bounds__(256)
 radix_hist_lo_kernel(const T* __restrict__ x, long long A, long long S, long long N, long long s,
                      const long long* __restrict__ sel, unsigned* __restrict__ hist) {
   const uint32_t want = (uint32_t)sel[0];
-  for_each_positive<T, 256>(x, A, S, N, s, [&](uint32_t b) {
+  for_each_positive<T, 256>(x, A, S, N, s, 0u, [&](uint32_t b) {
     uint32_t bin = b >> 16;
     if (bin >= (uint32_t)kHiBins) bin = kHiBins - 1;
     if (bin == want) atomicAdd(&hist[b & 0xFFFFu], 1u);
@@ -136,8 +153,13 @@ radix_hist_lo_kernel(const T* __restrict__ x, long long A, long long S, long lon
 // bits: level 1 takes k from sel_in[1], and writes the threshold  float((sel_in[0] << 16) | b)  to thr.
 __global__ void __launch_bounds__(1024)
 radix_pick_kernel(const unsigned* __restrict__ hist, int nbins, long long k, const long long* __restrict__ sel_in,
-                  int level, long long* __restrict__ sel_out, float* __restrict__ thr) {
+                  int level, long long* __restrict__ sel_out, float* __restrict__ thr, const long long* __restrict__ need) {
+  // sel_out[3] = 1 when the histogram held fewer than k members (with a floored histogram: the floor was too high).
+  // `need`: the pick runs only if need[3] != 0 (read by every thread before anything is written: need may be sel_out).
+  const bool run_it = need == nullptr || need[3] != 0;
   __shared__ long long s_part[1024];
+  __syncthreads();
+  if (!run_it) return;
   __shared__ long long s_above;  // count in the chunks above the chosen chunk
   __shared__ int s_chunk;
   if (level == 1) k = sel_in[1];
@@ -157,6 +179,7 @@ radix_pick_kernel(const unsigned* __restrict__ hist, int nbins, long long k, con
       run += s_part[i];
     }
     sel_out[2] = run;
+    sel_out[3] = (level == 0 && run < k) ? 1 : 0;
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -230,37 +253,40 @@ threshold_mask_kernel(const T* __restrict__ x, const float* __restrict__ thr, lo
 }
 
 // ---- dense rows -> padded sparse lists --------------------------------------------------------------
-template <typename T>
-__device__ __forceinline__ float to_float(T v);
-template <>
-__device__ __forceinline__ float to_float<float>(float v) { return v; }
-template <>
-__device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
-
 constexpr int RC_THREADS = 256;
 
+// 16 bytes of a row as raw words: V elements of type T; element i as a float, and a scalar fall-back loader that packs
+// the in-range elements of an unaligned or ragged vector (zeros elsewhere).
 template <typename T>
 struct RowVec;
 template <>
 struct RowVec<float> {
   static constexpr int V = 4;
-  __device__ static void load(const float* p, float (&f)[4]) {
-    const float4 v = __ldcs(reinterpret_cast<const float4*>(p));
-    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+  __device__ static float get(const uint4& u, int i) {
+    return __uint_as_float(i == 0 ? u.x : i == 1 ? u.y : i == 2 ? u.z : u.w);
+  }
+  __device__ static uint4 gather(const float* p, long long n_valid) {
+    uint4 u = make_uint4(0u, 0u, 0u, 0u);
+    if (n_valid > 0) u.x = __float_as_uint(p[0]);
+    if (n_valid > 1) u.y = __float_as_uint(p[1]);
+    if (n_valid > 2) u.z = __float_as_uint(p[2]);
+    if (n_valid > 3) u.w = __float_as_uint(p[3]);
+    return u;
   }
 };
 template <>
 struct RowVec<__nv_bfloat16> {
   static constexpr int V = 8;
-  __device__ static void load(const __nv_bfloat16* p, float (&f)[8]) {
-    const uint4 u = __ldcs(reinterpret_cast<const uint4*>(p));
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+  __device__ static float get(const uint4& u, int i) {
+    const unsigned w = (i >> 1) == 0 ? u.x : (i >> 1) == 1 ? u.y : (i >> 1) == 2 ? u.z : u.w;
+    return __uint_as_float((i & 1) ? (w & 0xffff0000u) : (w << 16));
+  }
+  __device__ static uint4 gather(const __nv_bfloat16* p, long long n_valid) {
+    unsigned w[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 t = __bfloat1622float2(h[i]);
-      f[2 * i] = t.x;
-      f[2 * i + 1] = t.y;
-    }
+    for (int i = 0; i < 8; ++i)
+      if (i < n_valid) w[i >> 1] |= (unsigned)__bfloat16_as_ushort(p[i]) << ((i & 1) * 16);
+    return make_uint4(w[0], w[1], w[2], w[3]);
   }
 };
 
@@ -285,39 +311,54 @@ struct RowPredicate {
   bool has_thr, split_ties;
   float t;
   const float* col_thr;
+  // bf16 rows against a positive threshold that is itself a bf16 value: the comparison runs on the raw 16-bit patterns,
+  // two elements per instruction (as signed integers, positive floats order like their patterns and every negative
+  // float sorts below them)
+  bool raw16;
+  unsigned t2;  // the threshold's pattern in both halves of a word
 };
 
 // bit i of the two masks: element c + i is kept outright / equals the threshold
-template <int V>
-__device__ __forceinline__ void rc_classify(const float (&f)[V], long long c, long long end, const RowPredicate& q,
+template <typename T>
+__device__ __forceinline__ void rc_classify(const uint4& u, long long c, long long end, const RowPredicate& q,
                                             unsigned& m_strict, unsigned& m_tie) {
+  constexpr int V = RowVec<T>::V;
   m_strict = m_tie = 0;
+  if constexpr (V == 8) {
+    if (q.raw16) {  // (elements past the end of the row were loaded as zeros: never above or equal to a positive threshold)
+      const unsigned w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const unsigned g = q.split_ties ? __vcmpgts2(w[j], q.t2) : __vcmpges2(w[j], q.t2);
+        m_strict |= ((g & 1u) | ((g >> 15) & 2u)) << (2 * j);
+        if (q.split_ties) {
+          const unsigned e = __vcmpeq2(w[j], q.t2);
+          m_tie |= ((e & 1u) | ((e >> 15) & 2u)) << (2 * j);
+        }
+      }
+      return;
+    }
+  }
 #pragma unroll
   for (int i = 0; i < V; ++i) {
     const bool in = c + i < end;
+    const float f = RowVec<T>::get(u, i);
     if (q.split_ties) {
-      m_strict |= (unsigned)(in && f[i] > q.t) << i;
-      m_tie |= (unsigned)(in && f[i] == q.t) << i;
+      m_strict |= (unsigned)(in && f > q.t) << i;
+      m_tie |= (unsigned)(in && f == q.t) << i;
     } else if (q.col_thr != nullptr) {
-      m_strict |= (unsigned)(in && f[i] > q.col_thr[in ? c + i : 0]) << i;
+      m_strict |= (unsigned)(in && f > q.col_thr[in ? c + i : 0]) << i;
     } else {
-      m_strict |= (unsigned)(in && (q.has_thr ? (f[i] >= q.t) : (f[i] != 0.0f))) << i;
+      m_strict |= (unsigned)(in && (q.has_thr ? (f >= q.t) : (f != 0.0f))) << i;
     }
   }
 }
 
 template <typename T>
-__device__ __forceinline__ void rc_load(const T* xr, long long c, long long end, bool vec_ok, float (&f)[RowVec<T>::V]) {
-  constexpr int V = RowVec<T>::V;
-  if (c >= end) {
-#pragma unroll
-    for (int i = 0; i < V; ++i) f[i] = 0.0f;
-  } else if (vec_ok) {
-    RowVec<T>::load(xr + c, f);
-  } else {
-#pragma unroll
-    for (int i = 0; i < V; ++i) f[i] = c + i < end ? to_float<T>(xr[c + i]) : 0.0f;
-  }
+__device__ __forceinline__ uint4 rc_load(const T* xr, long long c, long long end, bool vec_ok) {
+  if (c >= end) return make_uint4(0u, 0u, 0u, 0u);
+  if (vec_ok) return __ldcs(reinterpret_cast<const uint4*>(xr + c));
+  return RowVec<T>::gather(xr + c, end - c);
 }
 
 template <typename T>
@@ -333,6 +374,13 @@ row_compact_kernel(const T* __restrict__ x, int B, long long N, int cap, int* __
   q.t = q.has_thr ? *thr : 0.0f;
   q.split_ties = q.has_thr && (ties != nullptr || tie_quota != nullptr);
   q.col_thr = col_thr;
+  q.raw16 = false;
+  q.t2 = 0u;
+  if constexpr (V == 8) {
+    const __nv_bfloat16 tb = __float2bfloat16(q.t);
+    q.raw16 = q.has_thr && q.t > 0.0f && __bfloat162float(tb) == q.t;
+    q.t2 = (unsigned)__bfloat16_as_ushort(tb) * 0x10001u;
+  }
   const bool vec_ok = (N % V == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0);
   __shared__ int s_a[NW], s_b[NW];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -348,13 +396,13 @@ row_compact_kernel(const T* __restrict__ x, int B, long long N, int cap, int* __
     if (counting || seg_counts == nullptr) {
       // ---- pass 1: this segment's counts
       for (long long c0 = s0; c0 < s1; c0 += stride) {
-        float f[RC_U][V];
+        uint4 raw[RC_U];
 #pragma unroll
-        for (int u = 0; u < RC_U; ++u) rc_load<T>(xr, c0 + ((long long)u * 32 + lane) * V, s1, vec_ok, f[u]);
+        for (int u = 0; u < RC_U; ++u) raw[u] = rc_load<T>(xr, c0 + ((long long)u * 32 + lane) * V, s1, vec_ok);
 #pragma unroll
         for (int u = 0; u < RC_U; ++u) {
           unsigned ms, mt;
-          rc_classify<V>(f[u], c0 + ((long long)u * 32 + lane) * V, s1, q, ms, mt);
+          rc_classify<T>(raw[u], c0 + ((long long)u * 32 + lane) * V, s1, q, ms, mt);
           n_s += __popc(ms);
           n_t += __popc(mt);
         }
@@ -394,14 +442,14 @@ row_compact_kernel(const T* __restrict__ x, int B, long long N, int cap, int* __
     int S_seen = s_before, T_seen = t_before;
     if (n_s + n_t > 0) {
       for (long long c0 = s0; c0 < s1; c0 += stride) {
-        float f[RC_U][V];
+        uint4 raw[RC_U];
 #pragma unroll
-        for (int u = 0; u < RC_U; ++u) rc_load<T>(xr, c0 + ((long long)u * 32 + lane) * V, s1, vec_ok, f[u]);
+        for (int u = 0; u < RC_U; ++u) raw[u] = rc_load<T>(xr, c0 + ((long long)u * 32 + lane) * V, s1, vec_ok);
 #pragma unroll
         for (int u = 0; u < RC_U; ++u) {
           const long long c = c0 + ((long long)u * 32 + lane) * V;
           unsigned ms, mt;
-          rc_classify<V>(f[u], c, s1, q, ms, mt);
+          rc_classify<T>(raw[u], c, s1, q, ms, mt);
           if (__ballot_sync(0xffffffffu, (ms | mt) != 0u) == 0u) continue;  // nothing kept in these 32 vectors
           const int mine = __popc(ms) | (__popc(mt) << 16);  // both counts in one word (at most 256 each per warp)
           int inc = mine;
@@ -422,7 +470,8 @@ row_compact_kernel(const T* __restrict__ x, int B, long long N, int cap, int* __
             if (keep) {
               if (slot < cap) {
                 idx[(size_t)row * cap + slot] = (int)(c + i);
-                val[(size_t)row * cap + slot] = col_div != nullptr ? f[u][i] / col_div[c + i] : f[u][i];
+                const float f = RowVec<T>::get(raw[u], i);
+                val[(size_t)row * cap + slot] = col_div != nullptr ? f / col_div[c + i] : f;
               }
               ++slot;
             }
@@ -495,7 +544,8 @@ gather_rows_cast_kernel(const TI* __restrict__ src, const int* __restrict__ keep
 }  // namespace
 
 int radix_hist_launch(int dtype, const void* x, long long A, long long S, long long N, long long s, int level,
-                      const long long* sel, unsigned* hist, cudaStream_t stream) {
+                      const long long* sel, unsigned* hist, const float* floor, const long long* need,
+                      cudaStream_t stream) {
   if (A <= 0 || N <= 0 || s < 0 || s >= S) return (int)cudaErrorInvalidValue;
   if (level == 0) {
     const size_t smem = (size_t)kHiBins * 4;
@@ -503,12 +553,12 @@ int radix_hist_launch(int dtype, const void* x, long long A, long long S, long l
     if (dtype == 0) {
       e = cudaFuncSetAttribute(radix_hist_hi_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return (int)e;
-      radix_hist_hi_kernel<float><<<148, HIST_THREADS, smem, stream>>>(static_cast<const float*>(x), A, S, N, s, hist);
+      radix_hist_hi_kernel<float><<<148, HIST_THREADS, smem, stream>>>(static_cast<const float*>(x), A, S, N, s, hist, floor, need);
     } else {
       e = cudaFuncSetAttribute(radix_hist_hi_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return (int)e;
       radix_hist_hi_kernel<__nv_bfloat16>
-          <<<148, HIST_THREADS, smem, stream>>>(static_cast<const __nv_bfloat16*>(x), A, S, N, s, hist);
+          <<<148, HIST_THREADS, smem, stream>>>(static_cast<const __nv_bfloat16*>(x), A, S, N, s, hist, floor, need);
     }
   } else {
     if (dtype == 0)
@@ -523,9 +573,9 @@ int radix_hist_launch(int dtype, const void* x, long long A, long long S, long l
 int radix_hi_bins() { return kHiBins; }
 
 int radix_pick_launch(const unsigned* hist, int nbins, long long k, const long long* sel_in, int level, long long* sel_out,
-                      float* thr, cudaStream_t stream) {
+                      float* thr, const long long* need, cudaStream_t stream) {
   if (nbins <= 0 || nbins > 65536 || (level == 1 && sel_in == nullptr)) return (int)cudaErrorInvalidValue;
-  radix_pick_kernel<<<1, 1024, 0, stream>>>(hist, nbins, k, sel_in, level, sel_out, thr);
+  radix_pick_kernel<<<1, 1024, 0, stream>>>(hist, nbins, k, sel_in, level, sel_out, thr, need);
   return (int)cudaGetLastError();
 }
 

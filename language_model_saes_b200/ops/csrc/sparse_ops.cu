@@ -563,30 +563,45 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
           }
         }
       }
-      for (int e = e0; e < e1; ++e) {
-        const int ent = (int)LMSAE_IDX(p.entries[e], p.n_codes);
-        const int row = (int)LMSAE_IDX(ent / p.k, p.n_rows);
-        const float a = p.act[ent];
-        const float da = p.dact[ent];
-        // codes beyond the first k_main slots of a row (auxiliary codes) multiply the auxiliary output gradient
-        const __nv_bfloat16* gmat = (p.dxhat_aux != nullptr && ent - row * p.k >= p.k_main) ? p.dxhat_aux : p.dxhat;
-        if (c0 == 0 && threadIdx.x == 0) bias_g += da;
+      // The entries' metadata (position, token row, code, code gradient) is fetched 32 entries at a time, one entry per
+      // lane, and handed round by shuffles: one coalesced load and one integer division per entry and warp instead of
+      // three dependent broadcast loads and a division per entry and THREAD, and the row gathers of successive entries
+      // no longer wait for index loads in between.
+      for (int eb = e0; eb < e1; eb += 32) {
+        const int n_e = min(32, e1 - eb);
+        int row_l = 0, aux_l = 0;
+        float a_l = 0.0f, da_l = 0.0f;
+        if (lane < n_e) {
+          const int ent = (int)LMSAE_IDX(p.entries[eb + lane], p.n_codes);
+          row_l = (int)LMSAE_IDX(ent / p.k, p.n_rows);
+          a_l = p.act[ent];
+          da_l = p.dact[ent];
+          // codes beyond the first k_main slots of a row (auxiliary codes) multiply the auxiliary output gradient
+          aux_l = (p.dxhat_aux != nullptr && ent - row_l * p.k >= p.k_main) ? 1 : 0;
+        }
+        for (int j = 0; j < n_e; ++j) {
+          const int row = __shfl_sync(0xffffffffu, row_l, j);
+          const float a = __shfl_sync(0xffffffffu, a_l, j);
+          const float da = __shfl_sync(0xffffffffu, da_l, j);
+          const __nv_bfloat16* gmat = __shfl_sync(0xffffffffu, aux_l, j) ? p.dxhat_aux : p.dxhat;
+          if (c0 == 0 && threadIdx.x == 0) bias_g += da;
 #pragma unroll
-        for (int v = 0; v < VEC; ++v) {
-          if (in[v]) {
-            if constexpr (doD) {
-              const uint2 ud = __ldg(reinterpret_cast<const uint2*>(gmat + (size_t)row * p.d + c[v]));
-              const float2 d01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ud.x));
-              const float2 d23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ud.y));
-              gD[v][0] = fmaf(a, d01.x, gD[v][0]); gD[v][1] = fmaf(a, d01.y, gD[v][1]);
-              gD[v][2] = fmaf(a, d23.x, gD[v][2]); gD[v][3] = fmaf(a, d23.y, gD[v][3]);
-            }
-            if constexpr (doE) {
-              const uint2 ux = __ldg(reinterpret_cast<const uint2*>(p.x + (size_t)row * p.d + c[v]));
-              const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ux.x));
-              const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ux.y));
-              gE[v][0] = fmaf(da, x01.x, gE[v][0]); gE[v][1] = fmaf(da, x01.y, gE[v][1]);
-              gE[v][2] = fmaf(da, x23.x, gE[v][2]); gE[v][3] = fmaf(da, x23.y, gE[v][3]);
+          for (int v = 0; v < VEC; ++v) {
+            if (in[v]) {
+              if constexpr (doD) {
+                const uint2 ud = __ldg(reinterpret_cast<const uint2*>(gmat + (size_t)row * p.d + c[v]));
+                const float2 d01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ud.x));
+                const float2 d23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ud.y));
+                gD[v][0] = fmaf(a, d01.x, gD[v][0]); gD[v][1] = fmaf(a, d01.y, gD[v][1]);
+                gD[v][2] = fmaf(a, d23.x, gD[v][2]); gD[v][3] = fmaf(a, d23.y, gD[v][3]);
+              }
+              if constexpr (doE) {
+                const uint2 ux = __ldg(reinterpret_cast<const uint2*>(p.x + (size_t)row * p.d + c[v]));
+                const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ux.x));
+                const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ux.y));
+                gE[v][0] = fmaf(da, x01.x, gE[v][0]); gE[v][1] = fmaf(da, x01.y, gE[v][1]);
+                gE[v][2] = fmaf(da, x23.x, gE[v][2]); gE[v][3] = fmaf(da, x23.y, gE[v][3]);
+              }
             }
           }
         }
@@ -717,9 +732,11 @@ int sparse_grad_adam_launch(const GradAdamParams& p, cudaStream_t stream) {
     else
       sparse_grad_adam_kernel<1, 4, 3><<<blocks, GA_THREADS, 0, stream>>>(p);
   } else {
-    // one-sided: half the registers, so five CTAs (rows in flight) fit an SM
-    if (p.ctas_per_sm < 1 || p.ctas_per_sm > 5) blocks = rows < 148 * 5 ? rows : 148 * 5;
-    if (doD) sparse_grad_adam_kernel<1, 5, 1><<<blocks, GA_THREADS, 0, stream>>>(p);
+    // one-sided: fewer registers; the encoder side fits five CTAs (rows in flight) per SM, the decoder side (row norms,
+    // norm penalty) four without spilling
+    const int per_sm = doD ? 4 : 5;
+    if (p.ctas_per_sm < 1 || p.ctas_per_sm > per_sm) blocks = rows < 148 * per_sm ? rows : 148 * per_sm;
+    if (doD) sparse_grad_adam_kernel<1, 4, 1><<<blocks, GA_THREADS, 0, stream>>>(p);
     else sparse_grad_adam_kernel<1, 5, 2><<<blocks, GA_THREADS, 0, stream>>>(p);
   }
   return (int)cudaGetLastError();

@@ -120,6 +120,7 @@ class FusedTopKSAEStep:
         self.betas, self.eps = betas, eps
         self.use_gate = cfg.sparsity_include_decoder_norm
         self.batch_level = cfg.act_fn == "batchtopk"
+        self._batch_thr: torch.Tensor | None = None  # last batch-level threshold (device), a hint for the next selection
         self.WE = sae.W_E.data.t()
         self.WD = sae.W_D.data
         assert self.WE.is_contiguous() and self.WD.is_contiguous(), "weights must be feature-major and contiguous"
@@ -399,7 +400,10 @@ class FusedTopKSAEStep:
         self._mark("encoder_gemm_hidden")
         B = x.shape[0]
         tp_group = self.tp_group if self.tp > 1 else None
-        thr, n_ties = S.positive_thresholds(G.view(1, 1, -1), k * B, tp_group, return_remaining=True)
+        # (the previous batch's threshold, lowered by a quarter, as the histogram pass's floor: see positive_thresholds)
+        floor = self._batch_thr * 0.75 if self._batch_thr is not None and G.is_cuda else None
+        thr, n_ties = S.positive_thresholds(G.view(1, 1, -1), k * B, tp_group, return_remaining=True, floor=floor)
+        self._batch_thr = thr
         self._mark("batch_threshold_select")
         # exactly k * B codes: of the entries equal to the (bf16) threshold only as many as the selection still needs
         cap = -(-self.batch_list_factor * k // 8) * 8

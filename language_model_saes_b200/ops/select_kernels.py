@@ -37,10 +37,16 @@ def _kernel_ok(x: torch.Tensor) -> bool:
 
 
 @torch.no_grad()
-def positive_thresholds(x3: torch.Tensor, k: int, group=None, return_remaining: bool = False):
+def positive_thresholds(x3: torch.Tensor, k: int, group=None, return_remaining: bool = False, floor: torch.Tensor | None = None):
     """``x3``: contiguous ``[A, S, N]``. Returns fp32 ``[S]``: for every segment ``s`` the k-th largest positive value of
     ``x3[:, s, :]``, taken over the union of all ranks of ``group`` when one is given. ``return_remaining`` (GPU kernels
-    only) also returns int64 ``[S]``: how many of the entries equal to the threshold the selection of ``k`` includes."""
+    only) also returns int64 ``[S]``: how many of the entries equal to the threshold the selection of ``k`` includes.
+
+    ``floor`` (16-bit data, one segment, GPU kernels; fp32 one-element device tensor, the same on every rank): a guess of a
+    lower bound of the result, e.g. a fraction of the previous batch's threshold. The histogram pass then counts only
+    values of at least ``floor``, which removes nearly all of its shared-memory atomics. The result does not depend on
+    the guess: when fewer than ``k`` values reach the floor, a second pass without it runs (decided on the device, the
+    host launches both and reads nothing)."""
     A, S, N = x3.shape
     world = dist.get_world_size(group) if group is not None else 1
     if not _kernel_ok(x3):
@@ -71,18 +77,25 @@ def positive_thresholds(x3: torch.Tensor, k: int, group=None, return_remaining: 
     thr = torch.empty(S, dtype=torch.float32, device=dev)
     remaining = torch.zeros(S, dtype=torch.int64, device=dev)
     half = x3.dtype == torch.bfloat16  # 16-bit data: the first level already resolves the value
+    floored = floor is not None and half and S == 1
     for s in range(S):
         hist_hi.zero_()
-        ext.radix_hist(x3, A, S, N, s, 0, None, hist_hi)
+        ext.radix_hist(x3, A, S, N, s, 0, None, hist_hi, floor.reshape(1).float() if floored else None, None)
         if world > 1:
             dist.all_reduce(hist_hi, group=group)
-        ext.radix_pick(hist_hi, nhi, int(k), None, 0, sel0, thr[s : s + 1] if half else None)
+        ext.radix_pick(hist_hi, nhi, int(k), None, 0, sel0, thr[s : s + 1] if half else None, None)
+        if floored:  # the repeat without the floor: both kernels return at once unless sel0[3] says the floor was too high
+            hist_hi.zero_()
+            ext.radix_hist(x3, A, S, N, s, 0, None, hist_hi, None, sel0)
+            if world > 1:
+                dist.all_reduce(hist_hi, group=group)
+            ext.radix_pick(hist_hi, nhi, int(k), None, 0, sel0, thr[s : s + 1], sel0)
         if not half:
             hist_lo.zero_()
-            ext.radix_hist(x3, A, S, N, s, 1, sel0, hist_lo)
+            ext.radix_hist(x3, A, S, N, s, 1, sel0, hist_lo, None, None)
             if world > 1:
                 dist.all_reduce(hist_lo, group=group)
-            ext.radix_pick(hist_lo, 65536, 0, sel0, 1, sel1, thr[s : s + 1])
+            ext.radix_pick(hist_lo, 65536, 0, sel0, 1, sel1, thr[s : s + 1], None)
         remaining[s : s + 1].copy_((sel0 if half else sel1)[1:2])
     return (thr, remaining) if return_remaining else thr
 

@@ -70,6 +70,22 @@ def test_radix_threshold_exact_value_fp32():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(512, 8192), (37, 1003)])
+def test_radix_threshold_with_a_floor_guess_does_not_depend_on_the_guess(shape):
+    """16-bit data: a floor below the result skips most of the histogram, a floor above it triggers the repeat without a
+    floor on the device; threshold and tie count equal the plain call's either way."""
+    torch.manual_seed(2)
+    x = torch.randn(*shape, device="cuda").to(torch.bfloat16).contiguous()
+    k = shape[0] * 12
+    thr0, rem0 = S.positive_thresholds(x.view(1, 1, -1), k, return_remaining=True)
+    assert thr0.item() == torch.topk(x.float().reshape(-1), k).values[-1].item()
+    for factor in (0.0, 0.5, 0.75, 1.0, 1.5, 100.0):
+        floor = thr0 * factor
+        thr, rem = S.positive_thresholds(x.view(1, 1, -1), k, return_remaining=True, floor=floor)
+        assert thr.item() == thr0.item() and rem.item() == rem0.item(), factor
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("B,N,k", [(64, 4096, 50), (7, 1000, 1), (300, 33000, 700), (4, 256, 0)])
 def test_row_compaction_matches_nonzero(dtype, B, N, k):
