@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 #include <torch/extension.h>
 
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -94,7 +95,7 @@ int64_t encoder_gemm(const Tensor& x, const Tensor& w, const c10::optional<Tenso
                      const c10::optional<Tensor>& gate, int64_t mode, int64_t k, int64_t num_splits,
                      const c10::optional<Tensor>& H, const c10::optional<Tensor>& cand_val,
                      const c10::optional<Tensor>& cand_idx, const Tensor& status, int64_t n_index_offset,
-                     bool resume_topk) {
+                     bool resume_topk, int64_t units) {
   CHECK_T(x, torch::kBFloat16);
   CHECK_T(w, torch::kBFloat16);
   CHECK_T(status, torch::kInt32);
@@ -107,6 +108,7 @@ int64_t encoder_gemm(const Tensor& x, const Tensor& w, const c10::optional<Tenso
   TORCH_CHECK(p.K % 8 == 0 && p.N % 8 == 0, "K and N must be multiples of 8");
   p.num_panels = (p.M + 127) / 128;
   p.num_splits = (int)num_splits;
+  p.units = (int)units;  // 0: num_splits ranges for every panel (pair); else that many work units dealt out raggedly
   const int n_tiles = (p.N + 255) / 256;
   TORCH_CHECK(p.num_splits >= 1 && p.num_splits <= n_tiles, "num_splits must be in [1, number of N tiles]");
   if (bias.has_value()) { CHECK_T(*bias, torch::kFloat32); TORCH_CHECK(bias->numel() == p.N); }
@@ -138,7 +140,10 @@ int64_t encoder_gemm(const Tensor& x, const Tensor& w, const c10::optional<Tenso
   }
   TORCH_CHECK(mode & 3, "mode must request H and/or top-k");
   // bit 3 asks for the CTA-pair kernel; it needs whole pairs of 128-row panels, otherwise the single-CTA kernel runs
-  if ((mode & 8) && (p.num_panels % 2 != 0)) mode &= ~(int64_t)8;
+  if ((mode & 8) && (p.num_panels % 2 != 0)) {
+    mode &= ~(int64_t)8;
+    p.units = 0;  // (a ragged deal was sized for pairs)
+  }
   const CUtensorMap ta = make_bf16_tile_map(x.data_ptr(), p.M, p.K, 128);
   const CUtensorMap tb = make_bf16_tile_map(w.data_ptr(), p.N, p.K, (mode & 8) ? 128 : 256);
   check_cuda(lmsae::enc_gemm_launch(ta, tb, p, (int)mode, at::cuda::getCurrentCUDAStream()), "encoder_gemm launch");
@@ -426,6 +431,9 @@ void sparse_grad_adam(const Tensor& offsets, const Tensor& entries, const Tensor
   p.h = make_hyper(lr, beta1, beta2, eps, step);
   p.update = update ? 1 : 0;
   p.ctas_per_sm = (int)ctas_per_sm;
+  // warp-per-row kernel for short rows unless LMSAE_ADAM_ROWWARP=0 (read once)
+  static const int rowwarp = [] { const char* e = std::getenv("LMSAE_ADAM_ROWWARP"); return (e != nullptr && e[0] == '0') ? 0 : 1; }();
+  p.use_rowwarp = rowwarp;
   if (status.has_value()) { CHECK_T(*status, torch::kInt32); }
   p.status = opt_ptr<const int>(status);
   if (wd_self_scale.has_value()) { CHECK_T(*wd_self_scale, torch::kFloat32); TORCH_CHECK(wd_self_scale->numel() == p.F); }

@@ -99,11 +99,31 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   const bool leader = cta_rank == 0;
   const int unit = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
   const int units_per_split = PAIR ? p.num_panels / 2 : p.num_panels;
-  const int panel = PAIR ? (unit % units_per_split) * 2 + (int)cta_rank : unit % units_per_split;
-  const int split = unit / units_per_split;
+  // ragged deal (p.units != 0): the first `extra` panel units get base + 1 column ranges, the others base; units of one
+  // range index are consecutive within their group, so the CTAs that run together sweep the same B tiles
+  int panel_unit, split, my_splits;
+  if (p.units == 0) {
+    panel_unit = unit % units_per_split;
+    split = unit / units_per_split;
+    my_splits = p.num_splits;
+  } else {
+    const int base = p.units / units_per_split, extra = p.units % units_per_split;
+    const int first = extra * (base + 1);
+    if (unit < first) {
+      panel_unit = unit % extra;
+      split = unit / extra;
+      my_splits = base + 1;
+    } else {
+      const int rest = units_per_split - extra;
+      panel_unit = extra + (unit - first) % rest;
+      split = (unit - first) / rest;
+      my_splits = base;
+    }
+  }
+  const int panel = PAIR ? panel_unit * 2 + (int)cta_rank : panel_unit;
   const int num_n_tiles = (p.N + BN - 1) / BN;
-  const int tile_begin = (int)(((long long)split * num_n_tiles) / p.num_splits);
-  const int tile_end = (int)(((long long)(split + 1) * num_n_tiles) / p.num_splits);
+  const int tile_begin = (int)(((long long)split * num_n_tiles) / my_splits);
+  const int tile_end = (int)(((long long)(split + 1) * num_n_tiles) / my_splits);
   const int num_k_stages = (p.K + BK - 1) / BK;
   const int m0 = panel * BM;
 
@@ -413,6 +433,14 @@ enc_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         p.cand_val[o + s] = valid ? my_slot_val[s * BM] : 0.0f;
         p.cand_idx[o + s] = valid ? my_slot_idx[s * BM] : -1;
       }
+      // a panel with fewer ranges than the lists have room for: its last range also marks the unused lists empty
+      if (split == my_splits - 1) {
+        for (int s = my_splits * KS; s < p.num_splits * KS; ++s) {
+          const long long e = (long long)row * ((long long)p.num_splits * KS) + s;
+          p.cand_val[e] = 0.0f;
+          p.cand_idx[e] = -1;
+        }
+      }
     }
   }
 
@@ -442,7 +470,7 @@ static cudaError_t launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, 
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamicBytes);
   if (e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(p.num_panels * p.num_splits);
+  cfg.gridDim = dim3(p.units != 0 ? p.units * (PAIR ? 2 : 1) : p.num_panels * p.num_splits);
   cfg.blockDim = dim3(NUM_THREADS);
   cfg.dynamicSmemBytes = L::kDynamicBytes;
   cfg.stream = stream;
@@ -466,6 +494,12 @@ int enc_gemm_launch(const CUtensorMap& ta, const CUtensorMap& tb, const EncGemmP
   const bool wh = mode & 1, tk = mode & 2, pair = mode & 8, compact = mode & 16;
   if (pair && (p.num_panels % 2 != 0)) return (int)cudaErrorInvalidValue;
   if (p.heads > 1 && (p.K % (p.heads * BK) != 0 || p.b_rows_per_head < p.N)) return (int)cudaErrorInvalidValue;
+  if (p.units != 0) {  // ragged deal: every panel unit gets at least one range, none more ranges than there are tiles
+    const int panel_units = pair ? p.num_panels / 2 : p.num_panels;
+    const int base = p.units / panel_units, extra = p.units % panel_units;
+    if (base < 1 || base + (extra > 0 ? 1 : 0) != p.num_splits || p.num_splits > (p.N + BN - 1) / BN)
+      return (int)cudaErrorInvalidValue;
+  }
   cudaError_t e;
   if (!tk) {
     if (pair) e = launch_variant<true, false, 6, 0, true>(ta, tb, p, stream);

@@ -11,6 +11,11 @@ struct EncGemmParams {
   int M, N, K;
   int num_panels;
   int num_splits;
+  // Work units (one CTA, or one CTA pair = two adjacent panels) launched: 0 = num_splits per panel unit. Otherwise the
+  // units are dealt out raggedly, units / panel_units to every panel unit and one more to the first units % panel_units
+  // of them (num_splits is then the larger count and sizes the candidate lists), so that a batch whose panel count does
+  // not divide the SM count still occupies every SM.
+  int units;
   const float* bias;
   const float* gate;
   __nv_bfloat16* H;
@@ -125,6 +130,7 @@ struct GradAdamParams {
   int update;
   int f_begin, f_end;  // feature rows handled by this launch
   int ctas_per_sm;     // 0 = fill the GPU (4 per SM); 1..4 = leave registers free for a concurrently running kernel
+  int use_rowwarp;     // != 0: rows of at most 1024 columns (a multiple of 128) take the warp-per-row kernel
   const int* status;   // kernels' status word: a recorded error turns the update into a no-op (nullptr: not checked)
   // Dense gradient rows for a subset of the features, added to the rows rebuilt from the entry lists: feature f takes
   // row extra_row[f] (when >= 0) of the fp32 matrices extra_gD / extra_gE [rows, d] and element extra_row[f] of extra_gb.

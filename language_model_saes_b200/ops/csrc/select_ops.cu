@@ -88,24 +88,47 @@ __device__ __forceinline__ void for_each_positive(const T* __restrict__ x, long 
   const long long chunks_per_row = (N + chunk - 1) / chunk;
   const bool vec_ok = (N % V == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0);
   const uint32_t floor2 = (floor_bits >> 16) * 0x10001u;  // the floor rounded down to 16 bits, in both halves
-  for (long long item = blockIdx.x; item < A * chunks_per_row; item += gridDim.x) {
+  const long long total = A * chunks_per_row;
+  if (vec_ok) {
+    // four chunks per round, all four loads issued before the first is looked at (one CTA of 1024 threads per SM has
+    // no other way to keep enough bytes in flight)
+    constexpr int U = 4;
+    for (long long item0 = blockIdx.x; item0 < total; item0 += (long long)gridDim.x * U) {
+      uint4 raw[U];
+      bool have[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long item = item0 + (long long)u * gridDim.x;
+        have[u] = false;
+        if (item < total) {
+          const long long a = item / chunks_per_row, ch = item - a * chunks_per_row;
+          const long long e = ch * chunk + (long long)threadIdx.x * V;
+          if (e < N) {
+            raw[u] = __ldcs(reinterpret_cast<const uint4*>(x + (a * S + s) * N + e));
+            have[u] = true;
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (!have[u] || Vec<T>::all_below(raw[u], floor2)) continue;
+        uint32_t b[V];
+        Vec<T>::decode(raw[u], b);
+#pragma unroll
+        for (int i = 0; i < V; ++i)
+          if (b[i] != 0 && b[i] >= floor_bits) visit(b[i]);
+      }
+    }
+    return;
+  }
+  for (long long item = blockIdx.x; item < total; item += gridDim.x) {
     const long long a = item / chunks_per_row, ch = item - a * chunks_per_row;
     const T* row = x + (a * S + s) * N;
     const long long e = ch * chunk + (long long)threadIdx.x * V;
     if (e >= N) continue;
-    if (vec_ok) {
-      const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(row + e));
-      if (Vec<T>::all_below(raw, floor2)) continue;
-      uint32_t b[V];
-      Vec<T>::decode(raw, b);
-#pragma unroll
-      for (int i = 0; i < V; ++i)
-        if (b[i] != 0 && b[i] >= floor_bits) visit(b[i]);
-    } else {
-      for (int i = 0; i < V && e + i < N; ++i) {
-        const uint32_t b = positive_bits<T>(row[e + i]);
-        if (b != 0 && b >= floor_bits) visit(b);
-      }
+    for (int i = 0; i < V && e + i < N; ++i) {
+      const uint32_t b = positive_bits<T>(row[e + i]);
+      if (b != 0 && b >= floor_bits) visit(b);
     }
   }
 }

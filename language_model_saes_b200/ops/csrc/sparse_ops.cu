@@ -714,6 +714,154 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Short rows (d <= 1024, a multiple of 128): one WARP per feature row. With rows of 3 KB a CTA per row spends its time in
+// the dependent chain offsets -> entries -> codes -> gathered rows -> parameters, and a block barrier per row for the
+// norm; here sixteen rows are in flight per SM (eight warps per CTA, two CTAs), a lane owns four consecutive columns of
+// every 128-column chunk, the row norm is a warp reduction, and nothing synchronises the block. A two-sided update
+// runs as two launches, one per side. Not supported here (the CTA-per-row kernel
+// takes those launches): extra dense rows, publication to replicas, dense gradient outputs.
+// ---------------------------------------------------------------------------------------------
+constexpr int RW_MAX_CHUNKS = 8;  // d <= 1024
+constexpr int RW_GROUP = 4;       // parameter chunks loaded together (12 x 16 bytes in flight per lane)
+
+// One side of one row. G: gather source (d x_hat for the decoder side, x for the encoder side); coef_l: this lane's
+// entry's coefficient (code for the decoder side, code gradient for the encoder side), row_l / aux_l likewise.
+template <bool IS_D>
+__device__ __forceinline__ void rowwarp_side(const GradAdamParams& p, int f, int e0, int e1, int lane, int nch, float gmul,
+                                             float& gsq_local) {
+  float* W = IS_D ? p.WD : p.WE;
+  float* M1 = IS_D ? p.mD : p.mE;
+  float* M2 = IS_D ? p.vD : p.vE;
+  __nv_bfloat16* SH = IS_D ? p.WD_bf16 : p.WE_bf16;
+  const __nv_bfloat16* G = IS_D ? p.dxhat : p.x;
+  float g[RW_MAX_CHUNKS][4];
+#pragma unroll
+  for (int c = 0; c < RW_MAX_CHUNKS; ++c) g[c][0] = g[c][1] = g[c][2] = g[c][3] = 0.0f;
+  float bias_g = 0.0f;
+  for (int eb = e0; eb < e1; eb += 32) {
+    const int n_e = min(32, e1 - eb);
+    int row_l = 0, aux_l = 0;
+    float coef_l = 0.0f;
+    if (lane < n_e) {
+      const int ent = (int)LMSAE_IDX(p.entries[eb + lane], p.n_codes);
+      row_l = (int)LMSAE_IDX(ent / p.k, p.n_rows);
+      coef_l = IS_D ? p.act[ent] : p.dact[ent];
+      aux_l = (IS_D && p.dxhat_aux != nullptr && ent - row_l * p.k >= p.k_main) ? 1 : 0;
+    }
+    if (!IS_D) bias_g += coef_l;  // summed over the lanes below
+    for (int j = 0; j < n_e; ++j) {
+      const int row = __shfl_sync(0xffffffffu, row_l, j);
+      const float a = __shfl_sync(0xffffffffu, coef_l, j);
+      const __nv_bfloat16* src = (IS_D && __shfl_sync(0xffffffffu, aux_l, j)) ? p.dxhat_aux : G;
+      const __nv_bfloat16* gr = src + (size_t)row * p.d + lane * 4;
+#pragma unroll
+      for (int c = 0; c < RW_MAX_CHUNKS; ++c) {
+        if (c < nch) {
+          const uint2 u = __ldg(reinterpret_cast<const uint2*>(gr + c * 128));
+          const float2 v01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+          const float2 v23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+          g[c][0] = fmaf(a, v01.x, g[c][0]); g[c][1] = fmaf(a, v01.y, g[c][1]);
+          g[c][2] = fmaf(a, v23.x, g[c][2]); g[c][3] = fmaf(a, v23.y, g[c][3]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < RW_MAX_CHUNKS; ++c) {
+    if (c < nch) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        g[c][i] *= gmul;
+        gsq_local += g[c][i] * g[c][i];
+      }
+    }
+  }
+  if (!IS_D) {
+    bias_g = warp_sum(bias_g) * gmul;
+    if (lane == 0) gsq_local += bias_g * bias_g;
+  }
+  if (!p.update) return;
+  const float self_scale = (IS_D && p.wd_self_scale != nullptr) ? p.wd_self_scale[f] * gmul : 0.0f;
+  float norm_sq = 0.0f;
+  const size_t o0 = (size_t)f * p.d + lane * 4, os0 = (size_t)(f - p.state_f0) * p.d + lane * 4;
+#pragma unroll
+  for (int c0 = 0; c0 < RW_MAX_CHUNKS; c0 += RW_GROUP) {
+    if (c0 >= nch) break;
+    float4 w[RW_GROUP], m[RW_GROUP], v[RW_GROUP];
+#pragma unroll
+    for (int q = 0; q < RW_GROUP; ++q) {
+      if (c0 + q < nch) {
+        w[q] = ldcs4(W + o0 + (c0 + q) * 128);
+        m[q] = ldcs4(M1 + os0 + (c0 + q) * 128);
+        v[q] = ldcs4(M2 + os0 + (c0 + q) * 128);
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < RW_GROUP; ++q) {
+      if (c0 + q < nch) {
+        float* gg = g[c0 + q];
+        if (IS_D && self_scale != 0.0f) {
+          gg[0] = fmaf(self_scale, w[q].x, gg[0]); gg[1] = fmaf(self_scale, w[q].y, gg[1]);
+          gg[2] = fmaf(self_scale, w[q].z, gg[2]); gg[3] = fmaf(self_scale, w[q].w, gg[3]);
+        }
+        adam_elem(w[q].x, m[q].x, v[q].x, gg[0], p.h); adam_elem(w[q].y, m[q].y, v[q].y, gg[1], p.h);
+        adam_elem(w[q].z, m[q].z, v[q].z, gg[2], p.h); adam_elem(w[q].w, m[q].w, v[q].w, gg[3], p.h);
+        stcs4(W + o0 + (c0 + q) * 128, w[q]);
+        stcs4(M1 + os0 + (c0 + q) * 128, m[q]);
+        stcs4(M2 + os0 + (c0 + q) * 128, v[q]);
+        if (IS_D) norm_sq += w[q].x * w[q].x + w[q].y * w[q].y + w[q].z * w[q].z + w[q].w * w[q].w;
+        uint2 sh;
+        sh.x = pack_bf16x2(w[q].x, w[q].y);
+        sh.y = pack_bf16x2(w[q].z, w[q].w);
+        *reinterpret_cast<uint2*>(SH + o0 + (c0 + q) * 128) = sh;
+      }
+    }
+  }
+  if (IS_D) {
+    if (p.dec_norm != nullptr || p.norm_sq_accum != nullptr) {
+      norm_sq = warp_sum(norm_sq);
+      if (lane == 0) {
+        if (p.norm_sq_accum != nullptr) p.norm_sq_accum[f] += norm_sq;  // one warp per row and launch
+        else p.dec_norm[f] = sqrtf(norm_sq);
+      }
+    }
+  } else if (lane == 0 && p.bE != nullptr) {
+    float b = p.bE[f], m = p.mbE[f - p.state_f0], v = p.vbE[f - p.state_f0];
+    adam_elem(b, m, v, bias_g, p.h);
+    p.mbE[f - p.state_f0] = m;
+    p.vbE[f - p.state_f0] = v;
+    p.bE[f] = b;
+  }
+}
+
+template <int SIDES>
+__global__ void __launch_bounds__(GA_THREADS, 2)
+sparse_grad_adam_rowwarp_kernel(const GradAdamParams p) {
+  __shared__ float s_gsq[GA_THREADS / 32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float gmul = p.grad_mul != nullptr ? *p.grad_mul : 1.0f;
+  const bool skip = p.status != nullptr && *reinterpret_cast<const volatile int*>(p.status) != 0;  // see the kernel above
+  const int nch = p.d / 128;
+  float gsq_local = 0.0f;
+  const int warps = gridDim.x * (GA_THREADS / 32);
+  for (int f = p.f_begin + blockIdx.x * (GA_THREADS / 32) + warp; f < p.f_end && !skip; f += warps) {
+    const int e0 = p.offsets[f], e1 = p.offsets[f + 1];
+    if constexpr ((SIDES & 1) != 0) rowwarp_side<true>(p, f, e0, e1, lane, nch, gmul, gsq_local);
+    if constexpr ((SIDES & 2) != 0) rowwarp_side<false>(p, f, e0, e1, lane, nch, gmul, gsq_local);
+  }
+  if (p.grad_sq_sum != nullptr) {
+    gsq_local = warp_sum(gsq_local);
+    if (lane == 0) s_gsq[warp] = gsq_local;
+    __syncthreads();
+    if (warp == 0) {
+      float t = lane < GA_THREADS / 32 ? s_gsq[lane] : 0.0f;
+      t = warp_sum(t);
+      if (lane == 0) atomicAdd(p.grad_sq_sum, t);
+    }
+  }
+}
+
 int sparse_grad_adam_launch(const GradAdamParams& p, cudaStream_t stream) {
   if (p.d % 4 != 0) return (int)cudaErrorInvalidValue;
   const int rows = p.f_end - p.f_begin;
@@ -726,6 +874,17 @@ int sparse_grad_adam_launch(const GradAdamParams& p, cudaStream_t stream) {
   const bool doD = p.WD != nullptr, doE = p.WE != nullptr;
   if (!doD && !doE) return (int)cudaErrorInvalidValue;
   if (!(doD && doE) && p.n_pub > 0) return (int)cudaErrorInvalidValue;  // rows are published by two-sided launches only
+  if (p.d <= 128 * RW_MAX_CHUNKS && p.d % 128 == 0 && p.extra_row == nullptr && p.n_pub == 0 && p.gD_out == nullptr &&
+      p.gE_out == nullptr && p.ctas_per_sm == 0 && p.use_rowwarp != 0) {
+    // short rows: a warp per row
+    const int per_cta = GA_THREADS / 32;
+    int rw_blocks = (rows + per_cta - 1) / per_cta;
+    if (rw_blocks > 148 * 2) rw_blocks = 148 * 2;
+    // (a two-sided update is two launches: both sides in one kernel do not fit the register budget of two CTAs per SM)
+    if (doD) sparse_grad_adam_rowwarp_kernel<1><<<rw_blocks, GA_THREADS, 0, stream>>>(p);
+    if (doE) sparse_grad_adam_rowwarp_kernel<2><<<rw_blocks, GA_THREADS, 0, stream>>>(p);
+    return (int)cudaGetLastError();
+  }
   if (doD && doE) {
     if (p.ctas_per_sm >= 1 && p.ctas_per_sm <= 2)
       sparse_grad_adam_kernel<2, 2, 3><<<blocks, GA_THREADS, 0, stream>>>(p);

@@ -110,43 +110,49 @@ class FusedCLTStep:
     def sync_params(self) -> None:
         pass
 
-    def encode(self, x: torch.Tensor, k: int) -> tuple[torch.Tensor, torch.Tensor]:
-        """``x [B, L, d]`` bf16 -> codes ``(idx = layer * F + feature, act) [B, L * k]`` over this rank's features."""
+    def encode(self, x: torch.Tensor, k: int, xt: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+        """``x [B, L, d]`` bf16 -> codes ``(idx = layer * F + feature, act) [B, L * k]`` over this rank's features.
+        ``xt``: the same activations layer-major ``[L, B, d]`` when the caller already has them."""
         B, L, F = x.shape[0], self.L, self.F
         gate_all = self.norm_sq.sqrt().view(L, F) if self.use_gate else None
+        if xt is None:
+            xt = x.transpose(0, 1).contiguous()  # one copy instead of one per layer
         idxs, acts = [], []
         if self.tp == 1:
             for layer in range(L):
                 gate = gate_all[layer] if gate_all is not None else None
-                i, a = K.encoder_topk(x[:, layer].contiguous(), self.WE_bf16[layer], self.bE[layer], gate, k)
-                idxs.append(torch.where(i >= 0, i + layer * F, i))
+                i, a = K.encoder_topk(xt[layer], self.WE_bf16[layer], self.bE[layer], gate, k)
+                idxs.append(i)
                 acts.append(a)
-            return torch.cat(idxs, dim=1).contiguous(), torch.cat(acts, dim=1).contiguous()
-        # feature shards: every layer's local top-k list first, then ONE all-gather of all layers' lists, then the merges
-        loc_g = torch.empty(L, B, k, dtype=torch.float32, device=x.device)
-        loc_i = torch.empty(L, B, k, dtype=torch.int32, device=x.device)
-        for layer in range(L):
-            xl = x[:, layer].contiguous()
-            gate = gate_all[layer] if gate_all is not None else None
-            if xl.is_cuda:
-                cv, ci, _ = K.encoder_topk_candidates(xl, self.WE_bf16[layer], self.bE[layer], gate, k)
-                i_l, g_l = K.topk_merge(cv, ci, k, gate, emit_gated=True)
-            else:
-                i_l, a_l = K.encoder_topk(xl, self.WE_bf16[layer], self.bE[layer], gate, k)
-                g_l = a_l * gate[i_l.clamp_min(0).long()] if gate is not None else a_l
-            loc_g[layer], loc_i[layer] = g_l, i_l
-        all_g = torch.empty(self.tp, L, B, k, dtype=torch.float32, device=x.device)
-        all_i = torch.empty(self.tp, L, B, k, dtype=torch.int32, device=x.device)
-        dist.all_gather_into_tensor(all_g.view(self.tp * L, B, k), loc_g, group=self.tp_group)
-        dist.all_gather_into_tensor(all_i.view(self.tp * L, B, k), loc_i, group=self.tp_group)
-        all_g = all_g.permute(1, 2, 0, 3).reshape(L, B, self.tp * k).contiguous()
-        all_i = all_i.permute(1, 2, 0, 3).reshape(L, B, self.tp * k).contiguous()
-        for layer in range(L):
-            gate = gate_all[layer] if gate_all is not None else None
-            i, a = K.topk_merge(all_g[layer], all_i[layer], k, gate, own=(self.tp_rank * k, (self.tp_rank + 1) * k))
-            idxs.append(torch.where(i >= 0, i + layer * F, i))
-            acts.append(a)
-        return torch.cat(idxs, dim=1).contiguous(), torch.cat(acts, dim=1).contiguous()
+        else:
+            # feature shards: every layer's local top-k list first, then ONE all-gather of all layers' lists, then the merges
+            loc_g = torch.empty(L, B, k, dtype=torch.float32, device=x.device)
+            loc_i = torch.empty(L, B, k, dtype=torch.int32, device=x.device)
+            for layer in range(L):
+                gate = gate_all[layer] if gate_all is not None else None
+                if x.is_cuda:
+                    cv, ci, _ = K.encoder_topk_candidates(xt[layer], self.WE_bf16[layer], self.bE[layer], gate, k)
+                    i_l, g_l = K.topk_merge(cv, ci, k, gate, emit_gated=True)
+                else:
+                    i_l, a_l = K.encoder_topk(xt[layer], self.WE_bf16[layer], self.bE[layer], gate, k)
+                    g_l = a_l * gate[i_l.clamp_min(0).long()] if gate is not None else a_l
+                loc_g[layer], loc_i[layer] = g_l, i_l
+            all_g = torch.empty(self.tp, L, B, k, dtype=torch.float32, device=x.device)
+            all_i = torch.empty(self.tp, L, B, k, dtype=torch.int32, device=x.device)
+            dist.all_gather_into_tensor(all_g.view(self.tp * L, B, k), loc_g, group=self.tp_group)
+            dist.all_gather_into_tensor(all_i.view(self.tp * L, B, k), loc_i, group=self.tp_group)
+            all_g = all_g.permute(1, 2, 0, 3).reshape(L, B, self.tp * k).contiguous()
+            all_i = all_i.permute(1, 2, 0, 3).reshape(L, B, self.tp * k).contiguous()
+            for layer in range(L):
+                gate = gate_all[layer] if gate_all is not None else None
+                i, a = K.topk_merge(all_g[layer], all_i[layer], k, gate, own=(self.tp_rank * k, (self.tp_rank + 1) * k))
+                idxs.append(i)
+                acts.append(a)
+        # layer * F is added to all lists at once (empty slots stay -1)
+        idx = torch.stack(idxs, dim=1)  # [B, L, k]
+        offset = (torch.arange(L, device=x.device, dtype=idx.dtype) * F).view(1, L, 1)
+        idx = torch.where(idx >= 0, idx + offset, idx).view(B, L * k)
+        return idx, torch.stack(acts, dim=1).view(B, L * k)
 
     def _decode(self, idx: torch.Tensor, act: torch.Tensor) -> torch.Tensor:
         """Reconstruction ``[L, B, d]`` fp32 (summed over feature shards, decoder biases added)."""
@@ -165,11 +171,14 @@ class FusedCLTStep:
         K._ext().clt_decode(idx, act, list(self.WD_bf16), None, part)  # bf16 partial rows straight into the symmetric buffer
         return self.comm.all_reduce(L * B).view(L, B, d).float() + self.bD[:, None, :]
 
-    def step(self, x: torch.Tensor, label: torch.Tensor, k: int, lr: float) -> torch.Tensor:
-        """``x [B, L, d]`` normalised bf16 inputs of the L source layers, ``label [L, B, d]`` bf16 targets. Returns the mean
-        loss (0-d device tensor)."""
+    def step(self, x: torch.Tensor, label: torch.Tensor, k: int, lr: float, xt: torch.Tensor | None = None) -> torch.Tensor:
+        """``x [B, L, d]`` normalised bf16 inputs of the L source layers (any strides when ``xt``, the same activations as a
+        contiguous ``[L, B, d]``, comes with it), ``label [L, B, d]`` bf16 targets. Returns the mean loss (0-d device
+        tensor)."""
         B, L, F, d = x.shape[0], self.L, self.F, self.d
-        idx, act = self.encode(x, k)
+        if xt is None:
+            xt = x.transpose(0, 1).contiguous()  # [L, B, d]: the layers' rows for the encoder GEMMs and the encoder-side update
+        idx, act = self.encode(x, k, xt)
         y = self._decode(idx, act)
         self.loss_sum.zero_()
         dy = K.mse_loss_grad(y.view(L * B, d), label.reshape(L * B, d).contiguous(), None, None, 2.0 / (L * B), self.loss_sum)
@@ -193,7 +202,7 @@ class FusedCLTStep:
         (mE, vE), (mb, vb) = self.state["W_E"], self.state["b_E"]
         for s in range(L):  # encoder side, one launch per source layer
             g.F, g.offsets = F, off[s * F : (s + 1) * F + 1]
-            xs = x[:, s].contiguous()
+            xs = xt[s]
             K.sparse_grad_adam(g, act, dact, xs, xs, None, None, None, None, self.WE[s], mE[s], vE[s], self.WE_bf16[s], self.bE[s], mb[s],
                                vb[s], None, None, None, lr, b1, b2, self.eps, self.t, True)  # fmt: skip
         m, v = self.state["b_D"]

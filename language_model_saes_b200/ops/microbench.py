@@ -97,7 +97,7 @@ def main(argv=None):
     if want("hidden3"):
         H3 = torch.empty(M, F, dtype=torch.bfloat16, device=dev)
         st = K.status_buffer(dev)
-        fn3 = lambda: K._ext().encoder_gemm(x, w, b, None, 1 | 4, 0, K.choose_splits(M, F), H3, None, None, st, 0, False)  # noqa: E731
+        fn3 = lambda: K._ext().encoder_gemm(x, w, b, None, 1 | 4, 0, K.choose_splits(M, F), H3, None, None, st, 0, False, 0)  # noqa: E731
         report("encoder_gemm_write_h_3stages", timed(fn3), flops=flops)
         del H3
     if want("hidden_pair"):

@@ -114,6 +114,28 @@ def choose_splits(M: int, N: int, num_sms: int = NUM_SMS_B200) -> int:
     return max(1, min(n_tiles, num_sms // max(panels, 1)))
 
 
+def choose_units(M: int, N: int, pair: bool, num_sms: int = NUM_SMS_B200) -> tuple[int, int]:
+    """Ragged deal of the encoder GEMM's work: ``(units, num_splits)``. A unit is one CTA, or one CTA pair covering two
+    adjacent 128-row panels; with ``P`` panel units and room for ``Q`` units on the GPU every panel unit sweeps
+    ``Q // P`` column ranges and the first ``Q % P`` of them one more, so that batch sizes whose panel count does not
+    divide the SM count (4096 rows = 16 pairs on 74 SM pairs) still occupy every SM. ``num_splits`` is the larger count
+    (it sizes the candidate lists). ``units == 0``: the uniform deal of ``choose_splits`` is already full or the only
+    one possible."""
+    panels = (M + 127) // 128
+    if pair and panels % 2:
+        pair = False
+    P = panels // 2 if pair else panels
+    Q = num_sms // 2 if pair else num_sms
+    n_tiles = (N + 255) // 256
+    uniform = choose_splits(M, N, num_sms)
+    if P >= Q or Q % P == 0:
+        return 0, uniform
+    base, extra = Q // P, Q % P
+    if base + 1 > n_tiles:
+        return 0, min(uniform, n_tiles)
+    return Q, base + 1
+
+
 def candidate_slots(k: int) -> int:
     return 32 if k <= 32 else 64
 
@@ -169,8 +191,19 @@ def encoder_hidden(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, 
         return (h * gate if gate is not None else h).to(torch.bfloat16)
     M, N = x.shape[0], w.shape[0]
     H = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
-    _ext().encoder_gemm(x, w, bias, gate, 1 | _pair_bit(pair), 0, choose_splits(M, N), H, None, None, status_buffer(x.device), 0, False)
+    units, S = _deal(M, N, pair, None)
+    _ext().encoder_gemm(x, w, bias, gate, 1 | _pair_bit(pair), 0, S, H, None, None, status_buffer(x.device), 0, False, units)
     return H
+
+
+def _deal(M: int, N: int, pair: bool | None, num_splits: int | None) -> tuple[int, int]:
+    """(units, num_splits) of an encoder GEMM launch: an explicit ``num_splits`` is a uniform deal, else the ragged one
+    where it fills more SMs (``LMSAE_GEMM_RAGGED=0`` keeps the uniform deal)."""
+    if num_splits:
+        return 0, num_splits
+    if os.environ.get("LMSAE_GEMM_RAGGED", "1") == "0":
+        return 0, choose_splits(M, N)
+    return choose_units(M, N, bool(_pair_bit(pair)))
 
 
 def encoder_topk_candidates(
@@ -192,7 +225,7 @@ def encoder_topk_candidates(
     slices of ``bias`` / ``gate``), its first row as ``n_index_offset`` and, from the second chunk on, the previous
     call's ``(cand_val, cand_idx)`` as ``resume``; the buffers are updated in place and the result equals one sweep."""
     M, N = x.shape[0], w.shape[0]
-    S = num_splits or choose_splits(M, N)
+    units, S = _deal(M, N, pair, num_splits)
     KS = candidate_slots(k)
     C = S * KS
     if resume is not None:
@@ -202,7 +235,8 @@ def encoder_topk_candidates(
         cand_val = torch.empty(M, C, dtype=torch.float32, device=x.device)
         cand_idx = torch.empty(M, C, dtype=torch.int32, device=x.device)
     mode = 2 | (1 if H is not None else 0) | _pair_bit(pair) | (16 if compact_smem else 0)
-    _ext().encoder_gemm(x, w, bias, gate, mode, k, S, H, cand_val, cand_idx, status_buffer(x.device), n_index_offset, resume is not None)
+    _ext().encoder_gemm(x, w, bias, gate, mode, k, S, H, cand_val, cand_idx, status_buffer(x.device), n_index_offset, resume is not None,
+                        units)  # fmt: skip
     return cand_val, cand_idx, C
 
 
@@ -271,7 +305,8 @@ def encoder_topk(
         cv, ci, _ = encoder_topk_candidates(x, w, bias, gate, k, H=H, pair=pair)
         idx, act = topk_merge(cv, ci, k, gate)
     else:
-        _ext().encoder_gemm(x, w, bias, None, 1 | _pair_bit(pair), 0, choose_splits(M, N), H, None, None, status_buffer(x.device), 0, False)
+        units, S = _deal(M, N, pair, None)
+        _ext().encoder_gemm(x, w, bias, None, 1 | _pair_bit(pair), 0, S, H, None, None, status_buffer(x.device), 0, False, units)
         idx, act = row_topk(H, k, gate, None)
     return (idx, act, H) if return_hidden else (idx, act)
 

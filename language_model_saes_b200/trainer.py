@@ -1016,13 +1016,15 @@ class Trainer:
         if mask is not None and not batch.get("_mask_all", None if mask.device.type == "cpu" else bool(mask.all())):
             raise NotImplementedError("the fused cross-layer transcoder path trains on unmasked tokens; set use_fused_kernels=False")
         d = sae.cfg.d_model
-        x = torch.stack([self._normalised_bf16(sae, batch[hp], hp).reshape(-1, d) for hp in sae.cfg.hook_points_in], dim=1)
+        # layer-major [layers, tokens, d]: what the per-layer GEMMs and the update kernels read
+        xt = torch.stack([self._normalised_bf16(sae, batch[hp], hp).reshape(-1, d) for hp in sae.cfg.hook_points_in], dim=0)
+        x = xt.transpose(0, 1)
         y = torch.stack([self._normalised_bf16(sae, batch[hp], hp).reshape(-1, d) for hp in sae.cfg.hook_points_out], dim=0)
         k = self._current_k(sae)
         if k is not None:
             sae.set_current_k(k)
         lr = float(self.cfg.lr) * (self._lr_lambda(self.cur_step) if self._lr_lambda is not None else 1.0)
-        loss = f.step(x, y, sae.current_k, lr)
+        loss = f.step(x, y, sae.current_k, lr, xt=xt)
         if not self.cfg.skip_metrics_calculation and (self.cur_step + 1) % self.cfg.log_frequency == 0:
             out = {"losses/overall_loss": float(loss), "losses/mse_loss": float(loss)}
             out.update(self._details({}, lr))

@@ -124,7 +124,44 @@ def test_sparse_decode_and_loss(B, k, F, d):
     assert torch.allclose(loss2[0], rls, rtol=1e-4)
 
 
-@pytest.mark.parametrize("B,k,F,d", [(64, 8, 256, 128), (512, 50, 4096, 1024), (100, 3, 1000, 4096)])
+@pytest.mark.parametrize("d", [256, 768, 1536])  # warp-per-row kernel (short rows) and CTA-per-row kernel
+@pytest.mark.parametrize("side", ["decoder", "encoder"])
+def test_one_sided_sparse_grad_adam_matches_the_plain_statement(d, side):
+    """One-sided launches (decoder side with a norm penalty's self-scale and accumulated squared norms, encoder side with
+    the bias) against the wrapper's plain-torch path on CPU copies of the same tensors, twice in a row."""
+    B, k, F = 300, 6, 700
+    idx, act = _codes(B, k, F, seed=5)
+    g = torch.Generator().manual_seed(7)
+    dact = torch.randn(B, k, generator=g)
+    dact[idx.cpu() < 0] = 0
+    rows = (torch.randn(B, d, generator=g) * 0.1).to(torch.bfloat16)
+    W, m, v = torch.randn(F, d, generator=g), torch.rand(F, d, generator=g) * 0.01, torch.rand(F, d, generator=g) * 0.01
+    b, mb, vb = torch.randn(F, generator=g), torch.rand(F, generator=g) * 0.01, torch.rand(F, generator=g) * 0.01
+    scale = torch.rand(F, generator=g) * 0.1
+    cpu = dict(idx=idx.cpu(), act=act.cpu(), dact=dact, rows=rows, W=W, m=m, v=v, W16=W.to(torch.bfloat16), b=b, mb=mb, vb=vb,
+               scale=scale, acc=torch.zeros(F))  # fmt: skip
+    gpu = {n_: t.clone().to(DEV) for n_, t in cpu.items()}
+
+    def run(t, step):
+        groups = K.FeatureGroups(F, B * k, t["idx"].device).build(t["idx"])
+        if side == "decoder":
+            K.sparse_grad_adam(groups, t["act"], t["dact"], t["rows"], t["rows"], t["W"], t["m"], t["v"], t["W16"], None, None, None, None,
+                               None, None, None, None, None, None, 1e-3, 0.9, 0.999, 1e-8, step, True, wd_self_scale=t["scale"],
+                               norm_sq_accum=t["acc"])  # fmt: skip
+        else:
+            K.sparse_grad_adam(groups, t["act"], t["dact"], t["rows"], t["rows"], None, None, None, None, t["W"], t["m"], t["v"], t["W16"],
+                               t["b"], t["mb"], t["vb"], None, None, None, 1e-3, 0.9, 0.999, 1e-8, step, True)  # fmt: skip
+
+    for step in (1, 2):
+        run(cpu, step)
+        run(gpu, step)
+        K.check_status(torch.device(DEV))
+    for n_ in ("W", "m", "v", "b", "mb", "vb", "acc"):
+        assert torch.allclose(gpu[n_].cpu(), cpu[n_], atol=2e-5, rtol=2e-4), (n_, float((gpu[n_].cpu() - cpu[n_]).abs().max()))
+    assert torch.allclose(gpu["W16"].float().cpu(), cpu["W"], atol=2e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("B,k,F,d", [(64, 8, 256, 128), (300, 20, 1500, 768), (512, 50, 4096, 1024), (100, 3, 1000, 4096)])
 def test_sparse_grad_adam(B, k, F, d):
     idx, act = _codes(B, k, F, seed=11)
     g = torch.Generator().manual_seed(13)
