@@ -66,6 +66,31 @@ def test_encoder_topk_fused(M, N, Kd, k, use_gate, pair):
     assert (srt[:, 1:] != srt[:, :-1]).all()
 
 
+@pytest.mark.parametrize("M,N,pair", [(1024, 8192, True), (768, 6144, True), (640, 2560, False)])
+def test_encoder_gemm_with_a_ragged_deal_of_column_ranges(M, N, pair, monkeypatch):
+    """``LMSAE_GEMM_RAGGED=1``: panel units get unequal numbers of column ranges so that every SM (pair) has work; the
+    unused candidate lists of the panels with fewer ranges are marked empty. Same codes and pre-activations as the
+    plain product."""
+    monkeypatch.setenv("LMSAE_GEMM_RAGGED", "1")
+    units, splits = K.choose_units(M, N, pair)
+    assert units > 0 and units % ((M // 128) // (2 if pair else 1)) != 0  # the deal really is ragged for these shapes
+    x, w, b, gate = _mk(M, N, 128, seed=4)
+    k = 24
+    idx, act = K.encoder_topk(x, w, b, gate, k, pair=pair)
+    H = K.encoder_hidden(x, w, b, pair=pair)
+    K.check_status(x.device)
+    h = K.ref_hidden(x, w, b)
+    assert (H.float() - h).abs().max().item() < 2e-2 * max(1.0, h.abs().max().item())
+    g = torch.where(h * gate > 0, h * gate, torch.zeros_like(h))
+    kth = torch.topk(g, k, dim=-1).values[:, -1:]
+    dense = _codes_to_dense(idx, act, N)
+    sel = dense != 0
+    assert (sel.sum(-1) == (g > 0).sum(-1).clamp(max=k)).all()
+    gsel = torch.where(sel, g, torch.full_like(g, float("inf")))
+    assert (gsel.min(-1).values >= kth.squeeze(-1) - 1e-3).all()
+    assert torch.allclose(dense[sel], h[sel], atol=2e-3, rtol=2e-3)
+
+
 @pytest.mark.parametrize("k", [16, 100, 512])
 def test_row_topk(k):
     M, N = 64, 4096
