@@ -66,7 +66,7 @@ def test_encoder_topk_fused(M, N, Kd, k, use_gate, pair):
     assert (srt[:, 1:] != srt[:, :-1]).all()
 
 
-@pytest.mark.parametrize("M,N,pair", [(1024, 8192, True), (768, 6144, True), (640, 2560, False)])
+@pytest.mark.parametrize("M,N,pair", [(1024, 8192, True), (768, 8192, True), (640, 8192, False)])
 def test_encoder_gemm_with_a_ragged_deal_of_column_ranges(M, N, pair, monkeypatch):
     """``LMSAE_GEMM_RAGGED=1``: panel units get unequal numbers of column ranges so that every SM (pair) has work; the
     unused candidate lists of the panels with fewer ranges are marked empty. Same codes and pre-activations as the
