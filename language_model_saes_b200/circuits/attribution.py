@@ -546,7 +546,9 @@ def _extract_topk_pairwise_attributions(q_side: NodeIndexedMatrix, k_side: NodeI
     q_role = q_top.dimensions[0] + k_top.dimensions[1]
     k_role = q_top.dimensions[1] + k_top.dimensions[0]
     n = min(topk, int((values != 0).sum()))
-    top_v, top_i = torch.topk(values, n)
+    # the strongest NON-ZERO entries: an entry zeroed by the de-duplication above (or absent from the graph) must not
+    # outrank a negative one and come back labelled with a pair whose true term is not zero
+    top_v, top_i = torch.topk(values.masked_fill(values == 0, float("-inf")), n)
     return NodeIndexed(top_v, (q_role.offsets_to_nodes(top_i), k_role.offsets_to_nodes(top_i)))
 
 
