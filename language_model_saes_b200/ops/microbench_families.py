@@ -126,15 +126,15 @@ def main(argv=None):
         # decoder-side sparse gradient + Adam of a cross-layer transcoder's last target layer: 12 source layers x 24576
         # features, rows of 768 columns, 64 codes per token and source layer on 2048 tokens (5.3 codes per feature)
         B, L, Fd, d, k = 2048, a.clt_layers, 24576, 768, 64
-        F = L * Fd
+        n_feat = L * Fd
         idx = torch.cat([torch.randint(0, Fd, (B, k), device=dev, dtype=torch.int32) + l * Fd for l in range(L)], dim=1).contiguous()
         act = torch.rand(B, L * k, device=dev)
         dy = torch.randn(B, d, device=dev).to(torch.bfloat16)
-        W = torch.randn(F, d, device=dev) / d**0.5
+        W = torch.randn(n_feat, d, device=dev) / d**0.5
         m, v = torch.zeros_like(W), torch.zeros_like(W)
         W16 = W.to(torch.bfloat16)
-        acc = torch.zeros(F, device=dev)
-        groups = K.FeatureGroups(F, idx.numel(), dev).build(idx)
+        acc = torch.zeros(n_feat, device=dev)
+        groups = K.FeatureGroups(n_feat, idx.numel(), dev).build(idx)
         step = [0]
 
         def decoder_side():
@@ -143,8 +143,8 @@ def main(argv=None):
                                2e-4, 0.9, 0.999, 1e-8, step[0], True, norm_sq_accum=acc)  # fmt: skip
 
         t = _timeit(decoder_side, a.iters, a.warmup, flush)
-        gbs = F * d * 26 / t[0] / 1e6
-        print(json.dumps({"case": f"sparse_grad_adam_decoder_side_{F}x768_5codes_per_feature", "ms_ours": round(t[0], 4), "gbs": round(gbs, 1),
+        gbs = n_feat * d * 26 / t[0] / 1e6
+        print(json.dumps({"case": f"sparse_grad_adam_decoder_side_{n_feat}x768_5codes_per_feature", "ms_ours": round(t[0], 4), "gbs": round(gbs, 1),
                           "fraction_of_measured_copy": round(gbs / 6547.2, 3), "clocks": sampler[0].stop()}), flush=True)  # fmt: skip
         sampler[0] = ClockSampler(torch.cuda.current_device())
         sampler[0].start()
