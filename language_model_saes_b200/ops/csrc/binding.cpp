@@ -439,13 +439,21 @@ void sparse_grad_adam(const Tensor& offsets, const Tensor& entries, const Tensor
   if (wd_self_scale.has_value()) { CHECK_T(*wd_self_scale, torch::kFloat32); TORCH_CHECK(wd_self_scale->numel() == p.F); }
   p.wd_self_scale = opt_ptr<const float>(wd_self_scale);
   if (extra_row.has_value()) {
-    TORCH_CHECK(extra_gD.has_value() && extra_gE.has_value(), "extra gradient rows come with both matrices");
-    CHECK_T(*extra_row, torch::kInt32); CHECK_T(*extra_gD, torch::kFloat32); CHECK_T(*extra_gE, torch::kFloat32);
-    TORCH_CHECK(extra_row->numel() == p.F && extra_gD->dim() == 2 && extra_gD->size(1) == p.d && extra_gE->sizes() == extra_gD->sizes());
+    // dense gradient rows for one or both matrices (a side without rows passes nothing)
+    TORCH_CHECK(extra_gD.has_value() || extra_gE.has_value(), "extra gradient rows need at least one matrix");
+    CHECK_T(*extra_row, torch::kInt32);
+    TORCH_CHECK(extra_row->numel() == p.F, "extra_row: one entry per feature");
+    int64_t n_extra = -1;
+    for (const auto* g : {&extra_gD, &extra_gE}) {
+      if (!g->has_value()) continue;
+      CHECK_T(**g, torch::kFloat32);
+      TORCH_CHECK((*g)->dim() == 2 && (*g)->size(1) == p.d && (n_extra < 0 || (*g)->size(0) == n_extra), "extra gradient rows must be [rows, d]");
+      n_extra = (*g)->size(0);
+    }
     p.extra_row = extra_row->data_ptr<int>();
-    p.extra_gD = extra_gD->data_ptr<float>();
-    p.extra_gE = extra_gE->data_ptr<float>();
-    if (extra_gb.has_value()) { CHECK_T(*extra_gb, torch::kFloat32); TORCH_CHECK(extra_gb->numel() == extra_gD->size(0)); }
+    p.extra_gD = opt_ptr<const float>(extra_gD);
+    p.extra_gE = opt_ptr<const float>(extra_gE);
+    if (extra_gb.has_value()) { CHECK_T(*extra_gb, torch::kFloat32); TORCH_CHECK(extra_gb->numel() == n_extra); }
     p.extra_gb = opt_ptr<const float>(extra_gb);
   }
   if (!pub_table.empty()) {

@@ -339,6 +339,7 @@ struct RowPredicate {
   // float sorts below them)
   bool raw16;
   unsigned t2;  // the threshold's pattern in both halves of a word
+  bool raw16_nonzero;  // bf16 rows, "keep what is not zero": a packed test of the 15 magnitude bits
 };
 
 // bit i of the two masks: element c + i is kept outright / equals the threshold
@@ -348,6 +349,15 @@ __device__ __forceinline__ void rc_classify(const uint4& u, long long c, long lo
   constexpr int V = RowVec<T>::V;
   m_strict = m_tie = 0;
   if constexpr (V == 8) {
+    if (q.raw16_nonzero) {  // (+0 and -0 are both "zero"; elements past the end of the row were loaded as zeros)
+      const unsigned w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const unsigned g = __vcmpne2(w[j] & 0x7fff7fffu, 0u);
+        m_strict |= ((g & 1u) | ((g >> 15) & 2u)) << (2 * j);
+      }
+      return;
+    }
     if (q.raw16) {  // (elements past the end of the row were loaded as zeros: never above or equal to a positive threshold)
       const unsigned w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
@@ -361,6 +371,18 @@ __device__ __forceinline__ void rc_classify(const uint4& u, long long c, long lo
       }
       return;
     }
+  }
+  if (q.col_thr != nullptr && c + V <= end && (c & 3) == 0) {
+    // a whole vector against its columns' thresholds, fetched four at a time
+    float th[V];
+#pragma unroll
+    for (int j = 0; j < V / 4; ++j) {
+      const float4 t4 = __ldg(reinterpret_cast<const float4*>(q.col_thr + c) + j);
+      th[4 * j] = t4.x; th[4 * j + 1] = t4.y; th[4 * j + 2] = t4.z; th[4 * j + 3] = t4.w;
+    }
+#pragma unroll
+    for (int i = 0; i < V; ++i) m_strict |= (unsigned)(RowVec<T>::get(u, i) > th[i]) << i;
+    return;
   }
 #pragma unroll
   for (int i = 0; i < V; ++i) {
@@ -399,6 +421,7 @@ row_compact_kernel(const T* __restrict__ x, int B, long long N, int cap, int* __
   q.col_thr = col_thr;
   q.raw16 = false;
   q.t2 = 0u;
+  q.raw16_nonzero = V == 8 && !q.has_thr && col_thr == nullptr;
   if constexpr (V == 8) {
     const __nv_bfloat16 tb = __float2bfloat16(q.t);
     q.raw16 = q.has_thr && q.t > 0.0f && __bfloat162float(tb) == q.t;

@@ -541,11 +541,11 @@ sparse_grad_adam_kernel(const GradAdamParams p) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) gD[v][i] = gE[v][i] = 0.0f;
         if (xr >= 0 && in[v]) {
-          if constexpr (doD) {
+          if (doD && p.extra_gD != nullptr) {
             const float4 a = *reinterpret_cast<const float4*>(p.extra_gD + (size_t)xr * p.d + c[v]);
             gD[v][0] = a.x; gD[v][1] = a.y; gD[v][2] = a.z; gD[v][3] = a.w;
           }
-          if constexpr (doE) {
+          if (doE && p.extra_gE != nullptr) {
             const float4 b = *reinterpret_cast<const float4*>(p.extra_gE + (size_t)xr * p.d + c[v]);
             gE[v][0] = b.x; gE[v][1] = b.y; gE[v][2] = b.z; gE[v][3] = b.w;
           }

@@ -41,6 +41,7 @@ import torch.distributed as dist
 from ..parallel.mesh import mesh_dim_size, mesh_group
 from . import sae_kernels as K
 from . import select_kernels as S
+from .fused_step import _mm_f32
 
 
 class FusedCrosscoderStep:
@@ -118,7 +119,6 @@ class FusedCrosscoderStep:
         if trainer_cfg is not None:
             checks += [
                 (trainer_cfg.sparsity_loss_type in (None, "tanh"), "sparsity loss other than tanh"),
-                (not trainer_cfg.lp_coefficient, "lp loss"),
                 (not trainer_cfg.auxk_coefficient, "aux-k loss"),
                 (trainer_cfg.optimizer_class == "adam", "optimizer is not adam"),
                 (trainer_cfg.amp_dtype == torch.bfloat16, "amp dtype is not bf16"),
@@ -163,9 +163,15 @@ class FusedCrosscoderStep:
         return self.comm.all_reduce(B) if self.head_size > 1 else P
 
     def step(self, x: torch.Tensor, lr: float, l1_coefficient: float = 0.0, tanh_stretch: float = 4.0,
-             row_weight: torch.Tensor | None = None) -> torch.Tensor:  # fmt: skip
+             row_weight: torch.Tensor | None = None, lp_coefficient: float = 0.0) -> torch.Tensor:  # fmt: skip
         """``x``: normalised bf16 activations ``[B, H_l, d]`` of this rank's heads (they are also the labels). Returns the
-        mean loss over tokens and this rank's heads (0-d device tensor); ``self.last`` holds its parts."""
+        mean loss over tokens and this rank's heads (0-d device tensor); ``self.last`` holds its parts.
+
+        ``lp_coefficient``: weight of the pre-activation penalty ``sum_f relu(theta_f - S_bf) * ||W_D,h row f||`` (mean over
+        tokens and heads; models/sparse_dictionary.py:928-936 of the reference project), which pulls the summed
+        pre-activations of INACTIVE features towards their thresholds. It is dense in ``S``: its encoder gradient is one
+        more GEMM per head (``1[S < theta]^T . x_h``, handed to the update kernel as dense gradient rows), its other
+        gradients are column sums of ``S`` against the thresholds."""
         assert row_weight is None, "token masks are not supported on this path"
         B, H_l, d = x.shape
         H, F, cap = self.H, self.F, self.cap
@@ -194,6 +200,21 @@ class FusedCrosscoderStep:
         l_s_sum = torch.zeros((), dtype=torch.float32, device=x.device)
         per_head = []
         c = float(tanh_stretch)
+        lp = None
+        if lp_coefficient:
+            c_lp = lp_coefficient / (B * H)
+            Sf = S_sum.float()
+            below = Sf < theta  # [B, F]: where the penalty is active
+            count = below.sum(0).float()  # per feature: tokens below the threshold
+            gap = torch.relu(theta - Sf).sum(0)  # per feature: summed distance to the threshold
+            n_local = self.dec_norm.sum(0)  # [F]: norms summed over this rank's heads ...
+            n_all = n_local.clone()
+            if self.head_size > 1:  # ... and over all heads: the shared sum feels every head's term
+                dist.all_reduce(n_all, group=self.head_group)
+            dtheta += c_lp * n_local * count  # (summed over the head ranks below, with the rest of d theta)
+            lp = {"mask": below.to(torch.bfloat16), "row_scale": -c_lp * n_all, "gb": -c_lp * n_all * count, "gap": gap,
+                  "rows": torch.arange(F, dtype=torch.int32, device=x.device), "c": c_lp}  # fmt: skip
+            l_p_sum = c_lp * (gap * n_local).sum() * H / H_l  # mean over tokens and THIS rank's heads
         for h in range(H_l):
             xh = x[:, h].contiguous()
             n_h = self.dec_norm[h]
@@ -213,6 +234,9 @@ class FusedCrosscoderStep:
                 per_feat = torch.zeros(F + 1024, dtype=torch.float32, device=x.device)
                 per_feat.index_add_(0, scat, (coef * act * sech2 * active).reshape(-1))
                 self_scale = per_feat[:F] / n_h
+            if lp is not None:  # the penalty's pull on this head's decoder norms: d / d W_D[f] = c * gap_f * W_D[f] / ||W_D[f]||
+                pull = lp["c"] * lp["gap"] / n_h
+                self_scale = pull if self_scale is None else self_scale + pull
             dS_h = dact * active
             dS += dS_h
             # threshold gradient: dense part (reconstruction gradient at every entry inside the window) ...
@@ -233,17 +257,22 @@ class FusedCrosscoderStep:
         b1, b2 = self.betas
         for h, (xh, act, dxhat, self_scale) in enumerate(per_head):
             (mE, vE), (mD, vD), (mb, vb) = self.state["W_E"], self.state["W_D"], self.state["b_E"]
+            extra = None
+            if lp is not None:  # dense encoder gradient rows of the pre-activation penalty: -c N_f (1[S < theta]^T x_h)[f, :]
+                gE = _mm_f32(lp["mask"].t(), xh) * lp["row_scale"].unsqueeze(1)
+                extra = (lp["rows"], None, gE, lp["gb"])
             K.sparse_grad_adam(self.groups, act, dS, xh, dxhat, self.WD[h], mD[h], vD[h], self.WD_bf16[h], self.WE[h], mE[h], vE[h],
                                self.WE_bf16[h], self.bE[h], mb[h], vb[h], self.dec_norm[h], None, None, lr, b1, b2, self.eps, self.t,
-                               True, wd_self_scale=self_scale)  # fmt: skip
+                               True, wd_self_scale=self_scale, extra=extra)  # fmt: skip
             m, v = self.state["b_D"]
             K.adam_flat(self.bD[h], K.colsum_bf16(dxhat), m[h], v[h], lr, b1, b2, self.eps, self.t)
         m, v = self.state["log_theta"]
         K.adam_flat(self.log_theta, dtheta * theta, m, v, lr * self.jumprelu_lr_factor, b1, b2, self.eps, self.t)
         l_rec = (self.loss_sum / (B * H_l)).squeeze(0)
         l_s = l1_coefficient * l_s_sum / (B * H_l)
-        self.last = {"l_rec": l_rec, "l_s": l_s, "l0": valid.sum() / B}
-        return l_rec + l_s
+        l_p = l_p_sum if lp is not None else torch.zeros((), device=x.device)
+        self.last = {"l_rec": l_rec, "l_s": l_s, "l_p": l_p, "l0": valid.sum() / B}
+        return l_rec + l_s + l_p
 
     def optimizer_state(self) -> dict:
         out = {"step": self.t}

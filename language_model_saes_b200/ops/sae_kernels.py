@@ -604,8 +604,10 @@ def sparse_grad_adam(
             row_of, xD, xE, xb = extra
             sel = (row_of >= 0).nonzero().squeeze(-1)
             r = row_of[sel].long()
-            gD[sel] += xD[r]
-            gE[sel] += xE[r]
+            if xD is not None:
+                gD[sel] += xD[r]
+            if xE is not None:
+                gE[sel] += xE[r]
             if xb is not None:
                 gb[sel] += xb[r]
         mul = float(grad_mul) if grad_mul is not None else 1.0

@@ -174,12 +174,14 @@ def dense_rows_to_sparse(acts: torch.Tensor, cap: int | None = None) -> tuple[to
     ext = K._ext()
     B = acts.shape[0]
     nnz = torch.empty(B, dtype=torch.int32, device=acts.device)
+    seg = None
     if cap is None:
-        ext.row_compact(acts, None, None, nnz, None, None, None, None, None, None)
+        seg = torch.empty(B, 8, 2, dtype=torch.int32, device=acts.device)  # the counting pass leaves them for the compaction
+        ext.row_compact(acts, None, None, nnz, None, None, None, None, None, seg)
         cap = max(8, -(-int(nnz.max()) // 8) * 8)
     idx = torch.empty(B, cap, dtype=torch.int32, device=acts.device)
     val = torch.empty(B, cap, dtype=torch.float32, device=acts.device)
-    ext.row_compact(acts, idx, val, nnz, None, None, None, None, None, None)
+    ext.row_compact(acts, idx, val, nnz, None, None, None, None, None, seg)
     return idx, val
 
 

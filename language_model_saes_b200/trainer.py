@@ -990,11 +990,13 @@ class Trainer:
         x = torch.stack(cols, dim=1)
         lr = float(self.cfg.lr) * (self._lr_lambda(self.cur_step) if self._lr_lambda is not None else 1.0)
         l1 = self._l1_coefficient() if self.cfg.sparsity_loss_type == "tanh" else 0.0
-        loss = f.step(x, lr, l1_coefficient=l1, tanh_stretch=self.cfg.tanh_stretch_coefficient)
+        loss = f.step(x, lr, l1_coefficient=l1, tanh_stretch=self.cfg.tanh_stretch_coefficient,
+                      lp_coefficient=float(self.cfg.lp_coefficient or 0.0))
         if not self.cfg.skip_metrics_calculation and (self.cur_step + 1) % self.cfg.log_frequency == 0:
             last = {k: float(v) for k, v in f.last.items()}
             out = {"losses/overall_loss": float(loss), "losses/mse_loss": last["l_rec"], "losses/sparsity_loss": last["l_s"],
-                   "metrics/l0_candidates": last["l0"], "details/list_overflow_tokens": int(f.list_overflow)}  # fmt: skip
+                   "losses/lp_loss": last["l_p"], "metrics/l0_candidates": last["l0"],
+                   "details/list_overflow_tokens": int(f.list_overflow)}  # fmt: skip
             out.update(self._details({"l1_coefficient": l1}, lr))
             out.update(sae.log_statistics())
             self._emit(sae, out)

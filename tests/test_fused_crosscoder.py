@@ -30,8 +30,8 @@ def _model(dev, H=3, d=64, F=512, thr=-0.5):
 
 
 @pytest.mark.parametrize("dev", DEVICES)
-@pytest.mark.parametrize("l1", [0.0, 3e-2])
-def test_fused_crosscoder_step_matches_autograd(dev, l1):
+@pytest.mark.parametrize("l1,lp", [(0.0, 0.0), (3e-2, 0.0), (0.0, 2e-3), (3e-2, 2e-3)])
+def test_fused_crosscoder_step_matches_autograd(dev, l1, lp):
     H, d, F, B, lr, steps = 3, 64, 512, 256, 1e-3, 4
     ref = _model(dev, H, d, F)
     fused_model = copy.deepcopy(ref)
@@ -51,11 +51,14 @@ def test_fused_crosscoder_step_matches_autograd(dev, l1):
         opt.zero_grad()
         batch = {f"s{h}": x[:, h].float() for h in range(H)} | {"tokens": tokens}
         with torch.autocast(dev, dtype=torch.bfloat16, enabled=dev == "cuda"):
-            out = ref.compute_loss(batch, sparsity_loss_type="tanh" if l1 else None, l1_coefficient=l1, return_aux_data=True)
+            out = ref.compute_loss(batch, sparsity_loss_type="tanh" if l1 else None, l1_coefficient=l1, lp_coefficient=lp,
+                                   return_aux_data=True)  # fmt: skip
         out["loss"].backward()
         opt.step()
         ref_losses.append(float(out["loss"].detach()))
-        fused_losses.append(float(engine.step(x, lr, l1_coefficient=l1)))
+        fused_losses.append(float(engine.step(x, lr, l1_coefficient=l1, lp_coefficient=lp)))
+        if lp:
+            assert float(engine.last["l_p"]) > 0 and abs(float(engine.last["l_p"]) - float(out["l_p"].mean())) < 3e-2 * float(out["l_p"].mean())
     assert int(engine.list_overflow) == 0
     r, f = torch.tensor(ref_losses), torch.tensor(fused_losses)
     tol = 3e-2 if dev == "cuda" else 2e-3  # (the GPU reference runs under bf16 autocast)
@@ -71,8 +74,8 @@ def test_fused_crosscoder_step_matches_autograd(dev, l1):
 
 
 @pytest.mark.parametrize("dev", DEVICES)
-@pytest.mark.parametrize("l1", [0.0, 3e-2])
-def test_jumprelu_sae_is_the_one_head_case_of_the_fused_step(dev, l1):
+@pytest.mark.parametrize("l1,lp", [(0.0, 0.0), (3e-2, 0.0), (3e-2, 2e-3)])
+def test_jumprelu_sae_is_the_one_head_case_of_the_fused_step(dev, l1, lp):
     """A JumpReLU ``SparseAutoEncoder`` on the same step (parameters viewed with a head axis of one) against autograd on the
     model: losses, every parameter after a few Adam steps, and the optimizer state in the model's parameter shapes."""
     from language_model_saes_b200.models.sae import SAEConfig, SparseAutoEncoder
@@ -107,11 +110,12 @@ def test_jumprelu_sae_is_the_one_head_case_of_the_fused_step(dev, l1):
         x = (x * (d**0.5 / x.norm(dim=-1).mean())).to(torch.bfloat16)
         opt.zero_grad()
         with torch.autocast(dev, dtype=torch.bfloat16, enabled=dev == "cuda"):
-            out = ref.compute_loss({"h": x.float(), "tokens": tokens}, sparsity_loss_type="tanh" if l1 else None, l1_coefficient=l1)
+            out = ref.compute_loss({"h": x.float(), "tokens": tokens}, sparsity_loss_type="tanh" if l1 else None, l1_coefficient=l1,
+                                   lp_coefficient=lp)  # fmt: skip
         out["loss"].backward()
         opt.step()
         ref_losses.append(float(out["loss"].detach()))
-        fused_losses.append(float(engine.step(x.unsqueeze(1), lr, l1_coefficient=l1)))
+        fused_losses.append(float(engine.step(x.unsqueeze(1), lr, l1_coefficient=l1, lp_coefficient=lp)))
     r, f = torch.tensor(ref_losses), torch.tensor(fused_losses)
     assert torch.allclose(r, f, rtol=3e-2 if dev == "cuda" else 2e-3), (ref_losses, fused_losses)
     start = dict(make().named_parameters())

@@ -513,13 +513,13 @@ def test_in_place_all_reduce_kernel_and_head_parallel_fused_crosscoder():
         opt.zero_grad()
         batch = {f"s{2 * rank + h}": mine[:, h].float() for h in range(2)} | {"tokens": tokens}
         with torch.autocast("cuda", dtype=torch.bfloat16):
-            out = ref.compute_loss(batch, sparsity_loss_type="tanh", l1_coefficient=3e-2, return_aux_data=True)
+            out = ref.compute_loss(batch, sparsity_loss_type="tanh", l1_coefficient=3e-2, lp_coefficient=2e-3, return_aux_data=True)
         out["loss"].backward()
         thr = ref.activation_function.log_jumprelu_threshold
         dist.all_reduce(thr.grad, group=group)  # shared parameter: the trainer sums its gradient over the head ranks
         opt.step()
         ref_losses.append(float(out["loss"].detach()))
-        local = engine.step(mine, lr, l1_coefficient=3e-2)
+        local = engine.step(mine, lr, l1_coefficient=3e-2, lp_coefficient=2e-3)
         dist.all_reduce(local, group=group)
         fused_losses.append(float(local) / 2)
     K.check_status(dev)
