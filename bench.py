@@ -16,11 +16,8 @@ import argparse
 import gc
 import json
 import os
-import statistics
-import subprocess
 import sys
 import tempfile
-import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))

@@ -33,8 +33,6 @@ takes it too: its parameters are viewed as ``[1, F, d]`` / ``[1, F]`` / ``[1, d]
 
 from __future__ import annotations
 
-import math
-
 import torch
 import torch.distributed as dist
 
