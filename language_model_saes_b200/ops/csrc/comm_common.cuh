@@ -40,6 +40,7 @@ __device__ __forceinline__ bool signal_peers_when_grid_done(const PeerTable& pt,
   __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
+    lmsae_jitter();
     const unsigned prev = atomicAdd(done_counter, 1u);
     s_last = (prev == gridDim.x - 1);
     if (s_last) *done_counter = 0;
@@ -65,6 +66,7 @@ __device__ __forceinline__ bool wait_all_sources(const PeerTable& pt, int phase,
   if (threadIdx.x < 32) {
     long long waited = 0;
     if ((int)threadIdx.x < pt.world) {
+      lmsae_jitter();
       const long long t0 = clock64();
       if (!wait_flag_sys(flag_slot(pt, pt.rank, phase, threadIdx.x), epoch)) {
         report_status(status, kTimeoutPeerFlag, phase, (int)threadIdx.x);

@@ -65,6 +65,10 @@ __global__ void __launch_bounds__(SC_THREADS)
 sparse_decode_scatter_kernel(const PeerTable pt, const int* __restrict__ idx, const float* __restrict__ val, int B, int k,
                              int d, int F, const __nv_bfloat16* __restrict__ W, int compact, uint32_t epoch,
                              unsigned* done_counter) {
+#ifdef LMSAE_BOUNDS_CHECK
+  if (threadIdx.x == 0) lmsae_jitter();  // debug build: blocks start their stores at perturbed times
+  __syncthreads();
+#endif
   const int nvec = d / 8;
   const int rows_per_rank = B / pt.world;
   for (int row = blockIdx.x; row < B; row += gridDim.x) {
@@ -237,6 +241,10 @@ reduce_loss_push_kernel(const PeerTable pt, int B, int d, const __nv_bfloat16* _
 template <bool MC>
 __global__ void __launch_bounds__(256)
 exchange_rows_kernel(const PeerTable pt, const RowExchange ex, uint32_t epoch, unsigned* done_counter, int* status) {
+#ifdef LMSAE_BOUNDS_CHECK
+  if (threadIdx.x == 0) lmsae_jitter();  // debug build: blocks start their stores at perturbed times
+  __syncthreads();
+#endif
   for (int i = 0; i < ex.n; ++i) {
     const uint4* s = reinterpret_cast<const uint4*>(ex.src[i]);
     const long long nvec = ex.nbytes[i] / 16;

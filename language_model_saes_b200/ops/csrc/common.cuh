@@ -350,6 +350,18 @@ __device__ __forceinline__ void red_release_gpu_add(uint32_t* p, uint32_t v) {
   asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+// Debug build only: a pseudo-random pause of up to ~8 us (different per block and per call), placed in front of every
+// flag publication and flag wait and at the start of the communicating kernels. It perturbs the order in which blocks
+// and ranks reach their synchronisation points, so that a protocol that only works for one lucky interleaving fails in
+// the small-case tests instead of in a long run.
+__device__ __forceinline__ void lmsae_jitter() {
+#ifdef LMSAE_BOUNDS_CHECK
+  const unsigned long long t = (unsigned long long)clock64();
+  const unsigned ns = (unsigned)(((t ^ (t >> 13)) * 2654435761ull + (unsigned long long)blockIdx.x * 40503ull) >> 5) & 0x1fffu;
+  __nanosleep(ns);
+#endif
+}
+
 // Bounded spin until *flag >= target (flags only grow). Returns false when the budget ran out.
 __device__ __forceinline__ bool wait_flag_sys(const uint32_t* flag, uint32_t target) {
   if (ld_acquire_sys(flag) >= target) return true;

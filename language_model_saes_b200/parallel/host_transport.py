@@ -26,21 +26,24 @@ import torch
 import torch.distributed as dist
 
 from ..ops import sae_kernels as K
-from .symm import _MAX_PEERS, _NUM_PHASES, PHASE_CAND, PHASE_DXHAT, PHASE_NAMES, PHASE_PARTIAL, step_buffer_layout
+from .symm import (_MAX_PEERS, _NUM_PHASES, PHASE_CAND, PHASE_DXHAT, PHASE_NAMES, PHASE_PARTIAL, check_guards, fill_guards, guards_wanted,
+                   step_buffer_layout)  # fmt: skip
 
 _PHASE_NAMES = PHASE_NAMES
 
 
 class HostPeerComm:
     def __init__(self, group: dist.ProcessGroup | None, batch: int, k_max: int, d_model: int, timeout_s: float = 5.0,
-                 faults: dict | None = None, directory: str | None = None, partial_dtype: torch.dtype = torch.bfloat16):  # fmt: skip
+                 faults: dict | None = None, directory: str | None = None, partial_dtype: torch.dtype = torch.bfloat16,
+                 guards: bool | None = None):  # fmt: skip
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         assert self.world <= _MAX_PEERS and batch % self.world == 0
         self.B, self.k_max, self.d = batch, k_max, d_model
         self.partial_dtype = partial_dtype
-        self.lay = step_buffer_layout(batch, self.world, k_max, d_model, partial_dtype.itemsize)
+        self.lay = step_buffer_layout(batch, self.world, k_max, d_model, partial_dtype.itemsize,
+                                      guards=guards_wanted() if guards is None else guards)
         self.timeout_s = timeout_s
         self.faults = dict(faults or {})
         self.epochs = [0] * _NUM_PHASES
@@ -57,9 +60,16 @@ class HostPeerComm:
         self.path = box[0]
         self._map = np.memmap(self.path, dtype=np.uint8, mode="r+", shape=(self.world, self.lay["nbytes"]))
         self.bufs = [torch.from_numpy(self._map[p]) for p in range(self.world)]
+        fill_guards(self.bufs[self.rank], self.lay)  # (no bands in the regular layout)
         dist.barrier(group=group)
         if self.rank == 0:
             os.unlink(self.path)  # the mappings keep the memory alive; nothing is left behind when the ranks exit
+
+    def check_guards(self) -> None:
+        """Debug layouts: raise when anyone wrote into a guard band of this rank's buffer."""
+        bad = check_guards(self.bufs[self.rank], self.lay)
+        if bad:
+            raise RuntimeError(f"rank {self.rank}: stores ran past the end of the step buffer region(s) {bad}")
 
     # ---- views into a rank's buffer -------------------------------------------------------------
     def _region(self, peer: int, name: str, shape: tuple[int, ...], dtype: torch.dtype, extra_off: int = 0) -> torch.Tensor:

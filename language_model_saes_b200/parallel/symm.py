@@ -103,20 +103,47 @@ class WaitStats:
         return out
 
 
-def step_buffer_layout(batch: int, world: int, k_max: int, d_model: int, partial_itemsize: int = 2) -> dict[str, int]:
+GUARD_BYTES = 256  # width of a guard band between two regions of a step buffer (debug layouts only)
+GUARD_PATTERN = 0xA5
+
+
+def guards_wanted() -> bool:
+    """Debug layouts (guard bands between the regions of the step buffers, checked by ``check_guards``) are on with the
+    bounds-checked build of the kernels (``LMSAE_NATIVE_CHECKED=1``) or with ``LMSAE_BUFFER_GUARDS=1``."""
+    return os.environ.get("LMSAE_NATIVE_CHECKED") == "1" or os.environ.get("LMSAE_BUFFER_GUARDS") == "1"
+
+
+def step_buffer_layout(batch: int, world: int, k_max: int, d_model: int, partial_itemsize: int = 2, guards: bool = False) -> dict:
     """Byte offsets of the regions of one rank's buffer for the fused step (the same on every rank): ``flags``
     ``[phase][source rank]`` epoch words, two candidate landing zones ``cand_val`` / ``cand_idx`` ``[2][B][world * k]``,
     ``partial`` ``[world][B / world][d]`` (or ``[B][d]`` when the owner reads through the switch) in fp32 or bf16,
-    ``dxhat`` ``[B][d]`` bf16, and the total ``nbytes``."""
+    ``dxhat`` ``[B][d]`` bf16, and the total ``nbytes``. With ``guards`` every region is followed by a band of
+    ``GUARD_BYTES`` that nothing may write (``lay["guards"]``: their offsets): a store that runs past a region by a row
+    or a slot lands there instead of in its neighbour, and ``check_guards`` finds it."""
     lay, off = {}, 0
     cand = _align(batch * world * k_max * 4)
+    bands = []
     for name, nbytes in (("flags", FLAG_BYTES), ("cand_val", 2 * cand), ("cand_idx", 2 * cand),
                          ("partial", batch * d_model * partial_itemsize), ("dxhat", batch * d_model * 2)):  # fmt: skip
         lay[name] = off
         off = _align(off + nbytes)
+        if guards:
+            bands.append((name, off))
+            off = _align(off + GUARD_BYTES)
     lay["cand_stride"] = cand
+    lay["guards"] = bands
     lay["nbytes"] = off
     return lay
+
+
+def fill_guards(buf: torch.Tensor, lay: dict) -> None:
+    for _, off in lay["guards"]:
+        buf[off : off + GUARD_BYTES] = GUARD_PATTERN
+
+
+def check_guards(buf: torch.Tensor, lay: dict) -> list[str]:
+    """Names of the regions whose guard band (the bytes right behind the region) no longer holds the pattern."""
+    return [name for name, off in lay["guards"] if not bool((buf[off : off + GUARD_BYTES] == GUARD_PATTERN).all())]
 
 
 class SymmComm:
@@ -137,10 +164,11 @@ class SymmComm:
         assert partial_dtype in (torch.float32, torch.bfloat16)
         self.B, self.k_max, self.d = batch, k_max, d_model
         self.partial_dtype = partial_dtype
-        lay = step_buffer_layout(batch, self.world, k_max, d_model, partial_dtype.itemsize)
+        lay = step_buffer_layout(batch, self.world, k_max, d_model, partial_dtype.itemsize, guards=guards_wanted())
         self.lay = lay
         self.partial_off, self.dxhat_off, self.nbytes = lay["partial"], lay["dxhat"], lay["nbytes"]
         self.buf, self.handle, self.ptrs, self.multicast_ptr = _rendezvous(self.nbytes, group, device)
+        fill_guards(self.buf, lay)  # (no bands in the regular layout)
         if use_multicast is None:
             use_multicast = os.environ.get("LMSAE_STEP_MULTICAST", "0") == "1"
         self.use_multicast = bool(use_multicast and self.multicast_ptr and partial_dtype == torch.bfloat16)
@@ -150,6 +178,12 @@ class SymmComm:
         self.device = device
         torch.cuda.synchronize(device)
         dist.barrier(group=group)
+
+    def check_guards(self) -> None:
+        """Debug layouts: raise when a kernel (of any rank) wrote into a guard band of this rank's buffer. Synchronises."""
+        bad = check_guards(self.buf, self.lay)
+        if bad:
+            raise RuntimeError(f"rank {self.rank}: stores ran past the end of the step buffer region(s) {bad}")
 
     def table(self, cand_parity: int = 0) -> list[int]:
         off = cand_parity * self.lay["cand_stride"]

@@ -274,10 +274,27 @@ def test_peer_memory_protocol_on_the_host_matches_collectives():
     dist.all_reduce(more)
     assert torch.allclose(more / 2, more_ref, rtol=1e-4)
     # partial rows in bf16 (the default on the wire): same protocol, reconstruction rounded like a bf16 all-reduce
-    comm16 = HostPeerComm(mesh_group(mesh, "model"), xs[0].shape[0], 8, 32, timeout_s=20.0)
+    # ... on the debug layout: a guard band behind every region of the buffers; the steps leave all of them untouched
+    comm16 = HostPeerComm(mesh_group(mesh, "model"), xs[0].shape[0], 8, 32, timeout_s=20.0, guards=True)
+    assert [n for n, _ in comm16.lay["guards"]] == ["flags", "cand_val", "cand_idx", "partial", "dxhat"]
     _, got16 = _run_fused_comm(_sharded_copy(full, mesh), xs, 8, comm16)
     dist.all_reduce(got16)
     assert torch.allclose(got16 / 2, want, rtol=2e-2), (got16 / 2, want)
+    comm16.check_guards()
+    dist.barrier()
+    # a store that runs one row past the end of the peer's gradient region is caught by that rank's check
+    if dist.get_rank() == 0:
+        end = comm16.lay["dxhat"] + xs[0].shape[0] * 32 * 2
+        comm16.bufs[1][end : end + 64] = 0
+    dist.barrier()
+    if dist.get_rank() == 1:
+        try:
+            comm16.check_guards()
+            raise AssertionError("the overrun went unnoticed")
+        except RuntimeError as e:
+            assert "dxhat" in str(e)
+    else:
+        comm16.check_guards()
 
 
 @distributed_test(nproc_per_node=2, backend="gloo")

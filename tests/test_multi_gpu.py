@@ -101,6 +101,9 @@ def test_peer_memory_step_matches_nccl_and_single_gpu():
             K.check_status(dev)
             assert torch.equal(ia.sort(dim=1).values, ib.sort(dim=1).values), name
             assert torch.allclose(xa, xb, atol=1e-3, rtol=1e-3), name
+        # debug layouts (bounds-checked build or LMSAE_BUFFER_GUARDS=1): nothing wrote past a region of the step buffers
+        dist.barrier()
+        comm.check_guards()
 
 
 @needs2
