@@ -50,9 +50,9 @@ class AuxK:
     """State and settings of the Aux-K loss on the fused path: per-feature count of valid tokens since the feature
     last fired; a feature is dead once the count reaches ``dead_threshold`` (trainer.py:403-454 of the reference).
 
-    Nothing here makes the host wait for the device. The dead features of a step are gathered into a compact dictionary
+    Nothing here makes the host wait for the step it is issuing. The dead features of a step are gathered into a compact dictionary
     of ``capacity`` rows for the auxiliary encoder pass; the capacity follows the number of dead features with a lag: the
-    count of every step is copied to pinned memory and read once its copy has completed, a step or two later, and the
+    count of every step is copied to pinned memory and read two steps later, and the
     capacity is then set to that count plus a quarter plus 1024 rows (at least ``k_aux``, in steps of 256 rows): every
     product of the auxiliary pass costs in proportion to the capacity, so the headroom is kept small. Should the dead
     features of a step outnumber the capacity (they grew by more than that within the lag), that step's auxiliary
@@ -65,7 +65,7 @@ class AuxK:
         self.is_dead = self.tokens_since_last_activation >= dead_threshold
         self.capacity = self._bucket(int(self.is_dead.sum()))
         self.truncated_steps = torch.zeros((), dtype=torch.long, device=device)
-        self._pending: tuple[torch.Tensor, object] | None = None
+        self._pending: list[tuple[torch.Tensor, object]] = []
 
     def _bucket(self, n_dead: int) -> int:
         rows = max(self.k_aux, n_dead + n_dead // 4 + 1024)
@@ -79,22 +79,26 @@ class AuxK:
         self.is_dead = self.tokens_since_last_activation >= self.dead_threshold
         return self.is_dead
 
+    LAG = 2  # steps between a count leaving the device and its use: the same on every rank, so capacities agree
+
     def observe(self, n_dead: torch.Tensor) -> None:
-        """Feed the lagged capacity estimate with this step's number of dead features (0-d device tensor)."""
+        """Feed the lagged capacity estimate with this step's number of dead features (0-d device tensor). The count is
+        copied to pinned memory now and read ``LAG`` steps later (its copy has long completed by then, the wait on its
+        event returns at once). The lag is a fixed number of steps rather than "whenever the copy is seen to be done",
+        because replicas and shards that exchange buffers sized by the capacity must all switch in the same step."""
         self.truncated_steps += n_dead > self.capacity
         if not n_dead.is_cuda:
             self.capacity = self._bucket(int(n_dead))
             return
-        if self._pending is not None:
-            host, ev = self._pending
-            if not ev.query():
-                return  # the previous copy is still in flight: keep the capacity, look again next step
-            self.capacity = self._bucket(int(host))
         host = torch.empty((), dtype=torch.long, pin_memory=True)
         host.copy_(n_dead, non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
-        self._pending = (host, ev)
+        self._pending.append((host, ev))
+        if len(self._pending) > self.LAG:
+            old, old_ev = self._pending.pop(0)
+            old_ev.synchronize()
+            self.capacity = self._bucket(int(old))
 
 
 class FusedTopKSAEStep:
