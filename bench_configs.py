@@ -654,6 +654,9 @@ def run_config5(args, bench) -> None:
         if impl == "ours" and os.environ.get("LMSAE_BENCH_ATTN", "") in ("library", "tensor_core"):
             lorsa_kw["attention_kernel"] = os.environ["LMSAE_BENCH_ATTN"]
         jobs.append(("lorsa", pkg.LorsaConfig(**lorsa_kw), ["blocks.6.ln1.hook_normalized", "blocks.6.hook_attn_out"], (T // S, S), 8))
+        only = os.environ.get("LMSAE_BENCH_C5_PARTS")  # "clt" or "lorsa": run one of the two parts (for launch lists)
+        if only:
+            jobs = [j for j in jobs if j[0] in only.split(",")]
         for name, cfg, keys, shape, seed in jobs:
             torch.manual_seed(0)
             sae = pkg.SparseDictionary.from_config(cfg, device_mesh=mesh)
@@ -712,7 +715,7 @@ def run_config5(args, bench) -> None:
         return
     if rank == 0:
         both = {"ms": sum(p["ms"] for p in parts.values()), "e2e_ms": sum(p["e2e_ms"] for p in parts.values()),
-                "clocks": parts["clt"]["clocks"], "final_loss": parts["lorsa"].get("final_loss")}  # fmt: skip
+                "clocks": next(iter(parts.values()))["clocks"], "final_loss": list(parts.values())[-1].get("final_loss")}  # fmt: skip
         _emit(bench, impl, metric, config, world, args, T, both, h2d=(2 * L + 2) * T * D * 2 // 1,
               extra={"path": "Trainer.fit(CrossLayerTranscoder), then Trainer.fit(LowRankSparseAttention)", "gpu_launches": _launches(impl),
                      "parts_ms_per_step": {k: {"device_timed": v["ms"] / Ks, "e2e": v["e2e_ms"] / Ks} for k, v in parts.items()}})  # fmt: skip
