@@ -1,0 +1,250 @@
+"""One training step of a low-rank sparse attention dictionary (Lorsa) with a TopK activation over its OV heads as a short
+fixed sequence of kernels, without an autograd graph over the model.
+
+What it computes is the reference's step for a ``LowRankSparseAttention`` (models/lorsa.py:642-661 projections and rotary
+embedding, :714-725 attention with the OV group as the value width, :764-782 activation gated by the decoder norms,
+:784-829 decode; MSE over tokens) with Adam. On the generic path that step is some 230 kernel launches, two thirds of
+them small element-wise kernels that autograd and autocast put around the few products that matter; here it is:
+
+1. three tcgen05 GEMMs ``x W^T + b`` for Q, K (all QK heads in one product each) and V, bf16 results
+2. rotary embedding of Q and K (a handful of element-wise kernels on bf16), library attention with one head per QK head
+   whose value width is the head's OV group                          -> pre-activations z [tokens, F] bf16
+3. radix row top-k of ``z * ||W_O row||`` (positive entries)          -> codes (idx, act) [tokens, k]
+4. sparse decode fused with the loss, d x_hat and d act (the kernel of the TopK SAE step; feature shards: sparse decode,
+   all-reduce, loss kernel, code-gradient kernel)
+5. d z = d act scattered to its positions; attention backward (the library's, through a one-node autograd call on the
+   attention alone); inverse rotation of d q, d k
+6. three library GEMMs for the projection gradients (``d q^T x`` ...), column sums for the biases
+7. updates: ``W_O`` by the sparse gradient + Adam kernel (rows rebuilt from the codes, bf16 shadow and row norms in the
+   same pass), the dense projections and biases by the flat Adam kernel.
+
+Restrictions: ``topk`` activation, rotary or no positional embedding (no ``rotary_scale``, no QK layer norm), Adam, fp32
+parameters with bf16 compute, sharding over ``model`` (heads) only, unmasked tokens.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from ..parallel.mesh import mesh_dim_size, mesh_group, mesh_local_rank
+from . import sae_kernels as K
+from .fused_step import _mm_f32, merge_codes_over_shards
+
+
+def _rotate(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, adjacent: bool, rd: int) -> torch.Tensor:
+    """Rotary embedding of ``x [b, s, h, d_head]`` on its first ``rd`` channels (models/lorsa.py:666-712 of the reference
+    project); with ``-sin`` the same call is the inverse rotation, which is also the backward pass of the forward one."""
+    xr = x[..., :rd]
+    if adjacent:
+        turned = torch.stack((-xr[..., 1::2], xr[..., ::2]), dim=-1).flatten(-2)
+    else:
+        n = rd // 2
+        turned = torch.cat((-xr[..., n:], xr[..., :n]), dim=-1)
+    out = xr * cos + turned * sin
+    return out if rd == x.shape[-1] else torch.cat([out, x[..., rd:]], dim=-1)
+
+
+class FusedLorsaStep:
+    def __init__(self, lorsa, betas: tuple[float, float] = (0.9, 0.999), eps: float = 1e-8):
+        cfg = lorsa.cfg
+        self.m = lorsa
+        self.betas, self.eps = betas, eps
+        self.tp = mesh_dim_size(lorsa.device_mesh, "model")
+        self.tp_rank = mesh_local_rank(lorsa.device_mesh, "model")
+        self.tp_group = mesh_group(lorsa.device_mesh, "model")
+        self.h, self.d, self.dqk = lorsa.W_Q.shape  # local QK heads, d_model, QK head width
+        self.F = lorsa.W_V.shape[0]  # local OV heads
+        self.group_size = self.F // self.h
+        self.own_rows = (0, self.F)  # no sharding of the optimizer state over data ranks
+        self.use_gate = cfg.sparsity_include_decoder_norm
+        self.rotary = cfg.positional_embedding_type == "rotary"
+        self.params = {"W_Q": lorsa.W_Q.data, "W_K": lorsa.W_K.data, "W_V": lorsa.W_V.data, "W_O": lorsa.W_O.data,
+                       "b_Q": lorsa.b_Q.data, "b_K": lorsa.b_K.data, "b_V": lorsa.b_V.data}  # fmt: skip
+        if cfg.use_decoder_bias:
+            self.params["b_D"] = lorsa.b_D.data
+        assert all(p.dtype == torch.float32 and p.is_contiguous() for p in self.params.values())
+        dev = lorsa.W_V.device
+        self.state = {n: (torch.zeros_like(p), torch.zeros_like(p)) for n, p in self.params.items()}
+        bf = lambda *s: torch.empty(*s, dtype=torch.bfloat16, device=dev)  # noqa: E731
+        self.WQ16, self.WK16 = bf(self.h * self.dqk, self.d), bf(self.h * self.dqk, self.d)  # [head x channel, d]: rows of x W^T
+        self.WV16, self.WO16 = bf(self.F, self.d), bf(self.F, self.d)
+        self.dec_norm = torch.empty(self.F, dtype=torch.float32, device=dev)
+        self.loss_sum = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.groups: K.FeatureGroups | None = None
+        self.t = 0
+        self.refresh()
+
+    @staticmethod
+    def supports(lorsa, trainer_cfg=None) -> tuple[bool, str]:
+        from ..models.lorsa import LowRankSparseAttention
+
+        cfg = lorsa.cfg
+        if type(lorsa) is not LowRankSparseAttention:
+            return False, "model is not a LowRankSparseAttention"
+        checks = [
+            (cfg.act_fn == "topk", "activation is not topk"),
+            (lorsa.W_V.is_cuda or trainer_cfg is None, "not on a CUDA device"),
+            (cfg.dtype == torch.float32, "parameters are not fp32"),
+            (cfg.positional_embedding_type in ("rotary", "none"), "positional embedding"),
+            (cfg.rotary_scale == 1 and not cfg.use_post_qk_ln, "rotary scale / QK layer norm"),
+            (cfg.d_model % 64 == 0 and cfg.d_qk_head % 8 == 0 and lorsa.W_V.shape[0] % 8 == 0, "d_model / head widths not aligned"),
+            (lorsa.W_V.shape[0] % max(lorsa.W_Q.shape[0], 1) == 0 and (lorsa.W_V.shape[0] // max(lorsa.W_Q.shape[0], 1)) % 8 == 0,
+             "OV group size not a multiple of 8"),
+            (mesh_dim_size(lorsa.device_mesh, "data") == 1, "data parallelism"),
+            (not any(hp.fwd_hooks or hp.bwd_hooks for hp in lorsa.hook_points()), "hooks are attached"),
+        ]  # fmt: skip
+        if trainer_cfg is not None:
+            checks += [
+                (trainer_cfg.sparsity_loss_type is None, "sparsity loss"),
+                (not trainer_cfg.lp_coefficient, "lp loss"),
+                (not trainer_cfg.auxk_coefficient, "aux-k loss"),
+                (trainer_cfg.optimizer_class == "adam", "optimizer is not adam"),
+                (trainer_cfg.amp_dtype == torch.bfloat16, "amp dtype is not bf16"),
+                (trainer_cfg.gradient_accumulation_steps == 1, "gradient accumulation"),
+                (not trainer_cfg.clip_grad_norm, "gradient clipping"),
+            ]
+        for ok, why in checks:
+            if not ok:
+                return False, why
+        return True, ""
+
+    # ---- shadows ---------------------------------------------------------------------------------
+    def _refresh_qk(self) -> None:
+        # parameters are [head, d, channel]; the GEMM wants the rows of W^T: [head x channel, d]
+        self.WQ16.copy_(self.params["W_Q"].permute(0, 2, 1).reshape(self.h * self.dqk, self.d))
+        self.WK16.copy_(self.params["W_K"].permute(0, 2, 1).reshape(self.h * self.dqk, self.d))
+
+    def refresh(self) -> None:
+        """Re-derive the bf16 shadows and decoder norms from the fp32 masters (after loading / editing weights)."""
+        self._refresh_qk()
+        K.row_norm_shadow(self.params["W_V"], None, self.WV16)
+        K.row_norm_shadow(self.params["W_O"], self.dec_norm, self.WO16)
+
+    def join(self) -> None:
+        pass
+
+    def sync_params(self) -> None:
+        pass
+
+    # ---- forward pieces -----------------------------------------------------------------------------
+    def _rot_tables(self, s: int, dtype: torch.dtype) -> tuple[torch.Tensor, torch.Tensor]:
+        cos = self.m.rotary_cos[None, :s, None, :].to(dtype)
+        sin = self.m.rotary_sin[None, :s, None, :].to(dtype)
+        return cos, sin
+
+    def _project(self, X: torch.Tensor, b: int, s: int):
+        """``X [tokens, d]`` bf16 -> rotated ``q, k [b, s, h, dqk]`` and ``v [b, s, h, group]`` (bf16 on CUDA)."""
+        q = K.encoder_hidden(X, self.WQ16, self.params["b_Q"].reshape(-1)).view(b, s, self.h, self.dqk)
+        k = K.encoder_hidden(X, self.WK16, self.params["b_K"].reshape(-1)).view(b, s, self.h, self.dqk)
+        v = K.encoder_hidden(X, self.WV16, self.params["b_V"]).view(b, s, self.h, self.group_size)
+        if self.rotary:
+            cos, sin = self._rot_tables(s, q.dtype)
+            adj, rd = self.m.cfg.rotary_adjacent_pairs, self.m.cfg.rotary_dim
+            q, k = _rotate(q, cos, sin, adj, rd), _rotate(k, cos, sin, adj, rd)
+        return q, k, v
+
+    def _attention(self, q, k, v):
+        """Library attention on ``[b, h, s, *]`` views; fp32 on CPU (the plain statement), bf16 on CUDA."""
+        if not q.is_cuda:
+            q, k, v = q.float(), k.float(), v.float()
+        return F.scaled_dot_product_attention(q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3),
+                                              scale=1.0 / self.m.attn_scale, is_causal=True)  # fmt: skip
+
+    def encode(self, x: torch.Tensor, k_top: int) -> tuple[torch.Tensor, torch.Tensor]:
+        """``x [b, s, d]`` bf16 -> codes ``(idx, act) [tokens, k]`` over this rank's OV heads."""
+        b, s, _ = x.shape
+        with torch.no_grad():
+            q, k, v = self._project(x.reshape(b * s, self.d).contiguous(), b, s)
+            z = self._attention(q, k, v).permute(0, 2, 1, 3).reshape(b * s, self.F)
+        return self._select(z, k_top)
+
+    def _select(self, z: torch.Tensor, k_top: int) -> tuple[torch.Tensor, torch.Tensor]:
+        gate = self.dec_norm if self.use_gate else None
+        zz = z if z.is_cuda else z.float()
+        idx, act = K.row_topk(zz.to(torch.bfloat16) if z.is_cuda else zz, k_top, gate, None)
+        if self.tp > 1:
+            idx, act = merge_codes_over_shards(idx, act, gate, k_top, self.tp, self.tp_rank, self.tp_group)
+        return idx, act
+
+    # ---- the step ---------------------------------------------------------------------------------
+    def step(self, x: torch.Tensor, label: torch.Tensor, k_top: int, lr: float) -> torch.Tensor:
+        """``x [b, s, d]`` normalised bf16 inputs, ``label [b, s, d]`` bf16 targets (the attention layer's output). Returns
+        the mean loss over tokens (0-d device tensor)."""
+        b, s, d = x.shape
+        T = b * s
+        X = x.reshape(T, d).contiguous()
+        Y = label.reshape(T, d).contiguous()
+        grad_scale = 2.0 / T
+        q, k, v = self._project(X, b, s)
+        # the attention alone keeps an autograd node (its backward is the library's); everything around it is explicit
+        ql, kl, vl = (t.detach().requires_grad_(True) for t in (q, k, v))
+        with torch.enable_grad():
+            out = self._attention(ql, kl, vl)  # [b, h, s, group]
+        z = out.detach().permute(0, 2, 1, 3).reshape(T, self.F)
+        idx, act = self._select(z, k_top)
+        self.loss_sum.zero_()
+        WO16 = self.WO16
+        bD = self.params.get("b_D")
+        if self.tp == 1:
+            dxhat, dact, _ = K.sparse_decode_loss(idx, act, WO16, bD, Y, None, grad_scale, self.loss_sum)
+        else:
+            xhat = K.sparse_decode(idx, act, WO16, None, torch.float32)
+            dist.all_reduce(xhat, group=self.tp_group)
+            dxhat = K.mse_loss_grad(xhat, Y, bD, None, grad_scale, self.loss_sum)
+            dact = K.sparse_dact(idx, WO16, dxhat)
+        # d z: the activation passes the gradient where a head was selected (its value is the pre-activation itself)
+        dz = torch.zeros(T, self.F + 8, dtype=z.dtype if z.is_cuda else torch.float32, device=x.device)
+        dz.scatter_(1, torch.where(idx >= 0, idx, torch.full_like(idx, self.F)).long(), dact.to(dz.dtype))
+        dz = dz[:, : self.F].reshape(b, s, self.h, self.group_size).permute(0, 2, 1, 3)
+        dq, dk, dv = torch.autograd.grad(out, (ql, kl, vl), dz.to(out.dtype))
+        if self.rotary:
+            cos, sin = self._rot_tables(s, dq.dtype)
+            adj, rd = self.m.cfg.rotary_adjacent_pairs, self.m.cfg.rotary_dim
+            dq, dk = _rotate(dq, cos, -sin, adj, rd), _rotate(dk, cos, -sin, adj, rd)
+        low = torch.bfloat16 if x.is_cuda else torch.float32
+        dQ = dq.reshape(T, self.h * self.dqk).to(low)
+        dK = dk.reshape(T, self.h * self.dqk).to(low)
+        dV = dv.reshape(T, self.F).to(low)
+        Xl = X.to(low)
+        grads = {
+            # [head x channel, d] -> the parameter's [head, d, channel]
+            "W_Q": _mm_f32(dQ.t(), Xl).view(self.h, self.dqk, d).permute(0, 2, 1).contiguous(),
+            "W_K": _mm_f32(dK.t(), Xl).view(self.h, self.dqk, d).permute(0, 2, 1).contiguous(),
+            "W_V": _mm_f32(dV.t(), Xl),
+            "b_Q": dQ.sum(0, dtype=torch.float32).view(self.h, self.dqk),
+            "b_K": dK.sum(0, dtype=torch.float32).view(self.h, self.dqk),
+            "b_V": dV.sum(0, dtype=torch.float32),
+        }
+        if bD is not None:
+            grads["b_D"] = K.colsum_bf16(dxhat)
+        self.t += 1
+        b1, b2 = self.betas
+        # W_O: rows rebuilt from the codes (act x d x_hat), Adam, bf16 shadow and row norms in one pass
+        if self.groups is None or self.groups.entries.numel() < idx.numel():
+            self.groups = K.FeatureGroups(self.F, idx.numel(), x.device)
+        self.groups.build(idx)
+        mO, vO = self.state["W_O"]
+        K.sparse_grad_adam(self.groups, act, dact, dxhat, dxhat, self.params["W_O"], mO, vO, WO16, None, None, None, None, None, None, None,
+                           self.dec_norm, None, None, lr, b1, b2, self.eps, self.t, True)  # fmt: skip
+        for name, g in grads.items():
+            m_, v_ = self.state[name]
+            shadow = self.WV16.view(-1) if name == "W_V" else None
+            K.adam_flat(self.params[name].view(-1), g.reshape(-1), m_.view(-1), v_.view(-1), lr, b1, b2, self.eps, self.t, shadow=shadow)
+        self._refresh_qk()
+        return (self.loss_sum / T).squeeze(0)
+
+    # ---- optimizer state in the model's parameter shapes -------------------------------------------------
+    def optimizer_state(self) -> dict:
+        out = {"step": self.t}
+        for name, (m_, v_) in self.state.items():
+            out[name] = {"exp_avg": m_, "exp_avg_sq": v_}
+        return out
+
+    def load_optimizer_state(self, sd: dict) -> None:
+        self.t = int(sd["step"])
+        for name, (m_, v_) in self.state.items():
+            if name in sd:
+                m_.copy_(sd[name]["exp_avg"])
+                v_.copy_(sd[name]["exp_avg_sq"])

@@ -46,6 +46,22 @@ def _mm_f32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     return a.float() @ b.float()
 
 
+def merge_codes_over_shards(idx_l: torch.Tensor, act_l: torch.Tensor, gate_l: torch.Tensor | None, k: int, tp: int, tp_rank: int,
+                            group) -> tuple[torch.Tensor, torch.Tensor]:  # fmt: skip
+    """Every shard holds its own top-``k`` codes ``(idx_l, act_l)`` of each row; keep those that are among the ``k``
+    largest gated values of the row over all shards (all-gather of the lists, merge, own slots only, packed from slot 0)."""
+    B = idx_l.shape[0]
+    g_l = act_l * gate_l[idx_l.clamp_min(0).long()] if gate_l is not None else act_l
+    all_g = torch.empty(tp * B, k, dtype=torch.float32, device=idx_l.device)
+    all_i = torch.empty(tp * B, k, dtype=torch.int32, device=idx_l.device)
+    dist.all_gather_into_tensor(all_g, g_l.float().contiguous(), group=group)
+    dist.all_gather_into_tensor(all_i, idx_l.contiguous(), group=group)
+    all_g = all_g.view(tp, B, k).permute(1, 0, 2).reshape(B, tp * k).contiguous()
+    all_i = all_i.view(tp, B, k).permute(1, 0, 2).reshape(B, tp * k).contiguous()
+    merge = K.topk_merge if k <= 64 else K.ref_topk_merge  # the merge kernel's lists hold at most 64 codes per row
+    return merge(all_g, all_i, k, gate_l, own=(tp_rank * k, (tp_rank + 1) * k))
+
+
 class AuxK:
     """State and settings of the Aux-K loss on the fused path: per-feature count of valid tokens since the feature
     last fired; a feature is dead once the count reaches ``dead_threshold`` (trainer.py:403-454 of the reference).
@@ -712,18 +728,7 @@ class FusedTopKSAEStep:
         return ((self.loss_sum + self.aux_sum) / n_local).squeeze(0)
 
     def _merge_shard_codes(self, idx_l: torch.Tensor, act_l: torch.Tensor, gate_l: torch.Tensor | None, k: int):
-        """Every shard holds its own top-``k`` codes ``(idx_l, act_l)`` of each row; keep those that are among the
-        ``k`` largest gated values of the row over all shards (all-gather of the lists, merge, own slots only)."""
-        B = idx_l.shape[0]
-        g_l = act_l * gate_l[idx_l.clamp_min(0).long()] if gate_l is not None else act_l
-        all_g = torch.empty(self.tp * B, k, dtype=torch.float32, device=idx_l.device)
-        all_i = torch.empty(self.tp * B, k, dtype=torch.int32, device=idx_l.device)
-        dist.all_gather_into_tensor(all_g, g_l.float().contiguous(), group=self.tp_group)
-        dist.all_gather_into_tensor(all_i, idx_l.contiguous(), group=self.tp_group)
-        all_g = all_g.view(self.tp, B, k).permute(1, 0, 2).reshape(B, self.tp * k).contiguous()
-        all_i = all_i.view(self.tp, B, k).permute(1, 0, 2).reshape(B, self.tp * k).contiguous()
-        merge = K.topk_merge if k <= 64 else K.ref_topk_merge  # the merge kernel's lists hold at most 64 codes per row
-        return merge(all_g, all_i, k, gate_l, own=(self.tp_rank * k, (self.tp_rank + 1) * k))
+        return merge_codes_over_shards(idx_l, act_l, gate_l, k, self.tp, self.tp_rank, self.tp_group)
 
     def _gather_rows(self, *tensors: torch.Tensor) -> list[torch.Tensor]:
         out = []

@@ -498,17 +498,22 @@ class Trainer:
             from .ops.fused_crosscoder import FusedCrosscoderStep
 
             from .ops.fused_clt import FusedCLTStep
+            from .ops.fused_lorsa import FusedLorsaStep
 
             ok_cc, why_cc = (False, "disabled") if not self.cfg.use_fused_kernels else FusedCrosscoderStep.supports(sae, self.cfg)
             ok_clt, why_clt = (False, "disabled") if not self.cfg.use_fused_kernels else FusedCLTStep.supports(sae, self.cfg)
+            ok_lorsa, why_lorsa = (False, "disabled") if not self.cfg.use_fused_kernels else FusedLorsaStep.supports(sae, self.cfg)
             if ok_cc:
                 self.fused = FusedCrosscoderStep(sae, betas=self.cfg.betas, jumprelu_lr_factor=self.cfg.jumprelu_lr_factor)
                 logger.info(f"Training the JumpReLU {type(sae).__name__} on the fused sm_100a kernel path")
             elif ok_clt:
                 self.fused = FusedCLTStep(sae, betas=self.cfg.betas)
                 logger.info("Training the cross-layer transcoder on the fused sm_100a kernel path")
+            elif ok_lorsa:
+                self.fused = FusedLorsaStep(sae, betas=self.cfg.betas)
+                logger.info("Training the low-rank sparse attention dictionary on the fused kernel path")
             else:
-                reason = {"Crosscoder": why_cc, "CrossLayerTranscoder": why_clt}.get(type(sae).__name__, why)
+                reason = {"Crosscoder": why_cc, "CrossLayerTranscoder": why_clt, "LowRankSparseAttention": why_lorsa}.get(type(sae).__name__, why)
                 if type(sae).__name__ == "SparseAutoEncoder" and sae.cfg.act_fn == "jumprelu":
                     reason = why_cc
                 logger.info(f"Training on the generic autograd path ({reason})")
@@ -1034,10 +1039,34 @@ class Trainer:
             self._emit(sae, out)
         return loss
 
+    def _fused_lorsa_iteration(self, sae: SparseDictionary, batch: dict[str, Tensor]) -> Tensor:
+        """One step of ``ops.fused_lorsa.FusedLorsaStep``: inputs and targets ``[batch, seq, d_model]``."""
+        f = self.fused
+        mask = batch.get("mask")
+        if mask is not None and not batch.get("_mask_all", None if mask.device.type == "cpu" else bool(mask.all())):
+            raise NotImplementedError("the fused Lorsa path trains on unmasked tokens; set use_fused_kernels=False for masked batches")
+        hin, hout = sae.cfg.hook_point_in, sae.cfg.hook_point_out
+        x = self._normalised_bf16(sae, batch[hin], hin)
+        y = self._normalised_bf16(sae, batch[hout], hout)
+        assert x.ndim == 3, "low-rank sparse attention trains on [batch, seq, d_model] activations"
+        k = self._current_k(sae)
+        if k is not None:
+            sae.set_current_k(k)
+        lr = float(self.cfg.lr) * (self._lr_lambda(self.cur_step) if self._lr_lambda is not None else 1.0)
+        loss = f.step(x, y, sae.current_k, lr)
+        if not self.cfg.skip_metrics_calculation and (self.cur_step + 1) % self.cfg.log_frequency == 0:
+            out = {"losses/overall_loss": float(loss), "losses/mse_loss": float(loss)}
+            out.update(self._details({}, lr))
+            out.update(sae.log_statistics())
+            self._emit(sae, out)
+        return loss
+
     def _fused_iteration(self, sae: SparseDictionary, batch: dict[str, Tensor]) -> Tensor:
         f = self.fused
         if type(f).__name__ == "FusedCrosscoderStep":
             return self._fused_crosscoder_iteration(sae, batch)
+        if type(f).__name__ == "FusedLorsaStep":
+            return self._fused_lorsa_iteration(sae, batch)
         if type(f).__name__ == "FusedCLTStep":
             return self._fused_clt_iteration(sae, batch)
         hin, hout = sae.cfg.hook_point_in, sae.cfg.hook_point_out

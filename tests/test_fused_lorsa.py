@@ -1,0 +1,167 @@
+"""The fused low-rank sparse attention step (``ops.fused_lorsa.FusedLorsaStep``) against the generic autograd path of
+the same model: losses and every parameter after a few Adam steps. On the CPU the step runs the plain-torch statements of
+its kernels (the math and the step's own bookkeeping are what is checked); on a GPU the kernels themselves."""
+
+import copy
+
+import pytest
+import torch
+
+from language_model_saes_b200.models.lorsa import LorsaConfig, LowRankSparseAttention
+from language_model_saes_b200.ops.fused_lorsa import FusedLorsaStep, _rotate
+
+DEVICES = [pytest.param("cuda", marks=pytest.mark.gpu), "cpu"]
+
+
+def _model(dev, d=64, nqk=2, dqk=16, n_ov=64, n_ctx=32, k=6, **kw):
+    torch.manual_seed(0)
+    cfg = LorsaConfig(hook_point_in="blocks.1.ln1.hook_normalized", hook_point_out="blocks.1.hook_attn_out", d_model=d,
+                      expansion_factor=n_ov / d, n_qk_heads=nqk, d_qk_head=dqk, rotary_dim=kw.pop("rotary_dim", dqk), n_ctx=n_ctx,
+                      act_fn="topk", top_k=k, device=dev, dtype=torch.float32, norm_activation="inference", **kw)  # fmt: skip
+    m = LowRankSparseAttention(cfg)
+    m.init_parameters()
+    with torch.no_grad():
+        m.W_Q.mul_(3.0)  # attention patterns that are not flat
+        m.W_K.mul_(3.0)
+        for b in (m.b_Q, m.b_K, m.b_V, m.b_D):
+            b.normal_(std=0.05)
+    return m
+
+
+def _batches(dev, n, b, s, d, seed=1):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    mix = torch.randn(d, d, device=dev, generator=g) / d**0.5
+    out = []
+    for _ in range(n):
+        x = torch.randn(b, s, d, device=dev, generator=g)
+        y = torch.tanh(x @ mix).cumsum(1) / 4 + 0.1 * torch.randn(b, s, d, device=dev, generator=g)
+        out.append((x.to(torch.bfloat16), y.to(torch.bfloat16)))
+    return out
+
+
+@pytest.mark.parametrize("adjacent,rotary_dim", [(True, 16), (False, 16), (True, 8)])
+def test_inverse_rotation_is_the_backward_of_the_rotation(adjacent, rotary_dim):
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(2, 5, 3, 16, generator=g, requires_grad=True)
+    ang = torch.rand(5, rotary_dim // 2, generator=g) * 6
+    ang = ang.repeat_interleave(2, dim=1) if adjacent else ang.repeat(1, 2)
+    cos, sin = ang.cos()[None, :, None, :], ang.sin()[None, :, None, :]
+    y = _rotate(x, cos, sin, adjacent, rotary_dim)
+    assert torch.allclose(_rotate(y, cos, -sin, adjacent, rotary_dim), x, atol=1e-6)  # a rotation: undone by the opposite angle
+    dy = torch.randn(y.shape, generator=g)
+    (dx,) = torch.autograd.grad(y, x, dy)
+    assert torch.allclose(dx, _rotate(dy, cos, -sin, adjacent, rotary_dim), atol=1e-6)
+
+
+@pytest.mark.parametrize("dev", DEVICES)
+@pytest.mark.parametrize("variant", ["rotary", "half_split_partial_rotary", "no_positions_no_gate"])
+def test_fused_lorsa_step_matches_autograd(dev, variant):
+    kw = {"rotary": {}, "half_split_partial_rotary": dict(rotary_adjacent_pairs=False, rotary_dim=8),
+          "no_positions_no_gate": dict(positional_embedding_type="none", sparsity_include_decoder_norm=False)}[variant]  # fmt: skip
+    d, b, s, lr, steps = 64, 3, 32, 1e-3, 4
+    ref = _model(dev, d=d, n_ctx=s, **kw)
+    fused_model = copy.deepcopy(ref)
+    ok, why = FusedLorsaStep.supports(fused_model)
+    assert ok, why
+    engine = FusedLorsaStep(fused_model)
+    opt = torch.optim.Adam(ref.parameters(), lr=lr)
+    start = {n: p.detach().clone() for n, p in ref.named_parameters()}
+    ref_losses, fused_losses = [], []
+    hin, hout = ref.cfg.hook_point_in, ref.cfg.hook_point_out
+    for x, y in _batches(dev, steps, b, s, d):
+        opt.zero_grad()
+        batch = {hin: x.float(), hout: y.float(), "tokens": torch.zeros(b, s, dtype=torch.long, device=dev)}
+        with torch.autocast(dev, dtype=torch.bfloat16, enabled=dev == "cuda"):
+            out = ref.compute_loss(batch, sparsity_loss_type=None, return_aux_data=True)
+        out["loss"].backward()
+        opt.step()
+        ref_losses.append(float(out["loss"].detach()))
+        fused_losses.append(float(engine.step(x, y, ref.cfg.top_k, lr)))
+    r, f = torch.tensor(ref_losses), torch.tensor(fused_losses)
+    assert torch.allclose(r, f, rtol=3e-2 if dev == "cuda" else 5e-3), (ref_losses, fused_losses)
+    # Adam's first steps move every weight that got any gradient by about lr whatever the gradient's size: compare the
+    # movement, not a rounding tolerance
+    for name, a in ref.named_parameters():
+        if name == "b_K" and variant != "rotary":
+            # one bias on every key shifts each score row by a constant, which the softmax ignores: without positions
+            # (and on the columns that a partial rotation leaves alone) the true gradient is zero and Adam steps along
+            # rounding noise in both implementations
+            continue
+        bb = dict(fused_model.named_parameters())[name].detach().float()
+        moved = (a.detach().float() - start[name].float()).abs().mean()
+        tol = (0.3 if dev == "cuda" else 0.08) * (3.0 if name == "b_K" else 1.0)  # b_K: small gradient, see above
+        assert float((a.detach().float() - bb).abs().mean()) < tol * float(moved) + 1e-7, name
+    # codes outside a step (evaluation): the same heads as the model's own encoder picks
+    x, _ = _batches(dev, 1, b, s, d, seed=5)[0]
+    idx, act = engine.encode(x, ref.cfg.top_k)
+    with torch.no_grad(), torch.autocast(dev, dtype=torch.bfloat16, enabled=dev == "cuda"):
+        acts = fused_model.encode(x.float())
+    want = (acts.reshape(b * s, -1) != 0).sum(-1)
+    assert torch.equal((idx >= 0).sum(-1), want) or float(((idx >= 0).sum(-1) - want).abs().float().mean()) < 0.5
+    state = engine.optimizer_state()
+    for name, p in fused_model.named_parameters():
+        assert state[name]["exp_avg"].shape == p.shape, name
+
+
+def _tp_body():
+    import torch.distributed as dist
+
+    from language_model_saes_b200.parallel.mesh import DimMap, build_mesh
+
+    d, b, s, lr = 64, 2, 16, 1e-3
+    full = _model("cpu", d=d, nqk=4, dqk=16, n_ov=64, n_ctx=s, k=6)
+    single = copy.deepcopy(full)
+    e1 = FusedLorsaStep(single)
+    mesh = build_mesh("cpu", (1, 2), ("data", "model"))
+    shard = LowRankSparseAttention(full.cfg.model_copy(), mesh)
+    shard.load_full_state_dict(full.full_state_dict())
+    e2 = FusedLorsaStep(shard)
+    assert e2.tp == 2 and e2.h == 2 and e2.F == 32
+    for x, y in _batches("cpu", 3, b, s, d):
+        want = e1.step(x, y, 6, lr)
+        got = e2.step(x, y, 6, lr)
+        assert torch.allclose(want, got, rtol=1e-4), (want, got)
+    for name in ("W_Q", "W_K", "W_V", "W_O", "b_Q", "b_V"):
+        whole = DimMap({"model": 0}).gather(getattr(shard, name).data, mesh)
+        assert torch.allclose(whole, getattr(single, name).data, atol=2e-5), name
+    assert torch.allclose(shard.b_D.data, single.b_D.data, atol=2e-5)
+    dist.barrier()
+
+
+def test_fused_lorsa_step_head_shards_match_single():
+    from language_model_saes_b200.testing import distributed_test
+
+    distributed_test(nproc_per_node=2, backend="gloo")(_tp_body)()
+
+
+@pytest.mark.gpu
+def test_trainer_picks_the_fused_lorsa_path_and_the_loss_goes_down():
+    import tempfile
+
+    from language_model_saes_b200.trainer import Trainer, TrainerConfig
+
+    d, b, s, steps = 64, 8, 64, 30
+    m = _model("cuda", d=d, nqk=4, dqk=16, n_ov=256, n_ctx=s, k=16)
+    hin, hout = m.cfg.hook_point_in, m.cfg.hook_point_out
+    data = _batches("cuda", 4, b, s, d)
+
+    def stream():
+        for i in range(steps + 1):
+            x, y = data[i % len(data)]
+            yield {hin: x, hout: y, "tokens": torch.zeros(b, s, dtype=torch.long, device="cuda")}
+
+    losses = []
+    with tempfile.TemporaryDirectory() as tmp:
+        tr = Trainer(TrainerConfig(total_training_tokens=steps * b * s, lr=2e-3, lr_warm_up_steps=2, log_frequency=10**6, n_checkpoints=0,
+                                   exp_result_path=tmp, skip_metrics_calculation=True))  # fmt: skip
+        orig = tr._fused_iteration
+
+        def spy(*a, **kw):
+            out = orig(*a, **kw)
+            losses.append(float(out))
+            return out
+
+        tr._fused_iteration = spy
+        tr.fit(m, stream())
+        assert type(tr.fused).__name__ == "FusedLorsaStep"
+    assert len(losses) == steps and all(l == l for l in losses) and sum(losses[-5:]) < sum(losses[:5]), losses
