@@ -410,8 +410,12 @@ class LowRankSparseAttention(SparseDictionary):
             return attention_kernels.causal_attention(q, k, None, 1 / self.attn_scale, vt=vt).reshape(b, s, -1)
         vg = v.view(b, s, h, -1)
         value = vg.permute(0, 2, 1, 3)
-        z = F.scaled_dot_product_attention(q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), value,
-                                           scale=1 / self.attn_scale, is_causal=True)  # fmt: skip
+        import contextlib
+
+        # on CUDA the library's cuDNN backend is kept out: its backward pass was seen to return wrong gradients here
+        with attention_kernels.library_attention_backends() if q.is_cuda else contextlib.nullcontext():
+            z = F.scaled_dot_product_attention(q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), value,
+                                               scale=1 / self.attn_scale, is_causal=True)  # fmt: skip
         return z.permute(0, 2, 1, 3).reshape(b, s, -1)
 
     def encode(

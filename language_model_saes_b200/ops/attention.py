@@ -16,6 +16,21 @@ import torch
 from . import sae_kernels as K
 
 
+def library_attention_backends():
+    """Context in which ``scaled_dot_product_attention`` may pick its memory-efficient or its plain backend only.
+
+    A value width that differs from the query/key width rules the flash backend out, and the library then prefers its
+    cuDNN backend on this architecture. With torch 2.11 / cuDNN 9 on sm_100 that backend's BACKWARD pass returned input
+    gradients that depended on what the allocator's recycled memory held: correct in a fresh process, unrelated to the
+    true gradient (cosine near 0) or NaN once freed blocks had been filled with a NaN pattern, for several stride layouts
+    of the output gradient and at both a tiny and a training-size shape; its forward pass and both passes of the
+    memory-efficient backend were correct in every such run. The backward pass follows the forward's choice, so the
+    context is only needed around the forward call."""
+    from torch.nn.attention import SDPBackend, sdpa_kernel
+
+    return sdpa_kernel([SDPBackend.EFFICIENT_ATTENTION, SDPBackend.MATH])
+
+
 def ref_causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float) -> tuple[torch.Tensor, torch.Tensor]:
     """fp32 ``(out [b, s, h, dv], lse [b, h, s])``."""
     s = q.shape[1]

@@ -29,6 +29,7 @@ import torch.distributed as dist
 import torch.nn.functional as F
 
 from ..parallel.mesh import mesh_dim_size, mesh_group, mesh_local_rank
+from .attention import library_attention_backends
 from . import sae_kernels as K
 from .fused_step import _mm_f32, merge_codes_over_shards
 
@@ -146,11 +147,15 @@ class FusedLorsaStep:
         return q, k, v
 
     def _attention(self, q, k, v):
-        """Library attention on ``[b, h, s, *]`` views; fp32 on CPU (the plain statement), bf16 on CUDA."""
+        """Library attention on ``[b, h, s, *]`` views; fp32 on CPU (the plain statement), bf16 on CUDA, where the backend is
+        pinned (see ``library_attention_backends``)."""
         if not q.is_cuda:
             q, k, v = q.float(), k.float(), v.float()
-        return F.scaled_dot_product_attention(q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3),
-                                              scale=1.0 / self.m.attn_scale, is_causal=True)  # fmt: skip
+            return F.scaled_dot_product_attention(q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3),
+                                                  scale=1.0 / self.m.attn_scale, is_causal=True)  # fmt: skip
+        with library_attention_backends():
+            return F.scaled_dot_product_attention(q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3),
+                                                  scale=1.0 / self.m.attn_scale, is_causal=True)  # fmt: skip
 
     def encode(self, x: torch.Tensor, k_top: int) -> tuple[torch.Tensor, torch.Tensor]:
         """``x [b, s, d]`` bf16 -> codes ``(idx, act) [tokens, k]`` over this rank's OV heads."""

@@ -39,6 +39,18 @@ def _batches(dev, n, b, s, d, seed=1):
     return out
 
 
+def _fill_freed_memory_with_nans(dev):
+    """Leave NaN bit patterns (as bf16 pairs and as fp32) in blocks of many sizes that the caching allocator will hand out
+    again: a kernel that reads memory nobody wrote then shows up as NaN instead of passing on a fresh process's zeros."""
+    if dev != "cuda":
+        return
+    keep = []
+    for n, c in ((128, 1000), (1024, 1000), (16384, 1000), (131072, 200), (1 << 20, 32), (32 << 20, 2)):
+        keep += [torch.full((n,), 0x7FC07FC0, dtype=torch.int32, device=dev) for _ in range(c)]
+    del keep
+    torch.cuda.synchronize()
+
+
 @pytest.mark.parametrize("adjacent,rotary_dim", [(True, 16), (False, 16), (True, 8)])
 def test_inverse_rotation_is_the_backward_of_the_rotation(adjacent, rotary_dim):
     g = torch.Generator().manual_seed(0)
@@ -69,6 +81,7 @@ def test_fused_lorsa_step_matches_autograd(dev, variant):
     ref_losses, fused_losses = [], []
     hin, hout = ref.cfg.hook_point_in, ref.cfg.hook_point_out
     for x, y in _batches(dev, steps, b, s, d):
+        _fill_freed_memory_with_nans(dev)
         opt.zero_grad()
         batch = {hin: x.float(), hout: y.float(), "tokens": torch.zeros(b, s, dtype=torch.long, device=dev)}
         with torch.autocast(dev, dtype=torch.bfloat16, enabled=dev == "cuda"):
