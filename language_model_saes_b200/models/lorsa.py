@@ -53,8 +53,8 @@ class LorsaConfig(SparseDictionaryConfig):
     attn_scale: float | None = None
     attention_kernel: Literal["library", "tensor_core"] = "library"
     """``tensor_core``: this package's tcgen05 kernels (``ops/csrc/attention.cu``: forward, dQ, dK/dV; bf16 models, d_qk 64
-    or 128, OV group a multiple of 64). ``library``: ``scaled_dot_product_attention``, which on a B200 is currently the
-    faster of the two at the shapes measured (see ``ops/microbench_families.py --case attn``)."""
+    or 128, OV group a multiple of 64). ``library``: ``scaled_dot_product_attention`` restricted to its memory-efficient
+    backend (``ops.attention.library_attention_backends`` says why the cuDNN backend is kept out)."""
     use_post_qk_ln: bool = False
     normalization_type: Literal["LN", "RMS"] | None = None
     eps: float = 1e-6
