@@ -7,13 +7,14 @@ embedding, :714-725 attention with the OV group as the value width, :764-782 act
 them small element-wise kernels that autograd and autocast put around the few products that matter; here it is:
 
 1. three tcgen05 GEMMs ``x W^T + b`` for Q, K (all QK heads in one product each) and V, bf16 results
-2. rotary embedding of Q and K (a handful of element-wise kernels on bf16), library attention with one head per QK head
-   whose value width is the head's OV group                          -> pre-activations z [tokens, F] bf16
+2. rotary embedding of Q and K (a handful of element-wise kernels on bf16), attention with one head per QK head whose
+   value width is the head's OV group (this package's tcgen05 kernels, or the library's memory-efficient backend for
+   shapes they do not take)                                          -> pre-activations z [tokens, F] bf16
 3. radix row top-k of ``z * ||W_O row||`` (positive entries)          -> codes (idx, act) [tokens, k]
 4. sparse decode fused with the loss, d x_hat and d act (the kernel of the TopK SAE step; feature shards: sparse decode,
    all-reduce, loss kernel, code-gradient kernel)
-5. d z = d act scattered to its positions; attention backward (the library's, through a one-node autograd call on the
-   attention alone); inverse rotation of d q, d k
+5. d z = d act scattered to its positions; attention backward (the dQ and dK/dV kernels, or the library's, through a
+   one-node autograd call on the attention alone); inverse rotation of d q, d k
 6. three library GEMMs for the projection gradients (``d q^T x`` ...), column sums for the biases
 7. updates: ``W_O`` by the sparse gradient + Adam kernel (rows rebuilt from the codes, bf16 shadow and row norms in the
    same pass), the dense projections and biases by the flat Adam kernel.
@@ -24,11 +25,14 @@ parameters with bf16 compute, sharding over ``model`` (heads) only, unmasked tok
 
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 import torch.nn.functional as F
 
 from ..parallel.mesh import mesh_dim_size, mesh_group, mesh_local_rank
+from . import attention as attention_kernels
 from .attention import library_attention_backends
 from . import sae_kernels as K
 from .fused_step import _mm_f32, merge_codes_over_shards
@@ -48,8 +52,13 @@ def _rotate(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, adjacent: boo
 
 
 class FusedLorsaStep:
-    def __init__(self, lorsa, betas: tuple[float, float] = (0.9, 0.999), eps: float = 1e-8):
+    def __init__(self, lorsa, betas: tuple[float, float] = (0.9, 0.999), eps: float = 1e-8, attention: str | None = None):
+        """``attention``: ``"tensor_core"`` (this package's tcgen05 forward, dQ and dK/dV kernels, where the shape allows:
+        d_qk 64 or 128, OV group a multiple of 64, sequence a multiple of 8) or ``"library"``; default from
+        ``LMSAE_LORSA_ATTENTION``, else ``tensor_core``."""
         cfg = lorsa.cfg
+        self.attention = attention or os.environ.get("LMSAE_LORSA_ATTENTION", "tensor_core")
+        assert self.attention in ("tensor_core", "library"), self.attention
         self.m = lorsa
         self.betas, self.eps = betas, eps
         self.tp = mesh_dim_size(lorsa.device_mesh, "model")
@@ -153,6 +162,8 @@ class FusedLorsaStep:
             q, k, v = q.float(), k.float(), v.float()
             return F.scaled_dot_product_attention(q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3),
                                                   scale=1.0 / self.m.attn_scale, is_causal=True)  # fmt: skip
+        if self.attention == "tensor_core" and attention_kernels.supported(q, v):
+            return attention_kernels.causal_attention(q, k, v, 1.0 / self.m.attn_scale).permute(0, 2, 1, 3)
         with library_attention_backends():
             return F.scaled_dot_product_attention(q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3),
                                                   scale=1.0 / self.m.attn_scale, is_causal=True)  # fmt: skip

@@ -66,16 +66,24 @@ def test_inverse_rotation_is_the_backward_of_the_rotation(adjacent, rotary_dim):
 
 
 @pytest.mark.parametrize("dev", DEVICES)
-@pytest.mark.parametrize("variant", ["rotary", "half_split_partial_rotary", "no_positions_no_gate"])
+@pytest.mark.parametrize("variant", ["rotary", "half_split_partial_rotary", "no_positions_no_gate", "rotary_wide_heads",
+                                     "rotary_wide_heads_library"])  # fmt: skip
 def test_fused_lorsa_step_matches_autograd(dev, variant):
     kw = {"rotary": {}, "half_split_partial_rotary": dict(rotary_adjacent_pairs=False, rotary_dim=8),
-          "no_positions_no_gate": dict(positional_embedding_type="none", sparsity_include_decoder_norm=False)}[variant]  # fmt: skip
+          "no_positions_no_gate": dict(positional_embedding_type="none", sparsity_include_decoder_norm=False),
+          # head widths that the tensor-core attention kernels take (on a GPU the step then runs them)
+          "rotary_wide_heads": dict(dqk=64, n_ov=128), "rotary_wide_heads_library": dict(dqk=64, n_ov=128)}[variant]  # fmt: skip
     d, b, s, lr, steps = 64, 3, 32, 1e-3, 4
     ref = _model(dev, d=d, n_ctx=s, **kw)
     fused_model = copy.deepcopy(ref)
     ok, why = FusedLorsaStep.supports(fused_model)
     assert ok, why
-    engine = FusedLorsaStep(fused_model)
+    engine = FusedLorsaStep(fused_model, attention="library" if variant.endswith("library") else "tensor_core")
+    if dev == "cuda":
+        from language_model_saes_b200.ops import attention as A
+
+        q = torch.empty(b, s, engine.h, engine.dqk, device=dev)
+        assert A.supported(q, torch.empty(b, s, engine.h, engine.group_size, device=dev)) == variant.startswith("rotary_wide")
     opt = torch.optim.Adam(ref.parameters(), lr=lr)
     start = {n: p.detach().clone() for n, p in ref.named_parameters()}
     ref_losses, fused_losses = [], []
