@@ -733,6 +733,29 @@ void jumprelu_window_grad(const Tensor& G, const Tensor& S, const Tensor& n, con
              "jumprelu_window_grad launch");
 }
 
+// Rotary embedding (sin_sign = 1) or its inverse (-1) of xa and xb [batch x seq, heads, width] bf16 into oa and ob;
+// cos / sin fp32 [>= seq, rd] (see rotary.cu).
+void rotary_pair(const Tensor& xa, const Tensor& xb, const Tensor& oa, const Tensor& ob, const Tensor& cos_t, const Tensor& sin_t,
+                 int64_t seq, bool adjacent, double sin_sign) {
+  CHECK_T(xa, torch::kBFloat16);
+  CHECK_T(xb, torch::kBFloat16);
+  CHECK_T(oa, torch::kBFloat16);
+  CHECK_T(ob, torch::kBFloat16);
+  CHECK_T(cos_t, torch::kFloat32);
+  CHECK_T(sin_t, torch::kFloat32);
+  TORCH_CHECK(xa.dim() == 3 && xb.sizes() == xa.sizes() && oa.sizes() == xa.sizes() && ob.sizes() == xa.sizes(), "rotary: shapes differ");
+  TORCH_CHECK(cos_t.dim() == 2 && sin_t.sizes() == cos_t.sizes() && cos_t.size(0) >= seq, "rotary: tables must be [>= seq, rd]");
+  const int64_t tokens = xa.size(0), heads = xa.size(1), width = xa.size(2), rd = cos_t.size(1);
+  TORCH_CHECK(seq >= 1 && tokens % seq == 0, "rotary: tokens must be batch x seq");
+  TORCH_CHECK(width % 8 == 0 && rd <= width && rd % (adjacent ? 8 : 16) == 0, "rotary: head width / rotary width not aligned");
+  const c10::cuda::CUDAGuard guard(xa.device());
+  check_cuda(lmsae::rotary_pair_launch(reinterpret_cast<const __nv_bfloat16*>(xa.data_ptr()), reinterpret_cast<const __nv_bfloat16*>(xb.data_ptr()),
+                                       reinterpret_cast<__nv_bfloat16*>(oa.data_ptr()), reinterpret_cast<__nv_bfloat16*>(ob.data_ptr()),
+                                       cos_t.data_ptr<float>(), sin_t.data_ptr<float>(), tokens, (int)seq, (int)heads, (int)width, (int)rd,
+                                       adjacent ? 1 : 0, (float)sin_sign, at::cuda::getCurrentCUDAStream()),
+             "rotary_pair launch");
+}
+
 void exclusive_scan(const Tensor& counts, const Tensor& offsets, const Tensor& block_sums) {
   CHECK_T(counts, torch::kInt32);
   CHECK_T(offsets, torch::kInt32);
@@ -1085,6 +1108,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("threshold_mask", &threshold_mask);
   m.def("row_compact", &row_compact);
   m.def("jumprelu_window_grad", &jumprelu_window_grad);
+  m.def("rotary_pair", &rotary_pair);
   m.def("exclusive_scan", &exclusive_scan);
   m.def("gather_rows_cast", &gather_rows_cast);
   m.def("clt_decode", &clt_decode);

@@ -199,6 +199,11 @@ int gather_rows_cast_launch(int in_dtype, int out_dtype, const void* src, const 
                             int d, void* out, long long out_rows, cudaStream_t stream);
 int exclusive_scan_launch(const int* counts, int n, int* offsets, int* block_sums_buf, cudaStream_t stream);
 
+// ---- rotary embedding of two [tokens, heads, width] bf16 tensors in one launch (rotary.cu) ----------------------
+int rotary_pair_launch(const __nv_bfloat16* xa, const __nv_bfloat16* xb, __nv_bfloat16* oa, __nv_bfloat16* ob, const float* cos_t,
+                       const float* sin_t, long long tokens, int seq, int heads, int width, int rd, int adjacent, float sin_sign,
+                       cudaStream_t stream);
+
 // ---- causal attention with d_v != d_qk (attention.cu) ------------------------------------------------
 struct AttnParams {
   int batch, seq, heads, dqk, dv;

@@ -7,7 +7,7 @@ embedding, :714-725 attention with the OV group as the value width, :764-782 act
 them small element-wise kernels that autograd and autocast put around the few products that matter; here it is:
 
 1. three tcgen05 GEMMs ``x W^T + b`` for Q, K (all QK heads in one product each) and V, bf16 results
-2. rotary embedding of Q and K (a handful of element-wise kernels on bf16), attention with one head per QK head whose
+2. rotary embedding of Q and K (one kernel for both), attention with one head per QK head whose
    value width is the head's OV group (this package's tcgen05 kernels, or the library's memory-efficient backend for
    shapes they do not take)                                          -> pre-activations z [tokens, F] bf16
 3. radix row top-k of ``z * ||W_O row||`` (positive entries)          -> codes (idx, act) [tokens, k]
@@ -49,6 +49,24 @@ def _rotate(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, adjacent: boo
         turned = torch.cat((-xr[..., n:], xr[..., :n]), dim=-1)
     out = xr * cos + turned * sin
     return out if rd == x.shape[-1] else torch.cat([out, x[..., rd:]], dim=-1)
+
+
+def rotate_pair(a: torch.Tensor, b: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, adjacent: bool, inverse: bool = False):
+    """Rotary embedding (or its inverse) of two ``[batch, seq, heads, width]`` tensors with tables ``cos, sin [n_ctx, rd]``:
+    one kernel for both on a GPU (bf16 tensors, fp32 tables, aligned widths), ``_rotate`` otherwise."""
+    bsz, s, h, w = a.shape
+    rd = cos.shape[-1]
+    fast = (a.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and cos.dtype == torch.float32 and w % 8 == 0
+            and rd % (8 if adjacent else 16) == 0 and cos.is_contiguous() and sin.is_contiguous())  # fmt: skip
+    if not fast:
+        c, sn = cos[None, :s, None, :].to(a.dtype), sin[None, :s, None, :].to(a.dtype)
+        sn = -sn if inverse else sn
+        return _rotate(a, c, sn, adjacent, rd), _rotate(b, c, sn, adjacent, rd)
+    a, b = a.contiguous(), b.contiguous()
+    oa, ob = torch.empty_like(a), torch.empty_like(b)
+    K._ext().rotary_pair(a.view(bsz * s, h, w), b.view(bsz * s, h, w), oa.view(bsz * s, h, w), ob.view(bsz * s, h, w), cos, sin, s, adjacent,
+                         -1.0 if inverse else 1.0)  # fmt: skip
+    return oa, ob
 
 
 class FusedLorsaStep:
@@ -139,20 +157,13 @@ class FusedLorsaStep:
         pass
 
     # ---- forward pieces -----------------------------------------------------------------------------
-    def _rot_tables(self, s: int, dtype: torch.dtype) -> tuple[torch.Tensor, torch.Tensor]:
-        cos = self.m.rotary_cos[None, :s, None, :].to(dtype)
-        sin = self.m.rotary_sin[None, :s, None, :].to(dtype)
-        return cos, sin
-
     def _project(self, X: torch.Tensor, b: int, s: int):
         """``X [tokens, d]`` bf16 -> rotated ``q, k [b, s, h, dqk]`` and ``v [b, s, h, group]`` (bf16 on CUDA)."""
         q = K.encoder_hidden(X, self.WQ16, self.params["b_Q"].reshape(-1)).view(b, s, self.h, self.dqk)
         k = K.encoder_hidden(X, self.WK16, self.params["b_K"].reshape(-1)).view(b, s, self.h, self.dqk)
         v = K.encoder_hidden(X, self.WV16, self.params["b_V"]).view(b, s, self.h, self.group_size)
         if self.rotary:
-            cos, sin = self._rot_tables(s, q.dtype)
-            adj, rd = self.m.cfg.rotary_adjacent_pairs, self.m.cfg.rotary_dim
-            q, k = _rotate(q, cos, sin, adj, rd), _rotate(k, cos, sin, adj, rd)
+            q, k = rotate_pair(q, k, self.m.rotary_cos, self.m.rotary_sin, self.m.cfg.rotary_adjacent_pairs)
         return q, k, v
 
     def _attention(self, q, k, v):
@@ -216,9 +227,7 @@ class FusedLorsaStep:
         dz = dz[:, : self.F].reshape(b, s, self.h, self.group_size).permute(0, 2, 1, 3)
         dq, dk, dv = torch.autograd.grad(out, (ql, kl, vl), dz.to(out.dtype))
         if self.rotary:
-            cos, sin = self._rot_tables(s, dq.dtype)
-            adj, rd = self.m.cfg.rotary_adjacent_pairs, self.m.cfg.rotary_dim
-            dq, dk = _rotate(dq, cos, -sin, adj, rd), _rotate(dk, cos, -sin, adj, rd)
+            dq, dk = rotate_pair(dq, dk, self.m.rotary_cos, self.m.rotary_sin, self.m.cfg.rotary_adjacent_pairs, inverse=True)
         low = torch.bfloat16 if x.is_cuda else torch.float32
         dQ = dq.reshape(T, self.h * self.dqk).to(low)
         dK = dk.reshape(T, self.h * self.dqk).to(low)

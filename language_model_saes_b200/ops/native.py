@@ -25,7 +25,7 @@ _CSRC = Path(__file__).resolve().parent / "csrc"
 # ``bounds_report`` of the extension) and clamped instead of read out of bounds.
 _CHECKED = os.environ.get("LMSAE_NATIVE_CHECKED", "0") == "1"
 _BUILD_DIR = Path(__file__).resolve().parent / ("_native_build_checked" if _CHECKED else "_native_build")
-_SOURCES = ["binding.cpp", "encoder_gemm.cu", "topk_merge.cu", "sparse_ops.cu", "comm_ops.cu", "no_alloc.cu", "jumprelu.cu", "clt_ops.cu", "select_ops.cu", "attention.cu"]
+_SOURCES = ["binding.cpp", "encoder_gemm.cu", "topk_merge.cu", "sparse_ops.cu", "comm_ops.cu", "no_alloc.cu", "jumprelu.cu", "clt_ops.cu", "select_ops.cu", "attention.cu", "rotary.cu"]
 _CUDA_FLAGS = [
     "-gencode",
     "arch=compute_100a,code=sm_100a",

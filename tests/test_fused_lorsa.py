@@ -8,7 +8,7 @@ import pytest
 import torch
 
 from language_model_saes_b200.models.lorsa import LorsaConfig, LowRankSparseAttention
-from language_model_saes_b200.ops.fused_lorsa import FusedLorsaStep, _rotate
+from language_model_saes_b200.ops.fused_lorsa import FusedLorsaStep, _rotate, rotate_pair
 
 DEVICES = [pytest.param("cuda", marks=pytest.mark.gpu), "cpu"]
 
@@ -63,6 +63,30 @@ def test_inverse_rotation_is_the_backward_of_the_rotation(adjacent, rotary_dim):
     dy = torch.randn(y.shape, generator=g)
     (dx,) = torch.autograd.grad(y, x, dy)
     assert torch.allclose(dx, _rotate(dy, cos, -sin, adjacent, rotary_dim), atol=1e-6)
+
+
+@pytest.mark.parametrize("dev", DEVICES)
+@pytest.mark.parametrize("adjacent,width,rotary_dim", [(True, 16, 16), (True, 64, 64), (True, 32, 16), (False, 64, 64), (False, 64, 32), (False, 16, 8)])
+@pytest.mark.parametrize("inverse", [False, True])
+def test_rotation_of_two_tensors_matches_the_plain_statement(dev, adjacent, width, rotary_dim, inverse):
+    """On a GPU the aligned cases run the one-launch kernel (bf16 in and out, fp32 arithmetic); the others and the CPU
+    run the torch statement. Either way the result is the fp32 rotation of the same bf16 inputs up to one rounding."""
+    g = torch.Generator(device=dev).manual_seed(0)
+    b, s, h = 3, 24, 5
+    qa = torch.randn(b, s, h, width, device=dev, generator=g).to(torch.bfloat16)
+    ka = torch.randn(b, s, h, width, device=dev, generator=g).to(torch.bfloat16)
+    ang = torch.rand(s + 3, rotary_dim // 2, device=dev, generator=g) * 6  # a table longer than the sequence
+    ang = ang.repeat_interleave(2, dim=1) if adjacent else ang.repeat(1, 2)
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    oq, ok = rotate_pair(qa, ka, cos, sin, adjacent, inverse=inverse)
+    sn = -sin if inverse else sin
+    for got, x in ((oq, qa), (ok, ka)):
+        want = _rotate(x.float(), cos[None, :s, None, :], sn[None, :s, None, :], adjacent, rotary_dim)
+        assert got.shape == x.shape and got.dtype == x.dtype
+        assert torch.allclose(got.float(), want, atol=3e-2, rtol=2e-2)
+        if dev == "cuda" and rotary_dim % (8 if adjacent else 16) == 0:
+            # the kernel rounds once, from the fp32 result (a fused multiply-add may move a tie)
+            assert float((got != want.to(torch.bfloat16)).float().mean()) < 1e-3
 
 
 @pytest.mark.parametrize("dev", DEVICES)
