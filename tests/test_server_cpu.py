@@ -151,17 +151,20 @@ def test_ui_pages_are_served_and_call_existing_routes(server):
     import re
 
     http, _, names = server
-    page, script = http.get("/ui/index.html"), http.get("/ui/pages.js")
-    assert page.status_code == 200 and 'src="pages.js"' in page.text and script.status_code == 200
+    page = http.get("/ui/index.html")
+    assert page.status_code == 200 and 'src="pages.js"' in page.text
+    scripts = [http.get(f"/ui/{name}") for name in re.findall(r'<script src="([^"]+)">', page.text)]
+    assert len(scripts) >= 5 and all(s.status_code == 200 for s in scripts)
     routes = {(m, r.path) for r in http.app.routes for m in getattr(r, "methods", ())}
     as_route = lambda p: re.sub(r"\$\{[^}]*\}", "{}", p.split("?")[0])  # noqa: E731
     known = {(m, re.sub(r"\{[^}]*\}", "{}", p)) for m, p in routes}
     called = set()
-    for text in (page.text, script.text):
-        for m in re.finditer(r"api\((`|\")(/[^`\"]*)\1(?:,\s*(?:jsonOpts\(\"(\w+)\"|\{\s*method:\s*(?:\"(\w+)\"|[^}]*\?\s*\"(\w+)\"\s*:\s*\"(\w+)\")))?", text):
+    for text in [s.text for s in scripts]:
+        for m in re.finditer(r"api\((`|\")(/[^`\"]*)\1(?:\s*\+\s*query\(\{[^}]*\}\))?(?:,\s*(?:jsonOpts\(\"(\w+)\"|\{\s*method:\s*(?:\"(\w+)\"|[^}]*\?\s*\"(\w+)\"\s*:\s*\"(\w+)\")))?", text):
             methods = [g for g in m.groups()[2:] if g] or ["GET"]
             called |= {(meth, as_route(m.group(2))) for meth in methods}
     assert len(called) > 20
+    called = {(m, p.replace("/features/random", "/features/{}")) for m, p in called}  # "random" stands for a feature index
     missing = sorted(c for c in called if c not in known)
     assert not missing, missing
     # the pages' data sources answer for the fixtures of this module
