@@ -20,7 +20,7 @@ them small element-wise kernels that autograd and autocast put around the few pr
    same pass), the dense projections and biases by the flat Adam kernel.
 
 Restrictions: ``topk`` activation, rotary or no positional embedding (no ``rotary_scale``, no QK layer norm), Adam, fp32
-parameters with bf16 compute, sharding over ``model`` (heads) only, unmasked tokens.
+parameters with bf16 compute, sharding over ``model`` (heads) only.
 """
 
 from __future__ import annotations
@@ -189,16 +189,17 @@ class FusedLorsaStep:
 
     def _select(self, z: torch.Tensor, k_top: int) -> tuple[torch.Tensor, torch.Tensor]:
         gate = self.dec_norm if self.use_gate else None
-        zz = z if z.is_cuda else z.float()
-        idx, act = K.row_topk(zz.to(torch.bfloat16) if z.is_cuda else zz, k_top, gate, None)
+        idx, act = K.row_topk(z.to(torch.bfloat16) if z.is_cuda else z.float(), k_top, gate, None)
         if self.tp > 1:
             idx, act = merge_codes_over_shards(idx, act, gate, k_top, self.tp, self.tp_rank, self.tp_group)
         return idx, act
 
     # ---- the step ---------------------------------------------------------------------------------
-    def step(self, x: torch.Tensor, label: torch.Tensor, k_top: int, lr: float) -> torch.Tensor:
+    def step(self, x: torch.Tensor, label: torch.Tensor, k_top: int, lr: float, row_weight: torch.Tensor | None = None) -> torch.Tensor:
         """``x [b, s, d]`` normalised bf16 inputs, ``label [b, s, d]`` bf16 targets (the attention layer's output). Returns
-        the mean loss over tokens (0-d device tensor)."""
+        the mean loss over tokens (0-d device tensor). ``row_weight [b x s]`` fp32 weighs every token's squared error
+        (0 for masked tokens and ``tokens / valid tokens`` for the others gives the mean over valid tokens; masked
+        tokens still serve as keys and values of later positions, as they do in the model's own forward pass)."""
         b, s, d = x.shape
         T = b * s
         X = x.reshape(T, d).contiguous()
@@ -215,11 +216,11 @@ class FusedLorsaStep:
         WO16 = self.WO16
         bD = self.params.get("b_D")
         if self.tp == 1:
-            dxhat, dact, _ = K.sparse_decode_loss(idx, act, WO16, bD, Y, None, grad_scale, self.loss_sum)
+            dxhat, dact, _ = K.sparse_decode_loss(idx, act, WO16, bD, Y, row_weight, grad_scale, self.loss_sum)
         else:
             xhat = K.sparse_decode(idx, act, WO16, None, torch.float32)
             dist.all_reduce(xhat, group=self.tp_group)
-            dxhat = K.mse_loss_grad(xhat, Y, bD, None, grad_scale, self.loss_sum)
+            dxhat = K.mse_loss_grad(xhat, Y, bD, row_weight, grad_scale, self.loss_sum)
             dact = K.sparse_dact(idx, WO16, dxhat)
         # d z: the activation passes the gradient where a head was selected (its value is the pre-activation itself)
         dz = torch.zeros(T, self.F + 8, dtype=z.dtype if z.is_cuda else torch.float32, device=x.device)

@@ -1043,8 +1043,11 @@ class Trainer:
         """One step of ``ops.fused_lorsa.FusedLorsaStep``: inputs and targets ``[batch, seq, d_model]``."""
         f = self.fused
         mask = batch.get("mask")
-        if mask is not None and not batch.get("_mask_all", None if mask.device.type == "cpu" else bool(mask.all())):
-            raise NotImplementedError("the fused Lorsa path trains on unmasked tokens; set use_fused_kernels=False for masked batches")
+        row_weight = None
+        if mask is not None and not batch.get("_mask_all", False):
+            # masked tokens weigh 0, the others tokens / valid tokens, computed on the device (no wait for the count)
+            w = mask.reshape(-1).float()
+            row_weight = w * (w.numel() / w.sum().clamp_min(1.0))
         hin, hout = sae.cfg.hook_point_in, sae.cfg.hook_point_out
         x = self._normalised_bf16(sae, batch[hin], hin)
         y = self._normalised_bf16(sae, batch[hout], hout)
@@ -1053,7 +1056,7 @@ class Trainer:
         if k is not None:
             sae.set_current_k(k)
         lr = float(self.cfg.lr) * (self._lr_lambda(self.cur_step) if self._lr_lambda is not None else 1.0)
-        loss = f.step(x, y, sae.current_k, lr)
+        loss = f.step(x, y, sae.current_k, lr, row_weight=row_weight)
         if not self.cfg.skip_metrics_calculation and (self.cur_step + 1) % self.cfg.log_frequency == 0:
             out = {"losses/overall_loss": float(loss), "losses/mse_loss": float(loss)}
             out.update(self._details({}, lr))

@@ -193,7 +193,9 @@ def test_trainer_picks_the_fused_lorsa_path_and_the_loss_goes_down():
     def stream():
         for i in range(steps + 1):
             x, y = data[i % len(data)]
-            yield {hin: x, hout: y, "tokens": torch.zeros(b, s, dtype=torch.long, device="cuda")}
+            mask = torch.ones(b, s, dtype=torch.bool, device="cuda")
+            mask[:, 0] = False  # the path with row weights
+            yield {hin: x, hout: y, "tokens": torch.zeros(b, s, dtype=torch.long, device="cuda"), "mask": mask}
 
     losses = []
     with tempfile.TemporaryDirectory() as tmp:
@@ -210,3 +212,34 @@ def test_trainer_picks_the_fused_lorsa_path_and_the_loss_goes_down():
         tr.fit(m, stream())
         assert type(tr.fused).__name__ == "FusedLorsaStep"
     assert len(losses) == steps and all(l == l for l in losses) and sum(losses[-5:]) < sum(losses[:5]), losses
+
+
+@pytest.mark.parametrize("dev", DEVICES)
+def test_fused_lorsa_step_with_a_token_mask_matches_autograd(dev):
+    """Masked tokens carry no loss (mean over the valid ones) but stay in the sequence as keys and values."""
+    d, b, s, lr = 64, 3, 32, 1e-3
+    ref = _model(dev, d=d, n_ctx=s)
+    fused_model = copy.deepcopy(ref)
+    engine = FusedLorsaStep(fused_model)
+    opt = torch.optim.Adam(ref.parameters(), lr=lr)
+    start = {n: p.detach().clone() for n, p in ref.named_parameters()}
+    hin, hout = ref.cfg.hook_point_in, ref.cfg.hook_point_out
+    g = torch.Generator(device=dev).manual_seed(3)
+    for x, y in _batches(dev, 3, b, s, d):
+        _fill_freed_memory_with_nans(dev)
+        mask = torch.rand(b, s, device=dev, generator=g) > 0.3
+        mask[:, 0] = False  # e.g. a beginning-of-sequence token
+        opt.zero_grad()
+        batch = {hin: x.float(), hout: y.float(), "tokens": torch.zeros(b, s, dtype=torch.long, device=dev), "mask": mask}
+        with torch.autocast(dev, dtype=torch.bfloat16, enabled=dev == "cuda"):
+            out = ref.compute_loss(batch, sparsity_loss_type=None, return_aux_data=True)
+        out["loss"].backward()
+        opt.step()
+        w = mask.reshape(-1).float()
+        got = engine.step(x, y, ref.cfg.top_k, lr, row_weight=w * (w.numel() / w.sum()))
+        assert torch.allclose(out["loss"].detach().float(), got, rtol=3e-2 if dev == "cuda" else 5e-3), (out["loss"], got)
+    for name, a in ref.named_parameters():
+        bb = dict(fused_model.named_parameters())[name].detach().float()
+        moved = (a.detach().float() - start[name].float()).abs().mean()
+        tol = (0.3 if dev == "cuda" else 0.08) * (3.0 if name == "b_K" else 1.0)
+        assert float((a.detach().float() - bb).abs().mean()) < tol * float(moved) + 1e-7, name
