@@ -834,6 +834,25 @@ class Trainer:
             batch = {**batch, "_n_valid": n, "_mask_all": n == mask.numel()}
         return batch
 
+    def _all_tokens_valid(self, batch: dict[str, Any]) -> bool:
+        """Whether the batch's mask (if any) is all true. A mask in host memory was summarised when the batch came in; a
+        mask on the device costs one read, which is remembered for as long as the very same tensor object comes back
+        unmodified (a stream that reuses one device mask for every batch is asked once, not once per step). The tensor is
+        kept referenced meanwhile, so that its memory cannot be handed to another mask that would look the same."""
+        mask = batch.get("mask")
+        if mask is None:
+            return True
+        if "_mask_all" in batch:
+            return bool(batch["_mask_all"])
+        if mask.device.type == "cpu":
+            return bool(mask.all())
+        seen = getattr(self, "_device_mask_seen", None)
+        if seen is not None and seen[0] is mask and seen[1] == mask._version and seen[2] is not None:
+            return seen[2]
+        ok = bool(mask.all())
+        self._device_mask_seen = (mask, mask._version, ok)
+        return ok
+
     def _count_tokens(self, batch: dict[str, Any]) -> int:
         """Valid tokens of a batch for the progress counters. A mask that lives on the device is counted there and folded
         in at the next logging step (one read per logging interval instead of one per step)."""
@@ -977,8 +996,7 @@ class Trainer:
         """One step of ``ops.fused_crosscoder.FusedCrosscoderStep``: this rank's hook points, normalised, stacked to
         ``[tokens, local heads, d_model]`` in bf16."""
         f = self.fused
-        mask = batch.get("mask")
-        if mask is not None and not batch.get("_mask_all", None if mask.device.type == "cpu" else bool(mask.all())):
+        if not self._all_tokens_valid(batch):
             raise NotImplementedError("the fused crosscoder path trains on unmasked tokens; set use_fused_kernels=False for masked batches")
         cols = []
         for hp in sae.local_hook_points() if hasattr(sae, "local_hook_points") else [sae.cfg.hook_point_in]:
@@ -1019,8 +1037,7 @@ class Trainer:
     def _fused_clt_iteration(self, sae: SparseDictionary, batch: dict[str, Tensor]) -> Tensor:
         """One step of ``ops.fused_clt.FusedCLTStep``: inputs ``[tokens, layers, d]``, targets ``[layers, tokens, d]``."""
         f = self.fused
-        mask = batch.get("mask")
-        if mask is not None and not batch.get("_mask_all", None if mask.device.type == "cpu" else bool(mask.all())):
+        if not self._all_tokens_valid(batch):
             raise NotImplementedError("the fused cross-layer transcoder path trains on unmasked tokens; set use_fused_kernels=False")
         d = sae.cfg.d_model
         # layer-major [layers, tokens, d]: what the per-layer GEMMs and the update kernels read
@@ -1044,10 +1061,20 @@ class Trainer:
         f = self.fused
         mask = batch.get("mask")
         row_weight = None
-        if mask is not None and not batch.get("_mask_all", False):
-            # masked tokens weigh 0, the others tokens / valid tokens, computed on the device (no wait for the count)
-            w = mask.reshape(-1).float()
-            row_weight = w * (w.numel() / w.sum().clamp_min(1.0))
+        if mask is not None:
+            all_valid = batch.get("_mask_all")
+            if all_valid is None and mask.device.type != "cpu":
+                # A mask on the device is not read back for its own sake: weights cost a few small kernels, a read stalls the
+                # host. Only when the very same tensor comes back (a stream that reuses one mask) is it worth asking once.
+                seen = getattr(self, "_device_mask_seen", None)
+                if seen is not None and seen[0] is mask and seen[1] == mask._version:
+                    all_valid = self._all_tokens_valid(batch)
+                else:
+                    self._device_mask_seen = (mask, mask._version, None)
+            if not all_valid:
+                # masked tokens weigh 0, the others tokens / valid tokens, computed on the device (no wait for the count)
+                w = mask.reshape(-1).float()
+                row_weight = w * (w.numel() / w.sum().clamp_min(1.0))
         hin, hout = sae.cfg.hook_point_in, sae.cfg.hook_point_out
         x = self._normalised_bf16(sae, batch[hin], hin)
         y = self._normalised_bf16(sae, batch[hout], hout)

@@ -301,3 +301,32 @@ def test_closed_form_lr_factor_equals_the_torch_scheduler_for_every_schedule():
             assert abs(sched.get_last_lr()[0] - base * factor(s)) <= 1e-9 + 1e-6 * base, (name, s)
             opt.step()
             sched.step()
+
+
+def test_trainer_remembers_whether_a_reused_device_mask_is_all_true(tmp_path):
+    """The fused paths that refuse masked tokens ask a device mask once per tensor object, not once per step; a changed or
+    different tensor is asked again (here on the CPU, with the device branch reached through a stand-in device type)."""
+    from language_model_saes_b200.trainer import Trainer, TrainerConfig
+
+    tr = Trainer(TrainerConfig(total_training_tokens=10, exp_result_path=str(tmp_path), n_checkpoints=0))
+    assert tr._all_tokens_valid({}) and tr._all_tokens_valid({"mask": torch.ones(4, dtype=torch.bool)})
+    assert not tr._all_tokens_valid({"mask": torch.tensor([True, False])})
+    assert tr._all_tokens_valid({"mask": torch.tensor([True, False]), "_mask_all": True})  # the summary made on arrival wins
+
+    class OnDevice(torch.Tensor):  # a CPU tensor that says it lives elsewhere, and counts how often it is read
+        reads = 0
+
+        @property
+        def device(self):
+            return torch.device("meta")
+
+        def all(self, *a, **k):
+            OnDevice.reads += 1
+            return torch.Tensor.all(self.as_subclass(torch.Tensor), *a, **k)
+
+    m = torch.ones(6, dtype=torch.bool).as_subclass(OnDevice)
+    assert tr._all_tokens_valid({"mask": m}) and tr._all_tokens_valid({"mask": m}) and OnDevice.reads == 1
+    m[2] = False  # an in-place change is seen through the tensor's version counter
+    assert not tr._all_tokens_valid({"mask": m}) and OnDevice.reads == 2
+    other = torch.ones(6, dtype=torch.bool).as_subclass(OnDevice)
+    assert tr._all_tokens_valid({"mask": other}) and OnDevice.reads == 3
