@@ -1037,8 +1037,8 @@ class Trainer:
     def _fused_clt_iteration(self, sae: SparseDictionary, batch: dict[str, Tensor]) -> Tensor:
         """One step of ``ops.fused_clt.FusedCLTStep``: inputs ``[tokens, layers, d]``, targets ``[layers, tokens, d]``."""
         f = self.fused
-        if not self._all_tokens_valid(batch):
-            raise NotImplementedError("the fused cross-layer transcoder path trains on unmasked tokens; set use_fused_kernels=False")
+        # a token mask in the batch plays no part: this model's loss is the mean over all tokens and layers on the generic
+        # path too (models/clt.py compute_loss; clt.py:1059-1067 of the reference project)
         d = sae.cfg.d_model
         # layer-major [layers, tokens, d]: what the per-layer GEMMs and the update kernels read
         xt = torch.stack([self._normalised_bf16(sae, batch[hp], hp).reshape(-1, d) for hp in sae.cfg.hook_points_in], dim=0)
