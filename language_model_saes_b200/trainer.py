@@ -643,6 +643,27 @@ class Trainer:
             self._emit(sae, out)
 
     @torch.no_grad()
+    def _family_metrics(self, sae: SparseDictionary, batch: dict[str, Tensor]) -> dict[str, Any]:
+        """The generic path's metric set (explained variance, l0, error norms, feature frequencies, the model's own
+        figures) for ONE batch, from the model's own forward pass without a graph: what the fused steps of the crosscoder,
+        cross-layer transcoder and Lorsa families log on a logging step (their kernels keep no dense reconstruction to
+        measure). The batch is the logging step's, seen after that step's update. Collective under a mesh: every rank
+        reaches it on the same steps."""
+        nb = sae.normalize_activations(batch)
+        dev_type = torch.device(sae.cfg.device).type
+        amp = self.cfg.amp_dtype is not None and (dev_type == "cuda" or self.cfg.amp_dtype == torch.bfloat16)
+        with torch.autocast(device_type=dev_type, dtype=self.cfg.amp_dtype, enabled=amp):
+            ctx = self._training_step(sae, nb)
+            metrics = [FrequencyMetric(sae), LossMetric(sae), MeanFeatureActMetric(sae), ExplainedVarianceMetric(sae),
+                       L0Metric(sae), L2NormErrorMetric(sae), ModelSpecificMetric(sae)]  # fmt: skip
+            for metric in metrics:
+                ctx = {**ctx, **metric.update(ctx)}
+            out: dict[str, Any] = {}
+            for metric in metrics:
+                out.update(metric.compute())
+        return out
+
+    @torch.no_grad()
     def _log_fused(self, sae: SparseDictionary, x: Tensor, label: Tensor, mask: Tensor | None, loss: Tensor, lr: float):
         """Metrics of the fused path. Per step only three small device accumulations happen (loss, per-feature
         fire counts from the step's counting sort, token count); the dense quantities (explained variance,
@@ -1017,9 +1038,10 @@ class Trainer:
                       lp_coefficient=float(self.cfg.lp_coefficient or 0.0))
         if not self.cfg.skip_metrics_calculation and (self.cur_step + 1) % self.cfg.log_frequency == 0:
             last = {k: float(v) for k, v in f.last.items()}
-            out = {"losses/overall_loss": float(loss), "losses/mse_loss": last["l_rec"], "losses/sparsity_loss": last["l_s"],
-                   "losses/lp_loss": last["l_p"], "metrics/l0_candidates": last["l0"],
-                   "details/list_overflow_tokens": int(f.list_overflow)}  # fmt: skip
+            out = self._family_metrics(sae, batch)
+            out.update({"losses/overall_loss": float(loss), "losses/mse_loss": last["l_rec"], "losses/sparsity_loss": last["l_s"],
+                        "losses/lp_loss": last["l_p"], "metrics/l0_candidates": last["l0"],
+                        "details/list_overflow_tokens": int(f.list_overflow)})  # fmt: skip
             out.update(self._details({"l1_coefficient": l1}, lr))
             out.update(sae.log_statistics())
             self._emit(sae, out)
@@ -1050,7 +1072,8 @@ class Trainer:
         lr = float(self.cfg.lr) * (self._lr_lambda(self.cur_step) if self._lr_lambda is not None else 1.0)
         loss = f.step(x, y, sae.current_k, lr, xt=xt)
         if not self.cfg.skip_metrics_calculation and (self.cur_step + 1) % self.cfg.log_frequency == 0:
-            out = {"losses/overall_loss": float(loss), "losses/mse_loss": float(loss)}
+            out = self._family_metrics(sae, batch)
+            out.update({"losses/overall_loss": float(loss), "losses/mse_loss": float(loss)})
             out.update(self._details({}, lr))
             out.update(sae.log_statistics())
             self._emit(sae, out)
@@ -1085,7 +1108,8 @@ class Trainer:
         lr = float(self.cfg.lr) * (self._lr_lambda(self.cur_step) if self._lr_lambda is not None else 1.0)
         loss = f.step(x, y, sae.current_k, lr, row_weight=row_weight)
         if not self.cfg.skip_metrics_calculation and (self.cur_step + 1) % self.cfg.log_frequency == 0:
-            out = {"losses/overall_loss": float(loss), "losses/mse_loss": float(loss)}
+            out = self._family_metrics(sae, batch)
+            out.update({"losses/overall_loss": float(loss), "losses/mse_loss": float(loss)})
             out.update(self._details({}, lr))
             out.update(sae.log_statistics())
             self._emit(sae, out)

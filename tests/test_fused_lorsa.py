@@ -200,7 +200,10 @@ def test_trainer_picks_the_fused_lorsa_path_and_the_loss_goes_down():
     losses = []
     with tempfile.TemporaryDirectory() as tmp:
         tr = Trainer(TrainerConfig(total_training_tokens=steps * b * s, lr=2e-3, lr_warm_up_steps=2, log_frequency=10**6, n_checkpoints=0,
-                                   exp_result_path=tmp, skip_metrics_calculation=True))  # fmt: skip
+                                   exp_result_path=tmp, skip_metrics_calculation=False))  # fmt: skip
+        tr.cfg.log_frequency = 10
+        emitted = []
+        tr._emit = lambda sae, out: emitted.append(out)
         orig = tr._fused_iteration
 
         def spy(*a, **kw):
@@ -211,6 +214,7 @@ def test_trainer_picks_the_fused_lorsa_path_and_the_loss_goes_down():
         tr._fused_iteration = spy
         tr.fit(m, stream())
         assert type(tr.fused).__name__ == "FusedLorsaStep"
+        assert len(emitted) == steps // 10 and all("metrics/explained_variance" in e and "details/current_learning_rate" in e for e in emitted)
     assert len(losses) == steps and all(l == l for l in losses) and sum(losses[-5:]) < sum(losses[:5]), losses
 
 
@@ -243,3 +247,25 @@ def test_fused_lorsa_step_with_a_token_mask_matches_autograd(dev):
         moved = (a.detach().float() - start[name].float()).abs().mean()
         tol = (0.3 if dev == "cuda" else 0.08) * (3.0 if name == "b_K" else 1.0)
         assert float((a.detach().float() - bb).abs().mean()) < tol * float(moved) + 1e-7, name
+
+
+def test_family_metrics_of_a_logging_step_come_from_the_models_own_forward(tmp_path):
+    """What the fused Lorsa / CLT / crosscoder iterations log on a logging step: the generic path's metric names, computed
+    without a graph from one batch (here after a two-step CPU fit, which sets the trainer's schedules up)."""
+    from language_model_saes_b200.trainer import Trainer, TrainerConfig
+
+    d, b, s = 64, 2, 16
+    m = _model("cpu", d=d, n_ctx=s)
+    hin, hout = m.cfg.hook_point_in, m.cfg.hook_point_out
+    data = _batches("cpu", 3, b, s, d)
+    batches = [{hin: x.float(), hout: y.float(), "tokens": torch.zeros(b, s, dtype=torch.long)} for x, y in data]
+    tr = Trainer(TrainerConfig(total_training_tokens=2 * b * s, lr=1e-3, lr_warm_up_steps=1, log_frequency=10**6, n_checkpoints=0,
+                               exp_result_path=str(tmp_path), skip_metrics_calculation=True))  # fmt: skip
+    tr.fit(m, iter(batches))
+    before = {n: p.detach().clone() for n, p in m.named_parameters()}
+    out = tr._family_metrics(m, batches[0])
+    for key in ("metrics/explained_variance", "metrics/l0", "metrics/l2_norm_error", "losses/mse_loss"):
+        assert key in out, (key, sorted(out))
+    assert 0 < float(out["metrics/l0"]) <= m.cfg.top_k
+    assert all(p.grad is None or not p.grad.any() for p in m.parameters())
+    assert all(torch.equal(before[n], p) for n, p in m.named_parameters())  # a measurement: nothing moves
