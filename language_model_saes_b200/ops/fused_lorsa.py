@@ -20,7 +20,8 @@ them small element-wise kernels that autograd and autocast put around the few pr
    same pass), the dense projections and biases by the flat Adam kernel.
 
 Restrictions: ``topk`` activation, rotary or no positional embedding (no ``rotary_scale``, no QK layer norm), Adam, fp32
-parameters with bf16 compute, sharding over ``model`` (heads) only.
+parameters with bf16 compute; heads sharded over ``model``, sequences split over ``data`` (replicas sum their dense
+gradients in one collective and gather codes and output gradients for the sparse update of ``W_O``).
 """
 
 from __future__ import annotations
@@ -82,6 +83,8 @@ class FusedLorsaStep:
         self.tp = mesh_dim_size(lorsa.device_mesh, "model")
         self.tp_rank = mesh_local_rank(lorsa.device_mesh, "model")
         self.tp_group = mesh_group(lorsa.device_mesh, "model")
+        self.dp = mesh_dim_size(lorsa.device_mesh, "data")
+        self.dp_group = mesh_group(lorsa.device_mesh, "data")
         self.h, self.d, self.dqk = lorsa.W_Q.shape  # local QK heads, d_model, QK head width
         self.F = lorsa.W_V.shape[0]  # local OV heads
         self.group_size = self.F // self.h
@@ -120,7 +123,6 @@ class FusedLorsaStep:
             (cfg.d_model % 64 == 0 and cfg.d_qk_head % 8 == 0 and lorsa.W_V.shape[0] % 8 == 0, "d_model / head widths not aligned"),
             (lorsa.W_V.shape[0] % max(lorsa.W_Q.shape[0], 1) == 0 and (lorsa.W_V.shape[0] // max(lorsa.W_Q.shape[0], 1)) % 8 == 0,
              "OV group size not a multiple of 8"),
-            (mesh_dim_size(lorsa.device_mesh, "data") == 1, "data parallelism"),
             (not any(hp.fwd_hooks or hp.bwd_hooks for hp in lorsa.hook_points()), "hooks are attached"),
         ]  # fmt: skip
         if trainer_cfg is not None:
@@ -201,16 +203,17 @@ class FusedLorsaStep:
         (0 for masked tokens and ``tokens / valid tokens`` for the others gives the mean over valid tokens; masked
         tokens still serve as keys and values of later positions, as they do in the model's own forward pass)."""
         b, s, d = x.shape
-        T = b * s
-        X = x.reshape(T, d).contiguous()
-        Y = label.reshape(T, d).contiguous()
+        T_l = b * s  # this replica's tokens
+        T = T_l * self.dp  # the step's tokens: every replica brings the same number of sequences
+        X = x.reshape(T_l, d).contiguous()
+        Y = label.reshape(T_l, d).contiguous()
         grad_scale = 2.0 / T
         q, k, v = self._project(X, b, s)
         # the attention alone keeps an autograd node (its backward is the library's); everything around it is explicit
         ql, kl, vl = (t.detach().requires_grad_(True) for t in (q, k, v))
         with torch.enable_grad():
             out = self._attention(ql, kl, vl)  # [b, h, s, group]
-        z = out.detach().permute(0, 2, 1, 3).reshape(T, self.F)
+        z = out.detach().permute(0, 2, 1, 3).reshape(T_l, self.F)
         idx, act = self._select(z, k_top)
         self.loss_sum.zero_()
         WO16 = self.WO16
@@ -223,16 +226,16 @@ class FusedLorsaStep:
             dxhat = K.mse_loss_grad(xhat, Y, bD, row_weight, grad_scale, self.loss_sum)
             dact = K.sparse_dact(idx, WO16, dxhat)
         # d z: the activation passes the gradient where a head was selected (its value is the pre-activation itself)
-        dz = torch.zeros(T, self.F + 8, dtype=z.dtype if z.is_cuda else torch.float32, device=x.device)
+        dz = torch.zeros(T_l, self.F + 8, dtype=z.dtype if z.is_cuda else torch.float32, device=x.device)
         dz.scatter_(1, torch.where(idx >= 0, idx, torch.full_like(idx, self.F)).long(), dact.to(dz.dtype))
         dz = dz[:, : self.F].reshape(b, s, self.h, self.group_size).permute(0, 2, 1, 3)
         dq, dk, dv = torch.autograd.grad(out, (ql, kl, vl), dz.to(out.dtype))
         if self.rotary:
             dq, dk = rotate_pair(dq, dk, self.m.rotary_cos, self.m.rotary_sin, self.m.cfg.rotary_adjacent_pairs, inverse=True)
         low = torch.bfloat16 if x.is_cuda else torch.float32
-        dQ = dq.reshape(T, self.h * self.dqk).to(low)
-        dK = dk.reshape(T, self.h * self.dqk).to(low)
-        dV = dv.reshape(T, self.F).to(low)
+        dQ = dq.reshape(T_l, self.h * self.dqk).to(low)
+        dK = dk.reshape(T_l, self.h * self.dqk).to(low)
+        dV = dv.reshape(T_l, self.F).to(low)
         Xl = X.to(low)
         grads = {
             # [head x channel, d] -> the parameter's [head, d, channel]
@@ -245,6 +248,19 @@ class FusedLorsaStep:
         }
         if bD is not None:
             grads["b_D"] = K.colsum_bf16(dxhat)
+        if self.dp > 1:
+            # Replicas: the dense gradients (some 50 MB at 8192 heads) are summed in one collective on a flat buffer; for W_O the
+            # codes and the output gradient of every replica (a few MB) are gathered and each replica rebuilds the same rows, so
+            # that no dense [F, d] gradient exists here either. Every replica then applies the same update.
+            names = list(grads)
+            flat = torch.cat([grads[n].reshape(-1) for n in names])
+            dist.all_reduce(flat, group=self.dp_group)
+            off = 0
+            for n in names:
+                grads[n] = flat[off : off + grads[n].numel()].view(grads[n].shape)
+                off += grads[n].numel()
+            idx, act, dact, dxhat = (self._gather_rows(t) for t in (idx, act, dact, dxhat))
+            dist.all_reduce(self.loss_sum, group=self.dp_group)
         self.t += 1
         b1, b2 = self.betas
         # W_O: rows rebuilt from the codes (act x d x_hat), Adam, bf16 shadow and row norms in one pass
@@ -260,6 +276,13 @@ class FusedLorsaStep:
             K.adam_flat(self.params[name].view(-1), g.reshape(-1), m_.view(-1), v_.view(-1), lr, b1, b2, self.eps, self.t, shadow=shadow)
         self._refresh_qk()
         return (self.loss_sum / T).squeeze(0)
+
+    def _gather_rows(self, t: torch.Tensor) -> torch.Tensor:
+        """``[rows, n]`` of every replica stacked in rank order."""
+        t = t.contiguous()
+        out = torch.empty(self.dp * t.shape[0], *t.shape[1:], dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(out, t, group=self.dp_group)
+        return out
 
     # ---- optimizer state in the model's parameter shapes -------------------------------------------------
     def optimizer_state(self) -> dict:

@@ -1097,7 +1097,10 @@ class Trainer:
             if not all_valid:
                 # masked tokens weigh 0, the others tokens / valid tokens, computed on the device (no wait for the count)
                 w = mask.reshape(-1).float()
-                row_weight = w * (w.numel() / w.sum().clamp_min(1.0))
+                n = w.sum()
+                if f.dp > 1:  # the mean is over the valid tokens of all replicas
+                    dist.all_reduce(n, group=f.dp_group)
+                row_weight = w * (w.numel() * f.dp / n.clamp_min(1.0))
         hin, hout = sae.cfg.hook_point_in, sae.cfg.hook_point_out
         x = self._normalised_bf16(sae, batch[hin], hin)
         y = self._normalised_bf16(sae, batch[hout], hout)

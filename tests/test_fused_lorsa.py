@@ -173,6 +173,40 @@ def _tp_body():
     dist.barrier()
 
 
+def _dp_body():
+    import torch.distributed as dist
+
+    from language_model_saes_b200.parallel.mesh import build_mesh
+
+    d, b, s, lr = 64, 4, 16, 1e-3
+    full = _model("cpu", d=d, nqk=4, dqk=16, n_ov=64, n_ctx=s, k=6)
+    single = copy.deepcopy(full)
+    e1 = FusedLorsaStep(single)
+    r = dist.get_rank()
+    mesh = build_mesh("cpu", (2, 1), ("data", "model"))
+    rep = LowRankSparseAttention(full.cfg.model_copy(), mesh)
+    rep.load_full_state_dict(full.full_state_dict())
+    e2 = FusedLorsaStep(rep)
+    assert e2.dp == 2 and e2.tp == 1
+    g = torch.Generator().manual_seed(11)
+    for x, y in _batches("cpu", 3, b, s, d):
+        mask = torch.rand(b, s, generator=g) > 0.25
+        w = mask.reshape(-1).float()
+        want = e1.step(x, y, 6, lr, row_weight=w * (w.numel() / w.sum()))
+        half = slice(r * b // 2, (r + 1) * b // 2)  # whole sequences per replica
+        got = e2.step(x[half], y[half], 6, lr, row_weight=w.view(b, s)[half].reshape(-1) * (w.numel() / w.sum()))
+        assert torch.allclose(want, got, rtol=1e-4), (want, got)
+    for name, p in single.named_parameters():
+        assert torch.allclose(dict(rep.named_parameters())[name].data, p.data, atol=2e-5), name
+    dist.barrier()
+
+
+def test_fused_lorsa_step_replicas_match_single():
+    from language_model_saes_b200.testing import distributed_test
+
+    distributed_test(nproc_per_node=2, backend="gloo")(_dp_body)()
+
+
 def test_fused_lorsa_step_head_shards_match_single():
     from language_model_saes_b200.testing import distributed_test
 
