@@ -18,8 +18,9 @@ tokens) with Adam. How it computes it:
    shadow, squared row norms accumulated into the per-feature norm over target layers); per SOURCE layer one launch over
    ``W_E[s]`` (encoder side only). No dense gradient tensor exists; the reference materialises one per decoder.
 
-Restrictions: ``topk`` activation with k <= 64, no sparsity loss, Adam, fp32 parameters with bf16 compute, feature
-(``model``) sharding only.
+Restrictions: ``topk`` activation with k <= 64, no sparsity loss, Adam, fp32 parameters with bf16 compute. Features may
+be sharded over ``model`` and tokens split over ``data`` (replicas gather each other's codes, output gradients and inputs
+and rebuild the same sparse rows).
 """
 
 from __future__ import annotations
@@ -40,6 +41,8 @@ class FusedCLTStep:
         self.tp = mesh_dim_size(clt.device_mesh, "model")
         self.tp_rank = mesh_local_rank(clt.device_mesh, "model")
         self.tp_group = mesh_group(clt.device_mesh, "model")
+        self.dp = mesh_dim_size(clt.device_mesh, "data")
+        self.dp_group = mesh_group(clt.device_mesh, "data")
         self.L, self.F, self.d = cfg.n_layers, clt.d_sae_local, cfg.d_model
         self.use_gate = cfg.sparsity_include_decoder_norm
         L, F, d = self.L, self.F, self.d
@@ -78,7 +81,6 @@ class FusedCLTStep:
             (clt.b_E.is_cuda or trainer_cfg is None, "not on a CUDA device"),
             (cfg.dtype == torch.float32, "parameters are not fp32"),
             (cfg.d_model % 8 == 0 and clt.d_sae_local % 8 == 0, "d_model / local d_sae not multiples of 8"),
-            (mesh_dim_size(clt.device_mesh, "data") == 1, "data parallelism"),
             (not any(hp.fwd_hooks or hp.bwd_hooks for hp in clt.hook_points()), "hooks are attached"),
         ]
         if trainer_cfg is not None:
@@ -181,9 +183,17 @@ class FusedCLTStep:
         idx, act = self.encode(x, k, xt)
         y = self._decode(idx, act)
         self.loss_sum.zero_()
-        dy = K.mse_loss_grad(y.view(L * B, d), label.reshape(L * B, d).contiguous(), None, None, 2.0 / (L * B), self.loss_sum)
+        n_rows = L * B * self.dp  # (layer, token) pairs of the whole step: every replica brings B tokens
+        dy = K.mse_loss_grad(y.view(L * B, d), label.reshape(L * B, d).contiguous(), None, None, 2.0 / n_rows, self.loss_sum)
         dy = dy.view(L, B, d)
         dact = CK.clt_dact(idx, self.WD_bf16, dy)
+        if self.dp > 1:
+            # Replicas: codes, their gradients, the output gradients and the inputs of every replica are gathered (rows in rank
+            # order) and each replica rebuilds the same sparse rows of W_D and W_E from them: the same update everywhere, no
+            # dense gradient of the 78 decoder matrices to sum.
+            idx, act, dact = (self._gather_rows(t) for t in (idx, act, dact))
+            dy, xt = self._gather_layer_rows(dy), self._gather_layer_rows(xt)
+            dist.all_reduce(self.loss_sum, group=self.dp_group)
         if self.groups is None or self.groups.entries.numel() < idx.numel():
             self.groups = K.FeatureGroups(L * F, idx.numel(), x.device)
         self.groups.build(idx)
@@ -207,7 +217,21 @@ class FusedCLTStep:
                                vb[s], None, None, None, lr, b1, b2, self.eps, self.t, True)  # fmt: skip
         m, v = self.state["b_D"]
         K.adam_flat(self.bD.view(-1), dy.float().sum(dim=1).reshape(-1), m.view(-1), v.view(-1), lr, b1, b2, self.eps, self.t)
-        return (self.loss_sum / (L * B)).squeeze(0)
+        return (self.loss_sum / n_rows).squeeze(0)
+
+    def _gather_rows(self, t: torch.Tensor) -> torch.Tensor:
+        """``[rows, n]`` of every replica stacked in rank order."""
+        t = t.contiguous()
+        out = torch.empty(self.dp * t.shape[0], *t.shape[1:], dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(out, t, group=self.dp_group)
+        return out
+
+    def _gather_layer_rows(self, t: torch.Tensor) -> torch.Tensor:
+        """``[L, rows, d]`` of every replica -> ``[L, replicas x rows, d]`` with each layer's rows in rank order."""
+        L, B, d = t.shape
+        out = torch.empty(self.dp, L, B, d, dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(out.view(self.dp * L, B, d), t.contiguous(), group=self.dp_group)
+        return out.permute(1, 0, 2, 3).reshape(L, self.dp * B, d)
 
     def optimizer_state(self) -> dict:
         out = {"step": self.t, "W_E": {"exp_avg": self.state["W_E"][0].transpose(1, 2), "exp_avg_sq": self.state["W_E"][1].transpose(1, 2)},

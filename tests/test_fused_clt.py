@@ -98,3 +98,35 @@ def test_fused_clt_step_with_feature_shards_matches_one_process():
         assert close(DimMap({"model": 1}).gather(sharded.W_D[t].data, mesh), single.W_D[t].data), t
     assert close(DimMap({"model": 2}).gather(sharded.W_E.data, mesh), single.W_E.data)
     dist.barrier()
+
+
+@distributed_test(nproc_per_node=2, backend="gloo")
+def test_fused_clt_step_with_replicas_matches_one_process():
+    """Tokens split over two gloo ranks: each replica encodes and decodes its own half, then both rebuild the same sparse
+    updates from the gathered codes; same losses and weights as one process on the whole batch."""
+    import torch.distributed as dist
+
+    from language_model_saes_b200.parallel.mesh import build_mesh
+
+    L, d, F, k, B, lr, steps = 3, 64, 256, 8, 64, 1e-3, 3
+    full = _model("cpu", L, d, F, k, True)
+    mesh = build_mesh("cpu", (2, 1), ("data", "model"))
+    single = copy.deepcopy(full)
+    replica = CrossLayerTranscoder(full.cfg.model_copy(), mesh)
+    replica.load_full_state_dict(full.full_state_dict())
+    e1, e2 = FusedCLTStep(single), FusedCLTStep(replica)
+    assert e2.dp == 2
+    r, half = dist.get_rank(), B // 2
+    g = torch.Generator().manual_seed(1)
+    for _ in range(steps):
+        x = torch.randn(B, L, d, generator=g).to(torch.bfloat16)
+        y = torch.randn(L, B, d, generator=g).to(torch.bfloat16)
+        a = e1.step(x, y, k, lr)
+        b = e2.step(x[r * half : (r + 1) * half], y[:, r * half : (r + 1) * half], k, lr)
+        assert torch.allclose(a, b, rtol=1e-4), (a, b)
+    for t in range(L):
+        assert torch.allclose(replica.W_D[t].data, single.W_D[t].data, atol=1e-6), t
+        assert torch.allclose(replica.b_D[t].data, single.b_D[t].data, atol=1e-6), t
+    assert torch.allclose(replica.W_E.data, single.W_E.data, atol=1e-6)
+    assert torch.allclose(replica.b_E.data, single.b_E.data, atol=1e-6)
+    dist.barrier()
