@@ -51,6 +51,8 @@ class FusedCrosscoderStep:
         self.single = cc.W_D.ndim == 2  # a plain SAE: one head, parameters without the head axis
         self.head_size = mesh_dim_size(cc.device_mesh, "head")
         self.head_group = mesh_group(cc.device_mesh, "head")
+        self.dp = mesh_dim_size(cc.device_mesh, "data")
+        self.dp_group = mesh_group(cc.device_mesh, "data")
         self.window = float(cfg.jumprelu_threshold_window)
         self.cap = -(-list_width // 8) * 8
         self.jumprelu_lr_factor = jumprelu_lr_factor
@@ -111,7 +113,7 @@ class FusedCrosscoderStep:
             (cfg.dtype == torch.float32, "parameters are not fp32"),
             (cfg.d_model % 64 == 0, "d_model is not a multiple of 64"),
             (n_features % 8 == 0, "d_sae is not a multiple of 8"),
-            (mesh_dim_size(cc.device_mesh, "model") == 1 and mesh_dim_size(cc.device_mesh, "data") == 1, "model/data sharding"),
+            (mesh_dim_size(cc.device_mesh, "model") == 1, "feature sharding"),
             (not any(hp.fwd_hooks or hp.bwd_hooks for hp in cc.hook_points()), "hooks are attached"),
         ]  # fmt: skip
         if trainer_cfg is not None:
@@ -122,6 +124,7 @@ class FusedCrosscoderStep:
                 (trainer_cfg.amp_dtype == torch.bfloat16, "amp dtype is not bf16"),
                 (trainer_cfg.gradient_accumulation_steps == 1, "gradient accumulation"),
                 (not trainer_cfg.clip_grad_norm, "gradient clipping"),
+                (not trainer_cfg.lp_coefficient or mesh_dim_size(cc.device_mesh, "data") == 1, "lp loss with data parallelism"),
             ]
         for ok, why in checks:
             if not ok:
@@ -171,11 +174,13 @@ class FusedCrosscoderStep:
         more GEMM per head (``1[S < theta]^T . x_h``, handed to the update kernel as dense gradient rows), its other
         gradients are column sums of ``S`` against the thresholds."""
         assert row_weight is None, "token masks are not supported on this path"
-        B, H_l, d = x.shape
+        assert not lp_coefficient or self.dp == 1, "the pre-activation penalty is not built for replicas"
+        B_l, H_l, d = x.shape  # this replica's tokens
+        B = B_l * self.dp  # the step's tokens: every replica brings the same number
         H, F, cap = self.H, self.F, self.cap
         grad_scale = 2.0 / (B * H)
         x = x.contiguous()
-        S_sum = self._head_sum(x.view(B, H_l * d))
+        S_sum = self._head_sum(x.view(B_l, H_l * d))
         theta = self.log_theta.exp()
         t_head = theta / self.dec_norm  # [H_l, F]: a head is active where S > theta / ||W_D,h row||
         t_min = t_head.amin(0)
@@ -186,13 +191,10 @@ class FusedCrosscoderStep:
         valid = idx >= 0
         # scatter target of the per-feature sums below: empty slots go to a dump element of their own row (sending them all
         # to one element would serialise a million atomic additions on it)
-        dump = F + (torch.arange(B, device=x.device) % 1024).unsqueeze(1)
+        dump = F + (torch.arange(B_l, device=x.device) % 1024).unsqueeze(1)
         scat = torch.where(valid, safe, dump.expand_as(safe)).reshape(-1)
-        if self.groups is None or self.groups.entries.numel() < idx.numel():
-            self.groups = K.FeatureGroups(F, idx.numel(), x.device)
-        self.groups.build(idx)
         self.loss_sum.zero_()
-        dS = torch.zeros(B, cap, dtype=torch.float32, device=x.device)
+        dS = torch.zeros(B_l, cap, dtype=torch.float32, device=x.device)
         dtheta_buf = torch.zeros(F + 1024, dtype=torch.float32, device=x.device)
         dtheta = dtheta_buf[:F]
         l_s_sum = torch.zeros((), dtype=torch.float32, device=x.device)
@@ -251,6 +253,26 @@ class FusedCrosscoderStep:
         if self.head_size > 1:  # the lists are the same on every rank: the sum over heads is element-wise
             dist.all_reduce(dS, group=self.head_group)
             dist.all_reduce(dtheta, group=self.head_group)
+        n_valid = valid.sum()
+        if self.dp > 1:
+            # Replicas: what is a sum over tokens (threshold gradient, the penalty's pull on the decoder norms, the losses) is
+            # summed over the replicas; the lists, their gradients, the inputs and the output gradients of every replica are
+            # gathered in rank order, and every replica rebuilds the same sparse rows from them.
+            dist.all_reduce(dtheta, group=self.dp_group)
+            sums = torch.cat([self.loss_sum, l_s_sum.reshape(1), n_valid.reshape(1).float()])
+            dist.all_reduce(sums, group=self.dp_group)
+            self.loss_sum.copy_(sums[:1])
+            l_s_sum, n_valid = sums[1], sums[2]
+            idx, dS = self._gather_rows(idx), self._gather_rows(dS)
+            gathered = []
+            for xh, act, dxhat, self_scale in per_head:
+                if self_scale is not None:
+                    dist.all_reduce(self_scale, group=self.dp_group)
+                gathered.append((self._gather_rows(xh), self._gather_rows(act), self._gather_rows(dxhat), self_scale))
+            per_head = gathered
+        if self.groups is None or self.groups.entries.numel() < idx.numel():
+            self.groups = K.FeatureGroups(F, idx.numel(), x.device)
+        self.groups.build(idx)
         self.t += 1
         b1, b2 = self.betas
         for h, (xh, act, dxhat, self_scale) in enumerate(per_head):
@@ -269,8 +291,15 @@ class FusedCrosscoderStep:
         l_rec = (self.loss_sum / (B * H_l)).squeeze(0)
         l_s = l1_coefficient * l_s_sum / (B * H_l)
         l_p = l_p_sum if lp is not None else torch.zeros((), device=x.device)
-        self.last = {"l_rec": l_rec, "l_s": l_s, "l_p": l_p, "l0": valid.sum() / B}
+        self.last = {"l_rec": l_rec, "l_s": l_s, "l_p": l_p, "l0": n_valid / B}
         return l_rec + l_s + l_p
+
+    def _gather_rows(self, t: torch.Tensor) -> torch.Tensor:
+        """``[rows, n]`` of every replica stacked in rank order."""
+        t = t.contiguous()
+        out = torch.empty(self.dp * t.shape[0], *t.shape[1:], dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(out, t, group=self.dp_group)
+        return out
 
     def optimizer_state(self) -> dict:
         out = {"step": self.t}

@@ -217,3 +217,40 @@ def test_trainer_trains_a_jumprelu_sae_on_the_fused_path():
         tr.fit(m, stream())
         assert type(tr.fused).__name__ == "FusedCrosscoderStep" and tr.fused.single
     assert len(losses) == steps and all(l == l for l in losses) and sum(losses[-5:]) < sum(losses[:5]), losses
+
+
+def _replica_body():
+    import torch.distributed as dist
+
+    from language_model_saes_b200.parallel.mesh import build_mesh
+
+    H, d, F, B, lr, steps, l1 = 3, 64, 512, 128, 1e-3, 3, 3e-2
+    full = _model("cpu", H, d, F)
+    single = copy.deepcopy(full)
+    mesh = build_mesh("cpu", (2, 1), ("data", "model"))
+    replica = Crosscoder(full.cfg.model_copy(), mesh)
+    replica.load_full_state_dict(full.full_state_dict())
+    e1, e2 = FusedCrosscoderStep(single, list_width=F), FusedCrosscoderStep(replica, list_width=F)
+    assert e2.dp == 2 and FusedCrosscoderStep.supports(replica)[0]
+    g = torch.Generator().manual_seed(1)
+    basis = torch.randn(8, d, generator=g)
+    r, half = dist.get_rank(), B // 2
+    for _ in range(steps):
+        z = torch.randn(B, 8, generator=g)
+        x = torch.stack([z @ basis * (1 + 0.2 * h) + 0.3 * torch.randn(B, d, generator=g) for h in range(H)], dim=1)
+        x = (x * (d**0.5 / x.norm(dim=-1).mean())).to(torch.bfloat16)
+        a = e1.step(x, lr, l1_coefficient=l1)
+        b = e2.step(x[r * half : (r + 1) * half], lr, l1_coefficient=l1)
+        assert torch.allclose(a, b, rtol=1e-4), (a, b)
+        assert torch.allclose(e1.last["l0"], e2.last["l0"])
+    for (name, p), (_, q) in zip(single.named_parameters(), replica.named_parameters()):
+        assert torch.allclose(p.data, q.data, atol=2e-6), name
+    dist.barrier()
+
+
+def test_fused_crosscoder_step_with_replicas_matches_one_process():
+    """Tokens split over two gloo ranks (reconstruction and tanh sparsity losses, shared thresholds): same losses and
+    parameters as one process on the whole batch."""
+    from language_model_saes_b200.testing import distributed_test
+
+    distributed_test(nproc_per_node=2, backend="gloo")(_replica_body)()
