@@ -141,7 +141,9 @@ class LinkGraph {
       const cls = (n.node_id === sel ? "sel " : "") + (this.pinned.has(n.node_id) ? "pin " : "") + (sel && !near.has(n.node_id) ? "dim" : "");
       s += this.shape(n, p, cls);
     }
+    const before = this.host.firstElementChild, scrollLeft = before ? before.scrollLeft : 0;  // a redraw keeps the view where it was
     this.host.innerHTML = `<div style="overflow:auto; max-width:100%">${s}</svg></div>`;
+    this.host.firstElementChild.scrollLeft = scrollLeft;
     const svg = this.host.querySelector("svg");
     // the pointer snaps to the nearest node within 14 px, so that small nodes are easy to hit
     const pick = ev => {
