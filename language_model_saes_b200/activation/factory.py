@@ -17,7 +17,6 @@ from pathlib import Path
 from typing import Any, Callable, Iterable, Iterator, Optional
 
 import numpy as np
-import torch
 from pydantic import BaseModel, ConfigDict
 
 from ..config import BaseConfig, OptionalTorchDType

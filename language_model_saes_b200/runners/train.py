@@ -32,7 +32,7 @@ from ..models.crosscoder import CrosscoderConfig
 from ..models.lorsa import LorsaConfig
 from ..models.molt import MOLTConfig
 from ..models.sae import SAEConfig
-from ..models.sparse_dictionary import SparseDictionary, SparseDictionaryConfig
+from ..models.sparse_dictionary import SparseDictionary
 from ..parallel.mesh import is_primary_rank
 from ..resource_loaders import load_dataset, load_model
 from ..trainer import Trainer, TrainerConfig, WandbConfig

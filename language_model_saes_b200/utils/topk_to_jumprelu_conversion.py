@@ -9,7 +9,7 @@ divided by each feature's decoder norm and the flag is cleared, so that encoding
 from __future__ import annotations
 
 import math
-from typing import Iterable, Optional
+from typing import Iterable
 
 import torch
 

@@ -14,9 +14,9 @@ from language_model_saes_b200.database import MongoClient, MongoDBConfig, SAERec
 from language_model_saes_b200.evaluator import EvalConfig, Evaluator
 from language_model_saes_b200.hooks import HookPoint
 from language_model_saes_b200.initializer import Initializer, InitializerConfig
-from language_model_saes_b200.models.clt import CLTConfig, CrossLayerTranscoder
+from language_model_saes_b200.models.clt import CLTConfig
 from language_model_saes_b200.models.crosscoder import Crosscoder, CrosscoderConfig
-from language_model_saes_b200.models.lorsa import LorsaConfig, LowRankSparseAttention
+from language_model_saes_b200.models.lorsa import LorsaConfig
 from language_model_saes_b200.models.sae import SAEConfig, SparseAutoEncoder
 from language_model_saes_b200.models.sparse_dictionary import SparseDictionary
 from language_model_saes_b200.parallel.mesh import build_mesh, execute_and_broadcast

@@ -8,7 +8,6 @@ import shutil
 import sys
 import types
 from dataclasses import dataclass, field
-from pathlib import Path
 
 import pytest
 import torch

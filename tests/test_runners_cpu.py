@@ -10,7 +10,6 @@ import torch
 
 from language_model_saes_b200.activation.factory import ActivationFactoryActivationsSource, ActivationFactoryConfig, ActivationFactoryTarget
 from language_model_saes_b200.analysis import DirectLogitAttributorConfig, FeatureAnalyzerConfig
-from language_model_saes_b200.backend.language_model import LanguageModelConfig
 from language_model_saes_b200.config import DatasetConfig
 from language_model_saes_b200.evaluator import EvalConfig
 from language_model_saes_b200.initializer import InitializerConfig
