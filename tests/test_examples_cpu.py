@@ -60,6 +60,28 @@ def test_settings_examples_validate(script, recorded, monkeypatch):
     assert sum(len(v) for v in recorded.values()) >= 1, f"{script} called no runner"
 
 
+@pytest.mark.parametrize("family", ["clt", "lorsa"])
+def test_clt_and_lorsa_training_example_meets_the_fused_step_conditions(family, recorded, monkeypatch):
+    _run(EXAMPLES / "train_clt_and_lorsa_topk.py", ["--family", family], monkeypatch)
+    (settings,) = recorded[f"train_{family}"]
+    import copy
+
+    from language_model_saes_b200.models.sparse_dictionary import SparseDictionary
+    from language_model_saes_b200.ops.fused_clt import FusedCLTStep
+    from language_model_saes_b200.ops.fused_lorsa import FusedLorsaStep
+
+    # a narrow copy of the model on the CPU: the conditions on the configuration are the same (the device one is set aside)
+    small = {"clt": dict(expansion_factor=1, device="cpu"), "lorsa": dict(expansion_factor=1, n_qk_heads=12, device="cpu")}[family]
+    model = SparseDictionary.from_config(settings.sae.model_copy(update=small))
+    trainer_cfg = copy.copy(settings.trainer)
+    import torch
+
+    monkeypatch.setattr(torch.Tensor, "is_cuda", property(lambda self: True))  # only the question "is it on a GPU" is answered for it
+    ok, why = (FusedCLTStep if family == "clt" else FusedLorsaStep).supports(model, trainer_cfg)
+    monkeypatch.undo()
+    assert ok, why
+
+
 def test_family_config_example_builds_every_family_on_the_meta_device(capsys, monkeypatch):
     _run(EXAMPLES / "train_crosscoder_clt_lorsa.py", [], monkeypatch)
     out = capsys.readouterr().out
