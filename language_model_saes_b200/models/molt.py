@@ -221,6 +221,12 @@ class MixtureOfLinearTransform(SparseDictionary):
             n = U.shape[0]
             f = feature_acts[..., off : off + n]
             off += n
+            if self.cfg.use_triton_kernel and n > 0:
+                # only the active (token, transform) pairs: gather kernels instead of two dense products over all transforms
+                from ..ops.molt_sparse import molt_group_decode
+
+                out = out + molt_group_decode(f, x, U, V).to(out.dtype)
+                continue
             Vx = torch.einsum("...d,crd->...cr", x.to(V.dtype), V)
             out = out + torch.einsum("...cr,cdr->...d", f.unsqueeze(-1) * Vx, U)
         return out
