@@ -17,7 +17,9 @@ function shade(a, max) {
 function renderSample(s, max, opts = {}) {
   const id = "s" + (++sampleSeq);
   sampleStore.set(id, s);
-  const tokOff = s.token_offset || 0, textOff = s.text_offset || 0, text = s.text || "";
+  const tokOff = s.token_offset || 0, textOff = s.text_offset || 0;
+  // token ranges count characters (code points), a string's own indices count UTF-16 units: cut on an array of characters
+  const chars = Array.from(s.text || ""), text = { slice: (a, b) => chars.slice(a, b).join("") };
   const act = new Map((s.feature_acts_indices || []).map((i, k) => [i - tokOff, s.feature_acts_values[k]]));
   let peak = -1, peakV = 0;
   act.forEach((v, i) => { if (v > peakV) { peakV = v; peak = i; } });
