@@ -33,6 +33,8 @@ takes it too: its parameters are viewed as ``[1, F, d]`` / ``[1, F]`` / ``[1, d]
 
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -40,6 +42,12 @@ from ..parallel.mesh import mesh_dim_size, mesh_group
 from . import sae_kernels as K
 from . import select_kernels as S
 from .fused_step import _mm_f32
+
+
+def TANH_QUAD_ON_FUSED_PATH() -> bool:
+    """The ``tanh-quad`` penalty on the fused step is verified against autograd on the CPU (the step's torch statements) and
+    uses the same kernels as the ``tanh`` penalty, but it has not run on a GPU: the trainer takes it only on request."""
+    return os.environ.get("LMSAE_FUSED_TANH_QUAD", "0") == "1"
 
 
 class FusedCrosscoderStep:
@@ -118,7 +126,8 @@ class FusedCrosscoderStep:
         ]  # fmt: skip
         if trainer_cfg is not None:
             checks += [
-                (trainer_cfg.sparsity_loss_type in (None, "tanh"), "sparsity loss other than tanh"),
+                (trainer_cfg.sparsity_loss_type in (None, "tanh") or (trainer_cfg.sparsity_loss_type == "tanh-quad" and TANH_QUAD_ON_FUSED_PATH()),
+                 "sparsity loss other than tanh (tanh-quad: set LMSAE_FUSED_TANH_QUAD=1)"),
                 (not trainer_cfg.auxk_coefficient, "aux-k loss"),
                 (trainer_cfg.optimizer_class == "adam", "optimizer is not adam"),
                 (trainer_cfg.amp_dtype == torch.bfloat16, "amp dtype is not bf16"),
@@ -164,7 +173,8 @@ class FusedCrosscoderStep:
         return self.comm.all_reduce(B) if self.head_size > 1 else P
 
     def step(self, x: torch.Tensor, lr: float, l1_coefficient: float = 0.0, tanh_stretch: float = 4.0,
-             row_weight: torch.Tensor | None = None, lp_coefficient: float = 0.0) -> torch.Tensor:  # fmt: skip
+             row_weight: torch.Tensor | None = None, lp_coefficient: float = 0.0, sparsity_loss_type: str = "tanh",
+             frequency_scale: float = 0.01) -> torch.Tensor:  # fmt: skip
         """``x``: normalised bf16 activations ``[B, H_l, d]`` of this rank's heads (they are also the labels). Returns the
         mean loss over tokens and this rank's heads (0-d device tensor); ``self.last`` holds its parts.
 
@@ -175,6 +185,8 @@ class FusedCrosscoderStep:
         gradients are column sums of ``S`` against the thresholds."""
         assert row_weight is None, "token masks are not supported on this path"
         assert not lp_coefficient or self.dp == 1, "the pre-activation penalty is not built for replicas"
+        assert sparsity_loss_type in ("tanh", "tanh-quad"), sparsity_loss_type
+        quad = bool(l1_coefficient) and sparsity_loss_type == "tanh-quad"
         B_l, H_l, d = x.shape  # this replica's tokens
         B = B_l * self.dp  # the step's tokens: every replica brings the same number
         H, F, cap = self.H, self.F, self.cap
@@ -215,6 +227,24 @@ class FusedCrosscoderStep:
             lp = {"mask": below.to(torch.bfloat16), "row_scale": -c_lp * n_all, "gb": -c_lp * n_all * count, "gap": gap,
                   "rows": torch.arange(F, dtype=torch.int32, device=x.device), "c": c_lp}  # fmt: skip
             l_p_sum = c_lp * (gap * n_local).sum() * H / H_l  # mean over tokens and THIS rank's heads
+        mult = None  # per-feature factor on every derivative of the sparsity penalty (1 for the plain tanh penalty)
+        if quad:
+            # tanh-quad: l_s = l1 * sum_f q_f (1 + q_f / scale) with q_f the mean of tanh(c * act * norm) over ALL tokens and
+            # heads (models/sparse_dictionary.py:906-915 of the reference project). Its derivative with respect to one entry is
+            # the tanh penalty's times (1 + 2 q_f / scale): one pass over the lists for q, then the tanh code with that factor.
+            q_sum = torch.zeros(F + 1024, dtype=torch.float32, device=x.device)
+            for h in range(H_l):
+                active_h = valid & (s_val > t_head[h][safe])
+                u_h = torch.tanh(c * s_val * self.dec_norm[h][safe]) * active_h
+                q_sum.index_add_(0, scat, u_h.reshape(-1))
+            q = q_sum[:F]
+            if self.head_size > 1:
+                dist.all_reduce(q, group=self.head_group)
+            if self.dp > 1:
+                dist.all_reduce(q, group=self.dp_group)
+            q = q / (B * H)
+            mult = 1.0 + 2.0 * q / frequency_scale
+            l_s_quad = l1_coefficient * (q * (1.0 + q / frequency_scale)).sum()
         for h in range(H_l):
             xh = x[:, h].contiguous()
             n_h = self.dec_norm[h]
@@ -229,10 +259,11 @@ class FusedCrosscoderStep:
                 sech2 = 1.0 - u * u
                 l_s_sum = l_s_sum + (u * active).sum()
                 coef = l1_coefficient * c / (B * H)
-                dact = dact + coef * n_e * sech2 * active
+                m_e = mult[safe] if mult is not None else 1.0  # the tanh-quad factor of every entry's feature
+                dact = dact + coef * n_e * sech2 * active * m_e
                 # the penalty also pulls on the decoder norm: d / d W_D[f] = (sum_b coef * act * sech^2) * W_D[f] / ||W_D[f]||
                 per_feat = torch.zeros(F + 1024, dtype=torch.float32, device=x.device)
-                per_feat.index_add_(0, scat, (coef * act * sech2 * active).reshape(-1))
+                per_feat.index_add_(0, scat, (coef * act * sech2 * active * m_e).reshape(-1))
                 self_scale = per_feat[:F] / n_h
             if lp is not None:  # the penalty's pull on this head's decoder norms: d / d W_D[f] = c * gap_f * W_D[f] / ||W_D[f]||
                 pull = lp["c"] * lp["gap"] / n_h
@@ -243,11 +274,20 @@ class FusedCrosscoderStep:
             # (the tanh penalty's derivative with respect to the JumpReLU output is coef at every entry with zero activation:
             # the dense pass adds it per window hit)
             G = K.encoder_hidden(dxhat, self.WD_bf16[h], None)  # [B, F] bf16 = d x_hat . W_D^T
-            S.jumprelu_window_grad(G, S_sum, n_h, theta, self.window, dtheta, add_per_hit=coef if l1_coefficient else 0.0)
+            if mult is None:
+                S.jumprelu_window_grad(G, S_sum, n_h, theta, self.window, dtheta, add_per_hit=coef if l1_coefficient else 0.0)
+            else:
+                # the per-hit term carries a per-feature factor here: the kernel runs with 0 and with 1 per hit; the difference
+                # of the two sums is (hits of the feature) x (-theta / window), which is then scaled by coef x factor
+                d0 = torch.zeros(F, dtype=torch.float32, device=x.device)
+                d1 = torch.zeros(F, dtype=torch.float32, device=x.device)
+                S.jumprelu_window_grad(G, S_sum, n_h, theta, self.window, d0, add_per_hit=0.0)
+                S.jumprelu_window_grad(G, S_sum, n_h, theta, self.window, d1, add_per_hit=1.0)
+                dtheta += d0 + coef * mult * (d1 - d0)
             if l1_coefficient:  # ... and the active entries, whose derivative is coef * sech^2, are corrected on the lists
                 x_e = s_val * n_e
                 hit = active & ((x_e - theta[safe]).abs() < 0.5 * self.window)
-                contrib = coef * (sech2 - 1.0) * (-theta[safe] / self.window) * hit
+                contrib = coef * (sech2 - 1.0) * (-theta[safe] / self.window) * hit * m_e
                 dtheta_buf.index_add_(0, scat, contrib.reshape(-1))
             per_head.append((xh, act, dxhat, self_scale))
         if self.head_size > 1:  # the lists are the same on every rank: the sum over heads is element-wise
@@ -289,7 +329,7 @@ class FusedCrosscoderStep:
         m, v = self.state["log_theta"]
         K.adam_flat(self.log_theta, dtheta * theta, m, v, lr * self.jumprelu_lr_factor, b1, b2, self.eps, self.t)
         l_rec = (self.loss_sum / (B * H_l)).squeeze(0)
-        l_s = l1_coefficient * l_s_sum / (B * H_l)
+        l_s = l_s_quad if quad else l1_coefficient * l_s_sum / (B * H_l)
         l_p = l_p_sum if lp is not None else torch.zeros((), device=x.device)
         self.last = {"l_rec": l_rec, "l_s": l_s, "l_p": l_p, "l0": n_valid / B}
         return l_rec + l_s + l_p

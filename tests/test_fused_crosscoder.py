@@ -254,3 +254,80 @@ def test_fused_crosscoder_step_with_replicas_matches_one_process():
     from language_model_saes_b200.testing import distributed_test
 
     distributed_test(nproc_per_node=2, backend="gloo")(_replica_body)()
+
+
+@pytest.mark.parametrize("H", [3, 1])
+def test_tanh_quad_penalty_on_the_fused_step_matches_autograd(H):
+    """The frequency-weighted penalty ``l1 * sum_f q_f (1 + q_f / scale)`` (the reference's usual choice for JumpReLU
+    dictionaries): losses and every parameter after a few Adam steps against the model's own loss on the CPU. A large
+    ``l1`` and a small scale make the penalty's gradients (decoder norms, thresholds, encoder) count."""
+    dev, d, F, B, lr, steps, l1, scale = "cpu", 64, 512, 256, 1e-3, 4, 5e-2, 0.05
+    ref = _model(dev, H, d, F)
+    fused_model = copy.deepcopy(ref)
+    engine = FusedCrosscoderStep(fused_model, list_width=F)
+    g = torch.Generator().manual_seed(2)
+    basis = torch.randn(8, d, generator=g)
+    opt = torch.optim.Adam(ref.parameters(), lr=lr)
+    start = {n: p.detach().clone() for n, p in ref.named_parameters()}
+    tokens = torch.zeros(B, dtype=torch.long)
+    for _ in range(steps):
+        z = torch.randn(B, 8, generator=g)
+        x = torch.stack([z @ basis * (1 + 0.2 * h) + 0.3 * torch.randn(B, d, generator=g) for h in range(H)], dim=1)
+        x = (x * (d**0.5 / x.norm(dim=-1).mean())).to(torch.bfloat16)
+        opt.zero_grad()
+        batch = {f"s{h}": x[:, h].float() for h in range(H)} | {"tokens": tokens}
+        out = ref.compute_loss(batch, sparsity_loss_type="tanh-quad", l1_coefficient=l1, frequency_scale=scale, return_aux_data=True)
+        out["loss"].backward()
+        opt.step()
+        got = engine.step(x, lr, l1_coefficient=l1, sparsity_loss_type="tanh-quad", frequency_scale=scale)
+        assert torch.allclose(out["loss"].detach(), got, rtol=2e-3), (out["loss"], got)
+        assert torch.allclose(out["l_s"].detach().float().mean(), engine.last["l_s"], rtol=5e-3)
+        assert float(engine.last["l_s"]) > 0.02 * float(got)  # the penalty is a visible part of the loss
+    for name, a in ref.named_parameters():
+        b = dict(fused_model.named_parameters())[name].detach().float()
+        moved = (a.detach().float() - start[name].float()).abs().mean()
+        assert float((a.detach().float() - b).abs().mean()) < 0.05 * float(moved) + 1e-7, name
+
+
+def _quad_replica_body():
+    import torch.distributed as dist
+
+    from language_model_saes_b200.parallel.mesh import build_mesh
+
+    H, d, F, B, lr, l1, scale = 2, 64, 256, 128, 1e-3, 5e-2, 0.05
+    full = _model("cpu", H, d, F)
+    single = copy.deepcopy(full)
+    replica = Crosscoder(full.cfg.model_copy(), build_mesh("cpu", (2, 1), ("data", "model")))
+    replica.load_full_state_dict(full.full_state_dict())
+    e1, e2 = FusedCrosscoderStep(single, list_width=F), FusedCrosscoderStep(replica, list_width=F)
+    g = torch.Generator().manual_seed(4)
+    r, half = dist.get_rank(), B // 2
+    for _ in range(3):
+        x = (torch.randn(B, H, d, generator=g) * 1.5).to(torch.bfloat16)
+        a = e1.step(x, lr, l1_coefficient=l1, sparsity_loss_type="tanh-quad", frequency_scale=scale)
+        b = e2.step(x[r * half : (r + 1) * half], lr, l1_coefficient=l1, sparsity_loss_type="tanh-quad", frequency_scale=scale)
+        assert torch.allclose(a, b, rtol=1e-4), (a, b)  # the frequencies are those of the whole batch on every replica
+    for (name, p), (_, q) in zip(single.named_parameters(), replica.named_parameters()):
+        assert torch.allclose(p.data, q.data, atol=2e-6), name
+    dist.barrier()
+
+
+def test_tanh_quad_penalty_with_replicas_matches_one_process():
+    from language_model_saes_b200.testing import distributed_test
+
+    distributed_test(nproc_per_node=2, backend="gloo")(_quad_replica_body)()
+
+
+def test_trainer_takes_the_fused_step_for_tanh_quad_only_on_request(monkeypatch, tmp_path):
+    from language_model_saes_b200.trainer import TrainerConfig
+
+    m = _model("cpu", 2, 64, 256)
+    cfg = TrainerConfig(total_training_tokens=10, exp_result_path=str(tmp_path), n_checkpoints=0, sparsity_loss_type="tanh-quad", l1_coefficient=0.3)
+    monkeypatch.setattr(torch.Tensor, "is_cuda", property(lambda self: True))  # only "is it on a GPU" is answered for the model
+    monkeypatch.delenv("LMSAE_FUSED_TANH_QUAD", raising=False)
+    ok, why = FusedCrosscoderStep.supports(m, cfg)
+    assert not ok and "tanh-quad" in why
+    monkeypatch.setenv("LMSAE_FUSED_TANH_QUAD", "1")
+    assert FusedCrosscoderStep.supports(m, cfg) == (True, "")
+    cfg.sparsity_loss_type = "power"
+    assert not FusedCrosscoderStep.supports(m, cfg)[0]
