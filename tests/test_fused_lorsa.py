@@ -303,3 +303,22 @@ def test_family_metrics_of_a_logging_step_come_from_the_models_own_forward(tmp_p
     assert 0 < float(out["metrics/l0"]) <= m.cfg.top_k
     assert all(p.grad is None or not p.grad.any() for p in m.parameters())
     assert all(torch.equal(before[n], p) for n, p in m.named_parameters())  # a measurement: nothing moves
+
+
+def test_fused_lorsa_optimizer_state_round_trip_continues_the_run():
+    """Moments and step counter saved by parameter name and loaded into a fresh engine: the next step is the same."""
+    d, b, s, lr = 64, 2, 16, 1e-3
+    m1 = _model("cpu", d=d, n_ctx=s)
+    e1 = FusedLorsaStep(m1)
+    data = _batches("cpu", 3, b, s, d)
+    for x, y in data[:2]:
+        e1.step(x, y, 6, lr)
+    m2 = copy.deepcopy(m1)
+    saved = {k: ({kk: vv.clone() for kk, vv in v.items()} if isinstance(v, dict) else v) for k, v in e1.optimizer_state().items()}
+    e2 = FusedLorsaStep(m2)
+    e2.load_optimizer_state(saved)
+    assert e2.t == e1.t == 2
+    x, y = data[2]
+    assert torch.equal(e1.step(x, y, 6, lr), e2.step(x, y, 6, lr))
+    for (name, p), (_, q) in zip(m1.named_parameters(), m2.named_parameters()):
+        assert torch.equal(p, q), name
