@@ -191,6 +191,9 @@ class ExplainedVarianceMetric(_ShardAware):
         label, rec, mask = ctx["label"].float(), ctx["reconstructed"].float(), ctx.get("mask")
         specs = self.sae.specs.label(label)
         label_mean = apply_token_mask(label, specs, mask, "mean")[0]
+        # the mean goes back under the token axes it was taken over, wherever the model keeps them ([layers, batch, d] for a
+        # cross-layer transcoder, where a plain trailing-axes broadcast would pair layers with tokens)
+        label_mean = label_mean.reshape([1 if s in ("batch", "context") else label.shape[i] for i, s in enumerate(specs)])
         err = (rec - label).pow(2).sum(dim=-1)
         var = (label - label_mean).pow(2).sum(dim=-1)
         legacy = apply_token_mask(1 - err / var, specs[:-1], mask, "mean")[0]

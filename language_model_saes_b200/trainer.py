@@ -893,11 +893,12 @@ class Trainer:
 
     def _kernel_status(self, sae: SparseDictionary) -> Tensor | None:
         """The status word of this model's device when hand-written kernels are in play (read back with the loss)."""
-        if self.fused is None:
+        dev = next(sae.parameters()).device
+        if self.fused is None or dev.type != "cuda":
             return None
         from .ops import sae_kernels as K
 
-        return K.status_buffer(next(sae.parameters()).device)
+        return K.status_buffer(dev)
 
     def _make_heartbeat(self):
         if self.cfg.heartbeat_timeout_s is None or not dist.is_initialized() or dist.get_world_size() == 1:
