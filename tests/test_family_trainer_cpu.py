@@ -160,3 +160,63 @@ def test_explained_variance_of_a_layer_major_label_uses_per_layer_means():
         var = (lab - lab.mean(1, keepdim=True)).pow(2).sum(-1).mean(1)
         assert torch.allclose(out["explained_variance"], 1 - err / var, atol=1e-5)
         assert 0.85 < float(out["explained_variance"].mean()) < 0.95
+
+
+@pytest.fixture
+def crosscoder_on_cpu(monkeypatch):
+    from language_model_saes_b200.ops.fused_crosscoder import FusedCrosscoderStep
+
+    orig = FusedCrosscoderStep.supports
+    monkeypatch.setattr(FusedCrosscoderStep, "supports", staticmethod(lambda model, trainer_cfg=None, _orig=orig: _orig(model, None)))
+
+
+def jumprelu_sae(seed=0):
+    from language_model_saes_b200.models.sae import SAEConfig, SparseAutoEncoder
+
+    torch.manual_seed(seed)
+    cfg = SAEConfig(hook_point_in="h", hook_point_out="h", d_model=64, expansion_factor=4, act_fn="jumprelu", device="cpu", dtype=torch.float32,
+                    norm_activation="inference")  # fmt: skip
+    m = SparseAutoEncoder(cfg)
+    m.init_parameters(encoder_uniform_bound=0.2, decoder_uniform_bound=0.2, init_log_jumprelu_threshold_value=-1.0)
+    m.set_decoder_to_fixed_norm(1.0, True)
+    m.init_encoder_with_decoder_transpose()
+    return m
+
+
+def sae_stream(n, B=64, d=64, seed=3):
+    g = torch.Generator().manual_seed(seed)
+    basis = torch.randn(10, d, generator=g)
+    for _ in range(n):
+        x = torch.randn(B, 10, generator=g) @ basis + 0.05 * torch.randn(B, d, generator=g)
+        yield {"h": x * (d**0.5 / x.norm(dim=-1).mean()), "tokens": torch.ones(B, dtype=torch.long)}
+
+
+@pytest.mark.parametrize("penalty", ["tanh", "tanh-quad"])
+def test_jumprelu_sae_fit_on_the_fused_step_follows_the_generic_run_and_resumes(crosscoder_on_cpu, tmp_path, penalty):
+    kw = dict(sparsity_loss_type=penalty, l1_coefficient=0.02, jumprelu_lr_factor=0.5)
+    fused = jumprelu_sae()
+    tr = trainer(tmp_path / "fused", 64 * 10, log_frequency=5, skip_metrics_calculation=False, **kw)
+    emitted = []
+    tr._emit = lambda sae, out: emitted.append(out)
+    assert tr.fit(fused, sae_stream(11)) is None
+    assert type(tr.fused).__name__ == "FusedCrosscoderStep" and tr.fused.single
+    assert len(emitted) == 2 and {"losses/sparsity_loss", "metrics/explained_variance", "metrics/l0"} <= set(emitted[0])
+    generic = jumprelu_sae()
+    tg = trainer(tmp_path / "generic", 64 * 10, use_fused_kernels=False, amp_dtype=torch.float32, **kw)
+    assert tg.fit(generic, sae_stream(11)) is None and tg.fused is None
+    start = jumprelu_sae()
+    for (name, p), (_, q), (_, p0) in zip(fused.named_parameters(), generic.named_parameters(), start.named_parameters()):
+        moved = float((q - p0).abs().mean())
+        assert float((p - q).abs().mean()) < 0.1 * moved + 1e-7, name
+    # resume half-way: same end state as the uninterrupted fused run
+    first = jumprelu_sae()
+    t1 = trainer(tmp_path / "part", 64 * 10, **kw)
+    data = sae_stream(11)
+    assert t1.fit(first, (next(data) for _ in range(5))) is True
+    t1.save_checkpoint(first, tmp_path / "part")
+    ckpt = tmp_path / "part" / "checkpoints" / "step_5"
+    second = SparseDictionary.from_pretrained(str(ckpt), fold_activation_scale=False, device="cpu", dtype=torch.float32)
+    t2 = Trainer.from_checkpoint(second, str(ckpt))
+    assert t2.fit(second, data) is None and t2.cur_step == 10 and type(t2.fused).__name__ == "FusedCrosscoderStep"
+    for (k, a), b in zip(fused.state_dict().items(), second.state_dict().values()):
+        assert torch.allclose(a, b, atol=1e-6), k
