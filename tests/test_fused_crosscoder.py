@@ -331,3 +331,70 @@ def test_trainer_takes_the_fused_step_for_tanh_quad_only_on_request(monkeypatch,
     assert FusedCrosscoderStep.supports(m, cfg) == (True, "")
     cfg.sparsity_loss_type = "power"
     assert not FusedCrosscoderStep.supports(m, cfg)[0]
+
+
+def _head_parallel_body(penalty: str, lp: float, dims=(2, 1, 1)):
+    """Heads over the ``head`` ranks (and tokens over ``data`` ranks when there are any) against ONE process holding all
+    heads and the whole batch: the sum over heads of the pre-activations, the frequencies of the tanh-quad penalty and the
+    shared thresholds' gradient cross ranks."""
+    import torch.distributed as dist
+
+    from language_model_saes_b200.parallel.mesh import DimMap, build_mesh
+
+    H, d, F, B, lr, l1, scale = 4, 64, 256, 128, 1e-3, 5e-2, 0.05
+    full = _model("cpu", H, d, F)
+    single = copy.deepcopy(full)
+    mesh = build_mesh("cpu", dims, ("head", "data", "model"))
+    sharded = Crosscoder(full.cfg.model_copy(), mesh)
+    sharded.load_full_state_dict(full.full_state_dict())
+    e1, e2 = FusedCrosscoderStep(single, list_width=F), FusedCrosscoderStep(sharded, list_width=F)
+    hp, dp = dims[0], dims[1]
+    assert e2.head_size == hp and e2.dp == dp and e2.H_l == H // hp
+    hr, dr = mesh.get_local_rank("head"), mesh.get_local_rank("data")
+    per, rows = H // hp, B // dp
+    g = torch.Generator().manual_seed(7)
+    kw = dict(l1_coefficient=l1, sparsity_loss_type=penalty, frequency_scale=scale, lp_coefficient=lp)
+    for _ in range(3):
+        x = (torch.randn(B, H, d, generator=g) * 1.5).to(torch.bfloat16)
+        want = e1.step(x, lr, **kw)
+        mine = x[dr * rows : (dr + 1) * rows, hr * per : (hr + 1) * per].contiguous()
+        e2.step(mine, lr, **kw)
+        # reconstruction loss: mean over tokens and this rank's heads -> mean over the head ranks is the single-process value
+        l_rec = e2.last["l_rec"].clone()
+        dist.all_reduce(l_rec, group=mesh.get_group("head"))
+        assert torch.allclose(l_rec / hp, e1.last["l_rec"], rtol=1e-4), (l_rec / hp, e1.last["l_rec"])
+        assert torch.allclose(e1.last["l0"], e2.last["l0"])
+        if penalty == "tanh-quad":
+            assert torch.allclose(e1.last["l_s"], e2.last["l_s"], rtol=1e-4)  # one global figure
+        assert torch.isfinite(want)
+    for name in ("W_D", "W_E", "b_E", "b_D"):
+        whole = DimMap({"head": 0}).gather(getattr(sharded, name).data, mesh)
+        assert torch.allclose(whole, getattr(single, name).data, atol=5e-6), name
+    a, b = single.activation_function.log_jumprelu_threshold.data, sharded.activation_function.log_jumprelu_threshold.data
+    assert torch.allclose(a, b, atol=5e-6)
+    dist.barrier()
+
+
+def _heads_tanh_lp_body():
+    _head_parallel_body("tanh", 2e-3)
+
+
+def _heads_quad_body():
+    _head_parallel_body("tanh-quad", 0.0)
+
+
+def _heads_and_replicas_body():
+    _head_parallel_body("tanh-quad", 0.0, dims=(2, 2, 1))
+
+
+@pytest.mark.parametrize("body", ["_heads_tanh_lp_body", "_heads_quad_body"])
+def test_fused_crosscoder_step_with_heads_over_two_ranks_matches_one_process(body):
+    from language_model_saes_b200.testing import distributed_test
+
+    distributed_test(nproc_per_node=2, backend="gloo")(globals()[body])()
+
+
+def test_fused_crosscoder_step_with_heads_and_replicas_on_four_ranks_matches_one_process():
+    from language_model_saes_b200.testing import distributed_test
+
+    distributed_test(nproc_per_node=4, backend="gloo")(_heads_and_replicas_body)()
