@@ -130,3 +130,36 @@ def test_fused_clt_step_with_replicas_matches_one_process():
     assert torch.allclose(replica.W_E.data, single.W_E.data, atol=1e-6)
     assert torch.allclose(replica.b_E.data, single.b_E.data, atol=1e-6)
     dist.barrier()
+
+
+@distributed_test(nproc_per_node=4, backend="gloo")
+def test_fused_clt_step_with_feature_shards_and_replicas_on_four_ranks_matches_one_process():
+    import torch.distributed as dist
+
+    from language_model_saes_b200.parallel.mesh import DimMap, build_mesh
+
+    L, d, F, k, B, lr, steps = 3, 64, 256, 8, 64, 1e-3, 3
+    full = _model("cpu", L, d, F, k, True)
+    mesh = build_mesh("cpu", (2, 2), ("data", "model"))
+    single = copy.deepcopy(full)
+    sharded = CrossLayerTranscoder(full.cfg.model_copy(), mesh)
+    sharded.load_full_state_dict(full.full_state_dict())
+    e1, e2 = FusedCLTStep(single), FusedCLTStep(sharded)
+    assert e2.tp == 2 and e2.dp == 2
+    dr, half = mesh.get_local_rank("data"), B // 2
+    g = torch.Generator().manual_seed(1)
+    for _ in range(steps):
+        x = torch.randn(B, L, d, generator=g).to(torch.bfloat16)
+        y = torch.randn(L, B, d, generator=g).to(torch.bfloat16)
+        a = e1.step(x, y, k, lr)
+        b = e2.step(x[dr * half : (dr + 1) * half], y[:, dr * half : (dr + 1) * half], k, lr)
+        assert torch.allclose(a, b, rtol=1e-4), (a, b)
+
+    def close(a, b):  # see the feature-shard test: a flipped bf16 rounding moves a few weights by up to lr per step
+        diff = (a - b).abs()
+        return float(diff.mean()) < 2e-6 and float(diff.max()) <= 2.2 * lr * steps
+
+    for t in range(L):
+        assert close(DimMap({"model": 1}).gather(sharded.W_D[t].data, mesh), single.W_D[t].data), t
+    assert close(DimMap({"model": 2}).gather(sharded.W_E.data, mesh), single.W_E.data)
+    dist.barrier()

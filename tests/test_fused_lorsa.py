@@ -322,3 +322,36 @@ def test_fused_lorsa_optimizer_state_round_trip_continues_the_run():
     assert torch.equal(e1.step(x, y, 6, lr), e2.step(x, y, 6, lr))
     for (name, p), (_, q) in zip(m1.named_parameters(), m2.named_parameters()):
         assert torch.equal(p, q), name
+
+
+def _tp_dp_body():
+    import torch.distributed as dist
+
+    from language_model_saes_b200.parallel.mesh import DimMap, build_mesh
+
+    d, b, s, lr = 64, 4, 16, 1e-3
+    full = _model("cpu", d=d, nqk=4, dqk=16, n_ov=64, n_ctx=s, k=6)
+    single = copy.deepcopy(full)
+    e1 = FusedLorsaStep(single)
+    mesh = build_mesh("cpu", (2, 2), ("data", "model"))
+    shard = LowRankSparseAttention(full.cfg.model_copy(), mesh)
+    shard.load_full_state_dict(full.full_state_dict())
+    e2 = FusedLorsaStep(shard)
+    assert e2.tp == 2 and e2.dp == 2
+    dr = mesh.get_local_rank("data")
+    for x, y in _batches("cpu", 3, b, s, d):
+        want = e1.step(x, y, 6, lr)
+        half = slice(dr * b // 2, (dr + 1) * b // 2)
+        got = e2.step(x[half], y[half], 6, lr)
+        assert torch.allclose(want, got, rtol=1e-4), (want, got)
+    for name in ("W_Q", "W_K", "W_V", "W_O", "b_Q", "b_V"):
+        whole = DimMap({"model": 0}).gather(getattr(shard, name).data, mesh)
+        assert torch.allclose(whole, getattr(single, name).data, atol=2e-5), name
+    assert torch.allclose(shard.b_D.data, single.b_D.data, atol=2e-5)
+    dist.barrier()
+
+
+def test_fused_lorsa_step_head_shards_and_replicas_on_four_ranks_match_single():
+    from language_model_saes_b200.testing import distributed_test
+
+    distributed_test(nproc_per_node=4, backend="gloo")(_tp_dp_body)()
