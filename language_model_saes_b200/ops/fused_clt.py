@@ -25,12 +25,20 @@ and rebuild the same sparse rows).
 
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 
 from ..parallel.mesh import mesh_dim_size, mesh_group, mesh_local_rank
 from . import clt_kernels as CK
 from . import sae_kernels as K
+
+
+def LAYERTOPK_ON_FUSED_PATH() -> bool:
+    """``layertopk`` on the fused step is verified against autograd on the CPU and composed of kernels that have GPU tests of
+    their own, but the composition has not run on a GPU: the trainer takes it only on request."""
+    return os.environ.get("LMSAE_FUSED_LAYERTOPK", "0") == "1"
 
 
 class FusedCLTStep:
@@ -45,6 +53,7 @@ class FusedCLTStep:
         self.dp_group = mesh_group(clt.device_mesh, "data")
         self.L, self.F, self.d = cfg.n_layers, clt.d_sae_local, cfg.d_model
         self.use_gate = cfg.sparsity_include_decoder_norm
+        self.joint = cfg.act_fn == "layertopk"  # k codes per token over all layers together, instead of k per layer
         L, F, d = self.L, self.F, self.d
         self.WE = clt.W_E.data.transpose(1, 2)  # [L, F, d] contiguous view of the parameter's storage
         assert self.WE.is_contiguous() and self.WE.dtype == torch.float32
@@ -76,8 +85,9 @@ class FusedCLTStep:
         if type(clt) is not CrossLayerTranscoder:
             return False, "model is not a CrossLayerTranscoder"
         checks = [
-            (cfg.act_fn == "topk", "activation is not the per-layer topk"),
-            (cfg.top_k <= 64, "k > 64"),
+            (cfg.act_fn == "topk" or (cfg.act_fn == "layertopk" and LAYERTOPK_ON_FUSED_PATH()),
+             "activation is not the per-layer topk (layertopk: set LMSAE_FUSED_LAYERTOPK=1)"),
+            (cfg.top_k <= (64 if cfg.act_fn == "topk" else 512), "k above the list width of the step"),
             (clt.b_E.is_cuda or trainer_cfg is None, "not on a CUDA device"),
             (cfg.dtype == torch.float32, "parameters are not fp32"),
             (cfg.d_model % 8 == 0 and clt.d_sae_local % 8 == 0, "d_model / local d_sae not multiples of 8"),
@@ -90,7 +100,7 @@ class FusedCLTStep:
                 (trainer_cfg.amp_dtype == torch.bfloat16, "amp dtype is not bf16"),
                 (trainer_cfg.gradient_accumulation_steps == 1, "gradient accumulation"),
                 (not trainer_cfg.clip_grad_norm, "gradient clipping"),
-                (not trainer_cfg.initial_k or trainer_cfg.initial_k <= 64, "k schedule starting above 64"),
+                (not trainer_cfg.initial_k or trainer_cfg.initial_k <= (64 if cfg.act_fn == "topk" else 512), "k schedule starting above the list width"),
             ]
         for ok, why in checks:
             if not ok:
@@ -119,6 +129,8 @@ class FusedCLTStep:
         gate_all = self.norm_sq.sqrt().view(L, F) if self.use_gate else None
         if xt is None:
             xt = x.transpose(0, 1).contiguous()  # one copy instead of one per layer
+        if self.joint:
+            return self._encode_joint(xt, k, gate_all)
         idxs, acts = [], []
         if self.tp == 1:
             for layer in range(L):
@@ -155,6 +167,47 @@ class FusedCLTStep:
         offset = (torch.arange(L, device=x.device, dtype=idx.dtype) * F).view(1, L, 1)
         idx = torch.where(idx >= 0, idx + offset, idx).view(B, L * k)
         return idx, torch.stack(acts, dim=1).view(B, L * k)
+
+    def _encode_joint(self, xt: torch.Tensor, k: int, gate_all: torch.Tensor | None) -> tuple[torch.Tensor, torch.Tensor]:
+        """``layertopk``: the k largest gated pre-activations of a token over ALL (layer, feature) pairs (models/clt.py
+        :298-304 of the reference project). Any of them is among the k largest of its own layer, so every layer contributes
+        its own top-k list (GEMM with the fused epilogue up to k = 64, pre-activations + radix row top-k above) and the k
+        best of the ``L k`` candidates are kept; feature shards then exchange their lists as the SAE step does."""
+        L, F, B = self.L, self.F, xt.shape[1]
+        kk = min(k, F)
+        idxs, acts, gated = [], [], []
+        for layer in range(L):
+            gate = gate_all[layer] if gate_all is not None else None
+            i, a = K.encoder_topk(xt[layer], self.WE_bf16[layer], self.bE[layer], gate, kk)
+            idxs.append(torch.where(i >= 0, i + layer * F, i))
+            acts.append(a)
+            gated.append(a * gate[i.clamp_min(0).long()] if gate is not None else a)
+        idx, act, g = torch.cat(idxs, dim=1), torch.cat(acts, dim=1), torch.cat(gated, dim=1)  # [B, L kk]
+        g = torch.where(idx >= 0, g, torch.full_like(g, float("-inf")))
+        top_g, pos = g.topk(min(k, g.shape[1]), dim=1)
+        idx, act = torch.gather(idx, 1, pos), torch.gather(act, 1, pos)
+        keep = (top_g > 0) & (idx >= 0)  # only positive gated pre-activations fire
+        idx, act, top_g = torch.where(keep, idx, torch.full_like(idx, -1)), torch.where(keep, act, torch.zeros_like(act)), top_g.clamp_min(0)
+        if idx.shape[1] < k:  # fewer candidates than k: pad the lists
+            pad = k - idx.shape[1]
+            idx = torch.nn.functional.pad(idx, (0, pad), value=-1)
+            act, top_g = torch.nn.functional.pad(act, (0, pad)), torch.nn.functional.pad(top_g, (0, pad))
+        if self.tp == 1:
+            return idx.contiguous(), act.contiguous()
+        # feature shards: every shard's k best (gated values and local indices) to all, the k best of tp k kept, own slots only
+        all_g = torch.empty(self.tp * B, k, dtype=torch.float32, device=idx.device)
+        all_i = torch.empty(self.tp * B, k, dtype=torch.int32, device=idx.device)
+        dist.all_gather_into_tensor(all_g, top_g.float().contiguous(), group=self.tp_group)
+        dist.all_gather_into_tensor(all_i, idx.to(torch.int32).contiguous(), group=self.tp_group)
+        all_g = all_g.view(self.tp, B, k).permute(1, 0, 2).reshape(B, self.tp * k)
+        all_i = all_i.view(self.tp, B, k).permute(1, 0, 2).reshape(B, self.tp * k)
+        all_g = torch.where(all_i >= 0, all_g, torch.full_like(all_g, float("-inf")))
+        _, pos = all_g.topk(k, dim=1)
+        mine = (pos >= self.tp_rank * k) & (pos < (self.tp_rank + 1) * k) & (torch.gather(all_g, 1, pos) > 0)
+        chosen = torch.zeros(B, self.tp * k + 1, dtype=torch.bool, device=idx.device)
+        chosen.scatter_(1, torch.where(mine, pos, torch.full_like(pos, self.tp * k)), True)
+        own = chosen[:, self.tp_rank * k : (self.tp_rank + 1) * k]
+        return torch.where(own, idx, torch.full_like(idx, -1)).contiguous(), torch.where(own, act, torch.zeros_like(act)).contiguous()
 
     def _decode(self, idx: torch.Tensor, act: torch.Tensor) -> torch.Tensor:
         """Reconstruction ``[L, B, d]`` fp32 (summed over feature shards, decoder biases added)."""

@@ -163,3 +163,94 @@ def test_fused_clt_step_with_feature_shards_and_replicas_on_four_ranks_matches_o
         assert close(DimMap({"model": 1}).gather(sharded.W_D[t].data, mesh), single.W_D[t].data), t
     assert close(DimMap({"model": 2}).gather(sharded.W_E.data, mesh), single.W_E.data)
     dist.barrier()
+
+
+def _layertopk_model(k=12, gate=True):
+    m = _model("cpu", 3, 64, 256, k, gate)
+    m.cfg.act_fn = "layertopk"
+    m.activation_function = m.activation_function_factory(m.device_mesh)
+    return m
+
+
+@pytest.mark.parametrize("gate", [True, False])
+def test_fused_clt_step_with_layertopk_matches_autograd(gate, monkeypatch):
+    """k codes per token over all layers together (not k per layer): selection, losses and parameters against the model."""
+    L, d, F, k, B, lr, steps = 3, 64, 256, 12, 96, 1e-3, 4
+    ref = _layertopk_model(k, gate)
+    start = {n: p.detach().clone() for n, p in ref.named_parameters()}
+    fused_model = copy.deepcopy(ref)
+    monkeypatch.delenv("LMSAE_FUSED_LAYERTOPK", raising=False)
+    assert not FusedCLTStep.supports(fused_model)[0]  # on request only, until it has run on a GPU
+    monkeypatch.setenv("LMSAE_FUSED_LAYERTOPK", "1")
+    assert FusedCLTStep.supports(fused_model)[0]
+    engine = FusedCLTStep(fused_model)
+    g = torch.Generator().manual_seed(1)
+    basis = torch.randn(6, d, generator=g)
+    opt = torch.optim.Adam(ref.parameters(), lr=lr)
+    tokens = torch.zeros(B, dtype=torch.long)
+    for step in range(steps):
+        z = torch.randn(B, 6, generator=g)
+        x = torch.stack([z @ basis * (1 + 0.1 * l) + 0.2 * torch.randn(B, d, generator=g) for l in range(L)], dim=1).to(torch.bfloat16)
+        y = torch.stack([(z @ basis).roll(l + 1, dims=-1) + 0.2 * torch.randn(B, d, generator=g) for l in range(L)], dim=0).to(torch.bfloat16)
+        batch = {h: x[:, l].float() for l, h in enumerate(ref.cfg.hook_points_in)} | {h: y[l].float() for l, h in enumerate(ref.cfg.hook_points_out)}
+        batch["tokens"] = tokens
+        opt.zero_grad()
+        out = ref.compute_loss(batch, return_aux_data=True)
+        if step == 0:  # the two models are still the same: the same codes, k per token in all, spread unevenly over the layers
+            idx, act = engine.encode(x, k)
+            assert idx.shape == (B, k)
+            dense = torch.zeros(B, L * F)
+            dense.scatter_(1, idx.clamp_min(0).long(), torch.where(idx >= 0, act, torch.zeros_like(act)))
+            want = out["feature_acts"].detach().reshape(B, L * F)
+            both = (dense != 0) & (want != 0)
+            # (the engine's weights are rounded to bf16: a near-tie at the k-th place may fall the other way)
+            assert int(((dense != 0) != (want != 0)).sum()) <= 0.02 * B * k
+            assert torch.allclose(dense[both], want[both], atol=5e-2, rtol=2e-2)
+            assert int((want != 0).sum(-1).max()) <= k and len(set((want.view(B, L, F) != 0).sum(-1).reshape(-1).tolist())) > 2
+        out["loss"].backward()
+        opt.step()
+        got = engine.step(x, y, k, lr)
+        assert torch.allclose(out["loss"].detach(), got, rtol=2e-3), (out["loss"], got)
+    for name, p in ref.named_parameters():
+        a, b = p.detach().float(), dict(fused_model.named_parameters())[name].detach().float()
+        moved = (a - start[name].float()).abs().mean()
+        assert float((a - b).abs().mean()) < 0.05 * float(moved) + 1e-7, name
+
+
+@distributed_test(nproc_per_node=2, backend="gloo")
+def test_fused_clt_step_with_layertopk_and_feature_shards_matches_one_process():
+    import os
+
+    import torch.distributed as dist
+
+    from language_model_saes_b200.parallel.mesh import DimMap, build_mesh
+
+    os.environ["LMSAE_FUSED_LAYERTOPK"] = "1"
+    L, d, F, k, B, lr, steps = 3, 64, 256, 12, 64, 1e-3, 3
+    full = _layertopk_model(k)
+    mesh = build_mesh("cpu", (1, 2), ("data", "model"))
+    single = copy.deepcopy(full)
+    sharded = CrossLayerTranscoder(full.cfg.model_copy(), mesh)
+    sharded.load_full_state_dict(full.full_state_dict())
+    e1, e2 = FusedCLTStep(single), FusedCLTStep(sharded)
+    assert e2.joint and e2.tp == 2
+    g = torch.Generator().manual_seed(1)
+    for _ in range(steps):
+        x = torch.randn(B, L, d, generator=g).to(torch.bfloat16)
+        y = torch.randn(L, B, d, generator=g).to(torch.bfloat16)
+        i1, _ = e1.encode(x, k)
+        i2, _ = e2.encode(x, k)
+        n_mine = (i2 >= 0).sum().reshape(1)
+        dist.all_reduce(n_mine)
+        assert int(n_mine) == int((i1 >= 0).sum())  # the shards' kept codes add up to the single-process selection
+        a, b = e1.step(x, y, k, lr), e2.step(x, y, k, lr)
+        assert torch.allclose(a, b, rtol=1e-4), (a, b)
+
+    def close(a, b):
+        diff = (a - b).abs()
+        return float(diff.mean()) < 2e-6 and float(diff.max()) <= 2.2 * lr * steps
+
+    for t in range(L):
+        assert close(DimMap({"model": 1}).gather(sharded.W_D[t].data, mesh), single.W_D[t].data), t
+    assert close(DimMap({"model": 2}).gather(sharded.W_E.data, mesh), single.W_E.data)
+    dist.barrier()
