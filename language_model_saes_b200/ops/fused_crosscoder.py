@@ -103,7 +103,6 @@ class FusedCrosscoderStep:
         cfg = cc.cfg
         if type(cc) is SparseAutoEncoder:
             sae_checks = [
-                (cfg.hook_point_in == cfg.hook_point_out, "the SAE does not reconstruct its own input"),
                 (not cfg.use_glu_encoder, "GLU encoder"),
                 (cfg.sparsity_include_decoder_norm, "activations are not gated by the decoder norms"),
                 (cfg.use_decoder_bias, "no decoder bias"),
@@ -174,7 +173,7 @@ class FusedCrosscoderStep:
 
     def step(self, x: torch.Tensor, lr: float, l1_coefficient: float = 0.0, tanh_stretch: float = 4.0,
              row_weight: torch.Tensor | None = None, lp_coefficient: float = 0.0, sparsity_loss_type: str = "tanh",
-             frequency_scale: float = 0.01) -> torch.Tensor:  # fmt: skip
+             frequency_scale: float = 0.01, label: torch.Tensor | None = None) -> torch.Tensor:  # fmt: skip
         """``x``: normalised bf16 activations ``[B, H_l, d]`` of this rank's heads (they are also the labels). Returns the
         mean loss over tokens and this rank's heads (0-d device tensor); ``self.last`` holds its parts.
 
@@ -186,6 +185,9 @@ class FusedCrosscoderStep:
         assert row_weight is None, "token masks are not supported on this path"
         assert not lp_coefficient or self.dp == 1, "the pre-activation penalty is not built for replicas"
         assert sparsity_loss_type in ("tanh", "tanh-quad"), sparsity_loss_type
+        # ``label [B, H_l, d]``: targets that differ from the inputs (a transcoder reads one hook point and reconstructs
+        # another); the inputs still feed the encoder and its gradient
+        assert label is None or label.shape == x.shape
         quad = bool(l1_coefficient) and sparsity_loss_type == "tanh-quad"
         B_l, H_l, d = x.shape  # this replica's tokens
         B = B_l * self.dp  # the step's tokens: every replica brings the same number
@@ -250,7 +252,8 @@ class FusedCrosscoderStep:
             n_h = self.dec_norm[h]
             active = valid & (s_val > t_head[h][safe])
             act = torch.where(active, s_val, torch.zeros_like(s_val))
-            dxhat, dact, _ = K.sparse_decode_loss(idx, act, self.WD_bf16[h], self.bD[h], xh, None, grad_scale, self.loss_sum)
+            target = xh if label is None else label[:, h].contiguous()
+            dxhat, dact, _ = K.sparse_decode_loss(idx, act, self.WD_bf16[h], self.bD[h], target, None, grad_scale, self.loss_sum)
             n_e = n_h[safe]
             self_scale = None
             coef = 0.0

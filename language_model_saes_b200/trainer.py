@@ -1033,11 +1033,14 @@ class Trainer:
                 raw = torch.nn.functional.pad(raw, (0, sae.cfg.d_model - raw.shape[-1]))
             cols.append(raw.to(torch.bfloat16))
         x = torch.stack(cols, dim=1)
+        label = None
+        if f.single and sae.cfg.hook_point_out != sae.cfg.hook_point_in:  # a transcoder: the target is another hook point
+            label = self._normalised_bf16(sae, batch[sae.cfg.hook_point_out], sae.cfg.hook_point_out).unsqueeze(1)
         lr = float(self.cfg.lr) * (self._lr_lambda(self.cur_step) if self._lr_lambda is not None else 1.0)
         l1 = self._l1_coefficient() if self.cfg.sparsity_loss_type in ("tanh", "tanh-quad") else 0.0
         loss = f.step(x, lr, l1_coefficient=l1, tanh_stretch=self.cfg.tanh_stretch_coefficient,
                       lp_coefficient=float(self.cfg.lp_coefficient or 0.0), sparsity_loss_type=self.cfg.sparsity_loss_type or "tanh",
-                      frequency_scale=self.cfg.frequency_scale)
+                      frequency_scale=self.cfg.frequency_scale, label=label)
         if not self.cfg.skip_metrics_calculation and (self.cur_step + 1) % self.cfg.log_frequency == 0:
             last = {k: float(v) for k, v in f.last.items()}
             out = self._family_metrics(sae, batch)

@@ -220,3 +220,47 @@ def test_jumprelu_sae_fit_on_the_fused_step_follows_the_generic_run_and_resumes(
     assert t2.fit(second, data) is None and t2.cur_step == 10 and type(t2.fused).__name__ == "FusedCrosscoderStep"
     for (k, a), b in zip(fused.state_dict().items(), second.state_dict().values()):
         assert torch.allclose(a, b, atol=1e-6), k
+
+
+def jumprelu_transcoder(seed=0):
+    from language_model_saes_b200.models.sae import SAEConfig, SparseAutoEncoder
+
+    torch.manual_seed(seed)
+    cfg = SAEConfig(hook_point_in="pre", hook_point_out="post", d_model=64, expansion_factor=4, act_fn="jumprelu", device="cpu",
+                    dtype=torch.float32, norm_activation="inference")  # fmt: skip
+    m = SparseAutoEncoder(cfg)
+    m.init_parameters(encoder_uniform_bound=0.2, decoder_uniform_bound=0.2, init_log_jumprelu_threshold_value=-1.0)
+    m.set_decoder_to_fixed_norm(1.0, True)
+    m.init_encoder_with_decoder_transpose()
+    return m
+
+
+def transcoder_stream(n, B=64, d=64, seed=5):
+    g = torch.Generator().manual_seed(seed)
+    basis, mix = torch.randn(10, d, generator=g), torch.randn(d, d, generator=g) / d**0.5
+    for _ in range(n):
+        x = torch.randn(B, 10, generator=g) @ basis + 0.05 * torch.randn(B, d, generator=g)
+        x = x * (d**0.5 / x.norm(dim=-1).mean())
+        yield {"pre": x, "post": torch.tanh(x @ mix) * 3, "tokens": torch.ones(B, dtype=torch.long)}
+
+
+def test_jumprelu_transcoder_trains_on_the_fused_step_towards_its_own_target(crosscoder_on_cpu, tmp_path):
+    """A JumpReLU dictionary that reads one hook point and reconstructs another: the fused step takes the other hook point's
+    activations as targets and follows the generic run."""
+    kw = dict(sparsity_loss_type="tanh", l1_coefficient=0.02, jumprelu_lr_factor=0.5)
+    fused = jumprelu_transcoder()
+    tr = trainer(tmp_path / "fused", 64 * 8, **kw)
+    assert tr.fit(fused, transcoder_stream(9)) is None
+    assert type(tr.fused).__name__ == "FusedCrosscoderStep" and tr.fused.single
+    generic = jumprelu_transcoder()
+    tg = trainer(tmp_path / "generic", 64 * 8, use_fused_kernels=False, amp_dtype=torch.float32, **kw)
+    assert tg.fit(generic, transcoder_stream(9)) is None and tg.fused is None
+    start = jumprelu_transcoder()
+    for (name, p), (_, q), (_, p0) in zip(fused.named_parameters(), generic.named_parameters(), start.named_parameters()):
+        moved = float((q - p0).abs().mean())
+        assert float((p - q).abs().mean()) < 0.1 * moved + 1e-7, name
+    # and it is the target that is being learned: the error against "post" fell from where the untrained model stands
+    batch = next(transcoder_stream(1, seed=9))
+    with torch.no_grad():
+        err = [float((m.decode(m.encode(batch["pre"])) - batch["post"]).pow(2).mean()) for m in (start, fused)]
+    assert err[1] < err[0]
