@@ -50,6 +50,12 @@ def TANH_QUAD_ON_FUSED_PATH() -> bool:
     return os.environ.get("LMSAE_FUSED_TANH_QUAD", "0") == "1"
 
 
+def FEATURE_SHARDS_ON_FUSED_PATH() -> bool:
+    """Feature (``model``) shards of this step are verified against one process with ``gloo`` ranks on the CPU and use the
+    kernels and NCCL calls of the other steps' shard paths, but have not run on GPUs: the trainer takes them only on request."""
+    return os.environ.get("LMSAE_FUSED_JUMPRELU_SHARDS", "0") == "1"
+
+
 class FusedCrosscoderStep:
     def __init__(self, cc, betas: tuple[float, float] = (0.9, 0.999), eps: float = 1e-8, list_width: int = 256,
                  jumprelu_lr_factor: float = 1.0):  # fmt: skip
@@ -61,6 +67,8 @@ class FusedCrosscoderStep:
         self.head_group = mesh_group(cc.device_mesh, "head")
         self.dp = mesh_dim_size(cc.device_mesh, "data")
         self.dp_group = mesh_group(cc.device_mesh, "data")
+        self.tp = mesh_dim_size(cc.device_mesh, "model")  # features split over ranks: everything per feature stays local
+        self.tp_group = mesh_group(cc.device_mesh, "model")
         self.window = float(cfg.jumprelu_threshold_window)
         self.cap = -(-list_width // 8) * 8
         self.jumprelu_lr_factor = jumprelu_lr_factor
@@ -120,7 +128,7 @@ class FusedCrosscoderStep:
             (cfg.dtype == torch.float32, "parameters are not fp32"),
             (cfg.d_model % 64 == 0, "d_model is not a multiple of 64"),
             (n_features % 8 == 0, "d_sae is not a multiple of 8"),
-            (mesh_dim_size(cc.device_mesh, "model") == 1, "feature sharding"),
+            (mesh_dim_size(cc.device_mesh, "model") == 1 or FEATURE_SHARDS_ON_FUSED_PATH(), "feature sharding (set LMSAE_FUSED_JUMPRELU_SHARDS=1)"),
             (not any(hp.fwd_hooks or hp.bwd_hooks for hp in cc.hook_points()), "hooks are attached"),
         ]  # fmt: skip
         if trainer_cfg is not None:
@@ -253,7 +261,15 @@ class FusedCrosscoderStep:
             active = valid & (s_val > t_head[h][safe])
             act = torch.where(active, s_val, torch.zeros_like(s_val))
             target = xh if label is None else label[:, h].contiguous()
-            dxhat, dact, _ = K.sparse_decode_loss(idx, act, self.WD_bf16[h], self.bD[h], target, None, grad_scale, self.loss_sum)
+            if self.tp == 1:
+                dxhat, dact, _ = K.sparse_decode_loss(idx, act, self.WD_bf16[h], self.bD[h], target, None, grad_scale, self.loss_sum)
+            else:
+                # feature shards: partial reconstructions summed over the shards, then loss and output gradient (the same on
+                # every shard), then the code gradients of this shard's features
+                xhat = K.sparse_decode(idx, act, self.WD_bf16[h], None, torch.float32)
+                dist.all_reduce(xhat, group=self.tp_group)
+                dxhat = K.mse_loss_grad(xhat, target, self.bD[h], None, grad_scale, self.loss_sum)
+                dact = K.sparse_dact(idx, self.WD_bf16[h], dxhat)
             n_e = n_h[safe]
             self_scale = None
             coef = 0.0
@@ -297,6 +313,14 @@ class FusedCrosscoderStep:
             dist.all_reduce(dS, group=self.head_group)
             dist.all_reduce(dtheta, group=self.head_group)
         n_valid = valid.sum()
+        if self.tp > 1:  # figures that are sums over features: the shards' parts add up (reporting only)
+            part = torch.stack([l_s_sum, n_valid.float(), l_s_quad if quad else l_s_sum.new_zeros(()), l_p_sum if lp is not None else l_s_sum.new_zeros(())])
+            dist.all_reduce(part, group=self.tp_group)
+            l_s_sum, n_valid = part[0], part[1]
+            if quad:
+                l_s_quad = part[2]
+            if lp is not None:
+                l_p_sum = part[3]
         if self.dp > 1:
             # Replicas: what is a sum over tokens (threshold gradient, the penalty's pull on the decoder norms, the losses) is
             # summed over the replicas; the lists, their gradients, the inputs and the output gradients of every replica are

@@ -398,3 +398,87 @@ def test_fused_crosscoder_step_with_heads_and_replicas_on_four_ranks_matches_one
     from language_model_saes_b200.testing import distributed_test
 
     distributed_test(nproc_per_node=4, backend="gloo")(_heads_and_replicas_body)()
+
+
+def _sae_shards_body():
+    """A JumpReLU SAE (tanh-quad penalty and the pre-activation penalty) with its features over two ranks against one process."""
+    import torch.distributed as dist
+
+    from language_model_saes_b200.models.sae import SAEConfig, SparseAutoEncoder
+    from language_model_saes_b200.parallel.mesh import DimMap, build_mesh
+
+    d, F, B, lr = 64, 256, 96, 1e-3
+    torch.manual_seed(0)
+    cfg = SAEConfig(hook_point_in="h", hook_point_out="h", d_model=d, expansion_factor=F / d, act_fn="jumprelu", device="cpu", dtype=torch.float32,
+                    norm_activation="inference")  # fmt: skip
+    full = SparseAutoEncoder(cfg)
+    full.init_parameters(encoder_uniform_bound=0.2, decoder_uniform_bound=0.2, init_log_jumprelu_threshold_value=-1.0)
+    full.set_decoder_to_fixed_norm(1.0, True)
+    full.init_encoder_with_decoder_transpose()
+    single = copy.deepcopy(full)
+    mesh = build_mesh("cpu", (1, 2), ("data", "model"))
+    shard = SparseAutoEncoder(cfg.model_copy(), mesh)
+    shard.load_full_state_dict(full.full_state_dict())
+    e1, e2 = FusedCrosscoderStep(single, list_width=F), FusedCrosscoderStep(shard, list_width=F // 2)
+    assert e2.tp == 2 and e2.F == F // 2 and e2.single
+    g = torch.Generator().manual_seed(3)
+    basis = torch.randn(10, d, generator=g)
+    kw = dict(l1_coefficient=5e-2, sparsity_loss_type="tanh-quad", frequency_scale=0.05)
+    for step in range(3):
+        x = torch.randn(B, 10, generator=g) @ basis + 0.05 * torch.randn(B, d, generator=g)
+        x = (x * (d**0.5 / x.norm(dim=-1).mean())).to(torch.bfloat16).unsqueeze(1)
+        extra = dict(lp_coefficient=2e-3) if step == 2 else {}
+        a, b = e1.step(x, lr, **kw, **extra), e2.step(x, lr, **kw, **extra)
+        assert torch.allclose(a, b, rtol=1e-4), (a, b)
+        for key in ("l_rec", "l_s", "l_p", "l0"):
+            assert torch.allclose(e1.last[key].float(), e2.last[key].float(), rtol=1e-4, atol=1e-7), key
+    maps = shard.dim_maps()
+    for name, p in single.named_parameters():
+        q = dict(shard.named_parameters())[name].data
+        whole = maps[name].gather(q, mesh) if name in maps else q
+        assert torch.allclose(whole, p.data, atol=5e-6), name
+    dist.barrier()
+
+
+def test_jumprelu_sae_with_feature_shards_matches_one_process():
+    from language_model_saes_b200.testing import distributed_test
+
+    distributed_test(nproc_per_node=2, backend="gloo")(_sae_shards_body)()
+
+
+def _heads_and_shards_body():
+    """Crosscoder: heads over two ranks x features over two ranks."""
+    import torch.distributed as dist
+
+    from language_model_saes_b200.parallel.mesh import build_mesh
+
+    H, d, F, B, lr = 4, 64, 256, 96, 1e-3
+    full = _model("cpu", H, d, F)
+    single = copy.deepcopy(full)
+    mesh = build_mesh("cpu", (2, 1, 2), ("head", "data", "model"))
+    sharded = Crosscoder(full.cfg.model_copy(), mesh)
+    sharded.load_full_state_dict(full.full_state_dict())
+    e1, e2 = FusedCrosscoderStep(single, list_width=F), FusedCrosscoderStep(sharded, list_width=F // 2)
+    assert e2.head_size == 2 and e2.tp == 2 and e2.H_l == 2 and e2.F == F // 2
+    hr = mesh.get_local_rank("head")
+    g = torch.Generator().manual_seed(7)
+    kw = dict(l1_coefficient=3e-2, sparsity_loss_type="tanh")
+    for _ in range(3):
+        x = (torch.randn(B, H, d, generator=g) * 1.5).to(torch.bfloat16)
+        e1.step(x, lr, **kw)
+        e2.step(x[:, 2 * hr : 2 * hr + 2].contiguous(), lr, **kw)
+        l_rec = e2.last["l_rec"].clone()
+        dist.all_reduce(l_rec, group=mesh.get_group("head"))
+        assert torch.allclose(l_rec / 2, e1.last["l_rec"], rtol=1e-4)
+        assert torch.allclose(e1.last["l0"].float(), e2.last["l0"].float())
+    maps = sharded.dim_maps()
+    for name, p in single.named_parameters():
+        whole = maps[name].gather(dict(sharded.named_parameters())[name].data, mesh)
+        assert torch.allclose(whole, p.data, atol=5e-6), name
+    dist.barrier()
+
+
+def test_fused_crosscoder_step_with_heads_and_feature_shards_on_four_ranks_matches_one_process():
+    from language_model_saes_b200.testing import distributed_test
+
+    distributed_test(nproc_per_node=4, backend="gloo")(_heads_and_shards_body)()
