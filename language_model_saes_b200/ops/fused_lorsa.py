@@ -19,7 +19,8 @@ them small element-wise kernels that autograd and autocast put around the few pr
 7. updates: ``W_O`` by the sparse gradient + Adam kernel (rows rebuilt from the codes, bf16 shadow and row norms in the
    same pass), the dense projections and biases by the flat Adam kernel.
 
-Restrictions: ``topk`` activation, rotary or no positional embedding (no ``rotary_scale``, no QK layer norm), Adam, fp32
+Restrictions: ``topk`` activation, rotary or no positional embedding (no ``rotary_scale``; the per-head RMS norm of Q and K
+only on request, see ``QK_NORM_ON_FUSED_PATH``), Adam, fp32
 parameters with bf16 compute; heads sharded over ``model``, sequences split over ``data`` (replicas sum their dense
 gradients in one collective and gather codes and output gradients for the sparse update of ``W_O``).
 """
@@ -70,6 +71,12 @@ def rotate_pair(a: torch.Tensor, b: torch.Tensor, cos: torch.Tensor, sin: torch.
     return oa, ob
 
 
+def QK_NORM_ON_FUSED_PATH() -> bool:
+    """The per-head RMS norm of Q and K on the fused step is verified against autograd on the CPU (it is a second small
+    autograd node of torch statements in front of the rotation), but has not run on a GPU: taken only on request."""
+    return "1" in (os.environ.get("LMSAE_FUSED_LORSA_QK_NORM", "0"), os.environ.get("LMSAE_FUSED_CPU_VERIFIED", "0"))
+
+
 class FusedLorsaStep:
     def __init__(self, lorsa, betas: tuple[float, float] = (0.9, 0.999), eps: float = 1e-8, attention: str | None = None):
         """``attention``: ``"tensor_core"`` (this package's tcgen05 forward, dQ and dK/dV kernels, where the shape allows:
@@ -95,6 +102,9 @@ class FusedLorsaStep:
                        "b_Q": lorsa.b_Q.data, "b_K": lorsa.b_K.data, "b_V": lorsa.b_V.data}  # fmt: skip
         if cfg.use_decoder_bias:
             self.params["b_D"] = lorsa.b_D.data
+        self.qk_norm = bool(cfg.use_post_qk_ln)
+        if self.qk_norm:  # learned scales of the per-head RMS norms of Q and K
+            self.params["ln_q.w"], self.params["ln_k.w"] = lorsa.ln_q.w.data, lorsa.ln_k.w.data
         assert all(p.dtype == torch.float32 and p.is_contiguous() for p in self.params.values())
         dev = lorsa.W_V.device
         self.state = {n: (torch.zeros_like(p), torch.zeros_like(p)) for n, p in self.params.items()}
@@ -119,7 +129,8 @@ class FusedLorsaStep:
             (lorsa.W_V.is_cuda or trainer_cfg is None, "not on a CUDA device"),
             (cfg.dtype == torch.float32, "parameters are not fp32"),
             (cfg.positional_embedding_type in ("rotary", "none"), "positional embedding"),
-            (cfg.rotary_scale == 1 and not cfg.use_post_qk_ln, "rotary scale / QK layer norm"),
+            (cfg.rotary_scale == 1, "rotary scale"),
+            (not cfg.use_post_qk_ln or QK_NORM_ON_FUSED_PATH(), "QK layer norm (set LMSAE_FUSED_LORSA_QK_NORM=1)"),
             (cfg.d_model % 64 == 0 and cfg.d_qk_head % 8 == 0 and lorsa.W_V.shape[0] % 8 == 0, "d_model / head widths not aligned"),
             (lorsa.W_V.shape[0] % max(lorsa.W_Q.shape[0], 1) == 0 and (lorsa.W_V.shape[0] // max(lorsa.W_Q.shape[0], 1)) % 8 == 0,
              "OV group size not a multiple of 8"),
@@ -161,12 +172,22 @@ class FusedLorsaStep:
     # ---- forward pieces -----------------------------------------------------------------------------
     def _project(self, X: torch.Tensor, b: int, s: int):
         """``X [tokens, d]`` bf16 -> rotated ``q, k [b, s, h, dqk]`` and ``v [b, s, h, group]`` (bf16 on CUDA)."""
+        q, k, v = self._project_linear(X, b, s)
+        if self.qk_norm:
+            with torch.no_grad():
+                q, k = self.m.ln_q(q), self.m.ln_k(k)
+        return (*self._rotated(q, k), v)
+
+    def _project_linear(self, X: torch.Tensor, b: int, s: int):
         q = K.encoder_hidden(X, self.WQ16, self.params["b_Q"].reshape(-1)).view(b, s, self.h, self.dqk)
         k = K.encoder_hidden(X, self.WK16, self.params["b_K"].reshape(-1)).view(b, s, self.h, self.dqk)
         v = K.encoder_hidden(X, self.WV16, self.params["b_V"]).view(b, s, self.h, self.group_size)
+        return q, k, v
+
+    def _rotated(self, q: torch.Tensor, k: torch.Tensor):
         if self.rotary:
             q, k = rotate_pair(q, k, self.m.rotary_cos, self.m.rotary_sin, self.m.cfg.rotary_adjacent_pairs)
-        return q, k, v
+        return q, k
 
     def _attention(self, q, k, v):
         """Library attention on ``[b, h, s, *]`` views; fp32 on CPU (the plain statement), bf16 on CUDA, where the backend is
@@ -208,7 +229,18 @@ class FusedLorsaStep:
         X = x.reshape(T_l, d).contiguous()
         Y = label.reshape(T_l, d).contiguous()
         grad_scale = 2.0 / T
-        q, k, v = self._project(X, b, s)
+        norm_node = None
+        if self.qk_norm:
+            # a second small autograd node in front of the rotation: the per-head RMS norms of Q and K with their scales
+            q0, k0, v = self._project_linear(X, b, s)
+            q0, k0 = q0.detach().requires_grad_(True), k0.detach().requires_grad_(True)
+            wq, wk = self.m.ln_q.w, self.m.ln_k.w
+            with torch.enable_grad():
+                qn, kn = self.m.ln_q(q0), self.m.ln_k(k0)
+            norm_node = (qn, kn, q0, k0, wq, wk)
+            q, k = self._rotated(qn.detach(), kn.detach())
+        else:
+            q, k, v = self._project(X, b, s)
         # the attention alone keeps an autograd node (its backward is the library's); everything around it is explicit
         ql, kl, vl = (t.detach().requires_grad_(True) for t in (q, k, v))
         with torch.enable_grad():
@@ -232,6 +264,12 @@ class FusedLorsaStep:
         dq, dk, dv = torch.autograd.grad(out, (ql, kl, vl), dz.to(out.dtype))
         if self.rotary:
             dq, dk = rotate_pair(dq, dk, self.m.rotary_cos, self.m.rotary_sin, self.m.cfg.rotary_adjacent_pairs, inverse=True)
+        norm_grads = {}
+        if norm_node is not None:
+            qn, kn, q0, k0, wq, wk = norm_node
+            dq, gwq = torch.autograd.grad(qn, (q0, wq), dq.to(qn.dtype))
+            dk, gwk = torch.autograd.grad(kn, (k0, wk), dk.to(kn.dtype))
+            norm_grads = {"ln_q.w": gwq.float(), "ln_k.w": gwk.float()}
         low = torch.bfloat16 if x.is_cuda else torch.float32
         dQ = dq.reshape(T_l, self.h * self.dqk).to(low)
         dK = dk.reshape(T_l, self.h * self.dqk).to(low)
@@ -248,6 +286,7 @@ class FusedLorsaStep:
         }
         if bD is not None:
             grads["b_D"] = K.colsum_bf16(dxhat)
+        grads.update(norm_grads)
         if self.dp > 1:
             # Replicas: the dense gradients (some 50 MB at 8192 heads) are summed in one collective on a flat buffer; for W_O the
             # codes and the output gradient of every replica (a few MB) are gathered and each replica rebuilds the same rows, so

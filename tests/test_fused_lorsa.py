@@ -91,14 +91,23 @@ def test_rotation_of_two_tensors_matches_the_plain_statement(dev, adjacent, widt
 
 @pytest.mark.parametrize("dev", DEVICES)
 @pytest.mark.parametrize("variant", ["rotary", "half_split_partial_rotary", "no_positions_no_gate", "rotary_wide_heads",
-                                     "rotary_wide_heads_library"])  # fmt: skip
-def test_fused_lorsa_step_matches_autograd(dev, variant):
+                                     "rotary_wide_heads_library", "qk_norm"])  # fmt: skip
+def test_fused_lorsa_step_matches_autograd(dev, variant, monkeypatch):
+    if variant == "qk_norm":
+        if dev == "cuda":
+            pytest.skip("this variant is verified on the CPU only so far")
+        monkeypatch.setenv("LMSAE_FUSED_LORSA_QK_NORM", "1")
     kw = {"rotary": {}, "half_split_partial_rotary": dict(rotary_adjacent_pairs=False, rotary_dim=8),
+          "qk_norm": dict(use_post_qk_ln=True, normalization_type="RMS"),
           "no_positions_no_gate": dict(positional_embedding_type="none", sparsity_include_decoder_norm=False),
           # head widths that the tensor-core attention kernels take (on a GPU the step then runs them)
           "rotary_wide_heads": dict(dqk=64, n_ov=128), "rotary_wide_heads_library": dict(dqk=64, n_ov=128)}[variant]  # fmt: skip
     d, b, s, lr, steps = 64, 3, 32, 1e-3, 4
     ref = _model(dev, d=d, n_ctx=s, **kw)
+    if variant == "qk_norm":
+        with torch.no_grad():  # scales that are not all one
+            ref.ln_q.w.mul_(1 + 0.2 * torch.randn_like(ref.ln_q.w))
+            ref.ln_k.w.mul_(1 + 0.2 * torch.randn_like(ref.ln_k.w))
     fused_model = copy.deepcopy(ref)
     ok, why = FusedLorsaStep.supports(fused_model)
     assert ok, why
