@@ -54,6 +54,10 @@ class FusedCLTStep:
         self.L, self.F, self.d = cfg.n_layers, clt.d_sae_local, cfg.d_model
         self.use_gate = cfg.sparsity_include_decoder_norm
         self.joint = cfg.act_fn == "layertopk"  # k codes per token over all layers together, instead of k per layer
+        self.batch_level = cfg.act_fn in ("batchtopk", "batchlayertopk")  # k x batch codes per layer / over all layers
+        self.batch_all_layers = cfg.act_fn == "batchlayertopk"
+        self.batch_list_factor = int(os.environ.get("LMSAE_BATCH_LIST_FACTOR", "8"))
+        self.list_overflow = torch.zeros(1, dtype=torch.int64, device=clt.b_E.device)
         L, F, d = self.L, self.F, self.d
         self.WE = clt.W_E.data.transpose(1, 2)  # [L, F, d] contiguous view of the parameter's storage
         assert self.WE.is_contiguous() and self.WE.dtype == torch.float32
@@ -85,9 +89,13 @@ class FusedCLTStep:
         if type(clt) is not CrossLayerTranscoder:
             return False, "model is not a CrossLayerTranscoder"
         checks = [
-            (cfg.act_fn == "topk" or (cfg.act_fn == "layertopk" and LAYERTOPK_ON_FUSED_PATH()),
-             "activation is not the per-layer topk (layertopk: set LMSAE_FUSED_LAYERTOPK=1)"),
-            (cfg.top_k <= (64 if cfg.act_fn == "topk" else 512), "k above the list width of the step"),
+            (cfg.act_fn == "topk" or (cfg.act_fn in ("layertopk", "batchtopk", "batchlayertopk") and LAYERTOPK_ON_FUSED_PATH()),
+             "activation is not the per-layer topk (layertopk / batchtopk / batchlayertopk: set LMSAE_FUSED_LAYERTOPK=1)"),
+            (cfg.top_k <= {"topk": 64, "layertopk": 512}.get(cfg.act_fn, 96), "k above the list width of the step"),
+            # batch-level selections: lists of 8 k codes per layer (or in all); the decode kernel stages a row's codes on chip
+            (cfg.act_fn not in ("batchtopk", "batchlayertopk")
+             or (cfg.n_layers if cfg.act_fn == "batchtopk" else 1) * (-(-int(os.environ.get("LMSAE_BATCH_LIST_FACTOR", "8")) * cfg.top_k // 8) * 8) <= 6144,
+             "code lists of a token longer than 6144 entries"),
             (clt.b_E.is_cuda or trainer_cfg is None, "not on a CUDA device"),
             (cfg.dtype == torch.float32, "parameters are not fp32"),
             (cfg.d_model % 8 == 0 and clt.d_sae_local % 8 == 0, "d_model / local d_sae not multiples of 8"),
@@ -100,7 +108,8 @@ class FusedCLTStep:
                 (trainer_cfg.amp_dtype == torch.bfloat16, "amp dtype is not bf16"),
                 (trainer_cfg.gradient_accumulation_steps == 1, "gradient accumulation"),
                 (not trainer_cfg.clip_grad_norm, "gradient clipping"),
-                (not trainer_cfg.initial_k or trainer_cfg.initial_k <= (64 if cfg.act_fn == "topk" else 512), "k schedule starting above the list width"),
+                (not trainer_cfg.initial_k or trainer_cfg.initial_k <= {"topk": 64, "layertopk": 512}.get(cfg.act_fn, 96),
+                 "k schedule starting above the list width"),
             ]
         for ok, why in checks:
             if not ok:
@@ -131,6 +140,8 @@ class FusedCLTStep:
             xt = x.transpose(0, 1).contiguous()  # one copy instead of one per layer
         if self.joint:
             return self._encode_joint(xt, k, gate_all)
+        if self.batch_level:
+            return self._encode_batch_level(xt, k, gate_all)
         idxs, acts = [], []
         if self.tp == 1:
             for layer in range(L):
@@ -208,6 +219,34 @@ class FusedCLTStep:
         chosen.scatter_(1, torch.where(mine, pos, torch.full_like(pos, self.tp * k)), True)
         own = chosen[:, self.tp_rank * k : (self.tp_rank + 1) * k]
         return torch.where(own, idx, torch.full_like(idx, -1)).contiguous(), torch.where(own, act, torch.zeros_like(act)).contiguous()
+
+    def _encode_batch_level(self, xt: torch.Tensor, k: int, gate_all: torch.Tensor | None) -> tuple[torch.Tensor, torch.Tensor]:
+        """``batchtopk``: per layer the ``k x batch`` largest gated pre-activations of the whole batch (over all feature
+        shards); ``batchlayertopk``: the ``k x batch`` largest over all layers together (models/clt.py:330-368 of the
+        reference project). As in the SAE step: gated pre-activations in bf16, a radix select of the threshold (shards add
+        their histograms), one compaction pass into lists of fixed width (``LMSAE_BATCH_LIST_FACTOR`` x k per layer;
+        rows with more codes are counted in ``list_overflow``), nothing read back by the host."""
+        from . import select_kernels as S
+
+        L, F, B = self.L, self.F, xt.shape[1]
+        tp_group = self.tp_group if self.tp > 1 else None
+        G = [K.encoder_hidden(xt[layer], self.WE_bf16[layer], self.bE[layer], gate=gate_all[layer] if gate_all is not None else None)
+             for layer in range(L)]  # fmt: skip
+        if self.batch_all_layers:  # one threshold for everything
+            thr, ties = S.positive_thresholds(torch.stack(G, dim=1).view(1, 1, -1), k * B, tp_group, return_remaining=True)
+            cap = -(-self.batch_list_factor * k // 8) * 8
+            flat = torch.cat(G, dim=1)  # [B, L F]: column = layer * F + feature, the codes' index space
+            div = gate_all.reshape(-1) if gate_all is not None else None
+            return S.threshold_rows_to_sparse(flat, thr, div, n_ties=ties, tie_group=tp_group, cap=cap, overflow=self.list_overflow)
+        cap = -(-self.batch_list_factor * k // 8) * 8
+        idxs, acts = [], []
+        for layer in range(L):
+            thr, ties = S.positive_thresholds(G[layer].view(1, 1, -1), k * B, tp_group, return_remaining=True)
+            gate = gate_all[layer] if gate_all is not None else None
+            i, a = S.threshold_rows_to_sparse(G[layer], thr, gate, n_ties=ties, tie_group=tp_group, cap=cap, overflow=self.list_overflow)
+            idxs.append(torch.where(i >= 0, i + layer * F, i))
+            acts.append(a)
+        return torch.cat(idxs, dim=1).contiguous(), torch.cat(acts, dim=1).contiguous()
 
     def _decode(self, idx: torch.Tensor, act: torch.Tensor) -> torch.Tensor:
         """Reconstruction ``[L, B, d]`` fp32 (summed over feature shards, decoder biases added)."""
