@@ -171,13 +171,24 @@ function showConnections(c, graph, n) {
   const con = graph.connections(n.node_id), f = n.feature && typeof n.feature === "object" ? n.feature : null;
   let h = `<h2>${esc(n.feature_type)} <span class="muted">${layerName(n.layer, graph.maxLayer)} · position ${n.ctx_idx}</span></h2><p>${esc(nodeLabel(n))}</p>`;
   if (n.activation !== undefined && n.activation !== null) h += `<p class="muted">activation ${fmt(n.activation, 4)}</p>`;
-  if (f) h += featureSummary(f, { dictionary: n.sae_name, samples: 2 });
+  if (f) h += featureSummary(f, { dictionary: n.sae_name, samples: 2 }) +
+    `<div class="row"><input id="nodeInterp" style="flex:1" placeholder="interpretation of this feature" value="${esc(interpretationOf(f))}"><button id="nodeInterpSave">Save</button><span id="nodeInterpMsg" class="ok"></span></div>`;
   h += `<div class="row"><button id="pinNode">${graph.pinned.has(n.node_id) ? "unpin" : "pin"}</button>` +
     (n.qk_tracing_results ? `<button id="qkNode">QK tracing</button>` : "") + "</div>";
   h += `<h3>Inputs <span class="muted">${con.inputs.length}</span></h3>${con.inputs.length ? connectionRows(graph, con.inputs, "source") : "<p class='muted'>none kept at these thresholds</p>"}`;
   h += `<h3>Outputs <span class="muted">${con.outputs.length}</span></h3>${con.outputs.length ? connectionRows(graph, con.outputs, "target") : "<p class='muted'>none kept at these thresholds</p>"}`;
   box.innerHTML = h;
   $("pinNode").onclick = () => { graph.togglePin(n.node_id); showConnections(c, graph, n); };
+  if ($("nodeInterpSave")) $("nodeInterpSave").onclick = async () => {
+    // the label of every node of this feature changes with it: the record is shared by reference between the nodes of one fetch
+    try {
+      const text = $("nodeInterp").value;
+      await api(`/dictionaries/${enc(n.sae_name)}/features/${f.feature_index}/interpretation`, jsonOpts("PUT", { text }));
+      graph.g.nodes.forEach(m => { if (m.sae_name === n.sae_name && m.feature && typeof m.feature === "object" && m.feature.feature_index === f.feature_index) m.feature.interpretation = { text }; });
+      graph.draw();
+      $("nodeInterpMsg").textContent = "saved";
+    } catch (e) { $("nodeInterpMsg").textContent = e.message; }
+  };
   if ($("qkNode")) $("qkNode").onclick = () => { location.hash = `#/circuit/${c.circuit_id}/qk/${enc(n.node_id)}`; };
   box.querySelectorAll(".goNode").forEach(a => a.onclick = ev => { ev.preventDefault(); graph.select(a.dataset.id); });
 }

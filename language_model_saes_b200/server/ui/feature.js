@@ -194,6 +194,13 @@ function editBookmark(dict, index, done) {
   };
 }
 
+// left / right arrow keys step through the features of the open card (not while typing in a field)
+document.addEventListener("keydown", ev => {
+  if (ev.target && ["INPUT", "TEXTAREA", "SELECT"].includes(ev.target.tagName)) return;
+  const b = ev.key === "ArrowLeft" ? $("prevF") : ev.key === "ArrowRight" ? $("nextF") : null;
+  if (b && !b.disabled) b.click();
+});
+
 // a feature in a few lines (lists, the connections panel of a circuit): index, interpretation, one sample
 function featureSummary(f, opts = {}) {
   if (!f) return "";
