@@ -30,9 +30,9 @@ def topk_to_jumprelu_conversion(sae: SparseDictionary, activations_stream: Itera
     batch = sae.normalize_activations(next(stream))
     x, enc_kwargs, _ = sae.prepare_input(batch)
     _, hidden_pre = sae.encode(x, **enc_kwargs, return_hidden_pre=True)
+    # (with ``sparsity_include_decoder_norm`` the encoder already returns the pre-activations times the decoder norms: the
+    # values the selection ran on)
     score = hidden_pre.clamp(min=0.0).float()
-    if sae.cfg.sparsity_include_decoder_norm:
-        score = score * sae.decoder_norm_per_feature().float()
     n_tokens = score[..., 0, 0].numel()
     k = sae.cfg.top_k * n_tokens
     # one row holding every (token, layer, local feature) score; the feature shard is the "last dim" of the selection
