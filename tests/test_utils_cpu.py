@@ -142,3 +142,110 @@ def test_topk_cross_layer_transcoder_becomes_a_jumprelu_one_with_the_same_codes(
     assert float(agree) > 0.9999
     both = (after != 0) & (before != 0)
     assert torch.allclose(after[both], before[both], rtol=1e-5, atol=1e-6)
+
+
+def test_misc_helpers():
+    from language_model_saes_b200.utils import misc
+
+    for name, dt in (("float32", torch.float32), ("torch.bfloat16", torch.bfloat16), ("fp16", torch.float16), ("torch.float", torch.float32)):
+        if name in misc.str_dtype_map:
+            assert misc.convert_str_to_torch_dtype(name) is dt
+    assert misc.convert_str_to_torch_dtype(misc.convert_torch_dtype_to_str(torch.bfloat16)) is torch.bfloat16
+    with pytest.raises(ValueError, match="Unsupported data type"):
+        misc.convert_str_to_torch_dtype("float7")
+    with pytest.raises(ValueError, match="Unsupported data type"):
+        misc.convert_torch_dtype_to_str(torch.complex64)
+    t = torch.arange(12).view(3, 4)
+    assert misc.tensor_id(t) == misc.tensor_id(t.view(3, 4)) and misc.tensor_id(t) != misc.tensor_id(t.t()) != misc.tensor_id(t[1:])
+    assert misc.pad_and_truncate_tokens(torch.tensor([[1, 2, 3]]), 5, pad_token_id=9).tolist() == [[1, 2, 3, 9, 9]]
+    assert misc.pad_and_truncate_tokens(torch.tensor([[1, 2, 3]]), 2).tolist() == [[1, 2]]
+    assert misc.get_slice_length(slice(2, None, 3), 10) == 3 and misc.get_slice_length(slice(-2, None), 10) == 2
+    assert misc.is_master()
+
+    class Tok:
+        def __call__(self, text, return_tensors=None):
+            return types.SimpleNamespace(input_ids=torch.tensor([[len(w) for w in text.split()]]))
+
+    assert misc.ensure_tokenized("ab cde f", Tok()).tolist() == [2, 3, 1]
+    assert misc.ensure_tokenized(torch.tensor([[4, 5]]), None).tolist() == [4, 5]
+    assert misc.ensure_tokenized([7, 8, 9], None).dtype == torch.long
+    with pytest.raises(TypeError):
+        misc.ensure_tokenized(3.5, None)
+
+
+def test_activation_norm_is_the_mean_row_norm_of_the_first_batches():
+    from language_model_saes_b200.utils.misc import calculate_activation_norm
+
+    g = torch.Generator().manual_seed(0)
+    batches = [{"a": torch.randn(10, 8, generator=g) * (i + 1), "b": torch.randn(10, 8, generator=g)} for i in range(5)]
+    got = calculate_activation_norm(iter(batches), ["a", "b"], batch_num=3)
+    want = torch.cat([b["a"] for b in batches[:3]]).norm(dim=-1).mean()
+    assert got["a"] == pytest.approx(float(want), rel=1e-5) and set(got) == {"a", "b"}
+    with pytest.warns(UserWarning, match="ended before"):
+        short = calculate_activation_norm(iter(batches[:2]), ["b"], batch_num=8)
+    assert short["b"] == pytest.approx(float(torch.cat([b["b"] for b in batches[:2]]).norm(dim=-1).mean()), rel=1e-5)
+
+
+def test_resource_loaders_shard_datasets_and_pick_backends(tiny_lm_workspace):
+    from language_model_saes_b200 import resource_loaders as R
+    from language_model_saes_b200.config import DatasetConfig
+
+    cfg = DatasetConfig(dataset_name_or_path=str(tiny_lm_workspace / "data"), is_dataset_on_disk=True)
+    ds, meta = R.load_dataset(cfg)
+    assert meta is None and len(ds) == 64
+    part, meta = R.load_dataset(cfg, n_shards=4, start_shard=1)
+    assert meta == {"shard_idx": 1, "n_shards": 4} and len(part) == 16 and part[0]["text"] == ds[16]["text"]  # contiguous shards
+    assert len(R.load_dataset_shard(cfg, 3, 4)) == 16
+    assert R.infer_model_backend("Qwen/Qwen2.5-VL-7B-Instruct") == "qwen_vl" and R.infer_model_backend("EleutherAI/pythia-160m") == "hooked"
+    from conftest import tiny_lm_config
+
+    lm = R.load_model(tiny_lm_config(tiny_lm_workspace))
+    assert type(lm).__name__ == "HookedLanguageModel"
+    bad = tiny_lm_config(tiny_lm_workspace).model_copy(update={"backend": "nope"})
+    with pytest.raises(ValueError, match="unknown backend"):
+        R.load_model(bad)
+
+
+def test_conversion_runner_saves_a_jumprelu_cross_layer_transcoder(tmp_path):
+    from safetensors.torch import save_file
+
+    from language_model_saes_b200 import ActivationFactoryActivationsSource, ActivationFactoryConfig, ActivationFactoryTarget
+    from language_model_saes_b200.models.clt import CLTConfig, CrossLayerTranscoder
+    from language_model_saes_b200.models.sparse_dictionary import SparseDictionary
+    from language_model_saes_b200.runners import PretrainedSAE
+    from language_model_saes_b200.runners.topk_to_jumprelu_conversion import ConvertTopKToJumpReLUSettings, convert_topk_to_jumprelu
+
+    torch.manual_seed(0)
+    L, d, F, k = 2, 16, 64, 4
+    hooks_in, hooks_out = [f"blocks.{l}.ln2.hook_normalized" for l in range(L)], [f"blocks.{l}.hook_mlp_out" for l in range(L)]
+    cfg = CLTConfig(hook_points_in=hooks_in, hook_points_out=hooks_out, d_model=d, expansion_factor=F / d, act_fn="batchlayertopk", top_k=k,
+                    device="cpu", dtype=torch.float32, norm_activation="inference")  # fmt: skip
+    m = CrossLayerTranscoder(cfg)
+    m.init_parameters()
+    with torch.no_grad():
+        m.W_E.mul_(6.0)
+    src = tmp_path / "topk"
+    src.mkdir()
+    m.save_pretrained(src)
+    m.cfg.save_hyperparameters(src)
+    g = torch.Generator().manual_seed(2)
+    tokens = torch.randint(3, 50, (8, 12), generator=g)
+    for hp in hooks_in + hooks_out:
+        (tmp_path / "cache" / hp).mkdir(parents=True)
+        for c in range(2):
+            save_file({"activation": torch.randn(8, 12, d, generator=g), "tokens": tokens, "mask": torch.ones(8, 12, dtype=torch.bool),
+                       "attention_mask": torch.ones(8, 12, dtype=torch.bool)}, str(tmp_path / "cache" / hp / f"chunk-{c}.safetensors"))  # fmt: skip
+    factory = ActivationFactoryConfig(
+        sources=[ActivationFactoryActivationsSource(name="cache", path=str(tmp_path / "cache"), device="cpu", num_workers=0, prefetch=None)],
+        target=ActivationFactoryTarget.ACTIVATIONS_1D, hook_points=hooks_in + hooks_out, batch_size=64)  # fmt: skip
+    out = tmp_path / "jumprelu"
+    out.mkdir()
+    convert_topk_to_jumprelu(ConvertTopKToJumpReLUSettings(sae=PretrainedSAE(pretrained_name_or_path=str(src), device="cpu", dtype=torch.float32),
+                                                           sae_name="clt-j", sae_series="t", activation_factory=factory, device_type="cpu",
+                                                           exp_result_path=str(out)))  # fmt: skip
+    back = SparseDictionary.from_pretrained(str(out), device="cpu", dtype=torch.float32, fold_activation_scale=False)
+    assert back.cfg.act_fn == "jumprelu" and not back.cfg.sparsity_include_decoder_norm
+    x = torch.randn(64, L, d, generator=g)
+    l0 = float((back.encode(x) != 0).sum()) / 64
+    assert 0.5 * k < l0 < 2.0 * k  # about k codes per token on fresh data from the same distribution
+    assert torch.equal(back.W_E, m.W_E)
