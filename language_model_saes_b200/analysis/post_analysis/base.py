@@ -17,6 +17,7 @@ logger = get_logger("analysis.post_analysis")
 
 
 class PostAnalysisProcessor(ABC):
+    @torch.no_grad()  # records are measurements: nothing here is differentiated, whatever mode the caller is in
     def process(self, sae: SparseDictionary, act_times: torch.Tensor, n_analyzed_tokens: int, max_feature_acts: torch.Tensor,
                 sample_result: dict[str, dict[str, torch.Tensor]], mapper: KeyedDiscreteMapper, device_mesh=None,
                 activation_factory=None, activation_factory_process_kwargs: dict[str, Any] | None = None,
