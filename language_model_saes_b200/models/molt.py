@@ -196,7 +196,11 @@ class MixtureOfLinearTransform(SparseDictionary):
         self.b_E.div_(f_in)
         if self.cfg.use_decoder_bias:
             self.b_D.div_(f_out)
-        s = (f_in / f_out) ** 0.5
+        # The gate shrinks to a / f_in (the bias is divided, the encoder kept) and the transforms now see raw inputs
+        # x = x_n / f_in: keeping sum_c a_c U_c V_c x_n / f_out needs U V scaled by f_in^2 / f_out. (The reference scales by
+        # f_in / f_out, as for a dictionary whose decoder does not read the input, which changes the folded model's
+        # output by the factor 1 / f_in: models/molt.py:446-468 there.)
+        s = (f_in * f_in / f_out) ** 0.5
         for r in self.cfg.available_ranks:
             self.U_matrices[str(r)].data.mul_(s)
             self.V_matrices[str(r)].data.mul_(s)
