@@ -136,6 +136,12 @@ class SparseAutoEncoder(SparseDictionary):
         if self.cfg.use_decoder_bias:
             self.b_D.div_(f_out)
         self.W_D.mul_(f_in / f_out)
+        if isinstance(self.activation_function, JumpReLU):
+            # The pre-activations shrink by f_in (compared on their own) or, gated by the decoder norms (which grow by
+            # f_in / f_out), by f_out: the thresholds follow, or other features would fire after folding. (The reference
+            # leaves them as they are, models/sae.py:242-255 there; its cross-layer transcoder does move them.)
+            shift = math.log(f_out if self.cfg.sparsity_include_decoder_norm else f_in)
+            self.activation_function.log_jumprelu_threshold.data.sub_(shift)
         self.cfg.norm_activation = "inference"
 
     # ---- forward -----------------------------------------------------------------------------
