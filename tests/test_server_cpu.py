@@ -170,3 +170,66 @@ def test_ui_pages_are_served_and_call_existing_routes(server):
     # the pages' data sources answer for the fixtures of this module
     assert http.get("/admin/stats").json()["sae_count"] == len(names)
     assert http.get(f"/dictionaries/{names[0]}/features", params={"start": 0, "end": 2, "sample_length": 1}).status_code == 200
+
+
+def test_management_routes_rename_filter_and_delete(server):
+    """Runs last: it renames and deletes what the other tests read. Feature metrics and their filters, bookmark notes, renaming
+    a dictionary (its features, analyses, bookmarks and sets follow), renaming and deleting a set, grouping circuits."""
+    http, client, names = server
+    # metrics stored on features, and the filters of count / random
+    client.update_feature("tc-L1", 0, {"metric": {"score": 0.9, "depth": 2.0}}, sae_series="ser")
+    client.update_feature("tc-L1", 1, {"metric": {"score": 0.1}}, sae_series="ser")
+    assert http.get("/dictionaries/tc-L1/metrics").json() == {"metrics": ["depth", "score"]}
+    count = lambda f: http.get("/dictionaries/tc-L1/features/count", params={"metric_filters": json.dumps(f)}).json()["count"]  # noqa: E731
+    assert count({"score": {"$gte": 0.5}}) == 1
+    assert count({"score": {"$gte": 0.95}}) == 0
+    assert count({"score": {"$lte": 0.5}}) == 0  # feature 1 passes the filter but never fired
+    hit = http.get("/dictionaries/tc-L1/features/random", params={"metric_filters": json.dumps({"score": {"$gte": 0.5}})})
+    assert _unpack(hit)["feature_index"] == 0
+    miss = http.get("/dictionaries/tc-L1/features/random", params={"metric_filters": json.dumps({"score": {"$gte": 0.95}})})
+    assert miss.status_code == 404
+    # bookmark notes and tags
+    assert http.put("/dictionaries/tc-L1/features/0/bookmark", params={"notes": "n"}).status_code == 404
+    assert http.post("/dictionaries/tc-L1/features/0/bookmark").status_code == 200
+    # the tag list is the JSON body, the notes a query parameter
+    assert http.put("/dictionaries/tc-L1/features/0/bookmark", params={"notes": "look again"}, json=["a", "b"]).status_code == 200
+    mark = http.get("/bookmarks", params={"sae_name": "tc-L1"}).json()["bookmarks"][0]
+    assert mark["notes"] == "look again" and mark["tags"] == ["a", "b"]
+    # sets: create, edit, rename, clash, delete
+    if "all" not in http.get("/sae-sets").json():
+        assert http.post("/sae-sets", json={"name": "all", "sae_names": names}).status_code == 200
+    assert http.post("/sae-sets", json={"name": "mlp", "sae_names": ["tc-L0", "tc-L1"]}).status_code == 200
+    assert [s["name"] for s in http.get("/admin/sae-sets").json()] == ["all", "mlp"]
+    assert http.put("/admin/sae-sets/mlp", json={"new_name": "all"}).status_code == 409
+    assert http.put("/admin/sae-sets/mlp", json={}).json() == {"message": "No updates provided"}
+    assert http.put("/admin/sae-sets/nope", json={"new_name": "x"}).status_code == 404
+    assert http.put("/admin/sae-sets/mlp", json={"new_name": "transcoders", "sae_names": ["tc-L1"]}).status_code == 200
+    sets = {s["name"]: s["sae_names"] for s in http.get("/admin/sae-sets").json()}
+    assert sets["transcoders"] == ["tc-L1"] and "mlp" not in sets
+    # renaming a dictionary carries its records along
+    assert http.put("/admin/saes/tc-L1", json={"new_name": "tc-L0"}).status_code == 409
+    assert http.put("/admin/saes/tc-L1", json={"new_name": "mlp-L1", "model_name": "tiny"}).status_code == 200
+    assert "mlp-L1" in http.get("/dictionaries").json() and "tc-L1" not in http.get("/dictionaries").json()
+    assert _unpack(http.get("/dictionaries/mlp-L1/features/0"))["is_bookmarked"] is True
+    assert http.get("/dictionaries/mlp-L1/analyses").json() == ["default"]
+    sets = {s["name"]: s["sae_names"] for s in http.get("/admin/sae-sets").json()}
+    assert sets["transcoders"] == ["mlp-L1"] and "mlp-L1" in sets["all"] and "tc-L1" not in sets["all"]
+    assert _unpack(http.post("/dictionaries/mlp-L1/features/0/infer", params={"text": "the cat"}))["text"] == "the cat"
+    # deleting it removes its features and analyses
+    assert http.delete("/admin/saes/mlp-L1").status_code == 200
+    assert http.delete("/admin/saes/mlp-L1").status_code == 404
+    assert http.get("/dictionaries/mlp-L1/features/0").status_code == 404
+    assert http.get("/admin/stats").json()["sae_count"] == 3
+    assert http.delete("/admin/sae-sets/transcoders").status_code == 200
+    assert http.delete("/admin/sae-sets/transcoders").status_code == 404
+    # circuits in a group
+    left = [n for n in names if n != "tc-L1"]
+    assert http.put("/admin/sae-sets/all", json={"sae_names": left}).status_code == 200
+    req = {"input": {"input_type": "plain_text", "text": "a cat"}, "name": "c2", "max_feature_nodes": 8, "max_n_logits": 1, "desired_logit_prob": 0.3}
+    ids = [http.post("/circuits", params={"sae_set_name": "all"}, json={**req, "name": f"c{i}"}).json()["circuit_id"] for i in (2, 3)]
+    assert http.post("/admin/circuits/bulk-group", json={"circuit_ids": ids + ["missing"], "group": "batch"}).json() == {"message": "Updated 2 circuits"}
+    rows = http.get("/admin/circuits").json()
+    assert rows["total_count"] == 2 and {c["group"] for c in rows["circuits"]} == {"batch"}
+    assert http.put(f"/admin/circuits/{ids[0]}", json={"name": "renamed"}).status_code == 200
+    assert http.put("/admin/circuits/missing", json={"name": "x"}).status_code == 404
+    assert "renamed" in [c["name"] for c in http.get("/circuits").json()]
