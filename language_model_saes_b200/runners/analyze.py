@@ -18,7 +18,7 @@ from ..analysis.direct_logit_attributor import DirectLogitAttributor, DirectLogi
 from ..analysis.feature_analyzer import FeatureAnalyzer, FeatureAnalyzerConfig
 from ..backend.hooked_transformer import HookedTransformer
 from ..backend.language_model import LanguageModelConfig
-from ..config import DatasetConfig
+from ..config import DatasetConfig, TorchDType
 from ..database import MongoClient, MongoDBConfig
 from ..models.crosscoder import Crosscoder
 from ..models.sparse_dictionary import SparseDictionary
@@ -73,7 +73,7 @@ class AnalyzeSAESettings(BaseSettings):
     model_name: Optional[str] = None
     datasets: Optional[dict[str, Optional[DatasetConfig]]] = None
     analyzer: FeatureAnalyzerConfig
-    amp_dtype: torch.dtype = torch.bfloat16
+    amp_dtype: TorchDType = torch.bfloat16
     feature_analysis_name: str = "default"
     mongo: MongoDBConfig | None = None
     output_dir: Optional[Path] = None
@@ -127,7 +127,7 @@ class AnalyzeCrosscoderSettings(BaseSettings):
     sae_series: str
     activation_factories: list[ActivationFactoryConfig]
     analyzer: FeatureAnalyzerConfig
-    amp_dtype: torch.dtype = torch.bfloat16
+    amp_dtype: TorchDType = torch.bfloat16
     feature_analysis_name: str = "default"
     mongo: MongoDBConfig | None = None
     output_dir: Optional[Path] = None

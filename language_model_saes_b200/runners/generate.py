@@ -16,7 +16,7 @@ from ..activation.processors.cached_activation import CachedActivationLoader
 from ..activation.writer import ActivationWriter, ActivationWriterConfig
 from ..backend.language_model import LanguageModelConfig
 from ..activation.processors.activation import BufferShuffleConfig
-from ..config import DatasetConfig
+from ..config import DatasetConfig, OptionalTorchDType
 from ..database import MongoClient, MongoDBConfig
 from ..resource_loaders import load_dataset, load_model
 from ..utils.logging import get_distributed_logger, setup_logging
@@ -48,7 +48,7 @@ class GenerateActivationsSettings(BaseSettings):
     mongo: Optional[MongoDBConfig] = None
     ignore_token_ids: Optional[list[int]] = None
     device_type: str = "cuda"
-    override_dtype: torch.dtype | None = None
+    override_dtype: OptionalTorchDType = None
 
 
 def generate_activations(settings: GenerateActivationsSettings) -> None:

@@ -91,3 +91,71 @@ def test_public_names_and_alias_packages():
     assert L.TransformerLensLanguageModel is L.HookedLanguageModel
     for method in ("apply_saes", "detach_at", "attribute", "qk_trace", "run_with_cache_until", "run_with_ref_cache", "trace", "to_activations"):
         assert callable(getattr(L.HookedLanguageModel, method))
+
+
+def test_job_commands_run_from_settings_files(tiny_lm_workspace, tmp_path):
+    """``generate`` -> ``train`` -> ``analyze`` -> ``evaluate`` -> ``dla``, each from a settings file written by hand (strings
+    for dtypes and enums, as a user writes them), in the three text formats."""
+    import pickle
+
+    import yaml
+
+    hook = "blocks.1.hook_resid_post"
+    lm = {"model_name": "gpt2", "model_from_pretrained_path": str(tiny_lm_workspace / "model"), "local_files_only": True, "backend": "hooked",
+          "device": "cpu", "dtype": "float32", "max_length": 32, "bos_token_id": 0, "eos_token_id": 0, "pad_token_id": 1}  # fmt: skip
+    acts, out, ana = tmp_path / "acts", tmp_path / "sae", tmp_path / "analysis"
+    (tmp_path / "gen.yaml").write_text(yaml.safe_dump({
+        "model": lm, "model_name": "tiny", "dataset": {"dataset_name_or_path": str(tiny_lm_workspace / "data"), "is_dataset_on_disk": True},
+        "dataset_name": "toy", "hook_points": [hook], "output_dir": str(acts), "total_tokens": 1024, "context_size": 16,
+        "model_batch_size": 4, "batch_size": 4, "device_type": "cpu", "format": "safetensors"}))  # fmt: skip
+    r = runner.invoke(app, ["generate", str(tmp_path / "gen.yaml")])
+    assert r.exit_code == 0, (r.output, r.exception)
+    assert len(list((acts / hook).glob("*.safetensors"))) >= 4
+
+    def factory(target, batch):
+        return {"sources": [{"type": "activations", "name": "toy", "path": str(acts), "device": "cpu", "num_workers": 0, "prefetch": None}],
+                "target": target, "hook_points": [hook], "batch_size": batch, "num_workers": 0}  # fmt: skip
+
+    (tmp_path / "train.json").write_text(json.dumps({
+        "sae": {"hook_point_in": hook, "hook_point_out": hook, "d_model": 16, "expansion_factor": 4, "act_fn": "topk", "top_k": 4,
+                "device": "cpu", "dtype": "float32"},
+        "sae_name": "toy-sae", "sae_series": "test", "initializer": {},
+        "trainer": {"lr": 1e-3, "total_training_tokens": 512, "log_frequency": 4, "eval_frequency": 1000000, "n_checkpoints": 0,
+                    "lr_warm_up_steps": 2, "exp_result_path": str(out), "amp_dtype": "float32", "l1_coefficient": None},
+        "activation_factory": factory("activations-1d", 32), "device_type": "cpu"}))  # fmt: skip
+    r = runner.invoke(app, ["train", str(tmp_path / "train.json"), "--kind", "sae"])
+    assert r.exit_code == 0, (r.output, r.exception)
+    assert (out / "sae_weights.safetensors").exists() and json.loads((out / "config.json").read_text())["expansion_factor"] == 4
+
+    pre = {"pretrained_name_or_path": str(out), "device": "cpu", "dtype": "float32"}
+    f2 = factory("activations-2d", 4)
+    toml_src = "\n".join([
+        'sae_name = "toy-sae"', 'sae_series = "test"', f'output_dir = "{ana}"', 'device_type = "cpu"', 'amp_dtype = "float32"',
+        "[sae]", *(f'{k} = "{v}"' for k, v in pre.items()),
+        "[analyzer]", "total_analyzing_tokens = 256", "ignore_token_ids = [1]",
+        "[activation_factory]", f'target = "{f2["target"]}"', f'hook_points = ["{hook}"]', "batch_size = 4", "num_workers = 0",
+        "[[activation_factory.sources]]", 'type = "activations"', 'name = "toy"', f'path = "{acts}"', 'device = "cpu"', "num_workers = 0",
+    ])  # fmt: skip
+    (tmp_path / "analyze.toml").write_text(toml_src)
+    r = runner.invoke(app, ["analyze", str(tmp_path / "analyze.toml")])
+    assert r.exit_code == 0, (r.output, r.exception)
+    pkl = ana / "toy-sae" / "test" / "default_analysis_64_features.pkl"
+    with open(pkl, "rb") as f:
+        records = pickle.load(f)
+    assert len(records) == 64 and sum(rec["act_times"] for rec in records) > 0
+
+    (tmp_path / "eval.py").write_text("config = " + repr({
+        "sae": pre, "sae_name": "toy-sae", "sae_series": "test", "activation_factory": factory("activations-1d", 32),
+        "eval": {"total_eval_tokens": 128}, "device_type": "cpu"}) + "\n")  # fmt: skip
+    r = runner.invoke(app, ["evaluate", str(tmp_path / "eval.py")])
+    assert r.exit_code == 0, (r.output, r.exception)
+
+    (tmp_path / "dla.json").write_text(json.dumps({
+        "sae": pre, "sae_name": "toy-sae", "sae_series": "test", "model": lm, "model_name": "tiny",
+        "direct_logit_attributor": {"top_k": 2}, "analysis_file": str(pkl), "device_type": "cpu"}))  # fmt: skip
+    r = runner.invoke(app, ["dla", str(tmp_path / "dla.json")])
+    assert r.exit_code == 0, (r.output, r.exception)
+    with open(pkl, "rb") as f:
+        assert len(pickle.load(f)[0]["logits"]["top_positive"]) == 2
+    r = runner.invoke(app, ["train", str(tmp_path / "train.json"), "--kind", "nothing"])
+    assert r.exit_code != 0

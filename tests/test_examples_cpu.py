@@ -87,3 +87,27 @@ def test_family_config_example_builds_every_family_on_the_meta_device(capsys, mo
     out = capsys.readouterr().out
     for name in ("Crosscoder", "CrossLayerTranscoder", "LowRankSparseAttention", "MixtureOfLinearTransform"):
         assert name in out, out
+
+
+def test_every_example_settings_object_can_be_written_to_a_settings_file_and_read_back(recorded, monkeypatch, tmp_path):
+    """What the examples build in Python is what the command line reads from a file: dumped as JSON text (dtypes, enums and
+    paths become strings) and validated again, a settings object keeps every field."""
+    import json
+
+    for script in ("generate_activations.py", "analyze_and_serve.py", "train_topk_sae_from_cache.py", "train_batchtopk_jumprelu.py"):
+        if (EXAMPLES / script).exists():
+            _run(EXAMPLES / script, [], monkeypatch)
+    for family in ("clt", "lorsa"):
+        _run(EXAMPLES / "train_clt_and_lorsa_topk.py", ["--family", family], monkeypatch)
+    folder, root = EXAMPLES / "crosscoder_over_checkpoints", ["--root", str(tmp_path)]
+    _run(folder / "generate_activations.py", ["--steps", "step1", "--target", "1d"] + root, monkeypatch)
+    _run(folder / "train_crosscoder.py", ["--steps", "step1,step2", "--head-parallel", "2"] + root, monkeypatch)
+    _run(folder / "analyze_crosscoder.py", ["--steps", "step1,step2", "--name", "run"] + root, monkeypatch)
+    seen = 0
+    for name, calls in recorded.items():
+        for settings in calls:
+            text = json.dumps(settings.model_dump(mode="json"))
+            again = type(settings).model_validate(json.loads(text))
+            assert again.model_dump(mode="json") == settings.model_dump(mode="json"), name
+            seen += 1
+    assert seen >= 8
