@@ -1,0 +1,99 @@
+"""``train --kind crosscoder | clt | lorsa | molt`` from settings files, activations computed on the fly by the tiny language
+model: each family's runner builds its dictionary (with the data-dependent initialisation), trains a few steps on the CPU,
+saves weights and settings, and the saved dictionary loads again and reconstructs (runners/train.py of the reference
+project: train_crosscoder, train_clt, train_lorsa, train_molt)."""
+
+import json
+
+import pytest
+import torch
+from typer.testing import CliRunner
+
+from language_model_saes_b200.cli import app
+from language_model_saes_b200.models.sparse_dictionary import SparseDictionary
+
+runner = CliRunner()
+UNTIED = {"init_encoder_with_decoder_transpose": False}  # only dictionaries with one encoder per decoder can start tied
+
+
+def _settings(workspace, out, sae, hook_points, target, batch_size, *, name, trainer=None, initializer=None):
+    lm = {"model_name": "gpt2", "model_from_pretrained_path": str(workspace / "model"), "local_files_only": True, "backend": "hooked",
+          "device": "cpu", "dtype": "float32", "max_length": 32, "bos_token_id": 0, "eos_token_id": 0, "pad_token_id": 1}  # fmt: skip
+    factory = {"sources": [{"type": "dataset", "name": "toy", "prepend_bos": True}], "target": target, "hook_points": hook_points,
+               "batch_size": batch_size, "context_size": 16, "model_batch_size": 4, "num_workers": 0}  # fmt: skip
+    return {
+        "sae": {**sae, "device": "cpu", "dtype": "float32"}, "sae_name": name, "sae_series": "fam",
+        "initializer": initializer if initializer is not None else {},
+        "trainer": {"lr": 1e-3, "total_training_tokens": 384, "log_frequency": 2, "eval_frequency": 1000000, "n_checkpoints": 0, "lr_warm_up_steps": 2,
+                    "exp_result_path": str(out), "amp_dtype": "float32", "l1_coefficient": None, **(trainer or {})},
+        "model": lm, "model_name": "tiny", "datasets": {"toy": {"dataset_name_or_path": str(workspace / "data"), "is_dataset_on_disk": True}},
+        "device_type": "cpu",
+    }, factory  # fmt: skip
+
+
+def _train(kind, settings, tmp_path):
+    path = tmp_path / f"{kind}.json"
+    path.write_text(json.dumps(settings))
+    r = runner.invoke(app, ["train", str(path), "--kind", kind])
+    assert r.exit_code == 0, (r.output, r.exception)
+
+
+def _reload(out):
+    assert (out / "config.json").exists() and (out / "sae_weights.safetensors").exists()
+    m = SparseDictionary.from_pretrained(str(out), device="cpu", dtype=torch.float32)
+    assert all(torch.isfinite(p).all() for p in m.parameters())
+    return m
+
+
+def test_cross_layer_transcoder(tiny_lm_workspace, tmp_path):
+    out = tmp_path / "clt"
+    ins, outs = [f"blocks.{l}.ln2.hook_normalized" for l in range(2)], [f"blocks.{l}.hook_mlp_out" for l in range(2)]
+    s, f = _settings(tiny_lm_workspace, out, {"sae_type": "clt", "hook_points_in": ins, "hook_points_out": outs, "d_model": 16, "expansion_factor": 2,
+                                              "act_fn": "topk", "top_k": 4}, ins + outs, "activations-1d", 64, name="toy-clt", initializer=UNTIED)  # fmt: skip
+    _train("clt", {**s, "activation_factory": f}, tmp_path)
+    m = _reload(out)
+    assert type(m).__name__ == "CrossLayerTranscoder" and m.cfg.n_layers == 2
+    x = torch.randn(5, 2, 16)  # [tokens, layers, d]; the reconstruction comes back layer-major
+    assert m.forward(x).shape == (2, 5, 16)
+
+
+def test_low_rank_sparse_attention(tiny_lm_workspace, tmp_path):
+    out = tmp_path / "lorsa"
+    hin, hout = "blocks.1.ln1.hook_normalized", "blocks.1.hook_attn_out"
+    s, f = _settings(tiny_lm_workspace, out, {"sae_type": "lorsa", "hook_point_in": hin, "hook_point_out": hout, "d_model": 16, "expansion_factor": 2,
+                                              "n_qk_heads": 4, "d_qk_head": 8, "rotary_dim": 8, "n_ctx": 16, "act_fn": "topk", "top_k": 4,
+                                              "positional_embedding_type": "rotary"},
+                     [hin, hout], "activations-2d", 4, name="toy-lorsa", trainer={"total_training_tokens": 16 * 4 * 4}, initializer=UNTIED)  # fmt: skip
+    _train("lorsa", {**s, "activation_factory": f}, tmp_path)
+    m = _reload(out)
+    assert type(m).__name__ == "LowRankSparseAttention"
+    assert m.forward(torch.randn(2, 16, 16)).shape == (2, 16, 16)
+
+
+def test_mixture_of_linear_transforms(tiny_lm_workspace, tmp_path):
+    out = tmp_path / "molt"
+    hin, hout = "blocks.1.ln2.hook_normalized", "blocks.1.hook_mlp_out"
+    s, f = _settings(tiny_lm_workspace, out, {"sae_type": "molt", "hook_point_in": hin, "hook_point_out": hout, "d_model": 16, "expansion_factor": 2,
+                                              "rank_counts": {"2": 16, "4": 16}, "act_fn": "relu"},
+                     [hin, hout], "activations-1d", 64, name="toy-molt", trainer={"l1_coefficient": 1e-3}, initializer=UNTIED)  # fmt: skip
+    _train("molt", {**s, "activation_factory": f}, tmp_path)
+    m = _reload(out)
+    assert type(m).__name__ == "MixtureOfLinearTransform"
+    assert m.forward(torch.randn(5, 16)).shape == (5, 16)
+
+
+def test_crosscoder_over_two_layers_of_one_model(tiny_lm_workspace, tmp_path):
+    out = tmp_path / "cc"
+    hooks = ["blocks.0.hook_resid_post", "blocks.1.hook_resid_post"]
+    s, f = _settings(tiny_lm_workspace, out, {"sae_type": "crosscoder", "hook_points": hooks, "d_model": 16, "expansion_factor": 2, "act_fn": "topk",
+                                              "top_k": 4}, hooks, "activations-1d", 64, name="toy-cc")  # fmt: skip
+    _train("crosscoder", {**s, "activation_factories": [f]}, tmp_path)
+    m = _reload(out)
+    assert type(m).__name__ == "Crosscoder" and m.cfg.n_heads == 2
+    assert m.forward(torch.randn(5, 2, 16)).shape == (5, 2, 16)
+    # the head count has to match the hook points the factories deliver
+    bad = {**s, "activation_factories": [{**f, "hook_points": hooks[:1]}]}
+    path = tmp_path / "bad.json"
+    path.write_text(json.dumps(bad))
+    r = runner.invoke(app, ["train", str(path), "--kind", "crosscoder"])
+    assert r.exit_code != 0 and isinstance(r.exception, AssertionError)
