@@ -97,3 +97,47 @@ def test_crosscoder_over_two_layers_of_one_model(tiny_lm_workspace, tmp_path):
     path.write_text(json.dumps(bad))
     r = runner.invoke(app, ["train", str(path), "--kind", "crosscoder"])
     assert r.exit_code != 0 and isinstance(r.exception, AssertionError)
+
+
+def test_crosscoder_is_analysed_and_evaluated_from_cached_activations(tiny_lm_workspace, tmp_path):
+    """``generate`` (sequence-shaped cache of both hook points) -> ``train --kind crosscoder`` from the cache -> ``analyze --kind
+    crosscoder`` into a file -> ``evaluate --kind crosscoder``."""
+    import pickle
+
+    hooks = ["blocks.0.hook_resid_post", "blocks.1.hook_resid_post"]
+    acts, out, ana = tmp_path / "acts", tmp_path / "cc", tmp_path / "analysis"
+    s, _ = _settings(tiny_lm_workspace, out, {"sae_type": "crosscoder", "hook_points": hooks, "d_model": 16, "expansion_factor": 2, "act_fn": "topk",
+                                              "top_k": 4}, hooks, "activations-1d", 64, name="toy-cc")  # fmt: skip
+    gen = {"model": s["model"], "model_name": "tiny", "dataset": s["datasets"]["toy"], "dataset_name": "toy", "hook_points": hooks,
+           "output_dir": str(acts), "total_tokens": 1024, "context_size": 16, "model_batch_size": 4, "batch_size": 4, "device_type": "cpu",
+           "format": "safetensors"}  # fmt: skip
+    (tmp_path / "gen.json").write_text(json.dumps(gen))
+    r = runner.invoke(app, ["generate", str(tmp_path / "gen.json")])
+    assert r.exit_code == 0, (r.output, r.exception)
+
+    def cached(target, batch):
+        return {"sources": [{"type": "activations", "name": "toy", "path": str(acts), "device": "cpu", "num_workers": 0, "prefetch": None}],
+                "target": target, "hook_points": hooks, "batch_size": batch, "num_workers": 0}  # fmt: skip
+
+    train = {k: v for k, v in s.items() if k not in ("model", "datasets")} | {"activation_factories": [cached("activations-1d", 64)]}
+    _train("crosscoder", train, tmp_path)
+    assert _reload(out).cfg.n_heads == 2
+
+    pre = {"pretrained_name_or_path": str(out), "device": "cpu", "dtype": "float32"}
+    (tmp_path / "ana.json").write_text(json.dumps({
+        "sae": pre, "sae_name": "toy-cc", "sae_series": "fam", "activation_factories": [cached("activations-2d", 4)],
+        "analyzer": {"total_analyzing_tokens": 256}, "output_dir": str(ana), "device_type": "cpu", "amp_dtype": "bfloat16"}))  # fmt: skip
+    r = runner.invoke(app, ["analyze", str(tmp_path / "ana.json"), "--kind", "crosscoder"])
+    assert r.exit_code == 0, (r.output, r.exception)
+    (pkl,) = list((ana / "toy-cc" / "fam").glob("*.pkl"))
+    with open(pkl, "rb") as f:
+        records = pickle.load(f)
+    assert len(records) == 32 and sum(rec["act_times"] for rec in records) > 0
+    fired = next(rec for rec in records if rec["act_times"] > 0)
+    assert len(fired["decoder_norms"]) == 2 and len(fired["decoder_similarity_matrices"]) == 2  # one entry per head
+
+    (tmp_path / "eval.json").write_text(json.dumps({
+        "sae": pre, "sae_name": "toy-cc", "sae_series": "fam", "activation_factories": [cached("activations-1d", 64)],
+        "eval": {"total_eval_tokens": 128}, "device_type": "cpu"}))  # fmt: skip
+    r = runner.invoke(app, ["evaluate", str(tmp_path / "eval.json"), "--kind", "crosscoder"])
+    assert r.exit_code == 0, (r.output, r.exception)
