@@ -38,6 +38,25 @@ def _train(kind, settings, tmp_path):
     assert r.exit_code == 0, (r.output, r.exception)
 
 
+def _analyze(workspace, out, factory, name, tmp_path, **analyzer):
+    """``analyze`` of a saved dictionary of any family into a file; returns the feature records."""
+    import pickle
+
+    s, _ = _settings(workspace, out, {}, [], "", 0, name=name)
+    ana = tmp_path / "analysis"
+    cfg = {"sae": {"pretrained_name_or_path": str(out), "device": "cpu", "dtype": "float32"}, "sae_name": name, "sae_series": "fam",
+           "activation_factory": {**factory, "target": "activations-2d", "batch_size": 4}, "model": s["model"], "model_name": "tiny",
+           "datasets": s["datasets"], "analyzer": {"total_analyzing_tokens": 256, **analyzer}, "output_dir": str(ana), "device_type": "cpu",
+           "amp_dtype": "bfloat16"}  # fmt: skip
+    path = tmp_path / "analyze.json"
+    path.write_text(json.dumps(cfg))
+    r = runner.invoke(app, ["analyze", str(path)])
+    assert r.exit_code == 0, (r.output, r.exception)
+    (pkl,) = list((ana / name / "fam").glob("*.pkl"))
+    with open(pkl, "rb") as f:
+        return pickle.load(f)
+
+
 def _reload(out):
     assert (out / "config.json").exists() and (out / "sae_weights.safetensors").exists()
     m = SparseDictionary.from_pretrained(str(out), device="cpu", dtype=torch.float32)
@@ -55,6 +74,9 @@ def test_cross_layer_transcoder(tiny_lm_workspace, tmp_path):
     assert type(m).__name__ == "CrossLayerTranscoder" and m.cfg.n_layers == 2
     x = torch.randn(5, 2, 16)  # [tokens, layers, d]; the reconstruction comes back layer-major
     assert m.forward(x).shape == (2, 5, 16)
+    records = _analyze(tiny_lm_workspace, out, f, "toy-clt", tmp_path, clt_layer=0)  # one layer's features per analysis
+    assert len(records) == 32 and sum(r["act_times"] for r in records) > 0
+    assert len(next(r for r in records if r["act_times"] > 0)["decoder_norms"]) == 2  # layer 0 writes to both layers
 
 
 def test_low_rank_sparse_attention(tiny_lm_workspace, tmp_path):
@@ -68,6 +90,10 @@ def test_low_rank_sparse_attention(tiny_lm_workspace, tmp_path):
     m = _reload(out)
     assert type(m).__name__ == "LowRankSparseAttention"
     assert m.forward(torch.randn(2, 16, 16)).shape == (2, 16, 16)
+    records = _analyze(tiny_lm_workspace, out, f, "toy-lorsa", tmp_path)
+    assert len(records) == 32 and sum(r["act_times"] for r in records) > 0
+    top = next(r for r in records if r["act_times"] > 0)["samplings"][0]
+    assert "z_pattern_indices" in top and "z_pattern_values" in top  # which source positions a head read from
 
 
 def test_mixture_of_linear_transforms(tiny_lm_workspace, tmp_path):
