@@ -159,3 +159,48 @@ def test_job_commands_run_from_settings_files(tiny_lm_workspace, tmp_path):
         assert len(pickle.load(f)[0]["logits"]["top_positive"]) == 2
     r = runner.invoke(app, ["train", str(tmp_path / "train.json"), "--kind", "nothing"])
     assert r.exit_code != 0
+
+
+def test_a_run_that_outlives_its_stream_leaves_a_checkpoint_that_a_second_run_resumes(tiny_lm_workspace, tmp_path):
+    """The cache holds fewer tokens than the run wants: ``train`` ends with a trainer checkpoint (weights, optimizer, schedule,
+    counters) instead of final weights; a second ``train`` that names it (``sae.pretrained_name_or_path`` and
+    ``trainer.from_pretrained_path``) picks up at that step, finishes and writes the final weights."""
+    import torch
+
+    hook = "blocks.1.hook_resid_post"
+    lm = {"model_name": "gpt2", "model_from_pretrained_path": str(tiny_lm_workspace / "model"), "local_files_only": True, "backend": "hooked",
+          "device": "cpu", "dtype": "float32", "max_length": 32, "bos_token_id": 0, "eos_token_id": 0, "pad_token_id": 1}  # fmt: skip
+    acts, out = tmp_path / "acts", tmp_path / "sae"
+    (tmp_path / "gen.json").write_text(json.dumps({
+        "model": lm, "model_name": "tiny", "dataset": {"dataset_name_or_path": str(tiny_lm_workspace / "data"), "is_dataset_on_disk": True},
+        "dataset_name": "toy", "hook_points": [hook], "output_dir": str(acts), "total_tokens": 512, "context_size": 16,
+        "model_batch_size": 4, "batch_size": 4, "device_type": "cpu", "format": "safetensors"}))  # fmt: skip
+    assert runner.invoke(app, ["generate", str(tmp_path / "gen.json")]).exit_code == 0
+    settings = {
+        "sae": {"hook_point_in": hook, "hook_point_out": hook, "d_model": 16, "expansion_factor": 4, "act_fn": "topk", "top_k": 4,
+                "device": "cpu", "dtype": "float32"},
+        "sae_name": "toy-sae", "sae_series": "test", "initializer": {},
+        "trainer": {"lr": 1e-3, "total_training_tokens": 32 * 20, "log_frequency": 4, "eval_frequency": 1000000, "n_checkpoints": 0,
+                    "lr_warm_up_steps": 2, "exp_result_path": str(out), "amp_dtype": "float32", "l1_coefficient": None},
+        "activation_factory": {"sources": [{"type": "activations", "name": "toy", "path": str(acts), "device": "cpu", "num_workers": 0, "prefetch": None}],
+                               "target": "activations-1d", "hook_points": [hook], "batch_size": 32, "num_workers": 0},
+        "device_type": "cpu"}  # fmt: skip
+    (tmp_path / "first.json").write_text(json.dumps(settings))
+    r = runner.invoke(app, ["train", str(tmp_path / "first.json")])
+    assert r.exit_code == 0, (r.output, r.exception)
+    assert not (out / "sae_weights.safetensors").exists()
+    (ckpt,) = list((out / "checkpoints").glob("step_*"))
+    stopped_at = int(ckpt.name.split("_")[1])
+    assert 0 < stopped_at < 20
+    for name in ("sae_weights.safetensors", "config.json", "trainer.pt", "optimizer.pt", "scheduler.pt"):
+        assert (ckpt / name).exists(), name
+    state = torch.load(ckpt / "trainer.pt", weights_only=False)
+    assert state["cur_step"] == stopped_at and state["total_training_steps"] == 20
+
+    second = {**settings, "sae": {"pretrained_name_or_path": str(ckpt), "device": "cpu", "dtype": "float32"}, "initializer": None,
+              "trainer": {**settings["trainer"], "from_pretrained_path": str(ckpt), "exp_result_path": str(tmp_path / "resumed")}}  # fmt: skip
+    (tmp_path / "second.json").write_text(json.dumps(second))
+    r = runner.invoke(app, ["train", str(tmp_path / "second.json")])
+    assert r.exit_code == 0, (r.output, r.exception)
+    done = tmp_path / "resumed"  # the final weights go where the second run's settings say
+    assert (done / "sae_weights.safetensors").exists() and (done / "config.json").exists()
