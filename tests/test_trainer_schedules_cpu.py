@@ -119,3 +119,20 @@ def test_sparse_adam_moves_only_what_received_a_gradient(tmp_path):
     moved = (sae.W_D.detach() - before["W_D"]).abs().sum(-1) > 0
     assert 0 < int(moved.sum()) <= 32  # decoder rows of features that did not fire keep their values
     assert all(torch.isfinite(p).all() for p in sae.parameters())
+
+
+@pytest.mark.parametrize("mode,want", [("linear", [5, 10, 15]), ("log", [3, 5, 10])])
+def test_model_snapshots_are_taken_at_linear_or_log_spaced_steps(tmp_path, mode, want):
+    from safetensors.torch import load_file
+
+    sae = _sae("relu")
+    t = Trainer(_cfg(tmp_path, n_checkpoints=4, check_point_save_mode=mode, skip_metrics_calculation=True))
+    t.fit(sae, _stream(22))
+    files = sorted(int(p.stem) for p in (tmp_path / "checkpoints").glob("*.safetensors"))
+    assert files == want and t.checkpoint_thresholds == []
+    last = load_file(tmp_path / "checkpoints" / f"{want[-1]}.safetensors")
+    assert set(last) >= {"W_E", "W_D", "b_E", "b_D"} and not torch.equal(last["W_D"], sae.W_D.detach())  # training went on after it
+    # fewer steps than snapshots: every step at most once
+    short = Trainer(_cfg(tmp_path / "short", n_checkpoints=8, check_point_save_mode=mode, total_training_tokens=32 * 3))
+    short._initialize_trainer(sae, next(_stream(1)))
+    assert short.checkpoint_thresholds == sorted(set(short.checkpoint_thresholds)) and all(0 < s <= 3 for s in short.checkpoint_thresholds)
