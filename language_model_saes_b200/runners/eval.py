@@ -8,13 +8,15 @@ from pydantic_settings import BaseSettings
 
 from ..activation.factory import ActivationFactory, ActivationFactoryConfig
 from ..backend.language_model import LanguageModelConfig
+from ..config import DatasetConfig
+from ..database import MongoClient, MongoDBConfig
 from ..evaluator import EvalConfig, Evaluator
 from ..models.sparse_dictionary import SparseDictionary
 from ..parallel.mesh import mesh_local_rank
-from ..resource_loaders import load_model
+from ..resource_loaders import load_dataset, load_model
 from ..trainer import WandbConfig
 from ..utils.logging import get_distributed_logger, setup_logging
-from .utils import PretrainedSAE, init_wandb, make_mesh
+from .utils import PretrainedSAE, init_wandb, load_config, make_mesh
 
 logger = get_distributed_logger("runners.eval")
 
@@ -26,6 +28,12 @@ class EvaluateSAESettings(BaseSettings):
     activation_factory: ActivationFactoryConfig
     model: Optional[LanguageModelConfig] = None
     """With a model the downstream language-model loss is measured too."""
+    model_name: Optional[str] = None
+    datasets: Optional[dict[str, Optional[DatasetConfig]]] = None
+    """Datasets of the activation factory's dataset sources (a value of None is looked up in the database by its name), so
+    that a dictionary can be evaluated on activations computed on the fly; the reference's settings have the model only and
+    so evaluate from cached activations."""
+    mongo: Optional[MongoDBConfig] = None
     eval: EvalConfig
     model_parallel_size: int = 1
     fold_activation_scale: bool = False
@@ -42,9 +50,15 @@ def evaluate_sae(settings: EvaluateSAESettings) -> dict[str, float]:
         device=settings.sae.device, dtype=settings.sae.dtype, strict_loading=settings.sae.strict_loading,
     )  # fmt: skip
     logger.info(f"SAE model loaded: {type(sae).__name__}")
-    model = load_model(settings.model) if settings.model is not None else None
+    mongo = MongoClient(settings.mongo) if settings.mongo is not None else None
+    model_cfg = load_config(settings.model, settings.model_name, mongo, "model", required=False)
+    model = load_model(model_cfg) if model_cfg is not None else None
+    datasets = None
+    if settings.datasets is not None:
+        datasets = {n: load_dataset(load_config(c, n, mongo, "dataset"), device_mesh=mesh) for n, c in settings.datasets.items()}
     wandb_logger = init_wandb(settings.wandb, settings, mesh)
-    results = Evaluator(settings.eval).evaluate(sae, factory.process(model=model), wandb_logger, model=model)
+    stream = factory.process(model=model, model_name=settings.model_name, datasets=datasets)
+    results = Evaluator(settings.eval).evaluate(sae, stream, wandb_logger, model=model)
     logger.info("Evaluation completed")
     return results
 

@@ -57,6 +57,18 @@ def _analyze(workspace, out, factory, name, tmp_path, **analyzer):
         return pickle.load(f)
 
 
+def _evaluate(workspace, out, factory, name, tmp_path, tokens):
+    """``evaluate`` of a saved dictionary on activations computed on the fly."""
+    s, _ = _settings(workspace, out, {}, [], "", 0, name=name)
+    cfg = {"sae": {"pretrained_name_or_path": str(out), "device": "cpu", "dtype": "float32"}, "sae_name": name, "sae_series": "fam",
+           "activation_factory": factory, "model": s["model"], "model_name": "tiny", "datasets": s["datasets"],
+           "eval": {"total_eval_tokens": tokens}, "device_type": "cpu"}  # fmt: skip
+    path = tmp_path / "evaluate.json"
+    path.write_text(json.dumps(cfg))
+    r = runner.invoke(app, ["evaluate", str(path)])
+    assert r.exit_code == 0, (r.output, r.exception)
+
+
 def _reload(out):
     assert (out / "config.json").exists() and (out / "sae_weights.safetensors").exists()
     m = SparseDictionary.from_pretrained(str(out), device="cpu", dtype=torch.float32)
@@ -74,6 +86,7 @@ def test_cross_layer_transcoder(tiny_lm_workspace, tmp_path):
     assert type(m).__name__ == "CrossLayerTranscoder" and m.cfg.n_layers == 2
     x = torch.randn(5, 2, 16)  # [tokens, layers, d]; the reconstruction comes back layer-major
     assert m.forward(x).shape == (2, 5, 16)
+    _evaluate(tiny_lm_workspace, out, f, "toy-clt", tmp_path, 128)
     records = _analyze(tiny_lm_workspace, out, f, "toy-clt", tmp_path, clt_layer=0)  # one layer's features per analysis
     assert len(records) == 32 and sum(r["act_times"] for r in records) > 0
     assert len(next(r for r in records if r["act_times"] > 0)["decoder_norms"]) == 2  # layer 0 writes to both layers
@@ -90,6 +103,7 @@ def test_low_rank_sparse_attention(tiny_lm_workspace, tmp_path):
     m = _reload(out)
     assert type(m).__name__ == "LowRankSparseAttention"
     assert m.forward(torch.randn(2, 16, 16)).shape == (2, 16, 16)
+    _evaluate(tiny_lm_workspace, out, f, "toy-lorsa", tmp_path, 128)
     records = _analyze(tiny_lm_workspace, out, f, "toy-lorsa", tmp_path)
     assert len(records) == 32 and sum(r["act_times"] for r in records) > 0
     top = next(r for r in records if r["act_times"] > 0)["samplings"][0]
@@ -106,6 +120,7 @@ def test_mixture_of_linear_transforms(tiny_lm_workspace, tmp_path):
     m = _reload(out)
     assert type(m).__name__ == "MixtureOfLinearTransform"
     assert m.forward(torch.randn(5, 16)).shape == (5, 16)
+    _evaluate(tiny_lm_workspace, out, f, "toy-molt", tmp_path, 128)
 
 
 def test_crosscoder_over_two_layers_of_one_model(tiny_lm_workspace, tmp_path):
